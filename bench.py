@@ -1,0 +1,203 @@
+#!/usr/bin/env python
+"""Headline benchmark: single-request greedy decode tokens/s on the Qwen3-30B-A3B shape
+(48 layers, hidden 2048, 32 q / 4 kv heads of 128, 128 experts top-8, moe_inter 768,
+vocab 151936) with Q4_K_M weights, after a 512-token random prompt.
+
+    python bench.py --gpus N --steps K --warmup W          # own arm
+    python bench.py --impl reference ...                   # reference arm
+
+A step is one decode step (one token).  The device-timed value replays the decode graph
+K times back to back (the next step's input stays on the card) between two CUDA events;
+the end-to-end value drives the public ``DecodeEngine.step`` call once per token, which
+copies that step's token/position/slot words from pinned host memory and reads the pick
+(and the fault word) back every step.  Weights (about 17 GB) are far larger than L2, so
+every step streams them from HBM; no explicit L2 flush is needed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+BASELINE_TOKS = 164.1   # Qwen3-30B-A3B Q4_K_M decode, reference on 1x RTX 3090 (docs/numbers.md:70)
+METRIC = "decode tok/s (whole box, max over ranks)"
+
+
+def reference_arm(args) -> int:
+    why = ("reference is a Rust/cuda-oxide workspace (no setup.py/pyproject; pip: 'not installable'); "
+           "no cargo/rustc on this image and it has no sm_100 target")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons through nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.stop_flag = threading.Event()
+
+    def run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 7:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.1)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(s[0]) for s in self.samples)
+        reasons = set()
+        for s in self.samples:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(float(s[2]) for s in self.samples)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="own")
+    ap.add_argument("--model", default="qwen3-30b-a3b")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--ttft", type=int, default=0, help="also time a prompt of this many tokens (0 = skip)")
+    ap.add_argument("--no-pdl", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        print(json.dumps({"error": f"--gpus {args.gpus} but WORLD_SIZE={world}"}))
+        return 1
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        from bloomery_b200.parallel.bench_dist import run_distributed
+        return run_distributed(args, rank, local, world)
+
+    from bloomery_b200.models.spec import NAMED
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.ops import decode as K
+    from bloomery_b200.runtime.engine import DecodeEngine
+
+    if args.no_pdl:
+        K.set_pdl(False)
+    spec = NAMED[args.model]()
+    steps, warm = args.steps, max(3, args.warmup)
+    t0 = time.time()
+    w = Weights.from_items(spec, synth_tensors(spec, dev, seed=0, mix="Q4_K_M"), dev)
+    torch.cuda.synchronize()
+    t_load = time.time() - t0
+    ctx = max(args.prompt, args.ttft) + warm + 2 * steps + 64
+    eng = DecodeEngine(w, n_slots=1, slot_ctx=(ctx + 63) // 64 * 64)
+    g = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, spec.vocab, (args.prompt,), generator=g).tolist()
+
+    # prompt (timed as TTFT of this prompt length: prefill passes + first pick)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    first = eng.prefill(0, prompt)
+    torch.cuda.synchronize()
+    ttft_prompt_ms = (time.time() - t0) * 1e3
+
+    # ---- device-timed decode: W warm-up steps, then exactly K steps between two events
+    pos = len(prompt)
+    toks = eng.decode_chain(0, first, pos, warm)
+    pos += warm
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    eng.kv.ensure(0, pos + steps + 1)
+    eng.set_rows([(0, toks[-1], pos)])
+    eng.counters[2:3].zero_()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record()
+    for _ in range(steps):
+        eng.launch(1, True, True)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    sampler.stop_flag.set()
+    sampler.join()
+    eng.check_fault()
+    out_tokens = eng.hist[:steps].cpu().tolist()
+    pos += steps
+    tok_s = steps / (ms / 1e3)
+
+    # ---- end to end through the public step call: H2D of the step's words, D2H of the pick
+    tok = out_tokens[-1]
+    for _ in range(3):
+        tok = eng.step([(0, tok, pos)])[0]
+        pos += 1
+    n_e2e = min(steps, 128)
+    eng.kv.ensure(0, pos + n_e2e + 1)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        tok = eng.step([(0, tok, pos)])[0]
+        pos += 1
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e = {"value": n_e2e / e2e_s, "unit": "tok/s", "steps": n_e2e,
+           "h2d_bytes_per_step": int(eng.params_host.numel() * 4), "d2h_bytes_per_step": int(eng.tokens_out_host.numel() * 4)}
+
+    extra = {}
+    if args.ttft:
+        eng.reset(0)
+        p2 = torch.randint(0, spec.vocab, (args.ttft,), generator=g).tolist()
+        ts = []
+        for _ in range(3):
+            eng.reset(0)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            eng.prefill(0, p2)
+            torch.cuda.synchronize()
+            ts.append((time.perf_counter() - t0) * 1e3)
+        extra["ttft_ms_p50"] = sorted(ts)[1]
+        extra["ttft_prompt_tokens"] = args.ttft
+
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": tok_s / BASELINE_TOKS, "dtype": "q4_k_m weights, int8 dot / fp32 accumulate, f16 KV",
+        "data": "synthetic: seeded random token ids, random-init N(0,0.02) weights quantised Q4_K_M on the card",
+        "config": {"model": spec.name, "global_batch": 1, "seq_len": args.prompt + warm + steps,
+                   "prompt_tokens": args.prompt, "parallelism": "single", "l2": "weights (17 GB) exceed L2; no flush needed",
+                   "graph": "one CUDA graph per decode step", "pdl": not args.no_pdl},
+        "clocks": sampler.summary(), "e2e": e2e,
+        "gpu_launches": eng.launches_per_step * steps, "launches_per_step": eng.launches_per_step,
+        "ttft_ms_prompt": ttft_prompt_ms, "load_s": t_load, "weights_gb": w.n_bytes / 1e9,
+        "hbm_gbs_effective": None, **extra,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

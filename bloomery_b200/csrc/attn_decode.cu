@@ -1,0 +1,334 @@
+// Decode-time attention over a paged KV cache (GQA, head size 128 or 64):
+//   1. qk_norm_rope_append  per-head RMSNorm (optional) + NEOX RoPE + KV append
+//   2. flash_decode_seg     split-K online-softmax over a fixed number of segments
+//   3. flash_decode_merge   merge segments ascending, then quantise to q8 for o_proj
+//
+// Everything data-dependent (positions, sequence of each row, block table, live key
+// count) is read from device buffers, so one captured graph serves every step; the
+// segment grid is fixed per graph (the reference fixes 80: crates/gpu/src/flash_gqa.rs:350).
+// Numeric contract followed (crates/gpu/src/rope_neox.rs:1-40, flash_gqa.rs:1-45): f32
+// squares with f64 sums, NEOX pairs (i, i + HEAD/2) with fma forms, K and V rounded once
+// to f16 (RNE); masked keys weigh exactly 0 and are never loaded; a key count of 0 or
+// beyond the context raises FS_KEY_COUNT and writes NaN.
+//
+// KV layout per layer: [n_pages][n_kv][PAGE][HEAD] f16 for K and the same for V,
+// PAGE = 64 positions.  block_table[seq][i] names the page of positions 64i..64i+63.
+#include "common.cuh"
+
+namespace bl {
+
+constexpr int kPage = 64;
+constexpr int kKeyTile = 32;
+
+struct RopeArgs {
+  const float* qkv;      // [M, (n_q + 2 n_kv) * HEAD]
+  long qkv_stride;
+  const float* q_gain;   // [HEAD] or null
+  const float* k_gain;   // [HEAD] or null
+  const float* inv_freq; // [HEAD/2]
+  float eps;
+  float q_scale;         // 1/sqrt(HEAD) folded into q
+  int n_q, n_kv;
+  int M;
+  const int* row_pos;    // [M]
+  const int* row_seq;    // [M], < 0 = padding row
+  const int* block_table;
+  int max_pages;         // per sequence
+  int n_pages;           // pool size (bounds check)
+  __half* k_cache;
+  __half* v_cache;
+  float* q_out;          // [M, n_q, HEAD]
+  unsigned* fault;
+  int layer;
+};
+
+template <int HEAD>
+__global__ void __launch_bounds__(HEAD / 2) qk_norm_rope_append_kernel(const RopeArgs a) {
+  constexpr int HALF = HEAD / 2;
+  __shared__ double red[HALF / 32];
+  const int head = blockIdx.x, m = blockIdx.y, i = threadIdx.x;
+  pdl_wait();
+  pdl_launch();
+  const int seq = a.row_seq[m];
+  if (seq < 0) return;
+  const int pos = a.row_pos[m];
+  const float* src = a.qkv + (long)m * a.qkv_stride + (long)head * HEAD;
+  float x0 = src[i], x1 = src[i + HALF];
+  const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
+  if (is_q || is_k) {
+    const float* gain = is_q ? a.q_gain : a.k_gain;
+    if (gain) {
+      double ss = warp_sum_d((double)(x0 * x0) + (double)(x1 * x1));
+      if ((i & 31) == 0) red[i >> 5] = ss;
+      __syncthreads();
+      double tot = 0.0;
+#pragma unroll
+      for (int w = 0; w < HALF / 32; ++w) tot += red[w];
+      float scale = (float)(1.0 / sqrt(tot / (double)HEAD + (double)a.eps));
+      x0 = (scale * gain[i]) * x0;
+      x1 = (scale * gain[i + HALF]) * x1;
+    }
+    float ang = (float)pos * a.inv_freq[i];
+    float s, c;
+    sincosf(ang, &s, &c);
+    float y0 = fmaf(x0, c, -(x1 * s));
+    float y1 = fmaf(x0, s, x1 * c);
+    x0 = y0; x1 = y1;
+  }
+  if (is_q) {
+    float* q = a.q_out + ((long)m * a.n_q + head) * HEAD;
+    q[i] = x0 * a.q_scale;
+    q[i + HALF] = x1 * a.q_scale;
+    return;
+  }
+  const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+  const int pslot = pos / kPage;
+  int page = (pslot < a.max_pages) ? a.block_table[(long)seq * a.max_pages + pslot] : -1;
+  if (page < 0 || page >= a.n_pages) {
+    if (i == 0) raise_fault(a.fault, a.layer, FS_PAGE);
+    return;
+  }
+  __half* dst = (is_k ? a.k_cache : a.v_cache) + (((long)page * a.n_kv + kvh) * kPage + (pos % kPage)) * HEAD;
+  dst[i] = __float2half_rn(x0);
+  dst[i + HALF] = __float2half_rn(x1);
+}
+
+struct FlashArgs {
+  const float* q;        // [M, n_q, HEAD], pre-scaled
+  const __half* k_cache;
+  const __half* v_cache;
+  const int* row_pos;
+  const int* row_seq;
+  const int* block_table;
+  int max_pages, n_pages;
+  int n_q, n_kv, M, n_seg;
+  int ctx_limit;
+  float* part_ml;        // [M, n_q, n_seg, 2]
+  float* part_acc;       // [M, n_q, n_seg, HEAD]
+  unsigned* fault;
+  int layer;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// grid (n_seg, n_kv, M); 256 threads = 8 warps; warp w serves q heads w, w+8, ... of the group
+template <int HEAD, int HPW>
+__global__ void __launch_bounds__(256) flash_decode_seg_kernel(const FlashArgs a) {
+  constexpr int KSTR = HEAD + 8;      // padded f16 row stride for K: conflict-free 16-byte reads by key lanes
+  constexpr int DPL = HEAD / 32;      // output dims per lane
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int G = a.n_q / a.n_kv;
+  float* sq = reinterpret_cast<float*>(smem);                              // [G][HEAD]
+  __half* sk = reinterpret_cast<__half*>(smem + (size_t)G * HEAD * 4);     // [2][32][KSTR]
+  __half* sv = sk + 2 * kKeyTile * KSTR;                                   // [2][32][HEAD]
+  const int seg = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  pdl_wait();
+  pdl_launch();
+  const int seq = a.row_seq[m];
+  if (seq < 0) return;
+  const int n_keys = a.row_pos[m] + 1;
+  const bool bad = n_keys <= 0 || n_keys > a.ctx_limit;
+  if (bad && tid == 0 && seg == 0 && kvh == 0) raise_fault(a.fault, a.layer, FS_KEY_COUNT);
+
+  const int n_tiles = bad ? 0 : (n_keys + kKeyTile - 1) / kKeyTile;
+  const int tps = (n_tiles + a.n_seg - 1) / a.n_seg;
+  const int t0 = seg * tps, t1 = min(n_tiles, t0 + tps);
+
+  for (int i = tid; i < G * HEAD; i += 256)
+    sq[i] = a.q[((long)m * a.n_q + (long)kvh * G) * HEAD + i];
+
+  const int* bt = a.block_table + (long)seq * a.max_pages;
+  auto issue_tile = [&](int t, int stage) {
+    const int key0 = t * kKeyTile;
+    int page = bt[key0 / kPage];
+    page = (page < 0 || page >= a.n_pages) ? 0 : page;  // fault is raised by the append kernel; stay in bounds
+    const long base = (((long)page * a.n_kv + kvh) * kPage + (key0 % kPage)) * HEAD;
+    constexpr int CH = HEAD / 8;  // 16-byte chunks per row
+    for (int c = tid; c < kKeyTile * CH; c += 256) {
+      int r = c / CH, cc = c % CH;
+      cp_async16(sk + ((size_t)stage * kKeyTile + r) * KSTR + cc * 8, a.k_cache + base + (long)r * HEAD + cc * 8);
+      cp_async16(sv + ((size_t)stage * kKeyTile + r) * HEAD + cc * 8, a.v_cache + base + (long)r * HEAD + cc * 8);
+    }
+    cp_async_commit();
+  };
+
+  float mx[HPW], l[HPW], acc[HPW][DPL];
+#pragma unroll
+  for (int h = 0; h < HPW; ++h) {
+    mx[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
+  }
+
+  if (t0 < t1) issue_tile(t0, 0);
+  for (int t = t0; t < t1; ++t) {
+    const int stage = (t - t0) & 1;
+    if (t + 1 < t1) { issue_tile(t + 1, stage ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const int key = t * kKeyTile + lane;
+    const __half* krow = sk + ((size_t)stage * kKeyTile + lane) * KSTR;
+#pragma unroll
+    for (int h = 0; h < HPW; ++h) {
+      const int hg = warp + 8 * h;
+      if (hg < G) {
+        const float* qh = sq + hg * HEAD;
+        float s = 0.f;
+#pragma unroll
+        for (int d = 0; d < HEAD; d += 8) {
+          uint4 kv = *reinterpret_cast<const uint4*>(krow + d);
+          float4 q0 = *reinterpret_cast<const float4*>(qh + d);
+          float4 q1 = *reinterpret_cast<const float4*>(qh + d + 4);
+          float2 k0 = __half22float2(*reinterpret_cast<__half2*>(&kv.x));
+          float2 k1 = __half22float2(*reinterpret_cast<__half2*>(&kv.y));
+          float2 k2 = __half22float2(*reinterpret_cast<__half2*>(&kv.z));
+          float2 k3 = __half22float2(*reinterpret_cast<__half2*>(&kv.w));
+          s = fmaf(q0.x, k0.x, s); s = fmaf(q0.y, k0.y, s); s = fmaf(q0.z, k1.x, s); s = fmaf(q0.w, k1.y, s);
+          s = fmaf(q1.x, k2.x, s); s = fmaf(q1.y, k2.y, s); s = fmaf(q1.z, k3.x, s); s = fmaf(q1.w, k3.y, s);
+        }
+        if (key >= n_keys) s = -INFINITY;
+        float tmax = warp_max(s);
+        float nm = fmaxf(mx[h], tmax);
+        float corr = (mx[h] == -INFINITY) ? 0.f : __expf(mx[h] - nm);
+        float p = (s == -INFINITY) ? 0.f : __expf(s - nm);
+        l[h] = l[h] * corr + warp_sum(p);
+        mx[h] = nm;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
+        const __half* vbase = sv + (size_t)stage * kKeyTile * HEAD + lane * DPL;
+        const int kmax = min(kKeyTile, n_keys - t * kKeyTile);  // masked keys are never read
+#pragma unroll 4
+        for (int k = 0; k < kmax; ++k) {
+          float pk = __shfl_sync(0xffffffffu, p, k);
+          const __half* vr = vbase + (size_t)k * HEAD;
+          if constexpr (DPL == 4) {
+            uint2 vv = *reinterpret_cast<const uint2*>(vr);
+            float2 v0 = __half22float2(*reinterpret_cast<__half2*>(&vv.x));
+            float2 v1 = __half22float2(*reinterpret_cast<__half2*>(&vv.y));
+            acc[h][0] = fmaf(pk, v0.x, acc[h][0]); acc[h][1] = fmaf(pk, v0.y, acc[h][1]);
+            acc[h][2] = fmaf(pk, v1.x, acc[h][2]); acc[h][3] = fmaf(pk, v1.y, acc[h][3]);
+          } else {
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(pk, __half2float(vr[d]), acc[h][d]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int h = 0; h < HPW; ++h) {
+    const int hg = warp + 8 * h;
+    if (hg < G) {
+      const int qh = kvh * G + hg;
+      const long pidx = ((long)m * a.n_q + qh) * a.n_seg + seg;
+      if (lane == 0) {
+        a.part_ml[pidx * 2] = bad ? __int_as_float(0x7fc00000) : mx[h];
+        a.part_ml[pidx * 2 + 1] = l[h];
+      }
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) a.part_acc[pidx * HEAD + lane * DPL + d] = acc[h][d];
+    }
+  }
+}
+
+struct MergeArgs {
+  const float* part_ml;
+  const float* part_acc;
+  int n_q, n_seg, M;
+  const int* row_seq;
+  float* out;        // optional fp32 [M, n_q*HEAD]
+  int8_t* outq;      // q8 codes [M, n_q*HEAD]
+  float2* outds;     // [M, n_q*HEAD/32]
+};
+
+// grid (n_q, M), HEAD threads
+template <int HEAD>
+__global__ void __launch_bounds__(HEAD) flash_decode_merge_kernel(const MergeArgs a) {
+  const int qh = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
+  pdl_wait();
+  pdl_launch();
+  if (a.row_seq[m] < 0) return;
+  const long p0 = ((long)m * a.n_q + qh) * a.n_seg;
+  float mx = -INFINITY;
+  bool nan = false;
+  for (int s = 0; s < a.n_seg; ++s) {
+    float v = a.part_ml[(p0 + s) * 2];
+    nan |= (v != v);
+    mx = fmaxf(mx, v);
+  }
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < a.n_seg; ++s) {  // ascending segment order, fixed
+    float ms = a.part_ml[(p0 + s) * 2];
+    float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
+    den = fmaf(a.part_ml[(p0 + s) * 2 + 1], w, den);
+    num = fmaf(a.part_acc[(p0 + s) * HEAD + d], w, num);
+  }
+  float o = nan ? __int_as_float(0x7fc00000) : num / den;
+  const long col = (long)qh * HEAD + d;
+  const long width = (long)a.n_q * HEAD;
+  if (a.out) a.out[(long)m * width + col] = o;
+  float ds_d, ds_s;
+  int8_t q = q8_lane(o, ds_d, ds_s);
+  a.outq[(long)m * width + col] = q;
+  if ((d & 31) == 0) a.outds[((long)m * width + col) / 32] = make_float2(ds_d, ds_s);
+}
+
+}  // namespace bl
+
+using namespace bl;
+
+extern "C" {
+
+int bl_qk_norm_rope_append(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain,
+                           const float* inv_freq, float eps, float q_scale, int head, int n_q, int n_kv, int M,
+                           const int* row_pos, const int* row_seq, const int* block_table, int max_pages, int n_pages,
+                           void* k_cache, void* v_cache, float* q_out, unsigned* fault, int layer, cudaStream_t st) {
+  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
+  BL_REQUIRE(M >= 1 && n_q >= 1 && n_kv >= 1, BL_ERR_SHAPE);
+  RopeArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, M, row_pos, row_seq, block_table,
+             max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, q_out, fault, layer};
+  dim3 grid(n_q + 2 * n_kv, M);
+  if (head == 128) return (int)launch(qk_norm_rope_append_kernel<128>, grid, dim3(64), 0, st, a);
+  return (int)launch(qk_norm_rope_append_kernel<64>, grid, dim3(32), 0, st, a);
+}
+
+// Scratch: part_ml [M*n_q*n_seg*2] and part_acc [M*n_q*n_seg*head] floats, caller-owned.
+int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, const int* row_pos, const int* row_seq,
+                    const int* block_table, int max_pages, int n_pages, int head, int n_q, int n_kv, int M, int n_seg,
+                    int ctx_limit, float* part_ml, float* part_acc, float* out, int8_t* outq, float* outds,
+                    unsigned* fault, int layer, cudaStream_t st) {
+  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
+  BL_REQUIRE(n_q % n_kv == 0 && n_q / n_kv <= 16, BL_ERR_SHAPE);
+  BL_REQUIRE(n_seg >= 1 && M >= 1, BL_ERR_SHAPE);
+  const int G = n_q / n_kv;
+  FlashArgs a{q, (const __half*)k_cache, (const __half*)v_cache, row_pos, row_seq, block_table, max_pages, n_pages,
+              n_q, n_kv, M, n_seg, ctx_limit, part_ml, part_acc, fault, layer};
+  dim3 grid(n_seg, n_kv, M);
+  size_t smem = (size_t)G * head * 4 + 2 * kKeyTile * (head + 8) * 2 + 2 * kKeyTile * head * 2;
+  cudaError_t e;
+  if (head == 128) {
+    if (G <= 8) e = launch(flash_decode_seg_kernel<128, 1>, grid, dim3(256), smem, st, a);
+    else {
+      cudaFuncSetAttribute(flash_decode_seg_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+      e = launch(flash_decode_seg_kernel<128, 2>, grid, dim3(256), smem, st, a);
+    }
+  } else {
+    if (G <= 8) e = launch(flash_decode_seg_kernel<64, 1>, grid, dim3(256), smem, st, a);
+    else e = launch(flash_decode_seg_kernel<64, 2>, grid, dim3(256), smem, st, a);
+  }
+  if (e != cudaSuccess) return (int)e;
+  MergeArgs mg{part_ml, part_acc, n_q, n_seg, M, row_seq, out, outq, (float2*)outds};
+  if (head == 128) return (int)launch(flash_decode_merge_kernel<128>, dim3(n_q, M), dim3(128), 0, st, mg);
+  return (int)launch(flash_decode_merge_kernel<64>, dim3(n_q, M), dim3(64), 0, st, mg);
+}
+
+}  // extern "C"

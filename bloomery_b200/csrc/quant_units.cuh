@@ -1,0 +1,432 @@
+// Weight "units": 64 consecutive values of one weight row, decoded in registers and
+// dotted against the q8 activation form (int8 codes + {d, d*sum} per 32 values).
+//
+// The same code compiles for the device (sm_100a, dp4a) and for the host (scalar
+// mirror used by the CPU engine and by the CPU tests), which is how the byte-level
+// decode is checked without a GPU.  The reference keeps per-type device dots in
+// crates/gpu/src/lib.rs (q4k_gemv, q6k_gemv), crates/gpu/src/kquant/*.rs and
+// crates/gpu/src/q5.rs, and their CPU twins in crates/qdot/src/lib.rs.
+//
+// Resident layouts (what sits in HBM; values are never re-quantised, only re-laid):
+//   Q4_K  the file's 144-byte superblocks, unchanged (16-byte aligned)
+//   Q5_K  the file's 176-byte superblocks, unchanged
+//   Q6_K  224-byte superblocks: ql[128] qh[64] scales[16] d(f16) pad[14]
+//   Q8_0  per row: K int8 codes, then K/32 f16 scales, padded to 16 bytes
+//   F16/BF16/F32 rows unchanged
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#define BL_HD __host__ __device__ __forceinline__
+#else
+#define BL_HD inline
+#endif
+
+namespace bl {
+
+enum WType : int {
+  WT_F32 = 0,
+  WT_F16 = 1,
+  WT_Q8_0 = 8,
+  WT_Q4_K = 12,
+  WT_Q5_K = 13,
+  WT_Q6_K = 14,
+  WT_BF16 = 30,
+};
+
+struct u32x4 { uint32_t x, y, z, w; };
+
+BL_HD int dot4(uint32_t a, uint32_t b, int c) {
+#if defined(__CUDA_ARCH__)
+  return __dp4a((int)a, (int)b, c);
+#else
+  for (int i = 0; i < 4; ++i) c += (int)(int8_t)(a >> (8 * i)) * (int)(int8_t)(b >> (8 * i));
+  return c;
+#endif
+}
+
+// unsigned a (0..255 per byte) times signed b
+BL_HD int dot4_us(uint32_t a, uint32_t b, int c) {
+#if defined(__CUDA_ARCH__)
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+#else
+  for (int i = 0; i < 4; ++i) c += (int)(uint8_t)(a >> (8 * i)) * (int)(int8_t)(b >> (8 * i));
+  return c;
+#endif
+}
+
+BL_HD float half_bits_to_float(uint16_t h) {
+#if defined(__CUDA_ARCH__)
+  return __half2float(__ushort_as_half(h));
+#else
+  uint32_t sign = (uint32_t)(h & 0x8000) << 16;
+  uint32_t exp = (h >> 10) & 0x1F;
+  uint32_t man = h & 0x3FF;
+  uint32_t bits;
+  if (exp == 0) {
+    if (man == 0) {
+      bits = sign;
+    } else {
+      int e = -1;
+      do { man <<= 1; ++e; } while (!(man & 0x400));
+      bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3FF) << 13);
+    }
+  } else if (exp == 31) {
+    bits = sign | 0x7F800000u | (man << 13);
+  } else {
+    bits = sign | ((exp + 112) << 23) | (man << 13);
+  }
+  float f;
+  __builtin_memcpy(&f, &bits, 4);
+  return f;
+#endif
+}
+
+BL_HD uint32_t ld32(const uint8_t* p) {
+#if defined(__CUDA_ARCH__)
+  return *reinterpret_cast<const uint32_t*>(p);
+#else
+  uint32_t v; __builtin_memcpy(&v, p, 4); return v;
+#endif
+}
+
+BL_HD u32x4 ld128(const uint8_t* p) {
+#if defined(__CUDA_ARCH__)
+  uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+  return u32x4{v.x, v.y, v.z, v.w};
+#else
+  u32x4 v; __builtin_memcpy(&v, p, 16); return v;
+#endif
+}
+
+// activation view for one unit: 64 codes (16 words) and the two {d, s} pairs
+struct ActUnit {
+  const uint32_t* q;   // 16 words, 16-byte aligned
+  float d0, s0, d1, s1;
+};
+
+// ---------------------------------------------------------------------------------
+// Q4_K
+// ---------------------------------------------------------------------------------
+struct Q4K {
+  static constexpr int kType = WT_Q4_K;
+  static constexpr int kSbBytes = 144;
+  struct Regs { u32x4 q0, q1; uint32_t s0, s1, s2, dm; };
+  static BL_HD long row_bytes(int K) { return (long)(K / 256) * kSbBytes; }
+  // unit u of a row: superblock u/4, 64-value pair u%4
+  static BL_HD void load(const uint8_t* row, int u, Regs& r) {
+    const uint8_t* p = row + (long)(u >> 2) * kSbBytes;
+    int j = u & 3;
+    r.q0 = ld128(p + 16 + 32 * j);
+    r.q1 = ld128(p + 32 + 32 * j);
+    r.dm = ld32(p);
+    r.s0 = ld32(p + 4); r.s1 = ld32(p + 8); r.s2 = ld32(p + 12);
+  }
+  static BL_HD void scale_min(const Regs& r, int i, int& sc, int& mn) {
+    // 6-bit (scale, min) pair i of 8 from the 12 packed bytes
+    int b = i & 3;
+    uint32_t q_lo = (r.s0 >> (8 * b)) & 0xFF;     // bytes 0..3
+    uint32_t q_mid = (r.s1 >> (8 * b)) & 0xFF;    // bytes 4..7
+    uint32_t q_hi = (r.s2 >> (8 * b)) & 0xFF;     // bytes 8..11
+    if (i < 4) { sc = q_lo & 63; mn = q_mid & 63; }
+    else { sc = (q_hi & 0xF) | ((q_lo >> 6) << 4); mn = (q_hi >> 4) | ((q_mid >> 6) << 4); }
+  }
+  static BL_HD float dot(const Regs& r, int u, const ActUnit& a) {
+    int j = u & 3;
+    const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+    int lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo = dot4_us(w[i] & 0x0F0F0F0Fu, a.q[i], lo);
+      hi = dot4_us((w[i] >> 4) & 0x0F0F0F0Fu, a.q[8 + i], hi);
+    }
+    int sc0, mn0, sc1, mn1;
+    scale_min(r, 2 * j, sc0, mn0);
+    scale_min(r, 2 * j + 1, sc1, mn1);
+    float d = half_bits_to_float((uint16_t)(r.dm & 0xFFFF));
+    float dmin = half_bits_to_float((uint16_t)(r.dm >> 16));
+    float pos = a.d0 * (float)(sc0 * lo) + a.d1 * (float)(sc1 * hi);
+    float neg = a.s0 * (float)mn0 + a.s1 * (float)mn1;
+    return d * pos - dmin * neg;
+  }
+  // decode the unit's 64 values (for the embedding gather and the bf16 expander)
+  static BL_HD void decode(const Regs& r, int u, float* out) {
+    int j = u & 3;
+    const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+    int sc0, mn0, sc1, mn1;
+    scale_min(r, 2 * j, sc0, mn0);
+    scale_min(r, 2 * j + 1, sc1, mn1);
+    float d = half_bits_to_float((uint16_t)(r.dm & 0xFFFF));
+    float dmin = half_bits_to_float((uint16_t)(r.dm >> 16));
+    float d0 = d * sc0, m0 = dmin * mn0, d1 = d * sc1, m1 = dmin * mn1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        uint32_t byte = (w[i] >> (8 * b)) & 0xFF;
+        out[4 * i + b] = d0 * (float)(byte & 0xF) - m0;
+        out[32 + 4 * i + b] = d1 * (float)(byte >> 4) - m1;
+      }
+  }
+};
+
+// ---------------------------------------------------------------------------------
+// Q5_K
+// ---------------------------------------------------------------------------------
+struct Q5K {
+  static constexpr int kType = WT_Q5_K;
+  static constexpr int kSbBytes = 176;
+  struct Regs { u32x4 q0, q1, h0, h1; uint32_t s0, s1, s2, dm; };
+  static BL_HD long row_bytes(int K) { return (long)(K / 256) * kSbBytes; }
+  static BL_HD void load(const uint8_t* row, int u, Regs& r) {
+    const uint8_t* p = row + (long)(u >> 2) * kSbBytes;
+    int j = u & 3;
+    r.dm = ld32(p);
+    r.s0 = ld32(p + 4); r.s1 = ld32(p + 8); r.s2 = ld32(p + 12);
+    r.h0 = ld128(p + 16); r.h1 = ld128(p + 32);
+    r.q0 = ld128(p + 48 + 32 * j);
+    r.q1 = ld128(p + 64 + 32 * j);
+  }
+  static BL_HD void codes(const Regs& r, int u, uint32_t* lo5, uint32_t* hi5) {
+    int j = u & 3;
+    const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+    const uint32_t h[8] = {r.h0.x, r.h0.y, r.h0.z, r.h0.w, r.h1.x, r.h1.y, r.h1.z, r.h1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t hb0 = (h[i] >> (2 * j)) & 0x01010101u;
+      uint32_t hb1 = (h[i] >> (2 * j + 1)) & 0x01010101u;
+      lo5[i] = (w[i] & 0x0F0F0F0Fu) | (hb0 << 4);
+      hi5[i] = ((w[i] >> 4) & 0x0F0F0F0Fu) | (hb1 << 4);
+    }
+  }
+  static BL_HD float dot(const Regs& r, int u, const ActUnit& a) {
+    int j = u & 3;
+    uint32_t l5[8], h5[8];
+    codes(r, u, l5, h5);
+    int lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo = dot4_us(l5[i], a.q[i], lo);
+      hi = dot4_us(h5[i], a.q[8 + i], hi);
+    }
+    Q4K::Regs t; t.s0 = r.s0; t.s1 = r.s1; t.s2 = r.s2;
+    int sc0, mn0, sc1, mn1;
+    Q4K::scale_min(t, 2 * j, sc0, mn0);
+    Q4K::scale_min(t, 2 * j + 1, sc1, mn1);
+    float d = half_bits_to_float((uint16_t)(r.dm & 0xFFFF));
+    float dmin = half_bits_to_float((uint16_t)(r.dm >> 16));
+    float pos = a.d0 * (float)(sc0 * lo) + a.d1 * (float)(sc1 * hi);
+    float neg = a.s0 * (float)mn0 + a.s1 * (float)mn1;
+    return d * pos - dmin * neg;
+  }
+  static BL_HD void decode(const Regs& r, int u, float* out) {
+    int j = u & 3;
+    uint32_t l5[8], h5[8];
+    codes(r, u, l5, h5);
+    Q4K::Regs t; t.s0 = r.s0; t.s1 = r.s1; t.s2 = r.s2;
+    int sc0, mn0, sc1, mn1;
+    Q4K::scale_min(t, 2 * j, sc0, mn0);
+    Q4K::scale_min(t, 2 * j + 1, sc1, mn1);
+    float d = half_bits_to_float((uint16_t)(r.dm & 0xFFFF));
+    float dmin = half_bits_to_float((uint16_t)(r.dm >> 16));
+    float d0 = d * sc0, m0 = dmin * mn0, d1 = d * sc1, m1 = dmin * mn1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        out[4 * i + b] = d0 * (float)((l5[i] >> (8 * b)) & 0xFF) - m0;
+        out[32 + 4 * i + b] = d1 * (float)((h5[i] >> (8 * b)) & 0xFF) - m1;
+      }
+  }
+};
+
+// ---------------------------------------------------------------------------------
+// Q6_K (resident 224-byte superblocks)
+// ---------------------------------------------------------------------------------
+// Unit u of a superblock: half n = (u>>1)&1, 16-lane slice h = u&1.  It covers four
+// runs of 16 values at 128n + 32g + 16h (g = 0..3); the activation gather below
+// presents them to `dot` as if they were 64 consecutive values.
+struct Q6K {
+  static constexpr int kType = WT_Q6_K;
+  static constexpr int kSbBytes = 224;
+  static constexpr int kFileSbBytes = 210;
+  struct Regs { u32x4 la, lb, h; uint32_t sc[4]; uint32_t d; };
+  static BL_HD long row_bytes(int K) { return (long)(K / 256) * kSbBytes; }
+  static BL_HD void load(const uint8_t* row, int u, Regs& r) {
+    const uint8_t* p = row + (long)(u >> 2) * kSbBytes;
+    int n = (u >> 1) & 1, h = u & 1;
+    r.la = ld128(p + 64 * n + 16 * h);
+    r.lb = ld128(p + 64 * n + 32 + 16 * h);
+    r.h = ld128(p + 128 + 32 * n + 16 * h);
+    u32x4 s = ld128(p + 192);
+    r.sc[0] = s.x; r.sc[1] = s.y; r.sc[2] = s.z; r.sc[3] = s.w;
+    r.d = ld32(p + 208) & 0xFFFF;
+  }
+  static BL_HD int scale(const Regs& r, int idx) {  // idx 0..15, signed byte
+    return (int)(int8_t)((r.sc[idx >> 2] >> (8 * (idx & 3))) & 0xFF);
+  }
+  // four groups g of four words (16 codes each), codes already centred (q - 32)
+  static BL_HD void codes(const Regs& r, uint32_t c[4][4]) {
+    const uint32_t la[4] = {r.la.x, r.la.y, r.la.z, r.la.w};
+    const uint32_t lb[4] = {r.lb.x, r.lb.y, r.lb.z, r.lb.w};
+    const uint32_t hh[4] = {r.h.x, r.h.y, r.h.z, r.h.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      c[0][i] = (la[i] & 0x0F0F0F0Fu) | (((hh[i] >> 0) & 0x03030303u) << 4);
+      c[1][i] = (lb[i] & 0x0F0F0F0Fu) | (((hh[i] >> 2) & 0x03030303u) << 4);
+      c[2][i] = ((la[i] >> 4) & 0x0F0F0F0Fu) | (((hh[i] >> 4) & 0x03030303u) << 4);
+      c[3][i] = ((lb[i] >> 4) & 0x0F0F0F0Fu) | (((hh[i] >> 6) & 0x03030303u) << 4);
+    }
+  }
+  // `aq` points at the superblock's 256 codes (64 words); `ads` at its 8 {d,s} pairs
+  static BL_HD float dot_sb(const Regs& r, int u, const uint32_t* aq, const float* ads) {
+    int n = (u >> 1) & 1, h = u & 1;
+    uint32_t c[4][4];
+    codes(r, c);
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t* x = aq + (128 * n + 32 * g + 16 * h) / 4;
+      int s = 0, sx = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s = dot4_us(c[g][i], x[i], s);
+        sx = dot4(0x01010101u, x[i], sx);
+      }
+      s -= 32 * sx;
+      acc += ads[2 * (4 * n + g)] * (float)(scale(r, 8 * n + 2 * g + h) * s);
+    }
+    return half_bits_to_float((uint16_t)r.d) * acc;
+  }
+  static BL_HD void decode(const Regs& r, int u, float* out /*64: g*16 + i*/) {
+    int n = (u >> 1) & 1, h = u & 1;
+    uint32_t c[4][4];
+    codes(r, c);
+    float d = half_bits_to_float((uint16_t)r.d);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float ds = d * (float)scale(r, 8 * n + 2 * g + h);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          out[16 * g + 4 * i + b] = ds * (float)((int)((c[g][i] >> (8 * b)) & 0xFF) - 32);
+    }
+  }
+  // position inside the superblock of decoded element e (0..63) of unit u
+  static BL_HD int value_index(int u, int e) {
+    int n = (u >> 1) & 1, h = u & 1;
+    return 128 * n + 32 * (e >> 4) + 16 * h + (e & 15);
+  }
+};
+
+// ---------------------------------------------------------------------------------
+// Q8_0 (resident: codes then f16 scales per row)
+// ---------------------------------------------------------------------------------
+struct Q80 {
+  static constexpr int kType = WT_Q8_0;
+  struct Regs { u32x4 q[4]; uint32_t dd; };
+  static BL_HD long row_bytes(int K) { return (((long)K + K / 16) + 15) / 16 * 16; }
+  static BL_HD void load(const uint8_t* row, int u, int K, Regs& r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.q[i] = ld128(row + 64 * u + 16 * i);
+    r.dd = ld32(row + K + 4 * u);
+  }
+  static BL_HD float dot(const Regs& r, const ActUnit& a) {
+    const uint32_t w[16] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w,
+                            r.q[2].x, r.q[2].y, r.q[2].z, r.q[2].w, r.q[3].x, r.q[3].y, r.q[3].z, r.q[3].w};
+    int lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo = dot4(w[i], a.q[i], lo);
+      hi = dot4(w[8 + i], a.q[8 + i], hi);
+    }
+    float d0 = half_bits_to_float((uint16_t)(r.dd & 0xFFFF));
+    float d1 = half_bits_to_float((uint16_t)(r.dd >> 16));
+    return d0 * a.d0 * (float)lo + d1 * a.d1 * (float)hi;
+  }
+  static BL_HD void decode(const Regs& r, float* out) {
+    float d0 = half_bits_to_float((uint16_t)(r.dd & 0xFFFF));
+    float d1 = half_bits_to_float((uint16_t)(r.dd >> 16));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w[4] = {r.q[i].x, r.q[i].y, r.q[i].z, r.q[i].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          out[16 * i + 4 * k + b] = (i < 2 ? d0 : d1) * (float)(int8_t)((w[k] >> (8 * b)) & 0xFF);
+    }
+  }
+};
+
+
+// ---------------------------------------------------------------------------------
+// Uniform interface used by the templated kernels:
+//   T::loadu(row, u, K, regs)                     fetch unit u of a weight row
+//   T::dotu(regs, u, xq_row_words, xds_row)       dot with a q8 activation row
+//   T::decodeu(regs, u, out64), T::pos(u, e)      decoded values and their positions
+// ---------------------------------------------------------------------------------
+struct F2 { float x, y; };
+
+template <class T> struct Unit;
+
+template <> struct Unit<Q4K> {
+  using Regs = Q4K::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int, Regs& r) { Q4K::load(row, u, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    ActUnit a{xq + 16 * u, xds[2 * u].x, xds[2 * u].y, xds[2 * u + 1].x, xds[2 * u + 1].y};
+    return Q4K::dot(r, u, a);
+  }
+  static BL_HD void decodeu(const Regs& r, int u, float* o) { Q4K::decode(r, u, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
+template <> struct Unit<Q5K> {
+  using Regs = Q5K::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int, Regs& r) { Q5K::load(row, u, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    ActUnit a{xq + 16 * u, xds[2 * u].x, xds[2 * u].y, xds[2 * u + 1].x, xds[2 * u + 1].y};
+    return Q5K::dot(r, u, a);
+  }
+  static BL_HD void decodeu(const Regs& r, int u, float* o) { Q5K::decode(r, u, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
+template <> struct Unit<Q6K> {
+  using Regs = Q6K::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int, Regs& r) { Q6K::load(row, u, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    int sb = u >> 2;
+    return Q6K::dot_sb(r, u, xq + 64 * sb, reinterpret_cast<const float*>(xds + 8 * sb));
+  }
+  static BL_HD void decodeu(const Regs& r, int u, float* o) { Q6K::decode(r, u, o); }
+  static BL_HD int pos(int u, int e) { return 256 * (u >> 2) + Q6K::value_index(u, e); }
+};
+template <> struct Unit<Q80> {
+  using Regs = Q80::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int K, Regs& r) { Q80::load(row, u, K, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    ActUnit a{xq + 16 * u, xds[2 * u].x, xds[2 * u].y, xds[2 * u + 1].x, xds[2 * u + 1].y};
+    return Q80::dot(r, a);
+  }
+  static BL_HD void decodeu(const Regs& r, int, float* o) { Q80::decode(r, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
+
+// Resident row size for a weight type and row length.
+BL_HD long resident_row_bytes(int wtype, int K) {
+  switch (wtype) {
+    case WT_Q4_K: return Q4K::row_bytes(K);
+    case WT_Q5_K: return Q5K::row_bytes(K);
+    case WT_Q6_K: return Q6K::row_bytes(K);
+    case WT_Q8_0: return Q80::row_bytes(K);
+    case WT_F32: return 4L * K;
+    case WT_F16: case WT_BF16: return 2L * K;
+  }
+  return -1;
+}
+
+}  // namespace bl

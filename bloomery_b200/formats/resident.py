@@ -1,0 +1,86 @@
+"""Resident (in-HBM) layouts of quantised weights.
+
+Values are never re-quantised on load; some block types are only re-laid so that every
+16-byte vector load of the kernels is aligned (the reference does the same in
+``crates/gpu/src/weights.rs`` / ``planes.rs``: "resident formats per type").
+
+  Q4_K, Q5_K          file blocks unchanged (144 / 176 bytes, both multiples of 16)
+  Q6_K                210-byte file blocks padded to 224: ql[128] qh[64] sc[16] d pad[14]
+  Q8_0                per row: K int8 codes, then K/32 f16 scales, padded to 16 bytes
+  F32 / F16 / BF16    unchanged
+
+Works on CPU and CUDA tensors (the repack of a 30 B-parameter model runs on the card).
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from .quant import QTYPES
+
+# weight-type ids shared with csrc/quant_units.cuh (equal to the ggml ids)
+WT = {"F32": 0, "F16": 1, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30}
+INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0")
+FLOAT_TYPES = ("F32", "F16", "BF16")
+
+
+class UnsupportedType(ValueError):
+    pass
+
+
+def resident_row_bytes(qtype: str, k: int) -> int:
+    if qtype == "Q4_K":
+        return k // 256 * 144
+    if qtype == "Q5_K":
+        return k // 256 * 176
+    if qtype == "Q6_K":
+        return k // 256 * 224
+    if qtype == "Q8_0":
+        return (k + k // 16 + 15) // 16 * 16
+    if qtype == "F32":
+        return 4 * k
+    if qtype in ("F16", "BF16"):
+        return 2 * k
+    raise UnsupportedType(f"no resident layout for block type {qtype}")
+
+
+def to_resident(raw: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
+    """uint8 [rows, file_row_bytes] -> uint8 [rows, resident_row_bytes] (same device)."""
+    if raw.dtype != torch.uint8 or raw.dim() != 2:
+        raise ValueError("to_resident takes uint8 [rows, row_bytes]")
+    rows = raw.shape[0]
+    if raw.shape[1] != QTYPES[qtype].row_bytes(k):
+        raise ValueError(f"{qtype}: row of {raw.shape[1]} bytes does not match k={k}")
+    if qtype in ("Q4_K", "Q5_K", "F32", "F16", "BF16"):
+        return raw.contiguous()
+    if qtype == "Q6_K":
+        nsb = k // 256
+        out = torch.zeros(rows, nsb, 224, dtype=torch.uint8, device=raw.device)
+        out[..., :210] = raw.reshape(rows, nsb, 210)
+        return out.reshape(rows, nsb * 224)
+    if qtype == "Q8_0":
+        nb = k // 32
+        blk = raw.reshape(rows, nb, 34)
+        out = torch.zeros(rows, resident_row_bytes("Q8_0", k), dtype=torch.uint8, device=raw.device)
+        out[:, :k] = blk[..., 2:].reshape(rows, k)
+        out[:, k:k + 2 * nb] = blk[..., :2].reshape(rows, 2 * nb)
+        return out
+    raise UnsupportedType(f"no resident layout for block type {qtype}")
+
+
+def from_resident(res: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
+    """Inverse of :func:`to_resident` (used by tests and by slot files)."""
+    rows = res.shape[0]
+    if qtype in ("Q4_K", "Q5_K", "F32", "F16", "BF16"):
+        return res
+    if qtype == "Q6_K":
+        nsb = k // 256
+        return res.reshape(rows, nsb, 224)[..., :210].reshape(rows, nsb * 210).contiguous()
+    if qtype == "Q8_0":
+        nb = k // 32
+        out = torch.empty(rows, nb, 34, dtype=torch.uint8, device=res.device)
+        out[..., 2:] = res[:, :k].reshape(rows, nb, 32)
+        out[..., :2] = res[:, k:k + 2 * nb].reshape(rows, nb, 2)
+        return out.reshape(rows, nb * 34)
+    raise UnsupportedType(qtype)

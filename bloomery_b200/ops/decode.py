@@ -1,0 +1,142 @@
+"""Python face of the decode-chain CUDA kernels (``csrc/*_decode.cu``, ``decode_gemv.cu``).
+
+Each wrapper only marshals pointers and shapes; the host-side launch contract lives in
+the C launcher and comes back as a negative code that :func:`check` turns into an
+exception naming the call.  All launches go to the current torch stream, so they are
+capturable in a ``torch.cuda.CUDAGraph``.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..formats.resident import WT
+from ._lib import F, I, L, check, cuda, p, stream
+
+_sm_count_cache = {}
+
+
+def sm_count(device=None) -> int:
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    if dev not in _sm_count_cache:
+        _sm_count_cache[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _sm_count_cache[dev]
+
+
+@dataclass
+class QWeight:
+    """A weight matrix (or stack of expert matrices) in its resident layout."""
+
+    data: torch.Tensor        # uint8, [rows, resident_row_bytes] or [experts, rows, resident_row_bytes]
+    qtype: str
+    k: int
+
+    @property
+    def wt(self) -> int:
+        return WT[self.qtype]
+
+    @property
+    def rows(self) -> int:
+        return self.data.shape[-2]
+
+    @property
+    def n_bytes(self) -> int:
+        return self.data.numel()
+
+
+def set_pdl(on: bool) -> None:
+    cuda().bl_set_pdl(I(1 if on else 0))
+
+
+def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torch.Tensor] = None,
+         gain: Optional[torch.Tensor] = None, eps: float = 1e-6, xq: Optional[torch.Tensor] = None,
+         xds: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+         xq_out: Optional[torch.Tensor] = None, xds_out: Optional[torch.Tensor] = None,
+         fault: Optional[torch.Tensor] = None, layer: int = 0) -> None:
+    n = len(segs)
+    K = segs[0].k
+    wp = (ctypes.c_void_p * n)(*[s.data.data_ptr() for s in segs])
+    rows = (ctypes.c_int * n)(*[s.rows for s in segs])
+    wts = (ctypes.c_int * n)(*[s.wt for s in segs])
+    norm = x is not None
+    rc = cuda().bl_gemv(I(n), wp, rows, wts, I(K), I(M), I(1 if norm else 0),
+                        p(x), L(x.stride(0) if norm else 0), p(gain), F(eps), p(xq), p(xds),
+                        p(out), L(out.stride(0)), p(resid), L(resid.stride(0) if resid is not None else 0),
+                        p(xq_out), p(xds_out), p(fault), I(layer), I(sm_count()), stream())
+    check(rc, "bl_gemv")
+
+
+def qk_norm_rope_append(qkv: torch.Tensor, q_gain, k_gain, inv_freq: torch.Tensor, eps: float, q_scale: float,
+                        head: int, n_q: int, n_kv: int, M: int, row_pos, row_seq, block_table, n_pages: int,
+                        k_cache, v_cache, q_out, fault, layer: int) -> None:
+    rc = cuda().bl_qk_norm_rope_append(p(qkv), L(qkv.stride(0)), p(q_gain), p(k_gain), p(inv_freq), F(eps), F(q_scale),
+                                       I(head), I(n_q), I(n_kv), I(M), p(row_pos), p(row_seq), p(block_table),
+                                       I(block_table.shape[1]), I(n_pages), p(k_cache), p(v_cache), p(q_out), p(fault),
+                                       I(layer), stream())
+    check(rc, "bl_qk_norm_rope_append")
+
+
+def flash_decode(q, k_cache, v_cache, row_pos, row_seq, block_table, n_pages: int, head: int, n_q: int, n_kv: int,
+                 M: int, n_seg: int, ctx_limit: int, part_ml, part_acc, out, outq, outds, fault, layer: int) -> None:
+    rc = cuda().bl_flash_decode(p(q), p(k_cache), p(v_cache), p(row_pos), p(row_seq), p(block_table),
+                                I(block_table.shape[1]), I(n_pages), I(head), I(n_q), I(n_kv), I(M), I(n_seg),
+                                I(ctx_limit), p(part_ml), p(part_acc), p(out), p(outq), p(outds), p(fault), I(layer),
+                                stream())
+    check(rc, "bl_flash_decode")
+
+
+def router(x, gain, eps: float, w: QWeight, bias, M: int, top_k: int, mode: int, renorm: bool, scale: float,
+           n_group: int, topk_group: int, logits, ids, wts, xq_out, xds_out, xn_out, counter, heat, fault,
+           layer: int) -> None:
+    rc = cuda().bl_router(p(x), L(x.stride(0)), p(gain), F(eps), p(w.data), I(w.wt), p(bias), I(w.k), I(w.rows), I(M),
+                          I(top_k), I(mode), I(1 if renorm else 0), F(scale), I(n_group), I(topk_group), p(logits),
+                          p(ids), p(wts), p(xq_out), p(xds_out), p(xn_out), p(counter), p(heat), p(fault), I(layer),
+                          stream())
+    check(rc, "bl_router")
+
+
+def gate_up_sel(xq, xds, ids, slot_map, gate: QWeight, up: QWeight, n_expert: int, n_used: int, M: int, actq, actds,
+                act_f32, fault, layer: int) -> None:
+    rc = cuda().bl_gate_up_sel(p(xq), p(xds), p(ids), p(slot_map), p(gate.data), p(up.data), I(gate.wt), I(up.wt),
+                               I(gate.k), I(gate.rows), I(n_expert), I(n_used), I(M), p(actq), p(actds), p(act_f32),
+                               p(fault), I(layer), stream())
+    check(rc, "bl_gate_up_sel")
+
+
+def down_combine(actq, actds, ids, wts, slot_map, down: QWeight, n_expert: int, n_used: int, M: int, resid, extra,
+                 out, fault, layer: int) -> None:
+    rc = cuda().bl_down_combine(p(actq), p(actds), p(ids), p(wts), p(slot_map), p(down.data), I(down.wt), I(down.k),
+                                I(down.rows), I(n_expert), I(n_used), I(M), p(resid),
+                                L(resid.stride(0) if resid is not None else 0), p(extra),
+                                L(extra.stride(0) if extra is not None else 0), p(out), L(out.stride(0)), p(fault),
+                                I(layer), stream())
+    check(rc, "bl_down_combine")
+
+
+def embed_rows(tokens, M: int, table: QWeight, vocab: int, out, fault) -> None:
+    rc = cuda().bl_embed_rows(p(tokens), I(M), p(table.data), I(table.wt), I(table.k), I(vocab), p(out),
+                              L(out.stride(0)), p(fault), stream())
+    check(rc, "bl_embed_rows")
+
+
+def argmax_rows(logits, V: int, M: int, nblk: int, part_v, part_i, counter, tokens_out, best_val, fault) -> None:
+    rc = cuda().bl_argmax_rows(p(logits), L(logits.stride(0)), I(V), I(M), I(nblk), p(part_v), p(part_i), p(counter),
+                               p(tokens_out), p(best_val), p(fault), stream())
+    check(rc, "bl_argmax_rows")
+
+
+def fill_u32(t: torch.Tensor, value: int) -> None:
+    check(cuda().bl_fill_u32(p(t), ctypes.c_uint(value), I(t.numel()), stream()), "bl_fill_u32")
+
+
+def advance_rows(tokens, row_pos, row_seq, chosen, M: int, hist=None, hist_cap: int = 0, hist_count=None) -> None:
+    check(cuda().bl_advance_rows(p(tokens), p(row_pos), p(row_seq), p(chosen), I(M), p(hist), I(hist_cap),
+                                 p(hist_count), stream()), "bl_advance_rows")
+
+
+def swiglu_q8(gu: torch.Tensor, I_: int, M: int, actq, actds, act_f32=None) -> None:
+    check(cuda().bl_swiglu_q8(p(gu), L(gu.stride(0)), I(I_), I(M), p(actq), p(actds), p(act_f32), stream()),
+          "bl_swiglu_q8")

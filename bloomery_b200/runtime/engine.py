@@ -1,0 +1,312 @@
+"""GPU decode engine: static arenas, the per-layer kernel chain, one CUDA graph per
+row bucket, a device fault word with a bounded readback.
+
+Counterpart of the reference's ``GpuModel`` (``crates/gpu/src/model.rs``: ``step`` :1419,
+``launch_token`` :1471 = refresh params -> replay -> keep rows; ``step_ahead`` :1505;
+``MAX_PASS_ROWS = 8`` :369) and of its graph wrapper (``graph.rs``).  Everything that
+changes from step to step (token ids, positions, slot of each row, block table, live key
+counts, expert ids) lives in device buffers, so a captured graph is replayed unchanged.
+
+Per layer the chain is 8 launches:
+  norm+q8+QKV gemv | qk-norm+RoPE+append | flash segments | merge+q8 |
+  o_proj+residual | norm+router+top-k | gate·up·SwiGLU+q8 (sel) | down+combine+residual
+"""
+from __future__ import annotations
+
+import math
+import threading
+import time
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..models.spec import ModelSpec
+from ..models.weights import Weights
+from ..ops import decode as K
+from .kv import PAGE, KvPool
+
+MAX_ROWS = 8
+FAULT_CLEAN = 0xFFFFFFFF
+
+FAULT_SITES = {1: "token id out of range", 2: "non-finite activation", 3: "non-finite router logit",
+               4: "expert id out of range", 5: "key count out of range", 6: "KV page missing",
+               7: "device wait ran out", 8: "sampler"}
+
+
+class EngineFault(RuntimeError):
+    """The device fault word is set; the engine is poisoned until ``reset_fault``."""
+
+    def __init__(self, word: int):
+        self.word = word
+        self.layer, self.site = word >> 8, word & 0xFF
+        super().__init__(f"device fault at layer {self.layer}: {FAULT_SITES.get(self.site, self.site)}")
+
+
+class EngineStalled(RuntimeError):
+    """A bounded wait on the device ran out (the reference's ``GpuError::Stalled``)."""
+
+
+def bucket_of(m: int) -> int:
+    for b in (1, 2, 4, 8):
+        if m <= b:
+            return b
+    raise ValueError(f"{m} rows exceed a pass of {MAX_ROWS}")
+
+
+class DecodeEngine:
+    def __init__(self, weights: Weights, n_slots: int = 1, slot_ctx: int = 4096, n_seg: Optional[int] = None,
+                 use_graphs: bool = True, keep_logits: bool = True, engine_bound_s: float = 60.0):
+        self.w = weights
+        self.spec: ModelSpec = weights.spec
+        s = self.spec
+        if s.mla:
+            raise ValueError("MLA models run on MlaEngine")
+        self.device = weights.device
+        dev = self.device
+        self.n_slots, self.slot_ctx = n_slots, slot_ctx
+        self.use_graphs = use_graphs
+        self.bound_s = engine_bound_s
+        max_pages = (slot_ctx + PAGE - 1) // PAGE
+        self.kv = KvPool(s.n_layer, s.n_kv, s.head_dim, n_slots * max_pages, n_slots, max_pages, dev)
+        sm = K.sm_count(dev)
+        self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, sm // s.n_kv)))
+        H, V = s.hidden, s.vocab
+        f32 = dict(dtype=torch.float32, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        R = MAX_ROWS
+        # step parameters: tokens, positions, slot of each row (one H2D copy)
+        self.params = torch.zeros(3, R, **i32)
+        self.params[2].fill_(-1)
+        self.params_host = torch.zeros(3, R, dtype=torch.int32, pin_memory=True)
+        self.tokens, self.row_pos, self.row_seq = self.params[0], self.params[1], self.params[2]
+        self.x = torch.zeros(R, H, **f32)
+        qkv_w = s.q_rows + 2 * s.kv_rows
+        self.qkv = torch.zeros(R, qkv_w, **f32)
+        self.q_out = torch.zeros(R, s.n_q, s.head_dim, **f32)
+        self.part_ml = torch.zeros(R * s.n_q * self.n_seg * 2, **f32)
+        self.part_acc = torch.zeros(R * s.n_q * self.n_seg * s.head_dim, **f32)
+        self.attn_q = torch.zeros(R, s.q_rows, dtype=torch.int8, device=dev)
+        self.attn_ds = torch.zeros(R, s.q_rows // 32, 2, **f32)
+        self.xq = torch.zeros(R, H, dtype=torch.int8, device=dev)
+        self.xds = torch.zeros(R, H // 32, 2, **f32)
+        if s.is_moe:
+            self.r_logits = torch.zeros(R, s.n_expert, **f32)
+            self.r_ids = torch.zeros(R, s.n_used, **i32)
+            self.r_wts = torch.zeros(R, s.n_used, **f32)
+            self.actq = torch.zeros(R, s.n_used, s.moe_inter, dtype=torch.int8, device=dev)
+            self.actds = torch.zeros(R, s.n_used, s.moe_inter // 32, 2, **f32)
+            self.heat = torch.zeros(s.n_layer, s.n_expert, **i32)
+        if s.dense_inter and (s.first_dense > 0 or not s.is_moe):
+            self.gu = torch.zeros(R, 2 * s.dense_inter, **f32)
+            self.dactq = torch.zeros(R, s.dense_inter, dtype=torch.int8, device=dev)
+            self.dactds = torch.zeros(R, s.dense_inter // 32, 2, **f32)
+        self.counters = torch.zeros(4, **i32)
+        self.logits = torch.zeros(R, V, **f32)
+        self.am_blocks = 64
+        self.am_v = torch.zeros(R * self.am_blocks, **f32)
+        self.am_i = torch.zeros(R * self.am_blocks, **i32)
+        self.tokens_out = torch.zeros(R + 1, **i32)
+        self.tokens_out_host = torch.zeros(R + 1, dtype=torch.int32, pin_memory=True)
+        self.fault = torch.full((1,), -1, **i32)  # 0xFFFFFFFF
+        self.hist_cap = 4096
+        self.hist = torch.zeros(self.hist_cap * R, **i32)
+        inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float64) / s.head_dim))
+        self.inv_freq = (inv / s.rope_scale).float().to(dev)
+        self.graphs: Dict[Tuple[int, bool, bool], torch.cuda.CUDAGraph] = {}
+        self.poisoned: Optional[int] = None
+        self.slot_len = [0] * n_slots
+        self.launches_per_step = 0
+        self.steps = 0
+        self._stream = torch.cuda.Stream(device=dev)
+        self._done = torch.cuda.Event()
+        self._lock = threading.Lock()
+
+    # ---------------------------------------------------------------------------------
+    # the kernel chain
+    # ---------------------------------------------------------------------------------
+    def enqueue(self, M: int, head: bool = True, advance: bool = False) -> int:
+        """Enqueue one pass of M rows on the current stream; returns the launch count."""
+        s, w = self.spec, self.w
+        n = 0
+        x = self.x
+        K.embed_rows(self.tokens, M, w.q["token_embd.weight"], s.vocab, x, self.fault); n += 1
+        kvp = self.kv
+        for il in range(s.n_layer):
+            b = f"blk.{il}."
+            K.gemv([w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
+                   x=x, gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il); n += 1
+            K.qk_norm_rope_append(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
+                                  self.inv_freq, s.rms_eps, 1.0 / math.sqrt(s.head_dim), s.head_dim, s.n_q, s.n_kv, M,
+                                  self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out,
+                                  self.fault, il); n += 1
+            K.flash_decode(self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
+                           s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
+                           self.attn_q, self.attn_ds, self.fault, il); n += 2
+            K.gemv([w.q[b + "attn_output.weight"]], M, x, xq=self.attn_q, xds=self.attn_ds, resid=x,
+                   fault=self.fault, layer=il); n += 1
+            if s.layer_is_moe(il):
+                K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"],
+                         w.f.get(b + "exp_probs_b.bias"), M, s.n_used, 0 if s.router_mode == "softmax" else 1,
+                         s.router_renorm, s.router_scale, s.n_group, s.topk_group, self.r_logits, self.r_ids,
+                         self.r_wts, self.xq, self.xds, None, self.counters[0:1], self.heat[il], self.fault, il); n += 1
+                K.gate_up_sel(self.xq, self.xds, self.r_ids, None, w.q[b + "ffn_gate_exps.weight"],
+                              w.q[b + "ffn_up_exps.weight"], s.n_expert, s.n_used, M, self.actq, self.actds, None,
+                              self.fault, il); n += 1
+                K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, None, w.q[b + "ffn_down_exps.weight"],
+                               s.n_expert, s.n_used, M, x, None, x, self.fault, il); n += 1
+            else:
+                K.gemv([w.q[b + "ffn_gate.weight"], w.q[b + "ffn_up.weight"]], M, self.gu, x=x,
+                       gain=w.f[b + "ffn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il); n += 1
+                K.swiglu_q8(self.gu, s.dense_inter, M, self.dactq, self.dactds); n += 1
+                K.gemv([w.q[b + "ffn_down.weight"]], M, x, xq=self.dactq, xds=self.dactds, resid=x,
+                       fault=self.fault, layer=il); n += 1
+        if head:
+            head_w = w.q.get("output.weight", w.q["token_embd.weight"])
+            K.gemv([head_w], M, self.logits, x=x, gain=w.f["output_norm.weight"], eps=s.rms_eps,
+                   fault=self.fault, layer=s.n_layer); n += 1
+            K.argmax_rows(self.logits, s.vocab, M, self.am_blocks, self.am_v, self.am_i, self.counters[1:2],
+                          self.tokens_out, None, self.fault); n += 1
+            if advance:
+                K.advance_rows(self.tokens, self.row_pos, self.row_seq, self.tokens_out, M, self.hist, self.hist_cap,
+                               self.counters[2:3]); n += 1
+        return n
+
+    def _graph(self, M: int, head: bool, advance: bool) -> torch.cuda.CUDAGraph:
+        key = (M, head, advance)
+        g = self.graphs.get(key)
+        if g is None:
+            # warm up eagerly once (sets function attributes, loads modules), then capture
+            st = self._stream
+            st.wait_stream(torch.cuda.current_stream(self.device))
+            saved = self.params.clone()
+            with torch.cuda.stream(st):
+                self.params[2].fill_(-1)        # padding rows only: touches no KV
+                self.enqueue(M, head, False)
+                st.synchronize()
+                self.params.copy_(saved)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=st):
+                    self.launches_per_step = self.enqueue(M, head, advance)
+            torch.cuda.current_stream(self.device).wait_stream(st)
+            self.graphs[key] = g
+        return g
+
+    # ---------------------------------------------------------------------------------
+    # host protocol
+    # ---------------------------------------------------------------------------------
+    def set_rows(self, rows: Sequence[Tuple[int, int, int]]) -> int:
+        """rows = [(slot, token, position)]; pads to the bucket; returns the bucket size."""
+        m = len(rows)
+        M = bucket_of(m)
+        ph = self.params_host
+        ph[2].fill_(-1)
+        for i, (slot, tok, pos) in enumerate(rows):
+            ph[0, i], ph[1, i], ph[2, i] = tok, pos, slot
+            self.kv.ensure(slot, pos + 1)
+            self.kv.own(slot, pos)
+        self.kv.sync_table()
+        self.params.copy_(ph, non_blocking=True)
+        return M
+
+    def launch(self, M: int, head: bool = True, advance: bool = False) -> None:
+        if self.poisoned is not None:
+            raise EngineFault(self.poisoned)
+        if self.use_graphs:
+            self._graph(M, head, advance).replay()
+        else:
+            self.enqueue(M, head, advance)
+        self.steps += 1
+
+    def read_tokens(self, m: int) -> List[int]:
+        """Bounded readback of the chosen tokens and the fault word."""
+        self.tokens_out_host.copy_(self.tokens_out, non_blocking=True)
+        self._done.record()
+        t0 = time.monotonic()
+        while not self._done.query():
+            if time.monotonic() - t0 > self.bound_s:
+                raise EngineStalled(f"no answer from the device within {self.bound_s:.0f} s")
+            time.sleep(0)
+        # the kernel writes the fault copy at index M (the bucket size)
+        return self.tokens_out_host.tolist()
+
+    def step(self, rows: Sequence[Tuple[int, int, int]], head: bool = True) -> List[int]:
+        """One pass over ``rows``; returns the greedy token of every row."""
+        with self._lock:
+            M = self.set_rows(rows)
+            self.launch(M, head, False)
+            for slot, _, pos in rows:
+                self.slot_len[slot] = max(self.slot_len[slot], pos + 1)
+            if not head:
+                return []
+            out = self.read_tokens(len(rows))
+            word = out[M] & 0xFFFFFFFF
+            if word != FAULT_CLEAN:
+                self.poisoned = word
+                raise EngineFault(word)
+            return out[:len(rows)]
+
+    def prefill(self, slot: int, tokens: Sequence[int], start: int = 0) -> int:
+        """Feed a prompt through passes of up to 8 rows; returns the greedy token after it."""
+        last = None
+        n = len(tokens)
+        i = 0
+        while i < n:
+            chunk = tokens[i:i + MAX_ROWS]
+            is_last = i + len(chunk) >= n
+            rows = [(slot, int(t), start + i + j) for j, t in enumerate(chunk)]
+            out = self.step(rows, head=is_last)
+            if is_last:
+                last = out[len(chunk) - 1]
+            i += len(chunk)
+        return last
+
+    def score(self, slot: int, tokens: Sequence[int], start: int = 0) -> List[int]:
+        """Greedy pick after every position of ``tokens`` (teacher forcing; the head runs on each pass)."""
+        picks: List[int] = []
+        for i in range(0, len(tokens), MAX_ROWS):
+            chunk = tokens[i:i + MAX_ROWS]
+            picks += self.step([(slot, int(t), start + i + j) for j, t in enumerate(chunk)], head=True)
+        return picks
+
+    def decode_chain(self, slot: int, first_token: int, start_pos: int, n_steps: int) -> List[int]:
+        """Greedy decode of ``n_steps`` tokens with the next step's input kept on the card:
+        the graph ends in a kernel that feeds the pick back and advances the position, so
+        replays are launched back to back and read once (``step_ahead`` in the reference)."""
+        self.kv.ensure(slot, start_pos + n_steps + 1)
+        with self._lock:
+            if n_steps > self.hist_cap:
+                raise ValueError(f"a chain of {n_steps} steps exceeds the history ring of {self.hist_cap}")
+            self.set_rows([(slot, first_token, start_pos)])
+            self.counters[2:3].zero_()
+            for i in range(n_steps):
+                self.launch(1, True, True)
+            out = self.hist[:n_steps].cpu().tolist()
+            self.slot_len[slot] = start_pos + n_steps
+            self.check_fault()
+            return out
+
+    def check_fault(self) -> None:
+        word = int(self.fault.cpu().item()) & 0xFFFFFFFF
+        if word != FAULT_CLEAN:
+            self.poisoned = word
+            raise EngineFault(word)
+
+    def reset_fault(self) -> None:
+        self.fault.fill_(-1)
+        self.counters.zero_()
+        self.poisoned = None
+
+    def plant_fault(self, layer: int, site: int) -> None:
+        """Host-side injection used by tests (``GpuModel::plant_fault`` in the reference)."""
+        self.fault.fill_(((layer << 8) | site) - (1 << 32))
+
+    # slot management --------------------------------------------------------------------
+    def cut(self, slot: int, n_positions: int) -> None:
+        self.kv.truncate(slot, n_positions)
+        self.slot_len[slot] = min(self.slot_len[slot], n_positions)
+
+    def reset(self, slot: int) -> None:
+        self.cut(slot, 0)
+
+    def memory_report(self) -> Dict[str, int]:
+        return {"weights": self.w.n_bytes, "kv": self.kv.bytes}

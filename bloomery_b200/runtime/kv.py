@@ -1,0 +1,133 @@
+"""Paged KV pool: fixed-size pages of 64 positions, per-slot block tables, prefix sharing.
+
+The reference reserves each slot's whole context as a virtual range and backs pages
+lazily (``crates/gpu/src/room/mod.rs:1-52``, ``room/kv.rs:1-8``) and shares a prefix
+between slots copy-on-write (``Room::share``, ``room/mod.rs:22-31``).  Here the same
+capabilities sit on a block table that the kernels read from device memory: pages are
+handed out on demand, a shared prefix is a run of page ids present in two tables with
+a reference count, and a slot that appends into a shared page first takes its own copy.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+PAGE = 64
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class KvPool:
+    def __init__(self, n_layer: int, n_kv: int, head_dim: int, n_pages: int, n_slots: int, max_pages_per_slot: int,
+                 device, dtype=torch.float16):
+        self.n_layer, self.n_kv, self.head_dim = n_layer, n_kv, head_dim
+        self.n_pages, self.n_slots, self.max_pages = n_pages, n_slots, max_pages_per_slot
+        self.device = torch.device(device)
+        # [layer][page][kv head][position in page][dim]
+        self.k = torch.zeros(n_layer, n_pages, n_kv, PAGE, head_dim, dtype=dtype, device=self.device)
+        self.v = torch.zeros(n_layer, n_pages, n_kv, PAGE, head_dim, dtype=dtype, device=self.device)
+        self.table_host = torch.full((n_slots, max_pages_per_slot), -1, dtype=torch.int32,
+                                     pin_memory=self.device.type == "cuda")
+        self.table = torch.full((n_slots, max_pages_per_slot), -1, dtype=torch.int32, device=self.device)
+        self.free: List[int] = list(range(n_pages - 1, -1, -1))
+        self.refs: List[int] = [0] * n_pages
+        self.pages: List[List[int]] = [[] for _ in range(n_slots)]
+        self.dirty = False
+
+    @property
+    def bytes(self) -> int:
+        return 2 * self.k.numel() * self.k.element_size()
+
+    def free_pages(self) -> int:
+        return len(self.free)
+
+    def _take(self) -> int:
+        if not self.free:
+            raise OutOfPages("KV pool exhausted")
+        pg = self.free.pop()
+        self.refs[pg] = 1
+        return pg
+
+    def _drop(self, pg: int) -> None:
+        self.refs[pg] -= 1
+        if self.refs[pg] == 0:
+            self.free.append(pg)
+
+    def ensure(self, slot: int, n_positions: int) -> None:
+        """Back positions [0, n_positions) of a slot with pages."""
+        need = (n_positions + PAGE - 1) // PAGE
+        if need > self.max_pages:
+            raise OutOfPages(f"slot {slot}: {n_positions} positions exceed the slot context")
+        pl = self.pages[slot]
+        while len(pl) < need:
+            pg = self._take()
+            self.table_host[slot, len(pl)] = pg
+            pl.append(pg)
+            self.dirty = True
+
+    def own(self, slot: int, position: int) -> None:
+        """Copy-on-write: make the page holding ``position`` private before it is written."""
+        i = position // PAGE
+        pl = self.pages[slot]
+        if i < len(pl) and self.refs[pl[i]] > 1:
+            new = self._take()
+            self.k[:, new].copy_(self.k[:, pl[i]])
+            self.v[:, new].copy_(self.v[:, pl[i]])
+            self._drop(pl[i])
+            pl[i] = new
+            self.table_host[slot, i] = new
+            self.dirty = True
+
+    def truncate(self, slot: int, n_positions: int) -> None:
+        """Keep positions [0, n_positions); later pages go back to the pool (``cut``)."""
+        keep = (n_positions + PAGE - 1) // PAGE
+        pl = self.pages[slot]
+        while len(pl) > keep:
+            self._drop(pl.pop())
+            self.table_host[slot, len(pl)] = -1
+            self.dirty = True
+
+    def release(self, slot: int) -> None:
+        self.truncate(slot, 0)
+
+    def share_prefix(self, src: int, dst: int, n_positions: int) -> int:
+        """Map the whole pages of ``src`` covering [0, n_positions) into ``dst``; returns positions shared."""
+        self.release(dst)
+        full = min(n_positions // PAGE, len(self.pages[src]))
+        for i in range(full):
+            pg = self.pages[src][i]
+            self.refs[pg] += 1
+            self.pages[dst].append(pg)
+            self.table_host[dst, i] = pg
+        self.dirty = True
+        return full * PAGE
+
+    def sync_table(self) -> None:
+        """Push the host table to the device if it changed (small copy, outside any capture)."""
+        if self.dirty:
+            self.table.copy_(self.table_host, non_blocking=True)
+            self.dirty = False
+
+    # snapshots for the host prompt cache -------------------------------------------------
+    def snapshot(self, slot: int, n_positions: int, stream: Optional[torch.cuda.Stream] = None) -> Dict[str, torch.Tensor]:
+        """Copy a slot's first ``n_positions`` K/V rows to pinned host memory."""
+        n_pg = (n_positions + PAGE - 1) // PAGE
+        idx = torch.tensor(self.pages[slot][:n_pg], dtype=torch.long, device=self.device)
+        pin = self.device.type == "cuda"
+        k = torch.empty((self.n_layer, n_pg, self.n_kv, PAGE, self.head_dim), dtype=self.k.dtype, pin_memory=pin)
+        v = torch.empty_like(k, pin_memory=pin)
+        k.copy_(self.k.index_select(1, idx), non_blocking=True)
+        v.copy_(self.v.index_select(1, idx), non_blocking=True)
+        return {"k": k, "v": v, "n": torch.tensor(n_positions)}
+
+    def restore(self, slot: int, snap: Dict[str, torch.Tensor], n_positions: int) -> None:
+        n_positions = min(n_positions, int(snap["n"]))
+        self.release(slot)
+        self.ensure(slot, n_positions)
+        n_pg = (n_positions + PAGE - 1) // PAGE
+        idx = torch.tensor(self.pages[slot][:n_pg], dtype=torch.long, device=self.device)
+        self.k.index_copy_(1, idx, snap["k"][:, :n_pg].to(self.device, non_blocking=True))
+        self.v.index_copy_(1, idx, snap["v"][:, :n_pg].to(self.device, non_blocking=True))

@@ -1,0 +1,152 @@
+"""Block formats, GGUF reader/writer, resident layouts and the CPU quantised dots."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from bloomery_b200.formats import quant as Q
+from bloomery_b200.formats.gguf import Gguf, GgufError, GgufWriter, split_paths
+from bloomery_b200.formats.resident import from_resident, resident_row_bytes, to_resident
+from bloomery_b200.ops import host_ops as H
+
+ALL = list(Q.QUANTIZE)
+BAND = {"F32": 1e-7, "F16": 1e-3, "BF16": 8e-3, "Q8_0": 8e-3, "Q6_K": 3e-2, "Q5_K": 5e-2, "Q5_1": 5e-2, "Q5_0": 8e-2,
+        "Q4_K": 1e-1, "Q4_1": 1e-1, "Q4_0": 1.5e-1, "Q3_K": 3e-1, "Q2_K": 5e-1}
+
+
+@pytest.mark.parametrize("t", ALL)
+def test_roundtrip_band(t):
+    torch.manual_seed(0)
+    w = torch.randn(8, 1024) * 0.02
+    b = Q.quantize(w, t)
+    assert b.shape == (8, Q.QTYPES[t].row_bytes(1024))
+    y = Q.dequantize(b, t, 1024)
+    assert ((y - w).abs().max() / w.abs().max()).item() < BAND[t]
+
+
+@pytest.mark.parametrize("t", ALL)
+def test_requantize_is_stable(t):
+    """Decoding then re-encoding decoded values reproduces the same decoded values (a valid encoding)."""
+    torch.manual_seed(1)
+    w = torch.randn(4, 512) * 0.05
+    y = Q.dequantize(Q.quantize(w, t), t, 512)
+    y2 = Q.dequantize(Q.quantize(y, t), t, 512)
+    assert ((y2 - y).abs().max() / y.abs().max()).item() < BAND[t]
+
+
+def test_scale_min_pack_roundtrip():
+    sc = torch.randint(0, 64, (5, 8), dtype=torch.uint8)
+    mn = torch.randint(0, 64, (5, 8), dtype=torch.uint8)
+    s2, m2 = Q.unpack_scale_min_k4(Q.pack_scale_min_k4(sc, mn))
+    assert torch.equal(sc, s2) and torch.equal(mn, m2)
+
+
+def test_q4k_known_block():
+    """A hand-built block decodes by the format's rule: y = d*sc*q - dmin*m."""
+    blk = np.zeros(144, np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(0.5).tobytes(), np.uint8)
+    blk[2:4] = np.frombuffer(np.float16(0.25).tobytes(), np.uint8)
+    sc = torch.tensor([[1, 2, 3, 4, 5, 6, 7, 40]], dtype=torch.uint8)
+    mn = torch.tensor([[0, 1, 2, 3, 4, 5, 6, 33]], dtype=torch.uint8)
+    blk[4:16] = Q.pack_scale_min_k4(sc, mn)[0].numpy()
+    blk[16:] = 0x21  # low nibble 1, high nibble 2
+    y = Q.dequantize(torch.from_numpy(blk)[None], "Q4_K", 256)[0]
+    for sub in range(8):
+        q = 1 if sub % 2 == 0 else 2
+        want = 0.5 * int(sc[0, sub]) * q - 0.25 * int(mn[0, sub])
+        assert torch.allclose(y[32 * sub:32 * sub + 32], torch.full((32,), want))
+
+
+def test_gguf_write_read(tmp_path):
+    torch.manual_seed(2)
+    w = GgufWriter("qwen3moe")
+    w.set("qwen3moe.block_count", 2)
+    w.set("general.name", "fixture")
+    w.set("tokenizer.ggml.tokens", ["a", "b", "c"])
+    w.set("some.floats", [0.5, 1.5])
+    a = torch.randn(6, 256)
+    e = torch.randn(3, 4, 256)
+    w.add_quantized("a.weight", a, "Q4_K")
+    w.add_quantized("e.weight", e, "Q6_K")
+    w.add_f32("n.weight", torch.ones(256))
+    path = str(tmp_path / "m.gguf")
+    w.write(path)
+    with Gguf.open(path) as g:
+        assert g.arch == "qwen3moe" and g.arch_get("block_count") == 2
+        assert g.get("tokenizer.ggml.tokens") == ["a", "b", "c"]
+        assert g.tensors["a.weight"].shape == (6, 256) and g.tensors["a.weight"].ne == (256, 6)
+        assert g.tensors["e.weight"].shape == (3, 4, 256)
+        assert torch.equal(g.tensor_rows("a.weight").clone(), Q.quantize(a, "Q4_K"))
+        assert torch.allclose(g.tensor_f32("n.weight"), torch.ones(256))
+        assert g.tensor_f32("e.weight").shape == (3, 4, 256)
+        assert len(g.sha256("a.weight")) == 64
+    inv = Gguf.inventory(path)
+    assert set(inv.tensors) == {"a.weight", "e.weight", "n.weight"}
+    inv.close()
+
+
+def test_gguf_refuses_bad_files(tmp_path):
+    p = tmp_path / "bad.gguf"
+    p.write_bytes(b"NOPE" + b"\0" * 64)
+    with pytest.raises(GgufError, match="magic"):
+        Gguf.open(str(p))
+    p.write_bytes(b"GGUF")
+    with pytest.raises(GgufError, match="too short"):
+        Gguf.open(str(p))
+
+
+def test_gguf_truncated_data_is_refused(tmp_path):
+    w = GgufWriter("llama")
+    w.add_quantized("a.weight", torch.randn(4, 256), "Q8_0")
+    path = str(tmp_path / "t.gguf")
+    w.write(path)
+    data = open(path, "rb").read()
+    open(path, "wb").write(data[:-40])
+    with pytest.raises(GgufError, match="past the end"):
+        Gguf.open(path)
+    Gguf.inventory(path).close()  # header-only open still lists it
+
+
+def test_split_paths():
+    assert split_paths("/x/m-00002-of-00003.gguf") == [f"/x/m-0000{i}-of-00003.gguf" for i in (1, 2, 3)]
+    assert split_paths("/x/m.gguf") == ["/x/m.gguf"]
+
+
+def test_gguf_split_shards(tmp_path):
+    for i, name in ((1, "a.weight"), (2, "b.weight")):
+        w = GgufWriter("llama")
+        w.set("split.count", 2)
+        w.add_quantized(name, torch.randn(2, 256), "Q4_K")
+        w.write(str(tmp_path / f"m-0000{i}-of-00002.gguf"))
+    with Gguf.open(str(tmp_path / "m-00001-of-00002.gguf")) as g:
+        assert set(g.tensors) == {"a.weight", "b.weight"}
+        assert g.tensors["b.weight"].shard == 1
+        assert g.tensor_f32("b.weight").shape == (2, 256)
+
+
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0"])
+def test_resident_roundtrip_and_host_units(t):
+    torch.manual_seed(3)
+    K = 1024
+    w = torch.randn(24, K) * 0.02
+    raw = Q.quantize(w, t)
+    res = to_resident(raw, t, K)
+    assert res.shape[1] == resident_row_bytes(t, K) and res.shape[1] % 16 == 0
+    assert torch.equal(from_resident(res, t, K), raw)
+    wd = Q.dequantize(raw, t, K)
+    assert torch.equal(H.decode_rows(res, t, K), wd)            # unit decode is exact
+    x = torch.randn(3, K)
+    x[1, 5] = 40.0                                             # an outlier, as the reference's kernel gates use
+    codes, ds = H.act_q8(x)
+    c2, ds2 = Q.quantize_act_q8(x)
+    assert torch.equal(codes, c2) and torch.allclose(ds, ds2, rtol=1e-6, atol=0)
+    xa = Q.dequantize_act_q8(codes, ds)
+    ref = (xa.double() @ wd.double().T).float()                 # f64 dot on the same quantised activations
+    out = H.gemv(res, t, K, codes, ds)
+    assert ((out - ref).abs().max() / ref.abs().max()).item() < 1e-5
+    assert torch.equal(out, H.gemv(res, t, K, codes, ds))       # bit-identical rerun
+
+
+def test_host_pool():
+    assert H.pool_size() >= 1
