@@ -77,7 +77,12 @@ class DecodeEngine:
         # step parameters: tokens, positions, slot of each row (one H2D copy)
         self.params = torch.zeros(3, R, **i32)
         self.params[2].fill_(-1)
-        self.params_host = torch.zeros(3, R, dtype=torch.int32, pin_memory=True)
+        # pinned staging ring: a slot is rewritten only after the copy that read it has run
+        self._stage_n = 16
+        self._stage = [torch.zeros(3, R, dtype=torch.int32, pin_memory=True) for _ in range(self._stage_n)]
+        self._stage_ev = [None] * self._stage_n
+        self._stage_i = 0
+        self.params_host = self._stage[0]
         self.tokens, self.row_pos, self.row_seq = self.params[0], self.params[1], self.params[2]
         self.x = torch.zeros(R, H, **f32)
         qkv_w = s.q_rows + 2 * s.kv_rows
@@ -198,7 +203,11 @@ class DecodeEngine:
         """rows = [(slot, token, position)]; pads to the bucket; returns the bucket size."""
         m = len(rows)
         M = bucket_of(m)
-        ph = self.params_host
+        i = self._stage_i
+        self._stage_i = (i + 1) % self._stage_n
+        if self._stage_ev[i] is not None:
+            self._stage_ev[i].synchronize()
+        ph = self.params_host = self._stage[i]
         ph[2].fill_(-1)
         for i, (slot, tok, pos) in enumerate(rows):
             ph[0, i], ph[1, i], ph[2, i] = tok, pos, slot
@@ -206,6 +215,9 @@ class DecodeEngine:
             self.kv.own(slot, pos)
         self.kv.sync_table()
         self.params.copy_(ph, non_blocking=True)
+        ev = self._stage_ev[i] or torch.cuda.Event()
+        ev.record()
+        self._stage_ev[i] = ev
         return M
 
     def launch(self, M: int, head: bool = True, advance: bool = False) -> None:

@@ -108,7 +108,12 @@ class KvPool:
     def sync_table(self) -> None:
         """Push the host table to the device if it changed (small copy, outside any capture)."""
         if self.dirty:
-            self.table.copy_(self.table_host, non_blocking=True)
+            if self.device.type == "cuda":
+                # snapshot first: the host keeps editing table_host while the copy is in flight
+                snap = torch.empty_like(self.table_host, pin_memory=True).copy_(self.table_host)
+                self.table.copy_(snap, non_blocking=True)
+            else:
+                self.table.copy_(self.table_host)
             self.dirty = False
 
     # snapshots for the host prompt cache -------------------------------------------------
