@@ -1,18 +1,23 @@
 // Quantised GEMV for the decode chain (m <= 8 activation rows), weights dequantised
 // in registers and dotted with dp4a against q8 activations.
 //
-// One launch covers up to four weight segments that share an input (q, k, v
-// projections; or one matrix), each with its own block type.  A warp owns one weight
-// row at a time and loops over row groups (persistent grid sized to the SM count), so
-// the RMSNorm + q8 prologue runs once per block, not once per 8 rows.
+// Decode at one row is latency-bound, not bandwidth-bound, so the kernel is shaped to
+// keep one DRAM round trip on the critical path:
+//   * a warp owns R weight rows at a time and issues every load of its first tile into
+//     registers BEFORE griddepcontrol.wait and before the activation prologue, so under
+//     programmatic dependent launch the weight stream of kernel N+1 overlaps the tail
+//     of kernel N and its own RMSNorm prologue;
+//   * the prologue needs no second pass: q8 codes of x*gain do not depend on the RMS
+//     scale (it is a per-row scalar), so sum-of-squares and quantisation run in one
+//     sweep and the scale multiplies the finished dot products;
+//   * blocks are type-uniform (a tile of 8*R rows never straddles two weight segments),
+//     which keeps block-wide barriers out of divergent code.
+// One launch covers up to four weight segments that share an input (q, k, v).
 //
-// Blackwell specifics: the first row group of every block is pulled into L2 with a
-// bulk prefetch (cp.async.bulk.prefetch.L2) *before* griddepcontrol.wait, so under
-// programmatic dependent launch the weight stream of kernel N+1 overlaps the tail of
-// kernel N.  Behavioural counterpart of q4k_gemv/q6k_gemv(_mcol) in
-// crates/gpu/src/lib.rs:1604-1632 and qwen3moe_qkv_q4k / qwen3moe_o_resid_q4k in
-// crates/gpu/src/arch/qwen3moe/proj.rs: fixed lane split and a fixed xor-butterfly, so
-// reruns are bit-identical and each row of an m-row call equals its own 1-row call.
+// Behavioural counterpart of q4k_gemv/q6k_gemv(_mcol) in crates/gpu/src/lib.rs:1604-1632
+// and qwen3moe_qkv_q4k / qwen3moe_o_resid_q4k in crates/gpu/src/arch/qwen3moe/proj.rs:
+// fixed lane split and a fixed xor-butterfly, so reruns are bit-identical and each row of
+// an m-row call equals its own 1-row call.
 #include "common.cuh"
 
 namespace bl {
@@ -23,216 +28,304 @@ struct GemvSeg {
   const uint8_t* w;
   int rows;
   int wtype;
+  int blk0;        // first block of this segment
+  int nblk;        // blocks that share this segment's rows evenly
   long row_bytes;
 };
 
 struct GemvArgs {
   GemvSeg seg[4];
   int nseg;
-  int total_groups;  // sum over segments of ceil(rows / 8)
   int K;
   int M;
-  // input A: fp32 rows to be RMS-normalised and quantised in the prologue
-  const float* x;
+  const float* x;          // input A: fp32 rows, RMS-normalised and quantised in the prologue
   long x_stride;
   const float* gain;
   float eps;
-  // input B: rows already in q8 form
-  const int8_t* xq;
+  const int8_t* xq;        // input B: rows already in q8 form
   const float2* xds;
-  // outputs
   float* out;
   long out_stride;
-  const float* resid;  // optional, same layout as out
+  const float* resid;
   long resid_stride;
-  int8_t* xq_out;      // optional: block 0 publishes the prologue's q8 rows
-  float2* xds_out;
   unsigned* fault;
   int layer;
 };
 
-__device__ __forceinline__ void l2_prefetch_bulk(const void* p, unsigned bytes) {
-  // bytes must be a multiple of 16 and p 16-byte aligned
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-template <class T, int MB>
-__device__ __forceinline__ void row_dot(const uint8_t* row, int K, int lane, const int8_t* sq, const float2* sds,
-                                        float (&acc)[MB]) {
-  using U = Unit<T>;
-  const int nunits = K / 64;
+// ---- activation prologue ------------------------------------------------------------
+// sq/sds receive q8(x * gain) WITHOUT the RMS scale; s_scale[m] receives the scale.
+template <int MB, bool FLOATW>
+__device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, float2* sds, float* sx, float* s_scale,
+                                              double* red) {
+  const int K = a.K, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#pragma unroll 1
+  for (int m = 0; m < MB; ++m) {
+    const int ms = m < a.M ? m : a.M - 1;
+    const float* x = a.x + (long)ms * a.x_stride;
+    float ss = 0.f;
+    for (int i0 = tid * 8; i0 < K; i0 += 256 * 8) {
+      float4 x0 = *reinterpret_cast<const float4*>(x + i0), x1 = *reinterpret_cast<const float4*>(x + i0 + 4);
+      float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gain + i0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gain + i0 + 4));
+      float v[8] = {x0.x * g0.x, x0.y * g0.y, x0.z * g0.z, x0.w * g0.w, x1.x * g1.x, x1.y * g1.y, x1.z * g1.z, x1.w * g1.w};
+      ss += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
+      float amax = 0.f;
 #pragma unroll
-  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
-  for (int u = lane; u < nunits; u += 32) {
-    typename U::Regs r;
-    U::loadu(row, u, K, r);
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const float d = amax / 127.0f, inv = d > 0.f ? 1.0f / d : 0.f;
+      int q[8], sum = 0;
 #pragma unroll
-    for (int m = 0; m < MB; ++m) {
-      acc[m] += U::dotu(r, u, reinterpret_cast<const uint32_t*>(sq + (long)m * K),
-                        reinterpret_cast<const F2*>(sds + (long)m * (K / 32)));
+      for (int j = 0; j < 8; ++j) { q[j] = max(-127, min(127, __float2int_rn(v[j] * inv))); sum += q[j]; }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      uint2 packed;
+      packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((unsigned)(q[3] & 0xFF) << 24);
+      packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((unsigned)(q[7] & 0xFF) << 24);
+      *reinterpret_cast<uint2*>(sq + (long)m * K + i0) = packed;
+      if ((tid & 3) == 0) sds[(long)m * (K / 32) + i0 / 32] = make_float2(d, d * (float)sum);
+      if (FLOATW) {
+        *reinterpret_cast<float4*>(sx + (long)m * K + i0) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(sx + (long)m * K + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
     }
+    double tot = warp_sum_d((double)ss);
+    if (lane == 0) red[m * 8 + warp] = tot;
   }
+  __syncthreads();
+  if (tid < MB) {
+    double all = 0.0;
 #pragma unroll
-  for (int m = 0; m < MB; ++m) acc[m] = warp_sum(acc[m]);
+    for (int w = 0; w < 8; ++w) all += red[tid * 8 + w];
+    s_scale[tid] = 1.0f / sqrtf((float)(all / (double)K) + a.eps);
+  }
+  __syncthreads();
 }
 
 template <int MB>
-__device__ __forceinline__ void row_dot_float(const uint8_t* row, int wtype, int K, int lane, const float* sx,
-                                              float (&acc)[MB]) {
-#pragma unroll
-  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
-  for (int i = lane * 4; i < K; i += 128) {
-    float w0, w1, w2, w3;
-    if (wtype == WT_F32) {
-      float4 v = __ldg(reinterpret_cast<const float4*>(row) + i / 4);
-      w0 = v.x; w1 = v.y; w2 = v.z; w3 = v.w;
-    } else if (wtype == WT_F16) {
-      uint2 v = __ldg(reinterpret_cast<const uint2*>(row) + i / 4);
-      float2 a = __half22float2(*reinterpret_cast<__half2*>(&v.x));
-      float2 b = __half22float2(*reinterpret_cast<__half2*>(&v.y));
-      w0 = a.x; w1 = a.y; w2 = b.x; w3 = b.y;
-    } else {
-      uint2 v = __ldg(reinterpret_cast<const uint2*>(row) + i / 4);
-      float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v.x));
-      float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v.y));
-      w0 = a.x; w1 = a.y; w2 = b.x; w3 = b.y;
-    }
-#pragma unroll
-    for (int m = 0; m < MB; ++m) {
-      const float4 xv = *reinterpret_cast<const float4*>(sx + (long)m * K + i);
-      acc[m] = fmaf(w0, xv.x, fmaf(w1, xv.y, fmaf(w2, xv.z, fmaf(w3, xv.w, acc[m]))));
-    }
+__device__ __forceinline__ void prologue_q8in(const GemvArgs& a, int8_t* sq, float2* sds, float* s_scale) {
+  const int K = a.K, tid = threadIdx.x;
+  for (int i = tid; i < MB * K / 16; i += 256) {
+    int m = (i * 16) / K;
+    const int ms = m < a.M ? m : a.M - 1;
+    reinterpret_cast<uint4*>(sq)[i] = reinterpret_cast<const uint4*>(a.xq + (long)ms * K)[i - m * (K / 16)];
   }
-#pragma unroll
-  for (int m = 0; m < MB; ++m) acc[m] = warp_sum(acc[m]);
+  for (int i = tid; i < MB * (K / 32); i += 256) {
+    int m = i / (K / 32);
+    const int ms = m < a.M ? m : a.M - 1;
+    sds[i] = a.xds[(long)ms * (K / 32) + (i - m * (K / 32))];
+  }
+  if (tid < MB) s_scale[tid] = 1.0f;
+  __syncthreads();
 }
 
-// NORM: input A (fp32 + RMSNorm prologue); otherwise input B (q8 rows copied to smem).
-// FLOATW: some segment holds F32/F16/BF16 rows, so normalised fp32 rows are kept too.
-template <int MB, bool NORM, bool FLOATW>
-__global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
+// ---- the rows of one warp ---------------------------------------------------------------
+// A warp owns rows [r_lo, r_hi) of its segment and walks them R at a time; every load of a
+// chunk is issued before anything is computed.  C = units per lane per inner step.
+// `between` runs once per block, after the very first loads are in flight.
+template <class T, int MB, int R, int C, class Between>
+__device__ __forceinline__ void rows_q(const GemvArgs& a, const GemvSeg& s, int r_lo, int r_hi, int out_col0,
+                                       const int8_t* sq, const float2* sds, const float* s_scale, Between&& between) {
+  using U = Unit<T>;
+  const int K = a.K, lane = threadIdx.x & 31;
+  const int nunits = K / 64;
+  for (int r0 = r_lo; r0 < r_hi || r0 == r_lo; r0 += R) {
+    float acc[R][MB];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
+    for (int base = 0; base < nunits; base += 32 * C) {
+      typename U::Regs regs[R][C];
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const int u = base + c * 32 + lane;
+          // rows past the end re-read the segment's last row (their result is dropped)
+          const int rr = min(r0 + r, s.rows - 1);
+          if (u < nunits) U::loadu(s.w + (long)rr * s.row_bytes, u, K, regs[r][c]);
+        }
+      between();
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const int u = base + c * 32 + lane;
+        if (u < nunits) {
+#pragma unroll
+          for (int m = 0; m < MB; ++m) {
+            const uint32_t* xq = reinterpret_cast<const uint32_t*>(sq + (long)m * K);
+            const F2* xds = reinterpret_cast<const F2*>(sds + (long)m * (K / 32));
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r][m] += U::dotu(regs[r][c], u, xq, xds);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < MB; ++m) acc[r][m] = warp_sum(acc[r][m]);
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (r0 + r < r_hi) {
+          const int col = out_col0 + r0 + r;
+#pragma unroll
+          for (int m = 0; m < MB; ++m)
+            if (m < a.M) {
+              float v = acc[r][m] * s_scale[m];
+              if (a.resid) v += a.resid[(long)m * a.resid_stride + col];
+              a.out[(long)m * a.out_stride + col] = v;
+            }
+        }
+      }
+    }
+    if (r0 + R >= r_hi) break;
+  }
+}
+
+// float weights (F32 / F16 / BF16) against fp32 x*gain rows
+template <int MB, int R, class Between>
+__device__ __forceinline__ void rows_f(const GemvArgs& a, const GemvSeg& s, int r_lo, int r_hi, int out_col0,
+                                       const float* sx, const float* s_scale, Between&& between) {
+  const int K = a.K, lane = threadIdx.x & 31;
+  for (int r0 = r_lo; r0 < r_hi || r0 == r_lo; r0 += R) {
+    float acc[R][MB];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
+    for (int i = lane * 8; i < K; i += 256) {
+      float wv[R][8];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const uint8_t* row = s.w + (long)min(r0 + r, s.rows - 1) * s.row_bytes;
+        if (s.wtype == WT_F32) {
+          float4 p = __ldg(reinterpret_cast<const float4*>(row) + i / 4), q = __ldg(reinterpret_cast<const float4*>(row) + i / 4 + 1);
+          wv[r][0] = p.x; wv[r][1] = p.y; wv[r][2] = p.z; wv[r][3] = p.w; wv[r][4] = q.x; wv[r][5] = q.y; wv[r][6] = q.z; wv[r][7] = q.w;
+        } else {
+          uint4 p = __ldg(reinterpret_cast<const uint4*>(row) + i / 8);
+          const uint32_t ws[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = (s.wtype == WT_F16) ? __half22float2(*reinterpret_cast<const __half2*>(&ws[j]))
+                                           : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ws[j]));
+            wv[r][2 * j] = f.x; wv[r][2 * j + 1] = f.y;
+          }
+        }
+      }
+      between();
+#pragma unroll
+      for (int m = 0; m < MB; ++m) {
+        const float4 x0 = *reinterpret_cast<const float4*>(sx + (long)m * K + i);
+        const float4 x1 = *reinterpret_cast<const float4*>(sx + (long)m * K + i + 4);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float t = acc[r][m];
+          t = fmaf(wv[r][0], x0.x, t); t = fmaf(wv[r][1], x0.y, t); t = fmaf(wv[r][2], x0.z, t); t = fmaf(wv[r][3], x0.w, t);
+          t = fmaf(wv[r][4], x1.x, t); t = fmaf(wv[r][5], x1.y, t); t = fmaf(wv[r][6], x1.z, t); t = fmaf(wv[r][7], x1.w, t);
+          acc[r][m] = t;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < MB; ++m) acc[r][m] = warp_sum(acc[r][m]);
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        if (r0 + r < r_hi) {
+          const int col = out_col0 + r0 + r;
+#pragma unroll
+          for (int m = 0; m < MB; ++m)
+            if (m < a.M) {
+              float v = acc[r][m] * s_scale[m];
+              if (a.resid) v += a.resid[(long)m * a.resid_stride + col];
+              a.out[(long)m * a.out_stride + col] = v;
+            }
+        }
+    }
+    if (r0 + R >= r_hi) break;
+  }
+}
+
+template <int MB, int R, int C, bool NORM, bool FLOATW>
+__global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int K = a.K;
   int8_t* sq = reinterpret_cast<int8_t*>(smem);
   float2* sds = reinterpret_cast<float2*>(smem + (size_t)MB * K);
-  float* red = reinterpret_cast<float*>(sds + (size_t)MB * (K / 32));
-  float* sx = red + 64;  // only when FLOATW
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  double* red = reinterpret_cast<double*>(sds + (size_t)MB * (K / 32));
+  float* s_scale = reinterpret_cast<float*>(red + MB * 8);
+  float* sx = s_scale + 8;  // only when FLOATW
 
-  // Which row does this warp own in row group g?  Groups are laid out per segment.
-  auto locate = [&](int g, int& s, int& row) {
-    int gs = 0;
-    s = 0;
-#pragma unroll 1
-    for (; s < a.nseg; ++s) {
-      int ng = (a.seg[s].rows + 7) >> 3;
-      if (g < gs + ng) break;
-      gs += ng;
+  bool ready = false;
+  auto between = [&]() {
+    if (!ready) {
+      pdl_wait();
+      if (NORM) prologue_norm<MB, FLOATW>(a, sq, sds, sx, s_scale, red);
+      else prologue_q8in<MB>(a, sq, sds, s_scale);
+      pdl_launch();
+      ready = true;
     }
-    row = (g - gs) * 8 + warp;
   };
-
-  // weights do not depend on the predecessor: start them towards L2 now
-  for (int g = blockIdx.x, it = 0; g < a.total_groups && it < 2; g += gridDim.x, ++it) {
-    int s, row;
-    locate(g, s, row);
-    if (s < a.nseg && row < a.seg[s].rows && lane == 0 && (a.seg[s].row_bytes & 15) == 0)
-      l2_prefetch_bulk(a.seg[s].w + (long)row * a.seg[s].row_bytes, (unsigned)a.seg[s].row_bytes);
-  }
-  pdl_wait();
-
-  if (NORM) {
-#pragma unroll 1
-    for (int m = 0; m < MB; ++m) {
-      const int ms = m < a.M ? m : a.M - 1;
-      block_rmsnorm_q8(a.x + (long)ms * a.x_stride, a.gain, K, a.eps, sq + (long)m * K, sds + (long)m * (K / 32), red,
-                       FLOATW ? sx + (long)m * K : nullptr);
-    }
-    if (a.xq_out && blockIdx.x == 0) {
-      for (int i = tid; i < a.M * K / 16; i += 256)
-        reinterpret_cast<uint4*>(a.xq_out)[i] = reinterpret_cast<const uint4*>(sq)[i];
-      for (int i = tid; i < a.M * (K / 32); i += 256) a.xds_out[i] = sds[i];
-    }
-  } else {
-    for (int i = tid; i < MB * K / 16; i += 256) {
-      int m = (i * 16) / K;
-      const int ms = m < a.M ? m : a.M - 1;
-      reinterpret_cast<uint4*>(sq)[i] =
-          reinterpret_cast<const uint4*>(a.xq + (long)ms * K)[i - m * (K / 16)];
-    }
-    for (int i = tid; i < MB * (K / 32); i += 256) {
-      int m = i / (K / 32);
-      const int ms = m < a.M ? m : a.M - 1;
-      sds[i] = a.xds[(long)ms * (K / 32) + (i - m * (K / 32))];
-    }
-    __syncthreads();
-  }
-  pdl_launch();
-
-  int out_base[4];
   {
-    int o = 0;
-    for (int s = 0; s < 4; ++s) { out_base[s] = o; if (s < a.nseg) o += a.seg[s].rows; }
-  }
-
-#pragma unroll 1
-  for (int g = blockIdx.x; g < a.total_groups; g += gridDim.x) {
-    int s, row;
-    locate(g, s, row);
-    if (s >= a.nseg || row >= a.seg[s].rows) continue;
-    const uint8_t* wrow = a.seg[s].w + (long)row * a.seg[s].row_bytes;
-    float acc[MB];
-    switch (a.seg[s].wtype) {
-      case WT_Q4_K: row_dot<Q4K, MB>(wrow, K, lane, sq, sds, acc); break;
-      case WT_Q6_K: row_dot<Q6K, MB>(wrow, K, lane, sq, sds, acc); break;
-      case WT_Q5_K: row_dot<Q5K, MB>(wrow, K, lane, sq, sds, acc); break;
-      case WT_Q8_0: row_dot<Q80, MB>(wrow, K, lane, sq, sds, acc); break;
+    int si = 0, col0 = 0;
+#pragma unroll
+    for (int q = 1; q < 4; ++q)
+      if (q < a.nseg && (int)blockIdx.x >= a.seg[q].blk0) { si = q; }
+    for (int q = 0; q < si; ++q) col0 += a.seg[q].rows;
+    const GemvSeg& s = a.seg[si];
+    // even split of the segment's rows over its warps
+    const int W = s.nblk * 8, wg = ((int)blockIdx.x - s.blk0) * 8 + (threadIdx.x >> 5);
+    const int rpw = (s.rows + W - 1) / W;
+    const int r_lo = min(s.rows, wg * rpw), r_hi = min(s.rows, r_lo + rpw);
+    switch (s.wtype) {
+      case WT_Q4_K: rows_q<Q4K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+      case WT_Q6_K: rows_q<Q6K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+      case WT_Q5_K: rows_q<Q5K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+      case WT_Q8_0: rows_q<Q80, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
       default:
-        if (FLOATW) row_dot_float<MB>(wrow, a.seg[s].wtype, K, lane, sx, acc);
-        else {
-#pragma unroll
-          for (int m = 0; m < MB; ++m) acc[m] = __int_as_float(0x7fc00000);
-        }
-    }
-    if (lane == 0) {
-      const int col = out_base[s] + row;
-#pragma unroll
-      for (int m = 0; m < MB; ++m) {
-        if (m < a.M) {
-          float v = acc[m];
-          if (a.resid) v += a.resid[(long)m * a.resid_stride + col];
-          a.out[(long)m * a.out_stride + col] = v;
-        }
-      }
+        if (FLOATW) rows_f<MB, R>(a, s, r_lo, r_hi, col0, sx, s_scale, between);
     }
   }
+  between();
 }
 
 static size_t gemv_smem(int MB, int K, bool floatw) {
-  size_t b = (size_t)MB * K + (size_t)MB * (K / 32) * 8 + 64 * 4;
+  size_t b = (size_t)MB * K + (size_t)MB * (K / 32) * 8 + MB * 8 * 8 + 8 * 4;
   if (floatw) b += (size_t)MB * K * 4;
   return b;
 }
 
-template <int MB, bool NORM, bool FLOATW>
+template <int MB, int R, int C, bool NORM, bool FLOATW>
 static cudaError_t gemv_launch(const GemvArgs& a, int grid, cudaStream_t st) {
   size_t smem = gemv_smem(MB, a.K, FLOATW);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemv_kernel<MB, NORM, FLOATW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(gemv_kernel<MB, R, C, NORM, FLOATW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     attr_set = true;
   }
-  return launch(gemv_kernel<MB, NORM, FLOATW>, dim3(grid), dim3(256), smem, st, a);
+  return launch(gemv_kernel<MB, R, C, NORM, FLOATW>, dim3(grid), dim3(256), smem, st, a);
+}
+
+template <int R, int C, bool NORM, bool FLOATW>
+static cudaError_t gemv_dispatch_mb(const GemvArgs& a, int mb, int grid, cudaStream_t st) {
+  switch (mb) {
+    case 1: return gemv_launch<1, R, C, NORM, FLOATW>(a, grid, st);
+    case 2: return gemv_launch<2, R, C, NORM, FLOATW>(a, grid, st);
+    case 4: return gemv_launch<4, R, C, NORM, FLOATW>(a, grid, st);
+    default: return gemv_launch<8, R, C, NORM, FLOATW>(a, grid, st);
+  }
 }
 
 template <bool NORM, bool FLOATW>
-static cudaError_t gemv_dispatch_mb(const GemvArgs& a, int mb, int grid, cudaStream_t st) {
-  switch (mb) {
-    case 1: return gemv_launch<1, NORM, FLOATW>(a, grid, st);
-    case 2: return gemv_launch<2, NORM, FLOATW>(a, grid, st);
-    case 4: return gemv_launch<4, NORM, FLOATW>(a, grid, st);
-    default: return gemv_launch<8, NORM, FLOATW>(a, grid, st);
-  }
+static cudaError_t gemv_dispatch_shape(const GemvArgs& a, int mb, int R, int C, int grid, cudaStream_t st) {
+  if (C == 2) return gemv_dispatch_mb<1, 2, NORM, FLOATW>(a, mb, grid, st);
+  if (R >= 3) return gemv_dispatch_mb<3, 1, NORM, FLOATW>(a, mb, grid, st);
+  if (R == 2) return gemv_dispatch_mb<2, 1, NORM, FLOATW>(a, mb, grid, st);
+  return gemv_dispatch_mb<1, 1, NORM, FLOATW>(a, mb, grid, st);
 }
 
 }  // namespace bl
@@ -251,35 +344,51 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
             const int8_t* xq, const float* xds,
             float* out, long out_stride, const float* resid, long resid_stride,
             int8_t* xq_out, float* xds_out, unsigned* fault, int layer, int sm_count, cudaStream_t st) {
+  (void)xq_out; (void)xds_out;
   BL_REQUIRE(nseg >= 1 && nseg <= 4, BL_ERR_SHAPE);
   BL_REQUIRE(M >= 1 && M <= 8, BL_ERR_SHAPE);
   BL_REQUIRE(K > 0 && K % 256 == 0, BL_ERR_SHAPE);
+  BL_REQUIRE(!norm || (K % 2048 == 0 || K % 64 == 0), BL_ERR_SHAPE);
   GemvArgs a = {};
   a.nseg = nseg;
   bool floatw = false;
-  int groups = 0;
+  double total_bytes = 0;
+  long rbs[4];
   for (int s = 0; s < nseg; ++s) {
-    long rb = resident_row_bytes(wtypes[s], K);
-    BL_REQUIRE(rb > 0, BL_ERR_TYPE);
+    rbs[s] = resident_row_bytes(wtypes[s], K);
+    BL_REQUIRE(rbs[s] > 0, BL_ERR_TYPE);
     BL_REQUIRE(((uintptr_t)w[s] & 15) == 0, BL_ERR_ALIGN);
-    a.seg[s] = GemvSeg{(const uint8_t*)w[s], rows[s], wtypes[s], rb};
+    BL_REQUIRE(rows[s] >= 1, BL_ERR_SHAPE);
+    total_bytes += (double)rows[s] * rbs[s];
     if (wtypes[s] == WT_F32 || wtypes[s] == WT_F16 || wtypes[s] == WT_BF16) floatw = true;
-    groups += (rows[s] + 7) / 8;
   }
   BL_REQUIRE(!(floatw && !norm), BL_ERR_TYPE);
-  a.total_groups = groups;
+  const int mb = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
+  // One wave: at most two resident blocks per SM; each segment gets a share of the blocks
+  // in proportion to its bytes, never more blocks than it has 8-row groups.
+  const int budget = 2 * sm_count;
+  const int C = (K / 64 > 32) ? 2 : 1;
+  int grid = 0, rpw_max = 1;
+  for (int s = 0; s < nseg; ++s) {
+    int nb = (int)((double)budget * ((double)rows[s] * rbs[s] / total_bytes));
+    const int cap = (rows[s] + 7) / 8;
+    nb = nb < 1 ? 1 : nb > cap ? cap : nb;
+    a.seg[s] = GemvSeg{(const uint8_t*)w[s], rows[s], wtypes[s], grid, nb, rbs[s]};
+    grid += nb;
+    const int rpw = (rows[s] + nb * 8 - 1) / (nb * 8);
+    rpw_max = rpw > rpw_max ? rpw : rpw_max;
+  }
+  int R = C == 2 ? 1 : (rpw_max >= 3 ? 3 : rpw_max);
+  if (mb == 8 && R > 2) R = 2;
   a.K = K; a.M = M;
   a.x = x; a.x_stride = x_stride; a.gain = gain; a.eps = eps;
   a.xq = xq; a.xds = (const float2*)xds;
   a.out = out; a.out_stride = out_stride; a.resid = resid; a.resid_stride = resid_stride;
-  a.xq_out = xq_out; a.xds_out = (float2*)xds_out;
   a.fault = fault; a.layer = layer;
-  int mb = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
   BL_REQUIRE(gemv_smem(mb, K, floatw) <= 200 * 1024, BL_ERR_LIMIT);
-  int grid = groups < sm_count * 4 ? groups : sm_count * 4;
   cudaError_t e;
-  if (norm) e = floatw ? gemv_dispatch_mb<true, true>(a, mb, grid, st) : gemv_dispatch_mb<true, false>(a, mb, grid, st);
-  else e = gemv_dispatch_mb<false, false>(a, mb, grid, st);
+  if (norm) e = floatw ? gemv_dispatch_shape<true, true>(a, mb, R, C, grid, st) : gemv_dispatch_shape<true, false>(a, mb, R, C, grid, st);
+  else e = gemv_dispatch_shape<false, false>(a, mb, R, C, grid, st);
   return (int)e;
 }
 

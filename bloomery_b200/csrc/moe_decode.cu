@@ -24,208 +24,198 @@ struct RouterArgs {
   const float* x; long x_stride;       // [M, K] residual stream
   const float* gain; float eps;
   const uint8_t* w; int wtype;         // [E, K] F32 / F16 / BF16
-  const float* bias;                   // [E] selection bias (sigmoid mode) or null
-  int K, E, M, top_k;
-  int mode;                            // 0 softmax, 1 sigmoid
-  int renorm;                          // renormalise chosen weights
-  float scale;                         // weights multiplier after renormalisation
-  int n_group, topk_group;             // group-limited routing (1,1 = off)
-  float* logits;                       // [M, E] scratch
-  int* ids;                            // [M, top_k]
-  float* wts;                          // [M, top_k]
+  int K, E, M;
+  float* logits;                       // [M, E]
   int8_t* xq_out; float2* xds_out;     // q8 of the normed rows [M, K]
   float* xn_out;                       // optional fp32 normed rows [M, K]
-  unsigned* counter;                   // completion ticket, zero at rest
-  unsigned* heat;                      // optional [E] routed-count histogram (residency rule)
   unsigned* fault; int layer;
 };
 
+// Routing parameters shared by the router launch and its consumers.
+struct RouteParams {
+  const float* logits;   // [M, E]
+  const float* bias;     // [E] selection bias (sigmoid mode) or null
+  int E, top_k, mode, renorm;
+  float scale;
+  int n_group, topk_group;
+};
+
+// Block-wide routing of one row by rank counting: every thread owns up to two experts,
+// reads all scores from shared memory and counts how many beat its own (larger score, or
+// equal score at a smaller id); an expert of rank r < top_k is slot r.  No serial arg-max
+// rounds, so it is short enough to run redundantly in every consumer block.  Softmax
+// weights need only the chosen logits: w_j = exp(l_j - l_top) / sum over the chosen
+// (renormalised) or over all experts (not renormalised).
+struct __align__(16) RouteShared {
+  float sc[kMaxExperts];
+  float wv[kMaxExperts];
+  float gs[16];
+  int ids[kMaxTopK];
+  float wraw[kMaxTopK];
+  float total;
+};
+
+__device__ __forceinline__ bool route_block(const RouteParams& p, int m, RouteShared& sh, int& my_id, float& my_w) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  bool nonfinite = false;
+  for (int e = tid; e < p.E; e += nthr) {
+    const float l = __ldcg(p.logits + (long)m * p.E + e);
+    if (!isfinite(l)) nonfinite = true;
+    if (p.mode == 0) { sh.sc[e] = l; sh.wv[e] = l; }
+    else { const float sg = 1.0f / (1.0f + expf(-l)); sh.wv[e] = sg; sh.sc[e] = sg + (p.bias ? p.bias[e] : 0.f); }
+  }
+  if (tid < kMaxTopK) { sh.ids[tid] = 0; sh.wraw[tid] = 0.f; }
+  if (__syncthreads_or(nonfinite)) { my_id = 0; my_w = __int_as_float(0x7fc00000); return false; }
+  if (p.n_group > 1) {
+    const int gsz = p.E / p.n_group;
+    if (tid < p.n_group) {
+      float b1 = -INFINITY, b2 = -INFINITY;
+      for (int i = 0; i < gsz; ++i) { const float v = sh.sc[tid * gsz + i]; if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v; }
+      sh.gs[tid] = b1 + b2;
+    }
+    __syncthreads();
+    bool drop[2] = {false, false};
+    int c = 0;
+    for (int e = tid; e < p.E; e += nthr, ++c) {
+      const int g = e / gsz;
+      const float mine = sh.gs[g];
+      int rank = 0;
+      for (int o = 0; o < p.n_group; ++o) rank += (sh.gs[o] > mine || (sh.gs[o] == mine && o < g)) ? 1 : 0;
+      drop[c & 1] = rank >= p.topk_group;
+    }
+    c = 0;
+    for (int e = tid; e < p.E; e += nthr, ++c) if (drop[c & 1]) sh.sc[e] = -INFINITY;
+    __syncthreads();
+  }
+  for (int e = tid; e < p.E; e += nthr) {
+    const float v = sh.sc[e];
+    if (v == -INFINITY) continue;
+    int rank = 0;
+    for (int o = 0; o < p.E; o += 4) {
+      const float4 q = *reinterpret_cast<const float4*>(sh.sc + o);
+      rank += (q.x > v || (q.x == v && o < e)) ? 1 : 0;
+      rank += (q.y > v || (q.y == v && o + 1 < e)) ? 1 : 0;
+      rank += (q.z > v || (q.z == v && o + 2 < e)) ? 1 : 0;
+      rank += (q.w > v || (q.w == v && o + 3 < e)) ? 1 : 0;
+    }
+    if (rank < p.top_k) { sh.ids[rank] = e; sh.wraw[rank] = sh.wv[e]; }
+  }
+  if (p.mode == 0 && !p.renorm && tid < 32) {
+    double part = 0.0;
+    float top = -INFINITY;
+    for (int e = tid; e < p.E; e += 32) top = fmaxf(top, sh.wv[e]);
+    top = warp_max(top);
+    for (int e = tid; e < p.E; e += 32) part += (double)expf(sh.wv[e] - top);
+    part = warp_sum_d(part);
+    if (tid == 0) sh.total = (float)part;
+  }
+  __syncthreads();
+  const int t = tid & 31;
+  my_id = t < p.top_k ? sh.ids[t] : 0;
+  float w = 0.f;
+  if (t < p.top_k) {
+    if (p.mode == 0) {
+      const float top = sh.wraw[0];
+      w = expf(sh.wraw[t] - top);
+      if (p.renorm) {
+        double sum = 0.0;
+        for (int j = 0; j < p.top_k; ++j) sum += (double)expf(sh.wraw[j] - top);
+        w = w / (float)sum;
+      } else {
+        w = w / sh.total;
+      }
+    } else {
+      w = sh.wraw[t];
+      if (p.renorm) {
+        double sum = 0.0;
+        for (int j = 0; j < p.top_k; ++j) sum += (double)sh.wraw[j];
+        w = w / (float)sum;
+      }
+    }
+    w *= p.scale;
+  }
+  my_w = w;
+  return true;
+}
+
+// grid = E blocks (one expert each), 256 threads.  A thread owns 8 consecutive values per
+// 2048-value chunk; the router row, gain and x are loaded together, the dot product of
+// w with x*gain and the sum of squares run in the same sweep, and the RMS scale multiplies
+// the finished logit (so nothing waits for a normalisation pass).
 template <int MB>
 __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
-  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float s_dot[8][MB];
+  __shared__ double s_ss[8][MB];
+  __shared__ float s_scale[MB];
   const int K = a.K;
-  float* sx = reinterpret_cast<float*>(smem);                 // [MB][K]
-  int8_t* sq = reinterpret_cast<int8_t*>(sx + (size_t)MB * K);  // [MB][K]
-  float2* sds = reinterpret_cast<float2*>(sq + (size_t)MB * K);
-  float* red = reinterpret_cast<float*>(sds + (size_t)MB * (K / 32));
-  __shared__ unsigned s_ticket;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int e = blockIdx.x;
+  const long rb = resident_row_bytes(a.wtype, K);
+  const uint8_t* row = a.w + (long)e * rb;
 
-  {  // router rows towards L2 ahead of the dependency wait
-    int e = blockIdx.x * 8 + warp;
-    long rb = resident_row_bytes(a.wtype, K);
-    if (e < a.E && lane == 0)
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.w + e * rb), "r"((unsigned)rb) : "memory");
-  }
-  pdl_wait();
-#pragma unroll 1
-  for (int m = 0; m < MB; ++m) {
-    const int ms = m < a.M ? m : a.M - 1;
-    block_rmsnorm_q8(a.x + (long)ms * a.x_stride, a.gain, K, a.eps, sq + (long)m * K, sds + (long)m * (K / 32), red,
-                     sx + (long)m * K);
-  }
-  pdl_launch();
-  // every block holds the same normed rows; each publishes a slice of the q8 form
-  {
-    const int nb32 = K / 32;
-    for (int b = blockIdx.x; b < nb32; b += gridDim.x) {
-      for (int m = 0; m < a.M; ++m) {
-        if (tid < 8) reinterpret_cast<uint32_t*>(a.xq_out + (long)m * K + b * 32)[tid] =
-            reinterpret_cast<const uint32_t*>(sq + (long)m * K + b * 32)[tid];
-        if (tid == 8) a.xds_out[(long)m * nb32 + b] = sds[(long)m * nb32 + b];
-        if (a.xn_out && tid >= 32 && tid < 64) a.xn_out[(long)m * K + b * 32 + (tid - 32)] = sx[(long)m * K + b * 32 + (tid - 32)];
+  float dot[MB], ss[MB];
+#pragma unroll
+  for (int m = 0; m < MB; ++m) { dot[m] = 0.f; ss[m] = 0.f; }
+  bool waited = false;
+  for (int i0 = tid * 8; i0 < K; i0 += 2048) {
+    float wv[8];
+    if (a.wtype == WT_F32) {
+      float4 p = __ldg(reinterpret_cast<const float4*>(row) + i0 / 4), q = __ldg(reinterpret_cast<const float4*>(row) + i0 / 4 + 1);
+      wv[0] = p.x; wv[1] = p.y; wv[2] = p.z; wv[3] = p.w; wv[4] = q.x; wv[5] = q.y; wv[6] = q.z; wv[7] = q.w;
+    } else {
+      uint4 p = __ldg(reinterpret_cast<const uint4*>(row) + i0 / 8);
+      const uint32_t ws[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = (a.wtype == WT_F16) ? __half22float2(*reinterpret_cast<const __half2*>(&ws[j]))
+                                       : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ws[j]));
+        wv[2 * j] = f.x; wv[2 * j + 1] = f.y;
       }
     }
-  }
-  const int e = blockIdx.x * 8 + warp;
-  if (e < a.E) {
-    const uint8_t* row = a.w + (long)e * resident_row_bytes(a.wtype, K);
-    float acc[MB];
-#pragma unroll
-    for (int m = 0; m < MB; ++m) acc[m] = 0.f;
-    for (int i = lane * 4; i < K; i += 128) {
-      float w0, w1, w2, w3;
-      if (a.wtype == WT_F32) {
-        float4 v = __ldg(reinterpret_cast<const float4*>(row) + i / 4);
-        w0 = v.x; w1 = v.y; w2 = v.z; w3 = v.w;
-      } else if (a.wtype == WT_F16) {
-        uint2 v = __ldg(reinterpret_cast<const uint2*>(row) + i / 4);
-        float2 p = __half22float2(*reinterpret_cast<__half2*>(&v.x));
-        float2 q = __half22float2(*reinterpret_cast<__half2*>(&v.y));
-        w0 = p.x; w1 = p.y; w2 = q.x; w3 = q.y;
-      } else {
-        uint2 v = __ldg(reinterpret_cast<const uint2*>(row) + i / 4);
-        float2 p = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v.x));
-        float2 q = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v.y));
-        w0 = p.x; w1 = p.y; w2 = q.x; w3 = q.y;
-      }
-#pragma unroll
-      for (int m = 0; m < MB; ++m) {
-        const float4 xv = *reinterpret_cast<const float4*>(sx + (long)m * K + i);
-        acc[m] = fmaf(w0, xv.x, fmaf(w1, xv.y, fmaf(w2, xv.z, fmaf(w3, xv.w, acc[m]))));
-      }
-    }
+    float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gain + i0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gain + i0 + 4));
+    if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
     for (int m = 0; m < MB; ++m) {
-      float v = warp_sum(acc[m]);
-      if (lane == 0 && m < a.M) a.logits[(long)m * a.E + e] = v;
+      const int ms = m < a.M ? m : a.M - 1;
+      const float* x = a.x + (long)ms * a.x_stride + i0;
+      float4 x0 = *reinterpret_cast<const float4*>(x), x1 = *reinterpret_cast<const float4*>(x + 4);
+      ss[m] += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
+      float t = dot[m];
+      t = fmaf(wv[0], x0.x * g0.x, t); t = fmaf(wv[1], x0.y * g0.y, t); t = fmaf(wv[2], x0.z * g0.z, t); t = fmaf(wv[3], x0.w * g0.w, t);
+      t = fmaf(wv[4], x1.x * g1.x, t); t = fmaf(wv[5], x1.y * g1.y, t); t = fmaf(wv[6], x1.z * g1.z, t); t = fmaf(wv[7], x1.w * g1.w, t);
+      dot[m] = t;
     }
   }
-  // completion ticket: the last block to arrive routes every row
-  __threadfence();
+  if (!waited) pdl_wait();
+  pdl_launch();
+#pragma unroll
+  for (int m = 0; m < MB; ++m) {
+    float d = warp_sum(dot[m]);
+    double q = warp_sum_d((double)ss[m]);
+    if (lane == 0) { s_dot[warp][m] = d; s_ss[warp][m] = q; }
+  }
   __syncthreads();
-  if (tid == 0) s_ticket = atomicAdd(a.counter, 1u);
+  if (tid < MB) {
+    float d = 0.f; double q = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { d += s_dot[w][tid]; q += s_ss[w][tid]; }
+    const float scale = (float)(1.0 / sqrt(q / (double)K + (double)a.eps));
+    s_scale[tid] = scale;
+    if (tid < a.M) a.logits[(long)tid * a.E + e] = d * scale;
+  }
   __syncthreads();
-  if (s_ticket != gridDim.x - 1) return;
-  __threadfence();
-  if (tid == 0) *a.counter = 0u;  // at rest again for the next replay
-
-  constexpr int EPL = kMaxExperts / 32;  // experts per lane, strided: e = lane + 32 i
-  for (int m = warp; m < a.M; m += 8) {
-    float sc[EPL];     // choice score
-    float wv[EPL];     // weight value
-    bool finite = true;
-    float mxl = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      int ee = lane + 32 * i;
-      float v = ee < a.E ? __ldcg(a.logits + (long)m * a.E + ee) : -INFINITY;
-      if (ee < a.E && !isfinite(v)) finite = false;
-      sc[i] = v;
-      mxl = fmaxf(mxl, v);
-    }
-    finite = __all_sync(0xffffffffu, finite);
-    if (!finite) {
-      if (lane == 0) raise_fault(a.fault, a.layer, FS_ROUTER);
-      if (lane < a.top_k) { a.wts[(long)m * a.top_k + lane] = __int_as_float(0x7fc00000); a.ids[(long)m * a.top_k + lane] = 0; }
-      continue;
-    }
-    if (a.mode == 0) {
-      mxl = warp_max(mxl);
-      double part = 0.0;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        float ex = (lane + 32 * i < a.E) ? expf(sc[i] - mxl) : 0.f;
-        wv[i] = ex;
-        part += (double)ex;
-      }
-      double tot = warp_sum_d(part);
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) { wv[i] = wv[i] / (float)tot; sc[i] = (lane + 32 * i < a.E) ? wv[i] : -INFINITY; }
-    } else {
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        int ee = lane + 32 * i;
-        float sg = 1.0f / (1.0f + expf(-sc[i]));
-        wv[i] = sg;
-        sc[i] = ee < a.E ? sg + (a.bias ? a.bias[ee] : 0.f) : -INFINITY;
-      }
-    }
-    // group-limited choice: keep the topk_group groups with the largest sum of their two best scores
-    if (a.n_group > 1) {
-      const int gsz = a.E / a.n_group;
-      float gscore[16];
-      for (int g = 0; g < a.n_group && g < 16; ++g) {
-        float b1 = -INFINITY, b2 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-          int ee = lane + 32 * i;
-          if (ee < a.E && ee / gsz == g) { float v = sc[i]; if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v; }
-        }
-        // merge (b1, b2) pairs across lanes
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          float o1 = __shfl_xor_sync(0xffffffffu, b1, o), o2 = __shfl_xor_sync(0xffffffffu, b2, o);
-          float n1 = fmaxf(b1, o1);
-          float n2 = fmaxf(fminf(b1, o1), fmaxf(b2, o2));
-          b1 = n1; b2 = n2;
-        }
-        gscore[g] = b1 + b2;
-      }
-      unsigned keep = 0;
-      for (int t = 0; t < a.topk_group; ++t) {
-        int best = -1; float bv = -INFINITY;
-        for (int g = 0; g < a.n_group && g < 16; ++g)
-          if (!((keep >> g) & 1) && (best < 0 || gscore[g] > bv)) { best = g; bv = gscore[g]; }
-        if (best >= 0) keep |= 1u << best;
-      }
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        int ee = lane + 32 * i;
-        if (ee < a.E && !((keep >> (ee / gsz)) & 1)) sc[i] = -INFINITY;
-      }
-    }
-    // top-k: k rounds of warp arg-max, larger score first, ties to the smaller id
-    int my_id = 0; float my_w = 0.f;
-    double wsum = 0.0;
-    for (int t = 0; t < a.top_k; ++t) {
-      float bv = -INFINITY; int bi = 0x7fffffff; float bw = 0.f;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        int ee = lane + 32 * i;
-        if (ee < a.E && (sc[i] > bv || (sc[i] == bv && ee < bi))) { bv = sc[i]; bi = ee; bw = wv[i]; }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        float ow = __shfl_xor_sync(0xffffffffu, bw, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; bw = ow; }
-      }
-      if ((bi & 31) == lane) {
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) if (i == (bi >> 5)) sc[i] = -INFINITY;
-      }
-      if (lane == t) { my_id = bi; my_w = bw; }
-      wsum += (double)bw;  // slot order, same in every lane
-    }
-    if (lane < a.top_k) {
-      float w = my_w;
-      if (a.renorm) w = w / (float)wsum;
-      w *= a.scale;
-      a.ids[(long)m * a.top_k + lane] = my_id;
-      a.wts[(long)m * a.top_k + lane] = w;
-      if (a.heat) atomicAdd(a.heat + my_id, 1u);
+  // every block knows the scale; block b publishes 32-value blocks b, b + E, ... of the q8 rows
+  {
+    const int nb32 = K / 32;
+    for (int b = e * 8 + warp; b < nb32 * a.M; b += gridDim.x * 8) {
+      const int m = b / nb32, bb = b - m * nb32;
+      const int i = bb * 32 + lane;
+      const float v = a.x[(long)m * a.x_stride + i] * a.gain[i] * s_scale[m];
+      float d, sm;
+      int8_t qv = q8_lane(v, d, sm);
+      a.xq_out[(long)m * K + i] = qv;
+      if (a.xn_out) a.xn_out[(long)m * K + i] = v;
+      if (lane == 0) a.xds_out[(long)m * nb32 + bb] = make_float2(d, sm);
     }
   }
 }
@@ -236,7 +226,10 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
 // ------------------------------------------------------------------------------------
 struct GateUpArgs {
   const int8_t* xq; const float2* xds;   // [M, K] q8
-  const int* ids;                        // [M, n_used]
+  RouteParams route;                     // route.logits == null: ids are given
+  int* ids;                              // [M, n_used] read (given) or written (routed here)
+  float* wts;                            // [M, n_used] written when routed here
+  unsigned* heat;                        // optional [E] routed-count histogram
   const int* slot_map;                   // optional [E]: expert id -> resident slot (or kExpertElsewhere)
   const uint8_t* gate; const uint8_t* up; int gtype, utype;   // stacks [E_slots, I, K]
   int K, I, E, n_used, M;
@@ -245,46 +238,64 @@ struct GateUpArgs {
   unsigned* fault; int layer;
 };
 
-template <class TG, class TU>
-__device__ __forceinline__ void gate_up_rows(const uint8_t* g0, const uint8_t* u0, long grb, long urb, int K, int lane,
-                                             const int8_t* sq, const float2* sds, float (&gacc)[4], float (&uacc)[4]) {
-  using UG = Unit<TG>; using UU = Unit<TU>;
+// two activation outputs (2 gate rows + 2 up rows) of one warp
+template <class T>
+__device__ __forceinline__ void gate_up_rows(const uint8_t* g0, const uint8_t* u0, long rb, int K, int lane,
+                                             const int8_t* xq, const float2* xds, float (&gacc)[2], float (&uacc)[2]) {
+  using U = Unit<T>;
   const int nunits = K / 64;
 #pragma unroll
-  for (int r = 0; r < 4; ++r) { gacc[r] = 0.f; uacc[r] = 0.f; }
+  for (int r = 0; r < 2; ++r) { gacc[r] = 0.f; uacc[r] = 0.f; }
   for (int u = lane; u < nunits; u += 32) {
-    typename UG::Regs rg[4];
-    typename UU::Regs ru[4];
+    typename U::Regs rg[2], ru[2];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) { UG::loadu(g0 + r * grb, u, K, rg[r]); UU::loadu(u0 + r * urb, u, K, ru[r]); }
+    for (int r = 0; r < 2; ++r) { U::loadu(g0 + r * rb, u, K, rg[r]); U::loadu(u0 + r * rb, u, K, ru[r]); }
+    ActRegs act;   // activations straight from L2, behind the weight loads already in flight
+    ActOf<T>::load(reinterpret_cast<const uint32_t*>(xq), reinterpret_cast<const F2*>(xds), u, act);
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      gacc[r] += UG::dotu(rg[r], u, reinterpret_cast<const uint32_t*>(sq), reinterpret_cast<const F2*>(sds));
-      uacc[r] += UU::dotu(ru[r], u, reinterpret_cast<const uint32_t*>(sq), reinterpret_cast<const F2*>(sds));
-    }
+    for (int r = 0; r < 2; ++r) { gacc[r] += ActOf<T>::dot(rg[r], u, act); uacc[r] += ActOf<T>::dot(ru[r], u, act); }
   }
 #pragma unroll
-  for (int r = 0; r < 4; ++r) { gacc[r] = warp_sum(gacc[r]); uacc[r] = warp_sum(uacc[r]); }
+  for (int r = 0; r < 2; ++r) { gacc[r] = warp_sum(gacc[r]); uacc[r] = warp_sum(uacc[r]); }
 }
 
-__global__ void __launch_bounds__(256) gate_up_sel_kernel(const GateUpArgs a) {
-  extern __shared__ __align__(16) uint8_t smem[];
+// grid (I/32, n_used, M), 256 threads: warp w computes activation rows 4w..4w+3 of the chunk.
+// When route.logits is set, warp 0 of every block routes row m itself (redundantly, from
+// the router launch's logits) so no block waits on a completion counter; block (0, 0, m)
+// also publishes ids / weights / heat for the launches that follow.
+__global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a) {
   const int K = a.K;
-  int8_t* sq = reinterpret_cast<int8_t*>(smem);
-  float2* sds = reinterpret_cast<float2*>(smem + K);
   __shared__ float s_act[32];
+  __shared__ int s_e;
   const int chunk = blockIdx.x, j = blockIdx.y, m = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_wait();
   pdl_launch();
-  int e = a.ids[(long)m * a.n_used + j];
+  if (a.route.logits) {
+    __shared__ RouteShared rs;
+    int id; float w;
+    const bool ok = route_block(a.route, m, rs, id, w);
+    if (tid == 0) s_e = ok ? rs.ids[j] : -3;
+    if (chunk == 0 && j == 0 && warp == 0) {
+      if (!ok && lane == 0) raise_fault(a.fault, a.layer, FS_ROUTER);
+      if (lane < a.n_used) {
+        a.ids[(long)m * a.n_used + lane] = ok ? id : 0;
+        a.wts[(long)m * a.n_used + lane] = w;
+        if (ok && a.heat) atomicAdd(a.heat + id, 1u);
+      }
+    }
+  } else if (tid == 0) {
+    s_e = a.ids[(long)m * a.n_used + j];
+  }
+  __syncthreads();
+  int e = s_e;
   const long ob = ((long)m * a.n_used + j) * a.I + chunk * 32;
   bool skip = false, bad = false;
   if (e == kExpertElsewhere) skip = true;
-  else if (e < 0 || e >= a.E) { skip = true; bad = true; }
+  else if (e == -3) { skip = true; bad = true; }                 // router fault: NaN downstream
+  else if (e < 0 || e >= a.E) { skip = true; bad = true; if (tid == 0 && chunk == 0) raise_fault(a.fault, a.layer, FS_EXPERT_ID); }
   else if (a.slot_map) { e = a.slot_map[e]; if (e < 0) skip = true; }
   if (skip) {
-    if (bad && tid == 0 && chunk == 0) raise_fault(a.fault, a.layer, FS_EXPERT_ID);
     if (tid < 32) {
       a.actq[ob + tid] = 0;
       if (a.act_f32) a.act_f32[ob + tid] = bad ? __int_as_float(0x7fc00000) : 0.f;
@@ -292,30 +303,28 @@ __global__ void __launch_bounds__(256) gate_up_sel_kernel(const GateUpArgs a) {
     if (tid == 0) a.actds[ob / 32] = bad ? make_float2(__int_as_float(0x7fc00000), 0.f) : make_float2(0.f, 0.f);
     return;
   }
-  for (int i = tid; i < K / 16; i += 256)
-    reinterpret_cast<uint4*>(sq)[i] = reinterpret_cast<const uint4*>(a.xq + (long)m * K)[i];
-  for (int i = tid; i < K / 32; i += 256) sds[i] = a.xds[(long)m * (K / 32) + i];
-  __syncthreads();
-  const long grb = resident_row_bytes(a.gtype, K), urb = resident_row_bytes(a.utype, K);
-  const long row0 = (long)e * a.I + chunk * 32 + warp * 4;
-  const uint8_t* g0 = a.gate + row0 * grb;
-  const uint8_t* u0 = a.up + row0 * urb;
-  float gacc[4], uacc[4];
-  const int key = a.gtype * 64 + a.utype;
-  switch (key) {
-    case WT_Q4_K * 64 + WT_Q4_K: gate_up_rows<Q4K, Q4K>(g0, u0, grb, urb, K, lane, sq, sds, gacc, uacc); break;
-    case WT_Q5_K * 64 + WT_Q5_K: gate_up_rows<Q5K, Q5K>(g0, u0, grb, urb, K, lane, sq, sds, gacc, uacc); break;
-    case WT_Q6_K * 64 + WT_Q6_K: gate_up_rows<Q6K, Q6K>(g0, u0, grb, urb, K, lane, sq, sds, gacc, uacc); break;
-    case WT_Q8_0 * 64 + WT_Q8_0: gate_up_rows<Q80, Q80>(g0, u0, grb, urb, K, lane, sq, sds, gacc, uacc); break;
-    default:
+  const long rb = resident_row_bytes(a.gtype, K);
+  const int8_t* xq = a.xq + (long)m * K;
+  const float2* xds = a.xds + (long)m * (K / 32);
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    const long row0 = (long)e * a.I + chunk * 32 + warp * 4 + half * 2;
+    const uint8_t* g0 = a.gate + row0 * rb;
+    const uint8_t* u0 = a.up + row0 * rb;
+    float gacc[2], uacc[2];
+    switch (a.gtype) {
+      case WT_Q4_K: gate_up_rows<Q4K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+      case WT_Q5_K: gate_up_rows<Q5K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+      case WT_Q6_K: gate_up_rows<Q6K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+      case WT_Q8_0: gate_up_rows<Q80>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+      default: gacc[0] = gacc[1] = __int_as_float(0x7fc00000); uacc[0] = uacc[1] = 0.f;
+    }
+    if (lane == 0) {
 #pragma unroll
-      for (int r = 0; r < 4; ++r) { gacc[r] = __int_as_float(0x7fc00000); uacc[r] = 0.f; }
-  }
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      float g = gacc[r];
-      s_act[warp * 4 + r] = (g / (1.0f + expf(-g))) * uacc[r];
+      for (int r = 0; r < 2; ++r) {
+        float g = gacc[r];
+        s_act[warp * 4 + half * 2 + r] = (g / (1.0f + expf(-g))) * uacc[r];
+      }
     }
   }
   __syncthreads();
@@ -345,40 +354,51 @@ struct DownArgs {
   unsigned* fault; int layer;
 };
 
-template <class T>
-__device__ __forceinline__ float down_row(const DownArgs& a, int m, int d, int lane, const int8_t* sq, const float2* sds,
-                                          const int* s_slot, const float* s_w) {
+// UPL = units per lane (all loaded before any is used: one DRAM round trip per row)
+template <class T, int UPL>
+__device__ __forceinline__ float down_row(const DownArgs& a, int m, int d, int lane, const int* s_slot, const float* s_w) {
   using U = Unit<T>;
   const int upe = a.I / 64;              // units per expert row
   const int total = a.n_used * upe;
   const long rb = resident_row_bytes(T::kType, a.I);
+  typename U::Regs regs[UPL];
+  int jj[UPL], uu[UPL];
+#pragma unroll
+  for (int c = 0; c < UPL; ++c) {
+    const int t = lane + 32 * c;
+    jj[c] = -1; uu[c] = 0;
+    if (t < total) {
+      const int j = t / upe;
+      const int e = s_slot[j];
+      if (e >= 0) { jj[c] = j; uu[c] = t - j * upe; U::loadu(a.down + ((long)e * a.H + d) * rb, uu[c], a.I, regs[c]); }
+    }
+  }
   // per-slot partial sums kept separate, then added in ascending slot order
   float part[kMaxTopK];
 #pragma unroll
   for (int j = 0; j < kMaxTopK; ++j) part[j] = 0.f;
-  for (int t = lane; t < total; t += 32) {
-    const int j = t / upe, u = t - j * upe;
-    const int e = s_slot[j];
-    if (e < 0) continue;
-    typename U::Regs r;
-    U::loadu(a.down + ((long)e * a.H + d) * rb, u, a.I, r);
-    float v = U::dotu(r, u, reinterpret_cast<const uint32_t*>(sq + (long)j * a.I),
-                      reinterpret_cast<const F2*>(sds + (long)j * (a.I / 32)));
 #pragma unroll
-    for (int jj = 0; jj < kMaxTopK; ++jj) if (jj == j) part[jj] += v;
+  for (int c = 0; c < UPL; ++c) {
+    if (jj[c] >= 0) {
+      ActRegs act;
+      const long ab = ((long)m * a.n_used + jj[c]) * a.I;
+      ActOf<T>::load(reinterpret_cast<const uint32_t*>(a.actq + ab), reinterpret_cast<const F2*>(a.actds + ab / 32), uu[c], act);
+      float v = ActOf<T>::dot(regs[c], uu[c], act);
+#pragma unroll
+      for (int j = 0; j < kMaxTopK; ++j) if (j == jj[c]) part[j] += v;
+    }
   }
+  // router-weighted sum over slots in ascending order inside the lane, then one butterfly
   float y = 0.f;
 #pragma unroll
   for (int j = 0; j < kMaxTopK; ++j) {
-    if (j < a.n_used) y = fmaf(s_w[j], warp_sum(part[j]), y);
+    if (j < a.n_used) y = fmaf(s_w[j], part[j], y);
   }
-  return y;
+  return warp_sum(y);
 }
 
-__global__ void __launch_bounds__(256) down_combine_kernel(const DownArgs a) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  int8_t* sq = reinterpret_cast<int8_t*>(smem);                              // [n_used][I]
-  float2* sds = reinterpret_cast<float2*>(smem + (size_t)a.n_used * a.I);    // [n_used][I/32]
+template <int UPL>
+__global__ void __launch_bounds__(256, UPL <= 3 ? 2 : 1) down_combine_kernel(const DownArgs a) {
   __shared__ int s_slot[kMaxTopK];
   __shared__ float s_w[kMaxTopK];
   const int m = blockIdx.y;
@@ -393,11 +413,6 @@ __global__ void __launch_bounds__(256) down_combine_kernel(const DownArgs a) {
     else if (a.slot_map) { e = a.slot_map[e]; if (e < 0) e = -1; }
     s_slot[tid] = e; s_w[tid] = w;
   }
-  const long n16 = (long)a.n_used * a.I / 16;
-  for (long i = tid; i < n16; i += 256)
-    reinterpret_cast<uint4*>(sq)[i] = reinterpret_cast<const uint4*>(a.actq + (long)m * a.n_used * a.I)[i];
-  const long nds = (long)a.n_used * (a.I / 32);
-  for (long i = tid; i < nds; i += 256) sds[i] = a.actds[(long)m * nds + i];
   __syncthreads();
   bool bad = false;
   for (int j = 0; j < a.n_used; ++j) bad |= (s_slot[j] == -2);
@@ -405,10 +420,10 @@ __global__ void __launch_bounds__(256) down_combine_kernel(const DownArgs a) {
   if (d >= a.H) return;
   float y;
   switch (a.dtype) {
-    case WT_Q4_K: y = down_row<Q4K>(a, m, d, lane, sq, sds, s_slot, s_w); break;
-    case WT_Q6_K: y = down_row<Q6K>(a, m, d, lane, sq, sds, s_slot, s_w); break;
-    case WT_Q5_K: y = down_row<Q5K>(a, m, d, lane, sq, sds, s_slot, s_w); break;
-    case WT_Q8_0: y = down_row<Q80>(a, m, d, lane, sq, sds, s_slot, s_w); break;
+    case WT_Q4_K: y = down_row<Q4K, UPL>(a, m, d, lane, s_slot, s_w); break;
+    case WT_Q6_K: y = down_row<Q6K, UPL>(a, m, d, lane, s_slot, s_w); break;
+    case WT_Q5_K: y = down_row<Q5K, UPL>(a, m, d, lane, s_slot, s_w); break;
+    case WT_Q8_0: y = down_row<Q80, UPL>(a, m, d, lane, s_slot, s_w); break;
     default: y = __int_as_float(0x7fc00000);
   }
   if (lane == 0) {
@@ -425,46 +440,73 @@ using namespace bl;
 
 extern "C" {
 
-int bl_router(const float* x, long x_stride, const float* gain, float eps, const void* w, int wtype, const float* bias,
-              int K, int E, int M, int top_k, int mode, int renorm, float scale, int n_group, int topk_group,
-              float* logits, int* ids, float* wts, int8_t* xq_out, float* xds_out, float* xn_out, unsigned* counter,
-              unsigned* heat, unsigned* fault, int layer, cudaStream_t st) {
+// Router logits (RMS scale applied) for M rows + the q8 form of the normed rows.
+int bl_router(const float* x, long x_stride, const float* gain, float eps, const void* w, int wtype,
+              int K, int E, int M, float* logits, int8_t* xq_out, float* xds_out, float* xn_out, unsigned* fault,
+              int layer, cudaStream_t st) {
   BL_REQUIRE(E >= 1 && E <= kMaxExperts, BL_ERR_LIMIT);
-  BL_REQUIRE(top_k >= 1 && top_k <= kMaxTopK && top_k <= E, BL_ERR_LIMIT);
-  BL_REQUIRE(K % 128 == 0 && M >= 1 && M <= 8, BL_ERR_SHAPE);
+  BL_REQUIRE(K % 256 == 0 && M >= 1 && M <= 8, BL_ERR_SHAPE);
   BL_REQUIRE(wtype == WT_F32 || wtype == WT_F16 || wtype == WT_BF16, BL_ERR_TYPE);
-  BL_REQUIRE(n_group >= 1 && n_group <= 16 && E % n_group == 0 && topk_group >= 1 && topk_group <= n_group, BL_ERR_SHAPE);
-  RouterArgs a{x, x_stride, gain, eps, (const uint8_t*)w, wtype, bias, K, E, M, top_k, mode, renorm, scale, n_group,
-               topk_group, logits, ids, wts, xq_out, (float2*)xds_out, xn_out, counter, heat, fault, layer};
+  RouterArgs a{};
+  a.x = x; a.x_stride = x_stride; a.gain = gain; a.eps = eps; a.w = (const uint8_t*)w; a.wtype = wtype;
+  a.K = K; a.E = E; a.M = M; a.logits = logits; a.xq_out = xq_out; a.xds_out = (float2*)xds_out; a.xn_out = xn_out;
+  a.fault = fault; a.layer = layer;
   int mb = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
-  size_t smem = (size_t)mb * K * 5 + (size_t)mb * (K / 32) * 8 + 256;
-  BL_REQUIRE(smem <= 200 * 1024, BL_ERR_LIMIT);
-  dim3 grid((E + 7) / 8);
-#define BL_ROUTER_CASE(MBV)                                                                                  \
-  {                                                                                                          \
-    static bool set = false;                                                                                 \
-    if (!set) { cudaFuncSetAttribute(router_kernel<MBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; } \
-    return (int)launch(router_kernel<MBV>, grid, dim3(256), smem, st, a);                                    \
-  }
+  dim3 grid(E);
   switch (mb) {
-    case 1: BL_ROUTER_CASE(1)
-    case 2: BL_ROUTER_CASE(2)
-    case 4: BL_ROUTER_CASE(4)
-    default: BL_ROUTER_CASE(8)
+    case 1: return (int)launch(router_kernel<1>, grid, dim3(256), 0, st, a);
+    case 2: return (int)launch(router_kernel<2>, grid, dim3(256), 0, st, a);
+    case 4: return (int)launch(router_kernel<4>, grid, dim3(256), 0, st, a);
+    default: return (int)launch(router_kernel<8>, grid, dim3(256), 0, st, a);
   }
-#undef BL_ROUTER_CASE
 }
 
-int bl_gate_up_sel(const int8_t* xq, const float* xds, const int* ids, const int* slot_map, const void* gate,
-                   const void* up, int gtype, int utype, int K, int I, int E, int n_used, int M, int8_t* actq,
-                   float* actds, float* act_f32, unsigned* fault, int layer, cudaStream_t st) {
+// Standalone routing of M rows from logits (tests, prefill, host paths): one warp per row.
+__global__ void __launch_bounds__(256) route_rows_kernel(RouteParams p, int M, int* ids, float* wts, unsigned* heat,
+                                                         unsigned* fault, int layer) {
+  __shared__ RouteShared rs;
+  pdl_wait();
+  pdl_launch();
+  const int m = blockIdx.x, lane = threadIdx.x & 31;
+  int id; float w;
+  const bool ok = route_block(p, m, rs, id, w);
+  if (threadIdx.x >= 32) return;
+  if (!ok && lane == 0) raise_fault(fault, layer, FS_ROUTER);
+  if (lane < p.top_k) {
+    ids[(long)m * p.top_k + lane] = ok ? id : 0;
+    wts[(long)m * p.top_k + lane] = w;
+    if (ok && heat) atomicAdd(heat + id, 1u);
+  }
+}
+
+int bl_route_rows(const float* logits, const float* bias, int E, int M, int top_k, int mode, int renorm, float scale,
+                  int n_group, int topk_group, int* ids, float* wts, unsigned* heat, unsigned* fault, int layer,
+                  cudaStream_t st) {
+  BL_REQUIRE(E >= 4 && E % 4 == 0 && E <= kMaxExperts && top_k >= 1 && top_k <= kMaxTopK && top_k <= E, BL_ERR_LIMIT);
+  BL_REQUIRE(n_group >= 1 && n_group <= 16 && E % n_group == 0 && topk_group >= 1 && topk_group <= n_group, BL_ERR_SHAPE);
+  RouteParams p{logits, bias, E, top_k, mode, renorm, scale, n_group, topk_group};
+  return (int)launch(route_rows_kernel, dim3(M), dim3(256), 0, st, p, M, ids, wts, heat, fault, layer);
+}
+
+// route_logits != null: every block routes its row from the logits (and block 0 writes
+// ids / wts / heat); otherwise ids are read as given.
+int bl_gate_up_sel(const int8_t* xq, const float* xds, const float* route_logits, const float* bias, int top_k_mode,
+                   int renorm, float scale, int n_group, int topk_group, int* ids, float* wts, unsigned* heat,
+                   const int* slot_map, const void* gate, const void* up, int gtype, int utype, int K, int I, int E,
+                   int n_used, int M, int8_t* actq, float* actds, float* act_f32, unsigned* fault, int layer,
+                   cudaStream_t st) {
   BL_REQUIRE(K % 256 == 0 && I % 32 == 0 && M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
   BL_REQUIRE(gtype == utype, BL_ERR_TYPE);
   BL_REQUIRE(gtype == WT_Q4_K || gtype == WT_Q5_K || gtype == WT_Q6_K || gtype == WT_Q8_0, BL_ERR_TYPE);
-  GateUpArgs a{xq, (const float2*)xds, ids, slot_map, (const uint8_t*)gate, (const uint8_t*)up, gtype, utype, K, I, E,
-               n_used, M, actq, (float2*)actds, act_f32, fault, layer};
-  size_t smem = (size_t)K + (size_t)(K / 32) * 8;
-  return (int)launch(gate_up_sel_kernel, dim3(I / 32, n_used, M), dim3(256), smem, st, a);
+  BL_REQUIRE(E % 4 == 0 && E <= kMaxExperts && n_group >= 1 && n_group <= 16 && E % n_group == 0, BL_ERR_LIMIT);
+  GateUpArgs a{};
+  a.xq = xq; a.xds = (const float2*)xds;
+  a.route = RouteParams{route_logits, bias, E, n_used, top_k_mode, renorm, scale, n_group, topk_group};
+  a.ids = ids; a.wts = wts; a.heat = heat; a.slot_map = slot_map;
+  a.gate = (const uint8_t*)gate; a.up = (const uint8_t*)up; a.gtype = gtype; a.utype = utype;
+  a.K = K; a.I = I; a.E = E; a.n_used = n_used; a.M = M;
+  a.actq = actq; a.actds = (float2*)actds; a.act_f32 = act_f32; a.fault = fault; a.layer = layer;
+  return (int)launch(gate_up_sel_kernel, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
 }
 
 int bl_down_combine(const int8_t* actq, const float* actds, const int* ids, const float* wts, const int* slot_map,
@@ -476,11 +518,12 @@ int bl_down_combine(const int8_t* actq, const float* actds, const int* ids, cons
   BL_REQUIRE(dtype == WT_Q4_K || dtype == WT_Q5_K || dtype == WT_Q6_K || dtype == WT_Q8_0, BL_ERR_TYPE);
   DownArgs a{actq, (const float2*)actds, ids, wts, slot_map, (const uint8_t*)down, dtype, I, H, E, n_used, M, resid,
              resid_stride, extra, extra_stride, out, out_stride, fault, layer};
-  size_t smem = (size_t)n_used * I + (size_t)n_used * (I / 32) * 8;
-  BL_REQUIRE(smem <= 160 * 1024, BL_ERR_LIMIT);
-  static bool set = false;
-  if (!set) { cudaFuncSetAttribute(down_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); set = true; }
-  return (int)launch(down_combine_kernel, dim3((H + 7) / 8, M), dim3(256), smem, st, a);
+  const long total = (long)n_used * (I / 64);
+  BL_REQUIRE(total <= 512, BL_ERR_LIMIT);
+  dim3 grid((H + 7) / 8, M);
+  if (total <= 96) return (int)launch(down_combine_kernel<3>, grid, dim3(256), 0, st, a);
+  if (total <= 192) return (int)launch(down_combine_kernel<6>, grid, dim3(256), 0, st, a);
+  return (int)launch(down_combine_kernel<16>, grid, dim3(256), 0, st, a);
 }
 
 }  // extern "C"

@@ -267,7 +267,12 @@ struct Q6K {
     r.d = ld32(p + 208) & 0xFFFF;
   }
   static BL_HD int scale(const Regs& r, int idx) {  // idx 0..15, signed byte
-    return (int)(int8_t)((r.sc[idx >> 2] >> (8 * (idx & 3))) & 0xFF);
+    // selects instead of a dynamically indexed register array (which would live in local memory)
+    const int wi = idx >> 2;
+    const uint32_t lo = (wi & 1) ? r.sc[1] : r.sc[0];
+    const uint32_t hi = (wi & 1) ? r.sc[3] : r.sc[2];
+    const uint32_t word = (wi & 2) ? hi : lo;
+    return (int)(int8_t)((word >> (8 * (idx & 3))) & 0xFF);
   }
   // four groups g of four words (16 codes each), codes already centred (q - 32)
   static BL_HD void codes(const Regs& r, uint32_t c[4][4]) {
@@ -414,6 +419,66 @@ template <> struct Unit<Q80> {
   }
   static BL_HD void decodeu(const Regs& r, int, float* o) { Q80::decode(r, o); }
   static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
+
+
+// ---------------------------------------------------------------------------------
+// Activation registers of one unit: 16 code words and up to four {d, s} pairs, fetched
+// once (from shared or global memory) and reused against several weight rows.
+//   ActOf<T>::load(xq_row_words, xds_row, u, regs);  ActOf<T>::dot(wregs, u, regs)
+// ---------------------------------------------------------------------------------
+struct ActRegs { uint32_t q[16]; float d[4]; float s[4]; };
+
+BL_HD void ld_act128(const uint32_t* p, uint32_t* o) {
+#if defined(__CUDA_ARCH__)
+  uint4 v = *reinterpret_cast<const uint4*>(p);
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+#else
+  __builtin_memcpy(o, p, 16);
+#endif
+}
+
+template <class T> struct ActOf {
+  // 64 consecutive values: Q4_K, Q5_K, Q8_0
+  static BL_HD void load(const uint32_t* xq, const F2* xds, int u, ActRegs& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ld_act128(xq + 16 * u + 4 * i, a.q + 4 * i);
+    a.d[0] = xds[2 * u].x; a.s[0] = xds[2 * u].y; a.d[1] = xds[2 * u + 1].x; a.s[1] = xds[2 * u + 1].y;
+  }
+  static BL_HD float dot(const typename Unit<T>::Regs& r, int u, const ActRegs& a) {
+    ActUnit au{a.q, a.d[0], a.s[0], a.d[1], a.s[1]};
+    if constexpr (T::kType == WT_Q8_0) return Q80::dot(r, au);
+    else return T::dot(r, u, au);
+  }
+};
+
+template <> struct ActOf<Q6K> {
+  static BL_HD void load(const uint32_t* xq, const F2* xds, int u, ActRegs& a) {
+    const int sb = u >> 2, n = (u >> 1) & 1, h = u & 1;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      ld_act128(xq + 64 * sb + (128 * n + 32 * g + 16 * h) / 4, a.q + 4 * g);
+      a.d[g] = xds[8 * sb + 4 * n + g].x;
+    }
+  }
+  static BL_HD float dot(const Q6K::Regs& r, int u, const ActRegs& a) {
+    const int n = (u >> 1) & 1, h = u & 1;
+    uint32_t c[4][4];
+    Q6K::codes(r, c);
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      int s = 0, sx = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s = dot4_us(c[g][i], a.q[4 * g + i], s);
+        sx = dot4(0x01010101u, a.q[4 * g + i], sx);
+      }
+      s -= 32 * sx;
+      acc += a.d[g] * (float)(Q6K::scale(r, 8 * n + 2 * g + h) * s);
+    }
+    return half_bits_to_float((uint16_t)r.d) * acc;
+  }
 };
 
 // Resident row size for a weight type and row length.

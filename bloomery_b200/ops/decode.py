@@ -88,21 +88,44 @@ def flash_decode(q, k_cache, v_cache, row_pos, row_seq, block_table, n_pages: in
     check(rc, "bl_flash_decode")
 
 
-def router(x, gain, eps: float, w: QWeight, bias, M: int, top_k: int, mode: int, renorm: bool, scale: float,
-           n_group: int, topk_group: int, logits, ids, wts, xq_out, xds_out, xn_out, counter, heat, fault,
-           layer: int) -> None:
-    rc = cuda().bl_router(p(x), L(x.stride(0)), p(gain), F(eps), p(w.data), I(w.wt), p(bias), I(w.k), I(w.rows), I(M),
-                          I(top_k), I(mode), I(1 if renorm else 0), F(scale), I(n_group), I(topk_group), p(logits),
-                          p(ids), p(wts), p(xq_out), p(xds_out), p(xn_out), p(counter), p(heat), p(fault), I(layer),
-                          stream())
+def router(x, gain, eps: float, w: QWeight, M: int, logits, xq_out, xds_out, xn_out, fault, layer: int) -> None:
+    """Router logits of M rows (RMSNorm folded in) + the q8 form of the normed rows."""
+    rc = cuda().bl_router(p(x), L(x.stride(0)), p(gain), F(eps), p(w.data), I(w.wt), I(w.k), I(w.rows), I(M),
+                          p(logits), p(xq_out), p(xds_out), p(xn_out), p(fault), I(layer), stream())
     check(rc, "bl_router")
 
 
+@dataclass
+class RouteRule:
+    """How logits become (ids, weights): softmax or sigmoid scores, optional selection bias,
+    renormalisation, scale, optional group-limited choice."""
+
+    top_k: int
+    mode: int = 0              # 0 softmax, 1 sigmoid
+    renorm: bool = True
+    scale: float = 1.0
+    n_group: int = 1
+    topk_group: int = 1
+    bias: Optional[torch.Tensor] = None
+
+
+def route_rows(logits, rule: RouteRule, M: int, ids, wts, heat, fault, layer: int) -> None:
+    rc = cuda().bl_route_rows(p(logits), p(rule.bias), I(logits.shape[-1]), I(M), I(rule.top_k), I(rule.mode),
+                              I(1 if rule.renorm else 0), F(rule.scale), I(rule.n_group), I(rule.topk_group), p(ids),
+                              p(wts), p(heat), p(fault), I(layer), stream())
+    check(rc, "bl_route_rows")
+
+
 def gate_up_sel(xq, xds, ids, slot_map, gate: QWeight, up: QWeight, n_expert: int, n_used: int, M: int, actq, actds,
-                act_f32, fault, layer: int) -> None:
-    rc = cuda().bl_gate_up_sel(p(xq), p(xds), p(ids), p(slot_map), p(gate.data), p(up.data), I(gate.wt), I(up.wt),
-                               I(gate.k), I(gate.rows), I(n_expert), I(n_used), I(M), p(actq), p(actds), p(act_f32),
-                               p(fault), I(layer), stream())
+                act_f32, fault, layer: int, *, route_logits=None, rule: Optional[RouteRule] = None, wts=None,
+                heat=None) -> None:
+    """gate·up·SwiGLU of the chosen experts.  With ``route_logits`` every block routes its own
+    row (and ids / wts / heat are written for the launches that follow); else ``ids`` is read."""
+    r = rule or RouteRule(n_used)
+    rc = cuda().bl_gate_up_sel(p(xq), p(xds), p(route_logits), p(r.bias), I(r.mode), I(1 if r.renorm else 0),
+                               F(r.scale), I(r.n_group), I(r.topk_group), p(ids), p(wts), p(heat), p(slot_map),
+                               p(gate.data), p(up.data), I(gate.wt), I(up.wt), I(gate.k), I(gate.rows), I(n_expert),
+                               I(n_used), I(M), p(actq), p(actds), p(act_f32), p(fault), I(layer), stream())
     check(rc, "bl_gate_up_sel")
 
 

@@ -150,13 +150,12 @@ class DecodeEngine:
             K.gemv([w.q[b + "attn_output.weight"]], M, x, xq=self.attn_q, xds=self.attn_ds, resid=x,
                    fault=self.fault, layer=il); n += 1
             if s.layer_is_moe(il):
-                K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"],
-                         w.f.get(b + "exp_probs_b.bias"), M, s.n_used, 0 if s.router_mode == "softmax" else 1,
-                         s.router_renorm, s.router_scale, s.n_group, s.topk_group, self.r_logits, self.r_ids,
-                         self.r_wts, self.xq, self.xds, None, self.counters[0:1], self.heat[il], self.fault, il); n += 1
+                K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
+                         self.xq, self.xds, None, self.fault, il); n += 1
                 K.gate_up_sel(self.xq, self.xds, self.r_ids, None, w.q[b + "ffn_gate_exps.weight"],
                               w.q[b + "ffn_up_exps.weight"], s.n_expert, s.n_used, M, self.actq, self.actds, None,
-                              self.fault, il); n += 1
+                              self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=self.r_wts,
+                              heat=self.heat[il]); n += 1
                 K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, None, w.q[b + "ffn_down_exps.weight"],
                                s.n_expert, s.n_used, M, x, None, x, self.fault, il); n += 1
             else:
@@ -175,6 +174,11 @@ class DecodeEngine:
                 K.advance_rows(self.tokens, self.row_pos, self.row_seq, self.tokens_out, M, self.hist, self.hist_cap,
                                self.counters[2:3]); n += 1
         return n
+
+    def _rule(self, il: int) -> "K.RouteRule":
+        s = self.spec
+        return K.RouteRule(s.n_used, 0 if s.router_mode == "softmax" else 1, s.router_renorm, s.router_scale,
+                           s.n_group, s.topk_group, self.w.f.get(f"blk.{il}.exp_probs_b.bias"))
 
     def _graph(self, M: int, head: bool, advance: bool) -> torch.cuda.CUDAGraph:
         key = (M, head, advance)

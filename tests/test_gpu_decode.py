@@ -69,24 +69,24 @@ def test_router_softmax_topk():
     from bloomery_b200.models.cpu_ref import rms_norm, route
     from bloomery_b200.models.spec import ModelSpec
     from bloomery_b200.ops import decode as K
-    from bloomery_b200.ops.decode import QWeight
+    from bloomery_b200.ops.decode import QWeight, RouteRule
     torch.manual_seed(2)
     H, E, k, M = 2048, 128, 8, 5
     w = torch.randn(E, H) * 0.05
     x = torch.randn(M, H)
-    gain = torch.ones(H)
+    gain = 1 + 0.1 * torch.randn(H)
     qw = QWeight(w.contiguous().view(torch.uint8).reshape(E, -1).to(DEV), "F32", H)
     logits = torch.zeros(M, E, device=DEV)
     ids = torch.zeros(M, k, dtype=torch.int32, device=DEV)
     wts = torch.zeros(M, k, device=DEV)
     xq = torch.zeros(M, H, dtype=torch.int8, device=DEV)
     xds = torch.zeros(M, H // 32, 2, device=DEV)
-    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
     heat = torch.zeros(E, dtype=torch.int32, device=DEV)
     fault = torch.full((1,), -1, dtype=torch.int32, device=DEV)
-    for _ in range(2):  # the ticket returns to rest, so a replay works
-        K.router(x.to(DEV), gain.to(DEV), 1e-6, qw, None, M, k, 0, True, 1.0, 1, 1, logits, ids, wts, xq, xds, None,
-                 counter, heat, fault, 0)
+    rule = RouteRule(k)
+    for _ in range(2):
+        K.router(x.to(DEV), gain.to(DEV), 1e-6, qw, M, logits, xq, xds, None, fault, 0)
+        K.route_rows(logits, rule, M, ids, wts, heat, fault, 0)
     xn = rms_norm(x, gain, 1e-6)
     ref_logits = xn @ w.T
     assert torch.allclose(logits.cpu(), ref_logits, rtol=1e-4, atol=1e-4)
@@ -96,14 +96,15 @@ def test_router_softmax_topk():
     assert torch.allclose(wts.cpu(), rw, rtol=1e-5, atol=1e-6)
     c, ds = Q.quantize_act_q8(xn)
     assert (xq.cpu() != c).float().mean() < 1e-3
-    assert int(heat.sum()) == 2 * M * k and int(counter) == 0 and int(fault) == -1
+    assert torch.allclose(xds.cpu(), ds, rtol=1e-3, atol=1e-6)
+    assert int(heat.sum()) == 2 * M * k and int(fault) == -1
 
 
 def test_router_sigmoid_groups_and_fault():
-    from bloomery_b200.models.cpu_ref import rms_norm, route
+    from bloomery_b200.models.cpu_ref import route
     from bloomery_b200.models.spec import ModelSpec
     from bloomery_b200.ops import decode as K
-    from bloomery_b200.ops.decode import QWeight
+    from bloomery_b200.ops.decode import QWeight, RouteRule
     torch.manual_seed(3)
     H, E, k, M = 512, 256, 8, 3
     w = torch.randn(E, H) * 0.05
@@ -115,10 +116,10 @@ def test_router_sigmoid_groups_and_fault():
     wts = torch.zeros(M, k, device=DEV)
     xq = torch.zeros(M, H, dtype=torch.int8, device=DEV)
     xds = torch.zeros(M, H // 32, 2, device=DEV)
-    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
     fault = torch.full((1,), -1, dtype=torch.int32, device=DEV)
-    K.router(x.to(DEV), torch.ones(H, device=DEV), 1e-6, qw, bias.to(DEV), M, k, 1, True, 2.5, 8, 4, logits, ids, wts,
-             xq, xds, None, counter, None, fault, 0)
+    rule = RouteRule(k, 1, True, 2.5, 8, 4, bias.to(DEV))
+    K.router(x.to(DEV), torch.ones(H, device=DEV), 1e-6, qw, M, logits, xq, xds, None, fault, 0)
+    K.route_rows(logits, rule, M, ids, wts, None, fault, 0)
     spec = ModelSpec(n_expert=E, n_used=k, router_mode="sigmoid", router_renorm=True, router_scale=2.5, n_group=8,
                      topk_group=4)
     rid, rw = route(logits.cpu(), spec, bias)
@@ -127,10 +128,40 @@ def test_router_sigmoid_groups_and_fault():
     # a non-finite logit raises the router fault, writes NaN weights and never traps
     xb = x.clone()
     xb[1, 3] = float("nan")
-    K.router(xb.to(DEV), torch.ones(H, device=DEV), 1e-6, qw, bias.to(DEV), M, k, 1, True, 2.5, 8, 4, logits, ids, wts,
-             xq, xds, None, counter, None, fault, 5)
+    K.router(xb.to(DEV), torch.ones(H, device=DEV), 1e-6, qw, M, logits, xq, xds, None, fault, 5)
+    K.route_rows(logits, rule, M, ids, wts, None, fault, 5)
     assert (int(fault) & 0xFFFFFFFF) == (5 << 8 | 3)
     assert torch.isnan(wts[1]).all() and not torch.isnan(wts[0]).any()
+
+
+def test_gate_up_routes_like_route_rows():
+    """The routing done inside gate_up (from logits) equals the standalone routing launch."""
+    from bloomery_b200.ops import decode as K
+    from bloomery_b200.ops.decode import RouteRule
+    torch.manual_seed(8)
+    H, I, E, k, M = 512, 256, 16, 4, 3
+    gate, _ = _qw(torch.randn(E, I, H) * 0.03, "Q4_K")
+    up, _ = _qw(torch.randn(E, I, H) * 0.03, "Q4_K")
+    x = torch.randn(M, H)
+    c, ds = Q.quantize_act_q8(x)
+    logits = torch.randn(M, E, device=DEV)
+    fault = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    rule = RouteRule(k)
+    ids0 = torch.zeros(M, k, dtype=torch.int32, device=DEV); w0 = torch.zeros(M, k, device=DEV)
+    K.route_rows(logits, rule, M, ids0, w0, None, fault, 0)
+    outs = []
+    for routed in (False, True):
+        ids = ids0.clone() if not routed else torch.zeros_like(ids0)
+        wts = torch.zeros(M, k, device=DEV)
+        heat = torch.zeros(E, dtype=torch.int32, device=DEV)
+        actq = torch.zeros(M, k, I, dtype=torch.int8, device=DEV)
+        actds = torch.zeros(M, k, I // 32, 2, device=DEV)
+        K.gate_up_sel(c.to(DEV), ds.to(DEV), ids, None, gate, up, E, k, M, actq, actds, None, fault, 0,
+                      route_logits=logits if routed else None, rule=rule, wts=wts, heat=heat)
+        outs.append((actq.clone(), actds.clone()))
+        if routed:
+            assert torch.equal(ids, ids0) and torch.equal(wts, w0) and int(heat.sum()) == M * k
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
 
 
 @pytest.mark.parametrize("gt,dt", [("Q4_K", "Q4_K"), ("Q4_K", "Q6_K"), ("Q8_0", "Q8_0"), ("Q5_K", "Q5_K")])
