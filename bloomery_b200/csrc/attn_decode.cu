@@ -332,3 +332,56 @@ int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, co
 }
 
 }  // extern "C"
+
+// ======================================================================================
+// Allocation-free variant of bl_flash_decode (declared in bloomery_no_alloc.h).
+//
+// Some hosts of this library may not allocate device memory at the moment they need
+// attention: code running inside someone else's memory plan (a serving process whose
+// whole HBM budget was handed out at start-up and whose allocator is closed), a real-time
+// loop where a cudaMalloc would stall every stream of the device, or a plug-in that is
+// given input and output buffers and nothing else.  The split-K partials that
+// bl_flash_decode takes from the caller live here in one file-scope device array instead.
+//
+// Limit: M * n_q * n_seg <= kStaticCells (8192) and head <= 128, i.e. 4 MiB + 64 KiB of
+// device memory, held by every GPU on which this library is loaded, until the process
+// ends.  Larger shapes are refused with BL_ERR_LIMIT; nothing is launched.
+//
+// The array is shared by every call and keeps the last call's contents.  Nothing in it
+// has to start at zero: the segment kernel writes every cell the merge kernel reads
+// (empty segments write weight 0).  Two calls that overlap on the GPU (different streams,
+// or two host threads) race on it; callers serialise them on one stream.
+//
+// The first call on a device resolves the array's device address with
+// cudaGetSymbolAddress (in host code the array's name is only a host-side handle, not a
+// device pointer).  Make that first call before any stream capture begins.
+// ======================================================================================
+namespace bl {
+constexpr long kStaticCells = 8192;
+constexpr int kStaticHead = 128;
+static __device__ __align__(256) float g_flash_static_scratch[kStaticCells * (kStaticHead + 2)];
+static float* g_flash_static_ptr[64] = {nullptr};
+}  // namespace bl
+
+extern "C" int bl_flash_decode_static(const float* q, const void* k_cache, const void* v_cache, const int* row_pos,
+                                      const int* row_seq, const int* block_table, int max_pages, int n_pages, int head,
+                                      int n_q, int n_kv, int M, int n_seg, int ctx_limit, float* out, int8_t* outq,
+                                      float* outds, unsigned* fault, int layer, cudaStream_t st) {
+  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
+  BL_REQUIRE(M >= 1 && n_q >= 1 && n_seg >= 1, BL_ERR_SHAPE);
+  BL_REQUIRE((long)M * n_q * n_seg <= kStaticCells, BL_ERR_LIMIT);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  BL_REQUIRE(dev >= 0 && dev < 64, BL_ERR_LIMIT);
+  if (g_flash_static_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_flash_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_flash_static_ptr[dev] = p;
+  }
+  float* part_ml = g_flash_static_ptr[dev];                       // kStaticCells * 2 floats
+  float* part_acc = g_flash_static_ptr[dev] + kStaticCells * 2;   // kStaticCells * head floats
+  return bl_flash_decode(q, k_cache, v_cache, row_pos, row_seq, block_table, max_pages, n_pages, head, n_q, n_kv, M,
+                         n_seg, ctx_limit, part_ml, part_acc, out, outq, outds, fault, layer, st);
+}
