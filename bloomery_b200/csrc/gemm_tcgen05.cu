@@ -1,0 +1,433 @@
+// bf16 grouped GEMM on the 5th-generation tensor cores (sm_100a only):
+//   C[g][m, n] = sum_k A[m, k] * B[g][n, k]        fp32 accumulate in tensor memory
+//
+//   * operands staged by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into
+//     a 4-stage shared-memory ring; one elected thread issues tcgen05.mma (M=128, N=128,
+//     K=16 per instruction) with accumulators in TMEM; four epilogue warps read them back
+//     with tcgen05.ld while the next tile's main loop already runs (two TMEM buffers);
+//   * persistent: one CTA per SM walks a device-resident tile table, so row counts that
+//     are only known on the device (tokens per expert) never reach the host and the launch
+//     is capturable in a CUDA graph;
+//   * "dual" mode multiplies A with two B matrices (gate and up) in the same main loop and
+//     the epilogue writes silu(gate) * up, so the SwiGLU activation never round-trips HBM;
+//   * the epilogue can scatter: row r of the product goes to row dst_row[r] of the output,
+//     scaled by row_scale[r] -- the expert-parallel "combine" is this store aimed at the
+//     owning GPU's buffer (a peer pointer works: plain st.global over NVLink).
+//
+// Every wait (mbarrier phases) is bounded by the global timer; on expiry the CTA raises
+// status word 1, drains what it has in flight, frees its TMEM and returns.
+//
+// Role of this file in the reference: the grouped tensor-core GEMM of
+// crates/gpu/src/gemm/{grouped,kernels}.rs (mma.sync int8 tiles walking a route table)
+// and bf16_mma_gemm in crates/gpu/src/q8f32.rs; the reference has no sm_100 path at all.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace bl {
+
+constexpr int BM = 128, BN = 128, BK = 64;     // BK * 2 bytes = 128 = one swizzle atom row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int TILE_A_BYTES = BM * BK * 2;      // 16 KiB
+constexpr int TILE_B_BYTES = BN * BK * 2;      // 16 KiB
+constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+
+struct MTile { int group, row0, row_end, pad; };
+
+struct GemmArgs {
+  int N, K;
+  int tiles_n;
+  const MTile* mtiles;        // device table of 128-row tiles
+  const int* n_mtiles;        // device count
+  int max_mtiles;
+  int dual;                   // 1: B2 is used and the epilogue writes silu(A B^T) * (A B2^T)
+  float* c_f32;               // one of c_f32 / c_bf16
+  __nv_bfloat16* c_bf16;
+  long ldc;
+  const int* dst_row;         // optional scatter: output row of product row r (< 0 = drop)
+  const float* row_scale;     // optional per-row factor
+  const float* resid;         // optional addend, indexed like the output
+  long ldr;
+  unsigned* status;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait for the phase of parity `parity`; false when the limit ran out or another
+// role already gave up (abort flag set).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(bar);
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((it & 63) == 63) {
+      if (*abort_flag) return false;
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address
+  d |= (uint64_t)1 << 16;                               // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                               // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+  return d;
+}
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, M x N tile
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- the kernel ------------------------------------------------------------------------
+// 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 = epilogue
+// (their warp id modulo 4 covers the four 32-lane quarters of tensor memory).
+template <bool DUAL>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_b2, const GemmArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr int STAGE_BYTES = TILE_A_BYTES + (DUAL ? 2 : 1) * TILE_B_BYTES;
+  constexpr int ACC_COLS = DUAL ? 2 * BN : BN;         // TMEM columns per accumulator buffer
+  constexpr int TMEM_COLS = 2 * ACC_COLS;              // two buffers: 256 or 512 columns
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  pdl_launch();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  const int n_mt = min(*a.n_mtiles, a.max_mtiles);
+  const int total_tiles = n_mt * a.tiles_n;
+  const int kblocks = a.K / BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      int issued = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        const MTile mt = a.mtiles[t / a.tiles_n];
+        const int n0 = (t % a.tiles_n) * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) break;
+          uint8_t* sa = smem + (size_t)stage * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tma_a, kb * BK, mt.row0, &full_bar[stage]);
+          tma_load_3d(sa + TILE_A_BYTES, &tma_b, kb * BK, n0, mt.group, &full_bar[stage]);
+          if (DUAL) tma_load_3d(sa + TILE_A_BYTES + TILE_B_BYTES, &tma_b2, kb * BK, n0, mt.group, &full_bar[stage]);
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (*abort_flag) {
+        // our own copies may still be landing in shared memory: give the last ring of them a bounded wait
+        for (int s = 0; s < STAGES && s < issued; ++s) {
+          unsigned long long t0 = globaltimer();
+          while (globaltimer() - t0 < 2000000ull) {
+            uint32_t ok;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(smem_u32(&full_bar[s])), "r"(0u) : "memory");
+            if (ok) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN);
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++it) {
+        const int ab = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[ab], acc_phase ^ 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + ab * ACC_COLS;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+          const uint64_t da = umma_desc(sa), db = umma_desc(sa + TILE_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            umma_bf16(d0, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc, acc);
+            if (DUAL) {
+              const uint64_t db2 = umma_desc(sa + TILE_A_BYTES + TILE_B_BYTES);
+              umma_bf16(d0 + BN, da + (uint64_t)(k * UMMA_K * 2 / 16), db2 + (uint64_t)(k * UMMA_K * 2 / 16), idesc, acc);
+            }
+          }
+          umma_commit(&empty_bar[stage]);      // the stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[ab]);            // accumulator complete
+      }
+    }
+  } else {
+    const int q = warp & 3;                    // TMEM lane quarter of this warp
+    int it = 0;
+    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++it) {
+      const int ab = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const MTile mt = a.mtiles[t / a.tiles_n];
+      const int n0 = (t % a.tiles_n) * BN;
+      if (!mbar_wait(&acc_full[ab], acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int r = mt.row0 + q * 32 + lane;                 // product row of this thread
+      const bool live = r < mt.row_end;
+      long orow = r;
+      float scale = 1.0f;
+      if (live && a.dst_row) orow = a.dst_row[r];
+      if (live && a.row_scale) scale = a.row_scale[r];
+      const bool store = live && orow >= 0;
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + ab * ACC_COLS;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tbase + c * 32, v);
+        float f[32];
+        if (DUAL) {
+          uint32_t u[32];
+          tmem_ld32(tbase + BN + c * 32, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float g = __uint_as_float(v[i]);
+            f[i] = (g / (1.0f + __expf(-g))) * __uint_as_float(u[i]);
+          }
+        } else {
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+        }
+        const int col = n0 + c * 32;
+        if (store && col < a.N) {
+          if (a.row_scale) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] *= scale;
+          }
+          if (a.resid) {
+            const float* rr = a.resid + orow * a.ldr + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 x = *reinterpret_cast<const float4*>(rr + i);
+              f[i] += x.x; f[i + 1] += x.y; f[i + 2] += x.z; f[i + 3] += x.w;
+            }
+          }
+          if (a.c_f32) {
+            float* o = a.c_f32 + orow * a.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+          } else {
+            __nv_bfloat16* o = a.c_bf16 + orow * a.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 pk;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(f[i], f[i + 1]), p1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]), p3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
+              pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
+              pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
+              *reinterpret_cast<uint4*>(o + i) = pk;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[ab]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && s_abort && a.status) atomicMax(a.status, 1u);
+}
+
+// ---- tile table ----------------------------------------------------------------------
+// group_rows[g] rows for group g, laid out back to back in A (offsets = prefix sums).
+__global__ void build_mtiles_kernel(const int* group_rows, int n_groups, MTile* mtiles, int* n_mtiles, int max_mtiles,
+                                    int* group_offset_out) {
+  pdl_wait();
+  pdl_launch();
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int off = 0, n = 0;
+  for (int g = 0; g < n_groups; ++g) {
+    const int rows = group_rows[g];
+    if (group_offset_out) group_offset_out[g] = off;
+    for (int r = 0; r < rows; r += BM) {
+      if (n < max_mtiles) mtiles[n] = MTile{g, off + r, off + rows, 0};
+      ++n;
+    }
+    off += rows;
+  }
+  if (group_offset_out) group_offset_out[n_groups] = off;
+  *n_mtiles = n < max_mtiles ? n : max_mtiles;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                    const cuuint32_t* box) {
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = cuTensorMapEncodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims,
+                                      strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+}  // namespace bl
+
+using namespace bl;
+
+extern "C" {
+
+// Fill the tile table for a grouped GEMM from per-group row counts on the device.
+int bl_gemm_build_tiles(const int* group_rows, int n_groups, void* mtiles, int* n_mtiles, int max_mtiles,
+                        int* group_offsets, cudaStream_t st) {
+  BL_REQUIRE(n_groups >= 1 && max_mtiles >= 1, BL_ERR_SHAPE);
+  return (int)launch(build_mtiles_kernel, dim3(1), dim3(32), 0, st, group_rows, n_groups, (MTile*)mtiles, n_mtiles,
+                     max_mtiles, group_offsets);
+}
+
+// C = A * B[g]^T per 128-row tile of the table.  A: [rows_a, K] bf16 (lda elements);
+// B, B2: [n_groups, N, K] bf16.  Output row r -> dst_row[r] (or r), times row_scale[r],
+// plus resid.  Exactly one of c_f32 / c_bf16.  status: device word, set to 1 if a wait ran out.
+int bl_gemm_bf16(const void* A, long lda, long rows_a, const void* B, const void* B2, int n_groups, int N, int K,
+                 const void* mtiles, const int* n_mtiles, int max_mtiles, float* c_f32, void* c_bf16, long ldc,
+                 const int* dst_row, const float* row_scale, const float* resid, long ldr, unsigned* status,
+                 int sm_count, cudaStream_t st) {
+  BL_REQUIRE(K >= BK && K % BK == 0 && N >= 32 && N % 32 == 0, BL_ERR_SHAPE);
+  BL_REQUIRE(lda % 8 == 0 && rows_a >= 1 && n_groups >= 1, BL_ERR_SHAPE);
+  BL_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)B & 15) == 0 && ((uintptr_t)B2 & 15) == 0, BL_ERR_ALIGN);
+  BL_REQUIRE((c_f32 != nullptr) != (c_bf16 != nullptr), BL_ERR_SHAPE);
+  BL_REQUIRE(ldc % 8 == 0 && (!resid || ldr % 4 == 0), BL_ERR_SHAPE);
+  BL_REQUIRE(((uintptr_t)c_f32 & 15) == 0 && ((uintptr_t)c_bf16 & 15) == 0 && ((uintptr_t)resid & 15) == 0, BL_ERR_ALIGN);
+  CUtensorMap ma, mb, mb2;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows_a};
+    cuuint64_t str[1] = {(cuuint64_t)lda * 2};
+    cuuint32_t box[2] = {BK, BM};
+    int rc = make_map(&ma, A, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)N, (cuuint64_t)n_groups};
+    cuuint64_t str[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)N};
+    cuuint32_t box[3] = {BK, BN, 1};
+    int rc = make_map(&mb, B, 3, dims, str, box);
+    if (rc) return rc;
+    rc = make_map(&mb2, B2 ? B2 : B, 3, dims, str, box);
+    if (rc) return rc;
+  }
+  GemmArgs a{};
+  a.N = N; a.K = K; a.tiles_n = (N + BN - 1) / BN;
+  a.mtiles = (const MTile*)mtiles; a.n_mtiles = n_mtiles; a.max_mtiles = max_mtiles;
+  a.dual = B2 ? 1 : 0;
+  a.c_f32 = c_f32; a.c_bf16 = (__nv_bfloat16*)c_bf16; a.ldc = ldc;
+  a.dst_row = dst_row; a.row_scale = row_scale; a.resid = resid; a.ldr = ldr; a.status = status;
+  long tiles = (long)max_mtiles * a.tiles_n;
+  int grid = (int)(tiles < sm_count ? tiles : sm_count);
+  if (B2) {
+    const size_t smem = (size_t)STAGES * (TILE_A_BYTES + 2 * TILE_B_BYTES) + 1024;
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); set = true; }
+    return (int)launch(gemm_bf16_kernel<true>, dim3(grid), dim3(192), smem, st, ma, mb, mb2, a);
+  }
+  const size_t smem = (size_t)STAGES * (TILE_A_BYTES + TILE_B_BYTES) + 1024;
+  static bool set1 = false;
+  if (!set1) { cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); set1 = true; }
+  return (int)launch(gemm_bf16_kernel<false>, dim3(grid), dim3(192), smem, st, ma, mb, mb2, a);
+}
+
+}  // extern "C"

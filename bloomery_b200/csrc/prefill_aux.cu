@@ -1,0 +1,187 @@
+// Helpers of the prompt (prefill) path around the tcgen05 GEMM: block-quantised weights
+// expanded to bf16, RMSNorm to bf16, the expert permutation (count, scatter, gather) and
+// the slot-ordered combine.  The reference groups prompt rows by expert on the device in
+// gemm_route / grouped_buckets (crates/gpu/src/gemm/kernels.rs:88, q4k_sel.rs:492) and sums
+// slots in ascending order (crates/gpu/src/arch/qwen3moe/experts.rs:36-45).
+#include "common.cuh"
+
+namespace bl {
+
+template <class T>
+__device__ __forceinline__ void expand_units(const uint8_t* w, long rows, int K, __nv_bfloat16* out) {
+  using U = Unit<T>;
+  const int upr = K / 64;
+  const long total = rows * upr;
+  const long rb = resident_row_bytes(T::kType, K);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / upr;
+    const int u = (int)(i - r * upr);
+    typename U::Regs regs;
+    U::loadu(w + r * rb, u, K, regs);
+    float v[64];
+    U::decodeu(regs, u, v);
+    __nv_bfloat16* o = out + r * K;
+    if (T::kType == WT_Q6_K) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int p0 = U::pos(u, 16 * g);
+#pragma unroll
+        for (int e = 0; e < 16; e += 2)
+          *reinterpret_cast<__nv_bfloat162*>(o + p0 + e) = __floats2bfloat162_rn(v[16 * g + e], v[16 * g + e + 1]);
+      }
+    } else {
+      const int p0 = 64 * u;
+#pragma unroll
+      for (int e = 0; e < 64; e += 2)
+        *reinterpret_cast<__nv_bfloat162*>(o + p0 + e) = __floats2bfloat162_rn(v[e], v[e + 1]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) dequant_bf16_kernel(const uint8_t* w, int wtype, long rows, int K, __nv_bfloat16* out) {
+  pdl_wait();
+  pdl_launch();
+  switch (wtype) {
+    case WT_Q4_K: expand_units<Q4K>(w, rows, K, out); break;
+    case WT_Q5_K: expand_units<Q5K>(w, rows, K, out); break;
+    case WT_Q6_K: expand_units<Q6K>(w, rows, K, out); break;
+    case WT_Q8_0: expand_units<Q80>(w, rows, K, out); break;
+    default: {
+      const long total = rows * (long)K;
+      for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        float v;
+        if (wtype == WT_F32) v = reinterpret_cast<const float*>(w)[i];
+        else if (wtype == WT_F16) v = __half2float(reinterpret_cast<const __half*>(w)[i]);
+        else v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]);
+        out[i] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+// out[t, :] = bf16(RMSNorm(x[t, :]) * gain); gain == null: plain cast
+__global__ void __launch_bounds__(256) rmsnorm_bf16_kernel(const float* x, long x_stride, const float* gain, float eps, int K,
+                                                          __nv_bfloat16* out, long out_stride) {
+  __shared__ double red[8];
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const float* xr = x + (long)t * x_stride;
+  float scale = 1.0f;
+  if (gain) {
+    float ss = 0.f;
+    for (int i = tid; i < K; i += 256) { float v = xr[i]; ss += v * v; }
+    double tot = warp_sum_d((double)ss);
+    if ((tid & 31) == 0) red[tid >> 5] = tot;
+    __syncthreads();
+    double all = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) all += red[w];
+    scale = 1.0f / sqrtf((float)(all / (double)K) + eps);
+  }
+  for (int i = tid; i < K; i += 256)
+    out[(long)t * out_stride + i] = __float2bfloat16_rn(gain ? xr[i] * scale * gain[i] : xr[i]);
+}
+
+__global__ void moe_count_kernel(const int* ids, int n, int E, int* counts) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { const int e = ids[i]; if (e >= 0 && e < E) atomicAdd(counts + e, 1); }
+}
+
+// pos = offsets[e] + cursor[e]++ ; dst_row[pos] = flat slot index i; row_scale[pos] = weight
+__global__ void moe_scatter_kernel(const int* ids, const float* wts, int n, int E, const int* offsets, int* cursor,
+                                   int* pos_of, int* dst_row, float* row_scale) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int e = ids[i];
+  if (e < 0 || e >= E) { pos_of[i] = -1; return; }
+  const int p = offsets[e] + atomicAdd(cursor + e, 1);
+  pos_of[i] = p;
+  dst_row[p] = i;
+  row_scale[p] = wts[i];
+}
+
+// A_perm[p, :] = src[dst_row[p] / k, :]  (bf16 rows of K values, 16-byte vectors)
+__global__ void __launch_bounds__(256) gather_rows_bf16_kernel(const __nv_bfloat16* src, long src_stride, const int* dst_row,
+                                                              const int* n_rows, int k, int K, __nv_bfloat16* out) {
+  pdl_wait();
+  pdl_launch();
+  const int p = blockIdx.x;
+  if (p >= *n_rows) return;
+  const int t = dst_row[p] / k;
+  const uint4* s = reinterpret_cast<const uint4*>(src + (long)t * src_stride);
+  uint4* o = reinterpret_cast<uint4*>(out + (long)p * K);
+  for (int i = threadIdx.x; i < K / 8; i += 256) o[i] = s[i];
+}
+
+// x[t, :] = resid[t, :] + sum_j slot_out[t*k + j, :] in ascending j (rows of dropped slots are skipped)
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* slot_out, const int* pos_of, int k, int H,
+                                                         const float* resid, long resid_stride, float* out, long out_stride) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x * 4; i < H; i += 1024) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+      if (pos_of[t * k + j] < 0) continue;
+      const float4 v = *reinterpret_cast<const float4*>(slot_out + ((long)t * k + j) * H + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (resid) {
+      const float4 r = *reinterpret_cast<const float4*>(resid + (long)t * resid_stride + i);
+      acc.x += r.x; acc.y += r.y; acc.z += r.z; acc.w += r.w;
+    }
+    *reinterpret_cast<float4*>(out + (long)t * out_stride + i) = acc;
+  }
+}
+
+}  // namespace bl
+
+using namespace bl;
+
+extern "C" {
+
+int bl_dequant_bf16(const void* w, int wtype, long rows, int K, void* out, cudaStream_t st) {
+  BL_REQUIRE(rows >= 1 && K % 64 == 0, BL_ERR_SHAPE);
+  BL_REQUIRE(resident_row_bytes(wtype, K) > 0, BL_ERR_TYPE);
+  long work = rows * (K / 64);
+  int grid = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+  return (int)launch(dequant_bf16_kernel, dim3(grid), dim3(256), 0, st, (const uint8_t*)w, wtype, rows, K, (__nv_bfloat16*)out);
+}
+
+int bl_rmsnorm_bf16(const float* x, long x_stride, const float* gain, float eps, int T, int K, void* out, long out_stride,
+                    cudaStream_t st) {
+  BL_REQUIRE(T >= 1 && K >= 1, BL_ERR_SHAPE);
+  return (int)launch(rmsnorm_bf16_kernel, dim3(T), dim3(256), 0, st, x, x_stride, gain, eps, K, (__nv_bfloat16*)out, out_stride);
+}
+
+int bl_moe_count(const int* ids, int n, int E, int* counts, cudaStream_t st) {
+  BL_REQUIRE(n >= 1 && E >= 1, BL_ERR_SHAPE);
+  return (int)launch(moe_count_kernel, dim3((n + 255) / 256), dim3(256), 0, st, ids, n, E, counts);
+}
+
+int bl_moe_scatter(const int* ids, const float* wts, int n, int E, const int* offsets, int* cursor, int* pos_of,
+                   int* dst_row, float* row_scale, cudaStream_t st) {
+  BL_REQUIRE(n >= 1 && E >= 1, BL_ERR_SHAPE);
+  return (int)launch(moe_scatter_kernel, dim3((n + 255) / 256), dim3(256), 0, st, ids, wts, n, E, offsets, cursor, pos_of,
+                     dst_row, row_scale);
+}
+
+int bl_gather_rows_bf16(const void* src, long src_stride, const int* dst_row, const int* n_rows, int max_rows, int k, int K,
+                        void* out, cudaStream_t st) {
+  BL_REQUIRE(max_rows >= 1 && K % 8 == 0 && src_stride % 8 == 0, BL_ERR_SHAPE);
+  return (int)launch(gather_rows_bf16_kernel, dim3(max_rows), dim3(256), 0, st, (const __nv_bfloat16*)src, src_stride, dst_row,
+                     n_rows, k, K, (__nv_bfloat16*)out);
+}
+
+int bl_moe_combine(const float* slot_out, const int* pos_of, int T, int k, int H, const float* resid, long resid_stride,
+                   float* out, long out_stride, cudaStream_t st) {
+  BL_REQUIRE(T >= 1 && H % 4 == 0, BL_ERR_SHAPE);
+  return (int)launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, slot_out, pos_of, k, H, resid, resid_stride, out, out_stride);
+}
+
+}  // extern "C"

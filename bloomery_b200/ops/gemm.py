@@ -1,0 +1,89 @@
+"""Python face of the tcgen05 grouped GEMM (``csrc/gemm_tcgen05.cu``) and its helpers
+(``csrc/prefill_aux.cu``)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ._lib import F, I, L, check, cuda, p, stream
+from .decode import QWeight, sm_count
+
+BM = 128
+
+
+class TileTable:
+    """Device-resident table of 128-row tiles of a (grouped) GEMM."""
+
+    def __init__(self, max_rows: int, n_groups: int, device):
+        self.max_mtiles = max_rows // BM + n_groups + 1
+        self.n_groups = n_groups
+        self.mtiles = torch.zeros(self.max_mtiles, 4, dtype=torch.int32, device=device)
+        self.n_mtiles = torch.zeros(1, dtype=torch.int32, device=device)
+        self.offsets = torch.zeros(n_groups + 1, dtype=torch.int32, device=device)
+
+    def build(self, group_rows: torch.Tensor) -> None:
+        """group_rows int32 [n_groups] on the device; rows of group g follow group g-1 in A."""
+        check(cuda().bl_gemm_build_tiles(p(group_rows), I(self.n_groups), p(self.mtiles), p(self.n_mtiles),
+                                         I(self.max_mtiles), p(self.offsets), stream()), "bl_gemm_build_tiles")
+
+    @classmethod
+    def dense(cls, rows: int, device) -> "TileTable":
+        t = cls(rows, 1, device)
+        t.build(torch.tensor([rows], dtype=torch.int32, device=device))
+        return t
+
+
+def gemm_bf16(A: torch.Tensor, B: torch.Tensor, tiles: TileTable, *, out_f32: Optional[torch.Tensor] = None,
+              out_bf16: Optional[torch.Tensor] = None, B2: Optional[torch.Tensor] = None, dst_row=None, row_scale=None,
+              resid=None, status: Optional[torch.Tensor] = None) -> None:
+    """C = A @ B[g].T per tile.  A [rows, K] bf16; B (and B2) [G, N, K] or [N, K] bf16.
+    With B2 the output is silu(A B^T) * (A B2^T)."""
+    assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.stride(-1) == 1 and B.is_contiguous()
+    if B.dim() == 2:
+        B = B[None]
+        B2 = B2[None] if B2 is not None else None
+    G, N, Kd = B.shape
+    out = out_f32 if out_f32 is not None else out_bf16
+    rc = cuda().bl_gemm_bf16(p(A), L(A.stride(0)), L(A.shape[0]), p(B), p(B2), I(G), I(N), I(Kd), p(tiles.mtiles),
+                             p(tiles.n_mtiles), I(tiles.max_mtiles), p(out_f32), p(out_bf16), L(out.stride(0)),
+                             p(dst_row), p(row_scale), p(resid), L(resid.stride(0) if resid is not None else 0),
+                             p(status), I(sm_count()), stream())
+    check(rc, "bl_gemm_bf16")
+
+
+def dequant_bf16(w: QWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Expand a resident quantised weight (matrix or stack) to bf16 [..., rows, K]."""
+    lead = w.data.shape[:-1]
+    rows = 1
+    for d in lead:
+        rows *= d
+    if out is None:
+        out = torch.empty(*lead, w.k, dtype=torch.bfloat16, device=w.data.device)
+    check(cuda().bl_dequant_bf16(p(w.data), I(w.wt), L(rows), I(w.k), p(out), stream()), "bl_dequant_bf16")
+    return out
+
+
+def rmsnorm_bf16(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float, out: torch.Tensor) -> None:
+    check(cuda().bl_rmsnorm_bf16(p(x), L(x.stride(0)), p(gain), F(eps), I(x.shape[0]), I(x.shape[1]), p(out),
+                                 L(out.stride(0)), stream()), "bl_rmsnorm_bf16")
+
+
+def moe_count(ids: torch.Tensor, E: int, counts: torch.Tensor) -> None:
+    check(cuda().bl_moe_count(p(ids), I(ids.numel()), I(E), p(counts), stream()), "bl_moe_count")
+
+
+def moe_scatter(ids, wts, E: int, offsets, cursor, pos_of, dst_row, row_scale) -> None:
+    check(cuda().bl_moe_scatter(p(ids), p(wts), I(ids.numel()), I(E), p(offsets), p(cursor), p(pos_of), p(dst_row),
+                                p(row_scale), stream()), "bl_moe_scatter")
+
+
+def gather_rows_bf16(src, dst_row, n_rows, max_rows: int, k: int, out) -> None:
+    check(cuda().bl_gather_rows_bf16(p(src), L(src.stride(0)), p(dst_row), p(n_rows), I(max_rows), I(k),
+                                     I(src.shape[1]), p(out), stream()), "bl_gather_rows_bf16")
+
+
+def moe_combine(slot_out, pos_of, T: int, k: int, resid, out) -> None:
+    check(cuda().bl_moe_combine(p(slot_out), p(pos_of), I(T), I(k), I(out.shape[1]), p(resid),
+                                L(resid.stride(0) if resid is not None else 0), p(out), L(out.stride(0)), stream()),
+          "bl_moe_combine")

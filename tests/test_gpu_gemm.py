@@ -1,0 +1,123 @@
+"""tcgen05 / TMEM / TMA grouped GEMM against torch fp32 matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 512), (300, 768, 2048), (1000, 5120, 2048), (77, 2048, 768)])
+def test_dense_gemm_f32_out(M, N, K):
+    from bloomery_b200.ops import gemm as G
+    torch.manual_seed(0)
+    A = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()
+    C = torch.full((M, N), float("nan"), device=DEV)
+    st = _status()
+    G.gemm_bf16(A, B, G.TileTable.dense(M, DEV), out_f32=C, status=st)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    ref = A.float() @ B.float().T
+    assert torch.allclose(C, ref, rtol=1e-3, atol=1e-2), (C - ref).abs().max()
+
+
+def test_dense_gemm_bf16_out_resid_and_rerun():
+    from bloomery_b200.ops import gemm as G
+    torch.manual_seed(1)
+    M, N, K = 513, 2048, 4096
+    A = (torch.randn(M, K, device=DEV) * 0.1).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    R = torch.randn(M, N, device=DEV)
+    C = torch.zeros(M, N, device=DEV)
+    st = _status()
+    tiles = G.TileTable.dense(M, DEV)
+    G.gemm_bf16(A, B, tiles, out_f32=C, resid=R, status=st)
+    ref = A.float() @ B.float().T + R
+    assert torch.allclose(C, ref, rtol=1e-3, atol=2e-2)
+    C2 = torch.zeros_like(C)
+    G.gemm_bf16(A, B, tiles, out_f32=C2, resid=R, status=st)
+    assert torch.equal(C, C2)                                   # bit-identical rerun
+    Cb = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    G.gemm_bf16(A, B, tiles, out_bf16=Cb, status=st)
+    assert torch.allclose(Cb.float(), (A.float() @ B.float().T), rtol=2e-2, atol=5e-2)
+    assert int(st) == 0
+
+
+def test_grouped_dual_swiglu_and_scatter():
+    """The MoE prompt path: rows grouped by expert, gate/up fused with SwiGLU, down scattered with weights."""
+    from bloomery_b200.ops import gemm as G
+    torch.manual_seed(2)
+    E, H, I_, T, k = 8, 512, 256, 200, 2
+    ids = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
+    ids[5, 1] = -1                                              # a slot served elsewhere
+    wts = torch.rand(T, k, device=DEV)
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+    Wg = (torch.randn(E, I_, H, device=DEV) * 0.1).bfloat16()
+    Wu = (torch.randn(E, I_, H, device=DEV) * 0.1).bfloat16()
+    Wd = (torch.randn(E, H, I_, device=DEV) * 0.1).bfloat16()
+    n = T * k
+    counts = torch.zeros(E, dtype=torch.int32, device=DEV)
+    cursor = torch.zeros(E, dtype=torch.int32, device=DEV)
+    pos_of = torch.zeros(n, dtype=torch.int32, device=DEV)
+    cap = n + 128
+    dst_row = torch.full((cap,), -1, dtype=torch.int32, device=DEV)
+    row_scale = torch.zeros(cap, device=DEV)
+    tiles = G.TileTable(n, E, DEV)
+    G.moe_count(ids, E, counts)
+    tiles.build(counts)
+    G.moe_scatter(ids, wts, E, tiles.offsets, cursor, pos_of, dst_row, row_scale)
+    Ap = torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV)
+    G.gather_rows_bf16(x, dst_row, tiles.offsets[E:E + 1], cap, k, Ap)
+    act = torch.zeros(cap, I_, dtype=torch.bfloat16, device=DEV)
+    st = _status()
+    G.gemm_bf16(Ap, Wg, tiles, out_bf16=act, B2=Wu, status=st)
+    slot_out = torch.zeros(n, H, device=DEV)
+    G.gemm_bf16(act, Wd, tiles, out_f32=slot_out, dst_row=dst_row, row_scale=row_scale, status=st)
+    resid = torch.randn(T, H, device=DEV)
+    y = torch.zeros(T, H, device=DEV)
+    G.moe_combine(slot_out, pos_of, T, k, resid, y)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    ref = resid.clone()
+    xf = x.float()
+    for t in range(T):
+        for j in range(k):
+            e = int(ids[t, j])
+            if e < 0:
+                continue
+            g = xf[t] @ Wg[e].float().T
+            u = xf[t] @ Wu[e].float().T
+            a = (torch.nn.functional.silu(g) * u).bfloat16().float()
+            ref[t] += wts[t, j] * (a @ Wd[e].float().T)
+    assert torch.allclose(y, ref, rtol=2e-2, atol=2e-2), (y - ref).abs().max()
+
+
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0"])
+def test_dequant_bf16_matches_oracle(t):
+    from bloomery_b200.formats import quant as Q
+    from bloomery_b200.formats.resident import to_resident
+    from bloomery_b200.ops import gemm as G
+    from bloomery_b200.ops.decode import QWeight
+    torch.manual_seed(3)
+    w = torch.randn(3, 40, 512) * 0.02
+    raw = Q.quantize(w.reshape(-1, 512), t)
+    qw = QWeight(to_resident(raw, t, 512).to(DEV).reshape(3, 40, -1), t, 512)
+    out = G.dequant_bf16(qw)
+    ref = Q.dequantize(raw, t, 512).reshape(3, 40, 512).bfloat16()
+    assert torch.equal(out.cpu(), ref)
+
+
+def test_rmsnorm_bf16():
+    from bloomery_b200.models.cpu_ref import rms_norm
+    from bloomery_b200.ops import gemm as G
+    torch.manual_seed(4)
+    x = torch.randn(37, 2048, device=DEV)
+    g = 1 + 0.1 * torch.randn(2048, device=DEV)
+    out = torch.zeros(37, 2048, dtype=torch.bfloat16, device=DEV)
+    G.rmsnorm_bf16(x, g, 1e-6, out)
+    ref = rms_norm(x.cpu(), g.cpu(), 1e-6)
+    assert torch.allclose(out.float().cpu(), ref, rtol=1e-2, atol=1e-2)
