@@ -82,7 +82,7 @@ def main() -> int:
     ap.add_argument("--impl", default="own")
     ap.add_argument("--model", default="qwen3-30b-a3b")
     ap.add_argument("--prompt", type=int, default=512)
-    ap.add_argument("--ttft", type=int, default=0, help="also time a prompt of this many tokens (0 = skip)")
+    ap.add_argument("--ttft", type=int, default=4096, help="also time a prompt of this many tokens (0 = skip)")
     ap.add_argument("--no-pdl", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -181,6 +181,7 @@ def main() -> int:
             ts.append((time.perf_counter() - t0) * 1e3)
         extra["ttft_ms_p50"] = sorted(ts)[1]
         extra["ttft_prompt_tokens"] = args.ttft
+        extra["prefill_tok_s"] = args.ttft / (sorted(ts)[1] / 1e3)
 
     line = {
         "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,

@@ -40,6 +40,7 @@ struct RopeArgs {
   float* q_out;          // [M, n_q, HEAD]
   unsigned* fault;
   int layer;
+  __nv_bfloat16* q_bf16; // optional [n_q, M, HEAD] (head-major rows for the prompt GEMMs)
 };
 
 template <int HEAD>
@@ -76,9 +77,16 @@ __global__ void __launch_bounds__(HEAD / 2) qk_norm_rope_append_kernel(const Rop
     x0 = y0; x1 = y1;
   }
   if (is_q) {
-    float* q = a.q_out + ((long)m * a.n_q + head) * HEAD;
-    q[i] = x0 * a.q_scale;
-    q[i + HALF] = x1 * a.q_scale;
+    if (a.q_out) {
+      float* q = a.q_out + ((long)m * a.n_q + head) * HEAD;
+      q[i] = x0 * a.q_scale;
+      q[i + HALF] = x1 * a.q_scale;
+    }
+    if (a.q_bf16) {
+      __nv_bfloat16* q = a.q_bf16 + ((long)head * a.M + m) * HEAD;
+      q[i] = __float2bfloat16_rn(x0 * a.q_scale);
+      q[i + HALF] = __float2bfloat16_rn(x1 * a.q_scale);
+    }
     return;
   }
   const int kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
@@ -295,8 +303,23 @@ int bl_qk_norm_rope_append(const float* qkv, long qkv_stride, const float* q_gai
   BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
   BL_REQUIRE(M >= 1 && n_q >= 1 && n_kv >= 1, BL_ERR_SHAPE);
   RopeArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, M, row_pos, row_seq, block_table,
-             max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, q_out, fault, layer};
+             max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, q_out, fault, layer, nullptr};
   dim3 grid(n_q + 2 * n_kv, M);
+  if (head == 128) return (int)launch(qk_norm_rope_append_kernel<128>, grid, dim3(64), 0, st, a);
+  return (int)launch(qk_norm_rope_append_kernel<64>, grid, dim3(32), 0, st, a);
+}
+
+// Prompt form: the same kernel over T rows; q goes out as bf16 [n_q, T, head].
+int bl_qk_norm_rope_append_prefill(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain,
+                                   const float* inv_freq, float eps, float q_scale, int head, int n_q, int n_kv, int T,
+                                   const int* row_pos, const int* row_seq, const int* block_table, int max_pages,
+                                   int n_pages, void* k_cache, void* v_cache, void* q_bf16, unsigned* fault, int layer,
+                                   cudaStream_t st) {
+  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
+  BL_REQUIRE(T >= 1 && T <= 65535 && n_q >= 1 && n_kv >= 1, BL_ERR_SHAPE);
+  RopeArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, T, row_pos, row_seq, block_table,
+             max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, nullptr, fault, layer, (__nv_bfloat16*)q_bf16};
+  dim3 grid(n_q + 2 * n_kv, T);
   if (head == 128) return (int)launch(qk_norm_rope_append_kernel<128>, grid, dim3(64), 0, st, a);
   return (int)launch(qk_norm_rope_append_kernel<64>, grid, dim3(32), 0, st, a);
 }

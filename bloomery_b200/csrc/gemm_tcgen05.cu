@@ -334,20 +334,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
 // ---- tile table ----------------------------------------------------------------------
 // group_rows[g] rows for group g, laid out back to back in A (offsets = prefix sums).
+// A group's B-matrix index is g / group_div (several row groups may share one B, e.g. the
+// query heads of one KV head).
 __global__ void build_mtiles_kernel(const int* group_rows, int n_groups, MTile* mtiles, int* n_mtiles, int max_mtiles,
-                                    int* group_offset_out) {
+                                    int* group_offset_out, int group_div, int group_stride, int base) {
   pdl_wait();
   pdl_launch();
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  // group_stride > 0: group g starts at row base + g * group_stride of A (strided groups,
+  // e.g. one query chunk of every head); otherwise groups follow one another.
   int off = 0, n = 0;
   for (int g = 0; g < n_groups; ++g) {
     const int rows = group_rows[g];
+    if (group_stride > 0) off = base + g * group_stride;
     if (group_offset_out) group_offset_out[g] = off;
     for (int r = 0; r < rows; r += BM) {
-      if (n < max_mtiles) mtiles[n] = MTile{g, off + r, off + rows, 0};
+      if (n < max_mtiles) mtiles[n] = MTile{g / group_div, off + r, off + rows, 0};
       ++n;
     }
-    off += rows;
+    if (group_stride <= 0) off += rows;
   }
   if (group_offset_out) group_offset_out[n_groups] = off;
   *n_mtiles = n < max_mtiles ? n : max_mtiles;
@@ -374,10 +379,10 @@ extern "C" {
 
 // Fill the tile table for a grouped GEMM from per-group row counts on the device.
 int bl_gemm_build_tiles(const int* group_rows, int n_groups, void* mtiles, int* n_mtiles, int max_mtiles,
-                        int* group_offsets, cudaStream_t st) {
-  BL_REQUIRE(n_groups >= 1 && max_mtiles >= 1, BL_ERR_SHAPE);
+                        int* group_offsets, int group_div, int group_stride, int base, cudaStream_t st) {
+  BL_REQUIRE(n_groups >= 1 && max_mtiles >= 1 && group_div >= 1, BL_ERR_SHAPE);
   return (int)launch(build_mtiles_kernel, dim3(1), dim3(32), 0, st, group_rows, n_groups, (MTile*)mtiles, n_mtiles,
-                     max_mtiles, group_offsets);
+                     max_mtiles, group_offsets, group_div, group_stride, base);
 }
 
 // C = A * B[g]^T per 128-row tile of the table.  A: [rows_a, K] bf16 (lda elements);

@@ -143,13 +143,21 @@ __device__ __forceinline__ bool route_block(const RouteParams& p, int m, RouteSh
 // w with x*gain and the sum of squares run in the same sweep, and the RMS scale multiplies
 // the finished logit (so nothing waits for a normalisation pass).
 template <int MB>
-__global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
+__global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
   __shared__ float s_dot[8][MB];
   __shared__ double s_ss[8][MB];
   __shared__ float s_scale[MB];
-  const int K = a.K;
+  const int K = a0.K;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int e = blockIdx.x;
+  RouterArgs a = a0;                      // row group blockIdx.y: rows [8 y, 8 y + M)
+  if (blockIdx.y > 0) {
+    const long r0 = (long)blockIdx.y * MB;
+    a.x += r0 * a.x_stride; a.logits += r0 * a.E;
+    if (a.xq_out) { a.xq_out += r0 * K; a.xds_out += r0 * (K / 32); }
+    if (a.xn_out) a.xn_out += r0 * K;
+  }
+  a.M = min(MB, a0.M - (int)blockIdx.y * MB);
   const long rb = resident_row_bytes(a.wtype, K);
   const uint8_t* row = a.w + (long)e * rb;
 
@@ -205,7 +213,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
   }
   __syncthreads();
   // every block knows the scale; block b publishes 32-value blocks b, b + E, ... of the q8 rows
-  {
+  if (a.xq_out) {
     const int nb32 = K / 32;
     for (int b = e * 8 + warp; b < nb32 * a.M; b += gridDim.x * 8) {
       const int m = b / nb32, bb = b - m * nb32;
@@ -445,14 +453,14 @@ int bl_router(const float* x, long x_stride, const float* gain, float eps, const
               int K, int E, int M, float* logits, int8_t* xq_out, float* xds_out, float* xn_out, unsigned* fault,
               int layer, cudaStream_t st) {
   BL_REQUIRE(E >= 1 && E <= kMaxExperts, BL_ERR_LIMIT);
-  BL_REQUIRE(K % 256 == 0 && M >= 1 && M <= 8, BL_ERR_SHAPE);
+  BL_REQUIRE(K % 256 == 0 && M >= 1 && M <= 8 * 65535, BL_ERR_SHAPE);
   BL_REQUIRE(wtype == WT_F32 || wtype == WT_F16 || wtype == WT_BF16, BL_ERR_TYPE);
   RouterArgs a{};
   a.x = x; a.x_stride = x_stride; a.gain = gain; a.eps = eps; a.w = (const uint8_t*)w; a.wtype = wtype;
   a.K = K; a.E = E; a.M = M; a.logits = logits; a.xq_out = xq_out; a.xds_out = (float2*)xds_out; a.xn_out = xn_out;
   a.fault = fault; a.layer = layer;
   int mb = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
-  dim3 grid(E);
+  dim3 grid(E, (M + mb - 1) / mb);
   switch (mb) {
     case 1: return (int)launch(router_kernel<1>, grid, dim3(256), 0, st, a);
     case 2: return (int)launch(router_kernel<2>, grid, dim3(256), 0, st, a);

@@ -139,6 +139,63 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* slot_out,
   }
 }
 
+
+// Contiguous bf16 copies of one sequence's keys and values for the prompt GEMMs:
+//   Kb [n_kv][T_pad][HEAD], Vt [n_kv][HEAD][T_pad]; positions >= n_keys are zero.
+__global__ void __launch_bounds__(128) kv_gather_bf16_kernel(const __half* k_cache, const __half* v_cache, const int* block_table,
+                                                            int n_pages, int n_kv, int head, int n_keys, int T_pad,
+                                                            __nv_bfloat16* Kb, __nv_bfloat16* Vt) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x, kvh = blockIdx.y, d = threadIdx.x;
+  if (d >= head) return;
+  float kv = 0.f, vv = 0.f;
+  if (t < n_keys) {
+    int page = block_table[t / 64];
+    if (page >= 0 && page < n_pages) {
+      const long src = (((long)page * n_kv + kvh) * 64 + (t % 64)) * head + d;
+      kv = __half2float(k_cache[src]);
+      vv = __half2float(v_cache[src]);
+    }
+  }
+  Kb[((long)kvh * T_pad + t) * head + d] = __float2bfloat16_rn(kv);
+  Vt[((long)kvh * head + d) * T_pad + t] = __float2bfloat16_rn(vv);
+}
+
+// P[r, :] = softmax over keys 0..pos0 + (r % Tq) of S[r, :] (rows are head-major: r = h * Tq + tq);
+// masked and padded columns get exactly 0.
+__global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, long ldS, int Tq, int pos0, int T_pad,
+                                                            __nv_bfloat16* P, long ldP) {
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_launch();
+  const long r = blockIdx.x;
+  const int tq = (int)(r % Tq);
+  const int n_valid = min(T_pad, pos0 + tq + 1);
+  const float* s = S + r * ldS;
+  const int tid = threadIdx.x;
+  float mx = -INFINITY;
+  for (int i = tid; i < n_valid; i += 256) mx = fmaxf(mx, s[i]);
+  mx = warp_max(mx);
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+  __syncthreads();
+  float sum = 0.f;
+  for (int i = tid; i < n_valid; i += 256) sum += __expf(s[i] - mx);
+  sum = warp_sum(sum);
+  if ((tid & 31) == 0) red[tid >> 5] = sum;
+  __syncthreads();
+  sum = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) sum += red[w];
+  const float inv = 1.0f / sum;
+  __nv_bfloat16* p = P + r * ldP;
+  for (int i = tid; i < T_pad; i += 256) p[i] = __float2bfloat16_rn(i < n_valid ? __expf(s[i] - mx) * inv : 0.f);
+}
+
 }  // namespace bl
 
 using namespace bl;
@@ -182,6 +239,18 @@ int bl_moe_combine(const float* slot_out, const int* pos_of, int T, int k, int H
                    float* out, long out_stride, cudaStream_t st) {
   BL_REQUIRE(T >= 1 && H % 4 == 0, BL_ERR_SHAPE);
   return (int)launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, slot_out, pos_of, k, H, resid, resid_stride, out, out_stride);
+}
+
+int bl_kv_gather_bf16(const void* k_cache, const void* v_cache, const int* block_table, int n_pages, int n_kv, int head,
+                      int n_keys, int T_pad, void* Kb, void* Vt, cudaStream_t st) {
+  BL_REQUIRE(head <= 128 && T_pad >= 1 && n_keys <= T_pad, BL_ERR_SHAPE);
+  return (int)launch(kv_gather_bf16_kernel, dim3(T_pad, n_kv), dim3(128), 0, st, (const __half*)k_cache, (const __half*)v_cache,
+                     block_table, n_pages, n_kv, head, n_keys, T_pad, (__nv_bfloat16*)Kb, (__nv_bfloat16*)Vt);
+}
+
+int bl_softmax_causal(const float* S, long ldS, long rows, int Tq, int pos0, int T_pad, void* P, long ldP, cudaStream_t st) {
+  BL_REQUIRE(rows >= 1 && Tq >= 1 && T_pad >= 1, BL_ERR_SHAPE);
+  return (int)launch(softmax_causal_kernel, dim3((unsigned)rows), dim3(256), 0, st, S, ldS, Tq, pos0, T_pad, (__nv_bfloat16*)P, ldP);
 }
 
 }  // extern "C"

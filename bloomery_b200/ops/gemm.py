@@ -22,10 +22,13 @@ class TileTable:
         self.n_mtiles = torch.zeros(1, dtype=torch.int32, device=device)
         self.offsets = torch.zeros(n_groups + 1, dtype=torch.int32, device=device)
 
-    def build(self, group_rows: torch.Tensor) -> None:
-        """group_rows int32 [n_groups] on the device; rows of group g follow group g-1 in A."""
+    def build(self, group_rows: torch.Tensor, group_div: int = 1, group_stride: int = 0, base: int = 0) -> None:
+        """group_rows int32 [n_groups] on the device.  Rows of group g follow group g-1 in A
+        (or start at ``base + g * group_stride`` when ``group_stride`` > 0) and use B matrix
+        ``g // group_div``."""
         check(cuda().bl_gemm_build_tiles(p(group_rows), I(self.n_groups), p(self.mtiles), p(self.n_mtiles),
-                                         I(self.max_mtiles), p(self.offsets), stream()), "bl_gemm_build_tiles")
+                                         I(self.max_mtiles), p(self.offsets), I(group_div), I(group_stride), I(base),
+                                         stream()), "bl_gemm_build_tiles")
 
     @classmethod
     def dense(cls, rows: int, device) -> "TileTable":
@@ -87,3 +90,22 @@ def moe_combine(slot_out, pos_of, T: int, k: int, resid, out) -> None:
     check(cuda().bl_moe_combine(p(slot_out), p(pos_of), I(T), I(k), I(out.shape[1]), p(resid),
                                 L(resid.stride(0) if resid is not None else 0), p(out), L(out.stride(0)), stream()),
           "bl_moe_combine")
+
+
+def kv_gather_bf16(k_cache, v_cache, block_table_row, n_pages: int, n_kv: int, head: int, n_keys: int, T_pad: int, Kb, Vt):
+    check(cuda().bl_kv_gather_bf16(p(k_cache), p(v_cache), p(block_table_row), I(n_pages), I(n_kv), I(head), I(n_keys),
+                                   I(T_pad), p(Kb), p(Vt), stream()), "bl_kv_gather_bf16")
+
+
+def softmax_causal(S, rows: int, Tq: int, pos0: int, T_pad: int, P) -> None:
+    check(cuda().bl_softmax_causal(p(S), L(S.stride(0)), L(rows), I(Tq), I(pos0), I(T_pad), p(P), L(P.stride(0)),
+                                   stream()), "bl_softmax_causal")
+
+
+def qk_norm_rope_append_prefill(qkv, q_gain, k_gain, inv_freq, eps, q_scale, head, n_q, n_kv, T, row_pos, row_seq,
+                                block_table, n_pages, k_cache, v_cache, q_bf16, fault, layer) -> None:
+    rc = cuda().bl_qk_norm_rope_append_prefill(p(qkv), L(qkv.stride(0)), p(q_gain), p(k_gain), p(inv_freq), F(eps),
+                                               F(q_scale), I(head), I(n_q), I(n_kv), I(T), p(row_pos), p(row_seq),
+                                               p(block_table), I(block_table.shape[1]), I(n_pages), p(k_cache),
+                                               p(v_cache), p(q_bf16), p(fault), I(layer), stream())
+    check(rc, "bl_qk_norm_rope_append_prefill")

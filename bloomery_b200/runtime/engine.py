@@ -122,6 +122,9 @@ class DecodeEngine:
         self.slot_len = [0] * n_slots
         self.launches_per_step = 0
         self.steps = 0
+        self.gemm_threshold = 64      # prompts at least this long use the GEMM path (0 = never)
+        self.ubatch = 4096
+        self._gemm_prefill = None
         self._stream = torch.cuda.Stream(device=dev)
         self._done = torch.cuda.Event()
         self._lock = threading.Lock()
@@ -261,8 +264,31 @@ class DecodeEngine:
                 raise EngineFault(word)
             return out[:len(rows)]
 
-    def prefill(self, slot: int, tokens: Sequence[int], start: int = 0) -> int:
-        """Feed a prompt through passes of up to 8 rows; returns the greedy token after it."""
+    def prefill(self, slot: int, tokens: Sequence[int], start: int = 0, gemm: Optional[bool] = None) -> int:
+        """Feed a prompt; returns the greedy token after it.  Prompts of at least
+        ``gemm_threshold`` rows go through the tcgen05 GEMM path in micro-batches, shorter
+        ones through passes of up to 8 rows of the decode chain."""
+        n = len(tokens)
+        use_gemm = gemm if gemm is not None else (self.gemm_threshold > 0 and n >= self.gemm_threshold)
+        if use_gemm and n > 1:
+            if self._gemm_prefill is None:
+                from .prefill import GemmPrefill
+                self._gemm_prefill = GemmPrefill(self, ubatch=self.ubatch)
+            with self._lock:
+                if self.poisoned is not None:
+                    raise EngineFault(self.poisoned)
+                self._gemm_prefill.run(slot, tokens, start)
+                head_w = self.w.q.get("output.weight", self.w.q["token_embd.weight"])
+                K.gemv([head_w], 1, self.logits, x=self.x, gain=self.w.f["output_norm.weight"], eps=self.spec.rms_eps,
+                       fault=self.fault, layer=self.spec.n_layer)
+                K.argmax_rows(self.logits, self.spec.vocab, 1, self.am_blocks, self.am_v, self.am_i,
+                              self.counters[1:2], self.tokens_out, None, self.fault)
+                out = self.read_tokens(1)
+                word = out[1] & 0xFFFFFFFF
+                if word != FAULT_CLEAN:
+                    self.poisoned = word
+                    raise EngineFault(word)
+                return out[0]
         last = None
         n = len(tokens)
         i = 0

@@ -1,0 +1,187 @@
+"""Prompt (prefill) path on the tcgen05 GEMM: whole micro-batches of prompt rows per layer
+instead of 8-row passes.
+
+Counterpart of the reference's GEMM ubatches (``crates/gpu/src/arch/qwen3moe/ubatch.rs:1-40``:
+per layer norm -> QKV GEMM -> norm/RoPE/append -> prefill flash -> o GEMM -> router logits +
+route -> grouped gate/up GEMM with SwiGLU -> grouped down GEMM -> combine).  Here:
+
+  * block-quantised weights of the layer are expanded to bf16 scratch right before use
+    (one expander kernel per matrix; the scratch is shared by all layers);
+  * every matmul is the persistent TMA + tcgen05 kernel; gate and up run in one main loop
+    with SwiGLU in the epilogue; the down GEMM's epilogue scatters router-weighted rows to
+    their (token, slot) cell and a fixed-order combine adds slots in ascending order;
+  * attention is three launches per query chunk: Q K^T (grouped over heads, KV head shared
+    by its query heads), causal softmax, P V (epilogue writes token-major rows).
+
+Token bits are not equal to the 8-row pass path (bf16 operands, different sum order); a
+band test covers it, as the reference does (``ubatch.rs:19-30``).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..ops import decode as K
+from ..ops import gemm as G
+from .kv import PAGE
+
+
+class GemmPrefill:
+    def __init__(self, engine, ubatch: int = 2048, score_bytes: int = 1 << 30):
+        self.e = engine
+        self.ubatch = ubatch
+        self.score_bytes = score_bytes
+        self._buf = {}
+        self.status = torch.zeros(1, dtype=torch.int32, device=engine.device)
+        self.launches = 0
+
+    def _get(self, name: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= d
+        b = self._buf.get(name)
+        if b is None or b.numel() < n or b.dtype != dtype:
+            b = torch.empty(n, dtype=dtype, device=self.e.device)
+            self._buf[name] = b
+        return b[:n].view(*shape)
+
+    def run(self, slot: int, tokens: Sequence[int], start: int = 0) -> None:
+        """Append ``tokens`` at positions start.. of ``slot``; leaves the last row's hidden
+        state in ``engine.x[0]`` (the caller runs the head)."""
+        e = self.e
+        n = len(tokens)
+        e.kv.ensure(slot, start + n)
+        for p in range(start, start + n, PAGE):
+            e.kv.own(slot, p)
+        e.kv.sync_table()
+        i = 0
+        while i < n:
+            chunk = tokens[i:i + self.ubatch]
+            self._ubatch(slot, chunk, start + i)
+            i += len(chunk)
+        e.slot_len[slot] = max(e.slot_len[slot], start + n)
+
+    def _ubatch(self, slot: int, tokens: Sequence[int], p0: int) -> None:
+        e = self.e
+        s, w, dev = e.spec, e.w, e.device
+        T = len(tokens)
+        H, V = s.hidden, s.vocab
+        bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+        tok = torch.tensor(list(tokens), dtype=i32, device=dev)
+        row_pos = torch.arange(p0, p0 + T, dtype=i32, device=dev)
+        row_seq = torch.full((T,), slot, dtype=i32, device=dev)
+        x = self._get("x", (T, H), f32)
+        xn = self._get("xn", (T, H), bf)
+        K.embed_rows(tok, T, w.q["token_embd.weight"], V, x, e.fault)
+        qkv_w = s.q_rows + 2 * s.kv_rows
+        qkv = self._get("qkv", (T, qkv_w), f32)
+        wqkv = self._get("wqkv", (qkv_w, H), bf)
+        wo = self._get("wo", (H, s.q_rows), bf)
+        q_bf = self._get("q_bf", (s.n_q, T, s.head_dim), bf)
+        attn = self._get("attn", (T, s.q_rows), bf)
+        dense_tiles = G.TileTable.dense(T, dev)
+        n_keys = p0 + T
+        T_pad = (n_keys + 127) // 128 * 128
+        Kb = self._get("Kb", (s.n_kv, T_pad, s.head_dim), bf)
+        Vt = self._get("Vt", (s.n_kv, s.head_dim, T_pad), bf)
+        Tq_max = max(128, min(T, self.score_bytes // (s.n_q * T_pad * 4) // 128 * 128))
+        Gq = s.n_q // s.n_kv
+        if s.is_moe:
+            E, I_, k = s.n_expert, s.moe_inter, s.n_used
+            nslot = T * k
+            cap = nslot + 128
+            wg = self._get("wg", (E, I_, H), bf)
+            wu = self._get("wu", (E, I_, H), bf)
+            wd = self._get("wd", (E, H, I_), bf)
+            logits = self._get("rl", (T, E), f32)
+            ids = self._get("ids", (T, k), i32)
+            wts = self._get("wts", (T, k), f32)
+            counts = self._get("counts", (E,), i32)
+            cursor = self._get("cursor", (E,), i32)
+            pos_of = self._get("pos_of", (nslot,), i32)
+            dst_row = self._get("dst_row", (cap,), i32)
+            row_scale = self._get("row_scale", (cap,), f32)
+            Ap = self._get("Ap", (cap, H), bf)
+            act = self._get("act", (cap, I_), bf)
+            slot_out = self._get("slot_out", (nslot, H), f32)
+            moe_tiles = G.TileTable(nslot, E, dev)
+        if s.dense_inter and (s.first_dense > 0 or not s.is_moe):
+            Id = s.dense_inter
+            dg = self._get("dg", (Id, H), bf)
+            du = self._get("du", (Id, H), bf)
+            dd = self._get("dd", (H, Id), bf)
+            dact = self._get("dact", (T, Id), bf)
+        st = self.status
+        for il in range(s.n_layer):
+            b = f"blk.{il}."
+            G.rmsnorm_bf16(x, w.f[b + "attn_norm.weight"], s.rms_eps, xn)
+            G.dequant_bf16(w.q[b + "attn_q.weight"], wqkv[:s.q_rows])
+            G.dequant_bf16(w.q[b + "attn_k.weight"], wqkv[s.q_rows:s.q_rows + s.kv_rows])
+            G.dequant_bf16(w.q[b + "attn_v.weight"], wqkv[s.q_rows + s.kv_rows:])
+            G.gemm_bf16(xn, wqkv, dense_tiles, out_f32=qkv, status=st)
+            G.qk_norm_rope_append_prefill(qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
+                                          e.inv_freq, s.rms_eps, 1.0 / math.sqrt(s.head_dim), s.head_dim, s.n_q, s.n_kv,
+                                          T, row_pos, row_seq, e.kv.table, e.kv.n_pages, e.kv.k[il], e.kv.v[il], q_bf,
+                                          e.fault, il)
+            G.kv_gather_bf16(e.kv.k[il], e.kv.v[il], e.kv.table[slot], e.kv.n_pages, s.n_kv, s.head_dim, n_keys, T_pad,
+                             Kb, Vt)
+            for c0 in range(0, T, Tq_max):
+                Tq = min(Tq_max, T - c0)
+                rows = s.n_q * Tq
+                S = self._get("S", (rows, T_pad), f32)
+                P = self._get("P", (rows, T_pad), bf)
+                qk_tiles, pv_tiles, map_s, map_o = self._attn_tables(T, Tq, c0, s.n_q, Gq)
+                G.gemm_bf16(q_bf.view(s.n_q * T, s.head_dim), Kb, qk_tiles, out_f32=S, dst_row=map_s, status=st)
+                G.softmax_causal(S, rows, Tq, p0 + c0, T_pad, P)
+                G.gemm_bf16(P, Vt, pv_tiles, out_bf16=attn.view(T * s.n_q, s.head_dim), dst_row=map_o, status=st)
+            G.dequant_bf16(w.q[b + "attn_output.weight"], wo)
+            G.gemm_bf16(attn, wo, dense_tiles, out_f32=x, resid=x, status=st)
+            if s.layer_is_moe(il):
+                K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], T, logits, None,
+                         None, None, e.fault, il)
+                K.route_rows(logits, e._rule(il), T, ids, wts, e.heat[il], e.fault, il)
+                G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
+                counts.zero_(); cursor.zero_(); dst_row.fill_(-1)
+                G.moe_count(ids, E, counts)
+                moe_tiles.build(counts)
+                G.moe_scatter(ids, wts, E, moe_tiles.offsets, cursor, pos_of, dst_row, row_scale)
+                G.gather_rows_bf16(xn, dst_row, moe_tiles.offsets[E:E + 1], cap, k, Ap)
+                G.dequant_bf16(w.q[b + "ffn_gate_exps.weight"], wg)
+                G.dequant_bf16(w.q[b + "ffn_up_exps.weight"], wu)
+                G.gemm_bf16(Ap, wg, moe_tiles, out_bf16=act, B2=wu, status=st)
+                G.dequant_bf16(w.q[b + "ffn_down_exps.weight"], wd)
+                G.gemm_bf16(act, wd, moe_tiles, out_f32=slot_out, dst_row=dst_row, row_scale=row_scale, status=st)
+                G.moe_combine(slot_out, pos_of, T, k, x, x)
+            else:
+                G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
+                G.dequant_bf16(w.q[b + "ffn_gate.weight"], dg)
+                G.dequant_bf16(w.q[b + "ffn_up.weight"], du)
+                G.gemm_bf16(xn, dg, dense_tiles, out_bf16=dact, B2=du, status=st)
+                G.dequant_bf16(w.q[b + "ffn_down.weight"], dd)
+                G.gemm_bf16(dact, dd, dense_tiles, out_f32=x, resid=x, status=st)
+        e.x[0].copy_(x[T - 1])
+        if int(st.item()) != 0:
+            raise RuntimeError("a bounded wait inside the GEMM kernel ran out (status word set)")
+
+    def _attn_tables(self, T: int, Tq: int, c0: int, n_q: int, Gq: int):
+        key = ("attn", T, Tq, c0, n_q)
+        hit = self._buf.get(key)
+        if hit is not None:
+            return hit
+        dev = self.e.device
+        i32 = torch.int32
+        rows = torch.full((n_q,), Tq, dtype=i32, device=dev)
+        qk = G.TileTable(n_q * Tq, n_q, dev)
+        qk.build(rows, group_div=Gq, group_stride=T, base=c0)
+        pv = G.TileTable(n_q * Tq, n_q, dev)
+        pv.build(rows, group_div=Gq)
+        h = torch.arange(n_q, device=dev).view(n_q, 1)
+        i = torch.arange(Tq, device=dev).view(1, Tq)
+        map_s = torch.full((n_q * T,), -1, dtype=i32, device=dev)
+        map_s.view(n_q, T)[:, c0:c0 + Tq] = (h * Tq + i).to(i32)
+        map_o = ((c0 + i) * n_q + h).to(i32).reshape(-1).contiguous()   # index h*Tq + i -> token-major row
+        out = (qk, pv, map_s, map_o)
+        self._buf[key] = out
+        return out

@@ -121,3 +121,33 @@ def test_rmsnorm_bf16():
     G.rmsnorm_bf16(x, g, 1e-6, out)
     ref = rms_norm(x.cpu(), g.cpu(), 1e-6)
     assert torch.allclose(out.float().cpu(), ref, rtol=1e-2, atol=1e-2)
+
+
+def test_gemm_prefill_matches_pass_path_in_band():
+    """The GEMM prompt path against the 8-row pass path of the same engine: logits in a band,
+    KV rows close, and decode continues from either."""
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.engine import DecodeEngine
+    spec = tiny_qwen3moe()
+    w = Weights.from_items(spec, synth_tensors(spec, DEV, seed=3), DEV)
+    eng = DecodeEngine(w, n_slots=2, slot_ctx=1024)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, spec.vocab, (333,), generator=g).tolist()
+    t_pass = eng.prefill(0, prompt, gemm=False)
+    l_pass = eng.logits[(len(prompt) - 1) % 8].clone()
+    t_gemm = eng.prefill(1, prompt, gemm=True)
+    l_gemm = eng.logits[0].clone()
+    err = ((l_pass - l_gemm).abs().max() / l_pass.abs().max()).item()
+    assert err < 5e-2, err
+    k0 = eng.kv.k[:, eng.kv.pages[0][0]].float()
+    k1 = eng.kv.k[:, eng.kv.pages[1][0]].float()
+    assert ((k0 - k1).abs().mean() / k0.abs().mean()).item() < 3e-2      # bf16 operands vs q8 operands
+    # second micro-batch on top of the first (keys of both are attended)
+    more = torch.randint(0, spec.vocab, (100,), generator=g).tolist()
+    eng.prefill(0, more, start=len(prompt), gemm=False)
+    l2_pass = eng.logits[(len(more) - 1) % 8].clone()
+    eng.prefill(1, more, start=len(prompt), gemm=True)
+    l2_gemm = eng.logits[0].clone()
+    assert ((l2_pass - l2_gemm).abs().max() / l2_pass.abs().max()).item() < 5e-2
+    assert len(eng.decode_chain(1, t_gemm, len(prompt) + len(more), 4)) == 4
