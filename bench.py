@@ -84,6 +84,8 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--ttft", type=int, default=4096, help="also time a prompt of this many tokens (0 = skip)")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--nccl-baseline", dest="nccl_baseline", action="store_true",
+                    help="N > 1: do the per-layer reductions with NCCL all_reduce instead of the fused kernels")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

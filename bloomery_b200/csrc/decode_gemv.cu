@@ -50,6 +50,8 @@ struct GemvArgs {
   long resid_stride;
   unsigned* fault;
   int layer;
+  ReduceIn red;            // n_ranks > 0: x is "x + sum of every rank's partial rows" (consumer half)
+  PushOut push;            // n_ranks > 0: the result is a partial update pushed to every rank (producer half)
 };
 
 // ---- activation prologue ------------------------------------------------------------
@@ -58,13 +60,24 @@ template <int MB, bool FLOATW>
 __device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, float2* sds, float* sx, float* s_scale,
                                               double* red) {
   const int K = a.K, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool reduce = a.red.n_ranks > 0;
+  if (reduce) reduce_wait(a.red);
 #pragma unroll 1
   for (int m = 0; m < MB; ++m) {
     const int ms = m < a.M ? m : a.M - 1;
     const float* x = a.x + (long)ms * a.x_stride;
     float ss = 0.f;
     for (int i0 = tid * 8; i0 < K; i0 += 256 * 8) {
-      float4 x0 = *reinterpret_cast<const float4*>(x + i0), x1 = *reinterpret_cast<const float4*>(x + i0 + 4);
+      float4 x0, x1;
+      if (reduce) {
+        x0 = reduce_value4(a.red, x, ms, i0); x1 = reduce_value4(a.red, x, ms, i0 + 4);
+        if (blockIdx.x == 0 && m < a.M) {
+          *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0) = x0;
+          *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0 + 4) = x1;
+        }
+      } else {
+        x0 = *reinterpret_cast<const float4*>(x + i0); x1 = *reinterpret_cast<const float4*>(x + i0 + 4);
+      }
       float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gain + i0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gain + i0 + 4));
       float v[8] = {x0.x * g0.x, x0.y * g0.y, x0.z * g0.z, x0.w * g0.w, x1.x * g1.x, x1.y * g1.y, x1.z * g1.z, x1.w * g1.w};
       ss += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
@@ -174,6 +187,7 @@ __device__ __forceinline__ void rows_q(const GemvArgs& a, const GemvSeg& s, int 
           for (int m = 0; m < MB; ++m)
             if (m < a.M) {
               float v = acc[r][m] * s_scale[m];
+              if (a.push.n_ranks > 0) { a.push.local[(long)m * a.out_stride + col] = v; continue; }
               if (a.resid) v += a.resid[(long)m * a.resid_stride + col];
               a.out[(long)m * a.out_stride + col] = v;
             }
@@ -241,6 +255,7 @@ __device__ __forceinline__ void rows_f(const GemvArgs& a, const GemvSeg& s, int 
           for (int m = 0; m < MB; ++m)
             if (m < a.M) {
               float v = acc[r][m] * s_scale[m];
+              if (a.push.n_ranks > 0) { a.push.local[(long)m * a.out_stride + col] = v; continue; }
               if (a.resid) v += a.resid[(long)m * a.resid_stride + col];
               a.out[(long)m * a.out_stride + col] = v;
             }
@@ -291,6 +306,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
     }
   }
   between();
+  if (a.push.n_ranks > 0) push_finish(a.push);
 }
 
 static size_t gemv_smem(int MB, int K, bool floatw) {
@@ -343,8 +359,7 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
             int norm, const float* x, long x_stride, const float* gain, float eps,
             const int8_t* xq, const float* xds,
             float* out, long out_stride, const float* resid, long resid_stride,
-            int8_t* xq_out, float* xds_out, unsigned* fault, int layer, int sm_count, cudaStream_t st) {
-  (void)xq_out; (void)xds_out;
+            const void* red_desc, const void* push_desc, unsigned* fault, int layer, int sm_count, cudaStream_t st) {
   BL_REQUIRE(nseg >= 1 && nseg <= 4, BL_ERR_SHAPE);
   BL_REQUIRE(M >= 1 && M <= 8, BL_ERR_SHAPE);
   BL_REQUIRE(K > 0 && K % 256 == 0, BL_ERR_SHAPE);
@@ -385,6 +400,8 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
   a.xq = xq; a.xds = (const float2*)xds;
   a.out = out; a.out_stride = out_stride; a.resid = resid; a.resid_stride = resid_stride;
   a.fault = fault; a.layer = layer;
+  if (red_desc) { a.red = *(const ReduceIn*)red_desc; BL_REQUIRE(norm && a.red.n_ranks <= kMaxRanks && a.red.H == K, BL_ERR_SHAPE); }
+  if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks && a.push.n_floats % 4 == 0, BL_ERR_SHAPE); }
   BL_REQUIRE(gemv_smem(mb, K, floatw) <= 200 * 1024, BL_ERR_LIMIT);
   cudaError_t e;
   if (norm) e = floatw ? gemv_dispatch_shape<true, true>(a, mb, R, C, grid, st) : gemv_dispatch_shape<true, false>(a, mb, R, C, grid, st);

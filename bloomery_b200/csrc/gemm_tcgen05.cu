@@ -1,7 +1,7 @@
 // bf16 grouped GEMM on the 5th-generation tensor cores (sm_100a only):
 //   C[g][m, n] = sum_k A[m, k] * B[g][n, k]        fp32 accumulate in tensor memory
 //
-//   * operands staged by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into
+//   * operands staged by TMA (cp.async.bulk.tensor, 128-byte swizzle, every CTA fetches its own tiles) into
 //     a 4-stage shared-memory ring; one elected thread issues tcgen05.mma (M=128, N=128,
 //     K=16 per instruction) with accumulators in TMEM; four epilogue warps read them back
 //     with tcgen05.ld while the next tile's main loop already runs (two TMEM buffers);

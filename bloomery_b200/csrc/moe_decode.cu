@@ -29,6 +29,7 @@ struct RouterArgs {
   int8_t* xq_out; float2* xds_out;     // q8 of the normed rows [M, K]
   float* xn_out;                       // optional fp32 normed rows [M, K]
   unsigned* fault; int layer;
+  ReduceIn red;                        // n_ranks > 0: x = x + sum of every rank's partial rows
 };
 
 // Routing parameters shared by the router launch and its consumers.
@@ -181,12 +182,21 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
       }
     }
     float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gain + i0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gain + i0 + 4));
-    if (!waited) { pdl_wait(); waited = true; }
+    if (!waited) { pdl_wait(); waited = true; if (a.red.n_ranks > 0) reduce_wait(a.red); }
 #pragma unroll
     for (int m = 0; m < MB; ++m) {
       const int ms = m < a.M ? m : a.M - 1;
-      const float* x = a.x + (long)ms * a.x_stride + i0;
-      float4 x0 = *reinterpret_cast<const float4*>(x), x1 = *reinterpret_cast<const float4*>(x + 4);
+      const float* xr = a.x + (long)ms * a.x_stride;
+      float4 x0, x1;
+      if (a.red.n_ranks > 0) {
+        x0 = reduce_value4(a.red, xr, ms, i0); x1 = reduce_value4(a.red, xr, ms, i0 + 4);
+        if (e == 0 && m < a.M) {
+          *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0) = x0;
+          *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0 + 4) = x1;
+        }
+      } else {
+        x0 = *reinterpret_cast<const float4*>(xr + i0); x1 = *reinterpret_cast<const float4*>(xr + i0 + 4);
+      }
       ss[m] += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
       float t = dot[m];
       t = fmaf(wv[0], x0.x * g0.x, t); t = fmaf(wv[1], x0.y * g0.y, t); t = fmaf(wv[2], x0.z * g0.z, t); t = fmaf(wv[3], x0.w * g0.w, t);
@@ -194,7 +204,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
       dot[m] = t;
     }
   }
-  if (!waited) pdl_wait();
+  if (!waited) { pdl_wait(); if (a.red.n_ranks > 0) reduce_wait(a.red); }
   pdl_launch();
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
@@ -218,7 +228,8 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
     for (int b = e * 8 + warp; b < nb32 * a.M; b += gridDim.x * 8) {
       const int m = b / nb32, bb = b - m * nb32;
       const int i = bb * 32 + lane;
-      const float v = a.x[(long)m * a.x_stride + i] * a.gain[i] * s_scale[m];
+      const float xv = a.red.n_ranks > 0 ? reduce_value(a.red, a.x + (long)m * a.x_stride, m, i) : a.x[(long)m * a.x_stride + i];
+      const float v = xv * a.gain[i] * s_scale[m];
       float d, sm;
       int8_t qv = q8_lane(v, d, sm);
       a.xq_out[(long)m * K + i] = qv;
@@ -360,6 +371,7 @@ struct DownArgs {
   const float* extra; long extra_stride;    // optional addend (shared expert / host leg sum)
   float* out; long out_stride;
   unsigned* fault; int layer;
+  PushOut push;                             // n_ranks > 0: the result is this rank's partial update
 };
 
 // UPL = units per lane (all loaded before any is used: one DRAM round trip per row)
@@ -425,21 +437,27 @@ __global__ void __launch_bounds__(256, UPL <= 3 ? 2 : 1) down_combine_kernel(con
   bool bad = false;
   for (int j = 0; j < a.n_used; ++j) bad |= (s_slot[j] == -2);
   const int d = blockIdx.x * 8 + warp;
-  if (d >= a.H) return;
-  float y;
-  switch (a.dtype) {
-    case WT_Q4_K: y = down_row<Q4K, UPL>(a, m, d, lane, s_slot, s_w); break;
-    case WT_Q6_K: y = down_row<Q6K, UPL>(a, m, d, lane, s_slot, s_w); break;
-    case WT_Q5_K: y = down_row<Q5K, UPL>(a, m, d, lane, s_slot, s_w); break;
-    case WT_Q8_0: y = down_row<Q80, UPL>(a, m, d, lane, s_slot, s_w); break;
-    default: y = __int_as_float(0x7fc00000);
+  if (d < a.H) {
+    float y;
+    switch (a.dtype) {
+      case WT_Q4_K: y = down_row<Q4K, UPL>(a, m, d, lane, s_slot, s_w); break;
+      case WT_Q6_K: y = down_row<Q6K, UPL>(a, m, d, lane, s_slot, s_w); break;
+      case WT_Q5_K: y = down_row<Q5K, UPL>(a, m, d, lane, s_slot, s_w); break;
+      case WT_Q8_0: y = down_row<Q80, UPL>(a, m, d, lane, s_slot, s_w); break;
+      default: y = __int_as_float(0x7fc00000);
+    }
+    if (lane == 0) {
+      if (bad) { y = __int_as_float(0x7fc00000); if (d == 0) raise_fault(a.fault, a.layer, FS_EXPERT_ID); }
+      if (a.extra) y += a.extra[(long)m * a.extra_stride + d];
+      if (a.push.n_ranks > 0) {
+        a.push.local[(long)m * a.out_stride + d] = y;
+      } else {
+        if (a.resid) y += a.resid[(long)m * a.resid_stride + d];
+        a.out[(long)m * a.out_stride + d] = y;
+      }
+    }
   }
-  if (lane == 0) {
-    if (bad) { y = __int_as_float(0x7fc00000); if (d == 0) raise_fault(a.fault, a.layer, FS_EXPERT_ID); }
-    if (a.extra) y += a.extra[(long)m * a.extra_stride + d];
-    if (a.resid) y += a.resid[(long)m * a.resid_stride + d];
-    a.out[(long)m * a.out_stride + d] = y;
-  }
+  if (a.push.n_ranks > 0) push_finish(a.push);
 }
 
 }  // namespace bl
@@ -450,8 +468,8 @@ extern "C" {
 
 // Router logits (RMS scale applied) for M rows + the q8 form of the normed rows.
 int bl_router(const float* x, long x_stride, const float* gain, float eps, const void* w, int wtype,
-              int K, int E, int M, float* logits, int8_t* xq_out, float* xds_out, float* xn_out, unsigned* fault,
-              int layer, cudaStream_t st) {
+              int K, int E, int M, float* logits, int8_t* xq_out, float* xds_out, float* xn_out,
+              const void* red_desc, unsigned* fault, int layer, cudaStream_t st) {
   BL_REQUIRE(E >= 1 && E <= kMaxExperts, BL_ERR_LIMIT);
   BL_REQUIRE(K % 256 == 0 && M >= 1 && M <= 8 * 65535, BL_ERR_SHAPE);
   BL_REQUIRE(wtype == WT_F32 || wtype == WT_F16 || wtype == WT_BF16, BL_ERR_TYPE);
@@ -459,6 +477,7 @@ int bl_router(const float* x, long x_stride, const float* gain, float eps, const
   a.x = x; a.x_stride = x_stride; a.gain = gain; a.eps = eps; a.w = (const uint8_t*)w; a.wtype = wtype;
   a.K = K; a.E = E; a.M = M; a.logits = logits; a.xq_out = xq_out; a.xds_out = (float2*)xds_out; a.xn_out = xn_out;
   a.fault = fault; a.layer = layer;
+  if (red_desc) { a.red = *(const ReduceIn*)red_desc; BL_REQUIRE(M <= kMaxRows && a.red.n_ranks <= kMaxRanks && a.red.H == K, BL_ERR_SHAPE); }
   int mb = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
   dim3 grid(E, (M + mb - 1) / mb);
   switch (mb) {
@@ -520,12 +539,13 @@ int bl_gate_up_sel(const int8_t* xq, const float* xds, const float* route_logits
 int bl_down_combine(const int8_t* actq, const float* actds, const int* ids, const float* wts, const int* slot_map,
                     const void* down, int dtype, int I, int H, int E, int n_used, int M, const float* resid,
                     long resid_stride, const float* extra, long extra_stride, float* out, long out_stride,
-                    unsigned* fault, int layer, cudaStream_t st) {
+                    const void* push_desc, unsigned* fault, int layer, cudaStream_t st) {
   BL_REQUIRE(I % 256 == 0 || (dtype == WT_Q8_0 && I % 64 == 0), BL_ERR_SHAPE);
   BL_REQUIRE(M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
   BL_REQUIRE(dtype == WT_Q4_K || dtype == WT_Q5_K || dtype == WT_Q6_K || dtype == WT_Q8_0, BL_ERR_TYPE);
   DownArgs a{actq, (const float2*)actds, ids, wts, slot_map, (const uint8_t*)down, dtype, I, H, E, n_used, M, resid,
-             resid_stride, extra, extra_stride, out, out_stride, fault, layer};
+             resid_stride, extra, extra_stride, out, out_stride, fault, layer, PushOut{}};
+  if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks && M <= kMaxRows, BL_ERR_SHAPE); }
   const long total = (long)n_used * (I / 64);
   BL_REQUIRE(total <= 512, BL_ERR_LIMIT);
   dim3 grid((H + 7) / 8, M);

@@ -47,6 +47,26 @@ class QWeight:
         return self.data.numel()
 
 
+class PushOut(ctypes.Structure):
+    """Producer half of the fused all-reduce (mirrors ``bl::PushOut`` in csrc/common.cuh)."""
+
+    _fields_ = [("local", ctypes.c_void_p), ("peer_recv", ctypes.c_void_p * 8), ("peer_flag", ctypes.c_void_p * 8),
+                ("seq", ctypes.c_void_p), ("ticket", ctypes.c_void_p), ("n_ranks", ctypes.c_int),
+                ("my_rank", ctypes.c_int), ("n_floats", ctypes.c_int)]
+
+
+class ReduceIn(ctypes.Structure):
+    """Consumer half of the fused all-reduce (mirrors ``bl::ReduceIn``)."""
+
+    _fields_ = [("recv", ctypes.c_void_p), ("flags", ctypes.c_void_p), ("seq", ctypes.c_void_p),
+                ("x_out", ctypes.c_void_p), ("x_out_stride", ctypes.c_long), ("n_ranks", ctypes.c_int),
+                ("H", ctypes.c_int), ("fault", ctypes.c_void_p), ("layer", ctypes.c_int)]
+
+
+def _ref(s):
+    return ctypes.byref(s) if s is not None else ctypes.c_void_p(0)
+
+
 def set_pdl(on: bool) -> None:
     cuda().bl_set_pdl(I(1 if on else 0))
 
@@ -54,7 +74,7 @@ def set_pdl(on: bool) -> None:
 def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torch.Tensor] = None,
          gain: Optional[torch.Tensor] = None, eps: float = 1e-6, xq: Optional[torch.Tensor] = None,
          xds: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
-         xq_out: Optional[torch.Tensor] = None, xds_out: Optional[torch.Tensor] = None,
+         red: Optional[ReduceIn] = None, push: Optional[PushOut] = None,
          fault: Optional[torch.Tensor] = None, layer: int = 0) -> None:
     n = len(segs)
     K = segs[0].k
@@ -65,7 +85,7 @@ def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torc
     rc = cuda().bl_gemv(I(n), wp, rows, wts, I(K), I(M), I(1 if norm else 0),
                         p(x), L(x.stride(0) if norm else 0), p(gain), F(eps), p(xq), p(xds),
                         p(out), L(out.stride(0)), p(resid), L(resid.stride(0) if resid is not None else 0),
-                        p(xq_out), p(xds_out), p(fault), I(layer), I(sm_count()), stream())
+                        _ref(red), _ref(push), p(fault), I(layer), I(sm_count()), stream())
     check(rc, "bl_gemv")
 
 
@@ -88,10 +108,11 @@ def flash_decode(q, k_cache, v_cache, row_pos, row_seq, block_table, n_pages: in
     check(rc, "bl_flash_decode")
 
 
-def router(x, gain, eps: float, w: QWeight, M: int, logits, xq_out, xds_out, xn_out, fault, layer: int) -> None:
+def router(x, gain, eps: float, w: QWeight, M: int, logits, xq_out, xds_out, xn_out, fault, layer: int,
+           red: Optional[ReduceIn] = None) -> None:
     """Router logits of M rows (RMSNorm folded in) + the q8 form of the normed rows."""
     rc = cuda().bl_router(p(x), L(x.stride(0)), p(gain), F(eps), p(w.data), I(w.wt), I(w.k), I(w.rows), I(M),
-                          p(logits), p(xq_out), p(xds_out), p(xn_out), p(fault), I(layer), stream())
+                          p(logits), p(xq_out), p(xds_out), p(xn_out), _ref(red), p(fault), I(layer), stream())
     check(rc, "bl_router")
 
 
@@ -130,12 +151,12 @@ def gate_up_sel(xq, xds, ids, slot_map, gate: QWeight, up: QWeight, n_expert: in
 
 
 def down_combine(actq, actds, ids, wts, slot_map, down: QWeight, n_expert: int, n_used: int, M: int, resid, extra,
-                 out, fault, layer: int) -> None:
+                 out, fault, layer: int, push: Optional[PushOut] = None) -> None:
     rc = cuda().bl_down_combine(p(actq), p(actds), p(ids), p(wts), p(slot_map), p(down.data), I(down.wt), I(down.k),
                                 I(down.rows), I(n_expert), I(n_used), I(M), p(resid),
                                 L(resid.stride(0) if resid is not None else 0), p(extra),
-                                L(extra.stride(0) if extra is not None else 0), p(out), L(out.stride(0)), p(fault),
-                                I(layer), stream())
+                                L(extra.stride(0) if extra is not None else 0), p(out), L(out.stride(0)), _ref(push),
+                                p(fault), I(layer), stream())
     check(rc, "bl_down_combine")
 
 

@@ -1,0 +1,189 @@
+"""Tensor-parallel attention + expert-parallel MoE decode over the GPUs of one node.
+
+Each rank holds ``n_q / N`` query heads with their KV head(s), the matching K-slice of
+o_proj, and ``E / N`` routed experts; embeddings, norms, router and the output head are
+replicated (the reference's TP ranks split heads / FFN width and replicate router, norms
+and embedding the same way: ``crates/gpu-glm5next/src/tp/mod.rs:5-12``).
+
+Every layer needs two reductions of the residual update (after o_proj, after the
+experts).  They are not collectives of their own: the producing kernel pushes its partial
+rows into every peer's HBM over NVLink in its last block, and the next kernel's prologue
+waits for the N flags and adds the partials in rank order (``csrc/common.cuh``,
+"Fused all-reduce").  All ranks therefore hold bit-identical residual rows and pick the same
+token without exchanging it.  ``NcclBaseline`` below is the same engine with the two
+reductions done by ``torch.distributed.all_reduce`` -- the baseline the fused path is
+measured against.
+"""
+from __future__ import annotations
+
+import dataclasses
+import functools
+import math
+from typing import Iterator, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..formats.quant import QTYPES
+from ..models.spec import ModelSpec
+from ..models.weights import TensorItem, Weights
+from ..ops import decode as K
+from ..runtime.engine import DecodeEngine
+from .symm import SymmetricArena
+
+SITE_ATTN, SITE_MOE = 0, 1
+
+
+def shard_items(items: Iterator[TensorItem], spec: ModelSpec, rank: int, world: int) -> Iterator[TensorItem]:
+    """Slice a full tensor stream down to one rank's share (raw block bytes, no re-quantisation)."""
+    if spec.n_q % world or (spec.is_moe and spec.n_expert % world):
+        raise ValueError(f"{world} ranks do not divide {spec.n_q} heads / {spec.n_expert} experts")
+    hd = spec.head_dim
+    q_lo, q_hi = rank * spec.q_rows // world, (rank + 1) * spec.q_rows // world
+    if spec.n_kv >= world:
+        kv_lo, kv_hi = rank * spec.kv_rows // world, (rank + 1) * spec.kv_rows // world
+    else:
+        kvh = rank // (world // spec.n_kv)
+        kv_lo, kv_hi = kvh * hd, (kvh + 1) * hd
+    for name, shape, qtype, raw in items:
+        qt = QTYPES[qtype]
+        if name.endswith("attn_q.weight"):
+            yield name, (q_hi - q_lo, shape[1]), qtype, raw[q_lo:q_hi]
+        elif name.endswith("attn_k.weight") or name.endswith("attn_v.weight"):
+            yield name, (kv_hi - kv_lo, shape[1]), qtype, raw[kv_lo:kv_hi]
+        elif name.endswith("attn_output.weight"):
+            bv, bb = qt.block_values, qt.block_bytes
+            if q_lo % bv or q_hi % bv:
+                raise ValueError(f"{name}: a K-slice of {q_hi - q_lo} columns does not align to {bv}-value blocks")
+            blk = raw.reshape(shape[0], shape[1] // bv, bb)[:, q_lo // bv:q_hi // bv]
+            yield name, (shape[0], q_hi - q_lo), qtype, blk.reshape(shape[0], -1).contiguous()
+        elif "_exps.weight" in name:
+            e_lo, e_hi = rank * shape[0] // world, (rank + 1) * shape[0] // world
+            yield name, (e_hi - e_lo, shape[1], shape[2]), qtype, raw[e_lo * shape[1]:e_hi * shape[1]]
+        else:
+            yield name, shape, qtype, raw
+
+
+def local_spec(spec: ModelSpec, world: int) -> ModelSpec:
+    s = dataclasses.replace(spec)
+    s.n_q = spec.n_q // world
+    s.n_kv = max(1, spec.n_kv // world)
+    return s
+
+
+class ShardedEngine(DecodeEngine):
+    """One rank of the TP-attention + EP-experts decode engine."""
+
+    def __init__(self, weights: Weights, full_spec: ModelSpec, rank: int, world: int, group=None, fused: bool = True,
+                 arena: Optional[SymmetricArena] = None, **kw):
+        self.full_spec = full_spec
+        self.rank, self.world, self.group = rank, world, group
+        self.fused = fused
+        super().__init__(weights, **kw)
+        s, dev = self.spec, self.device
+        self.arena = arena or SymmetricArena(s.hidden, rank, world, dev, group, local_only=not fused)
+        self.xbuf = [self.x, torch.zeros_like(self.x)]
+        if s.is_moe:
+            e_per = s.n_expert // world
+            sm = torch.full((s.n_expert,), -1, dtype=torch.int32)
+            sm[rank * e_per:(rank + 1) * e_per] = torch.arange(e_per, dtype=torch.int32)
+            self.slot_map = sm.to(dev)
+        self.partial = torch.zeros(8, s.hidden, dtype=torch.float32, device=dev)
+
+    def enqueue(self, M: int, head: bool = True, advance: bool = False) -> int:
+        ops = self.build_ops(M, head, advance)
+        for op in ops:
+            op()
+        return sum(getattr(op, "launches", 1) for op in ops)
+
+    def build_ops(self, M: int, head: bool = True, advance: bool = False) -> List:
+        """The pass as a list of launch thunks (one kernel launch each unless marked), so a
+        test can interleave the launches of several emulated ranks on one GPU."""
+        s, w, ar = self.spec, self.w, self.arena
+        ops: List = []
+
+        def add(fn, *a, launches: int = 1, **k):
+            t = functools.partial(fn, *a, **k)
+            if launches != 1:
+                t = _Thunk(t, launches)
+            ops.append(t)
+
+        cur = 0
+        xb = self.xbuf
+        add(K.embed_rows, self.tokens, M, w.q["token_embd.weight"], s.vocab, xb[0], self.fault)
+        kvp = self.kv
+        fused = self.fused
+
+        def allreduce_into(xr: torch.Tensor, part: torch.Tensor):
+            # baseline: NCCL sums the partial rows, an eager add applies them to the residual
+            dist.all_reduce(part, group=self.group)
+            xr.add_(part)
+
+        pending = None     # site whose partials the next consumer has to add
+        for il in range(s.n_layer):
+            b = f"blk.{il}."
+            red = None
+            if fused and pending is not None:
+                red = ar.reduce(pending, xb[cur ^ 1], self.fault, il)
+            add(K.gemv, [w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
+                x=xb[cur], gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, red=red, fault=self.fault, layer=il)
+            if red is not None:
+                cur ^= 1
+            add(K.qk_norm_rope_append, self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
+                self.inv_freq, s.rms_eps, 1.0 / math.sqrt(s.head_dim), s.head_dim, s.n_q, s.n_kv, M,
+                self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out, self.fault, il)
+            add(K.flash_decode, self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
+                s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
+                self.attn_q, self.attn_ds, self.fault, il, launches=2)
+            if fused:
+                add(K.gemv, [w.q[b + "attn_output.weight"]], M, ar.local_slot(SITE_ATTN), xq=self.attn_q,
+                    xds=self.attn_ds, push=ar.push(SITE_ATTN, M), fault=self.fault, layer=il)
+                red = ar.reduce(SITE_ATTN, xb[cur ^ 1], self.fault, il)
+            else:
+                add(K.gemv, [w.q[b + "attn_output.weight"]], M, self.partial, xq=self.attn_q, xds=self.attn_ds,
+                    fault=self.fault, layer=il)
+                add(allreduce_into, xb[cur], self.partial, launches=2)
+                red = None
+            if not s.layer_is_moe(il):
+                raise NotImplementedError("dense FFN layers of a sharded model are not split yet")
+            add(K.router, xb[cur], w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M,
+                self.r_logits, self.xq, self.xds, None, self.fault, il, red=red)
+            if red is not None:
+                cur ^= 1
+            add(K.gate_up_sel, self.xq, self.xds, self.r_ids, self.slot_map, w.q[b + "ffn_gate_exps.weight"],
+                w.q[b + "ffn_up_exps.weight"], s.n_expert, s.n_used, M, self.actq, self.actds, None, self.fault, il,
+                route_logits=self.r_logits, rule=self._rule(il), wts=self.r_wts, heat=self.heat[il])
+            if fused:
+                add(K.down_combine, self.actq, self.actds, self.r_ids, self.r_wts, self.slot_map,
+                    w.q[b + "ffn_down_exps.weight"], s.n_expert, s.n_used, M, None, None, ar.local_slot(SITE_MOE),
+                    self.fault, il, push=ar.push(SITE_MOE, M))
+                pending = SITE_MOE
+            else:
+                add(K.down_combine, self.actq, self.actds, self.r_ids, self.r_wts, self.slot_map,
+                    w.q[b + "ffn_down_exps.weight"], s.n_expert, s.n_used, M, None, None, self.partial, self.fault, il)
+                add(allreduce_into, xb[cur], self.partial, launches=2)
+                pending = None
+        if head:
+            head_w = w.q.get("output.weight", w.q["token_embd.weight"])
+            red = ar.reduce(pending, xb[cur ^ 1], self.fault, s.n_layer) if (fused and pending is not None) else None
+            add(K.gemv, [head_w], M, self.logits, x=xb[cur], gain=w.f["output_norm.weight"], eps=s.rms_eps, red=red,
+                fault=self.fault, layer=s.n_layer)
+            add(K.argmax_rows, self.logits, s.vocab, M, self.am_blocks, self.am_v, self.am_i, self.counters[1:2],
+                self.tokens_out, None, self.fault)
+            if advance:
+                add(K.advance_rows, self.tokens, self.row_pos, self.row_seq, self.tokens_out, M, self.hist,
+                    self.hist_cap, self.counters[2:3])
+        elif fused and pending is not None:
+            # no head on this pass: a small consumer folds the last reduction into the residual rows
+            red = ar.reduce(pending, xb[cur ^ 1], self.fault, s.n_layer)
+            add(K.gemv, [w.q["blk.0.attn_k.weight"]], M, self.qkv, x=xb[cur], gain=w.f["output_norm.weight"],
+                eps=s.rms_eps, red=red, fault=self.fault, layer=s.n_layer)
+        return ops
+
+
+class _Thunk:
+    def __init__(self, fn, launches: int):
+        self.fn, self.launches = fn, launches
+
+    def __call__(self):
+        return self.fn()

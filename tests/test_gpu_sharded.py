@@ -1,0 +1,97 @@
+"""TP-attention + EP-experts engine with the fused reductions, two ranks emulated on one GPU.
+
+Kernels that wait on one another must never run as separate launches that could both be
+waiting, so the two ranks' launch lists are interleaved on one stream: launch i of rank 0,
+then launch i of rank 1.  Every consumer then finds both producers' flags already set and
+the bounded wait returns at once; what is checked is the data path (push into the peer's
+slot, flags, rank-ordered sum, residual ping-pong), against the single-GPU engine."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _engines(world=2):
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.parallel.sharded import ShardedEngine, local_spec, shard_items
+    from bloomery_b200.parallel.symm import SymmetricArena
+    from bloomery_b200.runtime.engine import DecodeEngine
+    spec = tiny_qwen3moe()
+    items = list(synth_tensors(spec, "cpu", seed=9))
+    ref = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=1, slot_ctx=256, use_graphs=False)
+    arenas = [SymmetricArena(spec.hidden, r, world, DEV, local_only=True) for r in range(world)]
+    for a in arenas:
+        a.adopt_peers(arenas)
+    engs = []
+    for r in range(world):
+        w = Weights.from_items(local_spec(spec, world), shard_items(iter(items), spec, r, world), DEV)
+        engs.append(ShardedEngine(w, spec, r, world, fused=True, arena=arenas[r], n_slots=1, slot_ctx=256,
+                                  use_graphs=False))
+    return spec, ref, engs
+
+
+def _lockstep(engs, rows):
+    Ms = [e.set_rows(rows) for e in engs]
+    lists = [e.build_ops(Ms[0], True, False) for e in engs]
+    assert len(set(len(l) for l in lists)) == 1
+    for step in zip(*lists):
+        for op in step:
+            op()
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_two_emulated_ranks_match_single_gpu(world):
+    spec, ref, engs = _engines(world)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, spec.vocab, (11,), generator=g).tolist()
+    pos = 0
+    for chunk in (toks[:8], toks[8:]):
+        rows = [(0, t, pos + i) for i, t in enumerate(chunk)]
+        ref.step(rows)
+        _lockstep(engs, rows)
+        pos += len(chunk)
+        n = len(chunk)
+        for e in engs:
+            assert (int(e.fault) & 0xFFFFFFFF) == 0xFFFFFFFF
+            assert torch.equal(e.logits[:n], engs[0].logits[:n])            # ranks agree bit for bit
+        err = ((engs[0].logits[:n] - ref.logits[:n]).abs().max() / ref.logits[:n].abs().max()).item()
+        assert err < 2e-2, err      # sum order differs; a 1-ulp change can flip a q8 code downstream
+        assert engs[0].tokens_out[:n].tolist() == engs[1].tokens_out[:n].tolist()
+
+
+def test_missing_peer_times_out_with_a_status_not_a_hang():
+    """A consumer whose peer never pushed gives up after its bounded wait and raises the
+    wait-timeout site in the fault word; the context stays usable."""
+    import time
+    spec, ref, engs = _engines(2)
+    e0 = engs[0]
+    rows = [(0, 5, 0)]
+    M = e0.set_rows(rows)
+    ops = e0.build_ops(M, True, False)
+    t0 = time.time()
+    for op in ops[:7]:            # embed .. router of layer 0: the router waits for rank 1, which never runs
+        op()
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 20
+    assert (int(e0.fault) & 0xFF) == 7                                      # FS_WAIT_TIMEOUT
+    x = torch.ones(4, device=DEV)
+    assert float((x + 1).sum()) == 8.0                                      # the context still answers
+
+
+def test_shard_items_partition_the_weights():
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import synth_tensors
+    from bloomery_b200.parallel.sharded import shard_items
+    spec = tiny_qwen3moe()
+    items = list(synth_tensors(spec, "cpu", seed=1))
+    full = {n: r for n, _, _, r in items}
+    parts = [{n: (sh, r) for n, sh, _, r in shard_items(iter(items), spec, rk, 2)} for rk in range(2)]
+    q = torch.cat([parts[0]["blk.0.attn_q.weight"][1], parts[1]["blk.0.attn_q.weight"][1]], 0)
+    assert torch.equal(q, full["blk.0.attn_q.weight"])
+    e = torch.cat([parts[0]["blk.1.ffn_down_exps.weight"][1], parts[1]["blk.1.ffn_down_exps.weight"][1]], 0)
+    assert torch.equal(e, full["blk.1.ffn_down_exps.weight"])
+    o0, o1 = parts[0]["blk.0.attn_output.weight"], parts[1]["blk.0.attn_output.weight"]
+    assert o0[0] == (spec.hidden, spec.q_rows // 2) and o0[1].shape[1] + o1[1].shape[1] == full["blk.0.attn_output.weight"].shape[1]
