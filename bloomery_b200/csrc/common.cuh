@@ -111,43 +111,44 @@ __device__ __forceinline__ void block_rmsnorm_q8(const float* __restrict__ x, co
 // ------------------------------------------------------------------------------------
 // Fused all-reduce of the residual-stream update across GPUs (tensor-parallel attention
 // output, expert-parallel MoE output), split into a producer half and a consumer half
-// that live inside the compute kernels:
+// that live inside the compute kernels.  The transport is flag-in-data: every element
+// travels as one 8-byte store {value bits, epoch}, which the hardware writes atomically,
+// so neither fences nor completion tickets nor separate flags are needed and the latency
+// is one NVLink write.
 //
 //   producer  the kernel that computes a partial [M, H] update (o_proj GEMV over this
 //             rank's heads; down-projection + combine over this rank's experts) stores
-//             it in its own receive slot; the last block to finish copies the rows into
-//             slot `my_rank` of every peer's receive buffer with 16-byte stores over
-//             NVLink, fences system-wide and then stores the site's sequence number into
-//             flag `my_rank` on every peer (st.release.sys).
-//   consumer  the next kernel's prologue (router / QKV / head GEMV) waits until all N
-//             flags reached the local sequence number, adds the N partial rows to the
-//             residual in rank order (bit-identical on every rank) and carries on; block 0
-//             also stores the new residual rows.
+//             each finished value, tagged with the site's epoch, into slot `my_rank` of
+//             every rank's receive buffer (plain st.global.v2 through the peer mapping).
+//   consumer  the next kernel's prologue (router / QKV / head GEMV) reads, for every
+//             element, the N tagged values, spinning on a slot until its tag equals the
+//             epoch, and adds them to the residual in rank order (bit-identical on every
+//             rank); block 0 also stores the new residual rows.
 //
-// Two sites (attention, MoE) alternate, each with its own buffers; a rank can only reach a
-// site's next producer after every rank consumed the previous one, so one buffer per site
-// suffices.  The wait is bounded (1 s on the global timer): on expiry the kernel raises
-// FS_WAIT_TIMEOUT in the fault word and continues, it never hangs.  The reference makes the
-// same reduction as "all-gather of f32 row spans + every rank sums parts in rank order"
-// through host-mapped pages (crates/gpu/src/host/link/gather.rs:1-27).
+// The epoch of a site is  step * sites_per_step + site_index + 1, where `step` is a device
+// word that the first kernel of every pass increments; all ranks run the same passes, so
+// they agree on it without talking.  Two buffers (attention site, MoE site) alternate: a
+// rank reaches a site's next producer only after every rank consumed the previous one.
+// Waits are bounded (1 s on the global timer, shared per block): on expiry the kernel
+// raises FS_WAIT_TIMEOUT in the fault word, yields NaN and continues; it never hangs.
+// The reference makes the same reduction as "all-gather of f32 row spans + every rank sums
+// parts in rank order" through host-mapped pages (crates/gpu/src/host/link/gather.rs:1-27).
 // ------------------------------------------------------------------------------------
 constexpr int kMaxRanks = 8;
 constexpr int kMaxRows = 8;
 
 struct PushOut {
-  float* local;                 // this rank's slot of its own receive buffer: [kMaxRows][H]
-  float* peer_recv[kMaxRanks];  // slot `my_rank` of every rank's receive buffer (own entry == local)
-  unsigned* peer_flag[kMaxRanks];
-  unsigned* seq;                // local sequence number of this site
-  unsigned* ticket;             // block-completion ticket, zero at rest
-  int n_ranks, my_rank, n_floats;
+  uint2* peer_recv[kMaxRanks];  // slot `my_rank` of every rank's receive buffer: [kMaxRows][H] of {bits, epoch}
+  const unsigned* step;         // device word: passes started so far
+  unsigned sites_per_step, site_index;
+  int n_ranks, my_rank;
 };
 
 struct ReduceIn {
-  const float* recv;            // [n_ranks][kMaxRows][H]
-  const unsigned* flags;        // [n_ranks]
-  const unsigned* seq;          // local sequence number of the site to consume
-  float* x_out;                 // residual rows to update (block 0 stores them), may equal the input
+  const uint2* recv;            // [n_ranks][kMaxRows][H] of {bits, epoch}
+  const unsigned* step;
+  unsigned sites_per_step, site_index;
+  float* x_out;                 // residual rows to update (block 0 stores them); never the input buffer
   long x_out_stride;
   int n_ranks, H;
   unsigned* fault;
@@ -160,67 +161,54 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
-// Every thread of every block calls this after its stores to p.local.
-__device__ __forceinline__ void push_finish(const PushOut& p) {
-  __shared__ int s_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(p.ticket, 1u) == gridDim.x * gridDim.y * gridDim.z - 1) ? 1 : 0;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  if (threadIdx.x == 0) *p.ticket = 0u;
-  const int n4 = p.n_floats / 4;
-  for (int r = 0; r < p.n_ranks; ++r) {
-    if (r == p.my_rank) continue;
-    float4* dst = reinterpret_cast<float4*>(p.peer_recv[r]);
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = __ldcg(reinterpret_cast<const float4*>(p.local) + i);
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < p.n_ranks) {
-    const unsigned e = *p.seq + 1u;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flag[threadIdx.x]), "r"(e) : "memory");
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) *p.seq = *p.seq + 1u;
+__device__ __forceinline__ unsigned site_epoch(const unsigned* step, unsigned sites_per_step, unsigned site_index) {
+  return *step * sites_per_step + site_index + 1u;
 }
 
-// Wait for every rank's flag (bounded); true when all arrived.  Called by all threads of a block.
-__device__ __forceinline__ bool reduce_wait(const ReduceIn& r) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if (threadIdx.x < r.n_ranks) {
-    const unsigned want = *r.seq;
-    const unsigned* f = r.flags + threadIdx.x;
-    unsigned long long t0 = 0;
-    for (unsigned it = 0;; ++it) {
-      unsigned v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-      if ((int)(v - want) >= 0) break;
-      if ((it & 255) == 255) {
-        const unsigned long long now = global_timer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > 1000000000ull) { s_ok = 0; raise_fault(r.fault, r.layer, FS_WAIT_TIMEOUT); break; }
-      }
+// One value of the partial update, tagged and stored into every rank's slot (own copy included).
+__device__ __forceinline__ void push_store(const PushOut& p, unsigned epoch, long idx, float v) {
+  const uint2 w = make_uint2(__float_as_uint(v), epoch);
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r)
+    if (r < p.n_ranks) {
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.peer_recv[r] + idx), "r"(w.x), "r"(w.y) : "memory");
+    }
+}
+
+// Per-block state of the consumer's bounded waits.
+struct ReduceWait {
+  unsigned epoch;
+  unsigned long long t0;
+  volatile int* gave_up;    // shared by the block
+};
+
+__device__ __forceinline__ float reduce_take(const ReduceIn& r, ReduceWait& w, const uint2* slot) {
+  for (unsigned it = 0;; ++it) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(slot) : "memory");
+    if (v.y == w.epoch) return __uint_as_float(v.x);
+    if ((it & 127) == 127) {
+      if (*w.gave_up) break;
+      const unsigned long long now = global_timer_ns();
+      if (w.t0 == 0) w.t0 = now;
+      else if (now - w.t0 > 1000000000ull) { *w.gave_up = 1; raise_fault(r.fault, r.layer, FS_WAIT_TIMEOUT); break; }
     }
   }
-  __syncthreads();
-  return s_ok != 0;
+  return __int_as_float(0x7fc00000);
 }
 
 // Residual value (row m, column i) after the reduction: x + sum over ranks in rank order.
-__device__ __forceinline__ float reduce_value(const ReduceIn& r, const float* x_row, int m, int i) {
+__device__ __forceinline__ float reduce_value(const ReduceIn& r, ReduceWait& w, const float* x_row, int m, int i) {
   float v = x_row[i];
-  for (int k = 0; k < r.n_ranks; ++k) v += __ldcg(r.recv + ((long)k * kMaxRows + m) * r.H + i);
+  for (int k = 0; k < r.n_ranks; ++k) v += reduce_take(r, w, r.recv + ((long)k * kMaxRows + m) * r.H + i);
   return v;
 }
-__device__ __forceinline__ float4 reduce_value4(const ReduceIn& r, const float* x_row, int m, int i) {
+__device__ __forceinline__ float4 reduce_value4(const ReduceIn& r, ReduceWait& w, const float* x_row, int m, int i) {
   float4 v = *reinterpret_cast<const float4*>(x_row + i);
   for (int k = 0; k < r.n_ranks; ++k) {
-    const float4 p = __ldcg(reinterpret_cast<const float4*>(r.recv + ((long)k * kMaxRows + m) * r.H + i));
-    v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    const uint2* s = r.recv + ((long)k * kMaxRows + m) * r.H + i;
+    v.x += reduce_take(r, w, s); v.y += reduce_take(r, w, s + 1);
+    v.z += reduce_take(r, w, s + 2); v.w += reduce_take(r, w, s + 3);
   }
   return v;
 }

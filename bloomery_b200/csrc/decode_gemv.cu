@@ -61,7 +61,13 @@ __device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, flo
                                               double* red) {
   const int K = a.K, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool reduce = a.red.n_ranks > 0;
-  if (reduce) reduce_wait(a.red);
+  __shared__ int s_gave_up;
+  ReduceWait rw{0u, 0ull, &s_gave_up};
+  if (reduce) {
+    if (tid == 0) s_gave_up = 0;
+    __syncthreads();
+    rw.epoch = site_epoch(a.red.step, a.red.sites_per_step, a.red.site_index);
+  }
 #pragma unroll 1
   for (int m = 0; m < MB; ++m) {
     const int ms = m < a.M ? m : a.M - 1;
@@ -70,7 +76,7 @@ __device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, flo
     for (int i0 = tid * 8; i0 < K; i0 += 256 * 8) {
       float4 x0, x1;
       if (reduce) {
-        x0 = reduce_value4(a.red, x, ms, i0); x1 = reduce_value4(a.red, x, ms, i0 + 4);
+        x0 = reduce_value4(a.red, rw, x, ms, i0); x1 = reduce_value4(a.red, rw, x, ms, i0 + 4);
         if (blockIdx.x == 0 && m < a.M) {
           *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0) = x0;
           *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0 + 4) = x1;
@@ -142,6 +148,7 @@ __device__ __forceinline__ void rows_q(const GemvArgs& a, const GemvSeg& s, int 
   using U = Unit<T>;
   const int K = a.K, lane = threadIdx.x & 31;
   const int nunits = K / 64;
+  const unsigned push_epoch = a.push.n_ranks > 0 ? site_epoch(a.push.step, a.push.sites_per_step, a.push.site_index) : 0u;
   for (int r0 = r_lo; r0 < r_hi || r0 == r_lo; r0 += R) {
     float acc[R][MB];
 #pragma unroll
@@ -187,7 +194,7 @@ __device__ __forceinline__ void rows_q(const GemvArgs& a, const GemvSeg& s, int 
           for (int m = 0; m < MB; ++m)
             if (m < a.M) {
               float v = acc[r][m] * s_scale[m];
-              if (a.push.n_ranks > 0) { a.push.local[(long)m * a.out_stride + col] = v; continue; }
+              if (a.push.n_ranks > 0) { push_store(a.push, push_epoch, (long)m * a.out_stride + col, v); continue; }
               if (a.resid) v += a.resid[(long)m * a.resid_stride + col];
               a.out[(long)m * a.out_stride + col] = v;
             }
@@ -203,6 +210,7 @@ template <int MB, int R, class Between>
 __device__ __forceinline__ void rows_f(const GemvArgs& a, const GemvSeg& s, int r_lo, int r_hi, int out_col0,
                                        const float* sx, const float* s_scale, Between&& between) {
   const int K = a.K, lane = threadIdx.x & 31;
+  const unsigned push_epoch = a.push.n_ranks > 0 ? site_epoch(a.push.step, a.push.sites_per_step, a.push.site_index) : 0u;
   for (int r0 = r_lo; r0 < r_hi || r0 == r_lo; r0 += R) {
     float acc[R][MB];
 #pragma unroll
@@ -255,7 +263,7 @@ __device__ __forceinline__ void rows_f(const GemvArgs& a, const GemvSeg& s, int 
           for (int m = 0; m < MB; ++m)
             if (m < a.M) {
               float v = acc[r][m] * s_scale[m];
-              if (a.push.n_ranks > 0) { a.push.local[(long)m * a.out_stride + col] = v; continue; }
+              if (a.push.n_ranks > 0) { push_store(a.push, push_epoch, (long)m * a.out_stride + col, v); continue; }
               if (a.resid) v += a.resid[(long)m * a.resid_stride + col];
               a.out[(long)m * a.out_stride + col] = v;
             }
@@ -306,7 +314,6 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
     }
   }
   between();
-  if (a.push.n_ranks > 0) push_finish(a.push);
 }
 
 static size_t gemv_smem(int MB, int K, bool floatw) {
@@ -401,7 +408,7 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
   a.out = out; a.out_stride = out_stride; a.resid = resid; a.resid_stride = resid_stride;
   a.fault = fault; a.layer = layer;
   if (red_desc) { a.red = *(const ReduceIn*)red_desc; BL_REQUIRE(norm && a.red.n_ranks <= kMaxRanks && a.red.H == K, BL_ERR_SHAPE); }
-  if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks && a.push.n_floats % 4 == 0, BL_ERR_SHAPE); }
+  if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks, BL_ERR_SHAPE); }
   BL_REQUIRE(gemv_smem(mb, K, floatw) <= 200 * 1024, BL_ERR_LIMIT);
   cudaError_t e;
   if (norm) e = floatw ? gemv_dispatch_shape<true, true>(a, mb, R, C, grid, st) : gemv_dispatch_shape<true, false>(a, mb, R, C, grid, st);

@@ -15,6 +15,7 @@ struct EmbedArgs {
   const uint8_t* table; int wtype; int K; int vocab;
   float* out; long out_stride;
   unsigned* fault;
+  unsigned* step;       // optional: pass counter, bumped once per launch (epochs of the fused reductions)
 };
 
 template <class T>
@@ -34,6 +35,7 @@ __global__ void __launch_bounds__(128) embed_rows_kernel(const EmbedArgs a) {
   const int m = blockIdx.x, tid = threadIdx.x;
   pdl_wait();
   pdl_launch();
+  if (a.step && m == 0 && tid == 0) *a.step = *a.step + 1u;
   const int tok = a.tokens[m];
   float* out = a.out + (long)m * a.out_stride;
   if (tok < 0 || tok >= a.vocab) {
@@ -168,10 +170,10 @@ using namespace bl;
 extern "C" {
 
 int bl_embed_rows(const int* tokens, int M, const void* table, int wtype, int K, int vocab, float* out, long out_stride,
-                  unsigned* fault, cudaStream_t st) {
+                  unsigned* fault, unsigned* step, cudaStream_t st) {
   BL_REQUIRE(M >= 1 && K % 64 == 0, BL_ERR_SHAPE);
   BL_REQUIRE(resident_row_bytes(wtype, K) > 0, BL_ERR_TYPE);
-  EmbedArgs a{tokens, M, (const uint8_t*)table, wtype, K, vocab, out, out_stride, fault};
+  EmbedArgs a{tokens, M, (const uint8_t*)table, wtype, K, vocab, out, out_stride, fault, step};
   return (int)launch(embed_rows_kernel, dim3(M), dim3(128), 0, st, a);
 }
 

@@ -166,6 +166,8 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
 #pragma unroll
   for (int m = 0; m < MB; ++m) { dot[m] = 0.f; ss[m] = 0.f; }
   bool waited = false;
+  __shared__ int s_gave_up;
+  ReduceWait rw{0u, 0ull, &s_gave_up};
   for (int i0 = tid * 8; i0 < K; i0 += 2048) {
     float wv[8];
     if (a.wtype == WT_F32) {
@@ -182,14 +184,21 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
       }
     }
     float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gain + i0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gain + i0 + 4));
-    if (!waited) { pdl_wait(); waited = true; if (a.red.n_ranks > 0) reduce_wait(a.red); }
+    if (!waited) {
+      pdl_wait(); waited = true;
+      if (a.red.n_ranks > 0) {
+        if (tid == 0) s_gave_up = 0;
+        __syncthreads();
+        rw.epoch = site_epoch(a.red.step, a.red.sites_per_step, a.red.site_index);
+      }
+    }
 #pragma unroll
     for (int m = 0; m < MB; ++m) {
       const int ms = m < a.M ? m : a.M - 1;
       const float* xr = a.x + (long)ms * a.x_stride;
       float4 x0, x1;
       if (a.red.n_ranks > 0) {
-        x0 = reduce_value4(a.red, xr, ms, i0); x1 = reduce_value4(a.red, xr, ms, i0 + 4);
+        x0 = reduce_value4(a.red, rw, xr, ms, i0); x1 = reduce_value4(a.red, rw, xr, ms, i0 + 4);
         if (e == 0 && m < a.M) {
           *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0) = x0;
           *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0 + 4) = x1;
@@ -204,7 +213,14 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
       dot[m] = t;
     }
   }
-  if (!waited) { pdl_wait(); if (a.red.n_ranks > 0) reduce_wait(a.red); }
+  if (!waited) {
+    pdl_wait();
+    if (a.red.n_ranks > 0) {
+      if (tid == 0) s_gave_up = 0;
+      __syncthreads();
+      rw.epoch = site_epoch(a.red.step, a.red.sites_per_step, a.red.site_index);
+    }
+  }
   pdl_launch();
 #pragma unroll
   for (int m = 0; m < MB; ++m) {
@@ -228,7 +244,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
     for (int b = e * 8 + warp; b < nb32 * a.M; b += gridDim.x * 8) {
       const int m = b / nb32, bb = b - m * nb32;
       const int i = bb * 32 + lane;
-      const float xv = a.red.n_ranks > 0 ? reduce_value(a.red, a.x + (long)m * a.x_stride, m, i) : a.x[(long)m * a.x_stride + i];
+      const float xv = a.red.n_ranks > 0 ? reduce_value(a.red, rw, a.x + (long)m * a.x_stride, m, i) : a.x[(long)m * a.x_stride + i];
       const float v = xv * a.gain[i] * s_scale[m];
       float d, sm;
       int8_t qv = q8_lane(v, d, sm);
@@ -450,14 +466,13 @@ __global__ void __launch_bounds__(256, UPL <= 3 ? 2 : 1) down_combine_kernel(con
       if (bad) { y = __int_as_float(0x7fc00000); if (d == 0) raise_fault(a.fault, a.layer, FS_EXPERT_ID); }
       if (a.extra) y += a.extra[(long)m * a.extra_stride + d];
       if (a.push.n_ranks > 0) {
-        a.push.local[(long)m * a.out_stride + d] = y;
+        push_store(a.push, site_epoch(a.push.step, a.push.sites_per_step, a.push.site_index), (long)m * a.out_stride + d, y);
       } else {
         if (a.resid) y += a.resid[(long)m * a.resid_stride + d];
         a.out[(long)m * a.out_stride + d] = y;
       }
     }
   }
-  if (a.push.n_ranks > 0) push_finish(a.push);
 }
 
 }  // namespace bl

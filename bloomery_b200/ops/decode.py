@@ -50,17 +50,16 @@ class QWeight:
 class PushOut(ctypes.Structure):
     """Producer half of the fused all-reduce (mirrors ``bl::PushOut`` in csrc/common.cuh)."""
 
-    _fields_ = [("local", ctypes.c_void_p), ("peer_recv", ctypes.c_void_p * 8), ("peer_flag", ctypes.c_void_p * 8),
-                ("seq", ctypes.c_void_p), ("ticket", ctypes.c_void_p), ("n_ranks", ctypes.c_int),
-                ("my_rank", ctypes.c_int), ("n_floats", ctypes.c_int)]
+    _fields_ = [("peer_recv", ctypes.c_void_p * 8), ("step", ctypes.c_void_p), ("sites_per_step", ctypes.c_uint),
+                ("site_index", ctypes.c_uint), ("n_ranks", ctypes.c_int), ("my_rank", ctypes.c_int)]
 
 
 class ReduceIn(ctypes.Structure):
     """Consumer half of the fused all-reduce (mirrors ``bl::ReduceIn``)."""
 
-    _fields_ = [("recv", ctypes.c_void_p), ("flags", ctypes.c_void_p), ("seq", ctypes.c_void_p),
-                ("x_out", ctypes.c_void_p), ("x_out_stride", ctypes.c_long), ("n_ranks", ctypes.c_int),
-                ("H", ctypes.c_int), ("fault", ctypes.c_void_p), ("layer", ctypes.c_int)]
+    _fields_ = [("recv", ctypes.c_void_p), ("step", ctypes.c_void_p), ("sites_per_step", ctypes.c_uint),
+                ("site_index", ctypes.c_uint), ("x_out", ctypes.c_void_p), ("x_out_stride", ctypes.c_long),
+                ("n_ranks", ctypes.c_int), ("H", ctypes.c_int), ("fault", ctypes.c_void_p), ("layer", ctypes.c_int)]
 
 
 def _ref(s):
@@ -160,9 +159,9 @@ def down_combine(actq, actds, ids, wts, slot_map, down: QWeight, n_expert: int, 
     check(rc, "bl_down_combine")
 
 
-def embed_rows(tokens, M: int, table: QWeight, vocab: int, out, fault) -> None:
+def embed_rows(tokens, M: int, table: QWeight, vocab: int, out, fault, step=None) -> None:
     rc = cuda().bl_embed_rows(p(tokens), I(M), p(table.data), I(table.wt), I(table.k), I(vocab), p(out),
-                              L(out.stride(0)), p(fault), stream())
+                              L(out.stride(0)), p(fault), p(step), stream())
     check(rc, "bl_embed_rows")
 
 

@@ -89,6 +89,7 @@ class ShardedEngine(DecodeEngine):
             sm[rank * e_per:(rank + 1) * e_per] = torch.arange(e_per, dtype=torch.int32)
             self.slot_map = sm.to(dev)
         self.partial = torch.zeros(8, s.hidden, dtype=torch.float32, device=dev)
+        self.arena.sites_per_step = 2 * s.n_layer
 
     def enqueue(self, M: int, head: bool = True, advance: bool = False) -> int:
         ops = self.build_ops(M, head, advance)
@@ -110,7 +111,7 @@ class ShardedEngine(DecodeEngine):
 
         cur = 0
         xb = self.xbuf
-        add(K.embed_rows, self.tokens, M, w.q["token_embd.weight"], s.vocab, xb[0], self.fault)
+        add(K.embed_rows, self.tokens, M, w.q["token_embd.weight"], s.vocab, xb[0], self.fault, self.arena.step)
         kvp = self.kv
         fused = self.fused
 
@@ -119,12 +120,13 @@ class ShardedEngine(DecodeEngine):
             dist.all_reduce(part, group=self.group)
             xr.add_(part)
 
-        pending = None     # site whose partials the next consumer has to add
+        pending = None     # (site, index) whose partials the next consumer has to add
+        H = s.hidden
         for il in range(s.n_layer):
             b = f"blk.{il}."
             red = None
             if fused and pending is not None:
-                red = ar.reduce(pending, xb[cur ^ 1], self.fault, il)
+                red = ar.reduce(pending[0], pending[1], xb[cur ^ 1], self.fault, il)
             add(K.gemv, [w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
                 x=xb[cur], gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, red=red, fault=self.fault, layer=il)
             if red is not None:
@@ -136,9 +138,9 @@ class ShardedEngine(DecodeEngine):
                 s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
                 self.attn_q, self.attn_ds, self.fault, il, launches=2)
             if fused:
-                add(K.gemv, [w.q[b + "attn_output.weight"]], M, ar.local_slot(SITE_ATTN), xq=self.attn_q,
-                    xds=self.attn_ds, push=ar.push(SITE_ATTN, M), fault=self.fault, layer=il)
-                red = ar.reduce(SITE_ATTN, xb[cur ^ 1], self.fault, il)
+                add(K.gemv, [w.q[b + "attn_output.weight"]], M, self.partial, xq=self.attn_q,
+                    xds=self.attn_ds, push=ar.push(SITE_ATTN, 2 * il), fault=self.fault, layer=il)
+                red = ar.reduce(SITE_ATTN, 2 * il, xb[cur ^ 1], self.fault, il)
             else:
                 add(K.gemv, [w.q[b + "attn_output.weight"]], M, self.partial, xq=self.attn_q, xds=self.attn_ds,
                     fault=self.fault, layer=il)
@@ -155,9 +157,9 @@ class ShardedEngine(DecodeEngine):
                 route_logits=self.r_logits, rule=self._rule(il), wts=self.r_wts, heat=self.heat[il])
             if fused:
                 add(K.down_combine, self.actq, self.actds, self.r_ids, self.r_wts, self.slot_map,
-                    w.q[b + "ffn_down_exps.weight"], s.n_expert, s.n_used, M, None, None, ar.local_slot(SITE_MOE),
-                    self.fault, il, push=ar.push(SITE_MOE, M))
-                pending = SITE_MOE
+                    w.q[b + "ffn_down_exps.weight"], s.n_expert, s.n_used, M, None, None, self.partial,
+                    self.fault, il, push=ar.push(SITE_MOE, 2 * il + 1))
+                pending = (SITE_MOE, 2 * il + 1)
             else:
                 add(K.down_combine, self.actq, self.actds, self.r_ids, self.r_wts, self.slot_map,
                     w.q[b + "ffn_down_exps.weight"], s.n_expert, s.n_used, M, None, None, self.partial, self.fault, il)
@@ -165,7 +167,7 @@ class ShardedEngine(DecodeEngine):
                 pending = None
         if head:
             head_w = w.q.get("output.weight", w.q["token_embd.weight"])
-            red = ar.reduce(pending, xb[cur ^ 1], self.fault, s.n_layer) if (fused and pending is not None) else None
+            red = ar.reduce(pending[0], pending[1], xb[cur ^ 1], self.fault, s.n_layer) if (fused and pending is not None) else None
             add(K.gemv, [head_w], M, self.logits, x=xb[cur], gain=w.f["output_norm.weight"], eps=s.rms_eps, red=red,
                 fault=self.fault, layer=s.n_layer)
             add(K.argmax_rows, self.logits, s.vocab, M, self.am_blocks, self.am_v, self.am_i, self.counters[1:2],
@@ -175,7 +177,7 @@ class ShardedEngine(DecodeEngine):
                     self.hist_cap, self.counters[2:3])
         elif fused and pending is not None:
             # no head on this pass: a small consumer folds the last reduction into the residual rows
-            red = ar.reduce(pending, xb[cur ^ 1], self.fault, s.n_layer)
+            red = ar.reduce(pending[0], pending[1], xb[cur ^ 1], self.fault, s.n_layer)
             add(K.gemv, [w.q["blk.0.attn_k.weight"]], M, self.qkv, x=xb[cur], gain=w.f["output_norm.weight"],
                 eps=s.rms_eps, red=red, fault=self.fault, layer=s.n_layer)
         return ops

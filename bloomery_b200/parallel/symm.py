@@ -7,9 +7,8 @@ The plumbing uses ``torch.distributed`` only: the buffers come from
 group); if that is unavailable the legacy CUDA IPC handles of ``torch`` storages are
 exchanged with ``all_gather_object``.  The kernels never see NCCL.
 
-Layout per rank (bytes):  recv  [2 sites][N ranks][8 rows][H] fp32
-                          flags [2 sites][N ranks] u32          (128-byte aligned)
-                          seq   [2] u32, ticket [2] u32          (local use only)
+Layout per rank:  recv [2 sites][N ranks][8 rows][H] of {value bits, epoch} (8 bytes each).
+The epoch rides in every element, so there are no separate flags.
 """
 from __future__ import annotations
 
@@ -32,9 +31,8 @@ class SymmetricArena:
             raise ValueError(f"at most {MAX_RANKS} ranks per node")
         self.H, self.rank, self.world = hidden, rank, world
         self.device = torch.device(device)
-        self.recv_bytes = 2 * world * MAX_ROWS * hidden * 4
-        self.flag_off = (self.recv_bytes + 127) // 128 * 128
-        self.total = self.flag_off + 256
+        self.recv_bytes = 2 * world * MAX_ROWS * hidden * 8
+        self.total = self.recv_bytes + 256
         self._keep = []
         if world == 1 or local_only:
             self.buf = torch.zeros(self.total, dtype=torch.uint8, device=self.device)
@@ -42,8 +40,9 @@ class SymmetricArena:
             self.how = "local"
         else:
             self.buf, self.ptrs, self.how = self._exchange(group)
-        # local bookkeeping words: seq[2], ticket[2]
-        self.words = torch.zeros(8, dtype=torch.int32, device=self.device)
+        # pass counter: the first kernel of every pass bumps it; epochs derive from it
+        self.step = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sites_per_step = 2
 
     def adopt_peers(self, arenas: List["SymmetricArena"]) -> None:
         """Single-process emulation: point at other arenas on the same device (tests)."""
@@ -82,29 +81,24 @@ class SymmetricArena:
 
     # ---- descriptors -----------------------------------------------------------------
     def _recv(self, base: int, site: int, slot: int) -> int:
-        return base + ((site * self.world + slot) * MAX_ROWS * self.H) * 4
+        return base + ((site * self.world + slot) * MAX_ROWS * self.H) * 8
 
-    def local_slot(self, site: int) -> torch.Tensor:
-        """This rank's own slot of its own receive buffer, as fp32 [8, H]."""
-        off = ((site * self.world + self.rank) * MAX_ROWS * self.H) * 4
-        return self.buf[off:off + MAX_ROWS * self.H * 4].view(torch.float32).view(MAX_ROWS, self.H)
-
-    def push(self, site: int, rows: int) -> PushOut:
+    def push(self, site: int, site_index: int) -> PushOut:
+        """Producer descriptor: ``site`` picks the buffer (0 attention, 1 MoE), ``site_index``
+        numbers the reduction inside the pass (unique per pass)."""
         p = PushOut()
-        p.local = self._recv(self.ptrs[self.rank], site, self.rank)
         for r in range(self.world):
             p.peer_recv[r] = self._recv(self.ptrs[r], site, self.rank)
-            p.peer_flag[r] = self.ptrs[r] + self.flag_off + (site * self.world + self.rank) * 4
-        p.seq = self.words.data_ptr() + site * 4
-        p.ticket = self.words.data_ptr() + (2 + site) * 4
-        p.n_ranks, p.my_rank, p.n_floats = self.world, self.rank, rows * self.H
+        p.step = self.step.data_ptr()
+        p.sites_per_step, p.site_index = self.sites_per_step, site_index
+        p.n_ranks, p.my_rank = self.world, self.rank
         return p
 
-    def reduce(self, site: int, x_out: torch.Tensor, fault: Optional[torch.Tensor], layer: int) -> ReduceIn:
+    def reduce(self, site: int, site_index: int, x_out: torch.Tensor, fault: Optional[torch.Tensor], layer: int) -> ReduceIn:
         r = ReduceIn()
         r.recv = self._recv(self.ptrs[self.rank], site, 0)
-        r.flags = self.ptrs[self.rank] + self.flag_off + site * self.world * 4
-        r.seq = self.words.data_ptr() + site * 4
+        r.step = self.step.data_ptr()
+        r.sites_per_step, r.site_index = self.sites_per_step, site_index
         r.x_out = x_out.data_ptr()
         r.x_out_stride = x_out.stride(0)
         r.n_ranks, r.H = self.world, self.H
