@@ -64,7 +64,7 @@ __device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, flo
   __shared__ int s_gave_up;
   ReduceWait rw{0u, 0ull, &s_gave_up};
   if (reduce) {
-    if (tid == 0) s_gave_up = 0;
+    if (tid == 0) s_gave_up = (a.red.fault && *a.red.fault != 0xFFFFFFFFu) ? 1 : 0;   // a poisoned engine no longer waits
     __syncthreads();
     rw.epoch = site_epoch(a.red.step, a.red.sites_per_step, a.red.site_index);
   }

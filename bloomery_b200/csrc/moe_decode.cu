@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
     if (!waited) {
       pdl_wait(); waited = true;
       if (a.red.n_ranks > 0) {
-        if (tid == 0) s_gave_up = 0;
+        if (tid == 0) s_gave_up = (a.red.fault && *a.red.fault != 0xFFFFFFFFu) ? 1 : 0;   // a poisoned engine no longer waits
         __syncthreads();
         rw.epoch = site_epoch(a.red.step, a.red.sites_per_step, a.red.site_index);
       }
@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
   if (!waited) {
     pdl_wait();
     if (a.red.n_ranks > 0) {
-      if (tid == 0) s_gave_up = 0;
+      if (tid == 0) s_gave_up = (a.red.fault && *a.red.fault != 0xFFFFFFFFu) ? 1 : 0;   // a poisoned engine no longer waits
       __syncthreads();
       rw.epoch = site_epoch(a.red.step, a.red.sites_per_step, a.red.site_index);
     }

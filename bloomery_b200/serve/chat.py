@@ -1,0 +1,423 @@
+"""Chat surface: Jinja chat templates with Hugging Face semantics, client-text guard marks,
+tool-call parsers (hermes JSON, Qwen XML, Mistral, GLM XML), the reasoning split and the
+structured-output constraint.
+
+Counterparts in the reference: ``crates/jinja`` (HF-semantics subset with strict errors),
+``crates/serve/src/{guard,hermes,qwenxml,glmxml,mistral,reasoning}.rs`` and
+``constrain/{schema,program}.rs``.  The template engine here is jinja2's immutable sandbox
+with the extras HF templates use (``raise_exception``, ``strftime_now``, ``tojson``,
+loop controls).
+"""
+from __future__ import annotations
+
+import datetime
+import json
+import re
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import jinja2
+from jinja2.sandbox import ImmutableSandboxedEnvironment
+
+CHATML = (
+    "{% for message in messages %}{{ '<|im_start|>' + message['role'] + '\\n' + message['content'] + '<|im_end|>' + '\\n' }}"
+    "{% endfor %}{% if add_generation_prompt %}{{ '<|im_start|>assistant\\n' }}{% endif %}"
+)
+
+# Private-use characters bracket client text inside the rendered prompt; they are split out
+# again after rendering so the tokenizer never parses control tokens inside them.
+G0, G1 = "\ue000", "\ue001"
+
+
+class TemplateError(ValueError):
+    pass
+
+
+def _raise(msg):
+    raise TemplateError(str(msg))
+
+
+def _env() -> ImmutableSandboxedEnvironment:
+    env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True, undefined=jinja2.StrictUndefined,
+                                        extensions=["jinja2.ext.loopcontrols"])
+    env.globals["raise_exception"] = _raise
+    env.globals["strftime_now"] = lambda fmt: datetime.datetime.now().strftime(fmt)
+    env.filters["tojson"] = lambda v, indent=None, ensure_ascii=False: json.dumps(v, indent=indent, ensure_ascii=ensure_ascii)
+    return env
+
+
+class ChatTemplate:
+    def __init__(self, source: Optional[str] = None, bos: str = "", eos: str = ""):
+        self.source = source or CHATML
+        self.bos, self.eos = bos, eos
+        try:
+            self.tpl = _env().from_string(self.source)
+        except jinja2.TemplateSyntaxError as exc:
+            raise TemplateError(f"chat template line {exc.lineno}: {exc.message}") from None
+
+    @staticmethod
+    def _guard(messages: Sequence[Dict[str, Any]]) -> List[Dict[str, Any]]:
+        out = []
+        for m in messages:
+            m = dict(m)
+            c = m.get("content")
+            if isinstance(c, str):
+                m["content"] = G0 + c + G1
+            elif isinstance(c, list):          # OpenAI content parts: text parts are joined
+                texts = [p.get("text", "") for p in c if isinstance(p, dict) and p.get("type") in ("text", "input_text", "output_text")]
+                bad = [p.get("type") for p in c if isinstance(p, dict) and p.get("type") not in ("text", "input_text", "output_text")]
+                if bad:
+                    raise TemplateError(f"content part type {bad[0]!r} is not supported by this model")
+                m["content"] = G0 + "".join(texts) + G1
+            elif c is None:
+                m["content"] = ""
+            out.append(m)
+        return out
+
+    def render(self, messages: Sequence[Dict[str, Any]], tools: Optional[List[dict]] = None, add_generation_prompt: bool = True,
+               **extra) -> List[Tuple[str, bool]]:
+        """Render to (text, trusted) segments: template markup is trusted, client text is not."""
+        try:
+            s = self.tpl.render(messages=self._guard(messages), tools=tools or None, add_generation_prompt=add_generation_prompt,
+                                bos_token=self.bos, eos_token=self.eos, **extra)
+        except TemplateError:
+            raise
+        except jinja2.TemplateError as exc:
+            raise TemplateError(f"chat template: {exc}") from None
+        segs: List[Tuple[str, bool]] = []
+        for i, part in enumerate(re.split(f"[{G0}{G1}]", s)):
+            if part:
+                segs.append((part, i % 2 == 0))
+        return segs
+
+    def render_text(self, messages, **kw) -> str:
+        return "".join(t for t, _ in self.render(messages, **kw))
+
+
+# ---------------------------------------------------------------------------------------
+# reasoning split
+# ---------------------------------------------------------------------------------------
+def split_reasoning(text: str, open_tag: str = "<think>", close_tag: str = "</think>", started: bool = False) -> Tuple[str, str]:
+    """(reasoning, content).  ``started``: the template already opened the think span."""
+    if started and close_tag in text:
+        r, _, c = text.partition(close_tag)
+        return r.strip(), c.lstrip("\n")
+    if started:
+        return text.strip(), ""
+    i = text.find(open_tag)
+    if i < 0:
+        return "", text
+    j = text.find(close_tag, i)
+    if j < 0:
+        return text[i + len(open_tag):].strip(), text[:i]
+    return text[i + len(open_tag):j].strip(), (text[:i] + text[j + len(close_tag):]).lstrip("\n")
+
+
+# ---------------------------------------------------------------------------------------
+# tool-call scanners
+# ---------------------------------------------------------------------------------------
+def _call(name: str, args: Any, idx: int) -> Dict[str, Any]:
+    return {"id": f"call_{idx}", "type": "function",
+            "function": {"name": name, "arguments": args if isinstance(args, str) else json.dumps(args, ensure_ascii=False)}}
+
+
+def parse_hermes(text: str) -> Tuple[str, List[dict]]:
+    """``<tool_call>{"name":..,"arguments":{..}}</tool_call>`` blocks (Hermes / Qwen2.5 / Qwen3)."""
+    calls, out, pos = [], [], 0
+    for m in re.finditer(r"<tool_call>\s*(.*?)\s*</tool_call>", text, re.S):
+        out.append(text[pos:m.start()])
+        pos = m.end()
+        try:
+            obj = json.loads(m.group(1))
+            calls.append(_call(obj["name"], obj.get("arguments", obj.get("parameters", {})), len(calls)))
+        except (json.JSONDecodeError, KeyError, TypeError):
+            out.append(m.group(0))
+    out.append(text[pos:])
+    return "".join(out).strip(), calls
+
+
+def parse_qwen_xml(text: str) -> Tuple[str, List[dict]]:
+    """``<tool_call><function=NAME><parameter=K>V</parameter>...</function></tool_call>`` (Qwen3-Coder)."""
+    calls, out, pos = [], [], 0
+    for m in re.finditer(r"<tool_call>\s*<function=([^>\s]+)>(.*?)</function>\s*</tool_call>", text, re.S):
+        out.append(text[pos:m.start()])
+        pos = m.end()
+        args = {}
+        for p in re.finditer(r"<parameter=([^>\s]+)>\n?(.*?)\n?</parameter>", m.group(2), re.S):
+            v = p.group(2)
+            try:
+                args[p.group(1)] = json.loads(v)
+            except json.JSONDecodeError:
+                args[p.group(1)] = v
+        calls.append(_call(m.group(1), args, len(calls)))
+    out.append(text[pos:])
+    return "".join(out).strip(), calls
+
+
+def parse_glm_xml(text: str) -> Tuple[str, List[dict]]:
+    """``<tool_call>NAME<arg_key>K</arg_key><arg_value>V</arg_value>...</tool_call>`` (GLM-4.5+)."""
+    calls, out, pos = [], [], 0
+    for m in re.finditer(r"<tool_call>\s*([^\s<]+)\s*(.*?)</tool_call>", text, re.S):
+        out.append(text[pos:m.start()])
+        pos = m.end()
+        keys = re.findall(r"<arg_key>(.*?)</arg_key>\s*<arg_value>(.*?)</arg_value>", m.group(2), re.S)
+        args = {}
+        for k, v in keys:
+            try:
+                args[k] = json.loads(v)
+            except json.JSONDecodeError:
+                args[k] = v
+        calls.append(_call(m.group(1), args, len(calls)))
+    out.append(text[pos:])
+    return "".join(out).strip(), calls
+
+
+def parse_mistral(text: str) -> Tuple[str, List[dict]]:
+    """``[TOOL_CALLS][{"name":..,"arguments":..}, ...]``."""
+    i = text.find("[TOOL_CALLS]")
+    if i < 0:
+        return text, []
+    try:
+        arr = json.loads(text[i + len("[TOOL_CALLS]"):].strip())
+        calls = [_call(o["name"], o.get("arguments", {}), k) for k, o in enumerate(arr if isinstance(arr, list) else [arr])]
+        return text[:i].strip(), calls
+    except (json.JSONDecodeError, KeyError, TypeError):
+        return text, []
+
+
+TOOL_PARSERS = {"hermes": parse_hermes, "qwenxml": parse_qwen_xml, "glmxml": parse_glm_xml, "mistral": parse_mistral}
+
+
+def detect_tool_format(template_source: str) -> str:
+    if "<function=" in template_source:
+        return "qwenxml"
+    if "<arg_key>" in template_source:
+        return "glmxml"
+    if "[TOOL_CALLS]" in template_source:
+        return "mistral"
+    return "hermes"
+
+
+def parse_tool_calls(text: str, fmt: str = "hermes") -> Tuple[str, List[dict]]:
+    content, calls = TOOL_PARSERS.get(fmt, parse_hermes)(text)
+    if not calls and fmt != "hermes":
+        content, calls = parse_hermes(text)
+    return content, calls
+
+
+class ToolCallStream:
+    """Streams ``tool_calls`` deltas: text outside call blocks passes through at once, a call
+    block is held until it closes, then emitted whole (chunking-invariant by construction)."""
+
+    def __init__(self, fmt: str = "hermes", open_tag: str = "<tool_call>", close_tag: str = "</tool_call>"):
+        self.fmt, self.open, self.close = fmt, open_tag, close_tag
+        self.buf = ""
+        self.n_calls = 0
+
+    def push(self, piece: str) -> Tuple[str, List[dict]]:
+        self.buf += piece
+        text_out, calls = "", []
+        while True:
+            i = self.buf.find(self.open)
+            if i < 0:
+                # keep a tail that may be the start of an opening tag
+                keep = 0
+                for k in range(min(len(self.open) - 1, len(self.buf)), 0, -1):
+                    if self.buf.endswith(self.open[:k]):
+                        keep = k
+                        break
+                text_out += self.buf[:len(self.buf) - keep]
+                self.buf = self.buf[len(self.buf) - keep:]
+                return text_out, calls
+            j = self.buf.find(self.close, i)
+            if j < 0:
+                text_out += self.buf[:i]
+                self.buf = self.buf[i:]
+                return text_out, calls
+            text_out += self.buf[:i]
+            _, got = parse_tool_calls(self.buf[i:j + len(self.close)], self.fmt)
+            for c in got:
+                c["id"] = f"call_{self.n_calls}"
+                c["index"] = self.n_calls
+                self.n_calls += 1
+                calls.append(c)
+            self.buf = self.buf[j + len(self.close):]
+
+    def flush(self) -> str:
+        s, self.buf = self.buf, ""
+        return s
+
+
+# ---------------------------------------------------------------------------------------
+# structured output: JSON (optionally against a schema subset) as a prefix validator
+# ---------------------------------------------------------------------------------------
+class JsonConstraint:
+    """Keeps the output a prefix of one JSON value and, when a schema is given, of a value the
+    schema subset accepts: ``type``, ``properties``, ``required``, ``items``, ``enum``,
+    ``const``, ``additionalProperties: false``, ``minItems``/``maxItems``.  ``allowed`` is asked
+    for every candidate piece before it is picked (masked pick), ``done`` when an end-of-turn
+    token is a candidate."""
+
+    def __init__(self, schema: Optional[dict] = None):
+        self.schema = schema
+
+    # -- a small incremental JSON scanner: returns (state, value-so-far validity) -----------
+    @staticmethod
+    def _scan(s: str):
+        """Returns ("bad" | "open" | "closed", depth_stack) for the text as a JSON prefix."""
+        stack: List[str] = []
+        i, n = 0, len(s)
+        expect = "value"            # value | key | colon | comma_or_end | end
+        while i < n:
+            c = s[i]
+            if c in " \t\r\n":
+                i += 1
+                continue
+            if expect == "end":
+                return "bad", stack
+            if expect in ("value", "key"):
+                if expect == "key" and c != '"':
+                    if c == "}" and stack and stack[-1] == "{0":
+                        stack.pop()
+                        expect = "comma_or_end" if stack else "end"
+                        i += 1
+                        continue
+                    return "bad", stack
+                if c == '"':
+                    j = i + 1
+                    while j < n:
+                        if s[j] == "\\":
+                            j += 2
+                            continue
+                        if s[j] == '"':
+                            break
+                        if ord(s[j]) < 0x20:
+                            return "bad", stack
+                        j += 1
+                    if j >= n:
+                        return "open", stack + ["str"]
+                    i = j + 1
+                    expect = "colon" if expect == "key" else ("comma_or_end" if stack else "end")
+                    continue
+                if c == "{":
+                    stack.append("{0")
+                    expect = "key"
+                    i += 1
+                    continue
+                if c == "[":
+                    stack.append("[0")
+                    expect = "value"
+                    i += 1
+                    continue
+                if c == "]" and stack and stack[-1] == "[0":
+                    stack.pop()
+                    expect = "comma_or_end" if stack else "end"
+                    i += 1
+                    continue
+                m = re.match(r"-?(?:0|[1-9]\d*)(?:\.\d+)?(?:[eE][+-]?\d+)?", s[i:])
+                if m and m.end() > 0:
+                    j = i + m.end()
+                    if j >= n:
+                        return "open", stack + ["num"]
+                    i = j
+                    expect = "comma_or_end" if stack else "end"
+                    continue
+                if re.match(r"-?(?:\d+\.?|\d+\.\d+[eE][+-]?)?$", s[i:]) and s[i:] not in ("",):
+                    return "open", stack + ["num"]
+                for lit in ("true", "false", "null"):
+                    if s.startswith(lit, i):
+                        i += len(lit)
+                        expect = "comma_or_end" if stack else "end"
+                        break
+                    if lit.startswith(s[i:]):
+                        return "open", stack + ["lit"]
+                else:
+                    return "bad", stack
+                continue
+            if expect == "colon":
+                if c != ":":
+                    return "bad", stack
+                expect = "value"
+                i += 1
+                continue
+            if expect == "comma_or_end":
+                top = stack[-1]
+                if c == ",":
+                    stack[-1] = top[0] + "1"
+                    expect = "key" if top[0] == "{" else "value"
+                    i += 1
+                    if expect == "key":
+                        stack[-1] = "{1"
+                    continue
+                if (c == "}" and top[0] == "{") or (c == "]" and top[0] == "["):
+                    stack.pop()
+                    expect = "comma_or_end" if stack else "end"
+                    i += 1
+                    continue
+                return "bad", stack
+        if expect == "end":
+            return "closed", stack
+        return "open", stack
+
+    def allowed(self, text: str, piece: str) -> bool:
+        state, _ = self._scan(text + piece)
+        if state == "bad":
+            return False
+        if self.schema is not None and state == "closed":
+            return self._valid((text + piece))
+        if self.schema is not None and self.schema.get("type") == "object" and (text + piece).lstrip()[:1] not in ("", "{"):
+            return False
+        if self.schema is not None and self.schema.get("type") == "array" and (text + piece).lstrip()[:1] not in ("", "["):
+            return False
+        return True
+
+    def closed(self, text: str) -> bool:
+        return self._scan(text)[0] == "closed" and text.strip()[:1] in "{["
+
+    def done(self, text: str) -> bool:
+        return self._scan(text)[0] == "closed" and (self.schema is None or self._valid(text))
+
+    def _valid(self, text: str) -> bool:
+        try:
+            return validate(json.loads(text), self.schema or {})
+        except json.JSONDecodeError:
+            return False
+
+
+def validate(v: Any, schema: dict) -> bool:
+    """The JSON-schema subset this server enforces."""
+    if "const" in schema:
+        return v == schema["const"]
+    if "enum" in schema:
+        return v in schema["enum"]
+    if "anyOf" in schema:
+        return any(validate(v, s) for s in schema["anyOf"])
+    t = schema.get("type")
+    if isinstance(t, list):
+        return any(validate(v, {**schema, "type": x}) for x in t)
+    if t == "object":
+        if not isinstance(v, dict):
+            return False
+        props = schema.get("properties", {})
+        if any(k not in v for k in schema.get("required", [])):
+            return False
+        if schema.get("additionalProperties") is False and any(k not in props for k in v):
+            return False
+        return all(validate(v[k], s) for k, s in props.items() if k in v)
+    if t == "array":
+        if not isinstance(v, list):
+            return False
+        if len(v) < schema.get("minItems", 0) or len(v) > schema.get("maxItems", 1 << 30):
+            return False
+        it = schema.get("items")
+        return all(validate(x, it) for x in v) if isinstance(it, dict) else True
+    if t == "string":
+        return isinstance(v, str)
+    if t == "integer":
+        return isinstance(v, int) and not isinstance(v, bool)
+    if t == "number":
+        return isinstance(v, (int, float)) and not isinstance(v, bool)
+    if t == "boolean":
+        return isinstance(v, bool)
+    if t == "null":
+        return v is None
+    return True

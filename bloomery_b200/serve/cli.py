@@ -1,0 +1,183 @@
+"""Process start: levers, flags, placement plan, early listener, load, ready.
+
+Order follows the reference (``crates/gpu-gates/src/bin/bloomery_serve.rs``): levers are parsed
+first and refused by name; flags resolve with their precedence; the listener binds *before*
+the model loads and answers ``loading``; ``plan`` / ``need`` / ``ctx`` / ``parallel`` lines go to
+stderr; JSON start events go to stdout; the exit code tells a supervisor what happened.
+"""
+from __future__ import annotations
+
+import json
+import os
+import signal
+import sys
+import time
+from typing import Any, Dict, List, Optional
+
+from ..utils import events, flags, levers, records
+from ..utils.exit_codes import Code, Refusal, WORDS
+
+
+def _host_free_bytes() -> int:
+    try:
+        with open("/proc/meminfo") as f:
+            for ln in f:
+                if ln.startswith("MemAvailable:"):
+                    return int(ln.split()[1]) * 1024
+    except OSError:
+        pass
+    return 8 << 30
+
+
+def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, free_bytes: List[int]) -> Dict[str, Any]:
+    """Context / slots / placement that fit (``docs/serving.md:84-87,200``): an unset context is the
+    model's trained limit, else the largest multiple of 1,024 >= 4,096 that fits; a set context is
+    never cut (refused with the largest that fits); 1,024 MiB margin per GPU."""
+    pl = flags.placement(opts, n_visible, spec.n_layer)
+    margin = int(levers.get("BLOOMERY_CARD_MARGIN"))
+    par = opts.get("parallel", "auto")
+    n_slots = 4 if par == "auto" else int(par)
+    if n_slots < 1:
+        raise Refusal(Code.USAGE, f"-np {par}: at least one slot")
+    per_tok = spec.kv_bytes_per_token() // max(1, len(pl.devices) if pl.mode == "tp" else 1)
+    asked = int(opts.get("ctx") or 0)
+    slot_ctx = int(opts.get("slot_ctx") or 0)
+    if pl.devices:
+        dev_free = min(free_bytes[d] for d in pl.devices)
+        share = weights_bytes // (len(pl.devices) if pl.mode == "tp" else 1)
+        room = dev_free - margin - share - (2 << 30)
+        if room <= 0 and pl.host_experts == "none":
+            raise Refusal(Code.NO_FIT, f"weights of {share >> 20} MiB per GPU do not fit {dev_free >> 20} MiB free "
+                                       f"(margin {margin >> 20} MiB); try --cpu-moe or more devices")
+        fit_tokens = max(0, room) // max(1, per_tok)
+    else:
+        fit_tokens = _host_free_bytes() // 2 // max(1, per_tok)
+    if asked:
+        total = asked
+        if total > fit_tokens:
+            best = fit_tokens // 1024 * 1024
+            raise Refusal(Code.NO_FIT, f"-c {asked} does not fit; the largest context that fits is {best}")
+    else:
+        total = min(spec.ctx_train * n_slots, fit_tokens // 1024 * 1024)
+        if total < 4096:
+            raise Refusal(Code.NO_FIT, "not even a context of 4,096 fits beside the weights")
+    if not slot_ctx:
+        slot_ctx = min(spec.ctx_train, total // n_slots if par != "auto" else max(4096, min(spec.ctx_train, total // n_slots)))
+    slot_ctx = slot_ctx // 64 * 64
+    return {"placement": pl, "n_slots": n_slots, "slot_ctx": slot_ctx, "ctx_total": slot_ctx * n_slots,
+            "kv_bytes": slot_ctx * n_slots * per_tok, "weights_bytes": weights_bytes}
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    events.enable()
+    try:
+        levers.at_main()
+        opts = flags.parse(argv)
+        if opts["version"]:
+            from .. import __version__
+            print(f"bloomery_b200 {__version__}")
+            return 0
+        if opts["levers"]:
+            print(levers.listing())
+            return 0
+        if opts["records_schema"]:
+            print(records.schema())
+            return 0
+        import torch
+        n_vis = torch.cuda.device_count() if torch.cuda.is_available() else 0
+        if opts["list_devices"]:
+            devs = [{"id": f"CUDA{i}", "name": torch.cuda.get_device_name(i),
+                     "free_mib": torch.cuda.mem_get_info(i)[0] >> 20, "total_mib": torch.cuda.mem_get_info(i)[1] >> 20}
+                    for i in range(n_vis)]
+            print(json.dumps(devs) if opts["json"] else "\n".join(f"{d['id']}: {d['name']} ({d['free_mib']} / {d['total_mib']} MiB free)" for d in devs) or "no CUDA device")
+            return 0
+        from .api import Server
+        server = Server(opts)
+        server.start()
+        signal.signal(signal.SIGINT, lambda *_: (setattr(server.state, "stop_cause", "signal"), server.state.stop_event.set()))
+        signal.signal(signal.SIGTERM, lambda *_: (setattr(server.state, "stop_cause", "signal"), server.state.stop_event.set()))
+        from .engine import GpuEngine, MockEngine
+        from .chat import ChatTemplate
+        template_src = None
+        if opts.get("chat_template_file"):
+            with open(opts["chat_template_file"]) as fh:
+                template_src = fh.read()
+        elif opts.get("chat_template"):
+            template_src = opts["chat_template"]
+        cache_mib = int(opts.get("cache_ram", -1))
+        cache_bytes = min(8 << 30, _host_free_bytes() // 2) if cache_mib < 0 else cache_mib << 20
+        if opts["mock"]:
+            eng = MockEngine(n_slots=4 if opts["parallel"] == "auto" else int(opts["parallel"]),
+                             slot_ctx=int(opts.get("ctx") or 4096), fail_at=int(opts.get("mock_fail_at", -1)))
+            opts["_place_word"] = "mock"
+            server.ready(eng, ChatTemplate(template_src), cache_bytes, int(opts["queue_depth"]))
+            return server.wait()
+        if not opts.get("model"):
+            raise Refusal(Code.NO_MODEL, "no model was named; use -m FILE (a GGUF file, any shard of a split) or --mock")
+        if not os.path.exists(opts["model"]):
+            raise Refusal(Code.NO_MODEL, f"{opts['model']}: no such file")
+        server.state.phase = "plan"
+        from ..formats.gguf import Gguf, GgufError
+        from ..models.spec import ModelSpec
+        try:
+            inv = Gguf.inventory(opts["model"])
+            spec = ModelSpec.from_gguf(inv)
+        except GgufError as exc:
+            raise Refusal(Code.LOAD, str(exc)) from None
+        except ValueError as exc:
+            raise Refusal(Code.UNSUPPORTED, str(exc)) from None
+        weights_bytes = sum(t.n_bytes for t in inv.tensors.values())
+        free = [torch.cuda.mem_get_info(i)[0] for i in range(n_vis)]
+        plan = plan_for(opts, spec, weights_bytes, n_vis, free)
+        pl = plan["placement"]
+        opts["_place_word"] = pl.word()
+        records.write("plan", model=spec.name, devices=[f"CUDA{d}" for d in pl.devices], weights_bytes=weights_bytes,
+                      kv_bytes=plan["kv_bytes"], ctx=plan["ctx_total"], slots=plan["n_slots"], place=pl.word())
+        records.write("need", weights_bytes=weights_bytes, kv_bytes_per_token=spec.kv_bytes_per_token(), host_bytes=0, fits=True)
+        records.write("ctx", asked=int(opts.get("ctx") or 0), served=plan["slot_ctx"], trained=spec.ctx_train)
+        records.write("parallel", slots=plan["n_slots"], slot_ctx=plan["slot_ctx"])
+        if opts["plan"] or opts["dry_run"]:
+            out = {"place": pl.word(), "devices": pl.devices, "slots": plan["n_slots"], "slot_ctx": plan["slot_ctx"],
+                   "weights_bytes": weights_bytes, "kv_bytes": plan["kv_bytes"]}
+            print(json.dumps(out) if opts["json"] else "\n".join(f"{k}: {v}" for k, v in out.items()))
+            server.state.stop_cause = "plan"
+            server.state.stop_event.set()
+            return server.stop()
+        if not pl.devices:
+            raise Refusal(Code.NO_DEVICE, "no CUDA device is visible; the CPU-only engine is started with -dev none on a model that fits host RAM"
+                          if n_vis == 0 and str(opts.get("dev") or "").lower() != "none" else "CPU-only serving goes through CpuEngine")
+        server.state.phase = "load"
+        t0 = time.time()
+        from ..models.weights import load_gguf
+        from ..runtime.engine import DecodeEngine
+        from .tokenizer import from_gguf
+        from ..ops import decode as K
+        K.set_pdl(bool(levers.get("BLOOMERY_PDL")))
+        dev = f"cuda:{pl.devices[0]}"
+        torch.cuda.set_device(pl.devices[0])
+        spec, w, g = load_gguf(opts["model"], dev)
+        records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
+        dec = DecodeEngine(w, n_slots=plan["n_slots"], slot_ctx=plan["slot_ctx"], use_graphs=bool(levers.get("BLOOMERY_GRAPHS")),
+                           engine_bound_s=float(levers.get("BLOOMERY_ENGINE_BOUND")))
+        dec.ubatch = int(opts.get("ubatch") or 4096)
+        if opts.get("prefill") == "steps":
+            dec.gemm_threshold = 0
+        tk = from_gguf(g, spec.vocab)
+        if template_src is None:
+            template_src = g.get("tokenizer.chat_template")
+        bos = tk.decode([tk.bos_id], skip_special=False) if tk.bos_id >= 0 else ""
+        eos = tk.decode([tk.eos_id], skip_special=False) if tk.eos_id >= 0 else ""
+        eng = GpuEngine(dec, tk, opts.get("alias") or spec.name or os.path.basename(opts["model"]))
+        if not opts.get("no_warmup"):
+            t1 = time.time()
+            dec.step([(0, max(0, tk.bos_id), 0)])
+            dec.reset(0)
+            records.write("setup", phase="warmup", seconds=round(time.time() - t1, 3))
+        server.ready(eng, ChatTemplate(template_src, bos, eos), cache_bytes, int(opts["queue_depth"]))
+        return server.wait()
+    except Refusal as r:
+        word, nxt = WORDS.get(r.code, ("refused", ""))
+        events.emit("error", code=int(r.code), word=word, message=str(r), next=nxt)
+        print(f"error: {r}", file=sys.stderr)
+        return int(r.code)

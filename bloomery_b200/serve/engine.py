@@ -1,0 +1,209 @@
+"""The engine surface the server drives, its GPU implementation and a mock.
+
+``Engine`` mirrors the reference's trait (``crates/serve/src/engine.rs:255-706``): prompt rows
+in, one row of logits (or a greedy pick) out per active slot, plus the slot operations the
+scheduler needs -- ``cut`` (keep a prefix), ``reset``, ``share_prefix`` (map another slot's KV
+pages copy-on-write), ``snapshot`` / ``restore`` (host prompt cache, slot files).
+``MockEngine`` is the byte-vocabulary engine of the serve tests (``crates/serve/src/mock.rs``):
+it echoes the prompt back, so every HTTP contract is testable without a model or a card.
+"""
+from __future__ import annotations
+
+import dataclasses
+import threading
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from .tokenizer import ByteTokenizer, Tokenizer
+
+
+@dataclasses.dataclass
+class Saved:
+    """A sequence state kept on the host: the ids it covers and the engine's bytes for them."""
+
+    ids: Tuple[int, ...]
+    payload: object
+    n_bytes: int
+
+
+class EngineError(RuntimeError):
+    """The engine cannot continue; the server answers 500, /health turns 503, exit code 70."""
+
+
+class Engine:
+    tokenizer: Tokenizer
+    model_name = "model"
+    n_slots = 1
+    slot_ctx = 4096
+    n_vocab = 0
+    max_rows = 8
+
+    def prefill(self, slot: int, ids: Sequence[int], start: int) -> None: ...
+    def step(self, rows: Sequence[Tuple[int, int, int]], want_logits: bool = True) -> List[Tuple[int, Optional[np.ndarray]]]:
+        """rows = (slot, token, position).  Returns per row (greedy id, logits row or None)."""
+        raise NotImplementedError
+    def cut(self, slot: int, n: int) -> None: ...
+    def reset(self, slot: int) -> None: ...
+    def share_prefix(self, src: int, dst: int, n: int) -> int:
+        return 0
+    def snapshot(self, slot: int, ids: Sequence[int]) -> Optional[Saved]:
+        return None
+    def restore(self, slot: int, saved: Saved, n: int) -> int:
+        return 0
+    def props(self) -> Dict[str, object]:
+        return {}
+    def embed(self, ids: Sequence[int]) -> Optional[np.ndarray]:
+        return None
+    def close(self) -> None: ...
+
+
+class MockEngine(Engine):
+    """Echo engine over the byte tokenizer: after a prompt it generates the prompt's own bytes
+    again (a bigram table of the prompt), then EOS.  ``fail_at`` makes the k-th step raise."""
+
+    def __init__(self, n_slots: int = 4, slot_ctx: int = 2048, fail_at: int = -1, step_delay: float = 0.0):
+        self.step_delay = step_delay
+        self.tokenizer = ByteTokenizer()
+        self.n_slots, self.slot_ctx, self.n_vocab = n_slots, slot_ctx, self.tokenizer.n_vocab
+        self.model_name = "mock-echo"
+        self.seq: List[List[int]] = [[] for _ in range(n_slots)]
+        self.prompt_len = [0] * n_slots
+        self.steps = 0
+        self.fail_at = fail_at
+        self.prefill_calls: List[Tuple[int, int, int]] = []
+        self.fresh = [True] * n_slots          # the next step of the slot carries the prompt's last token
+
+    def _logits(self, slot: int) -> np.ndarray:
+        seq = self.seq[slot]
+        row = np.full(self.n_vocab, -10.0, dtype=np.float32)
+        n_prompt = self.prompt_len[slot]
+        k = len(seq) - n_prompt
+        nxt = seq[k] if k < n_prompt else self.tokenizer.eos_id
+        if nxt >= 256 and k < n_prompt:
+            nxt = self.tokenizer.eos_id
+        row[nxt] = 10.0
+        row[(nxt + 1) % 256] = 8.0           # a runner-up so samplers have something to choose from
+        return row
+
+    def prefill(self, slot, ids, start):
+        self.prefill_calls.append((slot, start, len(ids)))
+        del self.seq[slot][start:]
+        self.seq[slot] += list(ids)
+        self.prompt_len[slot] = len(self.seq[slot])
+        self.fresh[slot] = True
+
+    def step(self, rows, want_logits=True):
+        self.steps += 1
+        if self.step_delay:
+            import time
+            time.sleep(self.step_delay)
+        if self.fail_at >= 0 and self.steps >= self.fail_at:
+            raise EngineError("mock engine failure (--mock-fail-at)")
+        out = []
+        for slot, tok, pos in rows:
+            del self.seq[slot][pos:]
+            self.seq[slot].append(tok)
+            if self.fresh[slot]:
+                self.prompt_len[slot] = pos + 1      # the first step after a prompt carries its last token
+                self.fresh[slot] = False
+            lg = self._logits(slot)
+            out.append((int(lg.argmax()), lg if want_logits else None))
+        return out
+
+    def cut(self, slot, n):
+        del self.seq[slot][n:]
+        self.prompt_len[slot] = min(self.prompt_len[slot], n)
+        self.fresh[slot] = True
+
+    def reset(self, slot):
+        self.seq[slot] = []
+        self.prompt_len[slot] = 0
+        self.fresh[slot] = True
+
+    def share_prefix(self, src, dst, n):
+        n = min(n, len(self.seq[src]))
+        self.seq[dst] = self.seq[src][:n]
+        self.prompt_len[dst] = n
+        self.fresh[dst] = True
+        return n
+
+    def snapshot(self, slot, ids):
+        return Saved(tuple(ids), list(self.seq[slot][:len(ids)]), 8 * len(ids))
+
+    def restore(self, slot, saved, n):
+        n = min(n, len(saved.ids))
+        self.seq[slot] = list(saved.payload[:n])
+        self.prompt_len[slot] = n
+        self.fresh[slot] = True
+        return n
+
+    def props(self):
+        return {"engine": "mock", "devices": []}
+
+
+class GpuEngine(Engine):
+    """``Engine`` over :class:`bloomery_b200.runtime.engine.DecodeEngine`."""
+
+    def __init__(self, dec, tokenizer: Tokenizer, model_name: str = "model"):
+        self.dec = dec
+        self.tokenizer = tokenizer
+        self.model_name = model_name
+        self.n_slots, self.slot_ctx, self.n_vocab = dec.n_slots, dec.slot_ctx, dec.spec.vocab
+        self._lock = threading.Lock()
+        self._last_logits: Dict[int, np.ndarray] = {}
+
+    def prefill(self, slot, ids, start):
+        from ..runtime.engine import EngineFault, EngineStalled
+        try:
+            if len(ids):
+                self.dec.prefill(slot, list(ids), start)
+        except (EngineFault, EngineStalled) as exc:
+            raise EngineError(str(exc)) from exc
+
+    def step(self, rows, want_logits=True):
+        from ..runtime.engine import EngineFault, EngineStalled
+        out = []
+        try:
+            for i in range(0, len(rows), self.max_rows):
+                chunk = list(rows[i:i + self.max_rows])
+                picks = self.dec.step(chunk)
+                lg = self.dec.logits[:len(chunk)].float().cpu().numpy() if want_logits else None
+                for j, pk in enumerate(picks):
+                    out.append((int(pk), lg[j] if lg is not None else None))
+        except (EngineFault, EngineStalled) as exc:
+            raise EngineError(str(exc)) from exc
+        return out
+
+    def cut(self, slot, n):
+        self.dec.cut(slot, n)
+
+    def reset(self, slot):
+        self.dec.reset(slot)
+
+    def share_prefix(self, src, dst, n):
+        got = self.dec.kv.share_prefix(src, dst, n)
+        self.dec.slot_len[dst] = got
+        self.dec.kv.sync_table()
+        return got
+
+    def snapshot(self, slot, ids):
+        n = len(ids)
+        if n == 0:
+            return None
+        snap = self.dec.kv.snapshot(slot, n)
+        nb = snap["k"].numel() * snap["k"].element_size() * 2
+        return Saved(tuple(ids), snap, nb)
+
+    def restore(self, slot, saved, n):
+        n = min(n, len(saved.ids))
+        self.dec.kv.restore(slot, saved.payload, n)
+        self.dec.kv.sync_table()
+        self.dec.slot_len[slot] = n
+        return n
+
+    def props(self):
+        s = self.dec.spec
+        return {"engine": "cuda", "arch": s.arch, "n_layer": s.n_layer, "n_expert": s.n_expert,
+                "memory": self.dec.memory_report(), "devices": [str(self.dec.device)],
+                "launches_per_step": self.dec.launches_per_step}

@@ -1,0 +1,371 @@
+"""Engine thread and generation loop.
+
+One thread owns the engine (``worker.rs:521,723`` in the reference).  Each round it
+(1) admits queued requests into free slots (prompt-cache lookup, prefix reuse by ``cut``,
+``share_prefix`` or ``restore``), (2) feeds one planned prompt chunk per starting request
+(cut on the prompt quantum while other slots decode, ``worker.rs:45-51``), and (3) runs **one
+decode round for all busy slots** as rows of one engine pass (``worker.rs:1047-1210``).
+Per request the loop samples (``sampler.py``), applies stop rules, the reasoning split and
+constraints, and pushes events to the HTTP thread (``genloop.rs``).
+"""
+from __future__ import annotations
+
+import dataclasses
+import itertools
+import math
+import queue
+import threading
+import time
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from .engine import Engine, EngineError
+from .promptcache import PromptCache, common_prefix
+from .sampler import Sampler, SamplingParams
+from .sched import Board, QueueFull, Slot
+from .tokenizer import StreamDecoder
+
+_ids = itertools.count(1)
+
+
+@dataclasses.dataclass
+class Request:
+    prompt_ids: List[int]
+    sampling: SamplingParams = dataclasses.field(default_factory=SamplingParams)
+    n_predict: int = -1
+    stop: List[str] = dataclasses.field(default_factory=list)
+    stream: bool = False
+    cache_prompt: bool = True
+    n_probs: int = 0
+    ignore_eos: bool = False
+    id_slot: Optional[int] = None
+    constraint: Any = None                  # object with allowed(text_so_far, piece) -> bool and done(text) -> bool
+    logit_bias: Dict[int, float] = dataclasses.field(default_factory=dict)
+    t_max_predict_ms: float = 0.0
+    id: int = dataclasses.field(default_factory=lambda: next(_ids))
+    events: "queue.Queue" = dataclasses.field(default_factory=queue.Queue)
+    cancelled: threading.Event = dataclasses.field(default_factory=threading.Event)
+    created: float = dataclasses.field(default_factory=time.time)
+
+
+@dataclasses.dataclass
+class Active:
+    req: Request
+    slot: Slot
+    sampler: Sampler
+    decoder: StreamDecoder
+    n_past: int = 0                 # positions of the prompt already in the slot
+    n_cached: int = 0
+    generated: List[int] = dataclasses.field(default_factory=list)
+    text: str = ""
+    sent: int = 0                   # characters of `text` already streamed
+    pending_token: Optional[int] = None
+    t_prompt0: float = 0.0
+    t_prompt1: float = 0.0
+    t_first: float = 0.0
+    probs: List[dict] = dataclasses.field(default_factory=list)
+    stop_type: str = ""
+    stop_word: str = ""
+    cache_ms: float = 0.0
+    draft_n: int = 0
+    draft_accepted: int = 0
+
+
+class Metrics:
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.c: Dict[str, float] = collections_default()
+
+    def add(self, name: str, v: float = 1.0):
+        with self.lock:
+            self.c[name] = self.c.get(name, 0.0) + v
+
+    def get(self, name: str) -> float:
+        return self.c.get(name, 0.0)
+
+
+def collections_default() -> Dict[str, float]:
+    return {"prompt_tokens_total": 0.0, "prompt_seconds_total": 0.0, "tokens_predicted_total": 0.0,
+            "tokens_predicted_seconds_total": 0.0, "n_decode_total": 0.0, "n_busy_slots_per_decode": 0.0,
+            "requests_total": 0.0, "requests_failed_total": 0.0, "round_seconds_total": 0.0,
+            "prompt_cache_hits_total": 0.0, "prompt_cache_tokens_total": 0.0, "draft_tokens_total": 0.0,
+            "draft_accepted_total": 0.0}
+
+
+class Worker(threading.Thread):
+    def __init__(self, engine: Engine, board: Board, cache: PromptCache, prompt_quantum: int = 2048,
+                 on_fatal: Optional[Callable[[BaseException], None]] = None):
+        super().__init__(name="serve-engine", daemon=True)
+        self.engine, self.board, self.cache = engine, board, cache
+        self.prompt_quantum = prompt_quantum
+        self.active: Dict[int, Active] = {}
+        self.stop_flag = threading.Event()
+        self.metrics = Metrics()
+        self.rounds_by_width: Dict[int, int] = {}
+        self.on_fatal = on_fatal
+        self.failed: Optional[BaseException] = None
+        self.actions: "queue.Queue" = queue.Queue()     # slot actions run on the engine thread
+
+    # ---------------------------------------------------------------- admission
+    def _admit(self) -> None:
+        while True:
+            got = self.board.next_request()
+            if got is None:
+                return
+            req, slot, shared = got
+            if req.cancelled.is_set():
+                self.board.release(slot)
+                continue
+            ids = req.prompt_ids
+            if len(ids) >= self.engine.slot_ctx:
+                req.events.put(("error", 400, f"the prompt of {len(ids)} tokens exceeds the slot context of {self.engine.slot_ctx}"))
+                self.board.release(slot)
+                continue
+            a = Active(req, slot, Sampler(req.sampling), StreamDecoder(self.engine.tokenizer))
+            a.t_prompt0 = time.time()
+            keep = shared if req.cache_prompt else 0
+            # a longer match in another slot (shared KV pages) or in the host cache beats the slot's own prefix
+            if req.cache_prompt:
+                donor, dn = None, keep
+                for other in self.board.slots:
+                    if other is not slot:
+                        n = common_prefix(other.ids, ids)
+                        if n > dn:
+                            donor, dn = other, n
+                if donor is not None:
+                    got_n = self.engine.share_prefix(donor.id, slot.id, dn)
+                    if got_n > keep:
+                        slot.ids = list(donor.ids[:got_n])
+                        keep = got_n
+                t0 = time.time()
+                saved, sn = self.cache.lookup(ids, at_least=keep + 1)
+                if saved is not None and sn > keep:
+                    got_n = self.engine.restore(slot.id, saved, sn)
+                    if got_n > keep:
+                        slot.ids = list(saved.ids[:got_n])
+                        keep = got_n
+                        self.metrics.add("prompt_cache_hits_total")
+                a.cache_ms = (time.time() - t0) * 1e3
+                self.cache.seconds += time.time() - t0
+            keep = min(keep, len(ids) - 1)         # at least one prompt token is always evaluated
+            keep = max(keep, 0)
+            self.engine.cut(slot.id, keep)
+            slot.ids = list(ids[:keep])
+            a.n_past = a.n_cached = keep
+            self.metrics.add("prompt_cache_tokens_total", keep)
+            self.active[slot.id] = a
+
+    # ---------------------------------------------------------------- prompt
+    def _feed_prompt(self, a: Active) -> None:
+        ids = a.req.prompt_ids
+        todo = len(ids) - 1 - a.n_past          # the last prompt token goes through the decode round
+        if todo <= 0:
+            a.pending_token = ids[-1]
+            a.t_prompt1 = time.time()
+            return
+        others_decoding = any(o.pending_token is not None for o in self.active.values() if o is not a)
+        n = min(todo, self.prompt_quantum) if others_decoding else todo
+        self.engine.prefill(a.slot.id, ids[a.n_past:a.n_past + n], a.n_past)
+        a.slot.ids += ids[a.n_past:a.n_past + n]
+        a.n_past += n
+        if a.n_past >= len(ids) - 1:
+            a.pending_token = ids[-1]
+            a.t_prompt1 = time.time()
+
+    # ---------------------------------------------------------------- decode
+    def _finish(self, a: Active, stop_type: str, word: str = "") -> None:
+        a.stop_type, a.stop_word = stop_type, word
+        tail = a.decoder.flush()
+        if tail and stop_type != "word":
+            a.text += tail
+        self._flush_text(a, final=True)
+        now = time.time()
+        n_prompt = len(a.req.prompt_ids)
+        prompt_ms = max(0.0, (a.t_prompt1 - a.t_prompt0) * 1e3)
+        pred_ms = max(0.0, (now - (a.t_first or now)) * 1e3)
+        timings = {"cache_n": a.n_cached, "prompt_n": n_prompt - a.n_cached, "prompt_ms": prompt_ms,
+                   "prompt_per_second": (n_prompt - a.n_cached) / max(prompt_ms / 1e3, 1e-9),
+                   "predicted_n": len(a.generated), "predicted_ms": pred_ms,
+                   "predicted_per_second": len(a.generated) / max(pred_ms / 1e3, 1e-9), "cache_ms": a.cache_ms,
+                   "draft_n": a.draft_n, "draft_n_accepted": a.draft_accepted}
+        a.req.events.put(("done", {"stop_type": stop_type, "stopping_word": word, "tokens_predicted": len(a.generated),
+                                   "tokens_evaluated": n_prompt, "tokens_cached": a.n_cached, "timings": timings,
+                                   "text": a.text, "tokens": list(a.generated), "probs": a.probs,
+                                   "truncated": False, "id_slot": a.slot.id}))
+        m = self.metrics
+        m.add("requests_total"); m.add("prompt_tokens_total", n_prompt - a.n_cached); m.add("prompt_seconds_total", prompt_ms / 1e3)
+        m.add("tokens_predicted_total", len(a.generated)); m.add("tokens_predicted_seconds_total", pred_ms / 1e3)
+        if a.req.cache_prompt and a.slot.ids:
+            t0 = time.time()
+            self.cache.put(self.engine.snapshot(a.slot.id, a.slot.ids))
+            self.cache.seconds += time.time() - t0
+        del self.active[a.slot.id]
+        self.board.release(a.slot)
+
+    def _flush_text(self, a: Active, final: bool = False) -> None:
+        if not a.req.stream:
+            return
+        # hold back a tail that could still grow into a stop string
+        hold = 0
+        if not final:
+            for s in a.req.stop:
+                for k in range(min(len(s) - 1, len(a.text) - a.sent), 0, -1):
+                    if a.text.endswith(s[:k]):
+                        hold = max(hold, k)
+                        break
+        upto = len(a.text) - hold
+        if upto > a.sent:
+            a.req.events.put(("text", a.text[a.sent:upto]))
+            a.sent = upto
+
+    def _pick(self, a: Active, greedy: int, logits: Optional[np.ndarray]) -> int:
+        req = a.req
+        if logits is None:
+            return greedy
+        row = logits
+        if req.logit_bias or (req.ignore_eos and self.engine.tokenizer.eos_id >= 0):
+            row = row.copy()
+            for t, b in req.logit_bias.items():
+                if 0 <= t < row.size:
+                    row[t] = -np.inf if b is False or b == float("-inf") else row[t] + b
+            if req.ignore_eos:
+                for t in (self.engine.tokenizer.eos_id, self.engine.tokenizer.eot_id):
+                    if t >= 0:
+                        row[t] = -np.inf
+        recent = a.slot.ids[-max(req.sampling.repeat_last_n, 0):] if req.sampling.repeat_last_n else []
+        if req.constraint is not None:
+            tok = self._constrained_pick(a, row, recent)
+        else:
+            tok = a.sampler.sample(row, recent)
+        if req.n_probs > 0:
+            top = np.argpartition(-row, min(req.n_probs, row.size - 1))[:req.n_probs]
+            top = top[np.argsort(-row[top], kind="stable")]
+            mx = float(np.max(row))
+            lse = mx + math.log(float(np.exp((row - mx).astype(np.float64)).sum()))
+            tk = self.engine.tokenizer
+            a.probs.append({"id": int(tok), "token": tk.decode([int(tok)], skip_special=False), "logprob": float(row[tok]) - lse,
+                            "top_logprobs": [{"id": int(t), "token": tk.decode([int(t)], skip_special=False),
+                                              "logprob": float(row[t]) - lse} for t in top]})
+        return tok
+
+    def _constrained_pick(self, a: Active, row: np.ndarray, recent) -> int:
+        """Masked pick: best-first over candidates until one keeps the output a valid prefix."""
+        tk = self.engine.tokenizer
+        order = np.argsort(-row, kind="stable")[:256]
+        for t in order:
+            t = int(t)
+            if tk.is_eog(t):
+                if a.req.constraint.done(a.text):
+                    return t
+                continue
+            piece = tk.decode([t], skip_special=True)
+            if piece and a.req.constraint.allowed(a.text, piece):
+                return t
+        return int(order[0])
+
+    def _decode_round(self) -> None:
+        rows, who = [], []
+        for a in self.active.values():
+            if a.pending_token is not None:
+                rows.append((a.slot.id, a.pending_token, len(a.slot.ids)))
+                who.append(a)
+        if not rows:
+            return
+        need_logits = any(w.req.sampling.temperature > 0 or w.req.sampling.penalizes or w.req.n_probs > 0
+                          or w.req.constraint is not None or w.req.logit_bias or w.req.ignore_eos for w in who)
+        t0 = time.time()
+        res = self.engine.step(rows, want_logits=need_logits)
+        dt = time.time() - t0
+        self.metrics.add("round_seconds_total", dt)
+        self.metrics.add("n_decode_total")
+        self.metrics.add("n_busy_slots_per_decode", len(rows))
+        self.rounds_by_width[len(rows)] = self.rounds_by_width.get(len(rows), 0) + 1
+        tk = self.engine.tokenizer
+        for a, (slot_id, tok_in, pos), (greedy, logits) in zip(who, rows, res):
+            a.slot.ids.append(tok_in)
+            tok = self._pick(a, greedy, logits)
+            now = time.time()
+            if not a.t_first:
+                a.t_first = now
+            req = a.req
+            if req.cancelled.is_set():
+                self._finish(a, "cancelled")
+                continue
+            if tk.is_eog(tok) and not req.ignore_eos:
+                self._finish(a, "eos")
+                continue
+            a.generated.append(tok)
+            a.slot.n_decoded = len(a.generated)
+            a.text += a.decoder.push(tok)
+            hit = None
+            for s in req.stop:
+                i = a.text.find(s, max(0, a.sent - len(s)))
+                if i >= 0 and (hit is None or i < hit[0]):
+                    hit = (i, s)
+            if hit is not None:
+                a.text = a.text[:hit[0]]
+                self._finish(a, "word", hit[1])
+                continue
+            self._flush_text(a)
+            if req.constraint is not None and req.constraint.done(a.text) and req.constraint.closed(a.text):
+                self._finish(a, "eos")
+                continue
+            if 0 <= req.n_predict <= len(a.generated):
+                self._finish(a, "limit")
+                continue
+            if len(a.slot.ids) + 1 >= self.engine.slot_ctx:
+                self._finish(a, "limit")
+                continue
+            if req.t_max_predict_ms and (now - a.t_first) * 1e3 > req.t_max_predict_ms:
+                self._finish(a, "limit")
+                continue
+            a.pending_token = tok
+
+    # ---------------------------------------------------------------- loop
+    def run(self) -> None:
+        try:
+            while not self.stop_flag.is_set():
+                while True:
+                    try:
+                        fn, done = self.actions.get_nowait()
+                    except queue.Empty:
+                        break
+                    try:
+                        done.put(("ok", fn()))
+                    except Exception as exc:       # noqa: BLE001 - reported to the caller of the action
+                        done.put(("error", exc))
+                self._admit()
+                for a in list(self.active.values()):
+                    if a.pending_token is None:
+                        self._feed_prompt(a)
+                self._decode_round()
+                if not self.active:
+                    with self.board.wake:
+                        if not self.board.queue and self.actions.empty() and not self.stop_flag.is_set():
+                            self.board.wake.wait(timeout=0.05)
+        except BaseException as exc:               # noqa: BLE001 - engine failure is fatal by contract
+            self.failed = exc
+            for a in list(self.active.values()):
+                a.req.events.put(("error", 500, f"engine failure: {exc}"))
+            self.metrics.add("requests_failed_total", len(self.active))
+            while self.board.queue:
+                self.board.queue.popleft().events.put(("error", 500, f"engine failure: {exc}"))
+            if self.on_fatal:
+                self.on_fatal(exc)
+
+    def run_on_engine_thread(self, fn: Callable[[], Any], timeout: float = 60.0):
+        """Run a slot action (save / restore / erase) between rounds, on the engine thread."""
+        done: "queue.Queue" = queue.Queue()
+        self.actions.put((fn, done))
+        with self.board.wake:
+            self.board.wake.notify_all()
+        kind, val = done.get(timeout=timeout)
+        if kind == "error":
+            raise val
+        return val
+
+    def shutdown(self) -> None:
+        self.stop_flag.set()
+        with self.board.wake:
+            self.board.wake.notify_all()

@@ -1,0 +1,254 @@
+"""llama-server flag spellings, their ``LLAMA_ARG_*`` twins, ``--config`` files, and the
+translation of the placement flags (``-dev``, ``-ts``, ``-ngl``, ``--cpu-moe``, ``-ncmoe``,
+``-ot``, ``-fit``/``-fitt``/``-fitc``, ``--place``) into one placement request.
+
+Counterpart of ``crates/gpu-gates/src/llama_place.rs:1-55`` and ``crates/serve/src/flag.rs``:
+precedence is command line > config file > ``LLAMA_ARG_*`` > default
+(``docs/serving.md:370-381``); an unknown *flag* is refused by name (exit 64) whereas an
+unknown *request field* is ignored; ``-sm row`` / ``-sm tensor`` and partial ``-ngl`` are
+refused by name.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+import re
+from typing import Any, Dict, List, Optional, Tuple
+
+from .exit_codes import Code, Refusal
+
+
+@dataclasses.dataclass
+class Flag:
+    names: Tuple[str, ...]
+    dest: str
+    kind: str = "str"            # str | int | float | bool | count
+    default: Any = None
+    env: Optional[str] = None
+    help: str = ""
+
+
+FLAGS: List[Flag] = [
+    Flag(("-m", "--model-file", "--model"), "model", env="LLAMA_ARG_MODEL", help="GGUF file (any shard) or checkpoint folder, or a seat name"),
+    Flag(("--hf", "-hf", "--hf-repo"), "hf", env="LLAMA_ARG_HF_REPO", help="<repo>[@rev][:quant] (needs network)"),
+    Flag(("--host",), "host", default="127.0.0.1", env="LLAMA_ARG_HOST"),
+    Flag(("--port",), "port", "int", 8080, env="LLAMA_ARG_PORT", help="0 = any free port"),
+    Flag(("-c", "--ctx-size"), "ctx", "int", 0, env="LLAMA_ARG_CTX_SIZE", help="0 = the model's trained limit or what fits"),
+    Flag(("-np", "--parallel"), "parallel", "str", "auto", env="LLAMA_ARG_N_PARALLEL", help="slots: N or auto"),
+    Flag(("--slot-ctx",), "slot_ctx", "int", 0),
+    Flag(("--queue-depth",), "queue_depth", "int", 64),
+    Flag(("-ub", "--ubatch-size"), "ubatch", "int", 4096, env="LLAMA_ARG_UBATCH"),
+    Flag(("-b", "--batch-size"), "batch", "int", 4096, env="LLAMA_ARG_BATCH"),
+    Flag(("-cram", "--cache-ram"), "cache_ram", "int", -1, env="LLAMA_ARG_CACHE_RAM", help="MiB of host prompt cache; -1 = min(8 GiB, half free)"),
+    Flag(("--cache-type-k", "-ctk"), "cache_type_k", default="f16", env="LLAMA_ARG_CACHE_TYPE_K"),
+    Flag(("--cache-type-v", "-ctv"), "cache_type_v", default="f16", env="LLAMA_ARG_CACHE_TYPE_V"),
+    Flag(("--chat-template-file",), "chat_template_file", env="LLAMA_ARG_CHAT_TEMPLATE_FILE"),
+    Flag(("--chat-template",), "chat_template", env="LLAMA_ARG_CHAT_TEMPLATE"),
+    Flag(("--jinja",), "jinja", "bool", True),
+    Flag(("-a", "--alias"), "alias", env="LLAMA_ARG_ALIAS"),
+    Flag(("--api-key",), "api_key", env="LLAMA_API_KEY"),
+    Flag(("--api-key-file",), "api_key_file"),
+    Flag(("--slot-save-path",), "slot_save_path"),
+    Flag(("--config",), "config"),
+    Flag(("--plan",), "plan", "bool", False), Flag(("--levers",), "levers", "bool", False),
+    Flag(("--list-devices",), "list_devices", "bool", False), Flag(("--recommend",), "recommend", "bool", False),
+    Flag(("--dry-run",), "dry_run", "bool", False), Flag(("--json",), "json", "bool", False),
+    Flag(("--version",), "version", "bool", False), Flag(("--records-schema",), "records_schema", "bool", False),
+    Flag(("--autotune",), "autotune", default="on"), Flag(("--prefill",), "prefill", default="batch"),
+    Flag(("--mmproj",), "mmproj"), Flag(("--no-mmproj",), "no_mmproj", "bool", False),
+    Flag(("-n", "--n-predict", "--predict"), "n_predict", "int", -1, env="LLAMA_ARG_N_PREDICT"),
+    Flag(("--temp",), "temp", "float", 0.8), Flag(("--top-k",), "top_k", "int", 40), Flag(("--top-p",), "top_p", "float", 0.95),
+    Flag(("--min-p",), "min_p", "float", 0.05), Flag(("--repeat-penalty",), "repeat_penalty", "float", 1.0),
+    Flag(("--repeat-last-n",), "repeat_last_n", "int", 64), Flag(("-s", "--seed"), "seed", "int", -1),
+    Flag(("--no-warmup",), "no_warmup", "bool", False), Flag(("--metrics",), "metrics", "bool", True),
+    Flag(("--slots",), "slots_endpoint", "bool", True), Flag(("--props",), "props_endpoint", "bool", True),
+    Flag(("-t", "--threads"), "threads", "int", 0, env="LLAMA_ARG_THREADS"),
+    Flag(("--draft", "--draft-max"), "draft_max", "int", 0), Flag(("--mock",), "mock", "bool", False),
+    Flag(("--mock-fail-at",), "mock_fail_at", "int", -1),
+    # placement
+    Flag(("-dev", "--device"), "dev", env="LLAMA_ARG_DEVICE", help="comma list: CUDA0,CUDA1,... or none"),
+    Flag(("-sm", "--split-mode"), "split_mode", default="layer", env="LLAMA_ARG_SPLIT_MODE"),
+    Flag(("-mg", "--main-gpu"), "main_gpu", "int", 0, env="LLAMA_ARG_MAIN_GPU"),
+    Flag(("-ts", "--tensor-split"), "tensor_split", env="LLAMA_ARG_TENSOR_SPLIT"),
+    Flag(("-ngl", "--gpu-layers", "--n-gpu-layers"), "ngl", "str", "all", env="LLAMA_ARG_N_GPU_LAYERS"),
+    Flag(("-cmoe", "--cpu-moe"), "cpu_moe", "bool", False, env="LLAMA_ARG_CPU_MOE"),
+    Flag(("-ncmoe", "--n-cpu-moe"), "n_cpu_moe", "int", 0, env="LLAMA_ARG_N_CPU_MOE"),
+    Flag(("-ot", "--override-tensor"), "override_tensor"),
+    Flag(("-fit", "--fit"), "fit", default="off"), Flag(("-fitt", "--fit-target"), "fit_target"),
+    Flag(("-fitc", "--fit-ctx"), "fit_ctx", "int", 4096), Flag(("-devd", "--device-draft"), "dev_draft"),
+    Flag(("--place",), "place", default=""),
+]
+_BY_NAME = {n: f for f in FLAGS for n in f.names}
+
+
+def _conv(f: Flag, raw: str):
+    try:
+        if f.kind == "int":
+            return int(raw)
+        if f.kind == "float":
+            return float(raw)
+        if f.kind == "bool":
+            return str(raw).lower() in ("1", "true", "on", "yes")
+    except ValueError:
+        raise Refusal(Code.USAGE, f"{f.names[0]} takes a {f.kind}, got {raw!r}") from None
+    return raw
+
+
+def parse(argv: List[str], environ=None) -> Dict[str, Any]:
+    """Resolve every flag with precedence CLI > --config > LLAMA_ARG_* > default."""
+    env = os.environ if environ is None else environ
+    cli: Dict[str, Any] = {}
+    i = 0
+    while i < len(argv):
+        a = argv[i]
+        name, eq, val = a.partition("=")
+        f = _BY_NAME.get(name)
+        if f is None:
+            raise Refusal(Code.USAGE, f"unknown flag {a!r}")
+        if f.kind == "bool":
+            cli[f.dest] = _conv(f, val) if eq else True
+        else:
+            if not eq:
+                i += 1
+                if i >= len(argv):
+                    raise Refusal(Code.USAGE, f"{name} needs a value")
+                val = argv[i]
+            cli[f.dest] = _conv(f, val)
+        i += 1
+    cfg: Dict[str, Any] = {}
+    if cli.get("config"):
+        try:
+            with open(cli["config"]) as fh:
+                raw = json.load(fh)
+        except (OSError, json.JSONDecodeError) as exc:
+            raise Refusal(Code.USAGE, f"--config {cli['config']}: {exc}") from None
+        for k, v in raw.items():
+            f = _BY_NAME.get(k) or _BY_NAME.get("--" + k.replace("_", "-"))
+            if f is None:
+                raise Refusal(Code.USAGE, f"--config: unknown key {k!r}")
+            cfg[f.dest] = _conv(f, v) if isinstance(v, str) else v
+    out: Dict[str, Any] = {}
+    for f in FLAGS:
+        if f.dest in cli:
+            out[f.dest] = cli[f.dest]
+        elif f.dest in cfg:
+            out[f.dest] = cfg[f.dest]
+        elif f.env and f.env in env:
+            out[f.dest] = _conv(f, env[f.env])
+        elif f.dest not in out:
+            out[f.dest] = f.default
+    return out
+
+
+@dataclasses.dataclass
+class Placement:
+    """What the placement flags ask for, in this build's terms."""
+
+    devices: List[int]                      # CUDA ordinals; empty = CPU only
+    mode: str = "a"                         # a = one GPU (whole model), tp = TP attention + EP experts over devices, cpu
+    expert_shares: Optional[List[float]] = None   # -ts: share of routed experts per device
+    host_experts: str = "none"              # none | all (--cpu-moe) | first:N (-ncmoe N) | pattern
+    host_pattern: Optional[str] = None
+    fit: bool = False
+    fit_targets_mib: Optional[List[int]] = None
+    fit_ctx: int = 4096
+    main_gpu: int = 0
+    draft_device: Optional[int] = None
+
+    def word(self) -> str:
+        if not self.devices:
+            return "cpu"
+        base = self.mode if len(self.devices) == 1 else f"{self.mode}{len(self.devices)}"
+        if self.host_experts != "none":
+            base += f"+host[{self.host_experts}]"
+        return base
+
+
+def _devices(spec: Optional[str], n_visible: int) -> List[int]:
+    if spec is None or spec == "":
+        return list(range(min(1, n_visible))) if n_visible else []
+    if spec.lower() == "none":
+        return []
+    out = []
+    for part in spec.split(","):
+        m = re.fullmatch(r"(?i)(?:cuda)?(\d+)", part.strip())
+        if not m:
+            raise Refusal(Code.USAGE, f"-dev {spec!r}: {part!r} is not CUDA<n>")
+        d = int(m.group(1))
+        if d >= n_visible:
+            raise Refusal(Code.NO_DEVICE, f"-dev names CUDA{d} but {n_visible} device(s) are visible")
+        out.append(d)
+    if len(set(out)) != len(out):
+        raise Refusal(Code.USAGE, f"-dev {spec!r} names a device twice")
+    return out
+
+
+def placement(opts: Dict[str, Any], n_visible: int, n_layer: int = 0) -> Placement:
+    sm = (opts.get("split_mode") or "layer").lower()
+    if sm in ("row", "tensor"):
+        raise Refusal(Code.USAGE, f"-sm {sm} is not served: layers are never split row-wise; use --place tp")
+    if sm not in ("none", "layer"):
+        raise Refusal(Code.USAGE, f"-sm {sm!r}: expected none or layer")
+    ngl = str(opts.get("ngl", "all")).lower()
+    if ngl not in ("all", "auto", "-1", "999") and not (ngl.isdigit() and (n_layer == 0 or int(ngl) >= n_layer)):
+        if ngl == "0":
+            devs: List[int] = []
+        else:
+            raise Refusal(Code.USAGE, f"-ngl {ngl}: only a full offload (or 0) is served; trunk layers are not split")
+    devs = [] if ngl == "0" else _devices(opts.get("dev"), n_visible)
+    pl = Placement(devices=devs, main_gpu=int(opts.get("main_gpu") or 0))
+    word = (opts.get("place") or "").lower()
+    if not devs:
+        pl.mode = "cpu"
+    elif word in ("", "a", "gate"):
+        pl.mode = "a" if len(devs) == 1 or sm == "none" else "tp"
+        if sm == "none":
+            pl.devices = [devs[min(pl.main_gpu, len(devs) - 1)]]
+    elif word in ("tp", "bp", "ep"):
+        pl.mode = "tp"
+    else:
+        try:
+            pl.devices = _devices(word, n_visible)
+            pl.mode = "tp" if len(pl.devices) > 1 else "a"
+        except Refusal:
+            raise Refusal(Code.USAGE, f"--place {word!r}: expected a, gate, bp, tp or a device list") from None
+    ts = opts.get("tensor_split")
+    if ts:
+        try:
+            shares = [float(x) for x in re.split(r"[,/]", ts)]
+        except ValueError:
+            raise Refusal(Code.USAGE, f"-ts {ts!r}: expected numbers separated by commas") from None
+        if len(shares) != len(pl.devices) or min(shares) < 0 or sum(shares) <= 0:
+            raise Refusal(Code.USAGE, f"-ts {ts!r}: need one non-negative share per device ({len(pl.devices)})")
+        tot = sum(shares)
+        pl.expert_shares = [s / tot for s in shares]
+    if opts.get("cpu_moe"):
+        pl.host_experts = "all"
+    elif int(opts.get("n_cpu_moe") or 0) > 0:
+        pl.host_experts = f"first:{int(opts['n_cpu_moe'])}"
+    ot = opts.get("override_tensor")
+    if ot:
+        pat, eq, where = ot.rpartition("=")
+        if not eq or where.upper() != "CPU":
+            raise Refusal(Code.USAGE, f"-ot {ot!r}: only <expert tensor pattern>=CPU is served")
+        if "exps" not in pat and "expert" not in pat:
+            raise Refusal(Code.USAGE, f"-ot {ot!r}: only routed-expert tensors may stay on the host")
+        pl.host_experts, pl.host_pattern = "pattern", pat
+    fit = str(opts.get("fit") or "off").lower()
+    if fit not in ("on", "off"):
+        raise Refusal(Code.USAGE, f"-fit {fit!r}: expected on or off")
+    pl.fit = fit == "on"
+    if opts.get("fit_target"):
+        try:
+            pl.fit_targets_mib = [int(x) for x in str(opts["fit_target"]).split(",")]
+        except ValueError:
+            raise Refusal(Code.USAGE, f"-fitt {opts['fit_target']!r}: expected MiB[,MiB...]") from None
+    pl.fit_ctx = int(opts.get("fit_ctx") or 4096)
+    if opts.get("dev_draft"):
+        pl.draft_device = _devices(opts["dev_draft"], n_visible)[0]
+    return pl
+
+
+def usage() -> str:
+    return "\n".join(f"  {', '.join(f.names):38s} {f.help}" for f in FLAGS)

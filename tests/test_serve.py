@@ -1,0 +1,192 @@
+"""HTTP contract on the mock engine (no model, no card), as the reference tests its server
+(``crates/serve/tests/*.rs`` on ``MockEngine``)."""
+import json
+import threading
+import time
+import urllib.error
+import urllib.request
+
+import pytest
+
+from bloomery_b200.serve.api import Server
+from bloomery_b200.serve.chat import ChatTemplate
+from bloomery_b200.serve.engine import MockEngine
+from bloomery_b200.utils import flags
+
+
+@pytest.fixture()
+def server(tmp_path):
+    opts = flags.parse(["--port", "0", "--mock", "--slot-save-path", str(tmp_path)])
+    s = Server(opts)
+    s.start()
+    s.ready(MockEngine(n_slots=2, slot_ctx=512), ChatTemplate(), 1 << 20)
+    yield s
+    s.state.stop_event.set()
+    s.stop()
+
+
+def call(s, path, body=None, method=None, headers=None):
+    data = json.dumps(body).encode() if body is not None else None
+    req = urllib.request.Request(s.url + path, data=data, method=method or ("POST" if data is not None else "GET"),
+                                 headers={"Content-Type": "application/json", **(headers or {})})
+    try:
+        r = urllib.request.urlopen(req)
+        raw = r.read()
+        return r.status, (json.loads(raw) if raw[:1] in (b"{", b"[") else raw.decode())
+    except urllib.error.HTTPError as e:
+        raw = e.read()
+        return e.code, (json.loads(raw) if raw[:1] == b"{" else raw.decode())
+
+
+def test_loading_then_ready():
+    opts = flags.parse(["--port", "0", "--mock"])
+    s = Server(opts)
+    s.start()
+    code, body = call(s, "/health")
+    assert code == 503 and body["error"]["message"] == "Loading model" and body["error"]["phase"] == "plan"
+    code, body = call(s, "/completion", {"prompt": "x"})
+    assert code == 503
+    s.ready(MockEngine(), ChatTemplate(), 0)
+    assert call(s, "/health")[0] == 200
+    s.state.stop_event.set()
+    assert s.stop() == 0
+
+
+def test_completion_echo_and_cache(server):
+    code, r = call(server, "/completion", {"prompt": "hello world", "n_predict": 64, "temperature": 0})
+    assert code == 200 and r["content"] == "hello world" and r["stop_type"] == "eos"
+    assert r["tokens_evaluated"] == 11 and r["tokens_cached"] == 0 and r["timings"]["predicted_n"] == 11
+    code, r = call(server, "/completion", {"prompt": "hello world, again", "n_predict": 3, "temperature": 0})
+    assert r["tokens_cached"] >= 11 and r["stop_type"] == "limit" and r["content"] == "hel"
+    code, r = call(server, "/completion", {"prompt": "hello world, again", "n_predict": 3, "cache_prompt": False})
+    assert r["tokens_cached"] == 0
+
+
+def test_stop_strings_and_token_prompt(server):
+    code, r = call(server, "/completion", {"prompt": "abcdefgh", "stop": ["de"], "temperature": 0})
+    assert r["content"] == "abc" and r["stop_type"] == "word" and r["stopping_word"] == "de"
+    code, r = call(server, "/completion", {"prompt": [104, 105], "n_predict": 8, "temperature": 0})
+    assert r["content"] == "hi"
+    code, r = call(server, "/completion", {"prompt": [70000]})
+    assert code == 400 and "vocabulary" in r["error"]["message"]
+
+
+def test_unknown_field_ignored_unsupported_refused(server):
+    code, r = call(server, "/completion", {"prompt": "ab", "n_predict": 2, "some_future_field": 1})
+    assert code == 200
+    code, r = call(server, "/completion", {"prompt": "ab", "grammar": "root ::= x"})
+    assert code == 400 and "grammar" in r["error"]["message"]
+
+
+def test_openai_completion_and_chat(server):
+    code, r = call(server, "/v1/completions", {"prompt": "xyz", "max_tokens": 2, "temperature": 0})
+    assert r["object"] == "text_completion" and r["choices"][0]["text"] == "xy" and r["choices"][0]["finish_reason"] == "length"
+    assert r["usage"]["completion_tokens"] == 2
+    code, r = call(server, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 5})
+    assert r["object"] == "chat.completion" and r["choices"][0]["message"]["role"] == "assistant"
+    assert r["usage"]["prompt_tokens"] > 10
+    code, r = call(server, "/v1/chat/completions", {"messages": []})
+    assert code == 400
+
+
+def test_chat_stream_sse(server):
+    req = urllib.request.Request(server.url + "/v1/chat/completions", data=json.dumps(
+        {"messages": [{"role": "user", "content": "stream"}], "max_tokens": 4, "stream": True,
+         "stream_options": {"include_usage": True}}).encode())
+    raw = urllib.request.urlopen(req).read().decode()
+    events = [json.loads(l[6:]) for l in raw.split("\n") if l.startswith("data: ") and l != "data: [DONE]"]
+    assert raw.rstrip().endswith("data: [DONE]")
+    assert events[0]["choices"][0]["delta"]["role"] == "assistant"
+    text = "".join(e["choices"][0]["delta"].get("content") or "" for e in events)
+    assert len(text) == 4 and events[-1]["choices"][0]["finish_reason"] == "length" and events[-1]["usage"]["completion_tokens"] == 4
+
+
+def test_anthropic_and_responses(server):
+    code, r = call(server, "/v1/messages", {"messages": [{"role": "user", "content": "yo"}], "max_tokens": 3, "system": "be brief"})
+    assert r["type"] == "message" and r["stop_reason"] == "max_tokens" and r["content"][0]["type"] == "text"
+    code, r = call(server, "/v1/messages", {"messages": [{"role": "user", "content": "yo"}]})
+    assert code == 400 and r["type"] == "error"
+    code, r = call(server, "/v1/messages/count_tokens", {"messages": [{"role": "user", "content": "yo"}]})
+    assert r["input_tokens"] > 0
+    code, r = call(server, "/v1/responses", {"input": "abc", "max_output_tokens": 3})
+    assert r["object"] == "response" and r["status"] == "incomplete" and len(r["output_text"]) == 3
+    rid = r["id"]
+    assert call(server, f"/v1/responses/{rid}")[1]["id"] == rid
+    code, r2 = call(server, "/v1/responses", {"input": "more", "previous_response_id": rid, "max_output_tokens": 2})
+    assert code == 200 and r2["usage"]["input_tokens"] > r["usage"]["input_tokens"]
+    assert call(server, f"/v1/responses/{rid}", method="DELETE")[1]["deleted"] is True
+    assert call(server, f"/v1/responses/{rid}")[0] == 404
+
+
+def test_tokenize_props_slots_metrics_models(server):
+    assert call(server, "/tokenize", {"content": "ab"})[1] == {"tokens": [97, 98]}
+    assert call(server, "/detokenize", {"tokens": [97, 98]})[1] == {"content": "ab"}
+    assert "<|im_start|>user" in call(server, "/apply-template", {"messages": [{"role": "user", "content": "q"}]})[1]["prompt"]
+    p = call(server, "/props")[1]
+    assert p["total_slots"] == 2 and p["default_generation_settings"]["params"]["top_k"] == 40
+    assert len(call(server, "/slots")[1]) == 2
+    assert "llamacpp:prompt_tokens_total" in call(server, "/metrics")[1]
+    assert call(server, "/v1/models")[1]["data"][0]["id"] == "mock-echo"
+    assert call(server, "/api/tags")[1]["models"][0]["name"] == "mock-echo"
+    assert call(server, "/nope")[0] == 404
+
+
+def test_slot_save_restore_erase(server):
+    call(server, "/completion", {"prompt": "remember me", "n_predict": 2, "id_slot": 0})
+    code, r = call(server, "/slots/0?action=save", {"filename": "s.bin"})
+    assert code == 200 and r["n_saved"] > 0
+    code, r = call(server, "/slots/0?action=erase", {})
+    assert r["n_erased"] > 0
+    code, r = call(server, "/slots/0?action=restore", {"filename": "s.bin"})
+    assert code == 200 and r["n_restored"] > 0
+    assert call(server, "/slots/0?action=bogus", {})[0] == 400
+    assert call(server, "/slots/9?action=erase", {})[0] == 404
+
+
+def test_two_concurrent_requests_share_rounds():
+    opts = flags.parse(["--port", "0", "--mock"])
+    server = Server(opts)
+    server.start()
+    server.ready(MockEngine(n_slots=2, slot_ctx=512, step_delay=0.003), ChatTemplate(), 0)
+    out = [None, None]
+
+    def go(i):
+        out[i] = call(server, "/completion", {"prompt": "abcdefghijklmnopqrstuvwxyz" * 2 + str(i), "temperature": 0})[1]
+    ts = [threading.Thread(target=go, args=(i,)) for i in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert out[0]["content"].endswith("0") and out[1]["content"].endswith("1")
+    assert 2 in server.state.worker.rounds_by_width          # one decode round served both slots
+    server.state.stop_event.set()
+    server.stop()
+
+
+def test_json_mode(server):
+    code, r = call(server, "/completion", {"prompt": '{"a": [1, 2, {"b": null}]} trailing', "temperature": 0,
+                                            "response_format": {"type": "json_object"}})
+    assert json.loads(r["content"]) == {"a": [1, 2, {"b": None}]}
+
+
+def test_api_key_and_shutdown():
+    opts = flags.parse(["--port", "0", "--mock", "--api-key", "sekret"])
+    s = Server(opts)
+    s.start()
+    s.ready(MockEngine(), ChatTemplate(), 0)
+    assert call(s, "/props")[0] == 401
+    assert call(s, "/props", headers={"Authorization": "Bearer sekret"})[0] == 200
+    assert call(s, "/health")[0] == 200
+    assert call(s, "/shutdown", {}, headers={"Authorization": "Bearer sekret"})[0] == 200
+    assert s.state.stop_event.wait(2)
+    assert s.stop() == 0
+
+
+def test_engine_failure_is_fatal():
+    opts = flags.parse(["--port", "0", "--mock"])
+    s = Server(opts)
+    s.start()
+    s.ready(MockEngine(fail_at=3), ChatTemplate(), 0)
+    code, r = call(s, "/completion", {"prompt": "abcdef", "temperature": 0})
+    assert code == 500 and "engine failure" in r["error"]["message"]
+    assert s.state.stop_event.wait(2)
+    assert call(s, "/health")[0] == 503
+    assert s.stop() == 70

@@ -1,0 +1,255 @@
+"""Host-side units of the serving layer: sampler chain, flags and levers, tokenizers,
+templates and tool-call scanners, prompt cache, slot board, records."""
+import io
+import json
+import math
+
+import numpy as np
+import pytest
+
+from bloomery_b200.serve import chat as C
+from bloomery_b200.serve.engine import Saved
+from bloomery_b200.serve.promptcache import PromptCache
+from bloomery_b200.serve.sampler import Sampler, SamplingParams, Xoshiro256, greedy_pick
+from bloomery_b200.serve.sched import Board, QueueFull
+from bloomery_b200.serve.tokenizer import B2U, BpeTokenizer, ByteTokenizer, SpmTokenizer, StreamDecoder
+from bloomery_b200.utils import flags, levers, records
+from bloomery_b200.utils.exit_codes import Code, Refusal
+
+
+# ---- sampler -----------------------------------------------------------------------------
+def test_greedy_tie_rule():
+    assert greedy_pick(np.array([1.0, 3.0, 3.0, 2.0], np.float32)) == 1           # equal wins at the lower id
+    assert greedy_pick(np.array([np.nan, 1.0, np.nan], np.float32)) == 1          # NaN never wins
+    assert greedy_pick(np.array([np.nan, np.nan], np.float32)) == 0               # all-NaN row -> id 0
+    assert greedy_pick(np.array([-0.0, 0.0], np.float32)) == 0                    # -0 == +0
+
+
+def test_xoshiro_reference_vector():
+    r = Xoshiro256(0)
+    # splitmix64(0) seeds: first state word is the well-known 0xE220A8397B1DCDAF
+    assert r.s[0] == 0xE220A8397B1DCDAF
+    a = [r.next_u64() for _ in range(3)]
+    assert len(set(a)) == 3 and all(0 <= x < 1 << 64 for x in a)
+    u = Xoshiro256(7).next_f64()
+    assert 0.0 <= u < 1.0
+
+
+def test_top_k_one_is_greedy_and_seed_is_reproducible():
+    rng = np.random.default_rng(0)
+    row = rng.normal(size=1000).astype(np.float32)
+    assert Sampler(SamplingParams(top_k=1)).sample(row) == greedy_pick(row)
+    a = [Sampler(SamplingParams(seed=5)).sample(row) for _ in range(3)]
+    assert a[0] == a[1] == a[2]
+    s = Sampler(SamplingParams(seed=5, top_k=0, top_p=1.0, min_p=0.0, temperature=1.0))
+    picks = {s.sample(row) for _ in range(50)}
+    assert len(picks) > 5
+
+
+def test_min_p_top_p_and_penalties():
+    row = np.array([5.0, 4.9, 1.0, 0.0, -3.0], np.float32)
+    s = Sampler(SamplingParams(top_k=0, top_p=1.0, min_p=0.5, temperature=1.0))
+    s.sample(row)
+    assert [c[0] for c in s.candidates] == [0, 1]               # logit >= max + ln(0.5)
+    s = Sampler(SamplingParams(top_k=0, top_p=0.5, min_p=0.0, temperature=1.0))
+    s.sample(row)
+    assert [c[0] for c in s.candidates] == [0]                  # shortest prefix whose mass reaches top_p
+    s = Sampler(SamplingParams(temperature=0.0, repeat_penalty=2.0, frequency_penalty=0.5, presence_penalty=1.0, repeat_last_n=8))
+    pen = s.penalized(row, [0, 0, 4])
+    assert pen[0] == pytest.approx(5.0 / 2 - (2 * 0.5 + 1.0)) and pen[4] == pytest.approx(-3.0 * 2 - (0.5 + 1.0))
+    assert s.sample(row, [0, 0, 4]) == 1                        # temperature <= 0: arg-max after penalties
+
+
+# ---- flags / levers / records -----------------------------------------------------------------
+def test_flag_precedence_and_unknown(tmp_path):
+    cfg = tmp_path / "c.json"
+    cfg.write_text(json.dumps({"--port": 1234, "ctx-size": "2048"}))
+    o = flags.parse(["--config", str(cfg), "-c", "4096"], environ={"LLAMA_ARG_PORT": "9", "LLAMA_ARG_HOST": "0.0.0.0"})
+    assert o["ctx"] == 4096 and o["port"] == 1234 and o["host"] == "0.0.0.0"          # CLI > config > env > default
+    with pytest.raises(Refusal) as e:
+        flags.parse(["--frobnicate"])
+    assert e.value.code == Code.USAGE and "--frobnicate" in str(e.value)
+    with pytest.raises(Refusal):
+        flags.parse(["--port", "abc"])
+
+
+def test_placement_words():
+    pl = flags.placement(flags.parse([], {}), n_visible=8, n_layer=48)
+    assert pl.devices == [0] and pl.mode == "a" and pl.word() == "a"
+    pl = flags.placement(flags.parse(["-dev", "CUDA0,CUDA1,CUDA2,CUDA3", "-ts", "1,1,1,1", "--cpu-moe"], {}), 8, 48)
+    assert pl.mode == "tp" and pl.expert_shares == [0.25] * 4 and pl.host_experts == "all" and pl.word() == "tp4+host[all]"
+    pl = flags.placement(flags.parse(["-ot", r"blk\.(1|2)\.ffn_.*_exps=CPU", "-ncmoe", "3"], {}), 1, 48)
+    assert pl.host_experts == "pattern"
+    for bad, word in ((["-sm", "row"], "row"), (["-ngl", "20"], "-ngl"), (["-ot", "attn_q=CPU"], "routed-expert"),
+                      (["-dev", "CUDA9"], "CUDA9"), (["-ts", "1,2"], "-ts")):
+        with pytest.raises(Refusal) as e:
+            flags.placement(flags.parse(bad, {}), 2, 48)
+        assert word in str(e.value)
+    assert flags.placement(flags.parse(["-dev", "none"], {}), 2, 48).word() == "cpu"
+    assert flags.placement(flags.parse(["-fit", "on", "-fitt", "1024,2048", "-fitc", "8192"], {}), 2, 48).fit_targets_mib == [1024, 2048]
+
+
+def test_levers():
+    v = levers.at_main({"BLOOMERY_RESIDENCY": "off", "BLOOMERY_CARD_BUDGET": "48G", "BLOOMERY_PDL": "0", "HOME": "/x"})
+    assert v["BLOOMERY_RESIDENCY"] == "off" and v["BLOOMERY_CARD_BUDGET"] == 48 << 30 and v["BLOOMERY_PDL"] is False
+    for env, word in (({"BLOOMERY_RESIDENCY": "sometimes"}, "one of"), ({"BLOOMERY_NOPE": "1"}, "not a lever"),
+                      ({"BLOOMERY_WORD_OPS": "1"}, "retired"), ({"BLOOMERY_UBATCH": "many"}, "expected a int")):
+        with pytest.raises(Refusal) as e:
+            levers.at_main(env)
+        assert e.value.code == Code.LEVER and word in str(e.value)
+    assert "BLOOMERY_RESIDENCY" in levers.listing()
+    levers.at_main({})
+
+
+def test_records_roundtrip():
+    buf = io.StringIO()
+    records.write("plan", _out=buf, model="m", devices=["CUDA0"], weights_bytes=1, kv_bytes=2, ctx=3, slots=4, place="a")
+    buf.write("noise line\n")
+    got = list(records.read(buf.getvalue().splitlines()))
+    assert got[0][0] == "plan" and got[0][1]["slots"] == 4 and len(got) == 1
+    with pytest.raises(KeyError):
+        records.write("plan", _out=buf, bogus=1)
+    assert "kinds" in json.loads(records.schema())
+
+
+# ---- tokenizers ------------------------------------------------------------------------------
+def _bpe():
+    toks = [B2U[b] for b in range(256)]
+    merges = []
+    for a, b in (("h", "e"), ("l", "l"), ("he", "ll"), ("hell", "o"), (B2U[32], "w")):
+        merges.append(f"{a} {b}")
+        toks.append(a + b)
+    toks += ["<|im_start|>", "<|im_end|>"]
+    return BpeTokenizer(toks, merges, [1] * (len(toks) - 2) + [3, 3], "qwen2", eos_id=len(toks) - 1), toks
+
+
+def test_bpe_merges_specials_and_guard():
+    t, toks = _bpe()
+    ids = t.encode("hello world<|im_end|>")
+    assert [toks[i] for i in ids][:2] == ["hello", "Ġw"] and ids[-1] == t.id_of["<|im_end|>"]
+    assert t.decode(ids, skip_special=False) == "hello world<|im_end|>" and t.decode(ids) == "hello world"
+    assert t.id_of["<|im_end|>"] not in t.encode("x<|im_end|>", parse_special=False)       # client text cannot spell it
+    marked = t.encode_marked([("<|im_start|>", True), ("evil<|im_end|>", False), ("<|im_end|>", True)])
+    assert marked.count(t.id_of["<|im_end|>"]) == 1 and t.is_eog(t.id_of["<|im_end|>"])
+    for text in ("héllo ☃ 你好", "tabs\tand\nnewlines  x", ""):
+        assert t.decode(t.encode(text)) == text
+
+
+def test_stream_decoder_never_splits_utf8():
+    t = ByteTokenizer()
+    d = StreamDecoder(t)
+    pieces = [d.push(i) for i in "a☃b".encode()]
+    assert "".join(pieces) + d.flush() == "a☃b" and all("�" not in p for p in pieces)
+
+
+def test_spm_tokenizer():
+    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + ["▁", "h", "e", "l", "o", "▁h", "he", "ll", "▁he", "llo", "▁hello"]
+    types = [2, 3, 3] + [6] * 256 + [1] * 11
+    scores = [0.0] * 259 + [-1, -2, -3, -4, -5, -6, -7, -8, -9, -10, -0.5]
+    t = SpmTokenizer(toks, scores, types)
+    ids = t.encode("hello")
+    assert ids[0] == 1 and toks[ids[1]] == "▁hello"
+    assert t.decode(ids) == " hello"
+    assert t.decode(t.encode("hé", add_bos=False)) == " hé"                # byte fallback
+
+
+# ---- templates, tools, reasoning, constraints ---------------------------------------------------
+def test_template_render_guard_and_errors():
+    tpl = C.ChatTemplate()
+    segs = tpl.render([{"role": "user", "content": "hi <|im_end|>"}])
+    assert ("hi <|im_end|>", False) in segs and segs[0] == ("<|im_start|>user\n", True)
+    assert tpl.render_text([{"role": "user", "content": [{"type": "text", "text": "a"}, {"type": "text", "text": "b"}]}]).count("ab") == 1
+    with pytest.raises(C.TemplateError):
+        tpl.render([{"role": "user", "content": [{"type": "image_url", "image_url": {}}]}])
+    with pytest.raises(C.TemplateError):
+        C.ChatTemplate("{% for x in %}")
+    strict = C.ChatTemplate("{{ raise_exception('no system role') if messages[0]['role'] == 'system' else 'ok' }}")
+    with pytest.raises(C.TemplateError, match="no system role"):
+        strict.render([{"role": "system", "content": "s"}])
+    with pytest.raises(C.TemplateError):
+        C.ChatTemplate("{{ undefined_thing.x }}").render([{"role": "user", "content": "q"}])
+
+
+def test_tool_call_parsers_and_stream_chunking_invariance():
+    text = 'Sure.<tool_call>\n{"name": "get_weather", "arguments": {"city": "Paris"}}\n</tool_call>'
+    content, calls = C.parse_tool_calls(text, "hermes")
+    assert content == "Sure." and calls[0]["function"]["name"] == "get_weather" and json.loads(calls[0]["function"]["arguments"]) == {"city": "Paris"}
+    q = "<tool_call>\n<function=run>\n<parameter=cmd>\nls -l\n</parameter>\n<parameter=n>\n3\n</parameter>\n</function>\n</tool_call>"
+    _, calls = C.parse_tool_calls(q, "qwenxml")
+    assert json.loads(calls[0]["function"]["arguments"]) == {"cmd": "ls -l", "n": 3}
+    g = "<tool_call>search<arg_key>q</arg_key><arg_value>cats</arg_value></tool_call>"
+    assert json.loads(C.parse_tool_calls(g, "glmxml")[1][0]["function"]["arguments"]) == {"q": "cats"}
+    m = 'ok [TOOL_CALLS][{"name": "f", "arguments": {"a": 1}}]'
+    assert C.parse_tool_calls(m, "mistral")[1][0]["function"]["name"] == "f"
+    assert C.detect_tool_format("... <function= ...") == "qwenxml" and C.detect_tool_format("plain") == "hermes"
+    # the streamed scanner gives the same calls and text however the text is chunked
+    for step in (1, 3, 7, len(text)):
+        s = C.ToolCallStream("hermes")
+        out, got = "", []
+        for i in range(0, len(text), step):
+            t, c = s.push(text[i:i + step])
+            out += t
+            got += c
+        out += s.flush()
+        assert out == "Sure." and len(got) == 1 and got[0]["function"]["name"] == "get_weather"
+
+
+def test_reasoning_split():
+    assert C.split_reasoning("<think>plan</think>\nanswer") == ("plan", "answer")
+    assert C.split_reasoning("plan</think>answer", started=True) == ("plan", "answer")
+    assert C.split_reasoning("no thinking") == ("", "no thinking")
+    assert C.split_reasoning("<think>unfinished") == ("unfinished", "")
+
+
+def test_json_constraint_prefixes_and_schema():
+    c = C.JsonConstraint()
+    assert c.allowed("", '{"a"') and c.allowed('{"a"', ": [1, 2") and not c.allowed('{"a"', " 1") and not c.allowed("", "}")
+    assert c.done('{"a": [1, 2.5e3, true, null]}') and not c.done('{"a": [1,') and not c.allowed('{"a": 1}', "x")
+    schema = {"type": "object", "properties": {"n": {"type": "integer"}, "t": {"enum": ["x", "y"]}}, "required": ["n"],
+              "additionalProperties": False}
+    s = C.JsonConstraint(schema)
+    assert s.done('{"n": 3, "t": "x"}') and not s.done('{"t": "x"}') and not s.done('{"n": 3, "z": 1}') and not s.done('{"n": "3"}')
+    assert not s.allowed("", "[") and s.allowed("", "{")
+    assert C.validate([1, 2], {"type": "array", "items": {"type": "number"}, "minItems": 2}) and not C.validate([1], {"type": "array", "minItems": 2})
+
+
+# ---- prompt cache and board -------------------------------------------------------------------------
+def test_prompt_cache_rules():
+    pc = PromptCache(100)
+    s = lambda ids, n: Saved(tuple(ids), None, n)
+    assert pc.put(s([1, 2, 3], 40)) and pc.put(s([9, 9], 40))
+    got, n = pc.lookup([1, 2, 3, 4, 5])
+    assert got.ids == (1, 2, 3) and n == 3
+    assert pc.put(s([1, 2, 3, 4], 40))                      # covers [1,2,3] wholly -> that one is evicted first
+    assert (1, 2, 3) not in pc._items and len(pc) == 2
+    assert pc.put(s([7], 40))                               # over budget: least recently used goes
+    assert pc.used <= 100 and (9, 9) not in pc._items
+    assert pc.lookup([5, 5])[0] is None and not pc.put(s([1], 1000))
+    pc2 = PromptCache(50)
+    pc2.put(s([1], 40), pending=True)
+    pc2.put(s([2], 40))
+    assert (1,) in pc2._items                               # a pending copy is pinned
+    pc2.settle([1])
+    assert pc2.used <= 50
+
+
+def test_board_slot_choice_and_queue():
+    class R:
+        def __init__(self, ids, i):
+            self.prompt_ids, self.id = ids, i
+    b = Board(3, queue_depth=2)
+    b.slots[0].ids = [1, 2, 3, 4, 5, 6, 7, 8, 9, 10]
+    b.slots[1].ids = [1, 2, 3]
+    slot, shared = b.pick_slot([1, 2, 3, 4, 5, 99])
+    assert slot.id == 0 and shared == 5                     # longest common prefix wins
+    slot, shared = b.pick_slot([50] * 40)
+    assert slot.id == 2 and shared == 0                     # nothing shared: the empty slot is preferred
+    slot, shared = b.pick_slot([1] + [77] * 30)
+    assert shared == 0                                      # below the 0.1 similarity floor
+    b.submit(R([1], 1)); b.submit(R([2], 2))
+    with pytest.raises(QueueFull):
+        b.submit(R([3], 3))
+    req, slot, _ = b.next_request()
+    assert req.id == 1 and slot.busy                        # oldest first
+    b.release(slot)
+    assert not slot.busy
