@@ -182,34 +182,82 @@ struct ReduceWait {
   volatile int* gave_up;    // shared by the block
 };
 
-__device__ __forceinline__ float reduce_take(const ReduceIn& r, ReduceWait& w, const uint2* slot) {
-  for (unsigned it = 0;; ++it) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(slot) : "memory");
-    if (v.y == w.epoch) return __uint_as_float(v.x);
-    if ((it & 127) == 127) {
-      if (*w.gave_up) break;
-      const unsigned long long now = global_timer_ns();
-      if (w.t0 == 0) w.t0 = now;
-      else if (now - w.t0 > 1000000000ull) { *w.gave_up = 1; raise_fault(r.fault, r.layer, FS_WAIT_TIMEOUT); break; }
-    }
-  }
-  return __int_as_float(0x7fc00000);
-}
-
-// Residual value (row m, column i) after the reduction: x + sum over ranks in rank order.
-__device__ __forceinline__ float reduce_value(const ReduceIn& r, ReduceWait& w, const float* x_row, int m, int i) {
-  float v = x_row[i];
-  for (int k = 0; k < r.n_ranks; ++k) v += reduce_take(r, w, r.recv + ((long)k * kMaxRows + m) * r.H + i);
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint2* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ float4 reduce_value4(const ReduceIn& r, ReduceWait& w, const float* x_row, int m, int i) {
-  float4 v = *reinterpret_cast<const float4*>(x_row + i);
-  for (int k = 0; k < r.n_ranks; ++k) {
-    const uint2* s = r.recv + ((long)k * kMaxRows + m) * r.H + i;
-    v.x += reduce_take(r, w, s); v.y += reduce_take(r, w, s + 1);
-    v.z += reduce_take(r, w, s + 2); v.w += reduce_take(r, w, s + 3);
+
+// Bounded re-poll bookkeeping shared by the batched readers below; true = keep polling.
+__device__ __forceinline__ bool reduce_again(const ReduceIn& r, ReduceWait& w, unsigned it) {
+  if ((it & 31) != 31) return true;
+  if (*w.gave_up) return false;
+  const unsigned long long now = global_timer_ns();
+  if (w.t0 == 0) { w.t0 = now; return true; }
+  if (now - w.t0 > 1000000000ull) { *w.gave_up = 1; raise_fault(r.fault, r.layer, FS_WAIT_TIMEOUT); return false; }
+  return true;
+}
+
+// acc[0..8) += the eight values (row m, columns i0..i0+7) of every rank, in rank order.
+// Two ranks' slots are fetched per round trip (eight 16-byte loads in flight), checked, and
+// only re-fetched if a tag is still old; values are added strictly in rank order so every
+// rank computes bit-identical sums.
+__device__ __forceinline__ void reduce_sum8(const ReduceIn& r, ReduceWait& w, int m, int i0, float (&acc)[8]) {
+  for (int k0 = 0; k0 < r.n_ranks; k0 += 2) {
+    const int n = min(2, r.n_ranks - k0);
+    uint4 b[2][4];
+    bool ok = false;
+    for (unsigned it = 0; !ok; ++it) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (j < n) {
+          const uint2* s = r.recv + ((long)(k0 + j) * kMaxRows + m) * r.H + i0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) b[j][q] = ld_volatile_v4(s + 2 * q);
+        }
+      ok = true;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (j < n) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) ok = ok && b[j][q].y == w.epoch && b[j][q].w == w.epoch;
+        }
+      if (!ok && !reduce_again(r, w, it)) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = __int_as_float(0x7fc00000);
+        return;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      if (j < n) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { acc[2 * q] += __uint_as_float(b[j][q].x); acc[2 * q + 1] += __uint_as_float(b[j][q].z); }
+      }
   }
+}
+
+// One column (row m, column i): every rank's slot is fetched before any tag is checked.
+__device__ __forceinline__ float reduce_value(const ReduceIn& r, ReduceWait& w, const float* x_row, int m, int i) {
+  float v = x_row[i];
+  uint2 b[kMaxRanks];
+  bool ok = false;
+  for (unsigned it = 0; !ok; ++it) {
+#pragma unroll
+    for (int k = 0; k < kMaxRanks; ++k)
+      if (k < r.n_ranks) {
+        const uint2* s = r.recv + ((long)k * kMaxRows + m) * r.H + i;
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(b[k].x), "=r"(b[k].y) : "l"(s) : "memory");
+      }
+    ok = true;
+#pragma unroll
+    for (int k = 0; k < kMaxRanks; ++k)
+      if (k < r.n_ranks) ok = ok && b[k].y == w.epoch;
+    if (!ok && !reduce_again(r, w, it)) return __int_as_float(0x7fc00000);
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxRanks; ++k)
+    if (k < r.n_ranks) v += __uint_as_float(b[k].x);
   return v;
 }
 

@@ -76,7 +76,10 @@ __device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, flo
     for (int i0 = tid * 8; i0 < K; i0 += 256 * 8) {
       float4 x0, x1;
       if (reduce) {
-        x0 = reduce_value4(a.red, rw, x, ms, i0); x1 = reduce_value4(a.red, rw, x, ms, i0 + 4);
+        x0 = *reinterpret_cast<const float4*>(x + i0); x1 = *reinterpret_cast<const float4*>(x + i0 + 4);
+        float acc8[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        reduce_sum8(a.red, rw, ms, i0, acc8);
+        x0 = make_float4(acc8[0], acc8[1], acc8[2], acc8[3]); x1 = make_float4(acc8[4], acc8[5], acc8[6], acc8[7]);
         if (blockIdx.x == 0 && m < a.M) {
           *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0) = x0;
           *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0 + 4) = x1;

@@ -198,7 +198,10 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
       const float* xr = a.x + (long)ms * a.x_stride;
       float4 x0, x1;
       if (a.red.n_ranks > 0) {
-        x0 = reduce_value4(a.red, rw, xr, ms, i0); x1 = reduce_value4(a.red, rw, xr, ms, i0 + 4);
+        x0 = *reinterpret_cast<const float4*>(xr + i0); x1 = *reinterpret_cast<const float4*>(xr + i0 + 4);
+        float acc8[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        reduce_sum8(a.red, rw, ms, i0, acc8);
+        x0 = make_float4(acc8[0], acc8[1], acc8[2], acc8[3]); x1 = make_float4(acc8[4], acc8[5], acc8[6], acc8[7]);
         if (e == 0 && m < a.M) {
           *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0) = x0;
           *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0 + 4) = x1;
