@@ -153,14 +153,7 @@ class DecodeEngine:
             K.gemv([w.q[b + "attn_output.weight"]], M, x, xq=self.attn_q, xds=self.attn_ds, resid=x,
                    fault=self.fault, layer=il); n += 1
             if s.layer_is_moe(il):
-                K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
-                         self.xq, self.xds, None, self.fault, il); n += 1
-                K.gate_up_sel(self.xq, self.xds, self.r_ids, None, w.q[b + "ffn_gate_exps.weight"],
-                              w.q[b + "ffn_up_exps.weight"], s.n_expert, s.n_used, M, self.actq, self.actds, None,
-                              self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=self.r_wts,
-                              heat=self.heat[il]); n += 1
-                K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, None, w.q[b + "ffn_down_exps.weight"],
-                               s.n_expert, s.n_used, M, x, None, x, self.fault, il); n += 1
+                n += self._moe(il, M, x)
             else:
                 K.gemv([w.q[b + "ffn_gate.weight"], w.q[b + "ffn_up.weight"]], M, self.gu, x=x,
                        gain=w.f[b + "ffn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il); n += 1
@@ -177,6 +170,23 @@ class DecodeEngine:
                 K.advance_rows(self.tokens, self.row_pos, self.row_seq, self.tokens_out, M, self.hist, self.hist_cap,
                                self.counters[2:3]); n += 1
         return n
+
+    def _moe(self, il: int, M: int, x: torch.Tensor) -> int:
+        """Router + routed experts + combine of one layer (3 launches); returns the launch count."""
+        s, w = self.spec, self.w
+        b = f"blk.{il}."
+        K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
+                 self.xq, self.xds, None, self.fault, il)
+        K.gate_up_sel(self.xq, self.xds, self.r_ids, None, w.q[b + "ffn_gate_exps.weight"],
+                      w.q[b + "ffn_up_exps.weight"], s.n_expert, s.n_used, M, self.actq, self.actds, None,
+                      self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=self.r_wts,
+                      heat=self.heat[il])
+        K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, None, w.q[b + "ffn_down_exps.weight"],
+                       s.n_expert, s.n_used, M, x, None, x, self.fault, il)
+        return 3
+
+    def _after_pass(self, n_rows: int) -> None:
+        """Hook between passes (residency boundaries live here in the tiered engine)."""
 
     def _rule(self, il: int) -> "K.RouteRule":
         s = self.spec
@@ -253,6 +263,7 @@ class DecodeEngine:
         with self._lock:
             M = self.set_rows(rows)
             self.launch(M, head, False)
+            self._after_pass(len(rows))
             for slot, _, pos in rows:
                 self.slot_len[slot] = max(self.slot_len[slot], pos + 1)
             if not head:
@@ -322,6 +333,7 @@ class DecodeEngine:
             self.counters[2:3].zero_()
             for i in range(n_steps):
                 self.launch(1, True, True)
+                self._after_pass(1)
             out = self.hist[:n_steps].cpu().tolist()
             self.slot_len[slot] = start_pos + n_steps
             self.check_fault()

@@ -1,0 +1,64 @@
+"""Decode engine for models whose routed experts do not all fit in HBM: a budgeted number of
+experts per layer stay resident in slots, the rest live in pinned host RAM; a routed slot
+whose expert is not resident is served by the CPU leg through the in-graph hand-off, and the
+residency rule keeps promoting the most-called experts (``runtime/residency.py``).
+
+Per MoE layer the chain becomes
+  router | route | hand-off (go) | gate·up of resident slots | wait | down + combine (+ host rows)
+so the card computes its resident experts while the CPU computes the cold ones (the
+reference's ``router -> handoff -> go -> [card experts] -> wait -> add``,
+``crates/gpu/src/host/mod.rs:12-27``).  ``--cpu-moe`` is this engine with zero resident slots.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import decode as K
+from .engine import DecodeEngine
+from .residency import HostTier, TieredExperts
+
+
+class TieredEngine(DecodeEngine):
+    def __init__(self, weights, resident_per_layer: int, residency: Optional[str] = "mid", **kw):
+        spec = weights.spec
+        self.tiered = TieredExperts(spec, weights, resident_per_layer, weights.device, rule=residency)
+        super().__init__(weights, **kw)
+        self.tier = HostTier(spec.n_layer, spec.hidden, spec.moe_inter, spec.n_used, self.device)
+        self.tiered.attach_host_tier(self.tier)
+        self.tier.start()
+
+    def _moe(self, il: int, M: int, x: torch.Tensor) -> int:
+        s, w, t = self.spec, self.w, self.tiered
+        b = f"blk.{il}."
+        sm = t.slot_map[il]
+        card = t.card[il]
+        K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
+                 self.xq, self.xds, None, self.fault, il)
+        K.route_rows(self.r_logits, self._rule(il), M, self.r_ids, self.r_wts, self.heat[il], self.fault, il)
+        self.tier.handoff(self.r_ids, self.r_wts, sm, self.xq, self.xds, M, s.n_used, s.hidden, s.n_expert, il)
+        K.gate_up_sel(self.xq, self.xds, self.r_ids, sm, card["ffn_gate_exps"], card["ffn_up_exps"], s.n_expert,
+                      s.n_used, M, self.actq, self.actds, None, self.fault, il)
+        self.tier.wait(M, s.hidden, self.fault, il)
+        K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, sm, card["ffn_down_exps"], s.n_expert, s.n_used,
+                       M, x, self.tier.extra, x, self.fault, il)
+        return 6
+
+    def _after_pass(self, n_rows: int) -> None:
+        self.tiered.boundary(self.heat, n_rows)
+
+    def memory_report(self):
+        r = super().memory_report()
+        r.update({"experts_card": self.tiered.card_bytes(), "experts_host": self.tiered.host_bytes()})
+        return r
+
+    def stats(self):
+        out = self.tier.stats()
+        out["flips"] = self.tiered.rule.total_flips if self.tiered.rule else 0
+        out["bytes_promoted"] = self.tiered.bytes_promoted
+        return out
+
+    def close(self) -> None:
+        self.tier.stop()
+        self.tier.close()

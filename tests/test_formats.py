@@ -150,3 +150,57 @@ def test_resident_roundtrip_and_host_units(t):
 
 def test_host_pool():
     assert H.pool_size() >= 1
+
+
+def test_cpu_expert_leg_matches_oracle():
+    """blh_moe_experts (C++ pool, unit dots) against the fp32 restatement on the same q8 inputs."""
+    import ctypes
+    from bloomery_b200.formats.resident import WT
+    from bloomery_b200.ops._lib import host
+    torch.manual_seed(5)
+    H, I, E, k, M = 512, 256, 6, 3, 2
+    gate = torch.randn(E, I, H) * 0.05; up = torch.randn(E, I, H) * 0.05; down = torch.randn(E, H, I) * 0.05
+    def res(w, t):
+        raw = Q.quantize(w.reshape(-1, w.shape[-1]), t)
+        return to_resident(raw, t, w.shape[-1]).contiguous(), Q.dequantize(raw, t, w.shape[-1]).reshape(w.shape)
+    gr, gd = res(gate, "Q4_K"); ur, ud = res(up, "Q4_K"); dr, dd = res(down, "Q6_K")
+    x = torch.randn(M, H)
+    codes, ds = H_act(x)
+    ids = torch.tensor([[0, 3, -1], [5, 1, 2]], dtype=torch.int32)
+    wts = torch.rand(M, k)
+    out = torch.zeros(M, H)
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    rc = host().blh_moe_experts(M, H, I, E, k, vp(ids), vp(wts), vp(codes), vp(ds), vp(gr), vp(ur), vp(dr), WT["Q4_K"], WT["Q6_K"], vp(out))
+    assert rc == 0
+    xa = Q.dequantize_act_q8(codes, ds).double()
+    ref = torch.zeros(M, H, dtype=torch.float64)
+    for m in range(M):
+        for j in range(k):
+            e = int(ids[m, j])
+            if e < 0:
+                continue
+            a = (torch.nn.functional.silu(xa[m] @ gd[e].double().T) * (xa[m] @ ud[e].double().T)).float()
+            ac, ads = Q.quantize_act_q8(a[None])
+            ref[m] += wts[m, j].double() * (Q.dequantize_act_q8(ac, ads)[0].double() @ dd[e].double().T)
+    assert ((out.double() - ref).abs().max() / ref.abs().max()).item() < 1e-3
+
+
+def H_act(x):
+    return H.act_q8(x)
+
+
+def test_residency_rule_is_deterministic_and_bounded():
+    from bloomery_b200.runtime.residency import ResidencyRule
+    def run():
+        r = ResidencyRule(2, 8, [[0, 1, 2], [0, 1, 2]], every=4, cap=3, margin=3.0, min_count=2, decay=0.9)
+        log = []
+        for step in range(12):
+            r.observe(0, [0, 0, 0, 5, 4, 0, 0, 1]); r.observe(1, [1, 1, 1, 0, 0, 0, 0, 0])
+            if r.kept(2):
+                log.append([(f.layer, f.newcomer, f.victim) for f in r.decide()])
+        return log, [sorted(s) for s in r.on_card]
+    a, b = run(), run()
+    assert a == b                                            # same history => same map
+    log, on = a
+    assert on[1] == [0, 1, 2] and 3 in on[0] and 4 in on[0]   # the hot ones were promoted, layer 1 untouched
+    assert all(len(f) <= 3 for f in log)

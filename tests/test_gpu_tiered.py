@@ -1,0 +1,64 @@
+"""Experts split between HBM slots and pinned host RAM: cold hits go through the in-graph
+hand-off to the CPU leg, hot experts get promoted by the residency rule; tokens stay the
+ones the all-on-card engine gives (in band: the CPU leg runs the same unit dots)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _pair(resident, residency="mid", graphs=True):
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.engine import DecodeEngine
+    from bloomery_b200.runtime.tiered import TieredEngine
+    spec = tiny_qwen3moe()
+    items = list(synth_tensors(spec, "cpu", seed=21))
+    full = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=1, slot_ctx=256, use_graphs=graphs)
+    tier = TieredEngine(Weights.from_items(spec, iter(items), DEV), resident, residency=residency, n_slots=1, slot_ctx=256,
+                        use_graphs=graphs)
+    return spec, full, tier
+
+
+@pytest.mark.parametrize("resident", [0, 5])
+def test_cold_experts_served_by_cpu_leg(resident):
+    spec, full, tier = _pair(resident, residency="off")
+    try:
+        g = torch.Generator().manual_seed(2)
+        prompt = torch.randint(0, spec.vocab, (21,), generator=g).tolist()
+        a = full.score(0, prompt)
+        b = tier.score(0, prompt)
+        n_last = len(prompt) % 8 or 8
+        err = ((full.logits[:n_last] - tier.logits[:n_last]).abs().max() / full.logits[:n_last].abs().max()).item()
+        assert err < 2e-2, err
+        assert sum(int(x == y) for x, y in zip(a, b)) >= len(prompt) - 2
+        st = tier.stats()
+        assert st["cold_slots_routed"] > 0 and st["cold_slots_served"] == st["cold_slots_routed"]
+        if resident == 0:
+            assert st["cold_slots_routed"] >= len(prompt) * spec.n_used * spec.n_layer      # --cpu-moe: every slot (plus warm-up passes)
+        assert (int(tier.fault) & 0xFFFFFFFF) == 0xFFFFFFFF
+        assert tier.memory_report()["experts_host"] > 0
+    finally:
+        tier.close()
+
+
+def test_promotion_lands_and_output_stays_in_band():
+    spec, full, tier = _pair(4, residency="high")
+    try:
+        g = torch.Generator().manual_seed(4)
+        prompt = torch.randint(0, spec.vocab, (40,), generator=g).tolist()
+        a = full.score(0, prompt)
+        b = tier.score(0, prompt)
+        st = tier.stats()
+        assert st["flips"] > 0 and st["bytes_promoted"] > 0
+        for il in tier.tiered.layers:                       # the device map mirrors the host's view
+            sm = tier.tiered.slot_map[il].cpu().tolist()
+            on = {e: s for e, s in enumerate(sm) if s >= 0}
+            assert on == tier.tiered.slot_of[il] and len(set(on.values())) == len(on) <= tier.tiered.n_slots
+        assert sum(int(x == y) for x, y in zip(a, b)) >= len(prompt) - 3
+        first = b[-1]
+        out = tier.decode_chain(0, first, len(prompt), 6)
+        assert len(out) == 6 and (int(tier.fault) & 0xFFFFFFFF) == 0xFFFFFFFF
+    finally:
+        tier.close()
