@@ -29,11 +29,15 @@
 
 namespace bl {
 
-constexpr int BM = 128, BN = 128, BK = 64;     // BK * 2 bytes = 128 = one swizzle atom row
+constexpr int BM = 128, BK = 64;               // BK * 2 bytes = 128 = one swizzle atom row
+// Tile width: 256 columns for a plain product (one B tile of 32 KiB per stage: 48 KiB of
+// operands feed 512 tensor-core cycles, which the L2 -> SM path sustains), 128 + 128 for the
+// dual (gate, up) product.
+constexpr int BN_SINGLE = 256, BN_DUAL = 128;
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
 constexpr int TILE_A_BYTES = BM * BK * 2;      // 16 KiB
-constexpr int TILE_B_BYTES = BN * BK * 2;      // 16 KiB
+constexpr int TILE_B128_BYTES = 128 * BK * 2;  // 16 KiB per 128 B-rows
 constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 
 struct MTile { int group, row0, row_end, pad; };
@@ -153,9 +157,11 @@ __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_b2, const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  constexpr int STAGE_BYTES = TILE_A_BYTES + (DUAL ? 2 : 1) * TILE_B_BYTES;
-  constexpr int ACC_COLS = DUAL ? 2 * BN : BN;         // TMEM columns per accumulator buffer
-  constexpr int TMEM_COLS = 2 * ACC_COLS;              // two buffers: 256 or 512 columns
+  constexpr int BN = DUAL ? BN_DUAL : BN_SINGLE;
+  constexpr int TILE_B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = TILE_A_BYTES + (DUAL ? 2 : 1) * TILE_B_BYTES;   // 48 KiB either way
+  constexpr int ACC_COLS = 256;                        // TMEM columns per accumulator buffer
+  constexpr int TMEM_COLS = 2 * ACC_COLS;              // two buffers: all 512 columns
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
@@ -409,27 +415,28 @@ int bl_gemm_bf16(const void* A, long lda, long rows_a, const void* B, const void
   {
     cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)N, (cuuint64_t)n_groups};
     cuuint64_t str[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)N};
-    cuuint32_t box[3] = {BK, BN, 1};
+    cuuint32_t box[3] = {BK, (cuuint32_t)(B2 ? BN_DUAL : BN_SINGLE), 1};
     int rc = make_map(&mb, B, 3, dims, str, box);
     if (rc) return rc;
     rc = make_map(&mb2, B2 ? B2 : B, 3, dims, str, box);
     if (rc) return rc;
   }
   GemmArgs a{};
-  a.N = N; a.K = K; a.tiles_n = (N + BN - 1) / BN;
+  a.N = N; a.K = K;
   a.mtiles = (const MTile*)mtiles; a.n_mtiles = n_mtiles; a.max_mtiles = max_mtiles;
   a.dual = B2 ? 1 : 0;
   a.c_f32 = c_f32; a.c_bf16 = (__nv_bfloat16*)c_bf16; a.ldc = ldc;
   a.dst_row = dst_row; a.row_scale = row_scale; a.resid = resid; a.ldr = ldr; a.status = status;
+  a.tiles_n = (N + (B2 ? BN_DUAL : BN_SINGLE) - 1) / (B2 ? BN_DUAL : BN_SINGLE);
   long tiles = (long)max_mtiles * a.tiles_n;
   int grid = (int)(tiles < sm_count ? tiles : sm_count);
   if (B2) {
-    const size_t smem = (size_t)STAGES * (TILE_A_BYTES + 2 * TILE_B_BYTES) + 1024;
+    const size_t smem = (size_t)STAGES * (TILE_A_BYTES + 2 * TILE_B128_BYTES) + 1024;
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); set = true; }
     return (int)launch(gemm_bf16_kernel<true>, dim3(grid), dim3(192), smem, st, ma, mb, mb2, a);
   }
-  const size_t smem = (size_t)STAGES * (TILE_A_BYTES + TILE_B_BYTES) + 1024;
+  const size_t smem = (size_t)STAGES * (TILE_A_BYTES + 2 * TILE_B128_BYTES) + 1024;
   static bool set1 = false;
   if (!set1) { cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); set1 = true; }
   return (int)launch(gemm_bf16_kernel<false>, dim3(grid), dim3(192), smem, st, ma, mb, mb2, a);

@@ -196,6 +196,37 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
   for (int i = tid; i < T_pad; i += 256) p[i] = __float2bfloat16_rn(i < n_valid ? __expf(s[i] - mx) * inv : 0.f);
 }
 
+
+// Split-precision rows for the prompt router: out[t] = [hi | hi | lo] with hi = bf16(xn) and
+// lo = bf16(xn - hi), xn = RMSNorm(x) * gain.  Against B = [Whi | Wlo | Whi] one bf16 GEMM of
+// depth 3K gives hi*Whi + hi*Wlo + lo*Whi, i.e. fp32-grade logits (the dropped lo*Wlo term is
+// ~2^-16 relative) on the tensor cores -- the reference splits hi/lo the same way for its
+// indexer scores (crates/gpu/src/indexer.rs:168).
+__global__ void __launch_bounds__(256) rmsnorm_hilo_kernel(const float* x, long x_stride, const float* gain, float eps, int K,
+                                                          __nv_bfloat16* out) {
+  __shared__ double red[8];
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const float* xr = x + (long)t * x_stride;
+  float ss = 0.f;
+  for (int i = tid; i < K; i += 256) { float v = xr[i]; ss += v * v; }
+  double tot = warp_sum_d((double)ss);
+  if ((tid & 31) == 0) red[tid >> 5] = tot;
+  __syncthreads();
+  double all = 0.0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) all += red[w];
+  const float scale = 1.0f / sqrtf((float)(all / (double)K) + eps);
+  __nv_bfloat16* o = out + (long)t * 3 * K;
+  for (int i = tid; i < K; i += 256) {
+    const float v = xr[i] * scale * gain[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    o[i] = hi; o[K + i] = hi;
+    o[2 * K + i] = __float2bfloat16_rn(v - __bfloat162float(hi));
+  }
+}
+
 }  // namespace bl
 
 using namespace bl;
@@ -251,6 +282,11 @@ int bl_kv_gather_bf16(const void* k_cache, const void* v_cache, const int* block
 int bl_softmax_causal(const float* S, long ldS, long rows, int Tq, int pos0, int T_pad, void* P, long ldP, cudaStream_t st) {
   BL_REQUIRE(rows >= 1 && Tq >= 1 && T_pad >= 1, BL_ERR_SHAPE);
   return (int)launch(softmax_causal_kernel, dim3((unsigned)rows), dim3(256), 0, st, S, ldS, Tq, pos0, T_pad, (__nv_bfloat16*)P, ldP);
+}
+
+int bl_rmsnorm_hilo(const float* x, long x_stride, const float* gain, float eps, int T, int K, void* out, cudaStream_t st) {
+  BL_REQUIRE(T >= 1 && K >= 1 && gain != nullptr, BL_ERR_SHAPE);
+  return (int)launch(rmsnorm_hilo_kernel, dim3(T), dim3(256), 0, st, x, x_stride, gain, eps, K, (__nv_bfloat16*)out);
 }
 
 }  // extern "C"

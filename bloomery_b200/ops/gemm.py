@@ -109,3 +109,16 @@ def qk_norm_rope_append_prefill(qkv, q_gain, k_gain, inv_freq, eps, q_scale, hea
                                                p(block_table), I(block_table.shape[1]), I(n_pages), p(k_cache),
                                                p(v_cache), p(q_bf16), p(fault), I(layer), stream())
     check(rc, "bl_qk_norm_rope_append_prefill")
+
+
+def rmsnorm_hilo(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out [T, 3K] bf16 = [hi | hi | lo] of RMSNorm(x) * gain (split-precision router rows)."""
+    check(cuda().bl_rmsnorm_hilo(p(x), L(x.stride(0)), p(gain), F(eps), I(x.shape[0]), I(x.shape[1]), p(out), stream()),
+          "bl_rmsnorm_hilo")
+
+
+def hilo_weights(w_f32: torch.Tensor) -> torch.Tensor:
+    """[E, K] fp32 -> [E, 3K] bf16 = [Whi | Wlo | Whi], the partner of :func:`rmsnorm_hilo`."""
+    hi = w_f32.bfloat16()
+    lo = (w_f32 - hi.float()).bfloat16()
+    return torch.cat([hi, lo, hi], 1).contiguous()

@@ -1,0 +1,73 @@
+"""Kernel micro-benchmark: each decode / prefill kernel alone at Qwen3-30B-A3B layer shapes, over a
+few layers of random weights, replayed from a CUDA graph and timed with CUDA events.
+
+    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|down|flash|gemm} [replays]
+
+It is also the small workload the ncu summaries under ``profiles/`` were captured on.
+"""
+import sys
+
+import torch
+from bloomery_b200.ops import decode as K
+from bloomery_b200.ops.decode import QWeight
+from bloomery_b200.formats.resident import resident_row_bytes
+dev = "cuda:0"
+torch.manual_seed(0)
+NL = 6
+H, QR, KVR, E, I, k = 2048, 4096, 512, 128, 768, 8
+def rw(rows, K_, t, stack=None):
+    rb = resident_row_bytes(t, K_)
+    shape = (rows, rb) if stack is None else (stack, rows, rb)
+    d = torch.randint(0, 256, shape, dtype=torch.uint8, device=dev)
+    return QWeight(d, t, K_)
+layers = []
+for l in range(NL):
+    layers.append(dict(q=rw(QR, H, "Q4_K"), k=rw(KVR, H, "Q4_K"), v=rw(KVR, H, "Q6_K"), o=rw(H, QR, "Q4_K"),
+                       r=QWeight((torch.randn(E, H, device=dev) * 0.05).view(torch.uint8).reshape(E, -1), "F32", H),
+                       g=rw(I, H, "Q4_K", E), u=rw(I, H, "Q4_K", E), d=rw(H, I, "Q6_K", E)))
+M = 1
+x = torch.randn(8, H, device=dev); gain = torch.ones(H, device=dev)
+qkv = torch.zeros(8, QR + 2 * KVR, device=dev)
+xq = torch.zeros(8, QR, dtype=torch.int8, device=dev); xds = torch.ones(8, QR // 32, 2, device=dev)
+fault = torch.full((1,), -1, dtype=torch.int32, device=dev)
+logits = torch.zeros(8, E, device=dev); ids = torch.zeros(8, k, dtype=torch.int32, device=dev); wts = torch.zeros(8, k, device=dev)
+hq = torch.zeros(8, H, dtype=torch.int8, device=dev); hds = torch.zeros(8, H // 32, 2, device=dev)
+cnt = torch.zeros(1, dtype=torch.int32, device=dev)
+actq = torch.zeros(8, k, I, dtype=torch.int8, device=dev); actds = torch.zeros(8, k, I // 32, 2, device=dev)
+which = sys.argv[1] if len(sys.argv) > 1 else "all"
+import math
+n_q, n_kv, hd, ctx = 32, 4, 128, 4096
+n_pages = ctx // 64
+kc = torch.randn(n_pages, n_kv, 64, hd, device=dev).half(); vc = torch.randn(n_pages, n_kv, 64, hd, device=dev).half()
+table = torch.arange(n_pages, dtype=torch.int32, device=dev)[None].contiguous()
+fpos = torch.tensor([ctx - 2], dtype=torch.int32, device=dev); fseq = torch.zeros(1, dtype=torch.int32, device=dev)
+fq = torch.randn(8, n_q, hd, device=dev) / math.sqrt(hd)
+n_seg = 37
+pml = torch.zeros(8 * n_q * n_seg * 2, device=dev); pacc = torch.zeros(8 * n_q * n_seg * hd, device=dev)
+if which == "gemm":
+    from bloomery_b200.ops import gemm as G
+    A = (torch.randn(4096, 2048, device=dev) * 0.1).bfloat16(); B = (torch.randn(5120, 2048, device=dev) * 0.1).bfloat16()
+    C = torch.zeros(4096, 5120, device=dev, dtype=torch.bfloat16); tt = G.TileTable.dense(4096, dev); gst = torch.zeros(1, dtype=torch.int32, device=dev)
+reps = int(sys.argv[2]) if len(sys.argv) > 2 else 4
+def chain():
+    for l in layers:
+        if which in ("all", "qkv"): K.gemv([l["q"], l["k"], l["v"]], M, qkv, x=x, gain=gain, fault=fault)
+        if which in ("all", "o"): K.gemv([l["o"]], M, x, xq=xq, xds=xds, resid=x, fault=fault)
+        if which in ("all", "router"): K.router(x, gain, 1e-6, l["r"], M, logits, hq, hds, None, fault, 0)
+        if which in ("all", "gateup"): K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0, route_logits=logits, rule=K.RouteRule(k), wts=wts)
+        if which in ("all", "flash"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
+        if which == "gemm": G.gemm_bf16(A, B, tt, out_bf16=C, status=gst)
+        if which in ("all", "down"): K.down_combine(actq, actds, ids, wts, None, l["d"], E, k, M, x, None, x, fault, 0)
+g = torch.cuda.CUDAGraph()
+s = torch.cuda.Stream()
+with torch.cuda.stream(s):
+    chain(); s.synchronize()
+    with torch.cuda.graph(g, stream=s):
+        chain()
+torch.cuda.synchronize()
+e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+for _ in range(3): g.replay()
+e0.record()
+for _ in range(reps): g.replay()
+e1.record(); torch.cuda.synchronize()
+print(which, "us per layer-chain:", e0.elapsed_time(e1) * 1000 / reps / NL)

@@ -34,6 +34,7 @@ class GemmPrefill:
         self.ubatch = ubatch
         self.score_bytes = score_bytes
         self._buf = {}
+        self._router_w = {}
         self.status = torch.zeros(1, dtype=torch.int32, device=engine.device)
         self.launches = 0
 
@@ -96,6 +97,7 @@ class GemmPrefill:
             wu = self._get("wu", (E, I_, H), bf)
             wd = self._get("wd", (E, H, I_), bf)
             logits = self._get("rl", (T, E), f32)
+            xn3 = self._get("xn3", (T, 3 * H), bf)
             ids = self._get("ids", (T, k), i32)
             wts = self._get("wts", (T, k), f32)
             counts = self._get("counts", (E,), i32)
@@ -139,8 +141,17 @@ class GemmPrefill:
             G.dequant_bf16(w.q[b + "attn_output.weight"], wo)
             G.gemm_bf16(attn, wo, dense_tiles, out_f32=x, resid=x, status=st)
             if s.layer_is_moe(il):
-                K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], T, logits, None,
-                         None, None, e.fault, il)
+                rw = w.q[b + "ffn_gate_inp.weight"]
+                if rw.qtype == "F32" and T >= 128 and E % 32 == 0:
+                    # split-precision tensor-core router: fp32-grade logits from one bf16 GEMM of depth 3K
+                    wr = self._router_w.get(il)
+                    if wr is None:
+                        wr = G.hilo_weights(rw.data.view(torch.float32).view(E, H))
+                        self._router_w[il] = wr
+                    G.rmsnorm_hilo(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn3)
+                    G.gemm_bf16(xn3, wr, dense_tiles, out_f32=logits, status=st)
+                else:
+                    K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, rw, T, logits, None, None, None, e.fault, il)
                 K.route_rows(logits, e._rule(il), T, ids, wts, e.heat[il], e.fault, il)
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
                 counts.zero_(); cursor.zero_(); dst_row.fill_(-1)

@@ -151,3 +151,21 @@ def test_gemm_prefill_matches_pass_path_in_band():
     l2_gemm = eng.logits[0].clone()
     assert ((l2_pass - l2_gemm).abs().max() / l2_pass.abs().max()).item() < 5e-2
     assert len(eng.decode_chain(1, t_gemm, len(prompt) + len(more), 4)) == 4
+
+
+def test_split_precision_router_logits_are_fp32_grade():
+    from bloomery_b200.models.cpu_ref import rms_norm
+    from bloomery_b200.ops import gemm as G
+    torch.manual_seed(6)
+    T, H, E = 300, 2048, 128
+    x = torch.randn(T, H, device=DEV) * 3
+    g = 1 + 0.1 * torch.randn(H, device=DEV)
+    W = torch.randn(E, H, device=DEV) * 0.05
+    a3 = torch.zeros(T, 3 * H, dtype=torch.bfloat16, device=DEV)
+    G.rmsnorm_hilo(x, g, 1e-6, a3)
+    logits = torch.zeros(T, E, device=DEV)
+    st = _status()
+    G.gemm_bf16(a3, G.hilo_weights(W), G.TileTable.dense(T, DEV), out_f32=logits, status=st)
+    ref = (rms_norm(x.cpu(), g.cpu(), 1e-6).double() @ W.cpu().double().T).float()
+    err = ((logits.cpu() - ref).abs().max() / ref.abs().max()).item()
+    assert err < 2e-4 and int(st) == 0, err                     # plain bf16 operands would sit near 1e-2
