@@ -183,3 +183,14 @@ def advance_rows(tokens, row_pos, row_seq, chosen, M: int, hist=None, hist_cap: 
 def swiglu_q8(gu: torch.Tensor, I_: int, M: int, actq, actds, act_f32=None) -> None:
     check(cuda().bl_swiglu_q8(p(gu), L(gu.stride(0)), I(I_), I(M), p(actq), p(actds), p(act_f32), stream()),
           "bl_swiglu_q8")
+
+
+def sample_rows(logits, V: int, M: int, params, seeds, draws, out_token, *, recent=None, n_recent=None, work=None,
+                out_n_cand=None, fault=None) -> None:
+    """The sampling chain on the card, one block per row (``csrc/sampler.cu``).
+    ``params`` fp32 [M, 8] = temperature, top_k, top_p, min_p, repeat_penalty, frequency_penalty,
+    presence_penalty, repeat_last_n; ``seeds``/``draws`` uint64-as-int64 [M]; ``recent`` int32 [M, W]."""
+    rc = cuda().bl_sample_rows(p(logits), L(logits.stride(0)), I(V), I(M), p(recent),
+                               I(recent.shape[1] if recent is not None else 0), p(n_recent), p(params), p(seeds), p(draws),
+                               p(work), p(out_token), p(out_n_cand), p(fault), stream())
+    check(rc, "bl_sample_rows")
