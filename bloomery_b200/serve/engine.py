@@ -113,8 +113,9 @@ class MockEngine(Engine):
 
     def cut(self, slot, n):
         del self.seq[slot][n:]
-        self.prompt_len[slot] = min(self.prompt_len[slot], n)
-        self.fresh[slot] = True
+        if n < self.prompt_len[slot]:           # cutting into the prompt starts a new one; dropping drafts does not
+            self.prompt_len[slot] = n
+            self.fresh[slot] = True
 
     def reset(self, slot):
         self.seq[slot] = []

@@ -105,6 +105,8 @@ class Worker(threading.Thread):
         self.rounds_by_width: Dict[int, int] = {}
         self.on_fatal = on_fatal
         self.failed: Optional[BaseException] = None
+        self.draft = None                       # runtime.speculative.NgramDraft (or another source with .propose)
+        self.width = None                       # runtime.speculative.WidthChooser
         self.actions: "queue.Queue" = queue.Queue()     # slot actions run on the engine thread
 
     # ---------------------------------------------------------------- admission
@@ -264,14 +266,36 @@ class Worker(threading.Thread):
                 return t
         return int(order[0])
 
+    def enable_drafting(self, draft, width) -> None:
+        """Turn on speculative decoding for greedy requests (``BLOOMERY_DRAFT``)."""
+        self.draft, self.width = draft, width
+
+    def _can_draft(self, a: Active) -> bool:
+        r = a.req
+        return (self.draft is not None and r.sampling.temperature <= 0 and not r.sampling.penalizes and r.constraint is None
+                and not r.logit_bias and r.n_probs == 0)
+
     def _decode_round(self) -> None:
-        rows, who = [], []
+        rows, spans = [], []                    # spans: (active, first row index, drafted ids)
         for a in self.active.values():
-            if a.pending_token is not None:
-                rows.append((a.slot.id, a.pending_token, len(a.slot.ids)))
-                who.append(a)
+            if a.pending_token is None:
+                continue
+            drafted: List[int] = []
+            if self._can_draft(a):
+                room = self.engine.slot_ctx - len(a.slot.ids) - 2
+                if a.req.n_predict >= 0:
+                    room = min(room, a.req.n_predict - len(a.generated) - 1)
+                k = self.width.choose(min(room, self.engine.max_rows - 1)) if room > 0 else 0
+                if k > 0:
+                    drafted = self.draft.propose(a.slot.ids + [a.pending_token], k)
+            base = len(a.slot.ids)
+            spans.append((a, len(rows), drafted))
+            rows.append((a.slot.id, a.pending_token, base))
+            for i, d in enumerate(drafted):
+                rows.append((a.slot.id, d, base + 1 + i))
         if not rows:
             return
+        who = [sp[0] for sp in spans]
         need_logits = any(w.req.sampling.temperature > 0 or w.req.sampling.penalizes or w.req.n_probs > 0
                           or w.req.constraint is not None or w.req.logit_bias or w.req.ignore_eos for w in who)
         t0 = time.time()
@@ -279,48 +303,73 @@ class Worker(threading.Thread):
         dt = time.time() - t0
         self.metrics.add("round_seconds_total", dt)
         self.metrics.add("n_decode_total")
-        self.metrics.add("n_busy_slots_per_decode", len(rows))
+        self.metrics.add("n_busy_slots_per_decode", len(spans))
         self.rounds_by_width[len(rows)] = self.rounds_by_width.get(len(rows), 0) + 1
+        if self.width is not None and len(spans) == 1:
+            self.width.observe_pass(len(rows), dt)
+        for a, r0, drafted in spans:
+            picks = [res[r0 + i][0] for i in range(len(drafted) + 1)]
+            kept = 0
+            if drafted:
+                from ..runtime.speculative import accept_prefix
+                kept = accept_prefix(drafted, picks)
+                a.draft_n += len(drafted)
+                a.draft_accepted += kept
+                self.metrics.add("draft_tokens_total", len(drafted))
+                self.metrics.add("draft_accepted_total", kept)
+                self.width.observe_accept(len(drafted), kept)
+                if kept < len(drafted):
+                    self.engine.cut(a.slot.id, len(a.slot.ids) + 1 + kept)     # rows of rejected drafts leave the KV
+            # the tokens this round settles: the pending one (now in the KV), then each kept draft
+            feed = [a.pending_token] + list(drafted[:kept])
+            outs = [picks[i] for i in range(kept + 1)]
+            for j, (tok_in, greedy) in enumerate(zip(feed, outs)):
+                logits = res[r0 + j][1] if j == 0 else None
+                if not self._settle(a, tok_in, greedy, logits):
+                    break
+
+    def _settle(self, a: Active, tok_in: int, greedy: int, logits: Optional[np.ndarray]) -> bool:
+        """Account one evaluated token and the token picked after it; False when the request ended."""
         tk = self.engine.tokenizer
-        for a, (slot_id, tok_in, pos), (greedy, logits) in zip(who, rows, res):
-            a.slot.ids.append(tok_in)
-            tok = self._pick(a, greedy, logits)
-            now = time.time()
-            if not a.t_first:
-                a.t_first = now
-            req = a.req
-            if req.cancelled.is_set():
-                self._finish(a, "cancelled")
-                continue
-            if tk.is_eog(tok) and not req.ignore_eos:
-                self._finish(a, "eos")
-                continue
-            a.generated.append(tok)
-            a.slot.n_decoded = len(a.generated)
-            a.text += a.decoder.push(tok)
-            hit = None
-            for s in req.stop:
-                i = a.text.find(s, max(0, a.sent - len(s)))
-                if i >= 0 and (hit is None or i < hit[0]):
-                    hit = (i, s)
-            if hit is not None:
-                a.text = a.text[:hit[0]]
-                self._finish(a, "word", hit[1])
-                continue
-            self._flush_text(a)
-            if req.constraint is not None and req.constraint.done(a.text) and req.constraint.closed(a.text):
-                self._finish(a, "eos")
-                continue
-            if 0 <= req.n_predict <= len(a.generated):
-                self._finish(a, "limit")
-                continue
-            if len(a.slot.ids) + 1 >= self.engine.slot_ctx:
-                self._finish(a, "limit")
-                continue
-            if req.t_max_predict_ms and (now - a.t_first) * 1e3 > req.t_max_predict_ms:
-                self._finish(a, "limit")
-                continue
-            a.pending_token = tok
+        a.slot.ids.append(tok_in)
+        tok = self._pick(a, greedy, logits)
+        now = time.time()
+        if not a.t_first:
+            a.t_first = now
+        req = a.req
+        if req.cancelled.is_set():
+            self._finish(a, "cancelled")
+            return False
+        if tk.is_eog(tok) and not req.ignore_eos:
+            self._finish(a, "eos")
+            return False
+        a.generated.append(tok)
+        a.slot.n_decoded = len(a.generated)
+        a.text += a.decoder.push(tok)
+        hit = None
+        for s in req.stop:
+            i = a.text.find(s, max(0, a.sent - len(s)))
+            if i >= 0 and (hit is None or i < hit[0]):
+                hit = (i, s)
+        if hit is not None:
+            a.text = a.text[:hit[0]]
+            self._finish(a, "word", hit[1])
+            return False
+        self._flush_text(a)
+        if req.constraint is not None and req.constraint.done(a.text) and req.constraint.closed(a.text):
+            self._finish(a, "eos")
+            return False
+        if 0 <= req.n_predict <= len(a.generated):
+            self._finish(a, "limit")
+            return False
+        if len(a.slot.ids) + 1 >= self.engine.slot_ctx:
+            self._finish(a, "limit")
+            return False
+        if req.t_max_predict_ms and (now - a.t_first) * 1e3 > req.t_max_predict_ms:
+            self._finish(a, "limit")
+            return False
+        a.pending_token = tok
+        return True
 
     # ---------------------------------------------------------------- loop
     def run(self) -> None:

@@ -190,3 +190,22 @@ def test_engine_failure_is_fatal():
     assert s.state.stop_event.wait(2)
     assert call(s, "/health")[0] == 503
     assert s.stop() == 70
+
+
+def test_speculative_drafts_change_passes_not_tokens():
+    """With the n-gram draft on, the echo engine's text is unchanged and several tokens settle per round."""
+    from bloomery_b200.runtime.speculative import NgramDraft, WidthChooser
+    outs = []
+    for drafting in (False, True):
+        s = Server(flags.parse(["--port", "0", "--mock"]))
+        s.start()
+        s.ready(MockEngine(n_slots=1, slot_ctx=512), ChatTemplate(), 0)
+        if drafting:
+            s.state.worker.enable_drafting(NgramDraft(), WidthChooser(max_width=7))
+        code, r = call(s, "/completion", {"prompt": "abcabcabcabc xyz abcabcabcabc xyz", "temperature": 0, "n_predict": 40})
+        outs.append((r["content"], r["timings"]["draft_n"], r["timings"]["draft_n_accepted"], s.state.worker.metrics.get("n_decode_total")))
+        s.state.stop_event.set()
+        s.stop()
+    assert outs[0][0] == outs[1][0]                      # same text
+    assert outs[0][1] == 0 and outs[1][1] > 0 and outs[1][2] > 0
+    assert outs[1][3] < outs[0][3]                       # fewer decode rounds for the same tokens

@@ -253,3 +253,21 @@ def test_board_slot_choice_and_queue():
     assert req.id == 1 and slot.busy                        # oldest first
     b.release(slot)
     assert not slot.busy
+
+
+def test_ngram_draft_and_width_chooser():
+    from bloomery_b200.runtime.speculative import NgramDraft, WidthChooser, accept_prefix
+    d = NgramDraft(max_n=3)
+    assert d.propose([1, 2, 3, 4, 9, 1, 2, 3], 3) == [4, 9, 1]
+    assert d.propose([5, 6, 7], 4) == []
+    assert accept_prefix([4, 9, 1], [4, 9, 7, 3]) == 2 and accept_prefix([4], [5, 0]) == 0
+    w = WidthChooser(max_width=4)
+    for _ in range(30):
+        w.observe_pass(1, 1.0); w.observe_pass(5, 1.1)
+        w.observe_accept(4, 4)
+    assert w.choose(4) == 4                              # high acceptance, cheap rows: draft wide
+    w2 = WidthChooser(max_width=4)
+    for _ in range(30):
+        w2.observe_pass(1, 1.0); w2.observe_pass(2, 1.9); w2.observe_pass(5, 4.5)
+        w2.observe_accept(4, 0)
+    assert w2.choose(4) == 0                             # nothing is ever accepted: plain steps
