@@ -42,6 +42,8 @@ float row_dot_any(int wtype, const uint8_t* row, int K, const int8_t* xq, const 
     case WT_Q5_K: return row_dot_scalar<Q5K>(row, K, xq, xds);
     case WT_Q6_K: return row_dot_scalar<Q6K>(row, K, xq, xds);
     case WT_Q8_0: return row_dot_scalar<Q80>(row, K, xq, xds);
+    case WT_NVFP4: return row_dot_scalar<NvFp4>(row, K, xq, xds);
+    case WT_FP8_B128: return row_dot_scalar<Fp8B128>(row, K, xq, xds);
   }
   return NAN;
 }
@@ -89,7 +91,7 @@ void blh_act_q8(const float* x, int M, int K, int8_t* codes, float* ds) {
 int blh_gemv(int wtype, const uint8_t* w, int rows, int K, const int8_t* xq, const float* xds, int M, float* out,
              long out_stride) {
   long rb = resident_row_bytes(wtype, K);
-  if (rb <= 0 || K % 256) return -1;
+  if (rb <= 0 || K % 64) return -1;
   blh::Pool::instance().parallel_for(rows, 64, [&](int r0, int r1) {
     for (int r = r0; r < r1; ++r)
       for (int m = 0; m < M; ++m)
@@ -109,6 +111,8 @@ int blh_decode_rows(int wtype, const uint8_t* w, int rows, int K, float* out) {
       case WT_Q5_K: row_decode<Q5K>(row, K, o); break;
       case WT_Q6_K: row_decode<Q6K>(row, K, o); break;
       case WT_Q8_0: row_decode<Q80>(row, K, o); break;
+      case WT_NVFP4: row_decode<NvFp4>(row, K, o); break;
+      case WT_FP8_B128: row_decode<Fp8B128>(row, K, o); break;
       default: return -1;
     }
   }

@@ -34,6 +34,8 @@ enum WType : int {
   WT_Q5_K = 13,
   WT_Q6_K = 14,
   WT_BF16 = 30,
+  WT_NVFP4 = 40,     // resident rows: K/2 code bytes, K/16 e4m3 scales, f32 tensor scale, pad to 16
+  WT_FP8_B128 = 41,  // resident rows: K e4m3 codes, K/128 f32 scales (the 128x128 block scale, per row), pad to 16
 };
 
 struct u32x4 { uint32_t x, y, z, w; };
@@ -370,6 +372,140 @@ struct Q80 {
 };
 
 
+
+// ---------------------------------------------------------------------------------
+// E4M3 and E2M1 scalar decoders (host and device)
+// ---------------------------------------------------------------------------------
+BL_HD float e4m3_to_float(uint8_t b) {
+  const int s = b >> 7, e = (b >> 3) & 15, m = b & 7;
+  float v;
+  if (e == 0) v = (float)m * 0.001953125f;                 // subnormal: m * 2^-9
+  else if (e == 15 && m == 7) v = __builtin_nanf("");        // the one NaN encoding (no infinities)
+  else {
+    uint32_t bits = (uint32_t)(e + 120) << 23 | (uint32_t)m << 20;   // 2^(e-7) * (1 + m/8)
+    __builtin_memcpy(&v, &bits, 4);
+  }
+  return s ? -v : v;
+}
+
+
+// four E4M3 bytes of one word -> four floats (the hardware converter on the device)
+BL_HD void e4m3x4_to_float(uint32_t w, float* o) {
+#if defined(__CUDA_ARCH__)
+  uint32_t h0, h1;
+  asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %2; cvt.rn.f16x2.e4m3x2 %0, lo; cvt.rn.f16x2.e4m3x2 %1, hi; }"
+      : "=r"(h0), "=r"(h1) : "r"(w));
+  const __half2 a = *reinterpret_cast<__half2*>(&h0), b = *reinterpret_cast<__half2*>(&h1);
+  const float2 fa = __half22float2(a), fb = __half22float2(b);
+  o[0] = fa.x; o[1] = fa.y; o[2] = fb.x; o[3] = fb.y;
+#else
+  for (int b = 0; b < 4; ++b) o[b] = e4m3_to_float((uint8_t)(w >> (8 * b)));
+#endif
+}
+
+// two E2M1 magnitudes per lookup: code & 7 -> {0, 0.5, 1, 1.5, 2, 3, 4, 6} * 2
+BL_HD int e2m1_x2(uint32_t code) {
+  const int mag = (int)((0x0C08060403020100ull >> (8 * (code & 7))) & 0xFF);
+  return (code & 8) ? -mag : mag;
+}
+
+// ---------------------------------------------------------------------------------
+// NVFP4: 16-value groups, E2M1 codes (low nibble first), E4M3 group scale, f32 tensor scale.
+// Codes are doubled to small integers and dotted with the q8 activations (the reference
+// runs NVFP4 experts on int8 activations too: crates/gpu/src/gemm/gemm32.rs, gemm_nvfp4p).
+// ---------------------------------------------------------------------------------
+struct NvFp4 {
+  static constexpr int kType = WT_NVFP4;
+  struct Regs { u32x4 q0, q1; uint32_t sc; float g; };
+  static BL_HD long row_bytes(int K) { return (((long)K / 2 + K / 16 + 4) + 15) / 16 * 16; }
+  static BL_HD void load(const uint8_t* row, int u, int K, Regs& r) {
+    r.q0 = ld128(row + 32 * u);
+    r.q1 = ld128(row + 32 * u + 16);
+    r.sc = ld32(row + K / 2 + 4 * u);
+    uint32_t gb = ld32(row + K / 2 + K / 16);
+    __builtin_memcpy(&r.g, &gb, 4);
+  }
+  // eight nibbles of one word -> two words of int8 (values x2)
+  static BL_HD void expand(uint32_t w, uint32_t& lo4, uint32_t& hi4) {
+    lo4 = 0; hi4 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo4 |= (uint32_t)(uint8_t)e2m1_x2((w >> (4 * i)) & 0xF) << (8 * i);
+      hi4 |= (uint32_t)(uint8_t)e2m1_x2((w >> (16 + 4 * i)) & 0xF) << (8 * i);
+    }
+  }
+  static BL_HD float dot(const Regs& r, const uint32_t* aq /*16 words*/, const float* ad /*d of the two 32-blocks*/) {
+    const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {                 // group g: values 16g..16g+15 = words 2g, 2g+1 of codes
+      int s = 0;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t lo4, hi4;
+        expand(w[2 * g + h], lo4, hi4);
+        s = dot4(lo4, aq[4 * g + 2 * h], s);
+        s = dot4(hi4, aq[4 * g + 2 * h + 1], s);
+      }
+      acc += e4m3_to_float((uint8_t)(r.sc >> (8 * g))) * ad[g >> 1] * (float)s;
+    }
+    return acc * r.g * 0.5f;
+  }
+  static BL_HD void decode(const Regs& r, float* out) {
+    const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const float sc = e4m3_to_float((uint8_t)(r.sc >> (8 * g))) * r.g * 0.5f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) out[16 * g + i] = sc * (float)e2m1_x2((w[2 * g + i / 8] >> (4 * (i & 7))) & 0xF);
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------
+// FP8 block-scaled (E4M3 codes, one f32 scale per 128 values of the row)
+// ---------------------------------------------------------------------------------
+struct Fp8B128 {
+  static constexpr int kType = WT_FP8_B128;
+  struct Regs { u32x4 q[4]; float sc; };
+  static BL_HD long row_bytes(int K) { return (((long)K + K / 32) + 15) / 16 * 16; }
+  static BL_HD void load(const uint8_t* row, int u, int K, Regs& r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.q[i] = ld128(row + 64 * u + 16 * i);
+    uint32_t sb = ld32(row + K + 4 * (u >> 1));
+    __builtin_memcpy(&r.sc, &sb, 4);
+  }
+  static BL_HD float dot(const Regs& r, const uint32_t* aq, const float* ad) {
+    float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w[4] = {r.q[i].x, r.q[i].y, r.q[i].z, r.q[i].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+      {
+        float wv[4];
+        e4m3x4_to_float(w[k], wv);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const float xv = (float)(int8_t)((aq[4 * i + k] >> (8 * b)) & 0xFF);
+          if (i < 2) acc0 = wv[b] * xv + acc0; else acc1 = wv[b] * xv + acc1;
+        }
+      }
+    }
+    return r.sc * (ad[0] * acc0 + ad[1] * acc1);
+  }
+  static BL_HD void decode(const Regs& r, float* out) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w[4] = {r.q[i].x, r.q[i].y, r.q[i].z, r.q[i].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) out[16 * i + 4 * k + b] = r.sc * e4m3_to_float((uint8_t)(w[k] >> (8 * b)));
+    }
+  }
+};
+
 // ---------------------------------------------------------------------------------
 // Uniform interface used by the templated kernels:
 //   T::loadu(row, u, K, regs)                     fetch unit u of a weight row
@@ -421,6 +557,27 @@ template <> struct Unit<Q80> {
   static BL_HD int pos(int u, int e) { return 64 * u + e; }
 };
 
+
+template <> struct Unit<NvFp4> {
+  using Regs = NvFp4::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int K, Regs& r) { NvFp4::load(row, u, K, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    const float ad[2] = {xds[2 * u].x, xds[2 * u + 1].x};
+    return NvFp4::dot(r, xq + 16 * u, ad);
+  }
+  static BL_HD void decodeu(const Regs& r, int, float* o) { NvFp4::decode(r, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
+template <> struct Unit<Fp8B128> {
+  using Regs = Fp8B128::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int K, Regs& r) { Fp8B128::load(row, u, K, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    const float ad[2] = {xds[2 * u].x, xds[2 * u + 1].x};
+    return Fp8B128::dot(r, xq + 16 * u, ad);
+  }
+  static BL_HD void decodeu(const Regs& r, int, float* o) { Fp8B128::decode(r, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
 
 // ---------------------------------------------------------------------------------
 // Activation registers of one unit: 16 code words and up to four {d, s} pairs, fetched
@@ -481,6 +638,23 @@ template <> struct ActOf<Q6K> {
   }
 };
 
+template <> struct ActOf<NvFp4> {
+  static BL_HD void load(const uint32_t* xq, const F2* xds, int u, ActRegs& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ld_act128(xq + 16 * u + 4 * i, a.q + 4 * i);
+    a.d[0] = xds[2 * u].x; a.d[1] = xds[2 * u + 1].x;
+  }
+  static BL_HD float dot(const NvFp4::Regs& r, int, const ActRegs& a) { return NvFp4::dot(r, a.q, a.d); }
+};
+template <> struct ActOf<Fp8B128> {
+  static BL_HD void load(const uint32_t* xq, const F2* xds, int u, ActRegs& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ld_act128(xq + 16 * u + 4 * i, a.q + 4 * i);
+    a.d[0] = xds[2 * u].x; a.d[1] = xds[2 * u + 1].x;
+  }
+  static BL_HD float dot(const Fp8B128::Regs& r, int, const ActRegs& a) { return Fp8B128::dot(r, a.q, a.d); }
+};
+
 // Resident row size for a weight type and row length.
 BL_HD long resident_row_bytes(int wtype, int K) {
   switch (wtype) {
@@ -488,6 +662,8 @@ BL_HD long resident_row_bytes(int wtype, int K) {
     case WT_Q5_K: return Q5K::row_bytes(K);
     case WT_Q6_K: return Q6K::row_bytes(K);
     case WT_Q8_0: return Q80::row_bytes(K);
+    case WT_NVFP4: return NvFp4::row_bytes(K);
+    case WT_FP8_B128: return Fp8B128::row_bytes(K);
     case WT_F32: return 4L * K;
     case WT_F16: case WT_BF16: return 2L * K;
   }

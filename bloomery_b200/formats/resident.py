@@ -8,6 +8,7 @@ Values are never re-quantised on load; some block types are only re-laid so that
   Q6_K                210-byte file blocks padded to 224: ql[128] qh[64] sc[16] d pad[14]
   Q8_0                per row: K int8 codes, then K/32 f16 scales, padded to 16 bytes
   F32 / F16 / BF16    unchanged
+  NVFP4, FP8_B128     rows built from checkpoint planes by ``formats/planes.py``
 
 Works on CPU and CUDA tensors (the repack of a 30 B-parameter model runs on the card).
 """
@@ -20,8 +21,9 @@ import torch
 from .quant import QTYPES
 
 # weight-type ids shared with csrc/quant_units.cuh (equal to the ggml ids)
-WT = {"F32": 0, "F16": 1, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30}
-INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0")
+WT = {"F32": 0, "F16": 1, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30, "NVFP4": 40, "FP8_B128": 41}
+INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0", "NVFP4", "FP8_B128")      # dotted against q8 activations
+PLANE_TYPES = ("NVFP4", "FP8_B128")
 FLOAT_TYPES = ("F32", "F16", "BF16")
 
 
@@ -42,7 +44,25 @@ def resident_row_bytes(qtype: str, k: int) -> int:
         return 4 * k
     if qtype in ("F16", "BF16"):
         return 2 * k
+    if qtype == "NVFP4":
+        return (k // 2 + k // 16 + 4 + 15) // 16 * 16
+    if qtype == "FP8_B128":
+        return (k + k // 32 + 15) // 16 * 16
     raise UnsupportedType(f"no resident layout for block type {qtype}")
+
+
+def quantize_resident(w: torch.Tensor, qtype: str) -> Tuple[torch.Tensor, torch.Tensor]:
+    """f32 [rows, K] -> (resident rows, the f32 values those rows decode to).  Fixtures and tests."""
+    from . import planes, quant
+    k = w.shape[-1]
+    if qtype == "NVFP4":
+        res = planes.nvfp4_resident(*planes.nvfp4_quantize(w))
+        return res, planes.resident_dequantize(res, qtype, k)
+    if qtype == "FP8_B128":
+        res = planes.fp8_b128_resident(*planes.fp8_b128_quantize(w))
+        return res, planes.resident_dequantize(res, qtype, k)
+    raw = quant.quantize(w, qtype)
+    return to_resident(raw, qtype, k), quant.dequantize(raw, qtype, k)
 
 
 def to_resident(raw: torch.Tensor, qtype: str, k: int) -> torch.Tensor:

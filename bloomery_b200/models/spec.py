@@ -124,6 +124,64 @@ class ModelSpec:
             )
         raise ValueError(f"architecture {arch!r} has no seat in this build")
 
+    @classmethod
+    def from_hf_config(cls, c: Dict[str, Any]) -> "ModelSpec":
+        """config.json of a checkpoint folder (the reference: ``crates/hf``, ``crates/model-hf``)."""
+        archs = c.get("architectures") or [""]
+        kind = str(c.get("model_type") or archs[0]).lower()
+        n_q = int(c["num_attention_heads"])
+        hidden = int(c["hidden_size"])
+        common = dict(
+            name=str(c.get("_name_or_path", "") or kind), n_layer=int(c["num_hidden_layers"]), hidden=hidden, n_q=n_q,
+            vocab=int(c["vocab_size"]), ctx_train=int(c.get("max_position_embeddings", 32768)),
+            rms_eps=float(c.get("rms_norm_eps", 1e-6)), rope_theta=float(c.get("rope_theta", 1e4)),
+            bos_id=int(c.get("bos_token_id", -1) if c.get("bos_token_id") is not None else -1),
+            eos_id=int(c["eos_token_id"][0] if isinstance(c.get("eos_token_id"), list) else (c.get("eos_token_id", -1) if c.get("eos_token_id") is not None else -1)),
+        )
+        if "deepseek" in kind or "kimi" in kind:
+            rope, nope = int(c.get("qk_rope_head_dim", 64)), int(c.get("qk_nope_head_dim", 128))
+            n_sh = int(c.get("n_shared_experts", 0) or 0)
+            return cls(arch="deepseek2", n_kv=n_q, head_dim=rope + nope, qk_norm=False,
+                       dense_inter=int(c.get("intermediate_size", 0)), n_expert=int(c.get("n_routed_experts", 0) or 0),
+                       n_used=int(c.get("num_experts_per_tok", 0) or 0), moe_inter=int(c.get("moe_intermediate_size", 0) or 0),
+                       n_shared=n_sh, shared_inter=n_sh * int(c.get("moe_intermediate_size", 0) or 0),
+                       first_dense=int(c.get("first_k_dense_replace", 0) or 0),
+                       router_mode="sigmoid" if c.get("scoring_func", "softmax") == "sigmoid" else "softmax",
+                       router_renorm=bool(c.get("norm_topk_prob", False)), router_scale=float(c.get("routed_scaling_factor", 1.0)),
+                       n_group=int(c.get("n_group", 1) or 1), topk_group=int(c.get("topk_group", 1) or 1), mla=True,
+                       q_lora=int(c.get("q_lora_rank") or 0), kv_lora=int(c.get("kv_lora_rank", 512)), rope_dim=rope,
+                       nope_dim=nope, v_dim=int(c.get("v_head_dim", 128)), n_mtp=int(c.get("num_nextn_predict_layers", 0) or 0),
+                       **common)
+        if kind in ("qwen3_moe", "qwen3moe", "qwen3moeforcausallm", "qwen3", "llama", "qwen2", "mistral", "qwen3forcausallm"):
+            n_exp = int(c.get("num_experts", 0) or 0)
+            return cls(arch="qwen3moe" if n_exp else ("qwen3" if "qwen3" in kind else "llama"),
+                       n_kv=int(c.get("num_key_value_heads", n_q)), head_dim=int(c.get("head_dim") or hidden // n_q),
+                       qk_norm="qwen3" in kind, dense_inter=int(c.get("intermediate_size", 0) or 0), n_expert=n_exp,
+                       n_used=int(c.get("num_experts_per_tok", 0) or 0), moe_inter=int(c.get("moe_intermediate_size", 0) or 0),
+                       router_mode="softmax", router_renorm=bool(c.get("norm_topk_prob", True)), **common)
+        raise ValueError(f"model type {kind!r} has no seat in this build")
+
+    def to_hf_config(self) -> Dict[str, Any]:
+        """The config.json this spec would be read back from (fixtures)."""
+        if self.mla:
+            return {"model_type": "deepseek_v3", "architectures": ["DeepseekV3ForCausalLM"], "num_hidden_layers": self.n_layer,
+                    "hidden_size": self.hidden, "num_attention_heads": self.n_q, "vocab_size": self.vocab,
+                    "max_position_embeddings": self.ctx_train, "rms_norm_eps": self.rms_eps, "rope_theta": self.rope_theta,
+                    "qk_rope_head_dim": self.rope_dim, "qk_nope_head_dim": self.nope_dim, "v_head_dim": self.v_dim,
+                    "q_lora_rank": self.q_lora or None, "kv_lora_rank": self.kv_lora, "intermediate_size": self.dense_inter,
+                    "n_routed_experts": self.n_expert, "num_experts_per_tok": self.n_used,
+                    "moe_intermediate_size": self.moe_inter, "n_shared_experts": self.n_shared,
+                    "first_k_dense_replace": self.first_dense, "scoring_func": self.router_mode,
+                    "norm_topk_prob": self.router_renorm, "routed_scaling_factor": self.router_scale,
+                    "n_group": self.n_group, "topk_group": self.topk_group, "num_nextn_predict_layers": self.n_mtp}
+        return {"model_type": "qwen3_moe" if self.is_moe else ("qwen3" if self.qk_norm else "llama"),
+                "architectures": ["Qwen3MoeForCausalLM" if self.is_moe else "Qwen3ForCausalLM"],
+                "num_hidden_layers": self.n_layer, "hidden_size": self.hidden, "num_attention_heads": self.n_q,
+                "num_key_value_heads": self.n_kv, "head_dim": self.head_dim, "vocab_size": self.vocab,
+                "max_position_embeddings": self.ctx_train, "rms_norm_eps": self.rms_eps, "rope_theta": self.rope_theta,
+                "intermediate_size": self.dense_inter, "num_experts": self.n_expert, "num_experts_per_tok": self.n_used,
+                "moe_intermediate_size": self.moe_inter, "norm_topk_prob": self.router_renorm}
+
 
 # The named benchmark / test shapes.
 def tiny_qwen3moe() -> ModelSpec:

@@ -20,7 +20,7 @@ import torch
 
 from ..formats import quant
 from ..formats.gguf import Gguf, GgufWriter
-from ..formats.resident import FLOAT_TYPES, INT_DOT_TYPES, UnsupportedType, to_resident
+from ..formats.resident import FLOAT_TYPES, INT_DOT_TYPES, PLANE_TYPES, UnsupportedType, quantize_resident, to_resident
 from ..ops.decode import QWeight
 from .spec import ModelSpec
 
@@ -65,6 +65,8 @@ def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K
             w = torch.ones(*shape, device=device) + _rand(shape, 0.02, gen, device)
         else:
             w = _rand(shape, std_, gen, device)
+        if t in PLANE_TYPES:                      # block-scaled float types travel as resident rows
+            return (name, tuple(shape), t, quantize_resident(w.reshape(-1, shape[-1]), t)[0])
         raw = quant.quantize(w.reshape(-1, shape[-1]), t)
         return (name, tuple(shape), t, raw)
 
@@ -149,7 +151,8 @@ class Weights:
             return
         if qtype not in INT_DOT_TYPES and qtype not in FLOAT_TYPES:
             raise UnsupportedType(f"{name}: block type {qtype} has no kernel in this build")
-        res = to_resident(raw.reshape(-1, raw.shape[-1]), qtype, k)
+        flat = raw.reshape(-1, raw.shape[-1])
+        res = flat.contiguous() if qtype in PLANE_TYPES else to_resident(flat, qtype, k)
         if len(shape) == 3:
             res = res.reshape(shape[0], shape[1], -1)
         self.q[name] = QWeight(res, qtype, k)
@@ -169,6 +172,9 @@ class Weights:
             return self.f[name].float()
         qw = self.q[name]
         flat = qw.data.reshape(-1, qw.data.shape[-1])
+        if qw.qtype in PLANE_TYPES:
+            from ..formats.planes import resident_dequantize
+            return resident_dequantize(flat, qw.qtype, qw.k).reshape(*qw.data.shape[:-1], qw.k)
         raw = from_resident(flat, qw.qtype, qw.k)
         out = quant.dequantize(raw, qw.qtype, qw.k)
         return out.reshape(*qw.data.shape[:-1], qw.k)
@@ -220,3 +226,147 @@ def load_gguf(path: str, device, ring_bytes: int = 256 << 20) -> Tuple[ModelSpec
     if use_ring:
         torch.cuda.synchronize(dev)
     return spec, w, g
+
+
+# ------------------------------------------------------------------------------------
+# Checkpoint folders (safetensors + config.json)
+# ------------------------------------------------------------------------------------
+_HF_LAYER = {
+    "input_layernorm.weight": "attn_norm.weight", "post_attention_layernorm.weight": "ffn_norm.weight",
+    "self_attn.q_proj": "attn_q", "self_attn.k_proj": "attn_k", "self_attn.v_proj": "attn_v",
+    "self_attn.o_proj": "attn_output", "self_attn.q_norm.weight": "attn_q_norm.weight",
+    "self_attn.k_norm.weight": "attn_k_norm.weight",
+    "self_attn.q_a_proj": "attn_q_a", "self_attn.q_a_layernorm.weight": "attn_q_a_norm.weight",
+    "self_attn.q_b_proj": "attn_q_b", "self_attn.kv_a_proj_with_mqa": "attn_kv_a_mqa",
+    "self_attn.kv_a_layernorm.weight": "attn_kv_a_norm.weight", "self_attn.kv_b_proj": "attn_kv_b",
+    "mlp.gate_proj": "ffn_gate", "mlp.up_proj": "ffn_up", "mlp.down_proj": "ffn_down",
+    "mlp.shared_experts.gate_proj": "ffn_gate_shexp", "mlp.shared_experts.up_proj": "ffn_up_shexp",
+    "mlp.shared_experts.down_proj": "ffn_down_shexp",
+    "mlp.gate.weight": "ffn_gate_inp.weight", "mlp.gate.e_score_correction_bias": "exp_probs_b.bias",
+}
+_HF_TOP = {"model.embed_tokens": "token_embd", "model.norm.weight": "output_norm.weight", "lm_head": "output"}
+
+
+def folder_items(folder, spec: ModelSpec) -> Iterator[TensorItem]:
+    """Tensors of a checkpoint folder under the GGUF names, quantised layers as resident rows.
+
+    Per-expert matrices are stacked into ``ffn_{gate,up,down}_exps``; norms, the router and its
+    selection bias become F32 (the reference reads folders through the same part names:
+    ``crates/gpu/src/folder.rs``, ``crates/hf/src/modelopt.rs``)."""
+    from ..formats import planes
+    scheme = planes.detect_scheme(folder.config)
+
+    def f32_item(src: str, dst: str) -> TensorItem:
+        t = folder.tensor(src).float().contiguous()
+        shape = tuple(t.shape)
+        return (dst, shape, "F32", t.reshape(-1, shape[-1]).view(torch.uint8))
+
+    def linear(stem: str, dst: str) -> TensorItem:
+        res, ty, k = planes.linear_resident(folder, stem, scheme)
+        return (dst + ".weight", (res.shape[0], k), ty, res)
+
+    yield linear("model.embed_tokens", "token_embd")
+    for il in range(spec.n_layer + spec.n_mtp):
+        hp, b = f"model.layers.{il}.", f"blk.{il}."
+        for src, dst in _HF_LAYER.items():
+            if src.endswith(".weight") or src.endswith("_bias"):
+                if hp + src in folder:
+                    yield f32_item(hp + src, b + dst)
+            elif any((hp + src + sfx) in folder for sfx in (".weight", ".weight_packed")):
+                yield linear(hp + src, b + dst)
+        if (hp + "mlp.experts.0.gate_proj.weight") in folder or (hp + "mlp.experts.0.gate_proj.weight_packed") in folder:
+            for proj, dst in (("gate_proj", "ffn_gate_exps"), ("up_proj", "ffn_up_exps"), ("down_proj", "ffn_down_exps")):
+                parts, ty, k = [], None, 0
+                for e in range(spec.n_expert):
+                    res, t1, k = planes.linear_resident(folder, f"{hp}mlp.experts.{e}.{proj}", scheme)
+                    if ty not in (None, t1):
+                        raise UnsupportedType(f"{hp}{proj}: experts of mixed types {ty} / {t1}")
+                    ty = t1
+                    parts.append(res)
+                stack = torch.stack(parts, 0)
+                yield (b + dst + ".weight", (spec.n_expert, stack.shape[1], k), ty, stack.reshape(-1, stack.shape[-1]))
+    yield f32_item("model.norm.weight", "output_norm.weight")
+    if "lm_head.weight" in folder:
+        yield linear("lm_head", "output")
+
+
+def load_folder(path: str, device) -> Tuple[ModelSpec, "Weights", object]:
+    from ..formats.safetensors import Folder
+    folder = Folder(path)
+    spec = ModelSpec.from_hf_config(folder.config)
+    w = Weights.from_items(spec, folder_items(folder, spec), device)
+    if torch.device(device).type == "cuda":
+        torch.cuda.synchronize(device)
+    return spec, w, folder
+
+
+def open_model(path: str, device, **kw):
+    """A path opens as a GGUF file (or first shard of a split) or as a checkpoint folder
+    (the reference's ``model_file``: ``crates/model-hf/src/lib.rs:1-12``)."""
+    import os
+    if os.path.isdir(path):
+        return load_folder(path, device)
+    return load_gguf(path, device, **kw)
+
+
+def write_folder(spec: ModelSpec, path: str, scheme: str = "fp8_b128", seed: int = 0, std: float = 0.02, shards: int = 2) -> None:
+    """Seeded synthetic checkpoint folder in one of the stored quantisation schemes (fixtures)."""
+    from ..formats import planes
+    from ..formats import safetensors as S
+    gen = torch.Generator().manual_seed(seed)
+    tensors: Dict[str, torch.Tensor] = {}
+    tags: Dict[str, str] = {}
+
+    def lin(stem: str, rows: int, k: int, quant_it: bool = True):
+        w = torch.randn(rows, k, generator=gen) * std
+        if not quant_it or scheme == "plain":
+            tensors[stem + ".weight"] = w.bfloat16()
+        elif scheme == "fp8_b128":
+            c, sc = planes.fp8_b128_quantize(w)
+            tensors[stem + ".weight"], tensors[stem + ".weight_scale_inv"] = c, sc
+            tags[stem + ".weight"] = "F8_E4M3"
+        else:
+            pk, sc, ts = planes.nvfp4_quantize(w)
+            tags[stem + ".weight_scale"] = "F8_E4M3"
+            tensors[stem + ".weight_scale"] = sc
+            if scheme == "nvfp4_modelopt":
+                tensors[stem + ".weight"], tensors[stem + ".weight_scale_2"] = pk, ts.reshape(())
+                tensors[stem + ".input_scale"] = torch.tensor(1.0)          # stored by ModelOpt; read and ignored
+            else:
+                tensors[stem + ".weight_packed"], tensors[stem + ".weight_global_scale"] = pk, (1.0 / ts).reshape(1)
+
+    def norm(name: str, n: int):
+        tensors[name] = (torch.ones(n) + 0.02 * torch.randn(n, generator=gen)).bfloat16()
+
+    H = spec.hidden
+    lin("model.embed_tokens", spec.vocab, H, quant_it=False)
+    for il in range(spec.n_layer):
+        hp = f"model.layers.{il}."
+        norm(hp + "input_layernorm.weight", H)
+        norm(hp + "post_attention_layernorm.weight", H)
+        lin(hp + "self_attn.q_proj", spec.q_rows, H)
+        lin(hp + "self_attn.k_proj", spec.kv_rows, H)
+        lin(hp + "self_attn.v_proj", spec.kv_rows, H)
+        lin(hp + "self_attn.o_proj", H, spec.q_rows)
+        if spec.qk_norm:
+            norm(hp + "self_attn.q_norm.weight", spec.head_dim)
+            norm(hp + "self_attn.k_norm.weight", spec.head_dim)
+        if spec.layer_is_moe(il):
+            tensors[hp + "mlp.gate.weight"] = (torch.randn(spec.n_expert, H, generator=gen) * std).bfloat16()
+            for e in range(spec.n_expert):
+                lin(f"{hp}mlp.experts.{e}.gate_proj", spec.moe_inter, H)
+                lin(f"{hp}mlp.experts.{e}.up_proj", spec.moe_inter, H)
+                lin(f"{hp}mlp.experts.{e}.down_proj", H, spec.moe_inter)
+        else:
+            lin(hp + "mlp.gate_proj", spec.dense_inter, H)
+            lin(hp + "mlp.up_proj", spec.dense_inter, H)
+            lin(hp + "mlp.down_proj", H, spec.dense_inter)
+    norm("model.norm.weight", H)
+    lin("lm_head", spec.vocab, H, quant_it=False)
+    qc = {"fp8_b128": {"quant_method": "fp8", "weight_block_size": [128, 128]},
+          "nvfp4_modelopt": {"quant_method": "modelopt", "quant_algo": "NVFP4"},
+          "nvfp4_ct": {"quant_method": "compressed-tensors", "format": "nvfp4-pack-quantized"}}.get(scheme)
+    cfg = spec.to_hf_config()
+    if qc:
+        cfg["quantization_config"] = qc
+    S.write_folder(path, tensors, cfg, shards=shards, dtypes=tags)

@@ -148,6 +148,94 @@ def test_resident_roundtrip_and_host_units(t):
     assert torch.equal(out, H.gemv(res, t, K, codes, ds))       # bit-identical rerun
 
 
+@pytest.mark.parametrize("t", ["NVFP4", "FP8_B128"])
+def test_plane_types_host_units(t):
+    from bloomery_b200.formats.resident import quantize_resident
+    torch.manual_seed(5)
+    K = 1024
+    w = torch.randn(24, K) * 0.02
+    w[3, 100] = 1.5
+    res, wd = quantize_resident(w, t)
+    assert res.shape[1] == resident_row_bytes(t, K) and res.shape[1] % 16 == 0
+    assert ((wd - w).pow(2).mean().sqrt() / w.pow(2).mean().sqrt()).item() < (0.15 if t == "NVFP4" else 0.04)
+    assert torch.equal(H.decode_rows(res, t, K), wd)            # unit decode is exact
+    x = torch.randn(3, K)
+    x[1, 5] = 40.0
+    codes, ds = H.act_q8(x)
+    ref = (Q.dequantize_act_q8(codes, ds).double() @ wd.double().T).float()
+    out = H.gemv(res, t, K, codes, ds)
+    assert ((out - ref).abs().max() / ref.abs().max()).item() < 1e-5
+    assert torch.equal(out, H.gemv(res, t, K, codes, ds))
+
+
+def test_e4m3_and_plane_refusals():
+    from bloomery_b200.formats import planes as P
+    c = torch.arange(256, dtype=torch.uint8)
+    ref = c.view(torch.float8_e4m3fn).float()
+    v = P.e4m3_decode(c)
+    ok = ~torch.isnan(ref)
+    assert torch.equal(v[ok], ref[ok]) and torch.isnan(v[~ok]).all()
+    x = torch.randn(4096) * 60
+    assert torch.equal(P.e4m3_encode(x), x.clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8))
+    codes, sc = P.fp8_b128_quantize(torch.randn(130, 256))
+    bad = codes.clone(); bad[0, 0] = 0x7F
+    with pytest.raises(P.PlaneError):
+        P.fp8_b128_resident(bad, sc)
+    bads = sc.clone(); bads[0, 0] = float("inf")
+    with pytest.raises(P.PlaneError):
+        P.fp8_b128_resident(codes, bads)
+    with pytest.raises(P.PlaneError):
+        P.fp8_b128_resident(codes[:, :192], sc)
+    pk, s, t = P.nvfp4_quantize(torch.randn(8, 128))
+    with pytest.raises(P.PlaneError):
+        P.nvfp4_resident(pk, s[:, :4], t)
+    # a compressed-tensors divisor and a ModelOpt multiplier describe the same values
+    a = P.nvfp4_resident(pk, s, t)
+    assert torch.equal(P.resident_dequantize(a, "NVFP4", 128), P.nvfp4_dequantize(pk, s, t))
+
+
+def test_safetensors_folder(tmp_path):
+    from bloomery_b200.formats import planes as P
+    from bloomery_b200.formats import safetensors as S
+    torch.manual_seed(6)
+    w = torch.randn(130, 256)
+    codes, sc = P.fp8_b128_quantize(w)
+    pk, s, t = P.nvfp4_quantize(w[:, :128].contiguous())
+    tensors = {"a.weight": codes, "a.weight_scale_inv": sc, "b.weight_packed": pk, "b.weight_scale": s,
+               "b.weight_global_scale": (1.0 / t).reshape(1), "n.weight": torch.randn(256).bfloat16()}
+    tags = {"a.weight": "F8_E4M3", "b.weight_scale": "F8_E4M3"}
+    S.write_folder(str(tmp_path / "m"), tensors, {"quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}},
+                   shards=3, dtypes=tags)
+    f = S.Folder(str(tmp_path / "m"))
+    assert set(f.names()) == set(tensors) and f.info("a.weight").dtype == "F8_E4M3"
+    for n, v in tensors.items():
+        assert torch.equal(f.tensor(n), v), n
+    assert P.detect_scheme(f.config) == "fp8_b128"
+    res, ty, k = P.linear_resident(f, "a", "fp8_b128")
+    assert ty == "FP8_B128" and k == 256 and torch.equal(P.resident_dequantize(res, ty, k), P.fp8_b128_dequantize(codes, sc))
+    res, ty, k = P.linear_resident(f, "b", "nvfp4_ct")
+    assert ty == "NVFP4" and torch.allclose(P.resident_dequantize(res, ty, k), P.nvfp4_dequantize(pk, s, t), rtol=1e-6)
+    res, ty, k = P.linear_resident(f, "n", "fp8_b128")        # an unquantised tensor inside a quantised folder
+    assert ty == "BF16"
+    f.close()
+    # refusals: truncated file, entry outside the file, missing shard
+    p = str(tmp_path / "one.safetensors")
+    S.write_file(p, {"x": torch.arange(10.)})
+    blob = open(p, "rb").read()
+    open(p, "wb").write(blob[:-4])
+    with pytest.raises(S.SafetensorsError):
+        S.Safetensors(p)
+    open(p, "wb").write(blob[:6])
+    with pytest.raises(S.SafetensorsError):
+        S.Safetensors(p)
+    import os
+    os.remove(str(tmp_path / "m" / "model-00002-of-00003.safetensors"))
+    with pytest.raises(S.SafetensorsError):
+        S.Folder(str(tmp_path / "m"))
+    with pytest.raises(P.PlaneError):
+        P.detect_scheme({"quantization_config": {"quant_method": "awq"}})
+
+
 def test_host_pool():
     assert H.pool_size() >= 1
 
@@ -204,3 +292,20 @@ def test_residency_rule_is_deterministic_and_bounded():
     log, on = a
     assert on[1] == [0, 1, 2] and 3 in on[0] and 4 in on[0]   # the hot ones were promoted, layer 1 untouched
     assert all(len(f) <= 3 for f in log)
+
+
+@pytest.mark.parametrize("scheme", ["fp8_b128", "nvfp4_modelopt", "nvfp4_ct", "plain"])
+def test_checkpoint_folder_opens_as_model(scheme, tmp_path):
+    from bloomery_b200.models import weights as W
+    from bloomery_b200.models.cpu_ref import CpuModel
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    spec = tiny_qwen3moe()
+    spec.vocab = 1024
+    W.write_folder(spec, str(tmp_path / "m"), scheme, seed=1, shards=3)
+    sp, w, folder = W.open_model(str(tmp_path / "m"), "cpu")
+    assert (sp.n_layer, sp.hidden, sp.n_expert, sp.n_used, sp.head_dim) == (4, 512, 16, 4, 64)
+    want = {"fp8_b128": "FP8_B128", "nvfp4_modelopt": "NVFP4", "nvfp4_ct": "NVFP4", "plain": "BF16"}[scheme]
+    assert w.q["blk.1.ffn_gate_exps.weight"].qtype == want and w.q["blk.1.ffn_gate_exps.weight"].data.shape[0] == 16
+    assert w.q["token_embd.weight"].qtype == "BF16" and w.f["blk.0.attn_norm.weight"].dtype == torch.float32
+    out = CpuModel(w).forward(torch.arange(6))
+    assert out.shape == (6, 1024) and bool(torch.isfinite(out).all())

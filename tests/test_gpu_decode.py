@@ -13,15 +13,16 @@ DEV = "cuda:0"
 
 
 def _qw(w, t):
+    from bloomery_b200.formats.resident import quantize_resident
     from bloomery_b200.ops.decode import QWeight
-    raw = Q.quantize(w.reshape(-1, w.shape[-1]), t)
-    res = to_resident(raw, t, w.shape[-1]).to(DEV)
+    res, wd = quantize_resident(w.reshape(-1, w.shape[-1]), t)
+    res = res.to(DEV)
     if w.dim() == 3:
         res = res.reshape(w.shape[0], w.shape[1], -1)
-    return QWeight(res, t, w.shape[-1]), Q.dequantize(raw, t, w.shape[-1]).reshape(w.shape)
+    return QWeight(res, t, w.shape[-1]), wd.reshape(w.shape)
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "NVFP4", "FP8_B128"])
 @pytest.mark.parametrize("M", [1, 3, 8])
 def test_gemv_norm_matches_fp32(t, M):
     from bloomery_b200.ops import decode as K
@@ -164,7 +165,8 @@ def test_gate_up_routes_like_route_rows():
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
 
 
-@pytest.mark.parametrize("gt,dt", [("Q4_K", "Q4_K"), ("Q4_K", "Q6_K"), ("Q8_0", "Q8_0"), ("Q5_K", "Q5_K")])
+@pytest.mark.parametrize("gt,dt", [("Q4_K", "Q4_K"), ("Q4_K", "Q6_K"), ("Q8_0", "Q8_0"), ("Q5_K", "Q5_K"), ("NVFP4", "NVFP4"),
+                                   ("FP8_B128", "FP8_B128")])
 def test_moe_sel_chain(gt, dt):
     from bloomery_b200.ops import decode as K
     torch.manual_seed(4)
@@ -275,7 +277,7 @@ def test_rope_append_flash_decode(head, n_q, n_kv):
     assert torch.isnan(out[1]).all() and not torch.isnan(out[0]).any()
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q6_K", "Q8_0", "F16"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q6_K", "Q8_0", "F16", "NVFP4", "FP8_B128"])
 def test_embed_and_argmax(t):
     from bloomery_b200.ops import decode as K
     from bloomery_b200.ops.decode import QWeight
@@ -362,6 +364,29 @@ def test_engine_logits_band_and_graph_equals_eager():
     eng.cut(0, len(prompt) - 1)
     eng.step([(0, prompt[-1], len(prompt) - 1)])
     assert torch.equal(eng.logits[0], eng2.logits[n_last - 1])
+
+
+@pytest.mark.parametrize("scheme", ["fp8_b128", "nvfp4_modelopt"])
+def test_engine_on_checkpoint_folder_logits_band(scheme, tmp_path):
+    """A block-scaled safetensors folder loads into resident planes and decodes within the q8 band of the oracle."""
+    from bloomery_b200.models import weights as W
+    from bloomery_b200.models.cpu_ref import CpuModel
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.runtime.engine import DecodeEngine
+    spec = tiny_qwen3moe()
+    spec.vocab = 4096
+    W.write_folder(spec, str(tmp_path / "m"), scheme, seed=3)
+    sp, wg, _ = W.open_model(str(tmp_path / "m"), DEV)
+    _, wc, _ = W.open_model(str(tmp_path / "m"), "cpu")
+    assert {"FP8_B128" if scheme == "fp8_b128" else "NVFP4", "BF16"} <= {q.qtype for q in wg.q.values()}
+    eng = DecodeEngine(wg, n_slots=1, slot_ctx=256, use_graphs=True)
+    g = torch.Generator().manual_seed(13)
+    prompt = torch.randint(0, sp.vocab, (21,), generator=g).tolist()
+    ref = CpuModel(wc).forward(torch.tensor(prompt))
+    eng.prefill(0, prompt)
+    n_last = len(prompt) % 8 or 8
+    err = ((eng.logits[:n_last].cpu() - ref[-n_last:]).abs().max() / ref.abs().max()).item()
+    assert err < 2e-2, err
 
 
 def test_engine_fault_poisons_and_resets():
