@@ -276,7 +276,9 @@ __device__ __forceinline__ void rows_f(const GemvArgs& a, const GemvSeg& s, int 
   }
 }
 
-template <int MB, int R, int C, bool NORM, bool FLOATW>
+// FAM: 0 = ggml integer-dot types, 1 = those plus float rows, 2 = block-scaled float planes (NVFP4, FP8).
+// One kernel per family keeps the register budget of the K-quant bodies free of the plane decoders.
+template <int MB, int R, int C, bool NORM, int FAM>
 __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int K = a.K;
@@ -290,7 +292,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
   auto between = [&]() {
     if (!ready) {
       pdl_wait();
-      if (NORM) prologue_norm<MB, FLOATW>(a, sq, sds, sx, s_scale, red);
+      if (NORM) prologue_norm<MB, FAM == 1>(a, sq, sds, sx, s_scale, red);
       else prologue_q8in<MB>(a, sq, sds, s_scale);
       pdl_launch();
       ready = true;
@@ -307,15 +309,21 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
     const int W = s.nblk * 8, wg = ((int)blockIdx.x - s.blk0) * 8 + (threadIdx.x >> 5);
     const int rpw = (s.rows + W - 1) / W;
     const int r_lo = min(s.rows, wg * rpw), r_hi = min(s.rows, r_lo + rpw);
-    switch (s.wtype) {
-      case WT_Q4_K: rows_q<Q4K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
-      case WT_Q6_K: rows_q<Q6K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
-      case WT_Q5_K: rows_q<Q5K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
-      case WT_Q8_0: rows_q<Q80, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
-      case WT_NVFP4: rows_q<NvFp4, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
-      case WT_FP8_B128: rows_q<Fp8B128, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
-      default:
-        if (FLOATW) rows_f<MB, R>(a, s, r_lo, r_hi, col0, sx, s_scale, between);
+    if constexpr (FAM == 2) {
+      switch (s.wtype) {
+        case WT_NVFP4: rows_q<NvFp4, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        case WT_FP8_B128: rows_q<Fp8B128, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        default: break;
+      }
+    } else {
+      switch (s.wtype) {
+        case WT_Q4_K: rows_q<Q4K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        case WT_Q6_K: rows_q<Q6K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        case WT_Q5_K: rows_q<Q5K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        case WT_Q8_0: rows_q<Q80, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        default:
+          if (FAM == 1) rows_f<MB, R>(a, s, r_lo, r_hi, col0, sx, s_scale, between);
+      }
     }
   }
   between();
@@ -327,33 +335,33 @@ static size_t gemv_smem(int MB, int K, bool floatw) {
   return b;
 }
 
-template <int MB, int R, int C, bool NORM, bool FLOATW>
+template <int MB, int R, int C, bool NORM, int FAM>
 static cudaError_t gemv_launch(const GemvArgs& a, int grid, cudaStream_t st) {
-  size_t smem = gemv_smem(MB, a.K, FLOATW);
+  size_t smem = gemv_smem(MB, a.K, FAM == 1);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemv_kernel<MB, R, C, NORM, FLOATW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(gemv_kernel<MB, R, C, NORM, FAM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     attr_set = true;
   }
-  return launch(gemv_kernel<MB, R, C, NORM, FLOATW>, dim3(grid), dim3(256), smem, st, a);
+  return launch(gemv_kernel<MB, R, C, NORM, FAM>, dim3(grid), dim3(256), smem, st, a);
 }
 
-template <int R, int C, bool NORM, bool FLOATW>
+template <int R, int C, bool NORM, int FAM>
 static cudaError_t gemv_dispatch_mb(const GemvArgs& a, int mb, int grid, cudaStream_t st) {
   switch (mb) {
-    case 1: return gemv_launch<1, R, C, NORM, FLOATW>(a, grid, st);
-    case 2: return gemv_launch<2, R, C, NORM, FLOATW>(a, grid, st);
-    case 4: return gemv_launch<4, R, C, NORM, FLOATW>(a, grid, st);
-    default: return gemv_launch<8, R, C, NORM, FLOATW>(a, grid, st);
+    case 1: return gemv_launch<1, R, C, NORM, FAM>(a, grid, st);
+    case 2: return gemv_launch<2, R, C, NORM, FAM>(a, grid, st);
+    case 4: return gemv_launch<4, R, C, NORM, FAM>(a, grid, st);
+    default: return gemv_launch<8, R, C, NORM, FAM>(a, grid, st);
   }
 }
 
-template <bool NORM, bool FLOATW>
+template <bool NORM, int FAM>
 static cudaError_t gemv_dispatch_shape(const GemvArgs& a, int mb, int R, int C, int grid, cudaStream_t st) {
-  if (C == 2) return gemv_dispatch_mb<1, 2, NORM, FLOATW>(a, mb, grid, st);
-  if (R >= 3) return gemv_dispatch_mb<3, 1, NORM, FLOATW>(a, mb, grid, st);
-  if (R == 2) return gemv_dispatch_mb<2, 1, NORM, FLOATW>(a, mb, grid, st);
-  return gemv_dispatch_mb<1, 1, NORM, FLOATW>(a, mb, grid, st);
+  if (C == 2) return gemv_dispatch_mb<1, 2, NORM, FAM>(a, mb, grid, st);
+  if (R >= 3) return gemv_dispatch_mb<3, 1, NORM, FAM>(a, mb, grid, st);
+  if (R == 2) return gemv_dispatch_mb<2, 1, NORM, FAM>(a, mb, grid, st);
+  return gemv_dispatch_mb<1, 1, NORM, FAM>(a, mb, grid, st);
 }
 
 }  // namespace bl
@@ -378,7 +386,7 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
   BL_REQUIRE(!norm || (K % 2048 == 0 || K % 64 == 0), BL_ERR_SHAPE);
   GemvArgs a = {};
   a.nseg = nseg;
-  bool floatw = false;
+  bool floatw = false, planes = false, ggml = false;
   double total_bytes = 0;
   long rbs[4];
   for (int s = 0; s < nseg; ++s) {
@@ -388,8 +396,11 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
     BL_REQUIRE(rows[s] >= 1, BL_ERR_SHAPE);
     total_bytes += (double)rows[s] * rbs[s];
     if (wtypes[s] == WT_F32 || wtypes[s] == WT_F16 || wtypes[s] == WT_BF16) floatw = true;
+    else if (wtypes[s] == WT_NVFP4 || wtypes[s] == WT_FP8_B128) planes = true;
+    else ggml = true;
   }
   BL_REQUIRE(!(floatw && !norm), BL_ERR_TYPE);
+  BL_REQUIRE(!(planes && (floatw || ggml)), BL_ERR_TYPE);   // one family per call
   const int mb = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
   // One wave: at most two resident blocks per SM; each segment gets a share of the blocks
   // in proportion to its bytes, never more blocks than it has 8-row groups.
@@ -416,8 +427,9 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
   if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks, BL_ERR_SHAPE); }
   BL_REQUIRE(gemv_smem(mb, K, floatw) <= 200 * 1024, BL_ERR_LIMIT);
   cudaError_t e;
-  if (norm) e = floatw ? gemv_dispatch_shape<true, true>(a, mb, R, C, grid, st) : gemv_dispatch_shape<true, false>(a, mb, R, C, grid, st);
-  else e = gemv_dispatch_shape<false, false>(a, mb, R, C, grid, st);
+  if (planes) e = norm ? gemv_dispatch_shape<true, 2>(a, mb, R, C, grid, st) : gemv_dispatch_shape<false, 2>(a, mb, R, C, grid, st);
+  else if (norm) e = floatw ? gemv_dispatch_shape<true, 1>(a, mb, R, C, grid, st) : gemv_dispatch_shape<true, 0>(a, mb, R, C, grid, st);
+  else e = gemv_dispatch_shape<false, 0>(a, mb, R, C, grid, st);
   return (int)e;
 }
 

@@ -1,0 +1,372 @@
+// Decode-time multi-head latent attention (DeepSeek-V2/V3, Kimi-K2 shape: latent 512 + RoPE 64).
+//
+// The cache keeps one row of 576 f16 values per position and layer: the RMS-normalised
+// compressed KV latent c (512) followed by the rotated shared key part (64).  Attention
+// runs in the latent space ("absorbed" form):
+//
+//   1. mla_kv_append   RMSNorm(c) * gain, interleaved-pair RoPE on the 64 rope dims, f16 append
+//   2. mla_q_absorb    per head: RoPE on q_rope, q_lat = W_kb[h]^T q_nope  -> q' [M, n_q, 576] (pre-scaled)
+//   3. mla_flash_seg   split-K online softmax of q' against the latent rows; the value of a key is
+//                      its first 512 entries (one read serves K and V)
+//   4. mla_merge_vup   merge segments ascending, v = W_vb[h] * latent (128 x 512 per head), q8 for o_proj
+//
+// The reference's latent flash and its absorbed-q f32 GEMV: crates/gpu/src/flash.rs,
+// crates/gpu/src/q8f32.rs (f32-activation sites "router, absorbed MLA q").  W_kb is kept as
+// [head][nope][512] and W_vb as [head][v_dim][512], both f32 or bf16 (the per-head products keep
+// f32 activations).
+#include "common.cuh"
+
+namespace bl {
+
+constexpr int kMlaPage = 64;
+constexpr int kLat = 512;
+constexpr int kRope = 64;
+constexpr int kRow = kLat + kRope;      // 576 values per cached position
+constexpr int kTile = 32;
+constexpr int kRowPad = kRow + 8;       // shared-memory row stride in halves: 16-byte reads by key lanes do not collide
+constexpr int kHeadsPerBlock = 16;      // 8 warps x 2 heads
+
+struct MlaAppendArgs {
+  const float* kv;         // [M, stride]: 512 latent values then 64 rope values
+  long stride;
+  const float* gain;       // [512]
+  const float* inv_freq;   // [32]
+  float eps;
+  int M;
+  const int* row_pos;
+  const int* row_seq;
+  const int* block_table;
+  int max_pages, n_pages;
+  __half* cache;           // [n_pages][64][576]
+  unsigned* fault;
+  int layer;
+};
+
+// grid (M), 256 threads
+__global__ void __launch_bounds__(256) mla_kv_append_kernel(const MlaAppendArgs a) {
+  __shared__ double red[8];
+  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
+  pdl_launch();
+  const int seq = a.row_seq[m];
+  if (seq < 0) return;
+  const int pos = a.row_pos[m];
+  const float* src = a.kv + (long)m * a.stride;
+  const float x0 = src[tid], x1 = src[tid + 256];
+  double ss = warp_sum_d((double)(x0 * x0) + (double)(x1 * x1));
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  double tot = 0.0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float scale = (float)(1.0 / sqrt(tot / (double)kLat + (double)a.eps));
+  const int pslot = pos / kMlaPage;
+  const int page = (pos >= 0 && pslot < a.max_pages) ? a.block_table[(long)seq * a.max_pages + pslot] : -1;
+  if (page < 0 || page >= a.n_pages) {
+    if (tid == 0) raise_fault(a.fault, a.layer, FS_PAGE);
+    return;
+  }
+  __half* dst = a.cache + ((long)page * kMlaPage + (pos % kMlaPage)) * kRow;
+  dst[tid] = __float2half_rn((scale * a.gain[tid]) * x0);
+  dst[tid + 256] = __float2half_rn((scale * a.gain[tid + 256]) * x1);
+  if (tid < kRope / 2) {
+    const float r0 = src[kLat + 2 * tid], r1 = src[kLat + 2 * tid + 1];
+    float s, c;
+    sincosf((float)pos * a.inv_freq[tid], &s, &c);
+    dst[kLat + 2 * tid] = __float2half_rn(fmaf(r0, c, -(r1 * s)));
+    dst[kLat + 2 * tid + 1] = __float2half_rn(fmaf(r0, s, r1 * c));
+  }
+}
+
+template <typename W> __device__ __forceinline__ float wf(const W* p, long i);
+template <> __device__ __forceinline__ float wf<float>(const float* p, long i) { return p[i]; }
+template <> __device__ __forceinline__ float wf<__nv_bfloat16>(const __nv_bfloat16* p, long i) { return __bfloat162float(p[i]); }
+
+struct MlaQArgs {
+  const float* q;          // [M, stride]: head h at h * (nope + 64): nope values then 64 rope values
+  long stride;
+  const void* w_kb;        // [n_q][nope][512]
+  const float* inv_freq;
+  float scale;             // softmax scale folded into q'
+  int n_q, nope, M;
+  const int* row_pos;
+  const int* row_seq;
+  float* q_lat;            // [M, n_q, 576]
+};
+
+// grid (n_q, M), 256 threads: thread t owns latent columns 2t, 2t+1
+template <typename W>
+__global__ void __launch_bounds__(256) mla_q_absorb_kernel(const MlaQArgs a) {
+  __shared__ float sq[128];
+  const int h = blockIdx.x, m = blockIdx.y, tid = threadIdx.x;
+  pdl_wait();
+  pdl_launch();
+  if (a.row_seq[m] < 0) return;
+  const float* src = a.q + (long)m * a.stride + (long)h * (a.nope + kRope);
+  if (tid < a.nope) sq[tid] = src[tid];
+  float* out = a.q_lat + ((long)m * a.n_q + h) * kRow;
+  if (tid >= 128 && tid < 128 + kRope / 2) {
+    const int j = tid - 128;
+    const float r0 = src[a.nope + 2 * j], r1 = src[a.nope + 2 * j + 1];
+    float s, c;
+    sincosf((float)a.row_pos[m] * a.inv_freq[j], &s, &c);
+    out[kLat + 2 * j] = fmaf(r0, c, -(r1 * s)) * a.scale;
+    out[kLat + 2 * j + 1] = fmaf(r0, s, r1 * c) * a.scale;
+  }
+  __syncthreads();
+  const W* w = reinterpret_cast<const W*>(a.w_kb) + (long)h * a.nope * kLat;
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+  for (int n = 0; n < a.nope; ++n) {
+    const float qn = sq[n];
+    a0 = fmaf(wf<W>(w, (long)n * kLat + 2 * tid), qn, a0);
+    a1 = fmaf(wf<W>(w, (long)n * kLat + 2 * tid + 1), qn, a1);
+  }
+  out[2 * tid] = a0 * a.scale;
+  out[2 * tid + 1] = a1 * a.scale;
+}
+
+struct MlaFlashArgs {
+  const float* q_lat;      // [M, n_q, 576]
+  const __half* cache;
+  const int* row_pos;
+  const int* row_seq;
+  const int* block_table;
+  int max_pages, n_pages;
+  int n_q, M, n_seg, ctx_limit;
+  float* part_ml;          // [M, n_q, n_seg, 2]
+  float* part_acc;         // [M, n_q, n_seg, 512]
+  unsigned* fault;
+  int layer;
+};
+
+__device__ __forceinline__ void mla_cp16(void* smem, const void* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+
+// grid (n_seg, ceil(n_q / 16), M), 256 threads; warp w serves heads 2w, 2w+1 of the block's 16
+__global__ void __launch_bounds__(256) mla_flash_seg_kernel(const MlaFlashArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* sq = reinterpret_cast<float*>(smem);                                         // [16][576]
+  __half* skv = reinterpret_cast<__half*>(smem + (size_t)kHeadsPerBlock * kRow * 4);  // [2][32][584]
+  const int seg = blockIdx.x, hb = blockIdx.y, m = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
+  pdl_launch();
+  const int seq = a.row_seq[m];
+  if (seq < 0) return;
+  const int n_keys = a.row_pos[m] + 1;
+  const bool bad = n_keys <= 0 || n_keys > a.ctx_limit;
+  if (bad && tid == 0 && seg == 0 && hb == 0) raise_fault(a.fault, a.layer, FS_KEY_COUNT);
+  const int n_tiles = bad ? 0 : (n_keys + kTile - 1) / kTile;
+  const int tps = (n_tiles + a.n_seg - 1) / a.n_seg;
+  const int t0 = seg * tps, t1 = min(n_tiles, t0 + tps);
+  const int h0 = hb * kHeadsPerBlock;
+  const int n_heads = min(kHeadsPerBlock, a.n_q - h0);
+  for (int i = tid; i < n_heads * kRow; i += 256) sq[i] = a.q_lat[((long)m * a.n_q + h0) * kRow + i];
+
+  const int* bt = a.block_table + (long)seq * a.max_pages;
+  auto issue_tile = [&](int t, int stage) {
+    const int key0 = t * kTile;
+    int page = bt[key0 / kMlaPage];
+    page = (page < 0 || page >= a.n_pages) ? 0 : page;     // the append kernel raises the fault; stay in bounds
+    const __half* base = a.cache + ((long)page * kMlaPage + (key0 % kMlaPage)) * kRow;
+    constexpr int CH = kRow / 8;                            // 72 chunks of 16 bytes per row
+    for (int c = tid; c < kTile * CH; c += 256) {
+      const int r = c / CH, cc = c % CH;
+      mla_cp16(skv + ((size_t)stage * kTile + r) * kRowPad + cc * 8, base + (long)r * kRow + cc * 8);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float mx[2], l[2], acc[2][16];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < 16; ++d) acc[h][d] = 0.f;
+  }
+  const bool live0 = 2 * warp < n_heads, live1 = 2 * warp + 1 < n_heads;
+
+  if (t0 < t1) issue_tile(t0, 0);
+  for (int t = t0; t < t1; ++t) {
+    const int stage = (t - t0) & 1;
+    if (t + 1 < t1) { issue_tile(t + 1, stage ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+    else { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+    __syncthreads();
+    if (live0) {
+      const __half* krow = skv + ((size_t)stage * kTile + lane) * kRowPad;
+      const float* q0p = sq + (2 * warp) * kRow;
+      const float* q1p = sq + (live1 ? 2 * warp + 1 : 2 * warp) * kRow;
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
+      for (int d = 0; d < kRow; d += 8) {
+        const uint4 kv = *reinterpret_cast<const uint4*>(krow + d);
+        const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kv.x));
+        const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kv.y));
+        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kv.z));
+        const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kv.w));
+        const float4 a0 = *reinterpret_cast<const float4*>(q0p + d), a1 = *reinterpret_cast<const float4*>(q0p + d + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(q1p + d), b1 = *reinterpret_cast<const float4*>(q1p + d + 4);
+        s0 = fmaf(a0.x, k0.x, s0); s0 = fmaf(a0.y, k0.y, s0); s0 = fmaf(a0.z, k1.x, s0); s0 = fmaf(a0.w, k1.y, s0);
+        s0 = fmaf(a1.x, k2.x, s0); s0 = fmaf(a1.y, k2.y, s0); s0 = fmaf(a1.z, k3.x, s0); s0 = fmaf(a1.w, k3.y, s0);
+        s1 = fmaf(b0.x, k0.x, s1); s1 = fmaf(b0.y, k0.y, s1); s1 = fmaf(b0.z, k1.x, s1); s1 = fmaf(b0.w, k1.y, s1);
+        s1 = fmaf(b1.x, k2.x, s1); s1 = fmaf(b1.y, k2.y, s1); s1 = fmaf(b1.z, k3.x, s1); s1 = fmaf(b1.w, k3.y, s1);
+      }
+      if (t * kTile + lane >= n_keys) { s0 = -INFINITY; s1 = -INFINITY; }
+      float p[2];
+      const float sc[2] = {s0, s1};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float nm = fmaxf(mx[h], warp_max(sc[h]));
+        const float corr = (mx[h] == -INFINITY) ? 0.f : __expf(mx[h] - nm);
+        p[h] = (sc[h] == -INFINITY) ? 0.f : __expf(sc[h] - nm);
+        l[h] = l[h] * corr + warp_sum(p[h]);
+        mx[h] = nm;
+#pragma unroll
+        for (int d = 0; d < 16; ++d) acc[h][d] *= corr;
+      }
+      // values: the first 512 entries of each row; lane owns dims 2*lane + 64*i, +1
+      const __half* vbase = skv + (size_t)stage * kTile * kRowPad + 2 * lane;
+      const int kmax = min(kTile, n_keys - t * kTile);       // masked keys are never read
+#pragma unroll 2
+      for (int k = 0; k < kmax; ++k) {
+        const float p0 = __shfl_sync(0xffffffffu, p[0], k), p1 = __shfl_sync(0xffffffffu, p[1], k);
+        const __half* vr = vbase + (size_t)k * kRowPad;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(vr + 64 * i));
+          acc[0][2 * i] = fmaf(p0, v.x, acc[0][2 * i]); acc[0][2 * i + 1] = fmaf(p0, v.y, acc[0][2 * i + 1]);
+          acc[1][2 * i] = fmaf(p1, v.x, acc[1][2 * i]); acc[1][2 * i + 1] = fmaf(p1, v.y, acc[1][2 * i + 1]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int hh = 2 * warp + h;
+    if (hh < n_heads) {
+      const long pidx = ((long)m * a.n_q + h0 + hh) * a.n_seg + seg;
+      if (lane == 0) {
+        a.part_ml[pidx * 2] = bad ? __int_as_float(0x7fc00000) : mx[h];
+        a.part_ml[pidx * 2 + 1] = l[h];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        a.part_acc[pidx * kLat + 2 * lane + 64 * i] = acc[h][2 * i];
+        a.part_acc[pidx * kLat + 2 * lane + 64 * i + 1] = acc[h][2 * i + 1];
+      }
+    }
+  }
+}
+
+struct MlaMergeArgs {
+  const float* part_ml;
+  const float* part_acc;
+  const void* w_vb;        // [n_q][v_dim][512]
+  int n_q, n_seg, M, v_dim;
+  const int* row_seq;
+  float* out;              // optional fp32 [M, n_q * v_dim]
+  int8_t* outq;            // q8 codes [M, n_q * v_dim]
+  float2* outds;           // [M, n_q * v_dim / 32]
+};
+
+// grid (n_q, M), 256 threads
+template <typename W>
+__global__ void __launch_bounds__(256) mla_merge_vup_kernel(const MlaMergeArgs a) {
+  __shared__ float slat[kLat];
+  __shared__ float so[128];
+  const int h = blockIdx.x, m = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
+  pdl_launch();
+  if (a.row_seq[m] < 0) return;
+  const long p0 = ((long)m * a.n_q + h) * a.n_seg;
+  float mx = -INFINITY;
+  bool nan = false;
+  for (int s = 0; s < a.n_seg; ++s) {
+    const float v = a.part_ml[(p0 + s) * 2];
+    nan |= (v != v);
+    mx = fmaxf(mx, v);
+  }
+  float n0 = 0.f, n1 = 0.f, den = 0.f;
+  for (int s = 0; s < a.n_seg; ++s) {                       // ascending segment order, fixed
+    const float ms = a.part_ml[(p0 + s) * 2];
+    const float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
+    den = fmaf(a.part_ml[(p0 + s) * 2 + 1], w, den);
+    n0 = fmaf(a.part_acc[(p0 + s) * kLat + tid], w, n0);
+    n1 = fmaf(a.part_acc[(p0 + s) * kLat + tid + 256], w, n1);
+  }
+  const float qnan = __int_as_float(0x7fc00000);
+  slat[tid] = nan ? qnan : n0 / den;
+  slat[tid + 256] = nan ? qnan : n1 / den;
+  __syncthreads();
+  const W* w = reinterpret_cast<const W*>(a.w_vb) + (long)h * a.v_dim * kLat;
+  for (int r = warp; r < a.v_dim; r += 8) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLat / 32; ++i) acc = fmaf(wf<W>(w, (long)r * kLat + lane + 32 * i), slat[lane + 32 * i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) so[r] = acc;
+  }
+  __syncthreads();
+  if (tid < a.v_dim) {
+    const float o = so[tid];
+    const long width = (long)a.n_q * a.v_dim, col = (long)h * a.v_dim + tid;
+    if (a.out) a.out[(long)m * width + col] = o;
+    float d, s;
+    const int8_t q = q8_lane(o, d, s);
+    a.outq[(long)m * width + col] = q;
+    if (lane == 0) a.outds[((long)m * width + col) / 32] = make_float2(d, s);
+  }
+}
+
+}  // namespace bl
+
+using namespace bl;
+
+extern "C" {
+
+int bl_mla_kv_append(const float* kv, long stride, const float* gain, const float* inv_freq, float eps, int kv_lora,
+                     int rope_dim, int M, const int* row_pos, const int* row_seq, const int* block_table, int max_pages,
+                     int n_pages, void* cache, unsigned* fault, int layer, cudaStream_t st) {
+  BL_REQUIRE(kv_lora == kLat && rope_dim == kRope && M >= 1, BL_ERR_SHAPE);
+  MlaAppendArgs a{kv, stride, gain, inv_freq, eps, M, row_pos, row_seq, block_table, max_pages, n_pages,
+                  (__half*)cache, fault, layer};
+  return (int)launch(mla_kv_append_kernel, dim3(M), dim3(256), 0, st, a);
+}
+
+// wtype: 0 = f32, 30 = bf16
+int bl_mla_q_absorb(const float* q, long stride, const void* w_kb, int wtype, const float* inv_freq, float scale, int n_q,
+                    int nope, int kv_lora, int rope_dim, int M, const int* row_pos, const int* row_seq, float* q_lat,
+                    cudaStream_t st) {
+  BL_REQUIRE(kv_lora == kLat && rope_dim == kRope && nope >= 1 && nope <= 128 && M >= 1, BL_ERR_SHAPE);
+  BL_REQUIRE(wtype == 0 || wtype == 30, BL_ERR_TYPE);
+  MlaQArgs a{q, stride, w_kb, inv_freq, scale, n_q, nope, M, row_pos, row_seq, q_lat};
+  if (wtype == 0) return (int)launch(mla_q_absorb_kernel<float>, dim3(n_q, M), dim3(256), 0, st, a);
+  return (int)launch(mla_q_absorb_kernel<__nv_bfloat16>, dim3(n_q, M), dim3(256), 0, st, a);
+}
+
+int bl_mla_flash_decode(const float* q_lat, const void* cache, const int* row_pos, const int* row_seq,
+                        const int* block_table, int max_pages, int n_pages, int n_q, int M, int n_seg, int ctx_limit,
+                        float* part_ml, float* part_acc, const void* w_vb, int wtype, int v_dim, float* out, int8_t* outq,
+                        float* outds, unsigned* fault, int layer, cudaStream_t st) {
+  BL_REQUIRE(n_q >= 1 && M >= 1 && n_seg >= 1 && v_dim >= 32 && v_dim <= 128 && v_dim % 32 == 0, BL_ERR_SHAPE);
+  BL_REQUIRE(wtype == 0 || wtype == 30, BL_ERR_TYPE);
+  const size_t smem = (size_t)kHeadsPerBlock * kRow * 4 + (size_t)2 * kTile * kRowPad * 2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(mla_flash_seg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  MlaFlashArgs f{q_lat, (const __half*)cache, row_pos, row_seq, block_table, max_pages, n_pages, n_q, M, n_seg, ctx_limit,
+                 part_ml, part_acc, fault, layer};
+  cudaError_t e = launch(mla_flash_seg_kernel, dim3(n_seg, (n_q + kHeadsPerBlock - 1) / kHeadsPerBlock, M), dim3(256), smem, st, f);
+  if (e != cudaSuccess) return (int)e;
+  MlaMergeArgs g{part_ml, part_acc, w_vb, n_q, n_seg, M, v_dim, row_seq, out, outq, (float2*)outds};
+  if (wtype == 0) return (int)launch(mla_merge_vup_kernel<float>, dim3(n_q, M), dim3(256), 0, st, g);
+  return (int)launch(mla_merge_vup_kernel<__nv_bfloat16>, dim3(n_q, M), dim3(256), 0, st, g);
+}
+
+}  // extern "C"

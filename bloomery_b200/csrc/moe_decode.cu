@@ -301,6 +301,9 @@ __device__ __forceinline__ void gate_up_rows(const uint8_t* g0, const uint8_t* u
 // When route.logits is set, warp 0 of every block routes row m itself (redundantly, from
 // the router launch's logits) so no block waits on a completion counter; block (0, 0, m)
 // also publishes ids / weights / heat for the launches that follow.
+// FAM 0 = ggml integer-dot types, FAM 2 = block-scaled float planes (one kernel per family keeps
+// the plane decoders out of the K-quant bodies' register budget)
+template <int FAM>
 __global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a) {
   const int K = a.K;
   __shared__ float s_act[32];
@@ -350,14 +353,20 @@ __global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a)
     const uint8_t* g0 = a.gate + row0 * rb;
     const uint8_t* u0 = a.up + row0 * rb;
     float gacc[2], uacc[2];
-    switch (a.gtype) {
-      case WT_Q4_K: gate_up_rows<Q4K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
-      case WT_Q5_K: gate_up_rows<Q5K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
-      case WT_Q6_K: gate_up_rows<Q6K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
-      case WT_Q8_0: gate_up_rows<Q80>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
-      case WT_NVFP4: gate_up_rows<NvFp4>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
-      case WT_FP8_B128: gate_up_rows<Fp8B128>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
-      default: gacc[0] = gacc[1] = __int_as_float(0x7fc00000); uacc[0] = uacc[1] = 0.f;
+    if constexpr (FAM == 2) {
+      switch (a.gtype) {
+        case WT_NVFP4: gate_up_rows<NvFp4>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_FP8_B128: gate_up_rows<Fp8B128>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        default: gacc[0] = gacc[1] = __int_as_float(0x7fc00000); uacc[0] = uacc[1] = 0.f;
+      }
+    } else {
+      switch (a.gtype) {
+        case WT_Q4_K: gate_up_rows<Q4K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q5_K: gate_up_rows<Q5K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q6_K: gate_up_rows<Q6K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q8_0: gate_up_rows<Q80>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        default: gacc[0] = gacc[1] = __int_as_float(0x7fc00000); uacc[0] = uacc[1] = 0.f;
+      }
     }
     if (lane == 0) {
 #pragma unroll
@@ -438,7 +447,7 @@ __device__ __forceinline__ float down_row(const DownArgs& a, int m, int d, int l
   return warp_sum(y);
 }
 
-template <int UPL>
+template <int UPL, int FAM>
 __global__ void __launch_bounds__(256, UPL <= 3 ? 2 : 1) down_combine_kernel(const DownArgs a) {
   __shared__ int s_slot[kMaxTopK];
   __shared__ float s_w[kMaxTopK];
@@ -460,14 +469,20 @@ __global__ void __launch_bounds__(256, UPL <= 3 ? 2 : 1) down_combine_kernel(con
   const int d = blockIdx.x * 8 + warp;
   if (d < a.H) {
     float y;
-    switch (a.dtype) {
-      case WT_Q4_K: y = down_row<Q4K, UPL>(a, m, d, lane, s_slot, s_w); break;
-      case WT_Q6_K: y = down_row<Q6K, UPL>(a, m, d, lane, s_slot, s_w); break;
-      case WT_Q5_K: y = down_row<Q5K, UPL>(a, m, d, lane, s_slot, s_w); break;
-      case WT_Q8_0: y = down_row<Q80, UPL>(a, m, d, lane, s_slot, s_w); break;
-      case WT_NVFP4: y = down_row<NvFp4, UPL>(a, m, d, lane, s_slot, s_w); break;
-      case WT_FP8_B128: y = down_row<Fp8B128, UPL>(a, m, d, lane, s_slot, s_w); break;
-      default: y = __int_as_float(0x7fc00000);
+    if constexpr (FAM == 2) {
+      switch (a.dtype) {
+        case WT_NVFP4: y = down_row<NvFp4, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_FP8_B128: y = down_row<Fp8B128, UPL>(a, m, d, lane, s_slot, s_w); break;
+        default: y = __int_as_float(0x7fc00000);
+      }
+    } else {
+      switch (a.dtype) {
+        case WT_Q4_K: y = down_row<Q4K, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q6_K: y = down_row<Q6K, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q5_K: y = down_row<Q5K, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q8_0: y = down_row<Q80, UPL>(a, m, d, lane, s_slot, s_w); break;
+        default: y = __int_as_float(0x7fc00000);
+      }
     }
     if (lane == 0) {
       if (bad) { y = __int_as_float(0x7fc00000); if (d == 0) raise_fault(a.fault, a.layer, FS_EXPERT_ID); }
@@ -555,7 +570,8 @@ int bl_gate_up_sel(const int8_t* xq, const float* xds, const float* route_logits
   a.gate = (const uint8_t*)gate; a.up = (const uint8_t*)up; a.gtype = gtype; a.utype = utype;
   a.K = K; a.I = I; a.E = E; a.n_used = n_used; a.M = M;
   a.actq = actq; a.actds = (float2*)actds; a.act_f32 = act_f32; a.fault = fault; a.layer = layer;
-  return (int)launch(gate_up_sel_kernel, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
+  if (gtype == WT_NVFP4 || gtype == WT_FP8_B128) return (int)launch(gate_up_sel_kernel<2>, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
+  return (int)launch(gate_up_sel_kernel<0>, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
 }
 
 int bl_down_combine(const int8_t* actq, const float* actds, const int* ids, const float* wts, const int* slot_map,
@@ -571,9 +587,14 @@ int bl_down_combine(const int8_t* actq, const float* actds, const int* ids, cons
   const long total = (long)n_used * (I / 64);
   BL_REQUIRE(total <= 512, BL_ERR_LIMIT);
   dim3 grid((H + 7) / 8, M);
-  if (total <= 96) return (int)launch(down_combine_kernel<3>, grid, dim3(256), 0, st, a);
-  if (total <= 192) return (int)launch(down_combine_kernel<6>, grid, dim3(256), 0, st, a);
-  return (int)launch(down_combine_kernel<16>, grid, dim3(256), 0, st, a);
+  if (dtype == WT_NVFP4 || dtype == WT_FP8_B128) {
+    if (total <= 96) return (int)launch(down_combine_kernel<3, 2>, grid, dim3(256), 0, st, a);
+    if (total <= 192) return (int)launch(down_combine_kernel<6, 2>, grid, dim3(256), 0, st, a);
+    return (int)launch(down_combine_kernel<16, 2>, grid, dim3(256), 0, st, a);
+  }
+  if (total <= 96) return (int)launch(down_combine_kernel<3, 0>, grid, dim3(256), 0, st, a);
+  if (total <= 192) return (int)launch(down_combine_kernel<6, 0>, grid, dim3(256), 0, st, a);
+  return (int)launch(down_combine_kernel<16, 0>, grid, dim3(256), 0, st, a);
 }
 
 }  // extern "C"
