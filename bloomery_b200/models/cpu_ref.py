@@ -34,6 +34,15 @@ def rope_neox(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> tor
     return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], -1)
 
 
+def rope_pairs(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """x [T, ..., D]; interleaved pairs (2i, 2i + 1), the DeepSeek convention."""
+    ang = pos.float()[:, None] * inv_freq[None, :]
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [x.shape[-1] // 2]
+    c, s = torch.cos(ang).reshape(shape), torch.sin(ang).reshape(shape)
+    x0, x1 = x[..., 0::2], x[..., 1::2]
+    return torch.stack([x0 * c - x1 * s, x0 * s + x1 * c], -1).reshape(x.shape)
+
+
 def route(logits: torch.Tensor, spec: ModelSpec, bias: Optional[torch.Tensor] = None):
     """[T, E] -> (ids [T, k], weights [T, k]) with the device's tie rule (smaller id wins)."""
     if spec.router_mode == "softmax":
@@ -66,13 +75,16 @@ class CpuModel:
         for n in list(weights.q) + list(weights.f):
             self.w[n] = weights.dequant(n).to(self.device)
         s = self.spec
-        self.inv_freq = (1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float64) / s.head_dim))).float().to(self.device)
+        from .rope import attn_scale, inv_freq_table
+        self.inv_freq = inv_freq_table(s, s.rope_dim if s.mla else s.head_dim).to(self.device)
+        self.scale = attn_scale(s)
         self.reset()
 
     def reset(self):
         s = self.spec
-        self.k: List[torch.Tensor] = [torch.zeros(0, s.n_kv, s.head_dim, device=self.device) for _ in range(s.n_layer)]
-        self.v: List[torch.Tensor] = [torch.zeros(0, s.n_kv, s.head_dim, device=self.device) for _ in range(s.n_layer)]
+        kd = (1, s.kv_lora + s.rope_dim) if s.mla else (s.n_kv, s.head_dim)
+        self.k: List[torch.Tensor] = [torch.zeros(0, *kd, device=self.device) for _ in range(s.n_layer)]
+        self.v: List[torch.Tensor] = [torch.zeros(0, *kd, device=self.device) for _ in range(s.n_layer)]
         self.n_past = 0
 
     def _q(self, x: torch.Tensor) -> torch.Tensor:
@@ -80,6 +92,62 @@ class CpuModel:
             return x
         c, ds = quantize_act_q8(x)
         return dequantize_act_q8(c, ds)
+
+
+    def _gqa(self, il: int, h: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        s, w = self.spec, self.w
+        b = f"blk.{il}."
+        T = h.shape[0]
+        q = (h @ w[b + "attn_q.weight"].T).reshape(T, s.n_q, s.head_dim)
+        k = (h @ w[b + "attn_k.weight"].T).reshape(T, s.n_kv, s.head_dim)
+        v = (h @ w[b + "attn_v.weight"].T).reshape(T, s.n_kv, s.head_dim)
+        if s.qk_norm:
+            q = rms_norm(q, w[b + "attn_q_norm.weight"], s.rms_eps)
+            k = rms_norm(k, w[b + "attn_k_norm.weight"], s.rms_eps)
+        q = rope_neox(q, pos, self.inv_freq)
+        k = rope_neox(k, pos, self.inv_freq)
+        k = k.half().float()
+        v = v.half().float()
+        self.k[il] = torch.cat([self.k[il], k], 0)
+        self.v[il] = torch.cat([self.v[il], v], 0)
+        G = s.n_q // s.n_kv
+        kk = self.k[il].repeat_interleave(G, 1)      # [S, n_q, D]
+        vv = self.v[il].repeat_interleave(G, 1)
+        S = kk.shape[0]
+        sc = torch.einsum("thd,shd->hts", q, kk) / math.sqrt(s.head_dim)
+        mask = torch.arange(S, device=self.device)[None, :] > pos[:, None]
+        sc = sc.masked_fill(mask[None], -float("inf"))
+        pr = torch.softmax(sc, -1)
+        att = torch.einsum("hts,shd->thd", pr, vv).reshape(T, s.q_rows)
+        return att
+
+    def _mla(self, il: int, h: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """Multi-head latent attention in its plain (un-absorbed) form: keys and values are rebuilt per head
+        from the cached latent, scores add the shared rotary part."""
+        s, w = self.spec, self.w
+        b = f"blk.{il}."
+        T = h.shape[0]
+        qk = s.nope_dim + s.rope_dim
+        if s.q_lora:
+            qa = h @ w[b + "attn_q_a.weight"].T
+            q = self._q(rms_norm(qa, w[b + "attn_q_a_norm.weight"], s.rms_eps)) @ w[b + "attn_q_b.weight"].T
+        else:
+            q = h @ w[b + "attn_q.weight"].T
+        q = q.reshape(T, s.n_q, qk)
+        q_nope, q_rope = q[..., :s.nope_dim], rope_pairs(q[..., s.nope_dim:], pos, self.inv_freq)
+        kva = h @ w[b + "attn_kv_a_mqa.weight"].T
+        c = rms_norm(kva[:, :s.kv_lora], w[b + "attn_kv_a_norm.weight"], s.rms_eps)
+        kr = rope_pairs(kva[:, s.kv_lora:], pos, self.inv_freq)
+        row = torch.cat([c, kr], -1).half().float()[:, None, :]
+        self.k[il] = torch.cat([self.k[il], row], 0)
+        lat, krope = self.k[il][:, 0, :s.kv_lora], self.k[il][:, 0, s.kv_lora:]
+        S = lat.shape[0]
+        k_nope = torch.einsum("hnc,sc->shn", w[b + "attn_k_b.weight"], lat)
+        v = torch.einsum("hvc,sc->shv", w[b + "attn_v_b.weight"], lat)
+        sc = (torch.einsum("thn,shn->hts", q_nope, k_nope) + torch.einsum("thr,sr->hts", q_rope, krope)) * self.scale
+        mask = torch.arange(S, device=self.device)[None, :] > pos[:, None]
+        pr = torch.softmax(sc.masked_fill(mask[None], -float("inf")), -1)
+        return torch.einsum("hts,shv->thv", pr, v).reshape(T, s.n_q * s.v_dim)
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, collect: Optional[dict] = None) -> torch.Tensor:
@@ -91,27 +159,7 @@ class CpuModel:
         for il in range(s.n_layer):
             b = f"blk.{il}."
             h = self._q(rms_norm(x, w[b + "attn_norm.weight"], s.rms_eps))
-            q = (h @ w[b + "attn_q.weight"].T).reshape(T, s.n_q, s.head_dim)
-            k = (h @ w[b + "attn_k.weight"].T).reshape(T, s.n_kv, s.head_dim)
-            v = (h @ w[b + "attn_v.weight"].T).reshape(T, s.n_kv, s.head_dim)
-            if s.qk_norm:
-                q = rms_norm(q, w[b + "attn_q_norm.weight"], s.rms_eps)
-                k = rms_norm(k, w[b + "attn_k_norm.weight"], s.rms_eps)
-            q = rope_neox(q, pos, self.inv_freq)
-            k = rope_neox(k, pos, self.inv_freq)
-            k = k.half().float()
-            v = v.half().float()
-            self.k[il] = torch.cat([self.k[il], k], 0)
-            self.v[il] = torch.cat([self.v[il], v], 0)
-            G = s.n_q // s.n_kv
-            kk = self.k[il].repeat_interleave(G, 1)      # [S, n_q, D]
-            vv = self.v[il].repeat_interleave(G, 1)
-            S = kk.shape[0]
-            sc = torch.einsum("thd,shd->hts", q, kk) / math.sqrt(s.head_dim)
-            mask = torch.arange(S, device=self.device)[None, :] > pos[:, None]
-            sc = sc.masked_fill(mask[None], -float("inf"))
-            pr = torch.softmax(sc, -1)
-            att = torch.einsum("hts,shd->thd", pr, vv).reshape(T, s.q_rows)
+            att = self._mla(il, h, pos) if s.mla else self._gqa(il, h, pos)
             x = x + self._q(att) @ w[b + "attn_output.weight"].T
             hn = rms_norm(x, w[b + "ffn_norm.weight"], s.rms_eps)
             if s.layer_is_moe(il):
@@ -131,6 +179,10 @@ class CpuModel:
                         a = self._q((torch.nn.functional.silu(g) * u)[None])[0]
                         acc = acc + wts[t, j] * (a @ w[b + "ffn_down_exps.weight"][e].T)
                     y[t] = acc
+                if s.n_shared:
+                    g = hq @ w[b + "ffn_gate_shexp.weight"].T
+                    u = hq @ w[b + "ffn_up_shexp.weight"].T
+                    y = y + self._q(torch.nn.functional.silu(g) * u) @ w[b + "ffn_down_shexp.weight"].T
                 x = x + y
             else:
                 hq = self._q(hn)

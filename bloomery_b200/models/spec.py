@@ -27,6 +27,11 @@ class ModelSpec:
     rms_eps: float = 1e-6
     rope_theta: float = 1e6
     rope_scale: float = 1.0
+    rope_yarn_factor: float = 1.0     # > 1: YaRN-scaled frequencies
+    rope_yarn_orig_ctx: int = 4096
+    rope_yarn_beta_fast: float = 32.0
+    rope_yarn_beta_slow: float = 1.0
+    rope_mscale_all_dim: float = 0.0
     qk_norm: bool = True
     # FFN
     dense_inter: int = 0
@@ -121,6 +126,9 @@ class ModelSpec:
                 rope_dim=int(a("rope.dimension_count", 64)),
                 nope_dim=int(a("attention.key_length", 192)) - int(a("rope.dimension_count", 64)),
                 v_dim=int(a("attention.value_length", 128)), n_mtp=int(a("nextn_predict_layers", 0) or 0),
+                rope_yarn_factor=float(a("rope.scaling.factor", 1.0) or 1.0) if a("rope.scaling.type", "") == "yarn" else 1.0,
+                rope_yarn_orig_ctx=int(a("rope.scaling.original_context_length", 4096) or 4096),
+                rope_mscale_all_dim=float(a("rope.scaling.yarn_log_multiplier", 0.0) or 0.0) * 10.0,
             )
         raise ValueError(f"architecture {arch!r} has no seat in this build")
 
@@ -151,7 +159,7 @@ class ModelSpec:
                        n_group=int(c.get("n_group", 1) or 1), topk_group=int(c.get("topk_group", 1) or 1), mla=True,
                        q_lora=int(c.get("q_lora_rank") or 0), kv_lora=int(c.get("kv_lora_rank", 512)), rope_dim=rope,
                        nope_dim=nope, v_dim=int(c.get("v_head_dim", 128)), n_mtp=int(c.get("num_nextn_predict_layers", 0) or 0),
-                       **common)
+                       **_yarn_fields(c.get("rope_scaling")), **common)
         if kind in ("qwen3_moe", "qwen3moe", "qwen3moeforcausallm", "qwen3", "llama", "qwen2", "mistral", "qwen3forcausallm"):
             n_exp = int(c.get("num_experts", 0) or 0)
             return cls(arch="qwen3moe" if n_exp else ("qwen3" if "qwen3" in kind else "llama"),
@@ -173,7 +181,12 @@ class ModelSpec:
                     "moe_intermediate_size": self.moe_inter, "n_shared_experts": self.n_shared,
                     "first_k_dense_replace": self.first_dense, "scoring_func": self.router_mode,
                     "norm_topk_prob": self.router_renorm, "routed_scaling_factor": self.router_scale,
-                    "n_group": self.n_group, "topk_group": self.topk_group, "num_nextn_predict_layers": self.n_mtp}
+                    "n_group": self.n_group, "topk_group": self.topk_group, "num_nextn_predict_layers": self.n_mtp,
+                    "rope_scaling": None if self.rope_yarn_factor <= 1.0 else {
+                        "type": "yarn", "factor": self.rope_yarn_factor,
+                        "original_max_position_embeddings": self.rope_yarn_orig_ctx, "beta_fast": self.rope_yarn_beta_fast,
+                        "beta_slow": self.rope_yarn_beta_slow, "mscale": self.rope_mscale_all_dim,
+                        "mscale_all_dim": self.rope_mscale_all_dim}}
         return {"model_type": "qwen3_moe" if self.is_moe else ("qwen3" if self.qk_norm else "llama"),
                 "architectures": ["Qwen3MoeForCausalLM" if self.is_moe else "Qwen3ForCausalLM"],
                 "num_hidden_layers": self.n_layer, "hidden_size": self.hidden, "num_attention_heads": self.n_q,
@@ -183,11 +196,40 @@ class ModelSpec:
                 "moe_intermediate_size": self.moe_inter, "norm_topk_prob": self.router_renorm}
 
 
+def _yarn_fields(rs) -> Dict[str, Any]:
+    if not isinstance(rs, dict) or str(rs.get("type", rs.get("rope_type", ""))).lower() != "yarn":
+        return {}
+    return {"rope_yarn_factor": float(rs.get("factor", 1.0)),
+            "rope_yarn_orig_ctx": int(rs.get("original_max_position_embeddings", 4096)),
+            "rope_yarn_beta_fast": float(rs.get("beta_fast", 32.0)), "rope_yarn_beta_slow": float(rs.get("beta_slow", 1.0)),
+            "rope_mscale_all_dim": float(rs.get("mscale_all_dim", 0.0))}
+
+
 # The named benchmark / test shapes.
 def tiny_qwen3moe() -> ModelSpec:
     return ModelSpec(arch="qwen3moe", name="tiny-qwen3moe", n_layer=4, hidden=512, n_q=8, n_kv=2, head_dim=64,
                      vocab=32000, ctx_train=4096, rms_eps=1e-6, rope_theta=1e6, qk_norm=True, n_expert=16, n_used=4,
                      moe_inter=256)
+
+
+def tiny_deepseek() -> ModelSpec:
+    """The DeepSeek-V3 layer plan at toy size: MLA (latent 512 + rope 64), a leading dense layer, sigmoid router
+    with selection bias and groups, one shared expert."""
+    return ModelSpec(arch="deepseek2", name="tiny-deepseek", n_layer=3, hidden=512, n_q=8, n_kv=8, head_dim=192,
+                     vocab=8192, ctx_train=4096, rms_eps=1e-6, rope_theta=1e4, qk_norm=False, dense_inter=1024,
+                     n_expert=16, n_used=4, moe_inter=256, n_shared=1, shared_inter=256, first_dense=1,
+                     router_mode="sigmoid", router_renorm=True, router_scale=2.5, n_group=4, topk_group=2, mla=True,
+                     q_lora=256, kv_lora=512, rope_dim=64, nope_dim=128, v_dim=128, rope_yarn_factor=4.0,
+                     rope_yarn_orig_ctx=1024, rope_mscale_all_dim=1.0)
+
+
+def deepseek_v3() -> ModelSpec:
+    return ModelSpec(arch="deepseek2", name="deepseek-v3-shaped", n_layer=61, hidden=7168, n_q=128, n_kv=128,
+                     head_dim=192, vocab=129280, ctx_train=163840, rms_eps=1e-6, rope_theta=1e4, qk_norm=False,
+                     dense_inter=18432, n_expert=256, n_used=8, moe_inter=2048, n_shared=1, shared_inter=2048,
+                     first_dense=3, router_mode="sigmoid", router_renorm=True, router_scale=2.5, n_group=8, topk_group=4,
+                     mla=True, q_lora=1536, kv_lora=512, rope_dim=64, nope_dim=128, v_dim=128, n_mtp=1,
+                     rope_yarn_factor=40.0, rope_yarn_orig_ctx=4096, rope_mscale_all_dim=1.0)
 
 
 def qwen3_30b_a3b() -> ModelSpec:

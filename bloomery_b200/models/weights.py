@@ -37,7 +37,7 @@ def q4_k_m_type(name: str, il: int, n_layer: int) -> str:
         return "F32"
     if name == "output.weight":
         return "Q6_K"
-    if name.endswith("attn_v.weight") or name.endswith("ffn_down_exps.weight") or name.endswith("ffn_down.weight"):
+    if name.endswith("attn_v.weight") or name.endswith("ffn_down_exps.weight") or name.endswith("ffn_down.weight") or name.endswith("ffn_down_shexp.weight"):
         return "Q6_K" if use_more_bits(il, n_layer) else "Q4_K"
     return "Q4_K"
 
@@ -74,19 +74,43 @@ def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K
     for il in range(L):
         b = f"blk.{il}."
         yield emit(b + "attn_norm.weight", (H,), il, ones=True)
-        yield emit(b + "attn_q.weight", (spec.q_rows, H), il)
-        yield emit(b + "attn_k.weight", (spec.kv_rows, H), il)
-        yield emit(b + "attn_v.weight", (spec.kv_rows, H), il)
-        if spec.qk_norm:
-            yield emit(b + "attn_q_norm.weight", (spec.head_dim,), il, ones=True)
-            yield emit(b + "attn_k_norm.weight", (spec.head_dim,), il, ones=True)
-        yield emit(b + "attn_output.weight", (H, spec.q_rows), il)
+        if spec.mla:
+            qk = spec.nope_dim + spec.rope_dim
+            if spec.q_lora:
+                yield emit(b + "attn_q_a.weight", (spec.q_lora, H), il)
+                yield emit(b + "attn_q_a_norm.weight", (spec.q_lora,), il, ones=True)
+                yield emit(b + "attn_q_b.weight", (spec.n_q * qk, spec.q_lora), il, std_=0.05)
+            else:
+                yield emit(b + "attn_q.weight", (spec.n_q * qk, H), il)
+            yield emit(b + "attn_kv_a_mqa.weight", (spec.kv_lora + spec.rope_dim, H), il, std_=0.05)
+            yield emit(b + "attn_kv_a_norm.weight", (spec.kv_lora,), il, ones=True)
+            # the per-head products keep float weights: [head][nope][latent] and [head][v][latent]
+            yield (b + "attn_k_b.weight", (spec.n_q, spec.nope_dim, spec.kv_lora), "F32",
+                   _rand((spec.n_q * spec.nope_dim, spec.kv_lora), 0.05, gen, device).view(torch.uint8))
+            yield (b + "attn_v_b.weight", (spec.n_q, spec.v_dim, spec.kv_lora), "F32",
+                   _rand((spec.n_q * spec.v_dim, spec.kv_lora), 0.05, gen, device).view(torch.uint8))
+            yield emit(b + "attn_output.weight", (H, spec.n_q * spec.v_dim), il)
+        else:
+            yield emit(b + "attn_q.weight", (spec.q_rows, H), il)
+            yield emit(b + "attn_k.weight", (spec.kv_rows, H), il)
+            yield emit(b + "attn_v.weight", (spec.kv_rows, H), il)
+            if spec.qk_norm:
+                yield emit(b + "attn_q_norm.weight", (spec.head_dim,), il, ones=True)
+                yield emit(b + "attn_k_norm.weight", (spec.head_dim,), il, ones=True)
+            yield emit(b + "attn_output.weight", (H, spec.q_rows), il)
         yield emit(b + "ffn_norm.weight", (H,), il, ones=True)
         if spec.layer_is_moe(il):
             yield emit(b + "ffn_gate_inp.weight", (spec.n_expert, H), il)
             yield emit(b + "ffn_gate_exps.weight", (spec.n_expert, spec.moe_inter, H), il)
             yield emit(b + "ffn_up_exps.weight", (spec.n_expert, spec.moe_inter, H), il)
             yield emit(b + "ffn_down_exps.weight", (spec.n_expert, H, spec.moe_inter), il)
+            if spec.router_mode == "sigmoid":
+                yield (b + "exp_probs_b.bias", (spec.n_expert,), "F32",
+                       _rand((1, spec.n_expert), 0.05, gen, device).view(torch.uint8))
+            if spec.n_shared:
+                yield emit(b + "ffn_gate_shexp.weight", (spec.shared_inter, H), il)
+                yield emit(b + "ffn_up_shexp.weight", (spec.shared_inter, H), il)
+                yield emit(b + "ffn_down_shexp.weight", (H, spec.shared_inter), il)
         else:
             yield emit(b + "ffn_gate.weight", (spec.dense_inter, H), il)
             yield emit(b + "ffn_up.weight", (spec.dense_inter, H), il)
@@ -111,6 +135,19 @@ def spec_metadata(spec: ModelSpec) -> Dict[str, object]:
         f"{a}.rope.freq_base": float(spec.rope_theta),
         f"{a}.vocab_size": spec.vocab,
     }
+    if spec.mla:
+        md.update({f"{a}.attention.q_lora_rank": spec.q_lora, f"{a}.attention.kv_lora_rank": spec.kv_lora,
+                   f"{a}.rope.dimension_count": spec.rope_dim, f"{a}.attention.key_length": spec.nope_dim + spec.rope_dim,
+                   f"{a}.attention.value_length": spec.v_dim, f"{a}.leading_dense_block_count": spec.first_dense,
+                   f"{a}.feed_forward_length": spec.dense_inter, f"{a}.expert_shared_count": spec.n_shared,
+                   f"{a}.expert_gating_func": 2 if spec.router_mode == "sigmoid" else 1,
+                   f"{a}.expert_weights_norm": bool(spec.router_renorm), f"{a}.expert_weights_scale": float(spec.router_scale),
+                   f"{a}.expert_group_count": spec.n_group, f"{a}.expert_group_used_count": spec.topk_group,
+                   f"{a}.nextn_predict_layers": spec.n_mtp})
+        if spec.rope_yarn_factor > 1.0:
+            md.update({f"{a}.rope.scaling.type": "yarn", f"{a}.rope.scaling.factor": float(spec.rope_yarn_factor),
+                       f"{a}.rope.scaling.original_context_length": spec.rope_yarn_orig_ctx,
+                       f"{a}.rope.scaling.yarn_log_multiplier": float(spec.rope_mscale_all_dim) * 0.1})
     if spec.is_moe:
         md[f"{a}.expert_count"] = spec.n_expert
         md[f"{a}.expert_used_count"] = spec.n_used
@@ -149,6 +186,9 @@ class Weights:
             self.f[name] = t
             self.n_bytes += t.numel() * 4
             return
+        if name.endswith(("attn_k_b.weight", "attn_v_b.weight", "attn_kv_b.weight")):
+            self._add_mla_heads(name, shape, qtype, raw)
+            return
         if qtype not in INT_DOT_TYPES and qtype not in FLOAT_TYPES:
             raise UnsupportedType(f"{name}: block type {qtype} has no kernel in this build")
         flat = raw.reshape(-1, raw.shape[-1])
@@ -157,6 +197,41 @@ class Weights:
             res = res.reshape(shape[0], shape[1], -1)
         self.q[name] = QWeight(res, qtype, k)
         self.n_bytes += res.numel()
+
+    def _add_mla_heads(self, name: str, shape, qtype: str, raw: torch.Tensor) -> None:
+        """The per-head MLA products run on float weights laid out [head][nope][latent] / [head][v][latent]:
+        bf16 stays bf16, anything else is decoded to f32 (exact).  Accepts the split GGUF tensors
+        (``attn_k_b`` stored [head][latent][nope], ``attn_v_b`` [head][v][latent]) and the joint checkpoint
+        matrix ``attn_kv_b`` [head * (nope + v), latent]."""
+        s = self.spec
+        k = shape[-1]
+        flat = raw.reshape(-1, raw.shape[-1])
+        if qtype == "BF16":
+            w = flat.view(torch.bfloat16)
+        elif qtype == "F32":
+            w = flat.view(torch.float32)
+        elif qtype == "F16":
+            w = flat.view(torch.float16).float()
+        elif qtype in PLANE_TYPES:
+            from ..formats.planes import resident_dequantize
+            w = resident_dequantize(flat, qtype, k)
+        else:
+            w = quant.dequantize(flat, qtype, k)
+        stem = name[:-len(name.split(".")[-2]) - len(".weight")]
+        if name.endswith("attn_kv_b.weight"):
+            w = w.reshape(s.n_q, s.nope_dim + s.v_dim, s.kv_lora)
+            parts = {"attn_k_b.weight": w[:, :s.nope_dim], "attn_v_b.weight": w[:, s.nope_dim:]}
+        elif name.endswith("attn_k_b.weight"):
+            if k == s.kv_lora:
+                parts = {"attn_k_b.weight": w.reshape(s.n_q, s.nope_dim, s.kv_lora)}
+            else:                       # the GGUF order [head][latent][nope]
+                parts = {"attn_k_b.weight": w.reshape(s.n_q, s.kv_lora, s.nope_dim).transpose(1, 2)}
+        else:
+            parts = {"attn_v_b.weight": w.reshape(s.n_q, s.v_dim, s.kv_lora)}
+        for leaf, t in parts.items():
+            t = t.contiguous().clone()
+            self.f[stem + leaf] = t
+            self.n_bytes += t.numel() * t.element_size()
 
     @classmethod
     def from_items(cls, spec: ModelSpec, items: Iterator[TensorItem], device) -> "Weights":

@@ -194,3 +194,38 @@ def sample_rows(logits, V: int, M: int, params, seeds, draws, out_token, *, rece
                                I(recent.shape[1] if recent is not None else 0), p(n_recent), p(params), p(seeds), p(draws),
                                p(work), p(out_token), p(out_n_cand), p(fault), stream())
     check(rc, "bl_sample_rows")
+
+
+# ---- multi-head latent attention (csrc/mla_decode.cu) ---------------------------------
+def _fw(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 30
+    raise TypeError(f"per-head MLA weights are f32 or bf16, got {t.dtype}")
+
+
+def mla_kv_append(kv, gain, inv_freq, eps: float, M: int, row_pos, row_seq, block_table, n_pages: int, cache, fault,
+                  layer: int, kv_lora: int = 512, rope_dim: int = 64) -> None:
+    """``kv`` fp32 [M, >=576] (a view is fine): RMSNorm the latent, rotate the shared key part, append as f16."""
+    rc = cuda().bl_mla_kv_append(p(kv), L(kv.stride(0)), p(gain), p(inv_freq), F(eps), I(kv_lora), I(rope_dim), I(M),
+                                 p(row_pos), p(row_seq), p(block_table), I(block_table.shape[1]), I(n_pages), p(cache),
+                                 p(fault), I(layer), stream())
+    check(rc, "bl_mla_kv_append")
+
+
+def mla_q_absorb(q, w_kb, inv_freq, scale: float, n_q: int, nope: int, M: int, row_pos, row_seq, q_lat,
+                 kv_lora: int = 512, rope_dim: int = 64) -> None:
+    """``q`` fp32 [M, n_q * (nope + 64)] -> ``q_lat`` fp32 [M, n_q, 576], pre-scaled; ``w_kb`` [n_q, nope, 512]."""
+    rc = cuda().bl_mla_q_absorb(p(q), L(q.stride(0)), p(w_kb), I(_fw(w_kb)), p(inv_freq), F(scale), I(n_q), I(nope),
+                                I(kv_lora), I(rope_dim), I(M), p(row_pos), p(row_seq), p(q_lat), stream())
+    check(rc, "bl_mla_q_absorb")
+
+
+def mla_flash_decode(q_lat, cache, row_pos, row_seq, block_table, n_pages: int, n_q: int, M: int, n_seg: int,
+                     ctx_limit: int, part_ml, part_acc, w_vb, v_dim: int, out, outq, outds, fault, layer: int) -> None:
+    """Latent flash decode (segments + merge) with the per-head value up-projection and the q8 form for o_proj."""
+    rc = cuda().bl_mla_flash_decode(p(q_lat), p(cache), p(row_pos), p(row_seq), p(block_table), I(block_table.shape[1]),
+                                    I(n_pages), I(n_q), I(M), I(n_seg), I(ctx_limit), p(part_ml), p(part_acc), p(w_vb),
+                                    I(_fw(w_vb)), I(v_dim), p(out), p(outq), p(outds), p(fault), I(layer), stream())
+    check(rc, "bl_mla_flash_decode")

@@ -59,17 +59,21 @@ class DecodeEngine:
         self.w = weights
         self.spec: ModelSpec = weights.spec
         s = self.spec
-        if s.mla:
-            raise ValueError("MLA models run on MlaEngine")
+        if s.mla and (s.kv_lora != 512 or s.rope_dim != 64 or s.nope_dim > 128 or s.v_dim > 128 or s.v_dim % 32):
+            raise ValueError("the latent attention kernels serve latent 512 + rope 64, nope and v up to 128")
         self.device = weights.device
         dev = self.device
         self.n_slots, self.slot_ctx = n_slots, slot_ctx
         self.use_graphs = use_graphs
         self.bound_s = engine_bound_s
         max_pages = (slot_ctx + PAGE - 1) // PAGE
-        self.kv = KvPool(s.n_layer, s.n_kv, s.head_dim, n_slots * max_pages, n_slots, max_pages, dev)
         sm = K.sm_count(dev)
-        self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, sm // s.n_kv)))
+        if s.mla:
+            self.kv = KvPool(s.n_layer, 1, s.kv_lora + s.rope_dim, n_slots * max_pages, n_slots, max_pages, dev, v_dim=0)
+            self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, 2 * sm // ((s.n_q + 15) // 16))))
+        else:
+            self.kv = KvPool(s.n_layer, s.n_kv, s.head_dim, n_slots * max_pages, n_slots, max_pages, dev)
+            self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, sm // s.n_kv)))
         H, V = s.hidden, s.vocab
         f32 = dict(dtype=torch.float32, device=dev)
         i32 = dict(dtype=torch.int32, device=dev)
@@ -85,13 +89,29 @@ class DecodeEngine:
         self.params_host = self._stage[0]
         self.tokens, self.row_pos, self.row_seq = self.params[0], self.params[1], self.params[2]
         self.x = torch.zeros(R, H, **f32)
-        qkv_w = s.q_rows + 2 * s.kv_rows
-        self.qkv = torch.zeros(R, qkv_w, **f32)
-        self.q_out = torch.zeros(R, s.n_q, s.head_dim, **f32)
-        self.part_ml = torch.zeros(R * s.n_q * self.n_seg * 2, **f32)
-        self.part_acc = torch.zeros(R * s.n_q * self.n_seg * s.head_dim, **f32)
-        self.attn_q = torch.zeros(R, s.q_rows, dtype=torch.int8, device=dev)
-        self.attn_ds = torch.zeros(R, s.q_rows // 32, 2, **f32)
+        from ..models.rope import attn_scale, inv_freq_table
+        self.attn_scale = attn_scale(s)
+        if s.mla:
+            qk = s.nope_dim + s.rope_dim
+            self.o_in = s.n_q * s.v_dim
+            # first projection: [q_a (or q) | latent + rope]; the q_b product follows when q is low-rank
+            self.qa_w = s.q_lora if s.q_lora else s.n_q * qk
+            self.qkv = torch.zeros(R, self.qa_w + s.kv_lora + s.rope_dim, **f32)
+            self.q_full = torch.zeros(R, s.n_q * qk, **f32) if s.q_lora else None
+            self.q_out = torch.zeros(R, s.n_q, s.kv_lora + s.rope_dim, **f32)
+            self.part_ml = torch.zeros(R * s.n_q * self.n_seg * 2, **f32)
+            self.part_acc = torch.zeros(R * s.n_q * self.n_seg * s.kv_lora, **f32)
+            self.inv_freq = inv_freq_table(s, s.rope_dim).to(dev)
+        else:
+            self.o_in = s.q_rows
+            qkv_w = s.q_rows + 2 * s.kv_rows
+            self.qkv = torch.zeros(R, qkv_w, **f32)
+            self.q_out = torch.zeros(R, s.n_q, s.head_dim, **f32)
+            self.part_ml = torch.zeros(R * s.n_q * self.n_seg * 2, **f32)
+            self.part_acc = torch.zeros(R * s.n_q * self.n_seg * s.head_dim, **f32)
+            self.inv_freq = inv_freq_table(s, s.head_dim).to(dev)
+        self.attn_q = torch.zeros(R, self.o_in, dtype=torch.int8, device=dev)
+        self.attn_ds = torch.zeros(R, self.o_in // 32, 2, **f32)
         self.xq = torch.zeros(R, H, dtype=torch.int8, device=dev)
         self.xds = torch.zeros(R, H // 32, 2, **f32)
         if s.is_moe:
@@ -101,6 +121,11 @@ class DecodeEngine:
             self.actq = torch.zeros(R, s.n_used, s.moe_inter, dtype=torch.int8, device=dev)
             self.actds = torch.zeros(R, s.n_used, s.moe_inter // 32, 2, **f32)
             self.heat = torch.zeros(s.n_layer, s.n_expert, **i32)
+            if s.n_shared:
+                self.sh_gu = torch.zeros(R, 2 * s.shared_inter, **f32)
+                self.sh_actq = torch.zeros(R, s.shared_inter, dtype=torch.int8, device=dev)
+                self.sh_actds = torch.zeros(R, s.shared_inter // 32, 2, **f32)
+                self.sh_out = torch.zeros(R, H, **f32)
         if s.dense_inter and (s.first_dense > 0 or not s.is_moe):
             self.gu = torch.zeros(R, 2 * s.dense_inter, **f32)
             self.dactq = torch.zeros(R, s.dense_inter, dtype=torch.int8, device=dev)
@@ -115,14 +140,13 @@ class DecodeEngine:
         self.fault = torch.full((1,), -1, **i32)  # 0xFFFFFFFF
         self.hist_cap = 4096
         self.hist = torch.zeros(self.hist_cap * R, **i32)
-        inv = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float64) / s.head_dim))
-        self.inv_freq = (inv / s.rope_scale).float().to(dev)
         self.graphs: Dict[Tuple[int, bool, bool], torch.cuda.CUDAGraph] = {}
         self.poisoned: Optional[int] = None
         self.slot_len = [0] * n_slots
         self.launches_per_step = 0
         self.steps = 0
-        self.gemm_threshold = 64      # prompts at least this long use the GEMM path (0 = never)
+        # prompts at least this long use the GEMM path (0 = never; the GEMM path serves the GQA + routed-expert plan)
+        self.gemm_threshold = 0 if (s.mla or s.n_shared) else 64
         self.ubatch = 4096
         self._gemm_prefill = None
         self._stream = torch.cuda.Stream(device=dev)
@@ -141,15 +165,7 @@ class DecodeEngine:
         kvp = self.kv
         for il in range(s.n_layer):
             b = f"blk.{il}."
-            K.gemv([w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
-                   x=x, gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il); n += 1
-            K.qk_norm_rope_append(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
-                                  self.inv_freq, s.rms_eps, 1.0 / math.sqrt(s.head_dim), s.head_dim, s.n_q, s.n_kv, M,
-                                  self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out,
-                                  self.fault, il); n += 1
-            K.flash_decode(self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
-                           s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
-                           self.attn_q, self.attn_ds, self.fault, il); n += 2
+            n += self._attn(il, M, x)
             K.gemv([w.q[b + "attn_output.weight"]], M, x, xq=self.attn_q, xds=self.attn_ds, resid=x,
                    fault=self.fault, layer=il); n += 1
             if s.layer_is_moe(il):
@@ -171,6 +187,47 @@ class DecodeEngine:
                                self.counters[2:3]); n += 1
         return n
 
+    def _attn(self, il: int, M: int, x: torch.Tensor) -> int:
+        """Attention of one layer up to the q8 rows that feed o_proj; returns the launch count."""
+        s, w, kvp = self.spec, self.w, self.kv
+        b = f"blk.{il}."
+        if s.mla:
+            return self._attn_mla(il, M, x)
+        K.gemv([w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
+               x=x, gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il)
+        K.qk_norm_rope_append(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
+                              self.inv_freq, s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M,
+                              self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out,
+                              self.fault, il)
+        K.flash_decode(self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
+                       s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
+                       self.attn_q, self.attn_ds, self.fault, il)
+        return 4
+
+    def _attn_mla(self, il: int, M: int, x: torch.Tensor) -> int:
+        """Latent attention: [q_a | kv_a] product, latent append, (q_b product), absorb, latent flash + value
+        up-projection (the reference's MLA seat: ``crates/gpu/src/flash.rs``, deepseek2 chain)."""
+        s, w, kvp = self.spec, self.w, self.kv
+        b = f"blk.{il}."
+        n = 0
+        first = w.q[b + "attn_q_a.weight"] if s.q_lora else w.q[b + "attn_q.weight"]
+        K.gemv([first, w.q[b + "attn_kv_a_mqa.weight"]], M, self.qkv, x=x, gain=w.f[b + "attn_norm.weight"],
+               eps=s.rms_eps, fault=self.fault, layer=il); n += 1
+        K.mla_kv_append(self.qkv[:, self.qa_w:], w.f[b + "attn_kv_a_norm.weight"], self.inv_freq, s.rms_eps, M,
+                        self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], self.fault, il); n += 1
+        if s.q_lora:
+            K.gemv([w.q[b + "attn_q_b.weight"]], M, self.q_full, x=self.qkv[:, :s.q_lora],
+                   gain=w.f[b + "attn_q_a_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il); n += 1
+            q = self.q_full
+        else:
+            q = self.qkv[:, :self.qa_w]
+        K.mla_q_absorb(q, w.f[b + "attn_k_b.weight"], self.inv_freq, self.attn_scale, s.n_q, s.nope_dim, M,
+                       self.row_pos, self.row_seq, self.q_out); n += 1
+        K.mla_flash_decode(self.q_out, kvp.k[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages, s.n_q, M,
+                           self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, w.f[b + "attn_v_b.weight"], s.v_dim,
+                           None, self.attn_q, self.attn_ds, self.fault, il); n += 2
+        return n
+
     def _moe(self, il: int, M: int, x: torch.Tensor) -> int:
         """Router + routed experts + combine of one layer (3 launches); returns the launch count."""
         s, w = self.spec, self.w
@@ -181,9 +238,18 @@ class DecodeEngine:
                       w.q[b + "ffn_up_exps.weight"], s.n_expert, s.n_used, M, self.actq, self.actds, None,
                       self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=self.r_wts,
                       heat=self.heat[il])
+        extra, n = None, 3
+        if s.n_shared:
+            # the shared expert reads the router's q8 rows and lands as an extra addend of the combine
+            K.gemv([w.q[b + "ffn_gate_shexp.weight"], w.q[b + "ffn_up_shexp.weight"]], M, self.sh_gu, xq=self.xq,
+                   xds=self.xds, fault=self.fault, layer=il)
+            K.swiglu_q8(self.sh_gu, s.shared_inter, M, self.sh_actq, self.sh_actds)
+            K.gemv([w.q[b + "ffn_down_shexp.weight"]], M, self.sh_out, xq=self.sh_actq, xds=self.sh_actds,
+                   fault=self.fault, layer=il)
+            extra, n = self.sh_out, 6
         K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, None, w.q[b + "ffn_down_exps.weight"],
-                       s.n_expert, s.n_used, M, x, None, x, self.fault, il)
-        return 3
+                       s.n_expert, s.n_used, M, x, extra, x, self.fault, il)
+        return n
 
     def _after_pass(self, n_rows: int) -> None:
         """Hook between passes (residency boundaries live here in the tiered engine)."""

@@ -22,13 +22,15 @@ class OutOfPages(RuntimeError):
 
 class KvPool:
     def __init__(self, n_layer: int, n_kv: int, head_dim: int, n_pages: int, n_slots: int, max_pages_per_slot: int,
-                 device, dtype=torch.float16):
+                 device, dtype=torch.float16, v_dim: Optional[int] = None):
         self.n_layer, self.n_kv, self.head_dim = n_layer, n_kv, head_dim
         self.n_pages, self.n_slots, self.max_pages = n_pages, n_slots, max_pages_per_slot
         self.device = torch.device(device)
         # [layer][page][kv head][position in page][dim]
         self.k = torch.zeros(n_layer, n_pages, n_kv, PAGE, head_dim, dtype=dtype, device=self.device)
-        self.v = torch.zeros(n_layer, n_pages, n_kv, PAGE, head_dim, dtype=dtype, device=self.device)
+        # a latent cache (MLA) keeps one row per position that serves as key and value: v_dim = 0
+        self.v = torch.zeros(n_layer, n_pages, n_kv, PAGE, head_dim if v_dim is None else v_dim, dtype=dtype,
+                             device=self.device)
         self.table_host = torch.full((n_slots, max_pages_per_slot), -1, dtype=torch.int32,
                                      pin_memory=self.device.type == "cuda")
         self.table = torch.full((n_slots, max_pages_per_slot), -1, dtype=torch.int32, device=self.device)
@@ -39,7 +41,7 @@ class KvPool:
 
     @property
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
     def free_pages(self) -> int:
         return len(self.free)

@@ -309,3 +309,35 @@ def test_checkpoint_folder_opens_as_model(scheme, tmp_path):
     assert w.q["token_embd.weight"].qtype == "BF16" and w.f["blk.0.attn_norm.weight"].dtype == torch.float32
     out = CpuModel(w).forward(torch.arange(6))
     assert out.shape == (6, 1024) and bool(torch.isfinite(out).all())
+
+
+def test_deepseek_shape_roundtrips_and_oracle_runs(tmp_path):
+    """The MLA / shared-expert / sigmoid-router plan survives GGUF and config.json, and the oracle's
+    incremental decode equals its one-shot forward."""
+    import dataclasses
+    from bloomery_b200.formats.gguf import Gguf
+    from bloomery_b200.models import weights as W
+    from bloomery_b200.models.cpu_ref import CpuModel
+    from bloomery_b200.models.spec import ModelSpec, tiny_deepseek
+    spec = tiny_deepseek()
+    spec.vocab = 512
+    items = list(W.synth_tensors(spec, "cpu", seed=2))
+    W.write_gguf(spec, iter(items), str(tmp_path / "d.gguf"))
+    sp2, w2, g = W.load_gguf(str(tmp_path / "d.gguf"), "cpu")
+    keys = ("n_layer", "hidden", "n_q", "q_lora", "kv_lora", "rope_dim", "nope_dim", "v_dim", "first_dense", "n_shared",
+            "router_mode", "router_renorm", "n_group", "topk_group", "n_expert", "n_used", "rope_yarn_factor",
+            "rope_yarn_orig_ctx")
+    for k in keys:
+        assert getattr(sp2, k) == getattr(spec, k), k
+    assert abs(sp2.router_scale - spec.router_scale) < 1e-6 and abs(sp2.rope_mscale_all_dim - 1.0) < 1e-6
+    sp3 = ModelSpec.from_hf_config(spec.to_hf_config())
+    for k in keys:
+        assert getattr(sp3, k) == getattr(spec, k), k
+    assert w2.f["blk.0.attn_k_b.weight"].shape == (8, 128, 512)
+    m = CpuModel(w2)
+    toks = torch.arange(7) * 31 % 512
+    full = m.forward(toks)
+    m.reset()
+    inc = torch.cat([m.forward(toks[:4]), m.forward(toks[4:])])
+    # batched and single-row products round differently, which can flip a q8 activation code
+    assert ((full - inc).abs().max() / full.abs().max()).item() < 2e-2
