@@ -68,6 +68,137 @@ def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, fre
             "kv_bytes": slot_ctx * n_slots * per_tok, "weights_bytes": weights_bytes}
 
 
+def _inventory(path: str):
+    """(spec, weights bytes, kind) of a model path: a GGUF file / split, or a checkpoint folder."""
+    from ..formats.gguf import Gguf, GgufError
+    from ..models.spec import ModelSpec
+    try:
+        if os.path.isdir(path):
+            from ..formats.safetensors import Folder, SafetensorsError
+            try:
+                f = Folder(path)
+            except SafetensorsError as exc:
+                raise Refusal(Code.LOAD, str(exc)) from None
+            if not f.config:
+                raise Refusal(Code.LOAD, f"{path}: no config.json beside the tensors")
+            nbytes = sum(f.info(n).end - f.info(n).begin for n in f.names())
+            spec = ModelSpec.from_hf_config(f.config)
+            f.close()
+            return spec, nbytes, "folder"
+        inv = Gguf.inventory(path)
+        return ModelSpec.from_gguf(inv), sum(t.n_bytes for t in inv.tensors.values()), "gguf"
+    except GgufError as exc:
+        raise Refusal(Code.LOAD, str(exc)) from None
+    except (ValueError, KeyError) as exc:
+        raise Refusal(Code.UNSUPPORTED, str(exc)) from None
+
+
+def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional[str]):
+    """Plan, load and build the engine the flags ask for: one GPU, several GPUs in lockstep, experts on the
+    host beside a GPU, or the CPU alone.  Returns (engine, chat template source, bos text, eos text)."""
+    import torch
+    from .engine import CpuEngine, GpuEngine
+    path = opts["model"]
+    spec, weights_bytes, kind = _inventory(path)
+    free = [torch.cuda.mem_get_info(i)[0] for i in range(n_vis)]
+    plan = plan_for(opts, spec, weights_bytes, n_vis, free)
+    pl = plan["placement"]
+    opts["_place_word"] = pl.word()
+    records.write("plan", model=spec.name, devices=[f"CUDA{d}" for d in pl.devices], weights_bytes=weights_bytes,
+                  kv_bytes=plan["kv_bytes"], ctx=plan["ctx_total"], slots=plan["n_slots"], place=pl.word())
+    records.write("need", weights_bytes=weights_bytes, kv_bytes_per_token=spec.kv_bytes_per_token(), host_bytes=0, fits=True)
+    records.write("ctx", asked=int(opts.get("ctx") or 0), served=plan["slot_ctx"], trained=spec.ctx_train)
+    records.write("parallel", slots=plan["n_slots"], slot_ctx=plan["slot_ctx"])
+    if opts["plan"] or opts["dry_run"]:
+        out = {"place": pl.word(), "devices": pl.devices, "slots": plan["n_slots"], "slot_ctx": plan["slot_ctx"],
+               "weights_bytes": weights_bytes, "kv_bytes": plan["kv_bytes"]}
+        print(json.dumps(out) if opts["json"] else "\n".join(f"{k}: {v}" for k, v in out.items()))
+        server.state.stop_cause = "plan"
+        server.state.stop_event.set()
+        raise _PlanOnly()
+    server.state.phase = "load"
+    t0 = time.time()
+    from ..models.weights import open_model
+    from ..ops import decode as K
+    from .tokenizer import from_folder, from_gguf
+    name = opts.get("alias") or spec.name or os.path.basename(path.rstrip("/"))
+
+    def surface(handle):
+        if kind == "gguf":
+            tk = from_gguf(handle, spec.vocab)
+            tsrc = template_src if template_src is not None else handle.get("tokenizer.chat_template")
+        else:
+            tk = from_folder(path, spec.vocab)
+            tsrc = template_src
+            tc = os.path.join(path, "tokenizer_config.json")
+            if tsrc is None and os.path.exists(tc):
+                tsrc = json.load(open(tc, encoding="utf-8")).get("chat_template")
+        bos = tk.decode([tk.bos_id], skip_special=False) if tk.bos_id >= 0 else ""
+        eos = tk.decode([tk.eos_id], skip_special=False) if tk.eos_id >= 0 else ""
+        return tk, tsrc, bos, eos
+
+    if not pl.devices:
+        if n_vis == 0 and str(opts.get("dev") or "").lower() != "none" and str(opts.get("ngl", "")) != "0":
+            raise Refusal(Code.NO_DEVICE, "no CUDA device is visible; -dev none starts the CPU-only engine on a model that fits host RAM")
+        _, w, handle = open_model(path, "cpu")
+        records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
+        tk, tsrc, bos, eos = surface(handle)
+        return CpuEngine(w, tk, plan["n_slots"], plan["slot_ctx"], name), tsrc, bos, eos
+    K.set_pdl(bool(levers.get("BLOOMERY_PDL")))
+    graphs = bool(levers.get("BLOOMERY_GRAPHS"))
+    bound = float(levers.get("BLOOMERY_ENGINE_BOUND"))
+    if pl.mode == "tp" and len(pl.devices) > 1:
+        if kind != "gguf":
+            raise Refusal(Code.UNSUPPORTED, "several GPUs in lockstep are served from GGUF files; load the folder on one GPU")
+        from ..parallel import serve_tp as TP
+        port = int(os.environ.get("BLOOMERY_TP_PORT", "0")) or (29600 + os.getpid() % 2000)
+        followers = TP.spawn_followers(path, pl.devices, port, plan["n_slots"], plan["slot_ctx"])
+        ctl = TP.init_groups(0, len(pl.devices), pl.devices[0], port)
+        dec, _, handle = TP.open_rank(path, 0, len(pl.devices), pl.devices[0], plan["n_slots"], plan["slot_ctx"],
+                                      use_graphs=graphs)
+        import torch.distributed as dist
+        dist.barrier()
+        records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
+        tk, tsrc, bos, eos = surface(handle)
+        eng = TP.leader_engine(dec, tk, name, TP.Lockstep(ctl))
+        eng.followers = followers
+    else:
+        dev = f"cuda:{pl.devices[0]}"
+        torch.cuda.set_device(pl.devices[0])
+        _, w, handle = open_model(path, dev)
+        records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
+        kw = dict(n_slots=plan["n_slots"], slot_ctx=plan["slot_ctx"], use_graphs=graphs, engine_bound_s=bound)
+        if pl.host_experts != "none" and spec.is_moe:
+            from ..runtime.tiered import TieredEngine
+            if pl.host_experts == "all":
+                resident = 0
+            elif pl.host_experts.startswith("first:"):
+                n_host_layers = min(spec.n_layer, int(pl.host_experts.split(":")[1]))
+                resident = spec.n_expert * (spec.n_layer - n_host_layers) // spec.n_layer // 4 * 4
+            else:
+                resident = 0
+            records.write("setup", phase="tier", seconds=0.0, resident_per_layer=resident, host=pl.host_experts)
+            dec = TieredEngine(w, resident, residency=str(levers.get("BLOOMERY_RESIDENCY")), **kw)
+        else:
+            from ..runtime.engine import DecodeEngine
+            dec = DecodeEngine(w, **kw)
+        dec.ubatch = int(opts.get("ubatch") or 4096)
+        if opts.get("prefill") == "steps":
+            dec.gemm_threshold = 0
+        tk, tsrc, bos, eos = surface(handle)
+        eng = GpuEngine(dec, tk, name)
+    if not opts.get("no_warmup"):
+        t1 = time.time()
+        eng.step([(0, max(0, tk.bos_id), 0)], want_logits=False)
+        eng.reset(0)
+        records.write("setup", phase="warmup", seconds=round(time.time() - t1, 3))
+    return eng, tsrc, bos, eos
+
+
+class _PlanOnly(Exception):
+    pass
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     events.enable()
@@ -118,64 +249,15 @@ def main(argv: Optional[List[str]] = None) -> int:
         if not os.path.exists(opts["model"]):
             raise Refusal(Code.NO_MODEL, f"{opts['model']}: no such file")
         server.state.phase = "plan"
-        from ..formats.gguf import Gguf, GgufError
-        from ..models.spec import ModelSpec
-        try:
-            inv = Gguf.inventory(opts["model"])
-            spec = ModelSpec.from_gguf(inv)
-        except GgufError as exc:
-            raise Refusal(Code.LOAD, str(exc)) from None
-        except ValueError as exc:
-            raise Refusal(Code.UNSUPPORTED, str(exc)) from None
-        weights_bytes = sum(t.n_bytes for t in inv.tensors.values())
-        free = [torch.cuda.mem_get_info(i)[0] for i in range(n_vis)]
-        plan = plan_for(opts, spec, weights_bytes, n_vis, free)
-        pl = plan["placement"]
-        opts["_place_word"] = pl.word()
-        records.write("plan", model=spec.name, devices=[f"CUDA{d}" for d in pl.devices], weights_bytes=weights_bytes,
-                      kv_bytes=plan["kv_bytes"], ctx=plan["ctx_total"], slots=plan["n_slots"], place=pl.word())
-        records.write("need", weights_bytes=weights_bytes, kv_bytes_per_token=spec.kv_bytes_per_token(), host_bytes=0, fits=True)
-        records.write("ctx", asked=int(opts.get("ctx") or 0), served=plan["slot_ctx"], trained=spec.ctx_train)
-        records.write("parallel", slots=plan["n_slots"], slot_ctx=plan["slot_ctx"])
-        if opts["plan"] or opts["dry_run"]:
-            out = {"place": pl.word(), "devices": pl.devices, "slots": plan["n_slots"], "slot_ctx": plan["slot_ctx"],
-                   "weights_bytes": weights_bytes, "kv_bytes": plan["kv_bytes"]}
-            print(json.dumps(out) if opts["json"] else "\n".join(f"{k}: {v}" for k, v in out.items()))
-            server.state.stop_cause = "plan"
-            server.state.stop_event.set()
-            return server.stop()
-        if not pl.devices:
-            raise Refusal(Code.NO_DEVICE, "no CUDA device is visible; the CPU-only engine is started with -dev none on a model that fits host RAM"
-                          if n_vis == 0 and str(opts.get("dev") or "").lower() != "none" else "CPU-only serving goes through CpuEngine")
-        server.state.phase = "load"
-        t0 = time.time()
-        from ..models.weights import load_gguf
-        from ..runtime.engine import DecodeEngine
-        from .tokenizer import from_gguf
-        from ..ops import decode as K
-        K.set_pdl(bool(levers.get("BLOOMERY_PDL")))
-        dev = f"cuda:{pl.devices[0]}"
-        torch.cuda.set_device(pl.devices[0])
-        spec, w, g = load_gguf(opts["model"], dev)
-        records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
-        dec = DecodeEngine(w, n_slots=plan["n_slots"], slot_ctx=plan["slot_ctx"], use_graphs=bool(levers.get("BLOOMERY_GRAPHS")),
-                           engine_bound_s=float(levers.get("BLOOMERY_ENGINE_BOUND")))
-        dec.ubatch = int(opts.get("ubatch") or 4096)
-        if opts.get("prefill") == "steps":
-            dec.gemm_threshold = 0
-        tk = from_gguf(g, spec.vocab)
-        if template_src is None:
-            template_src = g.get("tokenizer.chat_template")
-        bos = tk.decode([tk.bos_id], skip_special=False) if tk.bos_id >= 0 else ""
-        eos = tk.decode([tk.eos_id], skip_special=False) if tk.eos_id >= 0 else ""
-        eng = GpuEngine(dec, tk, opts.get("alias") or spec.name or os.path.basename(opts["model"]))
-        if not opts.get("no_warmup"):
-            t1 = time.time()
-            dec.step([(0, max(0, tk.bos_id), 0)])
-            dec.reset(0)
-            records.write("setup", phase="warmup", seconds=round(time.time() - t1, 3))
+        eng, template_src, bos, eos = open_engine(opts, server, n_vis, template_src)
         server.ready(eng, ChatTemplate(template_src, bos, eos), cache_bytes, int(opts["queue_depth"]))
+        draft = str(levers.get("BLOOMERY_DRAFT")).lower()
+        if draft == "ngram" and server.state.worker is not None:
+            from ..runtime.speculative import NgramDraft, WidthChooser
+            server.state.worker.enable_drafting(NgramDraft(), WidthChooser())
         return server.wait()
+    except _PlanOnly:
+        return server.stop()
     except Refusal as r:
         word, nxt = WORDS.get(r.code, ("refused", ""))
         events.emit("error", code=int(r.code), word=word, message=str(r), next=nxt)

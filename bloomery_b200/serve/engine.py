@@ -208,3 +208,90 @@ class GpuEngine(Engine):
         return {"engine": "cuda", "arch": s.arch, "n_layer": s.n_layer, "n_expert": s.n_expert,
                 "memory": self.dec.memory_report(), "devices": [str(self.dec.device)],
                 "launches_per_step": self.dec.launches_per_step}
+
+
+class CpuEngine(Engine):
+    """The CPU-only engine (``-dev none``): the plain PyTorch model, one KV list per slot, weights shared.
+
+    The reference keeps a host seat for models that fit RAM (``crates/model`` CPU engine;
+    ``crates/gpu-gates/src/bin/bloomery_serve.rs:46``)."""
+
+    max_rows = 8
+
+    def __init__(self, weights, tokenizer: Tokenizer, n_slots: int = 1, slot_ctx: int = 4096, model_name: str = "model"):
+        import copy
+        from ..models.cpu_ref import CpuModel
+        base = CpuModel(weights)
+        self.models = [base] + [copy.copy(base) for _ in range(n_slots - 1)]
+        for m in self.models:
+            m.reset()
+        self.tokenizer, self.model_name = tokenizer, model_name
+        self.n_slots, self.slot_ctx, self.n_vocab = n_slots, slot_ctx, weights.spec.vocab
+        self.spec = weights.spec
+
+    def _cut(self, m, n: int) -> None:
+        if n < m.n_past:
+            m.k = [k[:n] for k in m.k]
+            m.v = [v[:n] for v in m.v]
+            m.n_past = n
+
+    def prefill(self, slot, ids, start):
+        import torch
+        m = self.models[slot]
+        self._cut(m, start)
+        if m.n_past != start:
+            raise EngineError(f"slot {slot}: prompt rows start at {start} but {m.n_past} positions are kept")
+        if len(ids):
+            m.forward(torch.tensor(list(ids)))
+
+    def step(self, rows, want_logits=True):
+        import torch
+        from ..models.cpu_ref import greedy_pick
+        out = []
+        for slot, tok, pos in rows:
+            m = self.models[slot]
+            self._cut(m, pos)
+            if m.n_past != pos:
+                raise EngineError(f"slot {slot}: row at {pos} but {m.n_past} positions are kept")
+            if pos + 1 > self.slot_ctx:
+                raise EngineError(f"slot {slot}: position {pos} is beyond the slot context")
+            lg = m.forward(torch.tensor([tok]))[0]
+            if not bool(torch.isfinite(lg).all()):
+                raise EngineError("non-finite logits")
+            out.append((greedy_pick(lg), lg.numpy() if want_logits else None))
+        return out
+
+    def cut(self, slot, n):
+        self._cut(self.models[slot], n)
+
+    def reset(self, slot):
+        self.models[slot].reset()
+
+    def share_prefix(self, src, dst, n):
+        a, b = self.models[src], self.models[dst]
+        n = min(n, a.n_past)
+        b.k = [k[:n].clone() for k in a.k]
+        b.v = [v[:n].clone() for v in a.v]
+        b.n_past = n
+        return n
+
+    def snapshot(self, slot, ids):
+        m = self.models[slot]
+        n = min(len(ids), m.n_past)
+        if n == 0:
+            return None
+        pay = {"k": [k[:n].clone() for k in m.k], "v": [v[:n].clone() for v in m.v]}
+        nb = sum(t.numel() * 4 for t in pay["k"] + pay["v"])
+        return Saved(tuple(ids[:n]), pay, nb)
+
+    def restore(self, slot, saved, n):
+        m = self.models[slot]
+        n = min(n, len(saved.ids))
+        m.k = [k[:n].clone() for k in saved.payload["k"]]
+        m.v = [v[:n].clone() for v in saved.payload["v"]]
+        m.n_past = n
+        return n
+
+    def props(self):
+        s = self.spec
+        return {"engine": "cpu", "arch": s.arch, "n_layer": s.n_layer, "n_expert": s.n_expert, "devices": ["cpu"]}

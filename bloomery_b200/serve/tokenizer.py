@@ -333,3 +333,53 @@ def from_gguf(g, fallback_vocab: int = 0) -> Tokenizer:
         scores = [float(s) for s in scores] if scores is not None else [0.0] * len(tokens)
         return SpmTokenizer(tokens, scores, types, bos, eos, add_bos, bool(g.get("tokenizer.ggml.add_space_prefix", True)))
     raise ValueError(f"tokenizer model {model!r} is not supported")
+
+
+def from_folder(path: str, fallback_vocab: int = 0) -> Tokenizer:
+    """Tokenizer of a checkpoint folder: ``tokenizer.json`` (byte-level BPE: vocab, merges, added tokens) with
+    ids of BOS/EOS from ``tokenizer_config.json`` / ``config.json``; a folder without one gives bytes."""
+    import json
+    import os
+    tj = os.path.join(path, "tokenizer.json")
+    if not os.path.exists(tj):
+        return ByteTokenizer(fallback_vocab)
+    doc = json.load(open(tj, encoding="utf-8"))
+    model = doc.get("model") or {}
+    if str(model.get("type", "BPE")) != "BPE":
+        raise ValueError(f"tokenizer.json model type {model.get('type')!r} is not supported")
+    vocab = model.get("vocab") or {}
+    n = max(list(vocab.values()) + [a["id"] for a in doc.get("added_tokens", [])] + [-1]) + 1
+    n = max(n, fallback_vocab)
+    tokens = [f"[unused{i}]" for i in range(n)]
+    types = [T_UNUSED if "T_UNUSED" in globals() else T_NORMAL] * n
+    for tok, i in vocab.items():
+        tokens[i], types[i] = tok, T_NORMAL
+    for a in doc.get("added_tokens", []):
+        tokens[a["id"]] = a["content"]
+        types[a["id"]] = T_CONTROL if a.get("special") else T_USER if "T_USER" in globals() else T_NORMAL
+    merges = [m if isinstance(m, str) else " ".join(m) for m in model.get("merges", [])]
+    ids = {t: i for i, t in enumerate(tokens)}
+    cfg = {}
+    for fn in ("tokenizer_config.json", "config.json"):
+        fp = os.path.join(path, fn)
+        if os.path.exists(fp):
+            for k, v in json.load(open(fp, encoding="utf-8")).items():
+                cfg.setdefault(k, v)
+
+    def tid(key: str) -> int:
+        v = cfg.get(key + "_id", cfg.get(key))
+        if isinstance(v, dict):
+            v = v.get("content")
+        if isinstance(v, list):
+            v = v[0] if v else None
+        if isinstance(v, int):
+            return v
+        return ids.get(v, -1) if isinstance(v, str) else -1
+
+    pre = "default"
+    blob = json.dumps(doc.get("pre_tokenizer") or {})
+    if "\\p{N}{1,3}" in blob:
+        pre = "llama-bpe"
+    elif "\\p{N}" in blob and "(?i:'s|'t|'re|'ve|'m|'ll|'d)" in blob:
+        pre = "qwen2"
+    return BpeTokenizer(tokens, merges, types, pre, tid("bos_token"), tid("eos_token"), -1, bool(cfg.get("add_bos_token", False)))

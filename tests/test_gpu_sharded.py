@@ -95,3 +95,63 @@ def test_shard_items_partition_the_weights():
     assert torch.equal(e, full["blk.1.ffn_down_exps.weight"])
     o0, o1 = parts[0]["blk.0.attn_output.weight"], parts[1]["blk.0.attn_output.weight"]
     assert o0[0] == (spec.hidden, spec.q_rows // 2) and o0[1].shape[1] + o1[1].shape[1] == full["blk.0.attn_output.weight"].shape[1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_server_on_two_gpus_in_lockstep(tmp_path):
+    """The server process with ``--place tp -dev 0,1``: rank 0 serves HTTP, rank 1 follows the mirrored calls;
+    the greedy text equals the one-GPU server's on the same file (first tokens) and the cache path works."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+    from bloomery_b200.models import weights as W
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    spec = tiny_qwen3moe()
+    spec.vocab = 2048
+    path = str(tmp_path / "tiny.gguf")
+    W.write_gguf(spec, W.synth_tensors(spec, "cpu", seed=9), path)
+
+    def run(extra):
+        with socket.socket() as so:
+            so.bind(("127.0.0.1", 0))
+            port = so.getsockname()[1]
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        proc = subprocess.Popen([sys.executable, "-m", "bloomery_b200.serve", "-m", path, "--port", str(port), "-c", "2048",
+                                 "-np", "2"] + extra, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE)
+        url = f"http://127.0.0.1:{port}"
+
+        def call(p, body=None):
+            req = urllib.request.Request(url + p, data=json.dumps(body).encode() if body else None,
+                                         headers={"Content-Type": "application/json"})
+            return json.loads(urllib.request.urlopen(req, timeout=60).read())
+        try:
+            for _ in range(1200):
+                if proc.poll() is not None:
+                    raise AssertionError("server exited: " + proc.stderr.read().decode()[-3000:])
+                try:
+                    call("/health")
+                    break
+                except Exception:
+                    time.sleep(0.1)
+            else:
+                raise AssertionError("server did not become ready")
+            prompt = [3, 77, 200, 411, 9, 1500, 77, 200, 5, 6, 7]
+            r1 = call("/completion", {"prompt": prompt, "n_predict": 8, "temperature": 0, "return_tokens": True})
+            r2 = call("/completion", {"prompt": prompt + r1["tokens"][:3], "n_predict": 4, "temperature": 0, "return_tokens": True})
+            return r1, r2, call("/props")
+        finally:
+            proc.terminate()
+            try:
+                proc.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                proc.kill()
+
+    a1, a2, props = run(["--place", "tp", "-dev", "0,1"])
+    b1, b2, _ = run(["-dev", "0"])
+    assert len(a1["tokens"]) == 8 and a2["tokens_cached"] >= 11
+    assert a1["tokens"][:2] == b1["tokens"][:2], (a1["tokens"], b1["tokens"])
+    assert a2["tokens"] == a1["tokens"][3:7]

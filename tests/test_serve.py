@@ -209,3 +209,52 @@ def test_speculative_drafts_change_passes_not_tokens():
     assert outs[0][0] == outs[1][0]                      # same text
     assert outs[0][1] == 0 and outs[1][1] > 0 and outs[1][2] > 0
     assert outs[1][3] < outs[0][3]                       # fewer decode rounds for the same tokens
+
+
+def test_cpu_engine_serves_a_gguf_file(tmp_path):
+    """``-dev none``: the process opens a GGUF file, plans, loads the CPU engine and answers greedy text equal
+    to the oracle's continuation; a second request reuses the cached prefix; a third runs with n-gram drafting."""
+    import os
+    import subprocess
+    import sys
+    import torch
+    from bloomery_b200.models import weights as W
+    from bloomery_b200.models.cpu_ref import CpuModel
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    spec = tiny_qwen3moe()
+    spec.vocab, spec.n_layer = 512, 2
+    path = str(tmp_path / "tiny.gguf")
+    items = list(W.synth_tensors(spec, "cpu", seed=9))
+    W.write_gguf(spec, iter(items), path)
+    import socket
+    with socket.socket() as so:
+        so.bind(("127.0.0.1", 0))
+        port = so.getsockname()[1]
+    env = dict(os.environ, BLOOMERY_DRAFT="ngram")
+    proc = subprocess.Popen([sys.executable, "-m", "bloomery_b200.serve", "-m", path, "-dev", "none", "--port", str(port),
+                             "-c", "4096", "-np", "2", "--no-warmup"], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE)
+
+    class S:
+        url = f"http://127.0.0.1:{port}"
+    try:
+        for _ in range(600):
+            try:
+                if call(S, "/health")[0] == 200:
+                    break
+            except Exception:
+                pass
+            time.sleep(0.1)
+        else:
+            raise AssertionError("server did not become ready: " + proc.stderr.read().decode()[-2000:])
+        prompt = [3, 77, 200, 411, 9, 3, 77, 200]
+        code, r = call(S, "/completion", {"prompt": prompt, "n_predict": 6, "temperature": 0, "return_tokens": True})
+        assert code == 200, r
+        want = CpuModel(W.Weights.from_items(spec, iter(items), "cpu")).generate(prompt, 6)
+        assert r["tokens"] == want, (r["tokens"], want)
+        code, r2 = call(S, "/completion", {"prompt": prompt + want[:2], "n_predict": 4, "temperature": 0, "return_tokens": True})
+        assert code == 200 and r2["tokens"] == want[2:6] and r2["tokens_cached"] >= len(prompt)
+        code, props = call(S, "/props")
+        assert code == 200
+    finally:
+        proc.terminate()
+        proc.wait(timeout=20)
