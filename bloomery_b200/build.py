@@ -85,6 +85,15 @@ def _build_lib(name: str, sources: List[str], compiler: str, flags: List[str], l
     return lib
 
 
+def source_hash() -> str:
+    """Digest of the sources and flags the loaded CUDA library was built from (keys the cost store)."""
+    stamp = os.path.join(OUT, "libbloomery_cuda.so.hash")
+    try:
+        return open(stamp).read().strip()[:16]
+    except OSError:
+        return "unbuilt"
+
+
 def build_cuda(verbose: bool = False) -> str:
     srcs = sorted(os.path.join(CSRC, n) for n in os.listdir(CSRC) if n.endswith(".cu"))
     inc = []

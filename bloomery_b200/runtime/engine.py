@@ -152,6 +152,9 @@ class DecodeEngine:
         self._stream = torch.cuda.Stream(device=dev)
         self._done = torch.cuda.Event()
         self._lock = threading.Lock()
+        from .watchdog import Waits, Watchdog
+        self.waits = Waits()
+        self.watchdog: Optional[Watchdog] = None      # attached by the server; names a wedged wait, never kills
 
     # ---------------------------------------------------------------------------------
     # the kernel chain
@@ -317,10 +320,16 @@ class DecodeEngine:
         self.tokens_out_host.copy_(self.tokens_out, non_blocking=True)
         self._done.record()
         t0 = time.monotonic()
-        while not self._done.query():
-            if time.monotonic() - t0 > self.bound_s:
-                raise EngineStalled(f"no answer from the device within {self.bound_s:.0f} s")
-            time.sleep(0)
+        tok = self.watchdog.enter("step readback") if self.watchdog is not None else None
+        try:
+            while not self._done.query():
+                if time.monotonic() - t0 > self.bound_s:
+                    raise EngineStalled(f"no answer from the device within {self.bound_s:.0f} s")
+                time.sleep(0)
+        finally:
+            if tok is not None:
+                self.watchdog.leave(tok)
+            self.waits.add("card", time.monotonic() - t0)
         # the kernel writes the fault copy at index M (the bucket size)
         return self.tokens_out_host.tolist()
 

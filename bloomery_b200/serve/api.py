@@ -407,6 +407,12 @@ class Handler(BaseHTTPRequestHandler):
         g("draft_accepted_total", "Speculative tokens accepted", m.get("draft_accepted_total"))
         for w, n in sorted(st.worker.rounds_by_width.items()):
             lines.append(f'llamacpp:rounds_total{{width="{w}"}} {n}')
+        dec = getattr(st.engine, "dec", None)
+        if dec is not None and hasattr(dec, "waits"):
+            for name, val in sorted(dec.waits.metrics().items()):
+                g(name, "Engine-thread waits by kind", val)
+            wd = getattr(dec, "watchdog", None)
+            g("engine_wedged", "1 while a bounded engine wait has outlived its bound", int(bool(wd and wd.is_wedged())), "gauge")
         return "\n".join(lines) + "\n"
 
     def _slot_action(self, slot_id: int, action: str, body) -> None:

@@ -187,6 +187,15 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
             dec.gemm_threshold = 0
         tk, tsrc, bos, eos = surface(handle)
         eng = GpuEngine(dec, tk, name)
+    from ..runtime.watchdog import Watchdog
+    eng.dec.watchdog = Watchdog(name, bound_s=bound, report=lambda site, age: records.write(
+        "watchdog", model=name, site=site, seconds=round(age, 1))).start()
+    if bool(levers.get("BLOOMERY_AUTOTUNE")) and not (pl.mode == "tp" and len(pl.devices) > 1):
+        from ..runtime.autotune import CostStore, tune_decode_launch
+        from ..build import source_hash
+        store = CostStore(os.path.join(os.path.expanduser("~"), ".cache", "bloomery_b200", "costs.json"))
+        got = tune_decode_launch(eng.dec, store, build=source_hash())
+        records.write("setup", phase="autotune", seconds=0.0, winner=got["winner"], raced=got["raced"])
     if not opts.get("no_warmup"):
         t1 = time.time()
         eng.step([(0, max(0, tk.bos_id), 0)], want_logits=False)

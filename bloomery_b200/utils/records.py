@@ -12,7 +12,8 @@ KINDS: Dict[str, List[str]] = {
     "need": ["weights_bytes", "kv_bytes_per_token", "host_bytes", "fits"],
     "ctx": ["asked", "served", "trained"],
     "parallel": ["slots", "slot_ctx"],
-    "setup": ["phase", "seconds"],
+    "setup": ["phase", "seconds", "winner", "raced", "resident_per_layer", "host"],
+    "watchdog": ["model", "site", "seconds"],
     "request": ["id", "route", "slot", "prompt_tokens", "cached_tokens", "predicted_tokens", "prompt_ms",
                 "predicted_ms", "status"],
     "progress": ["slot", "tokens", "tok_per_s"],

@@ -1,0 +1,111 @@
+"""Host-side runtime parts: watchdog, waits, capture lock, cost store and race, route traces, census."""
+import threading
+import time
+
+import pytest
+
+from bloomery_b200.runtime import autotune as AT
+from bloomery_b200.runtime import route_trace as RT
+from bloomery_b200.runtime.watchdog import CaptureLock, Waits, Watchdog
+
+
+def test_watchdog_names_a_wedged_wait_once_and_never_kills():
+    now = [0.0]
+    seen = []
+    wd = Watchdog("m", bound_s=60.0, report=lambda site, age: seen.append((site, round(age))), clock=lambda: now[0])
+    a = wd.enter("step readback")
+    with wd.guard("prompt unit"):
+        now[0] = 30.0
+        assert wd.poll() == [] and not wd.is_wedged()
+    now[0] = 61.0
+    assert [s for s, _ in wd.poll()] == ["step readback"] and wd.is_wedged()
+    now[0] = 200.0
+    assert wd.poll() == []                       # reported once
+    wd.leave(a)
+    assert not wd.is_wedged() and seen == [("step readback", 61)]
+
+
+def test_watchdog_thread_runs_and_stops():
+    seen = []
+    wd = Watchdog("m", bound_s=0.05, period_s=0.02, report=lambda s, a: seen.append(s)).start()
+    t = wd.enter("host tier round")
+    time.sleep(0.3)
+    wd.stop()
+    assert seen == ["host tier round"]
+    wd.leave(t)
+
+
+def test_waits_totals():
+    w = Waits()
+    w.add("card", 0.5)
+    with w.timed("host_tier"):
+        time.sleep(0.01)
+    m = w.metrics()
+    assert m["wait_card_seconds_total"] == 0.5 and m["wait_card_total"] == 1 and m["wait_host_tier_seconds_total"] > 0.005
+
+
+def test_capture_lock_sync_waits_for_captures_and_blocks_new_ones():
+    lk = CaptureLock()
+    order = []
+    lk.acquire_shared()
+
+    def syncer():
+        with lk.sync():
+            order.append("sync")
+
+    def late_capture():
+        with lk.capture():
+            order.append("capture2")
+    t1 = threading.Thread(target=syncer)
+    t1.start()
+    time.sleep(0.05)
+    t2 = threading.Thread(target=late_capture)      # queued behind the waiting exclusive holder
+    t2.start()
+    time.sleep(0.05)
+    assert order == []
+    order.append("capture1 ends")
+    lk.release_shared()
+    t1.join(2)
+    t2.join(2)
+    assert order == ["capture1 ends", "sync", "capture2"]
+
+
+def test_cost_store_and_race(tmp_path):
+    p = str(tmp_path / "c" / "costs.json")
+    st = AT.CostStore(p)
+    k = AT.CostStore.key("B200", "12.9", "abc", {"hidden": 2048})
+    assert k == AT.CostStore.key("B200", "12.9", "abc", {"hidden": 2048}) and k != AT.CostStore.key("B200", "12.9", "abd", {"hidden": 2048})
+    assert st.get(k) is None
+    clock = {"a": [3.0, 1.0, 2.0], "b": [1.5, 1.5, 9.0]}
+    calls = []
+    win, costs = AT.race({"a": lambda: calls.append("a"), "b": lambda: calls.append("b")},
+                         time_one=lambda fn: (fn(), clock[calls[-1]].pop(0))[1], reps=3, flush=lambda: calls.append("flush"))
+    assert win == "b" and costs == {"a": 2.0, "b": 1.5} and calls.count("flush") == 6
+    st.put(k, costs)
+    assert AT.CostStore(p).get(k) == costs and AT.best_of({"x": 1.0, "a": 1.0}) == "a"
+    open(p, "w").write("{not json")
+    assert AT.CostStore(p).get(k) is None
+
+
+def test_route_trace_roundtrip_and_census(tmp_path):
+    p = str(tmp_path / "t" / "trace.blrt")
+    w = RT.RouteTraceWriter(p, n_layer=2, top_k=3)
+    w.add(0, 0, [5, 1, 9], [0.5, 0.25, 0.25])
+    w.add(0, 1, [2, 3, -1], [0.6, 0.3, 0.1])
+    with pytest.raises(ValueError):
+        w.add(1, 0, [1, 2], [0.5, 0.5])
+    w.close()
+    n_layer, k, it = RT.read_trace(p)
+    recs = list(it)
+    assert (n_layer, k) == (2, 3) and recs[0][:3] == (0, 0, [5, 1, 9]) and recs[1][2] == [2, 3, -1]
+    assert abs(recs[1][3][0] - 0.6) < 1e-6
+    open(p, "ab").write(b"xx")
+    with pytest.raises(ValueError):
+        list(RT.read_trace(p)[2])
+    c = RT.Census(2)
+    slot_map = [-1] * 10
+    slot_map[5] = 0
+    slot_map[2] = 1
+    c.add_picks(0, [5, 1, 9], slot_map)
+    c.add_picks(1, [2, 3, -1], slot_map)
+    assert c.totals() == {"card": 2, "host": 3, "peer": 1, "spare": 0} and abs(c.share("host") - 0.5) < 1e-9
