@@ -109,3 +109,45 @@ def test_route_trace_roundtrip_and_census(tmp_path):
     c.add_picks(0, [5, 1, 9], slot_map)
     c.add_picks(1, [2, 3, -1], slot_map)
     assert c.totals() == {"card": 2, "host": 3, "peer": 1, "spare": 0} and abs(c.share("host") - 0.5) < 1e-9
+
+
+def _inv(n_layer=4, n_expert=8, trunk_mib=100, expert_mib=10):
+    inv = [("token_embd.weight", trunk_mib << 20)]
+    for il in range(n_layer):
+        inv.append((f"blk.{il}.attn_q.weight", 8 << 20))
+        inv.append((f"blk.{il}.attn_norm.weight", 4096))
+        for part in ("gate", "up", "down"):
+            inv.append((f"blk.{il}.ffn_{part}_exps.weight", n_expert * expert_mib << 20))
+    return inv
+
+
+def test_placement_planner_rules():
+    from bloomery_b200.runtime import placement as P
+    kw = dict(n_layer=4, n_expert=8, first_dense=0, kv_bytes_per_token=1 << 16, n_kv_heads=4, ctx_train=32768,
+              margin=64 << 20, work_bytes=64 << 20)
+    inv = _inv()
+    everything = 100 + 4 * 8 + 4 * 3 * 8 * 10           # MiB: trunk + experts
+    big = P.plan(inv, budget=4 << 30, **kw)
+    assert big.resident_per_layer == 8 and big.host_bytes == 0 and big.word() == "a"
+    assert big.slot_ctx == 32768 and big.need()["fits"]
+    # an asked context is never cut: the refusal names the largest that fits
+    with pytest.raises(P.NoFit) as e:
+        P.plan(inv, budget=(everything + 128 + 600) << 20, ctx_ask=16384, **kw)
+    assert e.value.largest_ctx == 9216
+    # experts that do not fit: refused unless they may stay on the host
+    with pytest.raises(P.NoFit):
+        P.plan(inv, budget=700 << 20, **kw)
+    fit = P.plan(inv, budget=1250 << 20, host_experts="fit", ctx_ask=4096, **kw)
+    assert 0 < fit.resident_per_layer < 8 and fit.resident_per_layer % 4 == 0 and fit.spare_slots == 1
+    assert fit.host_bytes == 4 * 3 * 8 * 10 << 20 and fit.card_bytes <= fit.budget and "host[4/8]" in fit.word()
+    none = P.plan(inv, budget=700 << 20, host_experts="all", **kw)
+    assert none.resident_per_layer == 0 and all(p.where == "host" for p in none.places if p.split == "experts")
+    # a trunk that does not fit is a refusal even with every expert on the host
+    with pytest.raises(P.NoFit):
+        P.plan(inv, budget=200 << 20, host_experts="all", **kw)
+    # two ranks: heads and experts divide, the rest is replicated; KV divides with the KV heads
+    tp = P.plan(inv, budget=4 << 30, world=2, **kw)
+    assert tp.trunk_bytes == (100 << 20) + 4 * (4 << 20) + 4 * 4096 and tp.resident_per_layer == 4 and tp.word() == "tp2"
+    assert tp.kv_bytes == big.kv_bytes // 2
+    r0 = dict(P.rank_inventory(inv, 2, 0))
+    assert r0["blk.0.attn_q.weight"] == 4 << 20 and r0["token_embd.weight"] == 100 << 20
