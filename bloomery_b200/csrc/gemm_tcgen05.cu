@@ -57,7 +57,22 @@ struct GemmArgs {
   const float* resid;         // optional addend, indexed like the output
   long ldr;
   unsigned* status;
+  // distributed mode (several GPUs): rows of the output are owned by ranks in blocks of
+  // rows_per_owner; a finished value is ADDED into the owner's fp32 buffer (a peer pointer:
+  // red.global.add over NVLink), which is the reduce-scatter of a tensor-parallel product
+  // and the combine of an expert-parallel one.  dst_div maps dst_row (a flat slot index
+  // token * k + j) back to its token.
+  float* own_base[8];
+  int rows_per_owner;
+  int n_owners;
+  int dst_div;
+  int src_rows;               // > 0: A is row-sharded; product row = tile's source rank * src_rows + row in the shard
 };
+
+// One tensor map of A per source rank: m-tile t reads the map of rank mtiles[t].pad, so the
+// "all-gather" of a row-sharded activation is the TMA load itself (plain tile loads from the
+// peer's memory, one CTA per tile, no cluster multicast).
+struct AMaps { CUtensorMap m[8]; };
 
 // ---- PTX wrappers -------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -152,9 +167,13 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // ---- the kernel ------------------------------------------------------------------------
 // 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 = epilogue
 // (their warp id modulo 4 covers the four 32-lane quarters of tensor memory).
-template <bool DUAL>
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <bool DUAL, bool DIST>
 __global__ void __launch_bounds__(192, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+gemm_bf16_kernel(const __grid_constant__ AMaps tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_b2, const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr int BN = DUAL ? BN_DUAL : BN_SINGLE;
@@ -201,7 +220,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) break;
           uint8_t* sa = smem + (size_t)stage * STAGE_BYTES;
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-          tma_load_2d(sa, &tma_a, kb * BK, mt.row0, &full_bar[stage]);
+          tma_load_2d(sa, DIST ? &tma_a.m[mt.pad & 7] : &tma_a.m[0], kb * BK, mt.row0, &full_bar[stage]);
           tma_load_3d(sa + TILE_A_BYTES, &tma_b, kb * BK, n0, mt.group, &full_bar[stage]);
           if (DUAL) tma_load_3d(sa + TILE_A_BYTES + TILE_B_BYTES, &tma_b2, kb * BK, n0, mt.group, &full_bar[stage]);
           ++issued;
@@ -267,6 +286,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int r = mt.row0 + q * 32 + lane;                 // product row of this thread
       const bool live = r < mt.row_end;
       long orow = r;
+      if (DIST && a.src_rows > 0) orow += (long)mt.pad * a.src_rows;
       float scale = 1.0f;
       if (live && a.dst_row) orow = a.dst_row[r];
       if (live && a.row_scale) scale = a.row_scale[r];
@@ -305,7 +325,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               f[i] += x.x; f[i + 1] += x.y; f[i + 2] += x.z; f[i + 3] += x.w;
             }
           }
-          if (a.c_f32) {
+          if (DIST && a.n_owners > 0) {
+            const long tok = a.dst_div > 1 ? orow / a.dst_div : orow;
+            const int owner = (int)(tok / a.rows_per_owner);
+            float* o = a.own_base[owner & 7] + (tok - (long)owner * a.rows_per_owner) * a.ldc + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) red_add_v4(o + i, f[i], f[i + 1], f[i + 2], f[i + 3]);
+          } else if (a.c_f32) {
             float* o = a.c_f32 + orow * a.ldc + col;
 #pragma unroll
             for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
@@ -343,7 +369,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 // A group's B-matrix index is g / group_div (several row groups may share one B, e.g. the
 // query heads of one KV head).
 __global__ void build_mtiles_kernel(const int* group_rows, int n_groups, MTile* mtiles, int* n_mtiles, int max_mtiles,
-                                    int* group_offset_out, int group_div, int group_stride, int base) {
+                                    int* group_offset_out, int group_div, int group_stride, int base, int src_rows) {
   pdl_wait();
   pdl_launch();
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
@@ -355,7 +381,16 @@ __global__ void build_mtiles_kernel(const int* group_rows, int n_groups, MTile* 
     if (group_stride > 0) off = base + g * group_stride;
     if (group_offset_out) group_offset_out[g] = off;
     for (int r = 0; r < rows; r += BM) {
-      if (n < max_mtiles) mtiles[n] = MTile{g / group_div, off + r, off + rows, 0};
+      // src_rows > 0: A is row-sharded over ranks in blocks of src_rows; the tile reads rank (row / src_rows)'s map
+      if (n < max_mtiles) {
+        if (src_rows > 0) {
+          const int src = (off + r) / src_rows, lo = (off + r) - src * src_rows;
+          const int end = min(off + rows, (src + 1) * src_rows) - src * src_rows;
+          mtiles[n] = MTile{g / group_div, lo, end, src};
+        } else {
+          mtiles[n] = MTile{g / group_div, off + r, off + rows, 0};
+        }
+      }
       ++n;
     }
     if (group_stride <= 0) off += rows;
@@ -388,28 +423,46 @@ int bl_gemm_build_tiles(const int* group_rows, int n_groups, void* mtiles, int* 
                         int* group_offsets, int group_div, int group_stride, int base, cudaStream_t st) {
   BL_REQUIRE(n_groups >= 1 && max_mtiles >= 1 && group_div >= 1, BL_ERR_SHAPE);
   return (int)launch(build_mtiles_kernel, dim3(1), dim3(32), 0, st, group_rows, n_groups, (MTile*)mtiles, n_mtiles,
-                     max_mtiles, group_offsets, group_div, group_stride, base);
+                     max_mtiles, group_offsets, group_div, group_stride, base, 0);
+}
+
+// Tile table of a dense product whose A rows are sharded over ranks in blocks of src_rows (a multiple of 128).
+int bl_gemm_build_tiles_sharded(const int* total_rows, void* mtiles, int* n_mtiles, int max_mtiles, int src_rows,
+                                cudaStream_t st) {
+  BL_REQUIRE(max_mtiles >= 1 && src_rows >= BM && src_rows % BM == 0, BL_ERR_SHAPE);
+  return (int)launch(build_mtiles_kernel, dim3(1), dim3(32), 0, st, total_rows, 1, (MTile*)mtiles, n_mtiles, max_mtiles,
+                     (int*)nullptr, 1, 0, 0, src_rows);
 }
 
 // C = A * B[g]^T per 128-row tile of the table.  A: [rows_a, K] bf16 (lda elements);
 // B, B2: [n_groups, N, K] bf16.  Output row r -> dst_row[r] (or r), times row_scale[r],
 // plus resid.  Exactly one of c_f32 / c_bf16.  status: device word, set to 1 if a wait ran out.
-int bl_gemm_bf16(const void* A, long lda, long rows_a, const void* B, const void* B2, int n_groups, int N, int K,
-                 const void* mtiles, const int* n_mtiles, int max_mtiles, float* c_f32, void* c_bf16, long ldc,
-                 const int* dst_row, const float* row_scale, const float* resid, long ldr, unsigned* status,
-                 int sm_count, cudaStream_t st) {
+static int gemm_launch(const void* const* A_of_rank, int n_src, long lda, long rows_a, const void* B, const void* B2,
+                       int n_groups, int N, int K, const void* mtiles, const int* n_mtiles, int max_mtiles, float* c_f32,
+                       void* c_bf16, long ldc, const int* dst_row, const float* row_scale, const float* resid, long ldr,
+                       float* const* own_base, int n_owners, int rows_per_owner, int dst_div, int src_rows,
+                       unsigned* status, int sm_count, cudaStream_t st) {
   BL_REQUIRE(K >= BK && K % BK == 0 && N >= 32 && N % 32 == 0, BL_ERR_SHAPE);
-  BL_REQUIRE(lda % 8 == 0 && rows_a >= 1 && n_groups >= 1, BL_ERR_SHAPE);
-  BL_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)B & 15) == 0 && ((uintptr_t)B2 & 15) == 0, BL_ERR_ALIGN);
-  BL_REQUIRE((c_f32 != nullptr) != (c_bf16 != nullptr), BL_ERR_SHAPE);
+  BL_REQUIRE(lda % 8 == 0 && rows_a >= 1 && n_groups >= 1 && n_src >= 1 && n_src <= 8, BL_ERR_SHAPE);
+  BL_REQUIRE(((uintptr_t)B & 15) == 0 && ((uintptr_t)B2 & 15) == 0, BL_ERR_ALIGN);
+  const bool dist = n_src > 1 || n_owners > 0;
+  if (n_owners > 0) {
+    BL_REQUIRE(n_owners <= 8 && rows_per_owner >= 1 && c_f32 == nullptr && c_bf16 == nullptr && !resid && !B2, BL_ERR_SHAPE);
+    for (int r = 0; r < n_owners; ++r) BL_REQUIRE(own_base[r] && ((uintptr_t)own_base[r] & 15) == 0, BL_ERR_ALIGN);
+  } else {
+    BL_REQUIRE((c_f32 != nullptr) != (c_bf16 != nullptr), BL_ERR_SHAPE);
+  }
   BL_REQUIRE(ldc % 8 == 0 && (!resid || ldr % 4 == 0), BL_ERR_SHAPE);
   BL_REQUIRE(((uintptr_t)c_f32 & 15) == 0 && ((uintptr_t)c_bf16 & 15) == 0 && ((uintptr_t)resid & 15) == 0, BL_ERR_ALIGN);
-  CUtensorMap ma, mb, mb2;
-  {
+  AMaps ma;
+  CUtensorMap mb, mb2;
+  for (int r = 0; r < 8; ++r) {
+    const void* A = A_of_rank[r < n_src ? r : 0];
+    BL_REQUIRE(A && ((uintptr_t)A & 15) == 0, BL_ERR_ALIGN);
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows_a};
     cuuint64_t str[1] = {(cuuint64_t)lda * 2};
     cuuint32_t box[2] = {BK, BM};
-    int rc = make_map(&ma, A, 2, dims, str, box);
+    int rc = make_map(&ma.m[r], A, 2, dims, str, box);
     if (rc) return rc;
   }
   {
@@ -427,19 +480,43 @@ int bl_gemm_bf16(const void* A, long lda, long rows_a, const void* B, const void
   a.dual = B2 ? 1 : 0;
   a.c_f32 = c_f32; a.c_bf16 = (__nv_bfloat16*)c_bf16; a.ldc = ldc;
   a.dst_row = dst_row; a.row_scale = row_scale; a.resid = resid; a.ldr = ldr; a.status = status;
+  for (int r = 0; r < n_owners; ++r) a.own_base[r] = own_base[r];
+  a.n_owners = n_owners; a.rows_per_owner = rows_per_owner; a.dst_div = dst_div; a.src_rows = src_rows;
   a.tiles_n = (N + (B2 ? BN_DUAL : BN_SINGLE) - 1) / (B2 ? BN_DUAL : BN_SINGLE);
   long tiles = (long)max_mtiles * a.tiles_n;
   int grid = (int)(tiles < sm_count ? tiles : sm_count);
-  if (B2) {
-    const size_t smem = (size_t)STAGES * (TILE_A_BYTES + 2 * TILE_B128_BYTES) + 1024;
-    static bool set = false;
-    if (!set) { cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); set = true; }
-    return (int)launch(gemm_bf16_kernel<true>, dim3(grid), dim3(192), smem, st, ma, mb, mb2, a);
-  }
   const size_t smem = (size_t)STAGES * (TILE_A_BYTES + 2 * TILE_B128_BYTES) + 1024;
-  static bool set1 = false;
-  if (!set1) { cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); set1 = true; }
-  return (int)launch(gemm_bf16_kernel<false>, dim3(grid), dim3(192), smem, st, ma, mb, mb2, a);
+  auto go = [&](auto kernel, bool& set) {
+    if (!set) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); set = true; }
+    return (int)launch(kernel, dim3(grid), dim3(192), smem, st, ma, mb, mb2, a);
+  };
+  static bool s00 = false, s01 = false, s10 = false, s11 = false;
+  if (B2) return dist ? go(gemm_bf16_kernel<true, true>, s11) : go(gemm_bf16_kernel<true, false>, s10);
+  return dist ? go(gemm_bf16_kernel<false, true>, s01) : go(gemm_bf16_kernel<false, false>, s00);
+}
+
+int bl_gemm_bf16(const void* A, long lda, long rows_a, const void* B, const void* B2, int n_groups, int N, int K,
+                 const void* mtiles, const int* n_mtiles, int max_mtiles, float* c_f32, void* c_bf16, long ldc,
+                 const int* dst_row, const float* row_scale, const float* resid, long ldr, unsigned* status,
+                 int sm_count, cudaStream_t st) {
+  const void* As[1] = {A};
+  return gemm_launch(As, 1, lda, rows_a, B, B2, n_groups, N, K, mtiles, n_mtiles, max_mtiles, c_f32, c_bf16, ldc, dst_row,
+                     row_scale, resid, ldr, nullptr, 0, 0, 1, 0, status, sm_count, st);
+}
+
+// The several-GPU form.  A_of_rank: one pointer per source rank (each [rows_a, K], the rank's shard; tiles pick
+// their source by the table built with bl_gemm_build_tiles_sharded); n_src == 1 reads local rows only.
+// own_base / n_owners / rows_per_owner: when n_owners > 0 the product is added into the owners' buffers instead
+// of being stored (see GemmArgs); dst_div maps dst_row entries back to tokens.
+int bl_gemm_bf16_dist(const void* const* A_of_rank, int n_src, long lda, long rows_a, const void* B, const void* B2,
+                      int n_groups, int N, int K, const void* mtiles, const int* n_mtiles, int max_mtiles, float* c_f32,
+                      void* c_bf16, long ldc, const int* dst_row, const float* row_scale, float* const* own_base,
+                      int n_owners, int rows_per_owner, int dst_div, int src_rows, unsigned* status, int sm_count,
+                      cudaStream_t st) {
+  BL_REQUIRE(n_src == 1 || (src_rows >= BM && src_rows % BM == 0 && rows_a >= src_rows), BL_ERR_SHAPE);
+  return gemm_launch(A_of_rank, n_src, lda, rows_a, B, B2, n_groups, N, K, mtiles, n_mtiles, max_mtiles, c_f32, c_bf16, ldc,
+                     dst_row, row_scale, nullptr, 0, own_base, n_owners, rows_per_owner, dst_div < 1 ? 1 : dst_div,
+                     n_src > 1 ? src_rows : 0, status, sm_count, st);
 }
 
 }  // extern "C"

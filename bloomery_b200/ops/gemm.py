@@ -31,6 +31,15 @@ class TileTable:
                                          stream()), "bl_gemm_build_tiles")
 
     @classmethod
+    def sharded(cls, total_rows: int, src_rows: int, device) -> "TileTable":
+        """Dense product whose A rows live on several ranks in blocks of ``src_rows`` (a multiple of 128)."""
+        t = cls(total_rows, total_rows // src_rows + 1, device)
+        check(cuda().bl_gemm_build_tiles_sharded(p(torch.tensor([total_rows], dtype=torch.int32, device=device)),
+                                                 p(t.mtiles), p(t.n_mtiles), I(t.max_mtiles), I(src_rows), stream()),
+              "bl_gemm_build_tiles_sharded")
+        return t
+
+    @classmethod
     def dense(cls, rows: int, device) -> "TileTable":
         t = cls(rows, 1, device)
         t.build(torch.tensor([rows], dtype=torch.int32, device=device))
@@ -53,6 +62,52 @@ def gemm_bf16(A: torch.Tensor, B: torch.Tensor, tiles: TileTable, *, out_f32: Op
                              p(dst_row), p(row_scale), p(resid), L(resid.stride(0) if resid is not None else 0),
                              p(status), I(sm_count()), stream())
     check(rc, "bl_gemm_bf16")
+
+
+def _ptr_array(ptrs):
+    import ctypes
+    return (ctypes.c_void_p * len(ptrs))(*[int(x) for x in ptrs])
+
+
+def gemm_bf16_dist(A_ptrs, rows_a: int, lda: int, B: torch.Tensor, tiles: TileTable, *, src_rows: int = 0,
+                   out_f32: Optional[torch.Tensor] = None, out_bf16: Optional[torch.Tensor] = None,
+                   B2: Optional[torch.Tensor] = None, dst_row=None, row_scale=None, owners=None, rows_per_owner: int = 0,
+                   ldc: int = 0, dst_div: int = 1, status: Optional[torch.Tensor] = None) -> None:
+    """The several-GPU form of :func:`gemm_bf16`.  ``A_ptrs``: device addresses of every source rank's A shard
+    ([rows_a, K] bf16 each; one entry = local rows only).  ``owners``: device addresses of every rank's fp32
+    output shard; when given, product rows are added into the shard of the rank that owns them
+    (row // rows_per_owner) instead of being stored."""
+    if B.dim() == 2:
+        B = B[None]
+        B2 = B2[None] if B2 is not None else None
+    G, N, Kd = B.shape
+    out = out_f32 if out_f32 is not None else out_bf16
+    rc = cuda().bl_gemm_bf16_dist(_ptr_array(A_ptrs), I(len(A_ptrs)), L(lda), L(rows_a), p(B), p(B2), I(G), I(N), I(Kd),
+                                  p(tiles.mtiles), p(tiles.n_mtiles), I(tiles.max_mtiles), p(out_f32), p(out_bf16),
+                                  L(out.stride(0) if out is not None else ldc), p(dst_row), p(row_scale),
+                                  _ptr_array(owners) if owners else None, I(len(owners) if owners else 0),
+                                  I(rows_per_owner), I(dst_div), I(src_rows), p(status), I(sm_count()), stream())
+    check(rc, "bl_gemm_bf16_dist")
+
+
+def rank_barrier(peer_flag_ptrs, my_flags_ptr: int, epoch: int, rank: int, status: Optional[torch.Tensor]) -> None:
+    import ctypes
+    check(cuda().bl_rank_barrier(_ptr_array(peer_flag_ptrs), ctypes.c_void_p(my_flags_ptr), ctypes.c_uint(epoch & 0xFFFFFFFF),
+                                 I(len(peer_flag_ptrs)), I(rank), p(status), stream()), "bl_rank_barrier")
+
+
+def gather_rows_peer(src_ptrs, src_stride: int, rows_per_rank: int, dst_row, n_rows, max_rows: int, k: int, K_: int, out) -> None:
+    check(cuda().bl_gather_rows_peer(_ptr_array(src_ptrs), I(len(src_ptrs)), L(src_stride), I(rows_per_rank), p(dst_row),
+                                     p(n_rows), I(max_rows), I(k), I(K_), p(out), stream()), "bl_gather_rows_peer")
+
+
+def copy_bytes(src_ptr: int, dst_ptr: int, n_bytes: int) -> None:
+    import ctypes
+    check(cuda().bl_copy_bytes(ctypes.c_void_p(src_ptr), ctypes.c_void_p(dst_ptr), L(n_bytes), stream()), "bl_copy_bytes")
+
+
+def localize_ids(ids: torch.Tensor, e_lo: int, e_hi: int, out: torch.Tensor) -> None:
+    check(cuda().bl_localize_ids(p(ids), I(ids.numel()), I(e_lo), I(e_hi), p(out), stream()), "bl_localize_ids")
 
 
 def dequant_bf16(w: QWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -91,6 +91,10 @@ class ShardedEngine(DecodeEngine):
         self.partial = torch.zeros(8, s.hidden, dtype=torch.float32, device=dev)
         self.arena.sites_per_step = 2 * s.n_layer
 
+    def _new_gemm_prefill(self):
+        from .prefill_dist import ShardedGemmPrefill
+        return ShardedGemmPrefill(self, ubatch=self.ubatch, group=self.group, local_only=self.world == 1)
+
     def enqueue(self, M: int, head: bool = True, advance: bool = False) -> int:
         ops = self.build_ops(M, head, advance)
         for op in ops:

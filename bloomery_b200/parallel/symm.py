@@ -105,3 +105,34 @@ class SymmetricArena:
         r.fault = fault.data_ptr() if fault is not None else 0
         r.layer = layer
         return r
+
+
+class SymmetricBuffer:
+    """A byte buffer that exists on every rank with the same layout; ``ptrs[r]`` is rank r's copy as seen from
+    this process (peer memory for r != rank).  ``local_only`` gives an ordinary buffer whose peers are set
+    later with :meth:`adopt_peers` (several emulated ranks in one process)."""
+
+    def __init__(self, n_bytes: int, rank: int, world: int, device, group=None, local_only: bool = False):
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.total = (n_bytes + 255) // 256 * 256
+        self._keep = []
+        if world == 1 or local_only:
+            self.buf = torch.zeros(self.total, dtype=torch.uint8, device=self.device)
+            self.ptrs = [self.buf.data_ptr()] * world
+            self.how = "local"
+        else:
+            self.H = 0
+            self.buf, self.ptrs, self.how = SymmetricArena._exchange(self, group)
+
+    def adopt_peers(self, bufs: List["SymmetricBuffer"]) -> None:
+        self.ptrs = [b.buf.data_ptr() for b in bufs]
+
+    def view(self, offset: int, shape, dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= d
+        nb = n * torch.empty(0, dtype=dtype).element_size()
+        return self.buf[offset:offset + nb].view(dtype).view(*shape)
+
+    def peers(self, offset: int) -> List[int]:
+        return [p_ + offset for p_ in self.ptrs]

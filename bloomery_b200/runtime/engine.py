@@ -350,6 +350,10 @@ class DecodeEngine:
                 raise EngineFault(word)
             return out[:len(rows)]
 
+    def _new_gemm_prefill(self):
+        from .prefill import GemmPrefill
+        return GemmPrefill(self, ubatch=self.ubatch)
+
     def prefill(self, slot: int, tokens: Sequence[int], start: int = 0, gemm: Optional[bool] = None) -> int:
         """Feed a prompt; returns the greedy token after it.  Prompts of at least
         ``gemm_threshold`` rows go through the tcgen05 GEMM path in micro-batches, shorter
@@ -358,8 +362,7 @@ class DecodeEngine:
         use_gemm = gemm if gemm is not None else (self.gemm_threshold > 0 and n >= self.gemm_threshold)
         if use_gemm and n > 1:
             if self._gemm_prefill is None:
-                from .prefill import GemmPrefill
-                self._gemm_prefill = GemmPrefill(self, ubatch=self.ubatch)
+                self._gemm_prefill = self._new_gemm_prefill()
             with self._lock:
                 if self.poisoned is not None:
                     raise EngineFault(self.poisoned)

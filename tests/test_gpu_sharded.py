@@ -155,3 +155,41 @@ def test_server_on_two_gpus_in_lockstep(tmp_path):
     assert len(a1["tokens"]) == 8 and a2["tokens_cached"] >= 11
     assert a1["tokens"][:2] == b1["tokens"][:2], (a1["tokens"], b1["tokens"])
     assert a2["tokens"] == a1["tokens"][3:7]
+
+
+def test_sharded_gemm_prefill_two_emulated_ranks():
+    """The several-GPU prompt path (peer TMA loads for the all-gather, adds into the owner's rows for the
+    reduce-scatter and the expert combine), two ranks emulated on one GPU phase by phase, against the
+    one-GPU GEMM prompt path: hidden state of the last row, the KV rows written, and the next token."""
+    from bloomery_b200.parallel.prefill_dist import ShardedGemmPrefill
+    spec, ref, engs = _engines(2)
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, spec.vocab, (300,), generator=g).tolist()
+    ref.prefill(0, toks, gemm=True)
+    x_ref = ref.x[0].clone()
+    pres = [ShardedGemmPrefill(e, ubatch=512, local_only=True) for e in engs]
+    for p in pres:
+        p.sym.adopt_peers([q.sym for q in pres])
+    for e in engs:
+        e.kv.ensure(0, len(toks))
+        e.kv.sync_table()
+    lists = [p.phases(0, toks, 0) for p in pres]
+    assert len(set(len(l) for l in lists)) == 1 and len(lists[0]) == 4 * spec.n_layer + 1
+    for phase in zip(*lists):
+        for fns in phase:                     # rank 0's launches of the phase, then rank 1's: stream order is the barrier
+            for fn in fns:
+                fn()
+    torch.cuda.synchronize()
+    for p in pres:
+        assert int(p.status) == 0
+    for e in engs:
+        assert (int(e.fault) & 0xFFFFFFFF) == 0xFFFFFFFF
+        err = ((e.x[0] - x_ref).abs().max() / x_ref.abs().max()).item()
+        assert err < 3e-2, err
+    assert torch.allclose(engs[0].x[0], engs[1].x[0])
+    # rank r holds KV head r of the two; compare with the one-GPU cache (bf16 operands: band, not bits)
+    for r, e in enumerate(engs):
+        pg_ref, pg = ref.kv.pages[0][0], e.kv.pages[0][0]
+        a = ref.kv.k[1, pg_ref, r, :64].float()
+        b = e.kv.k[1, pg, 0, :64].float()
+        assert ((a - b).abs().mean() / a.abs().mean()).item() < 3e-2
