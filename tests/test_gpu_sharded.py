@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _engines(world=2):
+def _engines(world=2, slot_ctx=256):
     from bloomery_b200.models.spec import tiny_qwen3moe
     from bloomery_b200.models.weights import Weights, synth_tensors
     from bloomery_b200.parallel.sharded import ShardedEngine, local_spec, shard_items
@@ -20,14 +20,14 @@ def _engines(world=2):
     from bloomery_b200.runtime.engine import DecodeEngine
     spec = tiny_qwen3moe()
     items = list(synth_tensors(spec, "cpu", seed=9))
-    ref = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=1, slot_ctx=256, use_graphs=False)
+    ref = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=1, slot_ctx=slot_ctx, use_graphs=False)
     arenas = [SymmetricArena(spec.hidden, r, world, DEV, local_only=True) for r in range(world)]
     for a in arenas:
         a.adopt_peers(arenas)
     engs = []
     for r in range(world):
         w = Weights.from_items(local_spec(spec, world), shard_items(iter(items), spec, r, world), DEV)
-        engs.append(ShardedEngine(w, spec, r, world, fused=True, arena=arenas[r], n_slots=1, slot_ctx=256,
+        engs.append(ShardedEngine(w, spec, r, world, fused=True, arena=arenas[r], n_slots=1, slot_ctx=slot_ctx,
                                   use_graphs=False))
     return spec, ref, engs
 
@@ -162,7 +162,7 @@ def test_sharded_gemm_prefill_two_emulated_ranks():
     reduce-scatter and the expert combine), two ranks emulated on one GPU phase by phase, against the
     one-GPU GEMM prompt path: hidden state of the last row, the KV rows written, and the next token."""
     from bloomery_b200.parallel.prefill_dist import ShardedGemmPrefill
-    spec, ref, engs = _engines(2)
+    spec, ref, engs = _engines(2, slot_ctx=512)
     g = torch.Generator().manual_seed(5)
     toks = torch.randint(0, spec.vocab, (300,), generator=g).tolist()
     ref.prefill(0, toks, gemm=True)
