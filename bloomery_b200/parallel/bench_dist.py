@@ -29,7 +29,7 @@ def run_distributed(args, rank: int, local: int, world: int) -> int:
     torch.cuda.synchronize()
     t_load = time.time() - t0
     fused = not getattr(args, "nccl_baseline", False)
-    ctx = args.prompt + warm + 2 * steps + 64
+    ctx = max(args.prompt, getattr(args, 'ttft', 0) or 0) + warm + 2 * steps + 64
     eng = ShardedEngine(w, spec, rank, world, fused=fused, n_slots=1, slot_ctx=(ctx + 63) // 64 * 64,
                         use_graphs=fused)
     g = torch.Generator().manual_seed(1234)
@@ -86,6 +86,37 @@ def run_distributed(args, rank: int, local: int, world: int) -> int:
         pos += 1
     torch.cuda.synchronize()
     e2e_s = D.max_over_ranks(time.perf_counter() - t0, dev)
+    extra = {}
+    if getattr(args, "ttft", 0) and fused:
+        # time to first token of a long prompt through the several-GPU GEMM path (collectives inside the GEMMs)
+        p2 = torch.randint(0, spec.vocab, (args.ttft,), generator=g).tolist()
+        ts = []
+        for _ in range(3):
+            eng.reset(0)
+            torch.cuda.synchronize()
+            dist.barrier()
+            t0 = time.perf_counter()
+            eng.prefill(0, p2, gemm=True)
+            torch.cuda.synchronize()
+            ts.append(D.max_over_ranks((time.perf_counter() - t0) * 1e3, dev))
+        # the token after the prompt must be the same on every rank and (up to a bf16 arg-max flip) equal to the
+        # one the 8-row pass path gives
+        eng.reset(0)
+        tok_gemm = eng.prefill(0, p2, gemm=True)
+        eng.reset(0)
+        tok_steps = eng.prefill(0, p2[:512], gemm=False)
+        eng.reset(0)
+        tok_gemm_512 = eng.prefill(0, p2[:512], gemm=True)
+        tt = torch.tensor([tok_gemm, tok_gemm_512], dtype=torch.int64, device=dev)
+        tmx, tmn = tt.clone(), tt.clone()
+        dist.all_reduce(tmx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tmn, op=dist.ReduceOp.MIN)
+        extra = {"ttft_ms_p50": sorted(ts)[1], "ttft_prompt_tokens": args.ttft,
+                 "prefill_ranks_agree": bool((tmx == tmn).all().item()),
+                 "prefill_token_equals_pass_path_512": tok_gemm_512 == tok_steps,
+                 "prefill_tok_s": args.ttft / (sorted(ts)[1] / 1e3),
+                 "prefill_path": "tcgen05 GEMM; all-gather as peer TMA loads, reduce-scatter and expert combine as adds "
+                                 "into the owner's rows from the GEMM epilogue"}
     if rank == 0:
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm,
@@ -104,7 +135,7 @@ def run_distributed(args, rank: int, local: int, world: int) -> int:
                     "d2h_bytes_per_step": int(eng.tokens_out_host.numel() * 4) * world},
             "gpu_launches": eng.launches_per_step * steps * world, "launches_per_step": eng.launches_per_step,
             "ranks_agree": same, "ttft_ms_prompt": ttft_prompt_ms, "load_s": t_load,
-            "weights_gb_per_rank": w.n_bytes / 1e9,
+            "weights_gb_per_rank": w.n_bytes / 1e9, **extra,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()

@@ -184,7 +184,7 @@ def open_rank(model: str, rank: int, world: int, device: int, n_slots: int, slot
     w = Weights.from_items(local_spec(spec, world), shard_items(gguf_items(g), spec, rank, world), dev)
     torch.cuda.synchronize()
     eng = ShardedEngine(w, spec, rank, world, fused=fused, n_slots=n_slots, slot_ctx=slot_ctx, use_graphs=use_graphs and fused)
-    eng.gemm_threshold = 0        # prompts go through the sharded decode chain, 8 rows a pass
+    eng.gemm_threshold = 64 if fused else 0     # long prompts take the several-GPU GEMM path
     return eng, spec, g
 
 
