@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(256) flash_decode_seg_kernel(const FlashArgs a
   const int n_tiles = bad ? 0 : (n_keys + kKeyTile - 1) / kKeyTile;
   const int tps = (n_tiles + a.n_seg - 1) / a.n_seg;
   const int t0 = seg * tps, t1 = min(n_tiles, t0 + tps);
+  if (!bad && t0 >= t1) return;                  // past the row's last key tile: the merge does not read this segment
 
   for (int i = tid; i < G * HEAD; i += 256)
     sq[i] = a.q[((long)m * a.n_q + (long)kvh * G) * HEAD + i];
@@ -253,6 +254,8 @@ struct MergeArgs {
   const float* part_acc;
   int n_q, n_seg, M;
   const int* row_seq;
+  const int* row_pos;  // with ctx_limit: lets the merge skip the segments the row's keys never reach
+  int ctx_limit;
   float* out;        // optional fp32 [M, n_q*HEAD]
   int8_t* outq;      // q8 codes [M, n_q*HEAD]
   float2* outds;     // [M, n_q*HEAD/32]
@@ -266,15 +269,25 @@ __global__ void __launch_bounds__(HEAD) flash_decode_merge_kernel(const MergeArg
   pdl_launch();
   if (a.row_seq[m] < 0) return;
   const long p0 = ((long)m * a.n_q + qh) * a.n_seg;
+  // segments beyond the row's last key tile hold weight 0: the same split as the segment kernel says how many are live
+  int used = a.n_seg;
+  {
+    const int n_keys = a.row_pos[m] + 1;
+    if (n_keys > 0 && n_keys <= a.ctx_limit) {
+      const int n_tiles = (n_keys + kKeyTile - 1) / kKeyTile;
+      const int tps = (n_tiles + a.n_seg - 1) / a.n_seg;
+      used = (n_tiles + tps - 1) / tps;
+    }
+  }
   float mx = -INFINITY;
   bool nan = false;
-  for (int s = 0; s < a.n_seg; ++s) {
+  for (int s = 0; s < used; ++s) {
     float v = a.part_ml[(p0 + s) * 2];
     nan |= (v != v);
     mx = fmaxf(mx, v);
   }
   float num = 0.f, den = 0.f;
-  for (int s = 0; s < a.n_seg; ++s) {  // ascending segment order, fixed
+  for (int s = 0; s < used; ++s) {  // ascending segment order, fixed
     float ms = a.part_ml[(p0 + s) * 2];
     float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
     den = fmaf(a.part_ml[(p0 + s) * 2 + 1], w, den);
@@ -349,7 +362,7 @@ int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, co
     else e = launch(flash_decode_seg_kernel<64, 2>, grid, dim3(256), smem, st, a);
   }
   if (e != cudaSuccess) return (int)e;
-  MergeArgs mg{part_ml, part_acc, n_q, n_seg, M, row_seq, out, outq, (float2*)outds};
+  MergeArgs mg{part_ml, part_acc, n_q, n_seg, M, row_seq, row_pos, ctx_limit, out, outq, (float2*)outds};
   if (head == 128) return (int)launch(flash_decode_merge_kernel<128>, dim3(n_q, M), dim3(128), 0, st, mg);
   return (int)launch(flash_decode_merge_kernel<64>, dim3(n_q, M), dim3(64), 0, st, mg);
 }

@@ -165,6 +165,23 @@ __global__ void __launch_bounds__(32) swiglu_q8_kernel(const float* gu, long gu_
   if (lane == 0) actds[((long)m * I) / 32 + c] = make_float2(d, s);
 }
 
+
+// Input of the multi-token-prediction layer: row m = [ RMSNorm(e[m]) * enorm | RMSNorm(h[src[m]]) * hnorm ],
+// quantised to q8 for the eh_proj product (K = 2H).  e = embedding of the token that follows position m,
+// h = the trunk's final hidden state of the row it was computed in (src maps draft rows to pass rows).
+// grid (M), 256 threads; dynamic shared memory: nothing (red is static)
+__global__ void __launch_bounds__(256) mtp_prep_kernel(const float* e, long e_stride, const float* h, long h_stride,
+                                                       const int* src, const float* enorm, const float* hnorm, float eps,
+                                                       int H, int8_t* xq, float2* xds) {
+  __shared__ __align__(8) float red[64];
+  const int m = blockIdx.x;
+  pdl_wait();
+  pdl_launch();
+  const int sm = src ? src[m] : m;
+  block_rmsnorm_q8(e + (long)m * e_stride, enorm, H, eps, xq + (long)m * 2 * H, xds + (long)m * (2 * H / 32), red, nullptr);
+  block_rmsnorm_q8(h + (long)sm * h_stride, hnorm, H, eps, xq + (long)m * 2 * H + H, xds + (long)m * (2 * H / 32) + H / 32, red, nullptr);
+}
+
 }  // namespace bl
 
 using namespace bl;
@@ -202,6 +219,13 @@ int bl_swiglu_q8(const float* gu, long gu_stride, int I, int M, int8_t* actq, fl
                  cudaStream_t st) {
   BL_REQUIRE(I % 32 == 0 && M >= 1, BL_ERR_SHAPE);
   return (int)launch(swiglu_q8_kernel, dim3(I / 32, M), dim3(32), 0, st, gu, gu_stride, I, actq, (float2*)actds, act_f32);
+}
+
+int bl_mtp_prep(const float* e, long e_stride, const float* h, long h_stride, const int* src, const float* enorm,
+                const float* hnorm, float eps, int H, int M, int8_t* xq, float* xds, cudaStream_t st) {
+  BL_REQUIRE(H % 32 == 0 && M >= 1 && enorm && hnorm, BL_ERR_SHAPE);
+  return (int)launch(mtp_prep_kernel, dim3(M), dim3(256), 0, st, e, e_stride, h, h_stride, src, enorm, hnorm, eps, H, xq,
+                     (float2*)xds);
 }
 
 const char* bl_error_string(int code) {

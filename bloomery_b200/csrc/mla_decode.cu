@@ -162,6 +162,7 @@ __global__ void __launch_bounds__(256) mla_flash_seg_kernel(const MlaFlashArgs a
   const int n_tiles = bad ? 0 : (n_keys + kTile - 1) / kTile;
   const int tps = (n_tiles + a.n_seg - 1) / a.n_seg;
   const int t0 = seg * tps, t1 = min(n_tiles, t0 + tps);
+  if (!bad && t0 >= t1) return;                  // past the row's last key tile: the merge does not read this segment
   const int h0 = hb * kHeadsPerBlock;
   const int n_heads = min(kHeadsPerBlock, a.n_q - h0);
   for (int i = tid; i < n_heads * kRow; i += 256) sq[i] = a.q_lat[((long)m * a.n_q + h0) * kRow + i];
@@ -268,6 +269,8 @@ struct MlaMergeArgs {
   const void* w_vb;        // [n_q][v_dim][512]
   int n_q, n_seg, M, v_dim;
   const int* row_seq;
+  const int* row_pos;
+  int ctx_limit;
   float* out;              // optional fp32 [M, n_q * v_dim]
   int8_t* outq;            // q8 codes [M, n_q * v_dim]
   float2* outds;           // [M, n_q * v_dim / 32]
@@ -283,15 +286,24 @@ __global__ void __launch_bounds__(256) mla_merge_vup_kernel(const MlaMergeArgs a
   pdl_launch();
   if (a.row_seq[m] < 0) return;
   const long p0 = ((long)m * a.n_q + h) * a.n_seg;
+  int used = a.n_seg;                                       // segments past the row's last key tile weigh 0
+  {
+    const int n_keys = a.row_pos[m] + 1;
+    if (n_keys > 0 && n_keys <= a.ctx_limit) {
+      const int n_tiles = (n_keys + kTile - 1) / kTile;
+      const int tps = (n_tiles + a.n_seg - 1) / a.n_seg;
+      used = (n_tiles + tps - 1) / tps;
+    }
+  }
   float mx = -INFINITY;
   bool nan = false;
-  for (int s = 0; s < a.n_seg; ++s) {
+  for (int s = 0; s < used; ++s) {
     const float v = a.part_ml[(p0 + s) * 2];
     nan |= (v != v);
     mx = fmaxf(mx, v);
   }
   float n0 = 0.f, n1 = 0.f, den = 0.f;
-  for (int s = 0; s < a.n_seg; ++s) {                       // ascending segment order, fixed
+  for (int s = 0; s < used; ++s) {                          // ascending segment order, fixed
     const float ms = a.part_ml[(p0 + s) * 2];
     const float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
     den = fmaf(a.part_ml[(p0 + s) * 2 + 1], w, den);
@@ -364,7 +376,7 @@ int bl_mla_flash_decode(const float* q_lat, const void* cache, const int* row_po
                  part_ml, part_acc, fault, layer};
   cudaError_t e = launch(mla_flash_seg_kernel, dim3(n_seg, (n_q + kHeadsPerBlock - 1) / kHeadsPerBlock, M), dim3(256), smem, st, f);
   if (e != cudaSuccess) return (int)e;
-  MlaMergeArgs g{part_ml, part_acc, w_vb, n_q, n_seg, M, v_dim, row_seq, out, outq, (float2*)outds};
+  MlaMergeArgs g{part_ml, part_acc, w_vb, n_q, n_seg, M, v_dim, row_seq, row_pos, ctx_limit, out, outq, (float2*)outds};
   if (wtype == 0) return (int)launch(mla_merge_vup_kernel<float>, dim3(n_q, M), dim3(256), 0, st, g);
   return (int)launch(mla_merge_vup_kernel<__nv_bfloat16>, dim3(n_q, M), dim3(256), 0, st, g);
 }

@@ -83,8 +83,9 @@ class CpuModel:
     def reset(self):
         s = self.spec
         kd = (1, s.kv_lora + s.rope_dim) if s.mla else (s.n_kv, s.head_dim)
-        self.k: List[torch.Tensor] = [torch.zeros(0, *kd, device=self.device) for _ in range(s.n_layer)]
-        self.v: List[torch.Tensor] = [torch.zeros(0, *kd, device=self.device) for _ in range(s.n_layer)]
+        self.k: List[torch.Tensor] = [torch.zeros(0, *kd, device=self.device) for _ in range(s.n_layer + s.n_mtp)]
+        self.v: List[torch.Tensor] = [torch.zeros(0, *kd, device=self.device) for _ in range(s.n_layer + s.n_mtp)]
+        self.hidden: Optional[torch.Tensor] = None      # the trunk's final hidden rows of the last forward
         self.n_past = 0
 
     def _q(self, x: torch.Tensor) -> torch.Tensor:
@@ -149,6 +150,65 @@ class CpuModel:
         pr = torch.softmax(sc.masked_fill(mask[None], -float("inf")), -1)
         return torch.einsum("hts,shv->thv", pr, v).reshape(T, s.n_q * s.v_dim)
 
+    def _layer(self, il: int, x: torch.Tensor, pos: torch.Tensor, collect: Optional[dict] = None) -> torch.Tensor:
+        s, w = self.spec, self.w
+        T = x.shape[0]
+        b = f"blk.{il}."
+        h = self._q(rms_norm(x, w[b + "attn_norm.weight"], s.rms_eps))
+        att = self._mla(il, h, pos) if s.mla else self._gqa(il, h, pos)
+        x = x + self._q(att) @ w[b + "attn_output.weight"].T
+        hn = rms_norm(x, w[b + "ffn_norm.weight"], s.rms_eps)
+        if s.layer_is_moe(il):
+            logits = hn @ w[b + "ffn_gate_inp.weight"].T
+            ids, wts = route(logits, s, w.get(b + "exp_probs_b.bias"))
+            if collect is not None:
+                collect.setdefault("ids", []).append(ids)
+                collect.setdefault("wts", []).append(wts)
+            hq = self._q(hn)
+            y = torch.zeros_like(x)
+            for t in range(T):
+                acc = torch.zeros(s.hidden, device=self.device)
+                for j in range(s.n_used):
+                    e = int(ids[t, j])
+                    g = hq[t] @ w[b + "ffn_gate_exps.weight"][e].T
+                    u = hq[t] @ w[b + "ffn_up_exps.weight"][e].T
+                    a = self._q((torch.nn.functional.silu(g) * u)[None])[0]
+                    acc = acc + wts[t, j] * (a @ w[b + "ffn_down_exps.weight"][e].T)
+                y[t] = acc
+            if s.n_shared:
+                g = hq @ w[b + "ffn_gate_shexp.weight"].T
+                u = hq @ w[b + "ffn_up_shexp.weight"].T
+                y = y + self._q(torch.nn.functional.silu(g) * u) @ w[b + "ffn_down_shexp.weight"].T
+            x = x + y
+        else:
+            hq = self._q(hn)
+            g = hq @ w[b + "ffn_gate.weight"].T
+            u = hq @ w[b + "ffn_up.weight"].T
+            a = self._q(torch.nn.functional.silu(g) * u)
+            x = x + a @ w[b + "ffn_down.weight"].T
+        if collect is not None:
+            collect.setdefault("x", []).append(x.clone())
+        return x
+
+    @torch.no_grad()
+    def mtp_forward(self, next_tokens: torch.Tensor, hidden: torch.Tensor, pos: torch.Tensor, il: Optional[int] = None) -> torch.Tensor:
+        """Logits of the multi-token-prediction layer: row i combines the trunk's hidden state at ``pos[i]`` with
+        the embedding of the token that follows it and predicts the token after that; the layer keeps its own
+        KV rows at those positions (DeepSeek-V3's MTP module; the reference: ``crates/runtime/src/mtp``)."""
+        s, w = self.spec, self.w
+        il = s.n_layer if il is None else il
+        b = f"blk.{il}."
+        e = rms_norm(w["token_embd.weight"][next_tokens.long()], w[b + "nextn.enorm.weight"], s.rms_eps)
+        hh = rms_norm(hidden, w[b + "nextn.hnorm.weight"], s.rms_eps)
+        z = torch.cat([self._q(e), self._q(hh)], -1)          # each half is quantised on its own
+        x = z @ w[b + "nextn.eh_proj.weight"].T
+        if self.k[il].shape[0] > int(pos[0]):
+            self.k[il], self.v[il] = self.k[il][:int(pos[0])], self.v[il][:int(pos[0])]
+        x = self._layer(il, x, pos)
+        hn = self._q(rms_norm(x, w[b + "nextn.shared_head_norm.weight"], s.rms_eps))
+        head = w.get("output.weight", w["token_embd.weight"])
+        return hn @ head.T
+
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, collect: Optional[dict] = None) -> torch.Tensor:
         """tokens [T] appended to the sequence; returns logits [T, vocab]."""
@@ -157,41 +217,8 @@ class CpuModel:
         pos = torch.arange(self.n_past, self.n_past + T, device=self.device)
         x = w["token_embd.weight"][tokens.long()]
         for il in range(s.n_layer):
-            b = f"blk.{il}."
-            h = self._q(rms_norm(x, w[b + "attn_norm.weight"], s.rms_eps))
-            att = self._mla(il, h, pos) if s.mla else self._gqa(il, h, pos)
-            x = x + self._q(att) @ w[b + "attn_output.weight"].T
-            hn = rms_norm(x, w[b + "ffn_norm.weight"], s.rms_eps)
-            if s.layer_is_moe(il):
-                logits = hn @ w[b + "ffn_gate_inp.weight"].T
-                ids, wts = route(logits, s, w.get(b + "exp_probs_b.bias"))
-                if collect is not None:
-                    collect.setdefault("ids", []).append(ids)
-                    collect.setdefault("wts", []).append(wts)
-                hq = self._q(hn)
-                y = torch.zeros_like(x)
-                for t in range(T):
-                    acc = torch.zeros(s.hidden, device=self.device)
-                    for j in range(s.n_used):
-                        e = int(ids[t, j])
-                        g = hq[t] @ w[b + "ffn_gate_exps.weight"][e].T
-                        u = hq[t] @ w[b + "ffn_up_exps.weight"][e].T
-                        a = self._q((torch.nn.functional.silu(g) * u)[None])[0]
-                        acc = acc + wts[t, j] * (a @ w[b + "ffn_down_exps.weight"][e].T)
-                    y[t] = acc
-                if s.n_shared:
-                    g = hq @ w[b + "ffn_gate_shexp.weight"].T
-                    u = hq @ w[b + "ffn_up_shexp.weight"].T
-                    y = y + self._q(torch.nn.functional.silu(g) * u) @ w[b + "ffn_down_shexp.weight"].T
-                x = x + y
-            else:
-                hq = self._q(hn)
-                g = hq @ w[b + "ffn_gate.weight"].T
-                u = hq @ w[b + "ffn_up.weight"].T
-                a = self._q(torch.nn.functional.silu(g) * u)
-                x = x + a @ w[b + "ffn_down.weight"].T
-            if collect is not None:
-                collect.setdefault("x", []).append(x.clone())
+            x = self._layer(il, x, pos, collect)
+        self.hidden = x
         self.n_past += T
         h = self._q(rms_norm(x, w["output_norm.weight"], s.rms_eps))
         head = w.get("output.weight", w["token_embd.weight"])

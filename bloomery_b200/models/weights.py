@@ -33,7 +33,8 @@ def use_more_bits(i: int, n: int) -> bool:
 
 def q4_k_m_type(name: str, il: int, n_layer: int) -> str:
     """Type that llama.cpp's Q4_K_M recipe gives a tensor (norms and router stay F32)."""
-    if name.endswith("_norm.weight") or name.endswith("ffn_gate_inp.weight") or name.endswith(".bias"):
+    if name.endswith("_norm.weight") or name.endswith("ffn_gate_inp.weight") or name.endswith(".bias") \
+            or name.endswith("nextn.enorm.weight") or name.endswith("nextn.hnorm.weight"):
         return "F32"
     if name == "output.weight":
         return "Q6_K"
@@ -71,8 +72,13 @@ def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K
         return (name, tuple(shape), t, raw)
 
     yield emit("token_embd.weight", (spec.vocab, H))
-    for il in range(L):
+    for il in range(L + spec.n_mtp):
         b = f"blk.{il}."
+        if il >= L:        # a multi-token-prediction layer: a trunk block behind its own input projection
+            yield emit(b + "nextn.enorm.weight", (H,), il, ones=True)
+            yield emit(b + "nextn.hnorm.weight", (H,), il, ones=True)
+            yield emit(b + "nextn.eh_proj.weight", (H, 2 * H), il)
+            yield emit(b + "nextn.shared_head_norm.weight", (H,), il, ones=True)
         yield emit(b + "attn_norm.weight", (H,), il, ones=True)
         if spec.mla:
             qk = spec.nope_dim + spec.rope_dim

@@ -185,6 +185,12 @@ def swiglu_q8(gu: torch.Tensor, I_: int, M: int, actq, actds, act_f32=None) -> N
           "bl_swiglu_q8")
 
 
+def mtp_prep(e, h, src, enorm, hnorm, eps: float, M: int, xq, xds) -> None:
+    """q8 rows [M, 2H] = [norm(e) | norm(h[src])] for the multi-token-prediction layer's input product."""
+    check(cuda().bl_mtp_prep(p(e), L(e.stride(0)), p(h), L(h.stride(0)), p(src), p(enorm), p(hnorm), F(eps), I(e.shape[1]),
+                             I(M), p(xq), p(xds), stream()), "bl_mtp_prep")
+
+
 def sample_rows(logits, V: int, M: int, params, seeds, draws, out_token, *, recent=None, n_recent=None, work=None,
                 out_n_cand=None, fault=None) -> None:
     """The sampling chain on the card, one block per row (``csrc/sampler.cu``).

@@ -67,23 +67,25 @@ class DecodeEngine:
         self.use_graphs = use_graphs
         self.bound_s = engine_bound_s
         max_pages = (slot_ctx + PAGE - 1) // PAGE
+        # multi-token-prediction layers ride behind the trunk when the checkpoint carries them
+        self.n_mtp = s.n_mtp if f"blk.{s.n_layer}.nextn.eh_proj.weight" in weights.q else 0
         sm = K.sm_count(dev)
         if s.mla:
-            self.kv = KvPool(s.n_layer, 1, s.kv_lora + s.rope_dim, n_slots * max_pages, n_slots, max_pages, dev, v_dim=0)
+            self.kv = KvPool(s.n_layer + self.n_mtp, 1, s.kv_lora + s.rope_dim, n_slots * max_pages, n_slots, max_pages, dev, v_dim=0)
             self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, 2 * sm // ((s.n_q + 15) // 16))))
         else:
-            self.kv = KvPool(s.n_layer, s.n_kv, s.head_dim, n_slots * max_pages, n_slots, max_pages, dev)
+            self.kv = KvPool(s.n_layer + self.n_mtp, s.n_kv, s.head_dim, n_slots * max_pages, n_slots, max_pages, dev)
             self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, sm // s.n_kv)))
         H, V = s.hidden, s.vocab
         f32 = dict(dtype=torch.float32, device=dev)
         i32 = dict(dtype=torch.int32, device=dev)
         R = MAX_ROWS
         # step parameters: tokens, positions, slot of each row (one H2D copy)
-        self.params = torch.zeros(3, R, **i32)
+        self.params = torch.zeros(4, R, **i32)       # row 3: source row of a draft-layer row
         self.params[2].fill_(-1)
         # pinned staging ring: a slot is rewritten only after the copy that read it has run
         self._stage_n = 16
-        self._stage = [torch.zeros(3, R, dtype=torch.int32, pin_memory=True) for _ in range(self._stage_n)]
+        self._stage = [torch.zeros(4, R, dtype=torch.int32, pin_memory=True) for _ in range(self._stage_n)]
         self._stage_ev = [None] * self._stage_n
         self._stage_i = 0
         self.params_host = self._stage[0]
@@ -120,7 +122,7 @@ class DecodeEngine:
             self.r_wts = torch.zeros(R, s.n_used, **f32)
             self.actq = torch.zeros(R, s.n_used, s.moe_inter, dtype=torch.int8, device=dev)
             self.actds = torch.zeros(R, s.n_used, s.moe_inter // 32, 2, **f32)
-            self.heat = torch.zeros(s.n_layer, s.n_expert, **i32)
+            self.heat = torch.zeros(s.n_layer + self.n_mtp, s.n_expert, **i32)
             if s.n_shared:
                 self.sh_gu = torch.zeros(R, 2 * s.shared_inter, **f32)
                 self.sh_actq = torch.zeros(R, s.shared_inter, dtype=torch.int8, device=dev)
@@ -130,6 +132,12 @@ class DecodeEngine:
             self.gu = torch.zeros(R, 2 * s.dense_inter, **f32)
             self.dactq = torch.zeros(R, s.dense_inter, dtype=torch.int8, device=dev)
             self.dactds = torch.zeros(R, s.dense_inter // 32, 2, **f32)
+        if self.n_mtp:
+            self.mtp_e = torch.zeros(R, H, **f32)
+            self.mtp_x = torch.zeros(R, H, **f32)
+            self.mtp_xq = torch.zeros(R, 2 * H, dtype=torch.int8, device=dev)
+            self.mtp_xds = torch.zeros(R, 2 * H // 32, 2, **f32)
+            self.mtp_logits = torch.zeros(R, V, **f32)
         self.counters = torch.zeros(4, **i32)
         self.logits = torch.zeros(R, V, **f32)
         self.am_blocks = 64
@@ -155,6 +163,8 @@ class DecodeEngine:
         from .watchdog import Waits, Watchdog
         self.waits = Waits()
         self.watchdog: Optional[Watchdog] = None      # attached by the server; names a wedged wait, never kills
+        self.mtp_on = False                           # run the draft layer beside every pass (``enable_mtp``)
+        self.mtp_draft: Dict[int, Tuple[int, int]] = {}   # slot -> (number of ids the draft extends, drafted id)
 
     # ---------------------------------------------------------------------------------
     # the kernel chain
@@ -167,18 +177,7 @@ class DecodeEngine:
         K.embed_rows(self.tokens, M, w.q["token_embd.weight"], s.vocab, x, self.fault); n += 1
         kvp = self.kv
         for il in range(s.n_layer):
-            b = f"blk.{il}."
-            n += self._attn(il, M, x)
-            K.gemv([w.q[b + "attn_output.weight"]], M, x, xq=self.attn_q, xds=self.attn_ds, resid=x,
-                   fault=self.fault, layer=il); n += 1
-            if s.layer_is_moe(il):
-                n += self._moe(il, M, x)
-            else:
-                K.gemv([w.q[b + "ffn_gate.weight"], w.q[b + "ffn_up.weight"]], M, self.gu, x=x,
-                       gain=w.f[b + "ffn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il); n += 1
-                K.swiglu_q8(self.gu, s.dense_inter, M, self.dactq, self.dactds); n += 1
-                K.gemv([w.q[b + "ffn_down.weight"]], M, x, xq=self.dactq, xds=self.dactds, resid=x,
-                       fault=self.fault, layer=il); n += 1
+            n += self._layer(il, M, x)
         if head:
             head_w = w.q.get("output.weight", w.q["token_embd.weight"])
             K.gemv([head_w], M, self.logits, x=x, gain=w.f["output_norm.weight"], eps=s.rms_eps,
@@ -189,6 +188,107 @@ class DecodeEngine:
                 K.advance_rows(self.tokens, self.row_pos, self.row_seq, self.tokens_out, M, self.hist, self.hist_cap,
                                self.counters[2:3]); n += 1
         return n
+
+    def _layer(self, il: int, M: int, x: torch.Tensor) -> int:
+        """One transformer block on the residual rows ``x``; returns the launch count."""
+        s, w = self.spec, self.w
+        n = 0
+        b = f"blk.{il}."
+        n += self._attn(il, M, x)
+        K.gemv([w.q[b + "attn_output.weight"]], M, x, xq=self.attn_q, xds=self.attn_ds, resid=x,
+               fault=self.fault, layer=il); n += 1
+        if s.layer_is_moe(il):
+            n += self._moe(il, M, x)
+        else:
+            K.gemv([w.q[b + "ffn_gate.weight"], w.q[b + "ffn_up.weight"]], M, self.gu, x=x,
+                   gain=w.f[b + "ffn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il); n += 1
+            K.swiglu_q8(self.gu, s.dense_inter, M, self.dactq, self.dactds); n += 1
+            K.gemv([w.q[b + "ffn_down.weight"]], M, x, xq=self.dactq, xds=self.dactds, resid=x,
+                   fault=self.fault, layer=il); n += 1
+        return n
+
+    def enqueue_mtp(self, M: int) -> int:
+        """The draft layer on M rows: params row 0 = the token that FOLLOWS each position, row 3 = the pass row whose
+        final hidden state it pairs with (``self.x`` still holds the trunk's last pass).  Greedy draft ids land in
+        ``tokens_out`` like a trunk pass's picks (the reference: ``crates/app/src/mtp.rs:1-33``)."""
+        s, w = self.spec, self.w
+        il = s.n_layer
+        b = f"blk.{il}."
+        n = 0
+        K.embed_rows(self.tokens, M, w.q["token_embd.weight"], s.vocab, self.mtp_e, self.fault); n += 1
+        K.mtp_prep(self.mtp_e, self.x, self.params[3], w.f[b + "nextn.enorm.weight"], w.f[b + "nextn.hnorm.weight"],
+                   s.rms_eps, M, self.mtp_xq, self.mtp_xds); n += 1
+        K.gemv([w.q[b + "nextn.eh_proj.weight"]], M, self.mtp_x, xq=self.mtp_xq, xds=self.mtp_xds, fault=self.fault,
+               layer=il); n += 1
+        n += self._layer(il, M, self.mtp_x)
+        head_w = w.q.get("output.weight", w.q["token_embd.weight"])
+        K.gemv([head_w], M, self.mtp_logits, x=self.mtp_x, gain=w.f[b + "nextn.shared_head_norm.weight"], eps=s.rms_eps,
+               fault=self.fault, layer=il); n += 1
+        K.argmax_rows(self.mtp_logits, s.vocab, M, self.am_blocks, self.am_v, self.am_i, self.counters[1:2],
+                      self.tokens_out, None, self.fault); n += 1
+        return n
+
+    def mtp_step(self, rows: Sequence[Tuple[int, int, int, int]]) -> List[int]:
+        """rows = [(slot, next token, position, source row of the last trunk pass)]; returns the drafted id after
+        each row's next token (the layer's KV rows at those positions are written on the way)."""
+        if not self.n_mtp:
+            raise RuntimeError("this checkpoint has no multi-token-prediction layer")
+        with self._lock:
+            M = self.set_rows([(sl, tok, pos) for sl, tok, pos, _ in rows], src=[r[3] for r in rows])
+            if self.poisoned is not None:
+                raise EngineFault(self.poisoned)
+            if self.use_graphs:
+                key = ("mtp", M)
+                g = self.graphs.get(key)
+                if g is None:
+                    st = self._stream
+                    st.wait_stream(torch.cuda.current_stream(self.device))
+                    saved = self.params.clone()
+                    with torch.cuda.stream(st):
+                        self.params[2].fill_(-1)
+                        self.enqueue_mtp(M)
+                        st.synchronize()
+                        self.params.copy_(saved)
+                        g = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(g, stream=st):
+                            self.enqueue_mtp(M)
+                    torch.cuda.current_stream(self.device).wait_stream(st)
+                    self.graphs[key] = g
+                g.replay()
+            else:
+                self.enqueue_mtp(M)
+            out = self.read_tokens(len(rows))
+            word = out[M] & 0xFFFFFFFF
+            if word != FAULT_CLEAN:
+                self.poisoned = word
+                raise EngineFault(word)
+            return out[:len(rows)]
+
+    def enable_mtp(self, on: bool = True) -> bool:
+        self.mtp_on = bool(on) and self.n_mtp > 0
+        return self.mtp_on
+
+    def draft_after(self, rows: Sequence[Tuple[int, int, int]], picks: Sequence[int], slots=None) -> None:
+        """Run the draft layer for the rows of the pass that just ended (``self.x`` still holds their hidden states).
+        A row counts when every earlier row of its slot in the pass was followed by the token the trunk picked
+        (rows of rejected drafts are skipped); the last counted row of a slot leaves that slot's next draft."""
+        by_slot: Dict[int, List[int]] = {}
+        for i, (sl, _, _) in enumerate(rows):
+            if slots is None or sl in slots:
+                by_slot.setdefault(sl, []).append(i)
+        mrows, last_of = [], {}
+        for sl, idx in by_slot.items():
+            for j, ri in enumerate(idx):
+                if j > 0 and rows[ri][1] != picks[idx[j - 1]]:
+                    break
+                last_of[sl] = len(mrows)
+                mrows.append((sl, int(picks[ri]), rows[ri][2], ri))
+        for i in range(0, len(mrows), MAX_ROWS):
+            part = mrows[i:i + MAX_ROWS]
+            drafts = self.mtp_step(part)
+            for sl, k in last_of.items():
+                if i <= k < i + len(part):
+                    self.mtp_draft[sl] = (part[k - i][2] + 2, drafts[k - i])
 
     def _attn(self, il: int, M: int, x: torch.Tensor) -> int:
         """Attention of one layer up to the q8 rows that feed o_proj; returns the launch count."""
@@ -285,7 +385,7 @@ class DecodeEngine:
     # ---------------------------------------------------------------------------------
     # host protocol
     # ---------------------------------------------------------------------------------
-    def set_rows(self, rows: Sequence[Tuple[int, int, int]]) -> int:
+    def set_rows(self, rows: Sequence[Tuple[int, int, int]], src: Optional[Sequence[int]] = None) -> int:
         """rows = [(slot, token, position)]; pads to the bucket; returns the bucket size."""
         m = len(rows)
         M = bucket_of(m)
@@ -295,8 +395,9 @@ class DecodeEngine:
             self._stage_ev[i].synchronize()
         ph = self.params_host = self._stage[i]
         ph[2].fill_(-1)
-        for i, (slot, tok, pos) in enumerate(rows):
-            ph[0, i], ph[1, i], ph[2, i] = tok, pos, slot
+        for r, (slot, tok, pos) in enumerate(rows):
+            ph[0, r], ph[1, r], ph[2, r] = tok, pos, slot
+            ph[3, r] = src[r] if src is not None else r
             self.kv.ensure(slot, pos + 1)
             self.kv.own(slot, pos)
         self.kv.sync_table()
@@ -360,6 +461,7 @@ class DecodeEngine:
         ones through passes of up to 8 rows of the decode chain."""
         n = len(tokens)
         use_gemm = gemm if gemm is not None else (self.gemm_threshold > 0 and n >= self.gemm_threshold)
+        use_gemm = use_gemm and not self.mtp_on        # the draft layer's prompt rows run on the pass path
         if use_gemm and n > 1:
             if self._gemm_prefill is None:
                 self._gemm_prefill = self._new_gemm_prefill()
@@ -386,6 +488,15 @@ class DecodeEngine:
             is_last = i + len(chunk) >= n
             rows = [(slot, int(t), start + i + j) for j, t in enumerate(chunk)]
             out = self.step(rows, head=is_last)
+            if self.mtp_on:
+                # the draft layer keeps KV rows for the prompt too: row j pairs with the prompt token after it,
+                # the last row with the greedy pick
+                mrows = [(slot, int(tokens[i + j + 1]), start + i + j, j) for j in range(len(chunk)) if i + j + 1 < n]
+                if is_last:
+                    mrows.append((slot, int(out[len(chunk) - 1]), start + n - 1, len(chunk) - 1))
+                drafts = self.mtp_step(mrows)
+                if is_last:
+                    self.mtp_draft[slot] = (start + n + 1, drafts[-1])
             if is_last:
                 last = out[len(chunk) - 1]
             i += len(chunk)

@@ -38,6 +38,20 @@ class NgramDraft:
         return []
 
 
+class MtpDraft:
+    """Draft source backed by the model's own multi-token-prediction layer: the engine runs that layer beside
+    every pass and keeps, per slot, the id it predicts after the next token (``crates/runtime/src/mtp``:
+    the MTP window; one draft per step here)."""
+
+    wants_slot = True
+
+    def __init__(self, engine):
+        self.engine = engine
+
+    def propose(self, ids: Sequence[int], k: int, slot: int = 0) -> List[int]:
+        return self.engine.draft(slot, len(ids))[:k] if k > 0 else []
+
+
 class WidthChooser:
     def __init__(self, max_width: int = 7, prior_accept: float = 0.5):
         self.max_width = max_width

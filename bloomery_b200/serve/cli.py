@@ -264,6 +264,10 @@ def main(argv: Optional[List[str]] = None) -> int:
         if draft == "ngram" and server.state.worker is not None:
             from ..runtime.speculative import NgramDraft, WidthChooser
             server.state.worker.enable_drafting(NgramDraft(), WidthChooser())
+        elif draft in ("mtp", "auto") and server.state.worker is not None and getattr(getattr(eng, "dec", None), "n_mtp", 0):
+            from ..runtime.speculative import MtpDraft, WidthChooser
+            if eng.dec.enable_mtp():
+                server.state.worker.enable_drafting(MtpDraft(eng), WidthChooser(max_width=1))
         return server.wait()
     except _PlanOnly:
         return server.stop()

@@ -162,7 +162,7 @@ class GpuEngine(Engine):
         except (EngineFault, EngineStalled) as exc:
             raise EngineError(str(exc)) from exc
 
-    def step(self, rows, want_logits=True):
+    def step(self, rows, want_logits=True, draft_slots=None):
         from ..runtime.engine import EngineFault, EngineStalled
         out = []
         try:
@@ -170,6 +170,8 @@ class GpuEngine(Engine):
                 chunk = list(rows[i:i + self.max_rows])
                 picks = self.dec.step(chunk)
                 lg = self.dec.logits[:len(chunk)].float().cpu().numpy() if want_logits else None
+                if draft_slots and getattr(self.dec, "mtp_on", False):
+                    self.dec.draft_after(chunk, picks, draft_slots)
                 for j, pk in enumerate(picks):
                     out.append((int(pk), lg[j] if lg is not None else None))
         except (EngineFault, EngineStalled) as exc:
@@ -181,6 +183,11 @@ class GpuEngine(Engine):
 
     def reset(self, slot):
         self.dec.reset(slot)
+
+    def draft(self, slot: int, n_ids: int) -> List[int]:
+        """The draft layer's id for the position after ``n_ids`` known ids of ``slot`` ([] when there is none)."""
+        d = getattr(self.dec, "mtp_draft", {}).get(slot)
+        return [int(d[1])] if d is not None and d[0] == n_ids else []
 
     def share_prefix(self, src, dst, n):
         got = self.dec.kv.share_prefix(src, dst, n)

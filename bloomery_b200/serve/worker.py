@@ -287,7 +287,10 @@ class Worker(threading.Thread):
                     room = min(room, a.req.n_predict - len(a.generated) - 1)
                 k = self.width.choose(min(room, self.engine.max_rows - 1)) if room > 0 else 0
                 if k > 0:
-                    drafted = self.draft.propose(a.slot.ids + [a.pending_token], k)
+                    if getattr(self.draft, "wants_slot", False):
+                        drafted = self.draft.propose(a.slot.ids + [a.pending_token], k, a.slot.id)
+                    else:
+                        drafted = self.draft.propose(a.slot.ids + [a.pending_token], k)
             base = len(a.slot.ids)
             spans.append((a, len(rows), drafted))
             rows.append((a.slot.id, a.pending_token, base))
@@ -299,7 +302,11 @@ class Worker(threading.Thread):
         need_logits = any(w.req.sampling.temperature > 0 or w.req.sampling.penalizes or w.req.n_probs > 0
                           or w.req.constraint is not None or w.req.logit_bias or w.req.ignore_eos for w in who)
         t0 = time.time()
-        res = self.engine.step(rows, want_logits=need_logits)
+        if getattr(self.draft, "wants_slot", False):
+            res = self.engine.step(rows, want_logits=need_logits,
+                                   draft_slots={sp[0].slot.id for sp in spans if self._can_draft(sp[0])})
+        else:
+            res = self.engine.step(rows, want_logits=need_logits)
         dt = time.time() - t0
         self.metrics.add("round_seconds_total", dt)
         self.metrics.add("n_decode_total")

@@ -127,3 +127,58 @@ def test_deepseek_engine_matches_oracle():
         tok = eng.step([(0, tok, len(prompt) + i)])[0]
         single.append(tok)
     assert chain == single
+
+
+def test_mtp_draft_layer_matches_oracle_and_never_changes_tokens():
+    """The multi-token-prediction layer: its logits follow the oracle's, and verifying its drafts as extra rows
+    yields exactly the tokens of plain greedy decoding (a draft changes which passes run, never a token)."""
+    from bloomery_b200.models.cpu_ref import CpuModel, greedy_pick
+    from bloomery_b200.models.spec import tiny_deepseek
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.engine import DecodeEngine
+    spec = tiny_deepseek()
+    spec.n_mtp = 1
+    items = list(synth_tensors(spec, "cpu", seed=6))
+    eng = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=1, slot_ctx=512, use_graphs=True)
+    assert eng.n_mtp == 1 and eng.kv.k.shape[0] == spec.n_layer + 1
+    cpu = CpuModel(Weights.from_items(spec, iter(items), "cpu"))
+    g = torch.Generator().manual_seed(31)
+    prompt = torch.randint(0, spec.vocab, (21,), generator=g).tolist()
+    # plain greedy decoding first
+    first = eng.prefill(0, prompt)
+    plain, tok = [first], first
+    for i in range(12):
+        tok = eng.step([(0, tok, len(prompt) + i)])[0]
+        plain.append(tok)
+    # the same with the draft layer on
+    eng.reset(0)
+    assert eng.enable_mtp()
+    first2 = eng.prefill(0, prompt)
+    assert first2 == first and eng.mtp_draft[0][0] == len(prompt) + 1
+    # oracle of the draft layer over the prompt rows
+    ref_logits = cpu.forward(torch.tensor(prompt))
+    nxt = torch.tensor(prompt[1:] + [first])
+    ref_mtp = cpu.mtp_forward(nxt, cpu.hidden, torch.arange(len(prompt)))
+    n_last = len(prompt) % 8 or 8
+    got, want = eng.mtp_logits[n_last - 1].cpu(), ref_mtp[-1]
+    rms = ((got - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt()).item()
+    assert rms < 2e-2, rms
+    assert eng.mtp_draft[0][1] == int(torch.argmax(eng.mtp_logits[n_last - 1]))
+    # speculative loop: feed the pending token plus the draft, keep the draft when the trunk agrees
+    out, tok, pos, passes, kept_total = [first], first, len(prompt), 0, 0
+    while len(out) < 13:
+        d = eng.mtp_draft.get(0)
+        rows = [(0, tok, pos)]
+        if d is not None and d[0] == pos + 1:
+            rows.append((0, d[1], pos + 1))
+        picks = eng.step(rows)
+        passes += 1
+        kept = 1 if len(rows) == 2 and picks[0] == rows[1][1] else 0
+        if len(rows) == 2 and not kept:
+            eng.cut(0, pos + 1)
+        eng.draft_after(rows, picks)
+        out.extend(picks[:kept + 1])
+        kept_total += kept
+        tok, pos = picks[kept], pos + 1 + kept
+    assert out[:13] == plain[:13], (out, plain)
+    assert passes + kept_total >= 12
