@@ -51,6 +51,10 @@ __global__ void __launch_bounds__(128) embed_rows_kernel(const EmbedArgs a) {
     case WT_Q8_0: embed_row_q<Q80>(row, a.K, out, tid, 128); break;
     case WT_NVFP4: embed_row_q<NvFp4>(row, a.K, out, tid, 128); break;
     case WT_FP8_B128: embed_row_q<Fp8B128>(row, a.K, out, tid, 128); break;
+    case WT_Q4_0: embed_row_q<Q40>(row, a.K, out, tid, 128); break;
+    case WT_Q4_1: embed_row_q<Q41>(row, a.K, out, tid, 128); break;
+    case WT_Q5_0: embed_row_q<Q50>(row, a.K, out, tid, 128); break;
+    case WT_Q5_1: embed_row_q<Q51>(row, a.K, out, tid, 128); break;
     case WT_F32: for (int i = tid; i < a.K; i += 128) out[i] = reinterpret_cast<const float*>(row)[i]; break;
     case WT_F16: for (int i = tid; i < a.K; i += 128) out[i] = __half2float(reinterpret_cast<const __half*>(row)[i]); break;
     case WT_BF16: for (int i = tid; i < a.K; i += 128) out[i] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(row)[i]); break;

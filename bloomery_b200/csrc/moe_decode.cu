@@ -17,6 +17,12 @@
 
 namespace bl {
 
+// block-scaled planes and the re-laid 32-value block types share one kernel family
+static inline bool is_plane_family(int t) {
+  return t == WT_NVFP4 || t == WT_FP8_B128 || t == WT_Q4_0 || t == WT_Q4_1 || t == WT_Q5_0 || t == WT_Q5_1;
+}
+
+
 constexpr int kMaxExperts = 512;
 constexpr int kMaxTopK = 16;
 
@@ -357,6 +363,10 @@ __global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a)
       switch (a.gtype) {
         case WT_NVFP4: gate_up_rows<NvFp4>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         case WT_FP8_B128: gate_up_rows<Fp8B128>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q4_0: gate_up_rows<Q40>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q4_1: gate_up_rows<Q41>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q5_0: gate_up_rows<Q50>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q5_1: gate_up_rows<Q51>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         default: gacc[0] = gacc[1] = __int_as_float(0x7fc00000); uacc[0] = uacc[1] = 0.f;
       }
     } else {
@@ -473,6 +483,10 @@ __global__ void __launch_bounds__(256, UPL <= 3 ? 2 : 1) down_combine_kernel(con
       switch (a.dtype) {
         case WT_NVFP4: y = down_row<NvFp4, UPL>(a, m, d, lane, s_slot, s_w); break;
         case WT_FP8_B128: y = down_row<Fp8B128, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q4_0: y = down_row<Q40, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q4_1: y = down_row<Q41, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q5_0: y = down_row<Q50, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q5_1: y = down_row<Q51, UPL>(a, m, d, lane, s_slot, s_w); break;
         default: y = __int_as_float(0x7fc00000);
       }
     } else {
@@ -561,7 +575,7 @@ int bl_gate_up_sel(const int8_t* xq, const float* xds, const float* route_logits
                    cudaStream_t st) {
   BL_REQUIRE(K % 256 == 0 && I % 32 == 0 && M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
   BL_REQUIRE(gtype == utype, BL_ERR_TYPE);
-  BL_REQUIRE(gtype == WT_Q4_K || gtype == WT_Q5_K || gtype == WT_Q6_K || gtype == WT_Q8_0 || gtype == WT_NVFP4 || gtype == WT_FP8_B128, BL_ERR_TYPE);
+  BL_REQUIRE(gtype == WT_Q4_K || gtype == WT_Q5_K || gtype == WT_Q6_K || gtype == WT_Q8_0 || is_plane_family(gtype), BL_ERR_TYPE);
   BL_REQUIRE(E % 4 == 0 && E <= kMaxExperts && n_group >= 1 && n_group <= 16 && E % n_group == 0, BL_ERR_LIMIT);
   GateUpArgs a{};
   a.xq = xq; a.xds = (const float2*)xds;
@@ -570,7 +584,7 @@ int bl_gate_up_sel(const int8_t* xq, const float* xds, const float* route_logits
   a.gate = (const uint8_t*)gate; a.up = (const uint8_t*)up; a.gtype = gtype; a.utype = utype;
   a.K = K; a.I = I; a.E = E; a.n_used = n_used; a.M = M;
   a.actq = actq; a.actds = (float2*)actds; a.act_f32 = act_f32; a.fault = fault; a.layer = layer;
-  if (gtype == WT_NVFP4 || gtype == WT_FP8_B128) return (int)launch(gate_up_sel_kernel<2>, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
+  if (is_plane_family(gtype)) return (int)launch(gate_up_sel_kernel<2>, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
   return (int)launch(gate_up_sel_kernel<0>, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
 }
 
@@ -578,16 +592,17 @@ int bl_down_combine(const int8_t* actq, const float* actds, const int* ids, cons
                     const void* down, int dtype, int I, int H, int E, int n_used, int M, const float* resid,
                     long resid_stride, const float* extra, long extra_stride, float* out, long out_stride,
                     const void* push_desc, unsigned* fault, int layer, cudaStream_t st) {
-  BL_REQUIRE(I % 256 == 0 || ((dtype == WT_Q8_0 || dtype == WT_NVFP4) && I % 64 == 0) || (dtype == WT_FP8_B128 && I % 128 == 0), BL_ERR_SHAPE);
+  BL_REQUIRE(I % 256 == 0 || ((dtype == WT_Q8_0 || (is_plane_family(dtype) && dtype != WT_FP8_B128)) && I % 64 == 0) ||
+             (dtype == WT_FP8_B128 && I % 128 == 0), BL_ERR_SHAPE);
   BL_REQUIRE(M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
-  BL_REQUIRE(dtype == WT_Q4_K || dtype == WT_Q5_K || dtype == WT_Q6_K || dtype == WT_Q8_0 || dtype == WT_NVFP4 || dtype == WT_FP8_B128, BL_ERR_TYPE);
+  BL_REQUIRE(dtype == WT_Q4_K || dtype == WT_Q5_K || dtype == WT_Q6_K || dtype == WT_Q8_0 || is_plane_family(dtype), BL_ERR_TYPE);
   DownArgs a{actq, (const float2*)actds, ids, wts, slot_map, (const uint8_t*)down, dtype, I, H, E, n_used, M, resid,
              resid_stride, extra, extra_stride, out, out_stride, fault, layer, PushOut{}};
   if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks && M <= kMaxRows, BL_ERR_SHAPE); }
   const long total = (long)n_used * (I / 64);
   BL_REQUIRE(total <= 512, BL_ERR_LIMIT);
   dim3 grid((H + 7) / 8, M);
-  if (dtype == WT_NVFP4 || dtype == WT_FP8_B128) {
+  if (is_plane_family(dtype)) {
     if (total <= 96) return (int)launch(down_combine_kernel<3, 2>, grid, dim3(256), 0, st, a);
     if (total <= 192) return (int)launch(down_combine_kernel<6, 2>, grid, dim3(256), 0, st, a);
     return (int)launch(down_combine_kernel<16, 2>, grid, dim3(256), 0, st, a);

@@ -29,6 +29,10 @@ namespace bl {
 enum WType : int {
   WT_F32 = 0,
   WT_F16 = 1,
+  WT_Q4_0 = 2,
+  WT_Q4_1 = 3,
+  WT_Q5_0 = 6,
+  WT_Q5_1 = 7,
   WT_Q8_0 = 8,
   WT_Q4_K = 12,
   WT_Q5_K = 13,
@@ -373,6 +377,80 @@ struct Q80 {
 
 
 
+
+// ---------------------------------------------------------------------------------
+// The 32-value block family Q4_0 / Q4_1 / Q5_0 / Q5_1, re-laid as planes so every load is aligned:
+//   row = [codes K/2][fifth bits K/8 (5-bit types)][f16 d per block K/16][f16 m per block K/16 (_1 types)] pad 16
+// Codes keep the file's nibble order (byte i of a block: low nibble = value i, high nibble = value i + 16).
+// value = d * (q - 8 | 16)  (_0)   or   d * q + m  (_1)
+// ---------------------------------------------------------------------------------
+template <int BITS, bool HAS_MIN, int TYPE>
+struct Q32 {
+  static constexpr int kType = TYPE;
+  struct Regs { u32x4 q0, q1; uint32_t h0, h1, dd, mm; };
+  static BL_HD long off_d(int K) { return K / 2 + (BITS == 5 ? K / 8 : 0); }
+  static BL_HD long row_bytes(int K) { return ((off_d(K) + K / 16 + (HAS_MIN ? K / 16 : 0)) + 15) / 16 * 16; }
+  static BL_HD void load(const uint8_t* row, int u, int K, Regs& r) {
+    r.q0 = ld128(row + 32 * u);
+    r.q1 = ld128(row + 32 * u + 16);
+    if (BITS == 5) { r.h0 = ld32(row + K / 2 + 8 * u); r.h1 = ld32(row + K / 2 + 8 * u + 4); } else { r.h0 = r.h1 = 0; }
+    r.dd = ld32(row + off_d(K) + 4 * u);
+    r.mm = HAS_MIN ? ld32(row + off_d(K) + K / 16 + 4 * u) : 0u;
+  }
+  // four fifth-bits (bits 0..3 of x) to bit 4 of four bytes
+  static BL_HD uint32_t spread(uint32_t x) {
+    return ((x & 1u) | ((x & 2u) << 7) | ((x & 4u) << 14) | ((x & 8u) << 21)) << 4;
+  }
+  // the eight code words of block b (values 0..31 in order) as unsigned bytes
+  static BL_HD void codes(const Regs& r, int b, uint32_t* c) {
+    const u32x4& q = b ? r.q1 : r.q0;
+    const uint32_t h = b ? r.h1 : r.h0;
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      c[j] = w[j] & 0x0F0F0F0Fu;
+      c[4 + j] = (w[j] >> 4) & 0x0F0F0F0Fu;
+      if (BITS == 5) { c[j] |= spread(h >> (4 * j)); c[4 + j] |= spread(h >> (16 + 4 * j)); }
+    }
+  }
+  static BL_HD float dot(const Regs& r, const ActUnit& a) {
+    float acc = 0.f;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      uint32_t c[8];
+      codes(r, b, c);
+      int s = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s = dot4_us(c[j], a.q[8 * b + j], s);
+      const float d = half_bits_to_float((uint16_t)(r.dd >> (16 * b)));
+      const float da = b ? a.d1 : a.d0, sa = b ? a.s1 : a.s0;
+      if (HAS_MIN) acc += d * da * (float)s + half_bits_to_float((uint16_t)(r.mm >> (16 * b))) * sa;
+      else acc += d * (da * (float)s - (float)(BITS == 5 ? 16 : 8) * sa);
+    }
+    return acc;
+  }
+  static BL_HD void decode(const Regs& r, float* out) {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      uint32_t c[8];
+      codes(r, b, c);
+      const float d = half_bits_to_float((uint16_t)(r.dd >> (16 * b)));
+      const float m = HAS_MIN ? half_bits_to_float((uint16_t)(r.mm >> (16 * b))) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int q = (int)((c[j] >> (8 * k)) & 0xFF);
+          out[32 * b + 4 * j + k] = HAS_MIN ? d * (float)q + m : d * (float)(q - (BITS == 5 ? 16 : 8));
+        }
+    }
+  }
+};
+using Q40 = Q32<4, false, WT_Q4_0>;
+using Q41 = Q32<4, true, WT_Q4_1>;
+using Q50 = Q32<5, false, WT_Q5_0>;
+using Q51 = Q32<5, true, WT_Q5_1>;
+
 // ---------------------------------------------------------------------------------
 // E4M3 and E2M1 scalar decoders (host and device)
 // ---------------------------------------------------------------------------------
@@ -558,6 +636,18 @@ template <> struct Unit<Q80> {
 };
 
 
+template <int BITS, bool HAS_MIN, int TYPE> struct Unit<Q32<BITS, HAS_MIN, TYPE>> {
+  using T32 = Q32<BITS, HAS_MIN, TYPE>;
+  using Regs = typename T32::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int K, Regs& r) { T32::load(row, u, K, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    ActUnit a{xq + 16 * u, xds[2 * u].x, xds[2 * u].y, xds[2 * u + 1].x, xds[2 * u + 1].y};
+    return T32::dot(r, a);
+  }
+  static BL_HD void decodeu(const Regs& r, int, float* o) { T32::decode(r, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
+
 template <> struct Unit<NvFp4> {
   using Regs = NvFp4::Regs;
   static BL_HD void loadu(const uint8_t* row, int u, int K, Regs& r) { NvFp4::load(row, u, K, r); }
@@ -604,7 +694,8 @@ template <class T> struct ActOf {
   }
   static BL_HD float dot(const typename Unit<T>::Regs& r, int u, const ActRegs& a) {
     ActUnit au{a.q, a.d[0], a.s[0], a.d[1], a.s[1]};
-    if constexpr (T::kType == WT_Q8_0) return Q80::dot(r, au);
+    if constexpr (T::kType == WT_Q8_0 || T::kType == WT_Q4_0 || T::kType == WT_Q4_1 || T::kType == WT_Q5_0 ||
+                  T::kType == WT_Q5_1) return T::dot(r, au);
     else return T::dot(r, u, au);
   }
 };
@@ -662,6 +753,10 @@ BL_HD long resident_row_bytes(int wtype, int K) {
     case WT_Q5_K: return Q5K::row_bytes(K);
     case WT_Q6_K: return Q6K::row_bytes(K);
     case WT_Q8_0: return Q80::row_bytes(K);
+    case WT_Q4_0: return Q40::row_bytes(K);
+    case WT_Q4_1: return Q41::row_bytes(K);
+    case WT_Q5_0: return Q50::row_bytes(K);
+    case WT_Q5_1: return Q51::row_bytes(K);
     case WT_NVFP4: return NvFp4::row_bytes(K);
     case WT_FP8_B128: return Fp8B128::row_bytes(K);
     case WT_F32: return 4L * K;

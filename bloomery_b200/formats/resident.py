@@ -7,6 +7,8 @@ Values are never re-quantised on load; some block types are only re-laid so that
   Q4_K, Q5_K          file blocks unchanged (144 / 176 bytes, both multiples of 16)
   Q6_K                210-byte file blocks padded to 224: ql[128] qh[64] sc[16] d pad[14]
   Q8_0                per row: K int8 codes, then K/32 f16 scales, padded to 16 bytes
+  Q4_0 Q4_1 Q5_0 Q5_1 per row: nibble codes K/2, fifth bits K/8 (5-bit types), f16 d per block, f16 m per block
+                      (_1 types), padded to 16 bytes; nibble order inside a block as in the file
   F32 / F16 / BF16    unchanged
   NVFP4, FP8_B128     rows built from checkpoint planes by ``formats/planes.py``
 
@@ -21,14 +23,28 @@ import torch
 from .quant import QTYPES
 
 # weight-type ids shared with csrc/quant_units.cuh (equal to the ggml ids)
-WT = {"F32": 0, "F16": 1, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30, "NVFP4": 40, "FP8_B128": 41}
-INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0", "NVFP4", "FP8_B128")      # dotted against q8 activations
+WT = {"F32": 0, "F16": 1, "Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30, "NVFP4": 40, "FP8_B128": 41}
+INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "NVFP4", "FP8_B128")      # dotted against q8 activations
 PLANE_TYPES = ("NVFP4", "FP8_B128")
 FLOAT_TYPES = ("F32", "F16", "BF16")
 
 
 class UnsupportedType(ValueError):
     pass
+
+
+_Q32 = {"Q4_0": (4, False), "Q4_1": (4, True), "Q5_0": (5, False), "Q5_1": (5, True)}     # bits, has a min
+
+
+def _q32_fields(qtype: str):
+    """Byte ranges of d, m, qh, qs inside one file block."""
+    bits, has_min = _Q32[qtype]
+    o = 2
+    m = (o, o + 2) if has_min else None
+    o += 2 if has_min else 0
+    qh = (o, o + 4) if bits == 5 else None
+    o += 4 if bits == 5 else 0
+    return (0, 2), m, qh, (o, o + 16), o + 16
 
 
 def resident_row_bytes(qtype: str, k: int) -> int:
@@ -40,6 +56,9 @@ def resident_row_bytes(qtype: str, k: int) -> int:
         return k // 256 * 224
     if qtype == "Q8_0":
         return (k + k // 16 + 15) // 16 * 16
+    if qtype in _Q32:
+        bits, has_min = _Q32[qtype]
+        return (k // 2 + (k // 8 if bits == 5 else 0) + k // 16 * (2 if has_min else 1) + 15) // 16 * 16
     if qtype == "F32":
         return 4 * k
     if qtype in ("F16", "BF16"):
@@ -79,6 +98,21 @@ def to_resident(raw: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
         out = torch.zeros(rows, nsb, 224, dtype=torch.uint8, device=raw.device)
         out[..., :210] = raw.reshape(rows, nsb, 210)
         return out.reshape(rows, nsb * 224)
+    if qtype in _Q32:
+        d, m, qh, qs, bb = _q32_fields(qtype)
+        nb = k // 32
+        blk = raw.reshape(rows, nb, bb)
+        out = torch.zeros(rows, resident_row_bytes(qtype, k), dtype=torch.uint8, device=raw.device)
+        o = k // 2
+        out[:, :o] = blk[..., qs[0]:qs[1]].reshape(rows, o)
+        if qh:
+            out[:, o:o + k // 8] = blk[..., qh[0]:qh[1]].reshape(rows, k // 8)
+            o += k // 8
+        out[:, o:o + 2 * nb] = blk[..., d[0]:d[1]].reshape(rows, 2 * nb)
+        o += 2 * nb
+        if m:
+            out[:, o:o + 2 * nb] = blk[..., m[0]:m[1]].reshape(rows, 2 * nb)
+        return out
     if qtype == "Q8_0":
         nb = k // 32
         blk = raw.reshape(rows, nb, 34)
@@ -97,6 +131,20 @@ def from_resident(res: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
     if qtype == "Q6_K":
         nsb = k // 256
         return res.reshape(rows, nsb, 224)[..., :210].reshape(rows, nsb * 210).contiguous()
+    if qtype in _Q32:
+        d, m, qh, qs, bb = _q32_fields(qtype)
+        nb = k // 32
+        out = torch.empty(rows, nb, bb, dtype=torch.uint8, device=res.device)
+        o = k // 2
+        out[..., qs[0]:qs[1]] = res[:, :o].reshape(rows, nb, 16)
+        if qh:
+            out[..., qh[0]:qh[1]] = res[:, o:o + k // 8].reshape(rows, nb, 4)
+            o += k // 8
+        out[..., d[0]:d[1]] = res[:, o:o + 2 * nb].reshape(rows, nb, 2)
+        o += 2 * nb
+        if m:
+            out[..., m[0]:m[1]] = res[:, o:o + 2 * nb].reshape(rows, nb, 2)
+        return out.reshape(rows, nb * bb)
     if qtype == "Q8_0":
         nb = k // 32
         out = torch.empty(rows, nb, 34, dtype=torch.uint8, device=res.device)

@@ -70,11 +70,33 @@ def set_pdl(on: bool) -> None:
     cuda().bl_set_pdl(I(1 if on else 0))
 
 
+def _family(qtype: str) -> int:
+    """Kernel family of a weight type: 0 K-quants and Q8_0, 1 float rows, 2 planes and re-laid 32-value blocks."""
+    if qtype in ("F32", "F16", "BF16"):
+        return 1
+    return 2 if qtype in ("NVFP4", "FP8_B128", "Q4_0", "Q4_1", "Q5_0", "Q5_1") else 0
+
+
 def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torch.Tensor] = None,
          gain: Optional[torch.Tensor] = None, eps: float = 1e-6, xq: Optional[torch.Tensor] = None,
          xds: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
          red: Optional[ReduceIn] = None, push: Optional[PushOut] = None,
          fault: Optional[torch.Tensor] = None, layer: int = 0) -> None:
+    fams = [_family(sg.qtype) for sg in segs]
+    if len(set(fams) - {1}) > 1 or (2 in fams and 1 in fams):
+        # segments of different kernel families (e.g. a Q5_0 fallback tensor beside K-quants): one call per run
+        col, i = 0, 0
+        while i < len(segs):
+            j = i
+            while j < len(segs) and fams[j] == fams[i]:
+                j += 1
+            width = sum(sg.rows for sg in segs[i:j])
+            gemv(segs[i:j], M, out[:, col:col + width], x=x, gain=gain, eps=eps, xq=xq, xds=xds,
+                 resid=resid[:, col:col + width] if resid is not None else None, red=red if i == 0 else None,
+                 push=push, fault=fault, layer=layer)
+            col += width
+            i = j
+        return
     n = len(segs)
     K = segs[0].k
     wp = (ctypes.c_void_p * n)(*[s.data.data_ptr() for s in segs])
