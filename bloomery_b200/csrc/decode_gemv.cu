@@ -313,6 +313,8 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
       switch (s.wtype) {
         case WT_NVFP4: rows_q<NvFp4, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
         case WT_FP8_B128: rows_q<Fp8B128, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        case WT_Q2_K: rows_q<Q2K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        case WT_Q3_K: rows_q<Q3K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
         case WT_Q4_0: rows_q<Q40, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
         case WT_Q4_1: rows_q<Q41, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
         case WT_Q5_0: rows_q<Q50, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
@@ -401,7 +403,7 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
     total_bytes += (double)rows[s] * rbs[s];
     if (wtypes[s] == WT_F32 || wtypes[s] == WT_F16 || wtypes[s] == WT_BF16) floatw = true;
     else if (wtypes[s] == WT_NVFP4 || wtypes[s] == WT_FP8_B128 || wtypes[s] == WT_Q4_0 || wtypes[s] == WT_Q4_1 ||
-             wtypes[s] == WT_Q5_0 || wtypes[s] == WT_Q5_1) planes = true;
+             wtypes[s] == WT_Q5_0 || wtypes[s] == WT_Q5_1 || wtypes[s] == WT_Q2_K || wtypes[s] == WT_Q3_K) planes = true;
     else ggml = true;
   }
   BL_REQUIRE(!(floatw && !norm), BL_ERR_TYPE);

@@ -51,6 +51,8 @@ __global__ void __launch_bounds__(128) embed_rows_kernel(const EmbedArgs a) {
     case WT_Q8_0: embed_row_q<Q80>(row, a.K, out, tid, 128); break;
     case WT_NVFP4: embed_row_q<NvFp4>(row, a.K, out, tid, 128); break;
     case WT_FP8_B128: embed_row_q<Fp8B128>(row, a.K, out, tid, 128); break;
+    case WT_Q2_K: embed_row_q<Q2K>(row, a.K, out, tid, 128); break;
+    case WT_Q3_K: embed_row_q<Q3K>(row, a.K, out, tid, 128); break;
     case WT_Q4_0: embed_row_q<Q40>(row, a.K, out, tid, 128); break;
     case WT_Q4_1: embed_row_q<Q41>(row, a.K, out, tid, 128); break;
     case WT_Q5_0: embed_row_q<Q50>(row, a.K, out, tid, 128); break;

@@ -45,6 +45,8 @@ float dot_any(int wtype, const uint8_t* row, int K, const int8_t* xq, const floa
     case WT_Q8_0: return run(Q80{});
     case WT_NVFP4: return run(NvFp4{});
     case WT_FP8_B128: return run(Fp8B128{});
+    case WT_Q2_K: return run(Q2K{});
+    case WT_Q3_K: return run(Q3K{});
     case WT_Q4_0: return run(Q40{});
     case WT_Q4_1: return run(Q41{});
     case WT_Q5_0: return run(Q50{});

@@ -44,6 +44,8 @@ float row_dot_any(int wtype, const uint8_t* row, int K, const int8_t* xq, const 
     case WT_Q8_0: return row_dot_scalar<Q80>(row, K, xq, xds);
     case WT_NVFP4: return row_dot_scalar<NvFp4>(row, K, xq, xds);
     case WT_FP8_B128: return row_dot_scalar<Fp8B128>(row, K, xq, xds);
+    case WT_Q2_K: return row_dot_scalar<Q2K>(row, K, xq, xds);
+    case WT_Q3_K: return row_dot_scalar<Q3K>(row, K, xq, xds);
     case WT_Q4_0: return row_dot_scalar<Q40>(row, K, xq, xds);
     case WT_Q4_1: return row_dot_scalar<Q41>(row, K, xq, xds);
     case WT_Q5_0: return row_dot_scalar<Q50>(row, K, xq, xds);
@@ -117,6 +119,8 @@ int blh_decode_rows(int wtype, const uint8_t* w, int rows, int K, float* out) {
       case WT_Q8_0: row_decode<Q80>(row, K, o); break;
       case WT_NVFP4: row_decode<NvFp4>(row, K, o); break;
       case WT_FP8_B128: row_decode<Fp8B128>(row, K, o); break;
+      case WT_Q2_K: row_decode<Q2K>(row, K, o); break;
+      case WT_Q3_K: row_decode<Q3K>(row, K, o); break;
       case WT_Q4_0: row_decode<Q40>(row, K, o); break;
       case WT_Q4_1: row_decode<Q41>(row, K, o); break;
       case WT_Q5_0: row_decode<Q50>(row, K, o); break;

@@ -19,7 +19,7 @@ namespace bl {
 
 // block-scaled planes and the re-laid 32-value block types share one kernel family
 static inline bool is_plane_family(int t) {
-  return t == WT_NVFP4 || t == WT_FP8_B128 || t == WT_Q4_0 || t == WT_Q4_1 || t == WT_Q5_0 || t == WT_Q5_1;
+  return t == WT_NVFP4 || t == WT_FP8_B128 || t == WT_Q4_0 || t == WT_Q4_1 || t == WT_Q5_0 || t == WT_Q5_1 || t == WT_Q2_K || t == WT_Q3_K;
 }
 
 
@@ -363,6 +363,8 @@ __global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a)
       switch (a.gtype) {
         case WT_NVFP4: gate_up_rows<NvFp4>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         case WT_FP8_B128: gate_up_rows<Fp8B128>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q2_K: gate_up_rows<Q2K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q3_K: gate_up_rows<Q3K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         case WT_Q4_0: gate_up_rows<Q40>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         case WT_Q4_1: gate_up_rows<Q41>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         case WT_Q5_0: gate_up_rows<Q50>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
@@ -483,6 +485,8 @@ __global__ void __launch_bounds__(256, UPL <= 3 ? 2 : 1) down_combine_kernel(con
       switch (a.dtype) {
         case WT_NVFP4: y = down_row<NvFp4, UPL>(a, m, d, lane, s_slot, s_w); break;
         case WT_FP8_B128: y = down_row<Fp8B128, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q2_K: y = down_row<Q2K, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q3_K: y = down_row<Q3K, UPL>(a, m, d, lane, s_slot, s_w); break;
         case WT_Q4_0: y = down_row<Q40, UPL>(a, m, d, lane, s_slot, s_w); break;
         case WT_Q4_1: y = down_row<Q41, UPL>(a, m, d, lane, s_slot, s_w); break;
         case WT_Q5_0: y = down_row<Q50, UPL>(a, m, d, lane, s_slot, s_w); break;
@@ -592,7 +596,7 @@ int bl_down_combine(const int8_t* actq, const float* actds, const int* ids, cons
                     const void* down, int dtype, int I, int H, int E, int n_used, int M, const float* resid,
                     long resid_stride, const float* extra, long extra_stride, float* out, long out_stride,
                     const void* push_desc, unsigned* fault, int layer, cudaStream_t st) {
-  BL_REQUIRE(I % 256 == 0 || ((dtype == WT_Q8_0 || (is_plane_family(dtype) && dtype != WT_FP8_B128)) && I % 64 == 0) ||
+  BL_REQUIRE(I % 256 == 0 || ((dtype == WT_Q8_0 || (is_plane_family(dtype) && dtype != WT_FP8_B128 && dtype != WT_Q2_K && dtype != WT_Q3_K)) && I % 64 == 0) ||
              (dtype == WT_FP8_B128 && I % 128 == 0), BL_ERR_SHAPE);
   BL_REQUIRE(M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
   BL_REQUIRE(dtype == WT_Q4_K || dtype == WT_Q5_K || dtype == WT_Q6_K || dtype == WT_Q8_0 || is_plane_family(dtype), BL_ERR_TYPE);

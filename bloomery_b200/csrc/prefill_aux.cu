@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(256) dequant_bf16_kernel(const uint8_t* w, int
     case WT_Q8_0: expand_units<Q80>(w, rows, K, out); break;
     case WT_NVFP4: expand_units<NvFp4>(w, rows, K, out); break;
     case WT_FP8_B128: expand_units<Fp8B128>(w, rows, K, out); break;
+    case WT_Q2_K: expand_units<Q2K>(w, rows, K, out); break;
+    case WT_Q3_K: expand_units<Q3K>(w, rows, K, out); break;
     case WT_Q4_0: expand_units<Q40>(w, rows, K, out); break;
     case WT_Q4_1: expand_units<Q41>(w, rows, K, out); break;
     case WT_Q5_0: expand_units<Q50>(w, rows, K, out); break;

@@ -34,6 +34,8 @@ enum WType : int {
   WT_Q5_0 = 6,
   WT_Q5_1 = 7,
   WT_Q8_0 = 8,
+  WT_Q2_K = 10,
+  WT_Q3_K = 11,
   WT_Q4_K = 12,
   WT_Q5_K = 13,
   WT_Q6_K = 14,
@@ -378,6 +380,124 @@ struct Q80 {
 
 
 
+
+// ---------------------------------------------------------------------------------
+// Q2_K: 84-byte file blocks re-laid to 96: qs[64] scales[16] d dmin pad[12].
+// Unit u of a super-block: n = (u >> 1) & 1 picks the 32 code bytes, jp = u & 1 the bit pairs
+// (shifts 4jp and 4jp + 2); its 64 values are consecutive.  value = d * (sc & 15) * q - dmin * (sc >> 4).
+// ---------------------------------------------------------------------------------
+struct Q2K {
+  static constexpr int kType = WT_Q2_K;
+  static constexpr int kSbBytes = 96;
+  struct Regs { u32x4 q0, q1; uint32_t sc, dm; };
+  static BL_HD long row_bytes(int K) { return (long)(K / 256) * kSbBytes; }
+  static BL_HD void load(const uint8_t* row, int u, Regs& r) {
+    const uint8_t* p = row + (long)(u >> 2) * kSbBytes;
+    const int n = (u >> 1) & 1, jp = u & 1;
+    r.q0 = ld128(p + 32 * n);
+    r.q1 = ld128(p + 32 * n + 16);
+    r.sc = ld32(p + 64 + 8 * n + 4 * jp);
+    r.dm = ld32(p + 80);
+  }
+  static BL_HD float dot(const Regs& r, int u, const ActUnit& a) {
+    const int jp = u & 1;
+    const float d = half_bits_to_float((uint16_t)(r.dm & 0xFFFF)), dmin = half_bits_to_float((uint16_t)(r.dm >> 16));
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const u32x4& q = (g & 1) ? r.q1 : r.q0;
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      const int shift = 4 * jp + 2 * (g >> 1);
+      int s = 0, sx = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s = dot4_us((w[i] >> shift) & 0x03030303u, a.q[4 * g + i], s);
+        sx = dot4(0x01010101u, a.q[4 * g + i], sx);
+      }
+      const uint32_t scb = (r.sc >> (8 * g)) & 0xFF;
+      acc += ((g >> 1) ? a.d1 : a.d0) * (d * (float)(scb & 0xF) * (float)s - dmin * (float)(scb >> 4) * (float)sx);
+    }
+    return acc;
+  }
+  static BL_HD void decode(const Regs& r, int u, float* out) {
+    const int jp = u & 1;
+    const float d = half_bits_to_float((uint16_t)(r.dm & 0xFFFF)), dmin = half_bits_to_float((uint16_t)(r.dm >> 16));
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const u32x4& q = (g & 1) ? r.q1 : r.q0;
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      const int shift = 4 * jp + 2 * (g >> 1);
+      const uint32_t scb = (r.sc >> (8 * g)) & 0xFF;
+      const float dl = d * (float)(scb & 0xF), ml = dmin * (float)(scb >> 4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) out[16 * g + 4 * i + b] = (float)((w[i] >> (8 * b + shift)) & 3) * dl - ml;
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------
+// Q3_K: 110-byte file blocks re-laid to 128: qs[64] hmask[32] sc[16] (the 6-bit scales unpacked to
+// signed bytes, 32 already subtracted) d pad[14].  Units as for Q2_K.  value = d * sc * (q - (hbit ? 0 : 4)).
+// ---------------------------------------------------------------------------------
+struct Q3K {
+  static constexpr int kType = WT_Q3_K;
+  static constexpr int kSbBytes = 128;
+  struct Regs { u32x4 q0, q1, h0, h1; uint32_t sc, d; };
+  static BL_HD long row_bytes(int K) { return (long)(K / 256) * kSbBytes; }
+  static BL_HD void load(const uint8_t* row, int u, Regs& r) {
+    const uint8_t* p = row + (long)(u >> 2) * kSbBytes;
+    const int n = (u >> 1) & 1, jp = u & 1;
+    r.q0 = ld128(p + 32 * n);
+    r.q1 = ld128(p + 32 * n + 16);
+    r.h0 = ld128(p + 64);
+    r.h1 = ld128(p + 80);
+    r.sc = ld32(p + 96 + 8 * n + 4 * jp);
+    r.d = ld32(p + 112) & 0xFFFF;
+  }
+  static BL_HD float dot(const Regs& r, int u, const ActUnit& a) {
+    const int n = (u >> 1) & 1, jp = u & 1;
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const u32x4& q = (g & 1) ? r.q1 : r.q0;
+      const u32x4& h = (g & 1) ? r.h1 : r.h0;
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w}, hw[4] = {h.x, h.y, h.z, h.w};
+      const int shift = 4 * jp + 2 * (g >> 1), hbit = 4 * n + 2 * jp + (g >> 1);
+      int s = 0, sh = 0, sx = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s = dot4_us((w[i] >> shift) & 0x03030303u, a.q[4 * g + i], s);
+        sh = dot4_us((hw[i] >> hbit) & 0x01010101u, a.q[4 * g + i], sh);
+        sx = dot4(0x01010101u, a.q[4 * g + i], sx);
+      }
+      const int sc = (int)(int8_t)((r.sc >> (8 * g)) & 0xFF);
+      acc += ((g >> 1) ? a.d1 : a.d0) * (float)(sc * (s + 4 * sh - 4 * sx));
+    }
+    return half_bits_to_float((uint16_t)r.d) * acc;
+  }
+  static BL_HD void decode(const Regs& r, int u, float* out) {
+    const int n = (u >> 1) & 1, jp = u & 1;
+    const float d = half_bits_to_float((uint16_t)r.d);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const u32x4& q = (g & 1) ? r.q1 : r.q0;
+      const u32x4& h = (g & 1) ? r.h1 : r.h0;
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w}, hw[4] = {h.x, h.y, h.z, h.w};
+      const int shift = 4 * jp + 2 * (g >> 1), hbit = 4 * n + 2 * jp + (g >> 1);
+      const float dl = d * (float)(int)(int8_t)((r.sc >> (8 * g)) & 0xFF);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int qq = (int)((w[i] >> (8 * b + shift)) & 3) - (((hw[i] >> (8 * b + hbit)) & 1) ? 0 : 4);
+          out[16 * g + 4 * i + b] = (float)qq * dl;
+        }
+    }
+  }
+};
+
 // ---------------------------------------------------------------------------------
 // The 32-value block family Q4_0 / Q4_1 / Q5_0 / Q5_1, re-laid as planes so every load is aligned:
 //   row = [codes K/2][fifth bits K/8 (5-bit types)][f16 d per block K/16][f16 m per block K/16 (_1 types)] pad 16
@@ -636,6 +756,27 @@ template <> struct Unit<Q80> {
 };
 
 
+template <> struct Unit<Q2K> {
+  using Regs = Q2K::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int, Regs& r) { Q2K::load(row, u, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    ActUnit a{xq + 16 * u, xds[2 * u].x, xds[2 * u].y, xds[2 * u + 1].x, xds[2 * u + 1].y};
+    return Q2K::dot(r, u, a);
+  }
+  static BL_HD void decodeu(const Regs& r, int u, float* o) { Q2K::decode(r, u, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
+template <> struct Unit<Q3K> {
+  using Regs = Q3K::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int, Regs& r) { Q3K::load(row, u, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    ActUnit a{xq + 16 * u, xds[2 * u].x, xds[2 * u].y, xds[2 * u + 1].x, xds[2 * u + 1].y};
+    return Q3K::dot(r, u, a);
+  }
+  static BL_HD void decodeu(const Regs& r, int u, float* o) { Q3K::decode(r, u, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
+
 template <int BITS, bool HAS_MIN, int TYPE> struct Unit<Q32<BITS, HAS_MIN, TYPE>> {
   using T32 = Q32<BITS, HAS_MIN, TYPE>;
   using Regs = typename T32::Regs;
@@ -753,6 +894,8 @@ BL_HD long resident_row_bytes(int wtype, int K) {
     case WT_Q5_K: return Q5K::row_bytes(K);
     case WT_Q6_K: return Q6K::row_bytes(K);
     case WT_Q8_0: return Q80::row_bytes(K);
+    case WT_Q2_K: return Q2K::row_bytes(K);
+    case WT_Q3_K: return Q3K::row_bytes(K);
     case WT_Q4_0: return Q40::row_bytes(K);
     case WT_Q4_1: return Q41::row_bytes(K);
     case WT_Q5_0: return Q50::row_bytes(K);

@@ -6,6 +6,9 @@ Values are never re-quantised on load; some block types are only re-laid so that
 
   Q4_K, Q5_K          file blocks unchanged (144 / 176 bytes, both multiples of 16)
   Q6_K                210-byte file blocks padded to 224: ql[128] qh[64] sc[16] d pad[14]
+  Q2_K                84-byte file blocks re-laid to 96: qs[64] scales[16] d dmin pad[12]
+  Q3_K                110-byte file blocks re-laid to 128: qs[64] hmask[32] sc[16] d pad[14]; the sixteen 6-bit
+                      scales are unpacked to signed bytes with the 32 already subtracted (same values)
   Q8_0                per row: K int8 codes, then K/32 f16 scales, padded to 16 bytes
   Q4_0 Q4_1 Q5_0 Q5_1 per row: nibble codes K/2, fifth bits K/8 (5-bit types), f16 d per block, f16 m per block
                       (_1 types), padded to 16 bytes; nibble order inside a block as in the file
@@ -23,8 +26,8 @@ import torch
 from .quant import QTYPES
 
 # weight-type ids shared with csrc/quant_units.cuh (equal to the ggml ids)
-WT = {"F32": 0, "F16": 1, "Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30, "NVFP4": 40, "FP8_B128": 41}
-INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "NVFP4", "FP8_B128")      # dotted against q8 activations
+WT = {"F32": 0, "F16": 1, "Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30, "NVFP4": 40, "FP8_B128": 41}
+INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q2_K", "Q3_K", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "NVFP4", "FP8_B128")      # dotted against q8 activations
 PLANE_TYPES = ("NVFP4", "FP8_B128")
 FLOAT_TYPES = ("F32", "F16", "BF16")
 
@@ -56,6 +59,10 @@ def resident_row_bytes(qtype: str, k: int) -> int:
         return k // 256 * 224
     if qtype == "Q8_0":
         return (k + k // 16 + 15) // 16 * 16
+    if qtype == "Q2_K":
+        return k // 256 * 96
+    if qtype == "Q3_K":
+        return k // 256 * 128
     if qtype in _Q32:
         bits, has_min = _Q32[qtype]
         return (k // 2 + (k // 8 if bits == 5 else 0) + k // 16 * (2 if has_min else 1) + 15) // 16 * 16
@@ -98,6 +105,22 @@ def to_resident(raw: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
         out = torch.zeros(rows, nsb, 224, dtype=torch.uint8, device=raw.device)
         out[..., :210] = raw.reshape(rows, nsb, 210)
         return out.reshape(rows, nsb * 224)
+    if qtype == "Q2_K":
+        nsb = k // 256
+        blk = raw.reshape(rows, nsb, 84)
+        out = torch.zeros(rows, nsb, 96, dtype=torch.uint8, device=raw.device)
+        out[..., 0:64], out[..., 64:80], out[..., 80:84] = blk[..., 16:80], blk[..., 0:16], blk[..., 80:84]
+        return out.reshape(rows, nsb * 96)
+    if qtype == "Q3_K":
+        nsb = k // 256
+        blk = raw.reshape(rows, nsb, 110)
+        sb = blk[..., 96:108].to(torch.int32)
+        lo4 = torch.cat([sb[..., 0:8] & 0xF, sb[..., 0:8] >> 4], -1)
+        hi2 = torch.cat([(sb[..., 8:12] >> s) & 3 for s in (0, 2, 4, 6)], -1)
+        sc = ((lo4 | (hi2 << 4)) - 32).to(torch.int8).view(torch.uint8)
+        out = torch.zeros(rows, nsb, 128, dtype=torch.uint8, device=raw.device)
+        out[..., 0:64], out[..., 64:96], out[..., 96:112], out[..., 112:114] = blk[..., 32:96], blk[..., 0:32], sc, blk[..., 108:110]
+        return out.reshape(rows, nsb * 128)
     if qtype in _Q32:
         d, m, qh, qs, bb = _q32_fields(qtype)
         nb = k // 32
@@ -131,6 +154,24 @@ def from_resident(res: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
     if qtype == "Q6_K":
         nsb = k // 256
         return res.reshape(rows, nsb, 224)[..., :210].reshape(rows, nsb * 210).contiguous()
+    if qtype == "Q2_K":
+        nsb = k // 256
+        r = res.reshape(rows, nsb, 96)
+        out = torch.empty(rows, nsb, 84, dtype=torch.uint8, device=res.device)
+        out[..., 16:80], out[..., 0:16], out[..., 80:84] = r[..., 0:64], r[..., 64:80], r[..., 80:84]
+        return out.reshape(rows, nsb * 84)
+    if qtype == "Q3_K":
+        nsb = k // 256
+        r = res.reshape(rows, nsb, 128)
+        sc = r[..., 96:112].view(torch.int8).to(torch.int32) + 32          # back to the 6-bit codes
+        lo, hi = sc & 0xF, sc >> 4
+        packed = torch.zeros(rows, nsb, 12, dtype=torch.int32, device=res.device)
+        packed[..., 0:8] = lo[..., 0:8] | (lo[..., 8:16] << 4)
+        for j in range(4):
+            packed[..., 8:12] |= hi[..., 4 * j:4 * j + 4] << (2 * j)
+        out = torch.empty(rows, nsb, 110, dtype=torch.uint8, device=res.device)
+        out[..., 32:96], out[..., 0:32], out[..., 96:108], out[..., 108:110] = r[..., 0:64], r[..., 64:96], packed.to(torch.uint8), r[..., 112:114]
+        return out.reshape(rows, nsb * 110)
     if qtype in _Q32:
         d, m, qh, qs, bb = _q32_fields(qtype)
         nb = k // 32

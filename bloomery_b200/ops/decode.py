@@ -74,7 +74,7 @@ def _family(qtype: str) -> int:
     """Kernel family of a weight type: 0 K-quants and Q8_0, 1 float rows, 2 planes and re-laid 32-value blocks."""
     if qtype in ("F32", "F16", "BF16"):
         return 1
-    return 2 if qtype in ("NVFP4", "FP8_B128", "Q4_0", "Q4_1", "Q5_0", "Q5_1") else 0
+    return 2 if qtype in ("NVFP4", "FP8_B128", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K") else 0
 
 
 def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torch.Tensor] = None,

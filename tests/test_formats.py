@@ -125,7 +125,7 @@ def test_gguf_split_shards(tmp_path):
         assert g.tensor_f32("b.weight").shape == (2, 256)
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K"])
 def test_resident_roundtrip_and_host_units(t):
     torch.manual_seed(3)
     K = 1024

@@ -22,7 +22,7 @@ def _qw(w, t):
     return QWeight(res, t, w.shape[-1]), wd.reshape(w.shape)
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "NVFP4", "FP8_B128", "Q4_0", "Q4_1", "Q5_0", "Q5_1"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "NVFP4", "FP8_B128", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K"])
 @pytest.mark.parametrize("M", [1, 3, 8])
 def test_gemv_norm_matches_fp32(t, M):
     from bloomery_b200.ops import decode as K
@@ -166,7 +166,7 @@ def test_gate_up_routes_like_route_rows():
 
 
 @pytest.mark.parametrize("gt,dt", [("Q4_K", "Q4_K"), ("Q4_K", "Q6_K"), ("Q8_0", "Q8_0"), ("Q5_K", "Q5_K"), ("NVFP4", "NVFP4"),
-                                   ("FP8_B128", "FP8_B128"), ("Q4_0", "Q5_0"), ("Q5_1", "Q4_1")])
+                                   ("FP8_B128", "FP8_B128"), ("Q4_0", "Q5_0"), ("Q5_1", "Q4_1"), ("Q2_K", "Q3_K")])
 def test_moe_sel_chain(gt, dt):
     from bloomery_b200.ops import decode as K
     torch.manual_seed(4)
