@@ -55,7 +55,8 @@ def bucket_of(m: int) -> int:
 
 class DecodeEngine:
     def __init__(self, weights: Weights, n_slots: int = 1, slot_ctx: int = 4096, n_seg: Optional[int] = None,
-                 use_graphs: bool = True, keep_logits: bool = True, engine_bound_s: float = 60.0):
+                 use_graphs: bool = True, keep_logits: bool = True, engine_bound_s: float = 60.0,
+                 layers: Optional[Tuple[int, int]] = None, stage_first: bool = True, stage_last: bool = True):
         self.w = weights
         self.spec: ModelSpec = weights.spec
         s = self.spec
@@ -69,12 +70,16 @@ class DecodeEngine:
         max_pages = (slot_ctx + PAGE - 1) // PAGE
         # multi-token-prediction layers ride behind the trunk when the checkpoint carries them
         self.n_mtp = s.n_mtp if f"blk.{s.n_layer}.nextn.eh_proj.weight" in weights.q else 0
+        # pipeline stage: this engine runs layers [lo, hi) only; the first stage embeds, the last one has the head
+        self.lo, self.hi = layers if layers is not None else (0, s.n_layer)
+        self.stage_first, self.stage_last = stage_first, stage_last
+        n_kv_layers = (self.hi - self.lo) + (self.n_mtp if stage_last else 0)
         sm = K.sm_count(dev)
         if s.mla:
-            self.kv = KvPool(s.n_layer + self.n_mtp, 1, s.kv_lora + s.rope_dim, n_slots * max_pages, n_slots, max_pages, dev, v_dim=0)
+            self.kv = KvPool(n_kv_layers, 1, s.kv_lora + s.rope_dim, n_slots * max_pages, n_slots, max_pages, dev, v_dim=0)
             self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, 2 * sm // ((s.n_q + 15) // 16))))
         else:
-            self.kv = KvPool(s.n_layer + self.n_mtp, s.n_kv, s.head_dim, n_slots * max_pages, n_slots, max_pages, dev)
+            self.kv = KvPool(n_kv_layers, s.n_kv, s.head_dim, n_slots * max_pages, n_slots, max_pages, dev)
             self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, sm // s.n_kv)))
         H, V = s.hidden, s.vocab
         f32 = dict(dtype=torch.float32, device=dev)
@@ -154,7 +159,7 @@ class DecodeEngine:
         self.launches_per_step = 0
         self.steps = 0
         # prompts at least this long use the GEMM path (0 = never; the GEMM path serves the GQA + routed-expert plan)
-        self.gemm_threshold = 0 if (s.mla or s.n_shared) else 64
+        self.gemm_threshold = 0 if (s.mla or s.n_shared or layers is not None) else 64
         self.ubatch = 4096
         self._gemm_prefill = None
         self._stream = torch.cuda.Stream(device=dev)
@@ -174,11 +179,11 @@ class DecodeEngine:
         s, w = self.spec, self.w
         n = 0
         x = self.x
-        K.embed_rows(self.tokens, M, w.q["token_embd.weight"], s.vocab, x, self.fault); n += 1
-        kvp = self.kv
-        for il in range(s.n_layer):
+        if self.stage_first:
+            K.embed_rows(self.tokens, M, w.q["token_embd.weight"], s.vocab, x, self.fault); n += 1
+        for il in range(self.lo, self.hi):
             n += self._layer(il, M, x)
-        if head:
+        if head and self.stage_last:
             head_w = w.q.get("output.weight", w.q["token_embd.weight"])
             K.gemv([head_w], M, self.logits, x=x, gain=w.f["output_norm.weight"], eps=s.rms_eps,
                    fault=self.fault, layer=s.n_layer); n += 1
@@ -300,9 +305,9 @@ class DecodeEngine:
                x=x, gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il)
         K.qk_norm_rope_append(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
                               self.inv_freq, s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M,
-                              self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out,
+                              self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il - self.lo], kvp.v[il - self.lo], self.q_out,
                               self.fault, il)
-        K.flash_decode(self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
+        K.flash_decode(self.q_out, kvp.k[il - self.lo], kvp.v[il - self.lo], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
                        s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
                        self.attn_q, self.attn_ds, self.fault, il)
         return 4
@@ -317,7 +322,7 @@ class DecodeEngine:
         K.gemv([first, w.q[b + "attn_kv_a_mqa.weight"]], M, self.qkv, x=x, gain=w.f[b + "attn_norm.weight"],
                eps=s.rms_eps, fault=self.fault, layer=il); n += 1
         K.mla_kv_append(self.qkv[:, self.qa_w:], w.f[b + "attn_kv_a_norm.weight"], self.inv_freq, s.rms_eps, M,
-                        self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], self.fault, il); n += 1
+                        self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il - self.lo], self.fault, il); n += 1
         if s.q_lora:
             K.gemv([w.q[b + "attn_q_b.weight"]], M, self.q_full, x=self.qkv[:, :s.q_lora],
                    gain=w.f[b + "attn_q_a_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il); n += 1
@@ -326,7 +331,7 @@ class DecodeEngine:
             q = self.qkv[:, :self.qa_w]
         K.mla_q_absorb(q, w.f[b + "attn_k_b.weight"], self.inv_freq, self.attn_scale, s.n_q, s.nope_dim, M,
                        self.row_pos, self.row_seq, self.q_out); n += 1
-        K.mla_flash_decode(self.q_out, kvp.k[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages, s.n_q, M,
+        K.mla_flash_decode(self.q_out, kvp.k[il - self.lo], self.row_pos, self.row_seq, kvp.table, kvp.n_pages, s.n_q, M,
                            self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, w.f[b + "attn_v_b.weight"], s.v_dim,
                            None, self.attn_q, self.attn_ds, self.fault, il); n += 2
         return n

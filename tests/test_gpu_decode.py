@@ -418,3 +418,33 @@ def test_two_slots_one_pass():
     eng.prefill(0, a[:-1]); eng.prefill(1, b[:-1])
     eng.step([(0, a[-1], 3), (1, b[-1], 2)])
     assert torch.equal(eng.logits[0], la) and torch.equal(eng.logits[1], lb)
+
+
+def test_two_pipeline_stages_equal_one_stage_bit_for_bit():
+    """The stage axis: layers 0-1 and 2-3 as two engines with their own weights, KV and graphs (both on this GPU
+    here), hidden rows copied across the boundary; picks and logits equal the one-stage engine's exactly."""
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import synth_tensors
+    from bloomery_b200.parallel.pipeline import PipelineEngine, split_layers, stage_items
+    spec, one, _ = _tiny_engine(graphs=True, n_slots=2)
+    items = list(synth_tensors(spec, "cpu", seed=7))
+    assert split_layers(48, 3, [1, 1, 2]) == [(0, 12), (12, 24), (24, 48)]
+    pipe = PipelineEngine(spec, lambda lo, hi, f, l: stage_items(iter(items), spec, lo, hi, f, l), [DEV, DEV],
+                          n_slots=2, slot_ctx=512, use_graphs=True)
+    assert pipe.ranges == [(0, 2), (2, 4)] and "token_embd.weight" in pipe.stages[0].w.q
+    assert not any(k.startswith("blk.3.") for k in pipe.stages[0].w.q) and pipe.stages[1].kv.k.shape[0] == 2
+    g = torch.Generator().manual_seed(17)
+    prompt = torch.randint(0, spec.vocab, (19,), generator=g).tolist()
+    a, b = one.prefill(0, prompt, gemm=False), pipe.prefill(0, prompt)
+    assert a == b
+    n_last = len(prompt) % 8 or 8
+    assert torch.equal(one.logits[:n_last], pipe.logits[:n_last])
+    tok_a = tok_b = a
+    for i in range(6):
+        rows_a = [(0, tok_a, len(prompt) + i), (1, 5 + i, i)]
+        pa, pb = one.step(rows_a), pipe.step([(0, tok_b, len(prompt) + i), (1, 5 + i, i)])
+        assert pa == pb and torch.equal(one.logits[:2], pipe.logits[:2])
+        tok_a, tok_b = pa[0], pb[0]
+    pipe.cut(0, 10)
+    one.cut(0, 10)
+    assert one.step([(0, 7, 10)]) == pipe.step([(0, 7, 10)])
