@@ -467,7 +467,10 @@ class Handler(BaseHTTPRequestHandler):
         data = []
         for i, text in enumerate(items):
             ids = st.engine.tokenizer.encode(str(text))
-            vec = st.engine.embed(ids)
+            if len(ids) + 1 > st.engine.slot_ctx:
+                raise ApiError(400, f"input {i} has {len(ids)} tokens, more than the slot context of {st.engine.slot_ctx}")
+            # on the engine thread, between rounds: the engine's buffers belong to that thread
+            vec = st.worker.run_on_engine_thread(lambda ids=ids: st.engine.embed(ids)) if st.worker else st.engine.embed(ids)
             if vec is None:
                 raise ApiError(501, "this model has no embedding head", "not_supported_error")
             data.append({"object": "embedding", "index": i, "embedding": [float(x) for x in vec]})

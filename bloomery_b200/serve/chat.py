@@ -234,7 +234,10 @@ class ToolCallStream:
                 self.buf = self.buf[i:]
                 return text_out, calls
             text_out += self.buf[:i]
-            _, got = parse_tool_calls(self.buf[i:j + len(self.close)], self.fmt)
+            block = self.buf[i:j + len(self.close)]
+            _, got = parse_tool_calls(block, self.fmt)
+            if not got:
+                text_out += block              # a closed block that is no call stays text, as in the one-shot scan
             for c in got:
                 c["id"] = f"call_{self.n_calls}"
                 c["index"] = self.n_calls

@@ -179,6 +179,7 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
                 resident = 0
             records.write("setup", phase="tier", seconds=0.0, resident_per_layer=resident, host=pl.host_experts)
             dec = TieredEngine(w, resident, residency=str(levers.get("BLOOMERY_RESIDENCY")), **kw)
+            server.state.residency = dec.tiered          # POST /residency/reset forgets the heat counts
         else:
             from ..runtime.engine import DecodeEngine
             dec = DecodeEngine(w, **kw)

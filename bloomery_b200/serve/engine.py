@@ -184,6 +184,34 @@ class GpuEngine(Engine):
     def reset(self, slot):
         self.dec.reset(slot)
 
+    def embed(self, ids):
+        """Mean of the final hidden rows of ``ids`` (before the output norm), L2-normalised.  Runs in the last
+        slot, whose sequence is saved and put back, so it may be called between rounds of a busy server."""
+        import torch
+        dec = self.dec
+        if not hasattr(dec, "x") or not len(ids):
+            return None
+        slot = self.n_slots - 1
+        keep = dec.slot_len[slot]
+        snap = dec.kv.snapshot(slot, keep) if keep else None
+        try:
+            dec.reset(slot)
+            acc = torch.zeros(dec.spec.hidden, dtype=torch.float64, device=dec.device)
+            for i in range(0, len(ids), self.max_rows):
+                chunk = list(ids[i:i + self.max_rows])
+                dec.step([(slot, int(t), i + j) for j, t in enumerate(chunk)], head=False)
+                torch.cuda.current_stream(dec.device).synchronize()
+                acc += dec.x[:len(chunk)].double().sum(0)
+            v = (acc / len(ids)).float()
+            v = v / v.norm().clamp(min=1e-12)
+            return v.cpu().numpy()
+        finally:
+            dec.reset(slot)
+            if snap is not None:
+                dec.kv.restore(slot, snap, keep)
+                dec.kv.sync_table()
+                dec.slot_len[slot] = keep
+
     def draft(self, slot: int, n_ids: int) -> List[int]:
         """The draft layer's id for the position after ``n_ids`` known ids of ``slot`` ([] when there is none)."""
         d = getattr(self.dec, "mtp_draft", {}).get(slot)
@@ -298,6 +326,17 @@ class CpuEngine(Engine):
         m.v = [v[:n].clone() for v in saved.payload["v"]]
         m.n_past = n
         return n
+
+    def embed(self, ids):
+        import copy
+        import torch
+        if not len(ids):
+            return None
+        m = copy.copy(self.models[0])
+        m.reset()
+        m.forward(torch.tensor(list(ids)))
+        v = m.hidden.double().mean(0).float()
+        return (v / v.norm().clamp(min=1e-12)).numpy()
 
     def props(self):
         s = self.spec

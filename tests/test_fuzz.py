@@ -1,0 +1,109 @@
+"""Property tests of the text surfaces that take untrusted input: chat templates, tool-call scanners,
+the streaming scanner, the JSON constraint and the safetensors header reader.  Counterpart of the
+reference's fuzz targets (``fuzz/README.md``: jinja parse / render and the four tool-call scanners):
+whatever the bytes, these either answer or raise their own error type -- never another exception,
+never a hang."""
+import json
+import struct
+
+import pytest
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
+
+from bloomery_b200.serve import chat as C
+
+SET = settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+text = st.text(alphabet=st.characters(blacklist_categories=("Cs",)), max_size=200)
+tagged = st.lists(st.sampled_from(["<tool_call>", "</tool_call>", "<function=", "</function>", "<parameter=", "</parameter>",
+                                   "[TOOL_CALLS]", "{", "}", "[", "]", '"name"', ":", '"arguments"', ",", "<arg_key>",
+                                   "</arg_key>", "<arg_value>", "</arg_value>", "x", " ", "\n", '"', "\\"]),
+                  max_size=40).map("".join)
+
+
+@SET
+@given(st.one_of(text, tagged), st.sampled_from(["hermes", "qwen_xml", "glm_xml", "mistral"]))
+def test_tool_call_scanners_answer_or_pass_text_through(s, fmt):
+    content, calls = C.parse_tool_calls(s, fmt)
+    assert isinstance(content, str) and isinstance(calls, list)
+    for c in calls:
+        assert c["type"] == "function" and isinstance(c["function"]["name"], str)
+        json.loads(c["function"]["arguments"])               # arguments are always a JSON document
+
+
+@SET
+@given(st.one_of(text, tagged), st.integers(min_value=1, max_value=7))
+def test_streaming_scanner_equals_one_shot_on_any_split(s, step):
+    whole_content, whole_calls = C.parse_tool_calls(s, "hermes")
+    stream = C.ToolCallStream("hermes")
+    content, calls = "", []
+    for i in range(0, len(s), step):
+        c, k = stream.push(s[i:i + step])
+        content += c
+        calls += k
+    content += stream.flush()
+    assert [c["function"] for c in calls] == [c["function"] for c in whole_calls]
+    if not whole_calls:
+        assert content == s or content.strip() == whole_content.strip()
+
+
+@SET
+@given(text)
+def test_templates_render_or_raise_template_error(src):
+    try:
+        t = C.ChatTemplate(src)
+        out = t.render_text([{"role": "user", "content": "hi"}])
+        assert isinstance(out, str)
+    except C.TemplateError:
+        pass
+
+
+@SET
+@given(st.lists(st.fixed_dictionaries({"role": st.sampled_from(["system", "user", "assistant", "tool"]), "content": text}),
+                min_size=1, max_size=5))
+def test_default_template_keeps_untrusted_text_out_of_the_control_channel(msgs):
+    t = C.ChatTemplate()
+    out = t.render_text(msgs)
+    assert isinstance(out, str)
+    assert C.G0 not in out and C.G1 not in out          # guard marks never survive into the rendered text
+
+
+@SET
+@given(text, text)
+def test_json_constraint_never_raises(prefix, piece):
+    jc = C.JsonConstraint({"type": "object"})
+    assert jc.allowed(prefix, piece) in (True, False)
+    assert jc.closed(prefix) in (True, False) and jc.done(prefix) in (True, False)
+
+
+@SET
+@given(st.binary(max_size=200))
+def test_safetensors_reader_refuses_garbage_with_its_own_error(tmp_path_factory, blob):
+    from bloomery_b200.formats.safetensors import Safetensors, SafetensorsError
+    p = tmp_path_factory.mktemp("st") / "x.safetensors"
+    p.write_bytes(blob)
+    try:
+        Safetensors(str(p)).close()
+    except SafetensorsError:
+        pass
+
+
+def test_safetensors_header_tricks_are_refused(tmp_path):
+    from bloomery_b200.formats.safetensors import Safetensors, SafetensorsError
+    def file_with(header: dict, data: bytes = b"\0" * 64):
+        hj = json.dumps(header).encode()
+        p = tmp_path / "h.safetensors"
+        p.write_bytes(struct.pack("<Q", len(hj)) + hj + data)
+        return str(p)
+    bad = [
+        {"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 8]}},                 # shape does not match bytes
+        {"a": {"dtype": "F32", "shape": [4], "data_offsets": [60, 76]}},               # past the end of the file
+        {"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}, "b": {"dtype": "F32", "shape": [4], "data_offsets": [8, 24]}},
+        {"a": {"dtype": "Q9", "shape": [4], "data_offsets": [0, 16]}},
+        {"a": {"dtype": "F32", "shape": [4]}},
+        {"a": {"dtype": "F32", "shape": [4], "data_offsets": [16, 0]}},
+    ]
+    for h in bad:
+        with pytest.raises(SafetensorsError):
+            Safetensors(file_with(h))
+    ok = Safetensors(file_with({"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}, "__metadata__": {"k": "v"}}))
+    assert ok.tensor("a").shape == (4,) and ok.metadata == {"k": "v"}

@@ -255,6 +255,10 @@ def test_cpu_engine_serves_a_gguf_file(tmp_path):
         assert code == 200 and r2["tokens"] == want[2:6] and r2["tokens_cached"] >= len(prompt)
         code, props = call(S, "/props")
         assert code == 200
+        code, emb = call(S, "/v1/embeddings", {"input": ["abc", "abd"]})
+        assert code == 200 and len(emb["data"]) == 2 and len(emb["data"][0]["embedding"]) == spec.hidden
+        v0, v1 = (torch.tensor(d["embedding"]) for d in emb["data"])
+        assert abs(float(v0.norm()) - 1.0) < 1e-4 and 0.2 < float(v0 @ v1) < 0.99999
     finally:
         proc.terminate()
         proc.wait(timeout=20)
