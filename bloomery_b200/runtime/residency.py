@@ -151,7 +151,10 @@ class HostTier:
 class TieredExperts:
     """Expert stacks of every MoE layer split between pinned host RAM and HBM slots."""
 
-    def __init__(self, spec, weights, n_slots: int, device, rule: Optional[str] = "mid", delay: int = 2):
+    def __init__(self, spec, weights, n_slots: int, device, rule: Optional[str] = "mid", delay: int = 2,
+                 keep_host: bool = True):
+        """``keep_host=False``: the cold experts are not kept in RAM (a drive-backed arena serves them); promotion
+        has no source then, so the residency rule is off."""
         self.spec = spec
         self.device = torch.device(device)
         E = spec.n_expert
@@ -172,8 +175,9 @@ class TieredExperts:
             hq, cq = {}, {}
             for part in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"):
                 full = weights.q.pop(b + part + ".weight")
-                pinned = full.data.cpu().pin_memory() if self.device.type == "cuda" else full.data.cpu()
-                hq[part] = QWeight(pinned, full.qtype, full.k)
+                if keep_host:
+                    pinned = full.data.cpu().pin_memory() if self.device.type == "cuda" else full.data.cpu()
+                    hq[part] = QWeight(pinned, full.qtype, full.k)
                 slots = torch.zeros(self.n_slots + 1, *full.data.shape[1:], dtype=torch.uint8, device=self.device)
                 if self.n_slots:
                     slots[:self.n_slots].copy_(full.data[:self.n_slots])
@@ -186,7 +190,7 @@ class TieredExperts:
             self.slot_map[il] = sm.to(self.device)
             self.slot_of[il] = {e: e for e in range(self.n_slots)}
             self.spare[il] = self.n_slots
-        preset = PRESETS.get(rule or "off")
+        preset = PRESETS.get(rule or "off") if keep_host else None
         self.rule = ResidencyRule(spec.n_layer, E, [list(range(self.n_slots)) if il in self.host else [] for il in range(spec.n_layer)],
                                   **preset) if preset and self.n_slots else None
         self._heat_seen: Dict[int, torch.Tensor] = {}
@@ -200,6 +204,8 @@ class TieredExperts:
     def attach_host_tier(self, tier: HostTier) -> None:
         for il in self.layers:
             h = self.host[il]
+            if not h:
+                continue
             tier.set_layer(il, h["ffn_gate_exps"].data, h["ffn_up_exps"].data, h["ffn_down_exps"].data,
                            h["ffn_gate_exps"].qtype, h["ffn_down_exps"].qtype, self.spec.n_expert)
 

@@ -21,12 +21,18 @@ from .residency import HostTier, TieredExperts
 
 
 class TieredEngine(DecodeEngine):
-    def __init__(self, weights, resident_per_layer: int, residency: Optional[str] = "mid", **kw):
+    def __init__(self, weights, resident_per_layer: int, residency: Optional[str] = "mid", nvme=None, **kw):
+        """``nvme``: a :class:`bloomery_b200.runtime.nvtier.NvmeTier` over a side file of this model's experts; the
+        host leg then reads cold experts from its arena (paged from the drive) instead of RAM-resident stacks."""
         spec = weights.spec
-        self.tiered = TieredExperts(spec, weights, resident_per_layer, weights.device, rule=residency)
+        self.nvme = nvme
+        self.tiered = TieredExperts(spec, weights, resident_per_layer, weights.device, rule=residency,
+                                    keep_host=nvme is None)
         super().__init__(weights, **kw)
         self.tier = HostTier(spec.n_layer, spec.hidden, spec.moe_inter, spec.n_used, self.device)
         self.tiered.attach_host_tier(self.tier)
+        if nvme is not None:
+            nvme.attach(self.tier)
         self.tier.start()
 
     def _moe(self, il: int, M: int, x: torch.Tensor) -> int:
@@ -57,6 +63,8 @@ class TieredEngine(DecodeEngine):
         out = self.tier.stats()
         out["flips"] = self.tiered.rule.total_flips if self.tiered.rule else 0
         out["bytes_promoted"] = self.tiered.bytes_promoted
+        if self.nvme is not None:
+            out["nvme"] = self.nvme.stats()
         return out
 
     def close(self) -> None:

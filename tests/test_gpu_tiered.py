@@ -62,3 +62,31 @@ def test_promotion_lands_and_output_stays_in_band():
         assert len(out) == 6 and (int(tier.fault) & 0xFFFFFFFF) == 0xFFFFFFFF
     finally:
         tier.close()
+
+
+def test_cold_experts_paged_from_a_side_file(tmp_path):
+    """The drive-backed arena behind the in-graph hand-off: cold experts are read from the side file into RAM
+    slots on demand; tokens and logits stay those of the RAM-resident host tier."""
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.nvtier import NvmeTier, write_sidecar
+    from bloomery_b200.runtime.tiered import TieredEngine
+    spec = tiny_qwen3moe()
+    items = list(synth_tensors(spec, "cpu", seed=21))
+    path = str(tmp_path / "experts.side")
+    write_sidecar(Weights.from_items(spec, iter(items), "cpu"), path)
+    nv = NvmeTier(path, n_slots=10)
+    ram = TieredEngine(Weights.from_items(spec, iter(items), DEV), 4, residency="off", n_slots=1, slot_ctx=256)
+    drv = TieredEngine(Weights.from_items(spec, iter(items), DEV), 4, residency="off", nvme=nv, n_slots=1, slot_ctx=256)
+    try:
+        g = torch.Generator().manual_seed(6)
+        prompt = torch.randint(0, spec.vocab, (24,), generator=g).tolist()
+        a, b = ram.score(0, prompt), drv.score(0, prompt)
+        assert a == b and torch.equal(ram.logits[:8], drv.logits[:8])
+        st = drv.stats()["nvme"]
+        assert st["misses"] > 0 and st["hits"] > 0 and st["failed"] == 0 and st["evictions"] >= 0
+        assert drv.memory_report()["experts_host"] == 0
+    finally:
+        ram.close()
+        drv.close()
+        nv.close()

@@ -151,3 +151,49 @@ def test_placement_planner_rules():
     assert tp.kv_bytes == big.kv_bytes // 2
     r0 = dict(P.rank_inventory(inv, 2, 0))
     assert r0["blk.0.attn_q.weight"] == 4 << 20 and r0["token_embd.weight"] == 100 << 20
+
+
+def test_nvme_expert_arena_matches_ram_stacks_and_evicts_lru(tmp_path):
+    """Experts paged from a side file: the leg over the arena equals the leg over RAM-resident stacks bit for bit;
+    the arena holds n_slots experts per layer, evicts the least recently used, never a pinned one."""
+    import torch
+    from bloomery_b200.formats import quant as Q
+    from bloomery_b200.formats.resident import WT
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.ops._lib import host, p as vp
+    from bloomery_b200.runtime.nvtier import NvmeTier, write_sidecar
+    spec = tiny_qwen3moe()
+    spec.vocab, spec.n_layer = 256, 2
+    w = Weights.from_items(spec, synth_tensors(spec, "cpu", seed=4), "cpu")
+    path = str(tmp_path / "experts.side")
+    ix = write_sidecar(w, path)
+    assert set(ix["layers"]) == {"0", "1"} and all(v["blob"] % 4096 == 0 for v in ix["layers"].values())
+    nv = NvmeTier(path, n_slots=6)
+    torch.manual_seed(1)
+    M, k, H, E = 2, spec.n_used, spec.hidden, spec.n_expert
+
+    def leg(layer, ids):
+        x = torch.randn(M, H)
+        xq, xds = Q.quantize_act_q8(x)
+        wts = torch.rand(M, k)
+        got = nv.moe(layer, ids, wts, xq, xds)
+        g, u, d = (w.q[f"blk.{layer}.ffn_{n}_exps.weight"] for n in ("gate", "up", "down"))
+        ref = torch.zeros(M, H)
+        rc = host().blh_moe_experts(M, H, spec.moe_inter, E, k, vp(ids), vp(wts), vp(xq), vp(xds), vp(g.data), vp(u.data),
+                                    vp(d.data), WT[g.qtype], WT[d.qtype], vp(ref))
+        assert rc == 0 and torch.equal(got, ref)
+    a = torch.tensor([[0, 1, 2, 3], [1, 2, 4, -1]], dtype=torch.int32)
+    leg(0, a)
+    assert nv.resident(0) == [0, 1, 2, 3, 4] and nv.stats()["misses"] == 5
+    nv.pin(0, 0)
+    leg(0, torch.tensor([[5, 6, 7, 8], [5, 6, 7, 8]], dtype=torch.int32))      # 4 new experts into 6 slots: 3 of the old ones go
+    res = nv.resident(0)
+    assert 0 in res and {5, 6, 7, 8} <= set(res) and len(res) == 6 and nv.stats()["evictions"] == 3
+    leg(1, a)                                                                   # layers keep separate arenas
+    assert nv.resident(1) == [0, 1, 2, 3, 4]
+    st = nv.stats()
+    assert st["failed"] == 0 and st["bytes_read"] >= st["misses"] * min(v["blob"] for v in ix["layers"].values()) and st["hits"] >= 1
+    with pytest.raises(OSError):                                                # more distinct experts than slots in one call
+        nv.moe(0, torch.arange(8, dtype=torch.int32).reshape(2, 4) + 8, torch.rand(2, 4), *Q.quantize_act_q8(torch.randn(2, H)))
+    nv.close()
