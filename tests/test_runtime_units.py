@@ -197,3 +197,50 @@ def test_nvme_expert_arena_matches_ram_stacks_and_evicts_lru(tmp_path):
     with pytest.raises(OSError):                                                # more distinct experts than slots in one call
         nv.moe(0, torch.arange(8, dtype=torch.int32).reshape(2, 4) + 8, torch.rand(2, 4), *Q.quantize_act_q8(torch.randn(2, H)))
     nv.close()
+
+
+def test_expert_tier_node_over_tcp():
+    """A tier node on loopback: census with sha256-checked rows, the expert leg over the wire equals the local leg
+    bit for bit, a wrong model is refused at open, a lost node and a bad frame surface as TierLost."""
+    import socket
+    import torch
+    from bloomery_b200.formats import quant as Q
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.parallel import tier_node as TN
+    spec = tiny_qwen3moe()
+    spec.vocab, spec.n_layer = 256, 2
+    w = Weights.from_items(spec, synth_tensors(spec, "cpu", seed=4), "cpu")
+    other = Weights.from_items(spec, synth_tensors(spec, "cpu", seed=5), "cpu")
+    srv = TN.TierServer(w, layers=[1]).start()
+    try:
+        cl = TN.RemoteExpertTier(srv.addr, io_timeout=10)
+        census = cl.open(w)
+        assert list(census["layers"]) == ["1"] and census["n_expert"] == 16
+        torch.manual_seed(0)
+        ids = torch.tensor([[0, 5, 9, -1], [3, 5, 1, 2], [15, 14, 13, 12]], dtype=torch.int32)
+        wts = torch.rand(3, 4)
+        xq, xds = Q.quantize_act_q8(torch.randn(3, spec.hidden))
+        got = cl.moe(1, ids, wts, xq, xds)
+        assert torch.equal(got, TN.local_leg(w, 1, ids, wts, xq, xds)) and srv.served == 1
+        with pytest.raises(TN.TierLost):                     # a layer the node does not hold
+            cl.moe(0, ids, wts, xq, xds)
+        assert torch.equal(cl.moe(1, ids, wts, xq, xds), got)     # the channel survives an error answer
+        bad = TN.RemoteExpertTier(srv.addr, io_timeout=10)
+        with pytest.raises(TN.TierLost):                     # same shapes, other rows: the sha256 check refuses
+            bad.open(other)
+        bad.close()
+        with pytest.raises(ValueError):
+            TN.unpack_moe(TN.pack_moe(1, ids, wts, xq, xds)[:-3])
+        srv.close()
+        cl.sock.settimeout(1.0)
+        with pytest.raises(TN.TierLost):
+            for _ in range(50):                              # the node is gone: the next exchanges fail within their deadline
+                cl.moe(1, ids, wts, xq, xds)
+        with socket.socket() as so:
+            so.bind(("127.0.0.1", 0))
+            dead = so.getsockname()
+        with pytest.raises(TN.TierLost):
+            TN.RemoteExpertTier(dead, io_timeout=1).open()
+    finally:
+        srv.close()
