@@ -56,7 +56,8 @@ def bucket_of(m: int) -> int:
 class DecodeEngine:
     def __init__(self, weights: Weights, n_slots: int = 1, slot_ctx: int = 4096, n_seg: Optional[int] = None,
                  use_graphs: bool = True, keep_logits: bool = True, engine_bound_s: float = 60.0,
-                 layers: Optional[Tuple[int, int]] = None, stage_first: bool = True, stage_last: bool = True):
+                 layers: Optional[Tuple[int, int]] = None, stage_first: bool = True, stage_last: bool = True,
+                 kv_pages: Optional[int] = None):
         self.w = weights
         self.spec: ModelSpec = weights.spec
         s = self.spec
@@ -76,10 +77,11 @@ class DecodeEngine:
         n_kv_layers = (self.hi - self.lo) + (self.n_mtp if stage_last else 0)
         sm = K.sm_count(dev)
         if s.mla:
-            self.kv = KvPool(n_kv_layers, 1, s.kv_lora + s.rope_dim, n_slots * max_pages, n_slots, max_pages, dev, v_dim=0)
+            self.kv = KvPool(n_kv_layers, 1, s.kv_lora + s.rope_dim, kv_pages or n_slots * max_pages, n_slots, max_pages, dev, v_dim=0)
             self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, 2 * sm // ((s.n_q + 15) // 16))))
         else:
-            self.kv = KvPool(n_kv_layers, s.n_kv, s.head_dim, n_slots * max_pages, n_slots, max_pages, dev)
+            # kv_pages below n_slots * max_pages overcommits the pool: idle slots spill to pinned host memory
+            self.kv = KvPool(n_kv_layers, s.n_kv, s.head_dim, kv_pages or n_slots * max_pages, n_slots, max_pages, dev)
             self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, sm // s.n_kv)))
         H, V = s.hidden, s.vocab
         f32 = dict(dtype=torch.float32, device=dev)
@@ -400,6 +402,7 @@ class DecodeEngine:
             self._stage_ev[i].synchronize()
         ph = self.params_host = self._stage[i]
         ph[2].fill_(-1)
+        self.kv.protect = {r[0] for r in rows}          # slots of this pass never spill
         for r, (slot, tok, pos) in enumerate(rows):
             ph[0, r], ph[1, r], ph[2, r] = tok, pos, slot
             ph[3, r] = src[r] if src is not None else r

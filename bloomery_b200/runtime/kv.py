@@ -38,6 +38,16 @@ class KvPool:
         self.refs: List[int] = [0] * n_pages
         self.pages: List[List[int]] = [[] for _ in range(n_slots)]
         self.dirty = False
+        # host spill: when the pool runs dry, the least recently used slot that the current pass does not touch
+        # is copied to pinned host memory and its pages are reused; it comes back the next time it is needed
+        # (the reference backs such pages with host memory in place: crates/gpu/src/room/mod.rs ``Backing::Spill``)
+        self.spilled: Dict[int, tuple] = {}
+        self.protect: set = set()
+        self.stamp = [0] * n_slots
+        self.clock = 0
+        self.n_spills = 0
+        self.n_unspills = 0
+        self.allow_spill = True
 
     @property
     def bytes(self) -> int:
@@ -46,8 +56,26 @@ class KvPool:
     def free_pages(self) -> int:
         return len(self.free)
 
+    def touch(self, slot: int) -> None:
+        self.clock += 1
+        self.stamp[slot] = self.clock
+
+    def _spill_one(self) -> bool:
+        victims = [s for s in range(self.n_slots) if self.pages[s] and s not in self.protect
+                   and all(self.refs[p] == 1 for p in self.pages[s])]
+        if not victims or not self.allow_spill:
+            return False
+        s = min(victims, key=lambda v: self.stamp[v])
+        n = len(self.pages[s]) * PAGE
+        # stream order keeps this safe: the copy out is enqueued before anything that rewrites the pages
+        snap = self.snapshot(s, n)
+        self.release(s)
+        self.spilled[s] = (snap, n)
+        self.n_spills += 1
+        return True
+
     def _take(self) -> int:
-        if not self.free:
+        if not self.free and not self._spill_one():
             raise OutOfPages("KV pool exhausted")
         pg = self.free.pop()
         self.refs[pg] = 1
@@ -63,6 +91,12 @@ class KvPool:
         need = (n_positions + PAGE - 1) // PAGE
         if need > self.max_pages:
             raise OutOfPages(f"slot {slot}: {n_positions} positions exceed the slot context")
+        if slot in self.spilled:
+            snap, n = self.spilled.pop(slot)
+            self.protect.add(slot)
+            self.restore(slot, snap, n)
+            self.n_unspills += 1
+        self.touch(slot)
         pl = self.pages[slot]
         while len(pl) < need:
             pg = self._take()
@@ -86,6 +120,13 @@ class KvPool:
     def truncate(self, slot: int, n_positions: int) -> None:
         """Keep positions [0, n_positions); later pages go back to the pool (``cut``)."""
         keep = (n_positions + PAGE - 1) // PAGE
+        if slot in self.spilled:
+            snap, n = self.spilled[slot]
+            if keep == 0:
+                del self.spilled[slot]
+            else:
+                self.spilled[slot] = (snap, min(n, keep * PAGE))
+            return
         pl = self.pages[slot]
         while len(pl) > keep:
             self._drop(pl.pop())
@@ -98,6 +139,9 @@ class KvPool:
     def share_prefix(self, src: int, dst: int, n_positions: int) -> int:
         """Map the whole pages of ``src`` covering [0, n_positions) into ``dst``; returns positions shared."""
         self.release(dst)
+        if src in self.spilled:
+            self.protect.add(dst)
+            self.ensure(src, 1)              # bring the source back before its pages are mapped twice
         full = min(n_positions // PAGE, len(self.pages[src]))
         for i in range(full):
             pg = self.pages[src][i]
@@ -125,13 +169,14 @@ class KvPool:
         idx = torch.tensor(self.pages[slot][:n_pg], dtype=torch.long, device=self.device)
         pin = self.device.type == "cuda"
         k = torch.empty((self.n_layer, n_pg, self.n_kv, PAGE, self.head_dim), dtype=self.k.dtype, pin_memory=pin)
-        v = torch.empty_like(k, pin_memory=pin)
+        v = torch.empty((self.n_layer, n_pg, self.n_kv, PAGE, self.v.shape[-1]), dtype=self.v.dtype, pin_memory=pin)
         k.copy_(self.k.index_select(1, idx), non_blocking=True)
         v.copy_(self.v.index_select(1, idx), non_blocking=True)
         return {"k": k, "v": v, "n": torch.tensor(n_positions)}
 
     def restore(self, slot: int, snap: Dict[str, torch.Tensor], n_positions: int) -> None:
         n_positions = min(n_positions, int(snap["n"]))
+        self.spilled.pop(slot, None)
         self.release(slot)
         self.ensure(slot, n_positions)
         n_pg = (n_positions + PAGE - 1) // PAGE

@@ -448,3 +448,29 @@ def test_two_pipeline_stages_equal_one_stage_bit_for_bit():
     pipe.cut(0, 10)
     one.cut(0, 10)
     assert one.step([(0, 7, 10)]) == pipe.step([(0, 7, 10)])
+
+
+def test_overcommitted_kv_pool_spills_idle_slots_and_tokens_do_not_change():
+    """Three slots of 256 positions over a pool of 6 pages (384 positions): the idle slot's pages go to pinned host
+    memory when another slot needs them and come back when it runs again; every token equals the roomy engine's."""
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.engine import DecodeEngine
+    spec = tiny_qwen3moe()
+    items = list(synth_tensors(spec, "cpu", seed=7))
+    roomy = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=3, slot_ctx=256, use_graphs=True)
+    tight = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=3, slot_ctx=256, use_graphs=True, kv_pages=6)
+    g = torch.Generator().manual_seed(23)
+    prompts = [torch.randint(0, spec.vocab, (n,), generator=g).tolist() for n in (150, 130, 100)]
+    outs = {0: [], 1: []}
+    for which, eng in enumerate((roomy, tight)):
+        toks = [eng.prefill(sl, p, gemm=False) for sl, p in enumerate(prompts)]
+        lens = [len(p) for p in prompts]
+        for step in range(6):
+            sl = step % 3                                    # one slot at a time: the others are idle and may spill
+            toks[sl] = eng.step([(sl, toks[sl], lens[sl])])[0]
+            lens[sl] += 1
+            outs[which].append(toks[sl])
+        outs[which] = toks + outs[which]
+    assert outs[0] == outs[1]
+    assert tight.kv.n_spills >= 2 and tight.kv.n_unspills >= 2 and roomy.kv.n_spills == 0

@@ -244,3 +244,33 @@ def test_expert_tier_node_over_tcp():
             TN.RemoteExpertTier(dead, io_timeout=1).open()
     finally:
         srv.close()
+
+
+def test_kv_pool_spills_idle_slots_to_the_host_and_brings_them_back():
+    import torch
+    from bloomery_b200.runtime.kv import PAGE, KvPool, OutOfPages
+    kv = KvPool(n_layer=2, n_kv=1, head_dim=8, n_pages=4, n_slots=3, max_pages_per_slot=3, device="cpu")
+    def fill(slot, n, val):
+        kv.protect = {slot}
+        kv.ensure(slot, n)
+        for pg in kv.pages[slot]:
+            kv.k[:, pg] = val
+            kv.v[:, pg] = -val
+    fill(0, 2 * PAGE, 1.0)
+    fill(1, 2 * PAGE, 2.0)
+    assert kv.free_pages() == 0
+    fill(2, PAGE + 5, 3.0)                       # needs 2 pages: slot 0 (least recently used) goes to the host
+    assert 0 in kv.spilled and kv.n_spills == 1 and not kv.pages[0] and len(kv.pages[2]) == 2
+    kv.truncate(0, PAGE)                         # a cut reaches a spilled slot too
+    kv.protect = {0}
+    kv.ensure(0, PAGE)                           # comes back (slot 1 is now the oldest and leaves)
+    assert 0 not in kv.spilled and 1 in kv.spilled and kv.n_unspills == 1 and len(kv.pages[0]) == 1
+    assert float(kv.k[0, kv.pages[0][0]].mean()) == 1.0 and float(kv.v[1, kv.pages[0][0]].mean()) == -1.0
+    kv.protect = {1}
+    kv.ensure(1, 2 * PAGE)
+    assert all(float(kv.k[1, pg].mean()) == 2.0 for pg in kv.pages[1])
+    kv.protect = {0, 1, 2}
+    with pytest.raises(OutOfPages):              # every slot with pages is in the pass: nothing may leave
+        kv.ensure(0, 3 * PAGE)
+    kv.release(2)
+    kv.ensure(0, 2 * PAGE)
