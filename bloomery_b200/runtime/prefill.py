@@ -37,6 +37,8 @@ class GemmPrefill:
         self._router_w = {}
         self.status = torch.zeros(1, dtype=torch.int32, device=engine.device)
         self.launches = 0
+        # where a layer's expert stacks come from: the resident weights, or a streamer that brings them from the host
+        self.expert_source = None
 
     def _get(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
@@ -159,10 +161,14 @@ class GemmPrefill:
                 moe_tiles.build(counts)
                 G.moe_scatter(ids, wts, E, moe_tiles.offsets, cursor, pos_of, dst_row, row_scale)
                 G.gather_rows_bf16(xn, dst_row, moe_tiles.offsets[E:E + 1], cap, k, Ap)
-                G.dequant_bf16(w.q[b + "ffn_gate_exps.weight"], wg)
-                G.dequant_bf16(w.q[b + "ffn_up_exps.weight"], wu)
+                if self.expert_source is not None:
+                    qg, qu, qd = self.expert_source(il)
+                else:
+                    qg, qu, qd = (w.q[b + f"ffn_{n}_exps.weight"] for n in ("gate", "up", "down"))
+                G.dequant_bf16(qg, wg)
+                G.dequant_bf16(qu, wu)
                 G.gemm_bf16(Ap, wg, moe_tiles, out_bf16=act, B2=wu, status=st)
-                G.dequant_bf16(w.q[b + "ffn_down_exps.weight"], wd)
+                G.dequant_bf16(qd, wd)
                 G.gemm_bf16(act, wd, moe_tiles, out_f32=slot_out, dst_row=dst_row, row_scale=row_scale, status=st)
                 G.moe_combine(slot_out, pos_of, T, k, x, x)
             else:

@@ -17,6 +17,7 @@ import torch
 
 from ..ops import decode as K
 from .engine import DecodeEngine
+from ..ops.decode import QWeight
 from .residency import HostTier, TieredExperts
 
 
@@ -33,6 +34,7 @@ class TieredEngine(DecodeEngine):
         self.tiered.attach_host_tier(self.tier)
         if nvme is not None:
             nvme.attach(self.tier)
+            self.gemm_threshold = 0          # no RAM-resident stacks to stream from: prompts take the pass path
         self.tier.start()
 
     def _moe(self, il: int, M: int, x: torch.Tensor) -> int:
@@ -50,6 +52,16 @@ class TieredEngine(DecodeEngine):
         K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, sm, card["ffn_down_exps"], s.n_expert, s.n_used,
                        M, x, self.tier.extra, x, self.fault, il)
         return 6
+
+    def _new_gemm_prefill(self):
+        """Prompts take the GEMM path with the layer's whole expert stacks streamed from pinned host memory into a
+        two-half card ring on the copy stream, one layer ahead of the compute (the reference's prompt-time expert
+        stream: ``crates/gpu/src/host/xstream.rs``; there only the hottest host experts move, here the whole layer,
+        which the GEMM then reads as one stack)."""
+        from .prefill import GemmPrefill
+        pre = GemmPrefill(self, ubatch=self.ubatch)
+        pre.expert_source = ExpertStreamer(self.tiered, self.device).get
+        return pre
 
     def _after_pass(self, n_rows: int) -> None:
         self.tiered.boundary(self.heat, n_rows)
@@ -70,3 +82,48 @@ class TieredEngine(DecodeEngine):
     def close(self) -> None:
         self.tier.stop()
         self.tier.close()
+
+
+class ExpertStreamer:
+    """Double-buffered host -> card copies of whole expert stacks, layer by layer."""
+
+    PARTS = ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps")
+
+    def __init__(self, tiered: TieredExperts, device):
+        self.t = tiered
+        self.device = device
+        self.copy = torch.cuda.Stream(device=device)
+        size = {p: max(tiered.host[il][p].data.numel() for il in tiered.layers) for p in self.PARTS}
+        self.halves = [{p: torch.empty(size[p], dtype=torch.uint8, device=device) for p in self.PARTS} for _ in range(2)]
+        self.ready = {}            # layer -> (half index, event)
+        self.bytes = 0
+
+    def _issue(self, il: int, half: int) -> None:
+        cur = torch.cuda.current_stream(self.device)
+        gate = torch.cuda.Event()
+        gate.record(cur)                            # everything that read this half before is enqueued before here
+        self.copy.wait_event(gate)
+        with torch.cuda.stream(self.copy):
+            for p_ in self.PARTS:
+                src = self.t.host[il][p_].data
+                self.halves[half][p_][:src.numel()].copy_(src.reshape(-1), non_blocking=True)
+                self.bytes += src.numel()
+            ev = torch.cuda.Event()
+            ev.record(self.copy)
+        self.ready[il] = (half, ev)
+
+    def get(self, il: int):
+        layers = self.t.layers
+        k = layers.index(il)
+        if il not in self.ready:
+            self._issue(il, k % 2)
+        half, ev = self.ready.pop(il)
+        torch.cuda.current_stream(self.device).wait_event(ev)
+        nxt = layers[(k + 1) % len(layers)]          # the next layer (or the first one of the next micro-batch)
+        if nxt not in self.ready and len(layers) > 1:
+            self._issue(nxt, (half + 1) % 2)
+        out = []
+        for p_ in self.PARTS:
+            h = self.t.host[il][p_]
+            out.append(QWeight(self.halves[half][p_][:h.data.numel()].view(h.data.shape), h.qtype, h.k))
+        return out

@@ -90,3 +90,23 @@ def test_cold_experts_paged_from_a_side_file(tmp_path):
         ram.close()
         drv.close()
         nv.close()
+
+
+def test_prompt_streams_host_experts_through_the_gemm_path():
+    """A long prompt on the tiered engine: whole expert stacks stream from pinned host memory into a two-half card
+    ring one layer ahead of the GEMMs; the result is the all-on-card GEMM prompt path's, bit for bit."""
+    spec, full, tier = _pair(4, residency="off")
+    try:
+        g = torch.Generator().manual_seed(8)
+        prompt = torch.randint(0, spec.vocab, (200,), generator=g).tolist()
+        a = full.prefill(0, prompt, gemm=True)
+        b = tier.prefill(0, prompt, gemm=True)
+        assert a == b and torch.equal(full.logits[0], tier.logits[0])
+        assert tier._gemm_prefill.expert_source.__self__.bytes > 0
+        # decode continues on the split engine from the KV the prompt path wrote
+        ta = full.step([(0, a, len(prompt))])[0]
+        tb = tier.step([(0, b, len(prompt))])[0]
+        err = ((full.logits[0] - tier.logits[0]).abs().max() / full.logits[0].abs().max()).item()
+        assert err < 2e-2 and ta == tb
+    finally:
+        tier.close()
