@@ -11,6 +11,7 @@
 
 #include "../quant_units.cuh"
 #include "pool.h"
+#include "qdot_avx2.h"
 
 using namespace bl;
 
@@ -69,6 +70,11 @@ void row_decode(const uint8_t* row, int K, float* out) {
 }  // namespace
 
 extern "C" {
+
+// the vector path's dot of one row (tests compare it with the scalar mirror); returns 0 when there is none
+int blh_row_dot_fast(int wtype, const uint8_t* row, int K, const int8_t* xq, const float* xds, float* out) {
+  return blh::row_dot_fast(wtype, row, K, xq, xds, out) ? 1 : 0;
+}
 
 long blh_resident_row_bytes(int wtype, int K) { return resident_row_bytes(wtype, K); }
 

@@ -114,6 +114,8 @@ class PipelineEngine:
             last = i == len(self.stages) - 1
             with torch.cuda.device(st.device):
                 M = st.set_rows(rows)
+                if st.use_graphs:
+                    st._graph(M, head and last, False)      # capture (and its warm-up pass, which rewrites x) comes first
                 if prev is not None:
                     cur = torch.cuda.current_stream(st.device)
                     cur.wait_event(self._ev[i - 1])

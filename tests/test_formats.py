@@ -341,3 +341,30 @@ def test_deepseek_shape_roundtrips_and_oracle_runs(tmp_path):
     inc = torch.cat([m.forward(toks[:4]), m.forward(toks[4:])])
     # batched and single-row products round differently, which can flip a q8 activation code
     assert ((full - inc).abs().max() / full.abs().max()).item() < 2e-2
+
+
+@pytest.mark.parametrize("t", ["Q4_K", "Q6_K", "Q8_0"])
+def test_vector_row_dots_agree_with_the_scalar_units(t):
+    """The AVX2 paths of the host expert leg against the scalar mirror of the device units and an f64 dot."""
+    import ctypes
+    from bloomery_b200.formats.resident import WT
+    from bloomery_b200.ops._lib import host, p as vp
+    torch.manual_seed(11)
+    K = 2048
+    w = torch.randn(40, K) * 0.02
+    w[3, 7] = 0.9
+    raw = Q.quantize(w, t)
+    res = to_resident(raw, t, K)
+    wd = Q.dequantize(raw, t, K)
+    x = torch.randn(1, K)
+    x[0, 100] = -25.0
+    codes, ds = H.act_q8(x)
+    ref = (Q.dequantize_act_q8(codes, ds).double() @ wd.double().T)[0]
+    scalar = H.gemv(res, t, K, codes, ds)[0]
+    served = 0
+    for r in range(40):
+        o = ctypes.c_float()
+        served += host().blh_row_dot_fast(WT[t], vp(res[r]), K, vp(codes), vp(ds), ctypes.byref(o))
+        assert abs(o.value - float(ref[r])) <= 1e-5 * float(ref.abs().max())
+        assert abs(o.value - float(scalar[r])) <= 2e-6 * float(ref.abs().max())
+    assert served in (0, 40)            # 0 on a host without AVX2: the scalar units serve every type
