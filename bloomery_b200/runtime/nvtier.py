@@ -109,7 +109,7 @@ class NvmeTier:
 
     def attach(self, host_tier) -> None:
         """Let the host tier's service thread answer the card from this arena."""
-        self.lib.blh_host_tier_set_nv(ctypes.c_void_p(host_tier.handle), ctypes.c_void_p(self.h))
+        self.lib.blh_host_tier_set_nv(host_tier.handle, ctypes.c_void_p(self.h))
 
     def close(self) -> None:
         if self.h:
