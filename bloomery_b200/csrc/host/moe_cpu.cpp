@@ -187,8 +187,9 @@ struct NvTier {
     return ok;
   }
 
-  // make every expert of ids[] (>= 0) of `layer` present; false if a read failed or the arena is too small
-  bool ensure(int layer, const int* ids, int n) {
+  // make every expert of ids[] (>= 0) of `layer` present: 0 done, 1 the call needs more experts than there are
+  // free slots (the caller may split it), 2 a read failed
+  int ensure(int layer, const int* ids, int n) {
     NvLayer& L = layers[layer];
     ++tick;
     std::vector<int> need;
@@ -199,7 +200,12 @@ struct NvTier {
       if (s >= 0) { if (L.last_use[s] != tick) { L.last_use[s] = tick; ++hits; } continue; }
       if (std::find(need.begin(), need.end(), e) == need.end()) need.push_back(e);
     }
-    if (need.empty()) return true;
+    if (need.empty()) return 0;
+    {
+      int room = 0;
+      for (int s = 0; s < n_slots; ++s) room += (!L.pinned[s] && L.last_use[s] != tick) ? 1 : 0;
+      if ((int)need.size() > room) return 1;        // nothing was evicted yet
+    }
     std::vector<std::pair<long, uint8_t*>> reqs;
     std::vector<std::pair<int, int>> placed;           // (expert, slot)
     for (int e : need) {
@@ -210,7 +216,7 @@ struct NvTier {
         if (L.expert_in[s] < 0) { victim = s; break; }
         if (L.last_use[s] < oldest) { oldest = L.last_use[s]; victim = s; }
       }
-      if (victim < 0) { ++failed; return false; }
+      if (victim < 0) { ++failed; return 2; }
       if (L.expert_in[victim] >= 0) { L.slot_of[L.expert_in[victim]] = -1; ++evictions; }
       L.expert_in[victim] = e;
       L.last_use[victim] = tick;
@@ -221,9 +227,24 @@ struct NvTier {
     if (!read_all(reqs, L.blob)) {
       for (auto& p : placed) { L.expert_in[p.second] = -1; L.last_use[p.second] = 0; }
       ++failed;
-      return false;
+      return 2;
     }
     for (auto& p : placed) L.slot_of[p.first] = p.second;
+    return 0;
+  }
+
+  // the expert leg of M rows from the arena; rows are served one at a time when together they need more experts
+  // than the arena has slots.  false: a read failed or one row alone does not fit.
+  bool serve(int layer, int M, int n_used, const int* ids, const float* wts, const int8_t* xq, const float* xds, float* out,
+             float* act, int8_t* actq, float* actds) {
+    const int rc = ensure(layer, ids, M * n_used);
+    if (rc == 0) { moe_rows(stacks(layer), M, n_used, ids, wts, xq, xds, out, act, actq, actds); return true; }
+    if (rc == 2 || M == 1) { ++failed; return false; }
+    for (int m = 0; m < M; ++m) {
+      if (ensure(layer, ids + (long)m * n_used, n_used) != 0) { ++failed; return false; }
+      moe_rows(stacks(layer), 1, n_used, ids + (long)m * n_used, wts + (long)m * n_used, xq + (long)m * K,
+               xds + (long)m * (K / 32) * 2, out + (long)m * K, act, actq, actds);
+    }
     return true;
   }
 
@@ -277,10 +298,8 @@ struct Tier {
       float* out = (float*)(page + off_out());
       if (n_cold > 0 && nv && layer >= 0 && layer < nv->n_layers && M >= 1 && M <= max_rows) {
         const int* ids = (const int*)(page + off_ids());
-        if (nv->ensure(layer, ids, M * n_used)) {
-          moe_rows(nv->stacks(layer), M, n_used, ids, (const float*)(page + off_wts()), (const int8_t*)(page + off_xq()),
-                   (const float*)(page + off_xds()), out, act.data(), actq.data(), actds.data());
-        } else {
+        if (!nv->serve(layer, M, n_used, ids, (const float*)(page + off_wts()), (const int8_t*)(page + off_xq()),
+                       (const float*)(page + off_xds()), out, act.data(), actq.data(), actds.data())) {
           for (long i = 0; i < (long)max_rows * K; ++i) out[i] = std::nanf("");       // a failed read must not pass as zeros
         }
         cold_slots += n_cold;
@@ -408,7 +427,7 @@ void blh_nv_close(void* h) {
 int blh_nv_pin(void* h, int layer, int expert, int on) {
   NvTier* t = (NvTier*)h;
   if (layer < 0 || layer >= t->n_layers || expert < 0 || expert >= t->E) return -1;
-  if (on && !t->ensure(layer, &expert, 1)) return -2;
+  if (on && t->ensure(layer, &expert, 1) != 0) return -2;
   const int s = t->layers[layer].slot_of[expert];
   if (s >= 0) t->layers[layer].pinned[s] = on ? 1 : 0;
   return 0;
@@ -419,12 +438,10 @@ int blh_nv_moe_experts(void* h, int layer, int M, int n_used, const int* ids, co
                        const float* xds, float* out) {
   NvTier* t = (NvTier*)h;
   if (layer < 0 || layer >= t->n_layers) return -1;
-  if (!t->ensure(layer, ids, M * n_used)) return -2;
   std::vector<float> act((size_t)M * n_used * t->I);
   std::vector<int8_t> actq((size_t)M * n_used * t->I);
   std::vector<float> actds((size_t)M * n_used * (t->I / 32) * 2);
-  moe_rows(t->stacks(layer), M, n_used, ids, wts, xq, xds, out, act.data(), actq.data(), actds.data());
-  return 0;
+  return t->serve(layer, M, n_used, ids, wts, xq, xds, out, act.data(), actq.data(), actds.data()) ? 0 : -2;
 }
 
 // hits, misses, evictions, bytes read, nanoseconds reading, failures, direct I/O in use

@@ -194,8 +194,14 @@ def test_nvme_expert_arena_matches_ram_stacks_and_evicts_lru(tmp_path):
     assert nv.resident(1) == [0, 1, 2, 3, 4]
     st = nv.stats()
     assert st["failed"] == 0 and st["bytes_read"] >= st["misses"] * min(v["blob"] for v in ix["layers"].values()) and st["hits"] >= 1
-    with pytest.raises(OSError):                                                # more distinct experts than slots in one call
-        nv.moe(0, torch.arange(8, dtype=torch.int32).reshape(2, 4) + 8, torch.rand(2, 4), *Q.quantize_act_q8(torch.randn(2, H)))
+    leg(0, torch.arange(8, dtype=torch.int32).reshape(2, 4) + 8)               # 8 distinct experts, 6 slots: served row by row
+    for e in nv.resident(0)[:3]:
+        nv.pin(0, e)
+    pinned = set(nv.resident(0)[:3])
+    fresh = [e for e in range(E) if e not in nv.resident(0)][:4]
+    with pytest.raises(OSError):                                                # one row needs 4 slots, pins leave 3
+        nv.moe(0, torch.tensor([fresh], dtype=torch.int32), torch.rand(1, 4), *Q.quantize_act_q8(torch.randn(1, H)))
+    assert pinned <= set(nv.resident(0))
     nv.close()
 
 
