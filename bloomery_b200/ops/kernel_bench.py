@@ -1,7 +1,7 @@
 """Kernel micro-benchmark: each decode / prefill kernel alone at Qwen3-30B-A3B layer shapes, over a
 few layers of random weights, replayed from a CUDA graph and timed with CUDA events.
 
-    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|down|flash|gemm} [replays]
+    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|down|flash|gemm|gemmdist|mla|sampler} [replays]
 
 It is also the small workload the ncu summaries under ``profiles/`` were captured on.
 """
@@ -48,6 +48,29 @@ if which == "gemm":
     from bloomery_b200.ops import gemm as G
     A = (torch.randn(4096, 2048, device=dev) * 0.1).bfloat16(); B = (torch.randn(5120, 2048, device=dev) * 0.1).bfloat16()
     C = torch.zeros(4096, 5120, device=dev, dtype=torch.bfloat16); tt = G.TileTable.dense(4096, dev); gst = torch.zeros(1, dtype=torch.int32, device=dev)
+if which == "gemmdist":
+    # the several-GPU epilogue on one GPU: o_proj-shaped product whose rows are added into two "owners" (both local here)
+    from bloomery_b200.ops import gemm as G
+    A = (torch.randn(4096, 4096, device=dev) * 0.1).bfloat16(); B = (torch.randn(2048, 4096, device=dev) * 0.1).bfloat16()
+    own = [torch.zeros(2048, 2048, device=dev) for _ in range(2)]
+    tt = G.TileTable.dense(4096, dev); gst = torch.zeros(1, dtype=torch.int32, device=dev)
+if which == "mla":
+    mq, mctx = 128, 4096
+    mcache = torch.randn(mctx // 64, 64, 576, device=dev).half()
+    mtable = torch.arange(mctx // 64, dtype=torch.int32, device=dev)[None].contiguous()
+    mpos = torch.tensor([mctx - 2], dtype=torch.int32, device=dev); mseq = torch.zeros(1, dtype=torch.int32, device=dev)
+    mqlat = torch.randn(8, mq, 576, device=dev) * 0.05
+    mseg = 37
+    mml = torch.zeros(8 * mq * mseg * 2, device=dev); macc = torch.zeros(8 * mq * mseg * 512, device=dev)
+    mvb = (torch.randn(mq, 128, 512, device=dev) * 0.05).bfloat16()
+    moq = torch.zeros(8, mq * 128, dtype=torch.int8, device=dev); mods = torch.zeros(8, mq * 128 // 32, 2, device=dev)
+if which == "sampler":
+    V = 151936
+    slog = torch.randn(1, V, device=dev) * 3
+    spar = torch.tensor([[0.8, 40, 0.95, 0.05, 1.1, 0.0, 0.0, 64]], device=dev)
+    ssd = torch.tensor([1234], dtype=torch.int64, device=dev); sdr = torch.zeros(1, dtype=torch.int64, device=dev)
+    srec = torch.randint(0, V, (1, 64), dtype=torch.int32, device=dev); snrec = torch.tensor([64], dtype=torch.int32, device=dev)
+    swork = torch.zeros(1, V, device=dev); sout = torch.zeros(1, dtype=torch.int32, device=dev)
 reps = int(sys.argv[2]) if len(sys.argv) > 2 else 4
 def chain():
     for l in layers:
@@ -57,6 +80,9 @@ def chain():
         if which in ("all", "gateup"): K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0, route_logits=logits, rule=K.RouteRule(k), wts=wts)
         if which in ("all", "flash"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
         if which == "gemm": G.gemm_bf16(A, B, tt, out_bf16=C, status=gst)
+        if which == "gemmdist": G.gemm_bf16_dist([A.data_ptr()], 4096, 4096, B, tt, owners=[o.data_ptr() for o in own], rows_per_owner=2048, ldc=2048, status=gst)
+        if which == "mla": K.mla_flash_decode(mqlat, mcache, mpos, mseq, mtable, mctx // 64, mq, 1, mseg, mctx, mml, macc, mvb, 128, None, moq, mods, fault, 0)
+        if which == "sampler": K.sample_rows(slog, V, 1, spar, ssd, sdr, sout, recent=srec, n_recent=snrec, work=swork)
         if which in ("all", "down"): K.down_combine(actq, actds, ids, wts, None, l["d"], E, k, M, x, None, x, fault, 0)
 g = torch.cuda.CUDAGraph()
 s = torch.cuda.Stream()
