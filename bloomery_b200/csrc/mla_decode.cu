@@ -6,8 +6,9 @@
 //
 //   1. mla_kv_append   RMSNorm(c) * gain, interleaved-pair RoPE on the 64 rope dims, f16 append
 //   2. mla_q_absorb    per head: RoPE on q_rope, q_lat = W_kb[h]^T q_nope  -> q' [M, n_q, 576] (pre-scaled)
-//   3. mla_flash_seg   split-K online softmax of q' against the latent rows; the value of a key is
-//                      its first 512 entries (one read serves K and V)
+//   3. mla_flash_seg   split-K online softmax of q' against the latent rows on warp-level tensor-core tiles
+//                      (16 heads = the M dimension); the value of a key is its first 512 entries (one read
+//                      serves K and V)
 //   4. mla_merge_vup   merge segments ascending, v = W_vb[h] * latent (128 x 512 per head), q8 for o_proj
 //
 // The reference's latent flash and its absorbed-q f32 GEMV: crates/gpu/src/flash.rs,
@@ -145,13 +146,38 @@ __device__ __forceinline__ void mla_cp16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
 
-// grid (n_seg, ceil(n_q / 16), M), 256 threads; warp w serves heads 2w, 2w+1 of the block's 16
-__global__ void __launch_bounds__(256) mla_flash_seg_kernel(const MlaFlashArgs a) {
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+constexpr int kPStride = 40;            // f16 row stride of the probability tile (32 keys + pad: conflict-free fragment loads)
+constexpr int kSStride = 33;            // f32 row stride of the score tile
+
+// grid (n_seg, ceil(n_q / 16), M), 256 threads = 8 warps; one block = 16 heads x one key segment.
+// The 16 heads are the M dimension of warp-level tensor-core tiles (m16n8k16, f16 operands, f32 accumulate):
+//   scores  S[16 x 32] = Q[16 x 576] K^T   warps (w, w + 4) share key columns 8(w & 3).., each half of the 576 depth
+//   softmax            warp w owns head rows 2w, 2w + 1 (running max / sum in registers, probabilities to f16)
+//   values  O[16 x 512] += P[16 x 32] V    warp w owns latent columns 64w..64w + 63 (V fragments by ldmatrix.trans
+//                                          from the same rows the keys were read from)
+// The cache is f16 already, so the K / V tiles feed the tensor cores as they arrive (cp.async, two stages).
+__global__ void __launch_bounds__(256, 2) mla_flash_seg_kernel(const MlaFlashArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
-  float* sq = reinterpret_cast<float*>(smem);                                         // [16][576]
-  __half* skv = reinterpret_cast<__half*>(smem + (size_t)kHeadsPerBlock * kRow * 4);  // [2][32][584]
+  __half* sq = reinterpret_cast<__half*>(smem);                                  // [16][584] f16, pre-scaled q'
+  __half* skv = sq + kHeadsPerBlock * kRowPad;                                   // [2][32][584]
+  float* ss = reinterpret_cast<float*>(skv + 2 * kTile * kRowPad);              // [16][33] scores
+  float* spart = ss + kHeadsPerBlock * kSStride;                                 // [4][16][8] upper-half partial scores
+  __half* sp = reinterpret_cast<__half*>(spart + 4 * 16 * 8);                    // [16][40] probabilities
+  float* scorr = reinterpret_cast<float*>(sp + kHeadsPerBlock * kPStride);       // [16]
   const int seg = blockIdx.x, hb = blockIdx.y, m = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
   pdl_wait();
   pdl_launch();
   const int seq = a.row_seq[m];
@@ -165,11 +191,14 @@ __global__ void __launch_bounds__(256) mla_flash_seg_kernel(const MlaFlashArgs a
   if (!bad && t0 >= t1) return;                  // past the row's last key tile: the merge does not read this segment
   const int h0 = hb * kHeadsPerBlock;
   const int n_heads = min(kHeadsPerBlock, a.n_q - h0);
-  for (int i = tid; i < n_heads * kRow; i += 256) sq[i] = a.q_lat[((long)m * a.n_q + h0) * kRow + i];
+  for (int i = tid; i < kHeadsPerBlock * kRow; i += 256) {
+    const int r = i / kRow, c = i - r * kRow;
+    sq[r * kRowPad + c] = __float2half_rn(r < n_heads ? a.q_lat[((long)m * a.n_q + h0 + r) * kRow + c] : 0.f);
+  }
 
   const int* bt = a.block_table + (long)seq * a.max_pages;
-  auto issue_tile = [&](int t, int stage) {
-    const int key0 = t * kTile;
+  auto issue_tile = [&](int tl, int stage) {
+    const int key0 = tl * kTile;
     int page = bt[key0 / kMlaPage];
     page = (page < 0 || page >= a.n_pages) ? 0 : page;     // the append kernel raises the fault; stay in bounds
     const __half* base = a.cache + ((long)page * kMlaPage + (key0 % kMlaPage)) * kRow;
@@ -181,84 +210,114 @@ __global__ void __launch_bounds__(256) mla_flash_seg_kernel(const MlaFlashArgs a
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  float mx[2], l[2], acc[2][16];
+  float acc[8][4];                               // latent columns 64 warp + 8 j + {2t, 2t+1}, rows g and g + 8
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    mx[h] = -INFINITY; l[h] = 0.f;
-#pragma unroll
-    for (int d = 0; d < 16; ++d) acc[h][d] = 0.f;
-  }
-  const bool live0 = 2 * warp < n_heads, live1 = 2 * warp + 1 < n_heads;
+  for (int j = 0; j < 8; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+  float mx[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};    // of head rows 2 warp, 2 warp + 1
 
   if (t0 < t1) issue_tile(t0, 0);
-  for (int t = t0; t < t1; ++t) {
-    const int stage = (t - t0) & 1;
-    if (t + 1 < t1) { issue_tile(t + 1, stage ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+  for (int tl = t0; tl < t1; ++tl) {
+    const int stage = (tl - t0) & 1;
+    if (tl + 1 < t1) { issue_tile(tl + 1, stage ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
     else { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
     __syncthreads();
-    if (live0) {
-      const __half* krow = skv + ((size_t)stage * kTile + lane) * kRowPad;
-      const float* q0p = sq + (2 * warp) * kRow;
-      const float* q1p = sq + (live1 ? 2 * warp + 1 : 2 * warp) * kRow;
-      float s0 = 0.f, s1 = 0.f;
-#pragma unroll 4
-      for (int d = 0; d < kRow; d += 8) {
-        const uint4 kv = *reinterpret_cast<const uint4*>(krow + d);
-        const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kv.x));
-        const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kv.y));
-        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kv.z));
-        const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kv.w));
-        const float4 a0 = *reinterpret_cast<const float4*>(q0p + d), a1 = *reinterpret_cast<const float4*>(q0p + d + 4);
-        const float4 b0 = *reinterpret_cast<const float4*>(q1p + d), b1 = *reinterpret_cast<const float4*>(q1p + d + 4);
-        s0 = fmaf(a0.x, k0.x, s0); s0 = fmaf(a0.y, k0.y, s0); s0 = fmaf(a0.z, k1.x, s0); s0 = fmaf(a0.w, k1.y, s0);
-        s0 = fmaf(a1.x, k2.x, s0); s0 = fmaf(a1.y, k2.y, s0); s0 = fmaf(a1.z, k3.x, s0); s0 = fmaf(a1.w, k3.y, s0);
-        s1 = fmaf(b0.x, k0.x, s1); s1 = fmaf(b0.y, k0.y, s1); s1 = fmaf(b0.z, k1.x, s1); s1 = fmaf(b0.w, k1.y, s1);
-        s1 = fmaf(b1.x, k2.x, s1); s1 = fmaf(b1.y, k2.y, s1); s1 = fmaf(b1.z, k3.x, s1); s1 = fmaf(b1.w, k3.y, s1);
+    __half* kv = skv + (size_t)stage * kTile * kRowPad;
+    const int kmax = min(kTile, n_keys - tl * kTile);
+    if (kmax < kTile) {                          // rows past the last key: their probability is 0, keep 0 * x finite
+      for (int i = tid; i < (kTile - kmax) * (kRowPad / 2); i += 256)
+        reinterpret_cast<uint32_t*>(kv + (size_t)kmax * kRowPad)[i] = 0u;
+      __syncthreads();
+    }
+    // ---- scores ----------------------------------------------------------------------------------
+    {
+      const int nt = warp & 3, kh = warp >> 2;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const __half* qa = sq + g * kRowPad + 2 * t;
+      const __half* kb = kv + (size_t)(nt * 8 + g) * kRowPad + 2 * t;
+#pragma unroll 6
+      for (int ks = kh * 18; ks < kh * 18 + 18; ++ks) {
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa + ks * 16);
+        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qa + 8 * kRowPad + ks * 16);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + ks * 16 + 8);
+        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qa + 8 * kRowPad + ks * 16 + 8);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + ks * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + ks * 16 + 8);
+        mma_f16_16816(c, a0, a1, a2, a3, b0, b1);
       }
-      if (t * kTile + lane >= n_keys) { s0 = -INFINITY; s1 = -INFINITY; }
-      float p[2];
-      const float sc[2] = {s0, s1};
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const float nm = fmaxf(mx[h], warp_max(sc[h]));
-        const float corr = (mx[h] == -INFINITY) ? 0.f : __expf(mx[h] - nm);
-        p[h] = (sc[h] == -INFINITY) ? 0.f : __expf(sc[h] - nm);
-        l[h] = l[h] * corr + warp_sum(p[h]);
-        mx[h] = nm;
-#pragma unroll
-        for (int d = 0; d < 16; ++d) acc[h][d] *= corr;
+      if (kh == 1) {
+        float* o = spart + nt * 128;
+        o[g * 8 + 2 * t] = c[0]; o[g * 8 + 2 * t + 1] = c[1]; o[(g + 8) * 8 + 2 * t] = c[2]; o[(g + 8) * 8 + 2 * t + 1] = c[3];
       }
-      // values: the first 512 entries of each row; lane owns dims 2*lane + 64*i, +1
-      const __half* vbase = skv + (size_t)stage * kTile * kRowPad + 2 * lane;
-      const int kmax = min(kTile, n_keys - t * kTile);       // masked keys are never read
-#pragma unroll 2
-      for (int k = 0; k < kmax; ++k) {
-        const float p0 = __shfl_sync(0xffffffffu, p[0], k), p1 = __shfl_sync(0xffffffffu, p[1], k);
-        const __half* vr = vbase + (size_t)k * kRowPad;
+      __syncthreads();
+      if (kh == 0) {
+        const float* o = spart + nt * 128;
+        const int col = nt * 8 + 2 * t;
+        const bool m0 = col < kmax, m1 = col + 1 < kmax;
+        ss[g * kSStride + col] = m0 ? c[0] + o[g * 8 + 2 * t] : -INFINITY;
+        ss[g * kSStride + col + 1] = m1 ? c[1] + o[g * 8 + 2 * t + 1] : -INFINITY;
+        ss[(g + 8) * kSStride + col] = m0 ? c[2] + o[(g + 8) * 8 + 2 * t] : -INFINITY;
+        ss[(g + 8) * kSStride + col + 1] = m1 ? c[3] + o[(g + 8) * 8 + 2 * t + 1] : -INFINITY;
+      }
+    }
+    __syncthreads();
+    // ---- online softmax: warp w owns head rows 2w, 2w + 1 --------------------------------------------
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float2 v = __half22float2(*reinterpret_cast<const __half2*>(vr + 64 * i));
-          acc[0][2 * i] = fmaf(p0, v.x, acc[0][2 * i]); acc[0][2 * i + 1] = fmaf(p0, v.y, acc[0][2 * i + 1]);
-          acc[1][2 * i] = fmaf(p1, v.x, acc[1][2 * i]); acc[1][2 * i + 1] = fmaf(p1, v.y, acc[1][2 * i + 1]);
+    for (int h = 0; h < 2; ++h) {
+      const int r = 2 * warp + h;
+      const float sc = ss[r * kSStride + lane];
+      const float nm = fmaxf(mx[h], warp_max(sc));
+      const float corr = (mx[h] == -INFINITY) ? 0.f : __expf(mx[h] - nm);
+      const float pr = (sc == -INFINITY) ? 0.f : __expf(sc - nm);
+      l[h] = l[h] * corr + warp_sum(pr);
+      mx[h] = nm;
+      sp[r * kPStride + lane] = __float2half_rn(pr);
+      if (lane == 0) scorr[r] = corr;
+    }
+    __syncthreads();
+    // ---- values: warp w owns latent columns 64w .. 64w + 63 --------------------------------------------
+    {
+      const float c_lo = scorr[g], c_hi = scorr[g + 8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { acc[j][0] *= c_lo; acc[j][1] *= c_lo; acc[j][2] *= c_hi; acc[j][3] *= c_hi; }
+      const __half* pa = sp + g * kPStride + 2 * t;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(pa + ks * 16);
+        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(pa + 8 * kPStride + ks * 16);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(pa + ks * 16 + 8);
+        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(pa + 8 * kPStride + ks * 16 + 8);
+        // lane l addresses row (l & 7) of matrix (l >> 3): matrices 0, 1 = keys 16ks + 0..7, + 8..15 of column tile j,
+        // matrices 2, 3 = the same keys of column tile j + 1
+        const __half* vrow = kv + (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kRowPad + 64 * warp + (lane >> 4) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, vrow + j * 8);
+          mma_f16_16816(acc[j], a0, a1, a2, a3, b[0], b[1]);
+          mma_f16_16816(acc[j + 1], a0, a1, a2, a3, b[2], b[3]);
         }
       }
     }
     __syncthreads();
   }
+  // partial results of this segment
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int hh = 2 * warp + h;
-    if (hh < n_heads) {
-      const long pidx = ((long)m * a.n_q + h0 + hh) * a.n_seg + seg;
-      if (lane == 0) {
-        a.part_ml[pidx * 2] = bad ? __int_as_float(0x7fc00000) : mx[h];
-        a.part_ml[pidx * 2 + 1] = l[h];
-      }
+    const int r = 2 * warp + h;
+    if (r < n_heads && lane == 0) {
+      const long pidx = ((long)m * a.n_q + h0 + r) * a.n_seg + seg;
+      a.part_ml[pidx * 2] = bad ? __int_as_float(0x7fc00000) : mx[h];
+      a.part_ml[pidx * 2 + 1] = l[h];
+    }
+  }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        a.part_acc[pidx * kLat + 2 * lane + 64 * i] = acc[h][2 * i];
-        a.part_acc[pidx * kLat + 2 * lane + 64 * i + 1] = acc[h][2 * i + 1];
-      }
+  for (int hh = 0; hh < 2; ++hh) {
+    const int r = g + 8 * hh;
+    if (r < n_heads) {
+      const long pidx = ((long)m * a.n_q + h0 + r) * a.n_seg + seg;
+      float* o = a.part_acc + pidx * kLat + 64 * warp + 2 * t;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) *reinterpret_cast<float2*>(o + 8 * j) = make_float2(acc[j][2 * hh], acc[j][2 * hh + 1]);
     }
   }
 }
@@ -366,7 +425,8 @@ int bl_mla_flash_decode(const float* q_lat, const void* cache, const int* row_po
                         float* outds, unsigned* fault, int layer, cudaStream_t st) {
   BL_REQUIRE(n_q >= 1 && M >= 1 && n_seg >= 1 && v_dim >= 32 && v_dim <= 128 && v_dim % 32 == 0, BL_ERR_SHAPE);
   BL_REQUIRE(wtype == 0 || wtype == 30, BL_ERR_TYPE);
-  const size_t smem = (size_t)kHeadsPerBlock * kRow * 4 + (size_t)2 * kTile * kRowPad * 2;
+  const size_t smem = (size_t)kHeadsPerBlock * kRowPad * 2 + (size_t)2 * kTile * kRowPad * 2 +
+                      (size_t)(kHeadsPerBlock * kSStride + 4 * 16 * 8) * 4 + (size_t)kHeadsPerBlock * kPStride * 2 + 16 * 4;
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(mla_flash_seg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

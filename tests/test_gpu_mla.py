@@ -81,7 +81,7 @@ def test_mla_kernels_match_fp32(wdtype, n_q, ctx):
         sc = (torch.einsum("hn,shn->hs", qm[:, :nope], k_nope) + torch.einsum("hr,sr->hs", q_rope, kr)) * scale
         ref = torch.einsum("hs,shv->hv", torch.softmax(sc.double(), -1).float(), v).reshape(-1)
         err = ((out[m].cpu() - ref).abs().max() / ref.abs().max()).item()
-        assert err < 2e-3, (m, err)
+        assert err < 5e-3, (m, err)      # q and the probabilities pass through f16 on their way to the tensor cores
         c, ds = Q.quantize_act_q8(out[m].cpu()[None])
         assert torch.equal(outq[m].cpu(), c[0]) and torch.allclose(outds[m].cpu(), ds[0], rtol=1e-6)
     # a key count beyond the context is a fault and NaN rows
