@@ -83,6 +83,19 @@ template <typename W> __device__ __forceinline__ float wf(const W* p, long i);
 template <> __device__ __forceinline__ float wf<float>(const float* p, long i) { return p[i]; }
 template <> __device__ __forceinline__ float wf<__nv_bfloat16>(const __nv_bfloat16* p, long i) { return __bfloat162float(p[i]); }
 
+// eight consecutive weights as floats (16-byte loads for bf16, two for f32)
+template <typename W> __device__ __forceinline__ void load8(const W* p, float* o);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* o) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* o) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { o[2 * i] = __uint_as_float(w[i] << 16); o[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+
 struct MlaQArgs {
   const float* q;          // [M, stride]: head h at h * (nope + 64): nope values then 64 rope values
   long stride;
@@ -341,6 +354,23 @@ __global__ void __launch_bounds__(256) mla_merge_vup_kernel(const MlaMergeArgs a
   __shared__ float slat[kLat];
   __shared__ float so[128];
   const int h = blockIdx.x, m = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // weights do not depend on the launch before this one: the first row group is fetched ahead of the wait
+  const W* w = reinterpret_cast<const W*>(a.w_vb) + (long)h * a.v_dim * kLat;
+  auto load_group = [&](int r0, float (&dst)[4][16]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = r0 + 8 * q;
+      if (r < a.v_dim) {
+        load8<W>(w + (long)r * kLat + 8 * lane, dst[q]);
+        load8<W>(w + (long)r * kLat + 256 + 8 * lane, dst[q] + 8);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[q][i] = 0.f;
+      }
+    }
+  };
+  float cur[4][16];
+  load_group(warp, cur);
   pdl_wait();
   pdl_launch();
   if (a.row_seq[m] < 0) return;
@@ -356,13 +386,15 @@ __global__ void __launch_bounds__(256) mla_merge_vup_kernel(const MlaMergeArgs a
   }
   float mx = -INFINITY;
   bool nan = false;
+#pragma unroll 8
   for (int s = 0; s < used; ++s) {
     const float v = a.part_ml[(p0 + s) * 2];
     nan |= (v != v);
     mx = fmaxf(mx, v);
   }
   float n0 = 0.f, n1 = 0.f, den = 0.f;
-  for (int s = 0; s < used; ++s) {                          // ascending segment order, fixed
+#pragma unroll 8
+  for (int s = 0; s < used; ++s) {                          // ascending segment order, fixed; loads of 8 segments in flight
     const float ms = a.part_ml[(p0 + s) * 2];
     const float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
     den = fmaf(a.part_ml[(p0 + s) * 2 + 1], w, den);
@@ -373,13 +405,32 @@ __global__ void __launch_bounds__(256) mla_merge_vup_kernel(const MlaMergeArgs a
   slat[tid] = nan ? qnan : n0 / den;
   slat[tid + 256] = nan ? qnan : n1 / den;
   __syncthreads();
-  const W* w = reinterpret_cast<const W*>(a.w_vb) + (long)h * a.v_dim * kLat;
-  for (int r = warp; r < a.v_dim; r += 8) {
-    float acc = 0.f;
+  // value up-projection: warp w takes rows w, w + 8, ...; four rows at a time so that eight 16-byte weight loads
+  // are in flight; lane l covers latent columns 8l..8l+7 and 256 + 8l..  The first group's weights were fetched
+  // before the partials were merged, each later group's while the one before it is multiplied.
+  float xl[16];
 #pragma unroll
-    for (int i = 0; i < kLat / 32; ++i) acc = fmaf(wf<W>(w, (long)r * kLat + lane + 32 * i), slat[lane + 32 * i], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) so[r] = acc;
+  for (int i = 0; i < 8; ++i) { xl[i] = slat[8 * lane + i]; xl[8 + i] = slat[256 + 8 * lane + i]; }
+  for (int r0 = warp; r0 < a.v_dim; r0 += 32) {
+    float nxt[4][16];
+    const bool more = r0 + 32 < a.v_dim;
+    if (more) load_group(r0 + 32, nxt);
+    float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc4[q] = fmaf(cur[q][i], xl[i], acc4[q]);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float v = warp_sum(acc4[q]);
+      if (lane == 0 && r0 + 8 * q < a.v_dim) so[r0 + 8 * q] = v;
+    }
+    if (more) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) cur[q][i] = nxt[q][i];
+    }
   }
   __syncthreads();
   if (tid < a.v_dim) {
