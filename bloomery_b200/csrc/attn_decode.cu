@@ -281,13 +281,15 @@ __global__ void __launch_bounds__(HEAD) flash_decode_merge_kernel(const MergeArg
   }
   float mx = -INFINITY;
   bool nan = false;
+#pragma unroll 8
   for (int s = 0; s < used; ++s) {
     float v = a.part_ml[(p0 + s) * 2];
     nan |= (v != v);
     mx = fmaxf(mx, v);
   }
   float num = 0.f, den = 0.f;
-  for (int s = 0; s < used; ++s) {  // ascending segment order, fixed
+#pragma unroll 8
+  for (int s = 0; s < used; ++s) {  // ascending segment order, fixed; the loads of eight segments are in flight together
     float ms = a.part_ml[(p0 + s) * 2];
     float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
     den = fmaf(a.part_ml[(p0 + s) * 2 + 1], w, den);
