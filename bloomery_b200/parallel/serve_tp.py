@@ -102,6 +102,8 @@ def leader_engine(dec, tokenizer, model_name: str, chan: Lockstep):
     from ..serve.engine import GpuEngine, Saved
 
     class TpGpuEngine(GpuEngine):
+        device_sampling = False          # the followers do not mirror sampler state; the leader samples on the host
+
         def __init__(self):
             super().__init__(dec, tokenizer, model_name)
             self._sid = itertools.count(1)

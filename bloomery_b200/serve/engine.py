@@ -162,13 +162,53 @@ class GpuEngine(Engine):
         except (EngineFault, EngineStalled) as exc:
             raise EngineError(str(exc)) from exc
 
-    def step(self, rows, want_logits=True, draft_slots=None):
+    device_sampling = True
+
+    def _sample_on_device(self, n_rows: int, specs) -> Dict[int, int]:
+        """Run the sampling chain on the card for the rows of the last pass that carry a spec
+        (``(SamplingParams, draws so far, recent ids)``); returns row -> sampled id.  Same bits as the host chain
+        (``serve/sampler.py``) for the same seed and draw number."""
+        import torch
+        from ..ops import decode as K
+        dec = self.dec
+        dev = dec.device
+        M = n_rows
+        W = max([len(sp[2]) for sp in specs if sp is not None] + [1])
+        par = torch.zeros(M, 8, dtype=torch.float32)
+        par[:, 0] = 0.0                                    # rows without a spec: temperature 0 = the greedy pick
+        seeds = torch.zeros(M, dtype=torch.int64)
+        draws = torch.zeros(M, dtype=torch.int64)
+        rec = torch.zeros(M, W, dtype=torch.int32)
+        nrec = torch.zeros(M, dtype=torch.int32)
+        for r, sp in enumerate(specs):
+            if sp is None:
+                continue
+            p_, n_drawn, recent = sp
+            par[r] = torch.tensor([p_.temperature, p_.top_k, p_.top_p, p_.min_p, p_.repeat_penalty, p_.frequency_penalty,
+                                   p_.presence_penalty, p_.repeat_last_n])
+            seeds[r] = p_.seed if p_.seed < (1 << 63) else p_.seed - (1 << 64)
+            draws[r] = n_drawn
+            if len(recent):
+                rec[r, :len(recent)] = torch.tensor(list(recent), dtype=torch.int32)
+                nrec[r] = len(recent)
+        if getattr(self, "_samp_work", None) is None:
+            self._samp_work = torch.zeros(self.max_rows, self.n_vocab, device=dev)
+            self._samp_out = torch.zeros(self.max_rows, dtype=torch.int32, device=dev)
+        K.sample_rows(dec.logits[:M], self.n_vocab, M, par.to(dev), seeds.to(dev), draws.to(dev), self._samp_out,
+                      recent=rec.to(dev), n_recent=nrec.to(dev), work=self._samp_work)
+        got = self._samp_out[:M].cpu().tolist()
+        return {r: int(got[r]) for r, sp in enumerate(specs) if sp is not None}
+
+    def step(self, rows, want_logits=True, draft_slots=None, sampling=None):
         from ..runtime.engine import EngineFault, EngineStalled
         out = []
         try:
             for i in range(0, len(rows), self.max_rows):
                 chunk = list(rows[i:i + self.max_rows])
                 picks = self.dec.step(chunk)
+                if sampling is not None and any(sp is not None for sp in sampling[i:i + self.max_rows]):
+                    for r, tok in self._sample_on_device(len(chunk), sampling[i:i + self.max_rows]).items():
+                        picks[r] = tok
                 lg = self.dec.logits[:len(chunk)].float().cpu().numpy() if want_logits else None
                 if draft_slots and getattr(self.dec, "mtp_on", False):
                     self.dec.draft_after(chunk, picks, draft_slots)

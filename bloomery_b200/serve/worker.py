@@ -69,6 +69,7 @@ class Active:
     stop_word: str = ""
     cache_ms: float = 0.0
     draft_n: int = 0
+    n_drawn: int = 0              # uniforms consumed by the card's sampler for this request
     draft_accepted: int = 0
 
 
@@ -299,14 +300,35 @@ class Worker(threading.Thread):
         if not rows:
             return
         who = [sp[0] for sp in spans]
-        need_logits = any(w.req.sampling.temperature > 0 or w.req.sampling.penalizes or w.req.n_probs > 0
-                          or w.req.constraint is not None or w.req.logit_bias or w.req.ignore_eos for w in who)
+
+        def on_card(a: Active) -> bool:
+            """The card runs the whole sampling chain when nothing needs the logits on the host."""
+            r = a.req
+            return (getattr(self.engine, "device_sampling", False) and (r.sampling.temperature > 0 or r.sampling.penalizes)
+                    and r.n_probs == 0 and r.constraint is None and not r.logit_bias and not r.ignore_eos)
+
+        sampling = None
+        if any(on_card(a) for a in who):
+            sampling = [None] * len(rows)
+            for a, r0, drafted in spans:
+                if on_card(a) and not drafted:
+                    sp = a.req.sampling
+                    recent = (a.slot.ids + [a.pending_token])[-sp.repeat_last_n:] if sp.repeat_last_n > 0 else []
+                    sampling[r0] = (sp, a.n_drawn, recent)
+        need_logits = any((w.req.sampling.temperature > 0 or w.req.sampling.penalizes or w.req.n_probs > 0
+                           or w.req.constraint is not None or w.req.logit_bias or w.req.ignore_eos) and not on_card(w) for w in who)
         t0 = time.time()
+        kw = {}
         if getattr(self.draft, "wants_slot", False):
-            res = self.engine.step(rows, want_logits=need_logits,
-                                   draft_slots={sp[0].slot.id for sp in spans if self._can_draft(sp[0])})
-        else:
-            res = self.engine.step(rows, want_logits=need_logits)
+            kw["draft_slots"] = {sp[0].slot.id for sp in spans if self._can_draft(sp[0])}
+        if sampling is not None:
+            kw["sampling"] = sampling
+        res = self.engine.step(rows, want_logits=need_logits, **kw)
+        if sampling is not None:
+            for a, r0, _ in spans:
+                if sampling[r0] is not None:
+                    a.n_drawn += 1
+                    res[r0] = (res[r0][0], None)        # the id is the sampled one: nothing left to do on the host
         dt = time.time() - t0
         self.metrics.add("round_seconds_total", dt)
         self.metrics.add("n_decode_total")

@@ -68,3 +68,35 @@ def test_sampler_penalties_greedy_and_ties():
     assert picks[0][0] == Sampler(pen).sample(host[0], [10, 10, 3]) == 20      # the repeated best is penalised away
     assert picks[0][1] in (0, 1, 2, 3) and ncand[1] == 4
     assert picks[0][2] == 7                                                    # equal logits: the lower id
+
+
+def test_serving_engine_samples_on_the_card_like_the_host_chain():
+    """GpuEngine.step with a sampling spec returns the id the host chain picks from the same logits, seed and draw
+    number, with penalties over the recent window."""
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.engine import DecodeEngine
+    from bloomery_b200.serve.engine import GpuEngine
+    from bloomery_b200.serve.sampler import Sampler, SamplingParams
+    from bloomery_b200.serve.tokenizer import ByteTokenizer
+    spec = tiny_qwen3moe()
+    dec = DecodeEngine(Weights.from_items(spec, synth_tensors(spec, "cpu", seed=7), DEV), n_slots=2, slot_ctx=256)
+    eng = GpuEngine(dec, ByteTokenizer(spec.vocab), "tiny")
+    prompt = [5, 9, 300, 77, 9, 1234]
+    eng.prefill(0, prompt[:-1], 0)
+    eng.prefill(1, prompt[:-1], 0)
+    sp = SamplingParams(temperature=1.1, top_k=50, top_p=0.9, min_p=0.01, repeat_penalty=1.3, repeat_last_n=4, seed=99)
+    host = Sampler(sp)
+    tok_h, tok_d, ids = prompt[-1], prompt[-1], list(prompt[:-1])
+    agree = 0
+    for i in range(6):
+        pos = len(ids)
+        recent = (ids + [tok_h])[-4:]
+        res_h = eng.step([(0, tok_h, pos)], want_logits=True)
+        pick_h = host.sample(res_h[0][1], recent)
+        res_d = eng.step([(1, tok_d, pos)], want_logits=False, sampling=[(sp, i, recent)])
+        assert res_d[0][1] is None
+        agree += int(res_d[0][0] == pick_h)
+        ids.append(tok_h)
+        tok_h = tok_d = pick_h                 # keep both slots on the host chain's text
+    assert agree >= 5, agree                   # a probability that ties at fp32 rounding may order differently once
