@@ -97,7 +97,7 @@ def source_hash() -> str:
 def build_cuda(verbose: bool = False) -> str:
     srcs = sorted(os.path.join(CSRC, n) for n in os.listdir(CSRC) if n.endswith(".cu"))
     inc = []
-    return _build_lib("libbloomery_cuda.so", srcs, _nvcc(), NVCC_FLAGS + inc, ["-lcuda"], verbose)
+    return _build_lib("libbloomery_cuda.so", srcs, _nvcc(), NVCC_FLAGS + inc, [], verbose)
 
 
 def build_host(verbose: bool = False) -> str:
