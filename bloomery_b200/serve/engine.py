@@ -166,7 +166,7 @@ class GpuEngine(Engine):
 
     def _sample_on_device(self, n_rows: int, specs) -> Dict[int, int]:
         """Run the sampling chain on the card for the rows of the last pass that carry a spec
-        (``(SamplingParams, draws so far, recent ids)``); returns row -> sampled id.  Same bits as the host chain
+        (``[SamplingParams, draws so far, recent ids]``; the draw count is updated in place); returns row -> sampled id.  Same bits as the host chain
         (``serve/sampler.py``) for the same seed and draw number."""
         import torch
         from ..ops import decode as K
@@ -194,9 +194,14 @@ class GpuEngine(Engine):
         if getattr(self, "_samp_work", None) is None:
             self._samp_work = torch.zeros(self.max_rows, self.n_vocab, device=dev)
             self._samp_out = torch.zeros(self.max_rows, dtype=torch.int32, device=dev)
-        K.sample_rows(dec.logits[:M], self.n_vocab, M, par.to(dev), seeds.to(dev), draws.to(dev), self._samp_out,
+        draws_dev = draws.to(dev)
+        K.sample_rows(dec.logits[:M], self.n_vocab, M, par.to(dev), seeds.to(dev), draws_dev, self._samp_out,
                       recent=rec.to(dev), n_recent=nrec.to(dev), work=self._samp_work)
         got = self._samp_out[:M].cpu().tolist()
+        after = draws_dev.cpu().tolist()
+        for r, sp in enumerate(specs):
+            if sp is not None:
+                sp[1] = int(after[r])          # the chain draws only when more than one candidate survives
         return {r: int(got[r]) for r, sp in enumerate(specs) if sp is not None}
 
     def step(self, rows, want_logits=True, draft_slots=None, sampling=None):

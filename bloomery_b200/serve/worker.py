@@ -314,7 +314,7 @@ class Worker(threading.Thread):
                 if on_card(a) and not drafted:
                     sp = a.req.sampling
                     recent = (a.slot.ids + [a.pending_token])[-sp.repeat_last_n:] if sp.repeat_last_n > 0 else []
-                    sampling[r0] = (sp, a.n_drawn, recent)
+                    sampling[r0] = [sp, a.n_drawn, recent]
         need_logits = any((w.req.sampling.temperature > 0 or w.req.sampling.penalizes or w.req.n_probs > 0
                            or w.req.constraint is not None or w.req.logit_bias or w.req.ignore_eos) and not on_card(w) for w in who)
         t0 = time.time()
@@ -327,7 +327,7 @@ class Worker(threading.Thread):
         if sampling is not None:
             for a, r0, _ in spans:
                 if sampling[r0] is not None:
-                    a.n_drawn += 1
+                    a.n_drawn = sampling[r0][1]      # the engine wrote back how many uniforms the chain has used
                     res[r0] = (res[r0][0], None)        # the id is the sampled one: nothing left to do on the host
         dt = time.time() - t0
         self.metrics.add("round_seconds_total", dt)

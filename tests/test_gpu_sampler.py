@@ -88,13 +88,15 @@ def test_serving_engine_samples_on_the_card_like_the_host_chain():
     sp = SamplingParams(temperature=1.1, top_k=50, top_p=0.9, min_p=0.01, repeat_penalty=1.3, repeat_last_n=4, seed=99)
     host = Sampler(sp)
     tok_h, tok_d, ids = prompt[-1], prompt[-1], list(prompt[:-1])
-    agree = 0
+    agree = n_drawn = 0
     for i in range(6):
         pos = len(ids)
         recent = (ids + [tok_h])[-4:]
         res_h = eng.step([(0, tok_h, pos)], want_logits=True)
         pick_h = host.sample(res_h[0][1], recent)
-        res_d = eng.step([(1, tok_d, pos)], want_logits=False, sampling=[(sp, i, recent)])
+        spec_d = [sp, n_drawn, recent]
+        res_d = eng.step([(1, tok_d, pos)], want_logits=False, sampling=[spec_d])
+        n_drawn = spec_d[1]
         assert res_d[0][1] is None
         agree += int(res_d[0][0] == pick_h)
         ids.append(tok_h)

@@ -262,3 +262,60 @@ def test_cpu_engine_serves_a_gguf_file(tmp_path):
     finally:
         proc.terminate()
         proc.wait(timeout=20)
+
+
+def test_worker_hands_sampling_to_an_engine_that_samples_itself():
+    """An engine with ``device_sampling`` gets the request's chain, draw number and recent window with the rows and
+    returns the sampled id; the host sampler is not consulted and no logits are asked for.  Requests that need the
+    logits on the host (logit_bias, n_probs, constraints) stay on the host chain."""
+    from bloomery_b200.serve.sampler import Sampler
+
+    class SelfSampling(MockEngine):
+        device_sampling = True
+
+        def __init__(self, *a, **k):
+            super().__init__(*a, **k)
+            self.seen = []
+
+        def step(self, rows, want_logits=True, sampling=None):
+            res = super().step(rows, want_logits=True)
+            out = []
+            for i, (tok, lg) in enumerate(res):
+                sp = sampling[i] if sampling is not None else None
+                if sp is not None:
+                    params, n_drawn, recent = sp
+                    self.seen.append((n_drawn, list(recent), want_logits))
+                    s = Sampler(params)
+                    for _ in range(n_drawn):                 # replay the stream up to this draw
+                        s.rng.next_f64()
+                    used = [0]
+                    real = s.rng.next_f64
+                    s.rng.next_f64 = lambda: (used.__setitem__(0, used[0] + 1), real())[1]
+                    out.append((s.sample(lg, recent), None))
+                    sp[1] = n_drawn + used[0]                # a token with one surviving candidate draws nothing
+                else:
+                    out.append((tok, lg if want_logits else None))
+            return out
+
+    def run(engine, body):
+        s = Server(flags.parse(["--port", "0", "--mock"]))
+        s.start()
+        s.ready(engine, ChatTemplate(), 0)
+        code, r = call(s, "/completion", body)
+        s.state.stop_event.set()
+        s.stop()
+        assert code == 200, r
+        return r
+
+    body = {"prompt": "hello hello hello", "temperature": 0.9, "top_k": 20, "seed": 7, "n_predict": 12, "repeat_penalty": 1.2,
+            "repeat_last_n": 8}
+    eng = SelfSampling(n_slots=1, slot_ctx=512)
+    on_card = run(eng, body)
+    on_host = run(MockEngine(n_slots=1, slot_ctx=512), body)
+    assert on_card["content"] == on_host["content"]                       # same chain, same seed, same draws
+    ds = [d for d, _, _ in eng.seen]
+    assert ds == sorted(ds) and ds[0] == 0 and len(ds) >= 1
+    assert all(len(r) <= 8 for _, r, _ in eng.seen) and not any(w for _, _, w in eng.seen)
+    eng2 = SelfSampling(n_slots=1, slot_ctx=512)
+    run(eng2, dict(body, n_probs=2))
+    assert eng2.seen == []                                                # top-probabilities need the host's logits
