@@ -353,17 +353,6 @@ __global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a)
   const long rb = resident_row_bytes(a.gtype, K);
   const int8_t* xq = a.xq + (long)m * K;
   const float2* xds = a.xds + (long)m * (K / 32);
-  {
-    // the second half's four rows: ask L2 for them now, so their loads (issued after the first half's round trip
-    // to HBM) find them on the way instead of starting a second round trip
-    const long row1 = (long)e * a.I + chunk * 32 + warp * 4 + 2;
-    const uint8_t* pg = a.gate + row1 * rb;
-    const uint8_t* pu = a.up + row1 * rb;
-    for (long off = (long)lane * 32; off < 2 * rb; off += 1024) {
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(pg + off));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(pu + off));
-    }
-  }
 #pragma unroll 1
   for (int half = 0; half < 2; ++half) {
     const long row0 = (long)e * a.I + chunk * 32 + warp * 4 + half * 2;

@@ -1,7 +1,7 @@
 """Kernel micro-benchmark: each decode / prefill kernel alone at Qwen3-30B-A3B layer shapes, over a
 few layers of random weights, replayed from a CUDA graph and timed with CUDA events.
 
-    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|down|flash|gemm|gemmdist|mla|sampler} [replays]
+    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|flash|gemm|gemmdist|mla|sampler} [replays]
 
 It is also the small workload the ncu summaries under ``profiles/`` were captured on.
 """
@@ -35,6 +35,8 @@ hq = torch.zeros(8, H, dtype=torch.int8, device=dev); hds = torch.zeros(8, H // 
 cnt = torch.zeros(1, dtype=torch.int32, device=dev)
 actq = torch.zeros(8, k, I, dtype=torch.int8, device=dev); actds = torch.zeros(8, k, I // 32, 2, device=dev)
 which = sys.argv[1] if len(sys.argv) > 1 else "all"
+if which == "gateup_ids":
+    ids = torch.stack([torch.randperm(E)[:k] for _ in range(8)]).to(torch.int32).to(dev)
 import math
 n_q, n_kv, hd, ctx = 32, 4, 128, 4096
 n_pages = ctx // 64
@@ -78,6 +80,7 @@ def chain():
         if which in ("all", "o"): K.gemv([l["o"]], M, x, xq=xq, xds=xds, resid=x, fault=fault)
         if which in ("all", "router"): K.router(x, gain, 1e-6, l["r"], M, logits, hq, hds, None, fault, 0)
         if which in ("all", "gateup"): K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0, route_logits=logits, rule=K.RouteRule(k), wts=wts)
+        if which == "gateup_ids": K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0)
         if which in ("all", "flash"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
         if which == "gemm": G.gemm_bf16(A, B, tt, out_bf16=C, status=gst)
         if which == "gemmdist": G.gemm_bf16_dist([A.data_ptr()], 4096, 4096, B, tt, owners=[o.data_ptr() for o in own], rows_per_owner=2048, ldc=2048, status=gst)
