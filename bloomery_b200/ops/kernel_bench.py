@@ -1,7 +1,7 @@
 """Kernel micro-benchmark: each decode / prefill kernel alone at Qwen3-30B-A3B layer shapes, over a
 few layers of random weights, replayed from a CUDA graph and timed with CUDA events.
 
-    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|flash|gemm|gemmdist|mla|sampler} [replays]
+    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|rope|flash|gemm|gemmdist|mla|sampler} [replays]
 
 It is also the small workload the ncu summaries under ``profiles/`` were captured on.
 """
@@ -66,6 +66,11 @@ if which == "mla":
     mml = torch.zeros(8 * mq * mseg * 2, device=dev); macc = torch.zeros(8 * mq * mseg * 512, device=dev)
     mvb = (torch.randn(mq, 128, 512, device=dev) * 0.05).bfloat16()
     moq = torch.zeros(8, mq * 128, dtype=torch.int8, device=dev); mods = torch.zeros(8, mq * 128 // 32, 2, device=dev)
+if which == "rope":
+    r_inv = (1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))).float().to(dev)
+    r_g = torch.ones(hd, device=dev)
+    r_q = torch.zeros(8, n_q, hd, device=dev)
+    qkv.normal_()
 if which == "sampler":
     V = 151936
     slog = torch.randn(1, V, device=dev) * 3
@@ -81,11 +86,17 @@ def chain():
         if which in ("all", "router"): K.router(x, gain, 1e-6, l["r"], M, logits, hq, hds, None, fault, 0)
         if which in ("all", "gateup"): K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0, route_logits=logits, rule=K.RouteRule(k), wts=wts)
         if which == "gateup_ids": K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0)
+        if which == "rope": K.qk_norm_rope_append(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, 1, fpos, fseq, table, n_pages, kc, vc, r_q, fault, 0)
         if which in ("all", "flash"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
         if which == "gemm": G.gemm_bf16(A, B, tt, out_bf16=C, status=gst)
         if which == "gemmdist": G.gemm_bf16_dist([A.data_ptr()], 4096, 4096, B, tt, owners=[o.data_ptr() for o in own], rows_per_owner=2048, ldc=2048, status=gst)
         if which == "mla": K.mla_flash_decode(mqlat, mcache, mpos, mseq, mtable, mctx // 64, mq, 1, mseg, mctx, mml, macc, mvb, 128, None, moq, mods, fault, 0)
-        if which == "sampler": K.sample_rows(slog, V, 1, spar, ssd, sdr, sout, recent=srec, n_recent=snrec, work=swork)
+        if which == "rope":
+    r_inv = (1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))).float().to(dev)
+    r_g = torch.ones(hd, device=dev)
+    r_q = torch.zeros(8, n_q, hd, device=dev)
+    qkv.normal_()
+if which == "sampler": K.sample_rows(slog, V, 1, spar, ssd, sdr, sout, recent=srec, n_recent=snrec, work=swork)
         if which in ("all", "down"): K.down_combine(actq, actds, ids, wts, None, l["d"], E, k, M, x, None, x, fault, 0)
 g = torch.cuda.CUDAGraph()
 s = torch.cuda.Stream()
