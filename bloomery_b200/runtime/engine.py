@@ -93,6 +93,7 @@ class DecodeEngine:
         # pinned staging ring: a slot is rewritten only after the copy that read it has run
         self._stage_n = 16
         self._stage = [torch.zeros(4, R, dtype=torch.int32, pin_memory=True) for _ in range(self._stage_n)]
+        self._stage_np = [t.numpy() for t in self._stage]          # same memory: rows are written without tensor indexing
         self._stage_ev = [None] * self._stage_n
         self._stage_i = 0
         self.params_host = self._stage[0]
@@ -152,6 +153,7 @@ class DecodeEngine:
         self.am_i = torch.zeros(R * self.am_blocks, **i32)
         self.tokens_out = torch.zeros(R + 1, **i32)
         self.tokens_out_host = torch.zeros(R + 1, dtype=torch.int32, pin_memory=True)
+        self._tokens_out_np = self.tokens_out_host.numpy()
         self.fault = torch.full((1,), -1, **i32)  # 0xFFFFFFFF
         self.hist_cap = 4096
         self.hist = torch.zeros(self.hist_cap * R, **i32)
@@ -401,18 +403,22 @@ class DecodeEngine:
         if self._stage_ev[i] is not None:
             self._stage_ev[i].synchronize()
         ph = self.params_host = self._stage[i]
-        ph[2].fill_(-1)
+        hp = self._stage_np[i]
+        hp[2, :] = -1
         self.kv.protect = {r[0] for r in rows}          # slots of this pass never spill
         for r, (slot, tok, pos) in enumerate(rows):
-            ph[0, r], ph[1, r], ph[2, r] = tok, pos, slot
-            ph[3, r] = src[r] if src is not None else r
+            hp[0, r] = tok
+            hp[1, r] = pos
+            hp[2, r] = slot
+            hp[3, r] = src[r] if src is not None else r
             self.kv.ensure(slot, pos + 1)
             self.kv.own(slot, pos)
         self.kv.sync_table()
         self.params.copy_(ph, non_blocking=True)
-        ev = self._stage_ev[i] or torch.cuda.Event()
+        ev = self._stage_ev[i]
+        if ev is None:
+            ev = self._stage_ev[i] = torch.cuda.Event()
         ev.record()
-        self._stage_ev[i] = ev
         return M
 
     def launch(self, M: int, head: bool = True, advance: bool = False) -> None:
@@ -440,7 +446,7 @@ class DecodeEngine:
                 self.watchdog.leave(tok)
             self.waits.add("card", time.monotonic() - t0)
         # the kernel writes the fault copy at index M (the bucket size)
-        return self.tokens_out_host.tolist()
+        return self._tokens_out_np.tolist()
 
     def step(self, rows: Sequence[Tuple[int, int, int]], head: bool = True) -> List[int]:
         """One pass over ``rows``; returns the greedy token of every row."""
