@@ -91,12 +91,7 @@ def chain():
         if which == "gemm": G.gemm_bf16(A, B, tt, out_bf16=C, status=gst)
         if which == "gemmdist": G.gemm_bf16_dist([A.data_ptr()], 4096, 4096, B, tt, owners=[o.data_ptr() for o in own], rows_per_owner=2048, ldc=2048, status=gst)
         if which == "mla": K.mla_flash_decode(mqlat, mcache, mpos, mseq, mtable, mctx // 64, mq, 1, mseg, mctx, mml, macc, mvb, 128, None, moq, mods, fault, 0)
-        if which == "rope":
-    r_inv = (1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))).float().to(dev)
-    r_g = torch.ones(hd, device=dev)
-    r_q = torch.zeros(8, n_q, hd, device=dev)
-    qkv.normal_()
-if which == "sampler": K.sample_rows(slog, V, 1, spar, ssd, sdr, sout, recent=srec, n_recent=snrec, work=swork)
+        if which == "sampler": K.sample_rows(slog, V, 1, spar, ssd, sdr, sout, recent=srec, n_recent=snrec, work=swork)
         if which in ("all", "down"): K.down_combine(actq, actds, ids, wts, None, l["d"], E, k, M, x, None, x, fault, 0)
 g = torch.cuda.CUDAGraph()
 s = torch.cuda.Stream()
