@@ -39,6 +39,8 @@ class GemmPrefill:
         self.launches = 0
         # where a layer's expert stacks come from: the resident weights, or a streamer that brings them from the host
         self.expert_source = None
+        from .timing import PromptTiming
+        self.timing = PromptTiming()            # arm() it to get per-unit milliseconds of the next micro-batch
 
     def _get(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
@@ -120,6 +122,7 @@ class GemmPrefill:
         st = self.status
         for il in range(s.n_layer):
             b = f"blk.{il}."
+            self.timing.mark(il, "ffn")
             G.rmsnorm_bf16(x, w.f[b + "attn_norm.weight"], s.rms_eps, xn)
             G.dequant_bf16(w.q[b + "attn_q.weight"], wqkv[:s.q_rows])
             G.dequant_bf16(w.q[b + "attn_k.weight"], wqkv[s.q_rows:s.q_rows + s.kv_rows])
@@ -131,6 +134,7 @@ class GemmPrefill:
                                           e.fault, il)
             G.kv_gather_bf16(e.kv.k[il], e.kv.v[il], e.kv.table[slot], e.kv.n_pages, s.n_kv, s.head_dim, n_keys, T_pad,
                              Kb, Vt)
+            self.timing.mark(il, "qkv")
             for c0 in range(0, T, Tq_max):
                 Tq = min(Tq_max, T - c0)
                 rows = s.n_q * Tq
@@ -140,8 +144,10 @@ class GemmPrefill:
                 G.gemm_bf16(q_bf.view(s.n_q * T, s.head_dim), Kb, qk_tiles, out_f32=S, dst_row=map_s, status=st)
                 G.softmax_causal(S, rows, Tq, p0 + c0, T_pad, P)
                 G.gemm_bf16(P, Vt, pv_tiles, out_bf16=attn.view(T * s.n_q, s.head_dim), dst_row=map_o, status=st)
+            self.timing.mark(il, "attention")
             G.dequant_bf16(w.q[b + "attn_output.weight"], wo)
             G.gemm_bf16(attn, wo, dense_tiles, out_f32=x, resid=x, status=st)
+            self.timing.mark(il, "o_proj")
             if s.layer_is_moe(il):
                 rw = w.q[b + "ffn_gate_inp.weight"]
                 if rw.qtype == "F32" and T >= 128 and E % 32 == 0:

@@ -280,3 +280,25 @@ def test_kv_pool_spills_idle_slots_to_the_host_and_brings_them_back():
         kv.ensure(0, 3 * PAGE)
     kv.release(2)
     kv.ensure(0, 2 * PAGE)
+
+
+def test_host_profile_levels_and_heat_files(tmp_path):
+    import torch
+    from bloomery_b200.runtime.timing import HostProfile, PromptTiming, load_heat, save_heat
+    off, one, two = HostProfile(0), HostProfile(1), HostProfile(2)
+    for p in (off, one, two):
+        with p.span("matmul"):
+            pass
+        with p.span("rows", detail=True):
+            pass
+    assert off.report() == {} and set(one.report()) == {"matmul"} and set(two.report()) == {"matmul", "rows"}
+    assert one.report()["matmul"]["calls"] == 1
+    t = PromptTiming()
+    t.mark(0, "qkv")                              # not armed: nothing is kept, no CUDA needed
+    assert t.marks == [] and t.report() == {}
+    heat = torch.tensor([[1, 0, 5], [2, 2, 2]])
+    path = str(tmp_path / "heat.json")
+    save_heat(heat, path, model="m")
+    assert load_heat(path, 2, 3, model="m") == [[1, 0, 5], [2, 2, 2]]
+    assert load_heat(path, 2, 4) is None and load_heat(path, 2, 3, model="other") is None
+    assert load_heat(str(tmp_path / "none.json"), 2, 3) is None
