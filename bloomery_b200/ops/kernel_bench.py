@@ -1,7 +1,7 @@
 """Kernel micro-benchmark: each decode / prefill kernel alone at Qwen3-30B-A3B layer shapes, over a
 few layers of random weights, replayed from a CUDA graph and timed with CUDA events.
 
-    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|rope|flash|gemm|gemmdist|mla|sampler} [replays]
+    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|rope|flash|gemm|gemmdist|mla|sampler|gap} [replays]
 
 It is also the small workload the ncu summaries under ``profiles/`` were captured on.
 """
@@ -91,6 +91,8 @@ def chain():
         if which == "gemm": G.gemm_bf16(A, B, tt, out_bf16=C, status=gst)
         if which == "gemmdist": G.gemm_bf16_dist([A.data_ptr()], 4096, 4096, B, tt, owners=[o.data_ptr() for o in own], rows_per_owner=2048, ldc=2048, status=gst)
         if which == "mla": K.mla_flash_decode(mqlat, mcache, mpos, mseq, mtable, mctx // 64, mq, 1, mseg, mctx, mml, macc, mvb, 128, None, moq, mods, fault, 0)
+        if which == "gap":
+            for _ in range(8): K.fill_u32(cnt, 0)           # eight empty nodes: the number printed is 8 node gaps
         if which == "sampler": K.sample_rows(slog, V, 1, spar, ssd, sdr, sout, recent=srec, n_recent=snrec, work=swork)
         if which in ("all", "down"): K.down_combine(actq, actds, ids, wts, None, l["d"], E, k, M, x, None, x, fault, 0)
 g = torch.cuda.CUDAGraph()
