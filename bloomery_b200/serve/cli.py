@@ -46,6 +46,21 @@ def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, fre
         dev_free = min(free_bytes[d] for d in pl.devices)
         share = weights_bytes // (len(pl.devices) if pl.mode == "tp" else 1)
         room = dev_free - margin - share - (2 << 30)
+        if room <= 0 and pl.host_experts == "none" and pl.fit and spec.is_moe:
+            # -fit on: keep as many routed experts per layer on the card as fit, the rest on the host
+            expert_bytes = weights_bytes * 0.9 if not opts.get("_expert_bytes") else opts["_expert_bytes"]
+            trunk = weights_bytes - int(expert_bytes)
+            ctx_ask = asked or 4096 * n_slots
+            left = dev_free - margin - (2 << 30) - trunk - ctx_ask * per_tok
+            n_moe = max(1, spec.n_layer - spec.first_dense)
+            per_slot = int(expert_bytes) // max(1, spec.n_expert) // 1 if n_moe else 0      # one expert slot in every layer
+            fit_slots = max(0, left) // max(1, per_slot)
+            resident = max(0, (int(fit_slots) - 1)) // 4 * 4
+            if trunk + ctx_ask * per_tok + margin + (2 << 30) > dev_free:
+                raise Refusal(Code.NO_FIT, f"the trunk of {trunk >> 20} MiB does not fit {dev_free >> 20} MiB even with every "
+                                           f"routed expert on the host")
+            pl.host_experts = f"fit:{min(resident, spec.n_expert)}"
+            room = left - resident * per_slot + ctx_ask * per_tok      # what the context may use
         if room <= 0 and pl.host_experts == "none":
             raise Refusal(Code.NO_FIT, f"weights of {share >> 20} MiB per GPU do not fit {dev_free >> 20} MiB free "
                                        f"(margin {margin >> 20} MiB); try --cpu-moe or more devices")
@@ -93,6 +108,22 @@ def _inventory(path: str):
         raise Refusal(Code.UNSUPPORTED, str(exc)) from None
 
 
+def _expert_bytes(path: str, kind: str) -> int:
+    """Bytes of the routed-expert tensors of a model file (what may live on the host)."""
+    try:
+        if kind == "gguf":
+            from ..formats.gguf import Gguf
+            inv = Gguf.inventory(path)
+            return sum(t.n_bytes for n, t in inv.tensors.items() if "_exps." in n)
+        from ..formats.safetensors import Folder
+        f = Folder(path)
+        n = sum(f.info(t).end - f.info(t).begin for t in f.names() if ".mlp.experts." in t)
+        f.close()
+        return n
+    except Exception:  # noqa: BLE001 - the plan falls back to its own estimate
+        return 0
+
+
 def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional[str]):
     """Plan, load and build the engine the flags ask for: one GPU, several GPUs in lockstep, experts on the
     host beside a GPU, or the CPU alone.  Returns (engine, chat template source, bos text, eos text)."""
@@ -101,6 +132,7 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
     path = opts["model"]
     spec, weights_bytes, kind = _inventory(path)
     free = [torch.cuda.mem_get_info(i)[0] for i in range(n_vis)]
+    opts["_expert_bytes"] = _expert_bytes(path, kind)
     plan = plan_for(opts, spec, weights_bytes, n_vis, free)
     pl = plan["placement"]
     opts["_place_word"] = pl.word()
@@ -172,6 +204,8 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
             from ..runtime.tiered import TieredEngine
             if pl.host_experts == "all":
                 resident = 0
+            elif pl.host_experts.startswith("fit:"):
+                resident = int(pl.host_experts.split(":")[1])
             elif pl.host_experts.startswith("first:"):
                 n_host_layers = min(spec.n_layer, int(pl.host_experts.split(":")[1]))
                 resident = spec.n_expert * (spec.n_layer - n_host_layers) // spec.n_layer // 4 * 4

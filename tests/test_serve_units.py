@@ -271,3 +271,24 @@ def test_ngram_draft_and_width_chooser():
         w2.observe_pass(1, 1.0); w2.observe_pass(2, 1.9); w2.observe_pass(5, 4.5)
         w2.observe_accept(4, 0)
     assert w2.choose(4) == 0                             # nothing is ever accepted: plain steps
+
+
+def test_fit_on_keeps_what_fits_on_the_card():
+    """``-fit on`` on a card too small for the model: the plan keeps a multiple of four expert slots per layer on the
+    card and the rest on the host; without it the same ask is refused; a trunk that does not fit is refused either way."""
+    from bloomery_b200.models.spec import qwen3_30b_a3b
+    from bloomery_b200.serve.cli import plan_for
+    from bloomery_b200.utils.exit_codes import Refusal
+    spec = qwen3_30b_a3b()
+    opts = flags.parse(["-m", "x", "-fit", "on", "-np", "1", "-c", "8192"], {})
+    opts["_expert_bytes"] = 16_000_000_000
+    plan = plan_for(opts, spec, 17_500_000_000, 1, [12 << 30])
+    word = plan["placement"].host_experts
+    assert word.startswith("fit:") and 0 < int(word.split(":")[1]) < spec.n_expert and int(word.split(":")[1]) % 4 == 0
+    assert plan["slot_ctx"] == 8192
+    with pytest.raises(Refusal):
+        plan_for(flags.parse(["-m", "x", "-np", "1", "-c", "8192"], {}), spec, 17_500_000_000, 1, [12 << 30])
+    opts2 = flags.parse(["-m", "x", "-fit", "on", "-np", "1"], {})
+    opts2["_expert_bytes"] = 16_000_000_000
+    with pytest.raises(Refusal):
+        plan_for(opts2, spec, 17_500_000_000, 1, [3 << 30])
