@@ -130,6 +130,9 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
     import torch
     from .engine import CpuEngine, GpuEngine
     path = opts["model"]
+    for flag, key in (("-ctk", "cache_type_k"), ("-ctv", "cache_type_v")):
+        if str(opts.get(key) or "f16").lower() not in ("f16", "fp16"):
+            raise Refusal(Code.USAGE, f"{flag} {opts[key]}: the KV cache is f16 in this build (the attention kernels read f16 rows)")
     spec, weights_bytes, kind = _inventory(path)
     free = [torch.cuda.mem_get_info(i)[0] for i in range(n_vis)]
     opts["_expert_bytes"] = _expert_bytes(path, kind)

@@ -292,3 +292,25 @@ def test_fit_on_keeps_what_fits_on_the_card():
     opts2["_expert_bytes"] = 16_000_000_000
     with pytest.raises(Refusal):
         plan_for(opts2, spec, 17_500_000_000, 1, [3 << 30])
+
+
+def test_reference_sets_carry_the_model_identity(tmp_path):
+    from bloomery_b200.models import weights as W
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.utils import refset as R
+    spec = tiny_qwen3moe()
+    spec.vocab, spec.n_layer = 256, 1
+    a, b = str(tmp_path / "a.gguf"), str(tmp_path / "b.gguf")
+    W.write_gguf(spec, W.synth_tensors(spec, "cpu", seed=1), a)
+    W.write_gguf(spec, W.synth_tensors(spec, "cpu", seed=2), b)
+    out = str(tmp_path / "set.json")
+    assert R.main(["make", a, out, "--cases", "2", "--prompt-len", "6", "--new", "4"]) == 0
+    doc = R.read(out)
+    assert len(doc["cases"]) == 2 and len(doc["cases"][0]["greedy"]) == 4 and doc["arch"] == "qwen3moe"
+    assert R.main(["check", a, out, "--min-agree", "1.0"]) == 0
+    assert R.main(["check", b, out]) == 1                      # another model file: refused before any token is compared
+    agree, total = R.check(doc, a, lambda p, n: [doc["cases"][0]["greedy"][0]] + [0] * (n - 1), min_agree=0.0)
+    assert total == 8 and agree <= 5
+    open(out, "w").write("{}")
+    with pytest.raises(R.RefsetError):
+        R.read(out)
