@@ -249,6 +249,178 @@ __global__ void __launch_bounds__(256) flash_decode_seg_kernel(const FlashArgs a
   }
 }
 
+
+// ------------------------------------------------------------------------------------
+// The same segment pass on warp-level tensor-core tiles (opt-in: bl_set_flash_mma).
+// One block = one KV head x one key segment; its G <= 16 query heads are the M dimension of
+// m16n8k16 f16 tiles (rows past G are zero):
+//   scores  S[16 x 32] = Q[16 x HEAD] K^T    warps (w, w + 4) share key columns 8(w & 3).., each half of the depth
+//   softmax            warp w owns head rows 2w, 2w + 1
+//   values  O[16 x HEAD] += P[16 x 32] V     warp w owns output columns (HEAD / 8) w ..
+// K and V rows are f16 in the cache already and feed the tensor cores as they arrive.
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ void fa_mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void fa_ldmatrix_x2_trans(uint32_t (&r)[2], const void* smem_row) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+
+template <int HEAD>
+__global__ void __launch_bounds__(256, 2) flash_decode_seg_mma_kernel(const FlashArgs a) {
+  constexpr int STR = HEAD + 8;                  // f16 row stride of q, K and V tiles: fragment loads do not collide
+  constexpr int KS = HEAD / 16;                  // k-steps of the score product
+  constexpr int NT = HEAD / 64;                  // 8-column output tiles per warp in the value product
+  constexpr int PSTR = 40, SSTR = 33;
+  extern __shared__ __align__(16) uint8_t smem[];
+  __half* sq = reinterpret_cast<__half*>(smem);                         // [16][STR]
+  __half* sk = sq + 16 * STR;                                           // [2][32][STR]
+  __half* sv = sk + 2 * kKeyTile * STR;                                 // [2][32][STR]
+  float* ss = reinterpret_cast<float*>(sv + 2 * kKeyTile * STR);       // [16][33]
+  float* spart = ss + 16 * SSTR;                                        // [4][16][8]
+  __half* sp = reinterpret_cast<__half*>(spart + 512);                  // [16][40]
+  float* scorr = reinterpret_cast<float*>(sp + 16 * PSTR);              // [16]
+  const int G = a.n_q / a.n_kv;
+  const int seg = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  pdl_wait();
+  pdl_launch();
+  const int seq = a.row_seq[m];
+  if (seq < 0) return;
+  const int n_keys = a.row_pos[m] + 1;
+  const bool bad = n_keys <= 0 || n_keys > a.ctx_limit;
+  if (bad && tid == 0 && seg == 0 && kvh == 0) raise_fault(a.fault, a.layer, FS_KEY_COUNT);
+  const int n_tiles = bad ? 0 : (n_keys + kKeyTile - 1) / kKeyTile;
+  const int tps = (n_tiles + a.n_seg - 1) / a.n_seg;
+  const int t0 = seg * tps, t1 = min(n_tiles, t0 + tps);
+  if (!bad && t0 >= t1) return;
+  for (int i = tid; i < 16 * HEAD; i += 256) {
+    const int r = i / HEAD, c = i - r * HEAD;
+    sq[r * STR + c] = __float2half_rn(r < G ? a.q[((long)m * a.n_q + (long)kvh * G + r) * HEAD + c] : 0.f);
+  }
+  const int* bt = a.block_table + (long)seq * a.max_pages;
+  auto issue_tile = [&](int tl, int stage) {
+    const int key0 = tl * kKeyTile;
+    int page = bt[key0 / kPage];
+    page = (page < 0 || page >= a.n_pages) ? 0 : page;
+    const long base = (((long)page * a.n_kv + kvh) * kPage + (key0 % kPage)) * HEAD;
+    constexpr int CH = HEAD / 8;
+    for (int c = tid; c < kKeyTile * CH; c += 256) {
+      const int r = c / CH, cc = c % CH;
+      cp_async16(sk + ((size_t)stage * kKeyTile + r) * STR + cc * 8, a.k_cache + base + (long)r * HEAD + cc * 8);
+      cp_async16(sv + ((size_t)stage * kKeyTile + r) * STR + cc * 8, a.v_cache + base + (long)r * HEAD + cc * 8);
+    }
+    cp_async_commit();
+  };
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+  float mx[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  if (t0 < t1) issue_tile(t0, 0);
+  for (int tl = t0; tl < t1; ++tl) {
+    const int stage = (tl - t0) & 1;
+    if (tl + 1 < t1) { issue_tile(tl + 1, stage ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const __half* kt = sk + (size_t)stage * kKeyTile * STR;
+    __half* vt = sv + (size_t)stage * kKeyTile * STR;
+    const int kmax = min(kKeyTile, n_keys - tl * kKeyTile);
+    if (kmax < kKeyTile) {                        // value rows past the last key: weight 0, keep 0 * x finite
+      for (int i = tid; i < (kKeyTile - kmax) * (STR / 2); i += 256) reinterpret_cast<uint32_t*>(vt + (size_t)kmax * STR)[i] = 0u;
+      __syncthreads();
+    }
+    {
+      const int nt = warp & 3, kh = warp >> 2;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const __half* qa = sq + g * STR + 2 * t;
+      const __half* kb = kt + (size_t)(nt * 8 + g) * STR + 2 * t;
+#pragma unroll
+      for (int ks = kh * (KS / 2); ks < (kh + 1) * (KS / 2); ++ks) {
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qa + ks * 16);
+        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qa + 8 * STR + ks * 16);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qa + ks * 16 + 8);
+        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qa + 8 * STR + ks * 16 + 8);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + ks * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + ks * 16 + 8);
+        fa_mma_16816(c, a0, a1, a2, a3, b0, b1);
+      }
+      if (kh == 1) {
+        float* o = spart + nt * 128;
+        o[g * 8 + 2 * t] = c[0]; o[g * 8 + 2 * t + 1] = c[1]; o[(g + 8) * 8 + 2 * t] = c[2]; o[(g + 8) * 8 + 2 * t + 1] = c[3];
+      }
+      __syncthreads();
+      if (kh == 0) {
+        const float* o = spart + nt * 128;
+        const int col = nt * 8 + 2 * t;
+        const bool m0 = col < kmax, m1 = col + 1 < kmax;
+        ss[g * SSTR + col] = m0 ? c[0] + o[g * 8 + 2 * t] : -INFINITY;
+        ss[g * SSTR + col + 1] = m1 ? c[1] + o[g * 8 + 2 * t + 1] : -INFINITY;
+        ss[(g + 8) * SSTR + col] = m0 ? c[2] + o[(g + 8) * 8 + 2 * t] : -INFINITY;
+        ss[(g + 8) * SSTR + col + 1] = m1 ? c[3] + o[(g + 8) * 8 + 2 * t + 1] : -INFINITY;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = 2 * warp + h;
+      const float sc = ss[r * SSTR + lane];
+      const float nm = fmaxf(mx[h], warp_max(sc));
+      const float corr = (mx[h] == -INFINITY) ? 0.f : __expf(mx[h] - nm);
+      const float pr = (sc == -INFINITY) ? 0.f : __expf(sc - nm);
+      l[h] = l[h] * corr + warp_sum(pr);
+      mx[h] = nm;
+      sp[r * PSTR + lane] = __float2half_rn(pr);
+      if (lane == 0) scorr[r] = corr;
+    }
+    __syncthreads();
+    {
+      const float c_lo = scorr[g], c_hi = scorr[g + 8];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) { acc[j][0] *= c_lo; acc[j][1] *= c_lo; acc[j][2] *= c_hi; acc[j][3] *= c_hi; }
+      const __half* pa = sp + g * PSTR + 2 * t;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(pa + ks * 16);
+        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(pa + 8 * PSTR + ks * 16);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(pa + ks * 16 + 8);
+        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(pa + 8 * PSTR + ks * 16 + 8);
+        // lanes 0..15 address the 16 key rows of this k-step (matrix 0: rows 0..7, matrix 1: rows 8..15)
+        const __half* vrow = vt + (size_t)(ks * 16 + (lane & 15)) * STR + (HEAD / 8) * warp;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          uint32_t b[2];
+          fa_ldmatrix_x2_trans(b, vrow + j * 8);
+          fa_mma_16816(acc[j], a0, a1, a2, a3, b[0], b[1]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = 2 * warp + h;
+    if (r < G && lane == 0) {
+      const long pidx = ((long)m * a.n_q + (long)kvh * G + r) * a.n_seg + seg;
+      a.part_ml[pidx * 2] = bad ? __int_as_float(0x7fc00000) : mx[h];
+      a.part_ml[pidx * 2 + 1] = l[h];
+    }
+  }
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int r = g + 8 * hh;
+    if (r < G) {
+      const long pidx = ((long)m * a.n_q + (long)kvh * G + r) * a.n_seg + seg;
+      float* o = a.part_acc + pidx * HEAD + (HEAD / 8) * warp + 2 * t;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) *reinterpret_cast<float2*>(o + 8 * j) = make_float2(acc[j][2 * hh], acc[j][2 * hh + 1]);
+    }
+  }
+}
+
+int g_flash_mma = 0;
+
 struct MergeArgs {
   const float* part_ml;
   const float* part_acc;
@@ -339,6 +511,9 @@ int bl_qk_norm_rope_append_prefill(const float* qkv, long qkv_stride, const floa
   return (int)launch(qk_norm_rope_append_kernel<64>, grid, dim3(32), 0, st, a);
 }
 
+// 1: the segment pass runs on tensor-core tiles (flash_decode_seg_mma_kernel); 0: the fp32 kernel
+void bl_set_flash_mma(int on) { bl::g_flash_mma = on ? 1 : 0; }
+
 // Scratch: part_ml [M*n_q*n_seg*2] and part_acc [M*n_q*n_seg*head] floats, caller-owned.
 int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, const int* row_pos, const int* row_seq,
                     const int* block_table, int max_pages, int n_pages, int head, int n_q, int n_kv, int M, int n_seg,
@@ -353,7 +528,17 @@ int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, co
   dim3 grid(n_seg, n_kv, M);
   size_t smem = (size_t)G * head * 4 + 2 * kKeyTile * (head + 8) * 2 + 2 * kKeyTile * head * 2;
   cudaError_t e;
-  if (head == 128) {
+  if (g_flash_mma) {
+    const size_t sm2 = (size_t)(16 + 4 * kKeyTile) * (head + 8) * 2 + (16 * 33 + 512) * 4 + 16 * 40 * 2 + 64;
+    static bool set128 = false, set64 = false;
+    if (head == 128) {
+      if (!set128) { cudaFuncSetAttribute(flash_decode_seg_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2); set128 = true; }
+      e = launch(flash_decode_seg_mma_kernel<128>, grid, dim3(256), sm2, st, a);
+    } else {
+      if (!set64) { cudaFuncSetAttribute(flash_decode_seg_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2); set64 = true; }
+      e = launch(flash_decode_seg_mma_kernel<64>, grid, dim3(256), sm2, st, a);
+    }
+  } else if (head == 128) {
     if (G <= 8) e = launch(flash_decode_seg_kernel<128, 1>, grid, dim3(256), smem, st, a);
     else {
       cudaFuncSetAttribute(flash_decode_seg_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);

@@ -110,6 +110,11 @@ def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torc
     check(rc, "bl_gemv")
 
 
+def set_flash_mma(on: bool) -> None:
+    """Run the GQA decode segment pass on tensor-core tiles (f16 q and probabilities) instead of fp32 FMAs."""
+    cuda().bl_set_flash_mma(I(1 if on else 0))
+
+
 def qk_norm_rope_append(qkv: torch.Tensor, q_gain, k_gain, inv_freq: torch.Tensor, eps: float, q_scale: float,
                         head: int, n_q: int, n_kv: int, M: int, row_pos, row_seq, block_table, n_pages: int,
                         k_cache, v_cache, q_out, fault, layer: int) -> None:

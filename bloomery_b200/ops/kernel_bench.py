@@ -1,7 +1,7 @@
 """Kernel micro-benchmark: each decode / prefill kernel alone at Qwen3-30B-A3B layer shapes, over a
 few layers of random weights, replayed from a CUDA graph and timed with CUDA events.
 
-    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|rope|flash|gemm|gemmdist|mla|sampler|gap} [replays]
+    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|rope|flash|gemm|gemmdist|mla|sampler|gap|flash_mma} [replays]
 
 It is also the small workload the ncu summaries under ``profiles/`` were captured on.
 """
@@ -78,6 +78,8 @@ if which == "sampler":
     ssd = torch.tensor([1234], dtype=torch.int64, device=dev); sdr = torch.zeros(1, dtype=torch.int64, device=dev)
     srec = torch.randint(0, V, (1, 64), dtype=torch.int32, device=dev); snrec = torch.tensor([64], dtype=torch.int32, device=dev)
     swork = torch.zeros(1, V, device=dev); sout = torch.zeros(1, dtype=torch.int32, device=dev)
+if which == "flash_mma":
+    K.set_flash_mma(True)
 reps = int(sys.argv[2]) if len(sys.argv) > 2 else 4
 def chain():
     for l in layers:
@@ -87,7 +89,7 @@ def chain():
         if which in ("all", "gateup"): K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0, route_logits=logits, rule=K.RouteRule(k), wts=wts)
         if which == "gateup_ids": K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0)
         if which == "rope": K.qk_norm_rope_append(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, 1, fpos, fseq, table, n_pages, kc, vc, r_q, fault, 0)
-        if which in ("all", "flash"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
+        if which in ("all", "flash", "flash_mma"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
         if which == "gemm": G.gemm_bf16(A, B, tt, out_bf16=C, status=gst)
         if which == "gemmdist": G.gemm_bf16_dist([A.data_ptr()], 4096, 4096, B, tt, owners=[o.data_ptr() for o in own], rows_per_owner=2048, ldc=2048, status=gst)
         if which == "mla": K.mla_flash_decode(mqlat, mcache, mpos, mseq, mtable, mctx // 64, mq, 1, mseg, mctx, mml, macc, mvb, 128, None, moq, mods, fault, 0)

@@ -269,6 +269,20 @@ def test_rope_append_flash_decode(head, n_q, n_kv):
     c, ds = Q.quantize_act_q8(out.cpu())
     assert (outq.cpu() != c).float().mean() < 1e-3
     assert int(fault) == -1
+    # the tensor-tile variant of the segment pass (f16 q and probabilities): same result within the f16 band
+    out_mma = torch.zeros_like(out)
+    K.set_flash_mma(True)
+    try:
+        for _ in range(2):
+            K.flash_decode(q_out, kc_d, vc_d, d(pos), d(seq), d(table), n_pages, head, n_q, n_kv, M, n_seg, ctx, part_ml,
+                           part_acc, out_mma, outq, outds, fault, 0)
+    finally:
+        K.set_flash_mma(False)
+    scale = out.abs().max().item()
+    assert ((out_mma - out).abs().max().item()) < 5e-3 * max(scale, 1.0), (out_mma - out).abs().max()
+    assert int(fault) == -1
+    K.flash_decode(q_out, kc_d, vc_d, d(pos), d(seq), d(table), n_pages, head, n_q, n_kv, M, n_seg, ctx, part_ml,
+                   part_acc, out, outq, outds, fault, 0)
     # a key count beyond the context is a fault and NaN, not a trap
     bad = pos.clone(); bad[1] = ctx + 5
     K.flash_decode(q_out, kc_d, vc_d, d(bad), d(seq), d(table), n_pages, head, n_q, n_kv, M, n_seg, ctx, part_ml,
