@@ -1,7 +1,7 @@
 """Kernel micro-benchmark: each decode / prefill kernel alone at Qwen3-30B-A3B layer shapes, over a
 few layers of random weights, replayed from a CUDA graph and timed with CUDA events.
 
-    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|rope|flash|gemm|gemmdist|mla|sampler|gap|flash_mma} [replays]
+    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|rope|flash|gemm|gemmdist|mla|sampler|gap|flash_mma} [replays] [context]
 
 It is also the small workload the ncu summaries under ``profiles/`` were captured on.
 """
@@ -38,7 +38,7 @@ which = sys.argv[1] if len(sys.argv) > 1 else "all"
 if which == "gateup_ids":
     ids = torch.stack([torch.randperm(E)[:k] for _ in range(8)]).to(torch.int32).to(dev)
 import math
-n_q, n_kv, hd, ctx = 32, 4, 128, 4096
+n_q, n_kv, hd, ctx = 32, 4, 128, (int(sys.argv[3]) if len(sys.argv) > 3 else 4096)
 n_pages = ctx // 64
 kc = torch.randn(n_pages, n_kv, 64, hd, device=dev).half(); vc = torch.randn(n_pages, n_kv, 64, hd, device=dev).half()
 table = torch.arange(n_pages, dtype=torch.int32, device=dev)[None].contiguous()
