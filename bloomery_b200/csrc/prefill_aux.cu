@@ -7,53 +7,83 @@
 
 namespace bl {
 
+__device__ __forceinline__ uint4 pack8_bf16(const float* v) {
+  uint4 o;
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+  o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+  o.z = *reinterpret_cast<uint32_t*>(&c); o.w = *reinterpret_cast<uint32_t*>(&d);
+  return o;
+}
+
+// Units in row-major order are also in output order (64 u + e for every type but Q6_K), so a warp's 32 units are
+// 4 KiB of contiguous output: each lane parks its 128 bytes in shared memory and the warp writes them back as
+// full 512-byte rows.  Q6_K units own four separate runs of 16 values: those go out as 32-byte pieces.
 template <class T>
-__device__ __forceinline__ void expand_units(const uint8_t* w, long rows, int K, __nv_bfloat16* out) {
+__device__ __forceinline__ void expand_units(const uint8_t* w, long rows, int K, __nv_bfloat16* out, uint4 (*stage)[9]) {
   using U = Unit<T>;
   const int upr = K / 64;
   const long total = rows * upr;
   const long rb = resident_row_bytes(T::kType, K);
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-    const long r = i / upr;
-    const int u = (int)(i - r * upr);
-    typename U::Regs regs;
-    U::loadu(w + r * rb, u, K, regs);
+  const int lane = threadIdx.x & 31;
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (long base = (long)blockIdx.x * blockDim.x + (threadIdx.x & ~31); base < total; base += stride) {
+    const long i = base + lane;
     float v[64];
-    U::decodeu(regs, u, v);
-    __nv_bfloat16* o = out + r * K;
+    long r = 0;
+    int u = 0;
+    if (i < total) {
+      r = i / upr;
+      u = (int)(i - r * upr);
+      typename U::Regs regs;
+      U::loadu(w + r * rb, u, K, regs);
+      U::decodeu(regs, u, v);
+    }
     if (T::kType == WT_Q6_K) {
+      if (i < total) {
+        __nv_bfloat16* o = out + r * K;
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const int p0 = U::pos(u, 16 * g);
-#pragma unroll
-        for (int e = 0; e < 16; e += 2)
-          *reinterpret_cast<__nv_bfloat162*>(o + p0 + e) = __floats2bfloat162_rn(v[16 * g + e], v[16 * g + e + 1]);
+        for (int g = 0; g < 4; ++g) {
+          uint4* dst = reinterpret_cast<uint4*>(o + U::pos(u, 16 * g));
+          dst[0] = pack8_bf16(v + 16 * g);
+          dst[1] = pack8_bf16(v + 16 * g + 8);
+        }
       }
     } else {
-      const int p0 = 64 * u;
+      if (i < total) {
 #pragma unroll
-      for (int e = 0; e < 64; e += 2)
-        *reinterpret_cast<__nv_bfloat162*>(o + p0 + e) = __floats2bfloat162_rn(v[e], v[e + 1]);
+        for (int j = 0; j < 8; ++j) stage[lane][j] = pack8_bf16(v + 8 * j);
+      }
+      __syncwarp();
+      uint4* o = reinterpret_cast<uint4*>(out + base * 64);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int idx = j * 32 + lane, uu = idx >> 3;
+        if (base + uu < total) o[idx] = stage[uu][idx & 7];
+      }
+      __syncwarp();
     }
   }
 }
 
 __global__ void __launch_bounds__(256) dequant_bf16_kernel(const uint8_t* w, int wtype, long rows, int K, __nv_bfloat16* out) {
+  __shared__ uint4 s_stage[8][32][9];
+  uint4 (*stage)[9] = s_stage[threadIdx.x >> 5];
   pdl_wait();
   pdl_launch();
   switch (wtype) {
-    case WT_Q4_K: expand_units<Q4K>(w, rows, K, out); break;
-    case WT_Q5_K: expand_units<Q5K>(w, rows, K, out); break;
-    case WT_Q6_K: expand_units<Q6K>(w, rows, K, out); break;
-    case WT_Q8_0: expand_units<Q80>(w, rows, K, out); break;
-    case WT_NVFP4: expand_units<NvFp4>(w, rows, K, out); break;
-    case WT_FP8_B128: expand_units<Fp8B128>(w, rows, K, out); break;
-    case WT_Q2_K: expand_units<Q2K>(w, rows, K, out); break;
-    case WT_Q3_K: expand_units<Q3K>(w, rows, K, out); break;
-    case WT_Q4_0: expand_units<Q40>(w, rows, K, out); break;
-    case WT_Q4_1: expand_units<Q41>(w, rows, K, out); break;
-    case WT_Q5_0: expand_units<Q50>(w, rows, K, out); break;
-    case WT_Q5_1: expand_units<Q51>(w, rows, K, out); break;
+    case WT_Q4_K: expand_units<Q4K>(w, rows, K, out, stage); break;
+    case WT_Q5_K: expand_units<Q5K>(w, rows, K, out, stage); break;
+    case WT_Q6_K: expand_units<Q6K>(w, rows, K, out, stage); break;
+    case WT_Q8_0: expand_units<Q80>(w, rows, K, out, stage); break;
+    case WT_NVFP4: expand_units<NvFp4>(w, rows, K, out, stage); break;
+    case WT_FP8_B128: expand_units<Fp8B128>(w, rows, K, out, stage); break;
+    case WT_Q2_K: expand_units<Q2K>(w, rows, K, out, stage); break;
+    case WT_Q3_K: expand_units<Q3K>(w, rows, K, out, stage); break;
+    case WT_Q4_0: expand_units<Q40>(w, rows, K, out, stage); break;
+    case WT_Q4_1: expand_units<Q41>(w, rows, K, out, stage); break;
+    case WT_Q5_0: expand_units<Q50>(w, rows, K, out, stage); break;
+    case WT_Q5_1: expand_units<Q51>(w, rows, K, out, stage); break;
     default: {
       const long total = rows * (long)K;
       for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {

@@ -161,21 +161,27 @@ class GemmPrefill:
                 else:
                     K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, rw, T, logits, None, None, None, e.fault, il)
                 K.route_rows(logits, e._rule(il), T, ids, wts, e.heat[il], e.fault, il)
+                self.timing.mark(il, "route")
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
                 counts.zero_(); cursor.zero_(); dst_row.fill_(-1)
                 G.moe_count(ids, E, counts)
                 moe_tiles.build(counts)
                 G.moe_scatter(ids, wts, E, moe_tiles.offsets, cursor, pos_of, dst_row, row_scale)
                 G.gather_rows_bf16(xn, dst_row, moe_tiles.offsets[E:E + 1], cap, k, Ap)
+                self.timing.mark(il, "dispatch")
                 if self.expert_source is not None:
                     qg, qu, qd = self.expert_source(il)
                 else:
                     qg, qu, qd = (w.q[b + f"ffn_{n}_exps.weight"] for n in ("gate", "up", "down"))
                 G.dequant_bf16(qg, wg)
                 G.dequant_bf16(qu, wu)
+                self.timing.mark(il, "expand_gate_up")
                 G.gemm_bf16(Ap, wg, moe_tiles, out_bf16=act, B2=wu, status=st)
+                self.timing.mark(il, "gemm_gate_up")
                 G.dequant_bf16(qd, wd)
+                self.timing.mark(il, "expand_down")
                 G.gemm_bf16(act, wd, moe_tiles, out_f32=slot_out, dst_row=dst_row, row_scale=row_scale, status=st)
+                self.timing.mark(il, "gemm_down")
                 G.moe_combine(slot_out, pos_of, T, k, x, x)
             else:
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
