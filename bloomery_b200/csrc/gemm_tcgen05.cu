@@ -40,7 +40,17 @@ constexpr int TILE_A_BYTES = BM * BK * 2;      // 16 KiB
 constexpr int TILE_B128_BYTES = 128 * BK * 2;  // 16 KiB per 128 B-rows
 constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 
+// pad: in the several-GPU form the source rank of the tile's A rows; otherwise causal limits in units of 64:
+// low 16 bits = columns of the product that exist for this tile (0 = all), high 16 bits = depth blocks to run (0 = all).
 struct MTile { int group, row0, row_end, pad; };
+__device__ __forceinline__ bool tile_skipped(const MTile& mt, int n0) {
+  const int lim = mt.pad & 0xFFFF;
+  return lim != 0 && n0 >= lim * 64;
+}
+__device__ __forceinline__ int tile_kblocks(const MTile& mt, int kblocks) {
+  const int lim = (mt.pad >> 16) & 0xFFFF;
+  return lim != 0 && lim < kblocks ? lim : kblocks;
+}
 
 struct GemmArgs {
   int N, K;
@@ -216,7 +226,9 @@ gemm_bf16_kernel(const __grid_constant__ AMaps tma_a, const __grid_constant__ CU
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
         const MTile mt = a.mtiles[t / a.tiles_n];
         const int n0 = (t % a.tiles_n) * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        if (!DIST && tile_skipped(mt, n0)) continue;
+        const int kb_end = DIST ? kblocks : tile_kblocks(mt, kblocks);
+        for (int kb = 0; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) break;
           uint8_t* sa = smem + (size_t)stage * STAGE_BYTES;
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
@@ -245,14 +257,18 @@ gemm_bf16_kernel(const __grid_constant__ AMaps tma_a, const __grid_constant__ CU
       constexpr uint32_t idesc = umma_idesc(BM, BN);
       int stage = 0; uint32_t phase = 0;
       int it = 0;
-      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++it) {
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        const MTile mt = a.mtiles[t / a.tiles_n];
+        if (!DIST && tile_skipped(mt, (t % a.tiles_n) * BN)) continue;
+        const int kb_end = DIST ? kblocks : tile_kblocks(mt, kblocks);
         const int ab = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&acc_empty[ab], acc_phase ^ 1, abort_flag)) break;
         tc_fence_after();
         const uint32_t d0 = tmem_base + ab * ACC_COLS;
         bool ok = true;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = 0; kb < kb_end; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
@@ -276,11 +292,13 @@ gemm_bf16_kernel(const __grid_constant__ AMaps tma_a, const __grid_constant__ CU
   } else {
     const int q = warp & 3;                    // TMEM lane quarter of this warp
     int it = 0;
-    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++it) {
-      const int ab = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
+    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       const MTile mt = a.mtiles[t / a.tiles_n];
       const int n0 = (t % a.tiles_n) * BN;
+      if (!DIST && tile_skipped(mt, n0)) continue;
+      const int ab = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
       if (!mbar_wait(&acc_full[ab], acc_phase, abort_flag)) break;
       tc_fence_after();
       const int r = mt.row0 + q * 32 + lane;                 // product row of this thread
@@ -369,7 +387,8 @@ gemm_bf16_kernel(const __grid_constant__ AMaps tma_a, const __grid_constant__ CU
 // A group's B-matrix index is g / group_div (several row groups may share one B, e.g. the
 // query heads of one KV head).
 __global__ void build_mtiles_kernel(const int* group_rows, int n_groups, MTile* mtiles, int* n_mtiles, int max_mtiles,
-                                    int* group_offset_out, int group_div, int group_stride, int base, int src_rows) {
+                                    int* group_offset_out, int group_div, int group_stride, int base, int src_rows,
+                                    int causal_pos0, int causal_kind) {
   pdl_wait();
   pdl_launch();
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
@@ -388,7 +407,15 @@ __global__ void build_mtiles_kernel(const int* group_rows, int n_groups, MTile* 
           const int end = min(off + rows, (src + 1) * src_rows) - src * src_rows;
           mtiles[n] = MTile{g / group_div, lo, end, src};
         } else {
-          mtiles[n] = MTile{g / group_div, off + r, off + rows, 0};
+          // causal_kind 1: the product's columns are keys, a tile of queries r..r+127 of the group needs keys up to
+          // its last query's position; 2: the depth is keys.  Limits are counted in 64s.
+          int pad = 0;
+          if (causal_kind != 0) {
+            const int last = causal_pos0 + min(r + BM, rows);          // keys 0 .. last - 1
+            const int lim = min((last + 63) / 64, 0xFFFF);
+            pad = causal_kind == 1 ? lim : (lim << 16);
+          }
+          mtiles[n] = MTile{g / group_div, off + r, off + rows, pad};
         }
       }
       ++n;
@@ -434,7 +461,17 @@ int bl_gemm_build_tiles(const int* group_rows, int n_groups, void* mtiles, int* 
                         int* group_offsets, int group_div, int group_stride, int base, cudaStream_t st) {
   BL_REQUIRE(n_groups >= 1 && max_mtiles >= 1 && group_div >= 1, BL_ERR_SHAPE);
   return (int)launch(build_mtiles_kernel, dim3(1), dim3(32), 0, st, group_rows, n_groups, (MTile*)mtiles, n_mtiles,
-                     max_mtiles, group_offsets, group_div, group_stride, base, 0);
+                     max_mtiles, group_offsets, group_div, group_stride, base, 0, 0, 0);
+}
+
+// The same with causal limits: kind 1 = columns are keys (scores), kind 2 = depth is keys (values); a group's row r is
+// the query at position causal_pos0 + r.
+int bl_gemm_build_tiles_causal(const int* group_rows, int n_groups, void* mtiles, int* n_mtiles, int max_mtiles,
+                               int* group_offsets, int group_div, int group_stride, int base, int causal_pos0, int kind,
+                               cudaStream_t st) {
+  BL_REQUIRE(n_groups >= 1 && max_mtiles >= 1 && group_div >= 1 && (kind == 1 || kind == 2) && causal_pos0 >= 0, BL_ERR_SHAPE);
+  return (int)launch(build_mtiles_kernel, dim3(1), dim3(32), 0, st, group_rows, n_groups, (MTile*)mtiles, n_mtiles,
+                     max_mtiles, group_offsets, group_div, group_stride, base, 0, causal_pos0, kind);
 }
 
 // Tile table of a dense product whose A rows are sharded over ranks in blocks of src_rows (a multiple of 128).
@@ -442,7 +479,7 @@ int bl_gemm_build_tiles_sharded(const int* total_rows, void* mtiles, int* n_mtil
                                 cudaStream_t st) {
   BL_REQUIRE(max_mtiles >= 1 && src_rows >= BM && src_rows % BM == 0, BL_ERR_SHAPE);
   return (int)launch(build_mtiles_kernel, dim3(1), dim3(32), 0, st, total_rows, 1, (MTile*)mtiles, n_mtiles, max_mtiles,
-                     (int*)nullptr, 1, 0, 0, src_rows);
+                     (int*)nullptr, 1, 0, 0, src_rows, 0, 0);
 }
 
 // C = A * B[g]^T per 128-row tile of the table.  A: [rows_a, K] bf16 (lda elements);

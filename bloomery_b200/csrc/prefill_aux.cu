@@ -202,6 +202,8 @@ __global__ void __launch_bounds__(128) kv_gather_bf16_kernel(const __half* k_cac
 
 // P[r, :] = softmax over keys 0..pos0 + (r % Tq) of S[r, :] (rows are head-major: r = h * Tq + tq);
 // masked and padded columns get exactly 0.
+// One block per score row.  Rows of up to 8,192 keys are read once into registers (32 per thread); longer rows
+// re-read the scores for each of the three passes.
 __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, long ldS, int Tq, int pos0, int T_pad,
                                                             __nv_bfloat16* P, long ldP) {
   __shared__ float red[8];
@@ -212,8 +214,19 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
   const int n_valid = min(T_pad, pos0 + tq + 1);
   const float* s = S + r * ldS;
   const int tid = threadIdx.x;
+  const bool cached = T_pad <= 256 * 32;
+  float v[32];
   float mx = -INFINITY;
-  for (int i = tid; i < n_valid; i += 256) mx = fmaxf(mx, s[i]);
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int i = tid + 256 * j;
+      v[j] = i < n_valid ? s[i] : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+    }
+  } else {
+    for (int i = tid; i < n_valid; i += 256) mx = fmaxf(mx, s[i]);
+  }
   mx = warp_max(mx);
   if ((tid & 31) == 0) red[tid >> 5] = mx;
   __syncthreads();
@@ -222,7 +235,12 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
   for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
   __syncthreads();
   float sum = 0.f;
-  for (int i = tid; i < n_valid; i += 256) sum += __expf(s[i] - mx);
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { v[j] = (tid + 256 * j) < n_valid ? __expf(v[j] - mx) : 0.f; sum += v[j]; }
+  } else {
+    for (int i = tid; i < n_valid; i += 256) sum += __expf(s[i] - mx);
+  }
   sum = warp_sum(sum);
   if ((tid & 31) == 0) red[tid >> 5] = sum;
   __syncthreads();
@@ -231,7 +249,15 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
   for (int w = 0; w < 8; ++w) sum += red[w];
   const float inv = 1.0f / sum;
   __nv_bfloat16* p = P + r * ldP;
-  for (int i = tid; i < T_pad; i += 256) p[i] = __float2bfloat16_rn(i < n_valid ? __expf(s[i] - mx) * inv : 0.f);
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int i = tid + 256 * j;
+      if (i < T_pad) p[i] = __float2bfloat16_rn(v[j] * inv);
+    }
+  } else {
+    for (int i = tid; i < T_pad; i += 256) p[i] = __float2bfloat16_rn(i < n_valid ? __expf(s[i] - mx) * inv : 0.f);
+  }
 }
 
 

@@ -22,10 +22,19 @@ class TileTable:
         self.n_mtiles = torch.zeros(1, dtype=torch.int32, device=device)
         self.offsets = torch.zeros(n_groups + 1, dtype=torch.int32, device=device)
 
-    def build(self, group_rows: torch.Tensor, group_div: int = 1, group_stride: int = 0, base: int = 0) -> None:
+    def build(self, group_rows: torch.Tensor, group_div: int = 1, group_stride: int = 0, base: int = 0,
+              causal_pos0: int = -1, causal_kind: int = 0) -> None:
         """group_rows int32 [n_groups] on the device.  Rows of group g follow group g-1 in A
         (or start at ``base + g * group_stride`` when ``group_stride`` > 0) and use B matrix
         ``g // group_div``."""
+        if causal_kind:
+            # causal_kind 1: the product's columns are keys (scores), 2: its depth is keys (values); row r of a group
+            # is the query at position causal_pos0 + r: tiles beyond the diagonal are skipped / cut short
+            check(cuda().bl_gemm_build_tiles_causal(p(group_rows), I(self.n_groups), p(self.mtiles), p(self.n_mtiles),
+                                                    I(self.max_mtiles), p(self.offsets), I(group_div), I(group_stride),
+                                                    I(base), I(causal_pos0), I(causal_kind), stream()),
+                  "bl_gemm_build_tiles_causal")
+            return
         check(cuda().bl_gemm_build_tiles(p(group_rows), I(self.n_groups), p(self.mtiles), p(self.n_mtiles),
                                          I(self.max_mtiles), p(self.offsets), I(group_div), I(group_stride), I(base),
                                          stream()), "bl_gemm_build_tiles")

@@ -189,7 +189,7 @@ class ShardedGemmPrefill:
                     rows = s.n_q * Tq
                     S = self._get("S", (rows, T_pad), f32)
                     P = self._get("P", (rows, T_pad), bf)
-                    qk_tiles, pv_tiles, map_s, map_o = self._attn_tables(Tp, Tq, c0, s.n_q, Gq)
+                    qk_tiles, pv_tiles, map_s, map_o = self._attn_tables(Tp, Tq, c0, s.n_q, Gq, p0)
                     G.gemm_bf16(q_bf.view(s.n_q * Tp, hd), Kb, qk_tiles, out_f32=S, dst_row=map_s, status=st)
                     G.softmax_causal(S, rows, Tq, p0 + c0, T_pad, P)
                     G.gemm_bf16(P, Vt, pv_tiles, out_bf16=attn.view(Tp * s.n_q, hd), dst_row=map_o, status=st)
@@ -243,8 +243,8 @@ class ShardedGemmPrefill:
         out.append([last])
         return out
 
-    def _attn_tables(self, T: int, Tq: int, c0: int, n_q: int, Gq: int):
-        key = ("attn", T, Tq, c0, n_q)
+    def _attn_tables(self, T: int, Tq: int, c0: int, n_q: int, Gq: int, pos0: int = 0):
+        key = ("attn", T, Tq, c0, n_q, pos0)
         hit = self._buf.get(key)
         if hit is not None:
             return hit
@@ -252,9 +252,9 @@ class ShardedGemmPrefill:
         i32 = torch.int32
         rows = torch.full((n_q,), Tq, dtype=i32, device=dev)
         qk = G.TileTable(n_q * Tq, n_q, dev)
-        qk.build(rows, group_div=Gq, group_stride=T, base=c0)
+        qk.build(rows, group_div=Gq, group_stride=T, base=c0, causal_pos0=pos0 + c0, causal_kind=1)
         pv = G.TileTable(n_q * Tq, n_q, dev)
-        pv.build(rows, group_div=Gq)
+        pv.build(rows, group_div=Gq, causal_pos0=pos0 + c0, causal_kind=2)
         h = torch.arange(n_q, device=dev).view(n_q, 1)
         i = torch.arange(Tq, device=dev).view(1, Tq)
         map_s = torch.full((n_q * T,), -1, dtype=i32, device=dev)
