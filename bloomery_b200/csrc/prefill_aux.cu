@@ -202,8 +202,10 @@ __global__ void __launch_bounds__(128) kv_gather_bf16_kernel(const __half* k_cac
 
 // P[r, :] = softmax over keys 0..pos0 + (r % Tq) of S[r, :] (rows are head-major: r = h * Tq + tq);
 // masked and padded columns get exactly 0.
-// One block per score row.  Rows of up to 8,192 keys are read once into registers (32 per thread); longer rows
-// re-read the scores for each of the three passes.
+// One block per score row.  Thread t owns runs of eight consecutive keys (8 (t + 256 j) ..): two 16-byte loads and one
+// 16-byte store per run.  Rows of up to 8,192 keys are read once into registers; longer rows re-read their scores.
+// Probabilities are written (zeros past the row's last key) only as far as the values product of the row's
+// 128-query tile reads them: up to the 64-key block that holds the tile's last query.
 __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, long ldS, int Tq, int pos0, int T_pad,
                                                             __nv_bfloat16* P, long ldP) {
   __shared__ float red[8];
@@ -212,17 +214,25 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
   const long r = blockIdx.x;
   const int tq = (int)(r % Tq);
   const int n_valid = min(T_pad, pos0 + tq + 1);
+  const int n_write = min(T_pad, (pos0 + min(tq | 127, Tq - 1) + 1 + 63) / 64 * 64);
   const float* s = S + r * ldS;
   const int tid = threadIdx.x;
-  const bool cached = T_pad <= 256 * 32;
+  const bool cached = T_pad <= 256 * 32 && (ldS % 4) == 0 && (ldP % 8) == 0;
   float v[32];
   float mx = -INFINITY;
   if (cached) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int i = tid + 256 * j;
-      v[j] = i < n_valid ? s[i] : -INFINITY;
-      mx = fmaxf(mx, v[j]);
+    for (int j = 0; j < 4; ++j) {
+      const int i0 = 8 * (tid + 256 * j);
+      if (i0 < n_valid) {
+        const float4 a = *reinterpret_cast<const float4*>(s + i0), b = *reinterpret_cast<const float4*>(s + i0 + 4);
+        const float t8[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { v[8 * j + e] = (i0 + e) < n_valid ? t8[e] : -INFINITY; mx = fmaxf(mx, v[8 * j + e]); }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[8 * j + e] = -INFINITY;
+      }
     }
   } else {
     for (int i = tid; i < n_valid; i += 256) mx = fmaxf(mx, s[i]);
@@ -237,7 +247,7 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
   float sum = 0.f;
   if (cached) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { v[j] = (tid + 256 * j) < n_valid ? __expf(v[j] - mx) : 0.f; sum += v[j]; }
+    for (int j = 0; j < 32; ++j) { v[j] = v[j] == -INFINITY ? 0.f : __expf(v[j] - mx); sum += v[j]; }
   } else {
     for (int i = tid; i < n_valid; i += 256) sum += __expf(s[i] - mx);
   }
@@ -251,12 +261,17 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
   __nv_bfloat16* p = P + r * ldP;
   if (cached) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int i = tid + 256 * j;
-      if (i < T_pad) p[i] = __float2bfloat16_rn(v[j] * inv);
+    for (int j = 0; j < 4; ++j) {
+      const int i0 = 8 * (tid + 256 * j);
+      if (i0 < n_write) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = v[8 * j + e] * inv;
+        *reinterpret_cast<uint4*>(p + i0) = pack8_bf16(o);
+      }
     }
   } else {
-    for (int i = tid; i < T_pad; i += 256) p[i] = __float2bfloat16_rn(i < n_valid ? __expf(s[i] - mx) * inv : 0.f);
+    for (int i = tid; i < n_write; i += 256) p[i] = __float2bfloat16_rn(i < n_valid ? __expf(s[i] - mx) * inv : 0.f);
   }
 }
 

@@ -142,8 +142,11 @@ class GemmPrefill:
                 P = self._get("P", (rows, T_pad), bf)
                 qk_tiles, pv_tiles, map_s, map_o = self._attn_tables(T, Tq, c0, s.n_q, Gq, p0)
                 G.gemm_bf16(q_bf.view(s.n_q * T, s.head_dim), Kb, qk_tiles, out_f32=S, dst_row=map_s, status=st)
+                self.timing.mark(il, "scores")
                 G.softmax_causal(S, rows, Tq, p0 + c0, T_pad, P)
+                self.timing.mark(il, "softmax")
                 G.gemm_bf16(P, Vt, pv_tiles, out_bf16=attn.view(T * s.n_q, s.head_dim), dst_row=map_o, status=st)
+                self.timing.mark(il, "values")
             self.timing.mark(il, "attention")
             G.dequant_bf16(w.q[b + "attn_output.weight"], wo)
             G.gemm_bf16(attn, wo, dense_tiles, out_f32=x, resid=x, status=st)
