@@ -24,6 +24,8 @@ from __future__ import annotations
 
 from typing import Callable, List, Sequence
 
+import os
+
 import torch
 
 from ..ops import decode as K
@@ -36,6 +38,9 @@ Phase = List[Callable[[], None]]
 
 def _align(n: int, a: int = 256) -> int:
     return (n + a - 1) // a * a
+
+
+POISON = os.environ.get("BLOOMERY_POISON_SCRATCH", "0") == "1"
 
 
 class ShardedGemmPrefill:
@@ -70,6 +75,8 @@ class ShardedGemmPrefill:
         b = self._buf.get(name)
         if b is None or b.numel() < n or b.dtype != dtype:
             b = torch.empty(n, dtype=dtype, device=self.e.device)
+            if POISON:                      # scratch starts as NaN / -1: a read of something never written shows at once
+                b.fill_(float("nan") if dtype.is_floating_point else -1)
             self._buf[name] = b
         return b[:n].view(*shape)
 
@@ -125,6 +132,8 @@ class ShardedGemmPrefill:
         wo = self._get("wo", (H, s.q_rows), bf)
         q_bf = self._get("q_bf", (s.n_q, Tp, hd), bf)
         attn = self._get("attn", (Tp, s.q_rows), bf)
+        if Tp > T:
+            q_bf[:, T:].zero_()         # pad rows never pass the rope kernel (no sequence): their queries are zeros, not leftovers
         gather_tiles = G.TileTable.sharded(Tp, Tr, dev)
         dense_all = G.TileTable.dense(Tp, dev)
         dense_own = G.TileTable.dense(Tr, dev)

@@ -21,11 +21,16 @@ from __future__ import annotations
 import math
 from typing import List, Optional, Sequence
 
+import os
+
 import torch
 
 from ..ops import decode as K
 from ..ops import gemm as G
 from .kv import PAGE
+
+
+POISON = os.environ.get("BLOOMERY_POISON_SCRATCH", "0") == "1"
 
 
 class GemmPrefill:
@@ -49,6 +54,8 @@ class GemmPrefill:
         b = self._buf.get(name)
         if b is None or b.numel() < n or b.dtype != dtype:
             b = torch.empty(n, dtype=dtype, device=self.e.device)
+            if POISON:                      # scratch starts as NaN / -1: a read of something never written shows at once
+                b.fill_(float("nan") if dtype.is_floating_point else -1)
             self._buf[name] = b
         return b[:n].view(*shape)
 

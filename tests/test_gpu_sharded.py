@@ -157,11 +157,15 @@ def test_server_on_two_gpus_in_lockstep(tmp_path):
     assert a2["tokens"] == a1["tokens"][3:7]
 
 
-def test_sharded_gemm_prefill_two_emulated_ranks():
+def test_sharded_gemm_prefill_two_emulated_ranks(monkeypatch):
     """The several-GPU prompt path (peer TMA loads for the all-gather, adds into the owner's rows for the
     reduce-scatter and the expert combine), two ranks emulated on one GPU phase by phase, against the
     one-GPU GEMM prompt path: hidden state of the last row, the KV rows written, and the next token."""
+    import bloomery_b200.parallel.prefill_dist as PD
+    import bloomery_b200.runtime.prefill as PF
     from bloomery_b200.parallel.prefill_dist import ShardedGemmPrefill
+    monkeypatch.setattr(PD, "POISON", True)        # scratch starts as NaN: nothing may read what was never written
+    monkeypatch.setattr(PF, "POISON", True)
     spec, ref, engs = _engines(2, slot_ctx=512)
     g = torch.Generator().manual_seed(5)
     toks = torch.randint(0, spec.vocab, (300,), generator=g).tolist()
