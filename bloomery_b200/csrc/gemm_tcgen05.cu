@@ -77,6 +77,7 @@ struct GemmArgs {
   int n_owners;
   int dst_div;
   int src_rows;               // > 0: A is row-sharded; product row = tile's source rank * src_rows + row in the shard
+  int wide_stores;            // fp32 output rows start on 32-byte boundaries: the epilogue may use 256-bit stores
 };
 
 // One tensor map of A per source rank: m-tile t reads the map of rank mtiles[t].pad, so the
@@ -177,6 +178,10 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // ---- the kernel ------------------------------------------------------------------------
 // 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 = epilogue
 // (their warp id modulo 4 covers the four 32-lane quarters of tensor memory).
+__device__ __forceinline__ void st_global_v8(float* p, const float* v) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]),
+               "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
   asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
@@ -351,8 +356,14 @@ gemm_bf16_kernel(const __grid_constant__ AMaps tma_a, const __grid_constant__ CU
             for (int i = 0; i < 32; i += 4) red_add_v4(o + i, f[i], f[i + 1], f[i + 2], f[i + 3]);
           } else if (a.c_f32) {
             float* o = a.c_f32 + orow * a.ldc + col;
+            if (a.wide_stores) {
+              // 32-byte stores: every instruction fills whole sectors of the thread's row
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+              for (int i = 0; i < 32; i += 8) st_global_v8(o + i, f + i);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+            }
           } else {
             __nv_bfloat16* o = a.c_bf16 + orow * a.ldc + col;
 #pragma unroll
@@ -530,6 +541,7 @@ static int gemm_launch(const void* const* A_of_rank, int n_src, long lda, long r
   a.dst_row = dst_row; a.row_scale = row_scale; a.resid = resid; a.ldr = ldr; a.status = status;
   for (int r = 0; r < n_owners; ++r) a.own_base[r] = own_base[r];
   a.n_owners = n_owners; a.rows_per_owner = rows_per_owner; a.dst_div = dst_div; a.src_rows = src_rows;
+  a.wide_stores = (c_f32 && ((uintptr_t)c_f32 & 31) == 0 && ldc % 8 == 0) ? 1 : 0;
   a.tiles_n = (N + (B2 ? BN_DUAL : BN_SINGLE) - 1) / (B2 ? BN_DUAL : BN_SINGLE);
   long tiles = (long)max_mtiles * a.tiles_n;
   int grid = (int)(tiles < sm_count ? tiles : sm_count);
