@@ -82,6 +82,7 @@ def main() -> int:
     ap.add_argument("--impl", default="own")
     ap.add_argument("--model", default="qwen3-30b-a3b")
     ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--flash-mma", action="store_true", help="decode attention segments on tensor-core tiles")
     ap.add_argument("--ttft", type=int, default=4096, help="also time a prompt of this many tokens (0 = skip)")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--nccl-baseline", dest="nccl_baseline", action="store_true",
@@ -108,6 +109,9 @@ def main() -> int:
     from bloomery_b200.ops import decode as K
     from bloomery_b200.runtime.engine import DecodeEngine
 
+    if args.flash_mma:
+        from bloomery_b200.ops import decode as _K
+        _K.set_flash_mma(True)
     if args.no_pdl:
         K.set_pdl(False)
     spec = NAMED[args.model]()
@@ -192,7 +196,7 @@ def main() -> int:
         "data": "synthetic: seeded random token ids, random-init N(0,0.02) weights quantised Q4_K_M on the card",
         "config": {"model": spec.name, "global_batch": 1, "seq_len": args.prompt + warm + steps,
                    "prompt_tokens": args.prompt, "parallelism": "single", "l2": "weights (17 GB) exceed L2; no flush needed",
-                   "graph": "one CUDA graph per decode step", "pdl": not args.no_pdl},
+                   "graph": "one CUDA graph per decode step", "pdl": not args.no_pdl, "flash_mma": bool(args.flash_mma)},
         "clocks": sampler.summary(), "e2e": e2e,
         "gpu_launches": eng.launches_per_step * steps, "launches_per_step": eng.launches_per_step,
         "ttft_ms_prompt": ttft_prompt_ms, "load_s": t_load, "weights_gb": w.n_bytes / 1e9,

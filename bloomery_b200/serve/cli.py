@@ -180,6 +180,7 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
         tk, tsrc, bos, eos = surface(handle)
         return CpuEngine(w, tk, plan["n_slots"], plan["slot_ctx"], name), tsrc, bos, eos
     K.set_pdl(bool(levers.get("BLOOMERY_PDL")))
+    K.set_flash_mma(bool(levers.get("BLOOMERY_FLASH_MMA")))
     graphs = bool(levers.get("BLOOMERY_GRAPHS"))
     bound = float(levers.get("BLOOMERY_ENGINE_BOUND"))
     if pl.mode == "tp" and len(pl.devices) > 1:

@@ -48,6 +48,7 @@ REGISTRY: List[LeverSpec] = [
     LeverSpec("BLOOMERY_UBATCH", "int", 4096, "rows per prompt micro-batch"),
     LeverSpec("BLOOMERY_PREFILL", "word", "batch", "prompt path", ("batch", "steps")),
     LeverSpec("BLOOMERY_PDL", "bool", True, "programmatic dependent launch between decode kernels"),
+    LeverSpec("BLOOMERY_FLASH_MMA", "bool", False, "decode attention segments on tensor-core tiles (f16 queries and probabilities)"),
     LeverSpec("BLOOMERY_GRAPHS", "bool", True, "one CUDA graph per decode step"),
     LeverSpec("BLOOMERY_MTP_WIDTH", "int", 0, "draft ids per speculative pass (0 = chooser decides)"),
     LeverSpec("BLOOMERY_AUTOTUNE", "bool", True, "race equal kernel variants at load"),
