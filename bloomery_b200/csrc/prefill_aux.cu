@@ -206,6 +206,12 @@ __global__ void __launch_bounds__(128) kv_gather_bf16_kernel(const __half* k_cac
 // 16-byte store per run.  Rows of up to 8,192 keys are read once into registers; longer rows re-read their scores.
 // Probabilities are written (zeros past the row's last key) only as far as the values product of the row's
 // 128-query tile reads them: up to the 64-key block that holds the tile's last query.
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, long ldS, int Tq, int pos0, int T_pad,
                                                             __nv_bfloat16* P, long ldP) {
   __shared__ float red[8];
@@ -227,11 +233,15 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
       if (i0 < n_valid) {
         const float4 a = *reinterpret_cast<const float4*>(s + i0), b = *reinterpret_cast<const float4*>(s + i0 + 4);
         const float t8[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        if (i0 + 8 <= n_valid) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { v[8 * j + e] = (i0 + e) < n_valid ? t8[e] : -INFINITY; mx = fmaxf(mx, v[8 * j + e]); }
-      } else {
+          for (int e = 0; e < 8; ++e) v[8 * j + e] = t8[e];
+        } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[8 * j + e] = -INFINITY;
+          for (int e = 0; e < 8; ++e) v[8 * j + e] = (i0 + e) < n_valid ? t8[e] : -INFINITY;
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(v[8 * j], v[8 * j + 1]), fmaxf(v[8 * j + 2], v[8 * j + 3])),
+                             fmaxf(fmaxf(v[8 * j + 4], v[8 * j + 5]), fmaxf(v[8 * j + 6], v[8 * j + 7]))));
       }
     }
   } else {
@@ -246,8 +256,19 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
   __syncthreads();
   float sum = 0.f;
   if (cached) {
+    // runs past the row's last key are skipped whole; a masked key inside the last run holds -inf and
+    // comes out of ex2 as exactly 0 (the row's maximum is finite: key 0 is always valid)
+    const float mxl = mx * 1.4426950408889634f;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { v[j] = v[j] == -INFINITY ? 0.f : __expf(v[j] - mx); sum += v[j]; }
+    for (int j = 0; j < 4; ++j) {
+      if (8 * (tid + 256 * j) < n_valid) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          v[8 * j + e] = exp2_approx(fmaf(v[8 * j + e], 1.4426950408889634f, -mxl));
+          sum += v[8 * j + e];
+        }
+      }
+    }
   } else {
     for (int i = tid; i < n_valid; i += 256) sum += __expf(s[i] - mx);
   }
@@ -266,7 +287,7 @@ __global__ void __launch_bounds__(256) softmax_causal_kernel(const float* S, lon
       if (i0 < n_write) {
         float o[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = v[8 * j + e] * inv;
+        for (int e = 0; e < 8; ++e) o[e] = i0 < n_valid ? v[8 * j + e] * inv : 0.f;
         *reinterpret_cast<uint4*>(p + i0) = pack8_bf16(o);
       }
     }

@@ -169,3 +169,30 @@ def test_split_precision_router_logits_are_fp32_grade():
     ref = (rms_norm(x.cpu(), g.cpu(), 1e-6).double() @ W.cpu().double().T).float()
     err = ((logits.cpu() - ref).abs().max() / ref.abs().max()).item()
     assert err < 2e-4 and int(st) == 0, err                     # plain bf16 operands would sit near 1e-2
+
+
+@pytest.mark.parametrize("heads,Tq,pos0,T_pad", [(2, 128, 0, 128), (3, 256, 1000, 4096), (2, 384, 3700, 4096),
+                                                (1, 128, 8100, 8320)])
+def test_softmax_causal_rows(heads, Tq, pos0, T_pad):
+    """Causal softmax of score rows (head-major) against torch fp32: masked keys exactly 0 inside the written span;
+    covers the register path with every run in use and the re-reading path of rows longer than 8,192 keys."""
+    from bloomery_b200.ops import gemm as G
+    torch.manual_seed(7)
+    rows = heads * Tq
+    S = torch.randn(rows, T_pad, device=DEV) * 4.0
+    P = torch.full((rows, T_pad), float("nan"), device=DEV, dtype=torch.bfloat16)
+    G.softmax_causal(S, rows, Tq, pos0, T_pad, P)
+    torch.cuda.synchronize()
+    tq = torch.arange(rows, device=DEV) % Tq
+    n_valid = torch.clamp(pos0 + tq + 1, max=T_pad)
+    col = torch.arange(T_pad, device=DEV)
+    mask = col[None, :] < n_valid[:, None]
+    ref = torch.softmax(S.masked_fill(~mask, float("-inf")), dim=-1)
+    last = torch.clamp((tq | 127), max=Tq - 1)
+    n_write = torch.clamp((pos0 + last + 1 + 63) // 64 * 64, max=T_pad)
+    wr = col[None, :] < n_write[:, None]
+    got = P.float()
+    assert not torch.isnan(got[wr]).any()
+    assert torch.all(got[wr & ~mask] == 0)
+    assert torch.allclose(got[wr], ref[wr], rtol=1e-2, atol=1e-5), (got[wr] - ref[wr]).abs().max()
+    assert torch.allclose(got.masked_fill(~wr, 0).sum(-1), torch.ones(rows, device=DEV), atol=2e-2)
