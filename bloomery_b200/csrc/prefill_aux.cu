@@ -180,24 +180,33 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* slot_out,
 
 // Contiguous bf16 copies of one sequence's keys and values for the prompt GEMMs:
 //   Kb [n_kv][T_pad][HEAD], Vt [n_kv][HEAD][T_pad]; positions >= n_keys are zero.
-__global__ void __launch_bounds__(128) kv_gather_bf16_kernel(const __half* k_cache, const __half* v_cache, const int* block_table,
+// One block per (cache page of 64 keys, KV head): rows are read and the key rows written whole; the values
+// pass through a shared tile so that the transposed rows are written 128 contiguous bytes at a time.
+__global__ void __launch_bounds__(256) kv_gather_bf16_kernel(const __half* k_cache, const __half* v_cache, const int* block_table,
                                                             int n_pages, int n_kv, int head, int n_keys, int T_pad,
                                                             __nv_bfloat16* Kb, __nv_bfloat16* Vt) {
+  __shared__ __nv_bfloat16 sv[64][130];         // 65-word rows: the transposed read has no bank conflicts
   pdl_wait();
   pdl_launch();
-  const int t = blockIdx.x, kvh = blockIdx.y, d = threadIdx.x;
-  if (d >= head) return;
-  float kv = 0.f, vv = 0.f;
-  if (t < n_keys) {
-    int page = block_table[t / 64];
-    if (page >= 0 && page < n_pages) {
-      const long src = (((long)page * n_kv + kvh) * 64 + (t % 64)) * head + d;
-      kv = __half2float(k_cache[src]);
-      vv = __half2float(v_cache[src]);
+  const int t0 = blockIdx.x * 64, kvh = blockIdx.y, tid = threadIdx.x;
+  int page = t0 < n_keys ? block_table[t0 / 64] : -1;
+  if (page >= n_pages) page = -1;
+  const long src0 = ((long)page * n_kv + kvh) * 64 * head;
+  for (int i = tid; i < 64 * head; i += 256) {
+    const int tt = i / head, d = i - tt * head;
+    float kv = 0.f, vv = 0.f;
+    if (page >= 0 && t0 + tt < n_keys) {
+      kv = __half2float(k_cache[src0 + i]);
+      vv = __half2float(v_cache[src0 + i]);
     }
+    Kb[((long)kvh * T_pad + t0 + tt) * head + d] = __float2bfloat16_rn(kv);
+    sv[tt][d] = __float2bfloat16_rn(vv);
   }
-  Kb[((long)kvh * T_pad + t) * head + d] = __float2bfloat16_rn(kv);
-  Vt[((long)kvh * head + d) * T_pad + t] = __float2bfloat16_rn(vv);
+  __syncthreads();
+  for (int i = tid; i < 64 * head; i += 256) {
+    const int d = i >> 6, tt = i & 63;
+    Vt[((long)kvh * head + d) * T_pad + t0 + tt] = sv[tt][d];
+  }
 }
 
 // P[r, :] = softmax over keys 0..pos0 + (r % Tq) of S[r, :] (rows are head-major: r = h * Tq + tq);
@@ -374,8 +383,8 @@ int bl_moe_combine(const float* slot_out, const int* pos_of, int T, int k, int H
 
 int bl_kv_gather_bf16(const void* k_cache, const void* v_cache, const int* block_table, int n_pages, int n_kv, int head,
                       int n_keys, int T_pad, void* Kb, void* Vt, cudaStream_t st) {
-  BL_REQUIRE(head <= 128 && T_pad >= 1 && n_keys <= T_pad, BL_ERR_SHAPE);
-  return (int)launch(kv_gather_bf16_kernel, dim3(T_pad, n_kv), dim3(128), 0, st, (const __half*)k_cache, (const __half*)v_cache,
+  BL_REQUIRE(head <= 128 && T_pad >= 64 && T_pad % 64 == 0 && n_keys <= T_pad, BL_ERR_SHAPE);
+  return (int)launch(kv_gather_bf16_kernel, dim3(T_pad / 64, n_kv), dim3(256), 0, st, (const __half*)k_cache, (const __half*)v_cache,
                      block_table, n_pages, n_kv, head, n_keys, T_pad, (__nv_bfloat16*)Kb, (__nv_bfloat16*)Vt);
 }
 
