@@ -196,3 +196,27 @@ def test_softmax_causal_rows(heads, Tq, pos0, T_pad):
     assert torch.all(got[wr & ~mask] == 0)
     assert torch.allclose(got[wr], ref[wr], rtol=1e-2, atol=1e-5), (got[wr] - ref[wr]).abs().max()
     assert torch.allclose(got.masked_fill(~wr, 0).sum(-1), torch.ones(rows, device=DEV), atol=2e-2)
+
+
+@pytest.mark.parametrize("n_kv,head,n_keys,T_pad", [(2, 128, 200, 256), (4, 128, 64, 128), (1, 64, 321, 384)])
+def test_kv_gather_rows_and_transposed_values(n_kv, head, n_keys, T_pad):
+    """Paged f16 cache -> contiguous bf16 keys [n_kv, T_pad, head] and transposed values [n_kv, head, T_pad]
+    through a shuffled block table; positions past the last key are zero."""
+    from bloomery_b200.ops import gemm as G
+    torch.manual_seed(3)
+    n_pages = 12
+    k_cache = torch.randn(n_pages, n_kv, 64, head, device=DEV).half()
+    v_cache = torch.randn(n_pages, n_kv, 64, head, device=DEV).half()
+    table = torch.randperm(n_pages, device=DEV)[: (T_pad + 63) // 64].to(torch.int32).contiguous()
+    Kb = torch.full((n_kv, T_pad, head), float("nan"), device=DEV, dtype=torch.bfloat16)
+    Vt = torch.full((n_kv, head, T_pad), float("nan"), device=DEV, dtype=torch.bfloat16)
+    G.kv_gather_bf16(k_cache, v_cache, table, n_pages, n_kv, head, n_keys, T_pad, Kb, Vt)
+    torch.cuda.synchronize()
+    t = torch.arange(T_pad, device=DEV)
+    pages = table.long()[t // 64]
+    k_ref = k_cache[pages, :, t % 64].permute(1, 0, 2).float()          # [n_kv, T_pad, head]
+    v_ref = v_cache[pages, :, t % 64].permute(1, 0, 2).float()
+    k_ref[:, n_keys:] = 0
+    v_ref[:, n_keys:] = 0
+    assert torch.equal(Kb.float(), k_ref.bfloat16().float())
+    assert torch.equal(Vt.float(), v_ref.bfloat16().float().transpose(1, 2))
