@@ -5,7 +5,7 @@ Two shared objects are produced under ``bloomery_b200/_C``:
 * ``libbloomery_cuda.so`` -- every ``csrc/*.cu`` compiled for ``sm_100a`` only
   (``-gencode arch=compute_100a,code=sm_100a``); plain C ABI, loaded with ctypes.
 * ``libbloomery_host.so`` -- ``csrc/host/*.cpp``: GGUF block decode oracle, CPU
-  quantised dots (scalar mirror of the device units + AVX2 / AVX-512-VNNI paths picked
+  quantised dots (scalar mirror of the device units + AVX2 paths for Q4_K, Q6_K and Q8_0 rows picked
   at run time), the worker pool and the CPU expert leg.
 
 nvcc cross-compiles without a GPU, so ``python -m bloomery_b200.build`` is also the

@@ -6,6 +6,13 @@
 
 namespace blh {
 
+// spins on the generation word before a worker parks (BLOOMERY_SPIN; blh_pool_set_spin)
+static std::atomic<int> g_spin{[] {
+  if (const char* e = std::getenv("BLOOMERY_SPIN")) { int v = std::atoi(e); if (v >= 0) return v; }
+  return 20000;
+}()};
+static std::atomic<int> g_pin{-1};   // -1: follow BLOOMERY_PIN, 0 / 1: set by blh_pool_set_pin
+
 static int default_threads() {
   if (const char* e = std::getenv("BLOOMERY_THREADS")) {
     int v = std::atoi(e);
@@ -62,7 +69,8 @@ void Pool::run_chunks() {
 
 void Pool::worker_loop(int idx) {
   const char* pin = std::getenv("BLOOMERY_PIN");
-  if (!pin || std::strcmp(pin, "0") != 0) {
+  const int forced = g_pin.load();
+  if (forced == 1 || (forced < 0 && (!pin || std::strcmp(pin, "0") != 0))) {
     cpu_set_t allowed;
     CPU_ZERO(&allowed);
     if (sched_getaffinity(0, sizeof(allowed), &allowed) == 0) {
@@ -84,7 +92,7 @@ void Pool::worker_loop(int idx) {
     // spin, then park
     int spins = 0;
     while (generation_.load(std::memory_order_acquire) == seen_gen) {
-      if (++spins > 20000) {
+      if (++spins > g_spin.load(std::memory_order_relaxed)) {
         std::unique_lock<std::mutex> lk(mu_);
         cv_.wait(lk, [&] { return generation_.load() != seen_gen; });
         break;
@@ -126,4 +134,7 @@ void Pool::parallel_for(int n, int grain, const std::function<void(int, int)>& f
 extern "C" {
 int blh_pool_size() { return blh::Pool::instance().size(); }
 void blh_pool_resize(int n) { blh::Pool::instance().resize(n); }
+void blh_pool_set_spin(int spins) { blh::g_spin.store(spins < 0 ? 0 : spins); }
+// takes effect for workers started afterwards (call before blh_pool_resize)
+void blh_pool_set_pin(int on) { blh::g_pin.store(on ? 1 : 0); }
 }

@@ -88,7 +88,14 @@ class ModelSpec:
     def from_gguf(cls, g) -> "ModelSpec":
         arch = g.arch
         a = g.arch_get
-        if arch in ("qwen3moe", "qwen3", "llama", "qwen2", "qwen2moe"):
+        if arch in ("llama", "qwen2", "qwen2moe"):
+            # llama-arch files carry Q/K rows permuted for interleaved RoPE pairs, qwen2 files carry QKV biases and
+            # qwen2moe a gated shared expert: the chains here apply none of the three, so such a file is refused
+            # instead of being decoded to wrong logits
+            raise ValueError(f"architecture {arch!r} has no seat in this build")
+        if arch in ("qwen3moe", "qwen3"):
+            if any(n.endswith((".attn_q.bias", ".attn_k.bias", ".attn_v.bias")) for n in g.tensors):
+                raise ValueError(f"architecture {arch!r} with attention biases has no seat in this build")
             n_q = int(a("attention.head_count"))
             hidden = int(a("embedding_length"))
             head = int(a("attention.key_length", hidden // n_q))
@@ -242,14 +249,6 @@ def qwen3_235b_a22b() -> ModelSpec:
     return ModelSpec(arch="qwen3moe", name="qwen3-235b-a22b-shaped", n_layer=94, hidden=4096, n_q=64, n_kv=4,
                      head_dim=128, vocab=151936, ctx_train=40960, rms_eps=1e-6, rope_theta=1e6, qk_norm=True,
                      n_expert=128, n_used=8, moe_inter=1536)
-
-
-def deepseek_v3() -> ModelSpec:
-    return ModelSpec(arch="deepseek2", name="deepseek-v3-shaped", n_layer=61, hidden=7168, n_q=128, n_kv=128,
-                     head_dim=192, vocab=129280, ctx_train=163840, rms_eps=1e-6, rope_theta=1e4, qk_norm=False,
-                     dense_inter=18432, n_expert=256, n_used=8, moe_inter=2048, n_shared=1, shared_inter=2048,
-                     first_dense=3, router_mode="sigmoid", router_renorm=True, router_scale=2.5, n_group=8,
-                     topk_group=4, mla=True, q_lora=1536, kv_lora=512, rope_dim=64, nope_dim=128, v_dim=128, n_mtp=1)
 
 
 def kimi_k2() -> ModelSpec:

@@ -43,3 +43,13 @@ def decode_rows(w_res: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
 
 def pool_size() -> int:
     return int(host().blh_pool_size())
+
+
+def pool_configure(threads: int = 0, pin: bool = True, spin: int = 20000) -> int:
+    """Apply the host-pool levers (size, CPU pinning, spins before a worker parks); returns the pool size."""
+    h = host()
+    h.blh_pool_set_spin(I(int(spin)))
+    h.blh_pool_set_pin(I(1 if pin else 0))
+    if threads > 0 and threads != int(h.blh_pool_size()):
+        h.blh_pool_resize(I(int(threads)))
+    return int(h.blh_pool_size())

@@ -56,8 +56,8 @@ class _KvAll:
     def __init__(self, stages):
         self.stages = stages
 
-    def share_prefix(self, src, dst, n):
-        return min(st.kv.share_prefix(src, dst, n) for st in self.stages)
+    def share_prefix(self, src, dst, n, have=0):
+        return min(st.kv.share_prefix(src, dst, n, have) for st in self.stages)
 
     def sync_table(self):
         for st in self.stages:
@@ -65,7 +65,10 @@ class _KvAll:
                 st.kv.sync_table()
 
     def snapshot(self, slot, n):
+        from ..runtime.kv import snap_ready
         snaps = [st.kv.snapshot(slot, n) for st in self.stages]
+        for sn in snaps:
+            snap_ready(sn)                   # the bytes are read on the host right below
         return {"stages": snaps, "k": torch.cat([s["k"].reshape(-1).view(torch.uint8).cpu() for s in snaps])}
 
     def restore(self, slot, saved, n):

@@ -79,10 +79,11 @@ class _RankOps:
     def reset(self, slot):
         self.dec.reset(slot)
 
-    def share_prefix(self, src, dst, n):
-        got = self.dec.kv.share_prefix(src, dst, n)
-        self.dec.slot_len[dst] = got
-        self.dec.kv.sync_table()
+    def share_prefix(self, src, dst, n, have=0):
+        got = self.dec.kv.share_prefix(src, dst, n, have)
+        if got > 0:
+            self.dec.slot_len[dst] = got
+            self.dec.kv.sync_table()
 
     def snapshot(self, slot, n, sid):
         self.saved[sid] = self.dec.kv.snapshot(slot, n)
@@ -135,9 +136,9 @@ def leader_engine(dec, tokenizer, model_name: str, chan: Lockstep):
             self._send("reset", slot)
             super().reset(slot)
 
-        def share_prefix(self, src, dst, n):
-            self._send("share_prefix", src, dst, n)
-            return super().share_prefix(src, dst, n)
+        def share_prefix(self, src, dst, n, have=0):
+            self._send("share_prefix", src, dst, n, have)
+            return super().share_prefix(src, dst, n, have)
 
         def snapshot(self, slot, ids):
             if not len(ids):
@@ -224,7 +225,9 @@ def main(argv=None) -> int:
     ap.add_argument("--slot-ctx", type=int, default=4096)
     a = ap.parse_args(argv)
     ctl = init_groups(a.rank, a.world, a.device, a.port)
-    eng, _, _ = open_rank(a.model, a.rank, a.world, a.device, a.slots, a.slot_ctx)
+    from ..utils import levers
+    eng, _, _ = open_rank(a.model, a.rank, a.world, a.device, a.slots, a.slot_ctx,
+                          fused=bool(levers.get("BLOOMERY_FUSED_COMM")), use_graphs=bool(levers.get("BLOOMERY_GRAPHS")))
     dist.barrier()
     n = follow(_RankOps(eng), Lockstep(ctl), on_error=lambda op, exc: print(f"rank {a.rank}: {op}: {exc}", file=sys.stderr))
     print(f"rank {a.rank}: {n} mirrored calls", file=sys.stderr)

@@ -172,6 +172,10 @@ class DecodeEngine:
         from .watchdog import Waits, Watchdog
         self.waits = Waits()
         self.watchdog: Optional[Watchdog] = None      # attached by the server; names a wedged wait, never kills
+        from ..utils import levers
+        self.check_finite = bool(levers.get("BLOOMERY_CHECK_FINITE"))   # read the residual rows back after every pass
+        self.step_stats = bool(levers.get("BLOOMERY_STEP_STATS"))       # one stderr record every 256 passes
+        self.route_trace = None                       # a RouteTraceWriter when BLOOMERY_ROUTE_TRACE names a directory
         self.mtp_on = False                           # run the draft layer beside every pass (``enable_mtp``)
         self.mtp_draft: Dict[int, Tuple[int, int]] = {}   # slot -> (number of ids the draft extends, drafted id)
 
@@ -456,6 +460,14 @@ class DecodeEngine:
             self._after_pass(len(rows))
             for slot, _, pos in rows:
                 self.slot_len[slot] = max(self.slot_len[slot], pos + 1)
+            if self.check_finite and not bool(torch.isfinite(self.x[:len(rows)]).all()):
+                self.poisoned = (self.spec.n_layer << 8) | 2
+                raise EngineFault(self.poisoned)
+            if self.step_stats and self.steps % 256 == 0:
+                from ..utils import records
+                records.write("step_stats", steps=self.steps, card_wait_s=round(self.waits.ns.get("card", 0) / 1e9, 4),
+                              kv_free_pages=self.kv.free_pages(), kv_spills=self.kv.n_spills,
+                              free_bytes=int(torch.cuda.mem_get_info(self.device)[0]))
             if not head:
                 return []
             out = self.read_tokens(len(rows))

@@ -20,6 +20,13 @@ class OutOfPages(RuntimeError):
     pass
 
 
+def snap_ready(snap) -> None:
+    """Wait until a snapshot's device-to-host copies have landed (call before any host-side read of its tensors)."""
+    ev = snap.pop("_ev", None) if isinstance(snap, dict) else None
+    if ev is not None:
+        ev.synchronize()
+
+
 class KvPool:
     def __init__(self, n_layer: int, n_kv: int, head_dim: int, n_pages: int, n_slots: int, max_pages_per_slot: int,
                  device, dtype=torch.float16, v_dim: Optional[int] = None):
@@ -48,6 +55,7 @@ class KvPool:
         self.n_spills = 0
         self.n_unspills = 0
         self.allow_spill = True
+        self.floor_positions = 0        # a pool that holds fewer positions than this never spills (BLOOMERY_KV_FLOOR)
 
     @property
     def bytes(self) -> int:
@@ -63,7 +71,7 @@ class KvPool:
     def _spill_one(self) -> bool:
         victims = [s for s in range(self.n_slots) if self.pages[s] and s not in self.protect
                    and all(self.refs[p] == 1 for p in self.pages[s])]
-        if not victims or not self.allow_spill:
+        if not victims or not self.allow_spill or self.n_pages * PAGE < self.floor_positions:
             return False
         s = min(victims, key=lambda v: self.stamp[v])
         n = len(self.pages[s]) * PAGE
@@ -87,29 +95,41 @@ class KvPool:
             self.free.append(pg)
 
     def ensure(self, slot: int, n_positions: int) -> None:
-        """Back positions [0, n_positions) of a slot with pages."""
+        """Back positions [0, n_positions) of a slot with pages.  The slot itself is never the spill victim of
+        its own request: when only its pages could be taken, the pool is out of pages."""
         need = (n_positions + PAGE - 1) // PAGE
         if need > self.max_pages:
             raise OutOfPages(f"slot {slot}: {n_positions} positions exceed the slot context")
-        if slot in self.spilled:
-            snap, n = self.spilled.pop(slot)
-            self.protect.add(slot)
-            self.restore(slot, snap, n)
-            self.n_unspills += 1
-        self.touch(slot)
-        pl = self.pages[slot]
-        while len(pl) < need:
-            pg = self._take()
-            self.table_host[slot, len(pl)] = pg
-            pl.append(pg)
-            self.dirty = True
+        mine = slot not in self.protect
+        self.protect.add(slot)
+        try:
+            if slot in self.spilled:
+                snap, n = self.spilled.pop(slot)
+                self.restore(slot, snap, n)
+                self.n_unspills += 1
+            self.touch(slot)
+            pl = self.pages[slot]
+            while len(pl) < need:
+                pg = self._take()
+                self.table_host[slot, len(pl)] = pg
+                pl.append(pg)
+                self.dirty = True
+        finally:
+            if mine:
+                self.protect.discard(slot)
 
     def own(self, slot: int, position: int) -> None:
         """Copy-on-write: make the page holding ``position`` private before it is written."""
         i = position // PAGE
         pl = self.pages[slot]
         if i < len(pl) and self.refs[pl[i]] > 1:
-            new = self._take()
+            mine = slot not in self.protect
+            self.protect.add(slot)
+            try:
+                new = self._take()
+            finally:
+                if mine:
+                    self.protect.discard(slot)
             self.k[:, new].copy_(self.k[:, pl[i]])
             self.v[:, new].copy_(self.v[:, pl[i]])
             self._drop(pl[i])
@@ -136,13 +156,19 @@ class KvPool:
     def release(self, slot: int) -> None:
         self.truncate(slot, 0)
 
-    def share_prefix(self, src: int, dst: int, n_positions: int) -> int:
-        """Map the whole pages of ``src`` covering [0, n_positions) into ``dst``; returns positions shared."""
-        self.release(dst)
+    def share_prefix(self, src: int, dst: int, n_positions: int, have: int = 0) -> int:
+        """Map the whole pages of ``src`` covering [0, n_positions) into ``dst``; returns positions shared.
+        Only whole pages can be mapped, so the result is rounded down to a page; when that is no more than the
+        ``have`` positions ``dst`` already holds of the same prefix, ``dst`` is left untouched and 0 is returned."""
+        if (n_positions // PAGE) * PAGE <= have:
+            return 0
         if src in self.spilled:
-            self.protect.add(dst)
             self.ensure(src, 1)              # bring the source back before its pages are mapped twice
         full = min(n_positions // PAGE, len(self.pages[src]))
+        if full * PAGE <= have:
+            return 0
+        self.release(dst)
+        self.spilled.pop(dst, None)
         for i in range(full):
             pg = self.pages[src][i]
             self.refs[pg] += 1
@@ -172,10 +198,18 @@ class KvPool:
         v = torch.empty((self.n_layer, n_pg, self.n_kv, PAGE, self.v.shape[-1]), dtype=self.v.dtype, pin_memory=pin)
         k.copy_(self.k.index_select(1, idx), non_blocking=True)
         v.copy_(self.v.index_select(1, idx), non_blocking=True)
-        return {"k": k, "v": v, "n": torch.tensor(n_positions)}
+        snap = {"k": k, "v": v, "n": torch.tensor(n_positions)}
+        if pin:
+            # the two copies run behind the caller on the stream: anyone who reads the host bytes waits on this first
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            snap["_ev"] = ev
+        return snap
 
     def restore(self, slot: int, snap: Dict[str, torch.Tensor], n_positions: int) -> None:
         n_positions = min(n_positions, int(snap["n"]))
+        if (n_positions + PAGE - 1) // PAGE < snap["k"].shape[1]:
+            snap_ready(snap)                 # a partial restore slices on the host: the bytes must have landed
         self.spilled.pop(slot, None)
         self.release(slot)
         self.ensure(slot, n_positions)

@@ -30,7 +30,14 @@ from ..ops import gemm as G
 from .kv import PAGE
 
 
-POISON = os.environ.get("BLOOMERY_POISON_SCRATCH", "0") == "1"
+POISON = None          # None: follow the BLOOMERY_POISON lever; tests set True / False
+
+
+def _poison() -> bool:
+    if POISON is not None:
+        return bool(POISON)
+    from ..utils import levers
+    return bool(levers.get("BLOOMERY_POISON"))
 
 
 class GemmPrefill:
@@ -54,7 +61,7 @@ class GemmPrefill:
         b = self._buf.get(name)
         if b is None or b.numel() < n or b.dtype != dtype:
             b = torch.empty(n, dtype=dtype, device=self.e.device)
-            if POISON:                      # scratch starts as NaN / -1: a read of something never written shows at once
+            if _poison():                   # scratch starts as NaN / -1: a read of something never written shows at once
                 b.fill_(float("nan") if dtype.is_floating_point else -1)
             self._buf[name] = b
         return b[:n].view(*shape)

@@ -1,7 +1,7 @@
 """Expert placement at run time: cold routed experts in pinned host RAM, the most-called
 ones promoted into HBM slots on a side stream, cold hits served by the CPU leg.
 
-Pieces (``SURVEY`` names in the reference: ``crates/runtime/src/swaprule.rs`` rule,
+Pieces (in the reference: ``crates/runtime/src/swaprule.rs`` rule,
 ``crates/gpu/src/host/{swap,lane}.rs`` machine, ``host/{mod,step,handoff}.rs`` host tier):
 
 * :class:`ResidencyRule` -- pure host logic.  Heat of every expert is a decayed count of the

@@ -45,7 +45,10 @@ class PromptTiming:
 
 class HostProfile:
     def __init__(self, level: Optional[int] = None):
-        self.level = int(os.environ.get("BLOOMERY_PROFILE", "0")) if level is None else level
+        if level is None:
+            from ..utils import levers
+            level = int(levers.get("BLOOMERY_PROFILE"))
+        self.level = level
         self.totals: Dict[str, float] = {}
         self.calls: Dict[str, int] = {}
 

@@ -35,6 +35,8 @@ def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, fre
     never cut (refused with the largest that fits); 1,024 MiB margin per GPU."""
     pl = flags.placement(opts, n_visible, spec.n_layer)
     margin = int(levers.get("BLOOMERY_CARD_MARGIN"))
+    budget = int(levers.get("BLOOMERY_CARD_BUDGET"))       # HBM bytes routed experts may take per GPU (0 = what fits)
+    host_room = int(levers.get("BLOOMERY_HOST_ROOM"))      # pinned host bytes cold experts may take (0 = as needed)
     par = opts.get("parallel", "auto")
     n_slots = 4 if par == "auto" else int(par)
     if n_slots < 1:
@@ -46,6 +48,16 @@ def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, fre
         dev_free = min(free_bytes[d] for d in pl.devices)
         share = weights_bytes // (len(pl.devices) if pl.mode == "tp" else 1)
         room = dev_free - margin - share - (2 << 30)
+        ebytes = int(opts.get("_expert_bytes") or weights_bytes * 0.9)
+        over_budget = budget > 0 and spec.is_moe and ebytes // max(1, len(pl.devices) if pl.mode == "tp" else 1) > budget
+        if over_budget and pl.host_experts == "none":
+            # the expert budget is binding: as many experts per layer as it pays for stay on the card, the rest page from the host
+            per_expert = ebytes // max(1, spec.n_expert)
+            resident = max(0, budget // max(1, per_expert)) // 4 * 4
+            pl.host_experts = f"fit:{min(resident, spec.n_expert)}"
+            room = dev_free - margin - (weights_bytes - ebytes) - resident * per_expert - (2 << 30)
+        if host_room > 0 and pl.host_experts != "none" and ebytes > host_room:
+            raise Refusal(Code.NO_FIT, f"cold experts need {ebytes >> 20} MiB of pinned host memory, BLOOMERY_HOST_ROOM allows {host_room >> 20} MiB")
         if room <= 0 and pl.host_experts == "none" and pl.fit and spec.is_moe:
             # -fit on: keep as many routed experts per layer on the card as fit, the rest on the host
             expert_bytes = weights_bytes * 0.9 if not opts.get("_expert_bytes") else opts["_expert_bytes"]
@@ -179,6 +191,8 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
         records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
         tk, tsrc, bos, eos = surface(handle)
         return CpuEngine(w, tk, plan["n_slots"], plan["slot_ctx"], name), tsrc, bos, eos
+    from ..ops import host_ops
+    host_ops.pool_configure(int(levers.get("BLOOMERY_THREADS")), bool(levers.get("BLOOMERY_PIN")), int(levers.get("BLOOMERY_SPIN")))
     K.set_pdl(bool(levers.get("BLOOMERY_PDL")))
     K.set_flash_mma(bool(levers.get("BLOOMERY_FLASH_MMA")))
     graphs = bool(levers.get("BLOOMERY_GRAPHS"))
@@ -187,11 +201,11 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
         if kind != "gguf":
             raise Refusal(Code.UNSUPPORTED, "several GPUs in lockstep are served from GGUF files; load the folder on one GPU")
         from ..parallel import serve_tp as TP
-        port = int(os.environ.get("BLOOMERY_TP_PORT", "0")) or (29600 + os.getpid() % 2000)
+        port = int(levers.get("BLOOMERY_TP_PORT")) or (29600 + os.getpid() % 2000)
         followers = TP.spawn_followers(path, pl.devices, port, plan["n_slots"], plan["slot_ctx"])
         ctl = TP.init_groups(0, len(pl.devices), pl.devices[0], port)
         dec, _, handle = TP.open_rank(path, 0, len(pl.devices), pl.devices[0], plan["n_slots"], plan["slot_ctx"],
-                                      use_graphs=graphs)
+                                      fused=bool(levers.get("BLOOMERY_FUSED_COMM")), use_graphs=graphs)
         import torch.distributed as dist
         dist.barrier()
         records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
@@ -221,9 +235,16 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
         else:
             from ..runtime.engine import DecodeEngine
             dec = DecodeEngine(w, **kw)
-        dec.ubatch = int(opts.get("ubatch") or 4096)
-        if opts.get("prefill") == "steps":
+        dec.ubatch = int(opts.get("ubatch") or levers.get("BLOOMERY_UBATCH"))
+        if opts.get("prefill") == "steps" or str(levers.get("BLOOMERY_PREFILL")) == "steps":
             dec.gemm_threshold = 0
+        if str(levers.get("BLOOMERY_KV_HOST")) != "spill":
+            dec.kv.allow_spill = False
+        dec.kv.floor_positions = int(levers.get("BLOOMERY_KV_FLOOR"))
+        trace_dir = str(levers.get("BLOOMERY_ROUTE_TRACE"))
+        if trace_dir and spec.is_moe:
+            from ..runtime.route_trace import RouteTraceWriter
+            dec.route_trace = RouteTraceWriter(os.path.join(trace_dir, f"{name}.blrt"), spec.n_layer, spec.n_used)
         tk, tsrc, bos, eos = surface(handle)
         eng = GpuEngine(dec, tk, name)
     from ..runtime.watchdog import Watchdog
@@ -302,11 +323,13 @@ def main(argv: Optional[List[str]] = None) -> int:
         draft = str(levers.get("BLOOMERY_DRAFT")).lower()
         if draft == "ngram" and server.state.worker is not None:
             from ..runtime.speculative import NgramDraft, WidthChooser
-            server.state.worker.enable_drafting(NgramDraft(), WidthChooser())
+            width = int(levers.get("BLOOMERY_MTP_WIDTH")) or 7
+            server.state.worker.enable_drafting(NgramDraft(), WidthChooser(max_width=max(1, min(width, 7))))
         elif draft in ("mtp", "auto") and server.state.worker is not None and getattr(getattr(eng, "dec", None), "n_mtp", 0):
             from ..runtime.speculative import MtpDraft, WidthChooser
             if eng.dec.enable_mtp():
-                server.state.worker.enable_drafting(MtpDraft(eng), WidthChooser(max_width=1))
+                width = int(levers.get("BLOOMERY_MTP_WIDTH")) or 1
+                server.state.worker.enable_drafting(MtpDraft(eng), WidthChooser(max_width=max(1, min(width, 7))))
         return server.wait()
     except _PlanOnly:
         return server.stop()

@@ -45,7 +45,9 @@ class Engine:
         raise NotImplementedError
     def cut(self, slot: int, n: int) -> None: ...
     def reset(self, slot: int) -> None: ...
-    def share_prefix(self, src: int, dst: int, n: int) -> int:
+    def share_prefix(self, src: int, dst: int, n: int, have: int = 0) -> int:
+        """Share ``src``'s first ``n`` positions with ``dst``; ``have`` = positions of the same prefix ``dst`` already
+        holds.  Returns the positions ``dst`` now shares, or 0 with ``dst`` untouched when that would not beat ``have``."""
         return 0
     def snapshot(self, slot: int, ids: Sequence[int]) -> Optional[Saved]:
         return None
@@ -122,8 +124,10 @@ class MockEngine(Engine):
         self.prompt_len[slot] = 0
         self.fresh[slot] = True
 
-    def share_prefix(self, src, dst, n):
+    def share_prefix(self, src, dst, n, have=0):
         n = min(n, len(self.seq[src]))
+        if n <= have:
+            return 0
         self.seq[dst] = self.seq[src][:n]
         self.prompt_len[dst] = n
         self.fresh[dst] = True
@@ -262,10 +266,11 @@ class GpuEngine(Engine):
         d = getattr(self.dec, "mtp_draft", {}).get(slot)
         return [int(d[1])] if d is not None and d[0] == n_ids else []
 
-    def share_prefix(self, src, dst, n):
-        got = self.dec.kv.share_prefix(src, dst, n)
-        self.dec.slot_len[dst] = got
-        self.dec.kv.sync_table()
+    def share_prefix(self, src, dst, n, have=0):
+        got = self.dec.kv.share_prefix(src, dst, n, have)
+        if got > 0:
+            self.dec.slot_len[dst] = got
+            self.dec.kv.sync_table()
         return got
 
     def snapshot(self, slot, ids):
@@ -347,9 +352,11 @@ class CpuEngine(Engine):
     def reset(self, slot):
         self.models[slot].reset()
 
-    def share_prefix(self, src, dst, n):
+    def share_prefix(self, src, dst, n, have=0):
         a, b = self.models[src], self.models[dst]
         n = min(n, a.n_past)
+        if n <= have:
+            return 0
         b.k = [k[:n].clone() for k in a.k]
         b.v = [v[:n].clone() for v in a.v]
         b.n_past = n

@@ -18,9 +18,23 @@ MAGIC = b"BLSLOT01"
 VERSION = 1
 
 
+def _landed(payload) -> None:
+    """A snapshot's device-to-host copies run behind the caller; wait for them before the bytes are serialised."""
+    from ..runtime.kv import snap_ready
+    if isinstance(payload, dict):
+        snap_ready(payload)
+        for v in payload.values():
+            if isinstance(v, (dict, list)):
+                _landed(v)
+    elif isinstance(payload, list):
+        for v in payload:
+            _landed(v)
+
+
 def write_slot_file(path: str, n_vocab: int, ids: List[int], saved: Saved) -> int:
     import torch
     buf = io.BytesIO()
+    _landed(saved.payload if saved is not None else None)
     torch.save(saved.payload if saved is not None else None, buf)
     blob = buf.getvalue()
     with open(path, "wb") as f:

@@ -137,7 +137,7 @@ class Worker(threading.Thread):
                         if n > dn:
                             donor, dn = other, n
                 if donor is not None:
-                    got_n = self.engine.share_prefix(donor.id, slot.id, dn)
+                    got_n = self.engine.share_prefix(donor.id, slot.id, dn, keep)
                     if got_n > keep:
                         slot.ids = list(donor.ids[:got_n])
                         keep = got_n

@@ -14,6 +14,7 @@ KINDS: Dict[str, List[str]] = {
     "parallel": ["slots", "slot_ctx"],
     "setup": ["phase", "seconds", "winner", "raced", "resident_per_layer", "host"],
     "watchdog": ["model", "site", "seconds"],
+    "step_stats": ["steps", "card_wait_s", "kv_free_pages", "kv_spills", "free_bytes"],
     "request": ["id", "route", "slot", "prompt_tokens", "cached_tokens", "predicted_tokens", "prompt_ms",
                 "predicted_ms", "status"],
     "progress": ["slot", "tokens", "tok_per_s"],

@@ -302,3 +302,47 @@ def test_host_profile_levels_and_heat_files(tmp_path):
     assert load_heat(path, 2, 3, model="m") == [[1, 0, 5], [2, 2, 2]]
     assert load_heat(path, 2, 4) is None and load_heat(path, 2, 3, model="other") is None
     assert load_heat(str(tmp_path / "none.json"), 2, 3) is None
+
+
+def test_kv_pool_never_spills_the_slot_that_is_asking():
+    """A pool smaller than one slot's context: the requester must not become its own spill victim."""
+    from bloomery_b200.runtime.kv import PAGE, KvPool, OutOfPages
+    kv = KvPool(n_layer=1, n_kv=1, head_dim=8, n_pages=2, n_slots=2, max_pages_per_slot=4, device="cpu")
+    kv.protect = set()                            # as after a pass over other slots
+    kv.ensure(0, 2 * PAGE)
+    with pytest.raises(OutOfPages):
+        kv.ensure(0, 3 * PAGE)                    # only slot 0 holds pages and it is the one growing
+    assert 0 not in kv.spilled and len(kv.pages[0]) == 2 and kv.n_spills == 0
+    assert 0 not in kv.protect                    # the self-protection ends with the call
+
+
+def test_share_prefix_leaves_a_slot_alone_when_whole_pages_do_not_beat_its_own_prefix():
+    from bloomery_b200.runtime.kv import PAGE, KvPool
+    kv = KvPool(n_layer=1, n_kv=1, head_dim=8, n_pages=8, n_slots=2, max_pages_per_slot=4, device="cpu")
+    kv.ensure(0, 120)                             # donor: common prefix 120 -> one whole page (64) can be mapped
+    kv.ensure(1, 100)                             # the slot's own prefix: 100 positions
+    mine = list(kv.pages[1])
+    assert kv.share_prefix(0, 1, 120, have=100) == 0
+    assert kv.pages[1] == mine                    # untouched: its 100 positions are still there
+    assert kv.share_prefix(0, 1, 120, have=10) == PAGE
+    assert kv.pages[1] == kv.pages[0][:1] and kv.refs[kv.pages[0][0]] == 2
+    # copy-on-write: the donor is cut inside the shared page and appends; the sharer's page keeps its bytes
+    kv.k[:, kv.pages[0][0]] = 7.0
+    kv.truncate(0, 30)
+    kv.own(0, 30)
+    assert kv.pages[0][0] != kv.pages[1][0] and float(kv.k[0, kv.pages[1][0]].mean()) == 7.0
+    assert float(kv.k[0, kv.pages[0][0]].mean()) == 7.0      # the private copy starts from the shared bytes
+
+
+def test_levers_registry_rows_are_all_read_somewhere():
+    """Every registry row is read by the package (a declared lever that nothing reads is refused here)."""
+    import os, re
+    from bloomery_b200.utils import levers
+    root = os.path.join(os.path.dirname(levers.__file__), "..")
+    text = ""
+    for d, _, files in os.walk(root):
+        for f in files:
+            if f.endswith((".py", ".cpp", ".h", ".cu", ".cuh")) and not d.endswith("utils") or f in ("flags.py",):
+                text += open(os.path.join(d, f), errors="ignore").read()
+    dead = [l.name for l in levers.REGISTRY if not re.search(r'["\']' + l.name + r'["\']', text)]
+    assert dead == [], dead
