@@ -85,6 +85,8 @@ def main() -> int:
     ap.add_argument("--flash-mma", action="store_true", help="decode attention segments on tensor-core tiles")
     ap.add_argument("--ttft", type=int, default=4096, help="also time a prompt of this many tokens (0 = skip)")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-staged", dest="no_staged", action="store_true",
+                    help="register-streaming decode kernels instead of the shared-memory staged ones")
     ap.add_argument("--nccl-baseline", dest="nccl_baseline", action="store_true",
                     help="N > 1: do the per-layer reductions with NCCL all_reduce instead of the fused kernels")
     args = ap.parse_args()
@@ -114,6 +116,8 @@ def main() -> int:
         _K.set_flash_mma(True)
     if args.no_pdl:
         K.set_pdl(False)
+    if args.no_staged:
+        K.set_staged(False)
     spec = NAMED[args.model]()
     steps, warm = args.steps, max(3, args.warmup)
     t0 = time.time()
@@ -188,6 +192,36 @@ def main() -> int:
         extra["ttft_ms_p50"] = sorted(ts)[1]
         extra["ttft_prompt_tokens"] = args.ttft
         extra["prefill_tok_s"] = args.ttft / (sorted(ts)[1] / 1e3)
+        # decode behind that prompt (the published reference figure is decode after 4,096 ids)
+        n_deep = min(steps, 64)
+        tk = eng.decode_chain(0, 1, args.ttft, 4)
+        eng.kv.ensure(0, args.ttft + 4 + n_deep + 1)
+        eng.set_rows([(0, tk[-1], args.ttft + 4)])
+        eng.counters[2:3].zero_()
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        d0.record()
+        for _ in range(n_deep):
+            eng.launch(1, True, True)
+        d1.record()
+        torch.cuda.synchronize()
+        eng.check_fault()
+        deep = n_deep / (d0.elapsed_time(d1) / 1e3)
+        extra["decode_tok_s_after_prompt"] = {"context": args.ttft, "value": deep, "steps": n_deep, "vs_baseline": deep / BASELINE_TOKS}
+
+    # bytes of weights one decode step has to read: everything but the routed experts it did not choose
+    active = 0
+    for name, qw in w.q.items():
+        if name == "token_embd.weight" and "output.weight" in w.q:
+            continue
+        active += qw.n_bytes * (spec.n_used / spec.n_expert if "_exps." in name else 1.0)
+    gbs = active / (ms / steps / 1e3) / 1e9
+    peak, peak_src = 6650.0, "fallback"
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as fh:
+            peak, peak_src = float(json.load(fh)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        pass
 
     line = {
         "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
@@ -196,11 +230,13 @@ def main() -> int:
         "data": "synthetic: seeded random token ids, random-init N(0,0.02) weights quantised Q4_K_M on the card",
         "config": {"model": spec.name, "global_batch": 1, "seq_len": args.prompt + warm + steps,
                    "prompt_tokens": args.prompt, "parallelism": "single", "l2": "weights (17 GB) exceed L2; no flush needed",
-                   "graph": "one CUDA graph per decode step", "pdl": not args.no_pdl, "flash_mma": bool(args.flash_mma)},
+                   "graph": "one CUDA graph per decode step", "pdl": not args.no_pdl, "flash_mma": bool(args.flash_mma),
+                   "staged_kernels": not args.no_staged},
         "clocks": sampler.summary(), "e2e": e2e,
         "gpu_launches": eng.launches_per_step * steps, "launches_per_step": eng.launches_per_step,
         "ttft_ms_prompt": ttft_prompt_ms, "load_s": t_load, "weights_gb": w.n_bytes / 1e9,
-        "hbm_gbs_effective": None, **extra,
+        "active_weight_gb_per_step": active / 1e9, "hbm_gbs_effective": gbs,
+        "roofline_frac": gbs / peak, "roofline_peak": f"{peak:.0f} GB/s HBM copy rate ({peak_src})", **extra,
     }
     print(json.dumps(line))
     return 0

@@ -18,128 +18,11 @@
 // and qwen3moe_qkv_q4k / qwen3moe_o_resid_q4k in crates/gpu/src/arch/qwen3moe/proj.rs:
 // fixed lane split and a fixed xor-butterfly, so reruns are bit-identical and each row of
 // an m-row call equals its own 1-row call.
-#include "common.cuh"
+#include "gemv_common.cuh"
 
 namespace bl {
 
 int g_use_pdl = 1;
-
-struct GemvSeg {
-  const uint8_t* w;
-  int rows;
-  int wtype;
-  int blk0;        // first block of this segment
-  int nblk;        // blocks that share this segment's rows evenly
-  long row_bytes;
-};
-
-struct GemvArgs {
-  GemvSeg seg[4];
-  int nseg;
-  int K;
-  int M;
-  const float* x;          // input A: fp32 rows, RMS-normalised and quantised in the prologue
-  long x_stride;
-  const float* gain;
-  float eps;
-  const int8_t* xq;        // input B: rows already in q8 form
-  const float2* xds;
-  float* out;
-  long out_stride;
-  const float* resid;
-  long resid_stride;
-  unsigned* fault;
-  int layer;
-  ReduceIn red;            // n_ranks > 0: x is "x + sum of every rank's partial rows" (consumer half)
-  PushOut push;            // n_ranks > 0: the result is a partial update pushed to every rank (producer half)
-};
-
-// ---- activation prologue ------------------------------------------------------------
-// sq/sds receive q8(x * gain) WITHOUT the RMS scale; s_scale[m] receives the scale.
-template <int MB, bool FLOATW>
-__device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, float2* sds, float* sx, float* s_scale,
-                                              double* red) {
-  const int K = a.K, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool reduce = a.red.n_ranks > 0;
-  __shared__ int s_gave_up;
-  ReduceWait rw{0u, 0ull, &s_gave_up};
-  if (reduce) {
-    if (tid == 0) s_gave_up = (a.red.fault && *a.red.fault != 0xFFFFFFFFu) ? 1 : 0;   // a poisoned engine no longer waits
-    __syncthreads();
-    rw.epoch = site_epoch(a.red.step, a.red.sites_per_step, a.red.site_index);
-  }
-#pragma unroll 1
-  for (int m = 0; m < MB; ++m) {
-    const int ms = m < a.M ? m : a.M - 1;
-    const float* x = a.x + (long)ms * a.x_stride;
-    float ss = 0.f;
-    for (int i0 = tid * 8; i0 < K; i0 += 256 * 8) {
-      float4 x0, x1;
-      if (reduce) {
-        x0 = *reinterpret_cast<const float4*>(x + i0); x1 = *reinterpret_cast<const float4*>(x + i0 + 4);
-        float acc8[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-        reduce_sum8(a.red, rw, ms, i0, acc8);
-        x0 = make_float4(acc8[0], acc8[1], acc8[2], acc8[3]); x1 = make_float4(acc8[4], acc8[5], acc8[6], acc8[7]);
-        if (blockIdx.x == 0 && m < a.M) {
-          *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0) = x0;
-          *reinterpret_cast<float4*>(a.red.x_out + (long)m * a.red.x_out_stride + i0 + 4) = x1;
-        }
-      } else {
-        x0 = *reinterpret_cast<const float4*>(x + i0); x1 = *reinterpret_cast<const float4*>(x + i0 + 4);
-      }
-      float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gain + i0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gain + i0 + 4));
-      float v[8] = {x0.x * g0.x, x0.y * g0.y, x0.z * g0.z, x0.w * g0.w, x1.x * g1.x, x1.y * g1.y, x1.z * g1.z, x1.w * g1.w};
-      ss += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      const float d = amax / 127.0f, inv = d > 0.f ? 1.0f / d : 0.f;
-      int q[8], sum = 0;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { q[j] = max(-127, min(127, __float2int_rn(v[j] * inv))); sum += q[j]; }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      uint2 packed;
-      packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((unsigned)(q[3] & 0xFF) << 24);
-      packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((unsigned)(q[7] & 0xFF) << 24);
-      *reinterpret_cast<uint2*>(sq + (long)m * K + i0) = packed;
-      if ((tid & 3) == 0) sds[(long)m * (K / 32) + i0 / 32] = make_float2(d, d * (float)sum);
-      if (FLOATW) {
-        *reinterpret_cast<float4*>(sx + (long)m * K + i0) = make_float4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<float4*>(sx + (long)m * K + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
-      }
-    }
-    double tot = warp_sum_d((double)ss);
-    if (lane == 0) red[m * 8 + warp] = tot;
-  }
-  __syncthreads();
-  if (tid < MB) {
-    double all = 0.0;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) all += red[tid * 8 + w];
-    s_scale[tid] = 1.0f / sqrtf((float)(all / (double)K) + a.eps);
-  }
-  __syncthreads();
-}
-
-template <int MB>
-__device__ __forceinline__ void prologue_q8in(const GemvArgs& a, int8_t* sq, float2* sds, float* s_scale) {
-  const int K = a.K, tid = threadIdx.x;
-  for (int i = tid; i < MB * K / 16; i += 256) {
-    int m = (i * 16) / K;
-    const int ms = m < a.M ? m : a.M - 1;
-    reinterpret_cast<uint4*>(sq)[i] = reinterpret_cast<const uint4*>(a.xq + (long)ms * K)[i - m * (K / 16)];
-  }
-  for (int i = tid; i < MB * (K / 32); i += 256) {
-    int m = i / (K / 32);
-    const int ms = m < a.M ? m : a.M - 1;
-    sds[i] = a.xds[(long)ms * (K / 32) + (i - m * (K / 32))];
-  }
-  if (tid < MB) s_scale[tid] = 1.0f;
-  __syncthreads();
-}
 
 // ---- the rows of one warp ---------------------------------------------------------------
 // A warp owns rows [r_lo, r_hi) of its segment and walks them R at a time; every load of a

@@ -13,7 +13,7 @@
 // experts.rs:36-45); the elsewhere-sentinel for slots another tier serves
 // (crates/gpu/src/kquant/sel.rs doc).  The completion counter instead of a grid barrier
 // is the reference's measured choice (docs/gpu-design.md:52-64).
-#include "common.cuh"
+#include "route.cuh"
 
 namespace bl {
 
@@ -22,128 +22,6 @@ static inline bool is_plane_family(int t) {
   return t == WT_NVFP4 || t == WT_FP8_B128 || t == WT_Q4_0 || t == WT_Q4_1 || t == WT_Q5_0 || t == WT_Q5_1 || t == WT_Q2_K || t == WT_Q3_K;
 }
 
-
-constexpr int kMaxExperts = 512;
-constexpr int kMaxTopK = 16;
-
-struct RouterArgs {
-  const float* x; long x_stride;       // [M, K] residual stream
-  const float* gain; float eps;
-  const uint8_t* w; int wtype;         // [E, K] F32 / F16 / BF16
-  int K, E, M;
-  float* logits;                       // [M, E]
-  int8_t* xq_out; float2* xds_out;     // q8 of the normed rows [M, K]
-  float* xn_out;                       // optional fp32 normed rows [M, K]
-  unsigned* fault; int layer;
-  ReduceIn red;                        // n_ranks > 0: x = x + sum of every rank's partial rows
-};
-
-// Routing parameters shared by the router launch and its consumers.
-struct RouteParams {
-  const float* logits;   // [M, E]
-  const float* bias;     // [E] selection bias (sigmoid mode) or null
-  int E, top_k, mode, renorm;
-  float scale;
-  int n_group, topk_group;
-};
-
-// Block-wide routing of one row by rank counting: every thread owns up to two experts,
-// reads all scores from shared memory and counts how many beat its own (larger score, or
-// equal score at a smaller id); an expert of rank r < top_k is slot r.  No serial arg-max
-// rounds, so it is short enough to run redundantly in every consumer block.  Softmax
-// weights need only the chosen logits: w_j = exp(l_j - l_top) / sum over the chosen
-// (renormalised) or over all experts (not renormalised).
-struct __align__(16) RouteShared {
-  float sc[kMaxExperts];
-  float wv[kMaxExperts];
-  float gs[16];
-  int ids[kMaxTopK];
-  float wraw[kMaxTopK];
-  float total;
-};
-
-__device__ __forceinline__ bool route_block(const RouteParams& p, int m, RouteShared& sh, int& my_id, float& my_w) {
-  const int tid = threadIdx.x, nthr = blockDim.x;
-  bool nonfinite = false;
-  for (int e = tid; e < p.E; e += nthr) {
-    const float l = __ldcg(p.logits + (long)m * p.E + e);
-    if (!isfinite(l)) nonfinite = true;
-    if (p.mode == 0) { sh.sc[e] = l; sh.wv[e] = l; }
-    else { const float sg = 1.0f / (1.0f + expf(-l)); sh.wv[e] = sg; sh.sc[e] = sg + (p.bias ? p.bias[e] : 0.f); }
-  }
-  if (tid < kMaxTopK) { sh.ids[tid] = 0; sh.wraw[tid] = 0.f; }
-  if (__syncthreads_or(nonfinite)) { my_id = 0; my_w = __int_as_float(0x7fc00000); return false; }
-  if (p.n_group > 1) {
-    const int gsz = p.E / p.n_group;
-    if (tid < p.n_group) {
-      float b1 = -INFINITY, b2 = -INFINITY;
-      for (int i = 0; i < gsz; ++i) { const float v = sh.sc[tid * gsz + i]; if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v; }
-      sh.gs[tid] = b1 + b2;
-    }
-    __syncthreads();
-    bool drop[2] = {false, false};
-    int c = 0;
-    for (int e = tid; e < p.E; e += nthr, ++c) {
-      const int g = e / gsz;
-      const float mine = sh.gs[g];
-      int rank = 0;
-      for (int o = 0; o < p.n_group; ++o) rank += (sh.gs[o] > mine || (sh.gs[o] == mine && o < g)) ? 1 : 0;
-      drop[c & 1] = rank >= p.topk_group;
-    }
-    c = 0;
-    for (int e = tid; e < p.E; e += nthr, ++c) if (drop[c & 1]) sh.sc[e] = -INFINITY;
-    __syncthreads();
-  }
-  for (int e = tid; e < p.E; e += nthr) {
-    const float v = sh.sc[e];
-    if (v == -INFINITY) continue;
-    int rank = 0;
-    for (int o = 0; o < p.E; o += 4) {
-      const float4 q = *reinterpret_cast<const float4*>(sh.sc + o);
-      rank += (q.x > v || (q.x == v && o < e)) ? 1 : 0;
-      rank += (q.y > v || (q.y == v && o + 1 < e)) ? 1 : 0;
-      rank += (q.z > v || (q.z == v && o + 2 < e)) ? 1 : 0;
-      rank += (q.w > v || (q.w == v && o + 3 < e)) ? 1 : 0;
-    }
-    if (rank < p.top_k) { sh.ids[rank] = e; sh.wraw[rank] = sh.wv[e]; }
-  }
-  if (p.mode == 0 && !p.renorm && tid < 32) {
-    double part = 0.0;
-    float top = -INFINITY;
-    for (int e = tid; e < p.E; e += 32) top = fmaxf(top, sh.wv[e]);
-    top = warp_max(top);
-    for (int e = tid; e < p.E; e += 32) part += (double)expf(sh.wv[e] - top);
-    part = warp_sum_d(part);
-    if (tid == 0) sh.total = (float)part;
-  }
-  __syncthreads();
-  const int t = tid & 31;
-  my_id = t < p.top_k ? sh.ids[t] : 0;
-  float w = 0.f;
-  if (t < p.top_k) {
-    if (p.mode == 0) {
-      const float top = sh.wraw[0];
-      w = expf(sh.wraw[t] - top);
-      if (p.renorm) {
-        double sum = 0.0;
-        for (int j = 0; j < p.top_k; ++j) sum += (double)expf(sh.wraw[j] - top);
-        w = w / (float)sum;
-      } else {
-        w = w / sh.total;
-      }
-    } else {
-      w = sh.wraw[t];
-      if (p.renorm) {
-        double sum = 0.0;
-        for (int j = 0; j < p.top_k; ++j) sum += (double)sh.wraw[j];
-        w = w / (float)sum;
-      }
-    }
-    w *= p.scale;
-  }
-  my_w = w;
-  return true;
-}
 
 // grid = E blocks (one expert each), 256 threads.  A thread owns 8 consecutive values per
 // 2048-value chunk; the router row, gain and x are loaded together, the dot product of
@@ -244,9 +122,20 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
     for (int w = 0; w < 8; ++w) { d += s_dot[w][tid]; q += s_ss[w][tid]; }
     const float scale = (float)(1.0 / sqrt(q / (double)K + (double)a.eps));
     s_scale[tid] = scale;
-    if (tid < a.M) a.logits[(long)tid * a.E + e] = d * scale;
+    if (tid < a.M) { a.logits[(long)tid * a.E + e] = d * scale; __threadfence(); }
   }
   __syncthreads();
+  __shared__ int s_last;
+  if (a.ticket) {
+    // every logit of this block is stored: take a ticket; the block that draws the last one routes the rows
+    if (tid == 0) {
+      __threadfence();
+      const unsigned t = atomicAdd(a.ticket + blockIdx.y, 1u);
+      s_last = (t == gridDim.x - 1) ? 1 : 0;
+      if (s_last) a.ticket[blockIdx.y] = 0u;         // zero again for the next launch (graph replay)
+    }
+    __syncthreads();
+  }
   // every block knows the scale; block b publishes 32-value blocks b, b + E, ... of the q8 rows
   if (a.xq_out) {
     const int nb32 = K / 32;
@@ -260,6 +149,25 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
       a.xq_out[(long)m * K + i] = qv;
       if (a.xn_out) a.xn_out[(long)m * K + i] = v;
       if (lane == 0) a.xds_out[(long)m * nb32 + bb] = make_float2(d, sm);
+    }
+  }
+  if (a.ticket && s_last) {
+    __shared__ RouteShared rs;
+    __threadfence();
+    RouteParams p = a.route;
+    p.logits = a.logits;
+    for (int m = 0; m < a.M; ++m) {
+      int id; float w;
+      const bool ok = route_block(p, m, rs, id, w);
+      if (warp == 0) {
+        if (!ok && lane == 0) raise_fault(a.fault, a.layer, FS_ROUTER);
+        if (lane < p.top_k) {
+          a.ids[(long)m * p.top_k + lane] = ok ? id : -3;
+          a.wts[(long)m * p.top_k + lane] = w;
+          if (ok && a.heat) atomicAdd(a.heat + id, 1u);
+        }
+      }
+      __syncthreads();
     }
   }
 }
@@ -522,9 +430,12 @@ using namespace bl;
 extern "C" {
 
 // Router logits (RMS scale applied) for M rows + the q8 form of the normed rows.
+// ticket != null (one zeroed word per group of 8 rows): the launch also routes, i.e. writes ids / wts (and heat).
 int bl_router(const float* x, long x_stride, const float* gain, float eps, const void* w, int wtype,
               int K, int E, int M, float* logits, int8_t* xq_out, float* xds_out, float* xn_out,
-              const void* red_desc, unsigned* fault, int layer, cudaStream_t st) {
+              const void* red_desc, unsigned* fault, int layer,
+              unsigned* ticket, const float* bias, int top_k, int mode, int renorm, float scale, int n_group, int topk_group,
+              int* ids, float* wts, unsigned* heat, cudaStream_t st) {
   BL_REQUIRE(E >= 1 && E <= kMaxExperts, BL_ERR_LIMIT);
   BL_REQUIRE(K % 256 == 0 && M >= 1 && M <= 8 * 65535, BL_ERR_SHAPE);
   BL_REQUIRE(wtype == WT_F32 || wtype == WT_F16 || wtype == WT_BF16, BL_ERR_TYPE);
@@ -533,6 +444,12 @@ int bl_router(const float* x, long x_stride, const float* gain, float eps, const
   a.K = K; a.E = E; a.M = M; a.logits = logits; a.xq_out = xq_out; a.xds_out = (float2*)xds_out; a.xn_out = xn_out;
   a.fault = fault; a.layer = layer;
   if (red_desc) { a.red = *(const ReduceIn*)red_desc; BL_REQUIRE(M <= kMaxRows && a.red.n_ranks <= kMaxRanks && a.red.H == K, BL_ERR_SHAPE); }
+  if (ticket) {
+    BL_REQUIRE(E % 4 == 0 && top_k >= 1 && top_k <= kMaxTopK && top_k <= E && n_group >= 1 && n_group <= 16 && E % n_group == 0 &&
+               topk_group >= 1 && topk_group <= n_group && ids && wts, BL_ERR_SHAPE);
+    a.ticket = ticket; a.ids = ids; a.wts = wts; a.heat = heat;
+    a.route = RouteParams{nullptr, bias, E, top_k, mode, renorm, scale, n_group, topk_group};
+  }
   int mb = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
   dim3 grid(E, (M + mb - 1) / mb);
   switch (mb) {

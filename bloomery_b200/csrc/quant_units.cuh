@@ -103,7 +103,12 @@ BL_HD uint32_t ld32(const uint8_t* p) {
 }
 
 BL_HD u32x4 ld128(const uint8_t* p) {
-#if defined(__CUDA_ARCH__)
+#if defined(__CUDA_ARCH__) && defined(BL_UNITS_GENERIC_LD)
+  // a translation unit that reads weight units out of shared memory defines BL_UNITS_GENERIC_LD: a plain
+  // load works in every address space, the read-only-cache load below only in global memory
+  uint4 v = *reinterpret_cast<const uint4*>(p);
+  return u32x4{v.x, v.y, v.z, v.w};
+#elif defined(__CUDA_ARCH__)
   uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
   return u32x4{v.x, v.y, v.z, v.w};
 #else

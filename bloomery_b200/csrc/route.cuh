@@ -1,0 +1,136 @@
+// Routing shared by the decode MoE kernels: argument blocks and the block-wide top-k by rank counting.
+#pragma once
+#include "common.cuh"
+
+namespace bl {
+
+constexpr int kMaxExperts = 512;
+constexpr int kMaxTopK = 16;
+
+// Routing parameters shared by the router launch and its consumers.
+struct RouteParams {
+  const float* logits;   // [M, E]
+  const float* bias;     // [E] selection bias (sigmoid mode) or null
+  int E, top_k, mode, renorm;
+  float scale;
+  int n_group, topk_group;
+};
+
+struct RouterArgs {
+  const float* x; long x_stride;       // [M, K] residual stream
+  const float* gain; float eps;
+  const uint8_t* w; int wtype;         // [E, K] F32 / F16 / BF16
+  int K, E, M;
+  float* logits;                       // [M, E]
+  int8_t* xq_out; float2* xds_out;     // q8 of the normed rows [M, K]
+  float* xn_out;                       // optional fp32 normed rows [M, K]
+  unsigned* fault; int layer;
+  ReduceIn red;                        // n_ranks > 0: x = x + sum of every rank's partial rows
+  // ticket != null: the block that finishes last (completion ticket, one word per row group, zero between
+  // launches) turns the logits into (ids, weights) for the launches that follow and counts the picks
+  unsigned* ticket;
+  RouteParams route;                   // route.logits is ignored here (the kernel's own logits are routed)
+  int* ids; float* wts;                // [M, top_k]
+  unsigned* heat;                      // optional [E] routed-count histogram
+};
+
+// Block-wide routing of one row by rank counting: every thread owns up to two experts,
+// reads all scores from shared memory and counts how many beat its own (larger score, or
+// equal score at a smaller id); an expert of rank r < top_k is slot r.  No serial arg-max
+// rounds, so it is short enough to run redundantly in every consumer block.  Softmax
+// weights need only the chosen logits: w_j = exp(l_j - l_top) / sum over the chosen
+// (renormalised) or over all experts (not renormalised).
+struct __align__(16) RouteShared {
+  float sc[kMaxExperts];
+  float wv[kMaxExperts];
+  float gs[16];
+  int ids[kMaxTopK];
+  float wraw[kMaxTopK];
+  float total;
+};
+
+__device__ __forceinline__ bool route_block(const RouteParams& p, int m, RouteShared& sh, int& my_id, float& my_w) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  bool nonfinite = false;
+  for (int e = tid; e < p.E; e += nthr) {
+    const float l = __ldcg(p.logits + (long)m * p.E + e);
+    if (!isfinite(l)) nonfinite = true;
+    if (p.mode == 0) { sh.sc[e] = l; sh.wv[e] = l; }
+    else { const float sg = 1.0f / (1.0f + expf(-l)); sh.wv[e] = sg; sh.sc[e] = sg + (p.bias ? p.bias[e] : 0.f); }
+  }
+  if (tid < kMaxTopK) { sh.ids[tid] = 0; sh.wraw[tid] = 0.f; }
+  if (__syncthreads_or(nonfinite)) { my_id = 0; my_w = __int_as_float(0x7fc00000); return false; }
+  if (p.n_group > 1) {
+    const int gsz = p.E / p.n_group;
+    if (tid < p.n_group) {
+      float b1 = -INFINITY, b2 = -INFINITY;
+      for (int i = 0; i < gsz; ++i) { const float v = sh.sc[tid * gsz + i]; if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v; }
+      sh.gs[tid] = b1 + b2;
+    }
+    __syncthreads();
+    bool drop[2] = {false, false};
+    int c = 0;
+    for (int e = tid; e < p.E; e += nthr, ++c) {
+      const int g = e / gsz;
+      const float mine = sh.gs[g];
+      int rank = 0;
+      for (int o = 0; o < p.n_group; ++o) rank += (sh.gs[o] > mine || (sh.gs[o] == mine && o < g)) ? 1 : 0;
+      drop[c & 1] = rank >= p.topk_group;
+    }
+    c = 0;
+    for (int e = tid; e < p.E; e += nthr, ++c) if (drop[c & 1]) sh.sc[e] = -INFINITY;
+    __syncthreads();
+  }
+  for (int e = tid; e < p.E; e += nthr) {
+    const float v = sh.sc[e];
+    if (v == -INFINITY) continue;
+    int rank = 0;
+    for (int o = 0; o < p.E; o += 4) {
+      const float4 q = *reinterpret_cast<const float4*>(sh.sc + o);
+      rank += (q.x > v || (q.x == v && o < e)) ? 1 : 0;
+      rank += (q.y > v || (q.y == v && o + 1 < e)) ? 1 : 0;
+      rank += (q.z > v || (q.z == v && o + 2 < e)) ? 1 : 0;
+      rank += (q.w > v || (q.w == v && o + 3 < e)) ? 1 : 0;
+    }
+    if (rank < p.top_k) { sh.ids[rank] = e; sh.wraw[rank] = sh.wv[e]; }
+  }
+  if (p.mode == 0 && !p.renorm && tid < 32) {
+    double part = 0.0;
+    float top = -INFINITY;
+    for (int e = tid; e < p.E; e += 32) top = fmaxf(top, sh.wv[e]);
+    top = warp_max(top);
+    for (int e = tid; e < p.E; e += 32) part += (double)expf(sh.wv[e] - top);
+    part = warp_sum_d(part);
+    if (tid == 0) sh.total = (float)part;
+  }
+  __syncthreads();
+  const int t = tid & 31;
+  my_id = t < p.top_k ? sh.ids[t] : 0;
+  float w = 0.f;
+  if (t < p.top_k) {
+    if (p.mode == 0) {
+      const float top = sh.wraw[0];
+      w = expf(sh.wraw[t] - top);
+      if (p.renorm) {
+        double sum = 0.0;
+        for (int j = 0; j < p.top_k; ++j) sum += (double)expf(sh.wraw[j] - top);
+        w = w / (float)sum;
+      } else {
+        w = w / sh.total;
+      }
+    } else {
+      w = sh.wraw[t];
+      if (p.renorm) {
+        double sum = 0.0;
+        for (int j = 0; j < p.top_k; ++j) sum += (double)sh.wraw[j];
+        w = w / (float)sum;
+      }
+    }
+    w *= p.scale;
+  }
+  my_w = w;
+  return true;
+}
+
+
+}  // namespace bl

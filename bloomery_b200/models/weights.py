@@ -246,6 +246,16 @@ class Weights:
             w.add(name, shape, qtype, raw)
         return w
 
+    def to(self, device) -> "Weights":
+        """The same resident tensors on another device (plain copies: nothing is re-laid or re-quantised)."""
+        w = Weights(self.spec, device)
+        for name, qw in self.q.items():
+            w.q[name] = QWeight(qw.data.to(w.device, non_blocking=True), qw.qtype, qw.k)
+        for name, t in self.f.items():
+            w.f[name] = t.to(w.device, non_blocking=True)
+        w.n_bytes = self.n_bytes
+        return w
+
     def dequant(self, name: str) -> torch.Tensor:
         """fp32 copy of a weight (oracle use)."""
         from ..formats.resident import from_resident

@@ -77,6 +77,30 @@ def _family(qtype: str) -> int:
     return 2 if qtype in ("NVFP4", "FP8_B128", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K") else 0
 
 
+_STAGED = True
+_STAGE_SLICE_MAX = 90 * 1024
+
+
+def set_staged(on: bool) -> None:
+    """Use the shared-memory staged decode kernels (``csrc/decode_staged.cu``) where a launch's weight rows fit the
+    stage; off = the register-streaming kernels everywhere."""
+    global _STAGED
+    _STAGED = bool(on)
+
+
+def staged() -> bool:
+    return _STAGED
+
+
+def _gemv_fits_stage(segs: Sequence[QWeight], M: int) -> bool:
+    total = sum(s.data.numel() for s in segs)
+    K = segs[0].k
+    mb = 1 if M <= 1 else 2 if M <= 2 else 4 if M <= 4 else 8
+    act = mb * K * 5 // 4 + 4096
+    return total / (2 * sm_count()) <= _STAGE_SLICE_MAX * 0.85 and total / (2 * sm_count()) + act <= 190 * 1024 and all(
+        s.data.dim() == 2 for s in segs)
+
+
 def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torch.Tensor] = None,
          gain: Optional[torch.Tensor] = None, eps: float = 1e-6, xq: Optional[torch.Tensor] = None,
          xds: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
@@ -103,6 +127,14 @@ def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torc
     rows = (ctypes.c_int * n)(*[s.rows for s in segs])
     wts = (ctypes.c_int * n)(*[s.wt for s in segs])
     norm = x is not None
+    if _STAGED and 1 not in fams and _gemv_fits_stage(segs, M):
+        rc = cuda().bl_gemv_staged(I(n), wp, rows, wts, I(K), I(M), I(1 if norm else 0),
+                                   p(x), L(x.stride(0) if norm else 0), p(gain), F(eps), p(xq), p(xds),
+                                   p(out), L(out.stride(0)), p(resid), L(resid.stride(0) if resid is not None else 0),
+                                   _ref(red), _ref(push), p(fault), I(layer), I(sm_count()), stream())
+        if rc != -5:                         # -5: a block's rows would not fit the stage; the streaming kernel serves it
+            check(rc, "bl_gemv_staged")
+            return
     rc = cuda().bl_gemv(I(n), wp, rows, wts, I(K), I(M), I(1 if norm else 0),
                         p(x), L(x.stride(0) if norm else 0), p(gain), F(eps), p(xq), p(xds),
                         p(out), L(out.stride(0)), p(resid), L(resid.stride(0) if resid is not None else 0),
@@ -134,11 +166,31 @@ def flash_decode(q, k_cache, v_cache, row_pos, row_seq, block_table, n_pages: in
     check(rc, "bl_flash_decode")
 
 
+def attn_fused(qkv, q_gain, k_gain, inv_freq, eps: float, q_scale: float, head: int, n_q: int, n_kv: int, M: int,
+               row_pos, row_seq, block_table, n_pages: int, k_cache, v_cache, n_seg: int, ctx_limit: int, part_ml,
+               part_acc, tickets, out, outq, outds, fault, layer: int) -> None:
+    """Per-head RMSNorm + RoPE + KV append + split-K flash decode + merge + q8 rows for o_proj, one launch.
+    ``tickets``: int32 [M * n_kv], zero on entry (left zero)."""
+    rc = cuda().bl_attn_fused(p(qkv), L(qkv.stride(0)), p(q_gain), p(k_gain), p(inv_freq), F(eps), F(q_scale), I(head),
+                              I(n_q), I(n_kv), I(M), p(row_pos), p(row_seq), p(block_table), I(block_table.shape[1]),
+                              I(n_pages), p(k_cache), p(v_cache), I(n_seg), I(ctx_limit), p(part_ml), p(part_acc),
+                              p(tickets), p(out), p(outq), p(outds), p(fault), I(layer), stream())
+    check(rc, "bl_attn_fused")
+
+
 def router(x, gain, eps: float, w: QWeight, M: int, logits, xq_out, xds_out, xn_out, fault, layer: int,
-           red: Optional[ReduceIn] = None) -> None:
-    """Router logits of M rows (RMSNorm folded in) + the q8 form of the normed rows."""
+           red: Optional[ReduceIn] = None, *, rule: Optional["RouteRule"] = None, ids=None, wts=None, heat=None,
+           ticket=None) -> None:
+    """Router logits of M rows (RMSNorm folded in) + the q8 form of the normed rows.  With ``ticket`` (int32, one
+    zeroed word per 8 rows) and ``rule`` the launch also routes: its last block writes ``ids`` / ``wts`` / ``heat``."""
+    r = rule
     rc = cuda().bl_router(p(x), L(x.stride(0)), p(gain), F(eps), p(w.data), I(w.wt), I(w.k), I(w.rows), I(M),
-                          p(logits), p(xq_out), p(xds_out), p(xn_out), _ref(red), p(fault), I(layer), stream())
+                          p(logits), p(xq_out), p(xds_out), p(xn_out), _ref(red), p(fault), I(layer),
+                          p(ticket if r is not None else None), p(r.bias if r is not None else None),
+                          I(r.top_k if r is not None else 0), I(r.mode if r is not None else 0),
+                          I(1 if (r is not None and r.renorm) else 0), F(r.scale if r is not None else 1.0),
+                          I(r.n_group if r is not None else 1), I(r.topk_group if r is not None else 1),
+                          p(ids), p(wts), p(heat), stream())
     check(rc, "bl_router")
 
 
@@ -184,6 +236,37 @@ def down_combine(actq, actds, ids, wts, slot_map, down: QWeight, n_expert: int, 
                                 L(extra.stride(0) if extra is not None else 0), p(out), L(out.stride(0)), _ref(push),
                                 p(fault), I(layer), stream())
     check(rc, "bl_down_combine")
+
+
+def gate_up_staged(xq, xds, ids, slot_map, gate: QWeight, up: QWeight, n_expert: int, n_used: int, M: int, actq, actds,
+                   act_f32, fault, layer: int, down: Optional[QWeight] = None) -> None:
+    """gate.x, up.x, SwiGLU, q8 of the experts named in ``ids`` (shared-memory staged).  ``down``: the layer's down
+    stack, whose chosen matrices the launch asks L2 to prefetch for the launch that follows."""
+    deb = down.data.stride(0) if down is not None else 0
+    rc = cuda().bl_gate_up_staged(p(xq), p(xds), p(ids), p(slot_map), p(gate.data), p(up.data), I(gate.wt),
+                                  p(down.data if down is not None else None), L(deb), I(gate.k), I(gate.rows),
+                                  I(n_expert), I(n_used), I(M), p(actq), p(actds), p(act_f32), p(fault), I(layer), stream())
+    check(rc, "bl_gate_up_staged")
+
+
+def moe_fits_stage(gate: QWeight, down: QWeight, n_used: int) -> bool:
+    """Whether the staged expert kernels serve these stacks (a block's rows fit the shared-memory stage)."""
+    if not _STAGED or gate.qtype in ("F32", "F16", "BF16") or down.qtype in ("F32", "F16", "BF16"):
+        return False
+    rb_g = gate.data.shape[-1]
+    rb_d = down.data.shape[-1]
+    return 64 * rb_g + gate.k * 5 // 4 <= 180 * 1024 and n_used * 8 * rb_d + n_used * down.k * 5 // 4 <= 180 * 1024 and \
+        n_used * (down.k // 64) <= 512
+
+
+def down_staged(actq, actds, ids, wts, slot_map, down: QWeight, n_expert: int, n_used: int, M: int, resid, extra,
+                out, fault, layer: int, push: Optional[PushOut] = None) -> None:
+    rc = cuda().bl_down_staged(p(actq), p(actds), p(ids), p(wts), p(slot_map), p(down.data), I(down.wt), I(down.k),
+                               I(down.rows), I(n_expert), I(n_used), I(M), p(resid),
+                               L(resid.stride(0) if resid is not None else 0), p(extra),
+                               L(extra.stride(0) if extra is not None else 0), p(out), L(out.stride(0)), _ref(push),
+                               p(fault), I(layer), I(sm_count()), stream())
+    check(rc, "bl_down_staged")
 
 
 def embed_rows(tokens, M: int, table: QWeight, vocab: int, out, fault, step=None) -> None:

@@ -1,112 +1,179 @@
-"""Kernel micro-benchmark: each decode / prefill kernel alone at Qwen3-30B-A3B layer shapes, over a
-few layers of random weights, replayed from a CUDA graph and timed with CUDA events.
+"""Kernel micro-benchmark: each decode / prefill kernel alone (or the whole per-layer decode chain) at
+Qwen3-30B-A3B layer shapes, over a few layers of random weights, replayed from a CUDA graph and timed with
+CUDA events.
 
-    python -m bloomery_b200.ops.kernel_bench {all|qkv|o|router|gateup|gateup_ids|down|rope|flash|gemm|gemmdist|mla|sampler|gap|flash_mma} [replays] [context]
+    python -m bloomery_b200.ops.kernel_bench NAME [replays] [context] [--no-staged] [--rows M]
 
-It is also the small workload the ncu summaries under ``profiles/`` were captured on.
+NAME: chain (the six launches of a layer in order) | qkv | attn | o | router | gateup | down | rope | flash |
+flash_mma | gemm | gemmdist | mla | sampler | gap.  ``--no-staged`` runs the register-streaming kernels
+instead of the shared-memory staged ones.  It is also the small workload the ncu summaries under ``profiles/``
+were captured on.
 """
+import math
 import sys
 
-import torch
-from bloomery_b200.ops import decode as K
-from bloomery_b200.ops.decode import QWeight
-from bloomery_b200.formats.resident import resident_row_bytes
-dev = "cuda:0"
-torch.manual_seed(0)
 NL = 6
-H, QR, KVR, E, I, k = 2048, 4096, 512, 128, 768, 8
-def rw(rows, K_, t, stack=None):
-    rb = resident_row_bytes(t, K_)
-    shape = (rows, rb) if stack is None else (stack, rows, rb)
-    d = torch.randint(0, 256, shape, dtype=torch.uint8, device=dev)
-    return QWeight(d, t, K_)
-layers = []
-for l in range(NL):
-    layers.append(dict(q=rw(QR, H, "Q4_K"), k=rw(KVR, H, "Q4_K"), v=rw(KVR, H, "Q6_K"), o=rw(H, QR, "Q4_K"),
-                       r=QWeight((torch.randn(E, H, device=dev) * 0.05).view(torch.uint8).reshape(E, -1), "F32", H),
-                       g=rw(I, H, "Q4_K", E), u=rw(I, H, "Q4_K", E), d=rw(H, I, "Q6_K", E)))
-M = 1
-x = torch.randn(8, H, device=dev); gain = torch.ones(H, device=dev)
-qkv = torch.zeros(8, QR + 2 * KVR, device=dev)
-xq = torch.zeros(8, QR, dtype=torch.int8, device=dev); xds = torch.ones(8, QR // 32, 2, device=dev)
-fault = torch.full((1,), -1, dtype=torch.int32, device=dev)
-logits = torch.zeros(8, E, device=dev); ids = torch.zeros(8, k, dtype=torch.int32, device=dev); wts = torch.zeros(8, k, device=dev)
-hq = torch.zeros(8, H, dtype=torch.int8, device=dev); hds = torch.zeros(8, H // 32, 2, device=dev)
-cnt = torch.zeros(1, dtype=torch.int32, device=dev)
-actq = torch.zeros(8, k, I, dtype=torch.int8, device=dev); actds = torch.zeros(8, k, I // 32, 2, device=dev)
-which = sys.argv[1] if len(sys.argv) > 1 else "all"
-if which == "gateup_ids":
-    ids = torch.stack([torch.randperm(E)[:k] for _ in range(8)]).to(torch.int32).to(dev)
-import math
-n_q, n_kv, hd, ctx = 32, 4, 128, (int(sys.argv[3]) if len(sys.argv) > 3 else 4096)
-n_pages = ctx // 64
-kc = torch.randn(n_pages, n_kv, 64, hd, device=dev).half(); vc = torch.randn(n_pages, n_kv, 64, hd, device=dev).half()
-table = torch.arange(n_pages, dtype=torch.int32, device=dev)[None].contiguous()
-fpos = torch.tensor([ctx - 2], dtype=torch.int32, device=dev); fseq = torch.zeros(1, dtype=torch.int32, device=dev)
-fq = torch.randn(8, n_q, hd, device=dev) / math.sqrt(hd)
-n_seg = 37
-pml = torch.zeros(8 * n_q * n_seg * 2, device=dev); pacc = torch.zeros(8 * n_q * n_seg * hd, device=dev)
-if which == "gemm":
-    from bloomery_b200.ops import gemm as G
-    A = (torch.randn(4096, 2048, device=dev) * 0.1).bfloat16(); B = (torch.randn(5120, 2048, device=dev) * 0.1).bfloat16()
-    C = torch.zeros(4096, 5120, device=dev, dtype=torch.bfloat16); tt = G.TileTable.dense(4096, dev); gst = torch.zeros(1, dtype=torch.int32, device=dev)
-if which == "gemmdist":
-    # the several-GPU epilogue on one GPU: o_proj-shaped product whose rows are added into two "owners" (both local here)
-    from bloomery_b200.ops import gemm as G
-    A = (torch.randn(4096, 4096, device=dev) * 0.1).bfloat16(); B = (torch.randn(2048, 4096, device=dev) * 0.1).bfloat16()
-    own = [torch.zeros(2048, 2048, device=dev) for _ in range(2)]
-    tt = G.TileTable.dense(4096, dev); gst = torch.zeros(1, dtype=torch.int32, device=dev)
-if which == "mla":
-    mq, mctx = 128, 4096
-    mcache = torch.randn(mctx // 64, 64, 576, device=dev).half()
-    mtable = torch.arange(mctx // 64, dtype=torch.int32, device=dev)[None].contiguous()
-    mpos = torch.tensor([mctx - 2], dtype=torch.int32, device=dev); mseq = torch.zeros(1, dtype=torch.int32, device=dev)
-    mqlat = torch.randn(8, mq, 576, device=dev) * 0.05
-    mseg = 37
-    mml = torch.zeros(8 * mq * mseg * 2, device=dev); macc = torch.zeros(8 * mq * mseg * 512, device=dev)
-    mvb = (torch.randn(mq, 128, 512, device=dev) * 0.05).bfloat16()
-    moq = torch.zeros(8, mq * 128, dtype=torch.int8, device=dev); mods = torch.zeros(8, mq * 128 // 32, 2, device=dev)
-if which == "rope":
+H, QR, KVR, E, I, TOPK = 2048, 4096, 512, 128, 768, 8
+
+
+def main(argv=None) -> int:
+    import torch
+    from bloomery_b200.ops import decode as K
+    from bloomery_b200.ops.decode import QWeight
+    from bloomery_b200.formats.resident import resident_row_bytes
+
+    argv = list(sys.argv[1:] if argv is None else argv)
+    staged = "--no-staged" not in argv
+    rows = 1
+    if "--rows" in argv:
+        i = argv.index("--rows")
+        rows = int(argv[i + 1])
+        del argv[i:i + 2]
+    argv = [a for a in argv if a != "--no-staged"]
+    which = argv[0] if argv else "chain"
+    reps = int(argv[1]) if len(argv) > 1 else 4
+    ctx = int(argv[2]) if len(argv) > 2 else 4096
+    K.set_staged(staged)
+    dev = "cuda:0"
+    torch.manual_seed(0)
+    M = rows
+
+    def rw(n_rows, k_, t, stack=None):
+        rb = resident_row_bytes(t, k_)
+        shape = (n_rows, rb) if stack is None else (stack, n_rows, rb)
+        return QWeight(torch.randint(0, 256, shape, dtype=torch.uint8, device=dev), t, k_)
+
+    layers = []
+    for _ in range(NL):
+        layers.append(dict(q=rw(QR, H, "Q4_K"), k=rw(KVR, H, "Q4_K"), v=rw(KVR, H, "Q6_K"), o=rw(H, QR, "Q4_K"),
+                           r=QWeight((torch.randn(E, H, device=dev) * 0.05).view(torch.uint8).reshape(E, -1), "F32", H),
+                           g=rw(I, H, "Q4_K", E), u=rw(I, H, "Q4_K", E), d=rw(H, I, "Q6_K", E)))
+    x = torch.randn(8, H, device=dev)
+    gain = torch.ones(H, device=dev)
+    qkv = torch.randn(8, QR + 2 * KVR, device=dev)
+    xq = torch.zeros(8, QR, dtype=torch.int8, device=dev)
+    xds = torch.ones(8, QR // 32, 2, device=dev)
+    fault = torch.full((1,), -1, dtype=torch.int32, device=dev)
+    logits = torch.zeros(8, E, device=dev)
+    # distinct experts per row, so the expert launches stream eight different matrices as a real step does
+    ids = torch.stack([torch.randperm(E)[:TOPK] for _ in range(8)]).to(torch.int32).to(dev)
+    wts = torch.full((8, TOPK), 1.0 / TOPK, device=dev)
+    hq = torch.zeros(8, H, dtype=torch.int8, device=dev)
+    hds = torch.zeros(8, H // 32, 2, device=dev)
+    cnt = torch.zeros(1, dtype=torch.int32, device=dev)
+    actq = torch.zeros(8, TOPK, I, dtype=torch.int8, device=dev)
+    actds = torch.zeros(8, TOPK, I // 32, 2, device=dev)
+    tickets = torch.zeros(64, dtype=torch.int32, device=dev)
+    n_q, n_kv, hd = 32, 4, 128
+    n_pages = (ctx + 63) // 64
+    kc = torch.randn(n_pages, n_kv, 64, hd, device=dev).half()
+    vc = torch.randn(n_pages, n_kv, 64, hd, device=dev).half()
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev)[None].contiguous()
+    fpos = torch.full((8,), ctx - 2, dtype=torch.int32, device=dev)
+    fseq = torch.zeros(8, dtype=torch.int32, device=dev)
+    fq = torch.randn(8, n_q, hd, device=dev) / math.sqrt(hd)
+    n_seg = 37
+    pml = torch.zeros(8 * n_q * n_seg * 2, device=dev)
+    pacc = torch.zeros(8 * n_q * n_seg * hd, device=dev)
     r_inv = (1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))).float().to(dev)
     r_g = torch.ones(hd, device=dev)
     r_q = torch.zeros(8, n_q, hd, device=dev)
-    qkv.normal_()
-if which == "sampler":
-    V = 151936
-    slog = torch.randn(1, V, device=dev) * 3
-    spar = torch.tensor([[0.8, 40, 0.95, 0.05, 1.1, 0.0, 0.0, 64]], device=dev)
-    ssd = torch.tensor([1234], dtype=torch.int64, device=dev); sdr = torch.zeros(1, dtype=torch.int64, device=dev)
-    srec = torch.randint(0, V, (1, 64), dtype=torch.int32, device=dev); snrec = torch.tensor([64], dtype=torch.int32, device=dev)
-    swork = torch.zeros(1, V, device=dev); sout = torch.zeros(1, dtype=torch.int32, device=dev)
-if which == "flash_mma":
-    K.set_flash_mma(True)
-reps = int(sys.argv[2]) if len(sys.argv) > 2 else 4
-def chain():
-    for l in layers:
-        if which in ("all", "qkv"): K.gemv([l["q"], l["k"], l["v"]], M, qkv, x=x, gain=gain, fault=fault)
-        if which in ("all", "o"): K.gemv([l["o"]], M, x, xq=xq, xds=xds, resid=x, fault=fault)
-        if which in ("all", "router"): K.router(x, gain, 1e-6, l["r"], M, logits, hq, hds, None, fault, 0)
-        if which in ("all", "gateup"): K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0, route_logits=logits, rule=K.RouteRule(k), wts=wts)
-        if which == "gateup_ids": K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, k, M, actq, actds, None, fault, 0)
-        if which == "rope": K.qk_norm_rope_append(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, 1, fpos, fseq, table, n_pages, kc, vc, r_q, fault, 0)
-        if which in ("all", "flash", "flash_mma"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
-        if which == "gemm": G.gemm_bf16(A, B, tt, out_bf16=C, status=gst)
-        if which == "gemmdist": G.gemm_bf16_dist([A.data_ptr()], 4096, 4096, B, tt, owners=[o.data_ptr() for o in own], rows_per_owner=2048, ldc=2048, status=gst)
-        if which == "mla": K.mla_flash_decode(mqlat, mcache, mpos, mseq, mtable, mctx // 64, mq, 1, mseg, mctx, mml, macc, mvb, 128, None, moq, mods, fault, 0)
-        if which == "gap":
-            for _ in range(8): K.fill_u32(cnt, 0)           # eight empty nodes: the number printed is 8 node gaps
-        if which == "sampler": K.sample_rows(slog, V, 1, spar, ssd, sdr, sout, recent=srec, n_recent=snrec, work=swork)
-        if which in ("all", "down"): K.down_combine(actq, actds, ids, wts, None, l["d"], E, k, M, x, None, x, fault, 0)
-g = torch.cuda.CUDAGraph()
-s = torch.cuda.Stream()
-with torch.cuda.stream(s):
-    chain(); s.synchronize()
-    with torch.cuda.graph(g, stream=s):
+    rule = K.RouteRule(TOPK)
+    extra = {}
+    if which == "gemm":
+        from bloomery_b200.ops import gemm as G
+        extra = dict(G=G, A=(torch.randn(4096, 2048, device=dev) * 0.1).bfloat16(), B=(torch.randn(5120, 2048, device=dev) * 0.1).bfloat16(),
+                     C=torch.zeros(4096, 5120, device=dev, dtype=torch.bfloat16), tt=G.TileTable.dense(4096, dev),
+                     gst=torch.zeros(1, dtype=torch.int32, device=dev))
+    if which == "gemmdist":
+        # the several-GPU epilogue on one GPU: o_proj-shaped product whose rows are added into two "owners" (both local here)
+        from bloomery_b200.ops import gemm as G
+        extra = dict(G=G, A=(torch.randn(4096, 4096, device=dev) * 0.1).bfloat16(), B=(torch.randn(2048, 4096, device=dev) * 0.1).bfloat16(),
+                     own=[torch.zeros(2048, 2048, device=dev) for _ in range(2)], tt=G.TileTable.dense(4096, dev),
+                     gst=torch.zeros(1, dtype=torch.int32, device=dev))
+    if which == "mla":
+        mq, mctx, mseg = 128, 4096, 37
+        extra = dict(mq=mq, mctx=mctx, mseg=mseg, mcache=torch.randn(mctx // 64, 64, 576, device=dev).half(),
+                     mtable=torch.arange(mctx // 64, dtype=torch.int32, device=dev)[None].contiguous(),
+                     mpos=torch.tensor([mctx - 2], dtype=torch.int32, device=dev), mseq=torch.zeros(1, dtype=torch.int32, device=dev),
+                     mqlat=torch.randn(8, mq, 576, device=dev) * 0.05, mml=torch.zeros(8 * mq * mseg * 2, device=dev),
+                     macc=torch.zeros(8 * mq * mseg * 512, device=dev), mvb=(torch.randn(mq, 128, 512, device=dev) * 0.05).bfloat16(),
+                     moq=torch.zeros(8, mq * 128, dtype=torch.int8, device=dev), mods=torch.zeros(8, mq * 128 // 32, 2, device=dev))
+    if which == "sampler":
+        V = 151936
+        extra = dict(V=V, slog=torch.randn(1, V, device=dev) * 3, spar=torch.tensor([[0.8, 40, 0.95, 0.05, 1.1, 0.0, 0.0, 64]], device=dev),
+                     ssd=torch.tensor([1234], dtype=torch.int64, device=dev), sdr=torch.zeros(1, dtype=torch.int64, device=dev),
+                     srec=torch.randint(0, V, (1, 64), dtype=torch.int32, device=dev), snrec=torch.tensor([64], dtype=torch.int32, device=dev),
+                     swork=torch.zeros(1, V, device=dev), sout=torch.zeros(1, dtype=torch.int32, device=dev))
+    if which == "flash_mma":
+        K.set_flash_mma(True)
+    X = extra
+
+    def attn(l):
+        if staged:
+            K.attn_fused(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, M, fpos, fseq, table, n_pages, kc, vc,
+                         n_seg, ctx, pml, pacc, tickets, None, xq, xds, fault, 0)
+        else:
+            K.qk_norm_rope_append(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, M, fpos, fseq, table, n_pages,
+                                  kc, vc, r_q, fault, 0)
+            K.flash_decode(r_q, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, M, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
+
+    def router(l):
+        if staged:
+            K.router(x, gain, 1e-6, l["r"], M, logits, hq, hds, None, fault, 0, rule=rule, ids=ids, wts=wts, ticket=tickets[40:])
+        else:
+            K.router(x, gain, 1e-6, l["r"], M, logits, hq, hds, None, fault, 0)
+
+    def gateup(l, routed=True):
+        if staged:
+            K.gate_up_staged(hq, hds, ids, None, l["g"], l["u"], E, TOPK, M, actq, actds, None, fault, 0, down=l["d"])
+        elif routed:
+            K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, TOPK, M, actq, actds, None, fault, 0, route_logits=logits, rule=rule, wts=wts)
+        else:
+            K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, TOPK, M, actq, actds, None, fault, 0)
+
+    def down(l):
+        (K.down_staged if staged else K.down_combine)(actq, actds, ids, wts, None, l["d"], E, TOPK, M, x, None, x, fault, 0)
+
+    def chain():
+        for l in layers:
+            if which in ("chain", "qkv"): K.gemv([l["q"], l["k"], l["v"]], M, qkv, x=x, gain=gain, fault=fault)
+            if which in ("chain", "attn"): attn(l)
+            if which in ("chain", "o"): K.gemv([l["o"]], M, x, xq=xq, xds=xds, resid=x, fault=fault)
+            if which in ("chain", "router"): router(l)
+            if which in ("chain", "gateup"): gateup(l)
+            if which == "gateup_ids": gateup(l, routed=False)
+            if which in ("chain", "down"): down(l)
+            if which == "rope": K.qk_norm_rope_append(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, 1, fpos, fseq, table, n_pages, kc, vc, r_q, fault, 0)
+            if which in ("flash", "flash_mma"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
+            if which == "gemm": X["G"].gemm_bf16(X["A"], X["B"], X["tt"], out_bf16=X["C"], status=X["gst"])
+            if which == "gemmdist": X["G"].gemm_bf16_dist([X["A"].data_ptr()], 4096, 4096, X["B"], X["tt"], owners=[o.data_ptr() for o in X["own"]], rows_per_owner=2048, ldc=2048, status=X["gst"])
+            if which == "mla": K.mla_flash_decode(X["mqlat"], X["mcache"], X["mpos"], X["mseq"], X["mtable"], X["mctx"] // 64, X["mq"], 1, X["mseg"], X["mctx"], X["mml"], X["macc"], X["mvb"], 128, None, X["moq"], X["mods"], fault, 0)
+            if which == "gap":
+                for _ in range(8): K.fill_u32(cnt, 0)           # eight empty nodes: the number printed is 8 node gaps
+            if which == "sampler": K.sample_rows(X["slog"], X["V"], 1, X["spar"], X["ssd"], X["sdr"], X["sout"], recent=X["srec"], n_recent=X["snrec"], work=X["swork"])
+
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
         chain()
-torch.cuda.synchronize()
-e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-for _ in range(3): g.replay()
-e0.record()
-for _ in range(reps): g.replay()
-e1.record(); torch.cuda.synchronize()
-print(which, "us per layer-chain:", e0.elapsed_time(e1) * 1000 / reps / NL)
+        s.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            chain()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        g.replay()
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    word = int(fault.cpu().item()) & 0xFFFFFFFF
+    print(which, "staged" if staged else "streaming", f"rows={M} ctx={ctx}", "us per layer:", round(e0.elapsed_time(e1) * 1000 / reps / NL, 2),
+          "fault word:", hex(word))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

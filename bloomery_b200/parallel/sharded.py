@@ -135,12 +135,18 @@ class ShardedEngine(DecodeEngine):
                 x=xb[cur], gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, red=red, fault=self.fault, layer=il)
             if red is not None:
                 cur ^= 1
-            add(K.qk_norm_rope_append, self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
-                self.inv_freq, s.rms_eps, 1.0 / math.sqrt(s.head_dim), s.head_dim, s.n_q, s.n_kv, M,
-                self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out, self.fault, il)
-            add(K.flash_decode, self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
-                s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
-                self.attn_q, self.attn_ds, self.fault, il, launches=2)
+            if K.staged():
+                add(K.attn_fused, self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
+                    self.inv_freq, s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq,
+                    kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.n_seg, self.slot_ctx, self.part_ml, self.part_acc,
+                    self.tickets, None, self.attn_q, self.attn_ds, self.fault, il)
+            else:
+                add(K.qk_norm_rope_append, self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
+                    self.inv_freq, s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M,
+                    self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out, self.fault, il)
+                add(K.flash_decode, self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
+                    s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
+                    self.attn_q, self.attn_ds, self.fault, il, launches=2)
             if fused:
                 add(K.gemv, [w.q[b + "attn_output.weight"]], M, self.partial, xq=self.attn_q,
                     xds=self.attn_ds, push=ar.push(SITE_ATTN, 2 * il), fault=self.fault, layer=il)
@@ -152,21 +158,33 @@ class ShardedEngine(DecodeEngine):
                 red = None
             if not s.layer_is_moe(il):
                 raise NotImplementedError("dense FFN layers of a sharded model are not split yet")
-            add(K.router, xb[cur], w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M,
-                self.r_logits, self.xq, self.xds, None, self.fault, il, red=red)
+            ids, wts = self.r_ids_all[il], self.r_wts_all[il]
+            gate, up, down = w.q[b + "ffn_gate_exps.weight"], w.q[b + "ffn_up_exps.weight"], w.q[b + "ffn_down_exps.weight"]
+            staged = gate.qtype == up.qtype and K.moe_fits_stage(gate, down, s.n_used)
+            if staged:
+                add(K.router, xb[cur], w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M,
+                    self.r_logits, self.xq, self.xds, None, self.fault, il, red=red, rule=self._rule(il), ids=ids, wts=wts,
+                    heat=self.heat[il], ticket=self.tickets[8 * max(1, s.n_kv):])
+            else:
+                add(K.router, xb[cur], w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M,
+                    self.r_logits, self.xq, self.xds, None, self.fault, il, red=red)
             if red is not None:
                 cur ^= 1
-            add(K.gate_up_sel, self.xq, self.xds, self.r_ids, self.slot_map, w.q[b + "ffn_gate_exps.weight"],
-                w.q[b + "ffn_up_exps.weight"], s.n_expert, s.n_used, M, self.actq, self.actds, None, self.fault, il,
-                route_logits=self.r_logits, rule=self._rule(il), wts=self.r_wts, heat=self.heat[il])
+            if staged:
+                add(K.gate_up_staged, self.xq, self.xds, ids, self.slot_map, gate, up, s.n_expert, s.n_used, M, self.actq,
+                    self.actds, None, self.fault, il, down=down)
+            else:
+                add(K.gate_up_sel, self.xq, self.xds, ids, self.slot_map, gate, up, s.n_expert, s.n_used, M, self.actq,
+                    self.actds, None, self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=wts,
+                    heat=self.heat[il])
+            down_fn = K.down_staged if staged else K.down_combine
             if fused:
-                add(K.down_combine, self.actq, self.actds, self.r_ids, self.r_wts, self.slot_map,
-                    w.q[b + "ffn_down_exps.weight"], s.n_expert, s.n_used, M, None, None, self.partial,
-                    self.fault, il, push=ar.push(SITE_MOE, 2 * il + 1))
+                add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, None,
+                    self.partial, self.fault, il, push=ar.push(SITE_MOE, 2 * il + 1))
                 pending = (SITE_MOE, 2 * il + 1)
             else:
-                add(K.down_combine, self.actq, self.actds, self.r_ids, self.r_wts, self.slot_map,
-                    w.q[b + "ffn_down_exps.weight"], s.n_expert, s.n_used, M, None, None, self.partial, self.fault, il)
+                add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, None,
+                    self.partial, self.fault, il)
                 add(allreduce_into, xb[cur], self.partial, launches=2)
                 pending = None
         if head:

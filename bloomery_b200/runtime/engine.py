@@ -124,10 +124,15 @@ class DecodeEngine:
         self.attn_ds = torch.zeros(R, self.o_in // 32, 2, **f32)
         self.xq = torch.zeros(R, H, dtype=torch.int8, device=dev)
         self.xds = torch.zeros(R, H // 32, 2, **f32)
+        # completion tickets of the fused attention launch (one per row and KV head) and of the routing launch (one
+        # per group of 8 rows); the kernels leave them zero
+        self.tickets = torch.zeros(R * max(1, s.n_kv) + R, **i32)
         if s.is_moe:
             self.r_logits = torch.zeros(R, s.n_expert, **f32)
-            self.r_ids = torch.zeros(R, s.n_used, **i32)
-            self.r_wts = torch.zeros(R, s.n_used, **f32)
+            # chosen experts and weights of every layer of the last pass (the route trace reads them)
+            self.r_ids_all = torch.zeros(s.n_layer + self.n_mtp, R, s.n_used, **i32)
+            self.r_wts_all = torch.zeros(s.n_layer + self.n_mtp, R, s.n_used, **f32)
+            self.r_ids, self.r_wts = self.r_ids_all[0], self.r_wts_all[0]
             self.actq = torch.zeros(R, s.n_used, s.moe_inter, dtype=torch.int8, device=dev)
             self.actds = torch.zeros(R, s.n_used, s.moe_inter // 32, 2, **f32)
             self.heat = torch.zeros(s.n_layer + self.n_mtp, s.n_expert, **i32)
@@ -311,6 +316,12 @@ class DecodeEngine:
             return self._attn_mla(il, M, x)
         K.gemv([w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
                x=x, gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il)
+        if K.staged():
+            K.attn_fused(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"), self.inv_freq,
+                         s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq, kvp.table,
+                         kvp.n_pages, kvp.k[il - self.lo], kvp.v[il - self.lo], self.n_seg, self.slot_ctx, self.part_ml,
+                         self.part_acc, self.tickets, None, self.attn_q, self.attn_ds, self.fault, il)
+            return 2
         K.qk_norm_rope_append(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
                               self.inv_freq, s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M,
                               self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il - self.lo], kvp.v[il - self.lo], self.q_out,
@@ -348,12 +359,21 @@ class DecodeEngine:
         """Router + routed experts + combine of one layer (3 launches); returns the launch count."""
         s, w = self.spec, self.w
         b = f"blk.{il}."
-        K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
-                 self.xq, self.xds, None, self.fault, il)
-        K.gate_up_sel(self.xq, self.xds, self.r_ids, None, w.q[b + "ffn_gate_exps.weight"],
-                      w.q[b + "ffn_up_exps.weight"], s.n_expert, s.n_used, M, self.actq, self.actds, None,
-                      self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=self.r_wts,
-                      heat=self.heat[il])
+        ids, wts = self.r_ids_all[il], self.r_wts_all[il]
+        gate, up, down = w.q[b + "ffn_gate_exps.weight"], w.q[b + "ffn_up_exps.weight"], w.q[b + "ffn_down_exps.weight"]
+        staged = gate.qtype == up.qtype and K.moe_fits_stage(gate, down, s.n_used)
+        if staged:
+            # the routing launch's last block turns the logits into ids and weights; the expert launches read them
+            K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
+                     self.xq, self.xds, None, self.fault, il, rule=self._rule(il), ids=ids, wts=wts,
+                     heat=self.heat[il], ticket=self.tickets[MAX_ROWS * max(1, s.n_kv):])
+            K.gate_up_staged(self.xq, self.xds, ids, None, gate, up, s.n_expert, s.n_used, M, self.actq, self.actds,
+                             None, self.fault, il, down=down)
+        else:
+            K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
+                     self.xq, self.xds, None, self.fault, il)
+            K.gate_up_sel(self.xq, self.xds, ids, None, gate, up, s.n_expert, s.n_used, M, self.actq, self.actds, None,
+                          self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=wts, heat=self.heat[il])
         extra, n = None, 3
         if s.n_shared:
             # the shared expert reads the router's q8 rows and lands as an extra addend of the combine
@@ -363,8 +383,8 @@ class DecodeEngine:
             K.gemv([w.q[b + "ffn_down_shexp.weight"]], M, self.sh_out, xq=self.sh_actq, xds=self.sh_actds,
                    fault=self.fault, layer=il)
             extra, n = self.sh_out, 6
-        K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, None, w.q[b + "ffn_down_exps.weight"],
-                       s.n_expert, s.n_used, M, x, extra, x, self.fault, il)
+        (K.down_staged if staged else K.down_combine)(self.actq, self.actds, ids, wts, None, down, s.n_expert, s.n_used,
+                                                      M, x, extra, x, self.fault, il)
         return n
 
     def _after_pass(self, n_rows: int) -> None:
@@ -460,6 +480,13 @@ class DecodeEngine:
             self._after_pass(len(rows))
             for slot, _, pos in rows:
                 self.slot_len[slot] = max(self.slot_len[slot], pos + 1)
+            if self.route_trace is not None and self.spec.is_moe:
+                # the picks of every layer of this pass are still on the card: one read per pass
+                ids = self.r_ids_all[:, :len(rows)].cpu().tolist()
+                wts = self.r_wts_all[:, :len(rows)].cpu().tolist()
+                for il in range(self.spec.first_dense, self.spec.n_layer):
+                    for r, (_, _, pos) in enumerate(rows):
+                        self.route_trace.add(pos, il, ids[il][r], wts[il][r])
             if self.check_finite and not bool(torch.isfinite(self.x[:len(rows)]).all()):
                 self.poisoned = (self.spec.n_layer << 8) | 2
                 raise EngineFault(self.poisoned)

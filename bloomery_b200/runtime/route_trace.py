@@ -103,7 +103,7 @@ def trace_engine(engine, prompt: Sequence[int], n_new: int, path: str) -> int:
     def traced(il, M, x):
         n = orig(il, M, x)
         torch.cuda.current_stream().synchronize()
-        ids, wts = engine.r_ids[:M].cpu().tolist(), engine.r_wts[:M].cpu().tolist()
+        ids, wts = engine.r_ids_all[il][:M].cpu().tolist(), engine.r_wts_all[il][:M].cpu().tolist()
         for m, p in enumerate(state["pos"][:M]):
             w.add(p, il, ids[m], wts[m])
         return n

@@ -42,16 +42,24 @@ class TieredEngine(DecodeEngine):
         b = f"blk.{il}."
         sm = t.slot_map[il]
         card = t.card[il]
+        ids, wts = self.r_ids_all[il], self.r_wts_all[il]
+        # the routing launch's last block writes ids / weights / heat (completion ticket), so no routing launch follows
         K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
-                 self.xq, self.xds, None, self.fault, il)
-        K.route_rows(self.r_logits, self._rule(il), M, self.r_ids, self.r_wts, self.heat[il], self.fault, il)
-        self.tier.handoff(self.r_ids, self.r_wts, sm, self.xq, self.xds, M, s.n_used, s.hidden, s.n_expert, il)
-        K.gate_up_sel(self.xq, self.xds, self.r_ids, sm, card["ffn_gate_exps"], card["ffn_up_exps"], s.n_expert,
-                      s.n_used, M, self.actq, self.actds, None, self.fault, il)
+                 self.xq, self.xds, None, self.fault, il, rule=self._rule(il), ids=ids, wts=wts, heat=self.heat[il],
+                 ticket=self.tickets[8 * max(1, s.n_kv):])
+        self.tier.handoff(ids, wts, sm, self.xq, self.xds, M, s.n_used, s.hidden, s.n_expert, il)
+        staged = card["ffn_gate_exps"].data.shape[0] > 0 and card["ffn_gate_exps"].qtype == card["ffn_up_exps"].qtype and \
+            K.moe_fits_stage(card["ffn_gate_exps"], card["ffn_down_exps"], s.n_used)
+        if staged:
+            K.gate_up_staged(self.xq, self.xds, ids, sm, card["ffn_gate_exps"], card["ffn_up_exps"], s.n_expert, s.n_used, M,
+                             self.actq, self.actds, None, self.fault, il, down=card["ffn_down_exps"])
+        else:
+            K.gate_up_sel(self.xq, self.xds, ids, sm, card["ffn_gate_exps"], card["ffn_up_exps"], s.n_expert,
+                          s.n_used, M, self.actq, self.actds, None, self.fault, il)
         self.tier.wait(M, s.hidden, self.fault, il)
-        K.down_combine(self.actq, self.actds, self.r_ids, self.r_wts, sm, card["ffn_down_exps"], s.n_expert, s.n_used,
-                       M, x, self.tier.extra, x, self.fault, il)
-        return 6
+        (K.down_staged if staged else K.down_combine)(self.actq, self.actds, ids, wts, sm, card["ffn_down_exps"], s.n_expert,
+                                                      s.n_used, M, x, self.tier.extra, x, self.fault, il)
+        return 5
 
     def _new_gemm_prefill(self):
         """Prompts take the GEMM path with the layer's whole expert stacks streamed from pinned host memory into a

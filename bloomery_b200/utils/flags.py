@@ -197,6 +197,13 @@ def placement(opts: Dict[str, Any], n_visible: int, n_layer: int = 0) -> Placeme
         else:
             raise Refusal(Code.USAGE, f"-ngl {ngl}: only a full offload (or 0) is served; trunk layers are not split")
     devs = [] if ngl == "0" else _devices(opts.get("dev"), n_visible)
+    from . import levers
+    tp = int(levers.get("BLOOMERY_TP"))
+    if tp > 0 and devs and not opts.get("dev"):
+        # the lever names how many of the visible devices run in lockstep when -dev does not
+        if tp > len(devs):
+            raise Refusal(Code.USAGE, f"BLOOMERY_TP={tp}: only {len(devs)} device(s) are visible")
+        devs = devs[:tp]
     pl = Placement(devices=devs, main_gpu=int(opts.get("main_gpu") or 0))
     word = (opts.get("place") or "").lower()
     if not devs:

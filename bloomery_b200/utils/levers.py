@@ -61,7 +61,7 @@ REGISTRY: List[LeverSpec] = [
     LeverSpec("BLOOMERY_ENGINE_BOUND", "float", 60.0, "seconds an engine-thread wait may last"),
     LeverSpec("BLOOMERY_ROUTE_TRACE", "str", "", "directory for per-position router traces"),
     LeverSpec("BLOOMERY_TP_PORT", "int", 0, "rendezvous port of the lockstep ranks on 127.0.0.1 (0 = derived from the pid)"),
-    LeverSpec("BLOOMERY_DECODE_ROWS", "int", 64, "most rows of one batched decode round (slots that step together)"),
+    LeverSpec("BLOOMERY_STAGED", "bool", True, "decode kernels that stage their weight rows in shared memory with bulk copies"),
 ]
 RETIRED = {"BLOOMERY_WORD_OPS": "stream memops are not used on this build", "BLOOMERY_TIER_LINK": "there is no host-page link: GPUs talk over NVLink",
            "BLOOMERY_TIER_NODES": "multi-machine tiers are not built", "BLOOMERY_TP_NODES": "TP ranks come from torchrun, not from a node list"}
