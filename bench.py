@@ -85,6 +85,7 @@ def main() -> int:
     ap.add_argument("--flash-mma", action="store_true", help="decode attention segments on tensor-core tiles")
     ap.add_argument("--ttft", type=int, default=4096, help="also time a prompt of this many tokens (0 = skip)")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--staged-parts", dest="staged_parts", default="", help="ablation: which launches take the staged form (gemv,attn,moe,prefetch)")
     ap.add_argument("--no-staged", dest="no_staged", action="store_true",
                     help="register-streaming decode kernels instead of the shared-memory staged ones")
     ap.add_argument("--nccl-baseline", dest="nccl_baseline", action="store_true",
@@ -118,6 +119,8 @@ def main() -> int:
         K.set_pdl(False)
     if args.no_staged:
         K.set_staged(False)
+    if args.staged_parts:
+        K.set_staged_parts(args.staged_parts)
     spec = NAMED[args.model]()
     steps, warm = args.steps, max(3, args.warmup)
     t0 = time.time()

@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
   float* s_scale = reinterpret_cast<float*>(red + MB * 8);
   float* sx = s_scale + 8;  // only when FLOATW
 
+  if (a.n_pf > 0 && threadIdx.x == 0) prefetch_spans_l2(a.pf_ptr, a.pf_bytes, a.n_pf);
   bool ready = false;
   auto between = [&]() {
     if (!ready) {
@@ -268,12 +269,19 @@ int bl_gemv(int nseg, const void* const* w, const int* rows, const int* wtypes, 
             int norm, const float* x, long x_stride, const float* gain, float eps,
             const int8_t* xq, const float* xds,
             float* out, long out_stride, const float* resid, long resid_stride,
-            const void* red_desc, const void* push_desc, unsigned* fault, int layer, int sm_count, cudaStream_t st) {
+            const void* red_desc, const void* push_desc, unsigned* fault, int layer, int sm_count,
+            int n_pf, const void* const* pf_ptr, const long* pf_bytes, cudaStream_t st) {
   BL_REQUIRE(nseg >= 1 && nseg <= 4, BL_ERR_SHAPE);
   BL_REQUIRE(M >= 1 && M <= 8, BL_ERR_SHAPE);
   BL_REQUIRE(K > 0 && K % 256 == 0, BL_ERR_SHAPE);
   BL_REQUIRE(!norm || (K % 2048 == 0 || K % 64 == 0), BL_ERR_SHAPE);
+  BL_REQUIRE(n_pf >= 0 && n_pf <= 6, BL_ERR_SHAPE);
   GemvArgs a = {};
+  a.n_pf = n_pf;
+  for (int i = 0; i < n_pf; ++i) {
+    BL_REQUIRE(((uintptr_t)pf_ptr[i] & 15) == 0 && pf_bytes[i] >= 0, BL_ERR_ALIGN);
+    a.pf_ptr[i] = (const uint8_t*)pf_ptr[i]; a.pf_bytes[i] = pf_bytes[i];
+  }
   a.nseg = nseg;
   bool floatw = false, planes = false, ggml = false;
   double total_bytes = 0;

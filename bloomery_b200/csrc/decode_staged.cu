@@ -69,6 +69,42 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
 
 constexpr float kNaN = __builtin_nanf("");
 
+// Phase probe (kernel_bench --probe): when armed, thread 0 of block (0, 0, 0) stores the SM cycle counter at the
+// kernel's phase boundaries, which shows where a launch's microseconds go without a profiler.  Null in normal use.
+__device__ __forceinline__ void probe_mark(long long* probe, int i) {
+  if (probe && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) probe[i] = clock64();
+}
+
+// Activation registers of weight unit u out of a shared-memory row in layout 1 / 2 (act_chunk_pos): every load of
+// a warp touches 32 consecutive 16-byte chunks, so none meets a bank conflict.  `sds` stays linear.
+template <class T> struct StagedAct {
+  static constexpr int kLayout = 1;
+  static __device__ __forceinline__ void load(const int8_t* sq, const float2* sds, int u, int nunits, ActRegs& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = *reinterpret_cast<const uint4*>(sq + ((long)(i * nunits + u) << 4));
+      a.q[4 * i] = v.x; a.q[4 * i + 1] = v.y; a.q[4 * i + 2] = v.z; a.q[4 * i + 3] = v.w;
+    }
+    const float4 ds = *reinterpret_cast<const float4*>(sds + 2 * u);
+    a.d[0] = ds.x; a.s[0] = ds.y; a.d[1] = ds.z; a.s[1] = ds.w;
+  }
+};
+template <> struct StagedAct<Q6K> {
+  static constexpr int kLayout = 2;
+  static __device__ __forceinline__ void load(const int8_t* sq, const float2* sds, int u, int nunits, ActRegs& a) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint4 v = *reinterpret_cast<const uint4*>(sq + ((long)(g * nunits + u) << 4));
+      a.q[4 * g] = v.x; a.q[4 * g + 1] = v.y; a.q[4 * g + 2] = v.z; a.q[4 * g + 3] = v.w;
+    }
+    const int sb = u >> 2, n = (u >> 1) & 1;
+    const float4 d01 = *reinterpret_cast<const float4*>(sds + 8 * sb + 4 * n);
+    const float4 d23 = *reinterpret_cast<const float4*>(sds + 8 * sb + 4 * n + 2);
+    a.d[0] = d01.x; a.d[1] = d01.z; a.d[2] = d23.x; a.d[3] = d23.z;
+  }
+};
+__host__ __device__ inline int staged_layout(int wtype) { return wtype == WT_Q6_K ? 2 : 1; }
+
 // =======================================================================================================
 // gemv_staged
 // =======================================================================================================
@@ -91,10 +127,10 @@ __device__ __forceinline__ void rows_staged(const GemvArgs& a, const uint8_t* sw
       if constexpr (kPair) U::loadu(sw + (long)(two ? r + 8 : r) * rb, u, K, g1);
 #pragma unroll
       for (int m = 0; m < MB; ++m) {
-        const uint32_t* xq = reinterpret_cast<const uint32_t*>(sq + (long)m * K);
-        const F2* xds = reinterpret_cast<const F2*>(sds + (long)m * (K / 32));
-        acc0[m] += U::dotu(g0, u, xq, xds);
-        if constexpr (kPair) acc1[m] += U::dotu(g1, u, xq, xds);
+        ActRegs act;
+        StagedAct<T>::load(sq + (long)m * K, sds + (long)m * (K / 32), u, nunits, act);
+        acc0[m] += ActOf<T>::dot(g0, u, act);
+        if constexpr (kPair) acc1[m] += ActOf<T>::dot(g1, u, act);
       }
     }
 #pragma unroll
@@ -114,7 +150,7 @@ template <int MB, bool NORM, int FAM>
 __global__ void __launch_bounds__(256, 2) gemv_staged_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t bar;
-  pdl_launch();
+  if (a.dbg & 1) pdl_launch();
   const int K = a.K, tid = threadIdx.x;
   uint8_t* sw = smem;
   int8_t* sq = reinterpret_cast<int8_t*>(smem + a.stage_bytes);
@@ -136,17 +172,23 @@ __global__ void __launch_bounds__(256, 2) gemv_staged_kernel(const GemvArgs a) {
   const uint32_t bytes = (uint32_t)nrows * (uint32_t)s.row_bytes;
   if (tid == 0) {
     mbar_init(&bar, 1);
-    if (bytes) {                                      // weights never depend on the predecessor: fetch them now
+    if (bytes && !(a.dbg & 4)) {                      // weights never depend on the predecessor: fetch them now
       mbar_expect_tx(&bar, bytes);
       bulk_load_chunks(sw, s.w + (long)r_lo * s.row_bytes, bytes, &bar);
     }
   }
   __syncthreads();
   pdl_wait();
-  if (NORM) prologue_norm<MB, false>(a, sq, sds, nullptr, s_scale, red);
-  else prologue_q8in<MB>(a, sq, sds, s_scale);
+  // the dependents start now: their weight copies overlap this kernel's prologue and dot products (releasing them
+  // before the wait was measured slower: their blocks then sit on the SM through the whole predecessor)
+  if (!(a.dbg & 1)) pdl_launch();
+  if (!(a.dbg & 8)) {
+  if (NORM) prologue_norm<MB, false>(a, sq, sds, nullptr, s_scale, red, staged_layout(s.wtype));
+  else prologue_q8in<MB>(a, sq, sds, s_scale, staged_layout(s.wtype));
+  }
   bool ok = true;
-  if (bytes) ok = mbar_wait(&bar, 0, a.fault, a.layer);
+  if (bytes && !(a.dbg & 4)) ok = mbar_wait(&bar, 0, a.fault, a.layer);
+  if (!(a.dbg & 2)) {
   if constexpr (FAM == 0) {
   switch (s.wtype) {
     case WT_Q4_K: rows_staged<Q4K, MB>(a, sw, s.row_bytes, nrows, sq, sds, s_scale, s_out); break;
@@ -166,6 +208,7 @@ __global__ void __launch_bounds__(256, 2) gemv_staged_kernel(const GemvArgs a) {
     case WT_Q5_0: rows_staged<Q50, MB>(a, sw, s.row_bytes, nrows, sq, sds, s_scale, s_out); break;
     case WT_Q5_1: rows_staged<Q51, MB>(a, sw, s.row_bytes, nrows, sq, sds, s_scale, s_out); break;
     default: ok = false;
+  }
   }
   }
   __syncthreads();
@@ -201,6 +244,7 @@ struct AttnArgs {
   unsigned* tickets;                       // [M * n_kv], zero between launches (the last block resets its ticket)
   float* out; int8_t* outq; float2* outds; // attention rows [M, n_q * HEAD]: optional fp32, q8 codes, {d, s} per 32
   unsigned* fault; int layer;
+  long long* probe;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -246,7 +290,6 @@ template <int HEAD, int HPW>
 __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
   constexpr int KSTR = HEAD + 8, DPL = HEAD / 32;
   extern __shared__ __align__(128) uint8_t smem[];
-  pdl_launch();
   const int G = a.n_q / a.n_kv;
   float* sq = reinterpret_cast<float*>(smem);                              // [G][HEAD]
   __half* sk = reinterpret_cast<__half*>(smem + (size_t)G * HEAD * 4);     // [2][32][KSTR]
@@ -271,6 +314,7 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
     // padding rows and rows with a bad key count still publish rows for o_proj: zeros, or a NaN scale
     if (seg != 0) return;
     pdl_wait();
+    pdl_launch();
     if (bad && tid == 0 && kvh == 0) raise_fault(a.fault, a.layer, FS_KEY_COUNT);
     const long width = (long)a.n_q * HEAD;
     for (int i = tid; i < G * HEAD; i += 256) {
@@ -298,8 +342,11 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
     cp_async_commit();
   };
   // keys of earlier positions are already in the cache: the first tile streams in while the predecessor still runs
+  probe_mark(a.probe, 0);
   issue_tile(t0, 0);
   pdl_wait();
+  pdl_launch();
+  probe_mark(a.probe, 1);
 
   // ---- queries of this KV head's group: RMSNorm + RoPE into shared memory ---------------------------
   const float* row = a.qkv + (long)m * a.qkv_stride;
@@ -342,6 +389,7 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
       for (int j = 0; j < DPL; ++j) sq[hg * HEAD + lane + 32 * j] = y[j] * a.q_scale;
     }
   }
+  probe_mark(a.probe, 2);
   // ---- keys and values that this very pass appends --------------------------------------------------
   // Rows of the pass that belong to the same sequence at or before this row's position are not in the cache
   // yet (their owner blocks write them in this same launch), so a block computes the ones that fall inside its
@@ -381,6 +429,7 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
     }
   }
 
+  probe_mark(a.probe, 3);
   float mx[HPW], l[HPW], acc[HPW][DPL];
 #pragma unroll
   for (int h = 0; h < HPW; ++h) {
@@ -455,6 +504,7 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
     __syncthreads();
   }
 
+  probe_mark(a.probe, 4);
   if (used == 1) {
     // one segment covers the whole row: finish here, nothing to merge
 #pragma unroll
@@ -488,6 +538,7 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
     if (s_last) a.tickets[(long)m * a.n_kv + kvh] = 0u;       // ready for the next launch (graph replay)
   }
   __syncthreads();
+  probe_mark(a.probe, 5);
   if (!s_last) return;
   __threadfence();
 #pragma unroll
@@ -495,22 +546,47 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
     const int hg = warp + 8 * h;
     if (hg < G) {
       const long p0 = ((long)m * a.n_q + (long)kvh * G + hg) * a.n_seg;
+      // lanes fetch the segments' (max, sum) pairs side by side; the accumulators follow eight segments per
+      // round trip; the sums themselves still run over the segments in ascending order
       float gm = -INFINITY;
-      for (int s = 0; s < used; ++s) gm = fmaxf(gm, __ldcg(a.part_ml + (p0 + s) * 2));
+      for (int s0 = 0; s0 < used; s0 += 32) {
+        const int sg = s0 + lane;
+        if (sg < used) gm = fmaxf(gm, __ldcg(a.part_ml + (p0 + sg) * 2));
+      }
+      gm = warp_max(gm);
       float den = 0.f, num[DPL];
 #pragma unroll
       for (int d = 0; d < DPL; ++d) num[d] = 0.f;
-#pragma unroll 4
-      for (int s = 0; s < used; ++s) {                        // ascending segment order, fixed
-        const float ms = __ldcg(a.part_ml + (p0 + s) * 2);
-        const float w = (ms == -INFINITY) ? 0.f : __expf(ms - gm);
-        den = fmaf(__ldcg(a.part_ml + (p0 + s) * 2 + 1), w, den);
-        if constexpr (DPL == 4) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(a.part_acc + (p0 + s) * HEAD) + lane);
-          num[0] = fmaf(v.x, w, num[0]); num[1] = fmaf(v.y, w, num[1]); num[2] = fmaf(v.z, w, num[2]); num[3] = fmaf(v.w, w, num[3]);
-        } else {
+      for (int s0 = 0; s0 < used; s0 += 32) {
+        const int sg = s0 + lane;
+        float ms = -INFINITY, ls = 0.f;
+        if (sg < used) { const float2 v = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (p0 + sg) * 2)); ms = v.x; ls = v.y; }
+        const float wl = (ms == -INFINITY) ? 0.f : __expf(ms - gm);
+        const int cnt = min(32, used - s0);
+        for (int k0 = 0; k0 < cnt; k0 += 8) {
+          float v[8][DPL];
 #pragma unroll
-          for (int d = 0; d < DPL; ++d) num[d] = fmaf(__ldcg(a.part_acc + (p0 + s) * HEAD + lane * DPL + d), w, num[d]);
+          for (int k = 0; k < 8; ++k) {
+            if (k0 + k < cnt) {
+              const float* src = a.part_acc + (p0 + s0 + k0 + k) * HEAD + lane * DPL;
+              if constexpr (DPL == 4) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(src));
+                v[k][0] = t.x; v[k][1] = t.y; v[k][2] = t.z; v[k][3] = t.w;
+              } else {
+                const float2 t = __ldcg(reinterpret_cast<const float2*>(src));
+                v[k][0] = t.x; v[k][1] = t.y;
+              }
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            if (k0 + k < cnt) {
+              const float wk = __shfl_sync(0xffffffffu, wl, k0 + k), lk = __shfl_sync(0xffffffffu, ls, k0 + k);
+              den = fmaf(lk, wk, den);
+#pragma unroll
+              for (int d = 0; d < DPL; ++d) num[d] = fmaf(v[k][d], wk, num[d]);
+            }
+          }
         }
       }
       float o[DPL];
@@ -526,13 +602,17 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
 // =======================================================================================================
 struct GateUpStagedArgs {
   const int8_t* xq; const float2* xds;     // [M, K] q8 rows of the normed residual
-  const int* ids;                          // [M, n_used] chosen experts (written by the router launch)
+  RouteParams route;                       // route.logits != null: every block routes its row itself from the router
+                                           // launch's logits (block (0, 0, m) also publishes ids / wts / heat)
+  int* ids;                                // [M, n_used] chosen experts: read (route.logits == null) or written
+  float* wts; unsigned* heat;
   const int* slot_map;                     // optional [E]: expert id -> resident slot (or kExpertElsewhere)
   const uint8_t* gate; const uint8_t* up; int wtype;   // stacks [E_slots, I, row_bytes]
   const uint8_t* down; long down_expert_bytes;         // optional: the down stack, for the L2 prefetch
   int K, I, E, n_used, M;
   int8_t* actq; float2* actds; float* act_f32;         // [M, n_used, I]
   unsigned* fault; int layer;
+  long long* probe;
 };
 
 template <class T>
@@ -547,7 +627,7 @@ __device__ __forceinline__ void gate_up_rows_staged(const uint8_t* g0, const uin
 #pragma unroll
     for (int r = 0; r < 2; ++r) { U::loadu(g0 + r * rb, u, K, rg[r]); U::loadu(u0 + r * rb, u, K, ru[r]); }
     ActRegs act;
-    ActOf<T>::load(reinterpret_cast<const uint32_t*>(xq), reinterpret_cast<const F2*>(xds), u, act);
+    StagedAct<T>::load(xq, xds, u, nunits, act);
 #pragma unroll
     for (int r = 0; r < 2; ++r) { gacc[r] += ActOf<T>::dot(rg[r], u, act); uacc[r] += ActOf<T>::dot(ru[r], u, act); }
   }
@@ -561,7 +641,7 @@ __global__ void __launch_bounds__(256, 2) gate_up_staged_kernel(const GateUpStag
   __shared__ __align__(8) uint64_t bar;
   __shared__ float s_act[32];
   __shared__ int s_e;
-  pdl_launch();
+  __shared__ RouteWarpShared s_rw;
   const int K = a.K;
   const int chunk = blockIdx.x, j = blockIdx.y, m = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -571,11 +651,48 @@ __global__ void __launch_bounds__(256, 2) gate_up_staged_kernel(const GateUpStag
   uint8_t* su = smem + half_bytes;
   int8_t* sxq = reinterpret_cast<int8_t*>(smem + 2 * half_bytes);
   float2* sxds = reinterpret_cast<float2*>(sxq + K);
+  probe_mark(a.probe, 0);
   if (tid == 0) mbar_init(&bar, 1);
   __syncthreads();
   pdl_wait();
-  if (tid == 0) {
-    int e = a.ids[(long)m * a.n_used + j];
+  pdl_launch();
+  probe_mark(a.probe, 1);
+  const bool routed_here = a.route.logits != nullptr;
+  const bool warp_route = routed_here && route_warp_ok(a.route);
+  if (routed_here && !warp_route) {
+    // general shapes (expert groups, more than 256 experts): the block-wide routine
+    __shared__ RouteShared rs;
+    int id; float w;
+    const bool ok = route_block(a.route, m, rs, id, w);
+    if (tid < 32) {
+      if (tid < a.n_used) { s_rw.ids[tid] = ok ? id : -3; s_rw.wraw[tid] = w; }
+    }
+    __syncthreads();
+  }
+  if (warp == 0) {
+    int e;
+    if (routed_here) {
+      if (warp_route) {
+        int id; float w;
+        const bool ok = route_warp(a.route, m, s_rw, lane, id, w);
+        __syncwarp();
+        if (lane < a.n_used) { s_rw.ids[lane] = ok ? id : -3; s_rw.wraw[lane] = w; }
+        __syncwarp();
+      }
+      if (chunk == 0 && j == 0) {
+        if (lane == 0 && s_rw.ids[0] == -3) raise_fault(a.fault, a.layer, FS_ROUTER);
+        if (lane < a.n_used) {
+          const int id = s_rw.ids[lane];
+          a.ids[(long)m * a.n_used + lane] = id;
+          a.wts[(long)m * a.n_used + lane] = s_rw.wraw[lane];
+          if (id >= 0 && a.heat) atomicAdd(a.heat + id, 1u);
+        }
+      }
+      e = s_rw.ids[j];
+    } else {
+      e = a.ids[(long)m * a.n_used + j];
+    }
+  if (lane == 0) {
     if (e == kExpertElsewhere) e = -1;
     else if (e < 0 || e >= a.E) { e = -2; if (chunk == 0) raise_fault(a.fault, a.layer, FS_EXPERT_ID); }
     else if (a.slot_map) { e = a.slot_map[e]; if (e < 0) e = -1; }
@@ -592,14 +709,21 @@ __global__ void __launch_bounds__(256, 2) gate_up_staged_kernel(const GateUpStag
     }
     s_e = e;
   }
-  for (int i = tid; i < K / 16; i += 256)
-    reinterpret_cast<uint4*>(sxq)[i] = reinterpret_cast<const uint4*>(a.xq + (long)m * K)[i];
-  for (int i = tid; i < K / 32; i += 256) sxds[i] = a.xds[(long)m * (K / 32) + i];
+  }
+  probe_mark(a.probe, 2);
+  {
+    const int layout = staged_layout(a.wtype), nunits = K / 64;
+    for (int i = tid; i < K / 16; i += 256)
+      reinterpret_cast<uint4*>(sxq)[act_chunk_pos(i, nunits, layout)] = reinterpret_cast<const uint4*>(a.xq + (long)m * K)[i];
+    for (int i = tid; i < K / 32; i += 256) sxds[i] = a.xds[(long)m * (K / 32) + i];
+  }
   __syncthreads();
+  probe_mark(a.probe, 3);
   const int e = s_e;
   const long ob = ((long)m * a.n_used + j) * a.I + chunk * 32;
   bool ok = true;
   if (e >= 0) ok = mbar_wait(&bar, 0, a.fault, a.layer);
+  probe_mark(a.probe, 4);
   if (e < 0 || !ok) {
     const bool bad = e == -2 || !ok;                   // a slot served elsewhere contributes zeros; a fault NaN
     if (tid < 32) {
@@ -639,6 +763,7 @@ __global__ void __launch_bounds__(256, 2) gate_up_staged_kernel(const GateUpStag
     }
   }
   __syncthreads();
+  probe_mark(a.probe, 5);
   if (warp == 0) {
     const float v = s_act[lane];
     float d, s;
@@ -663,6 +788,7 @@ struct DownStagedArgs {
   float* out; long out_stride;
   unsigned* fault; int layer;
   PushOut push;
+  long long* probe;
 };
 
 template <class T, int UPL>
@@ -686,7 +812,7 @@ __device__ __forceinline__ float down_row_staged(const DownStagedArgs& a, const 
         U::loadu(sw + (long)j * slot_bytes + (long)r * rb, u, a.I, regs);
         ActRegs act;
         const long ab = (long)j * a.I;
-        ActOf<T>::load(reinterpret_cast<const uint32_t*>(sact + ab), reinterpret_cast<const F2*>(sads + ab / 32), u, act);
+        StagedAct<T>::load(sact + ab, sads + ab / 32, u, upe, act);
         const float v = ActOf<T>::dot(regs, u, act);
 #pragma unroll
         for (int q = 0; q < kMaxTopK; ++q) if (q == j) part[q] += v;
@@ -710,7 +836,6 @@ __global__ void __launch_bounds__(256, 2) down_staged_kernel(const DownStagedArg
   __shared__ float s_w[kMaxTopK];
   __shared__ float s_y[32];
   __shared__ int s_nvalid;
-  pdl_launch();
   const int m = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int d0 = blockIdx.x * a.rows_per_block;
@@ -720,9 +845,12 @@ __global__ void __launch_bounds__(256, 2) down_staged_kernel(const DownStagedArg
   uint8_t* sw = smem;                                                       // [n_used][rows_per_block][rb]
   int8_t* sact = reinterpret_cast<int8_t*>(smem + (size_t)a.n_used * slot_bytes);   // [n_used][I]
   float2* sads = reinterpret_cast<float2*>(sact + (size_t)a.n_used * a.I);  // [n_used][I / 32]
+  probe_mark(a.probe, 0);
   if (tid == 0) mbar_init(&bar, 1);
   __syncthreads();
   pdl_wait();
+  pdl_launch();
+  probe_mark(a.probe, 1);
   if (tid == 0) {
     int nvalid = 0;
     bool bad = false;
@@ -746,14 +874,19 @@ __global__ void __launch_bounds__(256, 2) down_staged_kernel(const DownStagedArg
   }
   {
     const long ab = (long)m * a.n_used * a.I;
-    for (int i = tid; i < a.n_used * a.I / 16; i += 256)
-      reinterpret_cast<uint4*>(sact)[i] = reinterpret_cast<const uint4*>(a.actq + ab)[i];
+    const int cps = a.I / 16, upe = a.I / 64, layout = staged_layout(a.dtype);      // chunks and units per slot row
+    for (int i = tid; i < a.n_used * cps; i += 256) {
+      const int j = i / cps, c = i - j * cps;
+      reinterpret_cast<uint4*>(sact)[j * cps + act_chunk_pos(c, upe, layout)] = reinterpret_cast<const uint4*>(a.actq + ab)[i];
+    }
     for (int i = tid; i < a.n_used * a.I / 32; i += 256) sads[i] = a.actds[ab / 32 + i];
   }
   __syncthreads();
+  probe_mark(a.probe, 2);
   const int nvalid = s_nvalid;
   bool ok = nvalid >= 0;
   if (nvalid > 0) ok = mbar_wait(&bar, 0, a.fault, a.layer) && ok;
+  probe_mark(a.probe, 3);
   for (int r = warp; r < nrows; r += 8) {
     float y;
     if constexpr (FAM == 0) {
@@ -780,6 +913,7 @@ __global__ void __launch_bounds__(256, 2) down_staged_kernel(const DownStagedArg
     if (lane == 0) s_y[r] = ok ? y : kNaN;
   }
   __syncthreads();
+  probe_mark(a.probe, 4);
   if (tid < nrows) {
     const int d = d0 + tid;
     float y = s_y[tid];
@@ -792,6 +926,9 @@ __global__ void __launch_bounds__(256, 2) down_staged_kernel(const DownStagedArg
     }
   }
 }
+
+int g_stage_dbg = 0;
+long long* g_stage_probe = nullptr;
 
 static bool staged_type(int t) {
   return t == WT_Q4_K || t == WT_Q5_K || t == WT_Q6_K || t == WT_Q8_0 || t == WT_NVFP4 || t == WT_FP8_B128 || t == WT_Q2_K ||
@@ -828,6 +965,12 @@ static cudaError_t gemv_staged_dispatch(const GemvArgs& a, int mb, int grid, siz
 using namespace bl;
 
 extern "C" {
+
+// Timing experiments on the staged GEMV (kernel_bench --dbg N): 1 = release the dependents first instead of after
+// the wait, 2 = skip the dot products, 4 = skip the bulk copy, 8 = skip the activation prologue.  0 in normal use.
+void bl_set_stage_debug(int flags) { bl::g_stage_dbg = flags; }
+// Arms (device pointer to 16 int64 words) or disarms (null) the phase probe of the attention / expert launches.
+void bl_set_stage_probe(long long* words) { bl::g_stage_probe = words; }
 
 // Same contract as bl_gemv for quantised weight rows.  Returns BL_ERR_LIMIT (and launches nothing) when the
 // weight rows of one block would not fit the shared-memory stage: the caller then uses bl_gemv.
@@ -879,6 +1022,7 @@ int bl_gemv_staged(int nseg, const void* const* w, const int* rows, const int* w
   a.xq = xq; a.xds = (const float2*)xds;
   a.out = out; a.out_stride = out_stride; a.resid = resid; a.resid_stride = resid_stride;
   a.fault = fault; a.layer = layer;
+  a.dbg = g_stage_dbg;
   if (red_desc) { a.red = *(const ReduceIn*)red_desc; BL_REQUIRE(norm && a.red.n_ranks <= kMaxRanks && a.red.H == K, BL_ERR_SHAPE); }
   if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks, BL_ERR_SHAPE); }
   cudaError_t e;
@@ -901,7 +1045,7 @@ int bl_attn_fused(const float* qkv, long qkv_stride, const float* q_gain, const 
   const int G = n_q / n_kv;
   AttnArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, M, n_seg, ctx_limit, row_pos, row_seq,
              block_table, max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, part_ml, part_acc, tickets, out, outq,
-             (float2*)outds, fault, layer};
+             (float2*)outds, fault, layer, g_stage_probe};
   dim3 grid(n_seg, n_kv, M);
   const int n_patch = M < kMaxPatch ? M : kMaxPatch;
   const size_t smem = (size_t)G * head * 4 + 2 * kKeyTile * (head + 8) * 2 + 2 * kKeyTile * head * 2 + (size_t)n_patch * 2 * head * 2;
@@ -919,9 +1063,12 @@ int bl_attn_fused(const float* qkv, long qkv_stride, const float* q_gain, const 
   return (int)e;
 }
 
-int bl_gate_up_staged(const int8_t* xq, const float* xds, const int* ids, const int* slot_map, const void* gate,
-                      const void* up, int wtype, const void* down, long down_expert_bytes, int K, int I, int E, int n_used,
-                      int M, int8_t* actq, float* actds, float* act_f32, unsigned* fault, int layer, cudaStream_t st) {
+// route_logits != null: every block routes its row from the logits (block (0, 0, m) writes ids / wts / heat);
+// otherwise ids are read as given.
+int bl_gate_up_staged(const int8_t* xq, const float* xds, const float* route_logits, const float* bias, int mode, int renorm,
+                      float scale, int n_group, int topk_group, int* ids, float* wts, unsigned* heat, const int* slot_map,
+                      const void* gate, const void* up, int wtype, const void* down, long down_expert_bytes, int K, int I, int E,
+                      int n_used, int M, int8_t* actq, float* actds, float* act_f32, unsigned* fault, int layer, cudaStream_t st) {
   BL_REQUIRE(K % 256 == 0 && I % 32 == 0 && M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
   BL_REQUIRE(staged_type(wtype), BL_ERR_TYPE);
   const long rb = resident_row_bytes(wtype, K);
@@ -929,8 +1076,13 @@ int bl_gate_up_staged(const int8_t* xq, const float* xds, const int* ids, const 
   const size_t smem = (size_t)64 * rb + K + (size_t)(K / 32) * 8 + 16;
   BL_REQUIRE(smem <= kStagedSmemMax && 64 * rb < (1 << 20), BL_ERR_LIMIT);
   BL_REQUIRE(((uintptr_t)gate & 15) == 0 && ((uintptr_t)up & 15) == 0 && ((uintptr_t)down & 15) == 0 && down_expert_bytes % 16 == 0, BL_ERR_ALIGN);
-  GateUpStagedArgs a{xq, (const float2*)xds, ids, slot_map, (const uint8_t*)gate, (const uint8_t*)up, wtype,
-                     (const uint8_t*)down, down_expert_bytes, K, I, E, n_used, M, actq, (float2*)actds, act_f32, fault, layer};
+  if (route_logits) {
+    BL_REQUIRE(E % 4 == 0 && E <= kMaxExperts && n_group >= 1 && n_group <= 16 && E % n_group == 0 && topk_group >= 1 &&
+               topk_group <= n_group && wts, BL_ERR_LIMIT);
+  }
+  GateUpStagedArgs a{xq, (const float2*)xds, RouteParams{route_logits, bias, E, n_used, mode, renorm, scale, n_group, topk_group},
+                     ids, wts, heat, slot_map, (const uint8_t*)gate, (const uint8_t*)up, wtype,
+                     (const uint8_t*)down, down_expert_bytes, K, I, E, n_used, M, actq, (float2*)actds, act_f32, fault, layer, g_stage_probe};
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(gate_up_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStagedSmemMax);
@@ -958,7 +1110,7 @@ int bl_down_staged(const int8_t* actq, const float* actds, const int* ids, const
   const size_t smem = (size_t)n_used * rpb * rb + (size_t)n_used * I + (size_t)n_used * (I / 32) * 8 + 16;
   BL_REQUIRE(smem <= kStagedSmemMax && (size_t)n_used * rpb * rb < (1 << 20), BL_ERR_LIMIT);
   DownStagedArgs a{actq, (const float2*)actds, ids, wts, slot_map, (const uint8_t*)down, dtype, I, H, E, n_used, M, rpb,
-                   resid, resid_stride, extra, extra_stride, out, out_stride, fault, layer, PushOut{}};
+                   resid, resid_stride, extra, extra_stride, out, out_stride, fault, layer, PushOut{}, g_stage_probe};
   if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks && M <= kMaxRows, BL_ERR_SHAPE); }
   dim3 grid((H + rpb - 1) / rpb, M);
   static bool attr_set = false;

@@ -35,13 +35,48 @@ struct GemvArgs {
   PushOut push;            // n_ranks > 0: the result is a partial update pushed to every rank (producer half)
   int stage_bytes;         // staged kernel: bytes of shared memory reserved for a block's weight rows
   int rpb_max;             // staged kernel: most rows any block owns
+  int dbg;                 // staged kernel: timing-experiment switches (0 in normal use)
+  // Weights that a LATER launch will stream (the next layer's projections): every block asks L2 to fetch its
+  // share of each span before it waits for its predecessor, so that launch finds them on chip.
+  const uint8_t* pf_ptr[6];
+  long pf_bytes[6];
+  int n_pf;
 };
+
+// One thread per block: ask L2 to prefetch this block's 1 / gridDim.x share of each span (16-byte granules).
+__device__ __forceinline__ void prefetch_spans_l2(const uint8_t* const* ptr, const long* bytes, int n) {
+  for (int i = 0; i < n; ++i) {
+    const long share = ((bytes[i] + gridDim.x - 1) / gridDim.x + 15) & ~15L;
+    const long lo = (long)blockIdx.x * share;
+    long left = bytes[i] - lo;
+    left = left < share ? left : share;
+    left &= ~15L;
+    for (long o = 0; o < left; o += 32768) {
+      const unsigned n_b = (unsigned)((left - o) < 32768 ? (left - o) : 32768);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr[i] + lo + o), "r"(n_b) : "memory");
+    }
+  }
+}
+
+
+// ---- shared-memory layout of a q8 activation row ----------------------------------------
+// The codes of a K-value row are kept in 16-byte chunks.  Layout 0 is linear.  The staged kernels read a
+// row with lane u fetching the four chunks of weight unit u, which in a linear row lie 64 bytes apart from the
+// next lane's (a 4-way bank conflict on every load); layouts 1 and 2 store chunk c where consecutive lanes
+// read consecutive chunks:
+//   1  units of 64 consecutive values (every type but Q6_K): chunk 4u + i sits at i * nunits + u
+//   2  Q6_K units (four runs of 16 values, 32 apart): chunk 16 sb + 8 n + 2 g + h sits at g * nunits + (4 sb + 2 n + h)
+__device__ __forceinline__ int act_chunk_pos(int c, int nunits, int layout) {
+  if (layout == 1) return (c & 3) * nunits + (c >> 2);
+  if (layout == 2) return ((c >> 1) & 3) * nunits + 4 * (c >> 4) + 2 * ((c >> 3) & 1) + (c & 1);
+  return c;
+}
 
 // ---- activation prologue ------------------------------------------------------------
 // sq/sds receive q8(x * gain) WITHOUT the RMS scale; s_scale[m] receives the scale.
 template <int MB, bool FLOATW>
 __device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, float2* sds, float* sx, float* s_scale,
-                                              double* red) {
+                                              double* red, int layout = 0) {
   const int K = a.K, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool reduce = a.red.n_ranks > 0;
   __shared__ int s_gave_up;
@@ -87,7 +122,7 @@ __device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, flo
       uint2 packed;
       packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((unsigned)(q[3] & 0xFF) << 24);
       packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((unsigned)(q[7] & 0xFF) << 24);
-      *reinterpret_cast<uint2*>(sq + (long)m * K + i0) = packed;
+      *reinterpret_cast<uint2*>(sq + (long)m * K + act_chunk_pos(i0 >> 4, K / 64, layout) * 16 + (i0 & 15)) = packed;
       if ((tid & 3) == 0) sds[(long)m * (K / 32) + i0 / 32] = make_float2(d, d * (float)sum);
       if (FLOATW) {
         *reinterpret_cast<float4*>(sx + (long)m * K + i0) = make_float4(v[0], v[1], v[2], v[3]);
@@ -108,12 +143,13 @@ __device__ __forceinline__ void prologue_norm(const GemvArgs& a, int8_t* sq, flo
 }
 
 template <int MB>
-__device__ __forceinline__ void prologue_q8in(const GemvArgs& a, int8_t* sq, float2* sds, float* s_scale) {
+__device__ __forceinline__ void prologue_q8in(const GemvArgs& a, int8_t* sq, float2* sds, float* s_scale, int layout = 0) {
   const int K = a.K, tid = threadIdx.x;
   for (int i = tid; i < MB * K / 16; i += 256) {
     int m = (i * 16) / K;
     const int ms = m < a.M ? m : a.M - 1;
-    reinterpret_cast<uint4*>(sq)[i] = reinterpret_cast<const uint4*>(a.xq + (long)ms * K)[i - m * (K / 16)];
+    const int c = i - m * (K / 16);
+    reinterpret_cast<uint4*>(sq)[m * (K / 16) + act_chunk_pos(c, K / 64, layout)] = reinterpret_cast<const uint4*>(a.xq + (long)ms * K)[c];
   }
   for (int i = tid; i < MB * (K / 32); i += 256) {
     int m = i / (K / 32);

@@ -188,6 +188,7 @@ struct GateUpArgs {
   int8_t* actq; float2* actds;           // [M, n_used, I] q8
   float* act_f32;                        // optional fp32 copy
   unsigned* fault; int layer;
+  const uint8_t* down; long down_expert_bytes;   // optional: the down stack, whose chosen matrices L2 is asked to prefetch
 };
 
 // two activation outputs (2 gate rows + 2 up rows) of one warp
@@ -227,6 +228,7 @@ __global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a)
   pdl_wait();
   pdl_launch();
   if (a.route.logits) {
+    // block-wide rank counting: measured faster here than top_k rounds of a single warp's arg-max
     __shared__ RouteShared rs;
     int id; float w;
     const bool ok = route_block(a.route, m, rs, id, w);
@@ -261,6 +263,14 @@ __global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a)
   const long rb = resident_row_bytes(a.gtype, K);
   const int8_t* xq = a.xq + (long)m * K;
   const float2* xds = a.xds + (long)m * (K / 32);
+  if (a.down && tid == 32) {
+    // the down launch that follows streams expert e's matrix: this block asks L2 for its 1 / gridDim.x share
+    const long share = (a.down_expert_bytes / gridDim.x) & ~15L;
+    for (long o = 0; o < share; o += 32768) {
+      const unsigned nb = (unsigned)((share - o) < 32768 ? (share - o) : 32768);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.down + (long)e * a.down_expert_bytes + (long)chunk * share + o), "r"(nb) : "memory");
+    }
+  }
 #pragma unroll 1
   for (int half = 0; half < 2; ++half) {
     const long row0 = (long)e * a.I + chunk * 32 + warp * 4 + half * 2;
@@ -493,7 +503,7 @@ int bl_gate_up_sel(const int8_t* xq, const float* xds, const float* route_logits
                    int renorm, float scale, int n_group, int topk_group, int* ids, float* wts, unsigned* heat,
                    const int* slot_map, const void* gate, const void* up, int gtype, int utype, int K, int I, int E,
                    int n_used, int M, int8_t* actq, float* actds, float* act_f32, unsigned* fault, int layer,
-                   cudaStream_t st) {
+                   const void* down, long down_expert_bytes, cudaStream_t st) {
   BL_REQUIRE(K % 256 == 0 && I % 32 == 0 && M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
   BL_REQUIRE(gtype == utype, BL_ERR_TYPE);
   BL_REQUIRE(gtype == WT_Q4_K || gtype == WT_Q5_K || gtype == WT_Q6_K || gtype == WT_Q8_0 || is_plane_family(gtype), BL_ERR_TYPE);
@@ -505,6 +515,8 @@ int bl_gate_up_sel(const int8_t* xq, const float* xds, const float* route_logits
   a.gate = (const uint8_t*)gate; a.up = (const uint8_t*)up; a.gtype = gtype; a.utype = utype;
   a.K = K; a.I = I; a.E = E; a.n_used = n_used; a.M = M;
   a.actq = actq; a.actds = (float2*)actds; a.act_f32 = act_f32; a.fault = fault; a.layer = layer;
+  BL_REQUIRE(((uintptr_t)down & 15) == 0 && down_expert_bytes % 16 == 0, BL_ERR_ALIGN);
+  a.down = (const uint8_t*)down; a.down_expert_bytes = down_expert_bytes;
   if (is_plane_family(gtype)) return (int)launch(gate_up_sel_kernel<2>, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
   return (int)launch(gate_up_sel_kernel<0>, dim3(I / 32, n_used, M), dim3(256), 0, st, a);
 }

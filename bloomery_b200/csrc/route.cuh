@@ -133,4 +133,90 @@ __device__ __forceinline__ bool route_block(const RouteParams& p, int m, RouteSh
 }
 
 
+// The same routing by ONE warp, for the common shape (one expert group, at most 256 experts, a multiple of 32):
+// no block barriers, so a kernel can route in warp 0 while its other warps fetch activations.  Scores, ranks,
+// weights and tie rule are those of route_block (same sums in the same order: the results are bit-equal).
+struct __align__(16) RouteWarpShared {
+  int ids[kMaxTopK];
+  float wraw[kMaxTopK];
+};
+
+__device__ __forceinline__ bool route_warp_ok(const RouteParams& p) { return p.n_group <= 1 && p.E <= 256 && (p.E % 32) == 0; }
+
+__device__ __forceinline__ bool route_warp(const RouteParams& p, int m, RouteWarpShared& sh, int lane, int& my_id, float& my_w) {
+  const int per = p.E / 32;
+  float sc[8], wv[8];
+  bool nonfinite = false;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    sc[c] = 0.f; wv[c] = 0.f;
+    if (c < per) {
+      const int e = lane + 32 * c;
+      const float l = __ldcg(p.logits + (long)m * p.E + e);
+      if (!isfinite(l)) nonfinite = true;
+      if (p.mode == 0) { sc[c] = l; wv[c] = l; }
+      else { const float sg = 1.0f / (1.0f + expf(-l)); wv[c] = sg; sc[c] = sg + (p.bias ? p.bias[e] : 0.f); }
+    }
+  }
+  if (lane < kMaxTopK) { sh.ids[lane] = 0; sh.wraw[lane] = 0.f; }
+  if (__any_sync(0xffffffffu, nonfinite)) { my_id = 0; my_w = __int_as_float(0x7fc00000); return false; }
+  // top_k rounds of a warp arg-max (larger score wins, equal scores go to the smaller id: the order rank counting
+  // gives); a single warp has no spare lanes for all-pairs counting, and a round is ~50 dependent instructions
+  for (int r = 0; r < p.top_k; ++r) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      if (c < per && sc[c] > bv) { bv = sc[c]; bi = lane + 32 * c; }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == (bi & 31)) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c == (bi >> 5)) { sh.ids[r] = bi; sh.wraw[r] = wv[c]; sc[c] = -INFINITY; }
+    }
+  }
+  float total = 1.f;
+  if (p.mode == 0 && !p.renorm) {
+    float top = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) if (c < per) top = fmaxf(top, wv[c]);
+    top = warp_max(top);
+    double part = 0.0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) if (c < per) part += (double)expf(wv[c] - top);
+    total = (float)warp_sum_d(part);
+  }
+  __syncwarp();
+  my_id = lane < p.top_k ? sh.ids[lane] : 0;
+  float w = 0.f;
+  if (lane < p.top_k) {
+    if (p.mode == 0) {
+      const float top = sh.wraw[0];
+      w = expf(sh.wraw[lane] - top);
+      if (p.renorm) {
+        double sum = 0.0;
+        for (int j = 0; j < p.top_k; ++j) sum += (double)expf(sh.wraw[j] - top);
+        w = w / (float)sum;
+      } else {
+        w = w / total;
+      }
+    } else {
+      w = sh.wraw[lane];
+      if (p.renorm) {
+        double sum = 0.0;
+        for (int j = 0; j < p.top_k; ++j) sum += (double)sh.wraw[j];
+        w = w / (float)sum;
+      }
+    }
+    w *= p.scale;
+  }
+  my_w = w;
+  return true;
+}
+
 }  // namespace bl

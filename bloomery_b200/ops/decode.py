@@ -79,6 +79,20 @@ def _family(qtype: str) -> int:
 
 _STAGED = True
 _STAGE_SLICE_MAX = 90 * 1024
+# which launches take the staged form when it is on (BLOOMERY_STAGED_PARTS): gemv, attn, moe, and prefetch (L2
+# prefetch of the next layer's projections and of the chosen down matrices).  Measured on the Qwen3-30B-A3B shape
+# (ms per decode step): none 2.09, attn 2.05, gemv +0.04, moe +0.22 (bulk copies that can only start once the
+# routing is known lose to per-thread loads), so the default keeps the fused attention launch and the prefetches.
+_PARTS = {"attn", "prefetch"}
+
+
+def set_staged_parts(parts) -> None:
+    global _PARTS
+    _PARTS = {x.strip() for x in (parts.split(",") if isinstance(parts, str) else parts) if x.strip()}
+
+
+def staged_part(name: str) -> bool:
+    return _STAGED and name in _PARTS
 
 
 def set_staged(on: bool) -> None:
@@ -105,7 +119,9 @@ def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torc
          gain: Optional[torch.Tensor] = None, eps: float = 1e-6, xq: Optional[torch.Tensor] = None,
          xds: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
          red: Optional[ReduceIn] = None, push: Optional[PushOut] = None,
-         fault: Optional[torch.Tensor] = None, layer: int = 0) -> None:
+         fault: Optional[torch.Tensor] = None, layer: int = 0, prefetch: Optional[Sequence[torch.Tensor]] = None) -> None:
+    """``prefetch``: up to six tensors a later launch will stream (the next layer's projections); the launch asks L2
+    for them before it waits for its predecessor."""
     fams = [_family(sg.qtype) for sg in segs]
     if len(set(fams) - {1}) > 1 or (2 in fams and 1 in fams):
         # segments of different kernel families (e.g. a Q5_0 fallback tensor beside K-quants): one call per run
@@ -117,7 +133,7 @@ def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torc
             width = sum(sg.rows for sg in segs[i:j])
             gemv(segs[i:j], M, out[:, col:col + width], x=x, gain=gain, eps=eps, xq=xq, xds=xds,
                  resid=resid[:, col:col + width] if resid is not None else None, red=red if i == 0 else None,
-                 push=push, fault=fault, layer=layer)
+                 push=push, fault=fault, layer=layer, prefetch=prefetch if i == 0 else None)
             col += width
             i = j
         return
@@ -127,7 +143,7 @@ def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torc
     rows = (ctypes.c_int * n)(*[s.rows for s in segs])
     wts = (ctypes.c_int * n)(*[s.wt for s in segs])
     norm = x is not None
-    if _STAGED and 1 not in fams and _gemv_fits_stage(segs, M):
+    if staged_part("gemv") and 1 not in fams and _gemv_fits_stage(segs, M):
         rc = cuda().bl_gemv_staged(I(n), wp, rows, wts, I(K), I(M), I(1 if norm else 0),
                                    p(x), L(x.stride(0) if norm else 0), p(gain), F(eps), p(xq), p(xds),
                                    p(out), L(out.stride(0)), p(resid), L(resid.stride(0) if resid is not None else 0),
@@ -135,10 +151,13 @@ def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torc
         if rc != -5:                         # -5: a block's rows would not fit the stage; the streaming kernel serves it
             check(rc, "bl_gemv_staged")
             return
+    pf = list(prefetch or [])[:6] if "prefetch" in _PARTS else []
+    pfp = (ctypes.c_void_p * max(1, len(pf)))(*[t.data_ptr() for t in pf])
+    pfb = (ctypes.c_long * max(1, len(pf)))(*[t.numel() * t.element_size() for t in pf])
     rc = cuda().bl_gemv(I(n), wp, rows, wts, I(K), I(M), I(1 if norm else 0),
                         p(x), L(x.stride(0) if norm else 0), p(gain), F(eps), p(xq), p(xds),
                         p(out), L(out.stride(0)), p(resid), L(resid.stride(0) if resid is not None else 0),
-                        _ref(red), _ref(push), p(fault), I(layer), I(sm_count()), stream())
+                        _ref(red), _ref(push), p(fault), I(layer), I(sm_count()), I(len(pf)), pfp, pfb, stream())
     check(rc, "bl_gemv")
 
 
@@ -217,14 +236,19 @@ def route_rows(logits, rule: RouteRule, M: int, ids, wts, heat, fault, layer: in
 
 def gate_up_sel(xq, xds, ids, slot_map, gate: QWeight, up: QWeight, n_expert: int, n_used: int, M: int, actq, actds,
                 act_f32, fault, layer: int, *, route_logits=None, rule: Optional[RouteRule] = None, wts=None,
-                heat=None) -> None:
+                heat=None, down: Optional[QWeight] = None) -> None:
     """gate·up·SwiGLU of the chosen experts.  With ``route_logits`` every block routes its own
-    row (and ids / wts / heat are written for the launches that follow); else ``ids`` is read."""
+    row (and ids / wts / heat are written for the launches that follow); else ``ids`` is read.  ``down``: the
+    layer's down stack; the launch asks L2 to prefetch the chosen experts' matrices for the launch that follows."""
     r = rule or RouteRule(n_used)
+    if "prefetch" not in _PARTS:
+        down = None
     rc = cuda().bl_gate_up_sel(p(xq), p(xds), p(route_logits), p(r.bias), I(r.mode), I(1 if r.renorm else 0),
                                F(r.scale), I(r.n_group), I(r.topk_group), p(ids), p(wts), p(heat), p(slot_map),
                                p(gate.data), p(up.data), I(gate.wt), I(up.wt), I(gate.k), I(gate.rows), I(n_expert),
-                               I(n_used), I(M), p(actq), p(actds), p(act_f32), p(fault), I(layer), stream())
+                               I(n_used), I(M), p(actq), p(actds), p(act_f32), p(fault), I(layer),
+                               p(down.data if down is not None else None), L(down.data.stride(0) if down is not None else 0),
+                               stream())
     check(rc, "bl_gate_up_sel")
 
 
@@ -239,19 +263,27 @@ def down_combine(actq, actds, ids, wts, slot_map, down: QWeight, n_expert: int, 
 
 
 def gate_up_staged(xq, xds, ids, slot_map, gate: QWeight, up: QWeight, n_expert: int, n_used: int, M: int, actq, actds,
-                   act_f32, fault, layer: int, down: Optional[QWeight] = None) -> None:
-    """gate.x, up.x, SwiGLU, q8 of the experts named in ``ids`` (shared-memory staged).  ``down``: the layer's down
-    stack, whose chosen matrices the launch asks L2 to prefetch for the launch that follows."""
+                   act_f32, fault, layer: int, down: Optional[QWeight] = None, *, route_logits=None,
+                   rule: Optional["RouteRule"] = None, wts=None, heat=None) -> None:
+    """gate.x, up.x, SwiGLU, q8 of the chosen experts (shared-memory staged).  With ``route_logits`` every block routes
+    its own row (warp 0, beside the activation fetch) and ``ids`` / ``wts`` / ``heat`` are written for the launches that
+    follow; else ``ids`` is read.  ``down``: the layer's down stack, whose chosen matrices the launch asks L2 to
+    prefetch for the launch that follows."""
+    r = rule or RouteRule(n_used)
+    if not staged_part("prefetch"):
+        down = None
     deb = down.data.stride(0) if down is not None else 0
-    rc = cuda().bl_gate_up_staged(p(xq), p(xds), p(ids), p(slot_map), p(gate.data), p(up.data), I(gate.wt),
-                                  p(down.data if down is not None else None), L(deb), I(gate.k), I(gate.rows),
-                                  I(n_expert), I(n_used), I(M), p(actq), p(actds), p(act_f32), p(fault), I(layer), stream())
+    rc = cuda().bl_gate_up_staged(p(xq), p(xds), p(route_logits), p(r.bias), I(r.mode), I(1 if r.renorm else 0), F(r.scale),
+                                  I(r.n_group), I(r.topk_group), p(ids), p(wts), p(heat), p(slot_map), p(gate.data),
+                                  p(up.data), I(gate.wt), p(down.data if down is not None else None), L(deb), I(gate.k),
+                                  I(gate.rows), I(n_expert), I(n_used), I(M), p(actq), p(actds), p(act_f32), p(fault),
+                                  I(layer), stream())
     check(rc, "bl_gate_up_staged")
 
 
 def moe_fits_stage(gate: QWeight, down: QWeight, n_used: int) -> bool:
     """Whether the staged expert kernels serve these stacks (a block's rows fit the shared-memory stage)."""
-    if not _STAGED or gate.qtype in ("F32", "F16", "BF16") or down.qtype in ("F32", "F16", "BF16"):
+    if not staged_part("moe") or gate.qtype in ("F32", "F16", "BF16") or down.qtype in ("F32", "F16", "BF16"):
         return False
     rb_g = gate.data.shape[-1]
     rb_d = down.data.shape[-1]

@@ -29,6 +29,17 @@ def main(argv=None) -> int:
         i = argv.index("--rows")
         rows = int(argv[i + 1])
         del argv[i:i + 2]
+    if "--dbg" in argv:
+        i = argv.index("--dbg")
+        from bloomery_b200.ops._lib import cuda
+        import ctypes
+        cuda().bl_set_stage_debug(ctypes.c_int(int(argv[i + 1])))
+        print("stage debug flags", argv[i + 1])
+        del argv[i:i + 2]
+    probe = None
+    if "--probe" in argv:
+        argv.remove("--probe")
+        probe = torch.zeros(16, dtype=torch.int64, device="cuda:0")
     argv = [a for a in argv if a != "--no-staged"]
     which = argv[0] if argv else "chain"
     reps = int(argv[1]) if len(argv) > 1 else 4
@@ -119,13 +130,16 @@ def main(argv=None) -> int:
             K.flash_decode(r_q, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, M, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
 
     def router(l):
-        if staged:
+        if which == "router_ticket":
             K.router(x, gain, 1e-6, l["r"], M, logits, hq, hds, None, fault, 0, rule=rule, ids=ids, wts=wts, ticket=tickets[40:])
         else:
             K.router(x, gain, 1e-6, l["r"], M, logits, hq, hds, None, fault, 0)
 
     def gateup(l, routed=True):
-        if staged:
+        if staged and routed:
+            K.gate_up_staged(hq, hds, ids, None, l["g"], l["u"], E, TOPK, M, actq, actds, None, fault, 0, down=l["d"],
+                             route_logits=logits, rule=rule, wts=wts)
+        elif staged:
             K.gate_up_staged(hq, hds, ids, None, l["g"], l["u"], E, TOPK, M, actq, actds, None, fault, 0, down=l["d"])
         elif routed:
             K.gate_up_sel(hq, hds, ids, None, l["g"], l["u"], E, TOPK, M, actq, actds, None, fault, 0, route_logits=logits, rule=rule, wts=wts)
@@ -140,7 +154,7 @@ def main(argv=None) -> int:
             if which in ("chain", "qkv"): K.gemv([l["q"], l["k"], l["v"]], M, qkv, x=x, gain=gain, fault=fault)
             if which in ("chain", "attn"): attn(l)
             if which in ("chain", "o"): K.gemv([l["o"]], M, x, xq=xq, xds=xds, resid=x, fault=fault)
-            if which in ("chain", "router"): router(l)
+            if which in ("chain", "router", "router_ticket"): router(l)
             if which in ("chain", "gateup"): gateup(l)
             if which == "gateup_ids": gateup(l, routed=False)
             if which in ("chain", "down"): down(l)
@@ -161,6 +175,19 @@ def main(argv=None) -> int:
         with torch.cuda.graph(g, stream=s):
             chain()
     torch.cuda.synchronize()
+    if probe is not None:
+        # one eager pass of the last layer with the phase probe armed: cycles between the marks of block (0, 0, 0)
+        from bloomery_b200.ops._lib import cuda
+        import ctypes
+        g.replay()
+        cuda().bl_set_stage_probe(ctypes.c_void_p(probe.data_ptr()))
+        with torch.cuda.stream(s):
+            chain()
+            s.synchronize()
+        cuda().bl_set_stage_probe(ctypes.c_void_p(0))
+        marks = probe.cpu().tolist()
+        live = [m for m in marks if m]
+        print("probe cycles between marks:", [b - a for a, b in zip(live, live[1:])])
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(3):
         g.replay()

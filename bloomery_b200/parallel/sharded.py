@@ -135,7 +135,7 @@ class ShardedEngine(DecodeEngine):
                 x=xb[cur], gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, red=red, fault=self.fault, layer=il)
             if red is not None:
                 cur ^= 1
-            if K.staged():
+            if K.staged_part("attn"):
                 add(K.attn_fused, self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
                     self.inv_freq, s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq,
                     kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.n_seg, self.slot_ctx, self.part_ml, self.part_acc,
@@ -161,18 +161,14 @@ class ShardedEngine(DecodeEngine):
             ids, wts = self.r_ids_all[il], self.r_wts_all[il]
             gate, up, down = w.q[b + "ffn_gate_exps.weight"], w.q[b + "ffn_up_exps.weight"], w.q[b + "ffn_down_exps.weight"]
             staged = gate.qtype == up.qtype and K.moe_fits_stage(gate, down, s.n_used)
-            if staged:
-                add(K.router, xb[cur], w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M,
-                    self.r_logits, self.xq, self.xds, None, self.fault, il, red=red, rule=self._rule(il), ids=ids, wts=wts,
-                    heat=self.heat[il], ticket=self.tickets[8 * max(1, s.n_kv):])
-            else:
-                add(K.router, xb[cur], w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M,
-                    self.r_logits, self.xq, self.xds, None, self.fault, il, red=red)
+            add(K.router, xb[cur], w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M,
+                self.r_logits, self.xq, self.xds, None, self.fault, il, red=red)
             if red is not None:
                 cur ^= 1
             if staged:
                 add(K.gate_up_staged, self.xq, self.xds, ids, self.slot_map, gate, up, s.n_expert, s.n_used, M, self.actq,
-                    self.actds, None, self.fault, il, down=down)
+                    self.actds, None, self.fault, il, down=down, route_logits=self.r_logits, rule=self._rule(il), wts=wts,
+                    heat=self.heat[il])
             else:
                 add(K.gate_up_sel, self.xq, self.xds, ids, self.slot_map, gate, up, s.n_expert, s.n_used, M, self.actq,
                     self.actds, None, self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=wts,

@@ -315,8 +315,9 @@ class DecodeEngine:
         if s.mla:
             return self._attn_mla(il, M, x)
         K.gemv([w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
-               x=x, gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il)
-        if K.staged():
+               x=x, gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il,
+               prefetch=self._static_next(il))
+        if K.staged_part("attn"):
             K.attn_fused(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"), self.inv_freq,
                          s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq, kvp.table,
                          kvp.n_pages, kvp.k[il - self.lo], kvp.v[il - self.lo], self.n_seg, self.slot_ctx, self.part_ml,
@@ -330,6 +331,13 @@ class DecodeEngine:
                        s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
                        self.attn_q, self.attn_ds, self.fault, il)
         return 4
+
+    def _static_next(self, il: int):
+        """Weights of the NEXT layer that do not depend on routing (projections, router): the first launch of a layer
+        asks L2 to fetch them, a whole layer ahead of their use."""
+        nb = f"blk.{il + 1}."
+        names = ("attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight", "ffn_gate_inp.weight")
+        return [self.w.q[nb + n].data for n in names if nb + n in self.w.q] if il + 1 < self.hi else None
 
     def _attn_mla(self, il: int, M: int, x: torch.Tensor) -> int:
         """Latent attention: [q_a | kv_a] product, latent append, (q_b product), absorb, latent flash + value
@@ -362,18 +370,17 @@ class DecodeEngine:
         ids, wts = self.r_ids_all[il], self.r_wts_all[il]
         gate, up, down = w.q[b + "ffn_gate_exps.weight"], w.q[b + "ffn_up_exps.weight"], w.q[b + "ffn_down_exps.weight"]
         staged = gate.qtype == up.qtype and K.moe_fits_stage(gate, down, s.n_used)
+        K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
+                 self.xq, self.xds, None, self.fault, il)
         if staged:
-            # the routing launch's last block turns the logits into ids and weights; the expert launches read them
-            K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
-                     self.xq, self.xds, None, self.fault, il, rule=self._rule(il), ids=ids, wts=wts,
-                     heat=self.heat[il], ticket=self.tickets[MAX_ROWS * max(1, s.n_kv):])
+            # warp 0 of every block routes its row from the logits while the other warps fetch the activations
             K.gate_up_staged(self.xq, self.xds, ids, None, gate, up, s.n_expert, s.n_used, M, self.actq, self.actds,
-                             None, self.fault, il, down=down)
+                             None, self.fault, il, down=down, route_logits=self.r_logits, rule=self._rule(il), wts=wts,
+                             heat=self.heat[il])
         else:
-            K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.r_logits,
-                     self.xq, self.xds, None, self.fault, il)
             K.gate_up_sel(self.xq, self.xds, ids, None, gate, up, s.n_expert, s.n_used, M, self.actq, self.actds, None,
-                          self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=wts, heat=self.heat[il])
+                          self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=wts, heat=self.heat[il],
+                          down=down)
         extra, n = None, 3
         if s.n_shared:
             # the shared expert reads the router's q8 rows and lands as an extra addend of the combine

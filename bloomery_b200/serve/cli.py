@@ -195,6 +195,7 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
     host_ops.pool_configure(int(levers.get("BLOOMERY_THREADS")), bool(levers.get("BLOOMERY_PIN")), int(levers.get("BLOOMERY_SPIN")))
     K.set_pdl(bool(levers.get("BLOOMERY_PDL")))
     K.set_staged(bool(levers.get("BLOOMERY_STAGED")))
+    K.set_staged_parts(str(levers.get("BLOOMERY_STAGED_PARTS")))
     K.set_flash_mma(bool(levers.get("BLOOMERY_FLASH_MMA")))
     graphs = bool(levers.get("BLOOMERY_GRAPHS"))
     bound = float(levers.get("BLOOMERY_ENGINE_BOUND"))

@@ -25,8 +25,10 @@ def _qw(w, t):
 def _staged_on():
     from bloomery_b200.ops import decode as K
     K.set_staged(True)
+    K.set_staged_parts("gemv,attn,moe,prefetch")
     yield
     K.set_staged(True)
+    K.set_staged_parts("attn,prefetch")
 
 
 @pytest.mark.parametrize("M", [1, 2, 5, 8])
@@ -235,8 +237,13 @@ def test_staged_experts_equal_streaming_bits_and_router_routes(gt, dt):
         out = torch.zeros(M, H, device=DEV)
         sm = slot_map.to(DEV)
         if on:
-            K.gate_up_staged(xq, xds, ids, sm, gate, up, E, k, M, actq, actds, None, fault, 0, down=down)
-            K.down_staged(actq, actds, ids, wts, sm, down, E, k, M, x, None, out, fault, 0)
+            # routed inside the launch (warp 0): the ids and weights it publishes equal the router launch's
+            ids3 = torch.full_like(ids, -9)
+            wts3 = torch.zeros_like(wts)
+            K.gate_up_staged(xq, xds, ids3, sm, gate, up, E, k, M, actq, actds, None, fault, 0, down=down, route_logits=logits,
+                             rule=rule, wts=wts3)
+            assert torch.equal(ids3, ids) and torch.equal(wts3, wts)
+            K.down_staged(actq, actds, ids3, wts3, sm, down, E, k, M, x, None, out, fault, 0)
         else:
             K.gate_up_sel(xq, xds, ids, sm, gate, up, E, k, M, actq, actds, None, fault, 0)
             K.down_combine(actq, actds, ids, wts, sm, down, E, k, M, x, None, out, fault, 0)
