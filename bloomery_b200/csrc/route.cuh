@@ -49,11 +49,13 @@ struct __align__(16) RouteShared {
   float total;
 };
 
-__device__ __forceinline__ bool route_block(const RouteParams& p, int m, RouteShared& sh, int& my_id, float& my_w) {
+// `smem_logits`: the row's logits in shared memory (a kernel that computed them itself); null = read p.logits.
+__device__ __forceinline__ bool route_block(const RouteParams& p, int m, RouteShared& sh, int& my_id, float& my_w,
+                                            const float* smem_logits = nullptr) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   bool nonfinite = false;
   for (int e = tid; e < p.E; e += nthr) {
-    const float l = __ldcg(p.logits + (long)m * p.E + e);
+    const float l = smem_logits ? smem_logits[e] : __ldcg(p.logits + (long)m * p.E + e);
     if (!isfinite(l)) nonfinite = true;
     if (p.mode == 0) { sh.sc[e] = l; sh.wv[e] = l; }
     else { const float sg = 1.0f / (1.0f + expf(-l)); sh.wv[e] = sg; sh.sc[e] = sg + (p.bias ? p.bias[e] : 0.f); }

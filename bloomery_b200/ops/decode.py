@@ -79,8 +79,11 @@ def _family(qtype: str) -> int:
 
 _STAGED = True
 _STAGE_SLICE_MAX = 90 * 1024
-# which launches take the staged form when it is on (BLOOMERY_STAGED_PARTS): gemv, attn, moe, and prefetch (L2
-# prefetch of the next layer's projections and of the chosen down matrices).  Measured on the Qwen3-30B-A3B shape
+# which launches take the staged form when it is on (BLOOMERY_STAGED_PARTS): gemv, attn, moe, prefetch (L2
+# prefetch of the next layer's projections and of the chosen down matrices) and cluster (a one-row pass runs a
+# layer's whole expert half as one thread-block-cluster launch; measured at top-6 on the Qwen3-30B-A3B layer shape:
+# 23.3 us against 18.9 us for the three launches, and a B200 holds only seven 16-CTA clusters of its 212 KB at once,
+# so top-8 models cannot use it: off by default).  Measured on the Qwen3-30B-A3B shape
 # (ms per decode step): none 2.09, attn 2.05, gemv +0.04, moe +0.22 (bulk copies that can only start once the
 # routing is known lose to per-thread loads), so the default keeps the fused attention launch and the prefetches.
 _PARTS = {"attn", "prefetch"}
@@ -299,6 +302,37 @@ def down_staged(actq, actds, ids, wts, slot_map, down: QWeight, n_expert: int, n
                                L(extra.stride(0) if extra is not None else 0), p(out), L(out.stride(0)), _ref(push),
                                p(fault), I(layer), I(sm_count()), stream())
     check(rc, "bl_down_staged")
+
+
+_cluster_fit_cache = {}
+
+
+def moe_cluster_fits(router: QWeight, gate: QWeight, up: QWeight, down: QWeight, n_used: int) -> bool:
+    """Whether the one-launch cluster form of a layer's expert half (``csrc/moe_cluster.cu``) serves these stacks on
+    the current device: shapes divide by the 16 CTAs of a cluster, a CTA's rows fit its shared memory, and one
+    16-CTA cluster per chosen expert can be resident at once."""
+    if "cluster" not in _PARTS:
+        return False
+    key = (torch.cuda.current_device(), router.qtype, gate.qtype, up.qtype, down.qtype, gate.k, gate.rows, router.rows, n_used)
+    if key not in _cluster_fit_cache:
+        rc = cuda().bl_moe_cluster_fits(I(gate.k), I(gate.rows), I(router.rows), I(n_used), I(router.wt), I(gate.wt),
+                                        I(up.wt), I(down.wt))
+        _cluster_fit_cache[key] = rc == 0
+    return _cluster_fit_cache[key]
+
+
+def moe_cluster(x, gain, eps: float, router: QWeight, rule: "RouteRule", slot_map, gate: QWeight, up: QWeight,
+                down: QWeight, n_used: int, extra, parts, tickets, x_out, logits, ids, wts, heat, fault, layer: int) -> None:
+    """Router + top-k + chosen experts + weighted sum + residual of ONE row in one thread-block-cluster launch.
+    ``x_out`` (a different buffer than ``x``) receives the new residual row; ``parts`` fp32 [n_used, H] and
+    ``tickets`` (16 zeroed int32 words, left zero) are scratch; logits / ids / wts / heat are published as the
+    three-launch chain publishes them."""
+    rc = cuda().bl_moe_cluster(p(x), p(gain), F(eps), p(router.data), I(router.wt), p(rule.bias), I(rule.mode),
+                               I(1 if rule.renorm else 0), F(rule.scale), I(rule.n_group), I(rule.topk_group),
+                               p(slot_map), p(gate.data), p(up.data), I(gate.wt), I(up.wt), p(down.data), I(down.wt),
+                               I(gate.k), I(gate.rows), I(router.rows), I(n_used), p(extra), p(parts), p(tickets),
+                               p(x_out), p(logits), p(ids), p(wts), p(heat), p(fault), I(layer), stream())
+    check(rc, "bl_moe_cluster")
 
 
 def embed_rows(tokens, M: int, table: QWeight, vocab: int, out, fault, step=None) -> None:

@@ -29,6 +29,11 @@ def main(argv=None) -> int:
         i = argv.index("--rows")
         rows = int(argv[i + 1])
         del argv[i:i + 2]
+    global TOPK
+    if "--topk" in argv:
+        i = argv.index("--topk")
+        TOPK = int(argv[i + 1])
+        del argv[i:i + 2]
     if "--dbg" in argv:
         i = argv.index("--dbg")
         from bloomery_b200.ops._lib import cuda
@@ -90,6 +95,8 @@ def main(argv=None) -> int:
     r_g = torch.ones(hd, device=dev)
     r_q = torch.zeros(8, n_q, hd, device=dev)
     rule = K.RouteRule(TOPK)
+    cparts = torch.zeros(TOPK, H, device=dev)
+    x2 = torch.zeros(8, H, device=dev)
     extra = {}
     if which == "gemm":
         from bloomery_b200.ops import gemm as G
@@ -158,6 +165,13 @@ def main(argv=None) -> int:
             if which in ("chain", "gateup"): gateup(l)
             if which == "gateup_ids": gateup(l, routed=False)
             if which in ("chain", "down"): down(l)
+            if which in ("cluster", "chain_cluster"):
+                if which == "chain_cluster":
+                    K.gemv([l["q"], l["k"], l["v"]], M, qkv, x=x, gain=gain, fault=fault)
+                    attn(l)
+                    K.gemv([l["o"]], M, x, xq=xq, xds=xds, resid=x, fault=fault)
+                K.moe_cluster(x, gain, 1e-6, l["r"], rule, None, l["g"], l["u"], l["d"], TOPK, None, cparts, tickets[44:], x2,
+                              logits, ids, wts, None, fault, 0)
             if which == "rope": K.qk_norm_rope_append(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, 1, fpos, fseq, table, n_pages, kc, vc, r_q, fault, 0)
             if which in ("flash", "flash_mma"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
             if which == "gemm": X["G"].gemm_bf16(X["A"], X["B"], X["tt"], out_bf16=X["C"], status=X["gst"])

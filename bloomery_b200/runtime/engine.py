@@ -126,7 +126,8 @@ class DecodeEngine:
         self.xds = torch.zeros(R, H // 32, 2, **f32)
         # completion tickets of the fused attention launch (one per row and KV head) and of the routing launch (one
         # per group of 8 rows); the kernels leave them zero
-        self.tickets = torch.zeros(R * max(1, s.n_kv) + R, **i32)
+        self.tickets = torch.zeros(R * max(1, s.n_kv) + R + 16, **i32)
+        self.x_alt = torch.zeros(R, H, **f32)        # the cluster launch of a layer's expert half writes the residual here
         if s.is_moe:
             self.r_logits = torch.zeros(R, s.n_expert, **f32)
             # chosen experts and weights of every layer of the last pass (the route trace reads them)
@@ -136,6 +137,7 @@ class DecodeEngine:
             self.actq = torch.zeros(R, s.n_used, s.moe_inter, dtype=torch.int8, device=dev)
             self.actds = torch.zeros(R, s.n_used, s.moe_inter // 32, 2, **f32)
             self.heat = torch.zeros(s.n_layer + self.n_mtp, s.n_expert, **i32)
+            self.moe_parts = torch.zeros(s.n_used, H, **f32)
             if s.n_shared:
                 self.sh_gu = torch.zeros(R, 2 * s.shared_inter, **f32)
                 self.sh_actq = torch.zeros(R, s.shared_inter, dtype=torch.int8, device=dev)
@@ -195,7 +197,11 @@ class DecodeEngine:
         if self.stage_first:
             K.embed_rows(self.tokens, M, w.q["token_embd.weight"], s.vocab, x, self.fault); n += 1
         for il in range(self.lo, self.hi):
-            n += self._layer(il, M, x)
+            x, nl = self._layer(il, M, x)
+            n += nl
+        if x is not self.x:
+            self.x.copy_(x); n += 1            # the residual rows of a finished pass live in self.x
+            x = self.x
         if head and self.stage_last:
             head_w = w.q.get("output.weight", w.q["token_embd.weight"])
             K.gemv([head_w], M, self.logits, x=x, gain=w.f["output_norm.weight"], eps=s.rms_eps,
@@ -207,8 +213,9 @@ class DecodeEngine:
                                self.counters[2:3]); n += 1
         return n
 
-    def _layer(self, il: int, M: int, x: torch.Tensor) -> int:
-        """One transformer block on the residual rows ``x``; returns the launch count."""
+    def _layer(self, il: int, M: int, x: torch.Tensor):
+        """One transformer block on the residual rows ``x``; returns (the buffer that now holds the residual rows,
+        the launch count)."""
         s, w = self.spec, self.w
         n = 0
         b = f"blk.{il}."
@@ -216,6 +223,14 @@ class DecodeEngine:
         K.gemv([w.q[b + "attn_output.weight"]], M, x, xq=self.attn_q, xds=self.attn_ds, resid=x,
                fault=self.fault, layer=il); n += 1
         if s.layer_is_moe(il):
+            if M == 1 and type(self)._moe is DecodeEngine._moe and not s.n_shared and self._cluster_ok(il):
+                # one row: router, routing, the chosen experts and the weighted sum as ONE cluster launch
+                other = self.x_alt if x is not self.x_alt else self.x
+                K.moe_cluster(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], self._rule(il), None,
+                              w.q[b + "ffn_gate_exps.weight"], w.q[b + "ffn_up_exps.weight"], w.q[b + "ffn_down_exps.weight"],
+                              s.n_used, None, self.moe_parts, self.tickets[MAX_ROWS * max(1, s.n_kv) + MAX_ROWS:], other,
+                              self.r_logits, self.r_ids_all[il], self.r_wts_all[il], self.heat[il], self.fault, il)
+                return other, n + 1
             n += self._moe(il, M, x)
         else:
             K.gemv([w.q[b + "ffn_gate.weight"], w.q[b + "ffn_up.weight"]], M, self.gu, x=x,
@@ -223,7 +238,12 @@ class DecodeEngine:
             K.swiglu_q8(self.gu, s.dense_inter, M, self.dactq, self.dactds); n += 1
             K.gemv([w.q[b + "ffn_down.weight"]], M, x, xq=self.dactq, xds=self.dactds, resid=x,
                    fault=self.fault, layer=il); n += 1
-        return n
+        return x, n
+
+    def _cluster_ok(self, il: int) -> bool:
+        w, b = self.w, f"blk.{il}."
+        return K.moe_cluster_fits(w.q[b + "ffn_gate_inp.weight"], w.q[b + "ffn_gate_exps.weight"],
+                                  w.q[b + "ffn_up_exps.weight"], w.q[b + "ffn_down_exps.weight"], self.spec.n_used)
 
     def enqueue_mtp(self, M: int) -> int:
         """The draft layer on M rows: params row 0 = the token that FOLLOWS each position, row 3 = the pass row whose
@@ -238,9 +258,10 @@ class DecodeEngine:
                    s.rms_eps, M, self.mtp_xq, self.mtp_xds); n += 1
         K.gemv([w.q[b + "nextn.eh_proj.weight"]], M, self.mtp_x, xq=self.mtp_xq, xds=self.mtp_xds, fault=self.fault,
                layer=il); n += 1
-        n += self._layer(il, M, self.mtp_x)
+        xo, nl = self._layer(il, M, self.mtp_x)
+        n += nl
         head_w = w.q.get("output.weight", w.q["token_embd.weight"])
-        K.gemv([head_w], M, self.mtp_logits, x=self.mtp_x, gain=w.f[b + "nextn.shared_head_norm.weight"], eps=s.rms_eps,
+        K.gemv([head_w], M, self.mtp_logits, x=xo, gain=w.f[b + "nextn.shared_head_norm.weight"], eps=s.rms_eps,
                fault=self.fault, layer=il); n += 1
         K.argmax_rows(self.mtp_logits, s.vocab, M, self.am_blocks, self.am_v, self.am_i, self.counters[1:2],
                       self.tokens_out, None, self.fault); n += 1

@@ -62,7 +62,7 @@ REGISTRY: List[LeverSpec] = [
     LeverSpec("BLOOMERY_ROUTE_TRACE", "str", "", "directory for per-position router traces"),
     LeverSpec("BLOOMERY_TP_PORT", "int", 0, "rendezvous port of the lockstep ranks on 127.0.0.1 (0 = derived from the pid)"),
     LeverSpec("BLOOMERY_STAGED", "bool", True, "decode kernels that stage their weight rows in shared memory with bulk copies"),
-    LeverSpec("BLOOMERY_STAGED_PARTS", "str", "attn,prefetch", "which launches take the staged form: gemv, attn, moe, prefetch (L2 prefetch of the down matrices)"),
+    LeverSpec("BLOOMERY_STAGED_PARTS", "str", "attn,prefetch", "which launches take the staged form: gemv, attn, moe, prefetch (L2 prefetches), cluster (one-row expert half as one cluster launch)"),
 ]
 RETIRED = {"BLOOMERY_WORD_OPS": "stream memops are not used on this build", "BLOOMERY_TIER_LINK": "there is no host-page link: GPUs talk over NVLink",
            "BLOOMERY_TIER_NODES": "multi-machine tiers are not built", "BLOOMERY_TP_NODES": "TP ranks come from torchrun, not from a node list"}

@@ -25,7 +25,7 @@ def _qw(w, t):
 def _staged_on():
     from bloomery_b200.ops import decode as K
     K.set_staged(True)
-    K.set_staged_parts("gemv,attn,moe,prefetch")
+    K.set_staged_parts("gemv,attn,moe,prefetch,cluster")
     yield
     K.set_staged(True)
     K.set_staged_parts("attn,prefetch")
@@ -264,6 +264,62 @@ def test_staged_experts_equal_streaming_bits_and_router_routes(gt, dt):
     assert torch.isnan(out[1]).all() and not torch.isnan(out[0]).any()
 
 
+@pytest.mark.parametrize("gt,dt,H,I,E,k", [("Q4_K", "Q6_K", 2048, 768, 128, 8), ("Q8_0", "Q8_0", 512, 256, 16, 4),
+                                            ("NVFP4", "NVFP4", 1024, 512, 32, 6), ("Q5_K", "Q4_K", 1024, 512, 64, 8)])
+def test_moe_cluster_launch_equals_the_three_launch_chain(gt, dt, H, I, E, k):
+    """Router + routing + experts + combine of one row as ONE cluster launch: same picks and weights, the new residual
+    row within float rounding of the chain's (the down projection is summed per slot before it is weighted)."""
+    from bloomery_b200.ops import decode as K
+    from bloomery_b200.ops.decode import QWeight, RouteRule
+    torch.manual_seed(11)
+    gate, _ = _qw(torch.randn(E, I, H) * 0.03, gt)
+    up, _ = _qw(torch.randn(E, I, H) * 0.03, gt)
+    down, _ = _qw(torch.randn(E, H, I) * 0.03, dt)
+    rw = torch.randn(E, H) * 0.05
+    rq = QWeight(rw.contiguous().view(torch.uint8).reshape(E, -1).to(DEV), "F32", H)
+    if not K.moe_cluster_fits(rq, gate, up, down, k):
+        pytest.skip("this device cannot hold one 16-CTA cluster per chosen expert")
+    x = torch.randn(1, H, device=DEV)
+    gain = (1 + 0.1 * torch.randn(H)).to(DEV)
+    fault = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    rule = RouteRule(k)
+    # the chain
+    logits = torch.zeros(1, E, device=DEV)
+    xq = torch.zeros(1, H, dtype=torch.int8, device=DEV)
+    xds = torch.zeros(1, H // 32, 2, device=DEV)
+    ids = torch.zeros(1, k, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(1, k, device=DEV)
+    actq = torch.zeros(1, k, I, dtype=torch.int8, device=DEV)
+    actds = torch.zeros(1, k, I // 32, 2, device=DEV)
+    ref = torch.zeros(1, H, device=DEV)
+    K.router(x, gain, 1e-6, rq, 1, logits, xq, xds, None, fault, 0)
+    K.gate_up_sel(xq, xds, ids, None, gate, up, E, k, 1, actq, actds, None, fault, 0, route_logits=logits, rule=rule, wts=wts)
+    K.down_combine(actq, actds, ids, wts, None, down, E, k, 1, x, None, ref, fault, 0)
+    # the cluster launch, twice (its tickets must return to zero by themselves), on poisoned scratch
+    parts = torch.full((k, H), float("nan"), device=DEV)
+    tickets = torch.zeros(16, dtype=torch.int32, device=DEV)
+    out = torch.full((1, H), float("nan"), device=DEV)
+    lg2 = torch.zeros(1, E, device=DEV)
+    ids2 = torch.full((1, k), -9, dtype=torch.int32, device=DEV)
+    wts2 = torch.zeros(1, k, device=DEV)
+    heat = torch.zeros(E, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        K.moe_cluster(x, gain, 1e-6, rq, rule, None, gate, up, down, k, None, parts, tickets, out, lg2, ids2, wts2, heat, fault, 0)
+    assert int(fault) == -1 and int(tickets.abs().sum()) == 0 and int(heat.sum()) == 2 * k
+    assert torch.equal(lg2, logits) and torch.equal(ids2, ids) and torch.equal(wts2, wts)
+    scale = ref.abs().max().item()
+    assert (out - ref).abs().max().item() < 2e-5 * max(scale, 1.0), (out - ref).abs().max().item()
+    # one chosen expert lives elsewhere (slot map -1): its slot adds nothing; an extra addend rides along
+    sm = torch.arange(E, dtype=torch.int32)
+    sm[int(ids[0, 2])] = -1
+    extra = torch.randn(1, H, device=DEV)
+    K.gate_up_sel(xq, xds, ids, sm.to(DEV), gate, up, E, k, 1, actq, actds, None, fault, 0)
+    K.down_combine(actq, actds, ids, wts, sm.to(DEV), down, E, k, 1, x, extra, ref, fault, 0)
+    K.moe_cluster(x, gain, 1e-6, rq, rule, sm.to(DEV), gate, up, down, k, extra, parts, tickets, out, lg2, ids2, wts2, heat, fault, 0)
+    assert (out - ref).abs().max().item() < 2e-5 * max(ref.abs().max().item(), 1.0)
+    assert int(fault) == -1
+
+
 def test_engine_tokens_do_not_depend_on_the_kernel_form():
     """Greedy tokens of the tiny model: staged kernels == streaming kernels (both under CUDA graphs)."""
     from bloomery_b200.models.spec import tiny_qwen3moe
@@ -276,6 +332,7 @@ def test_engine_tokens_do_not_depend_on_the_kernel_form():
     toks = []
     for on in (True, False):
         K.set_staged(on)
+        K.set_staged_parts("gemv,attn,moe,prefetch")       # the cluster launch sums the down rows in another order
         eng = DecodeEngine(w, n_slots=1, slot_ctx=256)
         first = eng.prefill(0, prompt, gemm=False)
         toks.append([first] + eng.decode_chain(0, first, len(prompt), 24))
