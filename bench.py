@@ -86,6 +86,9 @@ def main() -> int:
     ap.add_argument("--ttft", type=int, default=4096, help="also time a prompt of this many tokens (0 = skip)")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--staged-parts", dest="staged_parts", default="", help="ablation: which launches take the staged form (gemv,attn,moe,prefetch)")
+    ap.add_argument("--attn-clusters", dest="attn_clusters", type=int, default=-1, help="ablation: 1 / 0 = cluster form of the attention launch on / off")
+    ap.add_argument("--no-predict-down", dest="no_predict_down", action="store_true")
+    ap.add_argument("--predict", type=int, default=-1, help="ablation: experts the side-stream prediction prefetches per layer (0 = off)")
     ap.add_argument("--no-staged", dest="no_staged", action="store_true",
                     help="register-streaming decode kernels instead of the shared-memory staged ones")
     ap.add_argument("--nccl-baseline", dest="nccl_baseline", action="store_true",
@@ -129,6 +132,12 @@ def main() -> int:
     t_load = time.time() - t0
     ctx = max(args.prompt, args.ttft) + warm + 2 * steps + 64
     eng = DecodeEngine(w, n_slots=1, slot_ctx=(ctx + 63) // 64 * 64)
+    if args.attn_clusters >= 0:
+        eng.attn_clusters = bool(args.attn_clusters)
+    if args.predict >= 0:
+        eng.predict_experts = args.predict
+    if args.no_predict_down:
+        eng.predict_down = False
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, spec.vocab, (args.prompt,), generator=g).tolist()
 

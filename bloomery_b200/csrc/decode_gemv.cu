@@ -59,10 +59,11 @@ __device__ __forceinline__ void rows_q(const GemvArgs& a, const GemvSeg& s, int 
         if (u < nunits) {
 #pragma unroll
           for (int m = 0; m < MB; ++m) {
-            const uint32_t* xq = reinterpret_cast<const uint32_t*>(sq + (long)m * K);
-            const F2* xds = reinterpret_cast<const F2*>(sds + (long)m * (K / 32));
+            // the block's activation rows sit in the conflict-free chunk layout of its weight type
+            ActRegs act;
+            StagedAct<T>::load(sq + (long)m * K, sds + (long)m * (K / 32), u, nunits, act);
 #pragma unroll
-            for (int r = 0; r < R; ++r) acc[r][m] += U::dotu(regs[r][c], u, xq, xds);
+            for (int r = 0; r < R; ++r) acc[r][m] += ActOf<T>::dot(regs[r][c], u, act);
           }
         }
       }
@@ -172,22 +173,25 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
   float* sx = s_scale + 8;  // only when FLOATW
 
   if (a.n_pf > 0 && threadIdx.x == 0) prefetch_spans_l2(a.pf_ptr, a.pf_bytes, a.n_pf);
+  int si = 0, col0 = 0;
+#pragma unroll
+  for (int q = 1; q < 4; ++q)
+    if (q < a.nseg && (int)blockIdx.x >= a.seg[q].blk0) { si = q; }
+  for (int q = 0; q < si; ++q) col0 += a.seg[q].rows;
+  // a block serves one weight type: its q8 activation rows take the chunk layout that type's units read without
+  // bank conflicts (act_chunk_pos); float rows read the fp32 copy instead
+  const int act_layout = staged_layout(a.seg[si].wtype);
   bool ready = false;
   auto between = [&]() {
     if (!ready) {
       pdl_wait();
-      if (NORM) prologue_norm<MB, FAM == 1>(a, sq, sds, sx, s_scale, red);
-      else prologue_q8in<MB>(a, sq, sds, s_scale);
+      if (NORM) prologue_norm<MB, FAM == 1>(a, sq, sds, sx, s_scale, red, act_layout);
+      else prologue_q8in<MB>(a, sq, sds, s_scale, act_layout);
       pdl_launch();
       ready = true;
     }
   };
   {
-    int si = 0, col0 = 0;
-#pragma unroll
-    for (int q = 1; q < 4; ++q)
-      if (q < a.nseg && (int)blockIdx.x >= a.seg[q].blk0) { si = q; }
-    for (int q = 0; q < si; ++q) col0 += a.seg[q].rows;
     const GemvSeg& s = a.seg[si];
     // even split of the segment's rows over its warps
     const int W = s.nblk * 8, wg = ((int)blockIdx.x - s.blk0) * 8 + (threadIdx.x >> 5);

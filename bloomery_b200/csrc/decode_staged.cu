@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(256, 2) gemv_staged_kernel(const GemvArgs a) {
 // =======================================================================================================
 constexpr int kPage = 64;
 constexpr int kKeyTile = 32;
+constexpr int kStages = 4;        // key / value tiles in flight per block
 constexpr int kMaxPatch = 64;     // rows of one pass whose keys a block may have to take from the pass itself
 
 struct AttnArgs {
@@ -166,6 +167,7 @@ struct AttnArgs {
   float* out; int8_t* outq; float2* outds; // attention rows [M, n_q * HEAD]: optional fp32, q8 codes, {d, s} per 32
   unsigned* fault; int layer;
   long long* probe;
+  int recv_off;                            // cluster form: float offset of the merge buffer in dynamic shared memory
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -213,9 +215,9 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int G = a.n_q / a.n_kv;
   float* sq = reinterpret_cast<float*>(smem);                              // [G][HEAD]
-  __half* sk = reinterpret_cast<__half*>(smem + (size_t)G * HEAD * 4);     // [2][32][KSTR]
-  __half* sv = sk + 2 * kKeyTile * KSTR;                                   // [2][32][HEAD]
-  __half* snew = sv + 2 * kKeyTile * HEAD;                                 // [patch rows][2][HEAD]: keys and values of this pass
+  __half* sk = reinterpret_cast<__half*>(smem + (size_t)G * HEAD * 4);     // [kStages][32][KSTR]
+  __half* sv = sk + kStages * kKeyTile * KSTR;                             // [kStages][32][HEAD]
+  __half* snew = sv + kStages * kKeyTile * HEAD;                           // [patch rows][2][HEAD]: keys and values of this pass
   __shared__ int s_last, s_np;
   __shared__ int s_pm[kMaxPatch], s_ppos[kMaxPatch];
   const int seg = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
@@ -262,9 +264,14 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
     }
     cp_async_commit();
   };
-  // keys of earlier positions are already in the cache: the first tile streams in while the predecessor still runs
+  // keys of earlier positions are already in the cache: the first kStages tiles stream in while the predecessor
+  // still runs (one copy group per stage, empty past the last tile, so the group count stays uniform)
   probe_mark(a.probe, 0);
-  issue_tile(t0, 0);
+#pragma unroll
+  for (int st = 0; st < kStages; ++st) {
+    if (t0 + st < t1) issue_tile(t0 + st, st);
+    else cp_async_commit();
+  }
   pdl_wait();
   pdl_launch();
   probe_mark(a.probe, 1);
@@ -359,8 +366,8 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
     for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
   }
   for (int t = t0; t < t1; ++t) {
-    const int stage = (t - t0) & 1;
-    if (t + 1 < t1) { issue_tile(t + 1, stage ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    const int stage = (t - t0) % kStages;
+    cp_async_wait<kStages - 1>();                    // the oldest group in flight (tile t) has landed
     __syncthreads();
     bool patched = false;
     for (int idx = 0; idx < np; ++idx) {
@@ -423,6 +430,8 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
       }
     }
     __syncthreads();
+    if (t + kStages < t1) issue_tile(t + kStages, stage);     // refill the stage just read
+    else cp_async_commit();
   }
 
   probe_mark(a.probe, 4);
@@ -515,6 +524,274 @@ __global__ void __launch_bounds__(256, 2) attn_fused_kernel(const AttnArgs a) {
       for (int d = 0; d < DPL; ++d) o[d] = num[d] / den;
       head_out_q8<HEAD>(o, lane, ((long)kvh * G + hg) * HEAD, a, m);
     }
+  }
+}
+
+// The same attention launch with the key segments of one (row, KV head) held by the CTAs of a thread-block cluster:
+// the segments' partial results meet in distributed shared memory behind the cluster's hardware barrier instead of
+// going through global memory and a completion ticket, which takes the merge's L2 round trips off the critical path.
+// grid (CL, n_kv, M), cluster (CL, 1, 1); CTA c takes the c-th run of key tiles; head hg is merged by CTA hg % CL.
+template <int HEAD, int HPW>
+__global__ void __launch_bounds__(256, 2) attn_cluster_kernel(const AttnArgs a) {
+  constexpr int KSTR = HEAD + 8, DPL = HEAD / 32;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int G = a.n_q / a.n_kv;
+  float* sq = reinterpret_cast<float*>(smem);                              // [G][HEAD]
+  __half* sk = reinterpret_cast<__half*>(smem + (size_t)G * HEAD * 4);     // [kStages][32][KSTR]
+  __half* sv = sk + kStages * kKeyTile * KSTR;                             // [kStages][32][HEAD]
+  __half* snew = sv + kStages * kKeyTile * HEAD;                           // [patch rows][2][HEAD]: keys and values of this pass
+  __shared__ int s_np;
+  __shared__ int s_pm[kMaxPatch], s_ppos[kMaxPatch];
+  const int CL = (int)gridDim.x;
+  const int seg = (int)cluster_ctarank(), kvh = blockIdx.y, m = blockIdx.z;
+  float* s_recv = reinterpret_cast<float*>(smem) + a.recv_off;          // [heads merged here][CL][HEAD + 4]: {acc, max, sum}
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // positions, sequence and block table are step parameters: they do not depend on the predecessor kernel
+  const int seq = a.row_seq[m];
+  const int pos = a.row_pos[m];
+  const int n_keys = pos + 1;
+  const bool pad = seq < 0;
+  const bool bad = !pad && (n_keys <= 0 || n_keys > a.ctx_limit);
+  const int n_tiles = (pad || bad) ? 0 : (n_keys + kKeyTile - 1) / kKeyTile;
+  const int tps = max(1, (n_tiles + CL - 1) / CL);
+  const int t0 = min(n_tiles, seg * tps), t1 = min(n_tiles, t0 + tps);
+  if (pad || bad) {
+    // padding rows and rows with a bad key count still publish rows for o_proj: zeros, or a NaN scale
+    if (seg != 0) return;
+    pdl_wait();
+    pdl_launch();
+    if (bad && tid == 0 && kvh == 0) raise_fault(a.fault, a.layer, FS_KEY_COUNT);
+    const long width = (long)a.n_q * HEAD;
+    for (int i = tid; i < G * HEAD; i += 256) {
+      const long col = (long)kvh * G * HEAD + i;
+      a.outq[(long)m * width + col] = 0;
+      if (a.out) a.out[(long)m * width + col] = bad ? kNaN : 0.f;
+      if ((i & 31) == 0) a.outds[((long)m * width + col) / 32] = bad ? make_float2(kNaN, 0.f) : make_float2(0.f, 0.f);
+    }
+    return;
+  }
+  // a CTA past the row's last key tile still meets the cluster at its barrier, with an empty partial
+
+  const int* bt = a.block_table + (long)seq * a.max_pages;
+  auto issue_tile = [&](int t, int stage) {
+    const int key0 = t * kKeyTile;
+    int page = bt[key0 / kPage];
+    page = (page < 0 || page >= a.n_pages) ? 0 : page;      // the append below raises the fault; stay in bounds
+    const long base = (((long)page * a.n_kv + kvh) * kPage + (key0 % kPage)) * HEAD;
+    constexpr int CH = HEAD / 8;
+    for (int c = tid; c < kKeyTile * CH; c += 256) {
+      const int r = c / CH, cc = c % CH;
+      cp_async16(sk + ((size_t)stage * kKeyTile + r) * KSTR + cc * 8, a.k_cache + base + (long)r * HEAD + cc * 8);
+      cp_async16(sv + ((size_t)stage * kKeyTile + r) * HEAD + cc * 8, a.v_cache + base + (long)r * HEAD + cc * 8);
+    }
+    cp_async_commit();
+  };
+  // keys of earlier positions are already in the cache: the first kStages tiles stream in while the predecessor
+  // still runs (one copy group per stage, empty past the last tile, so the group count stays uniform)
+  probe_mark(a.probe, 0);
+#pragma unroll
+  for (int st = 0; st < kStages; ++st) {
+    if (t0 + st < t1) issue_tile(t0 + st, st);
+    else cp_async_commit();
+  }
+  pdl_wait();
+  pdl_launch();
+  probe_mark(a.probe, 1);
+
+  // ---- queries of this KV head's group: RMSNorm + RoPE into shared memory ---------------------------
+  const float* row = a.qkv + (long)m * a.qkv_stride;
+  auto norm_rope = [&](const float* src, const float* gain, bool rope, int at, float (&y)[DPL]) {
+    // lane owns elements lane + 32 j; NEOX pairs are (i, i + HALF)
+    float x[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) x[j] = src[lane + 32 * j];
+    if (gain) {
+      double ss = 0.0;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) ss += (double)(x[j] * x[j]);
+      ss = warp_sum_d(ss);
+      const float scale = (float)(1.0 / sqrt(ss / (double)HEAD + (double)a.eps));
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) x[j] = (scale * gain[lane + 32 * j]) * x[j];
+    }
+    if (rope) {
+#pragma unroll
+      for (int j = 0; j < DPL / 2; ++j) {
+        const int i = lane + 32 * j;
+        float sn, cs;
+        sincosf((float)at * a.inv_freq[i], &sn, &cs);
+        const float x0 = x[j], x1 = x[j + DPL / 2];
+        y[j] = fmaf(x0, cs, -(x1 * sn));
+        y[j + DPL / 2] = fmaf(x0, sn, x1 * cs);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) y[j] = x[j];
+    }
+  };
+#pragma unroll
+  for (int h = 0; h < HPW; ++h) {
+    const int hg = warp + 8 * h;
+    if (hg < G) {
+      float y[DPL];
+      norm_rope(row + ((long)kvh * G + hg) * HEAD, a.q_gain, true, pos, y);
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) sq[hg * HEAD + lane + 32 * j] = y[j] * a.q_scale;
+    }
+  }
+  probe_mark(a.probe, 2);
+  // ---- keys and values that this very pass appends --------------------------------------------------
+  // Rows of the pass that belong to the same sequence at or before this row's position are not in the cache
+  // yet (their owner blocks write them in this same launch), so a block computes the ones that fall inside its
+  // key range itself and patches them into the tiles; only the row's own block stores its row to the cache.
+  if (tid == 0) s_np = 0;
+  __syncthreads();
+  for (int mm = tid; mm < a.M; mm += 256) {
+    if (a.row_seq[mm] == seq) {
+      const int pp = a.row_pos[mm];
+      if (pp <= pos && pp >= t0 * kKeyTile && pp < t1 * kKeyTile) {
+        const int idx = atomicAdd(&s_np, 1);
+        if (idx < kMaxPatch) { s_pm[idx] = mm; s_ppos[idx] = pp; }
+      }
+    }
+  }
+  __syncthreads();
+  const int np = min(s_np, kMaxPatch);
+  for (int it = warp; it < 2 * np; it += 8) {
+    const int idx = it >> 1, mm = s_pm[idx], pp = s_ppos[idx];
+    const bool is_k = (it & 1) == 0;
+    float y[DPL];
+    const float* src = a.qkv + (long)mm * a.qkv_stride + ((long)a.n_q + (is_k ? 0 : a.n_kv) + kvh) * HEAD;
+    norm_rope(src, is_k ? a.k_gain : nullptr, is_k, pp, y);
+    __half* sn = snew + ((size_t)idx * 2 + (is_k ? 0 : 1)) * HEAD;
+    __half* dst = nullptr;
+    if (mm == m) {
+      const int pslot = pp / kPage;
+      const int page = (pslot < a.max_pages) ? bt[pslot] : -1;
+      if (page >= 0 && page < a.n_pages) dst = (is_k ? a.k_cache : a.v_cache) + (((long)page * a.n_kv + kvh) * kPage + (pp % kPage)) * HEAD;
+      else if (lane == 0 && is_k) raise_fault(a.fault, a.layer, FS_PAGE);
+    }
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+      const __half hv = __float2half_rn(y[j]);
+      sn[lane + 32 * j] = hv;
+      if (dst) dst[lane + 32 * j] = hv;
+    }
+  }
+
+  probe_mark(a.probe, 3);
+  float mx[HPW], l[HPW], acc[HPW][DPL];
+#pragma unroll
+  for (int h = 0; h < HPW; ++h) {
+    mx[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
+  }
+  for (int t = t0; t < t1; ++t) {
+    const int stage = (t - t0) % kStages;
+    cp_async_wait<kStages - 1>();                    // the oldest group in flight (tile t) has landed
+    __syncthreads();
+    bool patched = false;
+    for (int idx = 0; idx < np; ++idx) {
+      const int r = s_ppos[idx] - t * kKeyTile;
+      if (r >= 0 && r < kKeyTile) {                          // a row of this pass: the copy raced its store
+        for (int i = tid; i < HEAD; i += 256) {
+          sk[((size_t)stage * kKeyTile + r) * KSTR + i] = snew[(size_t)idx * 2 * HEAD + i];
+          sv[((size_t)stage * kKeyTile + r) * HEAD + i] = snew[((size_t)idx * 2 + 1) * HEAD + i];
+        }
+        patched = true;
+      }
+    }
+    if (patched) __syncthreads();
+    const int key = t * kKeyTile + lane;
+    const __half* krow = sk + ((size_t)stage * kKeyTile + lane) * KSTR;
+#pragma unroll
+    for (int h = 0; h < HPW; ++h) {
+      const int hg = warp + 8 * h;
+      if (hg < G) {
+        const float* qh = sq + hg * HEAD;
+        float s = 0.f;
+#pragma unroll
+        for (int d = 0; d < HEAD; d += 8) {
+          uint4 kv = *reinterpret_cast<const uint4*>(krow + d);
+          float4 q0 = *reinterpret_cast<const float4*>(qh + d);
+          float4 q1 = *reinterpret_cast<const float4*>(qh + d + 4);
+          float2 k0 = __half22float2(*reinterpret_cast<__half2*>(&kv.x));
+          float2 k1 = __half22float2(*reinterpret_cast<__half2*>(&kv.y));
+          float2 k2 = __half22float2(*reinterpret_cast<__half2*>(&kv.z));
+          float2 k3 = __half22float2(*reinterpret_cast<__half2*>(&kv.w));
+          s = fmaf(q0.x, k0.x, s); s = fmaf(q0.y, k0.y, s); s = fmaf(q0.z, k1.x, s); s = fmaf(q0.w, k1.y, s);
+          s = fmaf(q1.x, k2.x, s); s = fmaf(q1.y, k2.y, s); s = fmaf(q1.z, k3.x, s); s = fmaf(q1.w, k3.y, s);
+        }
+        if (key >= n_keys) s = -INFINITY;
+        const float tmax = warp_max(s);
+        const float nm = fmaxf(mx[h], tmax);
+        const float corr = (mx[h] == -INFINITY) ? 0.f : __expf(mx[h] - nm);
+        const float p = (s == -INFINITY) ? 0.f : __expf(s - nm);
+        l[h] = l[h] * corr + warp_sum(p);
+        mx[h] = nm;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
+        const __half* vbase = sv + (size_t)stage * kKeyTile * HEAD + lane * DPL;
+        const int kmax = min(kKeyTile, n_keys - t * kKeyTile);    // masked keys are never read
+#pragma unroll 4
+        for (int k = 0; k < kmax; ++k) {
+          const float pk = __shfl_sync(0xffffffffu, p, k);
+          const __half* vr = vbase + (size_t)k * HEAD;
+          if constexpr (DPL == 4) {
+            uint2 vv = *reinterpret_cast<const uint2*>(vr);
+            float2 v0 = __half22float2(*reinterpret_cast<__half2*>(&vv.x));
+            float2 v1 = __half22float2(*reinterpret_cast<__half2*>(&vv.y));
+            acc[h][0] = fmaf(pk, v0.x, acc[h][0]); acc[h][1] = fmaf(pk, v0.y, acc[h][1]);
+            acc[h][2] = fmaf(pk, v1.x, acc[h][2]); acc[h][3] = fmaf(pk, v1.y, acc[h][3]);
+          } else {
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(pk, __half2float(vr[d]), acc[h][d]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (t + kStages < t1) issue_tile(t + kStages, stage);     // refill the stage just read
+    else cp_async_commit();
+  }
+
+  probe_mark(a.probe, 4);
+  // ---- every segment's partial of head hg goes to CTA hg % CL; the cluster barrier; that CTA merges ----
+  constexpr int RS = HEAD + 4;                     // floats per partial: accumulators, max, sum, pad
+#pragma unroll
+  for (int h = 0; h < HPW; ++h) {
+    const int hg = warp + 8 * h;
+    if (hg < G) {
+      float* slot = s_recv + ((size_t)(hg / CL) * CL + seg) * RS;
+      const unsigned dst = (unsigned)(hg % CL);
+      if constexpr (DPL == 4) st_peer_v4(peer_addr(slot + lane * 4, dst), acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
+      else st_peer_v2(peer_addr(slot + lane * 2, dst), acc[h][0], acc[h][1]);
+      if (lane == 0) st_peer_v2(peer_addr(slot + HEAD, dst), mx[h], l[h]);
+    }
+  }
+  cluster_sync_all();
+  probe_mark(a.probe, 5);
+  for (int hs = warp; seg + hs * CL < G; hs += 8) {                // the heads this CTA merges, one warp each
+    const int hg = seg + hs * CL;
+    const float* base = s_recv + (size_t)hs * CL * RS;
+    float gm = -INFINITY;
+    for (int s = 0; s < CL; ++s) gm = fmaxf(gm, base[(size_t)s * RS + HEAD]);
+    float den = 0.f, num[DPL];
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) num[d] = 0.f;
+    for (int s = 0; s < CL; ++s) {                               // ascending segment order, fixed
+      const float ms = base[(size_t)s * RS + HEAD];
+      const float w = (ms == -INFINITY) ? 0.f : __expf(ms - gm);
+      den = fmaf(base[(size_t)s * RS + HEAD + 1], w, den);
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) num[d] = fmaf(base[(size_t)s * RS + lane * DPL + d], w, num[d]);
+    }
+    float o[DPL];
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) o[d] = num[d] / den;
+    head_out_q8<HEAD>(o, lane, ((long)kvh * G + hg) * HEAD, a, m);
   }
 }
 
@@ -861,6 +1138,29 @@ static cudaError_t gemv_staged_dispatch(const GemvArgs& a, int mb, int grid, siz
   }
 }
 
+template <int HEAD, int HPW>
+static int attn_cluster_launch(const AttnArgs& a, int CL, int n_kv, int M, size_t smem, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(attn_cluster_kernel<HEAD, HPW>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cudaFuncSetAttribute(attn_cluster_kernel<HEAD, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(CL, n_kv, M);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&cfg, attn_cluster_kernel<HEAD, HPW>, a);
+}
+
 }  // namespace bl
 
 using namespace bl;
@@ -946,16 +1246,16 @@ int bl_attn_fused(const float* qkv, long qkv_stride, const float* q_gain, const 
   const int G = n_q / n_kv;
   AttnArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, M, n_seg, ctx_limit, row_pos, row_seq,
              block_table, max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, part_ml, part_acc, tickets, out, outq,
-             (float2*)outds, fault, layer, g_stage_probe};
+             (float2*)outds, fault, layer, g_stage_probe, 0};
   dim3 grid(n_seg, n_kv, M);
   const int n_patch = M < kMaxPatch ? M : kMaxPatch;
-  const size_t smem = (size_t)G * head * 4 + 2 * kKeyTile * (head + 8) * 2 + 2 * kKeyTile * head * 2 + (size_t)n_patch * 2 * head * 2;
+  const size_t smem = (size_t)G * head * 4 + kStages * kKeyTile * (head + 8) * 2 + kStages * kKeyTile * head * 2 + (size_t)n_patch * 2 * head * 2;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(attn_fused_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    cudaFuncSetAttribute(attn_fused_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    cudaFuncSetAttribute(attn_fused_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    cudaFuncSetAttribute(attn_fused_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    cudaFuncSetAttribute(attn_fused_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    cudaFuncSetAttribute(attn_fused_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    cudaFuncSetAttribute(attn_fused_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    cudaFuncSetAttribute(attn_fused_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
     attr_set = true;
   }
   cudaError_t e;
@@ -966,6 +1266,29 @@ int bl_attn_fused(const float* qkv, long qkv_stride, const float* q_gain, const 
 
 // route_logits != null: every block routes its row from the logits (block (0, 0, m) writes ids / wts / heat);
 // otherwise ids are read as given.
+// bl_attn_fused with the key segments of a (row, KV head) spread over a thread-block cluster of `cluster` CTAs
+// (8 or 16) that merge through distributed shared memory: no scratch, no tickets.
+int bl_attn_cluster(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain, const float* inv_freq,
+                    float eps, float q_scale, int head, int n_q, int n_kv, int M, const int* row_pos, const int* row_seq,
+                    const int* block_table, int max_pages, int n_pages, void* k_cache, void* v_cache, int cluster,
+                    int ctx_limit, float* out, int8_t* outq, float* outds, unsigned* fault, int layer, cudaStream_t st) {
+  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
+  BL_REQUIRE(n_kv >= 1 && n_q % n_kv == 0 && n_q / n_kv <= 16, BL_ERR_SHAPE);
+  BL_REQUIRE((cluster == 8 || cluster == 16) && M >= 1 && max_pages >= 1 && (long)ctx_limit <= (long)max_pages * kPage, BL_ERR_SHAPE);
+  const int G = n_q / n_kv;
+  const int n_patch = M < kMaxPatch ? M : kMaxPatch;
+  size_t base = (size_t)G * head * 4 + kStages * kKeyTile * (head + 8) * 2 + kStages * kKeyTile * head * 2 + (size_t)n_patch * 2 * head * 2;
+  base = (base + 15) / 16 * 16;
+  const int heads_here = (G + cluster - 1) / cluster;
+  const size_t smem = base + (size_t)heads_here * cluster * (head + 4) * 4;
+  BL_REQUIRE(smem <= 110 * 1024, BL_ERR_LIMIT);
+  AttnArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, M, cluster, ctx_limit, row_pos, row_seq,
+             block_table, max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, nullptr, nullptr, nullptr, out, outq,
+             (float2*)outds, fault, layer, g_stage_probe, (int)(base / 4)};
+  if (head == 128) return G <= 8 ? attn_cluster_launch<128, 1>(a, cluster, n_kv, M, smem, st) : attn_cluster_launch<128, 2>(a, cluster, n_kv, M, smem, st);
+  return G <= 8 ? attn_cluster_launch<64, 1>(a, cluster, n_kv, M, smem, st) : attn_cluster_launch<64, 2>(a, cluster, n_kv, M, smem, st);
+}
+
 int bl_gate_up_staged(const int8_t* xq, const float* xds, const float* route_logits, const float* bias, int mode, int renorm,
                       float scale, int n_group, int topk_group, int* ids, float* wts, unsigned* heat, const int* slot_map,
                       const void* gate, const void* up, int wtype, const void* down, long down_expert_bytes, int K, int I, int E,

@@ -72,6 +72,36 @@ __device__ __forceinline__ int act_chunk_pos(int c, int nunits, int layout) {
   return c;
 }
 
+// Activation registers of weight unit u out of a shared-memory row in layout 1 / 2 (act_chunk_pos): every load of
+// a warp touches 32 consecutive 16-byte chunks, so none meets a bank conflict.  `sds` stays linear.
+template <class T> struct StagedAct {
+  static constexpr int kLayout = 1;
+  static __device__ __forceinline__ void load(const int8_t* sq, const float2* sds, int u, int nunits, ActRegs& a) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = *reinterpret_cast<const uint4*>(sq + ((long)(i * nunits + u) << 4));
+      a.q[4 * i] = v.x; a.q[4 * i + 1] = v.y; a.q[4 * i + 2] = v.z; a.q[4 * i + 3] = v.w;
+    }
+    const float4 ds = *reinterpret_cast<const float4*>(sds + 2 * u);
+    a.d[0] = ds.x; a.s[0] = ds.y; a.d[1] = ds.z; a.s[1] = ds.w;
+  }
+};
+template <> struct StagedAct<Q6K> {
+  static constexpr int kLayout = 2;
+  static __device__ __forceinline__ void load(const int8_t* sq, const float2* sds, int u, int nunits, ActRegs& a) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint4 v = *reinterpret_cast<const uint4*>(sq + ((long)(g * nunits + u) << 4));
+      a.q[4 * g] = v.x; a.q[4 * g + 1] = v.y; a.q[4 * g + 2] = v.z; a.q[4 * g + 3] = v.w;
+    }
+    const int sb = u >> 2, n = (u >> 1) & 1;
+    const float4 d01 = *reinterpret_cast<const float4*>(sds + 8 * sb + 4 * n);
+    const float4 d23 = *reinterpret_cast<const float4*>(sds + 8 * sb + 4 * n + 2);
+    a.d[0] = d01.x; a.d[1] = d01.z; a.d[2] = d23.x; a.d[3] = d23.z;
+  }
+};
+__host__ __device__ inline int staged_layout(int wtype) { return wtype == WT_Q6_K ? 2 : 1; }
+
 // ---- activation prologue ------------------------------------------------------------
 // sq/sds receive q8(x * gain) WITHOUT the RMS scale; s_scale[m] receives the scale.
 template <int MB, bool FLOATW>

@@ -30,25 +30,6 @@ namespace bl {
 
 constexpr int kCl = 16;                // CTAs per cluster
 
-__device__ __forceinline__ unsigned cluster_ctarank() {
-  unsigned r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// address of `local` (a shared-memory address of this CTA) in the CTA of rank `rank` of the cluster
-__device__ __forceinline__ uint32_t peer_addr(const void* local, unsigned rank) {
-  uint32_t out;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(local)), "r"(rank));
-  return out;
-}
-__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-
 struct MoeClusterArgs {
   const float* x;                        // [H] residual row (input)
   const float* gain; float eps;

@@ -159,6 +159,17 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a0) {
     for (int m = 0; m < a.M; ++m) {
       int id; float w;
       const bool ok = route_block(p, m, rs, id, w);
+      if (a.pf_gate) {
+        // prediction: publish the predicted slots for the prefetch launch that follows (one SM alone cannot issue
+        // tens of megabytes of prefetches fast enough; the follower spreads them over the whole card)
+        if (warp == 0 && lane < p.top_k) {
+          int e = ok ? rs.ids[lane] : -1;
+          if (e >= 0 && a.pf_slot_map) e = a.pf_slot_map[e];
+          a.ids[(long)m * p.top_k + lane] = e;
+        }
+        __syncthreads();
+        continue;
+      }
       if (warp == 0) {
         if (!ok && lane == 0) raise_fault(a.fault, a.layer, FS_ROUTER);
         if (lane < p.top_k) {
@@ -445,7 +456,9 @@ int bl_router(const float* x, long x_stride, const float* gain, float eps, const
               int K, int E, int M, float* logits, int8_t* xq_out, float* xds_out, float* xn_out,
               const void* red_desc, unsigned* fault, int layer,
               unsigned* ticket, const float* bias, int top_k, int mode, int renorm, float scale, int n_group, int topk_group,
-              int* ids, float* wts, unsigned* heat, cudaStream_t st) {
+              int* ids, float* wts, unsigned* heat,
+              const void* pf_gate, const void* pf_up, const void* pf_down, long pf_gate_bytes, long pf_down_bytes,
+              const int* pf_slot_map, cudaStream_t st) {
   BL_REQUIRE(E >= 1 && E <= kMaxExperts, BL_ERR_LIMIT);
   BL_REQUIRE(K % 256 == 0 && M >= 1 && M <= 8 * 65535, BL_ERR_SHAPE);
   BL_REQUIRE(wtype == WT_F32 || wtype == WT_F16 || wtype == WT_BF16, BL_ERR_TYPE);
@@ -456,8 +469,14 @@ int bl_router(const float* x, long x_stride, const float* gain, float eps, const
   if (red_desc) { a.red = *(const ReduceIn*)red_desc; BL_REQUIRE(M <= kMaxRows && a.red.n_ranks <= kMaxRanks && a.red.H == K, BL_ERR_SHAPE); }
   if (ticket) {
     BL_REQUIRE(E % 4 == 0 && top_k >= 1 && top_k <= kMaxTopK && top_k <= E && n_group >= 1 && n_group <= 16 && E % n_group == 0 &&
-               topk_group >= 1 && topk_group <= n_group && ids && wts, BL_ERR_SHAPE);
+               topk_group >= 1 && topk_group <= n_group && ((ids && wts) || pf_gate), BL_ERR_SHAPE);
     a.ticket = ticket; a.ids = ids; a.wts = wts; a.heat = heat;
+    if (pf_gate) {
+      BL_REQUIRE(pf_up && pf_down && pf_gate_bytes > 0 && pf_down_bytes > 0 && (((uintptr_t)pf_gate | (uintptr_t)pf_up | (uintptr_t)pf_down) & 15) == 0 &&
+                 pf_gate_bytes % 16 == 0 && pf_down_bytes % 16 == 0, BL_ERR_ALIGN);
+      a.pf_gate = (const uint8_t*)pf_gate; a.pf_up = (const uint8_t*)pf_up; a.pf_down = (const uint8_t*)pf_down;
+      a.pf_gate_bytes = pf_gate_bytes; a.pf_down_bytes = pf_down_bytes; a.pf_slot_map = pf_slot_map;
+    }
     a.route = RouteParams{nullptr, bias, E, top_k, mode, renorm, scale, n_group, topk_group};
   }
   int mb = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
@@ -467,6 +486,28 @@ int bl_router(const float* x, long x_stride, const float* gain, float eps, const
     case 2: return (int)launch(router_kernel<2>, grid, dim3(256), 0, st, a);
     case 4: return (int)launch(router_kernel<4>, grid, dim3(256), 0, st, a);
     default: return (int)launch(router_kernel<8>, grid, dim3(256), 0, st, a);
+  }
+}
+
+// Asks L2 to prefetch the gate / up (and optionally down) matrices of the experts named in ids[n] (negative = skip),
+// 32 KB pieces dealt round-robin over the blocks; lane 0 of every warp issues.
+__global__ void __launch_bounds__(256) prefetch_experts_kernel(const int* ids, int n, const uint8_t* gate, const uint8_t* up,
+                                                               const uint8_t* down, long gate_bytes, long down_bytes) {
+  pdl_wait();
+  pdl_launch();
+  const long gn = gate_bytes / 32768, dn = down ? down_bytes / 32768 : 0, per = 2 * gn + dn;
+  const long total = per * n;
+  const int wid = blockIdx.x * 8 + (threadIdx.x >> 5), nw = gridDim.x * 8;
+  if ((threadIdx.x & 31) != 0) return;
+  for (long c = wid; c < total; c += nw) {
+    const int q = (int)(c / per);
+    const long r = c - (long)q * per;
+    const int e = ids[q];
+    if (e < 0) continue;
+    const uint8_t* src = r < gn ? gate + e * gate_bytes + r * 32768
+                       : r < 2 * gn ? up + e * gate_bytes + (r - gn) * 32768
+                       : down + e * down_bytes + (r - 2 * gn) * 32768;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(32768u) : "memory");
   }
 }
 
@@ -486,6 +527,14 @@ __global__ void __launch_bounds__(256) route_rows_kernel(RouteParams p, int M, i
     wts[(long)m * p.top_k + lane] = w;
     if (ok && heat) atomicAdd(heat + id, 1u);
   }
+}
+
+int bl_prefetch_experts(const int* ids, int n, const void* gate, const void* up, const void* down, long gate_bytes,
+                        long down_bytes, int blocks, cudaStream_t st) {
+  BL_REQUIRE(n >= 1 && gate && up && gate_bytes > 0 && blocks >= 1, BL_ERR_SHAPE);
+  BL_REQUIRE((((uintptr_t)gate | (uintptr_t)up | (uintptr_t)down) & 15) == 0 && gate_bytes % 16 == 0 && down_bytes % 16 == 0, BL_ERR_ALIGN);
+  return (int)launch(prefetch_experts_kernel, dim3(blocks), dim3(256), 0, st, ids, n, (const uint8_t*)gate, (const uint8_t*)up,
+                     (const uint8_t*)down, gate_bytes, down_bytes);
 }
 
 int bl_route_rows(const float* logits, const float* bias, int E, int M, int top_k, int mode, int renorm, float scale,

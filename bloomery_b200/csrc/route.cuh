@@ -32,6 +32,12 @@ struct RouterArgs {
   RouteParams route;                   // route.logits is ignored here (the kernel's own logits are routed)
   int* ids; float* wts;                // [M, top_k]
   unsigned* heat;                      // optional [E] routed-count histogram
+  // Prediction form (pf_gate != null, with a ticket): the launch runs on the layer's INPUT rows, ahead of the
+  // attention launches, and its last block asks L2 to prefetch the gate / up / down matrices of the route.top_k
+  // best-scoring experts of each row.  Nothing is published: the real routing still happens on the real rows.
+  const uint8_t* pf_gate; const uint8_t* pf_up; const uint8_t* pf_down;
+  long pf_gate_bytes, pf_down_bytes;   // bytes of one expert's matrix in each stack
+  const int* pf_slot_map;              // optional [E]: expert id -> resident slot (negative = not on this device)
 };
 
 // Block-wide routing of one row by rank counting: every thread owns up to two experts,

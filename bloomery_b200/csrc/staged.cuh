@@ -56,35 +56,6 @@ __device__ __forceinline__ void probe_mark(long long* probe, int i) {
   if (probe && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) probe[i] = clock64();
 }
 
-// Activation registers of weight unit u out of a shared-memory row in layout 1 / 2 (act_chunk_pos): every load of
-// a warp touches 32 consecutive 16-byte chunks, so none meets a bank conflict.  `sds` stays linear.
-template <class T> struct StagedAct {
-  static constexpr int kLayout = 1;
-  static __device__ __forceinline__ void load(const int8_t* sq, const float2* sds, int u, int nunits, ActRegs& a) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 v = *reinterpret_cast<const uint4*>(sq + ((long)(i * nunits + u) << 4));
-      a.q[4 * i] = v.x; a.q[4 * i + 1] = v.y; a.q[4 * i + 2] = v.z; a.q[4 * i + 3] = v.w;
-    }
-    const float4 ds = *reinterpret_cast<const float4*>(sds + 2 * u);
-    a.d[0] = ds.x; a.s[0] = ds.y; a.d[1] = ds.z; a.s[1] = ds.w;
-  }
-};
-template <> struct StagedAct<Q6K> {
-  static constexpr int kLayout = 2;
-  static __device__ __forceinline__ void load(const int8_t* sq, const float2* sds, int u, int nunits, ActRegs& a) {
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      const uint4 v = *reinterpret_cast<const uint4*>(sq + ((long)(g * nunits + u) << 4));
-      a.q[4 * g] = v.x; a.q[4 * g + 1] = v.y; a.q[4 * g + 2] = v.z; a.q[4 * g + 3] = v.w;
-    }
-    const int sb = u >> 2, n = (u >> 1) & 1;
-    const float4 d01 = *reinterpret_cast<const float4*>(sds + 8 * sb + 4 * n);
-    const float4 d23 = *reinterpret_cast<const float4*>(sds + 8 * sb + 4 * n + 2);
-    a.d[0] = d01.x; a.d[1] = d01.z; a.d[2] = d23.x; a.d[3] = d23.z;
-  }
-};
-__host__ __device__ inline int staged_layout(int wtype) { return wtype == WT_Q6_K ? 2 : 1; }
 
 template <class T>
 __device__ __forceinline__ void gate_up_rows_staged(const uint8_t* g0, const uint8_t* u0, long rb, int K, int lane,
@@ -106,5 +77,32 @@ __device__ __forceinline__ void gate_up_rows_staged(const uint8_t* g0, const uin
   for (int r = 0; r < 2; ++r) { gacc[r] = warp_sum(gacc[r]); uacc[r] = warp_sum(uacc[r]); }
 }
 
+
+// ---- thread-block clusters: rank, hardware barrier, distributed shared memory ------------------------
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of `local` (a shared-memory address of this CTA) in the CTA of rank `rank` of the cluster
+__device__ __forceinline__ uint32_t peer_addr(const void* local, unsigned rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(local)), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ void st_peer_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void st_peer_v2(uint32_t addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
 
 }  // namespace bl

@@ -200,19 +200,47 @@ def attn_fused(qkv, q_gain, k_gain, inv_freq, eps: float, q_scale: float, head: 
     check(rc, "bl_attn_fused")
 
 
+def attn_cluster_size(n_kv: int, M: int) -> int:
+    """CTAs per cluster of the cluster form of the attention launch for M rows of n_kv KV heads (0 = use the ticket
+    form): 16 while a B200 can hold all n_kv * M clusters at once, else 8."""
+    if "attn" not in _PARTS or not _STAGED:
+        return 0
+    if n_kv * M <= 12:
+        return 16
+    return 8 if n_kv * M <= 32 else 0
+
+
+def attn_cluster(qkv, q_gain, k_gain, inv_freq, eps: float, q_scale: float, head: int, n_q: int, n_kv: int, M: int,
+                 row_pos, row_seq, block_table, n_pages: int, k_cache, v_cache, cluster: int, ctx_limit: int, out, outq,
+                 outds, fault, layer: int) -> None:
+    """The fused attention launch with the key segments of each (row, KV head) spread over a thread-block cluster
+    of ``cluster`` CTAs that merge through distributed shared memory (no scratch, no tickets)."""
+    rc = cuda().bl_attn_cluster(p(qkv), L(qkv.stride(0)), p(q_gain), p(k_gain), p(inv_freq), F(eps), F(q_scale), I(head),
+                                I(n_q), I(n_kv), I(M), p(row_pos), p(row_seq), p(block_table), I(block_table.shape[1]),
+                                I(n_pages), p(k_cache), p(v_cache), I(cluster), I(ctx_limit), p(out), p(outq), p(outds),
+                                p(fault), I(layer), stream())
+    check(rc, "bl_attn_cluster")
+
+
 def router(x, gain, eps: float, w: QWeight, M: int, logits, xq_out, xds_out, xn_out, fault, layer: int,
            red: Optional[ReduceIn] = None, *, rule: Optional["RouteRule"] = None, ids=None, wts=None, heat=None,
-           ticket=None) -> None:
+           ticket=None, predict=None, predict_slot_map=None) -> None:
     """Router logits of M rows (RMSNorm folded in) + the q8 form of the normed rows.  With ``ticket`` (int32, one
-    zeroed word per 8 rows) and ``rule`` the launch also routes: its last block writes ``ids`` / ``wts`` / ``heat``."""
+    zeroed word per 8 rows) and ``rule`` the launch also routes: its last block writes ``ids`` / ``wts`` / ``heat``.
+    ``predict`` = (gate, up, down) stacks: the prediction form -- run on a layer's INPUT rows, the last block asks L2
+    to prefetch the matrices of the ``rule.top_k`` best-scoring experts and publishes nothing."""
     r = rule
+    pg, pu, pd = predict if predict is not None else (None, None, None)
     rc = cuda().bl_router(p(x), L(x.stride(0)), p(gain), F(eps), p(w.data), I(w.wt), I(w.k), I(w.rows), I(M),
                           p(logits), p(xq_out), p(xds_out), p(xn_out), _ref(red), p(fault), I(layer),
                           p(ticket if r is not None else None), p(r.bias if r is not None else None),
                           I(r.top_k if r is not None else 0), I(r.mode if r is not None else 0),
                           I(1 if (r is not None and r.renorm) else 0), F(r.scale if r is not None else 1.0),
                           I(r.n_group if r is not None else 1), I(r.topk_group if r is not None else 1),
-                          p(ids), p(wts), p(heat), stream())
+                          p(ids), p(wts), p(heat),
+                          p(pg.data if pg is not None else None), p(pu.data if pu is not None else None),
+                          p(pd.data if pd is not None else None), L(pg.data.stride(0) if pg is not None else 0),
+                          L(pd.data.stride(0) if pd is not None else 0), p(predict_slot_map), stream())
     check(rc, "bl_router")
 
 
@@ -263,6 +291,14 @@ def down_combine(actq, actds, ids, wts, slot_map, down: QWeight, n_expert: int, 
                                 L(extra.stride(0) if extra is not None else 0), p(out), L(out.stride(0)), _ref(push),
                                 p(fault), I(layer), stream())
     check(rc, "bl_down_combine")
+
+
+def prefetch_experts(ids, n: int, gate: QWeight, up: QWeight, down: Optional[QWeight], blocks: int) -> None:
+    """Ask L2 to prefetch the gate / up (/ down) matrices of the ``n`` expert slots named in ``ids`` (negative = skip)."""
+    rc = cuda().bl_prefetch_experts(p(ids), I(n), p(gate.data), p(up.data), p(down.data if down is not None else None),
+                                    L(gate.data.stride(0)), L(down.data.stride(0) if down is not None else 0), I(blocks),
+                                    stream())
+    check(rc, "bl_prefetch_experts")
 
 
 def gate_up_staged(xq, xds, ids, slot_map, gate: QWeight, up: QWeight, n_expert: int, n_used: int, M: int, actq, actds,

@@ -128,7 +128,10 @@ def main(argv=None) -> int:
     X = extra
 
     def attn(l):
-        if staged:
+        if which == "attn_cluster" or (staged and which == "chain2"):
+            K.attn_cluster(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, M, fpos, fseq, table, n_pages, kc, vc,
+                           K.attn_cluster_size(n_kv, M) or 8, ctx, None, xq, xds, fault, 0)
+        elif staged:
             K.attn_fused(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, M, fpos, fseq, table, n_pages, kc, vc,
                          n_seg, ctx, pml, pacc, tickets, None, xq, xds, fault, 0)
         else:
@@ -158,13 +161,13 @@ def main(argv=None) -> int:
 
     def chain():
         for l in layers:
-            if which in ("chain", "qkv"): K.gemv([l["q"], l["k"], l["v"]], M, qkv, x=x, gain=gain, fault=fault)
-            if which in ("chain", "attn"): attn(l)
-            if which in ("chain", "o"): K.gemv([l["o"]], M, x, xq=xq, xds=xds, resid=x, fault=fault)
-            if which in ("chain", "router", "router_ticket"): router(l)
-            if which in ("chain", "gateup"): gateup(l)
+            if which in ("chain", "chain2", "qkv"): K.gemv([l["q"], l["k"], l["v"]], M, qkv, x=x, gain=gain, fault=fault)
+            if which in ("chain", "chain2", "attn", "attn_cluster"): attn(l)
+            if which in ("chain", "chain2", "o"): K.gemv([l["o"]], M, x, xq=xq, xds=xds, resid=x, fault=fault)
+            if which in ("chain", "chain2", "router", "router_ticket"): router(l)
+            if which in ("chain", "chain2", "gateup"): gateup(l)
             if which == "gateup_ids": gateup(l, routed=False)
-            if which in ("chain", "down"): down(l)
+            if which in ("chain", "chain2", "down"): down(l)
             if which in ("cluster", "chain_cluster"):
                 if which == "chain_cluster":
                     K.gemv([l["q"], l["k"], l["v"]], M, qkv, x=x, gain=gain, fault=fault)

@@ -82,7 +82,7 @@ def test_staged_gemv_o_proj_shape_and_fallback_for_big_matrices():
     assert torch.isfinite(o).all()
 
 
-def _attn_case(head, n_q, n_kv, rows, n_seg, ctx, seed=5, qk_norm=True):
+def _attn_case(head, n_q, n_kv, rows, n_seg, ctx, seed=5, qk_norm=True, cluster=0):
     """rows = [(seq, position)]; history of every sequence is random f16 rows below its first position in the pass."""
     from bloomery_b200.models.cpu_ref import rms_norm, rope_neox
     from bloomery_b200.ops import decode as K
@@ -122,6 +122,11 @@ def _attn_case(head, n_q, n_kv, rows, n_seg, ctx, seed=5, qk_norm=True):
     outq = torch.zeros(M, n_q * head, dtype=torch.int8, device=DEV)
     outds = torch.zeros(M, n_q * head // 32, 2, device=DEV)
     for _ in range(2):                              # twice: the tickets must come back to zero by themselves
+        if cluster:
+            K.attn_cluster(d(qkv), d(qg) if qk_norm else None, d(kg) if qk_norm else None, d(inv), 1e-6, 1 / math.sqrt(head),
+                           head, n_q, n_kv, M, d(pos), d(seq), d(table), n_pages, kc_d, vc_d, cluster, ctx, out, outq, outds,
+                           fault, 0)
+            continue
         K.attn_fused(d(qkv), d(qg) if qk_norm else None, d(kg) if qk_norm else None, d(inv), 1e-6, 1 / math.sqrt(head), head,
                      n_q, n_kv, M, d(pos), d(seq), d(table), n_pages, kc_d, vc_d, n_seg, ctx, part_ml, part_acc, tickets,
                      out, outq, outds, fault, 0)
@@ -170,6 +175,16 @@ def test_attn_fused_rows_of_one_sequence_see_each_other():
     _attn_case(128, 32, 4, [(0, 60 + i) for i in range(8)], n_seg=5, ctx=256)
     _attn_case(128, 32, 4, [(0, i) for i in range(8)], n_seg=5, ctx=256, seed=6)        # from an empty cache
     _attn_case(64, 8, 2, [(1, 100 + i) for i in range(3)] + [(0, 31 + i) for i in range(3)], n_seg=3, ctx=192, seed=7)
+
+
+@pytest.mark.parametrize("cluster", [8, 16])
+@pytest.mark.parametrize("head,n_q,n_kv", [(128, 32, 4), (64, 8, 2), (128, 64, 4)])
+def test_attn_cluster_form(head, n_q, n_kv, cluster):
+    """Key segments over a thread-block cluster, merged through distributed shared memory."""
+    if cluster == 16 and n_kv * 4 > 12:
+        pytest.skip("more 16-CTA clusters than one B200 holds at once")
+    _attn_case(head, n_q, n_kv, [(0, 0), (1, 332), (-1, 0), (2, 699)], n_seg=9, ctx=704, cluster=cluster)
+    _attn_case(head, n_q, n_kv, [(0, 60 + i) for i in range(3)], n_seg=5, ctx=256, cluster=cluster, seed=8)
 
 
 def test_attn_fused_without_qk_norm_and_with_one_segment():
