@@ -146,7 +146,9 @@ def gemv(segs: Sequence[QWeight], M: int, out: torch.Tensor, *, x: Optional[torc
     rows = (ctypes.c_int * n)(*[s.rows for s in segs])
     wts = (ctypes.c_int * n)(*[s.wt for s in segs])
     norm = x is not None
-    if staged_part("gemv") and 1 not in fams and _gemv_fits_stage(segs, M):
+    # a launch that pushes its rows to the peers takes the staged kernel whenever it fits: its epilogue stores each
+    # peer's rows as runs of consecutive columns (whole NVLink packets) instead of one 8-byte store per warp
+    if (staged_part("gemv") or (push is not None and _STAGED)) and 1 not in fams and _gemv_fits_stage(segs, M):
         rc = cuda().bl_gemv_staged(I(n), wp, rows, wts, I(K), I(M), I(1 if norm else 0),
                                    p(x), L(x.stride(0) if norm else 0), p(gain), F(eps), p(xq), p(xds),
                                    p(out), L(out.stride(0)), p(resid), L(resid.stride(0) if resid is not None else 0),
@@ -320,9 +322,9 @@ def gate_up_staged(xq, xds, ids, slot_map, gate: QWeight, up: QWeight, n_expert:
     check(rc, "bl_gate_up_staged")
 
 
-def moe_fits_stage(gate: QWeight, down: QWeight, n_used: int) -> bool:
+def moe_fits_stage(gate: QWeight, down: QWeight, n_used: int, force: bool = False) -> bool:
     """Whether the staged expert kernels serve these stacks (a block's rows fit the shared-memory stage)."""
-    if not staged_part("moe") or gate.qtype in ("F32", "F16", "BF16") or down.qtype in ("F32", "F16", "BF16"):
+    if not (staged_part("moe") or (force and _STAGED)) or gate.qtype in ("F32", "F16", "BF16") or down.qtype in ("F32", "F16", "BF16"):
         return False
     rb_g = gate.data.shape[-1]
     rb_d = down.data.shape[-1]

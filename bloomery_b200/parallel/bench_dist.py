@@ -30,6 +30,8 @@ def run_distributed(args, rank: int, local: int, world: int) -> int:
     t_load = time.time() - t0
     fused = not getattr(args, "nccl_baseline", False)
     ctx = max(args.prompt, getattr(args, 'ttft', 0) or 0) + warm + 2 * steps + 64
+    # the fused arm replays one CUDA graph per step.  The NCCL arm runs eager: captured into the step graph its
+    # all-reduces did not come back on two B200s (the run sat until its time limit), so that form is not used.
     eng = ShardedEngine(w, spec, rank, world, fused=fused, n_slots=1, slot_ctx=(ctx + 63) // 64 * 64,
                         use_graphs=fused)
     g = torch.Generator().manual_seed(1234)

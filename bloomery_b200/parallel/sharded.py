@@ -173,7 +173,8 @@ class ShardedEngine(DecodeEngine):
                 add(K.gate_up_sel, self.xq, self.xds, ids, self.slot_map, gate, up, s.n_expert, s.n_used, M, self.actq,
                     self.actds, None, self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=wts,
                     heat=self.heat[il])
-            down_fn = K.down_staged if staged else K.down_combine
+            # the pushing launch takes the staged form: it stores each peer's rows as runs of consecutive columns
+            down_fn = K.down_staged if (staged or (fused and K.moe_fits_stage(gate, down, s.n_used, force=True))) else K.down_combine
             if fused:
                 add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, None,
                     self.partial, self.fault, il, push=ar.push(SITE_MOE, 2 * il + 1))
