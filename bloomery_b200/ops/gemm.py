@@ -161,6 +161,19 @@ def kv_gather_bf16(k_cache, v_cache, block_table_row, n_pages: int, n_kv: int, h
                                    I(T_pad), p(Kb), p(Vt), stream()), "bl_kv_gather_bf16")
 
 
+def flash_prefill(q_bf: torch.Tensor, Kb: torch.Tensor, Vt: torch.Tensor, out: torch.Tensor, pos0: int,
+                  status: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of a prompt chunk on tcgen05 tiles (``csrc/flash_tcgen05.cu``): queries bf16 [n_q, T, 128]
+    (normalised, rotated, pre-scaled) at positions pos0.., keys bf16 [n_kv, T_pad, 128], values transposed bf16
+    [n_kv, 128, T_pad] (columns past the last key zero), output bf16 [T, n_q * 128]."""
+    n_q, T, hd = q_bf.shape
+    n_kv, T_pad, _ = Kb.shape
+    assert hd == 128 and Vt.shape == (n_kv, 128, T_pad) and q_bf.is_contiguous() and Kb.is_contiguous() and Vt.is_contiguous()
+    rc = cuda().bl_flash_prefill(p(q_bf), p(Kb), p(Vt), p(out), L(out.stride(0)), I(T), I(n_q), I(n_kv), I(pos0), I(T_pad),
+                                 p(status), stream())
+    check(rc, "bl_flash_prefill")
+
+
 def softmax_causal(S, rows: int, Tq: int, pos0: int, T_pad: int, P) -> None:
     check(cuda().bl_softmax_causal(p(S), L(S.stride(0)), L(rows), I(Tq), I(pos0), I(T_pad), p(P), L(P.stride(0)),
                                    stream()), "bl_softmax_causal")

@@ -51,6 +51,7 @@ class GemmPrefill:
         self.launches = 0
         # where a layer's expert stacks come from: the resident weights, or a streamer that brings them from the host
         self.expert_source = None
+        self.flash = True                       # head size 128: fused attention on tensor memory (csrc/flash_tcgen05.cu)
         from .timing import PromptTiming
         self.timing = PromptTiming()            # arm() it to get per-unit milliseconds of the next micro-batch
 
@@ -149,7 +150,11 @@ class GemmPrefill:
             G.kv_gather_bf16(e.kv.k[il], e.kv.v[il], e.kv.table[slot], e.kv.n_pages, s.n_kv, s.head_dim, n_keys, T_pad,
                              Kb, Vt)
             self.timing.mark(il, "qkv")
-            for c0 in range(0, T, Tq_max):
+            if s.head_dim == 128 and self.flash:
+                # scores, softmax and values in one tcgen05 launch: the score matrix stays in tensor memory
+                G.flash_prefill(q_bf, Kb, Vt, attn, p0, st)
+                self.timing.mark(il, "flash")
+            for c0 in range(0, T if not (s.head_dim == 128 and self.flash) else 0, Tq_max):
                 Tq = min(Tq_max, T - c0)
                 rows = s.n_q * Tq
                 S = self._get("S", (rows, T_pad), f32)
