@@ -74,6 +74,7 @@ class ShardedGemmPrefill:
         self._buf = {}
         self._router_w = {}
         self.emulated = local_only
+        self.flash = True                       # head size 128: fused attention on tensor memory (csrc/flash_tcgen05.cu)
 
     def _get(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
@@ -200,7 +201,10 @@ class ShardedGemmPrefill:
                                               e.inv_freq, s.rms_eps, e.attn_scale, hd, s.n_q, s.n_kv, Tp, row_pos,
                                               row_seq, e.kv.table, e.kv.n_pages, e.kv.k[il], e.kv.v[il], q_bf, e.fault, il)
                 G.kv_gather_bf16(e.kv.k[il], e.kv.v[il], e.kv.table[slot], e.kv.n_pages, s.n_kv, hd, n_keys, T_pad, Kb, Vt)
-                for c0 in range(0, Tp, Tq_max):
+                if hd == 128 and self.flash:
+                    # this rank's heads over the whole chunk: scores, softmax and values in one tcgen05 launch
+                    G.flash_prefill(q_bf, Kb, Vt, attn, p0, st)
+                for c0 in range(0, Tp if not (hd == 128 and self.flash) else 0, Tq_max):
                     Tq = min(Tq_max, Tp - c0)
                     rows = s.n_q * Tq
                     S = self._get("S", (rows, T_pad), f32)

@@ -51,6 +51,8 @@ class GemmPrefill:
         self.launches = 0
         # where a layer's expert stacks come from: the resident weights, or a streamer that brings them from the host
         self.expert_source = None
+        self.expand_ahead = True                # bf16 expansion of layer l + 1's weights on a side stream during layer l
+        self._side = None
         self.flash = True                       # head size 128: fused attention on tensor memory (csrc/flash_tcgen05.cu)
         from .timing import PromptTiming
         self.timing = PromptTiming()            # arm() it to get per-unit milliseconds of the next micro-batch
@@ -97,8 +99,12 @@ class GemmPrefill:
         K.embed_rows(tok, T, w.q["token_embd.weight"], V, x, e.fault)
         qkv_w = s.q_rows + 2 * s.kv_rows
         qkv = self._get("qkv", (T, qkv_w), f32)
-        wqkv = self._get("wqkv", (qkv_w, H), bf)
-        wo = self._get("wo", (H, s.q_rows), bf)
+        # Quantised weights are expanded to bf16 one layer AHEAD of their use, on a side stream: the expansion is bound
+        # by HBM traffic, the products by the tensor cores, so the two overlap.  Two sets of bf16 buffers alternate.
+        ahead = self.expert_source is None and self.expand_ahead
+        nset = 2 if ahead else 1
+        wqkv_s = [self._get(f"wqkv{i}", (qkv_w, H), bf) for i in range(nset)]
+        wo_s = [self._get(f"wo{i}", (H, s.q_rows), bf) for i in range(nset)]
         q_bf = self._get("q_bf", (s.n_q, T, s.head_dim), bf)
         attn = self._get("attn", (T, s.q_rows), bf)
         dense_tiles = G.TileTable.dense(T, dev)
@@ -112,9 +118,9 @@ class GemmPrefill:
             E, I_, k = s.n_expert, s.moe_inter, s.n_used
             nslot = T * k
             cap = nslot + 128
-            wg = self._get("wg", (E, I_, H), bf)
-            wu = self._get("wu", (E, I_, H), bf)
-            wd = self._get("wd", (E, H, I_), bf)
+            wg_s = [self._get(f"wg{i}", (E, I_, H), bf) for i in range(nset)]
+            wu_s = [self._get(f"wu{i}", (E, I_, H), bf) for i in range(nset)]
+            wd_s = [self._get(f"wd{i}", (E, H, I_), bf) for i in range(nset)]
             logits = self._get("rl", (T, E), f32)
             xn3 = self._get("xn3", (T, 3 * H), bf)
             ids = self._get("ids", (T, k), i32)
@@ -130,18 +136,69 @@ class GemmPrefill:
             moe_tiles = G.TileTable(nslot, E, dev)
         if s.dense_inter and (s.first_dense > 0 or not s.is_moe):
             Id = s.dense_inter
-            dg = self._get("dg", (Id, H), bf)
-            du = self._get("du", (Id, H), bf)
-            dd = self._get("dd", (H, Id), bf)
+            dg_s = [self._get(f"dg{i}", (Id, H), bf) for i in range(nset)]
+            du_s = [self._get(f"du{i}", (Id, H), bf) for i in range(nset)]
+            dd_s = [self._get(f"dd{i}", (H, Id), bf) for i in range(nset)]
             dact = self._get("dact", (T, Id), bf)
         st = self.status
+
+        def expand(il: int, which: str) -> None:
+            """bf16 copies of layer il's weights into buffer set il % nset: 'attn', 'gate_up', 'down' or 'all'."""
+            b = f"blk.{il}."
+            i = il % nset
+            if which in ("attn", "all"):
+                G.dequant_bf16(w.q[b + "attn_q.weight"], wqkv_s[i][:s.q_rows])
+                G.dequant_bf16(w.q[b + "attn_k.weight"], wqkv_s[i][s.q_rows:s.q_rows + s.kv_rows])
+                G.dequant_bf16(w.q[b + "attn_v.weight"], wqkv_s[i][s.q_rows + s.kv_rows:])
+                G.dequant_bf16(w.q[b + "attn_output.weight"], wo_s[i])
+            if s.layer_is_moe(il):
+                if self.expert_source is not None:
+                    qg, qu, qd = self.expert_source(il)
+                else:
+                    qg, qu, qd = (w.q[b + f"ffn_{n}_exps.weight"] for n in ("gate", "up", "down"))
+                if which in ("gate_up", "all"):
+                    G.dequant_bf16(qg, wg_s[i])
+                    G.dequant_bf16(qu, wu_s[i])
+                if which in ("down", "all"):
+                    G.dequant_bf16(qd, wd_s[i])
+            else:
+                if which in ("gate_up", "all"):
+                    G.dequant_bf16(w.q[b + "ffn_gate.weight"], dg_s[i])
+                    G.dequant_bf16(w.q[b + "ffn_up.weight"], du_s[i])
+                if which in ("down", "all"):
+                    G.dequant_bf16(w.q[b + "ffn_down.weight"], dd_s[i])
+
+        main = torch.cuda.current_stream(dev)
+        if ahead:
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=dev)
+            side = self._side
+            ready = [torch.cuda.Event() for _ in range(s.n_layer)]
+            freed = [torch.cuda.Event() for _ in range(s.n_layer)]
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                expand(0, "all")
+                ready[0].record(side)
         for il in range(s.n_layer):
             b = f"blk.{il}."
             self.timing.mark(il, "ffn")
+            i = il % nset
+            wqkv, wo = wqkv_s[i], wo_s[i]
+            if s.is_moe:
+                wg, wu, wd = wg_s[i], wu_s[i], wd_s[i]
+            if s.dense_inter and (s.first_dense > 0 or not s.is_moe):
+                dg, du, dd = dg_s[i], du_s[i], dd_s[i]
+            if ahead:
+                if il + 1 < s.n_layer:
+                    with torch.cuda.stream(side):
+                        if il >= 1:
+                            side.wait_event(freed[il - 1])          # the set's previous user (layer il - 1) is done with it
+                        expand(il + 1, "all")
+                        ready[il + 1].record(side)
+                main.wait_event(ready[il])
             G.rmsnorm_bf16(x, w.f[b + "attn_norm.weight"], s.rms_eps, xn)
-            G.dequant_bf16(w.q[b + "attn_q.weight"], wqkv[:s.q_rows])
-            G.dequant_bf16(w.q[b + "attn_k.weight"], wqkv[s.q_rows:s.q_rows + s.kv_rows])
-            G.dequant_bf16(w.q[b + "attn_v.weight"], wqkv[s.q_rows + s.kv_rows:])
+            if not ahead:
+                expand(il, "attn")
             G.gemm_bf16(xn, wqkv, dense_tiles, out_f32=qkv, status=st)
             G.qk_norm_rope_append_prefill(qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
                                           e.inv_freq, s.rms_eps, 1.0 / math.sqrt(s.head_dim), s.head_dim, s.n_q, s.n_kv,
@@ -167,7 +224,6 @@ class GemmPrefill:
                 G.gemm_bf16(P, Vt, pv_tiles, out_bf16=attn.view(T * s.n_q, s.head_dim), dst_row=map_o, status=st)
                 self.timing.mark(il, "values")
             self.timing.mark(il, "attention")
-            G.dequant_bf16(w.q[b + "attn_output.weight"], wo)
             G.gemm_bf16(attn, wo, dense_tiles, out_f32=x, resid=x, status=st)
             self.timing.mark(il, "o_proj")
             if s.layer_is_moe(il):
@@ -191,27 +247,29 @@ class GemmPrefill:
                 G.moe_scatter(ids, wts, E, moe_tiles.offsets, cursor, pos_of, dst_row, row_scale)
                 G.gather_rows_bf16(xn, dst_row, moe_tiles.offsets[E:E + 1], cap, k, Ap)
                 self.timing.mark(il, "dispatch")
-                if self.expert_source is not None:
-                    qg, qu, qd = self.expert_source(il)
-                else:
-                    qg, qu, qd = (w.q[b + f"ffn_{n}_exps.weight"] for n in ("gate", "up", "down"))
-                G.dequant_bf16(qg, wg)
-                G.dequant_bf16(qu, wu)
+                if not ahead:
+                    expand(il, "gate_up")
                 self.timing.mark(il, "expand_gate_up")
                 G.gemm_bf16(Ap, wg, moe_tiles, out_bf16=act, B2=wu, status=st)
                 self.timing.mark(il, "gemm_gate_up")
-                G.dequant_bf16(qd, wd)
+                if not ahead:
+                    expand(il, "down")
                 self.timing.mark(il, "expand_down")
                 G.gemm_bf16(act, wd, moe_tiles, out_f32=slot_out, dst_row=dst_row, row_scale=row_scale, status=st)
                 self.timing.mark(il, "gemm_down")
                 G.moe_combine(slot_out, pos_of, T, k, x, x)
             else:
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
-                G.dequant_bf16(w.q[b + "ffn_gate.weight"], dg)
-                G.dequant_bf16(w.q[b + "ffn_up.weight"], du)
+                if not ahead:
+                    expand(il, "gate_up")
                 G.gemm_bf16(xn, dg, dense_tiles, out_bf16=dact, B2=du, status=st)
-                G.dequant_bf16(w.q[b + "ffn_down.weight"], dd)
+                if not ahead:
+                    expand(il, "down")
                 G.gemm_bf16(dact, dd, dense_tiles, out_f32=x, resid=x, status=st)
+            if ahead:
+                freed[il].record(main)
+        if ahead:
+            main.wait_stream(side)
         e.x[0].copy_(x[T - 1])
         if int(st.item()) != 0:
             raise RuntimeError("a bounded wait inside the GEMM kernel ran out (status word set)")
