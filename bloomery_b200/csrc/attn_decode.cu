@@ -496,21 +496,6 @@ int bl_qk_norm_rope_append(const float* qkv, long qkv_stride, const float* q_gai
   return (int)launch(qk_norm_rope_append_kernel<64>, grid, dim3(32), 0, st, a);
 }
 
-// Prompt form: the same kernel over T rows; q goes out as bf16 [n_q, T, head].
-int bl_qk_norm_rope_append_prefill(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain,
-                                   const float* inv_freq, float eps, float q_scale, int head, int n_q, int n_kv, int T,
-                                   const int* row_pos, const int* row_seq, const int* block_table, int max_pages,
-                                   int n_pages, void* k_cache, void* v_cache, void* q_bf16, unsigned* fault, int layer,
-                                   cudaStream_t st) {
-  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
-  BL_REQUIRE(T >= 1 && T <= 65535 && n_q >= 1 && n_kv >= 1, BL_ERR_SHAPE);
-  RopeArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, T, row_pos, row_seq, block_table,
-             max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, nullptr, fault, layer, (__nv_bfloat16*)q_bf16};
-  dim3 grid(n_q + 2 * n_kv, T);
-  if (head == 128) return (int)launch(qk_norm_rope_append_kernel<128>, grid, dim3(64), 0, st, a);
-  return (int)launch(qk_norm_rope_append_kernel<64>, grid, dim3(32), 0, st, a);
-}
-
 // 1: the segment pass runs on tensor-core tiles (flash_decode_seg_mma_kernel); 0: the fp32 kernel
 void bl_set_flash_mma(int on) { bl::g_flash_mma = on ? 1 : 0; }
 

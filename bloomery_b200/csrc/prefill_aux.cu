@@ -143,6 +143,116 @@ __global__ void moe_scatter_kernel(const int* ids, const float* wts, int n, int 
   row_scale[p] = wts[i];
 }
 
+// The expert-sorted plan of a micro-batch in ONE launch (one block): count the routed slots per expert, prefix-sum
+// the counts into row offsets, write the grouped product's tile table, and scatter every slot to its row.
+//   ids / wts [n] flat (token-major) slot lists; pos_of[i] = row of slot i (-1: expert elsewhere);
+//   dst_row[p] = slot at row p (-1 in the padding rows up to `cap`); row_scale[p] = its router weight;
+//   offsets[E + 1]; mtiles / n_mtiles = 128-row tiles {expert, first row, end row of the expert, 0}.
+// Replaces count + tile build + scatter and three buffer clears (six launches, one of them a serial loop).
+struct MTilePlan { int group, row0, row_end, pad; };
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* ids, const float* wts, int n, int E, int cap, int* offsets,
+                                                        int* pos_of, int* dst_row, float* row_scale, MTilePlan* mtiles,
+                                                        int* n_mtiles, int max_mtiles) {
+  __shared__ int s_cnt[512], s_off[513], s_toff[513], s_cur[512];
+  pdl_wait();
+  pdl_launch();
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += 1024) { s_cnt[e] = 0; s_cur[e] = 0; }
+  __syncthreads();
+  for (int i = tid; i < n; i += 1024) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&s_cnt[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int off = 0, toff = 0;
+    for (int e = 0; e < E; ++e) {
+      s_off[e] = off; s_toff[e] = toff;
+      off += s_cnt[e];
+      toff += (s_cnt[e] + 127) / 128;
+    }
+    s_off[E] = off; s_toff[E] = toff;
+    *n_mtiles = toff < max_mtiles ? toff : max_mtiles;
+  }
+  __syncthreads();
+  for (int e = tid; e <= E; e += 1024) offsets[e] = s_off[e];
+  for (int e = tid; e < E; e += 1024) {
+    const int rows = s_cnt[e], off = s_off[e];
+    for (int r = 0, t = s_toff[e]; r < rows; r += 128, ++t)
+      if (t < max_mtiles) mtiles[t] = MTilePlan{e, off + r, off + rows, 0};
+  }
+  for (int p = s_off[E] + tid; p < cap; p += 1024) dst_row[p] = -1;
+  for (int i = tid; i < n; i += 1024) {
+    const int e = ids[i];
+    if (e < 0 || e >= E) { pos_of[i] = -1; continue; }
+    const int p = s_off[e] + atomicAdd(&s_cur[e], 1);
+    pos_of[i] = p;
+    dst_row[p] = i;
+    row_scale[p] = wts[i];
+  }
+}
+
+// Prompt form of the per-head RMSNorm + NEOX RoPE + KV append: one block per token, a warp per head (heads w, w + 8,
+// ...), the sines and cosines of the token's position computed once per lane and reused by every head.
+//   q -> bf16 [n_q][T][HEAD] (scaled), k / v -> the paged f16 cache.  Same arithmetic as the decode launch.
+template <int HEAD>
+__global__ void __launch_bounds__(256) rope_append_prefill_kernel(const float* qkv, long qkv_stride, const float* q_gain,
+                                                                  const float* k_gain, const float* inv_freq, float eps,
+                                                                  float q_scale, int n_q, int n_kv, int T, const int* row_pos,
+                                                                  const int* row_seq, const int* block_table, int max_pages,
+                                                                  int n_pages, __half* k_cache, __half* v_cache,
+                                                                  __nv_bfloat16* q_bf16, unsigned* fault, int layer) {
+  constexpr int DPL = HEAD / 32;
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int seq = row_seq[t];
+  if (seq < 0) return;
+  const int pos = row_pos[t];
+  float sn[DPL / 2], cs[DPL / 2];
+#pragma unroll
+  for (int j = 0; j < DPL / 2; ++j) sincosf((float)pos * inv_freq[lane + 32 * j], &sn[j], &cs[j]);
+  const int pslot = pos / 64;
+  const int page = (pslot < max_pages) ? block_table[(long)seq * max_pages + pslot] : -1;
+  const bool page_ok = page >= 0 && page < n_pages;
+  if (!page_ok && threadIdx.x == 0) raise_fault(fault, layer, FS_PAGE);
+  const float* row = qkv + (long)t * qkv_stride;
+  for (int head = warp; head < n_q + 2 * n_kv; head += 8) {
+    const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
+    float x[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) x[j] = row[(long)head * HEAD + lane + 32 * j];
+    const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+    if (gain) {
+      double ss = 0.0;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) ss += (double)(x[j] * x[j]);
+      ss = warp_sum_d(ss);
+      const float scale = (float)(1.0 / sqrt(ss / (double)HEAD + (double)eps));
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) x[j] = (scale * gain[lane + 32 * j]) * x[j];
+    }
+    if (is_q || is_k) {
+#pragma unroll
+      for (int j = 0; j < DPL / 2; ++j) {
+        const float x0 = x[j], x1 = x[j + DPL / 2];
+        x[j] = fmaf(x0, cs[j], -(x1 * sn[j]));
+        x[j + DPL / 2] = fmaf(x0, sn[j], x1 * cs[j]);
+      }
+    }
+    if (is_q) {
+      __nv_bfloat16* q = q_bf16 + ((long)head * T + t) * HEAD;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) q[lane + 32 * j] = __float2bfloat16_rn(x[j] * q_scale);
+    } else if (page_ok) {
+      const int kvh = is_k ? head - n_q : head - n_q - n_kv;
+      __half* dst = (is_k ? k_cache : v_cache) + (((long)page * n_kv + kvh) * 64 + (pos % 64)) * HEAD;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) dst[lane + 32 * j] = __float2half_rn(x[j]);
+    }
+  }
+}
+
 // A_perm[p, :] = src[dst_row[p] / k, :]  (bf16 rows of K values, 16-byte vectors)
 __global__ void __launch_bounds__(256) gather_rows_bf16_kernel(const __nv_bfloat16* src, long src_stride, const int* dst_row,
                                                               const int* n_rows, int k, int K, __nv_bfloat16* out) {
@@ -359,6 +469,28 @@ int bl_rmsnorm_bf16(const float* x, long x_stride, const float* gain, float eps,
 int bl_moe_count(const int* ids, int n, int E, int* counts, cudaStream_t st) {
   BL_REQUIRE(n >= 1 && E >= 1, BL_ERR_SHAPE);
   return (int)launch(moe_count_kernel, dim3((n + 255) / 256), dim3(256), 0, st, ids, n, E, counts);
+}
+
+int bl_moe_plan(const int* ids, const float* wts, int n, int E, int cap, int* offsets, int* pos_of, int* dst_row,
+                float* row_scale, void* mtiles, int* n_mtiles, int max_mtiles, cudaStream_t st) {
+  BL_REQUIRE(n >= 1 && E >= 1 && E <= 512 && cap >= n, BL_ERR_SHAPE);
+  return (int)launch(moe_plan_kernel, dim3(1), dim3(1024), 0, st, ids, wts, n, E, cap, offsets, pos_of, dst_row, row_scale,
+                     (MTilePlan*)mtiles, n_mtiles, max_mtiles);
+}
+
+int bl_rope_append_prefill(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain, const float* inv_freq,
+                           float eps, float q_scale, int head, int n_q, int n_kv, int T, const int* row_pos, const int* row_seq,
+                           const int* block_table, int max_pages, int n_pages, void* k_cache, void* v_cache, void* q_bf16,
+                           unsigned* fault, int layer, cudaStream_t st) {
+  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
+  BL_REQUIRE(T >= 1 && n_q >= 1 && n_kv >= 1 && q_bf16, BL_ERR_SHAPE);
+  if (head == 128)
+    return (int)launch(rope_append_prefill_kernel<128>, dim3(T), dim3(256), 0, st, qkv, qkv_stride, q_gain, k_gain, inv_freq, eps,
+                       q_scale, n_q, n_kv, T, row_pos, row_seq, block_table, max_pages, n_pages, (__half*)k_cache,
+                       (__half*)v_cache, (__nv_bfloat16*)q_bf16, fault, layer);
+  return (int)launch(rope_append_prefill_kernel<64>, dim3(T), dim3(256), 0, st, qkv, qkv_stride, q_gain, k_gain, inv_freq, eps,
+                     q_scale, n_q, n_kv, T, row_pos, row_seq, block_table, max_pages, n_pages, (__half*)k_cache,
+                     (__half*)v_cache, (__nv_bfloat16*)q_bf16, fault, layer);
 }
 
 int bl_moe_scatter(const int* ids, const float* wts, int n, int E, const int* offsets, int* cursor, int* pos_of,

@@ -179,13 +179,22 @@ def softmax_causal(S, rows: int, Tq: int, pos0: int, T_pad: int, P) -> None:
                                    stream()), "bl_softmax_causal")
 
 
+def moe_plan(ids, wts, E: int, tiles: "TileTable", pos_of, dst_row, row_scale) -> None:
+    """Count, offsets, tile table and scatter of a micro-batch's routed slots in one launch (``ids`` / ``wts`` flat)."""
+    n = ids.numel()
+    rc = cuda().bl_moe_plan(p(ids), p(wts), I(n), I(E), I(dst_row.numel()), p(tiles.offsets), p(pos_of), p(dst_row),
+                            p(row_scale), p(tiles.mtiles), p(tiles.n_mtiles), I(tiles.max_mtiles), stream())
+    check(rc, "bl_moe_plan")
+
+
 def qk_norm_rope_append_prefill(qkv, q_gain, k_gain, inv_freq, eps, q_scale, head, n_q, n_kv, T, row_pos, row_seq,
                                 block_table, n_pages, k_cache, v_cache, q_bf16, fault, layer) -> None:
-    rc = cuda().bl_qk_norm_rope_append_prefill(p(qkv), L(qkv.stride(0)), p(q_gain), p(k_gain), p(inv_freq), F(eps),
-                                               F(q_scale), I(head), I(n_q), I(n_kv), I(T), p(row_pos), p(row_seq),
-                                               p(block_table), I(block_table.shape[1]), I(n_pages), p(k_cache),
-                                               p(v_cache), p(q_bf16), p(fault), I(layer), stream())
-    check(rc, "bl_qk_norm_rope_append_prefill")
+    """Per-head RMSNorm + RoPE + KV append of T prompt rows: a block per token, a warp per head."""
+    rc = cuda().bl_rope_append_prefill(p(qkv), L(qkv.stride(0)), p(q_gain), p(k_gain), p(inv_freq), F(eps),
+                                       F(q_scale), I(head), I(n_q), I(n_kv), I(T), p(row_pos), p(row_seq),
+                                       p(block_table), I(block_table.shape[1]), I(n_pages), p(k_cache),
+                                       p(v_cache), p(q_bf16), p(fault), I(layer), stream())
+    check(rc, "bl_rope_append_prefill")
 
 
 def rmsnorm_hilo(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:

@@ -5,7 +5,7 @@ CUDA events.
     python -m bloomery_b200.ops.kernel_bench NAME [replays] [context] [--no-staged] [--rows M]
 
 NAME: chain (the six launches of a layer in order) | qkv | attn | o | router | gateup | down | rope | flash |
-flash_mma | gemm | gemmdist | mla | sampler | gap.  ``--no-staged`` runs the register-streaming kernels
+flash_mma | gemm | gemmdist | pflash | prope | mplan | mla | sampler | gap.  ``--no-staged`` runs the register-streaming kernels
 instead of the shared-memory staged ones.  It is also the small workload the ncu summaries under ``profiles/``
 were captured on.
 """
@@ -103,6 +103,25 @@ def main(argv=None) -> int:
         extra = dict(G=G, A=(torch.randn(4096, 2048, device=dev) * 0.1).bfloat16(), B=(torch.randn(5120, 2048, device=dev) * 0.1).bfloat16(),
                      C=torch.zeros(4096, 5120, device=dev, dtype=torch.bfloat16), tt=G.TileTable.dense(4096, dev),
                      gst=torch.zeros(1, dtype=torch.int32, device=dev))
+    if which == "pflash":
+        # prompt flash attention of `ctx` tokens (32 query heads over 4 key/value heads of 128)
+        from bloomery_b200.ops import gemm as G
+        tp = (ctx + 127) // 128 * 128
+        extra = dict(G=G, pq=(torch.randn(n_q, ctx, hd, device=dev) * 0.3).bfloat16(), pk=(torch.randn(n_kv, tp, hd, device=dev)).bfloat16(),
+                     pv=(torch.randn(n_kv, hd, tp, device=dev)).bfloat16(), po=torch.zeros(ctx, n_q * hd, device=dev, dtype=torch.bfloat16),
+                     gst=torch.zeros(1, dtype=torch.int32, device=dev))
+    if which == "prope":
+        # prompt RMSNorm + RoPE + KV append of `ctx` rows
+        from bloomery_b200.ops import gemm as G
+        extra = dict(G=G, rqkv=torch.randn(ctx, (n_q + 2 * n_kv) * hd, device=dev), rpos=torch.arange(ctx, dtype=torch.int32, device=dev),
+                     rseq=torch.zeros(ctx, dtype=torch.int32, device=dev), rqb=torch.zeros(n_q, ctx, hd, device=dev, dtype=torch.bfloat16))
+    if which == "mplan":
+        # routed-slot plan (count, offsets, tile table, scatter) of `ctx` tokens x 8 experts of 128
+        from bloomery_b200.ops import gemm as G
+        n = ctx * TOPK
+        extra = dict(G=G, mids=torch.stack([torch.randperm(E, device=dev)[:TOPK] for _ in range(ctx)]).to(torch.int32).contiguous(),
+                     mwts=torch.rand(ctx, TOPK, device=dev), mtt=G.TileTable(n, E, dev), mpos_of=torch.zeros(n, dtype=torch.int32, device=dev),
+                     mdst=torch.zeros(n + 128, dtype=torch.int32, device=dev), mscale=torch.zeros(n + 128, device=dev))
     if which == "gemmdist":
         # the several-GPU epilogue on one GPU: o_proj-shaped product whose rows are added into two "owners" (both local here)
         from bloomery_b200.ops import gemm as G
@@ -178,6 +197,9 @@ def main(argv=None) -> int:
             if which == "rope": K.qk_norm_rope_append(qkv, r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, 1, fpos, fseq, table, n_pages, kc, vc, r_q, fault, 0)
             if which in ("flash", "flash_mma"): K.flash_decode(fq, kc, vc, fpos, fseq, table, n_pages, hd, n_q, n_kv, 1, n_seg, ctx, pml, pacc, None, xq, xds, fault, 0)
             if which == "gemm": X["G"].gemm_bf16(X["A"], X["B"], X["tt"], out_bf16=X["C"], status=X["gst"])
+            if which == "pflash": X["G"].flash_prefill(X["pq"], X["pk"], X["pv"], X["po"], 0, X["gst"])
+            if which == "prope": X["G"].qk_norm_rope_append_prefill(X["rqkv"], r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, ctx, X["rpos"], X["rseq"], table, n_pages, kc, vc, X["rqb"], fault, 0)
+            if which == "mplan": X["G"].moe_plan(X["mids"], X["mwts"], E, X["mtt"], X["mpos_of"], X["mdst"], X["mscale"])
             if which == "gemmdist": X["G"].gemm_bf16_dist([X["A"].data_ptr()], 4096, 4096, X["B"], X["tt"], owners=[o.data_ptr() for o in X["own"]], rows_per_owner=2048, ldc=2048, status=X["gst"])
             if which == "mla": K.mla_flash_decode(X["mqlat"], X["mcache"], X["mpos"], X["mseq"], X["mtable"], X["mctx"] // 64, X["mq"], 1, X["mseg"], X["mctx"], X["mml"], X["macc"], X["mvb"], 128, None, X["moq"], X["mods"], fault, 0)
             if which == "gap":

@@ -239,10 +239,7 @@ class ShardedGemmPrefill:
                         G.copy_bytes(ids_peers[src], ids_all[src * Tr:].data_ptr(), Tr * k * 4)
                         G.copy_bytes(wts_peers[src], wts_all[src * Tr:].data_ptr(), Tr * k * 4)
                     G.localize_ids(ids_all, e_lo, e_lo + El, ids_loc)
-                    counts.zero_(); cursor.zero_(); dst_row.fill_(-1)
-                    G.moe_count(ids_loc, El, counts)
-                    moe_tiles.build(counts)
-                    G.moe_scatter(ids_loc, wts_all, El, moe_tiles.offsets, cursor, pos_of, dst_row, row_scale)
+                    G.moe_plan(ids_loc, wts_all, El, moe_tiles, pos_of, dst_row, row_scale)
                     # dispatch: pull the rows routed to this rank's experts from the ranks that own them
                     G.gather_rows_peer(xn_peers, H, Tr, dst_row, moe_tiles.offsets[El:El + 1], cap, k, H, Ap)
                     G.dequant_bf16(w.q[b + "ffn_gate_exps.weight"], wg)

@@ -200,10 +200,12 @@ class GemmPrefill:
             if not ahead:
                 expand(il, "attn")
             G.gemm_bf16(xn, wqkv, dense_tiles, out_f32=qkv, status=st)
+            self.timing.mark(il, "qkv_gemm")
             G.qk_norm_rope_append_prefill(qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
                                           e.inv_freq, s.rms_eps, 1.0 / math.sqrt(s.head_dim), s.head_dim, s.n_q, s.n_kv,
                                           T, row_pos, row_seq, e.kv.table, e.kv.n_pages, e.kv.k[il], e.kv.v[il], q_bf,
                                           e.fault, il)
+            self.timing.mark(il, "rope_append")
             G.kv_gather_bf16(e.kv.k[il], e.kv.v[il], e.kv.table[slot], e.kv.n_pages, s.n_kv, s.head_dim, n_keys, T_pad,
                              Kb, Vt)
             self.timing.mark(il, "qkv")
@@ -238,13 +240,12 @@ class GemmPrefill:
                     G.gemm_bf16(xn3, wr, dense_tiles, out_f32=logits, status=st)
                 else:
                     K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, rw, T, logits, None, None, None, e.fault, il)
+                self.timing.mark(il, "router_logits")
                 K.route_rows(logits, e._rule(il), T, ids, wts, e.heat[il], e.fault, il)
                 self.timing.mark(il, "route")
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
-                counts.zero_(); cursor.zero_(); dst_row.fill_(-1)
-                G.moe_count(ids, E, counts)
-                moe_tiles.build(counts)
-                G.moe_scatter(ids, wts, E, moe_tiles.offsets, cursor, pos_of, dst_row, row_scale)
+                G.moe_plan(ids, wts, E, moe_tiles, pos_of, dst_row, row_scale)
+                self.timing.mark(il, "count_scatter")
                 G.gather_rows_bf16(xn, dst_row, moe_tiles.offsets[E:E + 1], cap, k, Ap)
                 self.timing.mark(il, "dispatch")
                 if not ahead:
@@ -258,6 +259,7 @@ class GemmPrefill:
                 G.gemm_bf16(act, wd, moe_tiles, out_f32=slot_out, dst_row=dst_row, row_scale=row_scale, status=st)
                 self.timing.mark(il, "gemm_down")
                 G.moe_combine(slot_out, pos_of, T, k, x, x)
+                self.timing.mark(il, "combine")
             else:
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
                 if not ahead:

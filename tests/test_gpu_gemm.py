@@ -67,9 +67,23 @@ def test_grouped_dual_swiglu_and_scatter():
     dst_row = torch.full((cap,), -1, dtype=torch.int32, device=DEV)
     row_scale = torch.zeros(cap, device=DEV)
     tiles = G.TileTable(n, E, DEV)
-    G.moe_count(ids, E, counts)
-    tiles.build(counts)
-    G.moe_scatter(ids, wts, E, tiles.offsets, cursor, pos_of, dst_row, row_scale)
+    dst_row.fill_(7)                                            # the plan must clear the padding rows itself
+    G.moe_plan(ids, wts, E, tiles, pos_of, dst_row, row_scale)
+    torch.cuda.synchronize()
+    flat = ids.flatten().cpu()
+    cnt = torch.bincount(flat[flat >= 0], minlength=E)
+    off = torch.cat([torch.zeros(1, dtype=torch.long), cnt.cumsum(0)])
+    assert tiles.offsets.cpu().tolist() == off.tolist()
+    want_tiles = [(e, int(off[e]) + r, int(off[e + 1])) for e in range(E) for r in range(0, int(cnt[e]), 128)]
+    nmt = int(tiles.n_mtiles.item())
+    assert nmt == len(want_tiles)
+    assert [tuple(r[:3]) for r in tiles.mtiles.view(-1, 4)[:nmt].cpu().tolist()] == want_tiles
+    dr = dst_row.cpu()
+    assert (dr[int(off[E]):] == -1).all()
+    for e in range(E):                                          # each expert's rows hold exactly its slots
+        assert sorted(dr[int(off[e]):int(off[e + 1])].tolist()) == (flat == e).nonzero().flatten().tolist()
+    po = pos_of.cpu()
+    assert (po[flat < 0] == -1).all() and (dr[po[flat >= 0].long()] == (flat >= 0).nonzero().flatten()).all()
     Ap = torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV)
     G.gather_rows_bf16(x, dst_row, tiles.offsets[E:E + 1], cap, k, Ap)
     act = torch.zeros(cap, I_, dtype=torch.bfloat16, device=DEV)
