@@ -147,12 +147,12 @@ __global__ void moe_scatter_kernel(const int* ids, const float* wts, int n, int 
 // the counts into row offsets, write the grouped product's tile table, and scatter every slot to its row.
 //   ids / wts [n] flat (token-major) slot lists; pos_of[i] = row of slot i (-1: expert elsewhere);
 //   dst_row[p] = slot at row p (-1 in the padding rows up to `cap`); row_scale[p] = its router weight;
-//   offsets[E + 1]; mtiles / n_mtiles = 128-row tiles {expert, first row, end row of the expert, 0}.
+//   offsets[E + 1]; mtiles / n_mtiles = tiles of tile_rows rows {expert, first row, end row of the expert, 0}.
 // Replaces count + tile build + scatter and three buffer clears (six launches, one of them a serial loop).
 struct MTilePlan { int group, row0, row_end, pad; };
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* ids, const float* wts, int n, int E, int cap, int* offsets,
                                                         int* pos_of, int* dst_row, float* row_scale, MTilePlan* mtiles,
-                                                        int* n_mtiles, int max_mtiles) {
+                                                        int* n_mtiles, int max_mtiles, int tile_rows) {
   __shared__ int s_cnt[512], s_off[513], s_toff[513], s_cur[512];
   pdl_wait();
   pdl_launch();
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* ids, const fl
     for (int e = 0; e < E; ++e) {
       s_off[e] = off; s_toff[e] = toff;
       off += s_cnt[e];
-      toff += (s_cnt[e] + 127) / 128;
+      toff += (s_cnt[e] + tile_rows - 1) / tile_rows;
     }
     s_off[E] = off; s_toff[E] = toff;
     *n_mtiles = toff < max_mtiles ? toff : max_mtiles;
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* ids, const fl
   for (int e = tid; e <= E; e += 1024) offsets[e] = s_off[e];
   for (int e = tid; e < E; e += 1024) {
     const int rows = s_cnt[e], off = s_off[e];
-    for (int r = 0, t = s_toff[e]; r < rows; r += 128, ++t)
+    for (int r = 0, t = s_toff[e]; r < rows; r += tile_rows, ++t)
       if (t < max_mtiles) mtiles[t] = MTilePlan{e, off + r, off + rows, 0};
   }
   for (int p = s_off[E] + tid; p < cap; p += 1024) dst_row[p] = -1;
@@ -472,10 +472,10 @@ int bl_moe_count(const int* ids, int n, int E, int* counts, cudaStream_t st) {
 }
 
 int bl_moe_plan(const int* ids, const float* wts, int n, int E, int cap, int* offsets, int* pos_of, int* dst_row,
-                float* row_scale, void* mtiles, int* n_mtiles, int max_mtiles, cudaStream_t st) {
-  BL_REQUIRE(n >= 1 && E >= 1 && E <= 512 && cap >= n, BL_ERR_SHAPE);
+                float* row_scale, void* mtiles, int* n_mtiles, int max_mtiles, int tile_rows, cudaStream_t st) {
+  BL_REQUIRE(n >= 1 && E >= 1 && E <= 512 && cap >= n && tile_rows >= 8, BL_ERR_SHAPE);
   return (int)launch(moe_plan_kernel, dim3(1), dim3(1024), 0, st, ids, wts, n, E, cap, offsets, pos_of, dst_row, row_scale,
-                     (MTilePlan*)mtiles, n_mtiles, max_mtiles);
+                     (MTilePlan*)mtiles, n_mtiles, max_mtiles, tile_rows);
 }
 
 int bl_rope_append_prefill(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain, const float* inv_freq,

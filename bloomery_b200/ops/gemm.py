@@ -13,10 +13,12 @@ BM = 128
 
 
 class TileTable:
-    """Device-resident table of 128-row tiles of a (grouped) GEMM."""
+    """Device-resident table of row tiles of a (grouped) GEMM: 128 rows per tile, or ``tile_rows`` for the
+    quantised-weight GEMM, whose token tiles may be 32 rows."""
 
-    def __init__(self, max_rows: int, n_groups: int, device):
-        self.max_mtiles = max_rows // BM + n_groups + 1
+    def __init__(self, max_rows: int, n_groups: int, device, tile_rows: int = BM):
+        self.tile_rows = tile_rows
+        self.max_mtiles = max_rows // tile_rows + n_groups + 1
         self.n_groups = n_groups
         self.mtiles = torch.zeros(self.max_mtiles, 4, dtype=torch.int32, device=device)
         self.n_mtiles = torch.zeros(1, dtype=torch.int32, device=device)
@@ -49,9 +51,15 @@ class TileTable:
         return t
 
     @classmethod
-    def dense(cls, rows: int, device) -> "TileTable":
-        t = cls(rows, 1, device)
-        t.build(torch.tensor([rows], dtype=torch.int32, device=device))
+    def dense(cls, rows: int, device, tile_rows: int = BM) -> "TileTable":
+        t = cls(rows, 1, device, tile_rows)
+        if tile_rows == BM:
+            t.build(torch.tensor([rows], dtype=torch.int32, device=device))
+        else:
+            rows0 = list(range(0, rows, tile_rows))
+            t.mtiles[:len(rows0)] = torch.tensor([[0, r, rows, 0] for r in rows0], dtype=torch.int32).to(device)
+            t.n_mtiles.fill_(len(rows0))
+            t.offsets.copy_(torch.tensor([0, rows], dtype=torch.int32))
         return t
 
 
@@ -183,8 +191,31 @@ def moe_plan(ids, wts, E: int, tiles: "TileTable", pos_of, dst_row, row_scale) -
     """Count, offsets, tile table and scatter of a micro-batch's routed slots in one launch (``ids`` / ``wts`` flat)."""
     n = ids.numel()
     rc = cuda().bl_moe_plan(p(ids), p(wts), I(n), I(E), I(dst_row.numel()), p(tiles.offsets), p(pos_of), p(dst_row),
-                            p(row_scale), p(tiles.mtiles), p(tiles.n_mtiles), I(tiles.max_mtiles), stream())
+                            p(row_scale), p(tiles.mtiles), p(tiles.n_mtiles), I(tiles.max_mtiles), I(tiles.tile_rows),
+                            stream())
     check(rc, "bl_moe_plan")
+
+
+def qgemm_supports(w: QWeight) -> bool:
+    return bool(cuda().bl_qgemm_supports(I(w.wt))) and w.k % 256 == 0
+
+
+def qgemm(X: torch.Tensor, W: QWeight, tiles: TileTable, *, out_f32: Optional[torch.Tensor] = None,
+          out_bf16: Optional[torch.Tensor] = None, W2: Optional[QWeight] = None, dst_row=None, row_scale=None,
+          resid=None, status: Optional[torch.Tensor] = None) -> None:
+    """C = X @ W[g].T per token tile with W left block-quantised (``csrc/qgemm_tcgen05.cu``): X [rows, K] bf16, W (and
+    W2) resident Q4_K / Q5_K / Q6_K / Q8_0 matrices [N, bytes] or stacks [G, N, bytes]; tiles of 32 or 128 token rows.
+    With W2 the output is silu(X W^T) * (X W2^T)."""
+    assert X.dtype == torch.bfloat16 and X.stride(-1) == 1 and W.data.is_contiguous() and tiles.tile_rows in (32, 128)
+    assert W2 is None or (W2.wt == W.wt and W2.data.shape == W.data.shape and W2.data.is_contiguous())
+    G = W.data.shape[0] if W.data.dim() == 3 else 1
+    N = W.data.shape[-2]
+    out = out_f32 if out_f32 is not None else out_bf16
+    rc = cuda().bl_qgemm(p(X), L(X.stride(0)), L(X.shape[0]), p(W.data), p(W2.data if W2 is not None else None), I(W.wt),
+                         I(G), I(N), I(W.k), p(tiles.mtiles), p(tiles.n_mtiles), I(tiles.max_mtiles), I(tiles.tile_rows),
+                         p(out_f32), p(out_bf16), L(out.stride(0)), p(dst_row), p(row_scale), p(resid),
+                         L(resid.stride(0) if resid is not None else 0), p(status), I(sm_count()), stream())
+    check(rc, "bl_qgemm")
 
 
 def qk_norm_rope_append_prefill(qkv, q_gain, k_gain, inv_freq, eps, q_scale, head, n_q, n_kv, T, row_pos, row_seq,

@@ -5,7 +5,7 @@ CUDA events.
     python -m bloomery_b200.ops.kernel_bench NAME [replays] [context] [--no-staged] [--rows M]
 
 NAME: chain (the six launches of a layer in order) | qkv | attn | o | router | gateup | down | rope | flash |
-flash_mma | gemm | gemmdist | pflash | prope | mplan | mla | sampler | gap.  ``--no-staged`` runs the register-streaming kernels
+flash_mma | gemm | gemmdist | pflash | prope | mplan | qgu | qdown | bgu | bdown | mla | sampler | gap.  ``--no-staged`` runs the register-streaming kernels
 instead of the shared-memory staged ones.  It is also the small workload the ncu summaries under ``profiles/``
 were captured on.
 """
@@ -122,6 +122,22 @@ def main(argv=None) -> int:
         extra = dict(G=G, mids=torch.stack([torch.randperm(E, device=dev)[:TOPK] for _ in range(ctx)]).to(torch.int32).contiguous(),
                      mwts=torch.rand(ctx, TOPK, device=dev), mtt=G.TileTable(n, E, dev), mpos_of=torch.zeros(n, dtype=torch.int32, device=dev),
                      mdst=torch.zeros(n + 128, dtype=torch.int32, device=dev), mscale=torch.zeros(n + 128, device=dev))
+    if which in ("qgu", "qdown", "bgu", "bdown"):
+        # expert products of `ctx` tokens x 8 experts of 128: q* = quantised weights expanded inside the GEMM,
+        # b* = expansion launch + bf16 GEMM; --rows picks the token tile (32 or 128) of the q* forms
+        from bloomery_b200.ops import gemm as G
+        n = ctx * TOPK
+        tr = 32 if rows == 32 else 128
+        mids = torch.stack([torch.randperm(E, device=dev)[:TOPK] for _ in range(ctx)]).to(torch.int32).contiguous()
+        tt = G.TileTable(n, E, dev, tr if which[0] == "q" else 128)
+        dst = torch.zeros(n + 128, dtype=torch.int32, device=dev)
+        scale = torch.zeros(n + 128, device=dev)
+        G.moe_plan(mids, torch.rand(ctx, TOPK, device=dev), E, tt, torch.zeros(n, dtype=torch.int32, device=dev), dst, scale)
+        extra = dict(G=G, tt=tt, dst=dst, scale=scale, gst=torch.zeros(1, dtype=torch.int32, device=dev),
+                     xa=(torch.randn(n + 128, H, device=dev) * 0.3).bfloat16(), act=torch.zeros(n + 128, I, device=dev, dtype=torch.bfloat16),
+                     so=torch.zeros(n, H, device=dev), wg=torch.zeros(E, I, H, device=dev, dtype=torch.bfloat16),
+                     wu=torch.zeros(E, I, H, device=dev, dtype=torch.bfloat16), wd=torch.zeros(E, H, I, device=dev, dtype=torch.bfloat16))
+        M = 1
     if which == "gemmdist":
         # the several-GPU epilogue on one GPU: o_proj-shaped product whose rows are added into two "owners" (both local here)
         from bloomery_b200.ops import gemm as G
@@ -200,6 +216,14 @@ def main(argv=None) -> int:
             if which == "pflash": X["G"].flash_prefill(X["pq"], X["pk"], X["pv"], X["po"], 0, X["gst"])
             if which == "prope": X["G"].qk_norm_rope_append_prefill(X["rqkv"], r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, ctx, X["rpos"], X["rseq"], table, n_pages, kc, vc, X["rqb"], fault, 0)
             if which == "mplan": X["G"].moe_plan(X["mids"], X["mwts"], E, X["mtt"], X["mpos_of"], X["mdst"], X["mscale"])
+            if which == "qgu": X["G"].qgemm(X["xa"], l["g"], X["tt"], out_bf16=X["act"], W2=l["u"], status=X["gst"])
+            if which == "qdown": X["G"].qgemm(X["act"], l["d"], X["tt"], out_f32=X["so"], dst_row=X["dst"], row_scale=X["scale"], status=X["gst"])
+            if which == "bgu":
+                X["G"].dequant_bf16(l["g"], X["wg"]); X["G"].dequant_bf16(l["u"], X["wu"])
+                X["G"].gemm_bf16(X["xa"], X["wg"], X["tt"], out_bf16=X["act"], B2=X["wu"], status=X["gst"])
+            if which == "bdown":
+                X["G"].dequant_bf16(l["d"], X["wd"])
+                X["G"].gemm_bf16(X["act"], X["wd"], X["tt"], out_f32=X["so"], dst_row=X["dst"], row_scale=X["scale"], status=X["gst"])
             if which == "gemmdist": X["G"].gemm_bf16_dist([X["A"].data_ptr()], 4096, 4096, X["B"], X["tt"], owners=[o.data_ptr() for o in X["own"]], rows_per_owner=2048, ldc=2048, status=X["gst"])
             if which == "mla": K.mla_flash_decode(X["mqlat"], X["mcache"], X["mpos"], X["mseq"], X["mtable"], X["mctx"] // 64, X["mq"], 1, X["mseg"], X["mctx"], X["mml"], X["macc"], X["mvb"], 128, None, X["moq"], X["mods"], fault, 0)
             if which == "gap":

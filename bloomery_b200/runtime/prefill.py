@@ -54,6 +54,13 @@ class GemmPrefill:
         self.expand_ahead = True                # bf16 expansion of layer l + 1's weights on a side stream during layer l
         self._side = None
         self.flash = True                       # head size 128: fused attention on tensor memory (csrc/flash_tcgen05.cu)
+        # Resident bf16 copy of every layer's matrices, built by the first prompt that runs (58 GB for a 30 B-parameter
+        # mixture beside its 17 GB of Q4_K_M blocks): later prompts skip the expansion launches altogether.  None = only
+        # when the copy leaves a quarter of the card free; True / False force it.
+        from ..utils import levers
+        self.resident_bf16 = {"1": True, "0": False}.get(str(levers.get("BLOOMERY_PREFILL_BF16")), None)
+        self._resident = {}
+        self._resident_ok = None
         from .timing import PromptTiming
         self.timing = PromptTiming()            # arm() it to get per-unit milliseconds of the next micro-batch
 
@@ -101,7 +108,8 @@ class GemmPrefill:
         qkv = self._get("qkv", (T, qkv_w), f32)
         # Quantised weights are expanded to bf16 one layer AHEAD of their use, on a side stream: the expansion is bound
         # by HBM traffic, the products by the tensor cores, so the two overlap.  Two sets of bf16 buffers alternate.
-        ahead = self.expert_source is None and self.expand_ahead
+        resident = self._use_resident()
+        ahead = self.expert_source is None and self.expand_ahead and not resident
         nset = 2 if ahead else 1
         wqkv_s = [self._get(f"wqkv{i}", (qkv_w, H), bf) for i in range(nset)]
         wo_s = [self._get(f"wo{i}", (H, s.q_rows), bf) for i in range(nset)]
@@ -188,6 +196,22 @@ class GemmPrefill:
                 wg, wu, wd = wg_s[i], wu_s[i], wd_s[i]
             if s.dense_inter and (s.first_dense > 0 or not s.is_moe):
                 dg, du, dd = dg_s[i], du_s[i], dd_s[i]
+            if resident:
+                hit = self._resident.get(il)
+                if hit is None:
+                    # first use of this layer: expand into the shared scratch as always, then keep a copy
+                    expand(il, "all")
+                    hit = {"wqkv": wqkv.clone(), "wo": wo.clone()}
+                    if s.layer_is_moe(il):
+                        hit.update(wg=wg.clone(), wu=wu.clone(), wd=wd.clone())
+                    else:
+                        hit.update(dg=dg.clone(), du=du.clone(), dd=dd.clone())
+                    self._resident[il] = hit
+                wqkv, wo = hit["wqkv"], hit["wo"]
+                if s.layer_is_moe(il):
+                    wg, wu, wd = hit["wg"], hit["wu"], hit["wd"]
+                else:
+                    dg, du, dd = hit["dg"], hit["du"], hit["dd"]
             if ahead:
                 if il + 1 < s.n_layer:
                     with torch.cuda.stream(side):
@@ -197,7 +221,7 @@ class GemmPrefill:
                         ready[il + 1].record(side)
                 main.wait_event(ready[il])
             G.rmsnorm_bf16(x, w.f[b + "attn_norm.weight"], s.rms_eps, xn)
-            if not ahead:
+            if not ahead and not resident:
                 expand(il, "attn")
             G.gemm_bf16(xn, wqkv, dense_tiles, out_f32=qkv, status=st)
             self.timing.mark(il, "qkv_gemm")
@@ -248,12 +272,12 @@ class GemmPrefill:
                 self.timing.mark(il, "count_scatter")
                 G.gather_rows_bf16(xn, dst_row, moe_tiles.offsets[E:E + 1], cap, k, Ap)
                 self.timing.mark(il, "dispatch")
-                if not ahead:
+                if not ahead and not resident:
                     expand(il, "gate_up")
                 self.timing.mark(il, "expand_gate_up")
                 G.gemm_bf16(Ap, wg, moe_tiles, out_bf16=act, B2=wu, status=st)
                 self.timing.mark(il, "gemm_gate_up")
-                if not ahead:
+                if not ahead and not resident:
                     expand(il, "down")
                 self.timing.mark(il, "expand_down")
                 G.gemm_bf16(act, wd, moe_tiles, out_f32=slot_out, dst_row=dst_row, row_scale=row_scale, status=st)
@@ -262,10 +286,10 @@ class GemmPrefill:
                 self.timing.mark(il, "combine")
             else:
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn)
-                if not ahead:
+                if not ahead and not resident:
                     expand(il, "gate_up")
                 G.gemm_bf16(xn, dg, dense_tiles, out_bf16=dact, B2=du, status=st)
-                if not ahead:
+                if not ahead and not resident:
                     expand(il, "down")
                 G.gemm_bf16(dact, dd, dense_tiles, out_f32=x, resid=x, status=st)
             if ahead:
@@ -275,6 +299,22 @@ class GemmPrefill:
         e.x[0].copy_(x[T - 1])
         if int(st.item()) != 0:
             raise RuntimeError("a bounded wait inside the GEMM kernel ran out (status word set)")
+
+    def _use_resident(self) -> bool:
+        """Whether the layers' bf16 copies stay in HBM between prompts (decided once, before the first copy exists)."""
+        if self.expert_source is not None or self.resident_bf16 is False:
+            return False
+        if self._resident_ok is None:
+            if self.resident_bf16:
+                self._resident_ok = True
+            else:
+                s = self.e.spec
+                per_layer = (s.q_rows + 2 * s.kv_rows) * s.hidden + s.hidden * s.q_rows
+                per_layer += 3 * s.n_expert * s.moe_inter * s.hidden if s.is_moe else 3 * (s.dense_inter or 0) * s.hidden
+                need = 2 * per_layer * s.n_layer
+                free, total = torch.cuda.mem_get_info(self.e.device)
+                self._resident_ok = free - need >= total // 4
+        return self._resident_ok
 
     def _attn_tables(self, T: int, Tq: int, c0: int, n_q: int, Gq: int, pos0: int = 0):
         key = ("attn", T, Tq, c0, n_q, pos0)

@@ -1,0 +1,93 @@
+"""Quantised-weight tcgen05 GEMM (weights expanded in flight) against torch fp32 matmul of the same dequantised
+weights and bf16 activations."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def _weight(t, shape, K, seed):
+    from bloomery_b200.formats import quant as Q
+    from bloomery_b200.formats.resident import to_resident
+    from bloomery_b200.ops.decode import QWeight
+    g = torch.Generator().manual_seed(seed)
+    rows = 1
+    for d in shape:
+        rows *= d
+    w = torch.randn(rows, K, generator=g) * 0.05
+    raw = Q.quantize(w, t)
+    ref = Q.dequantize(raw, t, K).reshape(*shape, K)
+    return QWeight(to_resident(raw, t, K).to(DEV).reshape(*shape, -1).contiguous(), t, K), ref.to(DEV)
+
+
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0"])
+@pytest.mark.parametrize("rows,tile", [(300, 128), (45, 32), (128, 128)])
+def test_dense_qgemm(t, rows, tile):
+    from bloomery_b200.ops import gemm as G
+    N, K = 200, 1024                                            # N not a multiple of 128: the last weight tile is ragged
+    qw, ref_w = _weight(t, (N,), K, 1)
+    torch.manual_seed(2)
+    X = (torch.randn(rows, K, device=DEV) * 0.5).bfloat16()
+    R = torch.randn(rows, N, device=DEV)
+    C = torch.full((rows, N), float("nan"), device=DEV)
+    st = _status()
+    tiles = G.TileTable.dense(rows, DEV, tile)
+    G.qgemm(X, qw, tiles, out_f32=C, resid=R, status=st)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    ref = X.float() @ ref_w.bfloat16().float().T + R
+    assert torch.allclose(C, ref, rtol=1e-3, atol=1e-2), (C - ref).abs().max()
+    C2 = torch.zeros_like(C)
+    G.qgemm(X, qw, tiles, out_f32=C2, resid=R, status=st)
+    assert torch.equal(C, C2)                                   # bit-identical rerun
+
+
+@pytest.mark.parametrize("tile,T", [(128, 700), (32, 24)])
+def test_grouped_dual_swiglu_and_scatter_quantised(tile, T):
+    """The MoE path on quantised experts: rows grouped by expert, gate/up fused with SwiGLU (Q4_K), down (Q6_K)
+    scattered with the router weights; prompt-sized tiles and decode-batch tiles."""
+    from bloomery_b200.ops import gemm as G
+    torch.manual_seed(3)
+    E, k, H, I_ = 8, 2, 512, 256
+    wg, ref_g = _weight("Q4_K", (E, I_), H, 4)
+    wu, ref_u = _weight("Q4_K", (E, I_), H, 5)
+    wd, ref_d = _weight("Q6_K", (E, H), I_, 6)
+    ids = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
+    ids[5, 1] = -1
+    wts = torch.rand(T, k, device=DEV)
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+    n = T * k
+    cap = n + 128
+    pos_of = torch.zeros(n, dtype=torch.int32, device=DEV)
+    dst_row = torch.zeros(cap, dtype=torch.int32, device=DEV)
+    row_scale = torch.zeros(cap, device=DEV)
+    tiles = G.TileTable(n, E, DEV, tile)
+    G.moe_plan(ids, wts, E, tiles, pos_of, dst_row, row_scale)
+    Ap = torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV)
+    G.gather_rows_bf16(x, dst_row, tiles.offsets[E:E + 1], cap, k, Ap)
+    act = torch.zeros(cap, I_, dtype=torch.bfloat16, device=DEV)
+    st = _status()
+    G.qgemm(Ap, wg, tiles, out_bf16=act, W2=wu, status=st)
+    slot_out = torch.zeros(n, H, device=DEV)
+    G.qgemm(act, wd, tiles, out_f32=slot_out, dst_row=dst_row, row_scale=row_scale, status=st)
+    resid = torch.randn(T, H, device=DEV)
+    y = torch.zeros(T, H, device=DEV)
+    G.moe_combine(slot_out, pos_of, T, k, resid, y)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    ref = resid.clone()
+    xf = x.float()
+    Wg, Wu, Wd = ref_g.bfloat16().float(), ref_u.bfloat16().float(), ref_d.bfloat16().float()
+    for t_ in range(T):
+        for j in range(k):
+            e = int(ids[t_, j])
+            if e < 0:
+                continue
+            a = (torch.nn.functional.silu(xf[t_] @ Wg[e].T) * (xf[t_] @ Wu[e].T)).bfloat16().float()
+            ref[t_] += wts[t_, j] * (a @ Wd[e].T)
+    assert torch.allclose(y, ref, rtol=2e-2, atol=2e-2), (y - ref).abs().max()
