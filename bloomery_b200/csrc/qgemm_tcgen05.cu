@@ -5,9 +5,12 @@
 // (16 .. 128 per tile), so a decode batch of a few rows per expert pays for the tokens it has instead of a 128-row
 // tile, and a prompt tile expands each weight once for 128 tokens.
 //
-//   * weights: eight producer warps read the quantised blocks straight from global memory, decode 64-value units in
-//     registers and store bf16 into the 128-byte-swizzled A stage (generic-proxy stores, fence.proxy.async, mbarrier
-//     arrive) -- the bf16 form of a weight never exists in HBM;
+//   * weights: eight producer warps decode 64-value units in registers and store bf16 into the 128-byte-swizzled A
+//     stage (generic-proxy stores, fence.proxy.async, mbarrier arrive) -- the bf16 form of a weight never exists in
+//     HBM.  The quantised super-blocks of the tile's 128 rows reach the producers through a ring of raw TMA boxes
+//     ([128 rows x one super-block] of bytes, several in flight per SM, which is what a pass bound by weight
+//     streaming needs), or, where the ring does not fit beside the operand stages (gate+up at 128 tokens, Q8_0),
+//     by register loads one stage ahead;
 //   * tokens: one TMA thread loads [tokens x 64] bf16 boxes into the B stage of the same ring;
 //   * one elected thread issues tcgen05.mma (M = 128, N = tokens, K = 16) into TMEM, two accumulator buffers, so four
 //     epilogue warps read tile i back with tcgen05.ld while tile i + 1 accumulates;
@@ -21,6 +24,7 @@
 // Role in the reference: the int8 mma.sync grouped GEMMs that read quantised experts directly
 // (crates/gpu/src/gemm/q4k_sel.rs, q6k_sel.rs, kernels.rs); there the activations are quantised to q8 and the
 // product runs on mma.sync -- here the weights are expanded in flight and the product runs on tcgen05.
+#define BL_UNITS_GENERIC_LD 1      // weight units are also read out of shared memory here: plain loads
 #include "tc_common.cuh"
 
 namespace bl {
@@ -76,10 +80,15 @@ __device__ __forceinline__ void expand_unit(const typename Unit<T>::Regs& regs, 
 }
 
 // ---- fast expanders ---------------------------------------------------------------------
-// Integer-to-float conversions run at a quarter of the FMA rate, so the K-quant expanders avoid them: a code byte q
-// (< 128) dropped into mantissa bits 16..22 of 1.0f reads as X = 1 + q / 128, and the block's affine map
-// v = s * q + o becomes one FMA  v = (128 s) * X + (o - 128 s)  on a packed pair (fma.rn.f32x2).  The result equals
-// the fp32 decode to within an fp32 rounding of the offset, far below the bf16 rounding that follows.
+// Integer-to-float conversions run at a quarter of the FMA rate, so the K-quant expanders avoid them.
+//   exact form (token tiles of 128, i.e. prompts): a code byte q (< 128) dropped into mantissa bits 16..22 of 1.0f
+//   reads as X = 1 + q / 128, and the block's affine map v = s * q + o becomes one FMA
+//   v = (128 s) * X + (o - 128 s) on a packed pair (fma.rn.f32x2), rounded to bf16 once.  The result equals the fp32
+//   decode to within an fp32 rounding of the offset.
+//   short form (token tiles of 32 / 64, i.e. decode batches, where the expanders are the bottleneck): two code bytes
+//   become the bf16 pair (128 + q0, 128 + q1) with one byte permute, a packed bf16 subtract gives (q0, q1) exactly and
+//   a packed bf16 FMA gives s * q + o with s and o rounded to bf16: 1.5 instructions per value, at most about one
+//   more bf16 ulp of error per weight than the exact form.
 // FastUnit<T>::codes yields the unit's 64 code bytes in value order (16 words; word w belongs to group w / 4) and the
 // (scale, offset) pair of each of the four groups of 16 values.
 template <class T> struct FastUnit { static constexpr bool kHas = false; };
@@ -150,7 +159,32 @@ __device__ __forceinline__ uint4 fast8(uint32_t w0, uint32_t w1, float a, float 
   return out;
 }
 
-template <class T>
+// bf16x2 FMA / subtract on raw register pairs
+__device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf2_dup(float v) {
+  __nv_bfloat162 p = __float2bfloat162_rn(v);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+__device__ __forceinline__ uint4 short8(uint32_t w0, uint32_t w1, uint32_t s2, uint32_t o2) {
+  constexpr uint32_t k128 = 0x43004300u;                       // (128, 128) in bf16
+  uint4 out;
+  out.x = bf2_fma(bf2_sub(__byte_perm(w0, k128, 0x5150), k128), s2, o2);   // bytes (low to high): q0, 0x43, q1, 0x43
+  out.y = bf2_fma(bf2_sub(__byte_perm(w0, k128, 0x5352), k128), s2, o2);
+  out.z = bf2_fma(bf2_sub(__byte_perm(w1, k128, 0x5150), k128), s2, o2);
+  out.w = bf2_fma(bf2_sub(__byte_perm(w1, k128, 0x5352), k128), s2, o2);
+  return out;
+}
+
+template <class T, bool SHORT>
 __device__ __forceinline__ void expand_unit_fast(const typename Unit<T>::Regs& regs, int u, int kb, int row, uint8_t* sa) {
   uint32_t cw[16];
   float s[4], o[4];
@@ -158,21 +192,45 @@ __device__ __forceinline__ void expand_unit_fast(const typename Unit<T>::Regs& r
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int g = j >> 1;
-    const float a = 128.0f * s[g], c = o[g] - a;
     const int p = Unit<T>::pos(u, 8 * j) - QBK * kb;
     const int atom = p >> 6, ch = (p & 63) >> 3;
-    *reinterpret_cast<uint4*>(sa + atom * QATOM_A + row * 128 + ((ch ^ (row & 7)) << 4)) = fast8(cw[2 * j], cw[2 * j + 1], a, c);
+    uint4* dst = reinterpret_cast<uint4*>(sa + atom * QATOM_A + row * 128 + ((ch ^ (row & 7)) << 4));
+    if (SHORT) {
+      *dst = short8(cw[2 * j], cw[2 * j + 1], bf2_dup(s[g]), bf2_dup(o[g]));
+    } else {
+      const float a = 128.0f * s[g], c = o[g] - a;
+      *dst = fast8(cw[2 * j], cw[2 * j + 1], a, c);
+    }
   }
 }
-template <class T>
+template <class T, bool SHORT>
 __device__ __forceinline__ void expand_any(const typename Unit<T>::Regs& regs, int u, int kb, int row, uint8_t* sa) {
-  if constexpr (FastUnit<T>::kHas) expand_unit_fast<T>(regs, u, kb, row, sa);
+  if constexpr (FastUnit<T>::kHas) expand_unit_fast<T, SHORT>(regs, u, kb, row, sa);
   else expand_unit<T>(regs, u, kb, row, sa);
 }
 
 __host__ __device__ constexpr int q_stages(bool dual, int bn) {
   const int stage = (dual ? 2 : 1) * 2 * QATOM_A + 2 * bn * 128;
   const int n = (220 * 1024) / stage;
+  return n > 4 ? 4 : n;
+}
+// Raw ring: slots of [matrices][128 rows][super-block bytes]; 0 slots = the register-load path.
+template <class T> struct SbBytes { static constexpr int v = 0; };
+template <> struct SbBytes<Q4K> { static constexpr int v = Q4K::kSbBytes; };
+template <> struct SbBytes<Q5K> { static constexpr int v = Q5K::kSbBytes; };
+template <> struct SbBytes<Q6K> { static constexpr int v = Q6K::kSbBytes; };
+__host__ __device__ constexpr int q_raw_slots(int sb_bytes, bool dual, int bn) {
+  if (sb_bytes == 0) return 0;
+  const int stage = (dual ? 2 : 1) * 2 * QATOM_A + 2 * bn * 128;
+  const int raw = (dual ? 2 : 1) * QBM * sb_bytes;
+  const int n = (220 * 1024 - 2 * stage) / raw;
+  const int cap = dual ? 2 : 4;                                    // super-blocks in flight per SM; the rest goes to stages
+  return n > cap ? cap : (n < 0 ? 0 : n);
+}
+__host__ __device__ constexpr int q_stages_raw(int sb_bytes, bool dual, int bn) {
+  const int stage = (dual ? 2 : 1) * 2 * QATOM_A + 2 * bn * 128;
+  const int raw = (dual ? 2 : 1) * QBM * sb_bytes;
+  const int n = (220 * 1024 - q_raw_slots(sb_bytes, dual, bn) * raw) / stage;
   return n > 4 ? 4 : n;
 }
 __host__ __device__ constexpr int q_tmem_cols(bool dual, int bn) {
@@ -184,9 +242,14 @@ __host__ __device__ constexpr int q_tmem_cols(bool dual, int bn) {
 // (warp id modulo 4 = TMEM lane quarter), warps 6..13 = weight expanders.
 template <class T, bool DUAL, int BN>
 __global__ void __launch_bounds__(QTHREADS, 1)
-qgemm_kernel(const __grid_constant__ CUtensorMap tma_x, const QGemmArgs a) {
+qgemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
+             const __grid_constant__ CUtensorMap tma_w2, const QGemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  constexpr int STAGES = q_stages(DUAL, BN);
+  constexpr int SB = SbBytes<T>::v;
+  constexpr int RS = q_raw_slots(SB, DUAL, BN);                      // raw ring slots (0: register loads)
+  constexpr int RAW_MAT = QBM * SB;                                  // one matrix's 128 super-blocks
+  constexpr int RAW_SLOT = (DUAL ? 2 : 1) * RAW_MAT;
+  constexpr int STAGES = RS > 0 ? q_stages_raw(SB, DUAL, BN) : q_stages(DUAL, BN);
   constexpr int A_BYTES = 2 * QATOM_A;
   constexpr int B_ATOM = BN * 128;
   constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + 2 * B_ATOM;
@@ -194,6 +257,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tma_x, const QGemmArgs a) {
   constexpr int ACC_COLS = (DUAL ? 2 : 1) * BN;
   constexpr int TMEM_COLS = q_tmem_cols(DUAL, BN);
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ __align__(8) uint64_t raw_full[RS > 0 ? RS : 1], raw_empty[RS > 0 ? RS : 1];
+  uint8_t* const raw_ring = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023) + (size_t)STAGES * STAGE_BYTES;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -202,6 +267,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tma_x, const QGemmArgs a) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1 + QPRODUCERS / 32); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int r = 0; r < RS; ++r) { mbar_init(&raw_full[r], 1); mbar_init(&raw_empty[r], QPRODUCERS / 32); }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -224,10 +290,22 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tma_x, const QGemmArgs a) {
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
+      int rslot = 0; uint32_t rphase = 0;
       int issued = 0;
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
         const QTile mt = a.tiles[t / a.tiles_w];
+        const int n0 = (t % a.tiles_w) * QBM;
         for (int kb = 0; kb < kblocks; ++kb) {
+          if (RS > 0 && (kb & 1) == 0) {
+            // the super-block of stages kb and kb + 1: rows n0 .. n0 + 127 of the group's matrix (rows past the
+            // matrix arrive as zeros and are never stored)
+            if (!mbar_wait(&raw_empty[rslot], rphase ^ 1, abort_flag)) break;
+            uint8_t* dst = raw_ring + (size_t)rslot * RAW_SLOT;
+            mbar_expect_tx(&raw_full[rslot], RAW_SLOT);
+            tma_load_3d(dst, &tma_w, (kb >> 1) * SB, n0, mt.group, &raw_full[rslot]);
+            if (DUAL) tma_load_3d(dst + RAW_MAT, &tma_w2, (kb >> 1) * SB, n0, mt.group, &raw_full[rslot]);
+            if (++rslot == RS) { rslot = 0; rphase ^= 1; }
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) break;
           uint8_t* sb = smem + (size_t)stage * STAGE_BYTES + B_OFF;
           mbar_expect_tx(&full_bar[stage], 2 * B_ATOM);
@@ -342,12 +420,33 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tma_x, const QGemmArgs a) {
       tc_fence_after();
       uint8_t* sa = smem + (size_t)stage * STAGE_BYTES + (DUAL ? part * A_BYTES : 0);
 #pragma unroll
-      for (int i = 0; i < NU; ++i) expand_any<T>(r[i], 2 * kb + (DUAL ? i : part), kb, row, sa);
+      for (int i = 0; i < NU; ++i) expand_any<T, (BN < 128)>(r[i], 2 * kb + (DUAL ? i : part), kb, row, sa);
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_bar[stage]);
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     };
+    if constexpr (RS > 0) {
+      // raw ring: the tile's super-blocks arrive by TMA; a thread reads its row's units out of shared memory
+      int rslot = 0; uint32_t rphase = 0;
+      for (int t = blockIdx.x; t < total_tiles && ok && !*abort_flag; t += gridDim.x) {
+        for (int sbi = 0; sbi < kblocks / 2 && ok; ++sbi) {
+          if (!mbar_wait(&raw_full[rslot], rphase, abort_flag)) { ok = false; break; }
+          const uint8_t* rawrow = raw_ring + (size_t)rslot * RAW_SLOT + (DUAL ? part * RAW_MAT : 0) + row * SB - (long)sbi * SB;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int kb = 2 * sbi + half;
+            typename U::Regs r[NU];
+            fetch(rawrow, kb, r);
+            emit(kb, r);
+            if (!ok) break;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[rslot]);
+          if (++rslot == RS) { rslot = 0; rphase ^= 1; }
+        }
+      }
+    } else
     for (int t = blockIdx.x; t < total_tiles && ok && !*abort_flag; t += gridDim.x) {
       const QTile mt = a.tiles[t / a.tiles_w];
       int n = (t % a.tiles_w) * QBM + row;
@@ -375,25 +474,38 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tma_x, const QGemmArgs a) {
 }
 
 template <class T, bool DUAL, int BN>
-static int qgemm_go(const CUtensorMap& mx, const QGemmArgs& a, int grid, cudaStream_t st) {
-  constexpr int STAGES = q_stages(DUAL, BN);
-  constexpr size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * 2 * QATOM_A + 2 * BN * 128) + 1024;
+static int qgemm_go(const CUtensorMap& mx, const QGemmArgs& a, int n_groups, int grid, cudaStream_t st) {
+  constexpr int SB = SbBytes<T>::v;
+  constexpr int RS = q_raw_slots(SB, DUAL, BN);
+  constexpr int STAGES = RS > 0 ? q_stages_raw(SB, DUAL, BN) : q_stages(DUAL, BN);
+  constexpr size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * 2 * QATOM_A + 2 * BN * 128) + (size_t)RS * (DUAL ? 2 : 1) * QBM * SB + 1024;
+  CUtensorMap mw = mx, mw2 = mx;
+  if (RS > 0) {
+    cuuint64_t dims[3] = {(cuuint64_t)a.row_bytes, (cuuint64_t)a.N, (cuuint64_t)n_groups};
+    cuuint64_t str[2] = {(cuuint64_t)a.row_bytes, (cuuint64_t)a.group_bytes};
+    cuuint32_t box[3] = {(cuuint32_t)SB, QBM, 1};
+    int rc = make_map_u8(&mw, a.w, 3, dims, str, box);
+    if (rc) return rc;
+    if (DUAL) { rc = make_map_u8(&mw2, a.w2, 3, dims, str, box); if (rc) return rc; }
+  }
   static bool set = false;
   if (!set) {
     cudaFuncSetAttribute(qgemm_kernel<T, DUAL, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     set = true;
   }
-  return (int)launch(qgemm_kernel<T, DUAL, BN>, dim3(grid), dim3(QTHREADS), smem, st, mx, a);
+  return (int)launch(qgemm_kernel<T, DUAL, BN>, dim3(grid), dim3(QTHREADS), smem, st, mx, mw, mw2, a);
 }
 
 template <class T>
-static int qgemm_pick(bool dual, int bn, const CUtensorMap& mx, const QGemmArgs& a, int grid, cudaStream_t st) {
+static int qgemm_pick(bool dual, int bn, const CUtensorMap& mx, const QGemmArgs& a, int n_groups, int grid, cudaStream_t st) {
   if (dual) {
-    if (bn == 128) return qgemm_go<T, true, 128>(mx, a, grid, st);
-    if (bn == 32) return qgemm_go<T, true, 32>(mx, a, grid, st);
+    if (bn == 128) return qgemm_go<T, true, 128>(mx, a, n_groups, grid, st);
+    if (bn == 64) return qgemm_go<T, true, 64>(mx, a, n_groups, grid, st);
+    if (bn == 32) return qgemm_go<T, true, 32>(mx, a, n_groups, grid, st);
   } else {
-    if (bn == 128) return qgemm_go<T, false, 128>(mx, a, grid, st);
-    if (bn == 32) return qgemm_go<T, false, 32>(mx, a, grid, st);
+    if (bn == 128) return qgemm_go<T, false, 128>(mx, a, n_groups, grid, st);
+    if (bn == 64) return qgemm_go<T, false, 64>(mx, a, n_groups, grid, st);
+    if (bn == 32) return qgemm_go<T, false, 32>(mx, a, n_groups, grid, st);
   }
   return BL_ERR_SHAPE;
 }
@@ -409,14 +521,14 @@ int bl_qgemm_supports(int wtype) { return wtype == WT_Q4_K || wtype == WT_Q5_K |
 
 // C[dst_row[t] or t, n] = row_scale[t] * sum_k X[t, k] W[g][n, k] (+ resid), per token tile of the table.
 //   X [rows_x, K] bf16 (ldx elements); W, W2 [n_groups, N, row_bytes] resident blocks of type wtype;
-//   tiles: {group, row0, row_end, -} token tiles of at most tile_rows (32 or 128) rows; exactly one of c_f32 / c_bf16;
+//   tiles: {group, row0, row_end, -} token tiles of at most tile_rows (32, 64 or 128) rows; exactly one of c_f32 / c_bf16;
 //   W2 != null: output = silu(X W^T) * (X W2^T).  status: device word, set to 1 when a wait ran out.
 int bl_qgemm(const void* X, long ldx, long rows_x, const void* W, const void* W2, int wtype, int n_groups, int N, int K,
              const void* tiles, const int* n_tiles, int max_tiles, int tile_rows, float* c_f32, void* c_bf16, long ldc,
              const int* dst_row, const float* row_scale, const float* resid, long ldr, unsigned* status, int sm_count,
              cudaStream_t st) {
   BL_REQUIRE(K >= 256 && K % 256 == 0 && N >= 1 && rows_x >= 1 && n_groups >= 1 && max_tiles >= 1, BL_ERR_SHAPE);
-  BL_REQUIRE(tile_rows == 32 || tile_rows == 128, BL_ERR_SHAPE);
+  BL_REQUIRE(tile_rows == 32 || tile_rows == 64 || tile_rows == 128, BL_ERR_SHAPE);
   BL_REQUIRE(ldx % 8 == 0 && ((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)W2 & 15) == 0, BL_ERR_ALIGN);
   BL_REQUIRE((c_f32 != nullptr) != (c_bf16 != nullptr), BL_ERR_SHAPE);
   const long rb = resident_row_bytes(wtype, K);
@@ -440,10 +552,10 @@ int bl_qgemm(const void* X, long ldx, long rows_x, const void* W, const void* W2
   const int grid = (int)(tiles_total < sm_count ? tiles_total : sm_count);
   const bool dual = W2 != nullptr;
   switch (wtype) {
-    case WT_Q4_K: return qgemm_pick<Q4K>(dual, tile_rows, mx, a, grid, st);
-    case WT_Q5_K: return qgemm_pick<Q5K>(dual, tile_rows, mx, a, grid, st);
-    case WT_Q6_K: return qgemm_pick<Q6K>(dual, tile_rows, mx, a, grid, st);
-    case WT_Q8_0: return qgemm_pick<Q80>(dual, tile_rows, mx, a, grid, st);
+    case WT_Q4_K: return qgemm_pick<Q4K>(dual, tile_rows, mx, a, n_groups, grid, st);
+    case WT_Q5_K: return qgemm_pick<Q5K>(dual, tile_rows, mx, a, n_groups, grid, st);
+    case WT_Q6_K: return qgemm_pick<Q6K>(dual, tile_rows, mx, a, n_groups, grid, st);
+    case WT_Q8_0: return qgemm_pick<Q80>(dual, tile_rows, mx, a, n_groups, grid, st);
   }
   return BL_ERR_TYPE;
 }

@@ -5,7 +5,7 @@ CUDA events.
     python -m bloomery_b200.ops.kernel_bench NAME [replays] [context] [--no-staged] [--rows M]
 
 NAME: chain (the six launches of a layer in order) | qkv | attn | o | router | gateup | down | rope | flash |
-flash_mma | gemm | gemmdist | pflash | prope | mplan | qgu | qdown | bgu | bdown | mla | sampler | gap.  ``--no-staged`` runs the register-streaming kernels
+flash_mma | gemm | gemmdist | pflash | prope | mplan | qgu | qdown | qo | qq | bgu | bdown | mla | sampler | gap.  ``--no-staged`` runs the register-streaming kernels
 instead of the shared-memory staged ones.  It is also the small workload the ncu summaries under ``profiles/``
 were captured on.
 """
@@ -138,6 +138,14 @@ def main(argv=None) -> int:
                      so=torch.zeros(n, H, device=dev), wg=torch.zeros(E, I, H, device=dev, dtype=torch.bfloat16),
                      wu=torch.zeros(E, I, H, device=dev, dtype=torch.bfloat16), wd=torch.zeros(E, H, I, device=dev, dtype=torch.bfloat16))
         M = 1
+    if which in ("qo", "qq"):
+        # dense products of a decode batch of --rows tokens (one tile): o projection / q projection, weights quantised
+        from bloomery_b200.ops import gemm as G
+        tr = 64 if rows > 32 else 32
+        extra = dict(G=G, tt=G.TileTable.dense(rows, dev, tr), gst=torch.zeros(1, dtype=torch.int32, device=dev),
+                     xo=(torch.randn(rows, QR, device=dev) * 0.3).bfloat16(), xh=(torch.randn(rows, H, device=dev) * 0.3).bfloat16(),
+                     oo=torch.zeros(rows, H, device=dev), oq=torch.zeros(rows, QR, device=dev))
+        M = 1
     if which == "gemmdist":
         # the several-GPU epilogue on one GPU: o_proj-shaped product whose rows are added into two "owners" (both local here)
         from bloomery_b200.ops import gemm as G
@@ -216,6 +224,8 @@ def main(argv=None) -> int:
             if which == "pflash": X["G"].flash_prefill(X["pq"], X["pk"], X["pv"], X["po"], 0, X["gst"])
             if which == "prope": X["G"].qk_norm_rope_append_prefill(X["rqkv"], r_g, r_g, r_inv, 1e-6, 1.0 / math.sqrt(hd), hd, n_q, n_kv, ctx, X["rpos"], X["rseq"], table, n_pages, kc, vc, X["rqb"], fault, 0)
             if which == "mplan": X["G"].moe_plan(X["mids"], X["mwts"], E, X["mtt"], X["mpos_of"], X["mdst"], X["mscale"])
+            if which == "qo": X["G"].qgemm(X["xo"], l["o"], X["tt"], out_f32=X["oo"], status=X["gst"])
+            if which == "qq": X["G"].qgemm(X["xh"], l["q"], X["tt"], out_f32=X["oq"], status=X["gst"])
             if which == "qgu": X["G"].qgemm(X["xa"], l["g"], X["tt"], out_bf16=X["act"], W2=l["u"], status=X["gst"])
             if which == "qdown": X["G"].qgemm(X["act"], l["d"], X["tt"], out_f32=X["so"], dst_row=X["dst"], row_scale=X["scale"], status=X["gst"])
             if which == "bgu":

@@ -88,11 +88,16 @@ class BatchDecode:
         self.hist_cap = 1024
         self.hist = torch.zeros(self.hist_cap * R, **i32)
         self.status = torch.zeros(1, **i32)
-        self.dense_tiles: Dict[int, G.TileTable] = {m: G.TileTable.dense(m, dev, TILE) for m in BUCKETS if m <= R}
+        # dense products take the whole bucket as one token tile where a tile size exists for it
+        self.dense_tiles: Dict[int, G.TileTable] = {m: G.TileTable.dense(m, dev, 64 if m == 64 else TILE)
+                                                    for m in BUCKETS if m <= R}
         self.graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self.launches_per_step = 0
         self._scratch_w: Dict[str, torch.Tensor] = {}
         self._stream = torch.cuda.Stream(device=dev)
+        self._side = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
+        from .timing import PromptTiming
+        self.timing = PromptTiming()            # arm() it and call enqueue() eagerly for per-unit milliseconds of a pass
 
     # ---- products ---------------------------------------------------------------------------------------------
     def _mm(self, X, Wq, tiles, M, **kw):
@@ -123,11 +128,29 @@ class BatchDecode:
         q_scale = 1.0 / math.sqrt(s.head_dim)
         for il in range(s.n_layer):
             b = f"blk.{il}."
+            mark = self.timing.mark
+            mark(il, "ffn_tail")
             G.rmsnorm_bf16(x, w.f[b + "attn_norm.weight"], s.rms_eps, xn); n += 1
+            mark(il, "norm")
+            # the three projections are small grids (32 + 4 + 4 weight tiles on the 30 B shape): K and V run on side
+            # streams beside Q (parallel branches of the captured graph)
+            main = torch.cuda.current_stream(e.device)
+            fork = torch.cuda.Event()
+            fork.record(main)
+            joins = []
+            for side, name, lo, hi in ((self._side[0], "attn_k.weight", s.q_rows, s.q_rows + s.kv_rows),
+                                       (self._side[1], "attn_v.weight", s.q_rows + s.kv_rows, s.q_rows + 2 * s.kv_rows)):
+                side.wait_event(fork)
+                with torch.cuda.stream(side):
+                    n += self._mm(xn, w.q[b + name], tiles, M, out_f32=self.qkv[:M, lo:hi])
+                    ev = torch.cuda.Event()
+                    ev.record(side)
+                    joins.append(ev)
             n += self._mm(xn, w.q[b + "attn_q.weight"], tiles, M, out_f32=self.qkv[:M, :s.q_rows])
-            n += self._mm(xn, w.q[b + "attn_k.weight"], tiles, M, out_f32=self.qkv[:M, s.q_rows:s.q_rows + s.kv_rows])
-            n += self._mm(xn, w.q[b + "attn_v.weight"], tiles, M, out_f32=self.qkv[:M, s.q_rows + s.kv_rows:])
+            for ev in joins:
+                main.wait_event(ev)
             kvp = e.kv
+            mark(il, "qkv")
             K.qk_norm_rope_append(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"), e.inv_freq,
                                   s.rms_eps, q_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq, kvp.table,
                                   kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out, e.fault, il); n += 1
@@ -135,7 +158,9 @@ class BatchDecode:
                            s.n_q, s.n_kv, M, self.n_seg, e.slot_ctx, self.part_ml, self.part_acc, self.attn, self.attn_q,
                            self.attn_ds, e.fault, il); n += 2
             G.rmsnorm_bf16(self.attn[:M], None, s.rms_eps, self.attn_bf[:M]); n += 1
+            mark(il, "attention")
             n += self._mm(self.attn_bf[:M], w.q[b + "attn_output.weight"], tiles, M, out_f32=x, resid=x)
+            mark(il, "o_proj")
             if s.layer_is_moe(il):
                 E, k = s.n_expert, s.n_used
                 K.router(x, w.f[b + "ffn_norm.weight"], s.rms_eps, w.q[b + "ffn_gate_inp.weight"], M, self.logits_r, None,
@@ -145,12 +170,15 @@ class BatchDecode:
                 ids, wts = self.ids[:M], self.wts[:M]
                 G.moe_plan(ids, wts, E, self.moe_tiles, self.pos_of, self.dst_row, self.row_scale); n += 1
                 G.gather_rows_bf16(xn, self.dst_row, self.moe_tiles.offsets[E:E + 1], self.cap, k, self.Ap); n += 1
+                mark(il, "route_plan_gather")
                 qg, qu, qd = (w.q[b + f"ffn_{nm}_exps.weight"] for nm in ("gate", "up", "down"))
                 if not (G.qgemm_supports(qg) and qg.qtype == qu.qtype and G.qgemm_supports(qd)):
                     raise NotImplementedError(f"expert stacks of type {qg.qtype}/{qu.qtype}/{qd.qtype} in the batched pass")
                 G.qgemm(self.Ap, qg, self.moe_tiles, out_bf16=self.act, W2=qu, status=self.status); n += 1
+                mark(il, "gate_up")
                 G.qgemm(self.act, qd, self.moe_tiles, out_f32=self.slot_out, dst_row=self.dst_row, row_scale=self.row_scale,
                         status=self.status); n += 1
+                mark(il, "down")
                 G.moe_combine(self.slot_out, self.pos_of, M, k, x, x); n += 1
             else:
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn); n += 1

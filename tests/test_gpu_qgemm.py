@@ -26,7 +26,7 @@ def _weight(t, shape, K, seed):
 
 
 @pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0"])
-@pytest.mark.parametrize("rows,tile", [(300, 128), (45, 32), (128, 128)])
+@pytest.mark.parametrize("rows,tile", [(300, 128), (45, 32), (128, 128), (64, 64), (100, 64)])
 def test_dense_qgemm(t, rows, tile):
     from bloomery_b200.ops import gemm as G
     N, K = 200, 1024                                            # N not a multiple of 128: the last weight tile is ragged
@@ -41,7 +41,9 @@ def test_dense_qgemm(t, rows, tile):
     torch.cuda.synchronize()
     assert int(st) == 0
     ref = X.float() @ ref_w.bfloat16().float().T + R
-    assert torch.allclose(C, ref, rtol=1e-3, atol=1e-2), (C - ref).abs().max()
+    # tiles below 128 tokens use the short expander (scale and offset of a block rounded to bf16 before the FMA)
+    tol = dict(rtol=1e-3, atol=1e-2) if tile == 128 else dict(rtol=1e-2, atol=3e-2)
+    assert torch.allclose(C, ref, **tol), (C - ref).abs().max()
     C2 = torch.zeros_like(C)
     G.qgemm(X, qw, tiles, out_f32=C2, resid=R, status=st)
     assert torch.equal(C, C2)                                   # bit-identical rerun
