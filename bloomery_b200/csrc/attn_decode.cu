@@ -505,8 +505,10 @@ int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, co
                     int ctx_limit, float* part_ml, float* part_acc, float* out, int8_t* outq, float* outds,
                     unsigned* fault, int layer, cudaStream_t st) {
   BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
-  BL_REQUIRE(n_q % n_kv == 0 && n_q / n_kv <= 16, BL_ERR_SHAPE);
+  BL_REQUIRE(n_kv >= 1 && n_q >= 1 && n_q % n_kv == 0 && n_q / n_kv <= 16, BL_ERR_SHAPE);
   BL_REQUIRE(n_seg >= 1 && M >= 1, BL_ERR_SHAPE);
+  // the block table of a row holds max_pages pages of 64 positions: a context limit past that would index beyond it
+  BL_REQUIRE(max_pages >= 1 && (long)ctx_limit <= (long)max_pages * kPage, BL_ERR_SHAPE);
   const int G = n_q / n_kv;
   FlashArgs a{q, (const __half*)k_cache, (const __half*)v_cache, row_pos, row_seq, block_table, max_pages, n_pages,
               n_q, n_kv, M, n_seg, ctx_limit, part_ml, part_acc, fault, layer};

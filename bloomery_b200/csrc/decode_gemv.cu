@@ -215,6 +215,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvArgs a) {
         case WT_Q6_K: rows_q<Q6K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
         case WT_Q5_K: rows_q<Q5K, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
         case WT_Q8_0: rows_q<Q80, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
+        case WT_Q8_F32: rows_q<Q8F, MB, R, C>(a, s, r_lo, r_hi, col0, sq, sds, s_scale, between); break;
         default:
           if (FAM == 1) rows_f<MB, R>(a, s, r_lo, r_hi, col0, sx, s_scale, between);
       }

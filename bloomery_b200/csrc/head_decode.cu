@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(128) embed_rows_kernel(const EmbedArgs a) {
     case WT_Q5_K: embed_row_q<Q5K>(row, a.K, out, tid, 128); break;
     case WT_Q6_K: embed_row_q<Q6K>(row, a.K, out, tid, 128); break;
     case WT_Q8_0: embed_row_q<Q80>(row, a.K, out, tid, 128); break;
+    case WT_Q8_F32: embed_row_q<Q8F>(row, a.K, out, tid, 128); break;
     case WT_NVFP4: embed_row_q<NvFp4>(row, a.K, out, tid, 128); break;
     case WT_FP8_B128: embed_row_q<Fp8B128>(row, a.K, out, tid, 128); break;
     case WT_Q2_K: embed_row_q<Q2K>(row, a.K, out, tid, 128); break;

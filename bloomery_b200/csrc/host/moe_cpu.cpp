@@ -52,6 +52,7 @@ float dot_any(int wtype, const uint8_t* row, int K, const int8_t* xq, const floa
     case WT_Q5_K: return run(Q5K{});
     case WT_Q6_K: return run(Q6K{});
     case WT_Q8_0: return run(Q80{});
+    case WT_Q8_F32: return run(Q8F{});
     case WT_NVFP4: return run(NvFp4{});
     case WT_FP8_B128: return run(Fp8B128{});
     case WT_Q2_K: return run(Q2K{});

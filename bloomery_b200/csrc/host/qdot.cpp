@@ -43,6 +43,7 @@ float row_dot_any(int wtype, const uint8_t* row, int K, const int8_t* xq, const 
     case WT_Q5_K: return row_dot_scalar<Q5K>(row, K, xq, xds);
     case WT_Q6_K: return row_dot_scalar<Q6K>(row, K, xq, xds);
     case WT_Q8_0: return row_dot_scalar<Q80>(row, K, xq, xds);
+    case WT_Q8_F32: return row_dot_scalar<Q8F>(row, K, xq, xds);
     case WT_NVFP4: return row_dot_scalar<NvFp4>(row, K, xq, xds);
     case WT_FP8_B128: return row_dot_scalar<Fp8B128>(row, K, xq, xds);
     case WT_Q2_K: return row_dot_scalar<Q2K>(row, K, xq, xds);
@@ -123,6 +124,7 @@ int blh_decode_rows(int wtype, const uint8_t* w, int rows, int K, float* out) {
       case WT_Q5_K: row_decode<Q5K>(row, K, o); break;
       case WT_Q6_K: row_decode<Q6K>(row, K, o); break;
       case WT_Q8_0: row_decode<Q80>(row, K, o); break;
+      case WT_Q8_F32: row_decode<Q8F>(row, K, o); break;
       case WT_NVFP4: row_decode<NvFp4>(row, K, o); break;
       case WT_FP8_B128: row_decode<Fp8B128>(row, K, o); break;
       case WT_Q2_K: row_decode<Q2K>(row, K, o); break;

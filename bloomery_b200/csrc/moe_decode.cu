@@ -306,6 +306,7 @@ __global__ void __launch_bounds__(256, 2) gate_up_sel_kernel(const GateUpArgs a)
         case WT_Q5_K: gate_up_rows<Q5K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         case WT_Q6_K: gate_up_rows<Q6K>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         case WT_Q8_0: gate_up_rows<Q80>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
+        case WT_Q8_F32: gate_up_rows<Q8F>(g0, u0, rb, K, lane, xq, xds, gacc, uacc); break;
         default: gacc[0] = gacc[1] = __int_as_float(0x7fc00000); uacc[0] = uacc[1] = 0.f;
       }
     }
@@ -428,6 +429,7 @@ __global__ void __launch_bounds__(256, UPL <= 3 ? 2 : 1) down_combine_kernel(con
         case WT_Q6_K: y = down_row<Q6K, UPL>(a, m, d, lane, s_slot, s_w); break;
         case WT_Q5_K: y = down_row<Q5K, UPL>(a, m, d, lane, s_slot, s_w); break;
         case WT_Q8_0: y = down_row<Q80, UPL>(a, m, d, lane, s_slot, s_w); break;
+        case WT_Q8_F32: y = down_row<Q8F, UPL>(a, m, d, lane, s_slot, s_w); break;
         default: y = __int_as_float(0x7fc00000);
       }
     }
@@ -555,7 +557,7 @@ int bl_gate_up_sel(const int8_t* xq, const float* xds, const float* route_logits
                    const void* down, long down_expert_bytes, cudaStream_t st) {
   BL_REQUIRE(K % 256 == 0 && I % 32 == 0 && M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
   BL_REQUIRE(gtype == utype, BL_ERR_TYPE);
-  BL_REQUIRE(gtype == WT_Q4_K || gtype == WT_Q5_K || gtype == WT_Q6_K || gtype == WT_Q8_0 || is_plane_family(gtype), BL_ERR_TYPE);
+  BL_REQUIRE(gtype == WT_Q4_K || gtype == WT_Q5_K || gtype == WT_Q6_K || gtype == WT_Q8_0 || gtype == WT_Q8_F32 || is_plane_family(gtype), BL_ERR_TYPE);
   BL_REQUIRE(E % 4 == 0 && E <= kMaxExperts && n_group >= 1 && n_group <= 16 && E % n_group == 0, BL_ERR_LIMIT);
   GateUpArgs a{};
   a.xq = xq; a.xds = (const float2*)xds;
@@ -574,10 +576,10 @@ int bl_down_combine(const int8_t* actq, const float* actds, const int* ids, cons
                     const void* down, int dtype, int I, int H, int E, int n_used, int M, const float* resid,
                     long resid_stride, const float* extra, long extra_stride, float* out, long out_stride,
                     const void* push_desc, unsigned* fault, int layer, cudaStream_t st) {
-  BL_REQUIRE(I % 256 == 0 || ((dtype == WT_Q8_0 || (is_plane_family(dtype) && dtype != WT_FP8_B128 && dtype != WT_Q2_K && dtype != WT_Q3_K)) && I % 64 == 0) ||
+  BL_REQUIRE(I % 256 == 0 || ((dtype == WT_Q8_0 || dtype == WT_Q8_F32 || (is_plane_family(dtype) && dtype != WT_FP8_B128 && dtype != WT_Q2_K && dtype != WT_Q3_K)) && I % 64 == 0) ||
              (dtype == WT_FP8_B128 && I % 128 == 0), BL_ERR_SHAPE);
   BL_REQUIRE(M >= 1 && n_used >= 1 && n_used <= kMaxTopK, BL_ERR_SHAPE);
-  BL_REQUIRE(dtype == WT_Q4_K || dtype == WT_Q5_K || dtype == WT_Q6_K || dtype == WT_Q8_0 || is_plane_family(dtype), BL_ERR_TYPE);
+  BL_REQUIRE(dtype == WT_Q4_K || dtype == WT_Q5_K || dtype == WT_Q6_K || dtype == WT_Q8_0 || dtype == WT_Q8_F32 || is_plane_family(dtype), BL_ERR_TYPE);
   DownArgs a{actq, (const float2*)actds, ids, wts, slot_map, (const uint8_t*)down, dtype, I, H, E, n_used, M, resid,
              resid_stride, extra, extra_stride, out, out_stride, fault, layer, PushOut{}};
   if (push_desc) { a.push = *(const PushOut*)push_desc; BL_REQUIRE(a.push.n_ranks <= kMaxRanks && M <= kMaxRows, BL_ERR_SHAPE); }

@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(256) dequant_bf16_kernel(const uint8_t* w, int
     case WT_Q5_K: expand_units<Q5K>(w, rows, K, out, stage); break;
     case WT_Q6_K: expand_units<Q6K>(w, rows, K, out, stage); break;
     case WT_Q8_0: expand_units<Q80>(w, rows, K, out, stage); break;
+    case WT_Q8_F32: expand_units<Q8F>(w, rows, K, out, stage); break;
     case WT_NVFP4: expand_units<NvFp4>(w, rows, K, out, stage); break;
     case WT_FP8_B128: expand_units<Fp8B128>(w, rows, K, out, stage); break;
     case WT_Q2_K: expand_units<Q2K>(w, rows, K, out, stage); break;

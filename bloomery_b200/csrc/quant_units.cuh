@@ -41,7 +41,8 @@ enum WType : int {
   WT_Q6_K = 14,
   WT_BF16 = 30,
   WT_NVFP4 = 40,     // resident rows: K/2 code bytes, K/16 e4m3 scales, f32 tensor scale, pad to 16
-  WT_FP8_B128 = 41,  // resident rows: K e4m3 codes, K/128 f32 scales (the 128x128 block scale, per row), pad to 16
+  WT_FP8_B128 = 41,
+  WT_Q8_F32 = 50,    // resident rows: K int8 codes, K/32 f32 scales, pad to 16 (IQ4_NL / IQ4_XS / MXFP4 / IQ2_XXS files land here)  // resident rows: K e4m3 codes, K/128 f32 scales (the 128x128 block scale, per row), pad to 16
 };
 
 struct u32x4 { uint32_t x, y, z, w; };
@@ -385,6 +386,47 @@ struct Q80 {
 
 
 
+
+// ---------------------------------------------------------------------------------
+// Q8_F32 (resident only): int8 codes with one f32 scale per 32 values, value = code * scale.
+// The non-linear and grid types of the file format (IQ4_NL, IQ4_XS, MXFP4, IQ2_XXS) decode to exactly this form at
+// load: their codes are small integers from a code book and every 32 values share one scale, so no value changes.
+// ---------------------------------------------------------------------------------
+struct Q8F {
+  static constexpr int kType = WT_Q8_F32;
+  struct Regs { u32x4 q[4]; uint32_t d0, d1; };
+  static BL_HD long row_bytes(int K) { return (((long)K + K / 8) + 15) / 16 * 16; }
+  static BL_HD void load(const uint8_t* row, int u, int K, Regs& r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.q[i] = ld128(row + 64 * u + 16 * i);
+    r.d0 = ld32(row + K + 8 * u);
+    r.d1 = ld32(row + K + 8 * u + 4);
+  }
+  static BL_HD float scale(uint32_t bits) { float f; __builtin_memcpy(&f, &bits, 4); return f; }
+  static BL_HD float dot(const Regs& r, const ActUnit& a) {
+    const uint32_t w[16] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w,
+                            r.q[2].x, r.q[2].y, r.q[2].z, r.q[2].w, r.q[3].x, r.q[3].y, r.q[3].z, r.q[3].w};
+    int lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo = dot4(w[i], a.q[i], lo);
+      hi = dot4(w[8 + i], a.q[8 + i], hi);
+    }
+    return scale(r.d0) * a.d0 * (float)lo + scale(r.d1) * a.d1 * (float)hi;
+  }
+  static BL_HD void decode(const Regs& r, float* out) {
+    const float d0 = scale(r.d0), d1 = scale(r.d1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w[4] = {r.q[i].x, r.q[i].y, r.q[i].z, r.q[i].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          out[16 * i + 4 * k + b] = (i < 2 ? d0 : d1) * (float)(int8_t)((w[k] >> (8 * b)) & 0xFF);
+    }
+  }
+};
 
 // ---------------------------------------------------------------------------------
 // Q2_K: 84-byte file blocks re-laid to 96: qs[64] scales[16] d dmin pad[12].
@@ -749,6 +791,16 @@ template <> struct Unit<Q6K> {
   static BL_HD void decodeu(const Regs& r, int u, float* o) { Q6K::decode(r, u, o); }
   static BL_HD int pos(int u, int e) { return 256 * (u >> 2) + Q6K::value_index(u, e); }
 };
+template <> struct Unit<Q8F> {
+  using Regs = Q8F::Regs;
+  static BL_HD void loadu(const uint8_t* row, int u, int K, Regs& r) { Q8F::load(row, u, K, r); }
+  static BL_HD float dotu(const Regs& r, int u, const uint32_t* xq, const F2* xds) {
+    ActUnit a{xq + 16 * u, xds[2 * u].x, xds[2 * u].y, xds[2 * u + 1].x, xds[2 * u + 1].y};
+    return Q8F::dot(r, a);
+  }
+  static BL_HD void decodeu(const Regs& r, int, float* o) { Q8F::decode(r, o); }
+  static BL_HD int pos(int u, int e) { return 64 * u + e; }
+};
 template <> struct Unit<Q80> {
   using Regs = Q80::Regs;
   static BL_HD void loadu(const uint8_t* row, int u, int K, Regs& r) { Q80::load(row, u, K, r); }
@@ -840,7 +892,7 @@ template <class T> struct ActOf {
   }
   static BL_HD float dot(const typename Unit<T>::Regs& r, int u, const ActRegs& a) {
     ActUnit au{a.q, a.d[0], a.s[0], a.d[1], a.s[1]};
-    if constexpr (T::kType == WT_Q8_0 || T::kType == WT_Q4_0 || T::kType == WT_Q4_1 || T::kType == WT_Q5_0 ||
+    if constexpr (T::kType == WT_Q8_0 || T::kType == WT_Q8_F32 || T::kType == WT_Q4_0 || T::kType == WT_Q4_1 || T::kType == WT_Q5_0 ||
                   T::kType == WT_Q5_1) return T::dot(r, au);
     else return T::dot(r, u, au);
   }
@@ -899,6 +951,7 @@ BL_HD long resident_row_bytes(int wtype, int K) {
     case WT_Q5_K: return Q5K::row_bytes(K);
     case WT_Q6_K: return Q6K::row_bytes(K);
     case WT_Q8_0: return Q80::row_bytes(K);
+    case WT_Q8_F32: return Q8F::row_bytes(K);
     case WT_Q2_K: return Q2K::row_bytes(K);
     case WT_Q3_K: return Q3K::row_bytes(K);
     case WT_Q4_0: return Q40::row_bytes(K);

@@ -55,6 +55,7 @@ QTYPES: Dict[str, QType] = {
         QType("Q6_K", 14, 256, 210),
         QType("IQ2_XXS", 16, 256, 66),
         QType("IQ4_NL", 20, 32, 18),
+        QType("IQ4_XS", 23, 256, 136),
         QType("I8", 24, 1, 1),
         QType("I32", 26, 1, 4),
         QType("BF16", 30, 1, 2),
@@ -495,6 +496,221 @@ def _dq_plain(dtype):
     return dq
 
 
+# --------------------------------------------------------------------------------------
+# Non-linear 4-bit types (IQ4_NL, IQ4_XS), MXFP4 and the grid type IQ2_XXS.
+#   IQ4_NL   32 values: f16 d, 16 bytes of nibbles (value j low nibble of byte j, value j + 16 high); d * kvalues[q]
+#   IQ4_XS  256 values: f16 d, u16 scales_h, scales_l[4], qs[128]; 6-bit scale ls per 32, d * (ls - 32) * kvalues[q]
+#   MXFP4    32 values: E8M0 byte, 16 bytes of nibbles (same order); 2^(E-128) * kvalues_mxfp4[q]
+#   IQ2_XXS 256 values: f16 d, eight (idx u32, aux u32) pairs; per 8 values a grid byte and a 7-bit sign index, per 32
+#           a 4-bit scale s in aux[28:32]; d * (0.5 + s) * 0.25 * grid * sign
+# The encoders are plain nearest-code searches (fixtures and tests); the decoders are the file format.
+# --------------------------------------------------------------------------------------
+
+def _nibbles(qs: torch.Tensor) -> torch.Tensor:
+    """uint8 [..., 16] -> int64 codes [..., 32] in value order (low nibbles first)."""
+    q = qs.to(torch.int64)
+    return torch.cat([q & 0xF, q >> 4], -1)
+
+
+def _pack_nibbles(codes: torch.Tensor) -> torch.Tensor:
+    """int codes [..., 32] -> uint8 [..., 16]."""
+    return (codes[..., :16] | (codes[..., 16:] << 4)).to(torch.uint8)
+
+
+def _nearest_code(x: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """index of the table value nearest to every x."""
+    return (x[..., None] - table).abs().argmin(-1)
+
+
+def dequantize_iq4_nl(b: torch.Tensor, k: int) -> torch.Tensor:
+    from .iq_tables import KVALUES_IQ4NL
+    rows = b.shape[0]
+    blk = b.reshape(rows, k // 32, 18)
+    d = _bytes_f16(blk[..., 0:2])
+    lut = torch.tensor(KVALUES_IQ4NL, dtype=torch.float32, device=b.device)
+    return (lut[_nibbles(blk[..., 2:])] * d[..., None]).reshape(rows, k)
+
+
+def quantize_iq4_nl(w: torch.Tensor) -> torch.Tensor:
+    from .iq_tables import KVALUES_IQ4NL
+    rows, k = w.shape
+    x = w.float().reshape(rows, k // 32, 32)
+    lut = torch.tensor(KVALUES_IQ4NL, dtype=torch.float32, device=w.device)
+    # the value of largest magnitude lands on the table's end of the same sign
+    idx = x.abs().argmax(-1, keepdim=True)
+    mx = x.gather(-1, idx).squeeze(-1)
+    d = (mx / torch.where(mx < 0, lut[0], lut[15])).to(torch.float16).float()
+    inv = torch.where(d != 0, 1.0 / d, torch.zeros_like(d))
+    codes = _nearest_code(x * inv[..., None], lut)
+    out = torch.empty(rows, k // 32, 18, dtype=torch.uint8, device=w.device)
+    out[..., 0:2] = _f16_bytes(d)
+    out[..., 2:] = _pack_nibbles(codes)
+    return out.reshape(rows, -1)
+
+
+def _iq4_xs_scales(blk: torch.Tensor) -> torch.Tensor:
+    """6-bit sub-block scales [..., 8] of IQ4_XS blocks [..., 136]."""
+    sh = blk[..., 2].to(torch.int64) | (blk[..., 3].to(torch.int64) << 8)
+    sl = blk[..., 4:8].to(torch.int64)
+    ib = torch.arange(8, device=blk.device)
+    lo = (sl[..., ib // 2] >> (4 * (ib % 2))) & 0xF
+    hi = (sh[..., None] >> (2 * ib)) & 3
+    return lo | (hi << 4)
+
+
+def dequantize_iq4_xs(b: torch.Tensor, k: int) -> torch.Tensor:
+    from .iq_tables import KVALUES_IQ4NL
+    rows = b.shape[0]
+    blk = b.reshape(rows, k // 256, 136)
+    d = _bytes_f16(blk[..., 0:2])
+    dl = d[..., None] * (_iq4_xs_scales(blk) - 32).float()                     # [rows, nsb, 8]
+    lut = torch.tensor(KVALUES_IQ4NL, dtype=torch.float32, device=b.device)
+    v = lut[_nibbles(blk[..., 8:].reshape(rows, k // 256, 8, 16))]           # [rows, nsb, 8, 32]
+    return (v * dl[..., None]).reshape(rows, k)
+
+
+def quantize_iq4_xs(w: torch.Tensor) -> torch.Tensor:
+    from .iq_tables import KVALUES_IQ4NL
+    rows, k = w.shape
+    nsb = k // 256
+    x = w.float().reshape(rows, nsb, 8, 32)
+    lut = torch.tensor(KVALUES_IQ4NL, dtype=torch.float32, device=w.device)
+    idx = x.abs().argmax(-1, keepdim=True)
+    mx = x.gather(-1, idx).squeeze(-1)                                       # signed extreme of every sub-block
+    dl = mx / torch.where(mx < 0, lut[0], lut[15])                           # ideal sub-block scale (>= 0)
+    d = (dl.amax(-1) / 31.0).to(torch.float16).float()                       # ls - 32 in 0 .. 31
+    inv = torch.where(d != 0, 1.0 / d, torch.zeros_like(d))
+    ls = (torch.round(dl * inv[..., None]).clamp_(0, 31) + 32).to(torch.int64)
+    eff = d[..., None] * (ls - 32).float()
+    inv_eff = torch.where(eff != 0, 1.0 / eff, torch.zeros_like(eff))
+    codes = _nearest_code(x * inv_eff[..., None], lut)
+    out = torch.zeros(rows, nsb, 136, dtype=torch.uint8, device=w.device)
+    out[..., 0:2] = _f16_bytes(d)
+    sh = torch.zeros(rows, nsb, dtype=torch.int64, device=w.device)
+    for ib in range(8):
+        sh |= (ls[..., ib] >> 4) << (2 * ib)
+    out[..., 2] = (sh & 0xFF).to(torch.uint8)
+    out[..., 3] = (sh >> 8).to(torch.uint8)
+    out[..., 4:8] = ((ls[..., 0::2] & 0xF) | ((ls[..., 1::2] & 0xF) << 4)).to(torch.uint8)
+    out[..., 8:] = _pack_nibbles(codes).reshape(rows, nsb, 128)
+    return out.reshape(rows, -1)
+
+
+def dequantize_mxfp4(b: torch.Tensor, k: int) -> torch.Tensor:
+    from .iq_tables import KVALUES_MXFP4, e8m0_half
+    rows = b.shape[0]
+    blk = b.reshape(rows, k // 32, 17)
+    d = e8m0_half(blk[..., 0])
+    lut = torch.tensor(KVALUES_MXFP4, dtype=torch.float32, device=b.device)
+    return (lut[_nibbles(blk[..., 1:])] * d[..., None]).reshape(rows, k)
+
+
+def quantize_mxfp4(w: torch.Tensor) -> torch.Tensor:
+    from .iq_tables import KVALUES_MXFP4, e8m0_half
+    rows, k = w.shape
+    x = w.float().reshape(rows, k // 32, 32)
+    amax = x.abs().amax(-1).clamp_min(1e-30)
+    # smallest power-of-two block scale whose largest code (12 * half scale) covers the block
+    e = (torch.ceil(torch.log2(amax / 12.0)) + 128).clamp_(2, 254).to(torch.uint8)
+    d = e8m0_half(e)
+    lut = torch.tensor(KVALUES_MXFP4, dtype=torch.float32, device=w.device)
+    mag = _nearest_code((x / d[..., None]).abs(), lut[:8])
+    codes = mag | ((x < 0) & (mag > 0)).to(torch.int64) << 3
+    out = torch.empty(rows, k // 32, 17, dtype=torch.uint8, device=w.device)
+    out[..., 0] = e
+    out[..., 1:] = _pack_nibbles(codes)
+    return out.reshape(rows, -1)
+
+
+def _iq2_xxs_fields(b: torch.Tensor, k: int):
+    rows = b.shape[0]
+    blk = b.reshape(rows, k // 256, 66)
+    d = _bytes_f16(blk[..., 0:2])
+    words = blk[..., 2:].reshape(rows, k // 256, 8, 8).to(torch.int64)
+    gidx = words[..., 0:4]                                                   # [rows, nsb, 8, 4] grid entries
+    aux = words[..., 4] | (words[..., 5] << 8) | (words[..., 6] << 16) | (words[..., 7] << 24)
+    sidx = torch.stack([(aux >> (7 * l)) & 127 for l in range(4)], -1)      # [rows, nsb, 8, 4]
+    scale = aux >> 28                                                        # [rows, nsb, 8]
+    return d, gidx, sidx, scale
+
+
+def dequantize_iq2_xxs(b: torch.Tensor, k: int) -> torch.Tensor:
+    from .iq_tables import iq2_signs, iq2xxs_grid
+    rows = b.shape[0]
+    d, gidx, sidx, scale = _iq2_xxs_fields(b, k)
+    grid = iq2xxs_grid().to(b.device).float()
+    signs = iq2_signs().to(b.device)
+    db = d[..., None] * (0.5 + scale.float()) * 0.25                        # [rows, nsb, 8]
+    v = grid[gidx] * signs[sidx]                                             # [rows, nsb, 8, 4, 8]
+    return (v * db[..., None, None]).reshape(rows, k)
+
+
+def quantize_iq2_xxs(w: torch.Tensor) -> torch.Tensor:
+    """Nearest grid entry per eight values (exhaustive over the 256 entries), even sign parity by flipping the value
+    with the least at stake, one 4-bit scale per 32 values."""
+    from .iq_tables import iq2xxs_grid
+    rows, k = w.shape
+    nsb = k // 256
+    x = w.float().reshape(rows, nsb, 8, 4, 8)
+    grid = iq2xxs_grid().to(w.device).float()                                # [256, 8]
+    amax32 = x.abs().amax((-1, -2))                                          # [rows, nsb, 8]
+    # db * 43 covers the sub-block's largest magnitude; db = d * (0.5 + s) / 4 with s <= 15
+    db_ideal = amax32 / 43.0
+    d = (db_ideal.amax(-1) * 4.0 / 15.5).to(torch.float16).float()
+    inv_d = torch.where(d != 0, 1.0 / d, torch.zeros_like(d))
+    s = torch.round(db_ideal * 4.0 * inv_d[..., None] - 0.5).clamp_(0, 15).to(torch.int64)
+    db = d[..., None] * (0.5 + s.float()) * 0.25
+    inv_db = torch.where(db != 0, 1.0 / db, torch.zeros_like(db))
+    mag = x.abs() * inv_db[..., None, None]                                  # in grid units
+    err = ((mag[..., None, :] - grid) ** 2).sum(-1)                          # [rows, nsb, 8, 4, 256]
+    gidx = err.argmin(-1)
+    neg = x < 0
+    odd = neg.sum(-1) % 2 == 1
+    # an odd number of minus signs cannot be stored: flip the sign of the value whose product with its grid magnitude
+    # is smallest
+    stake = mag * grid[gidx]
+    flip = torch.nn.functional.one_hot(stake.argmin(-1), 8).bool() & odd[..., None]
+    neg = neg ^ flip
+    bits = (neg[..., :7].to(torch.int64) << torch.arange(7, device=w.device)).sum(-1)   # the eighth follows from parity
+    aux = (s << 28)
+    for l in range(4):
+        aux = aux | (bits[..., l] << (7 * l))
+    out = torch.zeros(rows, nsb, 66, dtype=torch.uint8, device=w.device)
+    out[..., 0:2] = _f16_bytes(d)
+    words = torch.zeros(rows, nsb, 8, 8, dtype=torch.int64, device=w.device)
+    words[..., 0:4] = gidx
+    for j in range(4):
+        words[..., 4 + j] = (aux >> (8 * j)) & 0xFF
+    out[..., 2:] = words.to(torch.uint8).reshape(rows, nsb, 64)
+    return out.reshape(rows, -1)
+
+
+def code_scale_form(b: torch.Tensor, qtype: str, k: int):
+    """Blocks of IQ4_NL / IQ4_XS / MXFP4 / IQ2_XXS as (int8 codes [rows, k], f32 scales [rows, k / 32]) with
+    value = code * scale exactly: every code of these types is a small integer and every 32 values share one scale."""
+    from .iq_tables import KVALUES_IQ4NL, KVALUES_MXFP4, e8m0_half, iq2_signs, iq2xxs_grid
+    rows = b.shape[0]
+    if qtype == "IQ4_NL":
+        blk = b.reshape(rows, k // 32, 18)
+        lut = torch.tensor(KVALUES_IQ4NL, dtype=torch.int8, device=b.device)
+        return lut[_nibbles(blk[..., 2:])].reshape(rows, k), _bytes_f16(blk[..., 0:2])
+    if qtype == "MXFP4":
+        blk = b.reshape(rows, k // 32, 17)
+        lut = torch.tensor(KVALUES_MXFP4, dtype=torch.int8, device=b.device)
+        return lut[_nibbles(blk[..., 1:])].reshape(rows, k), e8m0_half(blk[..., 0])
+    if qtype == "IQ4_XS":
+        blk = b.reshape(rows, k // 256, 136)
+        lut = torch.tensor(KVALUES_IQ4NL, dtype=torch.int8, device=b.device)
+        dl = _bytes_f16(blk[..., 0:2])[..., None] * (_iq4_xs_scales(blk) - 32).float()
+        return lut[_nibbles(blk[..., 8:].reshape(rows, k // 256, 8, 16))].reshape(rows, k), dl.reshape(rows, k // 32)
+    if qtype == "IQ2_XXS":
+        d, gidx, sidx, scale = _iq2_xxs_fields(b, k)
+        codes = (iq2xxs_grid().to(b.device).float()[gidx] * iq2_signs().to(b.device)[sidx]).to(torch.int8)
+        db = d[..., None] * (0.5 + scale.float()) * 0.25
+        return codes.reshape(rows, k), db.reshape(rows, k // 32)
+    raise ValueError(f"{qtype} has no code * scale form")
+
+
 QUANTIZE: Dict[str, Callable[[torch.Tensor], torch.Tensor]] = {
     "F32": _q_plain(torch.float32),
     "F16": _q_plain(torch.float16),
@@ -509,6 +725,10 @@ QUANTIZE: Dict[str, Callable[[torch.Tensor], torch.Tensor]] = {
     "Q4_K": quantize_q4_k,
     "Q5_K": quantize_q5_k,
     "Q6_K": quantize_q6_k,
+    "IQ4_NL": quantize_iq4_nl,
+    "IQ4_XS": quantize_iq4_xs,
+    "MXFP4": quantize_mxfp4,
+    "IQ2_XXS": quantize_iq2_xxs,
 }
 
 DEQUANTIZE: Dict[str, Callable[[torch.Tensor, int], torch.Tensor]] = {
@@ -525,6 +745,10 @@ DEQUANTIZE: Dict[str, Callable[[torch.Tensor, int], torch.Tensor]] = {
     "Q4_K": dequantize_q4_k,
     "Q5_K": dequantize_q5_k,
     "Q6_K": dequantize_q6_k,
+    "IQ4_NL": dequantize_iq4_nl,
+    "IQ4_XS": dequantize_iq4_xs,
+    "MXFP4": dequantize_mxfp4,
+    "IQ2_XXS": dequantize_iq2_xxs,
 }
 
 

@@ -14,6 +14,9 @@ Values are never re-quantised on load; some block types are only re-laid so that
                       (_1 types), padded to 16 bytes; nibble order inside a block as in the file
   F32 / F16 / BF16    unchanged
   NVFP4, FP8_B128     rows built from checkpoint planes by ``formats/planes.py``
+  IQ4_NL, IQ4_XS,     decoded at load to Q8_F32 rows: K int8 codes, then K/32 f32 scales, padded to 16.  Every code of
+  MXFP4, IQ2_XXS      these types is a small integer of a code book and every 32 values share one scale, so the rows
+                      hold the same values (9 bits per weight on the card whatever the file's rate)
 
 Works on CPU and CUDA tensors (the repack of a 30 B-parameter model runs on the card).
 """
@@ -26,14 +29,23 @@ import torch
 from .quant import QTYPES
 
 # weight-type ids shared with csrc/quant_units.cuh (equal to the ggml ids)
-WT = {"F32": 0, "F16": 1, "Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30, "NVFP4": 40, "FP8_B128": 41}
-INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q2_K", "Q3_K", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "NVFP4", "FP8_B128")      # dotted against q8 activations
+WT = {"F32": 0, "F16": 1, "Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30, "NVFP4": 40, "FP8_B128": 41, "Q8_F32": 50}
+INT_DOT_TYPES = ("Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q2_K", "Q3_K", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "NVFP4", "FP8_B128", "Q8_F32")      # dotted against q8 activations
 PLANE_TYPES = ("NVFP4", "FP8_B128")
 FLOAT_TYPES = ("F32", "F16", "BF16")
 
 
+# file types that are decoded to another resident type at load (value-preserving)
+LOAD_AS = {"IQ4_NL": "Q8_F32", "IQ4_XS": "Q8_F32", "MXFP4": "Q8_F32", "IQ2_XXS": "Q8_F32"}
+
+
 class UnsupportedType(ValueError):
     pass
+
+
+def resident_type(file_qtype: str) -> str:
+    """The type of the rows that :func:`to_resident` makes of a file type."""
+    return LOAD_AS.get(file_qtype, file_qtype)
 
 
 _Q32 = {"Q4_0": (4, False), "Q4_1": (4, True), "Q5_0": (5, False), "Q5_1": (5, True)}     # bits, has a min
@@ -59,6 +71,8 @@ def resident_row_bytes(qtype: str, k: int) -> int:
         return k // 256 * 224
     if qtype == "Q8_0":
         return (k + k // 16 + 15) // 16 * 16
+    if qtype == "Q8_F32":
+        return (k + k // 8 + 15) // 16 * 16
     if qtype == "Q2_K":
         return k // 256 * 96
     if qtype == "Q3_K":
@@ -100,6 +114,13 @@ def to_resident(raw: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
         raise ValueError(f"{qtype}: row of {raw.shape[1]} bytes does not match k={k}")
     if qtype in ("Q4_K", "Q5_K", "F32", "F16", "BF16"):
         return raw.contiguous()
+    if qtype in LOAD_AS:
+        from .quant import code_scale_form
+        codes, scales = code_scale_form(raw, qtype, k)
+        out = torch.zeros(rows, resident_row_bytes("Q8_F32", k), dtype=torch.uint8, device=raw.device)
+        out[:, :k] = codes.view(torch.uint8)
+        out[:, k:k + k // 8] = scales.contiguous().view(torch.uint8).reshape(rows, k // 8)
+        return out
     if qtype == "Q6_K":
         nsb = k // 256
         out = torch.zeros(rows, nsb, 224, dtype=torch.uint8, device=raw.device)
@@ -144,6 +165,14 @@ def to_resident(raw: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
         out[:, k:k + 2 * nb] = blk[..., :2].reshape(rows, 2 * nb)
         return out
     raise UnsupportedType(f"no resident layout for block type {qtype}")
+
+
+def decode_q8_f32(res: torch.Tensor, k: int) -> torch.Tensor:
+    """f32 values of Q8_F32 rows (code * scale, exact)."""
+    rows = res.shape[0]
+    codes = res[:, :k].contiguous().view(torch.int8).float().reshape(rows, k // 32, 32)
+    scales = res[:, k:k + k // 8].contiguous().view(torch.float32).reshape(rows, k // 32)
+    return (codes * scales[..., None]).reshape(rows, k)
 
 
 def from_resident(res: torch.Tensor, qtype: str, k: int) -> torch.Tensor:

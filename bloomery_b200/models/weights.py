@@ -20,7 +20,8 @@ import torch
 
 from ..formats import quant
 from ..formats.gguf import Gguf, GgufWriter
-from ..formats.resident import FLOAT_TYPES, INT_DOT_TYPES, PLANE_TYPES, UnsupportedType, quantize_resident, to_resident
+from ..formats.resident import (FLOAT_TYPES, INT_DOT_TYPES, PLANE_TYPES, UnsupportedType, quantize_resident, resident_type,
+                                to_resident)
 from ..ops.decode import QWeight
 from .spec import ModelSpec
 
@@ -195,13 +196,13 @@ class Weights:
         if name.endswith(("attn_k_b.weight", "attn_v_b.weight", "attn_kv_b.weight")):
             self._add_mla_heads(name, shape, qtype, raw)
             return
-        if qtype not in INT_DOT_TYPES and qtype not in FLOAT_TYPES:
+        if resident_type(qtype) not in INT_DOT_TYPES and qtype not in FLOAT_TYPES:
             raise UnsupportedType(f"{name}: block type {qtype} has no kernel in this build")
         flat = raw.reshape(-1, raw.shape[-1])
         res = flat.contiguous() if qtype in PLANE_TYPES else to_resident(flat, qtype, k)
         if len(shape) == 3:
             res = res.reshape(shape[0], shape[1], -1)
-        self.q[name] = QWeight(res, qtype, k)
+        self.q[name] = QWeight(res, resident_type(qtype), k)
         self.n_bytes += res.numel()
 
     def _add_mla_heads(self, name: str, shape, qtype: str, raw: torch.Tensor) -> None:
@@ -266,6 +267,9 @@ class Weights:
         if qw.qtype in PLANE_TYPES:
             from ..formats.planes import resident_dequantize
             return resident_dequantize(flat, qw.qtype, qw.k).reshape(*qw.data.shape[:-1], qw.k)
+        if qw.qtype == "Q8_F32":
+            from ..formats.resident import decode_q8_f32
+            return decode_q8_f32(flat, qw.k).reshape(*qw.data.shape[:-1], qw.k)
         raw = from_resident(flat, qw.qtype, qw.k)
         out = quant.dequantize(raw, qw.qtype, qw.k)
         return out.reshape(*qw.data.shape[:-1], qw.k)

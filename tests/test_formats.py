@@ -12,7 +12,8 @@ from bloomery_b200.ops import host_ops as H
 
 ALL = list(Q.QUANTIZE)
 BAND = {"F32": 1e-7, "F16": 1e-3, "BF16": 8e-3, "Q8_0": 8e-3, "Q6_K": 3e-2, "Q5_K": 5e-2, "Q5_1": 5e-2, "Q5_0": 8e-2,
-        "Q4_K": 1e-1, "Q4_1": 1e-1, "Q4_0": 1.5e-1, "Q3_K": 3e-1, "Q2_K": 5e-1}
+        "Q4_K": 1e-1, "Q4_1": 1e-1, "Q4_0": 1.5e-1, "Q3_K": 3e-1, "Q2_K": 5e-1, "IQ4_NL": 1.5e-1, "IQ4_XS": 1.5e-1,
+        "MXFP4": 2.5e-1, "IQ2_XXS": 6e-1}
 
 
 @pytest.mark.parametrize("t", ALL)
@@ -146,6 +147,70 @@ def test_resident_roundtrip_and_host_units(t):
     out = H.gemv(res, t, K, codes, ds)
     assert ((out - ref).abs().max() / ref.abs().max()).item() < 1e-5
     assert torch.equal(out, H.gemv(res, t, K, codes, ds))       # bit-identical rerun
+
+
+def _scalar_decode(raw: bytes, t: str):
+    """One block decoded value by value in plain Python integers and floats, straight from the format's definition."""
+    import struct
+    from bloomery_b200.formats.iq_tables import KVALUES_IQ4NL, KVALUES_MXFP4, iq2xxs_grid
+    half = lambda b: struct.unpack("<e", bytes(b))[0]
+    out = []
+    if t == "IQ4_NL":
+        d = half(raw[0:2])
+        out = [d * KVALUES_IQ4NL[raw[2 + j] & 15] for j in range(16)] + [d * KVALUES_IQ4NL[raw[2 + j] >> 4] for j in range(16)]
+    elif t == "MXFP4":
+        e = raw[0]
+        d = struct.unpack("<f", struct.pack("<I", (e - 1) << 23 if e >= 2 else (0x00400000 if e == 1 else 0x00200000)))[0]
+        out = [d * KVALUES_MXFP4[raw[1 + j] & 15] for j in range(16)] + [d * KVALUES_MXFP4[raw[1 + j] >> 4] for j in range(16)]
+    elif t == "IQ4_XS":
+        d = half(raw[0:2])
+        sh = raw[2] | raw[3] << 8
+        for ib in range(8):
+            ls = ((raw[4 + ib // 2] >> (4 * (ib % 2))) & 15) | (((sh >> (2 * ib)) & 3) << 4)
+            dl = d * (ls - 32)
+            q = raw[8 + 16 * ib:8 + 16 * ib + 16]
+            out += [dl * KVALUES_IQ4NL[b & 15] for b in q] + [dl * KVALUES_IQ4NL[b >> 4] for b in q]
+    elif t == "IQ2_XXS":
+        d = half(raw[0:2])
+        grid = iq2xxs_grid().tolist()
+        for ib in range(8):
+            w = raw[2 + 8 * ib:2 + 8 * ib + 8]
+            aux = w[4] | w[5] << 8 | w[6] << 16 | w[7] << 24
+            db = d * (0.5 + (aux >> 28)) * 0.25
+            for l in range(4):
+                s7 = (aux >> (7 * l)) & 127
+                signs = s7 | ((bin(s7).count("1") & 1) << 7)
+                out += [db * grid[w[l]][j] * (-1.0 if signs >> j & 1 else 1.0) for j in range(8)]
+    return out
+
+
+@pytest.mark.parametrize("t", ["IQ4_NL", "IQ4_XS", "MXFP4", "IQ2_XXS"])
+def test_codebook_types_decode_and_resident_form(t):
+    """Random block bytes (every code and scale the format can hold) decode as the format says, value by value; the
+    int8-code + f32-scale rows they are loaded as hold exactly those values; the host units dot them."""
+    from bloomery_b200.formats.resident import decode_q8_f32, resident_type
+    g = torch.Generator().manual_seed(11)
+    K = 512
+    qt = Q.QTYPES[t]
+    raw = torch.randint(0, 256, (5, qt.row_bytes(K)), dtype=torch.uint8, generator=g)
+    blk = raw.reshape(5, K // qt.block_values, qt.block_bytes)
+    if t == "MXFP4":
+        blk[..., 0] = torch.randint(100, 140, blk[..., 0].shape, generator=g).to(torch.uint8)      # scales in f32 range
+    else:
+        blk[..., 0:2] = Q._f16_bytes(torch.rand(blk.shape[:-1], generator=g) * 0.01 + 1e-3)          # a finite f16 d
+    raw = blk.reshape(5, -1).contiguous()
+    got = Q.dequantize(raw, t, K)
+    want = torch.tensor([sum((_scalar_decode(bytes(b.tolist()), t) for b in row), []) for row in blk], dtype=torch.float32)
+    assert torch.equal(got, want)
+    res = to_resident(raw, t, K)
+    assert resident_type(t) == "Q8_F32" and res.shape[1] == resident_row_bytes("Q8_F32", K)
+    assert torch.equal(decode_q8_f32(res, K), got)
+    assert torch.equal(H.decode_rows(res, "Q8_F32", K), got)
+    x = torch.randn(3, K)
+    codes, ds = H.act_q8(x)
+    ref = (Q.dequantize_act_q8(codes, ds).double() @ got.double().T).float()
+    out = H.gemv(res, "Q8_F32", K, codes, ds)
+    assert ((out - ref).abs().max() / ref.abs().max()).item() < 1e-5
 
 
 @pytest.mark.parametrize("t", ["NVFP4", "FP8_B128"])

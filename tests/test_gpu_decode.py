@@ -19,10 +19,12 @@ def _qw(w, t):
     res = res.to(DEV)
     if w.dim() == 3:
         res = res.reshape(w.shape[0], w.shape[1], -1)
-    return QWeight(res, t, w.shape[-1]), wd.reshape(w.shape)
+    from bloomery_b200.formats.resident import resident_type
+    return QWeight(res, resident_type(t), w.shape[-1]), wd.reshape(w.shape)
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "NVFP4", "FP8_B128", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "NVFP4", "FP8_B128", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K",
+                               "IQ4_NL", "IQ4_XS", "MXFP4", "IQ2_XXS"])
 @pytest.mark.parametrize("M", [1, 3, 8])
 def test_gemv_norm_matches_fp32(t, M):
     from bloomery_b200.ops import decode as K
@@ -166,7 +168,8 @@ def test_gate_up_routes_like_route_rows():
 
 
 @pytest.mark.parametrize("gt,dt", [("Q4_K", "Q4_K"), ("Q4_K", "Q6_K"), ("Q8_0", "Q8_0"), ("Q5_K", "Q5_K"), ("NVFP4", "NVFP4"),
-                                   ("FP8_B128", "FP8_B128"), ("Q4_0", "Q5_0"), ("Q5_1", "Q4_1"), ("Q2_K", "Q3_K")])
+                                   ("FP8_B128", "FP8_B128"), ("Q4_0", "Q5_0"), ("Q5_1", "Q4_1"), ("Q2_K", "Q3_K"),
+                                   ("IQ4_XS", "IQ4_NL"), ("MXFP4", "MXFP4"), ("IQ2_XXS", "Q4_K")])
 def test_moe_sel_chain(gt, dt):
     from bloomery_b200.ops import decode as K
     torch.manual_seed(4)
@@ -291,7 +294,7 @@ def test_rope_append_flash_decode(head, n_q, n_kv):
     assert torch.isnan(out[1]).all() and not torch.isnan(out[0]).any()
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q6_K", "Q8_0", "F16", "NVFP4", "FP8_B128", "Q4_0", "Q5_1"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q6_K", "Q8_0", "F16", "NVFP4", "FP8_B128", "Q4_0", "Q5_1", "IQ4_XS", "IQ2_XXS"])
 def test_embed_and_argmax(t):
     from bloomery_b200.ops import decode as K
     from bloomery_b200.ops.decode import QWeight
@@ -356,6 +359,23 @@ def test_engine_matches_cpu_oracle_tokens():
         tok = eng.step([(0, tok, len(prompt) + i)])[0]
         single.append(tok)
     assert chain == single
+
+
+@pytest.mark.parametrize("mix", ["IQ4_XS", "MXFP4", "IQ2_XXS"])
+def test_engine_on_codebook_types_matches_cpu_oracle(mix):
+    """A model whose matrices are all of a code-book block type (loaded as int8 codes + f32 scales): logits against
+    the CPU oracle over the same decoded weights."""
+    from bloomery_b200.models.cpu_ref import CpuModel
+    spec, eng, wc = _tiny_engine(mix=mix)
+    assert eng.w.q["blk.0.attn_q.weight"].qtype == "Q8_F32"
+    cpu = CpuModel(wc)
+    g = torch.Generator().manual_seed(13)
+    prompt = torch.randint(0, spec.vocab, (11,), generator=g).tolist()
+    ref = cpu.forward(torch.tensor(prompt))
+    eng.prefill(0, prompt, gemm=False)
+    n_last = len(prompt) % 8 or 8
+    err = ((eng.logits[:n_last].cpu() - ref[-n_last:]).abs().max() / ref[-n_last:].abs().max()).item()
+    assert err < 2e-2, err
 
 
 def test_engine_logits_band_and_graph_equals_eager():

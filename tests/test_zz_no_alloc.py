@@ -64,7 +64,9 @@ def test_static_scratch_entry_matches_ordinary_entry_twice():
     lib = cuda()
     assert hasattr(lib, "bl_flash_decode_static")
     # two different problems back to back: the second one runs over the first one's leftovers
-    for case in (_case(1, [700, 65, 1]), _case(2, [3, 1000, 512, 129], n_seg=7)):
+    # ... and a head size of 64 with 12 query heads per key/value head (the two-pass form of the segment kernel)
+    for case in (_case(1, [700, 65, 1]), _case(2, [3, 1000, 512, 129], n_seg=7),
+                 _case(4, [900, 64, 17], head=64, n_q=24, n_kv=2, n_seg=9)):
         rc, out, outq, outds = _run_static(lib, case)
         assert rc == 0
         ref_out, ref_q, ref_ds = _run_ordinary(case)
