@@ -74,6 +74,46 @@ class ClockSampler(threading.Thread):
                 "samples": len(sm), "power_w_max": max(float(s[2]) for s in self.samples)}
 
 
+def cpu_arm(args) -> int:
+    """``--cpu``: the tiny Qwen3-MoE shape on the host engine (quantised weights, q8 activation sites, the C++ expert
+    leg's arithmetic), 64 seeded prompt ids then 32 greedy tokens; wall-clock, since no device is involved."""
+    import torch
+    from bloomery_b200.models.cpu_ref import CpuModel, greedy_pick
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    spec = tiny_qwen3moe()
+    w = Weights.from_items(spec, synth_tensors(spec, "cpu", seed=0, mix="Q4_K_M"), "cpu")
+    m = CpuModel(w)
+    g = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, spec.vocab, (64,), generator=g)
+    n_gen = 32
+    best = None
+    for _ in range(max(1, min(args.warmup, 3))):
+        m.reset()
+        t0 = time.perf_counter()
+        tok = greedy_pick(m.forward(prompt)[-1])
+        t1 = time.perf_counter()
+        out = [tok]
+        for _ in range(n_gen - 1):
+            tok = greedy_pick(m.forward(torch.tensor([tok]))[0])
+            out.append(tok)
+        t2 = time.perf_counter()
+        run = (t1 - t0, t2 - t1, out)
+        if best is None or run[1] < best[1]:
+            best = run
+    ttft, dec, out = best
+    tok_s = (n_gen - 1) / dec
+    print(json.dumps({
+        "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": 0, "steps": n_gen - 1, "warmup": 1,
+        "ms_per_step": dec / (n_gen - 1) * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "q4_k_m weights, q8 activation sites, fp32 accumulate (host)", "data": "synthetic: seeded random ids, N(0,0.02) weights",
+        "config": {"model": spec.name, "global_batch": 1, "seq_len": 64 + n_gen, "prompt_tokens": 64, "parallelism": "cpu",
+                   "threads": torch.get_num_threads()},
+        "ttft_ms_prompt": ttft * 1e3, "prefill_tok_s": 64 / ttft, "tokens": out[:8], "gpu_launches": 0,
+        "e2e": {"value": n_gen / (ttft + dec), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+    return 0
+
+
 def batch_arm(args, spec, w, dev, local, steps, warm, t_load) -> int:
     """``--batch B``: B sequences, one token each per pass, through the batched tensor-core decode."""
     import torch
@@ -181,11 +221,15 @@ def main() -> int:
                     help="register-streaming decode kernels instead of the shared-memory staged ones")
     ap.add_argument("--batch", type=int, default=1,
                     help="sequences decoded together (16..64: the batched tensor-core pass; the value is the total of all sequences)")
+    ap.add_argument("--cpu", action="store_true",
+                    help="the CPU configuration: tiny Qwen3-MoE (Q4_K_M), 64-id prompt, 32 greedy tokens on the host engine, no GPU")
     ap.add_argument("--nccl-baseline", dest="nccl_baseline", action="store_true",
                     help="N > 1: do the per-layer reductions with NCCL all_reduce instead of the fused kernels")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.cpu:
+        return cpu_arm(args)
 
     import torch
     rank = int(os.environ.get("RANK", "0"))

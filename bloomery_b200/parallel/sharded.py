@@ -1,8 +1,10 @@
 """Tensor-parallel attention + expert-parallel MoE decode over the GPUs of one node.
 
 Each rank holds ``n_q / N`` query heads with their KV head(s), the matching K-slice of
-o_proj, and ``E / N`` routed experts; embeddings, norms, router and the output head are
-replicated (the reference's TP ranks split heads / FFN width and replicate router, norms
+o_proj, ``E / N`` routed experts and a ``1 / N`` slice of the width of every dense FFN and
+shared expert (rows of gate / up, columns of down); with latent attention the low-rank
+projections and the latent cache are replicated and the per-head products (q_b, k_b, v_b)
+follow the heads.  Embeddings, norms, router and the output head are replicated (the reference's TP ranks split heads / FFN width and replicate router, norms
 and embedding the same way: ``crates/gpu-glm5next/src/tp/mod.rs:5-12``).
 
 Every layer needs two reductions of the residual update (after o_proj, after the
@@ -40,23 +42,42 @@ def shard_items(items: Iterator[TensorItem], spec: ModelSpec, rank: int, world: 
         raise ValueError(f"{world} ranks do not divide {spec.n_q} heads / {spec.n_expert} experts")
     hd = spec.head_dim
     q_lo, q_hi = rank * spec.q_rows // world, (rank + 1) * spec.q_rows // world
+    # columns of o_proj: the heads' value rows (head_dim wide, or v_dim with latent attention)
+    o_w = spec.n_q * (spec.v_dim if spec.mla else hd)
+    o_lo, o_hi = rank * o_w // world, (rank + 1) * o_w // world
+    h_lo, h_hi = rank * spec.n_q // world, (rank + 1) * spec.n_q // world
+
+    def k_slice(name, shape, qtype, raw, lo, hi):
+        qt = QTYPES[qtype]
+        bv, bb = qt.block_values, qt.block_bytes
+        if lo % bv or hi % bv:
+            raise ValueError(f"{name}: a K-slice of {hi - lo} columns does not align to {bv}-value blocks")
+        blk = raw.reshape(shape[0], shape[1] // bv, bb)[:, lo // bv:hi // bv]
+        return name, (shape[0], hi - lo), qtype, blk.reshape(shape[0], -1).contiguous()
+
+    def row_slice(name, shape, qtype, raw):
+        lo, hi = rank * shape[0] // world, (rank + 1) * shape[0] // world
+        return name, (hi - lo, shape[1]), qtype, raw[lo:hi]
+
     if spec.n_kv >= world:
         kv_lo, kv_hi = rank * spec.kv_rows // world, (rank + 1) * spec.kv_rows // world
     else:
         kvh = rank // (world // spec.n_kv)
         kv_lo, kv_hi = kvh * hd, (kvh + 1) * hd
     for name, shape, qtype, raw in items:
-        qt = QTYPES[qtype]
-        if name.endswith("attn_q.weight"):
+        if name.endswith("attn_q.weight") or name.endswith("attn_q_b.weight"):
             yield name, (q_hi - q_lo, shape[1]), qtype, raw[q_lo:q_hi]
         elif name.endswith("attn_k.weight") or name.endswith("attn_v.weight"):
             yield name, (kv_hi - kv_lo, shape[1]), qtype, raw[kv_lo:kv_hi]
+        elif name.endswith("attn_k_b.weight") or name.endswith("attn_v_b.weight"):
+            per = shape[1]                                    # [head][rows per head][latent] stored as rows
+            yield name, (h_hi - h_lo, shape[1], shape[2]), qtype, raw.reshape(shape[0] * per, -1)[h_lo * per:h_hi * per]
         elif name.endswith("attn_output.weight"):
-            bv, bb = qt.block_values, qt.block_bytes
-            if q_lo % bv or q_hi % bv:
-                raise ValueError(f"{name}: a K-slice of {q_hi - q_lo} columns does not align to {bv}-value blocks")
-            blk = raw.reshape(shape[0], shape[1] // bv, bb)[:, q_lo // bv:q_hi // bv]
-            yield name, (shape[0], q_hi - q_lo), qtype, blk.reshape(shape[0], -1).contiguous()
+            yield k_slice(name, shape, qtype, raw, o_lo, o_hi)
+        elif name.endswith(("ffn_gate.weight", "ffn_up.weight", "ffn_gate_shexp.weight", "ffn_up_shexp.weight")):
+            yield row_slice(name, shape, qtype, raw)
+        elif name.endswith(("ffn_down.weight", "ffn_down_shexp.weight")):
+            yield k_slice(name, shape, qtype, raw, rank * shape[1] // world, (rank + 1) * shape[1] // world)
         elif "_exps.weight" in name:
             e_lo, e_hi = rank * shape[0] // world, (rank + 1) * shape[0] // world
             yield name, (e_hi - e_lo, shape[1], shape[2]), qtype, raw[e_lo * shape[1]:e_hi * shape[1]]
@@ -68,6 +89,10 @@ def local_spec(spec: ModelSpec, world: int) -> ModelSpec:
     s = dataclasses.replace(spec)
     s.n_q = spec.n_q // world
     s.n_kv = max(1, spec.n_kv // world)
+    if spec.dense_inter:
+        s.dense_inter = spec.dense_inter // world
+    if spec.n_shared:
+        s.shared_inter = spec.shared_inter // world
     return s
 
 
@@ -131,11 +156,35 @@ class ShardedEngine(DecodeEngine):
             red = None
             if fused and pending is not None:
                 red = ar.reduce(pending[0], pending[1], xb[cur ^ 1], self.fault, il)
-            add(K.gemv, [w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
-                x=xb[cur], gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, red=red, fault=self.fault, layer=il)
-            if red is not None:
-                cur ^= 1
-            if K.staged_part("attn"):
+            if s.mla:
+                # latent attention: the low-rank products and the latent append are the same on every rank, the per-head
+                # products run on this rank's heads
+                first = w.q[b + "attn_q_a.weight"] if s.q_lora else w.q[b + "attn_q.weight"]
+                add(K.gemv, [first, w.q[b + "attn_kv_a_mqa.weight"]], M, self.qkv, x=xb[cur],
+                    gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, red=red, fault=self.fault, layer=il)
+                if red is not None:
+                    cur ^= 1
+                add(K.mla_kv_append, self.qkv[:, self.qa_w:], w.f[b + "attn_kv_a_norm.weight"], self.inv_freq, s.rms_eps, M,
+                    self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il], self.fault, il)
+                if s.q_lora:
+                    add(K.gemv, [w.q[b + "attn_q_b.weight"]], M, self.q_full, x=self.qkv[:, :s.q_lora],
+                        gain=w.f[b + "attn_q_a_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il)
+                    q = self.q_full
+                else:
+                    q = self.qkv[:, :self.qa_w]
+                add(K.mla_q_absorb, q, w.f[b + "attn_k_b.weight"], self.inv_freq, self.attn_scale, s.n_q, s.nope_dim, M,
+                    self.row_pos, self.row_seq, self.q_out)
+                add(K.mla_flash_decode, self.q_out, kvp.k[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages, s.n_q, M,
+                    self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, w.f[b + "attn_v_b.weight"], s.v_dim, None,
+                    self.attn_q, self.attn_ds, self.fault, il, launches=2)
+            else:
+                add(K.gemv, [w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
+                    x=xb[cur], gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, red=red, fault=self.fault, layer=il)
+                if red is not None:
+                    cur ^= 1
+            if s.mla:
+                pass
+            elif K.staged_part("attn"):
                 add(K.attn_fused, self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
                     self.inv_freq, s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq,
                     kvp.table, kvp.n_pages, kvp.k[il], kvp.v[il], self.n_seg, self.slot_ctx, self.part_ml, self.part_acc,
@@ -157,7 +206,23 @@ class ShardedEngine(DecodeEngine):
                 add(allreduce_into, xb[cur], self.partial, launches=2)
                 red = None
             if not s.layer_is_moe(il):
-                raise NotImplementedError("dense FFN layers of a sharded model are not split yet")
+                # dense FFN: this rank's slice of the width; the down product's partial rows are the layer's second
+                # reduction
+                add(K.gemv, [w.q[b + "ffn_gate.weight"], w.q[b + "ffn_up.weight"]], M, self.gu, x=xb[cur],
+                    gain=w.f[b + "ffn_norm.weight"], eps=s.rms_eps, red=red, fault=self.fault, layer=il)
+                if red is not None:
+                    cur ^= 1
+                add(K.swiglu_q8, self.gu, s.dense_inter, M, self.dactq, self.dactds)
+                if fused:
+                    add(K.gemv, [w.q[b + "ffn_down.weight"]], M, self.partial, xq=self.dactq, xds=self.dactds,
+                        push=ar.push(SITE_MOE, 2 * il + 1), fault=self.fault, layer=il)
+                    pending = (SITE_MOE, 2 * il + 1)
+                else:
+                    add(K.gemv, [w.q[b + "ffn_down.weight"]], M, self.partial, xq=self.dactq, xds=self.dactds,
+                        fault=self.fault, layer=il)
+                    add(allreduce_into, xb[cur], self.partial, launches=2)
+                    pending = None
+                continue
             ids, wts = self.r_ids_all[il], self.r_wts_all[il]
             gate, up, down = w.q[b + "ffn_gate_exps.weight"], w.q[b + "ffn_up_exps.weight"], w.q[b + "ffn_down_exps.weight"]
             staged = gate.qtype == up.qtype and K.moe_fits_stage(gate, down, s.n_used)
@@ -173,14 +238,23 @@ class ShardedEngine(DecodeEngine):
                 add(K.gate_up_sel, self.xq, self.xds, ids, self.slot_map, gate, up, s.n_expert, s.n_used, M, self.actq,
                     self.actds, None, self.fault, il, route_logits=self.r_logits, rule=self._rule(il), wts=wts,
                     heat=self.heat[il])
+            extra = None
+            if s.n_shared:
+                # this rank's slice of the shared expert's width lands as an extra addend of the partial rows
+                add(K.gemv, [w.q[b + "ffn_gate_shexp.weight"], w.q[b + "ffn_up_shexp.weight"]], M, self.sh_gu, xq=self.xq,
+                    xds=self.xds, fault=self.fault, layer=il)
+                add(K.swiglu_q8, self.sh_gu, s.shared_inter, M, self.sh_actq, self.sh_actds)
+                add(K.gemv, [w.q[b + "ffn_down_shexp.weight"]], M, self.sh_out, xq=self.sh_actq, xds=self.sh_actds,
+                    fault=self.fault, layer=il)
+                extra = self.sh_out
             # the pushing launch takes the staged form: it stores each peer's rows as runs of consecutive columns
             down_fn = K.down_staged if (staged or (fused and K.moe_fits_stage(gate, down, s.n_used, force=True))) else K.down_combine
             if fused:
-                add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, None,
+                add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, extra,
                     self.partial, self.fault, il, push=ar.push(SITE_MOE, 2 * il + 1))
                 pending = (SITE_MOE, 2 * il + 1)
             else:
-                add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, None,
+                add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, extra,
                     self.partial, self.fault, il)
                 add(allreduce_into, xb[cur], self.partial, launches=2)
                 pending = None
@@ -197,7 +271,8 @@ class ShardedEngine(DecodeEngine):
         elif fused and pending is not None:
             # no head on this pass: a small consumer folds the last reduction into the residual rows
             red = ar.reduce(pending[0], pending[1], xb[cur ^ 1], self.fault, s.n_layer)
-            add(K.gemv, [w.q["blk.0.attn_k.weight"]], M, self.qkv, x=xb[cur], gain=w.f["output_norm.weight"],
+            small = w.q["blk.0.attn_kv_a_mqa.weight"] if s.mla else w.q["blk.0.attn_k.weight"]
+            add(K.gemv, [small], M, self.qkv, x=xb[cur], gain=w.f["output_norm.weight"],
                 eps=s.rms_eps, red=red, fault=self.fault, layer=s.n_layer)
         return ops
 

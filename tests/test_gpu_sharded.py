@@ -87,6 +87,31 @@ def test_four_and_eight_emulated_ranks_match_single_gpu(world):
         assert all(e.tokens_out[:n].tolist() == engs[0].tokens_out[:n].tolist() for e in engs)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_emulated_ranks_with_latent_attention_dense_layer_and_shared_expert(world):
+    """The DeepSeek layer plan over ranks: latent attention with the per-head products split by head, the leading dense
+    FFN and the shared expert split by width, sigmoid routing with groups over expert-parallel ranks."""
+    import dataclasses
+    from bloomery_b200.models.spec import tiny_deepseek
+    spec = dataclasses.replace(tiny_deepseek(), shared_inter=256 * world, dense_inter=1024)
+    spec, ref, engs = _engines(world, spec=spec)
+    g = torch.Generator().manual_seed(6)
+    toks = torch.randint(0, spec.vocab, (10,), generator=g).tolist()
+    pos = 0
+    for chunk in (toks[:8], toks[8:]):
+        rows = [(0, t, pos + i) for i, t in enumerate(chunk)]
+        ref.step(rows)
+        _lockstep(engs, rows)
+        pos += len(chunk)
+        n = len(chunk)
+        for e in engs:
+            assert (int(e.fault) & 0xFFFFFFFF) == 0xFFFFFFFF
+            assert torch.equal(e.logits[:n], engs[0].logits[:n])
+        err = ((engs[0].logits[:n] - ref.logits[:n]).abs().max() / ref.logits[:n].abs().max()).item()
+        assert err < 2e-2, err
+        assert all(e.tokens_out[:n].tolist() == engs[0].tokens_out[:n].tolist() for e in engs)
+
+
 def test_missing_peer_times_out_with_a_status_not_a_hang():
     """A consumer whose peer never pushed gives up after its bounded wait and raises the
     wait-timeout site in the fault word; the context stays usable."""
