@@ -221,6 +221,9 @@ def main() -> int:
                     help="register-streaming decode kernels instead of the shared-memory staged ones")
     ap.add_argument("--batch", type=int, default=1,
                     help="sequences decoded together (16..64: the batched tensor-core pass; the value is the total of all sequences)")
+    ap.add_argument("--mix", default="", help="weight type recipe of the synthetic model (Q4_K_M, Q8_0, FP8_B128, NVFP4, IQ4_XS, ...)")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="smoke runs only: cut the model to this many layers (the line is marked and is not a benchmark)")
     ap.add_argument("--cpu", action="store_true",
                     help="the CPU configuration: tiny Qwen3-MoE (Q4_K_M), 64-id prompt, 32 greedy tokens on the host engine, no GPU")
     ap.add_argument("--nccl-baseline", dest="nccl_baseline", action="store_true",
@@ -261,7 +264,7 @@ def main() -> int:
     spec = NAMED[args.model]()
     steps, warm = args.steps, max(3, args.warmup)
     t0 = time.time()
-    w = Weights.from_items(spec, synth_tensors(spec, dev, seed=0, mix="Q4_K_M"), dev)
+    w = Weights.from_items(spec, synth_tensors(spec, dev, seed=0, mix=args.mix or "Q4_K_M"), dev)
     torch.cuda.synchronize()
     t_load = time.time() - t0
     if args.batch > 1:

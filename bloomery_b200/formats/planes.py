@@ -76,7 +76,7 @@ def fp8_b128_quantize(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """f32 [N, K] -> (codes uint8 [N, K], scale_inv f32 [ceil(N/128), ceil(K/128)]) — a fixture writer."""
     n, k = w.shape
     nb, kb = (n + 127) // 128, (k + 127) // 128
-    pad = torch.zeros(nb * 128, kb * 128)
+    pad = torch.zeros(nb * 128, kb * 128, device=w.device)
     pad[:n, :k] = w
     blk = pad.reshape(nb, 128, kb, 128)
     amax = blk.abs().amax(dim=(1, 3)).clamp(min=1e-12)

@@ -22,7 +22,7 @@ Works on CPU and CUDA tensors (the repack of a 30 B-parameter model runs on the 
 """
 from __future__ import annotations
 
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 
@@ -91,18 +91,23 @@ def resident_row_bytes(qtype: str, k: int) -> int:
     raise UnsupportedType(f"no resident layout for block type {qtype}")
 
 
-def quantize_resident(w: torch.Tensor, qtype: str) -> Tuple[torch.Tensor, torch.Tensor]:
-    """f32 [rows, K] -> (resident rows, the f32 values those rows decode to).  Fixtures and tests."""
+def quantize_resident(w: torch.Tensor, qtype: str, values: bool = True) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """f32 [rows, K] -> (resident rows, the f32 values those rows decode to, or None when ``values`` is off).
+    Fixtures and tests."""
     from . import planes, quant
     k = w.shape[-1]
+    chunk = 1 << 15                     # rows per pass: the block-scaled quantisers make several full-size temporaries
+    if qtype in PLANE_TYPES and w.shape[0] > chunk:
+        parts = [quantize_resident(w[i:i + chunk], qtype, values) for i in range(0, w.shape[0], chunk)]
+        return torch.cat([p[0] for p in parts], 0), (torch.cat([p[1] for p in parts], 0) if values else None)
     if qtype == "NVFP4":
         res = planes.nvfp4_resident(*planes.nvfp4_quantize(w))
-        return res, planes.resident_dequantize(res, qtype, k)
+        return res, (planes.resident_dequantize(res, qtype, k) if values else None)
     if qtype == "FP8_B128":
         res = planes.fp8_b128_resident(*planes.fp8_b128_quantize(w))
-        return res, planes.resident_dequantize(res, qtype, k)
+        return res, (planes.resident_dequantize(res, qtype, k) if values else None)
     raw = quant.quantize(w, qtype)
-    return to_resident(raw, qtype, k), quant.dequantize(raw, qtype, k)
+    return to_resident(raw, qtype, k), (quant.dequantize(raw, qtype, k) if values else None)
 
 
 def to_resident(raw: torch.Tensor, qtype: str, k: int) -> torch.Tensor:

@@ -48,12 +48,42 @@ def _rand(shape, std, gen, device):
     return torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std
 
 
+def shard_shape(name: str, shape, spec: ModelSpec, rank: int, world: int):
+    """Shape of rank ``rank``'s share of a tensor under the head / expert / width split of the sharded engines
+    (``parallel/sharded.py`` ``shard_items``), and whether the tensor is split at all."""
+    shape = tuple(shape)
+    rows_split = ("attn_q.weight", "attn_q_b.weight", "ffn_gate.weight", "ffn_up.weight", "ffn_gate_shexp.weight",
+                  "ffn_up_shexp.weight")
+    cols_split = ("attn_output.weight", "ffn_down.weight", "ffn_down_shexp.weight")
+    if name.endswith(rows_split):
+        return (shape[0] // world,) + shape[1:], True
+    if name.endswith(("attn_k.weight", "attn_v.weight")):
+        return ((shape[0] // world if spec.n_kv >= world else spec.head_dim),) + shape[1:], True
+    if name.endswith(("attn_k_b.weight", "attn_v_b.weight")) or "_exps.weight" in name:
+        return (shape[0] // world,) + shape[1:], True
+    if name.endswith(cols_split):
+        return shape[:-1] + (shape[-1] // world,), True
+    return shape, False
+
+
 def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K_M", std: float = 0.02,
-                  with_vocab: bool = False) -> Iterator[TensorItem]:
-    """Seeded N(0, std) weights of ``spec``, quantised per ``mix`` ("Q4_K_M", "Q8_0", "F16", ...)."""
+                  with_vocab: bool = False, shard: Optional[Tuple[int, int]] = None) -> Iterator[TensorItem]:
+    """Seeded N(0, std) weights of ``spec``, quantised per ``mix`` ("Q4_K_M", "Q8_0", "F16", ...).
+
+    ``shard`` = (rank, world): only that rank's share of every split tensor is generated, in the local shape the
+    sharded engines load (a model that fits no single card is never built whole); every tensor is then seeded by its
+    name, so replicated tensors are equal on all ranks and split ones differ from rank to rank."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     H, L = spec.hidden, spec.n_layer
+    if shard is not None:
+        import zlib
+        full_gen = gen
+
+        class _PerTensor:
+            def reseed(self, name: str, split: bool) -> None:
+                full_gen.manual_seed((zlib.crc32(name.encode()) ^ (seed * 2654435761) ^ ((shard[0] + 1) * 7919 if split else 0)) & 0x7FFFFFFF)
+        per_tensor = _PerTensor()
 
     def qt(name: str, il: int) -> str:
         if mix == "Q4_K_M":
@@ -63,12 +93,15 @@ def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K
 
     def emit(name: str, shape, il: int = 0, std_=std, ones: bool = False) -> TensorItem:
         t = qt(name, il)
+        if shard is not None:
+            shape, split = shard_shape(name, shape, spec, shard[0], shard[1])
+            per_tensor.reseed(name, split)
         if ones:
             w = torch.ones(*shape, device=device) + _rand(shape, 0.02, gen, device)
         else:
             w = _rand(shape, std_, gen, device)
         if t in PLANE_TYPES:                      # block-scaled float types travel as resident rows
-            return (name, tuple(shape), t, quantize_resident(w.reshape(-1, shape[-1]), t)[0])
+            return (name, tuple(shape), t, quantize_resident(w.reshape(-1, shape[-1]), t, values=False)[0])
         raw = quant.quantize(w.reshape(-1, shape[-1]), t)
         return (name, tuple(shape), t, raw)
 
@@ -92,10 +125,16 @@ def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K
             yield emit(b + "attn_kv_a_mqa.weight", (spec.kv_lora + spec.rope_dim, H), il, std_=0.05)
             yield emit(b + "attn_kv_a_norm.weight", (spec.kv_lora,), il, ones=True)
             # the per-head products keep float weights: [head][nope][latent] and [head][v][latent]
-            yield (b + "attn_k_b.weight", (spec.n_q, spec.nope_dim, spec.kv_lora), "F32",
-                   _rand((spec.n_q * spec.nope_dim, spec.kv_lora), 0.05, gen, device).view(torch.uint8))
-            yield (b + "attn_v_b.weight", (spec.n_q, spec.v_dim, spec.kv_lora), "F32",
-                   _rand((spec.n_q * spec.v_dim, spec.kv_lora), 0.05, gen, device).view(torch.uint8))
+            nh = spec.n_q
+            if shard is not None:
+                nh = spec.n_q // shard[1]
+                per_tensor.reseed(b + "attn_k_b.weight", True)
+            yield (b + "attn_k_b.weight", (nh, spec.nope_dim, spec.kv_lora), "F32",
+                   _rand((nh * spec.nope_dim, spec.kv_lora), 0.05, gen, device).view(torch.uint8))
+            if shard is not None:
+                per_tensor.reseed(b + "attn_v_b.weight", True)
+            yield (b + "attn_v_b.weight", (nh, spec.v_dim, spec.kv_lora), "F32",
+                   _rand((nh * spec.v_dim, spec.kv_lora), 0.05, gen, device).view(torch.uint8))
             yield emit(b + "attn_output.weight", (H, spec.n_q * spec.v_dim), il)
         else:
             yield emit(b + "attn_q.weight", (spec.q_rows, H), il)
@@ -112,6 +151,8 @@ def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K
             yield emit(b + "ffn_up_exps.weight", (spec.n_expert, spec.moe_inter, H), il)
             yield emit(b + "ffn_down_exps.weight", (spec.n_expert, H, spec.moe_inter), il)
             if spec.router_mode == "sigmoid":
+                if shard is not None:
+                    per_tensor.reseed(b + "exp_probs_b.bias", False)
                 yield (b + "exp_probs_b.bias", (spec.n_expert,), "F32",
                        _rand((1, spec.n_expert), 0.05, gen, device).view(torch.uint8))
             if spec.n_shared:
