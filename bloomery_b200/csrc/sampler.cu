@@ -14,6 +14,13 @@
 // (crates/sampler/src/lib.rs:190-346); temperature <= 0 is the arg-max after penalties.
 // top_k is capped at kMaxCand (1024) on the card; top_k = 0 ("all") samples from the 1024
 // best, which carries all but a vanishing share of the mass.
+//
+// Few rows: one block per row leaves the card idle while 1,024 threads walk 150 k logits five
+// times, so up to 8 rows take two launches.  sample_select_kernel splits a row's vocabulary over
+// kSelBlocks blocks; each applies the penalties to its slice and writes its own top-k (same keys,
+// same tie rule, in ascending id order) to a candidate list; sample_rows_kernel then runs unchanged
+// on that list (ids through an index array).  The global top-k is a subset of the union of the
+// slices' top-k and the list keeps id order, so the picked token is the same, bit for bit.
 #include "common.cuh"
 
 namespace bl {
@@ -30,7 +37,11 @@ struct SampleArgs {
   int* out_token;           // [M]
   int* out_n_cand;          // optional [M]
   unsigned* fault;
+  const int* ids;           // optional [M, stride]: id of entry i of a row (a candidate list); null = i itself
+  int penalties_done;       // the rows already carry their penalties (candidate lists do)
 };
+
+constexpr int kSelBlocks = 32;
 
 __device__ __forceinline__ unsigned key_of(float v) {
   // order-preserving map float -> u32 (larger float = larger key); NaN sorts lowest
@@ -125,7 +136,8 @@ __global__ void __launch_bounds__(1024) sample_rows_kernel(const SampleArgs a) {
   // ---- penalties --------------------------------------------------------------------------
   const int n_rec = a.n_recent ? min(a.n_recent[m], a.recent_stride) : 0;
   const int win = min(n_rec, max(last_n, 0));
-  const bool penal = win > 0 && (rep != 1.0f || freq != 0.0f || pres != 0.0f);
+  const bool penal = !a.penalties_done && win > 0 && (rep != 1.0f || freq != 0.0f || pres != 0.0f);
+  const int* ids = a.ids ? a.ids + (long)m * a.stride : nullptr;
   if (penal) {
     float* w = a.work + (long)m * V;
     for (int i = tid; i < V; i += 1024) w[i] = row[i];
@@ -178,7 +190,7 @@ __global__ void __launch_bounds__(1024) sample_rows_kernel(const SampleArgs a) {
   __syncthreads();
   for (int i = tid; i < V; i += 1024) {
     const float v = row[i];
-    if (key_of(v) > kth) { const unsigned p = atomicAdd(&s_count, 1u); if (p < kMaxCand) { c_val[p] = v; c_id[p] = i; } }
+    if (key_of(v) > kth) { const unsigned p = atomicAdd(&s_count, 1u); if (p < kMaxCand) { c_val[p] = v; c_id[p] = ids ? ids[i] : i; } }
   }
   __syncthreads();
   {
@@ -194,7 +206,7 @@ __global__ void __launch_bounds__(1024) sample_rows_kernel(const SampleArgs a) {
     unsigned pos = incl - mine;
     for (int i = i0; i < i1 && pos < want; ++i)
       if (key_of(row[i]) == kth) {
-        if (base + pos < kMaxCand) { c_val[base + pos] = row[i]; c_id[base + pos] = i; }
+        if (base + pos < kMaxCand) { c_val[base + pos] = row[i]; c_id[base + pos] = ids ? ids[i] : i; }
         ++pos;
       }
     __syncthreads();
@@ -265,6 +277,108 @@ __global__ void __launch_bounds__(1024) sample_rows_kernel(const SampleArgs a) {
   }
 }
 
+// Stage 1 of the few-row form: block (slice, row) selects the slice's top_k and writes them in ascending id order to
+// cand_val / cand_id [M][kSelBlocks][cap]; unused cells hold NaN (the lowest key) and id INT_MAX.
+struct SelectArgs {
+  const float* logits; long stride; int V;
+  const int* recent; int recent_stride; const int* n_recent;
+  const float* params;
+  float* cand_val; int* cand_id; int cap;
+};
+
+__global__ void __launch_bounds__(1024) sample_select_kernel(const SelectArgs a) {
+  __shared__ unsigned hist[256];
+  __shared__ unsigned s_prefix, s_need;
+  __shared__ unsigned s_wt[32];
+  extern __shared__ float s_slice[];                     // the slice's (penalised) logits
+  const int blk = blockIdx.x, m = blockIdx.y, tid = threadIdx.x;
+  pdl_wait();
+  pdl_launch();
+  const float* P = a.params + (long)m * 8;
+  const float temperature = P[0], rep = P[4], freq = P[5], pres = P[6];
+  int top_k = (int)P[1];
+  const int last_n = (int)P[7];
+  const int per_blk = (a.V + kSelBlocks - 1) / kSelBlocks;
+  const int v0 = blk * per_blk, v1 = min(a.V, v0 + per_blk), n = max(0, v1 - v0);
+  const float* row = a.logits + (long)m * a.stride;
+  for (int i = tid; i < n; i += 1024) s_slice[i] = row[v0 + i];
+  __syncthreads();
+  const int n_rec = a.n_recent ? min(a.n_recent[m], a.recent_stride) : 0;
+  const int win = min(n_rec, max(last_n, 0));
+  if (win > 0 && (rep != 1.0f || freq != 0.0f || pres != 0.0f)) {
+    const int* rec = a.recent + (long)m * a.recent_stride + (n_rec - win);
+    for (int i = tid; i < win; i += 1024) {
+      const int t = rec[i];
+      if (t < v0 || t >= v1) continue;
+      bool first = true;
+      int count = 0;
+      for (int j = 0; j < win; ++j) { if (rec[j] == t) { if (j < i) first = false; ++count; } }
+      if (!first) continue;
+      float l = row[t];
+      l = (l <= 0.f) ? l * rep : l / rep;
+      s_slice[t - v0] = l - ((float)count * freq + pres);
+    }
+    __syncthreads();
+  }
+  if (temperature <= 0.f) top_k = 1;
+  if (top_k <= 0 || top_k > kMaxCand) top_k = kMaxCand;
+  top_k = min(top_k, a.cap);
+  float* out_v = a.cand_val + ((long)m * kSelBlocks + blk) * a.cap;
+  int* out_i = a.cand_id + ((long)m * kSelBlocks + blk) * a.cap;
+  const int want_all = min(top_k, n);
+  for (int i = want_all + tid; i < a.cap; i += 1024) { out_v[i] = __int_as_float(0x7fc00000); out_i[i] = 0x7fffffff; }
+  if (n == 0) return;
+  // radix select of the slice's want_all-th best key
+  if (tid == 0) { s_prefix = 0u; s_need = (unsigned)want_all; }
+  __syncthreads();
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    if (tid < 256) hist[tid] = 0u;
+    __syncthreads();
+    const unsigned prefix = s_prefix;
+    const unsigned mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+    for (int i = tid; i < n; i += 1024) {
+      const unsigned k = key_of(s_slice[i]);
+      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 0xFF], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      unsigned need = s_need, acc = 0;
+      int b = 255;
+      for (; b > 0; --b) { if (acc + hist[b] >= need) break; acc += hist[b]; }
+      s_need = need - acc;
+      s_prefix = prefix | ((unsigned)b << shift);
+    }
+    __syncthreads();
+  }
+  const unsigned kth = s_prefix, ties_wanted = s_need;
+  // ordered gather: every thread owns a contiguous id range; two block scans give the positions of the entries above
+  // kth and of the lowest-id ties at kth, so the list comes out in ascending id order
+  const int per = (n + 1023) / 1024;
+  const int i0 = min(n, tid * per), i1 = min(n, i0 + per);
+  unsigned above = 0, ties = 0;
+  for (int i = i0; i < i1; ++i) { const unsigned k = key_of(s_slice[i]); above += k > kth; ties += k == kth; }
+  const unsigned tie_incl = block_scan_u(ties, s_wt);
+  unsigned tie_pos = tie_incl - ties;                                   // ties before this thread's range
+  unsigned take = 0;                                                    // entries of this range that are kept
+  {
+    unsigned tp = tie_pos;
+    for (int i = i0; i < i1; ++i) {
+      const unsigned k = key_of(s_slice[i]);
+      if (k > kth) ++take;
+      else if (k == kth) { if (tp < ties_wanted) ++take; ++tp; }
+    }
+  }
+  const unsigned take_incl = block_scan_u(take, s_wt);
+  unsigned pos = take_incl - take;
+  for (int i = i0; i < i1; ++i) {
+    const unsigned k = key_of(s_slice[i]);
+    bool keep = k > kth;
+    if (k == kth) { keep = tie_pos < ties_wanted; ++tie_pos; }
+    if (keep) { if (pos < (unsigned)a.cap) { out_v[pos] = s_slice[i]; out_i[pos] = v0 + i; } ++pos; }
+  }
+}
+
 }  // namespace bl
 
 using namespace bl;
@@ -276,7 +390,30 @@ int bl_sample_rows(const float* logits, long stride, int V, int M, const int* re
                    const int* n_recent, const float* params, const unsigned long long* seeds, unsigned long long* draws,
                    float* work, int* out_token, int* out_n_cand, unsigned* fault, cudaStream_t st) {
   BL_REQUIRE(M >= 1 && V >= 1 && params != nullptr && out_token != nullptr, BL_ERR_SHAPE);
-  SampleArgs a{logits, stride, V, M, recent, recent_stride, n_recent, params, seeds, draws, work, out_token, out_n_cand, fault};
+  SampleArgs a{logits, stride, V, M, recent, recent_stride, n_recent, params, seeds, draws, work, out_token, out_n_cand, fault,
+               nullptr, 0};
+  return (int)launch(sample_rows_kernel, dim3(M), dim3(1024), 0, st, a);
+}
+
+// The few-row form (M <= 8 is where it pays): cand_val / cand_id are caller-owned scratch of M * 32 * cap cells, cap =
+// the largest top_k of the rows (at most 1024; rows with top_k <= 0 need 1024).  Same picks as bl_sample_rows.
+int bl_sample_rows_split(const float* logits, long stride, int V, int M, const int* recent, int recent_stride,
+                         const int* n_recent, const float* params, const unsigned long long* seeds,
+                         unsigned long long* draws, float* cand_val, int* cand_id, int cap, int* out_token,
+                         int* out_n_cand, unsigned* fault, cudaStream_t st) {
+  BL_REQUIRE(M >= 1 && V >= 1 && params != nullptr && out_token != nullptr && cand_val && cand_id, BL_ERR_SHAPE);
+  BL_REQUIRE(cap >= 1 && cap <= kMaxCand, BL_ERR_LIMIT);
+  const int per_blk = (V + kSelBlocks - 1) / kSelBlocks;
+  const size_t smem = (size_t)per_blk * 4;
+  BL_REQUIRE(smem <= 200 * 1024, BL_ERR_LIMIT);
+  static bool set = false;
+  if (!set) { cudaFuncSetAttribute(sample_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+  SelectArgs sa{logits, stride, V, recent, recent_stride, n_recent, params, cand_val, cand_id, cap};
+  cudaError_t e = launch(sample_select_kernel, dim3(kSelBlocks, M), dim3(1024), smem, st, sa);
+  if (e != cudaSuccess) return (int)e;
+  const int L = kSelBlocks * cap;
+  SampleArgs a{cand_val, (long)L, L, M, nullptr, 0, nullptr, params, seeds, draws, nullptr, out_token, out_n_cand, fault,
+               cand_id, 1};
   return (int)launch(sample_rows_kernel, dim3(M), dim3(1024), 0, st, a);
 }
 

@@ -405,11 +405,33 @@ def mtp_prep(e, h, src, enorm, hnorm, eps: float, M: int, xq, xds) -> None:
                              I(M), p(xq), p(xds), stream()), "bl_mtp_prep")
 
 
+_SPLIT_SCRATCH: dict = {}
+SAMPLER_SPLIT_ROWS = 8            # up to this many rows a row's vocabulary is split over 32 blocks (two launches)
+
+
 def sample_rows(logits, V: int, M: int, params, seeds, draws, out_token, *, recent=None, n_recent=None, work=None,
-                out_n_cand=None, fault=None) -> None:
-    """The sampling chain on the card, one block per row (``csrc/sampler.cu``).
+                out_n_cand=None, fault=None, split: Optional[bool] = None, cap: int = 1024) -> None:
+    """The sampling chain on the card (``csrc/sampler.cu``): one block per row, or for few rows (``split``, default
+    M <= 8) 32 blocks per row that each select their slice's top-k followed by the same chain on the candidate lists
+    -- the same picks, bit for bit.  ``cap``: the largest top_k of the rows (1024 when a row has top_k <= 0).
     ``params`` fp32 [M, 8] = temperature, top_k, top_p, min_p, repeat_penalty, frequency_penalty,
     presence_penalty, repeat_last_n; ``seeds``/``draws`` uint64-as-int64 [M]; ``recent`` int32 [M, W]."""
+    if split is None:
+        split = M <= SAMPLER_SPLIT_ROWS
+    if split:
+        cap = max(1, min(1024, cap))
+        key = (str(logits.device), cap)
+        sc = _SPLIT_SCRATCH.get(key)
+        if sc is None or sc[0].shape[0] < M:
+            rows = max(M, SAMPLER_SPLIT_ROWS)
+            sc = (torch.zeros(rows, 32 * cap, dtype=torch.float32, device=logits.device),
+                  torch.zeros(rows, 32 * cap, dtype=torch.int32, device=logits.device))
+            _SPLIT_SCRATCH[key] = sc
+        rc = cuda().bl_sample_rows_split(p(logits), L(logits.stride(0)), I(V), I(M), p(recent),
+                                         I(recent.shape[1] if recent is not None else 0), p(n_recent), p(params), p(seeds),
+                                         p(draws), p(sc[0]), p(sc[1]), I(cap), p(out_token), p(out_n_cand), p(fault), stream())
+        check(rc, "bl_sample_rows_split")
+        return
     rc = cuda().bl_sample_rows(p(logits), L(logits.stride(0)), I(V), I(M), p(recent),
                                I(recent.shape[1] if recent is not None else 0), p(n_recent), p(params), p(seeds), p(draws),
                                p(work), p(out_token), p(out_n_cand), p(fault), stream())

@@ -5,7 +5,7 @@ CUDA events.
     python -m bloomery_b200.ops.kernel_bench NAME [replays] [context] [--no-staged] [--rows M]
 
 NAME: chain (the six launches of a layer in order) | qkv | attn | o | router | gateup | down | rope | flash |
-flash_mma | gemm | gemmdist | pflash | prope | mplan | qgu | qdown | qo | qq | bgu | bdown | mla | sampler | gap.  ``--no-staged`` runs the register-streaming kernels
+flash_mma | gemm | gemmdist | pflash | prope | mplan | qgu | qdown | qo | qq | bgu | bdown | mla | sampler | sampler_split | gap.  ``--no-staged`` runs the register-streaming kernels
 instead of the shared-memory staged ones.  It is also the small workload the ncu summaries under ``profiles/``
 were captured on.
 """
@@ -160,7 +160,7 @@ def main(argv=None) -> int:
                      mqlat=torch.randn(8, mq, 576, device=dev) * 0.05, mml=torch.zeros(8 * mq * mseg * 2, device=dev),
                      macc=torch.zeros(8 * mq * mseg * 512, device=dev), mvb=(torch.randn(mq, 128, 512, device=dev) * 0.05).bfloat16(),
                      moq=torch.zeros(8, mq * 128, dtype=torch.int8, device=dev), mods=torch.zeros(8, mq * 128 // 32, 2, device=dev))
-    if which == "sampler":
+    if which in ("sampler", "sampler_split"):
         V = 151936
         extra = dict(V=V, slog=torch.randn(1, V, device=dev) * 3, spar=torch.tensor([[0.8, 40, 0.95, 0.05, 1.1, 0.0, 0.0, 64]], device=dev),
                      ssd=torch.tensor([1234], dtype=torch.int64, device=dev), sdr=torch.zeros(1, dtype=torch.int64, device=dev),
@@ -238,7 +238,8 @@ def main(argv=None) -> int:
             if which == "mla": K.mla_flash_decode(X["mqlat"], X["mcache"], X["mpos"], X["mseq"], X["mtable"], X["mctx"] // 64, X["mq"], 1, X["mseg"], X["mctx"], X["mml"], X["macc"], X["mvb"], 128, None, X["moq"], X["mods"], fault, 0)
             if which == "gap":
                 for _ in range(8): K.fill_u32(cnt, 0)           # eight empty nodes: the number printed is 8 node gaps
-            if which == "sampler": K.sample_rows(X["slog"], X["V"], 1, X["spar"], X["ssd"], X["sdr"], X["sout"], recent=X["srec"], n_recent=X["snrec"], work=X["swork"])
+            if which == "sampler": K.sample_rows(X["slog"], X["V"], 1, X["spar"], X["ssd"], X["sdr"], X["sout"], recent=X["srec"], n_recent=X["snrec"], work=X["swork"], split=False)
+            if which == "sampler_split": K.sample_rows(X["slog"], X["V"], 1, X["spar"], X["ssd"], X["sdr"], X["sout"], recent=X["srec"], n_recent=X["snrec"], work=X["swork"], split=True, cap=40)
 
     g = torch.cuda.CUDAGraph()
     s = torch.cuda.Stream()

@@ -199,8 +199,10 @@ class GpuEngine(Engine):
             self._samp_work = torch.zeros(self.max_rows, self.n_vocab, device=dev)
             self._samp_out = torch.zeros(self.max_rows, dtype=torch.int32, device=dev)
         draws_dev = draws.to(dev)
+        ks = [int(k) for k in par[:, 1].tolist()]
+        cap = 1024 if any(k <= 0 or k > 1024 for k in ks) else max(ks)
         K.sample_rows(dec.logits[:M], self.n_vocab, M, par.to(dev), seeds.to(dev), draws_dev, self._samp_out,
-                      recent=rec.to(dev), n_recent=nrec.to(dev), work=self._samp_work)
+                      recent=rec.to(dev), n_recent=nrec.to(dev), work=self._samp_work, cap=cap)
         got = self._samp_out[:M].cpu().tolist()
         after = draws_dev.cpu().tolist()
         for r, sp in enumerate(specs):

@@ -7,7 +7,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _run(logits, plist, seeds, recent=None, n_calls=1):
+def _run(logits, plist, seeds, recent=None, n_calls=1, split=None, cap=1024):
     from bloomery_b200.ops import decode as K
     M, V = logits.shape
     params = torch.tensor([[p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.frequency_penalty,
@@ -26,13 +26,14 @@ def _run(logits, plist, seeds, recent=None, n_calls=1):
         nrec = torch.tensor([len(r) for r in recent], dtype=torch.int32, device=DEV)
     picks = []
     for _ in range(n_calls):
-        K.sample_rows(logits, V, M, params, sd, draws, out, recent=rec, n_recent=nrec, work=work, out_n_cand=ncand)
+        K.sample_rows(logits, V, M, params, sd, draws, out, recent=rec, n_recent=nrec, work=work, out_n_cand=ncand, split=split, cap=cap)
         picks.append(out.cpu().tolist())
     return picks, ncand.cpu().tolist()
 
 
+@pytest.mark.parametrize("split", [False, True])
 @pytest.mark.parametrize("V", [32000, 151936])
-def test_sampler_matches_host_chain(V):
+def test_sampler_matches_host_chain(V, split):
     from bloomery_b200.serve.sampler import Sampler, SamplingParams
     g = torch.Generator().manual_seed(V)
     logits = (torch.randn(6, V, generator=g) * 3).to(DEV)
@@ -40,7 +41,7 @@ def test_sampler_matches_host_chain(V):
     plist = [SamplingParams(seed=1), SamplingParams(seed=2, top_k=5, top_p=1.0, min_p=0.0, temperature=1.3),
              SamplingParams(seed=3, top_k=200, top_p=0.7, min_p=0.0), SamplingParams(seed=4, top_k=1024, top_p=1.0, min_p=0.02, temperature=0.5),
              SamplingParams(seed=5, temperature=0.0), SamplingParams(seed=6, top_k=1)]
-    picks, ncand = _run(logits, plist, [p.seed for p in plist], n_calls=4)
+    picks, ncand = _run(logits, plist, [p.seed for p in plist], n_calls=4, split=split)
     host = logits.cpu().numpy()
     agree = total = 0
     for m, p in enumerate(plist):
@@ -54,7 +55,8 @@ def test_sampler_matches_host_chain(V):
     assert agree >= total - 1, (agree, total)          # a double-rounding difference may move one draw across a bin edge
 
 
-def test_sampler_penalties_greedy_and_ties():
+@pytest.mark.parametrize("split", [False, True])
+def test_sampler_penalties_greedy_and_ties(split):
     from bloomery_b200.serve.sampler import Sampler, SamplingParams
     V = 5000
     logits = torch.zeros(3, V, device=DEV)
@@ -63,11 +65,32 @@ def test_sampler_penalties_greedy_and_ties():
     logits[2, 7] = 3.0; logits[2, 9] = 3.0
     pen = SamplingParams(temperature=0.0, repeat_penalty=1.5, frequency_penalty=0.1, presence_penalty=0.2, repeat_last_n=8)
     plist = [pen, SamplingParams(seed=9, top_k=4, top_p=1.0, min_p=0.0, temperature=1.0), SamplingParams(temperature=0.0)]
-    picks, ncand = _run(logits, plist, [0, 9, 0], recent=[[10, 10, 3], [], []])
+    picks, ncand = _run(logits, plist, [0, 9, 0], recent=[[10, 10, 3], [], []], split=split)
     host = logits.cpu().numpy()
     assert picks[0][0] == Sampler(pen).sample(host[0], [10, 10, 3]) == 20      # the repeated best is penalised away
     assert picks[0][1] in (0, 1, 2, 3) and ncand[1] == 4
     assert picks[0][2] == 7                                                    # equal logits: the lower id
+
+
+def test_split_form_picks_the_same_ids_as_one_block_per_row():
+    """32 blocks per row + the chain on the candidate lists against one block per row: same ids, same candidate counts,
+    over penalties, ties, NaNs and a top-k that equals the candidate capacity."""
+    from bloomery_b200.serve.sampler import SamplingParams
+    g = torch.Generator().manual_seed(77)
+    V = 151936
+    logits = (torch.randn(8, V, generator=g) * 2).to(DEV)
+    logits[0, ::3] = 1.5                                 # a huge tie class straddling every slice
+    logits[1, 100:200] = float("nan")
+    logits[2, :] = -float("inf"); logits[2, 70000] = 0.0; logits[2, 5] = 0.0
+    plist = [SamplingParams(seed=1, top_k=64, top_p=0.95), SamplingParams(seed=2, top_k=40, repeat_penalty=1.3, repeat_last_n=64),
+             SamplingParams(seed=3, top_k=50), SamplingParams(seed=4, top_k=100, min_p=0.05, temperature=0.7),
+             SamplingParams(seed=5, temperature=0.0), SamplingParams(seed=6, top_k=1),
+             SamplingParams(seed=7, top_k=100, frequency_penalty=0.3, presence_penalty=0.2, repeat_last_n=16),
+             SamplingParams(seed=8, top_k=7, top_p=0.5)]
+    recent = [[], list(range(90, 150)), [], [], [], [], [5, 5, 9, 70000, 5], []]
+    a, na = _run(logits, plist, [p.seed for p in plist], recent=recent, n_calls=3, split=False)
+    b, nb = _run(logits, plist, [p.seed for p in plist], recent=recent, n_calls=3, split=True, cap=100)
+    assert a == b and na == nb
 
 
 def test_serving_engine_samples_on_the_card_like_the_host_chain():
