@@ -46,6 +46,13 @@ UNSUPPORTED_FIELDS = {"grammar": "GBNF grammars are not served; use response_for
                       "mirostat": None, "dynatemp_range": None, "xtc_probability": None, "dry_multiplier": None}
 
 
+GENERATING_ROUTES = ("/completion", "/completions", "/v1/completions", "/v1/chat/completions", "/chat/completions", "/v1/messages",
+                     "/v1/responses", "/v1/embeddings", "/embeddings", "/embedding")
+
+
+from .admit import Refused  # noqa: E402
+
+
 class ApiError(Exception):
     def __init__(self, status: int, message: str, kind: str = "invalid_request_error"):
         super().__init__(message)
@@ -65,7 +72,9 @@ class State:
         self.template: Optional[C.ChatTemplate] = None
         self.tool_format = "hermes"
         self.alias = args.get("alias")
-        self.api_keys = self._load_keys(args)
+        self.api_keys, key_limits = self._load_keys(args)
+        from .admit import Admission
+        self.admission = Admission(key_limits)
         self.t_start = time.time()
         self.responses: "collections.OrderedDict[str, dict]" = collections.OrderedDict()
         self.responses_bytes = 0
@@ -77,14 +86,23 @@ class State:
         self.residency = None
 
     @staticmethod
-    def _load_keys(args) -> List[str]:
-        keys = []
+    def _load_keys(args):
+        """Keys of ``--api-key`` (no limits) and of the key file, whose lines may carry limit fields
+        (``KEY inflight=2 rate=30/m burst=5``, see ``serve/admit.py``)."""
+        from .admit import parse_key_line
+        keys, limits = [], {}
         if args.get("api_key"):
             keys += [k for k in str(args["api_key"]).split(",") if k]
         if args.get("api_key_file"):
             with open(args["api_key_file"]) as fh:
-                keys += [ln.strip() for ln in fh if ln.strip() and not ln.startswith("#")]
-        return keys
+                for ln in fh:
+                    ln = ln.strip()
+                    if not ln or ln.startswith("#"):
+                        continue
+                    key, lim = parse_key_line(ln)
+                    keys.append(key)
+                    limits[key] = lim
+        return keys, limits
 
     @property
     def model_id(self) -> str:
@@ -228,7 +246,8 @@ class Handler(BaseHTTPRequestHandler):
             return True
         got = self.headers.get("Authorization", "")
         got = got[7:] if got.startswith("Bearer ") else self.headers.get("x-api-key", "")
-        return any(hmac.compare_digest(got, k) for k in keys)
+        self._key = next((k for k in keys if hmac.compare_digest(got, k)), None)
+        return self._key is not None
 
     def _loopback(self) -> bool:
         try:
@@ -302,6 +321,13 @@ class Handler(BaseHTTPRequestHandler):
                     return self._send(200, {"id": r["id"], "object": "response", "deleted": True})
                 raise ApiError(404, f"no route DELETE {path}", "not_found_error")
             body = self._body()
+            if path in GENERATING_ROUTES:
+                # a generating request takes one of its key's places (in flight, and of its rate bucket) until answered
+                release = st.admission.admit(getattr(self, "_key", None) or "")
+                try:
+                    return self._generating_route(path, body)
+                finally:
+                    release()
             if path in ("/completion", "/completions"):
                 return self._completion(body, "llama")
             if path == "/v1/completions":
@@ -352,6 +378,8 @@ class Handler(BaseHTTPRequestHandler):
             self._error(e.status, e.message, e.kind)
         except C.TemplateError as e:
             self._error(400, str(e))
+        except Refused as e:
+            self._send(429, {"error": {"code": 429, "message": str(e), "type": "rate_limit_error"}}, {"Retry-After": str(e.retry_after)})
         except QueueFull as e:
             self._send(503, {"error": {"code": 503, "message": str(e), "type": "unavailable_error"}}, {"Retry-After": "1"})
         except (BrokenPipeError, ConnectionResetError):
@@ -361,6 +389,19 @@ class Handler(BaseHTTPRequestHandler):
                 self._error(500, f"{type(e).__name__}: {e}", "server_error")
             except Exception:  # noqa: BLE001
                 pass
+
+    def _generating_route(self, path: str, body):
+        if path in ("/completion", "/completions"):
+            return self._completion(body, "llama")
+        if path == "/v1/completions":
+            return self._completion(body, "oai")
+        if path in ("/v1/chat/completions", "/chat/completions"):
+            return self._chat(body)
+        if path == "/v1/messages":
+            return self._messages(body)
+        if path == "/v1/responses":
+            return self._responses(body)
+        return self._embeddings(body)
 
     # ---- small surfaces ------------------------------------------------------------------
     def _model_card(self):

@@ -184,10 +184,105 @@ def parse_mistral(text: str) -> Tuple[str, List[dict]]:
         return text, []
 
 
-TOOL_PARSERS = {"hermes": parse_hermes, "qwenxml": parse_qwen_xml, "glmxml": parse_glm_xml, "mistral": parse_mistral}
+DSML = "\uff5cDSML\uff5c"          # the marker token of the DeepSeek-V3.2 / V4 tool markup: fullwidth bars around DSML
+
+
+def _dsml_tags(spaced: bool):
+    """(block open, block close, invoke open prefix, invoke close, parameter open prefix, parameter close) of one
+    spelling: plain ``<|DSML|tool_calls>`` or the spaced one whose tags carry a space after the marker and whose block
+    is ``calls``."""
+    sp = " " if spaced else ""
+    block = "calls" if spaced else "tool_calls"
+    return (f"<{DSML}{sp}{block}>", f"</{DSML}{sp}{block}>", f"<{DSML}{sp}invoke name=\"", f"</{DSML}{sp}invoke>",
+            f"<{DSML}{sp}parameter name=\"", f"</{DSML}{sp}parameter>")
+
+
+def parse_dsml(text: str, spaced: Optional[bool] = None) -> Tuple[str, List[dict]]:
+    """DSML tool calls (``crates/serve/src/dsml.rs`` in the reference):
+
+        <|DSML|tool_calls>
+        <|DSML|invoke name="NAME">
+        <|DSML|parameter name="KEY" string="true">RAW TEXT</|DSML|parameter>
+        <|DSML|parameter name="KEY" string="false">JSON</|DSML|parameter>
+        </|DSML|invoke>
+        </|DSML|tool_calls>
+
+    (bars are the fullwidth ones).  Arguments become a JSON object in parameter order; a ``string="false"`` value that
+    is not valid JSON is kept as a string.  A block that does not parse, or is still open at the end, stays content as
+    raw text.  ``spaced`` picks the spelling; None reads whichever the text opens with, never both."""
+    if spaced is None:
+        spaced = _dsml_tags(True)[0] in text and _dsml_tags(False)[0] not in text
+    b_open, b_close, i_open, i_close, p_open, p_close = _dsml_tags(spaced)
+    calls, out, pos = [], [], 0
+    while True:
+        i = text.find(b_open, pos)
+        if i < 0:
+            break
+        j = text.find(b_close, i)
+        if j < 0:
+            break                                  # an open block at the end of the text is content
+        body = text[i + len(b_open):j]
+        got = _dsml_block(body, i_open, i_close, p_open, p_close, len(calls))
+        lead = text[pos:i]
+        if got is None:
+            out.append(text[pos:j + len(b_close)])
+        else:
+            out.append(lead[:-2] if lead.endswith("\n\n") else lead)      # the template writes two newlines before a block
+            calls.extend(got)
+        pos = j + len(b_close)
+    out.append(text[pos:])
+    return "".join(out).strip(), calls
+
+
+def _dsml_block(body: str, i_open, i_close, p_open, p_close, first_index: int) -> Optional[List[dict]]:
+    """The calls of one block's inside, or None when it is not well-formed."""
+    calls, pos = [], 0
+    while True:
+        rest = body[pos:]
+        if not rest.strip():
+            return calls if calls else None
+        k = body.find(i_open, pos)
+        if k < 0 or body[pos:k].strip():
+            return None
+        q = body.find("\">", k + len(i_open))
+        e = body.find(i_close, k)
+        if q < 0 or e < 0 or q > e:
+            return None
+        name = body[k + len(i_open):q]
+        inner, ipos, args = body[q + 2:e], 0, {}
+        while True:
+            if not inner[ipos:].strip():
+                break
+            a = inner.find(p_open, ipos)
+            if a < 0 or inner[ipos:a].strip():
+                return None
+            m = re.match(r'([^"]*)" string="(true|false)">', inner[a + len(p_open):])
+            if not m:
+                return None
+            v0 = a + len(p_open) + m.end()
+            v1 = inner.find(p_close, v0)
+            if v1 < 0:
+                return None
+            raw = inner[v0:v1]
+            if m.group(2) == "true":
+                args[m.group(1)] = raw
+            else:
+                try:
+                    args[m.group(1)] = json.loads(raw)
+                except json.JSONDecodeError:
+                    args[m.group(1)] = raw
+            ipos = v1 + len(p_close)
+        calls.append(_call(name, args, first_index + len(calls)))
+        pos = e + len(i_close)
+
+
+TOOL_PARSERS = {"hermes": parse_hermes, "qwenxml": parse_qwen_xml, "glmxml": parse_glm_xml, "mistral": parse_mistral,
+                "dsml": lambda t: parse_dsml(t, False), "dsml_spaced": lambda t: parse_dsml(t, True)}
 
 
 def detect_tool_format(template_source: str) -> str:
+    if DSML in template_source:
+        return "dsml_spaced" if f"<{DSML} " in template_source else "dsml"
     if "<function=" in template_source:
         return "qwenxml"
     if "<arg_key>" in template_source:
@@ -209,6 +304,8 @@ class ToolCallStream:
     block is held until it closes, then emitted whole (chunking-invariant by construction)."""
 
     def __init__(self, fmt: str = "hermes", open_tag: str = "<tool_call>", close_tag: str = "</tool_call>"):
+        if fmt in ("dsml", "dsml_spaced"):
+            open_tag, close_tag = _dsml_tags(fmt == "dsml_spaced")[:2]
         self.fmt, self.open, self.close = fmt, open_tag, close_tag
         self.buf = ""
         self.n_calls = 0

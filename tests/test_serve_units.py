@@ -194,6 +194,73 @@ def test_tool_call_parsers_and_stream_chunking_invariance():
         assert out == "Sure." and len(got) == 1 and got[0]["function"]["name"] == "get_weather"
 
 
+def test_dsml_tool_calls_both_spellings_and_streaming():
+    D = C.DSML
+    plain = (f'On it.\n\n<{D}tool_calls>\n<{D}invoke name="get_weather">\n'
+             f'<{D}parameter name="city" string="true">Paris, "FR"</{D}parameter>\n'
+             f'<{D}parameter name="days" string="false">3</{D}parameter>\n'
+             f'<{D}parameter name="opts" string="false">{{"units": "c"}}</{D}parameter>\n'
+             f'<{D}parameter name="odd" string="false">not json</{D}parameter>\n'
+             f'</{D}invoke>\n<{D}invoke name="ping">\n</{D}invoke>\n</{D}tool_calls>')
+    content, calls = C.parse_tool_calls(plain, "dsml")
+    assert content == "On it." and [c["function"]["name"] for c in calls] == ["get_weather", "ping"]
+    args = json.loads(calls[0]["function"]["arguments"])
+    assert args == {"city": 'Paris, "FR"', "days": 3, "opts": {"units": "c"}, "odd": "not json"}
+    assert list(args) == ["city", "days", "opts", "odd"]                       # parameter order is kept
+    assert json.loads(calls[1]["function"]["arguments"]) == {}
+    spaced = (f'<{D} calls>\n<{D} invoke name="f">\n<{D} parameter name="x" string="false">1</{D} parameter>\n'
+              f'</{D} invoke>\n</{D} calls>')
+    assert json.loads(C.parse_tool_calls(spaced, "dsml_spaced")[1][0]["function"]["arguments"]) == {"x": 1}
+    assert C.parse_tool_calls(spaced, "dsml")[1] == []                          # a scan reads the one spelling it is given
+    assert C.detect_tool_format(f"... <{D} calls> ...") == "dsml_spaced" and C.detect_tool_format(f"<{D}tool_calls>") == "dsml"
+    # markup that does not parse, and a block still open at the end, stay content
+    broken = f'<{D}tool_calls>\n<{D}invoke name="f">\n<{D}parameter name="x">1</{D}parameter>\n</{D}invoke>\n</{D}tool_calls>'
+    assert C.parse_tool_calls(broken, "dsml") == (broken, [])
+    open_end = f'hello <{D}tool_calls>\n<{D}invoke name="f">'
+    assert C.parse_tool_calls(open_end, "dsml") == (open_end, [])
+    for step in (1, 2, 5, 11, len(plain)):                                      # chunking never changes the result
+        s = C.ToolCallStream("dsml")
+        out, got = "", []
+        for i in range(0, len(plain), step):
+            t, c = s.push(plain[i:i + step])
+            out += t
+            got += c
+        out += s.flush()
+        assert out.strip() == "On it." and [c["function"]["arguments"] for c in got] == [c["function"]["arguments"] for c in calls]
+
+
+def test_per_key_limits():
+    from bloomery_b200.serve.admit import Admission, LimitError, Limits, Refused, parse_key_line
+    key, lim = parse_key_line("sk-one inflight=2 rate=30/m burst=3")
+    assert key == "sk-one" and lim.inflight == 2 and lim.rate == (30, True) and lim.burst == 3 and lim.interval == 2.0
+    assert parse_key_line("sk-two")[1].inflight is None
+    for bad in ("k rate=5", "k rate=5/h", "k inflight=0", "k burst=2", "k colour=red", "k inflight"):
+        with pytest.raises(LimitError) as e:
+            parse_key_line(bad)
+        assert "k " not in str(e.value)                                           # the key is never in the message
+    now = [100.0]
+    adm = Admission({"a": Limits(inflight=2), "b": Limits(rate=(2, False), burst=2), "c": Limits()}, clock=lambda: now[0])
+    r1, r2 = adm.admit("a"), adm.admit("a")
+    with pytest.raises(Refused) as e:
+        adm.admit("a")
+    assert e.value.retry_after >= 1
+    r1(); r1()                                                                     # releasing twice frees one place
+    r3 = adm.admit("a")
+    with pytest.raises(Refused):
+        adm.admit("a")
+    r2(); r3()
+    adm.admit("b")(); adm.admit("b")()                                            # the burst
+    with pytest.raises(Refused):
+        adm.admit("b")                                                             # bucket empty: a request every 0.5 s
+    now[0] += 0.5
+    adm.admit("b")()
+    with pytest.raises(Refused):
+        adm.admit("b")
+    for _ in range(50):
+        adm.admit("c")                                                             # no limits, and keys count apart
+        adm.admit("unknown")
+
+
 def test_reasoning_split():
     assert C.split_reasoning("<think>plan</think>\nanswer") == ("plan", "answer")
     assert C.split_reasoning("plan</think>answer", started=True) == ("plan", "answer")
