@@ -160,19 +160,25 @@ def stops_from(body) -> List[str]:
     raise ApiError(400, "stop must be a string or a list of strings")
 
 
-def constraint_from(body) -> Optional[C.JsonConstraint]:
+def constraint_from(body):
+    """The structured-output constraint of a request: a segment program walked token by token when the schema compiles
+    to one (``serve/constrain.py``), else the JSON prefix validator."""
+    from .constrain import constraint_for
+
+    def pick(schema):
+        return constraint_for(schema) or C.JsonConstraint(schema)
     rf = body.get("response_format")
     if rf:
         t = rf.get("type")
         if t == "json_object":
-            return C.JsonConstraint(rf.get("schema"))
+            return pick(rf.get("schema"))
         if t == "json_schema":
             js = rf.get("json_schema") or {}
-            return C.JsonConstraint(js.get("schema", js))
+            return pick(js.get("schema", js))
         if t not in (None, "text"):
             raise ApiError(400, f"response_format.type {t!r} is not supported")
     if body.get("json_schema"):
-        return C.JsonConstraint(body["json_schema"])
+        return pick(body["json_schema"])
     return None
 
 

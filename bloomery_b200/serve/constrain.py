@@ -1,0 +1,265 @@
+"""Structured output as a program over text segments, walked token by token.
+
+A JSON schema (the subset below) compiles to a list of segments: literal text, a JSON string, a JSON number, a fork
+among segment lists, and an array that repeats its item.  A :class:`Walk` keeps the set of places the output may be at
+(one per fork option that still matches what was written, like the heads of an NFA) and answers, for a candidate token's
+text, whether some place accepts all of it.  Where every place agrees that literal text comes next the walk names it
+(:meth:`Walk.forced_text`): the server then takes the canonical tokens of that text without reading the logits at all
+(the jump arm) -- keys, punctuation and closing brackets of an object cost no sampling.  Once the program is spent only
+an end-of-generation token is allowed.
+
+The output is canonical JSON: ``", "`` and ``": "`` separators, no other whitespace, properties in schema order.
+
+Schema subset: ``type`` object (``properties`` in order, all emitted) / array (``items``, ``minItems``, ``maxItems``) /
+string (``maxLength``, ``enum``) / number / integer / boolean / null, ``const``, ``enum``, ``anyOf`` / ``oneOf``.
+Anything else raises :class:`Unsupported` and the caller falls back to the prefix validator of ``serve/chat.py``.
+
+The reference's counterpart is ``crates/serve/src/constrain/program.rs`` (parts, compile, walk with heads, the fixed-next
+shortcut); this one walks characters of token texts instead of precompiled id tries.
+"""
+from __future__ import annotations
+
+import json
+import re
+from typing import Any, List, Optional, Set, Tuple
+
+_NUM_FULL = re.compile(r"-?(0|[1-9]\d*)(\.\d+)?([eE][+-]?\d+)?\Z")
+_NUM_PREFIX = re.compile(r"-?((0|[1-9]\d*)((\.\d*)|((\.\d+)?[eE][+-]?\d*))?)?\Z")
+_INT_FULL = re.compile(r"-?(0|[1-9]\d*)\Z")
+_INT_PREFIX = re.compile(r"-?(0|[1-9]\d*)?\Z")
+_ESCAPES = '"\\/bfnrt'
+
+
+class Unsupported(ValueError):
+    """The schema uses something the segment program does not express."""
+
+
+def _merge(segs: List[tuple]) -> Tuple[tuple, ...]:
+    out: List[tuple] = []
+    for s in segs:
+        if s[0] == "lit" and not s[1]:
+            continue
+        if s[0] == "lit" and out and out[-1][0] == "lit":
+            out[-1] = ("lit", out[-1][1] + s[1])
+        else:
+            out.append(s)
+    return tuple(out)
+
+
+def compile_schema(schema: Any) -> Tuple[tuple, ...]:
+    """Schema -> segments."""
+    if not isinstance(schema, dict):
+        raise Unsupported("a schema is an object")
+    if "const" in schema:
+        return (("lit", json.dumps(schema["const"], ensure_ascii=False)),)
+    if "enum" in schema:
+        opts = schema["enum"]
+        if not isinstance(opts, list) or not opts:
+            raise Unsupported("enum takes a non-empty list")
+        return (("alt", tuple((("lit", json.dumps(v, ensure_ascii=False)),) for v in opts)),)
+    for word in ("anyOf", "oneOf"):
+        if word in schema:
+            return (("alt", tuple(compile_schema(s) for s in schema[word])),)
+    t = schema.get("type")
+    if isinstance(t, list):
+        return (("alt", tuple(compile_schema({**schema, "type": x}) for x in t)),)
+    if t == "object":
+        props = schema.get("properties")
+        if not isinstance(props, dict):
+            raise Unsupported("an object needs its properties listed")
+        segs: List[tuple] = [("lit", "{")]
+        for i, (key, sub) in enumerate(props.items()):
+            segs.append(("lit", (", " if i else "") + json.dumps(key, ensure_ascii=False) + ": "))
+            segs.extend(compile_schema(sub))
+        segs.append(("lit", "}"))
+        return _merge(segs)
+    if t == "array":
+        item = compile_schema(schema.get("items") if "items" in schema else _raise("an array needs items"))
+        lo, hi = int(schema.get("minItems", 0)), schema.get("maxItems")
+        return (("lit", "["), ("arr", item, lo, None if hi is None else int(hi), 0))
+    if t == "string":
+        return (("str", schema.get("maxLength")),)
+    if t == "number":
+        return (("num", False),)
+    if t == "integer":
+        return (("num", True),)
+    if t == "boolean":
+        return (("alt", ((("lit", "true"),), (("lit", "false"),))),)
+    if t == "null":
+        return (("lit", "null"),)
+    raise Unsupported(f"schema type {t!r}")
+
+
+def _raise(msg: str):
+    raise Unsupported(msg)
+
+
+Head = Tuple[Tuple[tuple, ...], int, Any]      # (segments, index, state inside the segment)
+
+
+def _start(seg: tuple) -> Any:
+    return {"lit": 0, "str": (0, 0), "num": ""}.get(seg[0])
+
+
+def _closure(heads) -> Set[Head]:
+    """Expand forks and arrays until every head stands on literal text, a string, a number or the end."""
+    out: Set[Head] = set()
+    todo = list(heads)
+    while todo:
+        segs, i, st = todo.pop()
+        if i >= len(segs):
+            out.add((segs, i, None))
+            continue
+        s = segs[i]
+        if s[0] == "alt":
+            for opt in s[1]:
+                ns = tuple(opt) + segs[i + 1:]
+                todo.append((ns, 0, _start(ns[0]) if ns else None))
+        elif s[0] == "arr":
+            _, item, lo, hi, count = s
+            rest = segs[i + 1:]
+            if count >= lo:
+                ns = _merge([("lit", "]")] + list(rest))
+                todo.append((ns, 0, 0))
+            if hi is None or count < hi:
+                ns = _merge([("lit", ", " if count else "")] + list(item)) + (("arr", item, lo, hi, count + 1),) + rest
+                todo.append((ns, 0, _start(ns[0])))
+        else:
+            out.add((segs, i, st))
+    return out
+
+
+def _next(segs, i) -> Set[Head]:
+    return _closure([(segs, i + 1, _start(segs[i + 1]) if i + 1 < len(segs) else None)])
+
+
+def _feed(head: Head, ch: str) -> Set[Head]:
+    segs, i, st = head
+    if i >= len(segs):
+        return set()
+    s = segs[i]
+    if s[0] == "lit":
+        if s[1][st] != ch:
+            return set()
+        return _next(segs, i) if st + 1 == len(s[1]) else {(segs, i, st + 1)}
+    if s[0] == "str":
+        phase, n = st
+        if phase == 0:
+            return {(segs, i, (1, 0))} if ch == '"' else set()
+        if phase == 2:
+            return {(segs, i, (1, n + 1))} if ch in _ESCAPES else set()
+        if ch == '"':
+            return _next(segs, i)
+        if ch == "\\":
+            return {(segs, i, (2, n))}
+        if ord(ch) < 0x20 or (s[1] is not None and n + 1 > s[1]):
+            return set()
+        return {(segs, i, (1, n + 1))}
+    if s[0] == "num":
+        full, prefix = (_INT_FULL, _INT_PREFIX) if s[1] else (_NUM_FULL, _NUM_PREFIX)
+        cand = st + ch
+        if prefix.match(cand) and len(cand) <= 40:
+            return {(segs, i, cand)}
+        if full.match(st):                       # the number is whole: this character belongs to what follows
+            out: Set[Head] = set()
+            for h in _next(segs, i):
+                out |= _feed(h, ch)
+            return out
+        return set()
+    return set()
+
+
+class Walk:
+    def __init__(self, program: Tuple[tuple, ...]):
+        self.heads: Set[Head] = _closure([(program, 0, _start(program[0]) if program else None)])
+
+    def _after(self, heads: Set[Head], text: str) -> Set[Head]:
+        for ch in text:
+            nxt: Set[Head] = set()
+            for h in heads:
+                nxt |= _feed(h, ch)
+            heads = nxt
+            if not heads:
+                break
+        return heads
+
+    def accepts(self, piece: str) -> bool:
+        return bool(piece) and bool(self._after(self.heads, piece))
+
+    def take(self, piece: str) -> None:
+        self.heads = self._after(self.heads, piece)
+
+    @property
+    def dead(self) -> bool:
+        return not self.heads
+
+    @property
+    def spent(self) -> bool:
+        """The output so far is a whole value (a number at the very end counts when it is whole)."""
+        for segs, i, st in self.heads:
+            if i >= len(segs):
+                return True
+            if i == len(segs) - 1 and segs[i][0] == "num" and (_INT_FULL if segs[i][1] else _NUM_FULL).match(st):
+                return True
+        return False
+
+    def forced_text(self) -> str:
+        """Literal text that every head writes next ('' when they disagree or stand in a string or number)."""
+        texts = []
+        for segs, i, st in self.heads:
+            if i >= len(segs) or segs[i][0] != "lit":
+                return ""
+            texts.append(segs[i][1][st:])
+        if not texts:
+            return ""
+        common = texts[0]
+        for t in texts[1:]:
+            k = 0
+            while k < len(common) and k < len(t) and common[k] == t[k]:
+                k += 1
+            common = common[:k]
+        return common
+
+
+class ProgramConstraint:
+    """The request-side face: the same ``allowed`` / ``done`` / ``closed`` calls as the prefix validator, answered by a
+    walk that follows the text written so far, plus ``forced_text`` for the jump arm."""
+
+    def __init__(self, schema: dict):
+        self.schema = schema
+        self.program = compile_schema(schema)
+        self._text = ""
+        self._walk = Walk(self.program)
+
+    def _at(self, text: str) -> Walk:
+        if text != self._text:
+            if text.startswith(self._text):
+                self._walk.take(text[len(self._text):])
+            else:
+                self._walk = Walk(self.program)
+                self._walk.take(text)
+            self._text = text
+        return self._walk
+
+    def allowed(self, text: str, piece: str) -> bool:
+        return self._at(text).accepts(piece)
+
+    def done(self, text: str) -> bool:
+        return self._at(text).spent
+
+    def closed(self, text: str) -> bool:
+        w = self._at(text)
+        return w.spent and all(i >= len(segs) for segs, i, _ in w.heads)
+
+    def forced_text(self, text: str) -> str:
+        return self._at(text).forced_text()
+
+
+def constraint_for(schema: Optional[dict]):
+    """A segment program when the schema compiles to one, else None (the caller keeps its prefix validator)."""
+    if not schema:
+        return None
+    try:
+        return ProgramConstraint(schema)
+    except Unsupported:
+        return None

@@ -253,18 +253,31 @@ class Worker(threading.Thread):
         return tok
 
     def _constrained_pick(self, a: Active, row: np.ndarray, recent) -> int:
-        """Masked pick: best-first over candidates until one keeps the output a valid prefix."""
+        """Masked pick: best-first over candidates until one keeps the output a valid prefix.  A segment program
+        (``serve/constrain.py``) that knows the literal text every continuation shares is not asked about candidates at
+        all: the first canonical token of that text is taken without reading the row (the jump arm)."""
         tk = self.engine.tokenizer
-        order = np.argsort(-row, kind="stable")[:256]
-        for t in order:
-            t = int(t)
-            if tk.is_eog(t):
-                if a.req.constraint.done(a.text):
+        forced = getattr(a.req.constraint, "forced_text", None)
+        if forced is not None:
+            text = forced(a.text)
+            if text:
+                ids = tk.encode(text, parse_special=False, add_bos=False)
+                if ids:
+                    piece = tk.decode([int(ids[0])], skip_special=True)
+                    if piece and text.startswith(piece):
+                        self.jumped = getattr(self, "jumped", 0) + 1
+                        return int(ids[0])
+        order = np.argsort(-row, kind="stable")
+        for lo, hi in ((0, 256), (256, order.size)):          # the best 256 first; the whole row only when none of them fits
+            for t in order[lo:hi]:
+                t = int(t)
+                if tk.is_eog(t):
+                    if a.req.constraint.done(a.text):
+                        return t
+                    continue
+                piece = tk.decode([t], skip_special=True)
+                if piece and a.req.constraint.allowed(a.text, piece):
                     return t
-                continue
-            piece = tk.decode([t], skip_special=True)
-            if piece and a.req.constraint.allowed(a.text, piece):
-                return t
         return int(order[0])
 
     def enable_drafting(self, draft, width) -> None:

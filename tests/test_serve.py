@@ -167,6 +167,37 @@ def test_json_mode(server):
     assert json.loads(r["content"]) == {"a": [1, 2, {"b": None}]}
 
 
+def test_schema_program_forces_keys_without_sampling(server):
+    """A schema that compiles to a segment program: the echo engine wants to write spaces and other keys, the program
+    keeps the canonical object, and its literal text is taken through the jump arm."""
+    schema = {"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "boolean"}}}
+    code, r = call(server, "/completion", {"prompt": '{"a":   41, "zzz": 1, "b": true} trailing', "temperature": 0, "n_predict": 64,
+                                            "response_format": {"type": "json_schema", "json_schema": {"schema": schema}}})
+    assert code == 200
+    got = json.loads(r["content"])
+    assert list(got) == ["a", "b"] and isinstance(got["a"], int) and isinstance(got["b"], bool)
+    assert r["content"].startswith('{"a": ') and getattr(server.state.worker, "jumped", 0) >= 3
+
+
+def test_key_file_limits_answer_429(tmp_path):
+    kf = tmp_path / "keys.txt"
+    kf.write_text("# keys\nslow rate=1/m burst=1\nfree\n")
+    opts = flags.parse(["--port", "0", "--mock", "--api-key-file", str(kf)])
+    s = Server(opts)
+    s.start()
+    s.ready(MockEngine(), ChatTemplate(), 0)
+    slow, free = {"Authorization": "Bearer slow"}, {"Authorization": "Bearer free"}
+    assert call(s, "/completion", {"prompt": "ab", "n_predict": 2}, headers=slow)[0] == 200
+    code, r = call(s, "/completion", {"prompt": "ab", "n_predict": 2}, headers=slow)
+    assert code == 429 and r["error"]["type"] == "rate_limit_error"
+    assert call(s, "/tokenize", {"content": "ab"}, headers=slow)[0] == 200          # not a generating route: no place taken
+    for _ in range(3):
+        assert call(s, "/completion", {"prompt": "ab", "n_predict": 2}, headers=free)[0] == 200
+    assert call(s, "/completion", {"prompt": "ab"}, headers={"Authorization": "Bearer nope"})[0] == 401
+    s.state.stop_event.set()
+    s.stop()
+
+
 def test_api_key_and_shutdown():
     opts = flags.parse(["--port", "0", "--mock", "--api-key", "sekret"])
     s = Server(opts)

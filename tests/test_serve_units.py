@@ -281,6 +281,45 @@ def test_json_constraint_prefixes_and_schema():
 
 
 # ---- prompt cache and board -------------------------------------------------------------------------
+def test_constraint_program_walk_and_jump_arm():
+    from bloomery_b200.serve.constrain import ProgramConstraint, Unsupported, Walk, compile_schema, constraint_for
+    schema = {"type": "object", "properties": {
+        "name": {"type": "string", "maxLength": 8}, "age": {"type": "integer"}, "ok": {"type": "boolean"},
+        "tags": {"type": "array", "items": {"enum": ["a", "b"]}, "minItems": 1, "maxItems": 2},
+        "pos": {"type": "object", "properties": {"x": {"type": "number"}}}, "kind": {"const": "v1"}}}
+    pc = ProgramConstraint(schema)
+    assert pc.forced_text("") == '{"name": '                                      # keys and punctuation are never sampled
+    good = '{"name": "Al\\"x", "age": -12, "ok": true, "tags": ["a", "b"], "pos": {"x": 1.5e3}, "kind": "v1"}'
+    w = Walk(pc.program)
+    for ch in good:
+        assert w.accepts(ch), ch
+        w.take(ch)
+    assert w.spent and not w.accepts(" ") and json.loads(good)["tags"] == ["a", "b"]
+    # pieces of several characters, as tokens are
+    assert pc.allowed('{"name": ', '"Bo') and pc.allowed('{"name": "Bo', '", "age": ') and not pc.allowed('{"name": "Bo', '", "ok"')
+    assert not pc.allowed('{"name": "12345678', "9") and pc.allowed('{"name": "12345678', '"')     # maxLength
+    assert pc.forced_text('{"name": "Bo"') == ', "age": ' and pc.forced_text('{"name": "Bo", "age": ') == ""
+    assert pc.allowed('{"name": "Bo", "age": ', "4") and not pc.allowed('{"name": "Bo", "age": ', "4.") and not pc.allowed('{"name": "Bo", "age": ', "04")
+    assert pc.allowed('{"name": "Bo", "age": 4', ', "ok": ')                     # a whole number hands the next character on
+    t = '{"name": "Bo", "age": 4, "ok": '
+    assert pc.forced_text(t) == "" and pc.allowed(t, "tr") and pc.allowed(t, "false") and not pc.allowed(t, "maybe")
+    t += 'false, "tags": ['
+    assert pc.forced_text(t) == '"' and not pc.allowed(t, "]")                   # minItems 1: the array may not close yet
+    t += '"a"'
+    assert pc.allowed(t, "]") and pc.allowed(t, ', "b"') and not pc.allowed(t, ', "c"')
+    t += ', "b"'
+    assert pc.forced_text(t) == '], "pos": {"x": ' and not pc.allowed(t, ', "a"')   # maxItems 2: only the close is left
+    t += '], "pos": {"x": 2'
+    assert not pc.done(t) and pc.allowed(t, '}, "kind": "v1"}')
+    t += '}, "kind": "v1"}'
+    assert pc.done(t) and pc.closed(t) and not pc.allowed(t, "x")
+    assert ProgramConstraint({"type": "number"}).done("3.25") and not ProgramConstraint({"type": "number"}).done("3.")
+    assert ProgramConstraint({"anyOf": [{"type": "null"}, {"type": "integer"}]}).allowed("", "nu")
+    with pytest.raises(Unsupported):
+        compile_schema({"type": "object"})                                        # no property list: not a program
+    assert constraint_for({"type": "object"}) is None and constraint_for(None) is None
+
+
 def test_prompt_cache_rules():
     pc = PromptCache(100)
     s = lambda ids, n: Saved(tuple(ids), None, n)
