@@ -4,13 +4,16 @@
 //
 // One CTA = one query head x 128 consecutive query positions (the 128 lanes of tensor memory).  Per 128-key tile:
 //   S = Q K^T          tcgen05.mma kind::f16, M = N = 128, depth 128 (two 64-wide swizzle atoms), into TMEM
-//   softmax            each of 128 threads owns one query row: tcgen05.ld of its 128 scores, running max / sum
-//                      (base-2 exponentials), causal mask on the diagonal tiles, probabilities as bf16 into a
-//                      128-byte-swizzled shared-memory tile
-//   O = O * corr       the running output is rescaled in TMEM (tcgen05.ld / tcgen05.st) when the row maximum moved
+//   softmax            two threads own one query row, 64 of its 128 scores each (one tcgen05.ld pass, the scores stay
+//                      in registers between the maximum and the exponentials): the halves' maxima meet through shared
+//                      memory and a bounded mbarrier, running max / sum in base 2, causal mask on the diagonal tiles,
+//                      probabilities as bf16 into a 128-byte-swizzled shared-memory tile (one swizzle atom per half)
+//   O = O * corr       the running output is rescaled in TMEM (tcgen05.ld / tcgen05.st), each half its 64 columns, and
+//                      only when the row maximum moved by more than 2^8: until then the old maximum keeps scaling the
+//                      exponentials (they stay below 2^8, far inside fp32 and bf16), so most tiles skip the round trip
 //   O += P V           tcgen05.mma with P as the A operand and the (dims x keys) value tile as B
-// Roles: warps 0..3 softmax (their warp id is their TMEM lane quarter), warp 4 the TMA producer (two-stage rings
-// for keys and values), warp 5 the MMA issuer and TMEM owner.  The score accumulator is double-buffered, so the
+// Roles: warps 0..3 and 6..9 softmax (warp id modulo 4 = TMEM lane quarter; 0..3 take score columns 0..63, 6..9
+// columns 64..127), warp 4 the TMA producer (two-stage rings for keys and values), warp 5 the MMA issuer and TMEM owner.  The score accumulator is double-buffered, so the
 // product of tile t + 1 runs while the softmax of tile t is still busy; the second product of tile t is issued one
 // iteration late for the same reason.  Every TMA load is a plain tile load of this GPU's own memory.
 //
@@ -49,11 +52,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
-__global__ void __launch_bounds__(192, 1)
+constexpr int FTHREADS = 320;
+constexpr float kLazy = 8.0f;                           // the maximum may lag by 2^8 before the output is rescaled
+
+__global__ void __launch_bounds__(FTHREADS, 1)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const FlashPrefillArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, o_done;
+  __shared__ __align__(8) uint64_t mx_full[2], l_full;
+  __shared__ float s_mx[2][2][FQ];                      // [score buffer][half][row]: the halves' tile maxima
+  __shared__ float s_l[2][FQ];                          // [half][row]: the halves' sums at the end
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -72,9 +81,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     mbar_init(&q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8); mbar_init(&mx_full[i], 8);
     }
-    mbar_init(&p_full, 4); mbar_init(&o_done, 1);
+    mbar_init(&p_full, 8); mbar_init(&o_done, 1); mbar_init(&l_full, 8);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -153,79 +162,97 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       if (ok && !*abort_flag) pv(n_t - 1);
     }
   } else {
-    // ---- softmax: thread = one query row ----------------------------------------------------------------
-    const int r = warp * 32 + lane;
+    // ---- softmax: two threads per query row, 64 score columns each ---------------------------------------
+    const int half = warp >= 6 ? 1 : 0;
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;
     const int qrow = q0 + r;
     const int qpos = a.pos0 + qrow;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+    const int col0 = half * 64;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int t = 0; t < n_t && !*abort_flag; ++t) {
       const int b = t & 1;
-      if (!mbar_wait(&s_full[b], (uint32_t)((t >> 1) & 1), abort_flag)) { ok = false; break; }
+      const uint32_t par = (uint32_t)((t >> 1) & 1);
+      if (!mbar_wait(&s_full[b], par, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int k0 = t * FKEYS;
-      const bool diag = k0 + FKEYS - 1 > a.pos0 + q0;           // some key of this tile lies past some query of it
-      const uint32_t tS = tS0 + b * FKEYS + lane_base;
+      const int k0 = t * FKEYS + col0;
+      const bool diag = t * FKEYS + FKEYS - 1 > a.pos0 + q0;    // some key of this tile lies past some query of it
+      const uint32_t tS = tS0 + b * FKEYS + lane_base + col0;
+      uint32_t v0[32], v1[32];
+      tmem_ld32(tS, v0);
+      tmem_ld32(tS + 32, v1);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        tmem_ld_wait();
+      if (diag) {                                               // only the tiles on the diagonal pay for the mask
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (diag && k0 + c * 32 + i > qpos) s = -INFINITY;
-          mx = fmaxf(mx, s);
+          if (k0 + i > qpos) v0[i] = 0xff800000u;               // -inf
+          if (k0 + 32 + i > qpos) v1[i] = 0xff800000u;
         }
       }
-      const float m_new = fmaxf(m, mx);
+      {
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;     // four chains instead of one
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          mx0 = fmaxf(mx0, __uint_as_float(v0[i])); mx1 = fmaxf(mx1, __uint_as_float(v0[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(v1[i])); mx3 = fmaxf(mx3, __uint_as_float(v1[i + 1]));
+        }
+        mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      }
+      // the other half's maximum of this row
+      s_mx[b][half][r] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&mx_full[b]);
+      if (!mbar_wait(&mx_full[b], par, abort_flag)) { ok = false; break; }
+      mx = fmaxf(mx, s_mx[b][half ^ 1][r]);
+      float m_new = fmaxf(m, mx);
+      if (m != -INFINITY && (m_new - m) * kLog2e <= kLazy) m_new = m;     // both halves see the same numbers: same choice
       const float mb = (m_new == -INFINITY) ? 0.f : m_new * kLog2e;       // a row with no key yet keeps zeros
       const float corr = (m == -INFINITY) ? 0.f : ex2(m * kLog2e - mb);
-      if (t > 0) {
+      // the previous value product has to be complete only when some row of this warp rescales its output
+      if (t > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
         if (!mbar_wait(&o_done, (uint32_t)((t - 1) & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, corr != 1.0f)) {
+        {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t v[32];
-            tmem_ld32(tO + lane_base + c * 32, v);
+            tmem_ld32(tO + lane_base + col0 + c * 32, v);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-            tmem_st32(tO + lane_base + c * 32, v);
+            tmem_st32(tO + lane_base + col0 + c * 32, v);
           }
           tmem_st_wait();
         }
       }
-      float rowsum = 0.f;
-      uint8_t* prow = sP + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        tmem_ld_wait();
+      float rowsum = 0.f, rowsum1 = 0.f;
+      uint8_t* prow = sP + half * FHALF + (r >> 3) * 1024 + (r & 7) * 128;     // this half's swizzle atom
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-          float p0 = ex2(s0 * kLog2e - mb), p1 = ex2(s1 * kLog2e - mb);
-          if (diag && k0 + c * 32 + i > qpos) p0 = 0.f;
-          if (diag && k0 + c * 32 + i + 1 > qpos) p1 = 0.f;
-          if (m_new == -INFINITY) { p0 = 0.f; p1 = 0.f; }
-          rowsum += p0 + p1;
+          // (s0, s1) * log2(e) - mb as one packed FMA; masked scores are -inf and 2^-inf = 0 (a row without any key
+          // has mb = 0 and only -inf scores, so it needs no special case)
+          uint32_t e0, e1;
+          asm("{\n\t.reg .b64 rs, rk, rm, rr;\n\t"
+              "mov.b64 rs, {%2, %3};\n\tmov.b64 rk, {%4, %4};\n\tmov.b64 rm, {%5, %5};\n\t"
+              "fma.rn.f32x2 rr, rs, rk, rm;\n\tmov.b64 {%0, %1}, rr;\n\t}"
+              : "=r"(e0), "=r"(e1) : "r"(c ? v1[i] : v0[i]), "r"(c ? v1[i + 1] : v0[i + 1]), "f"(kLog2e), "f"(-mb));
+          const float p0 = ex2(__uint_as_float(e0)), p1 = ex2(__uint_as_float(e1));
+          rowsum += p0; rowsum1 += p1;
           pk[i >> 1] = pack_bf16(p0, p1);
         }
-        // columns c*32 .. c*32+31 of row r: swizzle atom c >> 1, 16-byte chunks (c & 1) * 4 .. + 3, XOR-swizzled by the row
-        uint8_t* half = prow + (c >> 1) * FHALF;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int chunk = ((c & 1) * 4 + j) ^ (r & 7);
-          *reinterpret_cast<uint4*>(half + chunk * 16) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          const int chunk = (c * 4 + j) ^ (r & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
         }
       }
-      l = l * corr + rowsum;
+      l = l * corr + (rowsum + rowsum1);
       m = m_new;
       tc_fence_before();
       fence_async_smem();
@@ -234,22 +261,28 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     }
     if (ok && !*abort_flag && mbar_wait(&o_done, (uint32_t)((n_t - 1) & 1), abort_flag)) {
       tc_fence_after();
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      __nv_bfloat16* orow = a.out + (long)qrow * a.ldo + (long)h * FD;
+      s_l[half][r] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&l_full);
+      if (mbar_wait(&l_full, 0, abort_flag)) {
+        const float lt = s_l[0][r] + s_l[1][r];
+        const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+        __nv_bfloat16* orow = a.out + (long)qrow * a.ldo + (long)h * FD + col0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tO + lane_base + c * 32, v);
-        tmem_ld_wait();
-        if (qrow < a.T) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tO + lane_base + col0 + c * 32, v);
+          tmem_ld_wait();
+          if (qrow < a.T) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 pk;
-            pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-            pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-            pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-            pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + i) = pk;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 pk;
+              pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+              pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+              pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+              pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + i) = pk;
+            }
           }
         }
       }
@@ -308,7 +341,7 @@ int bl_flash_prefill(const void* q, const void* k, const void* vt, void* out, lo
     attr_set = true;
   }
   dim3 grid((T + FQ - 1) / FQ, n_q);
-  return (int)launch(flash_prefill_kernel, grid, dim3(192), (size_t)FSMEM, st, mq, mk, mv, a);
+  return (int)launch(flash_prefill_kernel, grid, dim3(FTHREADS), (size_t)FSMEM, st, mq, mk, mv, a);
 }
 
 }  // extern "C"
