@@ -5,8 +5,8 @@ Two shared objects are produced under ``bloomery_b200/_C``:
 * ``libbloomery_cuda.so`` -- every ``csrc/*.cu`` compiled for ``sm_100a`` only
   (``-gencode arch=compute_100a,code=sm_100a``); plain C ABI, loaded with ctypes.
 * ``libbloomery_host.so`` -- ``csrc/host/*.cpp``: GGUF block decode oracle, CPU
-  quantised dots (scalar mirror of the device units + AVX2 paths for Q4_K, Q6_K and Q8_0 rows picked
-  at run time), the worker pool and the CPU expert leg.
+  quantised dots (scalar mirror of the device units, AVX2 paths for Q4_K, Q6_K and Q8_0 rows and AVX-512 VNNI paths
+  for Q4_K, Q5_K, Q6_K, Q8_0 and the int8 + f32-scale rows, picked at run time by CPU feature), the worker pool and the CPU expert leg.
 
 nvcc cross-compiles without a GPU, so ``python -m bloomery_b200.build`` is also the
 "does it build" check.  A content hash of sources and flags makes a rebuild a no-op.

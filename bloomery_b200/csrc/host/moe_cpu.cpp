@@ -28,6 +28,7 @@
 #include "../quant_units.cuh"
 #include "pool.h"
 #include "qdot_avx2.h"
+#include "qdot_vnni.h"
 
 using namespace bl;
 
@@ -35,6 +36,7 @@ namespace {
 
 float dot_any(int wtype, const uint8_t* row, int K, const int8_t* xq, const float* xds) {
   float fast;
+  if (blh::row_dot_vnni(wtype, row, K, xq, xds, &fast)) return fast;        // AVX-512 VNNI where the CPU has it
   if (blh::row_dot_fast(wtype, row, K, xq, xds, &fast)) return fast;        // AVX2 paths of the Q4_K_M mix
   auto run = [&](auto tag) {
     using T = decltype(tag);

@@ -12,6 +12,7 @@
 #include "../quant_units.cuh"
 #include "pool.h"
 #include "qdot_avx2.h"
+#include "qdot_vnni.h"
 
 using namespace bl;
 
@@ -76,6 +77,12 @@ extern "C" {
 int blh_row_dot_fast(int wtype, const uint8_t* row, int K, const int8_t* xq, const float* xds, float* out) {
   return blh::row_dot_fast(wtype, row, K, xq, xds, out) ? 1 : 0;
 }
+
+// the AVX-512 VNNI path's dot of one row; 0 when the CPU lacks the instructions or the type has no such path
+int blh_row_dot_vnni(int wtype, const uint8_t* row, int K, const int8_t* xq, const float* xds, float* out) {
+  return blh::row_dot_vnni(wtype, row, K, xq, xds, out) ? 1 : 0;
+}
+int blh_cpu_has_vnni() { return blh::cpu_has_vnni() ? 1 : 0; }
 
 long blh_resident_row_bytes(int wtype, int K) { return resident_row_bytes(wtype, K); }
 

@@ -433,3 +433,34 @@ def test_vector_row_dots_agree_with_the_scalar_units(t):
         assert abs(o.value - float(ref[r])) <= 1e-5 * float(ref.abs().max())
         assert abs(o.value - float(scalar[r])) <= 2e-6 * float(ref.abs().max())
     assert served in (0, 40)            # 0 on a host without AVX2: the scalar units serve every type
+
+
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "IQ4_XS"])
+def test_vnni_row_dots_agree_with_the_scalar_units(t):
+    """The AVX-512 VNNI row dots (picked at run time where the CPU has them) against the f64 reference and the scalar
+    units; IQ4_XS stands for the int8-code + f32-scale rows every code-book type is loaded as."""
+    import ctypes
+    from bloomery_b200.formats.resident import WT, resident_type
+    from bloomery_b200.ops._lib import host, p as vp
+    torch.manual_seed(12)
+    K = 2048
+    w = torch.randn(33, K) * 0.02
+    w[5, 9] = -0.8
+    raw = Q.quantize(w, t)
+    res = to_resident(raw, t, K)
+    rt = resident_type(t)
+    wd = Q.dequantize(raw, t, K)
+    x = torch.randn(1, K)
+    x[0, 77] = 31.0
+    codes, ds = H.act_q8(x)
+    ref = (Q.dequantize_act_q8(codes, ds).double() @ wd.double().T)[0]
+    served = 0
+    for r in range(33):
+        o = ctypes.c_float()
+        served += host().blh_row_dot_vnni(WT[rt], vp(res[r]), K, vp(codes), vp(ds), ctypes.byref(o))
+        if served:
+            assert abs(o.value - float(ref[r])) <= 1e-5 * float(ref.abs().max()), (r, o.value, float(ref[r]))
+    assert served == (33 if host().blh_cpu_has_vnni() else 0)
+    # the pool's gemv takes the same path: its rows agree with the reference too
+    out = H.gemv(res, rt, K, codes, ds)[0]
+    assert ((out - ref.float()).abs().max() / ref.abs().max()).item() < 1e-5
