@@ -276,11 +276,80 @@ def _dsml_block(body: str, i_open, i_close, p_open, p_close, first_index: int) -
         pos = e + len(i_close)
 
 
+def parse_muse(text: str) -> Dict[str, Any]:
+    """The recipient protocol with ATEM call markup (``crates/serve/src/museatem.rs`` in the reference): a turn is one
+    or more messages `` to=<recipient><|message|>BODY`` ended by ``<|eom|>`` (more follow, each reopened by
+    ``<|start|>assistant``) or ``<|eot|>``.  Recipient ``self`` is reasoning, ``commentary`` and ``user`` are content,
+    any other name is a tool call whose body is
+
+        <atem:function_calls><atem:invoke name="NAME"><atem:parameter name="KEY">VALUE</atem:parameter></atem:invoke></atem:function_calls>
+
+    A value is JSON when it parses, else text.  Markup that does not parse, text that is no message open and a message
+    the text ends inside go to their channel as raw text.  Returns reasoning_content / content / tool_calls."""
+    reasoning, content, calls = [], [], []
+    pos = 0
+    head = re.compile(r"\s*(?:<\|start\|>assistant)?\s*to=([^\s<]+)<\|message\|>")
+    while pos < len(text):
+        m = head.match(text, pos)
+        if not m:
+            content.append(text[pos:])
+            break
+        ends = [(text.find(t, m.end()), t) for t in ("<|eom|>", "<|eot|>")]
+        ends = [(i, t) for i, t in ends if i >= 0]
+        end, tok = min(ends) if ends else (len(text), "")
+        body, who = text[m.end():end], m.group(1)
+        if who == "self":
+            reasoning.append(body)
+        elif who in ("commentary", "user"):
+            content.append(body)
+        else:
+            got = _atem_calls(body, len(calls)) if tok else None
+            if got is None:
+                content.append(text[pos:end + len(tok)])
+            else:
+                calls.extend(got)
+        pos = end + len(tok)
+        if tok == "<|eot|>":
+            content.append(text[pos:])
+            break
+    return {"reasoning_content": "\n".join(s.strip() for s in reasoning if s.strip()),
+            "content": "\n".join(s.strip() for s in content if s.strip()), "tool_calls": calls}
+
+
+def _atem_calls(body: str, first_index: int) -> Optional[List[dict]]:
+    m = re.fullmatch(r"\s*<atem:function_calls>(.*)</atem:function_calls>\s*", body, re.S)
+    if not m:
+        return None
+    calls, pos, inner = [], 0, m.group(1)
+    for inv in re.finditer(r'\s*<atem:invoke name="([^"]*)">(.*?)</atem:invoke>', inner, re.S):
+        if inv.start() != pos:
+            return None
+        args, ipos, params = {}, 0, inv.group(2)
+        for prm in re.finditer(r'\s*<atem:parameter name="([^"]*)">(.*?)</atem:parameter>', params, re.S):
+            if prm.start() != ipos:
+                return None
+            try:
+                args[prm.group(1)] = json.loads(prm.group(2))
+            except json.JSONDecodeError:
+                args[prm.group(1)] = prm.group(2)
+            ipos = prm.end()
+        if params[ipos:].strip():
+            return None
+        calls.append(_call(inv.group(1), args, first_index + len(calls)))
+        pos = inv.end()
+    if inner[pos:].strip() or not calls:
+        return None
+    return calls
+
+
 TOOL_PARSERS = {"hermes": parse_hermes, "qwenxml": parse_qwen_xml, "glmxml": parse_glm_xml, "mistral": parse_mistral,
-                "dsml": lambda t: parse_dsml(t, False), "dsml_spaced": lambda t: parse_dsml(t, True)}
+                "dsml": lambda t: parse_dsml(t, False), "dsml_spaced": lambda t: parse_dsml(t, True),
+                "muse": lambda t: (lambda r: (r["content"], r["tool_calls"]))(parse_muse(t))}
 
 
 def detect_tool_format(template_source: str) -> str:
+    if "<atem:" in template_source:
+        return "muse"
     if DSML in template_source:
         return "dsml_spaced" if f"<{DSML} " in template_source else "dsml"
     if "<function=" in template_source:

@@ -317,6 +317,10 @@ def main(argv: Optional[List[str]] = None) -> int:
             return server.wait()
         if not opts.get("model"):
             raise Refusal(Code.NO_MODEL, "no model was named; use -m FILE (a GGUF file, any shard of a split) or --mock")
+        from . import preflight
+        refusal = preflight.run(n_vis, str(opts.get("dev") or ""))
+        if refusal:
+            raise Refusal(Code.NO_DEVICE, refusal)
         if not os.path.exists(opts["model"]):
             raise Refusal(Code.NO_MODEL, f"{opts['model']}: no such file")
         server.state.phase = "plan"

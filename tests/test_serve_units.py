@@ -229,6 +229,39 @@ def test_dsml_tool_calls_both_spellings_and_streaming():
         assert out.strip() == "On it." and [c["function"]["arguments"] for c in got] == [c["function"]["arguments"] for c in calls]
 
 
+def test_muse_recipient_protocol_and_atem_calls():
+    text = (' to=self<|message|>think first<|eom|>\n<|start|>assistant to=commentary<|message|>working on it<|eom|>\n'
+            '<|start|>assistant to=get_weather<|message|><atem:function_calls>\n<atem:invoke name="get_weather">\n'
+            '<atem:parameter name="city">Paris</atem:parameter>\n<atem:parameter name="days">3</atem:parameter>\n'
+            '</atem:invoke>\n</atem:function_calls><|eom|>\n<|start|>assistant to=user<|message|>done<|eot|>')
+    r = C.parse_muse(text)
+    assert r["reasoning_content"] == "think first" and r["content"] == "working on it\ndone"
+    assert r["tool_calls"][0]["function"]["name"] == "get_weather"
+    assert json.loads(r["tool_calls"][0]["function"]["arguments"]) == {"city": "Paris", "days": 3}
+    assert C.parse_tool_calls(text, "muse")[1][0]["function"]["name"] == "get_weather"
+    broken = ' to=lookup<|message|><atem:function_calls><atem:invoke name="x">oops</atem:invoke></atem:function_calls><|eot|>'
+    rb = C.parse_muse(broken)
+    assert rb["tool_calls"] == [] and "oops" in rb["content"]                    # markup that does not parse stays content
+    assert C.parse_muse("plain text")["content"] == "plain text"
+    assert C.parse_muse(" to=user<|message|>cut off mid")["content"] == "cut off mid"
+    assert C.detect_tool_format("... <atem:invoke ...") == "muse"
+
+
+def test_preflight_verdicts():
+    from bloomery_b200.serve import preflight as P
+    assert P.cpu_gate(["sse4_2", "avx2", "fma", "f16c", "bmi2"]) is None
+    msg = P.cpu_gate(["sse4_2", "avx", "fma"])
+    assert "avx2" in msg and "f16c" in msg and "fma" not in msg.split(":")[0]
+    assert P.cpu_gate([], machine="aarch64") is None
+    assert P.parse_driver("NVRM version: NVIDIA UNIX Open Kernel Module for x86_64  580.159.01  Release") == (580, 159)
+    assert P.driver_gate("580.159") is None and P.driver_gate(None) is None and P.driver_gate("garbage") is None
+    assert "535.183" in P.driver_gate("535.183.01") and "R570" in P.driver_gate("535.183.01")
+    assert P.no_card(1, []) is None
+    assert "no CUDA device on this machine" in P.no_card(0, []) and "-dev none" in P.no_card(0, [])
+    assert "lists 2" in P.no_card(0, ["NVIDIA B200", "NVIDIA B200"])
+    assert P.run(0, "none") is None                                                # the CPU engine needs no card
+
+
 def test_per_key_limits():
     from bloomery_b200.serve.admit import Admission, LimitError, Limits, Refused, parse_key_line
     key, lim = parse_key_line("sk-one inflight=2 rate=30/m burst=3")
