@@ -226,6 +226,8 @@ def main() -> int:
                     help="smoke runs only: cut the model to this many layers (the line is marked and is not a benchmark)")
     ap.add_argument("--cpu", action="store_true",
                     help="the CPU configuration: tiny Qwen3-MoE (Q4_K_M), 64-id prompt, 32 greedy tokens on the host engine, no GPU")
+    ap.add_argument("--tp-attn", dest="tp_attn", action="store_true",
+                    help="N > 1: split the attention heads over the ranks for decode too (two reductions per layer)")
     ap.add_argument("--nccl-baseline", dest="nccl_baseline", action="store_true",
                     help="N > 1: do the per-layer reductions with NCCL all_reduce instead of the fused kernels")
     args = ap.parse_args()

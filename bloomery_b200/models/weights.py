@@ -48,10 +48,14 @@ def _rand(shape, std, gen, device):
     return torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std
 
 
-def shard_shape(name: str, shape, spec: ModelSpec, rank: int, world: int):
+def shard_shape(name: str, shape, spec: ModelSpec, rank: int, world: int, attn: bool = True):
     """Shape of rank ``rank``'s share of a tensor under the head / expert / width split of the sharded engines
-    (``parallel/sharded.py`` ``shard_items``), and whether the tensor is split at all."""
+    (``parallel/sharded.py`` ``shard_items``), and whether the tensor is split at all.  ``attn`` off leaves the
+    attention matrices whole (the replicated-attention engine)."""
     shape = tuple(shape)
+    if not attn and name.endswith(("attn_q.weight", "attn_q_b.weight", "attn_k.weight", "attn_v.weight", "attn_k_b.weight",
+                                   "attn_v_b.weight", "attn_output.weight")):
+        return shape, False
     rows_split = ("attn_q.weight", "attn_q_b.weight", "ffn_gate.weight", "ffn_up.weight", "ffn_gate_shexp.weight",
                   "ffn_up_shexp.weight")
     cols_split = ("attn_output.weight", "ffn_down.weight", "ffn_down_shexp.weight")
@@ -67,7 +71,7 @@ def shard_shape(name: str, shape, spec: ModelSpec, rank: int, world: int):
 
 
 def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K_M", std: float = 0.02,
-                  with_vocab: bool = False, shard: Optional[Tuple[int, int]] = None) -> Iterator[TensorItem]:
+                  with_vocab: bool = False, shard: Optional[Tuple[int, int]] = None, shard_attn: bool = True) -> Iterator[TensorItem]:
     """Seeded N(0, std) weights of ``spec``, quantised per ``mix`` ("Q4_K_M", "Q8_0", "F16", ...).
 
     ``shard`` = (rank, world): only that rank's share of every split tensor is generated, in the local shape the
@@ -94,7 +98,7 @@ def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K
     def emit(name: str, shape, il: int = 0, std_=std, ones: bool = False) -> TensorItem:
         t = qt(name, il)
         if shard is not None:
-            shape, split = shard_shape(name, shape, spec, shard[0], shard[1])
+            shape, split = shard_shape(name, shape, spec, shard[0], shard[1], shard_attn)
             per_tensor.reseed(name, split)
         if ones:
             w = torch.ones(*shape, device=device) + _rand(shape, 0.02, gen, device)
@@ -127,12 +131,12 @@ def synth_tensors(spec: ModelSpec, device="cpu", seed: int = 0, mix: str = "Q4_K
             # the per-head products keep float weights: [head][nope][latent] and [head][v][latent]
             nh = spec.n_q
             if shard is not None:
-                nh = spec.n_q // shard[1]
-                per_tensor.reseed(b + "attn_k_b.weight", True)
+                nh = spec.n_q // shard[1] if shard_attn else spec.n_q
+                per_tensor.reseed(b + "attn_k_b.weight", shard_attn)
             yield (b + "attn_k_b.weight", (nh, spec.nope_dim, spec.kv_lora), "F32",
                    _rand((nh * spec.nope_dim, spec.kv_lora), 0.05, gen, device).view(torch.uint8))
             if shard is not None:
-                per_tensor.reseed(b + "attn_v_b.weight", True)
+                per_tensor.reseed(b + "attn_v_b.weight", shard_attn)
             yield (b + "attn_v_b.weight", (nh, spec.v_dim, spec.kv_lora), "F32",
                    _rand((nh * spec.v_dim, spec.kv_lora), 0.05, gen, device).view(torch.uint8))
             yield emit(b + "attn_output.weight", (H, spec.n_q * spec.v_dim), il)

@@ -25,12 +25,14 @@ def run_distributed(args, rank: int, local: int, world: int) -> int:
     if getattr(args, "layers", 0):
         import dataclasses
         spec = dataclasses.replace(spec, n_layer=args.layers, n_mtp=0)
-    lspec = local_spec(spec, world)
+    # decode of a few rows: attention whole on every rank, FFN half split, one reduction per layer (--tp-attn: heads split too)
+    rep = not getattr(args, "tp_attn", False)
+    lspec = local_spec(spec, world, attn=not rep)
     steps, warm = args.steps, max(3, args.warmup)
     t0 = time.time()
     mix = getattr(args, "mix", "") or "Q4_K_M"
     # every rank builds only its own share (a model that fits no single card is never built whole)
-    w = Weights.from_items(lspec, synth_tensors(spec, dev, seed=0, mix=mix, shard=(rank, world)), dev)
+    w = Weights.from_items(lspec, synth_tensors(spec, dev, seed=0, mix=mix, shard=(rank, world), shard_attn=not rep), dev)
     torch.cuda.synchronize()
     t_load = time.time() - t0
     fused = not getattr(args, "nccl_baseline", False)
@@ -38,7 +40,9 @@ def run_distributed(args, rank: int, local: int, world: int) -> int:
     # the fused arm replays one CUDA graph per step.  The NCCL arm runs eager: captured into the step graph its
     # all-reduces did not come back on two B200s (the run sat until its time limit), so that form is not used.
     eng = ShardedEngine(w, spec, rank, world, fused=fused, n_slots=1, slot_ctx=(ctx + 63) // 64 * 64,
-                        use_graphs=fused)
+                        use_graphs=fused, attn_replicated=rep)
+    if rep:
+        eng.gemm_threshold = 0          # prompts of this engine take the pass path; the head-split engine below times TTFT
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, spec.vocab, (args.prompt,), generator=g).tolist()
     dist.barrier()
@@ -94,26 +98,32 @@ def run_distributed(args, rank: int, local: int, world: int) -> int:
     torch.cuda.synchronize()
     e2e_s = D.max_over_ranks(time.perf_counter() - t0, dev)
     extra = {}
-    if getattr(args, "ttft", 0) and fused and eng.gemm_threshold:
+    eng_p = eng
+    if getattr(args, "ttft", 0) and fused and rep and not (spec.mla or spec.n_shared):
+        # the prompt path splits the heads as well (all-gather / reduce-scatter inside the GEMMs): its own engine
+        lspec_tp = local_spec(spec, world)
+        w_tp = Weights.from_items(lspec_tp, synth_tensors(spec, dev, seed=0, mix=mix, shard=(rank, world)), dev)
+        eng_p = ShardedEngine(w_tp, spec, rank, world, fused=True, n_slots=1, slot_ctx=(ctx + 63) // 64 * 64, use_graphs=True)
+    if getattr(args, "ttft", 0) and fused and eng_p.gemm_threshold:
         # time to first token of a long prompt through the several-GPU GEMM path (collectives inside the GEMMs)
         p2 = torch.randint(0, spec.vocab, (args.ttft,), generator=g).tolist()
         ts = []
         for _ in range(3):
-            eng.reset(0)
+            eng_p.reset(0)
             torch.cuda.synchronize()
             dist.barrier()
             t0 = time.perf_counter()
-            eng.prefill(0, p2, gemm=True)
+            eng_p.prefill(0, p2, gemm=True)
             torch.cuda.synchronize()
             ts.append(D.max_over_ranks((time.perf_counter() - t0) * 1e3, dev))
         # the token after the prompt must be the same on every rank and (up to a bf16 arg-max flip) equal to the
         # one the 8-row pass path gives
-        eng.reset(0)
-        tok_gemm = eng.prefill(0, p2, gemm=True)
-        eng.reset(0)
-        tok_steps = eng.prefill(0, p2[:512], gemm=False)
-        eng.reset(0)
-        tok_gemm_512 = eng.prefill(0, p2[:512], gemm=True)
+        eng_p.reset(0)
+        tok_gemm = eng_p.prefill(0, p2, gemm=True)
+        eng_p.reset(0)
+        tok_steps = eng_p.prefill(0, p2[:512], gemm=False)
+        eng_p.reset(0)
+        tok_gemm_512 = eng_p.prefill(0, p2[:512], gemm=True)
         tt = torch.tensor([tok_gemm, tok_gemm_512], dtype=torch.int64, device=dev)
         tmx, tmn = tt.clone(), tt.clone()
         dist.all_reduce(tmx, op=dist.ReduceOp.MAX)
@@ -132,7 +142,9 @@ def run_distributed(args, rank: int, local: int, world: int) -> int:
             "dtype": f"{mix.lower()} weights, int8 dot / fp32 accumulate, f16 KV",
             "data": f"synthetic: seeded random token ids, random-init N(0,0.02) weights quantised {mix} on the card",
             "config": {"model": spec.name, "global_batch": 1, "seq_len": args.prompt + warm + steps,
-                       "prompt_tokens": args.prompt, "parallelism": f"tp{world} attention + ep{world} experts",
+                       "prompt_tokens": args.prompt, "parallelism": (f"ep{world} experts (FFN width split), attention replicated: one reduction per layer" if rep
+                                       else f"tp{world} attention + ep{world} experts"),
+                       "ttft_engine": f"tp{world} attention + ep{world} experts",
                        "reductions": "fused: producer pushes partial rows to peer HBM, consumer prologue sums"
                        if fused else "nccl all_reduce (baseline)",
                        "l2": "weights exceed L2; no flush needed", "graph": "one CUDA graph per decode step" if fused else "eager",

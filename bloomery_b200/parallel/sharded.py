@@ -36,8 +36,13 @@ from .symm import SymmetricArena
 SITE_ATTN, SITE_MOE = 0, 1
 
 
-def shard_items(items: Iterator[TensorItem], spec: ModelSpec, rank: int, world: int) -> Iterator[TensorItem]:
-    """Slice a full tensor stream down to one rank's share (raw block bytes, no re-quantisation)."""
+ATTN_NAMES = ("attn_q.weight", "attn_q_b.weight", "attn_k.weight", "attn_v.weight", "attn_k_b.weight", "attn_v_b.weight",
+              "attn_output.weight")
+
+
+def shard_items(items: Iterator[TensorItem], spec: ModelSpec, rank: int, world: int, attn: bool = True) -> Iterator[TensorItem]:
+    """Slice a full tensor stream down to one rank's share (raw block bytes, no re-quantisation).  ``attn`` off keeps
+    the attention matrices whole on every rank (the replicated-attention engine)."""
     if spec.n_q % world or (spec.is_moe and spec.n_expert % world):
         raise ValueError(f"{world} ranks do not divide {spec.n_q} heads / {spec.n_expert} experts")
     hd = spec.head_dim
@@ -65,7 +70,9 @@ def shard_items(items: Iterator[TensorItem], spec: ModelSpec, rank: int, world: 
         kvh = rank // (world // spec.n_kv)
         kv_lo, kv_hi = kvh * hd, (kvh + 1) * hd
     for name, shape, qtype, raw in items:
-        if name.endswith("attn_q.weight") or name.endswith("attn_q_b.weight"):
+        if not attn and name.endswith(ATTN_NAMES):
+            yield name, shape, qtype, raw
+        elif name.endswith("attn_q.weight") or name.endswith("attn_q_b.weight"):
             yield name, (q_hi - q_lo, shape[1]), qtype, raw[q_lo:q_hi]
         elif name.endswith("attn_k.weight") or name.endswith("attn_v.weight"):
             yield name, (kv_hi - kv_lo, shape[1]), qtype, raw[kv_lo:kv_hi]
@@ -85,10 +92,11 @@ def shard_items(items: Iterator[TensorItem], spec: ModelSpec, rank: int, world: 
             yield name, shape, qtype, raw
 
 
-def local_spec(spec: ModelSpec, world: int) -> ModelSpec:
+def local_spec(spec: ModelSpec, world: int, attn: bool = True) -> ModelSpec:
     s = dataclasses.replace(spec)
-    s.n_q = spec.n_q // world
-    s.n_kv = max(1, spec.n_kv // world)
+    if attn:
+        s.n_q = spec.n_q // world
+        s.n_kv = max(1, spec.n_kv // world)
     if spec.dense_inter:
         s.dense_inter = spec.dense_inter // world
     if spec.n_shared:
@@ -100,10 +108,15 @@ class ShardedEngine(DecodeEngine):
     """One rank of the TP-attention + EP-experts decode engine."""
 
     def __init__(self, weights: Weights, full_spec: ModelSpec, rank: int, world: int, group=None, fused: bool = True,
-                 arena: Optional[SymmetricArena] = None, **kw):
+                 arena: Optional[SymmetricArena] = None, attn_replicated: bool = False, **kw):
+        """``attn_replicated``: every rank runs the whole attention half on whole attention weights and only the FFN
+        half (experts by index, dense and shared width) is split, so a layer has ONE reduction instead of two.  For a
+        few rows of decode the chain is bound by latency, not by the bytes of the attention weights, and the
+        reduction it saves is worth more than the split: this is the form whose speed grows with the rank count."""
         self.full_spec = full_spec
         self.rank, self.world, self.group = rank, world, group
         self.fused = fused
+        self.attn_replicated = attn_replicated
         super().__init__(weights, **kw)
         s, dev = self.spec, self.device
         self.arena = arena or SymmetricArena(s.hidden, rank, world, dev, group, local_only=not fused)
@@ -151,9 +164,13 @@ class ShardedEngine(DecodeEngine):
 
         pending = None     # (site, index) whose partials the next consumer has to add
         H = s.hidden
+        rep = self.attn_replicated
         for il in range(s.n_layer):
             b = f"blk.{il}."
             red = None
+            # with one reduction per layer the two receive buffers alternate by layer: a rank that runs ahead writes
+            # layer l + 1 into the buffer its peers are not reading layer l from
+            site_ffn = (il & 1) if rep else SITE_MOE
             if fused and pending is not None:
                 red = ar.reduce(pending[0], pending[1], xb[cur ^ 1], self.fault, il)
             if s.mla:
@@ -196,7 +213,11 @@ class ShardedEngine(DecodeEngine):
                 add(K.flash_decode, self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
                     s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
                     self.attn_q, self.attn_ds, self.fault, il, launches=2)
-            if fused:
+            if rep:
+                add(K.gemv, [w.q[b + "attn_output.weight"]], M, xb[cur], xq=self.attn_q, xds=self.attn_ds, resid=xb[cur],
+                    fault=self.fault, layer=il)
+                red = None
+            elif fused:
                 add(K.gemv, [w.q[b + "attn_output.weight"]], M, self.partial, xq=self.attn_q,
                     xds=self.attn_ds, push=ar.push(SITE_ATTN, 2 * il), fault=self.fault, layer=il)
                 red = ar.reduce(SITE_ATTN, 2 * il, xb[cur ^ 1], self.fault, il)
@@ -215,8 +236,8 @@ class ShardedEngine(DecodeEngine):
                 add(K.swiglu_q8, self.gu, s.dense_inter, M, self.dactq, self.dactds)
                 if fused:
                     add(K.gemv, [w.q[b + "ffn_down.weight"]], M, self.partial, xq=self.dactq, xds=self.dactds,
-                        push=ar.push(SITE_MOE, 2 * il + 1), fault=self.fault, layer=il)
-                    pending = (SITE_MOE, 2 * il + 1)
+                        push=ar.push(site_ffn, 2 * il + 1), fault=self.fault, layer=il)
+                    pending = (site_ffn, 2 * il + 1)
                 else:
                     add(K.gemv, [w.q[b + "ffn_down.weight"]], M, self.partial, xq=self.dactq, xds=self.dactds,
                         fault=self.fault, layer=il)
@@ -251,8 +272,8 @@ class ShardedEngine(DecodeEngine):
             down_fn = K.down_staged if (staged or (fused and K.moe_fits_stage(gate, down, s.n_used, force=True))) else K.down_combine
             if fused:
                 add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, extra,
-                    self.partial, self.fault, il, push=ar.push(SITE_MOE, 2 * il + 1))
-                pending = (SITE_MOE, 2 * il + 1)
+                    self.partial, self.fault, il, push=ar.push(site_ffn, 2 * il + 1))
+                pending = (site_ffn, 2 * il + 1)
             else:
                 add(down_fn, self.actq, self.actds, ids, wts, self.slot_map, down, s.n_expert, s.n_used, M, None, extra,
                     self.partial, self.fault, il)

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _engines(world=2, slot_ctx=256, spec=None):
+def _engines(world=2, slot_ctx=256, spec=None, attn_replicated=False):
     from bloomery_b200.models.spec import tiny_qwen3moe
     from bloomery_b200.models.weights import Weights, synth_tensors
     from bloomery_b200.parallel.sharded import ShardedEngine, local_spec, shard_items
@@ -26,9 +26,10 @@ def _engines(world=2, slot_ctx=256, spec=None):
         a.adopt_peers(arenas)
     engs = []
     for r in range(world):
-        w = Weights.from_items(local_spec(spec, world), shard_items(iter(items), spec, r, world), DEV)
+        w = Weights.from_items(local_spec(spec, world, attn=not attn_replicated),
+                               shard_items(iter(items), spec, r, world, attn=not attn_replicated), DEV)
         engs.append(ShardedEngine(w, spec, r, world, fused=True, arena=arenas[r], n_slots=1, slot_ctx=slot_ctx,
-                                  use_graphs=False))
+                                  use_graphs=False, attn_replicated=attn_replicated))
     return spec, ref, engs
 
 
@@ -97,6 +98,31 @@ def test_emulated_ranks_with_latent_attention_dense_layer_and_shared_expert(worl
     spec, ref, engs = _engines(world, spec=spec)
     g = torch.Generator().manual_seed(6)
     toks = torch.randint(0, spec.vocab, (10,), generator=g).tolist()
+    pos = 0
+    for chunk in (toks[:8], toks[8:]):
+        rows = [(0, t, pos + i) for i, t in enumerate(chunk)]
+        ref.step(rows)
+        _lockstep(engs, rows)
+        pos += len(chunk)
+        n = len(chunk)
+        for e in engs:
+            assert (int(e.fault) & 0xFFFFFFFF) == 0xFFFFFFFF
+            assert torch.equal(e.logits[:n], engs[0].logits[:n])
+        err = ((engs[0].logits[:n] - ref.logits[:n]).abs().max() / ref.logits[:n].abs().max()).item()
+        assert err < 2e-2, err
+        assert all(e.tokens_out[:n].tolist() == engs[0].tokens_out[:n].tolist() for e in engs)
+
+
+@pytest.mark.parametrize("plan", ["qwen", "deepseek"])
+@pytest.mark.parametrize("world", [2, 4])
+def test_replicated_attention_one_reduction_per_layer(world, plan):
+    """Attention whole on every rank, only the FFN half split: one reduction per layer over alternating buffers."""
+    import dataclasses
+    from bloomery_b200.models.spec import tiny_deepseek
+    spec = dataclasses.replace(tiny_deepseek(), shared_inter=256 * world, dense_inter=1024) if plan == "deepseek" else None
+    spec, ref, engs = _engines(world, spec=spec, attn_replicated=True)
+    g = torch.Generator().manual_seed(8)
+    toks = torch.randint(0, spec.vocab, (11,), generator=g).tolist()
     pos = 0
     for chunk in (toks[:8], toks[8:]):
         rows = [(0, t, pos + i) for i, t in enumerate(chunk)]
