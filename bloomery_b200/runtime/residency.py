@@ -157,6 +157,7 @@ class TieredExperts:
         has no source then, so the residency rule is off."""
         self.spec = spec
         self.device = torch.device(device)
+        self.keep_host = keep_host
         E = spec.n_expert
         self.n_slots = max(0, min(n_slots, E))
         self.layers = [il for il in range(spec.n_layer) if spec.layer_is_moe(il)]
@@ -197,6 +198,50 @@ class TieredExperts:
 
     def card_bytes(self) -> int:
         return sum(q.data.numel() for c in self.card.values() for q in c.values())
+
+    def slot_bytes(self) -> int:
+        """Bytes of one resident slot in every routed layer (gate, up and down matrices; the types may differ by layer)."""
+        return sum(int(q.data[0].numel()) for il in self.layers for q in self.card[il].values())
+
+    def resize(self, n_slots: int, heat: Optional[torch.Tensor] = None) -> None:
+        """Change the number of resident slots of every routed layer (between passes, no captured pass alive).
+        Shrinking keeps the hottest residents by ``heat`` ([layer, expert] routed counts; slot order when absent) and
+        hands the rest to the host leg; growing copies the hottest host experts in.  Flips in flight are dropped: their
+        newcomers never became visible in the slot map."""
+        E = self.spec.n_expert
+        n_slots = max(0, min(n_slots, E))
+        if not self.keep_host and n_slots > self.n_slots:
+            raise ValueError("no RAM-resident experts to fill new slots from")
+        self.pending = []
+        for il in self.layers:
+            res = dict(self.slot_of[il])                                   # expert -> slot
+            h = heat[il].tolist() if heat is not None else None
+            rank = (lambda e: (-h[e], e)) if h is not None else (lambda e: (res.get(e, E), e))
+            keep = sorted(res, key=rank)[:n_slots]
+            more = []
+            if n_slots > len(keep):
+                more = sorted((e for e in range(E) if e not in res), key=(lambda e: (-h[e], e)) if h is not None else (lambda e: e))
+                more = more[:n_slots - len(keep)]
+            new_card, order = {}, keep + more
+            for part, old in self.card[il].items():
+                slots = torch.zeros(n_slots + 1, *old.data.shape[1:], dtype=torch.uint8, device=self.device)
+                for i, e in enumerate(keep):
+                    slots[i].copy_(old.data[res[e]])
+                for i, e in enumerate(more):
+                    slots[len(keep) + i].copy_(self.host[il][part].data[e], non_blocking=True)
+                new_card[part] = QWeight(slots, old.qtype, old.k)
+            self.card[il] = new_card
+            sm = torch.full((E,), -1, dtype=torch.int32)
+            for i, e in enumerate(order):
+                sm[e] = i
+            self.slot_map[il].copy_(sm.to(self.device))
+            self.slot_of[il] = {e: i for i, e in enumerate(order)}
+            self.spare[il] = n_slots
+            if self.rule is not None:
+                self.rule.on_card[il] = set(order)
+        self.n_slots = n_slots
+        if self.rule is not None and n_slots == 0:
+            self.rule = None
 
     def host_bytes(self) -> int:
         return sum(q.data.numel() for c in self.host.values() for q in c.values())

@@ -110,3 +110,50 @@ def test_prompt_streams_host_experts_through_the_gemm_path():
         assert err < 2e-2 and ta == tb
     finally:
         tier.close()
+
+
+def test_elastic_give_back_and_fill_keep_the_output():
+    """The experts give slots back (their experts fall to the host leg) and take them again; the slot map, the card's
+    copies and the model's output stay right through both moves."""
+    from bloomery_b200.runtime.elastic import ElasticStats, TieredBody, settle_to_margin, with_room
+    spec, full, tier = _pair(8, residency="off")
+    try:
+        g = torch.Generator().manual_seed(6)
+        prompt = torch.randint(0, spec.vocab, (17,), generator=g).tolist()
+        want = full.score(0, prompt)
+        ref = full.logits[0].clone()
+        body, stats = TieredBody(tier), ElasticStats()
+        unit = body.unit_bytes
+        before = tier.tiered.card_bytes()
+
+        def check(n_slots):
+            assert tier.tiered.n_slots == n_slots
+            for il in tier.tiered.layers:
+                sm = tier.tiered.slot_map[il].cpu().tolist()
+                on = {e: s_ for e, s_ in enumerate(sm) if s_ >= 0}
+                assert on == tier.tiered.slot_of[il] and sorted(on.values()) == list(range(n_slots))
+                for e, slot in on.items():
+                    for part in ("ffn_gate_exps", "ffn_down_exps"):
+                        assert torch.equal(tier.tiered.card[il][part].data[slot].cpu(), tier.tiered.host[il][part].data[e])
+            tier.reset(0)
+            got = tier.score(0, prompt)
+            err = ((tier.logits[0] - ref).abs().max() / ref.abs().max()).item()
+            assert err < 2e-2 and sum(int(x == y) for x, y in zip(want, got)) >= len(prompt) - 2
+
+        calls = []
+
+        def op():                                   # an allocation that is refused until three units came back
+            calls.append(1)
+            if tier.tiered.n_slots > 5:
+                raise torch.cuda.OutOfMemoryError("CUDA out of memory (test)")
+            return "ok"
+        assert with_room(op, body, 3 * unit, stats) == "ok" and len(calls) == 2
+        assert stats.give_backs == 1 and stats.bytes_given == before - tier.tiered.card_bytes() > 0
+        check(5)
+        assert settle_to_margin(body, free_bytes=10 * unit, margin_bytes=8 * unit, stats=stats) > 0      # two units free past the margin
+        check(7)
+        assert settle_to_margin(body, free_bytes=unit, margin_bytes=3 * unit, stats=stats) < 0           # two units short
+        check(5)
+        assert stats.fills == 1 and stats.give_backs == 2
+    finally:
+        tier.close()

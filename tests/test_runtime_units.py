@@ -346,3 +346,64 @@ def test_levers_registry_rows_are_all_read_somewhere():
                 text += open(os.path.join(d, f), errors="ignore").read()
     dead = [l.name for l in levers.REGISTRY if not re.search(r'["\']' + l.name + r'["\']', text)]
     assert dead == [], dead
+
+
+def test_elastic_with_room_and_settle_on_a_fake_body():
+    from bloomery_b200.runtime.elastic import ElasticStats, NoRoom, settle_to_margin, with_room
+
+    class Body:
+        unit_bytes = 100
+
+        def __init__(self, have):
+            self.have = have
+
+        def give_back(self, n):
+            steps = min(self.have, -(-n // 100))
+            self.have -= steps
+            return steps * 100
+
+        def fill(self, n):
+            steps = n // 100
+            self.have += steps
+            return steps * 100
+    b, st = Body(3), ElasticStats()
+    tries = []
+
+    def op():
+        tries.append(b.have)
+        if b.have > 1:
+            raise MemoryError("out of memory")
+        return 7
+    assert with_room(op, b, 150, st) == 7 and tries == [3, 1] and st.give_backs == 1 and st.bytes_given == 200 and st.retries == 1
+    with pytest.raises(NoRoom):
+        with_room(lambda: (_ for _ in ()).throw(MemoryError("out of memory")), Body(0), 50, st)
+    with pytest.raises(NoRoom):
+        with_room(lambda: (_ for _ in ()).throw(MemoryError("out of memory")), Body(5), 50, st)      # refused again after the give-back
+    with pytest.raises(KeyError):
+        with_room(lambda: {}["x"], b, 50, st)                                                       # not a memory refusal: untouched
+    b2 = Body(4)
+    assert settle_to_margin(b2, free_bytes=50, margin_bytes=260, stats=st) == -300 and b2.have == 1
+    assert settle_to_margin(b2, free_bytes=600, margin_bytes=260, stats=st) == 300 and b2.have == 4
+    assert settle_to_margin(b2, free_bytes=300, margin_bytes=260, stats=st) == 0                    # less than a unit to spare
+
+
+def test_tiered_experts_resize_keeps_the_hottest_on_cpu_tensors():
+    import torch
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.residency import TieredExperts
+    spec = tiny_qwen3moe()
+    w = Weights.from_items(spec, synth_tensors(spec, "cpu", seed=5), "cpu")
+    t = TieredExperts(spec, w, 6, "cpu", rule="off")
+    heat = torch.zeros(spec.n_layer, spec.n_expert)
+    heat[:, 3] = 9; heat[:, 11] = 8; heat[:, 0] = 7; heat[:, 14] = 6
+    t.resize(2, heat)
+    for il in t.layers:
+        assert t.slot_of[il] == {3: 0, 0: 1}                    # the hottest residents stay (11 and 14 were not on the card)
+        assert t.slot_map[il].tolist().count(-1) == spec.n_expert - 2
+    t.resize(4, heat)
+    for il in t.layers:
+        assert set(t.slot_of[il]) == {3, 0, 11, 14} and sorted(t.slot_of[il].values()) == [0, 1, 2, 3]
+        for e, slot in t.slot_of[il].items():
+            assert torch.equal(t.card[il]["ffn_up_exps"].data[slot], t.host[il]["ffn_up_exps"].data[e])
+    assert t.n_slots == 4 and t.slot_bytes() * 5 == t.card_bytes()      # n_slots + 1 spare in every layer
