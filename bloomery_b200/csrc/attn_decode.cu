@@ -41,6 +41,13 @@ struct RopeArgs {
   unsigned* fault;
   int layer;
   __nv_bfloat16* q_bf16; // optional [n_q, M, HEAD] (head-major rows for the prompt GEMMs)
+  int kv_q8;             // the caches hold q8_0 rows: HEAD/32 f16 scales, then HEAD int8 codes (34 bytes per 32 values)
+};
+
+// q8_0 key/value rows: per position and KV head HEAD / 32 f16 scales followed by HEAD int8 codes
+template <int HEAD> struct KvQ8 {
+  static constexpr int kRowBytes = HEAD / 32 * 34;
+  static constexpr int kCodes = HEAD / 16;       // byte offset of the codes (4-byte aligned for both head sizes)
 };
 
 template <int HEAD>
@@ -96,6 +103,24 @@ __global__ void __launch_bounds__(HEAD / 2) qk_norm_rope_append_kernel(const Rop
     if (i == 0) raise_fault(a.fault, a.layer, FS_PAGE);
     return;
   }
+  if (a.kv_q8) {
+    // this thread's two values sit in blocks i / 32 and (i + HALF) / 32; a warp holds both blocks whole
+    using Q = KvQ8<HEAD>;
+    uint8_t* row = reinterpret_cast<uint8_t*>(is_k ? a.k_cache : a.v_cache) +
+                   (((long)page * a.n_kv + kvh) * kPage + (pos % kPage)) * Q::kRowBytes;
+    const __half d0 = __float2half_rn(warp_max(fabsf(x0)) * (1.0f / 127.0f));
+    const __half d1 = __float2half_rn(warp_max(fabsf(x1)) * (1.0f / 127.0f));
+    const float f0 = __half2float(d0), f1 = __half2float(d1);
+    const int q0 = f0 > 0.f ? max(-127, min(127, __float2int_rn(x0 / f0))) : 0;
+    const int q1 = f1 > 0.f ? max(-127, min(127, __float2int_rn(x1 / f1))) : 0;
+    row[Q::kCodes + i] = (uint8_t)(int8_t)q0;
+    row[Q::kCodes + i + HALF] = (uint8_t)(int8_t)q1;
+    if ((i & 31) == 0) {
+      reinterpret_cast<__half*>(row)[i >> 5] = d0;
+      reinterpret_cast<__half*>(row)[(i + HALF) >> 5] = d1;
+    }
+    return;
+  }
   __half* dst = (is_k ? a.k_cache : a.v_cache) + (((long)page * a.n_kv + kvh) * kPage + (pos % kPage)) * HEAD;
   dst[i] = __float2half_rn(x0);
   dst[i + HALF] = __float2half_rn(x1);
@@ -115,6 +140,7 @@ struct FlashArgs {
   float* part_acc;       // [M, n_q, n_seg, HEAD]
   unsigned* fault;
   int layer;
+  int kv_q8;             // the caches hold q8_0 rows (KvQ8): tiles are expanded to f16 as they are staged
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -126,7 +152,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // grid (n_seg, n_kv, M); 256 threads = 8 warps; warp w serves q heads w, w+8, ... of the group
-template <int HEAD, int HPW>
+template <int HEAD, int HPW, bool Q8 = false>
 __global__ void __launch_bounds__(256) flash_decode_seg_kernel(const FlashArgs a) {
   constexpr int KSTR = HEAD + 8;      // padded f16 row stride for K: conflict-free 16-byte reads by key lanes
   constexpr int DPL = HEAD / 32;      // output dims per lane
@@ -159,8 +185,33 @@ __global__ void __launch_bounds__(256) flash_decode_seg_kernel(const FlashArgs a
     const int key0 = t * kKeyTile;
     int page = bt[key0 / kPage];
     page = (page < 0 || page >= a.n_pages) ? 0 : page;  // fault is raised by the append kernel; stay in bounds
-    const long base = (((long)page * a.n_kv + kvh) * kPage + (key0 % kPage)) * HEAD;
     constexpr int CH = HEAD / 8;  // 16-byte chunks per row
+    if constexpr (Q8) {
+      // q8_0 rows: eight codes and their block's scale per step, written to the same f16 tiles the dot loops read
+      using Q = KvQ8<HEAD>;
+      const long baseq = (((long)page * a.n_kv + kvh) * kPage + (key0 % kPage)) * Q::kRowBytes;
+      const uint8_t* kq = reinterpret_cast<const uint8_t*>(a.k_cache) + baseq;
+      const uint8_t* vq = reinterpret_cast<const uint8_t*>(a.v_cache) + baseq;
+      for (int c = tid; c < kKeyTile * CH; c += 256) {
+        const int r = c / CH, cc = c % CH;
+        auto expand = [&](const uint8_t* rowp, __half* dst) {
+          const float d = __half2float(reinterpret_cast<const __half*>(rowp)[cc >> 2]);
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(rowp + Q::kCodes + cc * 8);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(rowp + Q::kCodes + cc * 8 + 4);
+          __half2 h[4];
+          h[0] = __floats2half2_rn(d * (float)(int8_t)(w0 & 0xFF), d * (float)(int8_t)((w0 >> 8) & 0xFF));
+          h[1] = __floats2half2_rn(d * (float)(int8_t)((w0 >> 16) & 0xFF), d * (float)(int8_t)(w0 >> 24));
+          h[2] = __floats2half2_rn(d * (float)(int8_t)(w1 & 0xFF), d * (float)(int8_t)((w1 >> 8) & 0xFF));
+          h[3] = __floats2half2_rn(d * (float)(int8_t)((w1 >> 16) & 0xFF), d * (float)(int8_t)(w1 >> 24));
+          *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
+        };
+        expand(kq + (long)r * Q::kRowBytes, sk + ((size_t)stage * kKeyTile + r) * KSTR + cc * 8);
+        expand(vq + (long)r * Q::kRowBytes, sv + ((size_t)stage * kKeyTile + r) * HEAD + cc * 8);
+      }
+      cp_async_commit();
+      return;
+    }
+    const long base = (((long)page * a.n_kv + kvh) * kPage + (key0 % kPage)) * HEAD;
     for (int c = tid; c < kKeyTile * CH; c += 256) {
       int r = c / CH, cc = c % CH;
       cp_async16(sk + ((size_t)stage * kKeyTile + r) * KSTR + cc * 8, a.k_cache + base + (long)r * HEAD + cc * 8);
@@ -481,29 +532,49 @@ __global__ void __launch_bounds__(HEAD) flash_decode_merge_kernel(const MergeArg
 
 using namespace bl;
 
+static int rope_append_go(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain, const float* inv_freq,
+                          float eps, float q_scale, int head, int n_q, int n_kv, int M, const int* row_pos,
+                          const int* row_seq, const int* block_table, int max_pages, int n_pages, void* k_cache,
+                          void* v_cache, float* q_out, unsigned* fault, int layer, int kv_q8, cudaStream_t st) {
+  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
+  BL_REQUIRE(M >= 1 && n_q >= 1 && n_kv >= 1, BL_ERR_SHAPE);
+  RopeArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, M, row_pos, row_seq, block_table,
+             max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, q_out, fault, layer, nullptr, kv_q8};
+  dim3 grid(n_q + 2 * n_kv, M);
+  if (head == 128) return (int)launch(qk_norm_rope_append_kernel<128>, grid, dim3(64), 0, st, a);
+  return (int)launch(qk_norm_rope_append_kernel<64>, grid, dim3(32), 0, st, a);
+}
+
 extern "C" {
 
 int bl_qk_norm_rope_append(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain,
                            const float* inv_freq, float eps, float q_scale, int head, int n_q, int n_kv, int M,
                            const int* row_pos, const int* row_seq, const int* block_table, int max_pages, int n_pages,
                            void* k_cache, void* v_cache, float* q_out, unsigned* fault, int layer, cudaStream_t st) {
-  BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
-  BL_REQUIRE(M >= 1 && n_q >= 1 && n_kv >= 1, BL_ERR_SHAPE);
-  RopeArgs a{qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, n_q, n_kv, M, row_pos, row_seq, block_table,
-             max_pages, n_pages, (__half*)k_cache, (__half*)v_cache, q_out, fault, layer, nullptr};
-  dim3 grid(n_q + 2 * n_kv, M);
-  if (head == 128) return (int)launch(qk_norm_rope_append_kernel<128>, grid, dim3(64), 0, st, a);
-  return (int)launch(qk_norm_rope_append_kernel<64>, grid, dim3(32), 0, st, a);
+  return rope_append_go(qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, head, n_q, n_kv, M, row_pos, row_seq,
+                        block_table, max_pages, n_pages, k_cache, v_cache, q_out, fault, layer, 0, st);
+}
+
+// The same with q8_0 caches: rows of head / 32 f16 scales followed by head int8 codes (34 bytes per 32 values), written
+// with one scale per 32 values of the normalised, rotated row.  (The reference: crates/gpu/src/rope_neox.rs, the q8_0
+// append; --cache-type-k / -v q8_0.)
+int bl_qk_norm_rope_append_q8(const float* qkv, long qkv_stride, const float* q_gain, const float* k_gain,
+                              const float* inv_freq, float eps, float q_scale, int head, int n_q, int n_kv, int M,
+                              const int* row_pos, const int* row_seq, const int* block_table, int max_pages, int n_pages,
+                              void* k_cache, void* v_cache, float* q_out, unsigned* fault, int layer, cudaStream_t st) {
+  return rope_append_go(qkv, qkv_stride, q_gain, k_gain, inv_freq, eps, q_scale, head, n_q, n_kv, M, row_pos, row_seq,
+                        block_table, max_pages, n_pages, k_cache, v_cache, q_out, fault, layer, 1, st);
 }
 
 // 1: the segment pass runs on tensor-core tiles (flash_decode_seg_mma_kernel); 0: the fp32 kernel
 void bl_set_flash_mma(int on) { bl::g_flash_mma = on ? 1 : 0; }
 
-// Scratch: part_ml [M*n_q*n_seg*2] and part_acc [M*n_q*n_seg*head] floats, caller-owned.
-int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, const int* row_pos, const int* row_seq,
-                    const int* block_table, int max_pages, int n_pages, int head, int n_q, int n_kv, int M, int n_seg,
-                    int ctx_limit, float* part_ml, float* part_acc, float* out, int8_t* outq, float* outds,
-                    unsigned* fault, int layer, cudaStream_t st) {
+}  // extern "C"
+
+static int flash_decode_go(const float* q, const void* k_cache, const void* v_cache, const int* row_pos, const int* row_seq,
+                           const int* block_table, int max_pages, int n_pages, int head, int n_q, int n_kv, int M, int n_seg,
+                           int ctx_limit, float* part_ml, float* part_acc, float* out, int8_t* outq, float* outds,
+                           unsigned* fault, int layer, int kv_q8, cudaStream_t st) {
   BL_REQUIRE(head == 128 || head == 64, BL_ERR_SHAPE);
   BL_REQUIRE(n_kv >= 1 && n_q >= 1 && n_q % n_kv == 0 && n_q / n_kv <= 16, BL_ERR_SHAPE);
   BL_REQUIRE(n_seg >= 1 && M >= 1, BL_ERR_SHAPE);
@@ -511,11 +582,23 @@ int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, co
   BL_REQUIRE(max_pages >= 1 && (long)ctx_limit <= (long)max_pages * kPage, BL_ERR_SHAPE);
   const int G = n_q / n_kv;
   FlashArgs a{q, (const __half*)k_cache, (const __half*)v_cache, row_pos, row_seq, block_table, max_pages, n_pages,
-              n_q, n_kv, M, n_seg, ctx_limit, part_ml, part_acc, fault, layer};
+              n_q, n_kv, M, n_seg, ctx_limit, part_ml, part_acc, fault, layer, kv_q8};
   dim3 grid(n_seg, n_kv, M);
   size_t smem = (size_t)G * head * 4 + 2 * kKeyTile * (head + 8) * 2 + 2 * kKeyTile * head * 2;
   cudaError_t e;
-  if (g_flash_mma) {
+  if (kv_q8) {
+    // q8_0 caches: the fp32 segment kernel with tiles expanded to f16 as they are staged
+    if (head == 128) {
+      if (G <= 8) e = launch(flash_decode_seg_kernel<128, 1, true>, grid, dim3(256), smem, st, a);
+      else {
+        cudaFuncSetAttribute(flash_decode_seg_kernel<128, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        e = launch(flash_decode_seg_kernel<128, 2, true>, grid, dim3(256), smem, st, a);
+      }
+    } else {
+      if (G <= 8) e = launch(flash_decode_seg_kernel<64, 1, true>, grid, dim3(256), smem, st, a);
+      else e = launch(flash_decode_seg_kernel<64, 2, true>, grid, dim3(256), smem, st, a);
+    }
+  } else if (g_flash_mma) {
     const size_t sm2 = (size_t)(16 + 4 * kKeyTile) * (head + 8) * 2 + (16 * 33 + 512) * 4 + 16 * 40 * 2 + 64;
     static bool set128 = false, set64 = false;
     if (head == 128) {
@@ -539,6 +622,26 @@ int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, co
   MergeArgs mg{part_ml, part_acc, n_q, n_seg, M, row_seq, row_pos, ctx_limit, out, outq, (float2*)outds};
   if (head == 128) return (int)launch(flash_decode_merge_kernel<128>, dim3(n_q, M), dim3(128), 0, st, mg);
   return (int)launch(flash_decode_merge_kernel<64>, dim3(n_q, M), dim3(64), 0, st, mg);
+}
+
+extern "C" {
+
+// Scratch: part_ml [M*n_q*n_seg*2] and part_acc [M*n_q*n_seg*head] floats, caller-owned.
+int bl_flash_decode(const float* q, const void* k_cache, const void* v_cache, const int* row_pos, const int* row_seq,
+                    const int* block_table, int max_pages, int n_pages, int head, int n_q, int n_kv, int M, int n_seg,
+                    int ctx_limit, float* part_ml, float* part_acc, float* out, int8_t* outq, float* outds,
+                    unsigned* fault, int layer, cudaStream_t st) {
+  return flash_decode_go(q, k_cache, v_cache, row_pos, row_seq, block_table, max_pages, n_pages, head, n_q, n_kv, M, n_seg,
+                         ctx_limit, part_ml, part_acc, out, outq, outds, fault, layer, 0, st);
+}
+
+// The same over q8_0 caches (see bl_qk_norm_rope_append_q8).
+int bl_flash_decode_q8(const float* q, const void* k_cache, const void* v_cache, const int* row_pos, const int* row_seq,
+                       const int* block_table, int max_pages, int n_pages, int head, int n_q, int n_kv, int M, int n_seg,
+                       int ctx_limit, float* part_ml, float* part_acc, float* out, int8_t* outq, float* outds,
+                       unsigned* fault, int layer, cudaStream_t st) {
+  return flash_decode_go(q, k_cache, v_cache, row_pos, row_seq, block_table, max_pages, n_pages, head, n_q, n_kv, M, n_seg,
+                         ctx_limit, part_ml, part_acc, out, outq, outds, fault, layer, 1, st);
 }
 
 }  // extern "C"

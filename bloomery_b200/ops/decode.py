@@ -173,8 +173,10 @@ def set_flash_mma(on: bool) -> None:
 
 def qk_norm_rope_append(qkv: torch.Tensor, q_gain, k_gain, inv_freq: torch.Tensor, eps: float, q_scale: float,
                         head: int, n_q: int, n_kv: int, M: int, row_pos, row_seq, block_table, n_pages: int,
-                        k_cache, v_cache, q_out, fault, layer: int) -> None:
-    rc = cuda().bl_qk_norm_rope_append(p(qkv), L(qkv.stride(0)), p(q_gain), p(k_gain), p(inv_freq), F(eps), F(q_scale),
+                        k_cache, v_cache, q_out, fault, layer: int, kv_q8: bool = False) -> None:
+    """``kv_q8``: the caches are uint8 q8_0 rows (head / 32 f16 scales, then head int8 codes per position and KV head)."""
+    fn = cuda().bl_qk_norm_rope_append_q8 if kv_q8 else cuda().bl_qk_norm_rope_append
+    rc = fn(p(qkv), L(qkv.stride(0)), p(q_gain), p(k_gain), p(inv_freq), F(eps), F(q_scale),
                                        I(head), I(n_q), I(n_kv), I(M), p(row_pos), p(row_seq), p(block_table),
                                        I(block_table.shape[1]), I(n_pages), p(k_cache), p(v_cache), p(q_out), p(fault),
                                        I(layer), stream())
@@ -182,8 +184,10 @@ def qk_norm_rope_append(qkv: torch.Tensor, q_gain, k_gain, inv_freq: torch.Tenso
 
 
 def flash_decode(q, k_cache, v_cache, row_pos, row_seq, block_table, n_pages: int, head: int, n_q: int, n_kv: int,
-                 M: int, n_seg: int, ctx_limit: int, part_ml, part_acc, out, outq, outds, fault, layer: int) -> None:
-    rc = cuda().bl_flash_decode(p(q), p(k_cache), p(v_cache), p(row_pos), p(row_seq), p(block_table),
+                 M: int, n_seg: int, ctx_limit: int, part_ml, part_acc, out, outq, outds, fault, layer: int,
+                 kv_q8: bool = False) -> None:
+    fn = cuda().bl_flash_decode_q8 if kv_q8 else cuda().bl_flash_decode
+    rc = fn(p(q), p(k_cache), p(v_cache), p(row_pos), p(row_seq), p(block_table),
                                 I(block_table.shape[1]), I(n_pages), I(head), I(n_q), I(n_kv), I(M), I(n_seg),
                                 I(ctx_limit), p(part_ml), p(part_acc), p(out), p(outq), p(outds), p(fault), I(layer),
                                 stream())

@@ -153,10 +153,10 @@ class BatchDecode:
             mark(il, "qkv")
             K.qk_norm_rope_append(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"), e.inv_freq,
                                   s.rms_eps, q_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq, kvp.table,
-                                  kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out, e.fault, il); n += 1
+                                  kvp.n_pages, kvp.k[il], kvp.v[il], self.q_out, e.fault, il, kv_q8=e.kv_q8); n += 1
             K.flash_decode(self.q_out, kvp.k[il], kvp.v[il], self.row_pos, self.row_seq, kvp.table, kvp.n_pages, s.head_dim,
                            s.n_q, s.n_kv, M, self.n_seg, e.slot_ctx, self.part_ml, self.part_acc, self.attn, self.attn_q,
-                           self.attn_ds, e.fault, il); n += 2
+                           self.attn_ds, e.fault, il, kv_q8=e.kv_q8); n += 2
             G.rmsnorm_bf16(self.attn[:M], None, s.rms_eps, self.attn_bf[:M]); n += 1
             mark(il, "attention")
             n += self._mm(self.attn_bf[:M], w.q[b + "attn_output.weight"], tiles, M, out_f32=x, resid=x)

@@ -57,10 +57,18 @@ class DecodeEngine:
     def __init__(self, weights: Weights, n_slots: int = 1, slot_ctx: int = 4096, n_seg: Optional[int] = None,
                  use_graphs: bool = True, keep_logits: bool = True, engine_bound_s: float = 60.0,
                  layers: Optional[Tuple[int, int]] = None, stage_first: bool = True, stage_last: bool = True,
-                 kv_pages: Optional[int] = None):
+                 kv_pages: Optional[int] = None, kv_type: str = "f16"):
+        """``kv_type`` "q8_0": keys and values are kept as q8_0 rows (one f16 scale per 32 values, 34 bytes instead of
+        64), written by the append launch and expanded to f16 tiles inside the attention launch; GQA models only.
+        Prompts of such an engine take the 8-row pass path."""
         self.w = weights
         self.spec: ModelSpec = weights.spec
         s = self.spec
+        if kv_type not in ("f16", "q8_0"):
+            raise ValueError(f"KV cache type {kv_type!r}: f16 or q8_0")
+        self.kv_q8 = kv_type == "q8_0"
+        if self.kv_q8 and s.mla:
+            raise ValueError("the latent cache of MLA models is f16; q8_0 serves GQA caches")
         if s.mla and (s.kv_lora != 512 or s.rope_dim != 64 or s.nope_dim > 128 or s.v_dim > 128 or s.v_dim % 32):
             raise ValueError("the latent attention kernels serve latent 512 + rope 64, nope and v up to 128")
         self.device = weights.device
@@ -81,7 +89,11 @@ class DecodeEngine:
             self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, 2 * sm // ((s.n_q + 15) // 16))))
         else:
             # kv_pages below n_slots * max_pages overcommits the pool: idle slots spill to pinned host memory
-            self.kv = KvPool(n_kv_layers, s.n_kv, s.head_dim, kv_pages or n_slots * max_pages, n_slots, max_pages, dev)
+            if self.kv_q8:      # rows of head / 32 f16 scales + head int8 codes; the pool only moves pages of bytes
+                self.kv = KvPool(n_kv_layers, s.n_kv, s.head_dim // 32 * 34, kv_pages or n_slots * max_pages, n_slots,
+                                 max_pages, dev, dtype=torch.uint8)
+            else:
+                self.kv = KvPool(n_kv_layers, s.n_kv, s.head_dim, kv_pages or n_slots * max_pages, n_slots, max_pages, dev)
             self.n_seg = n_seg or max(1, min((slot_ctx + 31) // 32, max(1, sm // s.n_kv)))
         H, V = s.hidden, s.vocab
         f32 = dict(dtype=torch.float32, device=dev)
@@ -172,7 +184,7 @@ class DecodeEngine:
         self.launches_per_step = 0
         self.steps = 0
         # prompts at least this long use the GEMM path (0 = never; the GEMM path serves the GQA + routed-expert plan)
-        self.gemm_threshold = 0 if (s.mla or s.n_shared or layers is not None) else 64
+        self.gemm_threshold = 0 if (s.mla or s.n_shared or layers is not None or self.kv_q8) else 64
         self.ubatch = 4096
         self._gemm_prefill = None
         self._stream = torch.cuda.Stream(device=dev)
@@ -384,14 +396,14 @@ class DecodeEngine:
         K.gemv([w.q[b + "attn_q.weight"], w.q[b + "attn_k.weight"], w.q[b + "attn_v.weight"]], M, self.qkv,
                x=x, gain=w.f[b + "attn_norm.weight"], eps=s.rms_eps, fault=self.fault, layer=il,
                prefetch=self._static_next(il))
-        cl = K.attn_cluster_size(s.n_kv, M) if self.attn_clusters else 0
+        cl = K.attn_cluster_size(s.n_kv, M) if (self.attn_clusters and not self.kv_q8) else 0
         if cl:
             K.attn_cluster(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"), self.inv_freq,
                            s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq, kvp.table,
                            kvp.n_pages, kvp.k[il - self.lo], kvp.v[il - self.lo], cl, self.slot_ctx, None, self.attn_q,
                            self.attn_ds, self.fault, il)
             return 2
-        if K.staged_part("attn"):
+        if K.staged_part("attn") and not self.kv_q8:
             K.attn_fused(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"), self.inv_freq,
                          s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M, self.row_pos, self.row_seq, kvp.table,
                          kvp.n_pages, kvp.k[il - self.lo], kvp.v[il - self.lo], self.n_seg, self.slot_ctx, self.part_ml,
@@ -400,10 +412,10 @@ class DecodeEngine:
         K.qk_norm_rope_append(self.qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
                               self.inv_freq, s.rms_eps, self.attn_scale, s.head_dim, s.n_q, s.n_kv, M,
                               self.row_pos, self.row_seq, kvp.table, kvp.n_pages, kvp.k[il - self.lo], kvp.v[il - self.lo], self.q_out,
-                              self.fault, il)
+                              self.fault, il, kv_q8=self.kv_q8)
         K.flash_decode(self.q_out, kvp.k[il - self.lo], kvp.v[il - self.lo], self.row_pos, self.row_seq, kvp.table, kvp.n_pages,
                        s.head_dim, s.n_q, s.n_kv, M, self.n_seg, self.slot_ctx, self.part_ml, self.part_acc, None,
-                       self.attn_q, self.attn_ds, self.fault, il)
+                       self.attn_q, self.attn_ds, self.fault, il, kv_q8=self.kv_q8)
         return 4
 
     def _static_next(self, il: int):

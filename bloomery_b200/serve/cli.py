@@ -142,15 +142,23 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
     import torch
     from .engine import CpuEngine, GpuEngine
     path = opts["model"]
+    kinds = []
     for flag, key in (("-ctk", "cache_type_k"), ("-ctv", "cache_type_v")):
-        if str(opts.get(key) or "f16").lower() not in ("f16", "fp16"):
-            raise Refusal(Code.USAGE, f"{flag} {opts[key]}: the KV cache is f16 in this build (the attention kernels read f16 rows)")
+        kind = {"fp16": "f16"}.get(str(opts.get(key) or "f16").lower(), str(opts.get(key) or "f16").lower())
+        if kind not in ("f16", "q8_0"):
+            raise Refusal(Code.USAGE, f"{flag} {opts[key]}: the KV cache is f16 or q8_0 in this build")
+        kinds.append(kind)
+    if kinds[0] != kinds[1]:
+        raise Refusal(Code.USAGE, f"-ctk {kinds[0]} with -ctv {kinds[1]}: keys and values share one cache type here")
+    opts["_kv_type"] = kinds[0]
     spec, weights_bytes, kind = _inventory(path)
     free = [torch.cuda.mem_get_info(i)[0] for i in range(n_vis)]
     opts["_expert_bytes"] = _expert_bytes(path, kind)
     plan = plan_for(opts, spec, weights_bytes, n_vis, free)
     pl = plan["placement"]
     opts["_place_word"] = pl.word()
+    if opts.get("_kv_type", "f16") != "f16" and len(pl.devices) > 1:
+        raise Refusal(Code.USAGE, "-ctk q8_0: the several-GPU engines keep an f16 cache")
     records.write("plan", model=spec.name, devices=[f"CUDA{d}" for d in pl.devices], weights_bytes=weights_bytes,
                   kv_bytes=plan["kv_bytes"], ctx=plan["ctx_total"], slots=plan["n_slots"], place=pl.word())
     records.write("need", weights_bytes=weights_bytes, kv_bytes_per_token=spec.kv_bytes_per_token(), host_bytes=0, fits=True)
@@ -220,6 +228,10 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
         _, w, handle = open_model(path, dev)
         records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
         kw = dict(n_slots=plan["n_slots"], slot_ctx=plan["slot_ctx"], use_graphs=graphs, engine_bound_s=bound)
+        if opts.get("_kv_type", "f16") != "f16":
+            if spec.mla:
+                raise Refusal(Code.USAGE, "-ctk q8_0: the latent cache of this model is f16")
+            kw["kv_type"] = opts["_kv_type"]
         if pl.host_experts != "none" and spec.is_moe:
             from ..runtime.tiered import TieredEngine
             if pl.host_experts == "all":

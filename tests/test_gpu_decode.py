@@ -508,3 +508,89 @@ def test_overcommitted_kv_pool_spills_idle_slots_and_tokens_do_not_change():
         outs[which] = toks + outs[which]
     assert outs[0] == outs[1]
     assert tight.kv.n_spills >= 2 and tight.kv.n_unspills >= 2 and roomy.kv.n_spills == 0
+
+
+def _q8_rows(x):
+    """q8_0 rows as the append launch writes them (scales first, then codes) and the f16 values they decode to."""
+    n, hd = x.shape
+    blk = x.float().reshape(n, hd // 32, 32)
+    d = (blk.abs().amax(-1) / 127.0).half()
+    df = d.float()
+    q = torch.where(df[..., None] > 0, torch.round(blk / df[..., None].clamp_min(1e-30)), torch.zeros_like(blk)).clamp_(-127, 127)
+    rows = torch.cat([d.view(torch.uint8).reshape(n, -1), q.to(torch.int8).view(torch.uint8).reshape(n, hd)], 1)
+    return rows, (q * df[..., None]).reshape(n, hd).half()
+
+
+@pytest.mark.parametrize("head,n_q,n_kv", [(128, 32, 4), (64, 8, 2), (128, 48, 4)])
+def test_q8_0_kv_append_and_attention(head, n_q, n_kv):
+    """Keys and values kept as q8_0 rows: the append launch writes the rows a plain PyTorch quantiser writes, and
+    attention over them equals the f16 kernels over the decoded values."""
+    from bloomery_b200.ops import decode as K
+    torch.manual_seed(5)
+    M, n_pages, max_pages, n_seg = 3, 40, 12, 5
+    lens = [700, 65, 1]
+    rb = head // 32 * 34
+    kq = torch.zeros(n_pages, n_kv, 64, rb, dtype=torch.uint8, device=DEV)
+    vq = torch.zeros_like(kq)
+    kf = torch.zeros(n_pages, n_kv, 64, head, dtype=torch.float16, device=DEV)
+    vf = torch.zeros_like(kf)
+    table = torch.stack([torch.randperm(n_pages)[:max_pages] for _ in range(M)]).to(torch.int32).to(DEV)
+    # fill the history of every row with random q8 rows (and their decoded f16 twins)
+    for m, L in enumerate(lens):
+        for pos in range(L - 1):
+            page = int(table[m, pos // 64])
+            for c, cf in ((kq, kf), (vq, vf)):
+                rows, dec = _q8_rows(torch.randn(n_kv, head))
+                c[page, :, pos % 64] = rows.to(DEV)
+                cf[page, :, pos % 64] = dec.to(DEV)
+    qkv = torch.randn(M, (n_q + 2 * n_kv) * head, device=DEV)
+    gq, gk = 1 + 0.1 * torch.randn(head, device=DEV), 1 + 0.1 * torch.randn(head, device=DEV)
+    inv = (1.0 / (1e6 ** (torch.arange(0, head, 2, dtype=torch.float64) / head))).float().to(DEV)
+    pos = torch.tensor([L - 1 for L in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(M, dtype=torch.int32, device=DEV)
+    fault = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    outs = []
+    for q8, kc, vc in ((True, kq, vq), (False, kf, vf)):
+        q_out = torch.zeros(M, n_q, head, device=DEV)
+        K.qk_norm_rope_append(qkv, gq, gk, inv, 1e-6, 1.0 / math.sqrt(head), head, n_q, n_kv, M, pos, seq, table, n_pages,
+                              kc, vc, q_out, fault, 0, kv_q8=q8)
+        if not q8:
+            # the f16 twin gets the decoded values of the rows the q8 launch appended, so both caches hold the same numbers
+            for m, L in enumerate(lens):
+                page, off = int(table[m, (L - 1) // 64]), (L - 1) % 64
+                for cq_, cf_ in ((kq, kf), (vq, vf)):
+                    rows = cq_[page, :, off].cpu()
+                    d = rows[:, :head // 16].contiguous().view(torch.float16).float()
+                    codes = rows[:, head // 16:].contiguous().view(torch.int8).float().reshape(n_kv, head // 32, 32)
+                    want_rows, _ = _q8_rows(cf_[page, :, off].float().cpu())
+                    assert (rows[:, head // 16:].view(torch.int8).int() - want_rows[:, head // 16:].view(torch.int8).int()).abs().max() <= 1
+                    cf_[page, :, off] = (codes * d[..., None]).reshape(n_kv, head).half().to(DEV)
+        cells = M * n_q * n_seg
+        out = torch.zeros(M, n_q * head, device=DEV)
+        outq = torch.zeros(M, n_q * head, dtype=torch.int8, device=DEV)
+        outds = torch.zeros(M, n_q * head // 32, 2, device=DEV)
+        K.flash_decode(q_out, kc, vc, pos, seq, table, n_pages, head, n_q, n_kv, M, n_seg, max_pages * 64,
+                       torch.zeros(cells * 2, device=DEV), torch.zeros(cells * head, device=DEV), out, outq, outds, fault, 0, kv_q8=q8)
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert (int(fault) & 0xFFFFFFFF) == 0xFFFFFFFF
+    assert torch.allclose(outs[0], outs[1], rtol=1e-3, atol=1e-3), (outs[0] - outs[1]).abs().max()
+
+
+def test_engine_with_q8_0_kv_stays_in_band_and_halves_the_cache():
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.engine import DecodeEngine
+    spec = tiny_qwen3moe()
+    items = list(synth_tensors(spec, "cpu", seed=7))
+    f16 = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=1, slot_ctx=512)
+    q8 = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=1, slot_ctx=512, kv_type="q8_0")
+    assert q8.kv.bytes * 64 == f16.kv.bytes * 34
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, spec.vocab, (90,), generator=g).tolist()
+    a, b = f16.score(0, prompt), q8.score(0, prompt)
+    n_last = len(prompt) % 8 or 8
+    err = ((f16.logits[:n_last] - q8.logits[:n_last]).abs().max() / f16.logits[:n_last].abs().max()).item()
+    assert err < 3e-2, err
+    assert sum(int(x == y) for x, y in zip(a, b)) >= len(prompt) - 6
+    assert q8.decode_chain(0, b[-1], len(prompt), 6) == q8.decode_chain(0, b[-1], len(prompt), 6)      # replay is stable
