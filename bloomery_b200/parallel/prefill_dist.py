@@ -75,6 +75,28 @@ class ShardedGemmPrefill:
         self._router_w = {}
         self.emulated = local_only
         self.flash = True                       # head size 128: fused attention on tensor memory (csrc/flash_tcgen05.cu)
+        # resident bf16 copies of this rank's matrices, built by the first prompt (see GemmPrefill.resident_bf16)
+        from ..utils import levers
+        self.resident_bf16 = {"1": True, "0": False}.get(str(levers.get("BLOOMERY_PREFILL_BF16")), None)
+        self._resident = {}
+
+    def _bf16(self, il: int, name: str, scratch: torch.Tensor, fill) -> torch.Tensor:
+        """Layer il's matrix ``name`` in bf16: expanded into ``scratch`` by ``fill``, and kept as its own copy from then on
+        when the card has room (a quarter of it stays free), so later prompts skip the expansion."""
+        if self.resident_bf16 is False:
+            fill()
+            return scratch
+        hit = self._resident.get((il, name))
+        if hit is None:
+            fill()
+            if self.resident_bf16 is None:
+                free, total = torch.cuda.mem_get_info(self.e.device)
+                if free - scratch.numel() * 2 < total // 4:
+                    self.resident_bf16 = False
+                    return scratch
+            hit = scratch.clone()
+            self._resident[(il, name)] = hit
+        return hit
 
     def _get(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
@@ -192,11 +214,13 @@ class ShardedGemmPrefill:
             out.append(cur)                                   # ---- barrier: every xn shard is written
 
             def attention(b=b, il=il):
-                G.dequant_bf16(w.q[b + "attn_q.weight"], wqkv[:s.q_rows])
-                G.dequant_bf16(w.q[b + "attn_k.weight"], wqkv[s.q_rows:s.q_rows + s.kv_rows])
-                G.dequant_bf16(w.q[b + "attn_v.weight"], wqkv[s.q_rows + s.kv_rows:])
+                def fill_qkv():
+                    G.dequant_bf16(w.q[b + "attn_q.weight"], wqkv[:s.q_rows])
+                    G.dequant_bf16(w.q[b + "attn_k.weight"], wqkv[s.q_rows:s.q_rows + s.kv_rows])
+                    G.dequant_bf16(w.q[b + "attn_v.weight"], wqkv[s.q_rows + s.kv_rows:])
                 # all-gather fused: A tiles come from every rank's xn shard
-                G.gemm_bf16_dist(xn_peers, Tr, H, wqkv, gather_tiles, src_rows=Tr, out_f32=qkv, status=st)
+                G.gemm_bf16_dist(xn_peers, Tr, H, self._bf16(il, "wqkv", wqkv, fill_qkv), gather_tiles, src_rows=Tr,
+                                 out_f32=qkv, status=st)
                 G.qk_norm_rope_append_prefill(qkv, w.f.get(b + "attn_q_norm.weight"), w.f.get(b + "attn_k_norm.weight"),
                                               e.inv_freq, s.rms_eps, e.attn_scale, hd, s.n_q, s.n_kv, Tp, row_pos,
                                               row_seq, e.kv.table, e.kv.n_pages, e.kv.k[il], e.kv.v[il], q_bf, e.fault, il)
@@ -213,9 +237,9 @@ class ShardedGemmPrefill:
                     G.gemm_bf16(q_bf.view(s.n_q * Tp, hd), Kb, qk_tiles, out_f32=S, dst_row=map_s, status=st)
                     G.softmax_causal(S, rows, Tq, p0 + c0, T_pad, P)
                     G.gemm_bf16(P, Vt, pv_tiles, out_bf16=attn.view(Tp * s.n_q, hd), dst_row=map_o, status=st)
-                G.dequant_bf16(w.q[b + "attn_output.weight"], wo)
+                wo_l = self._bf16(il, "wo", wo, lambda: G.dequant_bf16(w.q[b + "attn_output.weight"], wo))
                 # reduce-scatter fused: partial rows are added into their owner's residual shard
-                G.gemm_bf16_dist([attn.data_ptr()], Tp, s.q_rows, wo, dense_all, owners=x_peers, rows_per_owner=Tr,
+                G.gemm_bf16_dist([attn.data_ptr()], Tp, s.q_rows, wo_l, dense_all, owners=x_peers, rows_per_owner=Tr,
                                  ldc=H, status=st)
             out.append([attention])                           # ---- barrier: every residual shard has all partials
             if s.layer_is_moe(il):
@@ -242,12 +266,12 @@ class ShardedGemmPrefill:
                     G.moe_plan(ids_loc, wts_all, El, moe_tiles, pos_of, dst_row, row_scale)
                     # dispatch: pull the rows routed to this rank's experts from the ranks that own them
                     G.gather_rows_peer(xn_peers, H, Tr, dst_row, moe_tiles.offsets[El:El + 1], cap, k, H, Ap)
-                    G.dequant_bf16(w.q[b + "ffn_gate_exps.weight"], wg)
-                    G.dequant_bf16(w.q[b + "ffn_up_exps.weight"], wu)
-                    G.gemm_bf16(Ap, wg, moe_tiles, out_bf16=act, B2=wu, status=st)
-                    G.dequant_bf16(w.q[b + "ffn_down_exps.weight"], wd)
+                    wg_l = self._bf16(il, "wg", wg, lambda: G.dequant_bf16(w.q[b + "ffn_gate_exps.weight"], wg))
+                    wu_l = self._bf16(il, "wu", wu, lambda: G.dequant_bf16(w.q[b + "ffn_up_exps.weight"], wu))
+                    G.gemm_bf16(Ap, wg_l, moe_tiles, out_bf16=act, B2=wu_l, status=st)
+                    wd_l = self._bf16(il, "wd", wd, lambda: G.dequant_bf16(w.q[b + "ffn_down_exps.weight"], wd))
                     # combine fused: weighted rows are added into the token owner's residual shard
-                    G.gemm_bf16_dist([act.data_ptr()], cap, I_, wd, moe_tiles, dst_row=dst_row, row_scale=row_scale,
+                    G.gemm_bf16_dist([act.data_ptr()], cap, I_, wd_l, moe_tiles, dst_row=dst_row, row_scale=row_scale,
                                      owners=x_peers, rows_per_owner=Tr, ldc=H, dst_div=k, status=st)
                 out.append([experts])                         # ---- barrier: every expert's rows have landed
                 cur = []
