@@ -113,6 +113,25 @@ def rank_barrier(peer_flag_ptrs, my_flags_ptr: int, epoch: int, rank: int, statu
                                  I(len(peer_flag_ptrs)), I(rank), p(status), stream()), "bl_rank_barrier")
 
 
+def rank_barrier_step(peer_flag_ptrs, my_flags_ptr: int, step: torch.Tensor, sites_per_step: int, site: int, rank: int,
+                      status: Optional[torch.Tensor]) -> None:
+    """The barrier of a captured pass: its epoch comes from the device-side pass counter ``step``."""
+    import ctypes
+    check(cuda().bl_rank_barrier_step(_ptr_array(peer_flag_ptrs), ctypes.c_void_p(my_flags_ptr), p(step),
+                                      ctypes.c_uint(sites_per_step), ctypes.c_uint(site), I(len(peer_flag_ptrs)), I(rank),
+                                      p(status), stream()), "bl_rank_barrier_step")
+
+
+def push_rows(src: torch.Tensor, dst_ptrs, n_bytes: int) -> None:
+    """``n_bytes`` of ``src`` into every address of ``dst_ptrs`` (peer pointers included)."""
+    check(cuda().bl_push_rows(p(src), _ptr_array(dst_ptrs), I(len(dst_ptrs)), L(n_bytes), stream()), "bl_push_rows")
+
+
+def sum_ranks(gathered: torch.Tensor, slot_stride: int, n_ranks: int, x: torch.Tensor, n: int) -> None:
+    """x[:n] += gathered[0][:n] + gathered[1][:n] + ... in rank order (fp32; ``slot_stride`` floats between slots)."""
+    check(cuda().bl_sum_ranks(p(gathered), L(slot_stride), I(n_ranks), p(x), L(n), stream()), "bl_sum_ranks")
+
+
 def gather_rows_peer(src_ptrs, src_stride: int, rows_per_rank: int, dst_row, n_rows, max_rows: int, k: int, K_: int, out) -> None:
     check(cuda().bl_gather_rows_peer(_ptr_array(src_ptrs), I(len(src_ptrs)), L(src_stride), I(rows_per_rank), p(dst_row),
                                      p(n_rows), I(max_rows), I(k), I(K_), p(out), stream()), "bl_gather_rows_peer")

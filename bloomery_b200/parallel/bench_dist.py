@@ -12,7 +12,109 @@ from . import dist as D
 from .sharded import ShardedEngine, local_spec, shard_items
 
 
+def run_batch_distributed(args, rank: int, local: int, world: int) -> int:
+    """``--batch B`` on N GPUs: B sequences per pass, experts split over the ranks, rows and attention replicated."""
+    from bench import METRIC, ClockSampler
+    from ..models.spec import NAMED
+    from ..models.weights import Weights, synth_tensors
+    from .batch_dist import ShardedBatchDecode
+    D.init("nccl")
+    dev = f"cuda:{local}"
+    spec = NAMED[args.model]()
+    mix = getattr(args, "mix", "") or "Q4_K_M"
+    B, steps, warm = args.batch, args.steps, max(3, args.warmup)
+    t0 = time.time()
+    lspec = local_spec(spec, world, attn=False)
+    w = Weights.from_items(lspec, synth_tensors(spec, dev, seed=0, mix=mix, shard=(rank, world), shard_attn=False), dev)
+    torch.cuda.synchronize()
+    t_load = time.time() - t0
+    ctx = (args.prompt + warm + 2 * steps + 64 + 63) // 64 * 64
+    eng = ShardedEngine(w, spec, rank, world, fused=True, n_slots=B, slot_ctx=ctx, use_graphs=True, attn_replicated=True)
+    eng.gemm_threshold = 0
+    bd = ShardedBatchDecode(eng, rank, world, max_rows=max(16, B))
+    g = torch.Generator().manual_seed(1234)
+    rows = []
+    dist.barrier()
+    t0 = time.time()
+    for slot in range(B):
+        prompt = torch.randint(0, spec.vocab, (args.prompt,), generator=g).tolist()
+        rows.append((slot, eng.prefill(slot, prompt, gemm=False), args.prompt))
+    torch.cuda.synchronize()
+    t_prompts = time.time() - t0
+    for slot in range(B):
+        eng.kv.ensure(slot, args.prompt + warm + 2 * steps + 8)
+    M = bd.set_rows(rows)
+    bd.counters[2:3].zero_()
+    dist.barrier()
+    for _ in range(warm):
+        bd.launch(M, advance=True)
+    torch.cuda.synchronize()
+    bd.counters[2:3].zero_()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    with torch.cuda.stream(bd._stream):
+        e0.record()
+    for _ in range(steps):
+        bd.launch(M, advance=True)
+    with torch.cuda.stream(bd._stream):
+        e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = D.max_over_ranks(e0.elapsed_time(e1), dev)
+    sampler.stop_flag.set()
+    sampler.join()
+    eng.check_fault()
+    bad = int(bd.status.item())
+    hist = bd.hist[:min(steps, bd.hist_cap) * M].view(-1, M)[:, :B]
+    tmax, tmin = hist.clone().long(), hist.clone().long()
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+    same = bool((tmax == tmin).all().item())
+    tok_s = B * steps / (ms / 1e3)
+    # end to end: host rows in, picks out, every pass (every rank feeds the same rows)
+    pos = args.prompt + warm + steps
+    cur = [(slot, int(hist[-1, slot]), pos) for slot in range(B)]
+    n_e2e = min(steps, 32)
+    for _ in range(2):
+        picks = bd.step(cur)
+        cur = [(s_, t_, p_ + 1) for (s_, _, p_), t_ in zip(cur, picks)]
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        picks = bd.step(cur)
+        cur = [(s_, t_, p_ + 1) for (s_, _, p_), t_ in zip(cur, picks)]
+    torch.cuda.synchronize()
+    e2e_s = D.max_over_ranks(time.perf_counter() - t0, dev)
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": f"{mix.lower()} weights expanded to bf16 inside the tcgen05 GEMM, fp32 accumulate, f16 KV",
+            "data": f"synthetic: seeded random token ids, random-init N(0,0.02) weights quantised {mix} on the card",
+            "config": {"model": spec.name, "global_batch": B, "seq_len": args.prompt + warm + steps, "prompt_tokens": args.prompt,
+                       "parallelism": f"ep{world} experts; rows and attention replicated; one rank-ordered all-reduce of the "
+                                      f"experts' partial rows per layer over NVLink peer memory",
+                       "graph": "one CUDA graph per pass", "rows_per_pass": M, "symmetric_memory": bd.sym.how,
+                       "note": "aggregate tokens/s of B concurrent sequences"},
+            "clocks": sampler.summary(),
+            "e2e": {"value": B * n_e2e / e2e_s, "unit": "tok/s", "steps": n_e2e,
+                    "h2d_bytes_per_step": int(bd.params_host.numel() * 4) * world,
+                    "d2h_bytes_per_step": int(bd.tokens_out_host.numel() * 4) * world},
+            "gpu_launches": bd.launches_per_step * steps * world, "launches_per_step": bd.launches_per_step,
+            "per_sequence_tok_s": tok_s / B, "ranks_agree": same, "wait_ran_out": bool(bad), "prompts_s": t_prompts,
+            "load_s": t_load, "weights_gb_per_rank": w.n_bytes / 1e9}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
 def run_distributed(args, rank: int, local: int, world: int) -> int:
+    if getattr(args, "batch", 1) > 1:
+        return run_batch_distributed(args, rank, local, world)
     from bench import BASELINE_TOKS, METRIC, ClockSampler
     from ..models.spec import NAMED
     from ..models.weights import Weights, synth_tensors

@@ -119,12 +119,47 @@ class BatchDecode:
 
     def enqueue(self, M: int, advance: bool = False) -> int:
         """Enqueue one pass of the first M row cells on the current stream; returns the launch count."""
+        n = 0
+        for n in self.enqueue_steps(M, advance):
+            pass
+        return n
+
+    def embed(self, M: int, x: torch.Tensor) -> None:
+        e = self.e
+        K.embed_rows(self.tokens, M, e.w.q["token_embd.weight"], e.spec.vocab, x, e.fault)
+
+    def experts(self, il: int, M: int, x: torch.Tensor, xn: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor):
+        """Routed experts of layer il on the routed rows; a generator of launch counts (it yields where ranks of a
+        several-GPU pass must meet; here it never does)."""
+        e = self.e
+        s, w = e.spec, e.w
+        b = f"blk.{il}."
+        E, k = s.n_expert, s.n_used
+        mark = self.timing.mark
+        n = 0
+        G.moe_plan(ids, wts, E, self.moe_tiles, self.pos_of, self.dst_row, self.row_scale); n += 1
+        G.gather_rows_bf16(xn, self.dst_row, self.moe_tiles.offsets[E:E + 1], self.cap, k, self.Ap); n += 1
+        mark(il, "route_plan_gather")
+        qg, qu, qd = (w.q[b + f"ffn_{nm}_exps.weight"] for nm in ("gate", "up", "down"))
+        if not (G.qgemm_supports(qg) and qg.qtype == qu.qtype and G.qgemm_supports(qd)):
+            raise NotImplementedError(f"expert stacks of type {qg.qtype}/{qu.qtype}/{qd.qtype} in the batched pass")
+        G.qgemm(self.Ap, qg, self.moe_tiles, out_bf16=self.act, W2=qu, status=self.status); n += 1
+        mark(il, "gate_up")
+        G.qgemm(self.act, qd, self.moe_tiles, out_f32=self.slot_out, dst_row=self.dst_row, row_scale=self.row_scale,
+                status=self.status); n += 1
+        mark(il, "down")
+        G.moe_combine(self.slot_out, self.pos_of, M, k, x, x); n += 1
+        yield n
+
+    def enqueue_steps(self, M: int, advance: bool = False):
+        """The pass as a generator: it yields its running launch count wherever the ranks of a several-GPU pass have to
+        meet (never, on one GPU), so a test can walk several emulated ranks in lockstep on one stream."""
         e = self.e
         s, w = e.spec, e.w
         tiles = self.dense_tiles[M]
         x, xn = self.x[:M], self.xn[:M]
         n = 0
-        K.embed_rows(self.tokens, M, w.q["token_embd.weight"], s.vocab, x, e.fault); n += 1
+        self.embed(M, x); n += 1
         q_scale = 1.0 / math.sqrt(s.head_dim)
         for il in range(s.n_layer):
             b = f"blk.{il}."
@@ -167,19 +202,11 @@ class BatchDecode:
                          None, None, e.fault, il); n += 1
                 K.route_rows(self.logits_r, e._rule(il), M, self.ids, self.wts, e.heat[il], e.fault, il); n += 1
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn); n += 1
-                ids, wts = self.ids[:M], self.wts[:M]
-                G.moe_plan(ids, wts, E, self.moe_tiles, self.pos_of, self.dst_row, self.row_scale); n += 1
-                G.gather_rows_bf16(xn, self.dst_row, self.moe_tiles.offsets[E:E + 1], self.cap, k, self.Ap); n += 1
-                mark(il, "route_plan_gather")
-                qg, qu, qd = (w.q[b + f"ffn_{nm}_exps.weight"] for nm in ("gate", "up", "down"))
-                if not (G.qgemm_supports(qg) and qg.qtype == qu.qtype and G.qgemm_supports(qd)):
-                    raise NotImplementedError(f"expert stacks of type {qg.qtype}/{qu.qtype}/{qd.qtype} in the batched pass")
-                G.qgemm(self.Ap, qg, self.moe_tiles, out_bf16=self.act, W2=qu, status=self.status); n += 1
-                mark(il, "gate_up")
-                G.qgemm(self.act, qd, self.moe_tiles, out_f32=self.slot_out, dst_row=self.dst_row, row_scale=self.row_scale,
-                        status=self.status); n += 1
-                mark(il, "down")
-                G.moe_combine(self.slot_out, self.pos_of, M, k, x, x); n += 1
+                for got in self.experts(il, M, x, xn, self.ids[:M], self.wts[:M]):
+                    if got is None:
+                        yield n                      # the ranks meet here
+                    else:
+                        n += got
             else:
                 G.rmsnorm_bf16(x, w.f[b + "ffn_norm.weight"], s.rms_eps, xn); n += 1
                 qg, qu = w.q[b + "ffn_gate.weight"], w.q[b + "ffn_up.weight"]
@@ -195,7 +222,7 @@ class BatchDecode:
         if advance:
             K.advance_rows(self.tokens, self.row_pos, self.row_seq, self.tokens_out, M, self.hist, self.hist_cap,
                            self.counters[2:3]); n += 1
-        return n
+        yield n
 
     # ---- driving ----------------------------------------------------------------------------------------------
     @staticmethod

@@ -75,3 +75,55 @@ def test_batched_chain_advances_every_sequence():
     hist = bd.hist[:4 * M].view(4, M).cpu()
     assert hist[:, :16].T.tolist() == seqs
     assert int(bd.status.item()) == 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_batched_pass_over_emulated_ranks_matches_one_gpu(world):
+    """Experts split over ranks, attention and rows replicated, partial rows met in the rank-ordered all-reduce: the
+    ranks walk a pass in lockstep on one stream and give the tokens and logits of the one-GPU batched pass."""
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.parallel.batch_dist import ShardedBatchDecode, lockstep
+    from bloomery_b200.parallel.sharded import shard_items
+    from bloomery_b200.runtime.batch_decode import BatchDecode
+    from bloomery_b200.runtime.engine import DecodeEngine
+    spec = tiny_qwen3moe()
+    items = list(synth_tensors(spec, DEV, seed=3))
+    n_rows = 19
+    full = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=n_rows, slot_ctx=256)
+    engs = [DecodeEngine(Weights.from_items(spec, shard_items(iter(items), spec, r, world, attn=False), DEV), n_slots=n_rows,
+                         slot_ctx=256) for r in range(world)]
+    g = torch.Generator().manual_seed(7)
+    rows = []
+    for slot in range(n_rows):
+        n = 4 + slot % 5
+        prompt = torch.randint(0, spec.vocab, (n,), generator=g).tolist()
+        first = full.prefill(slot, prompt, gemm=False)
+        rows.append((slot, first, n))
+        for e in engs:                               # the emulated ranks get the same KV history (their own engines cannot
+            for il in range(spec.n_layer):           # run a prompt: their expert stacks are partial)
+                e.kv.ensure(slot, n + 1)
+            e.kv.sync_table()
+    for e in engs:
+        e.kv.k.copy_(full.kv.k); e.kv.v.copy_(full.kv.v)
+        e.kv.table.copy_(full.kv.table); e.kv.table_host.copy_(full.kv.table_host)
+        e.kv.pages = [list(p_) for p_ in full.kv.pages]; e.kv.free = list(full.kv.free); e.kv.refs = list(full.kv.refs)
+        e.slot_len = list(full.slot_len)
+    ref = BatchDecode(full, max_rows=32)
+    want = ref.step(rows)
+    want_logits = ref.logits[:n_rows].clone()
+    ranks = [ShardedBatchDecode(e, r, world, max_rows=32, local_only=True) for r, e in enumerate(engs)]
+    for bd in ranks:
+        bd.sym.adopt_peers([b.sym for b in ranks])
+    Ms = [bd.set_rows(rows) for bd in ranks]
+    for bd in ranks:
+        bd._stream.synchronize()
+    lockstep(ranks, Ms[0])
+    torch.cuda.synchronize()
+    for bd in ranks:
+        assert int(bd.status.item()) == 0
+        assert torch.equal(bd.logits[:n_rows], ranks[0].logits[:n_rows])          # every rank holds the same bits
+        err = ((bd.logits[:n_rows] - want_logits).abs().amax(1) / want_logits.abs().amax(1)).max().item()
+        assert err < 2e-2, err
+    got = ranks[0].tokens_out[:n_rows].tolist()
+    assert sum(int(a == b) for a, b in zip(got, want)) >= n_rows - 2
