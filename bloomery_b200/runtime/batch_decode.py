@@ -94,7 +94,8 @@ class BatchDecode:
         self.graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self.launches_per_step = 0
         self._scratch_w: Dict[str, torch.Tensor] = {}
-        self._stream = torch.cuda.Stream(device=dev)
+        # the engine's own stream: its 8-row passes and prompts and these passes touch the same KV pages in order
+        self._stream = getattr(engine, "_stream", None) or torch.cuda.Stream(device=dev)
         self._side = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
         from .timing import PromptTiming
         self.timing = PromptTiming()            # arm() it and call enqueue() eagerly for per-unit milliseconds of a pass

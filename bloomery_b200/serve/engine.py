@@ -168,7 +168,22 @@ class GpuEngine(Engine):
 
     device_sampling = True
 
-    def _sample_on_device(self, n_rows: int, specs) -> Dict[int, int]:
+    batch_rows = 64             # more than max_rows rows in one round go through the batched tensor-core pass
+
+    def _batch(self):
+        """The batched pass of this engine (``runtime/batch_decode.py``), or None when the model is not one it serves."""
+        if not hasattr(self, "_bd"):
+            try:
+                from ..runtime.batch_decode import BatchDecode
+                from ..runtime.engine import DecodeEngine
+                if type(self.dec) is not DecodeEngine:
+                    raise NotImplementedError("tiered / sharded engines keep their own passes")
+                self._bd = BatchDecode(self.dec, max_rows=self.batch_rows)
+            except (NotImplementedError, ValueError):
+                self._bd = None
+        return self._bd
+
+    def _sample_on_device(self, n_rows: int, specs, logits=None) -> Dict[int, int]:
         """Run the sampling chain on the card for the rows of the last pass that carry a spec
         (``[SamplingParams, draws so far, recent ids]``; the draw count is updated in place); returns row -> sampled id.  Same bits as the host chain
         (``serve/sampler.py``) for the same seed and draw number."""
@@ -195,13 +210,13 @@ class GpuEngine(Engine):
             if len(recent):
                 rec[r, :len(recent)] = torch.tensor(list(recent), dtype=torch.int32)
                 nrec[r] = len(recent)
-        if getattr(self, "_samp_work", None) is None:
-            self._samp_work = torch.zeros(self.max_rows, self.n_vocab, device=dev)
-            self._samp_out = torch.zeros(self.max_rows, dtype=torch.int32, device=dev)
+        if getattr(self, "_samp_work", None) is None or self._samp_work.shape[0] < M:
+            self._samp_work = torch.zeros(max(M, self.max_rows), self.n_vocab, device=dev)
+            self._samp_out = torch.zeros(max(M, self.max_rows), dtype=torch.int32, device=dev)
         draws_dev = draws.to(dev)
         ks = [int(k) for k in par[:, 1].tolist()]
         cap = 1024 if any(k <= 0 or k > 1024 for k in ks) else max(ks)
-        K.sample_rows(dec.logits[:M], self.n_vocab, M, par.to(dev), seeds.to(dev), draws_dev, self._samp_out,
+        K.sample_rows((dec.logits if logits is None else logits)[:M], self.n_vocab, M, par.to(dev), seeds.to(dev), draws_dev, self._samp_out,
                       recent=rec.to(dev), n_recent=nrec.to(dev), work=self._samp_work, cap=cap)
         got = self._samp_out[:M].cpu().tolist()
         after = draws_dev.cpu().tolist()
@@ -214,6 +229,20 @@ class GpuEngine(Engine):
         from ..runtime.engine import EngineFault, EngineStalled
         out = []
         try:
+            bd = self._batch() if len(rows) > self.max_rows else None
+            if bd is not None:
+                # many sequences in one round: one batched pass per 64 rows instead of a pass per 8
+                for i in range(0, len(rows), self.batch_rows):
+                    chunk = list(rows[i:i + self.batch_rows])
+                    picks = bd.step(chunk)
+                    specs = sampling[i:i + self.batch_rows] if sampling is not None else None
+                    if specs is not None and any(sp is not None for sp in specs):
+                        for r, tok in self._sample_on_device(len(chunk), specs, logits=bd.logits).items():
+                            picks[r] = tok
+                    lg = bd.logits[:len(chunk)].float().cpu().numpy() if want_logits else None
+                    for j, pk in enumerate(picks):
+                        out.append((int(pk), lg[j] if lg is not None else None))
+                return out
             for i in range(0, len(rows), self.max_rows):
                 chunk = list(rows[i:i + self.max_rows])
                 picks = self.dec.step(chunk)

@@ -127,3 +127,42 @@ def test_batched_pass_over_emulated_ranks_matches_one_gpu(world):
         assert err < 2e-2, err
     got = ranks[0].tokens_out[:n_rows].tolist()
     assert sum(int(a == b) for a, b in zip(got, want)) >= n_rows - 2
+
+
+def test_serving_engine_takes_the_batched_pass_for_many_rows():
+    """GpuEngine.step with more rows than the 8-row chain holds: one batched pass serves them all, greedy picks and
+    sampled picks (the card's chain over the batched pass's logits) included."""
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.engine import DecodeEngine
+    from bloomery_b200.serve.engine import GpuEngine
+    from bloomery_b200.serve.sampler import Sampler, SamplingParams
+    from bloomery_b200.serve.tokenizer import ByteTokenizer
+    spec = tiny_qwen3moe()
+    n = 13
+    dec = DecodeEngine(Weights.from_items(spec, synth_tensors(spec, DEV, seed=3), DEV), n_slots=n, slot_ctx=256)
+    eng = GpuEngine(dec, ByteTokenizer(spec.vocab), "tiny")
+    g = torch.Generator().manual_seed(21)
+    rows = []
+    for slot in range(n):
+        ids = torch.randint(0, spec.vocab, (5 + slot,), generator=g).tolist()
+        eng.prefill(slot, ids[:-1], 0)
+        rows.append((slot, ids[-1], len(ids) - 1))
+    few = []
+    for i in range(0, n, 8):
+        few += eng.step(rows[i:i + 8], want_logits=True)          # the 8-row chain, for reference
+    for slot, _, pos in rows:
+        eng.cut(slot, pos)
+    sp = SamplingParams(temperature=0.9, top_k=40, top_p=0.95, seed=5)
+    specs = [None] * n
+    specs[4] = [sp, 0, []]
+    many = eng.step(rows, want_logits=True, sampling=specs)      # one batched pass
+    assert eng._batch() is not None and (64, False) in eng._batch().graphs or (16, False) in eng._batch().graphs
+    agree = 0
+    for i, ((t8, l8), (tb, lb)) in enumerate(zip(few, many)):
+        err = float(abs(l8 - lb).max() / abs(l8).max())
+        assert err < 8e-2, (i, err)              # bf16 rows against q8 rows on nearly flat random-init logits
+        if i != 4:
+            agree += int(t8 == tb)
+    assert agree >= n - 3
+    assert many[4][0] == Sampler(sp).sample(many[4][1], [])       # the sampled row follows the host chain on its logits
