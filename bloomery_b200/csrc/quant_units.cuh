@@ -41,8 +41,8 @@ enum WType : int {
   WT_Q6_K = 14,
   WT_BF16 = 30,
   WT_NVFP4 = 40,     // resident rows: K/2 code bytes, K/16 e4m3 scales, f32 tensor scale, pad to 16
-  WT_FP8_B128 = 41,
-  WT_Q8_F32 = 50,    // resident rows: K int8 codes, K/32 f32 scales, pad to 16 (IQ4_NL / IQ4_XS / MXFP4 / IQ2_XXS files land here)  // resident rows: K e4m3 codes, K/128 f32 scales (the 128x128 block scale, per row), pad to 16
+  WT_FP8_B128 = 41,  // resident rows: K e4m3 codes, K/128 f32 scales (the 128x128 block scale, per row), pad to 16
+  WT_Q8_F32 = 50,    // resident rows: K int8 codes, K/32 f32 scales, pad to 16 (IQ4_NL / IQ4_XS / MXFP4 / IQ2_XXS files land here)
 };
 
 struct u32x4 { uint32_t x, y, z, w; };

@@ -298,6 +298,21 @@ def main(argv: Optional[List[str]] = None) -> int:
         if opts["records_schema"]:
             print(records.schema())
             return 0
+        # -np N --engine-slots P (P < N): the engine is planned and built for P sequences, N slots take it in turns
+        turns = 0
+        es = int(opts.get("engine_slots") or 0)
+        if es:
+            if opts["parallel"] == "auto" or es < 1 or es >= int(opts["parallel"]):
+                raise Refusal(Code.USAGE, f"--engine-slots {es} takes a value below -np N (got -np {opts['parallel']})")
+            if str(opts.get("park")) not in ("states", "ids"):
+                raise Refusal(Code.USAGE, f"--park takes states or ids, got {opts['park']!r}")
+            turns, opts["parallel"] = int(opts["parallel"]), str(es)
+
+        def in_turns(eng):
+            if not turns:
+                return eng
+            from .swap import SwapEngine
+            return SwapEngine(eng, turns, str(opts["park"]), int(opts["park_ram"]) << 20)
         import torch
         n_vis = torch.cuda.device_count() if torch.cuda.is_available() else 0
         if opts["list_devices"]:
@@ -325,7 +340,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             eng = MockEngine(n_slots=4 if opts["parallel"] == "auto" else int(opts["parallel"]),
                              slot_ctx=int(opts.get("ctx") or 4096), fail_at=int(opts.get("mock_fail_at", -1)))
             opts["_place_word"] = "mock"
-            server.ready(eng, ChatTemplate(template_src), cache_bytes, int(opts["queue_depth"]))
+            server.ready(in_turns(eng), ChatTemplate(template_src), cache_bytes, int(opts["queue_depth"]))
             return server.wait()
         if not opts.get("model"):
             raise Refusal(Code.NO_MODEL, "no model was named; use -m FILE (a GGUF file, any shard of a split) or --mock")
@@ -337,8 +352,10 @@ def main(argv: Optional[List[str]] = None) -> int:
             raise Refusal(Code.NO_MODEL, f"{opts['model']}: no such file")
         server.state.phase = "plan"
         eng, template_src, bos, eos = open_engine(opts, server, n_vis, template_src)
-        server.ready(eng, ChatTemplate(template_src, bos, eos), cache_bytes, int(opts["queue_depth"]))
+        server.ready(in_turns(eng), ChatTemplate(template_src, bos, eos), cache_bytes, int(opts["queue_depth"]))
         draft = str(levers.get("BLOOMERY_DRAFT")).lower()
+        if turns and draft in ("mtp", "auto"):
+            draft = ""            # the draft layer's KV rows are the engine's own slots, not the slots that take turns
         if draft == "ngram" and server.state.worker is not None:
             from ..runtime.speculative import NgramDraft, WidthChooser
             width = int(levers.get("BLOOMERY_MTP_WIDTH")) or 7

@@ -289,10 +289,15 @@ class Worker(threading.Thread):
         return (self.draft is not None and r.sampling.temperature <= 0 and not r.sampling.penalizes and r.constraint is None
                 and not r.logit_bias and r.n_probs == 0)
 
-    def _decode_round(self) -> None:
+    def _turn(self):
+        """The slots that run this round when the engine's slots take it in turns (``serve/swap.py``), else None."""
+        turn = getattr(self.engine, "turn", None)
+        return turn([a.slot.id for a in self.active.values()]) if turn is not None else None
+
+    def _decode_round(self, live=None) -> None:
         rows, spans = [], []                    # spans: (active, first row index, drafted ids)
         for a in self.active.values():
-            if a.pending_token is None:
+            if a.pending_token is None or (live is not None and a.slot.id not in live):
                 continue
             drafted: List[int] = []
             if self._can_draft(a):
@@ -427,10 +432,11 @@ class Worker(threading.Thread):
                     except Exception as exc:       # noqa: BLE001 - reported to the caller of the action
                         done.put(("error", exc))
                 self._admit()
+                live = self._turn()
                 for a in list(self.active.values()):
-                    if a.pending_token is None:
+                    if a.pending_token is None and (live is None or a.slot.id in live):
                         self._feed_prompt(a)
-                self._decode_round()
+                self._decode_round(live)
                 if not self.active:
                     with self.board.wake:
                         if not self.board.queue and self.actions.empty() and not self.stop_flag.is_set():

@@ -38,6 +38,9 @@ FLAGS: List[Flag] = [
     Flag(("-np", "--parallel"), "parallel", "str", "auto", env="LLAMA_ARG_N_PARALLEL", help="slots: N or auto"),
     Flag(("--slot-ctx",), "slot_ctx", "int", 0),
     Flag(("--queue-depth",), "queue_depth", "int", 64),
+    Flag(("--engine-slots",), "engine_slots", "int", 0, help="sequences the engine holds; fewer than -np = the slots take it in turns"),
+    Flag(("--park",), "park", default="states", help="what a slot that leaves the engine keeps: states or ids"),
+    Flag(("--park-ram",), "park_ram", "int", 4096, help="MiB of parked slot states"),
     Flag(("-ub", "--ubatch-size"), "ubatch", "int", 4096, env="LLAMA_ARG_UBATCH"),
     Flag(("-b", "--batch-size"), "batch", "int", 4096, env="LLAMA_ARG_BATCH"),
     Flag(("-cram", "--cache-ram"), "cache_ram", "int", -1, env="LLAMA_ARG_CACHE_RAM", help="MiB of host prompt cache; -1 = min(8 GiB, half free)"),
