@@ -203,9 +203,78 @@ __device__ __forceinline__ void expand_unit_fast(const typename Unit<T>::Regs& r
     }
   }
 }
+// ---- float-coded types ---------------------------------------------------------------------
+// ChunkUnit<T>::chunk(regs, j) yields values 8j .. 8j+7 of the unit as eight bf16, never holding the unit's 64 floats.
+//   FP8 (E4M3 codes, one f32 scale per 128 values): the hardware converter takes two codes to an f16 pair; the pair
+//   widens to f32, takes the block scale and is rounded to bf16 once.
+//   NVFP4 (E2M1 codes, E4M3 scale per 16 values, f32 tensor scale): a code's magnitude is one of eight values, so two
+//   byte permutes with the code nibbles as selectors look up the low and the high byte of bf16(2 * magnitude) for four
+//   codes at once; the sign bits are gathered with two more permutes, and a packed bf16 multiply applies the group
+//   scale (rounded to bf16: the code values have two significant bits, so the product is exact in bf16 but for that
+//   rounding of the scale).
+template <class T> struct ChunkUnit { static constexpr bool kHas = false; };
+
+template <> struct ChunkUnit<Fp8B128> {
+  static constexpr bool kHas = true;
+  struct Pre { float sc; };
+  static __device__ __forceinline__ Pre pre(const Fp8B128::Regs& r) { return Pre{r.sc}; }
+  static __device__ __forceinline__ uint4 chunk(const Fp8B128::Regs& r, const Pre& pr, int j) {
+    const u32x4& q = r.q[j >> 1];
+    const uint32_t w0 = (j & 1) ? q.z : q.x, w1 = (j & 1) ? q.w : q.y;
+    float f[8];
+    e4m3x4_to_float(w0, f);
+    e4m3x4_to_float(w1, f + 4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= pr.sc;
+    return q_pack8(f);
+  }
+};
+
+template <> struct ChunkUnit<NvFp4> {
+  static constexpr bool kHas = true;
+  struct Pre { uint32_t s2[4]; };
+  static __device__ __forceinline__ Pre pre(const NvFp4::Regs& r) {
+    float sc[4];
+    e4m3x4_to_float(r.sc, sc);
+    Pre pr;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) pr.s2[g] = bf2_dup(sc[g] * r.g * 0.5f);   // the table below holds 2 * magnitude
+    return pr;
+  }
+  static __device__ __forceinline__ uint4 chunk(const NvFp4::Regs& r, const Pre& pr, int j) {
+    const uint32_t w = j == 0 ? r.q0.x : j == 1 ? r.q0.y : j == 2 ? r.q0.z : j == 3 ? r.q0.w
+                     : j == 4 ? r.q1.x : j == 5 ? r.q1.y : j == 6 ? r.q1.z : r.q1.w;
+    const uint32_t sel = w & 0x77777777u;
+    const uint32_t sodd = w & 0x80808080u, seven = (w << 4) & 0x80808080u;   // signs of the odd / the even codes
+    const uint32_t s2 = pr.s2[j >> 1];
+    uint32_t o[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t c = h ? sel >> 16 : sel;
+      const uint32_t lo4 = __byte_perm(0x40008000u, 0x4000C080u, c);
+      const uint32_t hi4 = __byte_perm(0x40403F00u, 0x41414040u, c) | __byte_perm(seven, sodd, h ? 0x7362 : 0x5140);
+      o[2 * h] = bf2_fma(__byte_perm(lo4, hi4, 0x5140), s2, 0u);
+      o[2 * h + 1] = bf2_fma(__byte_perm(lo4, hi4, 0x7362), s2, 0u);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+  }
+};
+
+template <class T>
+__device__ __forceinline__ void expand_unit_chunks(const typename Unit<T>::Regs& regs, int u, int kb, int row, uint8_t* sa) {
+  const typename ChunkUnit<T>::Pre pr = ChunkUnit<T>::pre(regs);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int p = Unit<T>::pos(u, 8 * j) - QBK * kb;
+    const int atom = p >> 6, ch = (p & 63) >> 3;
+    *reinterpret_cast<uint4*>(sa + atom * QATOM_A + row * 128 + ((ch ^ (row & 7)) << 4)) = ChunkUnit<T>::chunk(regs, pr, j);
+  }
+}
+
 template <class T, bool SHORT>
 __device__ __forceinline__ void expand_any(const typename Unit<T>::Regs& regs, int u, int kb, int row, uint8_t* sa) {
   if constexpr (FastUnit<T>::kHas) expand_unit_fast<T, SHORT>(regs, u, kb, row, sa);
+  else if constexpr (ChunkUnit<T>::kHas) expand_unit_chunks<T>(regs, u, kb, row, sa);
   else expand_unit<T>(regs, u, kb, row, sa);
 }
 
@@ -517,7 +586,10 @@ using namespace bl;
 extern "C" {
 
 // 1 when bl_qgemm has a kernel for this weight type
-int bl_qgemm_supports(int wtype) { return wtype == WT_Q4_K || wtype == WT_Q5_K || wtype == WT_Q6_K || wtype == WT_Q8_0; }
+int bl_qgemm_supports(int wtype) {
+  return wtype == WT_Q4_K || wtype == WT_Q5_K || wtype == WT_Q6_K || wtype == WT_Q8_0 || wtype == WT_FP8_B128 || wtype == WT_NVFP4 ||
+         wtype == WT_Q8_F32;
+}
 
 // C[dst_row[t] or t, n] = row_scale[t] * sum_k X[t, k] W[g][n, k] (+ resid), per token tile of the table.
 //   X [rows_x, K] bf16 (ldx elements); W, W2 [n_groups, N, row_bytes] resident blocks of type wtype;
@@ -556,6 +628,9 @@ int bl_qgemm(const void* X, long ldx, long rows_x, const void* W, const void* W2
     case WT_Q5_K: return qgemm_pick<Q5K>(dual, tile_rows, mx, a, n_groups, grid, st);
     case WT_Q6_K: return qgemm_pick<Q6K>(dual, tile_rows, mx, a, n_groups, grid, st);
     case WT_Q8_0: return qgemm_pick<Q80>(dual, tile_rows, mx, a, n_groups, grid, st);
+    case WT_FP8_B128: return qgemm_pick<Fp8B128>(dual, tile_rows, mx, a, n_groups, grid, st);
+    case WT_NVFP4: return qgemm_pick<NvFp4>(dual, tile_rows, mx, a, n_groups, grid, st);
+    case WT_Q8_F32: return qgemm_pick<Q8F>(dual, tile_rows, mx, a, n_groups, grid, st);
   }
   return BL_ERR_TYPE;
 }

@@ -223,7 +223,8 @@ def qgemm(X: torch.Tensor, W: QWeight, tiles: TileTable, *, out_f32: Optional[to
           out_bf16: Optional[torch.Tensor] = None, W2: Optional[QWeight] = None, dst_row=None, row_scale=None,
           resid=None, status: Optional[torch.Tensor] = None) -> None:
     """C = X @ W[g].T per token tile with W left block-quantised (``csrc/qgemm_tcgen05.cu``): X [rows, K] bf16, W (and
-    W2) resident Q4_K / Q5_K / Q6_K / Q8_0 matrices [N, bytes] or stacks [G, N, bytes]; tiles of 32, 64 or 128 token rows.
+    W2) resident Q4_K / Q5_K / Q6_K / Q8_0 / FP8_B128 / NVFP4 / Q8_F32 matrices [N, bytes] or stacks [G, N, bytes]; tiles of
+    32, 64 or 128 token rows.
     With W2 the output is silu(X W^T) * (X W2^T)."""
     assert X.dtype == torch.bfloat16 and X.stride(-1) == 1 and W.data.is_contiguous() and tiles.tile_rows in (32, 64, 128)
     assert W2 is None or (W2.wt == W.wt and W2.data.shape == W.data.shape and W2.data.is_contiguous())

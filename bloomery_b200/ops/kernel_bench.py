@@ -34,6 +34,11 @@ def main(argv=None) -> int:
         i = argv.index("--topk")
         TOPK = int(argv[i + 1])
         del argv[i:i + 2]
+    wtype = None                       # --wtype T: the expert stacks of every layer in resident type T (e.g. FP8_B128, NVFP4)
+    if "--wtype" in argv:
+        i = argv.index("--wtype")
+        wtype = argv[i + 1]
+        del argv[i:i + 2]
     if "--dbg" in argv:
         i = argv.index("--dbg")
         from bloomery_b200.ops._lib import cuda
@@ -63,7 +68,7 @@ def main(argv=None) -> int:
     for _ in range(NL):
         layers.append(dict(q=rw(QR, H, "Q4_K"), k=rw(KVR, H, "Q4_K"), v=rw(KVR, H, "Q6_K"), o=rw(H, QR, "Q4_K"),
                            r=QWeight((torch.randn(E, H, device=dev) * 0.05).view(torch.uint8).reshape(E, -1), "F32", H),
-                           g=rw(I, H, "Q4_K", E), u=rw(I, H, "Q4_K", E), d=rw(H, I, "Q6_K", E)))
+                           g=rw(I, H, wtype or "Q4_K", E), u=rw(I, H, wtype or "Q4_K", E), d=rw(H, I, wtype or "Q6_K", E)))
     x = torch.randn(8, H, device=dev)
     gain = torch.ones(H, device=dev)
     qkv = torch.randn(8, QR + 2 * KVR, device=dev)

@@ -7,19 +7,20 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _engine(n_slots):
+def _engine(n_slots, mix="Q4_K_M"):
     from bloomery_b200.models.spec import tiny_qwen3moe
     from bloomery_b200.models.weights import Weights, synth_tensors
     from bloomery_b200.runtime.engine import DecodeEngine
     spec = tiny_qwen3moe()
-    w = Weights.from_items(spec, synth_tensors(spec, DEV, seed=3), DEV)
+    w = Weights.from_items(spec, synth_tensors(spec, DEV, seed=3, mix=mix), DEV)
     return spec, DecodeEngine(w, n_slots=n_slots, slot_ctx=512)
 
 
-@pytest.mark.parametrize("n_rows", [11, 40])
-def test_batched_pass_matches_row_chain_in_band(n_rows):
+@pytest.mark.parametrize("n_rows,mix", [(11, "Q4_K_M"), (40, "Q4_K_M"), (19, "FP8_B128"), (19, "NVFP4")])
+def test_batched_pass_matches_row_chain_in_band(n_rows, mix):
+    """FP8 and NVFP4 checkpoints take the same pass: their codes are expanded inside the GEMM like the K-quants."""
     from bloomery_b200.runtime.batch_decode import BatchDecode
-    spec, eng = _engine(n_rows)
+    spec, eng = _engine(n_rows, mix)
     g = torch.Generator().manual_seed(7)
     rows = []
     for slot in range(n_rows):
