@@ -238,6 +238,38 @@ def qgemm(X: torch.Tensor, W: QWeight, tiles: TileTable, *, out_f32: Optional[to
     check(rc, "bl_qgemm")
 
 
+def fp8_rows(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, gain: Optional[torch.Tensor] = None,
+             eps: float = 0.0) -> None:
+    """E4M3 codes [M, K] (uint8) and 1 x 128 scales [M, K / 128] of the rows of ``x`` (bf16, or fp32 with an RMSNorm of
+    gain ``gain`` applied first): the activation side of :func:`fp8_gemm`."""
+    assert x.stride(-1) == 1 and codes.dtype == torch.uint8 and codes.stride(-1) == 1 and scales.is_contiguous()
+    assert x.dtype in (torch.bfloat16, torch.float32) and (gain is None or x.dtype == torch.float32)
+    M, Kd = x.shape
+    assert scales.shape[-1] == Kd // 128 and codes.shape[-1] == Kd
+    check(cuda().bl_fp8_rows(p(x), I(1 if x.dtype == torch.float32 else 0), L(x.stride(0)), p(gain), F(eps), I(M), I(Kd),
+                             p(codes), L(codes.stride(0)), p(scales), stream()), "bl_fp8_rows")
+
+
+def fp8_gemm(Xq: torch.Tensor, xs: torch.Tensor, W: QWeight, tiles: TileTable, *, out_f32: Optional[torch.Tensor] = None,
+             out_bf16: Optional[torch.Tensor] = None, W2: Optional[QWeight] = None, dst_row=None, row_scale=None,
+             resid=None, status: Optional[torch.Tensor] = None) -> None:
+    """The block-scaled FP8 product (``csrc/fp8gemm_tcgen05.cu``): both operands E4M3 into tcgen05 ``kind::f8f6f4``, the
+    128-wide partial sums promoted to fp32 with the weight block's and the activation row's scale.  ``Xq`` / ``xs``:
+    :func:`fp8_rows`; W (and W2) resident FP8_B128 matrices or stacks; tiles of 32 token rows.  Same epilogue options
+    as :func:`qgemm`."""
+    assert Xq.dtype == torch.uint8 and Xq.stride(-1) == 1 and xs.is_contiguous() and W.qtype == "FP8_B128"
+    assert W.data.is_contiguous() and tiles.tile_rows == 32 and Xq.shape[-1] == W.k and xs.shape == (Xq.shape[0], W.k // 128)
+    assert W2 is None or (W2.wt == W.wt and W2.data.shape == W.data.shape and W2.data.is_contiguous())
+    G = W.data.shape[0] if W.data.dim() == 3 else 1
+    N = W.data.shape[-2]
+    out = out_f32 if out_f32 is not None else out_bf16
+    rc = cuda().bl_fp8_gemm(p(Xq), L(Xq.stride(0)), L(Xq.shape[0]), p(xs), p(W.data), p(W2.data if W2 is not None else None),
+                            I(G), I(N), I(W.k), p(tiles.mtiles), p(tiles.n_mtiles), I(tiles.max_mtiles), I(tiles.tile_rows),
+                            p(out_f32), p(out_bf16), L(out.stride(0)), p(dst_row), p(row_scale), p(resid),
+                            L(resid.stride(0) if resid is not None else 0), p(status), I(sm_count()), stream())
+    check(rc, "bl_fp8_gemm")
+
+
 def qk_norm_rope_append_prefill(qkv, q_gain, k_gain, inv_freq, eps, q_scale, head, n_q, n_kv, T, row_pos, row_seq,
                                 block_table, n_pages, k_cache, v_cache, q_bf16, fault, layer) -> None:
     """Per-head RMSNorm + RoPE + KV append of T prompt rows: a block per token, a warp per head."""

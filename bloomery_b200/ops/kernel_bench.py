@@ -52,6 +52,8 @@ def main(argv=None) -> int:
         probe = torch.zeros(16, dtype=torch.int64, device="cuda:0")
     argv = [a for a in argv if a != "--no-staged"]
     which = argv[0] if argv else "chain"
+    if which in ("fgu", "fdown"):
+        wtype = "FP8_B128"             # f* = FP8 weights against E4M3 activations on the tensor cores (no expansion)
     reps = int(argv[1]) if len(argv) > 1 else 4
     ctx = int(argv[2]) if len(argv) > 2 else 4096
     K.set_staged(staged)
@@ -127,14 +129,14 @@ def main(argv=None) -> int:
         extra = dict(G=G, mids=torch.stack([torch.randperm(E, device=dev)[:TOPK] for _ in range(ctx)]).to(torch.int32).contiguous(),
                      mwts=torch.rand(ctx, TOPK, device=dev), mtt=G.TileTable(n, E, dev), mpos_of=torch.zeros(n, dtype=torch.int32, device=dev),
                      mdst=torch.zeros(n + 128, dtype=torch.int32, device=dev), mscale=torch.zeros(n + 128, device=dev))
-    if which in ("qgu", "qdown", "bgu", "bdown"):
+    if which in ("qgu", "qdown", "bgu", "bdown", "fgu", "fdown"):
         # expert products of `ctx` tokens x 8 experts of 128: q* = quantised weights expanded inside the GEMM,
         # b* = expansion launch + bf16 GEMM; --rows picks the token tile (32 or 128) of the q* forms
         from bloomery_b200.ops import gemm as G
         n = ctx * TOPK
-        tr = 32 if rows == 32 else 128
+        tr = 32 if rows == 32 or which[0] == "f" else 128
         mids = torch.stack([torch.randperm(E, device=dev)[:TOPK] for _ in range(ctx)]).to(torch.int32).contiguous()
-        tt = G.TileTable(n, E, dev, tr if which[0] == "q" else 128)
+        tt = G.TileTable(n, E, dev, tr if which[0] in "qf" else 128)
         dst = torch.zeros(n + 128, dtype=torch.int32, device=dev)
         scale = torch.zeros(n + 128, device=dev)
         G.moe_plan(mids, torch.rand(ctx, TOPK, device=dev), E, tt, torch.zeros(n, dtype=torch.int32, device=dev), dst, scale)
@@ -142,6 +144,9 @@ def main(argv=None) -> int:
                      xa=(torch.randn(n + 128, H, device=dev) * 0.3).bfloat16(), act=torch.zeros(n + 128, I, device=dev, dtype=torch.bfloat16),
                      so=torch.zeros(n, H, device=dev), wg=torch.zeros(E, I, H, device=dev, dtype=torch.bfloat16),
                      wu=torch.zeros(E, I, H, device=dev, dtype=torch.bfloat16), wd=torch.zeros(E, H, I, device=dev, dtype=torch.bfloat16))
+        if which[0] == "f":
+            extra.update(xa8=torch.randint(0, 120, (n + 128, H), dtype=torch.uint8, device=dev), xas=torch.rand(n + 128, H // 128, device=dev),
+                         act8=torch.randint(0, 120, (n + 128, I), dtype=torch.uint8, device=dev), acts=torch.rand(n + 128, I // 128, device=dev))
         M = 1
     if which in ("qo", "qq"):
         # dense products of a decode batch of --rows tokens (one tile): o projection / q projection, weights quantised
@@ -233,6 +238,8 @@ def main(argv=None) -> int:
             if which == "qq": X["G"].qgemm(X["xh"], l["q"], X["tt"], out_f32=X["oq"], status=X["gst"])
             if which == "qgu": X["G"].qgemm(X["xa"], l["g"], X["tt"], out_bf16=X["act"], W2=l["u"], status=X["gst"])
             if which == "qdown": X["G"].qgemm(X["act"], l["d"], X["tt"], out_f32=X["so"], dst_row=X["dst"], row_scale=X["scale"], status=X["gst"])
+            if which == "fgu": X["G"].fp8_gemm(X["xa8"], X["xas"], l["g"], X["tt"], out_bf16=X["act"], W2=l["u"], status=X["gst"])
+            if which == "fdown": X["G"].fp8_gemm(X["act8"], X["acts"], l["d"], X["tt"], out_f32=X["so"], dst_row=X["dst"], row_scale=X["scale"], status=X["gst"])
             if which == "bgu":
                 X["G"].dequant_bf16(l["g"], X["wg"]); X["G"].dequant_bf16(l["u"], X["wu"])
                 X["G"].gemm_bf16(X["xa"], X["wg"], X["tt"], out_bf16=X["act"], B2=X["wu"], status=X["gst"])

@@ -48,6 +48,7 @@ REGISTRY: List[LeverSpec] = [
     LeverSpec("BLOOMERY_UBATCH", "int", 4096, "rows per prompt micro-batch"),
     LeverSpec("BLOOMERY_PREFILL", "word", "batch", "prompt path", ("batch", "steps")),
     LeverSpec("BLOOMERY_PREFILL_BF16", "word", "auto", "resident bf16 copy of the weights for the prompt path (auto = when it leaves a quarter of the card free)", ("auto", "0", "1")),
+    LeverSpec("BLOOMERY_FP8_NATIVE", "bool", True, "batched pass: FP8 128x128 weights multiply E4M3 activations on the tensor cores (off = expand the weights to bf16 in flight)"),
     LeverSpec("BLOOMERY_PDL", "bool", True, "programmatic dependent launch between decode kernels"),
     LeverSpec("BLOOMERY_FLASH_MMA", "bool", False, "decode attention segments on tensor-core tiles (f16 queries and probabilities)"),
     LeverSpec("BLOOMERY_GRAPHS", "bool", True, "one CUDA graph per decode step"),

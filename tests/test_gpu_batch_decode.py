@@ -7,20 +7,31 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _engine(n_slots, mix="Q4_K_M"):
-    from bloomery_b200.models.spec import tiny_qwen3moe
+def _spec(arch):
+    from bloomery_b200.models.spec import tiny_deepseek, tiny_qwen3moe
+    return tiny_deepseek() if arch == "deepseek" else tiny_qwen3moe()
+
+
+def _engine(n_slots, mix="Q4_K_M", arch="qwen3moe"):
     from bloomery_b200.models.weights import Weights, synth_tensors
     from bloomery_b200.runtime.engine import DecodeEngine
-    spec = tiny_qwen3moe()
+    spec = _spec(arch)
     w = Weights.from_items(spec, synth_tensors(spec, DEV, seed=3, mix=mix), DEV)
     return spec, DecodeEngine(w, n_slots=n_slots, slot_ctx=512)
 
 
-@pytest.mark.parametrize("n_rows,mix", [(11, "Q4_K_M"), (40, "Q4_K_M"), (19, "FP8_B128"), (19, "NVFP4")])
-def test_batched_pass_matches_row_chain_in_band(n_rows, mix):
-    """FP8 and NVFP4 checkpoints take the same pass: their codes are expanded inside the GEMM like the K-quants."""
+@pytest.mark.parametrize("n_rows,mix,arch,native", [
+    (11, "Q4_K_M", "qwen3moe", True), (40, "Q4_K_M", "qwen3moe", True), (19, "FP8_B128", "qwen3moe", False),
+    (19, "FP8_B128", "qwen3moe", True), (19, "NVFP4", "qwen3moe", True), (21, "Q4_K_M", "deepseek", True),
+    (40, "FP8_B128", "deepseek", False), (40, "FP8_B128", "deepseek", True)])
+def test_batched_pass_matches_row_chain_in_band(n_rows, mix, arch, native):
+    """FP8 and NVFP4 checkpoints take the same pass, and so does the DeepSeek layer plan: latent attention, a leading
+    dense layer, sigmoid routing in groups, a shared expert.  FP8 weights run either expanded to bf16 inside the GEMM
+    (``native`` off) or against E4M3 activations on the tensor cores (on: the activations' 3 mantissa bits widen the
+    band)."""
     from bloomery_b200.runtime.batch_decode import BatchDecode
-    spec, eng = _engine(n_rows, mix)
+    spec, eng = _engine(n_rows, mix, arch)
+    fp8_acts = native and mix == "FP8_B128"
     g = torch.Generator().manual_seed(7)
     rows = []
     for slot in range(n_rows):
@@ -35,13 +46,14 @@ def test_batched_pass_matches_row_chain_in_band(n_rows, mix):
         ref_tok += eng.step(part)
         ref[i:i + len(part)] = eng.logits[:len(part)]
     bd = BatchDecode(eng, max_rows=64)
+    bd.fp8_native = native
     got_tok = bd.step(rows)                                     # same cells again: the KV rows are rewritten in place
     got = bd.logits[:n_rows]
     err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
-    assert err < 5e-2, err
+    assert err < (0.2 if fp8_acts else 5e-2), err
     top2 = ref.topk(2, dim=1).values
-    clear = ((top2[:, 0] - top2[:, 1]) > 0.1 * ref.abs().amax(dim=1)).cpu().tolist()
-    assert sum(clear) >= 1
+    clear = ((top2[:, 0] - top2[:, 1]) > (0.4 if fp8_acts else 0.1) * ref.abs().amax(dim=1)).cpu().tolist()
+    assert fp8_acts or sum(clear) >= 1
     assert all(a == b for a, b, c in zip(got_tok, ref_tok, clear) if c)
     again = bd.step(rows)
     assert again == got_tok                                     # replay of the captured pass is deterministic
@@ -78,18 +90,18 @@ def test_batched_chain_advances_every_sequence():
     assert int(bd.status.item()) == 0
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_batched_pass_over_emulated_ranks_matches_one_gpu(world):
+@pytest.mark.parametrize("world,arch", [(2, "qwen3moe"), (4, "qwen3moe"), (2, "deepseek"), (4, "deepseek")])
+def test_batched_pass_over_emulated_ranks_matches_one_gpu(world, arch):
     """Experts split over ranks, attention and rows replicated, partial rows met in the rank-ordered all-reduce: the
     ranks walk a pass in lockstep on one stream and give the tokens and logits of the one-GPU batched pass."""
-    from bloomery_b200.models.spec import tiny_qwen3moe
     from bloomery_b200.models.weights import Weights, synth_tensors
     from bloomery_b200.parallel.batch_dist import ShardedBatchDecode, lockstep
     from bloomery_b200.parallel.sharded import shard_items
     from bloomery_b200.runtime.batch_decode import BatchDecode
     from bloomery_b200.runtime.engine import DecodeEngine
-    spec = tiny_qwen3moe()
-    items = list(synth_tensors(spec, DEV, seed=3))
+    spec = _spec(arch)
+    # the toy DeepSeek widths split four ways leave 64 columns of the shared expert: blocks of 32 still divide them
+    items = list(synth_tensors(spec, DEV, seed=3, mix="Q8_0" if arch == "deepseek" else "Q4_K_M"))
     n_rows = 19
     full = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=n_rows, slot_ctx=256)
     engs = [DecodeEngine(Weights.from_items(spec, shard_items(iter(items), spec, r, world, attn=False), DEV), n_slots=n_rows,
