@@ -120,6 +120,7 @@ def batch_arm(args, spec, w, dev, local, steps, warm, t_load) -> int:
     from bloomery_b200.runtime.batch_decode import BatchDecode
     from bloomery_b200.runtime.engine import DecodeEngine
     B = args.batch
+    mix = args.mix or "Q4_K_M"
     ctx = (args.prompt + warm + 2 * steps + 64 + 63) // 64 * 64
     eng = DecodeEngine(w, n_slots=B, slot_ctx=ctx)
     bd = BatchDecode(eng, max_rows=max(16, B))
@@ -184,8 +185,10 @@ def batch_arm(args, spec, w, dev, local, steps, warm, t_load) -> int:
     line = {
         "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "q4_k_m weights expanded to bf16 inside the tcgen05 GEMM, fp32 accumulate, f16 KV",
-        "data": "synthetic: seeded random token ids, random-init N(0,0.02) weights quantised Q4_K_M on the card",
+        "dtype": (f"{mix.lower()} weights against e4m3 activations (1x128 scales) on tcgen05 kind::f8f6f4, fp32 promotion every 128 values, f16 KV"
+                  if mix == "FP8_B128" and bd.fp8_native else
+                  f"{mix.lower()} weights expanded to bf16 inside the tcgen05 GEMM, fp32 accumulate, f16 KV"),
+        "data": f"synthetic: seeded random token ids, random-init N(0,0.02) weights quantised {mix} on the card",
         "config": {"model": spec.name, "global_batch": B, "seq_len": args.prompt + warm + steps, "prompt_tokens": args.prompt,
                    "parallelism": "single", "l2": "weights (17 GB) exceed L2; no flush needed",
                    "graph": "one CUDA graph per pass", "rows_per_pass": M,
@@ -379,8 +382,8 @@ def main() -> int:
     line = {
         "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": tok_s / BASELINE_TOKS, "dtype": "q4_k_m weights, int8 dot / fp32 accumulate, f16 KV",
-        "data": "synthetic: seeded random token ids, random-init N(0,0.02) weights quantised Q4_K_M on the card",
+        "vs_baseline": tok_s / BASELINE_TOKS, "dtype": f"{(args.mix or 'Q4_K_M').lower()} weights, int8 dot / fp32 accumulate, f16 KV",
+        "data": f"synthetic: seeded random token ids, random-init N(0,0.02) weights quantised {args.mix or 'Q4_K_M'} on the card",
         "config": {"model": spec.name, "global_batch": 1, "seq_len": args.prompt + warm + steps,
                    "prompt_tokens": args.prompt, "parallelism": "single", "l2": "weights (17 GB) exceed L2; no flush needed",
                    "graph": "one CUDA graph per decode step", "pdl": not args.no_pdl, "flash_mma": bool(args.flash_mma),
