@@ -170,6 +170,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant
       const long wrow = (long)mt.group * a.group_bytes + (long)(n_ok ? n : a.N - 1) * a.row_bytes + a.K;
       const float* ws = reinterpret_cast<const float*>(a.w + wrow);
       const float* ws2 = DUAL ? reinterpret_cast<const float*>(a.w2 + wrow) : nullptr;
+      // the row's scales, four K blocks per 16-byte load, fetched four blocks ahead of their use (the scale strip of a
+      // row is padded to 16 bytes, so the last load stays inside the row)
+      const float4* ws4 = reinterpret_cast<const float4*>(ws);
+      const float4* ws24 = reinterpret_cast<const float4*>(ws2);
+      float4 w_cur = ws4[0], w_nxt = w_cur, w2_cur = DUAL ? ws24[0] : make_float4(0.f, 0.f, 0.f, 0.f), w2_nxt = w2_cur;
       // the activation scales of this tile's 32 tokens, [kb][token]; rows past the tile scale by zero
       if (ti > 0 && !mbar_wait(&xs_done, (uint32_t)(ti - 1) & 1u, abort_flag)) break;   // the previous tile's readers are done
       for (int i = et; i < kblocks * F8_BN; i += 128) {
@@ -182,10 +187,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant
       float acc[F8_BN], acc2[DUAL ? F8_BN : 1];
 #pragma unroll
       for (int i = 0; i < F8_BN; ++i) { acc[i] = 0.0f; if (DUAL) acc2[i] = 0.0f; }
-      float w_next = ws[0], w2_next = DUAL ? ws2[0] : 0.0f;
       for (int kb = 0; kb < kblocks; ++kb) {
-        const float wsc = w_next, wsc2 = w2_next;
-        if (kb + 1 < kblocks) { w_next = ws[kb + 1]; if (DUAL) w2_next = ws2[kb + 1]; }
+        const int j = kb & 3;
+        if (j == 0) {
+          if (kb > 0) { w_cur = w_nxt; if (DUAL) w2_cur = w2_nxt; }
+          if (kb + 4 < kblocks) { w_nxt = ws4[(kb >> 2) + 1]; if (DUAL) w2_nxt = ws24[(kb >> 2) + 1]; }
+        }
+        const float wsc = j == 0 ? w_cur.x : j == 1 ? w_cur.y : j == 2 ? w_cur.z : w_cur.w;
+        const float wsc2 = j == 0 ? w2_cur.x : j == 1 ? w2_cur.y : j == 2 ? w2_cur.z : w2_cur.w;
         if (!mbar_wait(&part_full[part], pphase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + part * ACC_COLS;
