@@ -229,7 +229,8 @@ class GpuEngine(Engine):
         from ..runtime.engine import EngineFault, EngineStalled
         out = []
         try:
-            bd = self._batch() if len(rows) > self.max_rows else None
+            # (with the draft layer on, every pass must also feed that layer's KV rows: those rounds keep the 8-row chain)
+            bd = self._batch() if len(rows) > self.max_rows and not getattr(self.dec, "mtp_on", False) else None
             if bd is not None:
                 # many sequences in one round: one batched pass per 64 rows instead of a pass per 8
                 for i in range(0, len(rows), self.batch_rows):
