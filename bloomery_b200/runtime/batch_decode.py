@@ -92,7 +92,10 @@ class BatchDecode:
             self.Ap = torch.zeros(self.cap, H, **bf)
             self.act = torch.zeros(self.cap, I_, **bf)
             self.slot_out = torch.zeros(n, H, **f32)
-            self.moe_tiles = G.TileTable(n, E, dev, TILE)
+            # bf16 expert stacks multiply as they are through the bf16 GEMM, whose token tiles are 128 rows
+            moe0 = next(il for il in range(s.n_layer) if s.layer_is_moe(il))
+            self.float_experts = e.w.q[f"blk.{moe0}.ffn_gate_exps.weight"].qtype == "BF16"
+            self.moe_tiles = G.TileTable(n, E, dev, 128 if self.float_experts else TILE)
         # widths come from the weights: a rank of a several-GPU engine holds a slice of the dense and shared widths
         wq = e.w.q
         dense = [il for il in range(s.n_layer) if not s.layer_is_moe(il)]
@@ -156,17 +159,27 @@ class BatchDecode:
         if G.qgemm_supports(Wq):
             G.qgemm(X, Wq, tiles, W2=W2, status=self.status, **kw)
             return 1
+        if Wq.qtype == "BF16":
+            # bf16 rows need no expansion: the bf16 GEMM reads them in place (token tiles of 128 rows)
+            if tiles.tile_rows != 128:
+                tiles = self._dense128(M)
+            G.gemm_bf16(X, Wq.data.view(torch.bfloat16), tiles, B2=W2.data.view(torch.bfloat16) if W2 is not None else None,
+                        status=self.status, **kw)
+            return 1
         assert W2 is None, "the SwiGLU pair needs a type with a quantised-weight kernel"
         name = f"{Wq.rows}x{Wq.k}"
         wb = self._scratch_w.get(name)
         if wb is None:
             wb = self._scratch_w[name] = torch.empty(Wq.rows, Wq.k, dtype=torch.bfloat16, device=self.e.device)
         G.dequant_bf16(Wq, wb)
-        dt = self._scratch_w.get(("t", M))
-        if dt is None:
-            dt = self._scratch_w[("t", M)] = G.TileTable.dense(M, self.e.device)
-        G.gemm_bf16(X, wb, dt, status=self.status, **kw)
+        G.gemm_bf16(X, wb, self._dense128(M), status=self.status, **kw)
         return 2
+
+    def _dense128(self, M: int):
+        t = self._scratch_w.get(("t", M))
+        if t is None:
+            t = self._scratch_w[("t", M)] = G.TileTable.dense(M, self.e.device)
+        return t
 
     def _dense32(self, M: int):
         t = self._scratch_w.get(("t32", M))
@@ -198,7 +211,10 @@ class BatchDecode:
                 pairs = [("ffn_gate.weight", "ffn_up.weight", None)]
             for g_, u_, d_ in pairs:
                 qg, qu = w.q[b + g_], w.q[b + u_]
-                if not (G.qgemm_supports(qg) and qg.qtype == qu.qtype and (d_ is None or G.qgemm_supports(w.q[b + d_]))):
+                ok = lambda q_: G.qgemm_supports(q_) or q_.qtype == "BF16"          # noqa: E731
+                if d_ is not None and (w.q[b + d_].qtype == "BF16") != (qg.qtype == "BF16"):
+                    raise NotImplementedError(f"{b}{d_}: expert stacks mix bf16 with block types")
+                if not (ok(qg) and qg.qtype == qu.qtype and (d_ is None or ok(w.q[b + d_]))):
                     raise NotImplementedError(f"{b}{g_}: type {qg.qtype}/{qu.qtype} has no kernel in the batched pass")
 
     def shared_expert(self, il: int, M: int, xn: torch.Tensor, tiles, out: torch.Tensor, resid: torch.Tensor) -> int:

@@ -565,8 +565,27 @@ class DecodeEngine:
         # the kernel writes the fault copy at index M (the bucket size)
         return self._tokens_out_np.tolist()
 
+    def _float_expert_pass(self):
+        """bf16 expert stacks have no int8-dot kernel: every pass of such a model, however few rows, is the batched
+        tensor-core pass (``runtime/batch_decode.py``), which multiplies bf16 rows in place."""
+        if not hasattr(self, "_float_pass"):
+            self._float_pass = None
+            s = self.spec
+            if s.is_moe and type(self) is DecodeEngine:
+                moe0 = next(il for il in range(s.n_layer) if s.layer_is_moe(il))
+                if self.w.q[f"blk.{moe0}.ffn_gate_exps.weight"].qtype == "BF16":
+                    from .batch_decode import BatchDecode
+                    self._float_pass = BatchDecode(self, max_rows=16)
+        return self._float_pass
+
     def step(self, rows: Sequence[Tuple[int, int, int]], head: bool = True) -> List[int]:
         """One pass over ``rows``; returns the greedy token of every row."""
+        bd = self._float_expert_pass()
+        if bd is not None:
+            with self._lock:
+                out = bd.step(rows)
+                self.logits[:len(rows)].copy_(bd.logits[:len(rows)])
+                return out if head else []
         with self._lock:
             M = self.set_rows(rows)
             self.launch(M, head, False)

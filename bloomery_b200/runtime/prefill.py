@@ -304,6 +304,8 @@ class GemmPrefill:
         """Whether the layers' bf16 copies stay in HBM between prompts (decided once, before the first copy exists)."""
         if self.expert_source is not None or self.resident_bf16 is False:
             return False
+        if any(q.qtype == "BF16" and q.data.dim() == 3 for q in self.e.w.q.values()):     # bf16 stacks: a copy would only double them
+            return False
         if self._resident_ok is None:
             if self.resident_bf16:
                 self._resident_ok = True

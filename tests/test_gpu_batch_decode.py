@@ -179,3 +179,37 @@ def test_serving_engine_takes_the_batched_pass_for_many_rows():
             agree += int(t8 == tb)
     assert agree >= n - 3
     assert many[4][0] == Sampler(sp).sample(many[4][1], [])       # the sampled row follows the host chain on its logits
+
+
+def test_bf16_expert_stacks_serve_through_the_batched_pass():
+    """A bf16 checkpoint has no int8-dot expert kernel: every pass of its engine, prompts of a few rows included, is the
+    batched tensor-core pass on the bf16 rows as they are.  Same seeded weights as Q8_0 rows give logits in a band."""
+    from bloomery_b200.runtime.batch_decode import BatchDecode
+    spec, e_bf = _engine(24, "BF16")
+    _, e_q8 = _engine(24, "Q8_0")
+    assert e_bf._float_expert_pass() is not None and e_q8._float_expert_pass() is None
+    g = torch.Generator().manual_seed(17)
+    rows = []
+    for slot in range(24):
+        n = (90 if slot == 0 else 4) + slot % 5                 # slot 0: the GEMM prompt path, the rest: passes of 8 rows
+        prompt = torch.randint(0, spec.vocab, (n,), generator=g).tolist()
+        a, b = e_q8.prefill(slot, prompt), e_bf.prefill(slot, prompt)
+        rows.append((slot, a, n))
+    ref_tok = e_q8.step(rows[:6])
+    ref = e_q8.logits[:6].clone()
+    got_tok = e_bf.step(rows[:6])                               # six rows: still the batched pass
+    got = e_bf.logits[:6]
+    err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
+    assert err < 5e-2, err
+    top2 = ref.topk(2, dim=1).values
+    clear = ((top2[:, 0] - top2[:, 1]) > 0.1 * ref.abs().amax(dim=1)).cpu().tolist()
+    assert all(x == y for x, y, c in zip(got_tok, ref_tok, clear) if c)
+    for e in (e_q8, e_bf):
+        for slot, _, n in rows[:6]:
+            e.cut(slot, n)
+    many = BatchDecode(e_bf, max_rows=32)                       # and a round of 24 sequences
+    wide = BatchDecode(e_q8, max_rows=32)
+    many.step(rows)
+    wide.step(rows)
+    err = ((many.logits[:24] - wide.logits[:24]).abs().amax(dim=1) / wide.logits[:24].abs().amax(dim=1)).max().item()
+    assert err < 5e-2, err
