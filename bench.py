@@ -187,6 +187,7 @@ def batch_arm(args, spec, w, dev, local, steps, warm, t_load) -> int:
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": (f"{mix.lower()} weights against e4m3 activations (1x128 scales) on tcgen05 kind::f8f6f4, fp32 promotion every 128 values, f16 KV"
                   if mix == "FP8_B128" and bd.fp8_native else
+                  "bf16 weights and activations on tcgen05 kind::f16, fp32 accumulate, f16 KV" if mix == "BF16" else
                   f"{mix.lower()} weights expanded to bf16 inside the tcgen05 GEMM, fp32 accumulate, f16 KV"),
         "data": f"synthetic: seeded random token ids, random-init N(0,0.02) weights quantised {mix} on the card",
         "config": {"model": spec.name, "global_batch": B, "seq_len": args.prompt + warm + steps, "prompt_tokens": args.prompt,

@@ -38,7 +38,7 @@ def run_batch_distributed(args, rank: int, local: int, world: int) -> int:
     t0 = time.time()
     for slot in range(B):
         prompt = torch.randint(0, spec.vocab, (args.prompt,), generator=g).tolist()
-        rows.append((slot, eng.prefill(slot, prompt, gemm=False), args.prompt))
+        rows.append((slot, bd.prefill(slot, prompt), args.prompt))     # passes of up to 64 positions of the one sequence
     torch.cuda.synchronize()
     t_prompts = time.time() - t0
     for slot in range(B):
@@ -95,6 +95,7 @@ def run_batch_distributed(args, rank: int, local: int, world: int) -> int:
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": (f"{mix.lower()} weights against e4m3 activations (1x128 scales) on tcgen05 kind::f8f6f4, fp32 promotion every 128 values, f16 KV"
                       if mix == "FP8_B128" and bd.fp8_native else
+                      "bf16 weights and activations on tcgen05 kind::f16, fp32 accumulate, f16 KV" if mix == "BF16" else
                       f"{mix.lower()} weights expanded to bf16 inside the tcgen05 GEMM, fp32 accumulate, f16 KV"),
             "data": f"synthetic: seeded random token ids, random-init N(0,0.02) weights quantised {mix} on the card",
             "config": {"model": spec.name, "global_batch": B, "seq_len": args.prompt + warm + steps, "prompt_tokens": args.prompt,

@@ -424,6 +424,16 @@ class BatchDecode:
         with torch.cuda.stream(self._stream):
             g.replay()
 
+    def prefill(self, slot: int, tokens: Sequence[int], start: int = 0) -> int:
+        """Feed a prompt through passes of up to ``max_rows`` consecutive positions of one sequence (every row attends
+        to the rows before it in the same pass); returns the greedy token after the last one.  The several-GPU form of
+        the pass has no other prompt path for models whose 8-row chain cannot run on a rank's share of the weights."""
+        last = -1
+        for i in range(0, len(tokens), self.R):
+            chunk = tokens[i:i + self.R]
+            last = self.step([(slot, int(t), start + i + j) for j, t in enumerate(chunk)])[len(chunk) - 1]
+        return last
+
     def step(self, rows: Sequence[Tuple[int, int, int]]) -> List[int]:
         """One pass: the arg-max token of every row."""
         M = self.set_rows(rows)

@@ -213,3 +213,27 @@ def test_bf16_expert_stacks_serve_through_the_batched_pass():
     wide.step(rows)
     err = ((many.logits[:24] - wide.logits[:24]).abs().amax(dim=1) / wide.logits[:24].abs().amax(dim=1)).max().item()
     assert err < 5e-2, err
+
+
+def test_prompt_through_passes_of_one_sequence_matches_the_row_chain():
+    """``BatchDecode.prefill``: up to 64 consecutive positions of one sequence per pass, each row attending to the rows
+    before it in the same pass; the token after the prompt and the next decode step match the 8-row chain's."""
+    from bloomery_b200.runtime.batch_decode import BatchDecode
+    spec, eng = _engine(2)
+    g = torch.Generator().manual_seed(23)
+    prompt = torch.randint(0, spec.vocab, (150,), generator=g).tolist()
+    want = eng.prefill(0, prompt, gemm=False)
+    ref = eng.logits[(150 - 1) % 8][None].clone()               # the chain's last pass held 6 rows: its last row's logits
+    bd = BatchDecode(eng, max_rows=64)
+    got = bd.prefill(1, prompt)
+    n_last = 150 - 128 - 1                                      # the last pass held 22 rows: its last row's logits
+    err = float((bd.logits[n_last] - ref[0]).abs().max() / ref.abs().max())
+    assert err < 5e-2, err
+    top2 = ref[0].topk(2).values
+    if float(top2[0] - top2[1]) > 0.1 * float(ref.abs().max()):
+        assert got == want
+    a = eng.step([(0, want, 150)])
+    la = eng.logits[:1].clone()
+    eng.step([(1, want, 150)])                                  # the chain decodes on top of the KV the passes wrote
+    err = float((eng.logits[0] - la[0]).abs().max() / la.abs().max())
+    assert err < 5e-2, err
