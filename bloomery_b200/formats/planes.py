@@ -176,8 +176,25 @@ def resident_dequantize(res: torch.Tensor, qtype: str, k: int) -> torch.Tensor:
 # ------------------------------------------------------------------------------------
 # Checkpoint naming -> one linear layer's resident rows
 # ------------------------------------------------------------------------------------
+def mxfp8_dequantize(codes: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """OCP MXFP8 (E4M3 codes [N, K], one E8M0 byte per 32 values [N, K / 32]) -> bf16 [N, K], exactly: a 3-bit mantissa
+    times a power of two always fits bf16 while the exponent stays in its range."""
+    n, k = codes.shape
+    if k % 32 or tuple(scales.shape) != (n, k // 32):
+        raise PlaneError(f"MXFP8 codes {tuple(codes.shape)} with scales {tuple(scales.shape)}: one scale byte per 32 values")
+    if bool((scales == 255).any()):
+        raise PlaneError("MXFP8 scale byte 255 (NaN)")
+    out = torch.empty(n, k, dtype=torch.bfloat16, device=codes.device)
+    for r0 in range(0, n, 8192):                       # rows per pass: the decode makes full-size f32 temporaries
+        c = codes[r0:r0 + 8192]
+        sc = torch.exp2(scales[r0:r0 + 8192].to(torch.float32) - 127.0)
+        v = e4m3_decode(c.view(torch.uint8)).reshape(c.shape[0], k // 32, 32) * sc[:, :, None]
+        out[r0:r0 + 8192] = v.reshape(c.shape[0], k).to(torch.bfloat16)
+    return out
+
+
 def detect_scheme(config: dict) -> str:
-    """'fp8_b128', 'nvfp4_modelopt', 'nvfp4_ct' or 'plain' from config.json's quantization block."""
+    """'fp8_b128', 'nvfp4_modelopt', 'nvfp4_ct', 'mxfp8' or 'plain' from config.json's quantization block."""
     q = config.get("quantization_config") or config.get("quantization") or {}
     method = str(q.get("quant_method", "")).lower()
     if method == "fp8":
@@ -185,6 +202,8 @@ def detect_scheme(config: dict) -> str:
         if bs and list(bs) != [128, 128]:
             raise PlaneError(f"fp8 block size {bs} is not 128x128")
         return "fp8_b128"
+    if method == "mxfp8":
+        return "mxfp8"
     if method == "modelopt" or "nvfp4" in str(q.get("quant_algo", "")).lower():
         return "nvfp4_modelopt"
     if method == "compressed-tensors":
@@ -205,6 +224,24 @@ def linear_resident(folder, stem: str, scheme: str) -> Tuple[torch.Tensor, str, 
         packed = folder.tensor(f"{stem}.weight")
         ts = folder.tensor(f"{stem}.weight_scale_2").float().reshape(-1)
         return nvfp4_resident(packed, folder.tensor(f"{stem}.weight_scale"), ts), "NVFP4", packed.shape[1] * 2
+    if scheme == "nvfp4_modelopt" and f"{stem}.weight_scale_2" in folder:
+        # the block scales are stored compressed (formats/csf.py): a base byte per row and 4-bit codes
+        from . import csf
+        enc = csf.encoding_of(folder, f"{stem}.weight_scale")
+        if enc is None:
+            raise PlaneError(f"{stem}: NVFP4 weight without block scales (plain, csf or csf_32x2_v1)")
+        packed = folder.tensor(f"{stem}.weight")
+        n, k = packed.shape[0], packed.shape[1] * 2
+        try:
+            scales = torch.from_numpy(csf.weight_scale(folder, f"{stem}.weight_scale", enc, n, k // 16))
+        except csf.CsfError as exc:
+            raise PlaneError(str(exc)) from None
+        ts = folder.tensor(f"{stem}.weight_scale_2").float().reshape(-1)
+        return nvfp4_resident(packed, scales, ts), "NVFP4", k
+    if scheme == "mxfp8" and f"{stem}.weight_scale" in folder:
+        # value-preserving load as bf16 rows (twice the bytes of the file: no kernel here reads 32-wide E8M0 scales)
+        w = mxfp8_dequantize(folder.tensor(f"{stem}.weight"), folder.tensor(f"{stem}.weight_scale"))
+        return w.contiguous().view(torch.uint8).reshape(w.shape[0], -1), "BF16", w.shape[1]
     if scheme == "nvfp4_ct" and f"{stem}.weight_packed" in folder:
         packed = folder.tensor(f"{stem}.weight_packed")
         div = folder.tensor(f"{stem}.weight_global_scale").float().reshape(-1)

@@ -464,3 +464,114 @@ def test_vnni_row_dots_agree_with_the_scalar_units(t):
     # the pool's gemv takes the same path: its rows agree with the reference too
     out = H.gemv(res, rt, K, codes, ds)[0]
     assert ((out - ref.float()).abs().max() / ref.abs().max()).item() < 1e-5
+
+
+def _scale_bytes(rows, cols, seed, spread=3, outliers=0.02):
+    """E4M3-like scale bytes: a row's bytes sit in a narrow window, a few far outside it."""
+    rng = np.random.default_rng(seed)
+    centre = rng.integers(40, 200, size=(rows, 1))
+    sc = np.clip(centre + rng.integers(-spread, spread + 9, size=(rows, cols)), 0, 255)
+    far = rng.random((rows, cols)) < outliers
+    sc[far] = rng.integers(0, 256, size=int(far.sum()))
+    return sc.astype(np.uint8)
+
+
+@pytest.mark.parametrize("rows,cols", [(32, 8), (64, 7), (160, 10), (4224, 6)])
+def test_compressed_nvfp4_scales_decode_to_the_bytes_they_encode(rows, cols):
+    from bloomery_b200.formats import csf
+    sc = _scale_bytes(rows, cols, rows + cols)
+    if cols % 2 == 0:
+        parts = csf.encode_csf(sc)
+        assert parts["nvfp4_csf_fixed"].shape == (rows // 16, 16 * (1 + cols // 2))
+        assert 0 < parts["nvfp4_csf_exceptions"].size < rows * cols // 8          # the window holds most bytes
+        got = csf.decode_csf("s", parts["nvfp4_csf_fixed"], parts["nvfp4_csf_exceptions"], rows, cols)
+        assert np.array_equal(got, sc)
+    p32 = csf.encode_csf32(sc)
+    blocks = rows // 32 * ((cols + 1) // 2)
+    tiles = -(-(rows // 32) // 4) * -(-((cols + 1) // 2) // 2)
+    assert p32["csf32_offsets"].size == blocks + -(-tiles // 32) and p32["csf32_codes"].size == rows * cols // 2
+    got = csf.decode_csf32("s", p32["csf32_bases"], p32["csf32_codes"], p32["csf32_page_bases"], p32["csf32_offsets"],
+                           p32["csf32_exceptions"], rows, cols)
+    assert np.array_equal(got, sc)
+    if rows == 4224:
+        assert p32["csf32_page_bases"].size > 1 and int(p32["csf32_page_bases"][1]) > 0     # more than one page of records
+
+
+def test_compressed_scales_breaking_a_rule_are_refused_by_name():
+    from bloomery_b200.formats import csf
+    sc = _scale_bytes(64, 8, 1)
+    a = csf.encode_csf(sc)
+    fixed, exc = a["nvfp4_csf_fixed"].copy(), a["nvfp4_csf_exceptions"].copy()
+    with pytest.raises(csf.CsfError, match="slabs"):
+        csf.decode_csf("s", fixed.reshape(-1)[:-1], exc, 64, 8)
+    with pytest.raises(csf.CsfError, match="multiple of 16"):
+        csf.decode_csf("s", fixed, exc, 60, 8)
+    bad = fixed.copy(); bad[1, 3] = 241
+    with pytest.raises(csf.CsfError, match="row 19 base 241"):
+        csf.decode_csf("s", bad, exc, 64, 8)
+    with pytest.raises(csf.CsfError, match="increasing"):
+        csf.decode_csf("s", fixed, exc[::-1].copy(), 64, 8)
+    with pytest.raises(csf.CsfError, match="below 512"):
+        csf.decode_csf("s", fixed, np.asarray([600], dtype=np.uint32), 64, 8)
+    b = csf.encode_csf32(sc)
+    args = lambda **kw: [kw.get(k, b[k]) for k in ("csf32_bases", "csf32_codes", "csf32_page_bases", "csf32_offsets", "csf32_exceptions")]  # noqa: E731
+    with pytest.raises(csf.CsfError, match="offsets hold"):
+        csf.decode_csf32("s", *args(csf32_offsets=b["csf32_offsets"][:-1]), 64, 8)
+    with pytest.raises(csf.CsfError, match="page 0: base 2"):
+        csf.decode_csf32("s", *args(csf32_page_bases=np.asarray([2], dtype=np.uint32)), 64, 8)
+    off = b["csf32_offsets"].copy(); off[-1] += 1
+    with pytest.raises(csf.CsfError, match="prefixes|records"):
+        csf.decode_csf32("s", *args(csf32_offsets=off), 64, 8)
+    if b["csf32_exceptions"].size:
+        recs = b["csf32_exceptions"].copy(); recs[0] = (recs[0] & 0xFF00) | 200          # place 200: row 100 of a 32-row block
+        with pytest.raises(csf.CsfError, match="outside its 32"):
+            csf.decode_csf32("s", *args(csf32_exceptions=recs), 64, 8)
+    with pytest.raises(csf.CsfError, match="records"):
+        csf.decode_csf32("s", *args(csf32_exceptions=np.append(b["csf32_exceptions"], np.uint16(5))), 64, 8)
+
+
+@pytest.mark.parametrize("enc", ["csf", "csf_32x2_v1"])
+def test_modelopt_checkpoint_with_compressed_scales_loads_like_the_plain_one(tmp_path, enc):
+    from bloomery_b200.formats import csf
+    from bloomery_b200.formats import planes as P
+    from bloomery_b200.formats import safetensors as S
+    torch.manual_seed(8)
+    w = torch.randn(64, 256)
+    pk, s, t = P.nvfp4_quantize(w)
+    parts = (csf.encode_csf if enc == "csf" else csf.encode_csf32)(s.view(torch.uint8).numpy())
+    tensors = {"a.weight": pk, "a.weight_scale_2": t.reshape(1)}
+    tags = {}
+    for suffix, arr in parts.items():
+        signed = {np.dtype(np.uint16): np.int16, np.dtype(np.uint32): np.int32}.get(arr.dtype)
+        tensors[f"a.weight_scale.{suffix}"] = torch.from_numpy(arr.view(signed) if signed else arr.copy())
+        if signed:
+            tags[f"a.weight_scale.{suffix}"] = "U16" if arr.dtype == np.uint16 else "U32"
+    S.write_folder(str(tmp_path / "m"), tensors, {"quantization_config": {"quant_method": "modelopt", "quant_algo": "NVFP4"}},
+                   dtypes=tags)
+    f = S.Folder(str(tmp_path / "m"))
+    res, ty, k = P.linear_resident(f, "a", "nvfp4_modelopt")
+    assert ty == "NVFP4" and k == 256
+    assert torch.equal(res, P.nvfp4_resident(pk, s, t))
+    f.close()
+
+
+def test_mxfp8_checkpoint_loads_as_exact_bf16_rows(tmp_path):
+    from bloomery_b200.formats import planes as P
+    from bloomery_b200.formats import safetensors as S
+    g = torch.Generator().manual_seed(9)
+    codes = torch.randint(0, 256, (48, 128), generator=g, dtype=torch.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x3A                               # no NaN codes
+    scales = torch.randint(110, 140, (48, 4), generator=g, dtype=torch.uint8)
+    want = (P.e4m3_decode(codes).reshape(48, 4, 32).double() * torch.exp2(scales.double() - 127)[:, :, None]).reshape(48, 128)
+    got = P.mxfp8_dequantize(codes, scales)
+    assert got.dtype == torch.bfloat16 and torch.equal(got.double(), want)          # exact: nothing is rounded
+    S.write_folder(str(tmp_path / "m"), {"a.weight": codes, "a.weight_scale": scales, "n.weight": torch.randn(16, 128).bfloat16()},
+                   {"quantization_config": {"quant_method": "mxfp8"}}, dtypes={"a.weight": "F8_E4M3", "a.weight_scale": "F8_E8M0"})
+    f = S.Folder(str(tmp_path / "m"))
+    assert P.detect_scheme(f.config) == "mxfp8"
+    res, ty, k = P.linear_resident(f, "a", "mxfp8")
+    assert ty == "BF16" and k == 128 and torch.equal(res.view(torch.bfloat16).double(), want)
+    assert P.linear_resident(f, "n", "mxfp8")[1] == "BF16"
+    f.close()
+    with pytest.raises(P.PlaneError, match="255"):
+        P.mxfp8_dequantize(codes, torch.full((48, 4), 255, dtype=torch.uint8))
