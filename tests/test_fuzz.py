@@ -107,3 +107,40 @@ def test_safetensors_header_tricks_are_refused(tmp_path):
             Safetensors(file_with(h))
     ok = Safetensors(file_with({"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}, "__metadata__": {"k": "v"}}))
     assert ok.tensor("a").shape == (4,) and ok.metadata == {"k": "v"}
+
+
+@SET
+@given(st.binary(max_size=600), st.binary(max_size=64), st.integers(min_value=0, max_value=96), st.integers(min_value=0, max_value=12))
+def test_compressed_scale_decoders_refuse_or_answer(fixed, exc, rows, cols):
+    """Whatever bytes stand where a checkpoint's compressed scales should be, the decoders answer with rows x cols bytes
+    or raise their own error."""
+    import numpy as np
+    from bloomery_b200.formats import csf
+    f8 = np.frombuffer(fixed, dtype=np.uint8)
+    words = np.frombuffer(exc[:len(exc) // 4 * 4], dtype=np.uint32)
+    try:
+        out = csf.decode_csf("s", f8, words, rows, cols)
+        assert out.shape == (rows, cols)
+    except csf.CsfError:
+        pass
+    half = np.frombuffer(exc[:len(exc) // 2 * 2], dtype=np.uint16)
+    try:
+        out = csf.decode_csf32("s", f8[:rows], f8[rows:rows + rows * cols // 2], words[:1], half, half[::-1].copy(), rows, cols)
+        assert out.shape == (rows, cols)
+    except csf.CsfError:
+        pass
+
+
+@SET
+@given(st.integers(min_value=1, max_value=4), st.integers(min_value=1, max_value=9), st.integers(min_value=0, max_value=2 ** 32 - 1))
+def test_compressed_scale_round_trip_on_any_bytes(slabs, cols, seed):
+    import numpy as np
+    from bloomery_b200.formats import csf
+    sc = np.random.default_rng(seed).integers(0, 256, size=(32 * slabs, cols), dtype=np.uint8)       # no window at all
+    p = csf.encode_csf32(sc) if (32 * slabs * cols) % 2 == 0 else None
+    if p is not None:
+        assert np.array_equal(csf.decode_csf32("s", p["csf32_bases"], p["csf32_codes"], p["csf32_page_bases"], p["csf32_offsets"],
+                                               p["csf32_exceptions"], 32 * slabs, cols), sc)
+    if cols % 2 == 0:
+        q = csf.encode_csf(sc)
+        assert np.array_equal(csf.decode_csf("s", q["nvfp4_csf_fixed"], q["nvfp4_csf_exceptions"], 32 * slabs, cols), sc)
