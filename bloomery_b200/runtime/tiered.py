@@ -71,6 +71,18 @@ class TieredEngine(DecodeEngine):
         pre.expert_source = ExpertStreamer(self.tiered, self.device).get
         return pre
 
+    def set_prompt_costs(self, costs) -> int:
+        """Derive ``gemm_threshold`` (the prompt width from which the layer's stacks are streamed to the card instead of
+        the rows taking the pass path with the host leg) from priced constants: the least width at which the split rule
+        of ``runtime/xsplit.py`` moves any host expert to the card.  Returns the threshold."""
+        from .xsplit import stream_gate
+        s = self.spec
+        n_host = max(1, s.n_expert - self.tiered.n_slots)
+        gate = stream_gate(costs, n_host)
+        if self.nvme is None:                # experts on a drive have no pinned stacks to stream from
+            self.gemm_threshold = max(2, gate)
+        return gate
+
     def _after_pass(self, n_rows: int) -> None:
         self.tiered.boundary(self.heat, n_rows)
 

@@ -1,4 +1,5 @@
 """Host-side runtime parts: watchdog, waits, capture lock, cost store and race, route traces, census."""
+import dataclasses
 import threading
 import time
 
@@ -407,3 +408,39 @@ def test_tiered_experts_resize_keeps_the_hottest_on_cpu_tensors():
         for e, slot in t.slot_of[il].items():
             assert torch.equal(t.card[il]["ffn_up_exps"].data[slot], t.host[il]["ffn_up_exps"].data[e])
     assert t.n_slots == 4 and t.slot_bytes() * 5 == t.card_bytes()      # n_slots + 1 spare in every layer
+
+
+def test_expert_split_rule_balances_card_and_host_sides():
+    """The prompt-time split of a layer's host experts (``runtime/xsplit.py``): hottest first, an expert moves to the card
+    while the card's side after it stays under the host's side without it."""
+    from bloomery_b200.runtime.xsplit import Costs, burst_share, split, stream_gate
+    c = Costs(lane_b_per_us=50e3, expert_bytes=10_000_000, host_us_fixed=400.0, host_us_per_row=30.0, card_us_fixed=5.0,
+              card_us_per_row=0.5, n_expert=8, top_k=2)
+    counts = [40, 0, 12, 3, 90, 0, 7, 1]
+    host = [0, 2, 3, 4, 6, 7]
+    sp = split(counts, host, c)
+    # hottest first: 4 (90 rows), 0 (40), 2 (12) ...; every streamed one is hotter than every kept one
+    assert sp.streamed[:2] == (4, 0) and set(sp.streamed) | set(sp.kept) == {0, 2, 3, 4, 6, 7}
+    assert min(counts[e] for e in sp.streamed) >= max(counts[e] for e in sp.kept)
+    assert sp.card_us <= sp.host_us                                  # the walk stops short of the crossing
+    rate = c.lane_b_per_us * (1 - burst_share(c, sum(counts[e] for e in host), 6))
+    assert abs(sp.beside_b_per_us - rate) < 1e-9 and rate < c.lane_b_per_us
+    nxt = sp.kept[0]                                                 # one more move would cross
+    more = sp.card_us + c.expert_bytes / rate + c.card_us_fixed + c.card_us_per_row * counts[nxt]
+    assert more > sp.host_us - max(c.host_us_fixed, c.host_us_per_row * counts[nxt])
+    assert split(counts, host, c) == sp                              # the same counts give the same split
+    assert split([1, 0, 0, 0, 0, 0, 0, 0], [0], c).streamed == ()    # a lone cold expert is not worth its copy
+    busy = split(counts, host, c, card_base_us=1e6)                  # a card already behind takes nothing
+    assert busy.streamed == () and len(busy.kept) == 6
+    with pytest.raises(ValueError):
+        split(counts[:-1], host, c)
+    with pytest.raises(ValueError):
+        split(counts, [0, 0], c)
+    # the gate: narrow prompts stream nothing, wide ones do, and a faster lane lowers the width
+    gate = stream_gate(c, n_host=6)
+    assert 1 < gate <= 1 << 16
+    per = lambda rows: [rows * c.top_k // c.n_expert] * c.n_expert            # noqa: E731
+    assert not split(per(gate - 1), list(range(6)), c).streamed and split(per(gate), list(range(6)), c).streamed
+    fast = dataclasses.replace(c, lane_b_per_us=500e3)
+    assert stream_gate(fast, n_host=6) < gate
+    assert stream_gate(dataclasses.replace(c, lane_b_per_us=1.0), n_host=6, limit=4096) == 4097
