@@ -193,8 +193,28 @@ def mxfp8_dequantize(codes: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def mxfp4_resident(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """OCP MXFP4 as checkpoints pack it (two E2M1 codes a byte, the even value in the low nibble, [N, K / 2]; one E8M0
+    byte per 32 values [N, K / 32]) -> resident ``Q8_F32`` rows: the doubled code values are small integers and half
+    the block scale puts the factor back, so value = code * scale exactly (the form the GGUF MXFP4 blocks load as)."""
+    from .iq_tables import KVALUES_MXFP4, e8m0_half
+    from .resident import resident_row_bytes
+    n, k = packed.shape[0], packed.shape[1] * 2
+    if k % 32 or tuple(scales.shape) != (n, k // 32):
+        raise PlaneError(f"MXFP4 codes {tuple(packed.shape)} with scales {tuple(scales.shape)}: one scale byte per 32 values")
+    if bool((scales == 255).any()):
+        raise PlaneError("MXFP4 scale byte 255 (NaN)")
+    lut = torch.tensor(KVALUES_MXFP4, dtype=torch.int8, device=packed.device)
+    p8 = packed.view(torch.uint8).to(torch.int64)
+    codes = torch.stack([lut[p8 & 15], lut[p8 >> 4]], dim=-1).reshape(n, k)
+    out = torch.zeros(n, resident_row_bytes("Q8_F32", k), dtype=torch.uint8, device=packed.device)
+    out[:, :k] = codes.view(torch.uint8)
+    out[:, k:k + k // 8] = e8m0_half(scales.view(torch.uint8)).contiguous().view(torch.uint8).reshape(n, k // 8)
+    return out
+
+
 def detect_scheme(config: dict) -> str:
-    """'fp8_b128', 'nvfp4_modelopt', 'nvfp4_ct', 'mxfp8' or 'plain' from config.json's quantization block."""
+    """'fp8_b128', 'nvfp4_modelopt', 'nvfp4_ct', 'mxfp4_ct', 'mxfp8' or 'plain' from config.json's quantization block."""
     q = config.get("quantization_config") or config.get("quantization") or {}
     method = str(q.get("quant_method", "")).lower()
     if method == "fp8":
@@ -207,7 +227,10 @@ def detect_scheme(config: dict) -> str:
     if method == "modelopt" or "nvfp4" in str(q.get("quant_algo", "")).lower():
         return "nvfp4_modelopt"
     if method == "compressed-tensors":
-        if str(q.get("format", "")).lower() != "nvfp4-pack-quantized":
+        fmt = str(q.get("format", "")).lower()
+        if fmt == "mxfp4-pack-quantized":
+            return "mxfp4_ct"
+        if fmt != "nvfp4-pack-quantized":
             raise PlaneError(f"compressed-tensors format {q.get('format')!r} is not read")
         return "nvfp4_ct"
     if method:
@@ -238,6 +261,9 @@ def linear_resident(folder, stem: str, scheme: str) -> Tuple[torch.Tensor, str, 
             raise PlaneError(str(exc)) from None
         ts = folder.tensor(f"{stem}.weight_scale_2").float().reshape(-1)
         return nvfp4_resident(packed, scales, ts), "NVFP4", k
+    if scheme == "mxfp4_ct" and f"{stem}.weight_packed" in folder:
+        packed = folder.tensor(f"{stem}.weight_packed")
+        return mxfp4_resident(packed, folder.tensor(f"{stem}.weight_scale")), "Q8_F32", packed.shape[1] * 2
     if scheme == "mxfp8" and f"{stem}.weight_scale" in folder:
         # value-preserving load as bf16 rows (twice the bytes of the file: no kernel here reads 32-wide E8M0 scales)
         w = mxfp8_dequantize(folder.tensor(f"{stem}.weight"), folder.tensor(f"{stem}.weight_scale"))

@@ -575,3 +575,23 @@ def test_mxfp8_checkpoint_loads_as_exact_bf16_rows(tmp_path):
     f.close()
     with pytest.raises(P.PlaneError, match="255"):
         P.mxfp8_dequantize(codes, torch.full((48, 4), 255, dtype=torch.uint8))
+
+
+def test_packed_mxfp4_checkpoint_loads_as_exact_code_rows(tmp_path):
+    from bloomery_b200.formats import planes as P
+    from bloomery_b200.formats import safetensors as S
+    from bloomery_b200.formats.resident import decode_q8_f32
+    g = torch.Generator().manual_seed(10)
+    packed = torch.randint(0, 256, (24, 64), generator=g, dtype=torch.uint8)               # 128 values a row
+    scales = torch.randint(118, 134, (24, 4), generator=g, dtype=torch.uint8)
+    mag = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=torch.float64)
+    vals = torch.stack([mag[(packed & 15).long()], mag[(packed >> 4).long()]], dim=-1).reshape(24, 4, 32)
+    want = (vals * torch.exp2(scales.double() - 127)[:, :, None]).reshape(24, 128)
+    S.write_folder(str(tmp_path / "m"), {"a.weight_packed": packed, "a.weight_scale": scales},
+                   {"quantization_config": {"quant_method": "compressed-tensors", "format": "mxfp4-pack-quantized"}})
+    f = S.Folder(str(tmp_path / "m"))
+    assert P.detect_scheme(f.config) == "mxfp4_ct"
+    res, ty, k = P.linear_resident(f, "a", "mxfp4_ct")
+    assert ty == "Q8_F32" and k == 128
+    assert torch.equal(decode_q8_f32(res, k).double(), want)
+    f.close()
