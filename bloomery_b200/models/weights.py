@@ -327,6 +327,17 @@ def load_gguf(path: str, device, ring_bytes: int = 256 << 20) -> Tuple[ModelSpec
     w = Weights(spec, device)
     dev = torch.device(device)
     use_ring = dev.type == "cuda"
+    # how warm the file is, then the kernel's read-ahead for a front-to-back pass over it (both best effort: a file
+    # system or platform that refuses leaves the load as it was)
+    from ..utils import osshim
+    g.page_cache = None
+    try:
+        seen = [osshim.populated(sh.map) for sh in g.shards]
+        g.page_cache = round(sum(p_.resident for p_ in seen) / max(1, sum(p_.pages for p_ in seen)), 4)
+        for sh in g.shards:
+            osshim.advise(sh.map, "sequential")
+    except OSError:
+        pass
     ring = [torch.empty(ring_bytes, dtype=torch.uint8, pin_memory=True) for _ in range(2)] if use_ring else None
     events = [None, None]
     slot = 0

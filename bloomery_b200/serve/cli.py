@@ -19,14 +19,11 @@ from ..utils.exit_codes import Code, Refusal, WORDS
 
 
 def _host_free_bytes() -> int:
+    from ..utils import osshim
     try:
-        with open("/proc/meminfo") as f:
-            for ln in f:
-                if ln.startswith("MemAvailable:"):
-                    return int(ln.split()[1]) * 1024
+        return osshim.host_memory().available
     except OSError:
-        pass
-    return 8 << 30
+        return 8 << 30
 
 
 def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, free_bytes: List[int]) -> Dict[str, Any]:
@@ -196,7 +193,7 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
         if n_vis == 0 and str(opts.get("dev") or "").lower() != "none" and str(opts.get("ngl", "")) != "0":
             raise Refusal(Code.NO_DEVICE, "no CUDA device is visible; -dev none starts the CPU-only engine on a model that fits host RAM")
         _, w, handle = open_model(path, "cpu")
-        records.write("setup", phase="load", seconds=round(time.time() - t0, 3))
+        records.write("setup", phase="load", seconds=round(time.time() - t0, 3), page_cache=getattr(handle, "page_cache", None))
         tk, tsrc, bos, eos = surface(handle)
         return CpuEngine(w, tk, plan["n_slots"], plan["slot_ctx"], name), tsrc, bos, eos
     from ..ops import host_ops

@@ -12,7 +12,7 @@ KINDS: Dict[str, List[str]] = {
     "need": ["weights_bytes", "kv_bytes_per_token", "host_bytes", "fits"],
     "ctx": ["asked", "served", "trained"],
     "parallel": ["slots", "slot_ctx"],
-    "setup": ["phase", "seconds", "winner", "raced", "resident_per_layer", "host"],
+    "setup": ["phase", "seconds", "winner", "raced", "resident_per_layer", "host", "page_cache"],
     "watchdog": ["model", "site", "seconds"],
     "step_stats": ["steps", "card_wait_s", "kv_free_pages", "kv_spills", "free_bytes"],
     "request": ["id", "route", "slot", "prompt_tokens", "cached_tokens", "predicted_tokens", "prompt_ms",

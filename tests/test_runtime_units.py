@@ -444,3 +444,58 @@ def test_expert_split_rule_balances_card_and_host_sides():
     fast = dataclasses.replace(c, lane_b_per_us=500e3)
     assert stream_gate(fast, n_host=6) < gate
     assert stream_gate(dataclasses.replace(c, lane_b_per_us=1.0), n_host=6, limit=4096) == 4097
+
+
+def test_os_shim_calls(tmp_path):
+    """The operating-system calls behind one module: masks, memory, free bytes, page-cache residency, advice, no-replace
+    rename; refusals carry the call's name."""
+    import mmap
+    import os
+    from bloomery_b200.utils import osshim as O
+    cpus = O.mask_cpus()
+    assert cpus and all(isinstance(c, int) for c in cpus)
+    O.set_mask(cpus)                                              # the mask it already has
+    with pytest.raises(O.OsError):
+        O.set_mask([])
+    hm = O.host_memory()
+    assert 0 < hm.available <= hm.total and (hm.locked_limit == -1 or hm.locked_limit >= 0)
+    fake = tmp_path / "meminfo"
+    fake.write_text("MemTotal:       1000 kB\nMemFree: 1 kB\nMemAvailable:    400 kB\n")
+    fm = O.host_memory(str(fake))
+    assert (fm.total, fm.available) == (1000 << 10, 400 << 10)
+    assert O.page_bytes() in (4096, 16384, 65536) and O.max_rss_bytes() > 0
+    assert O.free_bytes(str(tmp_path)) > 0
+    with pytest.raises(O.OsError) as err:
+        O.free_bytes(str(tmp_path / "missing"))
+    assert err.value.what == "statvfs"
+    p = tmp_path / "blob"
+    p.write_bytes(os.urandom(3 * O.page_bytes() + 100))
+    with open(p, "rb") as fh:
+        m = mmap.mmap(fh.fileno(), 0, access=mmap.ACCESS_READ)
+        O.advise(m, "sequential")
+        O.advise(m, "willneed")
+        _ = m[0], m[O.page_bytes()], m[-1]                       # touch every page
+        got = O.populated(m)
+        assert got.pages == 4 and got.resident == 4 and got.fraction == 1.0
+        assert O.populated(m, O.page_bytes(), O.page_bytes()).pages == 1
+        with pytest.raises(O.OsError):
+            O.populated(m, 1)                                     # not on a page boundary
+        with pytest.raises(O.OsError):
+            O.advise(m, "sideways")
+        O.fadvise_dontneed(fh.fileno())
+        m.close()
+    a, b = tmp_path / "a", tmp_path / "b"
+    a.write_text("first")
+    b.write_text("second")
+    with pytest.raises(O.OsError):
+        O.rename_noreplace(str(a), str(b))
+    assert b.read_text() == "second" and a.exists()
+    O.rename_noreplace(str(a), str(tmp_path / "c"))
+    assert (tmp_path / "c").read_text() == "first" and not a.exists()
+    fd = None
+    try:
+        fd = O.open_direct(str(p))
+    except O.OsError as exc:                                      # tmpfs and some overlays refuse O_DIRECT by name
+        assert exc.what == "open O_DIRECT"
+    if fd is not None:
+        os.close(fd)
