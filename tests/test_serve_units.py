@@ -453,3 +453,26 @@ def test_reference_sets_carry_the_model_identity(tmp_path):
     open(out, "w").write("{}")
     with pytest.raises(R.RefsetError):
         R.read(out)
+    # the logits kind: KL divergence over the oracle's top ids, and the flip rule for a different arg-max
+    lset = str(tmp_path / "lset.json")
+    assert R.main(["make", a, lset, "--cases", "2", "--prompt-len", "6", "--logits"]) == 0
+    assert R.main(["check", a, lset]) == 0                     # the same model: zero divergence, no flips
+    assert R.main(["check", b, lset]) == 1
+    ldoc = json.load(open(lset))
+    _, fn = R._logits_fn(a, "cpu")
+    same = R.check_logits(ldoc, a, fn)
+    assert same["mean_kld"] < 1e-9 and same["flips"] == same["misses"] == 0 and same["positions"] == 12
+    import torch
+
+    def nudged(ids):                                           # the runner-up of position 0 takes the lead by a hair
+        lg = fn(ids).clone()
+        top = lg[0].topk(2)
+        lg[0, top.indices[1]] = top.values[0] + 1e-3
+        return lg
+    lead = ldoc["cases"][0]["top_logp"][0][0] - ldoc["cases"][0]["top_logp"][0][1]
+    out_n = R.check_logits(ldoc, a, nudged, max_mean_kld=1.0, flip_margin=lead + 1.0)
+    assert out_n["flips"] == 2 and out_n["misses"] == 0        # once per case: the same nudge on both prompts' first row
+    with pytest.raises(R.RefsetError, match="pick another id"):
+        R.check_logits(ldoc, a, nudged, max_mean_kld=1.0, flip_margin=0.0)
+    with pytest.raises(R.RefsetError, match="KL divergence"):
+        R.check_logits(ldoc, a, lambda ids: fn(ids) * 0.0, max_mean_kld=1e-7, flip_margin=100.0)
