@@ -42,7 +42,17 @@ def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, fre
     asked = int(opts.get("ctx") or 0)
     slot_ctx = int(opts.get("slot_ctx") or 0)
     if pl.devices:
-        dev_free = min(free_bytes[d] for d in pl.devices)
+        if pl.fit_targets_mib:
+            # -fitt MiB[,MiB...]: what stays free on each device of the list (one value serves them all); the tightest
+            # device decides, since every rank holds the same share
+            t = pl.fit_targets_mib
+            if len(t) not in (1, len(pl.devices)):
+                raise Refusal(Code.USAGE, f"-fitt names {len(t)} targets for {len(pl.devices)} devices")
+            keep = [(t[0] if len(t) == 1 else t[i]) << 20 for i in range(len(pl.devices))]
+            dev_free = min(free_bytes[d] - k_ for d, k_ in zip(pl.devices, keep))
+            margin = 0
+        else:
+            dev_free = min(free_bytes[d] for d in pl.devices)
         share = weights_bytes // (len(pl.devices) if pl.mode == "tp" else 1)
         room = dev_free - margin - share - (2 << 30)
         ebytes = int(opts.get("_expert_bytes") or weights_bytes * 0.9)

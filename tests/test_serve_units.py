@@ -431,6 +431,20 @@ def test_fit_on_keeps_what_fits_on_the_card():
     opts2["_expert_bytes"] = 16_000_000_000
     with pytest.raises(Refusal):
         plan_for(opts2, spec, 17_500_000_000, 1, [3 << 30])
+    # -fitt: what stays free per device; a larger target leaves fewer resident experts, a list names every device
+    def resident(*extra):
+        o = flags.parse(["-m", "x", "-fit", "on", "-np", "1", "-c", "8192", *extra], {})
+        o["_expert_bytes"] = 16_000_000_000
+        return int(plan_for(o, spec, 17_500_000_000, 1, [12 << 30])["placement"].host_experts.split(":")[1])
+    assert resident("-fitt", "3072") < resident("-fitt", "512")
+    two = flags.parse(["-m", "x", "-dev", "CUDA0,CUDA1", "--place", "tp", "-np", "1", "-c", "8192", "-fitt", "1024,78000"], {})
+    with pytest.raises(Refusal):                               # the second device keeps 78,000 MiB of its 81,920 free: nothing fits there
+        plan_for(two, spec, 17_500_000_000, 2, [80 << 30, 80 << 30])
+    two = flags.parse(["-m", "x", "-dev", "CUDA0,CUDA1", "--place", "tp", "-np", "1", "-c", "8192", "-fitt", "1024,2048"], {})
+    assert plan_for(two, spec, 17_500_000_000, 2, [80 << 30, 80 << 30])["slot_ctx"] == 8192
+    bad = flags.parse(["-m", "x", "-dev", "CUDA0,CUDA1", "--place", "tp", "-fitt", "1,2,3"], {})
+    with pytest.raises(Refusal):
+        plan_for(bad, spec, 17_500_000_000, 2, [80 << 30, 80 << 30])
 
 
 def test_reference_sets_carry_the_model_identity(tmp_path):
