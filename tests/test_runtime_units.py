@@ -499,3 +499,33 @@ def test_os_shim_calls(tmp_path):
         assert exc.what == "open O_DIRECT"
     if fd is not None:
         os.close(fd)
+
+
+def test_interleaved_ab_harness(capsys):
+    """Two arms run alternately; the answer is medians, ratio, per-round wins and a sign test."""
+    import json
+    import sys
+    from bloomery_b200.ops import ab
+    assert ab.figure("noise\nqgu staged us per layer: 123.5 fault word: 0x0\nus per layer: 99.25 tail") == 99.25
+    assert ab.figure('{"metric": "m", "value": 4553.2, "unit": "tok/s"}') == 4553.2
+    with pytest.raises(ab.AbError):
+        ab.figure("nothing here")
+    order = []
+    vals = {"A": iter([10.0, 10.2, 9.9, 10.1, 10.0, 10.3]), "B": iter([8.0, 8.1, 8.2, 7.9, 8.0, 8.1])}
+
+    def fake(cmd, pattern, timeout):
+        order.append(cmd)
+        return next(vals[cmd])
+    series = ab.interleave("A", "B", 6, run=fake)
+    assert order == ["A", "B", "B", "A", "A", "B", "B", "A", "A", "B", "B", "A"]      # the arms swap places every round
+    got = ab.compare(series["a"], series["b"])
+    assert got["wins_b"] == 6 and got["wins_a"] == 0 and got["verdict"] == "b" and got["sign_test_p"] < 0.05
+    assert abs(got["ratio_b_over_a"] - 8.05 / 10.05) < 1e-9
+    assert ab.compare([1.0, 2.0, 1.0, 2.0], [2.0, 1.0, 2.0, 1.0])["verdict"] == "same"
+    assert ab.compare([5.0] * 6, [4.0] * 6, higher_is_better=True)["verdict"] == "a"
+    py = sys.executable
+    arm = lambda text: py + " -c " + '"' + text + '"'            # noqa: E731
+    rc = ab.main([arm("print('us per layer: 12.5')"), arm("print('us per layer: 25.0')"), "--rounds", "2"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and out["median_a"] == 12.5 and out["ratio_b_over_a"] == 2.0 and out["a"] == [12.5, 12.5]
+    assert ab.main([arm("import sys; sys.exit(3)"), arm("print(1)"), "--rounds", "1"]) == 1
