@@ -90,8 +90,9 @@ def test_batched_chain_advances_every_sequence():
     assert int(bd.status.item()) == 0
 
 
-@pytest.mark.parametrize("world,arch", [(2, "qwen3moe"), (4, "qwen3moe"), (2, "deepseek"), (4, "deepseek")])
-def test_batched_pass_over_emulated_ranks_matches_one_gpu(world, arch):
+@pytest.mark.parametrize("world,arch,mix", [(2, "qwen3moe", "Q4_K_M"), (4, "qwen3moe", "Q4_K_M"), (2, "deepseek", "Q8_0"),
+                                            (4, "deepseek", "Q8_0")])
+def test_batched_pass_over_emulated_ranks_matches_one_gpu(world, arch, mix):
     """Experts split over ranks, attention and rows replicated, partial rows met in the rank-ordered all-reduce: the
     ranks walk a pass in lockstep on one stream and give the tokens and logits of the one-GPU batched pass."""
     from bloomery_b200.models.weights import Weights, synth_tensors
@@ -100,8 +101,9 @@ def test_batched_pass_over_emulated_ranks_matches_one_gpu(world, arch):
     from bloomery_b200.runtime.batch_decode import BatchDecode
     from bloomery_b200.runtime.engine import DecodeEngine
     spec = _spec(arch)
-    # the toy DeepSeek widths split four ways leave 64 columns of the shared expert: blocks of 32 still divide them
-    items = list(synth_tensors(spec, DEV, seed=3, mix="Q8_0" if arch == "deepseek" else "Q4_K_M"))
+    # the toy DeepSeek widths split four ways leave 64 columns of the shared expert: blocks of 32 (Q8_0) still divide
+    # them (``shard_items`` cuts file-type rows; FP8 planes are built per rank by ``synth_tensors(shard=...)`` instead)
+    items = list(synth_tensors(spec, DEV, seed=3, mix=mix))
     n_rows = 19
     full = DecodeEngine(Weights.from_items(spec, iter(items), DEV), n_slots=n_rows, slot_ctx=256)
     engs = [DecodeEngine(Weights.from_items(spec, shard_items(iter(items), spec, r, world, attn=False), DEV), n_slots=n_rows,
