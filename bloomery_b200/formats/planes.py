@@ -213,6 +213,31 @@ def mxfp4_resident(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def resident_k_slice(res: torch.Tensor, qtype: str, k: int, lo: int, hi: int) -> torch.Tensor:
+    """Columns [lo, hi) of resident FP8_B128 / NVFP4 rows [N, row bytes] as resident rows of width ``hi - lo`` (what a
+    rank that holds a slice of a matrix's input width loads): codes and scales of the span, the row's tensor scale kept."""
+    from .resident import resident_row_bytes
+    n = res.shape[0]
+    if not 0 <= lo < hi <= k:
+        raise PlaneError(f"columns {lo}..{hi} of {k}")
+    w = hi - lo
+    out = torch.zeros(n, resident_row_bytes(qtype, w), dtype=torch.uint8, device=res.device)
+    if qtype == "FP8_B128":
+        if lo % 128 or hi % 128:
+            raise PlaneError(f"FP8_B128: a slice of columns {lo}..{hi} does not align to 128-value blocks")
+        out[:, :w] = res[:, lo:hi]
+        out[:, w:w + w // 32] = res[:, k + lo // 32:k + hi // 32]
+        return out
+    if qtype == "NVFP4":
+        if lo % 16 or hi % 16:
+            raise PlaneError(f"NVFP4: a slice of columns {lo}..{hi} does not align to 16-value groups")
+        out[:, :w // 2] = res[:, lo // 2:hi // 2]
+        out[:, w // 2:w // 2 + w // 16] = res[:, k // 2 + lo // 16:k // 2 + hi // 16]
+        out[:, w // 2 + w // 16:w // 2 + w // 16 + 4] = res[:, k // 2 + k // 16:k // 2 + k // 16 + 4]
+        return out
+    raise PlaneError(f"{qtype} rows are not plane rows")
+
+
 def detect_scheme(config: dict) -> str:
     """'fp8_b128', 'nvfp4_modelopt', 'nvfp4_ct', 'mxfp4_ct', 'mxfp8' or 'plain' from config.json's quantization block."""
     q = config.get("quantization_config") or config.get("quantization") or {}

@@ -27,6 +27,7 @@ import torch
 import torch.distributed as dist
 
 from ..formats.quant import QTYPES
+from ..formats.resident import PLANE_TYPES
 from ..models.spec import ModelSpec
 from ..models.weights import TensorItem, Weights
 from ..ops import decode as K
@@ -53,6 +54,13 @@ def shard_items(items: Iterator[TensorItem], spec: ModelSpec, rank: int, world: 
     h_lo, h_hi = rank * spec.n_q // world, (rank + 1) * spec.n_q // world
 
     def k_slice(name, shape, qtype, raw, lo, hi):
+        if qtype in PLANE_TYPES:
+            # FP8 / NVFP4 items already carry resident rows (codes, then scales): cut both parts of every row
+            from ..formats.planes import PlaneError, resident_k_slice
+            try:
+                return name, (shape[0], hi - lo), qtype, resident_k_slice(raw.reshape(shape[0], -1), qtype, shape[1], lo, hi)
+            except PlaneError as exc:
+                raise ValueError(f"{name}: {exc}") from None
         qt = QTYPES[qtype]
         bv, bb = qt.block_values, qt.block_bytes
         if lo % bv or hi % bv:

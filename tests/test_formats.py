@@ -595,3 +595,38 @@ def test_packed_mxfp4_checkpoint_loads_as_exact_code_rows(tmp_path):
     assert ty == "Q8_F32" and k == 128
     assert torch.equal(decode_q8_f32(res, k).double(), want)
     f.close()
+
+
+@pytest.mark.parametrize("t,lo,hi", [("FP8_B128", 128, 384), ("FP8_B128", 0, 512), ("NVFP4", 48, 304), ("NVFP4", 256, 512)])
+def test_plane_rows_slice_by_columns(t, lo, hi):
+    from bloomery_b200.formats import planes as P
+    from bloomery_b200.formats.resident import quantize_resident, resident_row_bytes
+    torch.manual_seed(12)
+    res, vals = quantize_resident(torch.randn(20, 512) * 0.1, t)
+    cut = P.resident_k_slice(res, t, 512, lo, hi)
+    assert cut.shape == (20, resident_row_bytes(t, hi - lo))
+    assert torch.equal(P.resident_dequantize(cut, t, hi - lo), vals[:, lo:hi])
+    with pytest.raises(P.PlaneError):
+        P.resident_k_slice(res, t, 512, lo + 8, hi)
+
+
+def test_fp8_model_shards_by_heads_experts_and_widths():
+    """``shard_items`` on a DeepSeek-shaped FP8 stream: every rank's share decodes to the matching slice of the whole."""
+    from bloomery_b200.models.spec import tiny_deepseek
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.parallel.sharded import local_spec, shard_items
+    spec = tiny_deepseek()
+    items = list(synth_tensors(spec, "cpu", seed=4, mix="FP8_B128"))
+    full = Weights.from_items(spec, iter(items), "cpu")
+    for rank in range(2):
+        w = Weights.from_items(local_spec(spec, 2, attn=False), shard_items(iter(items), spec, rank, 2, attn=False), "cpu")
+        d_full, d = full.dequant("blk.0.ffn_down.weight"), w.dequant("blk.0.ffn_down.weight")
+        half = d_full.shape[1] // 2
+        assert torch.equal(d, d_full[:, rank * half:(rank + 1) * half])                      # dense width: columns
+        g_full, g = full.dequant("blk.1.ffn_gate_shexp.weight"), w.dequant("blk.1.ffn_gate_shexp.weight")
+        assert torch.equal(g, g_full[rank * g.shape[0]:(rank + 1) * g.shape[0]])             # shared expert: rows
+        s_full, s_ = full.dequant("blk.1.ffn_down_shexp.weight"), w.dequant("blk.1.ffn_down_shexp.weight")
+        assert torch.equal(s_, s_full[:, rank * s_.shape[1]:(rank + 1) * s_.shape[1]])
+        e_full, e = full.dequant("blk.2.ffn_up_exps.weight"), w.dequant("blk.2.ffn_up_exps.weight")
+        assert torch.equal(e, e_full[rank * 8:(rank + 1) * 8])                               # experts: by index
+        assert torch.equal(w.dequant("blk.1.attn_output.weight"), full.dequant("blk.1.attn_output.weight"))   # attention whole
