@@ -1,7 +1,11 @@
-"""Per-key limits on the requests a key makes.
+"""Per-key limits on the requests a key makes, and the routes a key reaches.
 
-A line of the key file is ``KEY [inflight=N] [rate=N/s | rate=N/m] [burst=B]``:
+A line of the key file is ``KEY [scope=S[,S]] [inflight=N] [rate=N/s | rate=N/m] [burst=B]``:
 
+* ``scope=``: ``inference`` (generation, token counts, the tokenizer, embeddings, stored responses), ``read``
+  (``GET /props``, ``/slots``, ``/metrics``) or ``admin`` (every route; the default), comma-separated; ``inference`` and
+  ``read`` both reach the model list and lookups; slot actions, ``/residency/reset`` and ``/shutdown`` need ``admin``.  A
+  route outside the scope answers 403 (``permission_error``);
 * ``inflight=N``: the most generating requests the key may have open at once;
 * ``rate=N/s`` or ``rate=N/m`` with ``burst=B`` (``N`` unless set): a bucket of ``B`` requests that refills ``N`` a second
   or a minute, each generating request taking one.
@@ -25,11 +29,47 @@ class LimitError(ValueError):
     """A key-file line whose limit fields do not parse; the message names the field, never the key."""
 
 
+SCOPES = ("inference", "read", "admin")
+_INFERENCE_PREFIXES = ("/completion", "/completions", "/v1/completions", "/v1/chat/completions", "/chat/completions", "/v1/messages",
+                       "/v1/responses", "/v1/embeddings", "/embeddings", "/embedding", "/tokenize", "/detokenize",
+                       "/apply-template", "/v1/systemone")
+_READ_PATHS = ("/props", "/slots", "/metrics")
+_LOOKUP_PREFIXES = ("/v1/models", "/models", "/api/tags", "/api/show")
+
+
+def route_scope(method: str, path: str) -> str:
+    """The scope a request needs: ``public`` (health), ``lookup`` (model list: any scope), ``inference``, ``read`` or
+    ``admin``."""
+    path = path.rstrip("/") or "/"
+    if path in ("/health", "/v1/health") or method == "OPTIONS":
+        return "public"
+    if any(path == p_ or path.startswith(p_ + "/") for p_ in _LOOKUP_PREFIXES):
+        return "lookup"
+    if method == "GET" and path in _READ_PATHS:
+        return "read"
+    if any(path == p_ or path.startswith(p_ + "/") for p_ in _INFERENCE_PREFIXES):
+        return "inference"
+    return "admin"                             # slot actions, /residency/reset, /shutdown, anything unnamed
+
+
 class Limits:
-    def __init__(self, inflight: Optional[int] = None, rate: Optional[Tuple[int, bool]] = None, burst: Optional[int] = None):
+    def __init__(self, inflight: Optional[int] = None, rate: Optional[Tuple[int, bool]] = None, burst: Optional[int] = None,
+                 scopes: Optional[frozenset] = None):
         self.inflight = inflight
         self.rate = rate                      # (count, per_minute)
         self.burst = burst if burst is not None else (rate[0] if rate else None)
+        self.scopes = scopes if scopes is not None else frozenset(("admin",))
+
+    def reaches(self, method: str, path: str) -> bool:
+        need = route_scope(method, path)
+        if need == "public" or "admin" in self.scopes:
+            return True
+        if need == "lookup":
+            return bool(self.scopes & {"inference", "read"})
+        return need in self.scopes
+
+    def same(self, other: "Limits") -> bool:
+        return (self.inflight, self.rate, self.burst, self.scopes) == (other.inflight, other.rate, other.burst, other.scopes)
 
     @property
     def interval(self) -> float:
@@ -44,9 +84,18 @@ class Limits:
 
     @classmethod
     def parse(cls, fields) -> "Limits":
-        inflight = rate = burst = None
+        inflight = rate = burst = scopes = None
+        seen = set()
         for name, value in fields:
-            if name == "inflight":
+            if name in seen:
+                raise LimitError(f"{name}: named twice")
+            seen.add(name)
+            if name == "scope":
+                got = [v for v in value.split(",")]
+                if not value or any(v not in SCOPES for v in got):
+                    raise LimitError(f"scope={value}: takes inference, read or admin, comma-separated")
+                scopes = frozenset(got)
+            elif name == "inflight":
                 inflight = cls._count(name, value, value)
             elif name == "burst":
                 burst = cls._count(name, value, value)
@@ -58,10 +107,10 @@ class Limits:
                     raise LimitError(f"rate={value}: the unit is s or m")
                 rate = (cls._count(name, value, n), unit == "m")
             else:
-                raise LimitError(f"{name}: not a limit (inflight, rate, burst)")
+                raise LimitError(f"{name}: not a field of a key line (scope, inflight, rate, burst)")
         if burst is not None and rate is None:
             raise LimitError("burst: needs a rate beside it")
-        return cls(inflight, rate, burst)
+        return cls(inflight, rate, burst, scopes)
 
 
 def parse_key_line(line: str) -> Tuple[str, Limits]:

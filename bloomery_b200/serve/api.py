@@ -74,6 +74,7 @@ class State:
         self.alias = args.get("alias")
         self.api_keys, key_limits = self._load_keys(args)
         from .admit import Admission
+        self.key_limits = key_limits
         self.admission = Admission(key_limits)
         self.t_start = time.time()
         self.responses: "collections.OrderedDict[str, dict]" = collections.OrderedDict()
@@ -100,6 +101,8 @@ class State:
                     if not ln or ln.startswith("#"):
                         continue
                     key, lim = parse_key_line(ln)
+                    if key in limits and not limits[key].same(lim):
+                        raise ValueError(f"{args['api_key_file']}: a key is given twice with different fields")
                     keys.append(key)
                     limits[key] = lim
         return keys, limits
@@ -286,6 +289,10 @@ class Handler(BaseHTTPRequestHandler):
         try:
             if not self._authorised():
                 raise ApiError(401, "invalid API key", "authentication_error")
+            lim = st.key_limits.get(getattr(self, "_key", None)) if getattr(st, "key_limits", None) else None
+            if lim is not None and not lim.reaches(method, path):
+                self.close_connection = True
+                raise ApiError(403, "this key's scope does not reach this route", "permission_error")
             if path in ("/health", "/v1/health"):
                 if st.phase == "ready":
                     return self._send(200, {"status": "ok", "slots_idle": st.engine.n_slots - st.board.busy_count(),

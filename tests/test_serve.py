@@ -198,6 +198,29 @@ def test_key_file_limits_answer_429(tmp_path):
     s.stop()
 
 
+def test_key_scopes_answer_403_outside_their_routes(tmp_path):
+    kf = tmp_path / "keys.txt"
+    kf.write_text("app scope=inference\nwatch scope=read\nroot\n")
+    s = Server(flags.parse(["--port", "0", "--mock", "--api-key-file", str(kf), "--slot-save-path", str(tmp_path)]))
+    s.start()
+    s.ready(MockEngine(), ChatTemplate(), 0)
+    app, watch, root = ({"Authorization": f"Bearer {k}"} for k in ("app", "watch", "root"))
+    assert call(s, "/completion", {"prompt": "ab", "n_predict": 2}, headers=app)[0] == 200
+    code, r = call(s, "/props", headers=app)
+    assert code == 403 and r["error"]["type"] == "permission_error"
+    assert call(s, "/props", headers=watch)[0] == 200 and call(s, "/metrics", headers=watch)[0] == 200
+    assert call(s, "/completion", {"prompt": "ab"}, headers=watch)[0] == 403
+    assert call(s, "/v1/models", headers=app)[0] == 200 and call(s, "/v1/models", headers=watch)[0] == 200
+    assert call(s, "/slots/0?action=erase", {}, headers=app)[0] == 403
+    assert call(s, "/slots/0?action=erase", {}, headers=root)[0] == 200
+    assert call(s, "/health")[0] == 200
+    s.state.stop_event.set()
+    s.stop()
+    kf.write_text("app scope=inference\napp scope=read\n")
+    with pytest.raises(ValueError, match="given twice"):
+        Server(flags.parse(["--port", "0", "--mock", "--api-key-file", str(kf)]))
+
+
 def test_api_key_and_shutdown():
     opts = flags.parse(["--port", "0", "--mock", "--api-key", "sekret"])
     s = Server(opts)

@@ -292,6 +292,25 @@ def test_per_key_limits():
     for _ in range(50):
         adm.admit("c")                                                             # no limits, and keys count apart
         adm.admit("unknown")
+    # scopes: which routes a key reaches
+    from bloomery_b200.serve.admit import route_scope
+    inf, rd, adm_ = parse_key_line("k scope=inference")[1], parse_key_line("k scope=read")[1], parse_key_line("k")[1]
+    both = parse_key_line("k scope=inference,read inflight=1")[1]
+    assert adm_.scopes == {"admin"} and both.scopes == {"inference", "read"} and both.inflight == 1
+    table = [("POST", "/v1/chat/completions", "inference"), ("POST", "/tokenize", "inference"), ("GET", "/v1/responses/resp_1", "inference"),
+             ("POST", "/v1/messages/count_tokens", "inference"), ("POST", "/v1/embeddings", "inference"), ("GET", "/props", "read"),
+             ("GET", "/slots", "read"), ("GET", "/metrics", "read"), ("GET", "/v1/models", "lookup"), ("GET", "/v1/models/m", "lookup"),
+             ("POST", "/api/show", "lookup"), ("POST", "/slots/0", "admin"), ("POST", "/residency/reset", "admin"),
+             ("POST", "/shutdown", "admin"), ("GET", "/health", "public"), ("POST", "/props", "admin")]
+    for method, path, want in table:
+        assert route_scope(method, path) == want, (method, path)
+        assert adm_.reaches(method, path)
+        assert inf.reaches(method, path) == (want in ("inference", "lookup", "public"))
+        assert rd.reaches(method, path) == (want in ("read", "lookup", "public"))
+        assert both.reaches(method, path) == (want != "admin")
+    for bad in ("k scope=", "k scope=root", "k scope=read scope=admin", "k inflight=1 inflight=2"):
+        with pytest.raises(LimitError):
+            parse_key_line(bad)
 
 
 def test_reasoning_split():
