@@ -561,7 +561,8 @@ class Handler(BaseHTTPRequestHandler):
                        n_probs=n_probs, ignore_eos=bool(body.get("ignore_eos", False)),
                        id_slot=(int(body["id_slot"]) if body.get("id_slot", -1) not in (None, -1) else None),
                        constraint=constraint_from(body), logit_bias=lb,
-                       t_max_predict_ms=float(body.get("t_max_predict_ms") or 0))
+                       t_max_predict_ms=float(body.get("t_max_predict_ms") or 0),
+                       endpoint=(urlparse(self.path).path.rstrip("/") or "/"))
 
     def _prompt_ids(self, prompt) -> List[int]:
         tk = self.state.engine.tokenizer

@@ -14,6 +14,7 @@ import dataclasses
 import itertools
 import math
 import queue
+import sys
 import threading
 import time
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
@@ -43,6 +44,7 @@ class Request:
     constraint: Any = None                  # object with allowed(text_so_far, piece) -> bool and done(text) -> bool
     logit_bias: Dict[int, float] = dataclasses.field(default_factory=dict)
     t_max_predict_ms: float = 0.0
+    endpoint: str = ""                      # the route that made the request (the per-request log line names it)
     id: int = dataclasses.field(default_factory=lambda: next(_ids))
     events: "queue.Queue" = dataclasses.field(default_factory=queue.Queue)
     cancelled: threading.Event = dataclasses.field(default_factory=threading.Event)
@@ -109,6 +111,7 @@ class Worker(threading.Thread):
         self.draft = None                       # runtime.speculative.NgramDraft (or another source with .propose)
         self.width = None                       # runtime.speculative.WidthChooser
         self.actions: "queue.Queue" = queue.Queue()     # slot actions run on the engine thread
+        self.log_requests = True
 
     # ---------------------------------------------------------------- admission
     def _admit(self) -> None:
@@ -196,6 +199,7 @@ class Worker(threading.Thread):
                                    "tokens_evaluated": n_prompt, "tokens_cached": a.n_cached, "timings": timings,
                                    "text": a.text, "tokens": list(a.generated), "probs": a.probs,
                                    "truncated": False, "id_slot": a.slot.id}))
+        self._log_request(a, stop_type, n_prompt, prompt_ms, pred_ms)
         m = self.metrics
         m.add("requests_total"); m.add("prompt_tokens_total", n_prompt - a.n_cached); m.add("prompt_seconds_total", prompt_ms / 1e3)
         m.add("tokens_predicted_total", len(a.generated)); m.add("tokens_predicted_seconds_total", pred_ms / 1e3)
@@ -205,6 +209,21 @@ class Worker(threading.Thread):
             self.cache.seconds += time.time() - t0
         del self.active[a.slot.id]
         self.board.release(a.slot)
+
+    REASONS = {"eos": "eos", "word": "stop", "limit": "length", "cancelled": "cancel"}
+
+    def _log_request(self, a: Active, stop_type: str, n_prompt: int, prompt_ms: float, pred_ms: float) -> None:
+        """One stderr line a request when its generation ends (``docs/serving.md:466-470`` of the reference): what was
+        evaluated and reused, both rates, why it stopped, how full the slot's context is."""
+        if not self.log_requests:
+            return
+        new = n_prompt - a.n_cached
+        g = len(a.generated)
+        line = (f"bloomery-serve: request {a.req.id} {a.req.endpoint or '-'}: prompt {n_prompt} ids ({a.n_cached} reused) in "
+                f"{prompt_ms / 1e3:.3f} s, {new / max(prompt_ms / 1e3, 1e-9):.1f} ids/s; generated {g} ids in {pred_ms / 1e3:.3f} s, "
+                f"{g / max(pred_ms / 1e3, 1e-9):.1f} ids/s; stop {self.REASONS.get(stop_type, 'error')}; "
+                f"ctx {len(a.slot.ids)}/{self.engine.slot_ctx}")
+        print(line, file=sys.stderr, flush=True)
 
     def _flush_text(self, a: Active, final: bool = False) -> None:
         if not a.req.stream:

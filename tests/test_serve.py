@@ -373,3 +373,13 @@ def test_worker_hands_sampling_to_an_engine_that_samples_itself():
     eng2 = SelfSampling(n_slots=1, slot_ctx=512)
     run(eng2, dict(body, n_probs=2))
     assert eng2.seen == []                                                # top-probabilities need the host's logits
+
+
+def test_one_stderr_line_a_request(server, capfd):
+    capfd.readouterr()
+    code, r = call(server, "/completion", {"prompt": "hello there", "n_predict": 3, "temperature": 0})
+    assert code == 200
+    err = capfd.readouterr().err
+    line = next(ln for ln in err.splitlines() if ln.startswith("bloomery-serve: request "))
+    assert " /completion: prompt " in line and " ids/s; generated 3 ids in " in line and line.endswith("/512")
+    assert "stop length; ctx " in line
