@@ -168,7 +168,9 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
         raise Refusal(Code.USAGE, "-ctk q8_0: the several-GPU engines keep an f16 cache")
     records.write("plan", model=spec.name, devices=[f"CUDA{d}" for d in pl.devices], weights_bytes=weights_bytes,
                   kv_bytes=plan["kv_bytes"], ctx=plan["ctx_total"], slots=plan["n_slots"], place=pl.word())
-    records.write("need", weights_bytes=weights_bytes, kv_bytes_per_token=spec.kv_bytes_per_token(), host_bytes=0, fits=True)
+    need = need_record(opts, spec, weights_bytes, plan)
+    records.write("need", **need)
+    ask_need_hook(need)
     records.write("ctx", asked=int(opts.get("ctx") or 0), served=plan["slot_ctx"], trained=spec.ctx_train)
     records.write("parallel", slots=plan["n_slots"], slot_ctx=plan["slot_ctx"])
     if opts["plan"] or opts["dry_run"]:
@@ -285,6 +287,51 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
     return eng, tsrc, bos, eos
 
 
+def need_record(opts: Dict[str, Any], spec, weights_bytes: int, plan: Dict[str, Any]) -> Dict[str, Any]:
+    """What the placed load asks of the machine (``docs/serving.md`` "Starting under a broker" of the reference): host
+    bytes it will pin (cold experts and the upload ring), the prompt cache beside them, the bytes per card, the worker
+    threads and the CPUs the process may run on."""
+    from ..utils import osshim
+    pl = plan["placement"]
+    ebytes = int(opts.get("_expert_bytes") or 0)
+    pinned = 2 * (256 << 20)                                         # the two-slot upload ring
+    if pl.host_experts != "none" and spec.is_moe:
+        resident = int(pl.host_experts.split(":")[1]) if pl.host_experts.startswith("fit:") else 0
+        pinned += ebytes - ebytes // max(1, spec.n_expert) * resident            # the experts that stay on the host
+    cache_mib = int(opts.get("cache_ram", -1))
+    cache_ram = min(8 << 30, _host_free_bytes() // 2) if cache_mib < 0 else cache_mib << 20
+    n_dev = max(1, len(pl.devices))
+    share = (weights_bytes - (pinned - (512 << 20))) // (n_dev if pl.mode == "tp" else 1)
+    allowed = osshim.mask_cpus()
+    threads = int(levers.get("BLOOMERY_THREADS")) or len(allowed)
+    return {"weights_bytes": weights_bytes, "kv_bytes_per_token": spec.kv_bytes_per_token(), "host_bytes": pinned,
+            "fits": True, "bytes": pinned, "pinned": pinned, "cache_ram": cache_ram,
+            "cards": [f"CUDA{d}:{share + plan['kv_bytes'] // n_dev}" for d in pl.devices], "threads": threads, "allowed": allowed}
+
+
+def ask_need_hook(need: Dict[str, Any]) -> None:
+    """``BLOOMERY_NEED_HOOK``: a broker's say before a card is opened.  The program gets the need line on its standard
+    input; exit 0 goes on, 75 ends this process with 75 (the hook's last output line named) so the start can be queued
+    and asked again, anything else is a named error."""
+    hook = str(levers.get("BLOOMERY_NEED_HOOK") or "")
+    if not hook:
+        return
+    if not os.path.isabs(hook):
+        raise Refusal(Code.LEVER, f"BLOOMERY_NEED_HOOK={hook!r}: takes an absolute path")
+    import subprocess
+    line = "need " + " ".join(f"{k}={json.dumps(v, separators=(',', ':'))}" for k, v in need.items()) + "\n"
+    try:
+        done = subprocess.run([hook], input=line, capture_output=True, text=True, timeout=300)
+    except (OSError, subprocess.TimeoutExpired) as exc:
+        raise Refusal(Code.REFUSED, f"the need hook {hook} did not run: {exc}") from None
+    last = ((done.stdout or "") + (done.stderr or "")).strip().splitlines()[-1:] or [""]
+    if done.returncode == 0:
+        return
+    if done.returncode == int(Code.RETRY):
+        raise Refusal(Code.RETRY, f"the need hook asks to start later: {last[0]}")
+    raise Refusal(Code.REFUSED, f"the need hook {hook} exited {done.returncode}: {last[0]}")
+
+
 class _PlanOnly(Exception):
     pass
 
@@ -331,8 +378,14 @@ def main(argv: Optional[List[str]] = None) -> int:
         from .api import Server
         server = Server(opts)
         server.start()
-        signal.signal(signal.SIGINT, lambda *_: (setattr(server.state, "stop_cause", "signal"), server.state.stop_event.set()))
-        signal.signal(signal.SIGTERM, lambda *_: (setattr(server.state, "stop_cause", "signal"), server.state.stop_event.set()))
+        def on_signal(*_):
+            if server.state.stop_event.is_set():            # a second signal ends the process at once
+                print("bloomery-serve: second signal, leaving now", file=sys.stderr, flush=True)
+                os._exit(1)
+            server.state.stop_cause = "signal"
+            server.state.stop_event.set()
+        signal.signal(signal.SIGINT, on_signal)
+        signal.signal(signal.SIGTERM, on_signal)
         from .engine import GpuEngine, MockEngine
         from .chat import ChatTemplate
         template_src = None

@@ -112,6 +112,7 @@ class Worker(threading.Thread):
         self.width = None                       # runtime.speculative.WidthChooser
         self.actions: "queue.Queue" = queue.Queue()     # slot actions run on the engine thread
         self.log_requests = True
+        self.generating_every = 30.0            # seconds between the short lines of a request that is still generating
 
     # ---------------------------------------------------------------- admission
     def _admit(self) -> None:
@@ -224,6 +225,18 @@ class Worker(threading.Thread):
                 f"{g / max(pred_ms / 1e3, 1e-9):.1f} ids/s; stop {self.REASONS.get(stop_type, 'error')}; "
                 f"ctx {len(a.slot.ids)}/{self.engine.slot_ctx}")
         print(line, file=sys.stderr, flush=True)
+
+    def _log_generating(self) -> None:
+        """A request that has generated for more than ``generating_every`` seconds says so, and again every such span."""
+        if not self.log_requests or not self.active:
+            return
+        now = time.time()
+        for a in self.active.values():
+            since = getattr(a, "t_logged", None) or a.t_first
+            if since and now - since >= self.generating_every:
+                a.t_logged = now
+                print(f"bloomery-serve: request {a.req.id} {a.req.endpoint or '-'}: generating, {len(a.generated)} ids in "
+                      f"{now - a.t_first:.0f} s", file=sys.stderr, flush=True)
 
     def _flush_text(self, a: Active, final: bool = False) -> None:
         if not a.req.stream:
@@ -456,6 +469,7 @@ class Worker(threading.Thread):
                     if a.pending_token is None and (live is None or a.slot.id in live):
                         self._feed_prompt(a)
                 self._decode_round(live)
+                self._log_generating()
                 if not self.active:
                     with self.board.wake:
                         if not self.board.queue and self.actions.empty() and not self.stop_flag.is_set():

@@ -9,7 +9,8 @@ from typing import Dict, Iterable, Iterator, List, Tuple
 
 KINDS: Dict[str, List[str]] = {
     "plan": ["model", "devices", "weights_bytes", "kv_bytes", "ctx", "slots", "place"],
-    "need": ["weights_bytes", "kv_bytes_per_token", "host_bytes", "fits"],
+    "need": ["weights_bytes", "kv_bytes_per_token", "host_bytes", "fits", "bytes", "pinned", "cache_ram", "cards", "threads",
+             "allowed"],
     "ctx": ["asked", "served", "trained"],
     "parallel": ["slots", "slot_ctx"],
     "setup": ["phase", "seconds", "winner", "raced", "resident_per_layer", "host", "page_cache"],

@@ -383,3 +383,16 @@ def test_one_stderr_line_a_request(server, capfd):
     line = next(ln for ln in err.splitlines() if ln.startswith("bloomery-serve: request "))
     assert " /completion: prompt " in line and " ids/s; generated 3 ids in " in line and line.endswith("/512")
     assert "stop length; ctx " in line
+
+
+def test_long_generation_says_it_is_still_generating(capfd):
+    s = Server(flags.parse(["--port", "0", "--mock"]))
+    s.start()
+    s.ready(MockEngine(n_slots=1, slot_ctx=512, step_delay=0.01), ChatTemplate(), 0)
+    s.state.worker.generating_every = 0.05
+    capfd.readouterr()
+    assert call(s, "/completion", {"prompt": "abcdefghijklmnopqrstuvwxyz", "n_predict": 24, "temperature": 0})[0] == 200
+    err = capfd.readouterr().err
+    assert sum(1 for ln in err.splitlines() if ": generating, " in ln) >= 2
+    s.state.stop_event.set()
+    s.stop()

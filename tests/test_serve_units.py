@@ -509,3 +509,41 @@ def test_reference_sets_carry_the_model_identity(tmp_path):
         R.check_logits(ldoc, a, nudged, max_mean_kld=1.0, flip_margin=0.0)
     with pytest.raises(R.RefsetError, match="KL divergence"):
         R.check_logits(ldoc, a, lambda ids: fn(ids) * 0.0, max_mean_kld=1e-7, flip_margin=100.0)
+
+
+def test_need_record_and_broker_hook(tmp_path, monkeypatch):
+    """The placed load states what it asks of the machine, and a hook may let it go on (0), queue it (75) or stop it."""
+    import stat
+    from bloomery_b200.models.spec import qwen3_30b_a3b
+    from bloomery_b200.serve import cli
+    from bloomery_b200.utils import levers as LV
+    spec = qwen3_30b_a3b()
+    opts = flags.parse(["-m", "x", "-fit", "on", "-np", "1", "-c", "8192", "-cram", "512"], {})
+    opts["_expert_bytes"] = 16_000_000_000
+    plan = cli.plan_for(opts, spec, 17_500_000_000, 1, [12 << 30])
+    need = cli.need_record(opts, spec, 17_500_000_000, plan)
+    resident = int(plan["placement"].host_experts.split(":")[1])
+    assert need["pinned"] == (512 << 20) + 16_000_000_000 - 16_000_000_000 // 128 * resident
+    assert need["cache_ram"] == 512 << 20 and need["cards"][0].startswith("CUDA0:") and need["threads"] >= 1 and need["allowed"]
+    records.write("need", _out=io.StringIO(), **need)                 # every field is one the record kind knows
+
+    def hook(body):
+        p = tmp_path / "hook.sh"
+        p.write_text("#!/bin/sh\n" + body + "\n")
+        p.chmod(p.stat().st_mode | stat.S_IXUSR)
+        return str(p)
+    log = tmp_path / "need.log"
+    for body, want in ((f"cat >> {log}", None), ("echo busy until noon; exit 75", Code.RETRY), ("echo no; exit 3", Code.REFUSED)):
+        monkeypatch.setitem(LV._values, "BLOOMERY_NEED_HOOK", hook(body))
+        if want is None:
+            cli.ask_need_hook(need)
+            assert log.read_text().startswith("need weights_bytes=17500000000 ")
+        else:
+            with pytest.raises(Refusal) as e:
+                cli.ask_need_hook(need)
+            assert e.value.code == want and ("busy until noon" in str(e.value) or "exited 3: no" in str(e.value))
+    monkeypatch.setitem(LV._values, "BLOOMERY_NEED_HOOK", "relative/hook")
+    with pytest.raises(Refusal):
+        cli.ask_need_hook(need)
+    monkeypatch.setitem(LV._values, "BLOOMERY_NEED_HOOK", "")
+    cli.ask_need_hook(need)
