@@ -461,6 +461,13 @@ class Handler(BaseHTTPRequestHandler):
         g("draft_accepted_total", "Speculative tokens accepted", m.get("draft_accepted_total"))
         for w, n in sorted(st.worker.rounds_by_width.items()):
             lines.append(f'llamacpp:rounds_total{{width="{w}"}} {n}')
+        for w, sec in sorted(st.worker.round_seconds_by_width.items()):
+            lines.append(f'llamacpp:round_seconds_by_width_total{{width="{w}"}} {sec:.6f}')
+        source = {"NgramDraft": "ngram", "MtpDraft": "mtp"}.get(type(st.worker.draft).__name__, "none")
+        for depth, n in sorted(st.worker.draft_by_depth.items()):
+            lines.append(f'llamacpp:spec_decode_num_draft_tokens_by_depth_total{{source="{source}",depth="{depth}"}} {n}')
+            lines.append(f'llamacpp:spec_decode_num_accepted_tokens_by_depth_total{{source="{source}",depth="{depth}"}} '
+                         f'{st.worker.accepted_by_depth.get(depth, 0)}')
         dec = getattr(st.engine, "dec", None)
         if dec is not None and hasattr(dec, "waits"):
             for name, val in sorted(dec.waits.metrics().items()):

@@ -106,6 +106,9 @@ class Worker(threading.Thread):
         self.stop_flag = threading.Event()
         self.metrics = Metrics()
         self.rounds_by_width: Dict[int, int] = {}
+        self.round_seconds_by_width: Dict[int, float] = {}
+        self.draft_by_depth: Dict[int, int] = {}        # drafted ids by their place in the draft
+        self.accepted_by_depth: Dict[int, int] = {}
         self.on_fatal = on_fatal
         self.failed: Optional[BaseException] = None
         self.draft = None                       # runtime.speculative.NgramDraft (or another source with .propose)
@@ -384,6 +387,7 @@ class Worker(threading.Thread):
         self.metrics.add("n_decode_total")
         self.metrics.add("n_busy_slots_per_decode", len(spans))
         self.rounds_by_width[len(rows)] = self.rounds_by_width.get(len(rows), 0) + 1
+        self.round_seconds_by_width[len(rows)] = self.round_seconds_by_width.get(len(rows), 0.0) + dt
         if self.width is not None and len(spans) == 1:
             self.width.observe_pass(len(rows), dt)
         for a, r0, drafted in spans:
@@ -396,6 +400,10 @@ class Worker(threading.Thread):
                 a.draft_accepted += kept
                 self.metrics.add("draft_tokens_total", len(drafted))
                 self.metrics.add("draft_accepted_total", kept)
+                for depth in range(len(drafted)):
+                    self.draft_by_depth[depth] = self.draft_by_depth.get(depth, 0) + 1
+                    if depth < kept:
+                        self.accepted_by_depth[depth] = self.accepted_by_depth.get(depth, 0) + 1
                 self.width.observe_accept(len(drafted), kept)
                 if kept < len(drafted):
                     self.engine.cut(a.slot.id, len(a.slot.ids) + 1 + kept)     # rows of rejected drafts leave the KV

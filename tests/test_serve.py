@@ -258,6 +258,14 @@ def test_speculative_drafts_change_passes_not_tokens():
             s.state.worker.enable_drafting(NgramDraft(), WidthChooser(max_width=7))
         code, r = call(s, "/completion", {"prompt": "abcabcabcabc xyz abcabcabcabc xyz", "temperature": 0, "n_predict": 40})
         outs.append((r["content"], r["timings"]["draft_n"], r["timings"]["draft_n_accepted"], s.state.worker.metrics.get("n_decode_total")))
+        if drafting:
+            text = call(s, "/metrics")[1]
+            by_depth = [ln for ln in text.splitlines() if ln.startswith("llamacpp:spec_decode_num_draft_tokens_by_depth_total")]
+            assert by_depth and 'source="ngram",depth="0"' in by_depth[0]
+            assert sum(int(ln.rsplit(" ", 1)[1]) for ln in by_depth) == r["timings"]["draft_n"]          # the depths sum to the total
+            acc = [ln for ln in text.splitlines() if ln.startswith("llamacpp:spec_decode_num_accepted_tokens_by_depth_total")]
+            assert sum(int(ln.rsplit(" ", 1)[1]) for ln in acc) == r["timings"]["draft_n_accepted"]
+            assert "llamacpp:round_seconds_by_width_total{width=" in text
         s.state.stop_event.set()
         s.stop()
     assert outs[0][0] == outs[1][0]                      # same text
