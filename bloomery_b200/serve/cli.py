@@ -34,13 +34,21 @@ def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, fre
     margin = int(levers.get("BLOOMERY_CARD_MARGIN"))
     budget = int(levers.get("BLOOMERY_CARD_BUDGET"))       # HBM bytes routed experts may take per GPU (0 = what fits)
     host_room = int(levers.get("BLOOMERY_HOST_ROOM"))      # pinned host bytes cold experts may take (0 = as needed)
-    par = opts.get("parallel", "auto")
-    n_slots = 4 if par == "auto" else int(par)
+    par = str(opts.get("parallel", "1"))
+    auto = par == "auto"
+    asked = int(opts.get("ctx") or 0)
+    slot_ctx = int(opts.get("slot_ctx") or 0)
+    if auto and asked:
+        raise Refusal(Code.USAGE, "--parallel auto beside --ctx-size: auto counts slots of one request's context; name it with --slot-ctx")
+    if slot_ctx and asked:
+        raise Refusal(Code.USAGE, "--slot-ctx beside --ctx-size: one names a slot's share, the other the total")
+    try:
+        n_slots = 1 if auto else int(par)              # auto: the placement is chosen at one slot, the count follows
+    except ValueError:
+        raise Refusal(Code.USAGE, f"-np {par}: takes a count or auto") from None
     if n_slots < 1:
         raise Refusal(Code.USAGE, f"-np {par}: at least one slot")
     per_tok = spec.kv_bytes_per_token() // max(1, len(pl.devices) if pl.mode == "tp" else 1)
-    asked = int(opts.get("ctx") or 0)
-    slot_ctx = int(opts.get("slot_ctx") or 0)
     if pl.devices:
         if pl.fit_targets_mib:
             # -fitt MiB[,MiB...]: what stays free on each device of the list (one value serves them all); the tightest
@@ -86,20 +94,35 @@ def plan_for(opts: Dict[str, Any], spec, weights_bytes: int, n_visible: int, fre
         fit_tokens = max(0, room) // max(1, per_tok)
     else:
         fit_tokens = _host_free_bytes() // 2 // max(1, per_tok)
+    source = "flag"
+    if auto:
+        # the most slots, up to 8, that hold one request's context: --slot-ctx when set, else the context one slot
+        # takes with no flags -- and where that one slot already has to fit under the model's limit, one slot
+        one = slot_ctx or min(spec.ctx_train, fit_tokens // 1024 * 1024)
+        n_slots = 1 if (not slot_ctx and one < spec.ctx_train) else max(1, min(8, fit_tokens // max(1, one)))
+        source = "auto"
     if asked:
         total = asked
         if total > fit_tokens:
             best = fit_tokens // 1024 * 1024
             raise Refusal(Code.NO_FIT, f"-c {asked} does not fit; the largest context that fits is {best}")
+    elif slot_ctx:
+        total = slot_ctx * n_slots
+        if total > fit_tokens:
+            best = fit_tokens // n_slots // 1024 * 1024
+            raise Refusal(Code.NO_FIT, f"--slot-ctx {slot_ctx} x {n_slots} slots does not fit; the largest slot context that fits is {best}")
     else:
         total = min(spec.ctx_train * n_slots, fit_tokens // 1024 * 1024)
         if total < 4096:
             raise Refusal(Code.NO_FIT, "not even a context of 4,096 fits beside the weights")
+    rule = "set" if (asked or slot_ctx) else None
     if not slot_ctx:
-        slot_ctx = min(spec.ctx_train, total // n_slots if par != "auto" else max(4096, min(spec.ctx_train, total // n_slots)))
+        slot_ctx = min(spec.ctx_train, total // n_slots)
     slot_ctx = slot_ctx // 64 * 64
+    if rule is None:
+        rule = "target" if slot_ctx >= spec.ctx_train // 64 * 64 else "fitted"
     return {"placement": pl, "n_slots": n_slots, "slot_ctx": slot_ctx, "ctx_total": slot_ctx * n_slots,
-            "kv_bytes": slot_ctx * n_slots * per_tok, "weights_bytes": weights_bytes}
+            "kv_bytes": slot_ctx * n_slots * per_tok, "weights_bytes": weights_bytes, "ctx_rule": rule, "slots_from": source}
 
 
 def _inventory(path: str):
@@ -171,8 +194,8 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
     need = need_record(opts, spec, weights_bytes, plan)
     records.write("need", **need)
     ask_need_hook(need)
-    records.write("ctx", asked=int(opts.get("ctx") or 0), served=plan["slot_ctx"], trained=spec.ctx_train)
-    records.write("parallel", slots=plan["n_slots"], slot_ctx=plan["slot_ctx"])
+    records.write("ctx", asked=int(opts.get("ctx") or 0), served=plan["slot_ctx"], trained=spec.ctx_train, rule=plan["ctx_rule"])
+    records.write("parallel", slots=plan["n_slots"], slot_ctx=plan["slot_ctx"], source=plan["slots_from"])
     if opts["plan"] or opts["dry_run"]:
         out = {"place": pl.word(), "devices": pl.devices, "slots": plan["n_slots"], "slot_ctx": plan["slot_ctx"],
                "weights_bytes": weights_bytes, "kv_bytes": plan["kv_bytes"]}
@@ -397,7 +420,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         cache_mib = int(opts.get("cache_ram", -1))
         cache_bytes = min(8 << 30, _host_free_bytes() // 2) if cache_mib < 0 else cache_mib << 20
         if opts["mock"]:
-            eng = MockEngine(n_slots=4 if opts["parallel"] == "auto" else int(opts["parallel"]),
+            eng = MockEngine(n_slots=4 if opts["parallel"] == "auto" else int(opts["parallel"]),      # nothing to count from: four
                              slot_ctx=int(opts.get("ctx") or 4096), fail_at=int(opts.get("mock_fail_at", -1)))
             opts["_place_word"] = "mock"
             server.ready(in_turns(eng), ChatTemplate(template_src), cache_bytes, int(opts["queue_depth"]))

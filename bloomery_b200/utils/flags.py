@@ -35,7 +35,7 @@ FLAGS: List[Flag] = [
     Flag(("--host",), "host", default="127.0.0.1", env="LLAMA_ARG_HOST"),
     Flag(("--port",), "port", "int", 8080, env="LLAMA_ARG_PORT", help="0 = any free port"),
     Flag(("-c", "--ctx-size"), "ctx", "int", 0, env="LLAMA_ARG_CTX_SIZE", help="0 = the model's trained limit or what fits"),
-    Flag(("-np", "--parallel"), "parallel", "str", "auto", env="LLAMA_ARG_N_PARALLEL", help="slots: N or auto"),
+    Flag(("-np", "--parallel"), "parallel", "str", "1", env="LLAMA_ARG_N_PARALLEL", help="slots: N, or auto = as many (up to 8) as hold one request's context"),
     Flag(("--slot-ctx",), "slot_ctx", "int", 0),
     Flag(("--queue-depth",), "queue_depth", "int", 64),
     Flag(("--engine-slots",), "engine_slots", "int", 0, help="sequences the engine holds; fewer than -np = the slots take it in turns"),

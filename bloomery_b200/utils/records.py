@@ -11,8 +11,8 @@ KINDS: Dict[str, List[str]] = {
     "plan": ["model", "devices", "weights_bytes", "kv_bytes", "ctx", "slots", "place"],
     "need": ["weights_bytes", "kv_bytes_per_token", "host_bytes", "fits", "bytes", "pinned", "cache_ram", "cards", "threads",
              "allowed"],
-    "ctx": ["asked", "served", "trained"],
-    "parallel": ["slots", "slot_ctx"],
+    "ctx": ["asked", "served", "trained", "rule"],
+    "parallel": ["slots", "slot_ctx", "source"],
     "setup": ["phase", "seconds", "winner", "raced", "resident_per_layer", "host", "page_cache"],
     "watchdog": ["model", "site", "seconds"],
     "step_stats": ["steps", "card_wait_s", "kv_free_pages", "kv_spills", "free_bytes"],

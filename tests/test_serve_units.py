@@ -547,3 +547,33 @@ def test_need_record_and_broker_hook(tmp_path, monkeypatch):
         cli.ask_need_hook(need)
     monkeypatch.setitem(LV._values, "BLOOMERY_NEED_HOOK", "")
     cli.ask_need_hook(need)
+
+
+def test_slot_count_and_context_rules():
+    """One slot unless asked; ``auto`` counts from memory up to 8; a set context is never cut; the flags that contradict
+    each other are refused by name."""
+    from bloomery_b200.models.spec import qwen3_30b_a3b
+    from bloomery_b200.serve.cli import plan_for
+    spec = qwen3_30b_a3b()
+
+    def plan(argv, free=170 << 30):
+        return plan_for(flags.parse(["-m", "x", *argv], {}), spec, 17_500_000_000, 1, [free])
+    p = plan([])
+    assert (p["n_slots"], p["slot_ctx"], p["ctx_rule"], p["slots_from"]) == (1, spec.ctx_train // 64 * 64, "target", "flag")
+    p = plan(["-np", "auto"])
+    assert (p["n_slots"], p["ctx_rule"], p["slots_from"]) == (8, "target", "auto")
+    p = plan(["-np", "auto", "--slot-ctx", "32768"])
+    assert (p["n_slots"], p["slot_ctx"], p["ctx_rule"]) == (8, 32768, "set")
+    tight = plan(["-np", "auto"], free=22 << 30)                     # one slot already has to fit under the model's limit
+    assert tight["n_slots"] == 1 and tight["ctx_rule"] == "fitted" and 4096 <= tight["slot_ctx"] < spec.ctx_train
+    some = plan(["-np", "auto", "--slot-ctx", "16384"], free=27 << 30)
+    assert 1 <= some["n_slots"] < 8 and some["slot_ctx"] == 16384
+    assert plan(["-np", "2", "-c", "16384"])["slot_ctx"] == 8192      # a set total is shared
+    assert plan(["-np", "4", "--slot-ctx", "8192"])["ctx_total"] == 32768
+    for bad in (["-np", "auto", "-c", "8192"], ["--slot-ctx", "4096", "-c", "8192"], ["-np", "0"], ["-np", "many"]):
+        with pytest.raises(Refusal) as e:
+            plan(bad)
+        assert e.value.code == Code.USAGE
+    with pytest.raises(Refusal) as e:
+        plan(["-np", "4", "--slot-ctx", "40960"], free=26 << 30)
+    assert e.value.code == Code.NO_FIT and "largest slot context" in str(e.value)
