@@ -365,6 +365,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     try:
         levers.at_main()
         opts = flags.parse(argv)
+        for note in opts.get("_config_notes", ()):
+            print(f"bloomery-serve: {note}", file=sys.stderr)
         if opts["version"]:
             from .. import __version__
             print(f"bloomery_b200 {__version__}")

@@ -98,6 +98,64 @@ def _conv(f: Flag, raw: str):
     return raw
 
 
+# what a settings file may not hold: keys that ask the start to do something rather than set it
+_CONFIG_ACTIONS = ("plan", "levers", "help", "version", "list-devices", "records-schema", "recommend", "dry-run", "json", "config")
+# the entries whose value the start line may print (never a key)
+_CONFIG_SHOWN = ("ctx-size", "ubatch-size", "cache-ram", "parallel", "alias", "host", "port", "api-key-file", "slot-save-path",
+                 "chat-template-file")
+
+
+def _read_config(path: str, cli: Dict[str, Any], notes: List[str]) -> Dict[str, Any]:
+    """``--config FILE``: one JSON object whose keys are flags' long names without their dashes.  A string or a number is
+    the flag's value, ``true`` gives a switch, a list gives the flag once for each value; the command line replaces an
+    entry for the same flag.  ``notes`` gets one line an entry: what it was read as, or that a flag replaced it."""
+    def pairs(items):
+        seen = set()
+        for k, _ in items:
+            if k in seen:
+                raise Refusal(Code.USAGE, f"--config {path}: the key {k!r} is named twice")
+            seen.add(k)
+        return dict(items)
+    try:
+        with open(path) as fh:
+            raw = json.load(fh, object_pairs_hook=pairs)
+    except (OSError, json.JSONDecodeError) as exc:
+        raise Refusal(Code.USAGE, f"--config {path}: {exc}") from None
+    if not isinstance(raw, dict):
+        raise Refusal(Code.USAGE, f"--config {path}: the file is not one JSON object")
+    cfg: Dict[str, Any] = {}
+    for k, v in raw.items():
+        if k.startswith("-"):
+            raise Refusal(Code.USAGE, f"--config: the key {k!r} carries its dashes; keys are long names without them")
+        if k in _CONFIG_ACTIONS:
+            raise Refusal(Code.USAGE, f"--config: {k!r} asks the start to do something; a settings file only sets")
+        f = _BY_NAME.get("--" + k)
+        if f is None:
+            raise Refusal(Code.USAGE, f"--config: unknown key {k!r}")
+        if v is False or v is None or isinstance(v, dict) or (isinstance(v, list) and not v):
+            raise Refusal(Code.USAGE, f"--config: {k!r} has no value to give (false, null, an object and an empty list are not values; "
+                                      f"leave out a switch that is off)")
+        if f.kind == "bool":
+            if v is not True:
+                raise Refusal(Code.USAGE, f"--config: {k!r} is a switch; its value is true")
+            val: Any = True
+        else:
+            if v is True:
+                raise Refusal(Code.USAGE, f"--config: {k!r} takes a value, not true")
+            if isinstance(v, list):
+                if any(isinstance(x, (dict, list, bool)) or x is None for x in v):
+                    raise Refusal(Code.USAGE, f"--config: {k!r} lists something that is not a string or a number")
+                val = ",".join(str(x) for x in v)              # the flag once for each value
+            else:
+                val = _conv(f, str(v)) if not isinstance(v, str) else _conv(f, v)
+        if f.dest in cli:
+            notes.append(f"config {k}: replaced by the command line")
+            continue
+        cfg[f.dest] = val
+        notes.append(f"config {k}" + (f"={val}" if k in _CONFIG_SHOWN else (" on" if val is True else " set")))
+    return cfg
+
+
 def parse(argv: List[str], environ=None) -> Dict[str, Any]:
     """Resolve every flag with precedence CLI > --config > LLAMA_ARG_* > default."""
     env = os.environ if environ is None else environ
@@ -109,6 +167,8 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
         f = _BY_NAME.get(name)
         if f is None:
             raise Refusal(Code.USAGE, f"unknown flag {a!r}")
+        if f.dest == "config" and "config" in cli:
+            raise Refusal(Code.USAGE, "--config given twice")
         if f.kind == "bool":
             cli[f.dest] = _conv(f, val) if eq else True
         else:
@@ -120,17 +180,9 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
             cli[f.dest] = _conv(f, val)
         i += 1
     cfg: Dict[str, Any] = {}
+    notes: List[str] = []
     if cli.get("config"):
-        try:
-            with open(cli["config"]) as fh:
-                raw = json.load(fh)
-        except (OSError, json.JSONDecodeError) as exc:
-            raise Refusal(Code.USAGE, f"--config {cli['config']}: {exc}") from None
-        for k, v in raw.items():
-            f = _BY_NAME.get(k) or _BY_NAME.get("--" + k.replace("_", "-"))
-            if f is None:
-                raise Refusal(Code.USAGE, f"--config: unknown key {k!r}")
-            cfg[f.dest] = _conv(f, v) if isinstance(v, str) else v
+        cfg = _read_config(cli["config"], cli, notes)
     out: Dict[str, Any] = {}
     for f in FLAGS:
         if f.dest in cli:
@@ -141,6 +193,7 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
             out[f.dest] = _conv(f, env[f.env])
         elif f.dest not in out:
             out[f.dest] = f.default
+    out["_config_notes"] = notes
     return out
 
 

@@ -63,9 +63,24 @@ def test_min_p_top_p_and_penalties():
 # ---- flags / levers / records -----------------------------------------------------------------
 def test_flag_precedence_and_unknown(tmp_path):
     cfg = tmp_path / "c.json"
-    cfg.write_text(json.dumps({"--port": 1234, "ctx-size": "2048"}))
+    cfg.write_text(json.dumps({"port": 1234, "ctx-size": "2048", "api-key": ["k1", "k2"], "cpu-moe": True, "alias": "mine"}))
     o = flags.parse(["--config", str(cfg), "-c", "4096"], environ={"LLAMA_ARG_PORT": "9", "LLAMA_ARG_HOST": "0.0.0.0"})
     assert o["ctx"] == 4096 and o["port"] == 1234 and o["host"] == "0.0.0.0"          # CLI > config > env > default
+    assert o["api_key"] == "k1,k2" and o["cpu_moe"] is True
+    notes = o["_config_notes"]
+    assert "config ctx-size: replaced by the command line" in notes and "config port=1234" in notes and "config alias=mine" in notes
+    assert "config api-key set" in notes and not any("k1" in n for n in notes)        # a key is never printed
+    for doc, word in (('{"--port": 1}', "dashes"), ('{"plan": true}', "asks the start"), ('{"port": 1, "port": 2}', "twice"),
+                      ('{"cpu-moe": false}', "no value"), ('{"alias": null}', "no value"), ('{"alias": {}}', "no value"),
+                      ('{"api-key": []}', "no value"), ('{"cpu-moe": "yes"}', "switch"), ('{"port": true}', "takes a value"),
+                      ('[1]', "not one JSON object"), ('{"frobnicate": 1}', "unknown key")):
+        cfg.write_text(doc)
+        with pytest.raises(Refusal) as e:
+            flags.parse(["--config", str(cfg)], environ={})
+        assert e.value.code == Code.USAGE and word in str(e.value), (doc, str(e.value))
+    cfg.write_text("{}")
+    with pytest.raises(Refusal, match="twice"):
+        flags.parse(["--config", str(cfg), "--config", str(cfg)], environ={})
     with pytest.raises(Refusal) as e:
         flags.parse(["--frobnicate"])
     assert e.value.code == Code.USAGE and "--frobnicate" in str(e.value)
