@@ -179,6 +179,12 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
                 val = argv[i]
             cli[f.dest] = _conv(f, val)
         i += 1
+    # two sources of one thing on the command line are refused by name, never picked between
+    if "model" in cli and "hf" in cli:
+        raise Refusal(Code.USAGE, "the model is named twice: -m beside --hf")
+    placed = [n for n, d in (("--cpu-moe", "cpu_moe"), ("-ncmoe", "n_cpu_moe"), ("-ot", "override_tensor")) if cli.get(d)]
+    if len(placed) > 1:
+        raise Refusal(Code.USAGE, f"the routed experts' place is named twice: {placed[0]} beside {placed[1]}")
     cfg: Dict[str, Any] = {}
     notes: List[str] = []
     if cli.get("config"):

@@ -81,6 +81,11 @@ def test_flag_precedence_and_unknown(tmp_path):
     cfg.write_text("{}")
     with pytest.raises(Refusal, match="twice"):
         flags.parse(["--config", str(cfg), "--config", str(cfg)], environ={})
+    for argv in (["-m", "x", "--hf", "a/b"], ["--cpu-moe", "-ncmoe", "4"], ["-ncmoe", "2", "-ot", "exps=CPU"]):
+        with pytest.raises(Refusal, match="named twice"):
+            flags.parse(argv, environ={})
+    cfg.write_text('{"cpu-moe": true}')                          # a flag that sets the same thing another way replaces the entry's use
+    assert flags.parse(["--config", str(cfg), "-ncmoe", "4"], environ={})["n_cpu_moe"] == 4
     with pytest.raises(Refusal) as e:
         flags.parse(["--frobnicate"])
     assert e.value.code == Code.USAGE and "--frobnicate" in str(e.value)
