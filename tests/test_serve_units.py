@@ -98,7 +98,7 @@ def test_placement_words():
     assert pl.devices == [0] and pl.mode == "a" and pl.word() == "a"
     pl = flags.placement(flags.parse(["-dev", "CUDA0,CUDA1,CUDA2,CUDA3", "-ts", "1,1,1,1", "--cpu-moe"], {}), 8, 48)
     assert pl.mode == "tp" and pl.expert_shares == [0.25] * 4 and pl.host_experts == "all" and pl.word() == "tp4+host[all]"
-    pl = flags.placement(flags.parse(["-ot", r"blk\.(1|2)\.ffn_.*_exps=CPU", "-ncmoe", "3"], {}), 1, 48)
+    pl = flags.placement(flags.parse(["-ot", r"blk\.(1|2)\.ffn_.*_exps=CPU"], {}), 1, 48)
     assert pl.host_experts == "pattern"
     for bad, word in ((["-sm", "row"], "row"), (["-ngl", "20"], "-ngl"), (["-ot", "attn_q=CPU"], "routed-expert"),
                       (["-dev", "CUDA9"], "CUDA9"), (["-ts", "1,2"], "-ts")):
