@@ -21,6 +21,7 @@ import gzip
 import hmac
 import ipaddress
 import json
+import math
 import os
 import queue
 import socket
@@ -132,10 +133,19 @@ class State:
 # -------------------------------------------------------------------------------------------
 # request shaping
 # -------------------------------------------------------------------------------------------
+SAMPLER_ORDER = ("penalties", "top_k", "top_p", "min_p", "temperature")      # the chain this server runs, in its order
+I32_MAX = 2 ** 31 - 1
+
+
 def sampling_from(body: Dict[str, Any], defaults: Dict[str, Any]) -> SamplingParams:
     def f(name, dflt, alt=None):
         v = body.get(name, body.get(alt) if alt else None)
-        return dflt if v is None else v
+        if v is None:
+            return dflt
+        # a sampling field of the wrong type or a non-finite value is refused by name (null is unset)
+        if isinstance(v, bool) or not isinstance(v, (int, float)) or (isinstance(v, float) and not math.isfinite(v)):
+            raise ApiError(400, f"field {name!r} takes a finite number")
+        return v
     seed = f("seed", defaults.get("seed", -1))
     return SamplingParams(
         temperature=float(f("temperature", defaults.get("temp", 0.8))), top_k=int(f("top_k", defaults.get("top_k", 40))),
@@ -146,10 +156,36 @@ def sampling_from(body: Dict[str, Any], defaults: Dict[str, Any]) -> SamplingPar
         seed=int(seed) if seed is not None and int(seed) >= 0 else 0)
 
 
+# sampler stages this server lacks: refused when a request turns one on (the value that leaves it off passes)
+_OFF_VALUES = {"typical_p": (1, 1.0), "top_n_sigma": (-1, -1.0, 0, 0.0), "dry_multiplier": (0, 0.0), "xtc_probability": (0, 0.0),
+               "dynatemp_range": (0, 0.0), "mirostat": (0,), "mirostat_tau": None, "mirostat_eta": None, "dry_base": None,
+               "dry_allowed_length": None, "dry_penalty_last_n": None, "xtc_threshold": None, "dynatemp_exponent": None}
+
+
 def check_fields(body: Dict[str, Any]) -> None:
     for k, why in UNSUPPORTED_FIELDS.items():
         if k in body and body[k] not in (None, "", 0, 0.0, [], False):
             raise ApiError(400, f"field {k!r} is not supported" + (f": {why}" if why else ""))
+    for k, off in _OFF_VALUES.items():
+        if off is not None and body.get(k) is not None and body[k] not in off:
+            raise ApiError(400, f"field {k!r} turns on a sampler stage this server does not run")
+    order = body.get("samplers")
+    if order is not None:
+        if not isinstance(order, list) or not all(isinstance(x, str) for x in order):
+            raise ApiError(400, "field 'samplers' takes a list of sampler names")
+        unknown = [x for x in order if x not in SAMPLER_ORDER]
+        if unknown:
+            raise ApiError(400, f"field 'samplers' names {unknown[0]!r}, a sampler this server lacks")
+        want = [x for x in SAMPLER_ORDER if x in order]
+        if list(order) != want:
+            raise ApiError(400, f"field 'samplers' orders the chain as {order}; this server runs {want}")
+    for k in ("n_predict", "max_tokens", "max_completion_tokens", "max_output_tokens"):
+        v = body.get(k)
+        if v is not None and (isinstance(v, bool) or not isinstance(v, int) or not -1 <= v <= I32_MAX):
+            raise ApiError(400, f"field {k!r} takes a whole number from -1 to {I32_MAX}")
+    n = body.get("n")
+    if n is not None and (isinstance(n, bool) or not isinstance(n, int) or n != 1):
+        raise ApiError(400, "field 'n' above 1 is not served on this route")
 
 
 def stops_from(body) -> List[str]:
@@ -359,7 +395,9 @@ class Handler(BaseHTTPRequestHandler):
                 return self._embeddings(body)
             if path == "/tokenize":
                 tk = st.engine.tokenizer
-                ids = tk.encode(str(body.get("content", "")), parse_special=bool(body.get("parse_special", True)),
+                if not isinstance(body.get("content"), str):
+                    raise ApiError(400, "field 'content' takes a string")
+                ids = tk.encode(body["content"], parse_special=bool(body.get("parse_special", True)),
                                 add_bos=bool(body.get("add_special", False)))
                 if body.get("with_pieces"):
                     return self._send(200, {"tokens": [{"id": i, "piece": tk.decode([i], skip_special=False)} for i in ids]})
@@ -569,7 +607,17 @@ class Handler(BaseHTTPRequestHandler):
                        id_slot=(int(body["id_slot"]) if body.get("id_slot", -1) not in (None, -1) else None),
                        constraint=constraint_from(body), logit_bias=lb,
                        t_max_predict_ms=float(body.get("t_max_predict_ms") or 0),
-                       endpoint=(urlparse(self.path).path.rstrip("/") or "/"))
+                       endpoint=(urlparse(self.path).path.rstrip("/") or "/"), **self._reasoning_fields(body))
+
+    @staticmethod
+    def _reasoning_fields(body) -> Dict[str, Any]:
+        from . import reasoning as RS
+        choice = body.get("tool_choice")
+        try:
+            return {"reasoning_budget": RS.budget_from(body, forced_tool=choice == "required" or isinstance(choice, dict)),
+                    "reasoning_loop": RS.loop_flag(body)}
+        except RS.ReasoningError as exc:
+            raise ApiError(400, str(exc)) from None
 
     def _prompt_ids(self, prompt) -> List[int]:
         tk = self.state.engine.tokenizer
@@ -690,6 +738,11 @@ class Handler(BaseHTTPRequestHandler):
         segs = st.template.render(messages, tools=tools, add_generation_prompt=True, **extra)
         return st.engine.tokenizer.encode_marked(segs)
 
+    def _template_opened_think(self, ids: List[int]) -> bool:
+        """Whether the rendered prompt ends inside a think span the template opened itself."""
+        tail = self.state.engine.tokenizer.decode(list(ids[-16:]), skip_special=False)
+        return tail.rstrip().endswith("<think>")
+
     def _chat(self, body) -> None:
         st = self.state
         tools = body.get("tools")
@@ -698,11 +751,16 @@ class Handler(BaseHTTPRequestHandler):
                 pass
             elif not isinstance(body.get("tool_choice"), dict):
                 raise ApiError(400, f"tool_choice {body.get('tool_choice')!r} is not supported")
-        ids = self._chat_ids(body.get("messages"), tools if body.get("tool_choice") != "none" else None,
-                             **(body.get("chat_template_kwargs") or {}))
+        from . import reasoning as RS
+        try:
+            kwargs = RS.effort_kwargs(body.get("reasoning_effort"), body.get("chat_template_kwargs"))
+        except RS.ReasoningError as exc:
+            raise ApiError(400, str(exc)) from None
+        ids = self._chat_ids(body.get("messages"), tools if body.get("tool_choice") != "none" else None, **kwargs)
         req = self._make_request(body, ids)
+        req.think_started = self._template_opened_think(ids)
         rid = f"chatcmpl-{uuid.uuid4().hex[:24]}"
-        finish = {"eos": "stop", "word": "stop", "limit": "length", "cancelled": "stop"}
+        finish = {"eos": "stop", "word": "stop", "limit": "length", "cancelled": "stop", "reasoning_loop": "reasoning_loop"}
         want_reasoning = body.get("reasoning_format", "auto") != "none"
 
         def usage(d):
@@ -810,7 +868,8 @@ class Handler(BaseHTTPRequestHandler):
         b2["stop"] = body.get("stop_sequences")
         req = self._make_request(b2, ids)
         mid = f"msg_{uuid.uuid4().hex[:24]}"
-        reason = {"eos": "end_turn", "word": "stop_sequence", "limit": "max_tokens", "cancelled": "end_turn"}
+        reason = {"eos": "end_turn", "word": "stop_sequence", "limit": "max_tokens", "cancelled": "end_turn",
+                  "reasoning_loop": "reasoning_loop"}
         if req.stream:
             def start():
                 self._sse({"type": "message_start", "message": {"id": mid, "type": "message", "role": "assistant", "content": [],
@@ -891,7 +950,12 @@ class Handler(BaseHTTPRequestHandler):
         if body.get("tools"):
             tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
                                                        "parameters": t.get("parameters", {})}} for t in body["tools"] if t.get("type") == "function"]
-        ids = self._chat_ids(msgs, tools)
+        from . import reasoning as RS
+        try:
+            kwargs = RS.effort_kwargs((body.get("reasoning") or {}).get("effort") if isinstance(body.get("reasoning"), dict) else None, None)
+        except RS.ReasoningError as exc:
+            raise ApiError(400, str(exc)) from None
+        ids = self._chat_ids(msgs, tools, **kwargs)
         b2 = dict(body)
         fmt = (body.get("text") or {}).get("format")
         if fmt and fmt.get("type") in ("json_schema", "json_object"):
@@ -913,7 +977,7 @@ class Handler(BaseHTTPRequestHandler):
             for c in calls:
                 output.append({"type": "function_call", "id": f"fc_{uuid.uuid4().hex[:16]}", "call_id": c["id"],
                                "name": c["function"]["name"], "arguments": c["function"]["arguments"], "status": "completed"})
-            resp = {"id": rid, "object": "response", "created_at": int(time.time()), "status": "completed" if d["stop_type"] != "limit" else "incomplete",
+            resp = {"id": rid, "object": "response", "created_at": int(time.time()), "status": "completed" if d["stop_type"] not in ("limit", "reasoning_loop") else "incomplete",
                     "model": st.model_id, "output": output, "output_text": content,
                     "usage": {"input_tokens": d["tokens_evaluated"], "output_tokens": d["tokens_predicted"],
                               "total_tokens": d["tokens_evaluated"] + d["tokens_predicted"],

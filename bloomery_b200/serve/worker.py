@@ -10,6 +10,7 @@ constraints, and pushes events to the HTTP thread (``genloop.rs``).
 """
 from __future__ import annotations
 
+import collections
 import dataclasses
 import itertools
 import math
@@ -45,6 +46,9 @@ class Request:
     logit_bias: Dict[int, float] = dataclasses.field(default_factory=dict)
     t_max_predict_ms: float = 0.0
     endpoint: str = ""                      # the route that made the request (the per-request log line names it)
+    reasoning_budget: int = -1              # generated ids the think span may take (-1: no budget)
+    reasoning_loop: bool = False            # end a think span that repeats itself
+    think_started: bool = False             # the template already opened the think span
     id: int = dataclasses.field(default_factory=lambda: next(_ids))
     events: "queue.Queue" = dataclasses.field(default_factory=queue.Queue)
     cancelled: threading.Event = dataclasses.field(default_factory=threading.Event)
@@ -134,6 +138,13 @@ class Worker(threading.Thread):
                 continue
             a = Active(req, slot, Sampler(req.sampling), StreamDecoder(self.engine.tokenizer))
             a.t_prompt0 = time.time()
+            a.forced_ids = collections.deque()
+            a.span = None
+            if req.reasoning_budget >= 0 or req.reasoning_loop:
+                from .reasoning import ThinkSpan
+                a.span = ThinkSpan(started=req.think_started, budget=req.reasoning_budget, watch_loop=req.reasoning_loop)
+                if a.span.force_close(""):                        # a budget of 0 closes an opened span before its first id
+                    a.forced_ids.extend(self.engine.tokenizer.encode(a.span.close_tag, parse_special=True, add_bos=False))
             keep = shared if req.cache_prompt else 0
             # a longer match in another slot (shared KV pages) or in the host cache beats the slot's own prefix
             if req.cache_prompt:
@@ -214,7 +225,7 @@ class Worker(threading.Thread):
         del self.active[a.slot.id]
         self.board.release(a.slot)
 
-    REASONS = {"eos": "eos", "word": "stop", "limit": "length", "cancelled": "cancel"}
+    REASONS = {"eos": "eos", "word": "stop", "limit": "length", "cancelled": "cancel", "reasoning_loop": "reasoning_loop"}
 
     def _log_request(self, a: Active, stop_type: str, n_prompt: int, prompt_ms: float, pred_ms: float) -> None:
         """One stderr line a request when its generation ends (``docs/serving.md:466-470`` of the reference): what was
@@ -258,6 +269,11 @@ class Worker(threading.Thread):
             a.sent = upto
 
     def _pick(self, a: Active, greedy: int, logits: Optional[np.ndarray]) -> int:
+        if getattr(a, "forced_ids", None):
+            return int(a.forced_ids.popleft())               # text written for the model (the think span's closing tag)
+        return self._pick_free(a, greedy, logits)
+
+    def _pick_free(self, a: Active, greedy: int, logits: Optional[np.ndarray]) -> int:
         req = a.req
         if logits is None:
             return greedy
@@ -322,7 +338,7 @@ class Worker(threading.Thread):
     def _can_draft(self, a: Active) -> bool:
         r = a.req
         return (self.draft is not None and r.sampling.temperature <= 0 and not r.sampling.penalizes and r.constraint is None
-                and not r.logit_bias and r.n_probs == 0)
+                and not r.logit_bias and r.n_probs == 0 and getattr(a, "span", None) is None)
 
     def _turn(self):
         """The slots that run this round when the engine's slots take it in turns (``serve/swap.py``), else None."""
@@ -358,7 +374,8 @@ class Worker(threading.Thread):
             """The card runs the whole sampling chain when nothing needs the logits on the host."""
             r = a.req
             return (getattr(self.engine, "device_sampling", False) and (r.sampling.temperature > 0 or r.sampling.penalizes)
-                    and r.n_probs == 0 and r.constraint is None and not r.logit_bias and not r.ignore_eos)
+                    and r.n_probs == 0 and r.constraint is None and not r.logit_bias and not r.ignore_eos
+                    and getattr(a, "span", None) is None)
 
         sampling = None
         if any(on_card(a) for a in who):
@@ -443,6 +460,14 @@ class Worker(threading.Thread):
             self._finish(a, "word", hit[1])
             return False
         self._flush_text(a)
+        span = getattr(a, "span", None)
+        if span is not None:
+            span.note(a.text, len(a.generated))
+            if span.force_close(a.text):
+                a.forced_ids.extend(tk.encode(span.close_tag, parse_special=True, add_bos=False))
+            elif span.looping(a.text, a.generated):
+                self._finish(a, "reasoning_loop")
+                return False
         if req.constraint is not None and req.constraint.done(a.text) and req.constraint.closed(a.text):
             self._finish(a, "eos")
             return False

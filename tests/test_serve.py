@@ -404,3 +404,37 @@ def test_long_generation_says_it_is_still_generating(capfd):
     assert sum(1 for ln in err.splitlines() if ": generating, " in ln) >= 2
     s.state.stop_event.set()
     s.stop()
+
+
+def test_reasoning_budget_loop_and_refused_fields(server):
+    # the budget writes the closing tag for the model once the span has used its ids
+    code, r = call(server, "/completion", {"prompt": "<think>abcdefgh</think>done", "temperature": 0, "n_predict": 24,
+                                           "reasoning_budget": 4})
+    assert code == 200 and r["content"].startswith("<think>abc</think>")
+    # a span that repeats itself ends with its own stop type
+    big = Server(flags.parse(["--port", "0", "--mock"]))
+    big.start()
+    big.ready(MockEngine(n_slots=1, slot_ctx=2048), ChatTemplate(), 0)
+    code, r = call(big, "/completion", {"prompt": "<think>" + "a" * 400, "temperature": 0, "n_predict": 390, "reasoning_loop": True})
+    assert code == 200 and r["stop_type"] == "reasoning_loop" and 256 < r["tokens_predicted"] < 330
+    code, r = call(big, "/completion", {"prompt": "<think>" + "a" * 400, "temperature": 0, "n_predict": 390})
+    assert r["stop_type"] == "limit"                                   # off unless asked
+    big.state.stop_event.set()
+    big.stop()
+    for body, word in (({"reasoning_budget": -3}, "reasoning_budget"), ({"reasoning_loop": "yes"}, "reasoning_loop"),
+                       ({"temperature": "hot"}, "temperature"), ({"top_p": float("nan")}, "top_p"), ({"typical_p": 0.5}, "typical_p"),
+                       ({"mirostat": 2}, "mirostat"), ({"samplers": ["top_p", "top_k"]}, "samplers"),
+                       ({"samplers": ["top_k", "tail_free"]}, "tail_free"), ({"n_predict": -5}, "n_predict"), ({"n": 3}, "'n'")):
+        code, r = call(server, "/completion", {"prompt": "ab", **body})
+        assert code == 400 and word in r["error"]["message"], (body, r)
+    assert call(server, "/completion", {"prompt": "ab", "n_predict": 2, "typical_p": 1.0, "mirostat": 0, "samplers": ["top_k", "temperature"],
+                                        "temperature": None})[0] == 200
+    code, r = call(server, "/tokenize", {"content": 5})
+    assert code == 400 and "content" in r["error"]["message"]
+    code, r = call(server, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "reasoning_effort": "loud"})
+    assert code == 400 and "reasoning_effort" in r["error"]["message"]
+    code, r = call(server, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "reasoning_effort": "none",
+                                                    "chat_template_kwargs": {"enable_thinking": True}, "max_tokens": 2})
+    assert code == 400 and "opposite" in r["error"]["message"]
+    assert call(server, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "reasoning_effort": "low",
+                                                 "max_tokens": 2})[0] == 200

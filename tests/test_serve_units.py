@@ -597,3 +597,46 @@ def test_slot_count_and_context_rules():
     with pytest.raises(Refusal) as e:
         plan(["-np", "4", "--slot-ctx", "40960"], free=26 << 30)
     assert e.value.code == Code.NO_FIT and "largest slot context" in str(e.value)
+
+
+def test_reasoning_rules():
+    from bloomery_b200.serve import reasoning as RS
+    assert RS.effort_kwargs(None, {"a": 1}) == {"a": 1}
+    assert RS.effort_kwargs("none", None) == {"enable_thinking": False, "reasoning_effort": "none"}
+    assert RS.effort_kwargs("high", {"enable_thinking": True})["enable_thinking"] is True
+    for effort, kw in (("loud", None), (3, None), ("none", {"enable_thinking": True}), ("low", {"enable_thinking": False})):
+        with pytest.raises(RS.ReasoningError):
+            RS.effort_kwargs(effort, kw)
+    assert RS.budget_from({}) == -1 and RS.budget_from({"reasoning_budget": 0}) == 0
+    for bad in ({"reasoning_budget": -2}, {"reasoning_budget": 1.5}, {"reasoning_budget": True}):
+        with pytest.raises(RS.ReasoningError):
+            RS.budget_from(bad)
+    with pytest.raises(RS.ReasoningError):
+        RS.budget_from({"reasoning_budget": 10}, forced_tool=True)
+    assert RS.loop_flag({"reasoning_loop": True}) and not RS.loop_flag({"reasoning_loop": None})
+    with pytest.raises(RS.ReasoningError):
+        RS.loop_flag({"reasoning_loop": "yes"})
+    # the loop check: a cycle of up to 1,024 ids over at least 256 ids and one whole cycle
+    rng = np.random.default_rng(0)
+    free = rng.integers(0, 1000, 3000).tolist()
+    assert RS.find_loop(free) == 0
+    cyc = rng.integers(0, 1000, 7).tolist()
+    assert RS.find_loop(free[:100] + cyc * 36) == 0                    # 252 repeated ids: under the 256 + one cycle
+    assert RS.find_loop(free[:100] + cyc * 38) == 7
+    long_cycle = rng.integers(0, 1000, 600).tolist()
+    assert RS.find_loop(free[:50] + long_cycle * 2) == 600 and RS.find_loop(free[:50] + long_cycle + long_cycle[:500]) == 0
+    assert RS.find_loop([5] * 300) == 1
+    # the span: budget and forced close
+    sp = RS.ThinkSpan(budget=3)
+    text = ""
+    closes = []
+    for i, piece in enumerate(["<think>", "a", "b", "c", "d"]):
+        text += piece
+        sp.note(text, i + 1)
+        closes.append(sp.force_close(text))
+    assert closes == [False, False, True, False, False]                # once, when the span has used its three ids
+    sp0 = RS.ThinkSpan(started=True, budget=0)
+    assert sp0.force_close("") and not sp0.force_close("")
+    done = RS.ThinkSpan(started=True, budget=5)
+    done.note("x</think>", 1)
+    assert not done.inside("x</think> answer") and not done.force_close("x</think> answer")
