@@ -10,9 +10,12 @@ an end-of-generation token is allowed.
 
 The output is canonical JSON: ``", "`` and ``": "`` separators, no other whitespace, properties in schema order.
 
-Schema subset: ``type`` object (``properties`` in order, all emitted) / array (``items``, ``minItems``, ``maxItems``) /
-string (``maxLength``, ``enum``) / number / integer / boolean / null, ``const``, ``enum``, ``anyOf`` / ``oneOf``.
-Anything else raises :class:`Unsupported` and the caller falls back to the prefix validator of ``serve/chat.py``.
+Schema subset: ``type`` object (its ``required`` properties in order, then each optional one in order, each of which may
+be left out) / array (``items``, ``minItems``, ``maxItems``) / string (``maxLength``, ``enum``) / number / integer /
+boolean / null, ``const``, ``enum``, ``anyOf`` / ``oneOf``, a ``$ref`` into the schema itself (``#/$defs/...``, not
+recursive).  Any other keyword (``pattern``, ``minLength``, ``minimum``, ``allOf``, ...), a ``$ref`` outside the schema,
+more than 4,096 schemas or 128 nested levels raise :class:`Unsupported` naming it, and the caller falls back to the
+prefix validator of ``serve/chat.py``.
 
 The reference's counterpart is ``crates/serve/src/constrain/program.rs`` (parts, compile, walk with heads, the fixed-next
 shortcut); this one walks characters of token texts instead of precompiled id tries.
@@ -46,10 +49,39 @@ def _merge(segs: List[tuple]) -> Tuple[tuple, ...]:
     return tuple(out)
 
 
-def compile_schema(schema: Any) -> Tuple[tuple, ...]:
-    """Schema -> segments."""
+_ANNOTATIONS = ("title", "description", "default", "examples", "$schema", "$id", "$comment", "$defs", "definitions", "strict", "name")
+_KEYWORDS = {"object": ("properties", "required", "additionalProperties"), "array": ("items", "minItems", "maxItems"),
+             "string": ("maxLength",), "number": (), "integer": (), "boolean": (), "null": ()}
+MAX_SCHEMAS, MAX_DEPTH = 4096, 128
+
+
+def compile_schema(schema: Any, root: Any = None, _depth: int = 0, _count: Optional[List[int]] = None,
+                   _refs: Tuple[str, ...] = ()) -> Tuple[tuple, ...]:
+    """Schema -> segments.  ``root``: the document ``$ref`` pointers resolve in (the schema itself at the top)."""
     if not isinstance(schema, dict):
         raise Unsupported("a schema is an object")
+    root = schema if root is None else root
+    _count = [0] if _count is None else _count
+    _count[0] += 1
+    if _count[0] > MAX_SCHEMAS or _depth > MAX_DEPTH:
+        raise Unsupported(f"the schema writes out to more than {MAX_SCHEMAS} schemas or past {MAX_DEPTH} nested levels")
+    sub = lambda s_, refs=_refs: compile_schema(s_, root, _depth + 1, _count, refs)       # noqa: E731
+    if "$ref" in schema:
+        ref = schema["$ref"]
+        if not isinstance(ref, str) or not ref.startswith("#/"):
+            raise Unsupported(f"$ref {ref!r} points outside the schema")
+        if ref in _refs:
+            raise Unsupported(f"$ref {ref!r} is recursive")
+        node: Any = root
+        for part in ref[2:].split("/"):
+            part = part.replace("~1", "/").replace("~0", "~")
+            if not isinstance(node, dict) or part not in node:
+                raise Unsupported(f"$ref {ref!r} names nothing in the schema")
+            node = node[part]
+        extra = [k for k in schema if k != "$ref" and k not in _ANNOTATIONS]
+        if extra:
+            raise Unsupported(f"{extra[0]!r} beside a $ref")
+        return sub(node, _refs + (ref,))
     if "const" in schema:
         return (("lit", json.dumps(schema["const"], ensure_ascii=False)),)
     if "enum" in schema:
@@ -59,22 +91,49 @@ def compile_schema(schema: Any) -> Tuple[tuple, ...]:
         return (("alt", tuple((("lit", json.dumps(v, ensure_ascii=False)),) for v in opts)),)
     for word in ("anyOf", "oneOf"):
         if word in schema:
-            return (("alt", tuple(compile_schema(s) for s in schema[word])),)
+            if not isinstance(schema[word], list) or not schema[word]:
+                raise Unsupported(f"{word} takes a non-empty list")
+            return (("alt", tuple(sub(s_) for s_ in schema[word])),)
     t = schema.get("type")
     if isinstance(t, list):
-        return (("alt", tuple(compile_schema({**schema, "type": x}) for x in t)),)
+        return (("alt", tuple(sub({**schema, "type": x}) for x in t)),)
+    if t not in _KEYWORDS:
+        raise Unsupported(f"schema type {t!r}")
+    unknown = [k for k in schema if k != "type" and k not in _ANNOTATIONS and k not in _KEYWORDS[t]]
+    if unknown:
+        raise Unsupported(f"the keyword {unknown[0]!r} is outside the served subset")
     if t == "object":
         props = schema.get("properties")
         if not isinstance(props, dict):
             raise Unsupported("an object needs its properties listed")
+        if schema.get("additionalProperties") not in (None, False):
+            raise Unsupported("additionalProperties other than false")
+        req = schema.get("required", [])
+        if not isinstance(req, list) or any(r not in props for r in req):
+            raise Unsupported("required names a property the object does not list")
+        member = lambda key, lead: [("lit", lead + json.dumps(key, ensure_ascii=False) + ": ")] + list(sub(props[key]))     # noqa: E731
+        need = [k for k in props if k in req]
+        optional = [k for k in props if k not in req]
         segs: List[tuple] = [("lit", "{")]
-        for i, (key, sub) in enumerate(props.items()):
-            segs.append(("lit", (", " if i else "") + json.dumps(key, ensure_ascii=False) + ": "))
-            segs.extend(compile_schema(sub))
+        for i, key in enumerate(need):
+            segs += member(key, ", " if i else "")
+
+        def tail(keys) -> List[tuple]:
+            """Optional members after something was written: each may be left out."""
+            out: List[tuple] = []
+            for key in keys:
+                out.append(("alt", (_merge(member(key, ", ")), ())))
+            return out
+        if need or not optional:
+            segs += tail(optional)
+        else:
+            # nothing required: the first member written takes no comma, so fork on which optional one comes first
+            firsts = [_merge(member(key, "") + tail(optional[i + 1:])) for i, key in enumerate(optional)]
+            segs.append(("alt", tuple(firsts) + ((),)))
         segs.append(("lit", "}"))
         return _merge(segs)
     if t == "array":
-        item = compile_schema(schema.get("items") if "items" in schema else _raise("an array needs items"))
+        item = sub(schema.get("items") if "items" in schema else _raise("an array needs items"))
         lo, hi = int(schema.get("minItems", 0)), schema.get("maxItems")
         return (("lit", "["), ("arr", item, lo, None if hi is None else int(hi), 0))
     if t == "string":
@@ -85,9 +144,7 @@ def compile_schema(schema: Any) -> Tuple[tuple, ...]:
         return (("num", True),)
     if t == "boolean":
         return (("alt", ((("lit", "true"),), (("lit", "false"),))),)
-    if t == "null":
-        return (("lit", "null"),)
-    raise Unsupported(f"schema type {t!r}")
+    return (("lit", "null"),)
 
 
 def _raise(msg: str):

@@ -170,7 +170,7 @@ def test_json_mode(server):
 def test_schema_program_forces_keys_without_sampling(server):
     """A schema that compiles to a segment program: the echo engine wants to write spaces and other keys, the program
     keeps the canonical object, and its literal text is taken through the jump arm."""
-    schema = {"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "boolean"}}}
+    schema = {"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "boolean"}}, "required": ["a", "b"]}
     code, r = call(server, "/completion", {"prompt": '{"a":   41, "zzz": 1, "b": true} trailing', "temperature": 0, "n_predict": 64,
                                             "response_format": {"type": "json_schema", "json_schema": {"schema": schema}}})
     assert code == 200

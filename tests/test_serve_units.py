@@ -358,7 +358,8 @@ def test_constraint_program_walk_and_jump_arm():
     schema = {"type": "object", "properties": {
         "name": {"type": "string", "maxLength": 8}, "age": {"type": "integer"}, "ok": {"type": "boolean"},
         "tags": {"type": "array", "items": {"enum": ["a", "b"]}, "minItems": 1, "maxItems": 2},
-        "pos": {"type": "object", "properties": {"x": {"type": "number"}}}, "kind": {"const": "v1"}}}
+        "pos": {"type": "object", "properties": {"x": {"type": "number"}}, "required": ["x"]}, "kind": {"const": "v1"}},
+        "required": ["name", "age", "ok", "tags", "pos", "kind"]}
     pc = ProgramConstraint(schema)
     assert pc.forced_text("") == '{"name": '                                      # keys and punctuation are never sampled
     good = '{"name": "Al\\"x", "age": -12, "ok": true, "tags": ["a", "b"], "pos": {"x": 1.5e3}, "kind": "v1"}'
@@ -390,6 +391,35 @@ def test_constraint_program_walk_and_jump_arm():
     with pytest.raises(Unsupported):
         compile_schema({"type": "object"})                                        # no property list: not a program
     assert constraint_for({"type": "object"}) is None and constraint_for(None) is None
+    # required members in order, then each optional one in order, each of which may be left out
+    opt = ProgramConstraint({"type": "object", "required": ["id"], "properties": {
+        "note": {"type": "string"}, "id": {"type": "integer"}, "flag": {"type": "boolean"}}})
+    assert opt.forced_text("") == '{"id": '
+    for doc in ('{"id": 7}', '{"id": 7, "note": "x"}', '{"id": 7, "flag": true}', '{"id": 7, "note": "x", "flag": false}'):
+        assert opt.allowed("", doc) and opt.done(doc), doc
+    assert not opt.allowed("", '{"id": 7, "flag": true, "note": "x"}') and not opt.allowed("", '{"note": "x"')       # order; id first
+    free = ProgramConstraint({"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "integer"}}})
+    for doc in ("{}", '{"a": 1}', '{"b": 2}', '{"a": 1, "b": 2}'):
+        assert free.allowed("", doc) and free.done(doc), doc
+    assert not free.allowed("", '{, "b"') and not free.allowed("", '{"b": 2, "a"')
+    # a $ref into the schema itself; recursion and pointers outside it are not a program
+    refd = ProgramConstraint({"type": "object", "required": ["p", "q"], "properties": {"p": {"$ref": "#/$defs/pt"}, "q": {"$ref": "#/$defs/pt"}},
+                              "$defs": {"pt": {"type": "object", "required": ["x"], "properties": {"x": {"type": "number"}}}}})
+    assert refd.allowed("", '{"p": {"x": 1}, "q": {"x": 2.5}}')
+    for bad in ({"$ref": "other.json#/a"}, {"$ref": "#/$defs/missing", "$defs": {}},
+                {"$ref": "#/$defs/n", "$defs": {"n": {"type": "array", "items": {"$ref": "#/$defs/n"}}}},
+                {"type": "string", "pattern": "^a"}, {"type": "string", "minLength": 2}, {"type": "integer", "minimum": 0},
+                {"allOf": [{"type": "integer"}]}, {"type": "object", "properties": {}, "minProperties": 1},
+                {"type": "object", "properties": {"a": {"type": "integer"}}, "required": ["b"]},
+                {"type": "object", "properties": {}, "additionalProperties": True}):
+        with pytest.raises(Unsupported):
+            compile_schema(bad)
+        assert constraint_for(bad) is None
+    deep = {"type": "integer"}
+    for _ in range(140):
+        deep = {"type": "array", "items": deep}
+    with pytest.raises(Unsupported, match="nested levels"):
+        compile_schema(deep)
 
 
 def test_prompt_cache_rules():
