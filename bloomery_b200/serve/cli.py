@@ -439,6 +439,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         eng, template_src, bos, eos = open_engine(opts, server, n_vis, template_src)
         server.ready(in_turns(eng), ChatTemplate(template_src, bos, eos), cache_bytes, int(opts["queue_depth"]))
         draft = str(levers.get("BLOOMERY_DRAFT")).lower()
+        draft = "ngram" if draft == "lookup" else draft
         if turns and draft in ("mtp", "auto"):
             draft = ""            # the draft layer's KV rows are the engine's own slots, not the slots that take turns
         if draft == "ngram" and server.state.worker is not None:
