@@ -337,8 +337,18 @@ class Worker(threading.Thread):
 
     def _can_draft(self, a: Active) -> bool:
         r = a.req
-        return (self.draft is not None and r.sampling.temperature <= 0 and not r.sampling.penalizes and r.constraint is None
-                and not r.logit_bias and r.n_probs == 0 and getattr(a, "span", None) is None)
+        # greedy, biased, masked and probability-reporting requests draft alike (the kept ids are the request's own picks),
+        # and so do sampled ones on an engine that samples on the host; where the card runs the whole sampling chain a
+        # plain sampled request keeps that path (no logits row crosses to the host).  A think-span budget writes ids
+        # for the model, which a draft cannot foresee
+        return self.draft is not None and getattr(a, "span", None) is None and not self._card_samples(a)
+
+    def _card_samples(self, a: Active) -> bool:
+        """The card runs the whole sampling chain when nothing needs the logits on the host."""
+        r = a.req
+        return (getattr(self.engine, "device_sampling", False) and (r.sampling.temperature > 0 or r.sampling.penalizes)
+                and r.n_probs == 0 and r.constraint is None and not r.logit_bias and not r.ignore_eos
+                and getattr(a, "span", None) is None)
 
     def _turn(self):
         """The slots that run this round when the engine's slots take it in turns (``serve/swap.py``), else None."""
@@ -370,12 +380,7 @@ class Worker(threading.Thread):
             return
         who = [sp[0] for sp in spans]
 
-        def on_card(a: Active) -> bool:
-            """The card runs the whole sampling chain when nothing needs the logits on the host."""
-            r = a.req
-            return (getattr(self.engine, "device_sampling", False) and (r.sampling.temperature > 0 or r.sampling.penalizes)
-                    and r.n_probs == 0 and r.constraint is None and not r.logit_bias and not r.ignore_eos
-                    and getattr(a, "span", None) is None)
+        on_card = self._card_samples
 
         sampling = None
         if any(on_card(a) for a in who):
@@ -408,13 +413,23 @@ class Worker(threading.Thread):
         if self.width is not None and len(spans) == 1:
             self.width.observe_pass(len(rows), dt)
         for a, r0, drafted in spans:
-            picks = [res[r0 + i][0] for i in range(len(drafted) + 1)]
+            # Row j evaluated the pending token (j = 0) or draft j - 1; the request's own pick from that row -- greedy,
+            # sampled, biased or masked, whatever the request asks -- is the next token, and draft j is kept exactly when
+            # it equals that pick.  So a request takes the same ids with a draft as without one, sampled requests with
+            # their seed included: a draw is consumed only for a row whose pick is used.
+            base = len(a.slot.ids)
             kept = 0
+            alive = True
+            a.draft_n += len(drafted)              # before the rows settle: a request that ends in this pass reports them
+            for j in range(len(drafted) + 1):
+                tok_in = a.pending_token if j == 0 else drafted[j - 1]
+                if j > 0:
+                    a.draft_accepted += 1          # row j exists because draft j - 1 was kept
+                alive = self._settle(a, tok_in, res[r0 + j][0], res[r0 + j][1])
+                if not alive or j == len(drafted) or a.pending_token != drafted[j]:
+                    break
+                kept += 1
             if drafted:
-                from ..runtime.speculative import accept_prefix
-                kept = accept_prefix(drafted, picks)
-                a.draft_n += len(drafted)
-                a.draft_accepted += kept
                 self.metrics.add("draft_tokens_total", len(drafted))
                 self.metrics.add("draft_accepted_total", kept)
                 for depth in range(len(drafted)):
@@ -422,15 +437,8 @@ class Worker(threading.Thread):
                     if depth < kept:
                         self.accepted_by_depth[depth] = self.accepted_by_depth.get(depth, 0) + 1
                 self.width.observe_accept(len(drafted), kept)
-                if kept < len(drafted):
-                    self.engine.cut(a.slot.id, len(a.slot.ids) + 1 + kept)     # rows of rejected drafts leave the KV
-            # the tokens this round settles: the pending one (now in the KV), then each kept draft
-            feed = [a.pending_token] + list(drafted[:kept])
-            outs = [picks[i] for i in range(kept + 1)]
-            for j, (tok_in, greedy) in enumerate(zip(feed, outs)):
-                logits = res[r0 + j][1] if j == 0 else None
-                if not self._settle(a, tok_in, greedy, logits):
-                    break
+                if alive and kept < len(drafted):
+                    self.engine.cut(a.slot.id, base + 1 + kept)     # rows of rejected drafts leave the KV
 
     def _settle(self, a: Active, tok_in: int, greedy: int, logits: Optional[np.ndarray]) -> bool:
         """Account one evaluated token and the token picked after it; False when the request ended."""

@@ -273,6 +273,32 @@ def test_speculative_drafts_change_passes_not_tokens():
     assert outs[1][3] < outs[0][3]                       # fewer decode rounds for the same tokens
 
 
+def test_sampled_and_structured_requests_draft_to_the_same_ids():
+    """A sampled request (seeded), one with a logit bias and one asking for probabilities take the same ids with the
+    n-gram draft on as without it: every kept id is the request's own pick from its verified row."""
+    from bloomery_b200.runtime.speculative import NgramDraft, WidthChooser
+    bodies = [{"prompt": "abcabcabcabc xyz abcabcabcabc xyz", "temperature": 0.9, "seed": 11, "n_predict": 40, "top_k": 2},
+              {"prompt": "abcabcabcabc xyz abcabcabcabc xyz", "temperature": 0, "n_predict": 30, "logit_bias": {"98": 5.0}},
+              {"prompt": "abcabcabcabc xyz abcabcabcabc xyz", "temperature": 0, "n_predict": 20, "n_probs": 2}]
+    outs = []
+    for drafting in (False, True):
+        s = Server(flags.parse(["--port", "0", "--mock"]))
+        s.start()
+        s.ready(MockEngine(n_slots=1, slot_ctx=512), ChatTemplate(), 0)
+        if drafting:
+            s.state.worker.enable_drafting(NgramDraft(), WidthChooser(max_width=7))
+        got = []
+        for b in bodies:
+            code, r = call(s, "/completion", dict(b))
+            assert code == 200
+            got.append((r["content"], r["tokens_predicted"], [p["id"] for p in r.get("completion_probabilities", [])] if "n_probs" in b else None))
+        outs.append((got, s.state.worker.metrics.get("draft_accepted_total")))
+        s.state.stop_event.set()
+        s.stop()
+    assert outs[0][0] == outs[1][0]
+    assert outs[0][1] == 0 and outs[1][1] > 0
+
+
 def test_cpu_engine_serves_a_gguf_file(tmp_path):
     """``-dev none``: the process opens a GGUF file, plans, loads the CPU engine and answers greedy text equal
     to the oracle's continuation; a second request reuses the cached prefix; a third runs with n-gram drafting."""
