@@ -324,6 +324,11 @@ struct Tier {
 
 }  // namespace
 
+namespace blh {
+// the fastest dot this CPU has for a resident row against q8 activations (VNNI, AVX2, scalar), for the other host files
+float dot_row(int wtype, const uint8_t* row, int K, const int8_t* xq, const float* xds) { return dot_any(wtype, row, K, xq, xds); }
+}  // namespace blh
+
 extern "C" {
 
 int blh_moe_experts(int M, int K, int I, int E, int n_used, const int* ids, const float* wts, const int8_t* xq,

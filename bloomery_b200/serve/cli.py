@@ -230,6 +230,10 @@ def open_engine(opts: Dict[str, Any], server, n_vis: int, template_src: Optional
         _, w, handle = open_model(path, "cpu")
         records.write("setup", phase="load", seconds=round(time.time() - t0, 3), page_cache=getattr(handle, "page_cache", None))
         tk, tsrc, bos, eos = surface(handle)
+        from ..runtime.host_model import covers
+        if bool(levers.get("BLOOMERY_HOST_NATIVE")) and covers(w.spec):
+            from .engine import NativeCpuEngine
+            return NativeCpuEngine(w, tk, plan["n_slots"], plan["slot_ctx"], name), tsrc, bos, eos
         return CpuEngine(w, tk, plan["n_slots"], plan["slot_ctx"], name), tsrc, bos, eos
     from ..ops import host_ops
     host_ops.pool_configure(int(levers.get("BLOOMERY_THREADS")), bool(levers.get("BLOOMERY_PIN")), int(levers.get("BLOOMERY_SPIN")))

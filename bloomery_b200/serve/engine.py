@@ -425,3 +425,85 @@ class CpuEngine(Engine):
     def props(self):
         s = self.spec
         return {"engine": "cpu", "arch": s.arch, "n_layer": s.n_layer, "n_expert": s.n_expert, "devices": ["cpu"]}
+
+
+class NativeCpuEngine(CpuEngine):
+    """The CPU-only engine over the native host step (``runtime/host_model.py``): one decoder, and so one cache, per
+    slot; the weights stay in their resident quantised rows and are shared.  Embeddings come from the plain model, made
+    on first use."""
+
+    def __init__(self, weights, tokenizer: Tokenizer, n_slots: int = 1, slot_ctx: int = 4096, model_name: str = "model"):
+        from ..runtime.host_model import HostDecoder
+        self.weights = weights
+        self.models = [HostDecoder(weights, ctx=slot_ctx) for _ in range(n_slots)]
+        self.tokenizer, self.model_name = tokenizer, model_name
+        self.n_slots, self.slot_ctx, self.n_vocab = n_slots, slot_ctx, weights.spec.vocab
+        self.spec = weights.spec
+        self._oracle = None
+
+    def _cut(self, m, n: int) -> None:
+        m.cut(n)
+
+    def prefill(self, slot, ids, start):
+        m = self.models[slot]
+        m.cut(start)
+        if m.n_past != start:
+            raise EngineError(f"slot {slot}: prompt rows start at {start} but {m.n_past} positions are kept")
+        if start + len(ids) > self.slot_ctx:
+            raise EngineError(f"slot {slot}: the prompt ends beyond the slot context")
+        for t in ids:
+            m.step(int(t), want_logits=False)
+
+    def step(self, rows, want_logits=True):
+        import torch
+        from ..models.cpu_ref import greedy_pick
+        out = []
+        for slot, tok, pos in rows:
+            m = self.models[slot]
+            m.cut(pos)
+            if m.n_past != pos:
+                raise EngineError(f"slot {slot}: row at {pos} but {m.n_past} positions are kept")
+            if pos + 1 > self.slot_ctx:
+                raise EngineError(f"slot {slot}: position {pos} is beyond the slot context")
+            lg = m.step(int(tok))
+            if not bool(torch.isfinite(lg).all()):
+                raise EngineError("non-finite logits")
+            out.append((greedy_pick(lg), lg.numpy().copy() if want_logits else None))
+        return out
+
+    def reset(self, slot):
+        self.models[slot].reset()
+
+    def share_prefix(self, src, dst, n, have=0):
+        a, b = self.models[src], self.models[dst]
+        n = min(n, a.n_past)
+        if n <= have:
+            return 0
+        b.load_kv(*a.kv(n))
+        return n
+
+    def snapshot(self, slot, ids):
+        m = self.models[slot]
+        n = min(len(ids), m.n_past)
+        if n == 0:
+            return None
+        k, v = m.kv(n)
+        return Saved(tuple(ids[:n]), {"k": k, "v": v}, k.numel() * 8)
+
+    def restore(self, slot, saved, n):
+        n = min(n, len(saved.ids))
+        return self.models[slot].load_kv(saved.payload["k"], saved.payload["v"], n)
+
+    def embed(self, ids):
+        if self._oracle is None:
+            self._oracle = CpuEngine(self.weights, self.tokenizer, 1, self.slot_ctx, self.model_name)
+        return self._oracle.embed(ids)
+
+    def props(self):
+        out = dict(super().props())
+        out["engine"] = "cpu-native"
+        return out
+
+    def close(self):
+        for m in self.models:
+            m.close()

@@ -50,6 +50,7 @@ REGISTRY: List[LeverSpec] = [
     LeverSpec("BLOOMERY_PREFILL_BF16", "word", "auto", "resident bf16 copy of the weights for the prompt path (auto = when it leaves a quarter of the card free)", ("auto", "0", "1")),
     LeverSpec("BLOOMERY_FP8_NATIVE", "bool", True, "batched pass: FP8 128x128 weights multiply E4M3 activations on the tensor cores (off = expand the weights to bf16 in flight)"),
     LeverSpec("BLOOMERY_NEED_HOOK", "str", "", "absolute path of a program run once per placed load with the need line on its standard input (exit 0 goes on, 75 = ask again later)"),
+    LeverSpec("BLOOMERY_HOST_NATIVE", "bool", True, "-dev none: decode through the native host step where it covers the model (off = the plain PyTorch model)"),
     LeverSpec("BLOOMERY_PDL", "bool", True, "programmatic dependent launch between decode kernels"),
     LeverSpec("BLOOMERY_FLASH_MMA", "bool", False, "decode attention segments on tensor-core tiles (f16 queries and probabilities)"),
     LeverSpec("BLOOMERY_GRAPHS", "bool", True, "one CUDA graph per decode step"),

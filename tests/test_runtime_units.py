@@ -529,3 +529,77 @@ def test_interleaved_ab_harness(capsys):
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert rc == 0 and out["median_a"] == 12.5 and out["ratio_b_over_a"] == 2.0 and out["a"] == [12.5, 12.5]
     assert ab.main([arm("import sys; sys.exit(3)"), arm("print(1)"), "--rounds", "1"]) == 1
+
+
+def test_native_host_step_follows_the_oracle():
+    """``runtime/host_model.py``: the whole decode step in C++ on the resident quantised rows.  Where the router is not
+    at a near tie the logits equal the plain PyTorch model's to fp32 rounding; everywhere they stay in a band; the cache
+    can be cut, saved and put back."""
+    import torch
+    from bloomery_b200.models.cpu_ref import CpuModel
+    from bloomery_b200.models.spec import tiny_deepseek, tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.runtime.host_model import HostDecoder, covers
+    spec = tiny_qwen3moe()
+    assert covers(spec) and not covers(tiny_deepseek())
+    w = Weights.from_items(spec, synth_tensors(spec, "cpu", seed=0, mix="Q4_K_M"), "cpu")
+    oracle, hd = CpuModel(w), HostDecoder(w, ctx=64)
+    exact = 0
+    for seed in (1234, 4):
+        g = torch.Generator().manual_seed(seed)
+        prompt = torch.randint(0, spec.vocab, (20,), generator=g)
+        oracle.reset(); hd.reset()
+        ref, got = oracle.forward(prompt), hd.forward(prompt.tolist())
+        err = (got - ref).abs().amax(1) / ref.abs().amax(1)
+        assert float(err.max()) < 0.06, err
+        exact += int((err < 1e-5).sum())
+    assert exact >= 8                                            # positions before any routing near-tie: the same numbers
+    # cut and continue: the same rows again give the same logits bit for bit
+    hd.reset()
+    ids = torch.randint(0, spec.vocab, (12,), generator=torch.Generator().manual_seed(5)).tolist()
+    first = hd.forward(ids)
+    hd.cut(7)
+    again = torch.stack([hd.step(t).clone() for t in ids[7:]])
+    assert torch.equal(again, first[7:])
+    # save and put back into another decoder
+    k, v = hd.kv(9)
+    other = HostDecoder(w, ctx=64)
+    assert other.load_kv(k, v) == 9 and torch.equal(other.step(ids[9]), first[9])
+    with pytest.raises(ValueError):
+        other.load_kv(torch.zeros(spec.n_layer, 100, spec.n_kv * spec.head_dim), torch.zeros(spec.n_layer, 100, spec.n_kv * spec.head_dim))
+    with pytest.raises(NotImplementedError):
+        dspec = tiny_deepseek()
+        HostDecoder(Weights.from_items(dspec, synth_tensors(dspec, "cpu", seed=0, mix="Q8_0"), "cpu"))
+    hd.close(); other.close()
+
+
+def test_native_cpu_engine_slots_share_save_and_restore():
+    import numpy as np
+    import torch
+    from bloomery_b200.models.spec import tiny_qwen3moe
+    from bloomery_b200.models.weights import Weights, synth_tensors
+    from bloomery_b200.serve.engine import EngineError, NativeCpuEngine
+    from bloomery_b200.serve.tokenizer import ByteTokenizer
+    spec = tiny_qwen3moe()
+    w = Weights.from_items(spec, synth_tensors(spec, "cpu", seed=0, mix="Q4_K_M"), "cpu")
+    eng = NativeCpuEngine(w, ByteTokenizer(spec.vocab), n_slots=3, slot_ctx=48)
+    ids = torch.randint(0, spec.vocab, (14,), generator=torch.Generator().manual_seed(6)).tolist()
+    eng.prefill(0, ids[:-1], 0)
+    t0, l0 = eng.step([(0, ids[-1], 13)])[0]
+    assert eng.share_prefix(0, 1, 10, have=0) == 10 and eng.share_prefix(0, 1, 10, have=10) == 0
+    eng.prefill(1, ids[10:-1], 10)
+    t1, l1 = eng.step([(1, ids[-1], 13)])[0]
+    assert t1 == t0 and np.array_equal(l0, l1)                 # the shared prefix is the donor's own rows
+    saved = eng.snapshot(0, ids)
+    assert saved.n_bytes > 0 and eng.restore(2, saved, 13) == 13
+    t2, l2 = eng.step([(2, ids[-1], 13)])[0]
+    assert np.array_equal(l0, l2)
+    eng.cut(2, 5)
+    with pytest.raises(EngineError):
+        eng.step([(2, ids[-1], 9)])                            # a row past what the slot keeps
+    with pytest.raises(EngineError):
+        eng.prefill(2, list(range(60)), 0)                     # beyond the slot context
+    v = eng.embed(ids)
+    assert v is not None and abs(float(np.linalg.norm(v)) - 1.0) < 1e-4
+    assert eng.props()["engine"] == "cpu-native"
+    eng.close()
