@@ -50,7 +50,7 @@ def run_once(cmd: str, pattern: Optional[str], timeout: float) -> float:
 
 
 def compare(a: Sequence[float], b: Sequence[float], higher_is_better: bool = False) -> Dict[str, object]:
-    """Medians, spread and the per-round verdicts of two interleaved series (round i pairs a[i] with b[i])."""
+    """Medians, spread and the per-round outcomes of two interleaved series (round i pairs a[i] with b[i])."""
     if len(a) != len(b) or not a:
         raise AbError("two series of the same, non-zero length")
     better = (lambda x, y: x > y) if higher_is_better else (lambda x, y: x < y)
@@ -66,7 +66,7 @@ def compare(a: Sequence[float], b: Sequence[float], higher_is_better: bool = Fal
     p = min(1.0, 2 * sum(comb(decided, i) for i in range(k, decided + 1)) / 2 ** decided) if decided else 1.0
     return {"rounds": n, "median_a": med_a, "median_b": med_b, "ratio_b_over_a": med_b / med_a if med_a else float("nan"),
             "spread_a": spread(a), "spread_b": spread(b), "wins_a": wins_a, "wins_b": wins_b, "sign_test_p": p,
-            "verdict": "same" if p > 0.1 or wins_a == wins_b else ("a" if wins_a > wins_b else "b")}
+            "winner": "same" if p > 0.1 or wins_a == wins_b else ("a" if wins_a > wins_b else "b")}
 
 
 def interleave(cmd_a: str, cmd_b: str, rounds: int, pattern: Optional[str] = None, timeout: float = 900.0,

@@ -519,10 +519,10 @@ def test_interleaved_ab_harness(capsys):
     series = ab.interleave("A", "B", 6, run=fake)
     assert order == ["A", "B", "B", "A", "A", "B", "B", "A", "A", "B", "B", "A"]      # the arms swap places every round
     got = ab.compare(series["a"], series["b"])
-    assert got["wins_b"] == 6 and got["wins_a"] == 0 and got["verdict"] == "b" and got["sign_test_p"] < 0.05
+    assert got["wins_b"] == 6 and got["wins_a"] == 0 and got["winner"] == "b" and got["sign_test_p"] < 0.05
     assert abs(got["ratio_b_over_a"] - 8.05 / 10.05) < 1e-9
-    assert ab.compare([1.0, 2.0, 1.0, 2.0], [2.0, 1.0, 2.0, 1.0])["verdict"] == "same"
-    assert ab.compare([5.0] * 6, [4.0] * 6, higher_is_better=True)["verdict"] == "a"
+    assert ab.compare([1.0, 2.0, 1.0, 2.0], [2.0, 1.0, 2.0, 1.0])["winner"] == "same"
+    assert ab.compare([5.0] * 6, [4.0] * 6, higher_is_better=True)["winner"] == "a"
     py = sys.executable
     arm = lambda text: py + " -c " + '"' + text + '"'            # noqa: E731
     rc = ab.main([arm("print('us per layer: 12.5')"), arm("print('us per layer: 25.0')"), "--rounds", "2"])
