@@ -19,54 +19,107 @@ from ..ops.decode import QWeight
 I, F, P = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
 
+MAT = {n: i for i, n in enumerate(("q", "k", "v", "o", "q_a", "q_b", "kv_a", "gate", "up", "down", "sh_gate", "sh_up", "sh_down"))}
+VEC = {n: i for i, n in enumerate(("attn_norm", "q_norm", "k_norm", "ffn_norm", "router", "router_bias", "q_a_norm", "kv_a_norm",
+                                   "k_b", "v_b"))}
+
+
 def covers(spec) -> bool:
-    """Whether the native step serves this model: GQA attention, softmax routing without groups, every layer routed, no
-    shared expert."""
-    return (not spec.mla and spec.is_moe and spec.first_dense == 0 and not spec.n_shared and spec.router_mode == "softmax"
-            and spec.n_group <= 1 and spec.hidden % 256 == 0 and spec.moe_inter % 256 == 0 and spec.head_dim % 2 == 0)
+    """Whether the native step serves this model: grouped-query or latent attention, routed layers (softmax, or sigmoid
+    with bias and groups) with or without a shared expert, leading dense layers; widths the quantised row dots take."""
+    if spec.hidden % 256 or getattr(spec, "n_mtp", 0) and False:
+        return False
+    if spec.is_moe and (spec.moe_inter % 256 or spec.n_expert % max(1, spec.n_group)):
+        return False
+    if spec.n_shared and spec.shared_inter % 32:
+        return False
+    if (spec.first_dense or not spec.is_moe) and (not spec.dense_inter or spec.dense_inter % 32):
+        return False
+    if spec.mla:
+        return spec.kv_lora % 32 == 0 and spec.rope_dim % 2 == 0 and (spec.n_q * spec.v_dim) % 64 == 0 and (not spec.q_lora or spec.q_lora % 256 == 0)
+    return spec.head_dim % 2 == 0 and (spec.n_q * spec.head_dim) % 64 == 0
 
 
 class HostDecoder:
     def __init__(self, weights, ctx: int = 4096):
         s = self.spec = weights.spec
         if not covers(s):
-            raise NotImplementedError(f"{s.arch}: the native host step covers GQA models whose layers are all routed")
+            raise NotImplementedError(f"{s.arch}: the native host step does not cover this shape")
         if str(weights.device) != "cpu":
             raise ValueError("the host decoder reads weights in host memory")
         self.w = weights                          # keeps every tensor the C++ side points into alive
+        self._keep: List[torch.Tensor] = []       # float copies made for it (latent attention's per-head matrices)
         self.ctx = ctx
         self.n_past = 0
         lib = self.lib = host()
         lib.blh_model_create.restype = ctypes.c_void_p
-        from ..models.rope import inv_freq_table
-        self._inv = inv_freq_table(s, s.head_dim).float().contiguous()
-        self.h = lib.blh_model_create(I(s.n_layer), I(s.hidden), I(s.n_q), I(s.n_kv), I(s.head_dim), I(s.vocab), I(s.n_expert),
-                                      I(s.n_used), I(s.moe_inter), I(ctx), F(s.rms_eps), I(1 if s.router_renorm else 0),
-                                      F(s.router_scale), P(self._inv.data_ptr()))
+        from ..models.rope import attn_scale, inv_freq_table
+        self._inv = inv_freq_table(s, s.rope_dim if s.mla else s.head_dim).float().contiguous()
+        self.h = lib.blh_model_create(I(s.n_layer), I(s.hidden), I(s.n_q), I(max(1, s.n_kv)), I(s.head_dim), I(s.vocab),
+                                      I(s.n_expert if s.is_moe else 0), I(s.n_used if s.is_moe else 0), I(s.moe_inter if s.is_moe else 0),
+                                      I(ctx), F(s.rms_eps), I(1 if s.router_renorm else 0), F(s.router_scale),
+                                      P(self._inv.data_ptr()), I(self._inv.numel()))
         if not self.h:
             raise ValueError("the host decoder refused this shape")
+        rc = lib.blh_model_set_arch(P(self.h), I(1 if s.mla else 0), I(s.q_lora or 0), I(s.kv_lora or 0), I(s.rope_dim or 0),
+                                    I(s.nope_dim or 0), I(s.v_dim or 0), F(attn_scale(s)), I(s.first_dense if s.is_moe else s.n_layer),
+                                    I(s.dense_inter or 0), I(s.shared_inter if s.n_shared else 0),
+                                    I(0 if s.router_mode == "softmax" else 1), I(max(1, s.n_group)), I(max(1, s.topk_group)))
+        if rc != 0:
+            self.close()
+            raise NotImplementedError("the host decoder refused this layer plan")
         q, f = weights.q, weights.f
         embd = q["token_embd.weight"]
         out = q.get("output.weight", embd)
         lib.blh_model_set_io(P(self.h), self._p(embd), I(embd.wt), self._p(out), I(out.wt), P(f["output_norm.weight"].data_ptr()))
+
+        def mat(il, slot, name):
+            m = q[f"blk.{il}.{name}"]
+            if lib.blh_model_set_mat(P(self.h), I(il), I(MAT[slot]), self._p(m), I(m.wt), I(m.rows), I(m.k)) != 0:
+                raise NotImplementedError(f"blk.{il}.{name}: rows of type {m.qtype} and width {m.k} have no host dot")
+
+        def vec(il, slot, t):
+            if t is None:
+                return
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                t = t.float().contiguous()
+                self._keep.append(t)
+            lib.blh_model_set_vec(P(self.h), I(il), I(VEC[slot]), P(t.data_ptr()))
         for il in range(s.n_layer):
             b = f"blk.{il}."
-            router = q[b + "ffn_gate_inp.weight"]
-            if router.qtype != "F32":
-                raise NotImplementedError("the host router reads f32 rows")
-            g, u, d = q[b + "ffn_gate_exps.weight"], q[b + "ffn_up_exps.weight"], q[b + "ffn_down_exps.weight"]
-            if g.qtype != u.qtype:
-                raise NotImplementedError("gate and up stacks of different types")
-            qn, kn = f.get(b + "attn_q_norm.weight"), f.get(b + "attn_k_norm.weight")
-            mats = [q[b + n] for n in ("attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight")]
-            args = []
-            for m in mats:
-                args += [self._p(m), I(m.wt)]
-            lib.blh_model_set_layer(P(self.h), I(il), *args, P(f[b + "attn_norm.weight"].data_ptr()),
-                                    P(qn.data_ptr() if qn is not None else 0), P(kn.data_ptr() if kn is not None else 0),
-                                    P(f[b + "ffn_norm.weight"].data_ptr()), self._p(router), self._p(g), self._p(u), self._p(d),
-                                    I(g.wt), I(d.wt))
+            vec(il, "attn_norm", f[b + "attn_norm.weight"])
+            vec(il, "ffn_norm", f[b + "ffn_norm.weight"])
+            mat(il, "o", "attn_output.weight")
+            if s.mla:
+                if s.q_lora:
+                    mat(il, "q_a", "attn_q_a.weight"); mat(il, "q_b", "attn_q_b.weight")
+                    vec(il, "q_a_norm", f[b + "attn_q_a_norm.weight"])
+                else:
+                    mat(il, "q", "attn_q.weight")
+                mat(il, "kv_a", "attn_kv_a_mqa.weight")
+                vec(il, "kv_a_norm", f[b + "attn_kv_a_norm.weight"])
+                vec(il, "k_b", f[b + "attn_k_b.weight"]); vec(il, "v_b", f[b + "attn_v_b.weight"])
+            else:
+                mat(il, "q", "attn_q.weight"); mat(il, "k", "attn_k.weight"); mat(il, "v", "attn_v.weight")
+                vec(il, "q_norm", f.get(b + "attn_q_norm.weight")); vec(il, "k_norm", f.get(b + "attn_k_norm.weight"))
+            if s.layer_is_moe(il):
+                router = q[b + "ffn_gate_inp.weight"]
+                if router.qtype != "F32":
+                    raise NotImplementedError("the host router reads f32 rows")
+                lib.blh_model_set_vec(P(self.h), I(il), I(VEC["router"]), self._p(router))
+                vec(il, "router_bias", f.get(b + "exp_probs_b.bias"))
+                g, u, d = q[b + "ffn_gate_exps.weight"], q[b + "ffn_up_exps.weight"], q[b + "ffn_down_exps.weight"]
+                if g.qtype != u.qtype:
+                    raise NotImplementedError("gate and up stacks of different types")
+                lib.blh_model_set_experts(P(self.h), I(il), self._p(g), self._p(u), self._p(d), I(g.wt), I(d.wt))
+                if s.n_shared:
+                    mat(il, "sh_gate", "ffn_gate_shexp.weight"); mat(il, "sh_up", "ffn_up_shexp.weight")
+                    mat(il, "sh_down", "ffn_down_shexp.weight")
+            else:
+                mat(il, "gate", "ffn_gate.weight"); mat(il, "up", "ffn_up.weight"); mat(il, "down", "ffn_down.weight")
         self._logits = torch.zeros(s.vocab, dtype=torch.float32)
+        self._kw = (s.kv_lora + s.rope_dim) if s.mla else s.n_kv * s.head_dim
+        self._vw = 0 if s.mla else self._kw
 
     @staticmethod
     def _p(w: QWeight) -> ctypes.c_void_p:
@@ -94,8 +147,8 @@ class HostDecoder:
         """(k, v) of the first ``n`` positions (default: all kept), each [layer, n, n_kv * head] fp32."""
         s = self.spec
         n = self.n_past if n is None else min(n, self.n_past)
-        k = torch.empty(s.n_layer, n, s.n_kv * s.head_dim, dtype=torch.float32)
-        v = torch.empty_like(k)
+        k = torch.empty(s.n_layer, n, self._kw, dtype=torch.float32)
+        v = torch.empty(s.n_layer, n, self._vw, dtype=torch.float32)
         if self.lib.blh_model_kv_get(P(self.h), I(n), P(k.data_ptr()), P(v.data_ptr())) != 0:
             raise RuntimeError("blh_model_kv_get refused the span")
         return k, v
