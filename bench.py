@@ -108,7 +108,9 @@ def cpu_arm(args) -> int:
         t2 = time.perf_counter()
         run = (t1 - t0, t2 - t1, out)
         if best is None or run[1] < best[1]:
-            best = run
+            best = (min(run[0], best[0]) if best else run[0], run[1], run[2])
+        else:
+            best = (min(run[0], best[0]), best[1], best[2])
     # the oracle (plain PyTorch on the dequantised weights) on the same prompt: how many of the ids agree
     oracle = CpuModel(w)
     want = oracle.generate(prompt, n_gen)
