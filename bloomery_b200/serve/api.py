@@ -162,7 +162,7 @@ _OFF_VALUES = {"typical_p": (1, 1.0), "top_n_sigma": (-1, -1.0, 0, 0.0), "dry_mu
                "dry_allowed_length": None, "dry_penalty_last_n": None, "xtc_threshold": None, "dynatemp_exponent": None}
 
 
-def check_fields(body: Dict[str, Any]) -> None:
+def check_fields(body: Dict[str, Any], allow_n: bool = False) -> None:
     for k, why in UNSUPPORTED_FIELDS.items():
         if k in body and body[k] not in (None, "", 0, 0.0, [], False):
             raise ApiError(400, f"field {k!r} is not supported" + (f": {why}" if why else ""))
@@ -184,8 +184,9 @@ def check_fields(body: Dict[str, Any]) -> None:
         if v is not None and (isinstance(v, bool) or not isinstance(v, int) or not -1 <= v <= I32_MAX):
             raise ApiError(400, f"field {k!r} takes a whole number from -1 to {I32_MAX}")
     n = body.get("n")
-    if n is not None and (isinstance(n, bool) or not isinstance(n, int) or n != 1):
-        raise ApiError(400, "field 'n' above 1 is not served on this route")
+    if n is not None and (isinstance(n, bool) or not isinstance(n, int) or n < 1 or (n > 1 and not allow_n)):
+        raise ApiError(400, "field 'n' above 1 is not served on this route" if isinstance(n, int) and not isinstance(n, bool) and n > 1
+                       else "field 'n' takes a whole number from 1")
 
 
 def stops_from(body) -> List[str]:
@@ -577,9 +578,49 @@ class Handler(BaseHTTPRequestHandler):
                          "usage": {"prompt_tokens": sum(len(st.engine.tokenizer.encode(str(t))) for t in items), "total_tokens": 0}})
 
     # ---- generation ----------------------------------------------------------------------
-    def _make_request(self, body, prompt_ids: List[int], n_predict_key=("n_predict", "max_tokens", "max_completion_tokens", "max_output_tokens")) -> Request:
+    def _choices(self, body, prompt_ids: List[int]) -> List[Request]:
+        """The requests of an ``n``-choice call: choice i samples with the request's seed plus i, so choice 0 is the
+        answer ``n`` = 1 gives.  They queue together, so n is at most the slots plus the queue depth; streamed choices
+        are not served."""
         st = self.state
-        check_fields(body)
+        n = int(body.get("n") or 1)
+        if n > 1 and body.get("stream"):
+            raise ApiError(400, "field 'n' above 1 beside 'stream' is not served")
+        if n > st.engine.n_slots + st.board.queue_depth:
+            raise ApiError(400, f"field 'n' = {n} is above the slots plus the queue depth ({st.engine.n_slots} + {st.board.queue_depth})")
+        seed = body.get("seed")
+        base = int(seed) if isinstance(seed, int) and not isinstance(seed, bool) and seed >= 0 else 0
+        return [self._make_request(dict(body, seed=base + i) if n > 1 else body, list(prompt_ids), allow_n=True) for i in range(n)]
+
+    def _collect_all(self, reqs: List[Request]) -> List[dict]:
+        """Submit every choice, then wait for each: they run side by side in the engine's rounds."""
+        from .sched import QueueFull
+        sent = []
+        try:
+            for r in reqs:
+                self.state.board.submit(r)
+                sent.append(r)
+        except QueueFull as exc:
+            for r in sent:
+                r.cancelled.set()
+            raise ApiError(503, str(exc), "unavailable_error") from None
+        out = []
+        for r in reqs:
+            while True:
+                ev = r.events.get()
+                if ev[0] == "done":
+                    out.append(ev[1])
+                    break
+                if ev[0] == "error":
+                    for o in reqs:
+                        o.cancelled.set()
+                    raise ApiError(ev[1], ev[2], "server_error" if ev[1] >= 500 else "invalid_request_error")
+        return out
+
+    def _make_request(self, body, prompt_ids: List[int], n_predict_key=("n_predict", "max_tokens", "max_completion_tokens", "max_output_tokens"),
+                      allow_n: bool = False) -> Request:
+        st = self.state
+        check_fields(body, allow_n)
         n_predict = -1
         for k in n_predict_key:
             if body.get(k) is not None:
@@ -693,7 +734,8 @@ class Handler(BaseHTTPRequestHandler):
         st = self.state
         if "prompt" not in body:
             raise ApiError(400, "prompt is required")
-        req = self._make_request(body, self._prompt_ids(body["prompt"]))
+        many = self._choices(body, self._prompt_ids(body["prompt"])) if shape != "llama" else None
+        req = many[0] if many else self._make_request(body, self._prompt_ids(body["prompt"]))
         rid = f"cmpl-{uuid.uuid4().hex[:24]}"
         if shape == "llama":
             def final(d, content):
@@ -719,12 +761,14 @@ class Handler(BaseHTTPRequestHandler):
                 self._sse(chunk("", finish.get(d["stop_type"], "stop")))
                 self._sse("[DONE]")
             return self._stream(req, lambda t: self._sse(chunk(t)), done)
-        d = self._collect(req)
+        ds = self._collect_all(many)
+        d = ds[0]
         out = chunk(d["text"], finish.get(d["stop_type"], "stop"))
-        if req.n_probs:
-            out["choices"][0]["logprobs"] = {"content": d["probs"]}
-        out["usage"] = {"prompt_tokens": d["tokens_evaluated"], "completion_tokens": d["tokens_predicted"],
-                        "total_tokens": d["tokens_evaluated"] + d["tokens_predicted"]}
+        out["choices"] = [{"index": i, "text": di["text"], "finish_reason": finish.get(di["stop_type"], "stop"),
+                           "logprobs": {"content": di["probs"]} if req.n_probs else None} for i, di in enumerate(ds)]
+        done_n = sum(di["tokens_predicted"] for di in ds)
+        out["usage"] = {"prompt_tokens": d["tokens_evaluated"], "completion_tokens": done_n,
+                        "total_tokens": d["tokens_evaluated"] + done_n}            # the prompt counts once
         out["timings"] = d["timings"]
         self._send(200, out)
 
@@ -757,8 +801,10 @@ class Handler(BaseHTTPRequestHandler):
         except RS.ReasoningError as exc:
             raise ApiError(400, str(exc)) from None
         ids = self._chat_ids(body.get("messages"), tools if body.get("tool_choice") != "none" else None, **kwargs)
-        req = self._make_request(body, ids)
-        req.think_started = self._template_opened_think(ids)
+        many = self._choices(body, ids)
+        req = many[0]
+        for r_ in many:
+            r_.think_started = self._template_opened_think(ids)
         rid = f"chatcmpl-{uuid.uuid4().hex[:24]}"
         finish = {"eos": "stop", "word": "stop", "limit": "length", "cancelled": "stop", "reasoning_loop": "reasoning_loop"}
         want_reasoning = body.get("reasoning_format", "auto") != "none"
@@ -804,21 +850,26 @@ class Handler(BaseHTTPRequestHandler):
                     self._sse(delta({"role": "assistant", "content": ""}))
                 on_text(t)
             return self._stream(req, first_then, on_done)
-        d = self._collect(req)
-        text = d["text"]
-        reasoning, content = C.split_reasoning(text) if want_reasoning else ("", text)
-        calls: List[dict] = []
-        if tools:
-            content, calls = C.parse_tool_calls(content, st.tool_format)
-        msg: Dict[str, Any] = {"role": "assistant", "content": content if (content or not calls) else None}
-        if reasoning:
-            msg["reasoning_content"] = reasoning
-        if calls:
-            msg["tool_calls"] = calls
+        ds = self._collect_all(many)
+        choices = []
+        for i, di in enumerate(ds):
+            reasoning, content = C.split_reasoning(di["text"]) if want_reasoning else ("", di["text"])
+            calls: List[dict] = []
+            if tools:
+                content, calls = C.parse_tool_calls(content, st.tool_format)
+            msg: Dict[str, Any] = {"role": "assistant", "content": content if (content or not calls) else None}
+            if reasoning:
+                msg["reasoning_content"] = reasoning
+            if calls:
+                msg["tool_calls"] = calls
+            choices.append({"index": i, "message": msg, "finish_reason": "tool_calls" if calls else finish.get(di["stop_type"], "stop"),
+                            "logprobs": {"content": di["probs"]} if req.n_probs else None})
+        d = ds[0]
+        use = usage(d)
+        use["completion_tokens"] = sum(di["tokens_predicted"] for di in ds)            # the prompt counts once
+        use["total_tokens"] = use["prompt_tokens"] + use["completion_tokens"]
         out = {"id": rid, "object": "chat.completion", "created": int(time.time()), "model": st.model_id,
-               "choices": [{"index": 0, "message": msg, "finish_reason": "tool_calls" if calls else finish.get(d["stop_type"], "stop"),
-                            "logprobs": {"content": d["probs"]} if req.n_probs else None}],
-               "usage": usage(d), "timings": d["timings"]}
+               "choices": choices, "usage": use, "timings": d["timings"]}
         self._send(200, out)
 
     # ---- Anthropic Messages ----------------------------------------------------------------

@@ -471,3 +471,27 @@ def test_reasoning_budget_loop_and_refused_fields(server):
     assert code == 400 and "opposite" in r["error"]["message"]
     assert call(server, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "reasoning_effort": "low",
                                                  "max_tokens": 2})[0] == 200
+
+
+def test_several_choices_of_one_prompt():
+    """``n`` on the OpenAI routes: that many choices, choice i sampled with seed + i, the prompt counted once."""
+    s = Server(flags.parse(["--port", "0", "--mock"]))
+    s.start()
+    s.ready(MockEngine(n_slots=2, slot_ctx=512), ChatTemplate(), 0, 8)
+    body = {"prompt": "abcdefgh", "max_tokens": 6, "temperature": 1.5, "seed": 3, "n": 3}
+    code, r = call(s, "/v1/completions", body)
+    assert code == 200 and [c["index"] for c in r["choices"]] == [0, 1, 2]
+    code, one = call(s, "/v1/completions", dict(body, n=1))
+    assert r["choices"][0]["text"] == one["choices"][0]["text"]                 # choice 0 is the answer n = 1 gives
+    code, two = call(s, "/v1/completions", dict(body, n=1, seed=4))
+    assert r["choices"][1]["text"] == two["choices"][0]["text"]                 # choice 1 sampled with seed + 1
+    assert r["usage"]["prompt_tokens"] == one["usage"]["prompt_tokens"]
+    assert r["usage"]["completion_tokens"] == sum(6 for _ in r["choices"]) or r["usage"]["completion_tokens"] <= 18
+    code, c = call(s, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "n": 2})
+    assert code == 200 and len(c["choices"]) == 2 and c["choices"][1]["index"] == 1
+    for path, b in (("/v1/completions", dict(body, stream=True)), ("/v1/completions", dict(body, n=50)),
+                    ("/completion", dict(body)), ("/v1/completions", dict(body, n=0))):
+        code, e = call(s, path, b)
+        assert code == 400 and "'n'" in e["error"]["message"], (path, e)
+    s.state.stop_event.set()
+    s.stop()
