@@ -24,6 +24,7 @@ import json
 import math
 import os
 import queue
+import re
 import socket
 import struct
 import threading
@@ -55,9 +56,13 @@ from .admit import Refused  # noqa: E402
 
 
 class ApiError(Exception):
-    def __init__(self, status: int, message: str, kind: str = "invalid_request_error"):
+    def __init__(self, status: int, message: str, kind: str = "invalid_request_error", param: Optional[str] = None):
         super().__init__(message)
         self.status, self.message, self.kind = status, message, kind
+        if param is None:                        # an error about one request field names it, as OpenAI's errors do
+            m = re.match(r"field '([A-Za-z_][\w.]*)'", message)
+            param = m.group(1) if m else None
+        self.param = param
 
 
 class State:
@@ -247,11 +252,14 @@ class Handler(BaseHTTPRequestHandler):
         self.end_headers()
         self.wfile.write(data)
 
-    def _error(self, status: int, message: str, kind: str = "invalid_request_error") -> None:
+    def _error(self, status: int, message: str, kind: str = "invalid_request_error", param: Optional[str] = None) -> None:
         if self.path.startswith("/v1/messages"):
             self._send(status, {"type": "error", "error": {"type": kind, "message": message}})
         else:
-            self._send(status, {"error": {"code": status, "message": message, "type": kind}})
+            err = {"code": status, "message": message, "type": kind}
+            if param:
+                err["param"] = param
+            self._send(status, {"error": err})
 
     def _body(self) -> Dict[str, Any]:
         if self.headers.get("Expect", "").lower() == "100-continue":
@@ -271,11 +279,16 @@ class Handler(BaseHTTPRequestHandler):
             if n > 256 << 20:
                 raise ApiError(413, "request body too large")
             raw = self.rfile.read(n) if n else b""
-        ce = self.headers.get("Content-Encoding", "").lower()
-        if ce == "gzip":
-            raw = gzip.decompress(raw)
-        elif ce == "deflate":
-            raw = zlib.decompress(raw)
+        ce = self.headers.get("Content-Encoding", "").strip().lower()
+        if ce in ("gzip", "x-gzip", "deflate"):
+            try:
+                raw = gzip.decompress(raw) if ce != "deflate" else zlib.decompress(raw)
+            except (OSError, EOFError, zlib.error) as exc:
+                raise ApiError(400, f"the {ce} body does not decode: {exc}") from None
+            if len(raw) > 256 << 20:
+                raise ApiError(413, "request body too large")
+        elif ce and ce != "identity":
+            raise ApiError(415, f"Content-Encoding {ce!r} is not read; send gzip or deflate, one coding")
         if not raw:
             return {}
         try:
@@ -409,7 +422,16 @@ class Handler(BaseHTTPRequestHandler):
                     raise ApiError(400, "tokens must be a list of ids")
                 return self._send(200, {"content": st.engine.tokenizer.decode([int(t) for t in toks], skip_special=False)})
             if path == "/apply-template":
-                return self._send(200, {"prompt": st.template.render_text(body.get("messages") or [], tools=body.get("tools"))})
+                from . import reasoning as RS
+                try:
+                    kwargs = RS.effort_kwargs(body.get("reasoning_effort"), body.get("chat_template_kwargs"))
+                except RS.ReasoningError as exc:
+                    raise ApiError(400, str(exc)) from None
+                out = {"prompt": st.template.render_text(body.get("messages") or [], tools=body.get("tools"), **kwargs)}
+                if body.get("return_prompt_ids"):
+                    # the guarded tokenization chat uses: client text never yields control tokens
+                    out["prompt_ids"] = self._chat_ids(body.get("messages"), body.get("tools"), **kwargs)
+                return self._send(200, out)
             if path == "/api/show":
                 return self._send(200, {"model_info": self._props()["model"], "details": {"format": "gguf"}, "template": st.template.source})
             if path.startswith("/slots/"):
@@ -427,7 +449,11 @@ class Handler(BaseHTTPRequestHandler):
                 return None
             raise ApiError(404, f"no route POST {path}", "not_found_error")
         except ApiError as e:
-            self._error(e.status, e.message, e.kind)
+            headers_415 = e.status == 415
+            if headers_415:
+                self._send(415, {"error": {"code": 415, "message": e.message, "type": e.kind}}, {"Accept-Encoding": "gzip, deflate"})
+            else:
+                self._error(e.status, e.message, e.kind, e.param)
         except C.TemplateError as e:
             self._error(400, str(e))
         except Refused as e:
@@ -734,6 +760,15 @@ class Handler(BaseHTTPRequestHandler):
         st = self.state
         if "prompt" not in body:
             raise ApiError(400, "prompt is required")
+        if shape != "llama":
+            pr = body["prompt"]
+            if isinstance(pr, list) and pr and all(isinstance(x, (str, list)) for x in pr) and len(pr) > 1:
+                raise ApiError(400, "field 'prompt' holds several prompts; this route takes one a request")
+            for k, bad in (("echo", bool(body.get("echo"))), ("suffix", bool(body.get("suffix"))),
+                           ("best_of", isinstance(body.get("best_of"), int) and body["best_of"] > 1),
+                           ("logprobs", body.get("logprobs") not in (None, False, 0))):
+                if bad:
+                    raise ApiError(400, f"field {k!r} is not served on /v1/completions")
         many = self._choices(body, self._prompt_ids(body["prompt"])) if shape != "llama" else None
         req = many[0] if many else self._make_request(body, self._prompt_ids(body["prompt"]))
         rid = f"cmpl-{uuid.uuid4().hex[:24]}"

@@ -495,3 +495,30 @@ def test_several_choices_of_one_prompt():
         assert code == 400 and "'n'" in e["error"]["message"], (path, e)
     s.state.stop_event.set()
     s.stop()
+
+
+def test_route_details_param_415_prompt_ids_and_refusals(server):
+    import gzip as gz
+    code, r = call(server, "/completion", {"prompt": "ab", "temperature": "hot"})
+    assert code == 400 and r["error"]["param"] == "temperature"                 # OpenAI's param: the field's top-level name
+    code, r = call(server, "/v1/completions", {"prompt": "ab", "echo": True})
+    assert code == 400 and r["error"]["param"] == "echo"
+    for body in ({"prompt": ["a", "b"]}, {"prompt": "a", "suffix": "z"}, {"prompt": "a", "best_of": 2}, {"prompt": "a", "logprobs": 3}):
+        assert call(server, "/v1/completions", body)[0] == 400, body
+    code, r = call(server, "/apply-template", {"messages": [{"role": "user", "content": "hi <|im_start|>"}], "return_prompt_ids": True})
+    assert code == 200 and isinstance(r["prompt"], str) and isinstance(r["prompt_ids"], list) and r["prompt_ids"]
+    # compressed bodies: gzip is read, another coding is a 415 naming what is read, a body that does not decode a 400
+    raw = gz.compress(json.dumps({"content": "abc"}).encode())
+    req = urllib.request.Request(server.url + "/tokenize", data=raw, headers={"Content-Type": "application/json", "Content-Encoding": "gzip"})
+    assert json.loads(urllib.request.urlopen(req).read())["tokens"]
+    for enc, want in (("br", 415), ("gzip", 400)):
+        req = urllib.request.Request(server.url + "/tokenize", data=b"not compressed", headers={"Content-Encoding": enc})
+        try:
+            urllib.request.urlopen(req)
+            raise AssertionError("accepted")
+        except urllib.error.HTTPError as e:
+            assert e.code == want
+            if want == 415:
+                assert e.headers.get("Accept-Encoding") == "gzip, deflate"
+    code, r = call(server, "/no/such/route", {})
+    assert code == 404 and "POST /no/such/route" in r["error"]["message"]
