@@ -374,7 +374,7 @@ class Handler(BaseHTTPRequestHandler):
                     r = st.responses.get(path.split("/")[3])
                     if r is None:
                         raise ApiError(404, "no such response", "not_found_error")
-                    return self._send(200, r)
+                    return self._send(200, self._public(r))
                 raise ApiError(404, f"no route GET {path}", "not_found_error")
             if method == "DELETE":
                 if path.startswith("/v1/responses/"):
@@ -384,6 +384,15 @@ class Handler(BaseHTTPRequestHandler):
                     return self._send(200, {"id": r["id"], "object": "response", "deleted": True})
                 raise ApiError(404, f"no route DELETE {path}", "not_found_error")
             body = self._body()
+            if path.startswith("/v1/responses/") and path.endswith("/cancel"):
+                r = st.responses.get(path.split("/")[3])
+                if r is None:
+                    raise ApiError(404, "no such response", "not_found_error")
+                req_ = r.get("_req")
+                if req_ is not None and r.get("status") in ("queued", "in_progress"):
+                    req_.cancelled.set()
+                    r["status"] = "cancelled"
+                return self._send(200, self._public(r))
             if path in GENERATING_ROUTES:
                 # a generating request takes one of its key's places (in flight, and of its rate bucket) until answered
                 release = st.admission.admit(getattr(self, "_key", None) or "")
@@ -1046,6 +1055,11 @@ class Handler(BaseHTTPRequestHandler):
         fmt = (body.get("text") or {}).get("format")
         if fmt and fmt.get("type") in ("json_schema", "json_object"):
             b2["response_format"] = {"type": fmt["type"], "json_schema": {"schema": fmt.get("schema")}} if fmt["type"] == "json_schema" else {"type": "json_object"}
+        if body.get("conversation") is not None:
+            raise ApiError(400, "field 'conversation' is not served; continue with previous_response_id")
+        background = body.get("background") is True
+        if background and (body.get("store") is False or body.get("stream")):
+            raise ApiError(400, "field 'background' beside store: false or stream: true is not served")
         req = self._make_request(b2, ids)
         rid = f"resp_{uuid.uuid4().hex[:24]}"
 
@@ -1070,9 +1084,33 @@ class Handler(BaseHTTPRequestHandler):
                               "input_tokens_details": {"cached_tokens": d["tokens_cached"]}}}
             if body.get("store", True):
                 keep = dict(resp)
-                keep["_messages"] = msgs + [{"role": "assistant", "content": content}]
+                # a later previous_response_id continues the input and the output, not the instructions
+                convo = msgs[1:] if body.get("instructions") and msgs and msgs[0].get("role") == "system" else msgs
+                keep["_messages"] = convo + [{"role": "assistant", "content": content}]
                 self._store(keep)
             return resp
+        if background:
+            # answered `queued` at once; the generation runs behind it and the stored response turns completed,
+            # incomplete, cancelled or failed; a full store refuses new background work until finished ones leave
+            with st.lock:
+                running = sum(1 for r_ in st.responses.values() if r_.get("status") in ("queued", "in_progress"))
+            if running >= 1024:
+                raise ApiError(503, "the response store is full of running responses", "unavailable_error")
+            queued = {"id": rid, "object": "response", "created_at": int(time.time()), "status": "queued", "model": st.model_id,
+                      "output": [], "background": True, "_req": req, "_messages": msgs}
+            self._store(queued)
+
+            def work():
+                try:
+                    d = self._collect(req)
+                    cancelled = queued.get("status") == "cancelled" or d["stop_type"] == "cancelled"
+                    done = build(d)                      # stores the finished response under the same id
+                    if cancelled:
+                        st.responses[rid]["status"] = "cancelled"
+                except Exception as exc:             # noqa: BLE001 - the poller reads the failure
+                    queued.update(status="failed", error={"message": str(exc)})
+            threading.Thread(target=work, name=f"response-{rid}", daemon=True).start()
+            return self._send(200, self._public(queued))
         if req.stream:
             seq = [0]
 
@@ -1102,11 +1140,19 @@ class Handler(BaseHTTPRequestHandler):
             return self._stream(req, on_text, on_done)
         self._send(200, build(self._collect(req)))
 
+    @staticmethod
+    def _public(resp: dict) -> dict:
+        """A stored response without the server's own fields."""
+        return {k: v for k, v in resp.items() if not k.startswith("_")}
+
     def _store(self, resp: dict) -> None:
         """Bounded response store: 1,024 responses / 256 MiB (``response_store.rs``)."""
         st = self.state
-        size = len(json.dumps(resp))
+        size = len(json.dumps(self._public(resp), default=str)) + len(json.dumps(resp.get("_messages", []), default=str))
         with st.lock:
+            old = st.responses.get(resp["id"])
+            if old is not None:                      # a background response finishing under its own id
+                st.responses_bytes -= old.get("_size", 0)
             st.responses[resp["id"]] = resp
             st.responses_bytes += size
             resp["_size"] = size

@@ -522,3 +522,38 @@ def test_route_details_param_415_prompt_ids_and_refusals(server):
                 assert e.headers.get("Accept-Encoding") == "gzip, deflate"
     code, r = call(server, "/no/such/route", {})
     assert code == 404 and "POST /no/such/route" in r["error"]["message"]
+
+
+def test_background_responses_poll_cancel_and_refusals():
+    s = Server(flags.parse(["--port", "0", "--mock"]))
+    s.start()
+    s.ready(MockEngine(n_slots=1, slot_ctx=512, step_delay=0.01), ChatTemplate(), 0)
+    code, r = call(s, "/v1/responses", {"input": "abcdefghij", "max_output_tokens": 8, "background": True})
+    assert code == 200 and r["status"] == "queued" and "_req" not in r and "_messages" not in r
+    rid = r["id"]
+    for _ in range(200):
+        code, got = call(s, f"/v1/responses/{rid}")
+        if got["status"] not in ("queued", "in_progress"):
+            break
+        time.sleep(0.02)
+    assert got["status"] in ("completed", "incomplete") and got["output"]
+    # a running one can be cancelled
+    code, r2 = call(s, "/v1/responses", {"input": "abcdefghijklmnopqrstuvwxyz" * 3, "max_output_tokens": 200, "background": True})
+    code, c = call(s, f"/v1/responses/{r2['id']}/cancel", {})
+    assert code == 200 and c["status"] == "cancelled"
+    for _ in range(200):
+        if call(s, f"/v1/responses/{r2['id']}")[1]["status"] == "cancelled" and s.state.board.busy_count() == 0:
+            break
+        time.sleep(0.02)
+    assert s.state.board.busy_count() == 0 and call(s, f"/v1/responses/{r2['id']}")[1]["status"] == "cancelled"
+    assert call(s, "/v1/responses/resp_missing/cancel", {})[0] == 404
+    for body in ({"input": "a", "background": True, "stream": True}, {"input": "a", "background": True, "store": False},
+                 {"input": "a", "conversation": "conv_1"}):
+        assert call(s, "/v1/responses", body)[0] == 400, body
+    # previous_response_id continues the conversation without the old instructions
+    code, first = call(s, "/v1/responses", {"input": "hello", "instructions": "be brief", "max_output_tokens": 4})
+    kept = s.state.responses[first["id"]]["_messages"]
+    assert kept[0]["role"] == "user" and all(m.get("content") != "be brief" for m in kept)
+    assert call(s, "/v1/responses", {"input": "more", "previous_response_id": first["id"], "max_output_tokens": 4})[0] == 200
+    s.state.stop_event.set()
+    s.stop()
