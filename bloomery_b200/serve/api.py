@@ -360,9 +360,10 @@ class Handler(BaseHTTPRequestHandler):
                     return self._send(200, {"object": "list", "data": [self._model_card()]})
                 if path == "/api/tags":
                     return self._send(200, {"models": [{"name": st.model_id, "model": st.model_id, "details": {"format": "gguf"}}]})
-                if path.startswith("/v1/models/"):
-                    if path.split("/", 3)[3] != st.model_id:
-                        raise ApiError(404, "no such model", "not_found_error")
+                if path.startswith(("/v1/models/", "/models/")):
+                    name = path.split("/models/", 1)[1]
+                    if name != st.model_id:
+                        raise ApiError(404, f"no model {name!r} here; this server serves {st.model_id!r}", "not_found_error")
                     return self._send(200, self._model_card())
                 if path == "/props":
                     return self._send(200, self._props())
@@ -442,7 +443,15 @@ class Handler(BaseHTTPRequestHandler):
                     out["prompt_ids"] = self._chat_ids(body.get("messages"), body.get("tools"), **kwargs)
                 return self._send(200, out)
             if path == "/api/show":
-                return self._send(200, {"model_info": self._props()["model"], "details": {"format": "gguf"}, "template": st.template.source})
+                name = body.get("model") or body.get("name")
+                if name is not None and name != st.model_id:
+                    raise ApiError(404, f"no model {name!r} here; this server serves {st.model_id!r}", "not_found_error")
+                info = dict(self._props()["model"])
+                arch = str(info.get("arch") or "model")
+                info[f"{arch}.context_length"] = st.engine.slot_ctx          # the served context, as Ollama clients read it
+                caps = ["completion"] + (["tools"] if st.template is not None else [])
+                return self._send(200, {"model_info": info, "details": {"format": "gguf", "family": arch}, "template": st.template.source,
+                                        "capabilities": caps})
             if path.startswith("/slots/"):
                 return self._slot_action(int(path.split("/")[2]), (q.get("action") or [""])[0], body)
             if path == "/residency/reset":

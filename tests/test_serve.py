@@ -557,3 +557,15 @@ def test_background_responses_poll_cancel_and_refusals():
     assert call(s, "/v1/responses", {"input": "more", "previous_response_id": first["id"], "max_output_tokens": 4})[0] == 200
     s.state.stop_event.set()
     s.stop()
+
+
+def test_model_lookup_and_ollama_shapes(server):
+    assert call(server, "/v1/models/mock-echo")[0] == 200 and call(server, "/models/mock-echo")[0] == 200
+    code, r = call(server, "/v1/models/other")
+    assert code == 404 and "mock-echo" in r["error"]["message"]               # names what the server does serve
+    code, tags = call(server, "/api/tags")
+    assert code == 200 and tags["models"][0]["name"] == "mock-echo"
+    code, show = call(server, "/api/show", {"model": "mock-echo"})
+    assert code == 200 and "completion" in show["capabilities"] and show["template"]
+    assert any(k.endswith(".context_length") and v == 512 for k, v in show["model_info"].items())
+    assert call(server, "/api/show", {"model": "other"})[0] == 404
