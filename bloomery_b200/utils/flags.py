@@ -51,15 +51,15 @@ FLAGS: List[Flag] = [
     Flag(("--jinja",), "jinja", "bool", True),
     Flag(("-a", "--alias"), "alias", env="LLAMA_ARG_ALIAS"),
     Flag(("--api-key",), "api_key", env="LLAMA_API_KEY"),
-    Flag(("--api-key-file",), "api_key_file"),
-    Flag(("--slot-save-path",), "slot_save_path"),
+    Flag(("--api-key-file",), "api_key_file", env="LLAMA_ARG_API_KEY_FILE"),
+    Flag(("--slot-save-path",), "slot_save_path", env="LLAMA_ARG_SLOT_SAVE_PATH"),
     Flag(("--config",), "config"),
     Flag(("--plan",), "plan", "bool", False), Flag(("--levers",), "levers", "bool", False),
     Flag(("--list-devices",), "list_devices", "bool", False), Flag(("--recommend",), "recommend", "bool", False),
     Flag(("--dry-run",), "dry_run", "bool", False), Flag(("--json",), "json", "bool", False),
     Flag(("--version",), "version", "bool", False), Flag(("--records-schema",), "records_schema", "bool", False),
     Flag(("--autotune",), "autotune", default="on"), Flag(("--prefill",), "prefill", default="batch"),
-    Flag(("--mmproj",), "mmproj"), Flag(("--no-mmproj",), "no_mmproj", "bool", False),
+    Flag(("-mm", "--mmproj"), "mmproj", env="LLAMA_ARG_MMPROJ"), Flag(("--no-mmproj",), "no_mmproj", "bool", False),
     Flag(("-n", "--n-predict", "--predict"), "n_predict", "int", -1, env="LLAMA_ARG_N_PREDICT"),
     Flag(("--temp",), "temp", "float", 0.8), Flag(("--top-k",), "top_k", "int", 40), Flag(("--top-p",), "top_p", "float", 0.95),
     Flag(("--min-p",), "min_p", "float", 0.05), Flag(("--repeat-penalty",), "repeat_penalty", "float", 1.0),
@@ -77,9 +77,10 @@ FLAGS: List[Flag] = [
     Flag(("-ngl", "--gpu-layers", "--n-gpu-layers"), "ngl", "str", "all", env="LLAMA_ARG_N_GPU_LAYERS"),
     Flag(("-cmoe", "--cpu-moe"), "cpu_moe", "bool", False, env="LLAMA_ARG_CPU_MOE"),
     Flag(("-ncmoe", "--n-cpu-moe"), "n_cpu_moe", "int", 0, env="LLAMA_ARG_N_CPU_MOE"),
-    Flag(("-ot", "--override-tensor"), "override_tensor"),
-    Flag(("-fit", "--fit"), "fit", default="off"), Flag(("-fitt", "--fit-target"), "fit_target"),
-    Flag(("-fitc", "--fit-ctx"), "fit_ctx", "int", 4096), Flag(("-devd", "--device-draft"), "dev_draft"),
+    Flag(("-ot", "--override-tensor"), "override_tensor", env="LLAMA_ARG_OVERRIDE_TENSOR"),
+    Flag(("-fit", "--fit"), "fit", default="off", env="LLAMA_ARG_FIT"),
+    Flag(("-fitt", "--fit-target"), "fit_target", env="LLAMA_ARG_FIT_TARGET"),
+    Flag(("-fitc", "--fit-ctx"), "fit_ctx", "int", 4096, env="LLAMA_ARG_FIT_CTX"), Flag(("-devd", "--device-draft"), "dev_draft"),
     Flag(("--place",), "place", default=""),
 ]
 _BY_NAME = {n: f for f in FLAGS for n in f.names}
@@ -189,18 +190,69 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
     notes: List[str] = []
     if cli.get("config"):
         cfg = _read_config(cli["config"], cli, notes)
+    if "api_key" in cli and not [k for k in str(cli["api_key"]).split(",") if k]:
+        raise Refusal(Code.USAGE, "--api-key names no key")
     out: Dict[str, Any] = {}
+    from_env: Dict[str, str] = {}
+    set_above = set(cli) | set(cfg)
+    if "model" not in set_above and "hf" not in set_above and env.get("LLAMA_ARG_MODEL") and env.get("LLAMA_ARG_HF_REPO"):
+        raise Refusal(Code.USAGE, "the model is named twice: LLAMA_ARG_MODEL beside LLAMA_ARG_HF_REPO")
+    # --place replaces the variables that name cards; a model named above replaces both of the model's variables
+    displaced = {d: "--place" for d in _CARD_DESTS} if cli.get("place") or cfg.get("place") else {}
+    if "model" in set_above or "hf" in set_above:
+        displaced.update({"model": "the model named above", "hf": "the model named above"})
     for f in FLAGS:
         if f.dest in cli:
             out[f.dest] = cli[f.dest]
         elif f.dest in cfg:
             out[f.dest] = cfg[f.dest]
-        elif f.env and f.env in env:
-            out[f.dest] = _conv(f, env[f.env])
+        elif f.env and f.env in env and f.dest not in displaced:
+            out[f.dest] = _env_value(f, env[f.env])
+            from_env[f.dest] = f.env
         elif f.dest not in out:
             out[f.dest] = f.default
+        if f.env and f.env in env and f.dest not in from_env and f.dest != "api_key":
+            by = displaced.get(f.dest) or ("the command line" if f.dest in cli else "the settings file")
+            notes.append(f"{f.env}: replaced by {by}")
+    # keys add: the variable's keys count beside the command line's (no line prints one)
+    if "LLAMA_API_KEY" in env:
+        more = [k for k in env["LLAMA_API_KEY"].split(",") if k]
+        if not more:
+            raise Refusal(Code.USAGE, "LLAMA_API_KEY names no key")
+        if "api_key" not in from_env:
+            out["api_key"] = ",".join([k for k in str(out["api_key"]).split(",") if k] + more)
+            notes.append(f"LLAMA_API_KEY: {len(more)} key(s) added to the command line's")
+    known = {f.env for f in FLAGS if f.env}
+    for name in sorted(env):
+        if name.startswith("LLAMA_ARG_") and name not in known:
+            notes.append(f"{name} is set: not a variable this server reads")
     out["_config_notes"] = notes
+    out["_from_env"] = from_env
     return out
+
+
+_CARD_DESTS = ("dev", "split_mode", "tensor_split", "main_gpu")
+_SWITCH_ON, _SWITCH_OFF = ("on", "enabled", "true", "1"), ("off", "disabled", "false", "0")
+
+
+def _env_value(f: Flag, raw: str):
+    """A variable's value as its flag's: a refusal names the variable, and a switch takes llama-server's eight words only."""
+    if f.kind == "bool":
+        word = raw.strip().lower()
+        if word in _SWITCH_ON:
+            return True
+        if word in _SWITCH_OFF:
+            return False
+        raise Refusal(Code.USAGE, f"{f.env}={raw!r}: a switch takes {', '.join(_SWITCH_ON)} or {', '.join(_SWITCH_OFF)}")
+    try:
+        return _conv(f, raw)
+    except Refusal as exc:
+        raise Refusal(exc.code, f"{f.env}: {exc}") from None
+
+
+def _named(opts: Dict[str, Any], dest: str, flag: str) -> str:
+    """The name a refusal gives a setting: its variable when the variable set it, else the flag."""
+    return (opts.get("_from_env") or {}).get(dest) or flag
 
 
 @dataclasses.dataclass
@@ -227,7 +279,7 @@ class Placement:
         return base
 
 
-def _devices(spec: Optional[str], n_visible: int) -> List[int]:
+def _devices(spec: Optional[str], n_visible: int, name: str = "-dev") -> List[int]:
     if spec is None or spec == "":
         return list(range(min(1, n_visible))) if n_visible else []
     if spec.lower() == "none":
@@ -236,29 +288,29 @@ def _devices(spec: Optional[str], n_visible: int) -> List[int]:
     for part in spec.split(","):
         m = re.fullmatch(r"(?i)(?:cuda)?(\d+)", part.strip())
         if not m:
-            raise Refusal(Code.USAGE, f"-dev {spec!r}: {part!r} is not CUDA<n>")
+            raise Refusal(Code.USAGE, f"{name} {spec!r}: {part!r} is not CUDA<n>")
         d = int(m.group(1))
         if d >= n_visible:
-            raise Refusal(Code.NO_DEVICE, f"-dev names CUDA{d} but {n_visible} device(s) are visible")
+            raise Refusal(Code.NO_DEVICE, f"{name} names CUDA{d} but {n_visible} device(s) are visible")
         out.append(d)
     if len(set(out)) != len(out):
-        raise Refusal(Code.USAGE, f"-dev {spec!r} names a device twice")
+        raise Refusal(Code.USAGE, f"{name} {spec!r} names a device twice")
     return out
 
 
 def placement(opts: Dict[str, Any], n_visible: int, n_layer: int = 0) -> Placement:
     sm = (opts.get("split_mode") or "layer").lower()
     if sm in ("row", "tensor"):
-        raise Refusal(Code.USAGE, f"-sm {sm} is not served: layers are never split row-wise; use --place tp")
+        raise Refusal(Code.USAGE, f"{_named(opts, 'split_mode', '-sm')} {sm} is not served: layers are never split row-wise; use --place tp")
     if sm not in ("none", "layer"):
-        raise Refusal(Code.USAGE, f"-sm {sm!r}: expected none or layer")
+        raise Refusal(Code.USAGE, f"{_named(opts, 'split_mode', '-sm')} {sm!r}: expected none or layer")
     ngl = str(opts.get("ngl", "all")).lower()
     if ngl not in ("all", "auto", "-1", "999") and not (ngl.isdigit() and (n_layer == 0 or int(ngl) >= n_layer)):
         if ngl == "0":
             devs: List[int] = []
         else:
-            raise Refusal(Code.USAGE, f"-ngl {ngl}: only a full offload (or 0) is served; trunk layers are not split")
-    devs = [] if ngl == "0" else _devices(opts.get("dev"), n_visible)
+            raise Refusal(Code.USAGE, f"{_named(opts, 'ngl', '-ngl')} {ngl}: only a full offload (or 0) is served; trunk layers are not split")
+    devs = [] if ngl == "0" else _devices(opts.get("dev"), n_visible, _named(opts, "dev", "-dev"))
     from . import levers
     tp = int(levers.get("BLOOMERY_TP"))
     if tp > 0 and devs and not opts.get("dev"):
@@ -287,9 +339,9 @@ def placement(opts: Dict[str, Any], n_visible: int, n_layer: int = 0) -> Placeme
         try:
             shares = [float(x) for x in re.split(r"[,/]", ts)]
         except ValueError:
-            raise Refusal(Code.USAGE, f"-ts {ts!r}: expected numbers separated by commas") from None
+            raise Refusal(Code.USAGE, f"{_named(opts, 'tensor_split', '-ts')} {ts!r}: expected numbers separated by commas") from None
         if len(shares) != len(pl.devices) or min(shares) < 0 or sum(shares) <= 0:
-            raise Refusal(Code.USAGE, f"-ts {ts!r}: need one non-negative share per device ({len(pl.devices)})")
+            raise Refusal(Code.USAGE, f"{_named(opts, 'tensor_split', '-ts')} {ts!r}: need one non-negative share per device ({len(pl.devices)})")
         tot = sum(shares)
         pl.expert_shares = [s / tot for s in shares]
     if opts.get("cpu_moe"):
@@ -300,19 +352,19 @@ def placement(opts: Dict[str, Any], n_visible: int, n_layer: int = 0) -> Placeme
     if ot:
         pat, eq, where = ot.rpartition("=")
         if not eq or where.upper() != "CPU":
-            raise Refusal(Code.USAGE, f"-ot {ot!r}: only <expert tensor pattern>=CPU is served")
+            raise Refusal(Code.USAGE, f"{_named(opts, 'override_tensor', '-ot')} {ot!r}: only <expert tensor pattern>=CPU is served")
         if "exps" not in pat and "expert" not in pat:
-            raise Refusal(Code.USAGE, f"-ot {ot!r}: only routed-expert tensors may stay on the host")
+            raise Refusal(Code.USAGE, f"{_named(opts, 'override_tensor', '-ot')} {ot!r}: only routed-expert tensors may stay on the host")
         pl.host_experts, pl.host_pattern = "pattern", pat
     fit = str(opts.get("fit") or "off").lower()
     if fit not in ("on", "off"):
-        raise Refusal(Code.USAGE, f"-fit {fit!r}: expected on or off")
+        raise Refusal(Code.USAGE, f"{_named(opts, 'fit', '-fit')} {fit!r}: expected on or off")
     pl.fit = fit == "on"
     if opts.get("fit_target"):
         try:
             pl.fit_targets_mib = [int(x) for x in str(opts["fit_target"]).split(",")]
         except ValueError:
-            raise Refusal(Code.USAGE, f"-fitt {opts['fit_target']!r}: expected MiB[,MiB...]") from None
+            raise Refusal(Code.USAGE, f"{_named(opts, 'fit_target', '-fitt')} {opts['fit_target']!r}: expected MiB[,MiB...]") from None
     pl.fit_ctx = int(opts.get("fit_ctx") or 4096)
     if opts.get("dev_draft"):
         pl.draft_device = _devices(opts["dev_draft"], n_visible)[0]

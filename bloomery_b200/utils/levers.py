@@ -93,9 +93,28 @@ def at_main(environ=None) -> Dict[str, Any]:
         if spec.choices and val not in spec.choices:
             raise Refusal(Code.LEVER, f"{k}={v!r}: expected one of {', '.join(spec.choices)}")
         vals[k] = val
+    launch_queues(env)
     _values.clear()
     _values.update(vals)
     return vals
+
+
+LAUNCH_QUEUES = ("0.25x", "0.5x", "2x", "4x")
+
+
+def launch_queues(env) -> str:
+    """The CUDA driver's ``CUDA_SCALE_LAUNCH_QUEUES``: unset it becomes ``2x`` (a deeper launch queue per stream, so the
+    host thread of a prompt batch's many launches does not wait on it); NVIDIA's other values are kept; anything else
+    stops the start with a message, where the driver would ignore it.  Must run before the first CUDA call of the
+    process (the driver reads the variable when it initialises)."""
+    name = "CUDA_SCALE_LAUNCH_QUEUES"
+    v = env.get(name)
+    if v is None:
+        env[name] = "2x"
+        return "2x"
+    if v not in LAUNCH_QUEUES:
+        raise Refusal(Code.LEVER, f"{name}={v!r}: the driver takes {', '.join(LAUNCH_QUEUES)}")
+    return v
 
 
 def get(name: str):

@@ -670,3 +670,57 @@ def test_reasoning_rules():
     done = RS.ThinkSpan(started=True, budget=5)
     done.note("x</think>", 1)
     assert not done.inside("x</think> answer") and not done.force_close("x</think> answer")
+
+
+def test_llama_server_variables():
+    """A variable is its flag with that value; the command line wins and a line says so; keys add; a switch takes eight
+    words; a variable nobody reads gets a line; a refusal names the variable."""
+    from bloomery_b200.utils import flags, levers
+    from bloomery_b200.utils.exit_codes import Refusal
+    o = flags.parse(["-c", "4096"], {"LLAMA_ARG_CTX_SIZE": "8192", "LLAMA_ARG_UBATCH": "512", "LLAMA_ARG_FLASH_ATTN": "1",
+                                     "LLAMA_ARG_FIT": "on", "LLAMA_ARG_CPU_MOE": "enabled"})
+    assert o["ctx"] == 4096 and o["ubatch"] == 512 and o["fit"] == "on" and o["cpu_moe"] is True
+    notes = "\n".join(o["_config_notes"])
+    assert "LLAMA_ARG_CTX_SIZE: replaced by the command line" in notes
+    assert "LLAMA_ARG_FLASH_ATTN is set: not a variable this server reads" in notes
+    assert o["_from_env"]["ubatch"] == "LLAMA_ARG_UBATCH"
+    assert flags.parse([], {"LLAMA_ARG_CPU_MOE": "disabled"})["cpu_moe"] is False
+    with pytest.raises(Refusal, match="LLAMA_ARG_CPU_MOE"):
+        flags.parse([], {"LLAMA_ARG_CPU_MOE": "maybe"})
+    with pytest.raises(Refusal, match="LLAMA_ARG_CTX_SIZE"):
+        flags.parse([], {"LLAMA_ARG_CTX_SIZE": "lots"})
+    # keys add, an empty one ends the start, and no note prints a key
+    o = flags.parse(["--api-key", "k1"], {"LLAMA_API_KEY": "k2,k3"})
+    assert o["api_key"] == "k1,k2,k3" and not any("k2" in n for n in o["_config_notes"])
+    assert flags.parse([], {"LLAMA_API_KEY": "k9"})["api_key"] == "k9"
+    with pytest.raises(Refusal, match="LLAMA_API_KEY names no key"):
+        flags.parse([], {"LLAMA_API_KEY": ""})
+    with pytest.raises(Refusal, match="--api-key names no key"):
+        flags.parse(["--api-key", ""], {})
+    # the model: both variables set is refused; a model on the command line replaces both
+    with pytest.raises(Refusal, match="LLAMA_ARG_MODEL beside LLAMA_ARG_HF_REPO"):
+        flags.parse([], {"LLAMA_ARG_MODEL": "a.gguf", "LLAMA_ARG_HF_REPO": "x/y"})
+    o = flags.parse(["-m", "b.gguf"], {"LLAMA_ARG_MODEL": "a.gguf", "LLAMA_ARG_HF_REPO": "x/y"})
+    assert o["model"] == "b.gguf" and o["hf"] is None
+    # --place replaces the variables that name cards
+    o = flags.parse(["--place", "tp"], {"LLAMA_ARG_DEVICE": "CUDA3", "LLAMA_ARG_SPLIT_MODE": "row", "LLAMA_ARG_MAIN_GPU": "2"})
+    assert o["dev"] is None and o["split_mode"] == "layer" and o["main_gpu"] == 0
+    assert "LLAMA_ARG_SPLIT_MODE: replaced by --place" in "\n".join(o["_config_notes"])
+    # a variable whose flag would be refused ends the start under the variable's name
+    o = flags.parse([], {"LLAMA_ARG_SPLIT_MODE": "row"})
+    with pytest.raises(Refusal, match="LLAMA_ARG_SPLIT_MODE row is not served"):
+        flags.placement(o, 2)
+    with pytest.raises(Refusal, match="-sm row is not served"):
+        flags.placement(flags.parse(["-sm", "row"], {}), 2)
+    with pytest.raises(Refusal, match="LLAMA_ARG_DEVICE names CUDA5"):
+        flags.placement(flags.parse([], {"LLAMA_ARG_DEVICE": "CUDA5"}), 2)
+    # the driver's launch-queue variable: unset becomes 2x, NVIDIA's other values stay, anything else stops the start
+    env = {}
+    levers.at_main(env)
+    assert env["CUDA_SCALE_LAUNCH_QUEUES"] == "2x"
+    env = {"CUDA_SCALE_LAUNCH_QUEUES": "4x"}
+    levers.at_main(env)
+    assert env["CUDA_SCALE_LAUNCH_QUEUES"] == "4x"
+    with pytest.raises(Refusal, match="CUDA_SCALE_LAUNCH_QUEUES"):
+        levers.at_main({"CUDA_SCALE_LAUNCH_QUEUES": "8x"})
+    levers.at_main({})
