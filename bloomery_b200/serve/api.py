@@ -99,7 +99,8 @@ class State:
         from .admit import parse_key_line
         keys, limits = [], {}
         if args.get("api_key"):
-            keys += [k for k in str(args["api_key"]).split(",") if k]
+            from ..utils.flags import split_keys
+            keys += split_keys(str(args["api_key"]))
         if args.get("api_key_file"):
             with open(args["api_key_file"]) as fh:
                 for ln in fh:
@@ -165,6 +166,34 @@ def sampling_from(body: Dict[str, Any], defaults: Dict[str, Any]) -> SamplingPar
 _OFF_VALUES = {"typical_p": (1, 1.0), "top_n_sigma": (-1, -1.0, 0, 0.0), "dry_multiplier": (0, 0.0), "xtc_probability": (0, 0.0),
                "dynatemp_range": (0, 0.0), "mirostat": (0,), "mirostat_tau": None, "mirostat_eta": None, "dry_base": None,
                "dry_allowed_length": None, "dry_penalty_last_n": None, "xtc_threshold": None, "dynatemp_exponent": None}
+
+
+def logit_bias_from(body: Dict[str, Any], n_vocab: int = 0) -> Dict[int, float]:
+    """OpenAI's ``logit_bias``: an object from token ids to a number in -100 to 100.  The other forms clients send (an
+    array of pairs, ``false`` for "never", a token's text as the key) are refused by name rather than half-read, and so
+    are a value out of range and an id named twice (``"7"`` beside ``"07"``)."""
+    raw = body.get("logit_bias")
+    if raw is None:
+        return {}
+    def bad(why: str):
+        return ApiError(400, f"logit_bias: {why}", param="logit_bias")
+    if not isinstance(raw, dict):
+        raise bad("takes an object from token ids to numbers; an array of pairs is not read")
+    out: Dict[int, float] = {}
+    for k, v in raw.items():
+        if not isinstance(k, str) or not k.strip().lstrip("+").isdigit():
+            raise bad(f"the key {k!r} is not a token id (a token's text is not read)")
+        t = int(k)
+        if n_vocab and t >= n_vocab:
+            raise bad(f"the id {t} is outside the vocabulary of {n_vocab}")
+        if isinstance(v, bool) or not isinstance(v, (int, float)) or v != v:
+            raise bad(f"the value of {k!r} is not a number (false is not read; -100 bans an id)")
+        if not -100 <= v <= 100:
+            raise bad(f"the value of {k!r} is outside -100 to 100")
+        if t in out:
+            raise bad(f"the id {t} is named twice")
+        out[t] = float(v)
+    return out
 
 
 def check_fields(body: Dict[str, Any], allow_n: bool = False) -> None:
@@ -407,7 +436,7 @@ class Handler(BaseHTTPRequestHandler):
                 return self._completion(body, "oai")
             if path in ("/v1/chat/completions", "/chat/completions"):
                 return self._chat(body)
-            if path in ("/v1/chat/completions/input_tokens", "/v1/messages/count_tokens", "/v1/responses/input_tokens"):
+            if path in ("/v1/chat/completions/input_tokens", "/chat/completions/input_tokens", "/v1/messages/count_tokens", "/v1/responses/input_tokens"):
                 msgs = self._anthropic_messages(body) if "messages" in path and "/v1/messages" in path else body.get("messages") or self._responses_messages(body)
                 ids = self._chat_ids(msgs, body.get("tools"))
                 return self._send(200, {"input_tokens": len(ids)})
@@ -672,12 +701,7 @@ class Handler(BaseHTTPRequestHandler):
                 break
         if n_predict < 0 and st.args.get("n_predict", -1) >= 0:
             n_predict = int(st.args["n_predict"])
-        lb: Dict[int, float] = {}
-        raw_lb = body.get("logit_bias")
-        if isinstance(raw_lb, dict):
-            lb = {int(k): (False if v is False else float(v)) for k, v in raw_lb.items()}
-        elif isinstance(raw_lb, list):
-            lb = {int(p[0]): (False if p[1] is False else float(p[1])) for p in raw_lb if isinstance(p, list) and len(p) == 2}
+        lb = logit_bias_from(body, int(getattr(st.engine, "n_vocab", 0) or 0))
         n_probs = int(body.get("n_probs") or 0)
         if body.get("logprobs") is True:
             n_probs = max(n_probs, int(body.get("top_logprobs") or 1))

@@ -282,7 +282,7 @@ class Worker(threading.Thread):
             row = row.copy()
             for t, b in req.logit_bias.items():
                 if 0 <= t < row.size:
-                    row[t] = -np.inf if b is False or b == float("-inf") else row[t] + b
+                    row[t] = row[t] + b
             if req.ignore_eos:
                 for t in (self.engine.tokenizer.eos_id, self.engine.tokenizer.eot_id):
                     if t >= 0:
@@ -293,6 +293,7 @@ class Worker(threading.Thread):
         else:
             tok = a.sampler.sample(row, recent)
         if req.n_probs > 0:
+            row = logits                        # the probabilities reported are the model's own row, before any bias
             top = np.argpartition(-row, min(req.n_probs, row.size - 1))[:req.n_probs]
             top = top[np.argsort(-row[top], kind="stable")]
             mx = float(np.max(row))

@@ -190,7 +190,7 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
     notes: List[str] = []
     if cli.get("config"):
         cfg = _read_config(cli["config"], cli, notes)
-    if "api_key" in cli and not [k for k in str(cli["api_key"]).split(",") if k]:
+    if "api_key" in cli and not split_keys(str(cli["api_key"])):
         raise Refusal(Code.USAGE, "--api-key names no key")
     out: Dict[str, Any] = {}
     from_env: Dict[str, str] = {}
@@ -216,11 +216,11 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
             notes.append(f"{f.env}: replaced by {by}")
     # keys add: the variable's keys count beside the command line's (no line prints one)
     if "LLAMA_API_KEY" in env:
-        more = [k for k in env["LLAMA_API_KEY"].split(",") if k]
+        more = split_keys(env["LLAMA_API_KEY"])
         if not more:
             raise Refusal(Code.USAGE, "LLAMA_API_KEY names no key")
         if "api_key" not in from_env:
-            out["api_key"] = ",".join([k for k in str(out["api_key"]).split(",") if k] + more)
+            out["api_key"] = join_keys(split_keys(str(out["api_key"] or "")) + more)
             notes.append(f"LLAMA_API_KEY: {len(more)} key(s) added to the command line's")
     known = {f.env for f in FLAGS if f.env}
     for name in sorted(env):
@@ -229,6 +229,17 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
     out["_config_notes"] = notes
     out["_from_env"] = from_env
     return out
+
+
+def split_keys(text: str) -> List[str]:
+    """The keys of a comma-separated list; an item in double quotes may hold commas (a doubled quote inside is one)."""
+    import csv
+    rows = list(csv.reader([text], skipinitialspace=True)) if text else []
+    return [k for k in (rows[0] if rows else []) if k]
+
+
+def join_keys(keys: List[str]) -> str:
+    return ",".join('"' + k.replace('"', '""') + '"' if ("," in k or '"' in k) else k for k in keys)
 
 
 _CARD_DESTS = ("dev", "split_mode", "tensor_split", "main_gpu")

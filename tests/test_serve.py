@@ -524,6 +524,26 @@ def test_route_details_param_415_prompt_ids_and_refusals(server):
     assert code == 404 and "POST /no/such/route" in r["error"]["message"]
 
 
+def test_logit_bias_forms_and_unbiased_logprobs(server):
+    # only OpenAI's object is read: the other forms are refused by name
+    for lb in ([[98, 5.0]], False, {"abc": 1}, {"98": 101}, {"98": False}, {"7": 1, "07": 2}, {"999999": 1}):
+        code, r = call(server, "/completion", {"prompt": "ab", "n_predict": 2, "logit_bias": lb})
+        assert code == 400 and r["error"]["param"] == "logit_bias", lb
+    # the bias moves the pick; the probabilities reported stay the model's own
+    base = call(server, "/completion", {"prompt": "abcabc", "temperature": 0, "n_predict": 1, "n_probs": 3})[1]
+    first = base["completion_probabilities"][0]
+    other = first["top_logprobs"][1]
+    code, r = call(server, "/completion", {"prompt": "abcabc", "temperature": 0, "n_predict": 1, "n_probs": 3,
+                                           "logit_bias": {str(first["id"]): -100, str(other["id"]): 100}})
+    assert code == 200
+    got = r["completion_probabilities"][0]
+    assert got["id"] == other["id"]
+    assert abs(got["logprob"] - other["logprob"]) < 1e-4
+    assert [t["id"] for t in got["top_logprobs"]] == [t["id"] for t in first["top_logprobs"]]
+    code, r = call(server, "/chat/completions/input_tokens", {"messages": [{"role": "user", "content": "hi"}]})
+    assert code == 200 and r["input_tokens"] > 0
+
+
 def test_background_responses_poll_cancel_and_refusals():
     s = Server(flags.parse(["--port", "0", "--mock"]))
     s.start()

@@ -693,6 +693,8 @@ def test_llama_server_variables():
     o = flags.parse(["--api-key", "k1"], {"LLAMA_API_KEY": "k2,k3"})
     assert o["api_key"] == "k1,k2,k3" and not any("k2" in n for n in o["_config_notes"])
     assert flags.parse([], {"LLAMA_API_KEY": "k9"})["api_key"] == "k9"
+    o = flags.parse(["--api-key", '"a,b",c'], {"LLAMA_API_KEY": "d"})
+    assert flags.split_keys(o["api_key"]) == ["a,b", "c", "d"]
     with pytest.raises(Refusal, match="LLAMA_API_KEY names no key"):
         flags.parse([], {"LLAMA_API_KEY": ""})
     with pytest.raises(Refusal, match="--api-key names no key"):
