@@ -238,6 +238,14 @@ def constraint_from(body):
     """The structured-output constraint of a request: a segment program walked token by token when the schema compiles
     to one (``serve/constrain.py``), else the JSON prefix validator."""
     from .constrain import constraint_for
+    asked = (body.get("response_format") or {}).get("type") in ("json_schema", "json_object") or bool(body.get("json_schema"))
+    if asked:
+        # a document that must close cannot also be told never to end, nor share the reply with a budgeted think span
+        if body.get("ignore_eos"):
+            raise ApiError(400, "ignore_eos beside structured output: the document ends the reply", param="ignore_eos")
+        if body.get("reasoning_budget") not in (None, -1):
+            raise ApiError(400, "reasoning_budget beside structured output: the think span is closed at once there",
+                           param="reasoning_budget")
 
     def pick(schema):
         return constraint_for(schema) or C.JsonConstraint(schema)
@@ -864,14 +872,48 @@ class Handler(BaseHTTPRequestHandler):
         tail = self.state.engine.tokenizer.decode(list(ids[-16:]), skip_special=False)
         return tail.rstrip().endswith("<think>")
 
+    @staticmethod
+    def _forced_name(choice) -> Optional[str]:
+        """``"required"`` or the function a ``tool_choice`` names, in OpenAI's, the Responses API's or Anthropic's shape;
+        None when the choice forces nothing."""
+        if choice in (None, "auto", "none"):
+            return None
+        if choice == "required":
+            return "required"
+        if isinstance(choice, dict):
+            t = choice.get("type")
+            if t in ("auto", "none"):
+                return None
+            if t == "any":
+                return "required"
+            name = (choice.get("function") or {}).get("name") if isinstance(choice.get("function"), dict) else choice.get("name")
+            if t in ("function", "tool") and isinstance(name, str) and name:
+                return name
+        raise ApiError(400, f"tool_choice {choice!r} is not supported", param="tool_choice")
+
+    def _force_call(self, reqs: List[Request], body, tools, ids: List[int]) -> None:
+        """Hold each of ``reqs`` to one tool call when the request's ``tool_choice`` forces one: the call is written in
+        the framing the template renders calls in, its arguments follow the tool's schema, and a think span the template
+        opened stays free until the model closes it."""
+        forced = self._forced_name(body.get("tool_choice"))
+        if forced is None:
+            return
+        from .constrain import ForcedCall, Unsupported, forced_call_program
+        rf = body.get("response_format") or {}
+        if rf.get("type") in ("json_schema", "json_object") or body.get("json_schema"):
+            raise ApiError(400, "a JSON response_format beside a forced tool_choice: the reply is the call", param="response_format")
+        try:
+            program = forced_call_program(tools, forced, self.state.tool_format)
+        except Unsupported as exc:
+            raise ApiError(400, f"tool_choice: {exc}", param="tool_choice") from None
+        open_think = self._template_opened_think(ids)
+        for r_ in reqs:
+            r_.constraint = ForcedCall(program, think_open=open_think)
+
     def _chat(self, body) -> None:
         st = self.state
         tools = body.get("tools")
-        if body.get("tool_choice") not in (None, "auto", "none"):
-            if body.get("tool_choice") == "required":
-                pass
-            elif not isinstance(body.get("tool_choice"), dict):
-                raise ApiError(400, f"tool_choice {body.get('tool_choice')!r} is not supported")
+        self._forced_name(body.get("tool_choice"))
         from . import reasoning as RS
         try:
             kwargs = RS.effort_kwargs(body.get("reasoning_effort"), body.get("chat_template_kwargs"))
@@ -882,6 +924,7 @@ class Handler(BaseHTTPRequestHandler):
         req = many[0]
         for r_ in many:
             r_.think_started = self._template_opened_think(ids)
+        self._force_call(many, body, tools, ids)
         rid = f"chatcmpl-{uuid.uuid4().hex[:24]}"
         finish = {"eos": "stop", "word": "stop", "limit": "length", "cancelled": "stop", "reasoning_loop": "reasoning_loop"}
         want_reasoning = body.get("reasoning_format", "auto") != "none"
@@ -995,6 +1038,7 @@ class Handler(BaseHTTPRequestHandler):
         b2 = dict(body)
         b2["stop"] = body.get("stop_sequences")
         req = self._make_request(b2, ids)
+        self._force_call([req], body, tools, ids)
         mid = f"msg_{uuid.uuid4().hex[:24]}"
         reason = {"eos": "end_turn", "word": "stop_sequence", "limit": "max_tokens", "cancelled": "end_turn",
                   "reasoning_loop": "reasoning_loop"}
@@ -1094,6 +1138,7 @@ class Handler(BaseHTTPRequestHandler):
         if background and (body.get("store") is False or body.get("stream")):
             raise ApiError(400, "field 'background' beside store: false or stream: true is not served")
         req = self._make_request(b2, ids)
+        self._force_call([req], b2, tools, ids)
         rid = f"resp_{uuid.uuid4().hex[:24]}"
 
         def build(d):

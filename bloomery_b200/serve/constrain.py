@@ -155,7 +155,7 @@ Head = Tuple[Tuple[tuple, ...], int, Any]      # (segments, index, state inside 
 
 
 def _start(seg: tuple) -> Any:
-    return {"lit": 0, "str": (0, 0), "num": ""}.get(seg[0])
+    return {"lit": 0, "str": (0, 0), "num": "", "raw": 0}.get(seg[0])
 
 
 def _closure(heads) -> Set[Head]:
@@ -212,6 +212,14 @@ def _feed(head: Head, ch: str) -> Set[Head]:
         if ord(ch) < 0x20 or (s[1] is not None and n + 1 > s[1]):
             return set()
         return {(segs, i, (1, n + 1))}
+    if s[0] == "raw":
+        # one line of bare text inside a call's markup: no line break and no "<" (which could open or close a tag)
+        if ch not in "\n\r<" and ord(ch) >= 0x20:
+            return {(segs, i, 1)}
+        out_raw: Set[Head] = set()
+        for h in _next(segs, i):
+            out_raw |= _feed(h, ch)
+        return out_raw
     if s[0] == "num":
         full, prefix = (_INT_FULL, _INT_PREFIX) if s[1] else (_NUM_FULL, _NUM_PREFIX)
         cand = st + ch
@@ -310,6 +318,118 @@ class ProgramConstraint:
 
     def forced_text(self, text: str) -> str:
         return self._at(text).forced_text()
+
+
+FRAMINGS = ("hermes", "qwenxml")
+
+
+def _tool_fn(tool: Any) -> Tuple[str, dict]:
+    fn = tool.get("function", tool) if isinstance(tool, dict) else None
+    if not isinstance(fn, dict) or not isinstance(fn.get("name"), str) or not fn["name"]:
+        raise Unsupported("a tool needs a function with a name")
+    params = fn.get("parameters")
+    if params is None or params == {}:
+        params = {"type": "object", "properties": {}}
+    return fn["name"], params
+
+
+def _call_segments(name: str, params: dict, framing: str) -> Tuple[tuple, ...]:
+    """One call of ``name`` in the template's framing, its arguments held to ``params``."""
+    if not isinstance(params, dict) or "anyOf" in params or "oneOf" in params or "$ref" in params:
+        raise Unsupported(f"the forced tool {name!r} has parameters with a root anyOf or $ref")
+    if params.get("type") != "object":
+        raise Unsupported(f"the forced tool {name!r} has parameters that are not an object")
+    if "<" in name or "\n" in name:
+        raise Unsupported(f"the tool name {name!r} cannot be written inside a call's markup")
+    if framing == "hermes":
+        head = '<tool_call>\n{"name": ' + json.dumps(name, ensure_ascii=False) + ', "arguments": '
+        return _merge([("lit", head)] + list(compile_schema(params)) + [("lit", "}\n</tool_call>")])
+    # the <function=...><parameter=...> markup: a value on lines of its own, a string bare, anything else as JSON
+    props = params.get("properties") or {}
+    req = params.get("required", [])
+    if not isinstance(props, dict) or not isinstance(req, list) or any(r not in props for r in req):
+        raise Unsupported(f"the forced tool {name!r} lists its properties and required names")
+
+    def value(schema: Any) -> List[tuple]:
+        if isinstance(schema, dict) and schema.get("type") == "string" and "enum" not in schema and "const" not in schema:
+            if any(k not in _ANNOTATIONS and k not in ("type", "maxLength") for k in schema):
+                raise Unsupported("a string keyword outside the served subset")
+            return [("raw",)]
+        if isinstance(schema, dict) and isinstance(schema.get("enum"), list) and all(isinstance(v, str) for v in schema["enum"]):
+            if any("<" in v or "\n" in v for v in schema["enum"]):
+                raise Unsupported("a raw option with a < or a line break")
+            return [("alt", tuple((("lit", v),) for v in schema["enum"]))]
+        if isinstance(schema, dict) and ("anyOf" in schema or "oneOf" in schema):
+            raise Unsupported("an anyOf in a tool argument written raw")
+        return list(compile_schema(schema, params))
+
+    def member(key: str) -> List[tuple]:
+        if "<" in key or ">" in key or "\n" in key:
+            raise Unsupported(f"the property name {key!r} cannot be written inside a call's markup")
+        return [("lit", f"<parameter={key}>\n")] + value(props[key]) + [("lit", "\n</parameter>\n")]
+    segs: List[tuple] = [("lit", f"<tool_call>\n<function={name}>\n")]
+    for key in props:
+        segs += member(key) if key in req else [("alt", (_merge(member(key)), ()))]
+    segs.append(("lit", "</function>\n</tool_call>"))
+    return _merge(segs)
+
+
+def forced_call_program(tools: Any, choice: Any, framing: str) -> Tuple[tuple, ...]:
+    """The program of a reply that must be one tool call: ``choice`` is ``"required"`` (any of ``tools``) or a function's
+    name.  Raises :class:`Unsupported` naming what cannot be forced (the caller answers 400 with it)."""
+    if framing not in FRAMINGS:
+        raise Unsupported(f"a forced call is not written in this template's framing ({framing})")
+    if not isinstance(tools, list) or not tools:
+        raise Unsupported("a forced tool_choice needs tools")
+    fns = [_tool_fn(t) for t in tools]
+    if choice != "required":
+        fns = [f for f in fns if f[0] == choice]
+        if not fns:
+            raise Unsupported(f"tool_choice names {choice!r}, which is not among the tools")
+    calls = [_call_segments(n, p, framing) for n, p in fns]
+    return calls[0] if len(calls) == 1 else (("alt", tuple(calls)),)
+
+
+class ForcedCall(ProgramConstraint):
+    """A reply held to one tool call.  While a think span the template opened is still open the model writes freely
+    (it may not end there); the call starts after the span's close, with the line breaks a model puts between them."""
+
+    def __init__(self, program: Tuple[tuple, ...], think_open: bool = False, close_tag: str = "</think>"):
+        self.schema = None
+        self.program = (("alt", ((("lit", "\n\n"),), (("lit", "\n"),), ())),) + tuple(program) if think_open else tuple(program)
+        self.think_open, self.close_tag = think_open, close_tag
+        self._text = ""
+        self._walk = Walk(self.program)
+
+    def _split(self, text: str) -> Optional[str]:
+        """The part of the output the program governs (None: still inside the think span)."""
+        if not self.think_open:
+            return text
+        at = text.find(self.close_tag)
+        return None if at < 0 else text[at + len(self.close_tag):]
+
+    def allowed(self, text: str, piece: str) -> bool:
+        own = self._split(text)
+        if own is None:
+            whole = text + piece
+            at = whole.find(self.close_tag)
+            if at < 0:
+                return True
+            rest = whole[at + len(self.close_tag):]          # the piece closes the span: what follows it starts the call
+            return not rest or Walk(self.program).accepts(rest)
+        return super().allowed(own, piece)
+
+    def done(self, text: str) -> bool:
+        own = self._split(text)
+        return own is not None and super().done(own)
+
+    def closed(self, text: str) -> bool:
+        own = self._split(text)
+        return own is not None and super().closed(own)
+
+    def forced_text(self, text: str) -> str:
+        own = self._split(text)
+        return "" if own is None else super().forced_text(own)
 
 
 def constraint_for(schema: Optional[dict]):

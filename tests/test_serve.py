@@ -179,6 +179,42 @@ def test_schema_program_forces_keys_without_sampling(server):
     assert r["content"].startswith('{"a": ') and getattr(server.state.worker, "jumped", 0) >= 3
 
 
+def test_forced_tool_choice_writes_one_call(server):
+    """``tool_choice`` ``required`` or a named function holds the reply to one call in the template's framing, on the
+    chat, Messages and Responses routes; what cannot be forced is a 400 naming the field."""
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+                 "type": "object", "properties": {"unit": {"enum": ["c", "f"]}, "days": {"type": "integer"}}, "required": ["unit", "days"]}}},
+             {"type": "function", "function": {"name": "now"}}]
+    msgs = [{"role": "user", "content": "weather for 3 days"}]
+    code, r = call(server, "/v1/chat/completions", {"messages": msgs, "tools": tools, "max_tokens": 96,
+                                                    "tool_choice": {"type": "function", "function": {"name": "get_weather"}}})
+    assert code == 200, r
+    calls = r["choices"][0]["message"]["tool_calls"]
+    assert len(calls) == 1 and calls[0]["function"]["name"] == "get_weather"
+    args = json.loads(calls[0]["function"]["arguments"])
+    assert args["unit"] in ("c", "f") and isinstance(args["days"], int)
+    assert r["choices"][0]["finish_reason"] == "tool_calls"
+    code, r = call(server, "/v1/chat/completions", {"messages": msgs, "tools": tools[1:], "max_tokens": 64, "tool_choice": "required"})
+    assert code == 200 and r["choices"][0]["message"]["tool_calls"][0]["function"]["name"] == "now"
+    # Anthropic's any / tool and the Responses API's shapes force the same way
+    atools = [{"name": "now", "input_schema": {"type": "object", "properties": {}}}]
+    code, r = call(server, "/v1/messages", {"messages": msgs, "tools": atools, "max_tokens": 64, "tool_choice": {"type": "any"}})
+    assert code == 200 and [b["name"] for b in r["content"] if b["type"] == "tool_use"] == ["now"]
+    code, r = call(server, "/v1/responses", {"input": "time?", "tools": [{"type": "function", "name": "now"}], "max_output_tokens": 64,
+                                             "tool_choice": {"type": "function", "name": "now"}, "store": False})
+    assert code == 200 and [o["name"] for o in r["output"] if o["type"] == "function_call"] == ["now"]
+    # refusals name the field
+    for body, param in (({"tool_choice": {"type": "function", "function": {"name": "absent"}}}, "tool_choice"),
+                        ({"tool_choice": "required", "response_format": {"type": "json_object"}}, "response_format"),
+                        ({"tool_choice": "sometimes"}, "tool_choice"),
+                        ({"tool_choice": "required", "tools": [{"type": "function", "function": {"name": "f", "parameters": {"anyOf": [{"type": "object"}]}}}]}, "tool_choice")):
+        code, r = call(server, "/v1/chat/completions", dict({"messages": msgs, "tools": tools}, **body))
+        assert code == 400 and r["error"]["param"] == param, (body, r)
+    for body, param in (({"ignore_eos": True}, "ignore_eos"), ({"reasoning_budget": 8}, "reasoning_budget")):
+        code, r = call(server, "/completion", dict({"prompt": "x", "response_format": {"type": "json_object"}}, **body))
+        assert code == 400 and r["error"]["param"] == param
+
+
 def test_key_file_limits_answer_429(tmp_path):
     kf = tmp_path / "keys.txt"
     kf.write_text("# keys\nslow rate=1/m burst=1\nfree\n")

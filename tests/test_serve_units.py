@@ -726,3 +726,35 @@ def test_llama_server_variables():
     with pytest.raises(Refusal, match="CUDA_SCALE_LAUNCH_QUEUES"):
         levers.at_main({"CUDA_SCALE_LAUNCH_QUEUES": "8x"})
     levers.at_main({})
+
+
+def test_forced_call_programs_both_framings_and_open_think():
+    from bloomery_b200.serve import chat as C, constrain as K
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+                 "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}}, "required": ["city"]}}},
+             {"type": "function", "function": {"name": "now"}}]
+    texts = {"hermes": '<tool_call>\n{"name": "get_weather", "arguments": {"city": "Oslo", "days": 3}}\n</tool_call>',
+             "qwenxml": "<tool_call>\n<function=get_weather>\n<parameter=city>\nOslo\n</parameter>\n<parameter=days>\n3\n</parameter>\n"
+                        "</function>\n</tool_call>"}
+    for framing, text in texts.items():
+        c = K.ForcedCall(K.forced_call_program(tools, "required", framing))
+        assert c.forced_text("").startswith("<tool_call>\n")
+        for i in range(1, len(text)):
+            assert c.allowed(text[:i], text[i]), (framing, text[:i + 1])
+        assert c.done(text) and c.closed(text) and not c.allowed(text, "x")
+        parse = C.parse_hermes if framing == "hermes" else C.parse_qwen_xml
+        assert json.loads(parse(text)[1][0]["function"]["arguments"]) == {"city": "Oslo", "days": 3}
+        # the optional member may be left out; a raw string takes no "<" and no line break
+        short = text.replace(', "days": 3', "").replace("<parameter=days>\n3\n</parameter>\n", "")
+        assert K.ForcedCall(K.forced_call_program(tools, "get_weather", framing)).done(short)
+        # a think span the template opened stays free until its close; the reply cannot end inside it
+        t = K.ForcedCall(K.forced_call_program(tools, "get_weather", framing), think_open=True)
+        assert t.allowed("so", " anything <tool_call> at all") and not t.done("so") and t.forced_text("so") == ""
+        assert t.allowed("so", "</think>") and t.allowed("so", "</think>\n\n<tool") and not t.allowed("so", "</think>hello")
+        assert t.done("so</think>\n\n" + text) and t.done("so</think>" + text)
+    raw = K.ForcedCall(K.forced_call_program(tools, "get_weather", "qwenxml"))
+    assert not raw.allowed("<tool_call>\n<function=get_weather>\n<parameter=city>\nOs", "<b")
+    for bad_tools, choice, framing in ((tools, "absent", "hermes"), (tools, "required", "glmxml"), ([], "required", "hermes"),
+                                       ([{"type": "function", "function": {"name": "f", "parameters": {"$ref": "#/x"}}}], "f", "hermes")):
+        with pytest.raises(K.Unsupported):
+            K.forced_call_program(bad_tools, choice, framing)
