@@ -35,7 +35,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from typing import Any, Dict, List, Optional, Tuple
 from urllib.parse import parse_qs, urlparse
 
-from ..utils import events
+from ..utils import events, levers
 from . import chat as C
 from .engine import Engine, EngineError
 from .promptcache import PromptCache
@@ -896,9 +896,21 @@ class Handler(BaseHTTPRequestHandler):
         the framing the template renders calls in, its arguments follow the tool's schema, and a think span the template
         opened stays free until the model closes it."""
         forced = self._forced_name(body.get("tool_choice"))
+        from .constrain import ForcedCall, Unsupported, forced_call_program, watched_calls
         if forced is None:
+            choice = body.get("tool_choice")
+            off = choice == "none" or (isinstance(choice, dict) and choice.get("type") == "none")
+            if tools and not off and str(levers.get("BLOOMERY_WATCH_CALLS")) != "off":
+                for t in tools:                                    # an invalid tool is a 400; one outside the subset is unwatched
+                    fn = t.get("function", t) if isinstance(t, dict) else None
+                    if not isinstance(fn, dict) or not isinstance(fn.get("name"), str) or not fn["name"]:
+                        raise ApiError(400, "tools: each tool needs a function with a name", param="tools")
+                    if fn.get("parameters") is not None and not isinstance(fn["parameters"], dict):
+                        raise ApiError(400, f"tools: the parameters of {fn['name']!r} are not a schema object", param="tools")
+                for r_ in reqs:
+                    if r_.constraint is None:
+                        r_.constraint = watched_calls(tools, self.state.tool_format)
             return
-        from .constrain import ForcedCall, Unsupported, forced_call_program
         rf = body.get("response_format") or {}
         if rf.get("type") in ("json_schema", "json_object") or body.get("json_schema"):
             raise ApiError(400, "a JSON response_format beside a forced tool_choice: the reply is the call", param="response_format")

@@ -432,6 +432,78 @@ class ForcedCall(ProgramConstraint):
         return "" if own is None else super().forced_text(own)
 
 
+class WatchedCall:
+    """A free reply whose tool calls are watched: text is unconstrained until the model writes its framing's call opener;
+    from there the call follows the program a forced call compiles, until it closes, and the reply is free again.  The
+    reply may end anywhere outside a call and nowhere inside one."""
+
+    OPENER = "<tool_call>"
+
+    def __init__(self, program: Tuple[tuple, ...]):
+        self.program = tuple(program)
+        self._text = ""
+        self._state: Tuple[str, Optional[Walk]] = ("", None)          # (tail of the free text, walk of the open call)
+
+    def _step(self, state, chunk: str):
+        tail, walk = state
+        for ch in chunk:
+            if walk is not None:
+                heads = walk._after(walk.heads, ch)
+                if not heads:
+                    return None                                        # the call left its program
+                nw = Walk.__new__(Walk)
+                nw.heads = heads
+                walk = None if all(i >= len(segs) for segs, i, _ in heads) else nw
+                continue
+            tail = (tail + ch)[-len(self.OPENER):]
+            if tail == self.OPENER:
+                walk = Walk(self.program)
+                walk.take(self.OPENER)
+                tail = ""
+                if walk.dead:
+                    return None
+        return tail, walk
+
+    def _at(self, text: str):
+        if text != self._text:
+            if self._state is None and text.startswith(self._text):
+                self._text = text                                      # gave up watching: stays given up while the text grows
+                return None
+            base, state = (self._text, self._state) if text.startswith(self._text) else ("", ("", None))
+            self._state = self._step(state, text[len(base):])
+            self._text = text
+        return self._state
+
+    def free(self, text: str) -> bool:
+        """No call is open: the pick needs no mask (a reply that once left its program is no longer watched)."""
+        state = self._at(text)
+        return state is None or state[1] is None
+
+    def allowed(self, text: str, piece: str) -> bool:
+        state = self._at(text)
+        return bool(piece) and (state is None or self._step(state, piece) is not None)
+
+    def done(self, text: str) -> bool:
+        return self.free(text)
+
+    def closed(self, text: str) -> bool:
+        return False                                                   # the reply ends when the model ends it
+
+    def forced_text(self, text: str) -> str:
+        state = self._at(text)
+        return state[1].forced_text() if state is not None and state[1] is not None else ""
+
+
+def watched_calls(tools: Any, framing: str) -> Optional[WatchedCall]:
+    """The watch over a free reply's calls, or None where the calls stay unwatched: a framing the programs do not write,
+    or a tool schema outside the served subset."""
+    try:
+        program = forced_call_program(tools, "required", framing)
+    except Unsupported:
+        return None
+    return WatchedCall(program)
+
+
 def constraint_for(schema: Optional[dict]):
     """A segment program when the schema compiles to one, else None (the caller keeps its prefix validator)."""
     if not schema:

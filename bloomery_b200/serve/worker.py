@@ -288,7 +288,8 @@ class Worker(threading.Thread):
                     if t >= 0:
                         row[t] = -np.inf
         recent = a.slot.ids[-max(req.sampling.repeat_last_n, 0):] if req.sampling.repeat_last_n else []
-        if req.constraint is not None:
+        watch_free = getattr(req.constraint, "free", None)
+        if req.constraint is not None and not (watch_free is not None and watch_free(a.text)):
             tok = self._constrained_pick(a, row, recent)
         else:
             tok = a.sampler.sample(row, recent)
@@ -319,18 +320,25 @@ class Worker(threading.Thread):
                     if piece and text.startswith(piece):
                         self.jumped = getattr(self, "jumped", 0) + 1
                         return int(ids[0])
-        order = np.argsort(-row, kind="stable")
-        for lo, hi in ((0, 256), (256, order.size)):          # the best 256 first; the whole row only when none of them fits
-            for t in order[lo:hi]:
-                t = int(t)
-                if tk.is_eog(t):
-                    if a.req.constraint.done(a.text):
-                        return t
-                    continue
-                piece = tk.decode([t], skip_special=True)
-                if piece and a.req.constraint.allowed(a.text, piece):
-                    return t
-        return int(order[0])
+        def fits(t: int) -> bool:
+            if tk.is_eog(t):
+                return a.req.constraint.done(a.text)
+            piece = tk.decode([t], skip_special=True)
+            return bool(piece) and a.req.constraint.allowed(a.text, piece)
+        # the best 256 first (a partial sort); the whole row is sorted only when none of them fits
+        if row.size > 512:
+            head = np.argpartition(-row, 255)[:256]
+            head = head[np.lexsort((head, -row[head]))]               # by logit, the lower id first on a tie
+        else:
+            head = np.argsort(-row, kind="stable")
+        for t in head:
+            if fits(int(t)):
+                return int(t)
+        if row.size > 512:
+            for t in np.argsort(-row, kind="stable")[head.size:]:
+                if fits(int(t)):
+                    return int(t)
+        return int(head[0])
 
     def enable_drafting(self, draft, width) -> None:
         """Turn on speculative decoding for greedy requests (``BLOOMERY_DRAFT``)."""

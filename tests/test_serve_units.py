@@ -758,3 +758,25 @@ def test_forced_call_programs_both_framings_and_open_think():
                                        ([{"type": "function", "function": {"name": "f", "parameters": {"$ref": "#/x"}}}], "f", "hermes")):
         with pytest.raises(K.Unsupported):
             K.forced_call_program(bad_tools, choice, framing)
+
+
+def test_watched_calls_follow_the_schema_from_the_opener():
+    from bloomery_b200.serve import constrain as K
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+                 "type": "object", "properties": {"unit": {"enum": ["c", "f"]}}, "required": ["unit"]}}},
+             {"type": "function", "function": {"name": "now"}}]
+    w = K.watched_calls(tools, "hermes")
+    assert w.allowed("", "Let me <b>check</b> that. ") and w.done("Let me check") and w.forced_text("free") == ""
+    pre = "I will call.\n<tool_call>"
+    assert w.allowed("I will call.\n<tool_", "call>") and not w.done(pre)                  # no ending inside a call
+    assert w.forced_text(pre) == '\n{"name": "'
+    assert w.allowed(pre, '\n{"name": "now"') and not w.allowed(pre, '\n{"name": "later"') and not w.allowed(pre, '{"name"')
+    one = pre + '\n{"name": "get_weather", "arguments": {"unit": "c"}}\n</tool_call>'
+    assert w.done(one) and not w.closed(one) and w.allowed(one, "\n<tool_call>\n{") and w.allowed(one, " and that is all")
+    assert not w.allowed(pre + '\n{"name": "get_weather", "arguments": {"unit": "', "k")
+    two = one + "\n<tool_call>\n" + '{"name": "now", "arguments": {}}\n</tool_call>'
+    assert w.done(two)
+    # a framing the programs do not write, or a schema outside the subset, leaves the calls unwatched
+    assert K.watched_calls(tools, "glmxml") is None
+    assert K.watched_calls([{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {
+        "a": {"type": "string", "pattern": "x+"}}}}}], "hermes") is None
