@@ -474,7 +474,7 @@ class Handler(BaseHTTPRequestHandler):
                     kwargs = RS.effort_kwargs(body.get("reasoning_effort"), body.get("chat_template_kwargs"))
                 except RS.ReasoningError as exc:
                     raise ApiError(400, str(exc)) from None
-                out = {"prompt": st.template.render_text(body.get("messages") or [], tools=body.get("tools"), **kwargs)}
+                out = {"prompt": st.template.render_text(self._roles(body.get("messages") or []), tools=body.get("tools"), **kwargs)}
                 if body.get("return_prompt_ids"):
                     # the guarded tokenization chat uses: client text never yields control tokens
                     out["prompt_ids"] = self._chat_ids(body.get("messages"), body.get("tools"), **kwargs)
@@ -552,7 +552,11 @@ class Handler(BaseHTTPRequestHandler):
                 "total_slots": st.engine.n_slots, "model_path": a.get("model") or "", "model_alias": st.model_id,
                 "chat_template": st.template.source, "bos_token": st.template.bos, "eos_token": st.template.eos,
                 "model": st.engine.props(), "build_info": "bloomery_b200", "prompt_cache": st.cache.stats(),
-                "placement": a.get("_place_word", ""), "modalities": {"vision": False, "audio": False}}
+                "placement": a.get("_place_word", ""), "modalities": {"vision": False, "audio": False},
+                "thinking_off": self._thinking_off(), "tool_format": st.tool_format,
+                "engine": {"draft": {"kind": {"NgramDraft": "lookup", "MtpDraft": "mtp", "NoneType": "off"}.get(
+                                         type(getattr(st.worker, "draft", None)).__name__, type(getattr(st.worker, "draft", None)).__name__),
+                                     "max_width": int(getattr(getattr(st.worker, "width", None), "max_width", 0) or 0)}}}
 
     def _metrics(self) -> str:
         st = self.state
@@ -864,8 +868,29 @@ class Handler(BaseHTTPRequestHandler):
         for m in messages:
             if not isinstance(m, dict) or "role" not in m:
                 raise ApiError(400, "every message needs a role")
+        # a developer message reaches the template as system (the mapping llama-server makes), except on a template that
+        # names the developer role itself (GPT-OSS's)
+        messages = self._roles(messages)
         segs = st.template.render(messages, tools=tools, add_generation_prompt=True, **extra)
         return st.engine.tokenizer.encode_marked(segs)
+
+    def _roles(self, messages):
+        if isinstance(messages, list) and "developer" not in self.state.template.source \
+                and any(isinstance(m, dict) and m.get("role") == "developer" for m in messages):
+            return [dict(m, role="system") if isinstance(m, dict) and m.get("role") == "developer" else m for m in messages]
+        return messages
+
+    def _thinking_off(self) -> str:
+        """How this template turns thinking off: ``switch`` (it reads ``enable_thinking``), ``low_effort`` (no switch but
+        an effort header), ``off_word`` (its own word for no thinking, ``no_think``) or ``neither``."""
+        src = self.state.template.source
+        if "enable_thinking" in src:
+            return "switch"
+        if "no_think" in src:
+            return "off_word"
+        if "reasoning_effort" in src:
+            return "low_effort"
+        return "neither"
 
     def _template_opened_think(self, ids: List[int]) -> bool:
         """Whether the rendered prompt ends inside a think span the template opened itself."""

@@ -578,6 +578,12 @@ def test_logit_bias_forms_and_unbiased_logprobs(server):
     assert [t["id"] for t in got["top_logprobs"]] == [t["id"] for t in first["top_logprobs"]]
     code, r = call(server, "/chat/completions/input_tokens", {"messages": [{"role": "user", "content": "hi"}]})
     assert code == 200 and r["input_tokens"] > 0
+    # a developer message is the system message of the same text; /props names the template's thinking switch and the draft
+    as_dev = call(server, "/apply-template", {"messages": [{"role": "developer", "content": "be brief"}, {"role": "user", "content": "hi"}]})[1]
+    as_sys = call(server, "/apply-template", {"messages": [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]})[1]
+    assert as_dev["prompt"] == as_sys["prompt"] and "developer" not in as_dev["prompt"]
+    props = call(server, "/props")[1]
+    assert props["thinking_off"] in ("switch", "low_effort", "off_word", "neither") and props["engine"]["draft"]["kind"] == "off"
 
 
 def test_background_responses_poll_cancel_and_refusals():
