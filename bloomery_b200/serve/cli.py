@@ -359,6 +359,17 @@ def ask_need_hook(need: Dict[str, Any]) -> None:
     raise Refusal(Code.REFUSED, f"the need hook {hook} exited {done.returncode}: {last[0]}")
 
 
+def queue_depth_for(opts: Dict[str, Any], n_slots: int) -> int:
+    """Requests that may wait for a slot: 64 minus the slot count unless ``--queue-depth`` names fewer; more is refused."""
+    most = max(0, 64 - int(n_slots))
+    asked = int(opts.get("queue_depth", -1))
+    if asked < 0:
+        return most
+    if asked > most:
+        raise Refusal(Code.USAGE, f"--queue-depth {asked}: with {n_slots} slot(s) the most is {most} (64 minus the slots)")
+    return asked
+
+
 class _PlanOnly(Exception):
     pass
 
@@ -429,7 +440,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             eng = MockEngine(n_slots=4 if opts["parallel"] == "auto" else int(opts["parallel"]),      # nothing to count from: four
                              slot_ctx=int(opts.get("ctx") or 4096), fail_at=int(opts.get("mock_fail_at", -1)))
             opts["_place_word"] = "mock"
-            server.ready(in_turns(eng), ChatTemplate(template_src), cache_bytes, int(opts["queue_depth"]))
+            server.ready(in_turns(eng), ChatTemplate(template_src), cache_bytes, queue_depth_for(opts, turns or eng.n_slots))
             return server.wait()
         if not opts.get("model"):
             raise Refusal(Code.NO_MODEL, "no model was named; use -m FILE (a GGUF file, any shard of a split) or --mock")
@@ -441,7 +452,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             raise Refusal(Code.NO_MODEL, f"{opts['model']}: no such file")
         server.state.phase = "plan"
         eng, template_src, bos, eos = open_engine(opts, server, n_vis, template_src)
-        server.ready(in_turns(eng), ChatTemplate(template_src, bos, eos), cache_bytes, int(opts["queue_depth"]))
+        server.ready(in_turns(eng), ChatTemplate(template_src, bos, eos), cache_bytes, queue_depth_for(opts, turns or eng.n_slots))
         draft = str(levers.get("BLOOMERY_DRAFT")).lower()
         draft = "ngram" if draft == "lookup" else draft
         if turns and draft in ("mtp", "auto"):

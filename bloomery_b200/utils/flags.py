@@ -37,7 +37,7 @@ FLAGS: List[Flag] = [
     Flag(("-c", "--ctx-size"), "ctx", "int", 0, env="LLAMA_ARG_CTX_SIZE", help="0 = the model's trained limit or what fits"),
     Flag(("-np", "--parallel"), "parallel", "str", "1", env="LLAMA_ARG_N_PARALLEL", help="slots: N, or auto = as many (up to 8) as hold one request's context"),
     Flag(("--slot-ctx",), "slot_ctx", "int", 0),
-    Flag(("--queue-depth",), "queue_depth", "int", 64),
+    Flag(("--queue-depth",), "queue_depth", "int", -1, help="requests that may wait; default and most: 64 minus the slot count"),
     Flag(("--engine-slots",), "engine_slots", "int", 0, help="sequences the engine holds; fewer than -np = the slots take it in turns"),
     Flag(("--park",), "park", default="states", help="what a slot that leaves the engine keeps: states or ids"),
     Flag(("--park-ram",), "park_ram", "int", 4096, help="MiB of parked slot states"),

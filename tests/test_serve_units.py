@@ -780,3 +780,12 @@ def test_watched_calls_follow_the_schema_from_the_opener():
     assert K.watched_calls(tools, "glmxml") is None
     assert K.watched_calls([{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {
         "a": {"type": "string", "pattern": "x+"}}}}}], "hermes") is None
+
+
+def test_queue_depth_rule():
+    from bloomery_b200.serve.cli import queue_depth_for
+    from bloomery_b200.utils.exit_codes import Refusal
+    assert queue_depth_for({}, 1) == 63 and queue_depth_for({"queue_depth": -1}, 8) == 56
+    assert queue_depth_for({"queue_depth": 10}, 4) == 10 and queue_depth_for({"queue_depth": 0}, 4) == 0
+    with pytest.raises(Refusal, match="the most is 60"):
+        queue_depth_for({"queue_depth": 64}, 4)
