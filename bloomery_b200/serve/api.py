@@ -1012,14 +1012,27 @@ class Handler(BaseHTTPRequestHandler):
         for i, di in enumerate(ds):
             reasoning, content = C.split_reasoning(di["text"]) if want_reasoning else ("", di["text"])
             calls: List[dict] = []
+            cut_short = False
             if tools:
                 content, calls = C.parse_tool_calls(content, st.tool_format)
+                cut = C.cut_call(content, st.tool_format)
+                if cut is not None:
+                    # the reply stops inside a call: cut by the token limit it answers 200 with finish_reason length (the
+                    # call with the arguments read so far once its name is whole, its text as content before that); a
+                    # generation that ends on its own there has written no call a client can run
+                    if di["stop_type"] != "limit":
+                        raise ApiError(500, f"the generation ended inside the tool call {cut[1] or '(unnamed)'!r}", "server_error")
+                    cut_short = True
+                    if cut[1] is not None:
+                        content = cut[0]
+                        calls = calls + [{"id": f"call_{len(calls)}", "type": "function", "function": {"name": cut[1], "arguments": cut[2]}}]
             msg: Dict[str, Any] = {"role": "assistant", "content": content if (content or not calls) else None}
             if reasoning:
                 msg["reasoning_content"] = reasoning
             if calls:
                 msg["tool_calls"] = calls
-            choices.append({"index": i, "message": msg, "finish_reason": "tool_calls" if calls else finish.get(di["stop_type"], "stop"),
+            choices.append({"index": i, "message": msg,
+                            "finish_reason": "length" if cut_short else "tool_calls" if calls else finish.get(di["stop_type"], "stop"),
                             "logprobs": {"content": di["probs"]} if req.n_probs else None})
         d = ds[0]
         use = usage(d)

@@ -347,6 +347,31 @@ TOOL_PARSERS = {"hermes": parse_hermes, "qwenxml": parse_qwen_xml, "glmxml": par
                 "muse": lambda t: (lambda r: (r["content"], r["tool_calls"]))(parse_muse(t))}
 
 
+def cut_call(text: str, fmt: str = "hermes") -> Optional[Tuple[str, Optional[str], str]]:
+    """A reply that stops inside a call: ``(content before the call, the call's name once it is whole else None, the
+    arguments' text read so far)``; None when no call is open at the end.  JSON framing and the function/parameter markup
+    are read; in another framing an open call is named with no name."""
+    at = text.rfind("<tool_call>")
+    if at < 0 or "</tool_call>" in text[at:]:
+        return None
+    before, inside = text[:at].rstrip(), text[at + len("<tool_call>"):]
+    if fmt == "qwenxml":
+        m = re.match(r"\s*<function=([^>\s]+)>", inside)
+        if not m:
+            return before, None, inside
+        args = {}
+        for p in re.finditer(r"<parameter=([^>\s]+)>\n?(.*?)\n?</parameter>", inside[m.end():], re.S):
+            try:
+                args[p.group(1)] = json.loads(p.group(2))
+            except json.JSONDecodeError:
+                args[p.group(1)] = p.group(2)
+        return before, m.group(1), json.dumps(args, ensure_ascii=False)
+    m = re.match(r'\s*\{\s*"name"\s*:\s*"((?:[^"\\]|\\.)*)"\s*(?:,\s*"arguments"\s*:\s*)?', inside)
+    if not m:
+        return before, None, inside
+    return before, json.loads('"' + m.group(1) + '"'), inside[m.end():]
+
+
 def detect_tool_format(template_source: str) -> str:
     if "<atem:" in template_source:
         return "muse"

@@ -196,6 +196,15 @@ def test_forced_tool_choice_writes_one_call(server):
     assert r["choices"][0]["finish_reason"] == "tool_calls"
     code, r = call(server, "/v1/chat/completions", {"messages": msgs, "tools": tools[1:], "max_tokens": 64, "tool_choice": "required"})
     assert code == 200 and r["choices"][0]["message"]["tool_calls"][0]["function"]["name"] == "now"
+    # a call the token limit cuts: finish_reason length; the call with what was read once its name is whole, its text before
+    forced = {"messages": msgs, "tools": tools, "tool_choice": {"type": "function", "function": {"name": "get_weather"}}}
+    code, r = call(server, "/v1/chat/completions", dict(forced, max_tokens=60))
+    ch = r["choices"][0]
+    assert code == 200 and ch["finish_reason"] == "length" and ch["message"]["tool_calls"][0]["function"]["name"] == "get_weather"
+    assert ch["message"]["tool_calls"][0]["function"]["arguments"].startswith('{"unit": ')
+    code, r = call(server, "/v1/chat/completions", dict(forced, max_tokens=20))
+    ch = r["choices"][0]
+    assert code == 200 and ch["finish_reason"] == "length" and "tool_calls" not in ch["message"] and "<tool_call>" in ch["message"]["content"]
     # Anthropic's any / tool and the Responses API's shapes force the same way
     atools = [{"name": "now", "input_schema": {"type": "object", "properties": {}}}]
     code, r = call(server, "/v1/messages", {"messages": msgs, "tools": atools, "max_tokens": 64, "tool_choice": {"type": "any"}})
