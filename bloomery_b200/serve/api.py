@@ -722,11 +722,14 @@ class Handler(BaseHTTPRequestHandler):
         if not prompt_ids:
             tk = st.engine.tokenizer
             prompt_ids = [tk.bos_id] if tk.bos_id >= 0 else [0]
-        return Request(prompt_ids=prompt_ids, sampling=sampling_from(body, st.args), n_predict=n_predict, stop=stops_from(body),
+        constraint = constraint_from(body)
+        # structured output decodes greedily unless the request names a temperature itself
+        defaults = dict(st.args, temp=0.0) if constraint is not None else st.args
+        return Request(prompt_ids=prompt_ids, sampling=sampling_from(body, defaults), n_predict=n_predict, stop=stops_from(body),
                        stream=bool(body.get("stream", False)), cache_prompt=bool(body.get("cache_prompt", True)),
                        n_probs=n_probs, ignore_eos=bool(body.get("ignore_eos", False)),
                        id_slot=(int(body["id_slot"]) if body.get("id_slot", -1) not in (None, -1) else None),
-                       constraint=constraint_from(body), logit_bias=lb,
+                       constraint=constraint, logit_bias=lb,
                        t_max_predict_ms=float(body.get("t_max_predict_ms") or 0),
                        endpoint=(urlparse(self.path).path.rstrip("/") or "/"), **self._reasoning_fields(body))
 
@@ -946,6 +949,9 @@ class Handler(BaseHTTPRequestHandler):
         open_think = self._template_opened_think(ids)
         for r_ in reqs:
             r_.constraint = ForcedCall(program, think_open=open_think)
+            if body.get("temperature") is None:                      # a forced call decodes greedily unless the request says
+                import dataclasses
+                r_.sampling = dataclasses.replace(r_.sampling, temperature=0.0)
 
     def _chat(self, body) -> None:
         st = self.state

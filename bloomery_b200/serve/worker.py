@@ -325,6 +325,17 @@ class Worker(threading.Thread):
                 return a.req.constraint.done(a.text)
             piece = tk.decode([t], skip_special=True)
             return bool(piece) and a.req.constraint.allowed(a.text, piece)
+        sp = a.req.sampling
+        if sp.temperature > 0 or sp.penalizes:
+            # a positive temperature or a penalty draws with the request's own sampler from the masked row: the ids the
+            # constraint allows among the best 256 keep their logits, every other id is out
+            n_head = min(256, row.size)
+            head = np.argpartition(-row, n_head - 1)[:n_head] if row.size > n_head else np.arange(row.size)
+            keep = [int(t) for t in head if fits(int(t))]
+            if keep:
+                masked = np.full(row.size, -np.inf, dtype=np.float32)
+                masked[keep] = row[keep]
+                return int(a.sampler.sample(masked, recent))
         # the best 256 first (a partial sort); the whole row is sorted only when none of them fits
         if row.size > 512:
             head = np.argpartition(-row, 255)[:256]

@@ -179,6 +179,23 @@ def test_schema_program_forces_keys_without_sampling(server):
     assert r["content"].startswith('{"a": ') and getattr(server.state.worker, "jumped", 0) >= 3
 
 
+def test_structured_output_samples_from_the_masked_row(server):
+    """Unset, a structured-output request decodes greedily; a positive temperature draws with the request's sampler among
+    the ids the schema allows, so every draw is a valid document and the seed picks among the options."""
+    schema = {"type": "object", "properties": {"pick": {"enum": ["alpha", "beta", "gamma", "delta"]}}, "required": ["pick"]}
+    body = {"prompt": "choose", "n_predict": 48, "response_format": {"type": "json_schema", "json_schema": {"schema": schema}}}
+    greedy = {call(server, "/completion", dict(body, seed=s))[1]["content"] for s in range(3)}
+    assert len(greedy) == 1 and json.loads(greedy.pop())["pick"] in schema["properties"]["pick"]["enum"]
+    seen = set()
+    for s in range(12):
+        code, r = call(server, "/completion", dict(body, seed=s, temperature=3.0, top_k=0, top_p=1.0, min_p=0.0))
+        assert code == 200
+        seen.add(json.loads(r["content"])["pick"])
+    assert seen <= set(schema["properties"]["pick"]["enum"]) and len(seen) >= 2
+    same = [call(server, "/completion", dict(body, seed=5, temperature=3.0, top_k=0, top_p=1.0, min_p=0.0))[1]["content"] for _ in range(2)]
+    assert same[0] == same[1]
+
+
 def test_forced_tool_choice_writes_one_call(server):
     """``tool_choice`` ``required`` or a named function holds the reply to one call in the template's framing, on the
     chat, Messages and Responses routes; what cannot be forced is a 400 naming the field."""
