@@ -967,6 +967,12 @@ class Handler(BaseHTTPRequestHandler):
         req = many[0]
         for r_ in many:
             r_.think_started = self._template_opened_think(ids)
+        if many[0].think_started:
+            # a JSON response_format closes the span the template opened at once and writes the document after it
+            from .constrain import AfterThink
+            for r_ in many:
+                if r_.constraint is not None:
+                    r_.constraint, r_.reasoning_budget = AfterThink(r_.constraint), 0
         self._force_call(many, body, tools, ids)
         rid = f"chatcmpl-{uuid.uuid4().hex[:24]}"
         finish = {"eos": "stop", "word": "stop", "limit": "length", "cancelled": "stop", "reasoning_loop": "reasoning_loop"}
@@ -1016,7 +1022,7 @@ class Handler(BaseHTTPRequestHandler):
         ds = self._collect_all(many)
         choices = []
         for i, di in enumerate(ds):
-            reasoning, content = C.split_reasoning(di["text"]) if want_reasoning else ("", di["text"])
+            reasoning, content = C.split_reasoning(di["text"], started=req.think_started) if want_reasoning else ("", di["text"])
             calls: List[dict] = []
             cut_short = False
             if tools:
@@ -1094,6 +1100,7 @@ class Handler(BaseHTTPRequestHandler):
         b2 = dict(body)
         b2["stop"] = body.get("stop_sequences")
         req = self._make_request(b2, ids)
+        req.think_started = self._template_opened_think(ids)
         self._force_call([req], body, tools, ids)
         mid = f"msg_{uuid.uuid4().hex[:24]}"
         reason = {"eos": "end_turn", "word": "stop_sequence", "limit": "max_tokens", "cancelled": "end_turn",
@@ -1120,7 +1127,7 @@ class Handler(BaseHTTPRequestHandler):
                 self._sse({"type": "message_stop"}, "message_stop")
             return self._stream(req, on_text, on_done)
         d = self._collect(req)
-        reasoning, content = C.split_reasoning(d["text"])
+        reasoning, content = C.split_reasoning(d["text"], started=req.think_started)
         blocks: List[dict] = []
         calls: List[dict] = []
         if tools:
@@ -1194,11 +1201,15 @@ class Handler(BaseHTTPRequestHandler):
         if background and (body.get("store") is False or body.get("stream")):
             raise ApiError(400, "field 'background' beside store: false or stream: true is not served")
         req = self._make_request(b2, ids)
+        req.think_started = self._template_opened_think(ids)
+        if req.think_started and req.constraint is not None:
+            from .constrain import AfterThink
+            req.constraint, req.reasoning_budget = AfterThink(req.constraint), 0
         self._force_call([req], b2, tools, ids)
         rid = f"resp_{uuid.uuid4().hex[:24]}"
 
         def build(d):
-            reasoning, content = C.split_reasoning(d["text"])
+            reasoning, content = C.split_reasoning(d["text"], started=req.think_started)
             calls: List[dict] = []
             if tools:
                 content, calls = C.parse_tool_calls(content, st.tool_format)

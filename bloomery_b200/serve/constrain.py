@@ -432,6 +432,46 @@ class ForcedCall(ProgramConstraint):
         return "" if own is None else super().forced_text(own)
 
 
+class AfterThink:
+    """A document constraint behind a think span the template opened: the span is closed at once (the server writes the
+    closing tag for the model), and the inner constraint governs what follows it, after the line breaks a model puts
+    between the two."""
+
+    def __init__(self, inner, close_tag: str = "</think>"):
+        self.inner, self.close_tag = inner, close_tag
+
+    def _own(self, text: str) -> Optional[str]:
+        at = text.find(self.close_tag)
+        return None if at < 0 else text[at + len(self.close_tag):]
+
+    def allowed(self, text: str, piece: str) -> bool:
+        own = self._own(text)
+        if own is None:
+            return self.close_tag.startswith(text + piece) or (text + piece).startswith(self.close_tag)
+        if not own.strip("\n") and not piece.strip("\n"):
+            return len(own + piece) <= 2                              # at most a blank line before the document
+        lead = len(own) - len(own.lstrip("\n"))
+        if not own.strip("\n"):
+            piece, own = (own + piece).lstrip("\n"), ""
+            return len((own + piece)) > 0 and self.inner.allowed("", piece)
+        return self.inner.allowed(own[lead:], piece)
+
+    def done(self, text: str) -> bool:
+        own = self._own(text)
+        return own is not None and self.inner.done(own.lstrip("\n"))
+
+    def closed(self, text: str) -> bool:
+        own = self._own(text)
+        return own is not None and self.inner.closed(own.lstrip("\n"))
+
+    def forced_text(self, text: str) -> str:
+        own = self._own(text)
+        inner = getattr(self.inner, "forced_text", None)
+        if own is None or inner is None or (own and not own.strip("\n")):
+            return ""
+        return inner(own.lstrip("\n"))
+
+
 class WatchedCall:
     """A free reply whose tool calls are watched: text is unconstrained until the model writes its framing's call opener;
     from there the call follows the program a forced call compiles, until it closes, and the reply is free again.  The

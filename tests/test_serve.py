@@ -196,6 +196,27 @@ def test_structured_output_samples_from_the_masked_row(server):
     assert same[0] == same[1]
 
 
+def test_open_think_span_json_document_and_forced_call():
+    """On a template that opens the think span itself, a JSON response_format closes the span at once and writes the
+    document after it; a forced call leaves the span to the model and starts after its close."""
+    from bloomery_b200.serve.chat import CHATML
+    s = Server(flags.parse(["--port", "0", "--mock"]))
+    s.start()
+    s.ready(MockEngine(n_slots=1, slot_ctx=1024), ChatTemplate(CHATML.rstrip() + "<think>\n"), 0)
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}
+    msgs = [{"role": "user", "content": "answer"}]
+    code, r = call(s, "/v1/chat/completions", {"messages": msgs, "max_tokens": 64, "reasoning_format": "none",
+                                                "response_format": {"type": "json_schema", "json_schema": {"schema": schema}}})
+    assert code == 200, r
+    text = r["choices"][0]["message"]["content"]
+    assert text.startswith("</think>") and isinstance(json.loads(text[len("</think>"):])["ok"], bool)
+    code, r = call(s, "/v1/chat/completions", {"messages": msgs, "max_tokens": 64,
+                                                "response_format": {"type": "json_schema", "json_schema": {"schema": schema}}})
+    assert code == 200 and isinstance(json.loads(r["choices"][0]["message"]["content"])["ok"], bool)
+    s.state.stop_event.set()
+    s.stop()
+
+
 def test_forced_tool_choice_writes_one_call(server):
     """``tool_choice`` ``required`` or a named function holds the reply to one call in the template's framing, on the
     chat, Messages and Responses routes; what cannot be forced is a 400 naming the field."""
