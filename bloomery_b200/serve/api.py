@@ -983,8 +983,11 @@ class Handler(BaseHTTPRequestHandler):
                     "total_tokens": d["tokens_evaluated"] + d["tokens_predicted"],
                     "prompt_tokens_details": {"cached_tokens": d["tokens_cached"]}}
         if req.stream:
-            tcs = C.ToolCallStream(st.tool_format) if tools else None
+            # a JSON-framed call streams as the model writes it (name first, argument fragments after); the other
+            # framings send a call when it closes
+            tcs = (C.ToolCallDeltas() if st.tool_format == "hermes" else C.ToolCallStream(st.tool_format)) if tools else None
             saw_call = [False]
+            broke = [False]
 
             def delta(dl, fr=None):
                 return {"id": rid, "object": "chat.completion.chunk", "created": int(time.time()), "model": st.model_id,
@@ -993,7 +996,15 @@ class Handler(BaseHTTPRequestHandler):
             def on_text(t):
                 if tcs is None:
                     return self._sse(delta({"content": t}))
-                text, calls = tcs.push(t)
+                if broke[0]:
+                    return
+                try:
+                    text, calls = tcs.push(t)
+                except C.ToolStreamError as exc:
+                    # markup that stopped being a call after its name went out: the stream ends with an error naming it
+                    broke[0] = True
+                    req.cancelled.set()
+                    return self._sse({"error": {"code": 500, "message": str(exc), "type": "server_error"}})
                 if text:
                     self._sse(delta({"content": text}))
                 for c in calls:
@@ -1001,11 +1012,18 @@ class Handler(BaseHTTPRequestHandler):
                     self._sse(delta({"tool_calls": [c]}))
 
             def on_done(d):
+                if broke[0]:
+                    return self._sse("[DONE]")
+                inside = getattr(tcs, "open_call", None) if tcs is not None else None
                 if tcs is not None:
                     rest = tcs.flush()
                     if rest:
                         self._sse(delta({"content": rest}))
-                fin = delta({}, "tool_calls" if saw_call[0] else finish.get(d["stop_type"], "stop"))
+                if inside is not None and d["stop_type"] != "limit":
+                    self._sse({"error": {"code": 500, "message": f"the generation ended inside the tool call {inside or '(unnamed)'!r}",
+                                         "type": "server_error"}})
+                    return self._sse("[DONE]")
+                fin = delta({}, "length" if inside is not None else "tool_calls" if saw_call[0] else finish.get(d["stop_type"], "stop"))
                 if (body.get("stream_options") or {}).get("include_usage"):
                     fin["usage"] = usage(d)
                 fin["timings"] = d["timings"]

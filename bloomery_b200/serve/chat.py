@@ -441,6 +441,129 @@ class ToolCallStream:
         return s
 
 
+class ToolStreamError(ValueError):
+    """Markup that stopped being a call after its name went out."""
+
+    def __init__(self, name: str, why: str):
+        super().__init__(f"the tool call {name!r} {why}")
+        self.name = name
+
+
+class ToolCallDeltas:
+    """Streams a JSON-framed call (``<tool_call>{"name": .., "arguments": {..}}</tool_call>``) as the model writes it, in
+    OpenAI's shape: the first delta of a call carries ``index``, ``id``, ``type`` and ``function.name`` with empty
+    arguments, and ``function.arguments`` fragments follow as the text arrives, up to the brace that closes the
+    arguments.  Text outside calls passes through at once, less a tail that could still become the opening tag.  A block
+    that closes before its name is readable (another key order, no JSON) is scanned whole, as the one-shot parser would;
+    markup that stops being a call after the name went out raises :class:`ToolStreamError`."""
+
+    HEAD = re.compile(r'\s*\{\s*"name"\s*:\s*"((?:[^"\\]|\\.)*)"\s*,\s*"arguments"\s*:\s*')
+
+    def __init__(self, open_tag: str = "<tool_call>", close_tag: str = "</tool_call>"):
+        self.open, self.close = open_tag, close_tag
+        self.tail = re.compile(r"\s*\}\s*" + re.escape(close_tag))
+        self.buf = ""
+        self.state = "text"
+        self.n_calls = 0
+        self.name = ""
+        self.depth, self.in_str, self.esc = 0, False, False
+
+    @property
+    def open_call(self) -> Optional[str]:
+        """The call the stream stands inside ('' while its name is not whole), None outside a call."""
+        return None if self.state == "text" else (self.name if self.state != "head" else "")
+
+    def push(self, piece: str) -> Tuple[str, List[dict]]:
+        self.buf += piece
+        text_out, deltas = "", []
+        while True:
+            if self.state == "text":
+                i = self.buf.find(self.open)
+                if i < 0:
+                    keep = 0
+                    for k in range(min(len(self.open) - 1, len(self.buf)), 0, -1):
+                        if self.buf.endswith(self.open[:k]):
+                            keep = k
+                            break
+                    text_out += self.buf[:len(self.buf) - keep]
+                    self.buf = self.buf[len(self.buf) - keep:]
+                    return text_out, deltas
+                text_out += self.buf[:i]
+                self.buf = self.buf[i + len(self.open):]
+                self.state, self.name = "head", ""
+            if self.state == "head":
+                m = self.HEAD.match(self.buf)
+                j = self.buf.find(self.close)
+                if m and (j < 0 or m.end() <= j):
+                    self.name = json.loads('"' + m.group(1) + '"')
+                    deltas.append({"index": self.n_calls, "id": f"call_{self.n_calls}", "type": "function",
+                                   "function": {"name": self.name, "arguments": ""}})
+                    self.buf = self.buf[m.end():]
+                    self.state, self.depth, self.in_str, self.esc = "args", 0, False, False
+                elif j >= 0:
+                    block = self.open + self.buf[:j + len(self.close)]           # closed before its name was readable
+                    _, got = parse_hermes(block)
+                    if not got:
+                        text_out += block
+                    for c in got:
+                        c["id"], c["index"] = f"call_{self.n_calls}", self.n_calls
+                        self.n_calls += 1
+                        deltas.append(c)
+                    self.buf = self.buf[j + len(self.close):]
+                    self.state = "text"
+                    continue
+                else:
+                    return text_out, deltas
+            if self.state == "args":
+                n, frag_end = 0, None
+                for n, ch in enumerate(self.buf):
+                    if self.depth == 0 and not self.in_str:
+                        if ch.isspace():
+                            continue
+                        if ch not in "{[":
+                            raise ToolStreamError(self.name, "has arguments that are not a JSON object")
+                    if self.in_str:
+                        if self.esc:
+                            self.esc = False
+                        elif ch == "\\":
+                            self.esc = True
+                        elif ch == '"':
+                            self.in_str = False
+                    elif ch == '"':
+                        self.in_str = True
+                    elif ch in "{[":
+                        self.depth += 1
+                    elif ch in "}]":
+                        self.depth -= 1
+                        if self.depth == 0:
+                            frag_end = n + 1
+                            break
+                cut = frag_end if frag_end is not None else len(self.buf)
+                frag = self.buf[:cut] if (self.depth > 0 or frag_end is not None) else ""
+                if frag:
+                    deltas.append({"index": self.n_calls, "function": {"arguments": frag}})
+                self.buf = self.buf[cut:] if frag else self.buf
+                if frag_end is None:
+                    return text_out, deltas
+                self.state = "tail"
+            if self.state == "tail":
+                m = self.tail.match(self.buf)
+                if m:
+                    self.buf = self.buf[m.end():]
+                    self.n_calls += 1
+                    self.state = "text"
+                    continue
+                squeezed = re.sub(r"\s+", "", self.buf)
+                if ("}" + self.close).startswith(squeezed):
+                    return text_out, deltas
+                raise ToolStreamError(self.name, "is followed by text where its closing tag belongs")
+
+    def flush(self) -> str:
+        """What is left when the generation ends: text outside a call, or the unread head of a call."""
+        s, self.buf = (self.open + self.buf if self.state == "head" else self.buf if self.state == "text" else ""), ""
+        return s
+
+
 # ---------------------------------------------------------------------------------------
 # structured output: JSON (optionally against a schema subset) as a prefix validator
 # ---------------------------------------------------------------------------------------

@@ -144,3 +144,51 @@ def test_compressed_scale_round_trip_on_any_bytes(slabs, cols, seed):
     if cols % 2 == 0:
         q = csf.encode_csf(sc)
         assert np.array_equal(csf.decode_csf("s", q["nvfp4_csf_fixed"], q["nvfp4_csf_exceptions"], 32 * slabs, cols), sc)
+
+
+_json_values = st.recursive(st.one_of(st.none(), st.booleans(), st.integers(-99, 99), st.text(alphabet='ab"{}[]\\ <>/', max_size=6)),
+                            lambda kids: st.one_of(st.lists(kids, max_size=3), st.dictionaries(st.text(alphabet="ab}", max_size=3), kids, max_size=3)),
+                            max_leaves=8)
+
+
+@SET
+@given(st.lists(st.tuples(st.text(alphabet="abc_", min_size=1, max_size=6), st.dictionaries(st.text(alphabet="xy{", max_size=3), _json_values, max_size=3),
+                          st.text(alphabet="ab <\n", max_size=8)), min_size=1, max_size=3),
+       st.integers(min_value=1, max_value=9), st.booleans())
+def test_call_deltas_reassemble_to_the_one_shot_calls_on_any_split(calls, step, compact):
+    """Whatever the chunking and the JSON spacing, the streamed deltas of well-formed calls carry each name once, first,
+    and argument fragments that join to the call's arguments; text outside the calls passes through."""
+    sep = (",", ":") if compact else (", ", ": ")
+    s = ""
+    for name, args, between in calls:
+        s += between.replace("<", "") + "<tool_call>\n" + json.dumps({"name": name, "arguments": args}, separators=sep) + "\n</tool_call>"
+    whole_content, whole_calls = C.parse_hermes(s)
+    stream = C.ToolCallDeltas()
+    content, got = "", {}
+    for i in range(0, len(s), step):
+        c, ds = stream.push(s[i:i + step])
+        content += c
+        for d in ds:
+            slot = got.setdefault(d["index"], {"name": None, "args": ""})
+            if "name" in d["function"]:
+                assert slot["name"] is None and slot["args"] == "" and d["type"] == "function" and d["id"]
+                slot["name"] = d["function"]["name"]
+            slot["args"] += d["function"]["arguments"]
+    content += stream.flush()
+    assert stream.open_call is None
+    assert [(got[i]["name"], json.loads(got[i]["args"])) for i in sorted(got)] == [
+        (c["function"]["name"], json.loads(c["function"]["arguments"])) for c in whole_calls]
+    assert content.strip() == whole_content.strip() or "".join(content.split()) == "".join(whole_content.split())
+
+
+@SET
+@given(st.one_of(text, tagged), st.integers(min_value=1, max_value=7))
+def test_call_deltas_answer_or_raise_their_own_error(s, step):
+    stream = C.ToolCallDeltas()
+    try:
+        for i in range(0, len(s), step):
+            t, ds = stream.push(s[i:i + step])
+            assert isinstance(t, str) and isinstance(ds, list)
+        assert isinstance(stream.flush(), str)
+    except C.ToolStreamError as exc:
+        assert isinstance(exc.name, str)

@@ -101,6 +101,33 @@ def test_chat_stream_sse(server):
     assert len(text) == 4 and events[-1]["choices"][0]["finish_reason"] == "length" and events[-1]["usage"]["completion_tokens"] == 4
 
 
+def test_chat_stream_sends_a_call_as_it_is_written(server):
+    """A streamed chat reply sends a call in OpenAI's shape: a first delta with index, id, type and the name, then
+    argument fragments; a call the token limit cuts ends with finish_reason length."""
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+                 "type": "object", "properties": {"unit": {"enum": ["c", "f"]}, "days": {"type": "integer"}}, "required": ["unit", "days"]}}}]
+    body = {"messages": [{"role": "user", "content": "weather"}], "tools": tools, "stream": True, "max_tokens": 128,
+            "tool_choice": {"type": "function", "function": {"name": "get_weather"}}}
+
+    def events_of(b):
+        req = urllib.request.Request(server.url + "/v1/chat/completions", data=json.dumps(b).encode())
+        raw = urllib.request.urlopen(req).read().decode()
+        assert raw.rstrip().endswith("data: [DONE]")
+        return [json.loads(l[6:]) for l in raw.split("\n") if l.startswith("data: ") and l != "data: [DONE]"]
+    ev = events_of(body)
+    deltas = [c for e in ev if "choices" in e for c in (e["choices"][0]["delta"].get("tool_calls") or [])]
+    assert deltas[0]["index"] == 0 and deltas[0]["type"] == "function" and deltas[0]["id"] and deltas[0]["function"] == {
+        "name": "get_weather", "arguments": ""}
+    assert len(deltas) > 3 and all("name" not in d["function"] for d in deltas[1:])
+    args = json.loads("".join(d["function"]["arguments"] for d in deltas))
+    assert args["unit"] in ("c", "f") and isinstance(args["days"], int)
+    assert ev[-1]["choices"][0]["finish_reason"] == "tool_calls"
+    assert not "".join(e["choices"][0]["delta"].get("content") or "" for e in ev if "choices" in e).strip()
+    cut = events_of(dict(body, max_tokens=60))
+    assert cut[-1]["choices"][0]["finish_reason"] == "length"
+    assert any(e["choices"][0]["delta"].get("tool_calls") for e in cut if "choices" in e)
+
+
 def test_anthropic_and_responses(server):
     code, r = call(server, "/v1/messages", {"messages": [{"role": "user", "content": "yo"}], "max_tokens": 3, "system": "be brief"})
     assert r["type"] == "message" and r["stop_reason"] == "max_tokens" and r["content"][0]["type"] == "text"
