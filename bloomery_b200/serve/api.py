@@ -1190,8 +1190,10 @@ class Handler(BaseHTTPRequestHandler):
                 elif t == "function_call":
                     msgs.append({"role": "assistant", "content": "", "tool_calls": [{"id": it.get("call_id"), "type": "function",
                                  "function": {"name": it.get("name"), "arguments": it.get("arguments", "{}")}}]})
+                elif t == "item_reference":
+                    raise ApiError(400, "an item_reference input item is not served: send the item itself", param="input")
                 else:
-                    raise ApiError(400, f"input item type {t!r} is not supported")
+                    raise ApiError(400, f"input item type {t!r} is not supported", param="input")
         elif inp is not None:
             raise ApiError(400, "input must be a string or a list of items")
         return msgs
@@ -1200,9 +1202,28 @@ class Handler(BaseHTTPRequestHandler):
         st = self.state
         msgs = self._responses_messages(body)
         tools = None
+        spaces: Dict[str, str] = {}                     # a flattened function's bare name -> the namespace it came in
         if body.get("tools"):
-            tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
-                                                       "parameters": t.get("parameters", {})}} for t in body["tools"] if t.get("type") == "function"]
+            def fn(t):
+                return {"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
+                                                         "parameters": t.get("parameters", {})}}
+            tools = []
+            for t in body["tools"]:
+                if not isinstance(t, dict):
+                    raise ApiError(400, "tools: each tool is an object", param="tools")
+                if t.get("type") == "function":
+                    tools.append(fn(t))
+                elif t.get("type") == "namespace":
+                    # a namespace tool is flattened: each function inside serves under its bare name, and a call of it
+                    # carries the namespace in its item
+                    for inner in t.get("tools") or []:
+                        if isinstance(inner, dict) and inner.get("type", "function") == "function" and inner.get("name"):
+                            if inner["name"] in spaces or any(x["function"]["name"] == inner["name"] for x in tools):
+                                raise ApiError(400, f"tools: the function {inner['name']!r} is named twice once namespaces are flattened",
+                                               param="tools")
+                            spaces[inner["name"]] = str(t.get("name") or "")
+                            tools.append(fn(inner))
+            tools = tools or None
         from . import reasoning as RS
         try:
             kwargs = RS.effort_kwargs((body.get("reasoning") or {}).get("effort") if isinstance(body.get("reasoning"), dict) else None, None)
@@ -1240,6 +1261,8 @@ class Handler(BaseHTTPRequestHandler):
             for c in calls:
                 output.append({"type": "function_call", "id": f"fc_{uuid.uuid4().hex[:16]}", "call_id": c["id"],
                                "name": c["function"]["name"], "arguments": c["function"]["arguments"], "status": "completed"})
+                if c["function"]["name"] in spaces:
+                    output[-1]["namespace"] = spaces[c["function"]["name"]]
             resp = {"id": rid, "object": "response", "created_at": int(time.time()), "status": "completed" if d["stop_type"] not in ("limit", "reasoning_loop") else "incomplete",
                     "model": st.model_id, "output": output, "output_text": content,
                     "usage": {"input_tokens": d["tokens_evaluated"], "output_tokens": d["tokens_predicted"],

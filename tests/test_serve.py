@@ -277,6 +277,14 @@ def test_forced_tool_choice_writes_one_call(server):
     code, r = call(server, "/v1/responses", {"input": "time?", "tools": [{"type": "function", "name": "now"}], "max_output_tokens": 64,
                                              "tool_choice": {"type": "function", "name": "now"}, "store": False})
     assert code == 200 and [o["name"] for o in r["output"] if o["type"] == "function_call"] == ["now"]
+    # a namespace tool is flattened: its functions serve under their bare names and a call carries the namespace
+    ns = [{"type": "namespace", "name": "multi_agent_v1", "tools": [{"type": "function", "name": "spawn"}]}]
+    code, r = call(server, "/v1/responses", {"input": "go", "tools": ns, "max_output_tokens": 64, "store": False,
+                                             "tool_choice": {"type": "function", "name": "spawn"}})
+    item = [o for o in r["output"] if o["type"] == "function_call"][0]
+    assert code == 200 and item["name"] == "spawn" and item["namespace"] == "multi_agent_v1"
+    code, r = call(server, "/v1/responses", {"input": [{"type": "item_reference", "id": "msg_1"}]})
+    assert code == 400 and "item_reference" in r["error"]["message"]
     # refusals name the field
     for body, param in (({"tool_choice": {"type": "function", "function": {"name": "absent"}}}, "tool_choice"),
                         ({"tool_choice": "required", "response_format": {"type": "json_object"}}, "response_format"),
