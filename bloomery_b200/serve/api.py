@@ -448,6 +448,8 @@ class Handler(BaseHTTPRequestHandler):
                 msgs = self._anthropic_messages(body) if "messages" in path and "/v1/messages" in path else body.get("messages") or self._responses_messages(body)
                 ids = self._chat_ids(msgs, body.get("tools"))
                 return self._send(200, {"input_tokens": len(ids)})
+            if path in ("/v1/systemone", "/systemone"):
+                return self._systemone(body)
             if path == "/v1/messages":
                 return self._messages(body)
             if path == "/v1/responses":
@@ -1071,6 +1073,55 @@ class Handler(BaseHTTPRequestHandler):
         out = {"id": rid, "object": "chat.completion", "created": int(time.time()), "model": st.model_id,
                "choices": choices, "usage": use, "timings": d["timings"]}
         self._send(200, out)
+
+    # ---- the decision models' request on a generative model ----------------------------------
+    def _systemone(self, body) -> None:
+        """``POST /v1/systemone``: the schema text goes in the system message and the state in the user message, the
+        reply is held to a JSON object by the structured-output path, and each question's scores are the logits of the
+        tokens its options start with, read where the model picks (``serve/systemone.py``)."""
+        from . import systemone as S1
+        from .constrain import AfterThink
+        st = self.state
+        tk = st.engine.tokenizer
+        encode = lambda text: tk.encode(text, parse_special=False, add_bos=False)      # noqa: E731
+        try:
+            state, questions = S1.read_request(body)
+            schema = S1.plan(questions, encode)
+        except S1.SystemOneError as exc:
+            raise ApiError(exc.status, str(exc), "not_supported_error" if exc.status == 501 else "invalid_request_error") from None
+        cache = body.get("cache_prompt", True)
+        if not isinstance(cache, bool):
+            raise ApiError(400, "cache_prompt takes true or false", param="cache_prompt")
+        msgs = [{"role": "system", "content": S1.schema_text(questions)}, {"role": "user", "content": state}]
+        ids = self._chat_ids(msgs)
+        room = st.engine.slot_ctx - len(ids) - 1
+        if room < 16:
+            raise ApiError(400, f"the request of {len(ids)} ids leaves no room for the answers in a context of {st.engine.slot_ctx}",
+                           "exceed_context_size_error")
+        req = self._make_request({"response_format": {"type": "json_schema", "json_schema": {"schema": schema}}, "temperature": 0,
+                                  "cache_prompt": cache, "max_tokens": min(room, 64 + 48 * len(questions))}, ids)
+        if req.constraint is None or not hasattr(req.constraint, "forced_text"):
+            raise ApiError(400, "the questions' ids do not write out to a schema this server walks")
+        req.think_started = self._template_opened_think(ids)
+        if req.think_started:
+            req.constraint, req.reasoning_budget = AfterThink(req.constraint), 0
+        req.pick_rows = []
+        d = self._collect(req)
+        text = d["text"]
+        if req.think_started and "</think>" in text:
+            text = text[text.index("</think>") + len("</think>"):]
+        document = text.lstrip("\n")
+        lead = len(d["text"]) - len(document)
+        try:
+            got = S1.answers(questions, document, [(n - lead, row) for n, row in req.pick_rows], encode)
+        except S1.SystemOneError as exc:
+            raise ApiError(exc.status, str(exc), "server_error" if exc.status >= 500 else "invalid_request_error") from None
+        t = d["timings"]
+        self._send(200, {"model": st.model_id, "answers": got,
+                         "usage": {"input_tokens": d["tokens_evaluated"], "output_tokens": d["tokens_predicted"]},
+                         "timings": {"prompt_n": t.get("prompt_n", d["tokens_evaluated"] - d["tokens_cached"]),
+                                     "prompt_ms": t.get("prompt_ms", 0.0), "head_ms": t.get("predicted_ms", 0.0),
+                                     "cache_n": d["tokens_cached"]}})
 
     # ---- Anthropic Messages ----------------------------------------------------------------
     def _anthropic_messages(self, body) -> List[dict]:

@@ -49,6 +49,8 @@ class Request:
     reasoning_budget: int = -1              # generated ids the think span may take (-1: no budget)
     reasoning_loop: bool = False            # end a think span that repeats itself
     think_started: bool = False             # the template already opened the think span
+    pick_rows: Optional[List[Tuple[int, np.ndarray]]] = None   # when a list: (length of the text so far, logits row) of each
+                                                               # pick the constraint's walk read a row for
     id: int = dataclasses.field(default_factory=lambda: next(_ids))
     events: "queue.Queue" = dataclasses.field(default_factory=queue.Queue)
     cancelled: threading.Event = dataclasses.field(default_factory=threading.Event)
@@ -320,6 +322,9 @@ class Worker(threading.Thread):
                     if piece and text.startswith(piece):
                         self.jumped = getattr(self, "jumped", 0) + 1
                         return int(ids[0])
+        if a.req.pick_rows is not None:
+            a.req.pick_rows.append((len(a.text), np.array(row, dtype=np.float32, copy=True)))
+
         def fits(t: int) -> bool:
             if tk.is_eog(t):
                 return a.req.constraint.done(a.text)

@@ -128,6 +128,45 @@ def test_chat_stream_sends_a_call_as_it_is_written(server):
     assert any(e["choices"][0]["delta"].get("tool_calls") for e in cut if "choices" in e)
 
 
+def test_systemone_on_a_generative_model():
+    """The decision models' request answered by the served model: every question is one pick of the walk, the scores are
+    the logits of the tokens the options start with, and the body follows the decision models' formulas."""
+    body = {"state": "User: what is the weather in Seoul tomorrow?", "questions": {
+        "tool": {"type": "choice", "instructions": "Which tool next?", "criteria": {"web_search": "Look it up", "calculator": "Arithmetic", "none": "Answer"}},
+        "urgency": {"type": "score", "criteria": ["Can wait", "This week", "Today"]},
+        "outage": {"type": "noul"},
+        "twin": {"type": "choice", "criteria": {"ab": "first", "ac": "second"}}}}      # told apart after the shared "a
+    server = Server(flags.parse(["--port", "0", "--mock"]))
+    server.start()
+    server.ready(MockEngine(n_slots=1, slot_ctx=4096), ChatTemplate(), 1 << 20)
+    code, r = call(server, "/v1/systemone", body)
+    assert code == 200, r
+    assert list(r) == ["model", "answers", "usage", "timings"] and list(r["answers"]) == ["tool", "urgency", "outage", "twin"]
+    tool, urg, out, twin = (r["answers"][k] for k in ("tool", "urgency", "outage", "twin"))
+    assert tool["type"] == "choice" and tool["choice"] in body["questions"]["tool"]["criteria"]
+    assert list(tool["probabilities"]) == ["web_search", "calculator", "none"] and abs(sum(tool["probabilities"].values()) - 1) < 1e-3
+    assert tool["probabilities"][tool["choice"]] == max(tool["probabilities"].values())
+    u = 1 / 3
+    assert abs(tool["confidence"] - max(0.0, (max(tool["probabilities"].values()) - u) / (1 - u))) < 2e-3
+    assert urg["type"] == "score" and urg["legend"] == {"0": "Can wait", "1": "This week", "2": "Today"}
+    assert abs(urg["score"] - sum(i * urg["probabilities"][str(i)] for i in range(3))) < 2e-3 and 0 <= urg["confidence"] <= 1
+    assert out["type"] == "noul" and 0 <= out["noul"] <= 1
+    assert twin["choice"] in ("ab", "ac") and list(twin["probabilities"]) == ["ab", "ac"]
+    assert r["usage"]["input_tokens"] > 0 and r["usage"]["output_tokens"] > 0 and r["timings"]["cache_n"] >= 0
+    # the same request again restores its prompt from the cache
+    assert call(server, "/v1/systemone", body)[1]["timings"]["cache_n"] > 0
+    for bad, status in (({"questions": {"q": {"type": "noul"}}}, 400), ({"state": "s", "questions": {}}, 400),
+                        ({"state": "s", "questions": {"q": {"type": "rank"}}}, 400),
+                        ({"state": "s", "questions": {"q": {"type": "choice", "criteria": ["a"]}}}, 400),
+                        ({"state": "s", "questions": {"q": {"type": "score", "criteria": ["only"]}}}, 400),
+                        ({"state": "s", "questions": {"q": {"type": "noul"}}, "videos": ["x"]}, 501),
+                        ({"state": "s", "questions": {"q": {"type": "noul"}}, "images": ["data:image/png;base64,AA=="]}, 501),
+                        ({"state": "s", "questions": {"q": {"type": "noul"}}, "cache_prompt": "yes"}, 400)):
+        assert call(server, "/v1/systemone", bad)[0] == status, bad
+    server.state.stop_event.set()
+    server.stop()
+
+
 def test_anthropic_and_responses(server):
     code, r = call(server, "/v1/messages", {"messages": [{"role": "user", "content": "yo"}], "max_tokens": 3, "system": "be brief"})
     assert r["type"] == "message" and r["stop_reason"] == "max_tokens" and r["content"][0]["type"] == "text"

@@ -789,3 +789,48 @@ def test_queue_depth_rule():
     assert queue_depth_for({"queue_depth": 10}, 4) == 10 and queue_depth_for({"queue_depth": 0}, 4) == 0
     with pytest.raises(Refusal, match="the most is 60"):
         queue_depth_for({"queue_depth": 64}, 4)
+
+
+def test_systemone_formulas_and_letter_rule():
+    """The decision models' formulas on hand-computed cases: p(technical) = 1/(1+e^-2) = 0.8808 and its confidence
+    (0.8808 - 1/2) / (1/2) = 0.7616; softmax(0, 1, 0.5) = (0.1863, 0.5065, 0.3072), its score 1.1209 and confidence
+    1 - (0.1863 + 0.3072) / (2/3) = 0.2597; a noul of scores (1, -1) is 0.8808."""
+    from bloomery_b200.serve import systemone as S
+    assert abs(S.confidence_choice([0.7, 0.2, 0.1]) - 0.55) < 1e-12 and S.confidence_choice([0.25] * 4) == 0.0 and S.confidence_choice([1.0]) == 1.0
+    enc = lambda t: [300 if ch in "bc" else ord(ch) for ch in t]      # noqa: E731 - a vocabulary that cannot tell b from c
+    state, qs = S.read_request({"state": {"k": 1}, "questions": {
+        "department": {"type": "choice", "criteria": {"technical": "Bugs", "billing": "Pay"}},
+        "urgency": {"type": "score", "criteria": ["Can wait", "This week", "Today"]}, "outage": {"type": "noul"},
+        "twin": {"type": "choice", "criteria": {"ab": "x", "ac": "y"}}}})
+    assert state == '{"k": 1}'
+    schema = S.plan(qs, enc)
+    assert schema["required"] == ["department", "urgency", "outage", "twin"] and schema["properties"]["twin"] == {"enum": ["A", "B"]}
+    assert schema["properties"]["department"] == {"enum": ["technical", "billing"]} and not qs[0].by_letter and qs[3].by_letter
+    assert "A = ab: x" in S.schema_text(qs)
+    assert S.first_tokens(['"ab"', '"ac"'], enc) is None and S.first_tokens(['"ab"', '"ac"'], lambda t: list(t.encode())) == [98, 99]
+    assert S.answer(qs[0], "technical", [2.0, 0.0]) == {"type": "choice", "choice": "technical", "confidence": 0.7616,
+                                                        "probabilities": {"technical": 0.8808, "billing": 0.1192}}
+    assert S.answer(qs[1], 1, [0.0, 1.0, 0.5]) == {"type": "score", "score": 1.1209, "confidence": 0.2597,
+                                                   "legend": {"0": "Can wait", "1": "This week", "2": "Today"},
+                                                   "probabilities": {"0": 0.1863, "1": 0.5065, "2": 0.3072}}
+    assert S.answer(qs[2], True, [1.0, -1.0]) == {"type": "noul", "noul": 0.8808}
+    assert S.answer(qs[3], "B", [0.0, 0.0])["choice"] == "ac"         # the answer names the option, never the letter
+    # the pick rows are looked up where each question's options part in the canonical document
+    doc = '{"department": "billing", "urgency": 2, "outage": false, "twin": "A"}'
+    rows = []
+    for q, sc in zip(qs, ([2.0, 0.0], [0.0, 1.0, 0.5], [1.0, -1.0], [3.0, 1.0])):
+        lead = len(S._common(q.literals))
+        row = [0.0] * 301
+        for lit, v in zip(q.literals, sc):
+            row[enc(lit[lead:])[0]] = v
+        at = doc.index(json.dumps(q.id) + ": ") + len(json.dumps(q.id)) + 2 + lead
+        rows.append((at, row))
+    got = S.answers(qs, doc, rows, enc)
+    assert got["department"]["choice"] == "billing" and got["department"]["probabilities"]["technical"] == 0.8808
+    assert got["urgency"]["score"] == 1.1209 and got["outage"]["noul"] == 0.8808 and got["twin"]["choice"] == "ab"
+    with pytest.raises(S.SystemOneError):
+        S.answers(qs, doc[:-5], rows, enc)
+    with pytest.raises(S.SystemOneError):
+        S.plan(S.read_request({"state": "s", "questions": {"q": {"type": "choice", "criteria": {f"a{i:02d}": "x" for i in range(27)}}}})[1], enc)
+    with pytest.raises(S.SystemOneError, match="not finite"):
+        S.probabilities([0.0, float("inf")])
