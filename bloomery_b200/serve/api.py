@@ -589,6 +589,9 @@ class Handler(BaseHTTPRequestHandler):
             lines.append(f'llamacpp:rounds_total{{width="{w}"}} {n}')
         for w, sec in sorted(st.worker.round_seconds_by_width.items()):
             lines.append(f'llamacpp:round_seconds_by_width_total{{width="{w}"}} {sec:.6f}')
+        for w, sec in sorted(st.worker.round_card_wait_by_width.items()):
+            lines.append(f'llamacpp:round_card_wait_seconds_total{{width="{w}"}} {sec:.6f}')
+        g("card_wait_seconds_total", "Seconds the engine's host thread waited for the card", f"{float(m.get('card_wait_seconds_total') or 0.0):.6f}")
         source = {"NgramDraft": "ngram", "MtpDraft": "mtp"}.get(type(st.worker.draft).__name__, "none")
         for depth, n in sorted(st.worker.draft_by_depth.items()):
             lines.append(f'llamacpp:spec_decode_num_draft_tokens_by_depth_total{{source="{source}",depth="{depth}"}} {n}')

@@ -75,6 +75,7 @@ class MockEngine(Engine):
         self.fail_at = fail_at
         self.prefill_calls: List[Tuple[int, int, int]] = []
         self.fresh = [True] * n_slots          # the next step of the slot carries the prompt's last token
+        self.waited_s = 0.0                    # what step_delay has slept: this engine's stand-in for waiting on a card
 
     def _logits(self, slot: int) -> np.ndarray:
         seq = self.seq[slot]
@@ -88,6 +89,9 @@ class MockEngine(Engine):
         row[(nxt + 1) % 256] = 8.0           # a runner-up so samplers have something to choose from
         return row
 
+    def card_wait_seconds(self) -> float:
+        return self.waited_s
+
     def prefill(self, slot, ids, start):
         self.prefill_calls.append((slot, start, len(ids)))
         del self.seq[slot][start:]
@@ -100,6 +104,7 @@ class MockEngine(Engine):
         if self.step_delay:
             import time
             time.sleep(self.step_delay)
+            self.waited_s += self.step_delay
         if self.fail_at >= 0 and self.steps >= self.fail_at:
             raise EngineError("mock engine failure (--mock-fail-at)")
         out = []
@@ -258,6 +263,11 @@ class GpuEngine(Engine):
         except (EngineFault, EngineStalled) as exc:
             raise EngineError(str(exc)) from exc
         return out
+
+    def card_wait_seconds(self) -> float:
+        """Seconds this engine's host thread has waited for the card so far (the decode engine's own wait counter)."""
+        waits = getattr(self.dec, "waits", None)
+        return float(waits.ns.get("card", 0)) / 1e9 if waits is not None else 0.0
 
     def cut(self, slot, n):
         self.dec.cut(slot, n)

@@ -113,6 +113,7 @@ class Worker(threading.Thread):
         self.metrics = Metrics()
         self.rounds_by_width: Dict[int, int] = {}
         self.round_seconds_by_width: Dict[int, float] = {}
+        self.round_card_wait_by_width: Dict[int, float] = {}          # the part of a round the engine waited for the card
         self.draft_by_depth: Dict[int, int] = {}        # drafted ids by their place in the draft
         self.accepted_by_depth: Dict[int, int] = {}
         self.on_fatal = on_fatal
@@ -423,7 +424,13 @@ class Worker(threading.Thread):
             kw["draft_slots"] = {sp[0].slot.id for sp in spans if self._can_draft(sp[0])}
         if sampling is not None:
             kw["sampling"] = sampling
+        wait_of = getattr(self.engine, "card_wait_seconds", None)
+        w0 = wait_of() if wait_of is not None else 0.0
         res = self.engine.step(rows, want_logits=need_logits, **kw)
+        if wait_of is not None:
+            waited = max(0.0, wait_of() - w0)
+            self.round_card_wait_by_width[len(rows)] = self.round_card_wait_by_width.get(len(rows), 0.0) + waited
+            self.metrics.add("card_wait_seconds_total", waited)
         if sampling is not None:
             for a, r0, _ in spans:
                 if sampling[r0] is not None:

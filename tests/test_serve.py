@@ -592,6 +592,11 @@ def test_long_generation_says_it_is_still_generating(capfd):
     assert call(s, "/completion", {"prompt": "abcdefghijklmnopqrstuvwxyz", "n_predict": 24, "temperature": 0})[0] == 200
     err = capfd.readouterr().err
     assert sum(1 for ln in err.splitlines() if ": generating, " in ln) >= 2
+    # the rounds' card wait is counted by width beside their whole time, and never passes it
+    text = call(s, "/metrics")[1]
+    val = lambda name: float(next(ln for ln in text.splitlines() if ln.startswith(name)).split()[-1])       # noqa: E731
+    assert 0 < val('llamacpp:round_card_wait_seconds_total{width="1"}') <= val('llamacpp:round_seconds_by_width_total{width="1"}')
+    assert val("llamacpp:card_wait_seconds_total") > 0
     s.state.stop_event.set()
     s.stop()
 
