@@ -214,6 +214,11 @@ def parse(argv: List[str], environ=None) -> Dict[str, Any]:
         if f.env and f.env in env and f.dest not in from_env and f.dest != "api_key":
             by = displaced.get(f.dest) or ("the command line" if f.dest in cli else "the settings file")
             notes.append(f"{f.env}: replaced by {by}")
+    # llama-server's "no limit" for the prompt cache is refused: the cache is host memory beside the load, so it always has
+    # a budget (unset, the lesser of 8 GiB and half the host RAM the plan leaves)
+    if ("cache_ram" in cli or "cache_ram" in cfg or "cache_ram" in from_env) and int(out["cache_ram"]) < 0:
+        raise Refusal(Code.USAGE, f"{from_env.get('cache_ram', '--cache-ram')} {out['cache_ram']}: the prompt cache always has a "
+                                  f"budget; give MiB, 0 to turn it off, or leave it unset")
     # keys add: the variable's keys count beside the command line's (no line prints one)
     if "LLAMA_API_KEY" in env:
         more = split_keys(env["LLAMA_API_KEY"])

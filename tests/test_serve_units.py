@@ -716,6 +716,11 @@ def test_llama_server_variables():
         flags.placement(flags.parse(["-sm", "row"], {}), 2)
     with pytest.raises(Refusal, match="LLAMA_ARG_DEVICE names CUDA5"):
         flags.placement(flags.parse([], {"LLAMA_ARG_DEVICE": "CUDA5"}), 2)
+    # llama-server's "no limit" prompt cache is refused wherever it is named; unset keeps the default rule
+    for argv, env_ in ((["--cache-ram", "-1"], {}), ([], {"LLAMA_ARG_CACHE_RAM": "-1"})):
+        with pytest.raises(Refusal, match="always has a budget"):
+            flags.parse(argv, env_)
+    assert flags.parse([], {})["cache_ram"] == -1 and flags.parse(["-cram", "0"], {})["cache_ram"] == 0
     # the driver's launch-queue variable: unset becomes 2x, NVIDIA's other values stay, anything else stops the start
     env = {}
     levers.at_main(env)
