@@ -24,7 +24,7 @@ from __future__ import annotations
 
 import json
 import re
-from typing import Any, List, Optional, Set, Tuple
+from typing import Any, List, Optional, Sequence, Set, Tuple
 
 _NUM_FULL = re.compile(r"-?(0|[1-9]\d*)(\.\d+)?([eE][+-]?\d+)?\Z")
 _NUM_PREFIX = re.compile(r"-?((0|[1-9]\d*)((\.\d*)|((\.\d+)?[eE][+-]?\d*))?)?\Z")
@@ -209,7 +209,7 @@ def _feed(head: Head, ch: str) -> Set[Head]:
             return _next(segs, i)
         if ch == "\\":
             return {(segs, i, (2, n))}
-        if ord(ch) < 0x20 or (s[1] is not None and n + 1 > s[1]):
+        if ord(ch) < 0x20 or (s[1] is not None and n + 1 > s[1]) or (ch == "<" and len(s) > 2 and s[2]):
             return set()
         return {(segs, i, (1, n + 1))}
     if s[0] == "raw":
@@ -323,6 +323,24 @@ class ProgramConstraint:
 FRAMINGS = ("hermes", "qwenxml")
 
 
+def _no_lt(segs: Sequence[tuple]) -> Tuple[tuple, ...]:
+    """The same program inside a tool call's markup, where the reply is scanned for tags: a free string takes no ``<``,
+    and a ``<`` in fixed text (a constant, an option, a property name) is written as its JSON escape."""
+    out: List[tuple] = []
+    for s in segs:
+        if s[0] == "lit":
+            out.append(("lit", s[1].replace("<", "\\u003c")))
+        elif s[0] == "str":
+            out.append(("str", s[1], True))
+        elif s[0] == "alt":
+            out.append(("alt", tuple(_no_lt(o) for o in s[1])))
+        elif s[0] == "arr":
+            out.append(("arr", _no_lt(s[1])) + tuple(s[2:]))
+        else:
+            out.append(s)
+    return tuple(out)
+
+
 def _tool_fn(tool: Any) -> Tuple[str, dict]:
     fn = tool.get("function", tool) if isinstance(tool, dict) else None
     if not isinstance(fn, dict) or not isinstance(fn.get("name"), str) or not fn["name"]:
@@ -343,7 +361,7 @@ def _call_segments(name: str, params: dict, framing: str) -> Tuple[tuple, ...]:
         raise Unsupported(f"the tool name {name!r} cannot be written inside a call's markup")
     if framing == "hermes":
         head = '<tool_call>\n{"name": ' + json.dumps(name, ensure_ascii=False) + ', "arguments": '
-        return _merge([("lit", head)] + list(compile_schema(params)) + [("lit", "}\n</tool_call>")])
+        return _merge([("lit", head)] + list(_no_lt(compile_schema(params))) + [("lit", "}\n</tool_call>")])
     # the <function=...><parameter=...> markup: a value on lines of its own, a string bare, anything else as JSON
     props = params.get("properties") or {}
     req = params.get("required", [])

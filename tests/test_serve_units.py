@@ -757,6 +757,16 @@ def test_forced_call_programs_both_framings_and_open_think():
         assert t.allowed("so", " anything <tool_call> at all") and not t.done("so") and t.forced_text("so") == ""
         assert t.allowed("so", "</think>") and t.allowed("so", "</think>\n\n<tool") and not t.allowed("so", "</think>hello")
         assert t.done("so</think>\n\n" + text) and t.done("so</think>" + text)
+    # inside a JSON-framed call a free string takes no "<" and fixed text writes it as its escape, so the scan for tags
+    # never meets one the model wrote
+    lt = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {
+        "a<b": {"type": "string"}, "k": {"enum": ["x<y", "z"]}, "l": {"type": "array", "items": {"type": "string"}}}, "required": ["a<b", "k", "l"]}}}]
+    c = K.ForcedCall(K.forced_call_program(lt, "f", "hermes"))
+    head = '<tool_call>\n{"name": "f", "arguments": {"a\\u003cb": "hi'
+    assert c.forced_text("").endswith('{"a\\u003cb": ') and not c.allowed(head, "<") and c.allowed(head, "x")
+    whole = head + '", "k": "x\\u003cy", "l": ["q"]}}\n</tool_call>'
+    assert c.done(whole) and json.loads(C.parse_hermes(whole)[1][0]["function"]["arguments"]) == {"a<b": "hi", "k": "x<y", "l": ["q"]}
+    assert not c.allowed(head + '", "k": "x\\u003cy", "l": ["q', "<")
     raw = K.ForcedCall(K.forced_call_program(tools, "get_weather", "qwenxml"))
     assert not raw.allowed("<tool_call>\n<function=get_weather>\n<parameter=city>\nOs", "<b")
     for bad_tools, choice, framing in ((tools, "absent", "hermes"), (tools, "required", "glmxml"), ([], "required", "hermes"),
