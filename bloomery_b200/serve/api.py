@@ -248,6 +248,10 @@ def constraint_from(body):
                            param="reasoning_budget")
 
     def pick(schema):
+        from .constrain import unserved_keyword
+        bad = unserved_keyword(schema) if schema else None
+        if bad is not None:
+            raise ApiError(400, f"the schema keyword {bad!r} is outside the served subset", param="response_format")
         return constraint_for(schema) or C.JsonConstraint(schema)
     rf = body.get("response_format")
     if rf:

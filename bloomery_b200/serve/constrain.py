@@ -562,6 +562,37 @@ def watched_calls(tools: Any, framing: str) -> Optional[WatchedCall]:
     return WatchedCall(program)
 
 
+# what the prefix validator of serve/chat.py reads beside the program's own subset (free-form objects, open additional
+# properties): a keyword outside both is honoured by neither path, so the request is refused by that keyword's name
+_FALLBACK_KEYWORDS = {"type", "properties", "required", "additionalProperties", "items", "minItems", "maxItems", "enum", "const",
+                      "anyOf", "oneOf", "maxLength", "$ref"} | set(_ANNOTATIONS)
+
+
+def unserved_keyword(schema: Any, _depth: int = 0) -> Optional[str]:
+    """The first schema keyword no constraint of this server enforces (``pattern``, ``minLength``, ``minimum``, ``allOf``,
+    ``minProperties``, ...), or None."""
+    if not isinstance(schema, dict) or _depth > MAX_DEPTH:
+        return None
+    for k, v in schema.items():
+        if k not in _FALLBACK_KEYWORDS:
+            return k
+        if k in ("properties", "$defs", "definitions") and isinstance(v, dict):
+            for sub in v.values():
+                bad = unserved_keyword(sub, _depth + 1)
+                if bad:
+                    return bad
+        elif k == "items":
+            bad = unserved_keyword(v, _depth + 1)
+            if bad:
+                return bad
+        elif k in ("anyOf", "oneOf") and isinstance(v, list):
+            for sub in v:
+                bad = unserved_keyword(sub, _depth + 1)
+                if bad:
+                    return bad
+    return None
+
+
 def constraint_for(schema: Optional[dict]):
     """A segment program when the schema compiles to one, else None (the caller keeps its prefix validator)."""
     if not schema:

@@ -331,6 +331,10 @@ def test_forced_tool_choice_writes_one_call(server):
                         ({"tool_choice": "required", "tools": [{"type": "function", "function": {"name": "f", "parameters": {"anyOf": [{"type": "object"}]}}}]}, "tool_choice")):
         code, r = call(server, "/v1/chat/completions", dict({"messages": msgs, "tools": tools}, **body))
         assert code == 400 and r["error"]["param"] == param, (body, r)
+    for kw in ({"type": "string", "pattern": "x+"}, {"type": "object", "properties": {"a": {"type": "integer", "minimum": 3}}},
+               {"allOf": [{"type": "string"}]}, {"type": "array", "items": {"type": "string", "minLength": 2}}):
+        code, r = call(server, "/completion", {"prompt": "x", "response_format": {"type": "json_schema", "json_schema": {"schema": kw}}})
+        assert code == 400 and "outside the served subset" in r["error"]["message"], kw
     for body, param in (({"ignore_eos": True}, "ignore_eos"), ({"reasoning_budget": 8}, "reasoning_budget")):
         code, r = call(server, "/completion", dict({"prompt": "x", "response_format": {"type": "json_object"}}, **body))
         assert code == 400 and r["error"]["param"] == param
