@@ -320,7 +320,7 @@ class ProgramConstraint:
         return self._at(text).forced_text()
 
 
-FRAMINGS = ("hermes", "qwenxml")
+FRAMINGS = ("hermes", "qwenxml", "glmxml")
 
 
 def _no_lt(segs: Sequence[tuple]) -> Tuple[tuple, ...]:
@@ -385,6 +385,17 @@ def _call_segments(name: str, params: dict, framing: str) -> Tuple[tuple, ...]:
         if "<" in key or ">" in key or "\n" in key:
             raise Unsupported(f"the property name {key!r} cannot be written inside a call's markup")
         return [("lit", f"<parameter={key}>\n")] + value(props[key]) + [("lit", "\n</parameter>\n")]
+    if framing == "glmxml":
+        # <tool_call>NAME, then an <arg_key> / <arg_value> pair a member, a string bare (it holds no "<")
+        def pair(key: str) -> List[tuple]:
+            if "<" in key or "\n" in key:
+                raise Unsupported(f"the property name {key!r} cannot be written inside a call's markup")
+            return [("lit", f"<arg_key>{key}</arg_key>\n<arg_value>")] + value(props[key]) + [("lit", "</arg_value>\n")]
+        segs = [("lit", f"<tool_call>{name}\n")]
+        for key in props:
+            segs += pair(key) if key in req else [("alt", (_merge(pair(key)), ()))]
+        segs.append(("lit", "</tool_call>"))
+        return _merge(segs)
     segs: List[tuple] = [("lit", f"<tool_call>\n<function={name}>\n")]
     for key in props:
         segs += member(key) if key in req else [("alt", (_merge(member(key)), ()))]

@@ -741,16 +741,19 @@ def test_forced_call_programs_both_framings_and_open_think():
     texts = {"hermes": '<tool_call>\n{"name": "get_weather", "arguments": {"city": "Oslo", "days": 3}}\n</tool_call>',
              "qwenxml": "<tool_call>\n<function=get_weather>\n<parameter=city>\nOslo\n</parameter>\n<parameter=days>\n3\n</parameter>\n"
                         "</function>\n</tool_call>"}
+    texts["glmxml"] = ("<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Oslo</arg_value>\n<arg_key>days</arg_key>\n"
+                       "<arg_value>3</arg_value>\n</tool_call>")
     for framing, text in texts.items():
         c = K.ForcedCall(K.forced_call_program(tools, "required", framing))
-        assert c.forced_text("").startswith("<tool_call>\n")
+        assert c.forced_text("").startswith("<tool_call>")
         for i in range(1, len(text)):
             assert c.allowed(text[:i], text[i]), (framing, text[:i + 1])
         assert c.done(text) and c.closed(text) and not c.allowed(text, "x")
-        parse = C.parse_hermes if framing == "hermes" else C.parse_qwen_xml
+        parse = {"hermes": C.parse_hermes, "qwenxml": C.parse_qwen_xml, "glmxml": C.parse_glm_xml}[framing]
         assert json.loads(parse(text)[1][0]["function"]["arguments"]) == {"city": "Oslo", "days": 3}
         # the optional member may be left out; a raw string takes no "<" and no line break
-        short = text.replace(', "days": 3', "").replace("<parameter=days>\n3\n</parameter>\n", "")
+        short = text.replace(', "days": 3', "").replace("<parameter=days>\n3\n</parameter>\n", "").replace(
+            "<arg_key>days</arg_key>\n<arg_value>3</arg_value>\n", "")
         assert K.ForcedCall(K.forced_call_program(tools, "get_weather", framing)).done(short)
         # a think span the template opened stays free until its close; the reply cannot end inside it
         t = K.ForcedCall(K.forced_call_program(tools, "get_weather", framing), think_open=True)
@@ -769,7 +772,7 @@ def test_forced_call_programs_both_framings_and_open_think():
     assert not c.allowed(head + '", "k": "x\\u003cy", "l": ["q', "<")
     raw = K.ForcedCall(K.forced_call_program(tools, "get_weather", "qwenxml"))
     assert not raw.allowed("<tool_call>\n<function=get_weather>\n<parameter=city>\nOs", "<b")
-    for bad_tools, choice, framing in ((tools, "absent", "hermes"), (tools, "required", "glmxml"), ([], "required", "hermes"),
+    for bad_tools, choice, framing in ((tools, "absent", "hermes"), (tools, "required", "mistral"), ([], "required", "hermes"),
                                        ([{"type": "function", "function": {"name": "f", "parameters": {"$ref": "#/x"}}}], "f", "hermes")):
         with pytest.raises(K.Unsupported):
             K.forced_call_program(bad_tools, choice, framing)
@@ -792,7 +795,7 @@ def test_watched_calls_follow_the_schema_from_the_opener():
     two = one + "\n<tool_call>\n" + '{"name": "now", "arguments": {}}\n</tool_call>'
     assert w.done(two)
     # a framing the programs do not write, or a schema outside the subset, leaves the calls unwatched
-    assert K.watched_calls(tools, "glmxml") is None
+    assert K.watched_calls(tools, "mistral") is None and K.watched_calls(tools, "glmxml") is not None
     assert K.watched_calls([{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {
         "a": {"type": "string", "pattern": "x+"}}}}}], "hermes") is None
 
