@@ -320,7 +320,15 @@ class ProgramConstraint:
         return self._at(text).forced_text()
 
 
-FRAMINGS = ("hermes", "qwenxml", "glmxml")
+FRAMINGS = ("hermes", "qwenxml", "glmxml", "dsml", "dsml_spaced")
+
+
+def call_opener(framing: str) -> str:
+    """The text that opens a call (or a block of calls) in a framing."""
+    if framing in ("dsml", "dsml_spaced"):
+        from .chat import _dsml_tags
+        return _dsml_tags(framing == "dsml_spaced")[0]
+    return "<tool_call>"
 
 
 def _no_lt(segs: Sequence[tuple]) -> Tuple[tuple, ...]:
@@ -385,6 +393,27 @@ def _call_segments(name: str, params: dict, framing: str) -> Tuple[tuple, ...]:
         if "<" in key or ">" in key or "\n" in key:
             raise Unsupported(f"the property name {key!r} cannot be written inside a call's markup")
         return [("lit", f"<parameter={key}>\n")] + value(props[key]) + [("lit", "\n</parameter>\n")]
+    if framing in ("dsml", "dsml_spaced"):
+        # a block of one invoke; a parameter says whether its value is bare text (string="true") or JSON
+        from .chat import _dsml_tags
+        b_open, b_close, i_open, i_close, p_open, p_close = _dsml_tags(framing == "dsml_spaced")
+        if '"' in name:
+            raise Unsupported(f"the tool name {name!r} cannot be written inside a call's markup")
+
+        def param(key: str) -> List[tuple]:
+            if '"' in key or "<" in key or "\n" in key:
+                raise Unsupported(f"the property name {key!r} cannot be written inside a call's markup")
+            v = value(props[key])
+            sch = props[key]
+            bare = isinstance(sch, dict) and ((sch.get("type") == "string" and "enum" not in sch and "const" not in sch)
+                                              or (isinstance(sch.get("enum"), list) and all(isinstance(x, str) for x in sch["enum"])))
+            flag = "true" if bare else "false"
+            return [("lit", f'{p_open}{key}" string="{flag}">')] + v + [("lit", f"{p_close}\n")]
+        segs = [("lit", f'{b_open}\n{i_open}{name}">\n')]
+        for key in props:
+            segs += param(key) if key in req else [("alt", (_merge(param(key)), ()))]
+        segs.append(("lit", f"{i_close}\n{b_close}"))
+        return _merge(segs)
     if framing == "glmxml":
         # <tool_call>NAME, then an <arg_key> / <arg_value> pair a member, a string bare (it holds no "<")
         def pair(key: str) -> List[tuple]:
@@ -506,10 +535,9 @@ class WatchedCall:
     from there the call follows the program a forced call compiles, until it closes, and the reply is free again.  The
     reply may end anywhere outside a call and nowhere inside one."""
 
-    OPENER = "<tool_call>"
-
-    def __init__(self, program: Tuple[tuple, ...]):
+    def __init__(self, program: Tuple[tuple, ...], opener: str = "<tool_call>"):
         self.program = tuple(program)
+        self.OPENER = opener
         self._text = ""
         self._state: Tuple[str, Optional[Walk]] = ("", None)          # (tail of the free text, walk of the open call)
 
@@ -570,7 +598,7 @@ def watched_calls(tools: Any, framing: str) -> Optional[WatchedCall]:
         program = forced_call_program(tools, "required", framing)
     except Unsupported:
         return None
-    return WatchedCall(program)
+    return WatchedCall(program, call_opener(framing))
 
 
 # what the prefix validator of serve/chat.py reads beside the program's own subset (free-form objects, open additional

@@ -743,22 +743,29 @@ def test_forced_call_programs_both_framings_and_open_think():
                         "</function>\n</tool_call>"}
     texts["glmxml"] = ("<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Oslo</arg_value>\n<arg_key>days</arg_key>\n"
                        "<arg_value>3</arg_value>\n</tool_call>")
+    D = C.DSML
+    for framing, sp, blk in (("dsml", "", "tool_calls"), ("dsml_spaced", " ", "calls")):
+        texts[framing] = (f'<{D}{sp}{blk}>\n<{D}{sp}invoke name="get_weather">\n<{D}{sp}parameter name="city" string="true">Oslo</{D}{sp}parameter>\n'
+                          f'<{D}{sp}parameter name="days" string="false">3</{D}{sp}parameter>\n</{D}{sp}invoke>\n</{D}{sp}{blk}>')
     for framing, text in texts.items():
         c = K.ForcedCall(K.forced_call_program(tools, "required", framing))
-        assert c.forced_text("").startswith("<tool_call>")
+        assert c.forced_text("").startswith(K.call_opener(framing))
         for i in range(1, len(text)):
             assert c.allowed(text[:i], text[i]), (framing, text[:i + 1])
         assert c.done(text) and c.closed(text) and not c.allowed(text, "x")
-        parse = {"hermes": C.parse_hermes, "qwenxml": C.parse_qwen_xml, "glmxml": C.parse_glm_xml}[framing]
+        parse = {"hermes": C.parse_hermes, "qwenxml": C.parse_qwen_xml, "glmxml": C.parse_glm_xml, "dsml": C.parse_dsml,
+                 "dsml_spaced": C.parse_dsml}[framing]
         assert json.loads(parse(text)[1][0]["function"]["arguments"]) == {"city": "Oslo", "days": 3}
         # the optional member may be left out; a raw string takes no "<" and no line break
         short = text.replace(', "days": 3', "").replace("<parameter=days>\n3\n</parameter>\n", "").replace(
             "<arg_key>days</arg_key>\n<arg_value>3</arg_value>\n", "")
+        for sp in ("", " "):
+            short = short.replace(f'<{D}{sp}parameter name="days" string="false">3</{D}{sp}parameter>\n', "")
         assert K.ForcedCall(K.forced_call_program(tools, "get_weather", framing)).done(short)
         # a think span the template opened stays free until its close; the reply cannot end inside it
         t = K.ForcedCall(K.forced_call_program(tools, "get_weather", framing), think_open=True)
         assert t.allowed("so", " anything <tool_call> at all") and not t.done("so") and t.forced_text("so") == ""
-        assert t.allowed("so", "</think>") and t.allowed("so", "</think>\n\n<tool") and not t.allowed("so", "</think>hello")
+        assert t.allowed("so", "</think>") and t.allowed("so", "</think>\n\n" + K.call_opener(framing)[:5]) and not t.allowed("so", "</think>hello")
         assert t.done("so</think>\n\n" + text) and t.done("so</think>" + text)
     # inside a JSON-framed call a free string takes no "<" and fixed text writes it as its escape, so the scan for tags
     # never meets one the model wrote
