@@ -370,6 +370,33 @@ def queue_depth_for(opts: Dict[str, Any], n_slots: int) -> int:
     return asked
 
 
+def _views(server) -> None:
+    """The start screen below the record lines, and the live view's keys, when a person is watching (stderr and stdin
+    are terminals); a server under a supervisor gets neither."""
+    from . import screen
+    worker = server.state.worker
+    ring = screen.Ring()
+    if worker is not None:
+        worker.request_lines = ring
+    shown = [False]
+
+    def on_key(ch: str) -> None:
+        if ch != "d":
+            return
+        shown[0] = not shown[0]
+        if shown[0]:
+            m = worker.metrics if worker is not None else None
+            counters = {k: (m.get(k) if m is not None else 0.0) for k in ("n_decode_total", "tokens_predicted_total", "prompt_tokens_total")}
+            try:
+                width = os.get_terminal_size(sys.stderr.fileno()).columns
+            except (OSError, ValueError):
+                width = 80
+            sys.stderr.write(screen.live_view(ring, counters, width, screen.Style.of(os.environ)))
+            sys.stderr.flush()
+    keys = screen.watch_keys(on_key) if sys.stderr.isatty() else None
+    screen.draw_if_armed(server.url, live_keys=keys is not None)
+
+
 class _PlanOnly(Exception):
     pass
 
@@ -382,6 +409,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         opts = flags.parse(argv)
         for note in opts.get("_config_notes", ()):
             print(f"bloomery-serve: {note}", file=sys.stderr)
+        from . import screen
+        screen.arm(os.environ, sys.stderr.isatty(), str(levers.get("BLOOMERY_SCREEN")))
+        records.tap(screen.note)
         if opts["version"]:
             from .. import __version__
             print(f"bloomery_b200 {__version__}")
@@ -441,6 +471,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                              slot_ctx=int(opts.get("ctx") or 4096), fail_at=int(opts.get("mock_fail_at", -1)))
             opts["_place_word"] = "mock"
             server.ready(in_turns(eng), ChatTemplate(template_src), cache_bytes, queue_depth_for(opts, turns or eng.n_slots))
+            _views(server)
             return server.wait()
         if not opts.get("model"):
             raise Refusal(Code.NO_MODEL, "no model was named; use -m FILE (a GGUF file, any shard of a split) or --mock")
@@ -466,6 +497,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             if eng.dec.enable_mtp():
                 width = int(levers.get("BLOOMERY_MTP_WIDTH")) or 1
                 server.state.worker.enable_drafting(MtpDraft(eng), WidthChooser(max_width=max(1, min(width, 7))))
+        _views(server)
         return server.wait()
     except _PlanOnly:
         return server.stop()

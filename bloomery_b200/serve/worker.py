@@ -242,6 +242,9 @@ class Worker(threading.Thread):
                 f"{g / max(pred_ms / 1e3, 1e-9):.1f} ids/s; stop {self.REASONS.get(stop_type, 'error')}; "
                 f"ctx {len(a.slot.ids)}/{self.engine.slot_ctx}")
         print(line, file=sys.stderr, flush=True)
+        ring = getattr(self, "request_lines", None)
+        if ring is not None:
+            ring.push(line)                         # the live view's last requests
 
     def _log_generating(self) -> None:
         """A request that has generated for more than ``generating_every`` seconds says so, and again every such span."""

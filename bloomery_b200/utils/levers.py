@@ -36,6 +36,7 @@ _PARSERS: Dict[str, Callable[[str], Any]] = {
 
 REGISTRY: List[LeverSpec] = [
     LeverSpec("BLOOMERY_DRAFT", "word", "auto", "speculative draft source (lookup = the n-gram lookup draft, also spelled ngram)", ("auto", "off", "mtp", "ngram", "lookup")),
+    LeverSpec("BLOOMERY_SCREEN", "word", "on", "draw the start screen below the record lines when stderr is a terminal", ("on", "off")),
     LeverSpec("BLOOMERY_WATCH_CALLS", "word", "on", "hold a free reply's tool calls to their schemas from the call opener on", ("on", "off")),
     LeverSpec("BLOOMERY_RESIDENCY", "word", "mid", "hot-expert promotion rule", ("off", "low", "mid", "high")),
     LeverSpec("BLOOMERY_CARD_BUDGET", "bytes", 0, "HBM bytes routed experts may take per GPU (0 = what fits)"),

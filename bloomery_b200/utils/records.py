@@ -28,6 +28,15 @@ def schema() -> str:
     return json.dumps({"schema": "bloomery.record/1", "kinds": KINDS}, indent=1)
 
 
+_taps: List = []
+
+
+def tap(fn) -> None:
+    """Hand every record line written from now on to ``fn`` as well (the start screen reads the lines as printed)."""
+    if fn not in _taps:
+        _taps.append(fn)
+
+
 def write(kind: str, _out=None, **fields) -> None:
     if kind not in KINDS:
         raise KeyError(f"unknown record kind {kind!r}")
@@ -35,8 +44,11 @@ def write(kind: str, _out=None, **fields) -> None:
     if unknown:
         raise KeyError(f"record {kind!r} has no field(s) {sorted(unknown)}")
     out = _out or sys.stderr
-    out.write(f"{kind}\t{json.dumps({'t': round(time.time(), 3), **fields}, separators=(',', ':'))}\n")
+    line = f"{kind}\t{json.dumps({'t': round(time.time(), 3), **fields}, separators=(',', ':'))}\n"
+    out.write(line)
     out.flush()
+    for fn in _taps:
+        fn(line)
 
 
 def read(lines: Iterable[str]) -> Iterator[Tuple[str, dict]]:

@@ -859,3 +859,54 @@ def test_systemone_formulas_and_letter_rule():
         S.plan(S.read_request({"state": "s", "questions": {"q": {"type": "choice", "criteria": {f"a{i:02d}": "x" for i in range(27)}}}})[1], enc)
     with pytest.raises(S.SystemOneError, match="not finite"):
         S.probabilities([0.0, float("inf")])
+
+
+def test_start_screen_reads_the_record_lines_as_printed():
+    from bloomery_b200.serve import screen as S
+    from bloomery_b200.utils import records
+    plain = S.Style.of({"TERM": "dumb", "LANG": "en_US.UTF-8"})
+    assert plain == S.Style(False, False, False)
+    assert S.Style.of({"LANG": "en_US.UTF-8", "COLORTERM": "truecolor"}) == S.Style(True, True, True)
+    assert S.Style.of({"LC_ALL": "C", "LANG": "en_US.UTF-8", "NO_COLOR": "1"}) == S.Style(False, False, False)
+    assert S.Style.of({"NO_COLOR": "", "LANG": "C.UTF-8"}).color                         # set but empty does not count
+    assert "38;5;" in S.Style(True, False, True).paint("x", S.ORANGE) and "38;2;255;140;40" in S.Style(True, True, True).paint("x", S.ORANGE)
+    got: list = []
+    S.arm({}, True, "on")
+    records.tap(S.note)
+    import io
+    sink = io.StringIO()
+    records.write("plan", _out=sink, model="m", devices=[0, 1], weights_bytes=32 << 30, kv_bytes=4 << 30, ctx=32768, slots=4, place="tp2")
+    records.write("need", _out=sink, host_bytes=8 << 30, cache_ram=8 << 30)
+    records.write("ctx", _out=sink, asked=0, served=16384, trained=262144, rule="fitted")
+    records.write("ctx", _out=sink, asked=0, served=32768, trained=262144, rule="fitted")       # the last line of a kind is the row
+    records.write("parallel", _out=sink, slots=4, slot_ctx=8192, source="auto")
+    lines = S.records()
+    assert len(lines) == 5 and lines[0].startswith("plan\t")
+    wide = S.draw(lines, "http://127.0.0.1:8080", 120, plain, live_keys=True)
+    assert "serving on http://127.0.0.1:8080" in wide and "cards x2     32.0 GiB" in wide and "host          8.0 GiB" in wide
+    assert "context    32,768 (fitted)" in wide and "16,384" not in wide and "slots      4 (from auto)" in wide
+    assert "prompt cache 8.0 GiB" in wide and "d shows the live view" in wide and "unread" not in wide
+    assert any("where the model went" in ln and "how it serves" in ln for ln in wide.splitlines())       # side by side
+    narrow = S.draw(lines, "http://x", 50, plain)
+    assert not any("where the model went" in ln and "how it serves" in ln for ln in narrow.splitlines())
+    assert all(len(ln) <= 50 for ln in narrow.splitlines()) and "d shows" not in narrow
+    # a fact whose record was not printed is left off; a value that is no number is named, never dropped
+    few = S.draw(['ctx\t{"served":"lots"}', 'need\tnot json'], "http://x", 80, plain)
+    assert "where the model went" not in few and "ctx.served='lots'" in few and "need: not json" in few
+    with pytest.raises(ValueError):
+        S.draw(lines, "http://x", 3, plain)
+    # piped stderr is never armed
+    assert S.arm({}, False, "on") is False and S.draw_if_armed("http://x") is False
+    assert S.arm({}, True, "off") is False
+    S.arm({}, True, "on")
+    out = io.StringIO()
+    assert S.draw_if_armed("http://y", env={"TERM": "dumb"}, out=out) and "serving on http://y" in out.getvalue()
+    S.arm({}, False)
+    # the live view: the newest request lines under a line of counters, cut to the width
+    ring = S.Ring(3)
+    for i in range(5):
+        ring.push(f"bloomery-serve: request {i} /completion: prompt 10 ids")
+    view = S.live_view(ring, {"rounds": 12, "ids": 340}, 40, plain)
+    assert "request 4" in view and "request 1" not in view and "rounds 12" in view and all(len(ln) <= 40 for ln in view.splitlines())
+    assert "no request has ended yet" in S.live_view(S.Ring(), {}, 40, plain)
+    assert S.watch_keys(lambda ch: None, stdin=io.StringIO("d")) is None                 # stdin is no terminal: no keys
